@@ -1,0 +1,122 @@
+// Shared device helpers for the sm_100a kernels: bf16 packing, warp/block reductions,
+// status words and the bounded cross-GPU flag protocol used by the fused collectives.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "ifab_kernels.h"
+
+
+// Status word bits written by kernels instead of trapping. The host reads the word after a step.
+#define IFAB_STATUS_OK 0u
+#define IFAB_STATUS_PEER_TIMEOUT 1u   // a bounded wait on a peer flag ran out
+#define IFAB_STATUS_MBAR_TIMEOUT 2u   // a bounded wait on an mbarrier ran out
+#define IFAB_STATUS_BAD_INDEX 4u      // a page / expert / token index was out of range and skipped
+
+typedef __nv_bfloat16 bf16;
+
+namespace ifab {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// 8 bf16 packed in a uint4 -> 8 floats
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// streaming 16-byte load that does not pollute L1 (weights are read once per step)
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Cross-GPU flag protocol. Flags are 64-bit epochs in memory that every rank maps. A writer
+// publishes its data with plain stores, then one thread issues a system-scope release store of
+// the epoch; a reader spins (bounded) with system-scope acquire loads. The spin never exceeds
+// `limit` polls: when it runs out the caller records IFAB_STATUS_PEER_TIMEOUT and carries on so
+// the kernel always terminates and the context stays usable.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_release_sys(uint64_t* p, uint64_t v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_acquire_sys(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint64_t ld_relaxed_sys(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+// returns true when the flag reached `want` within `limit` polls
+__device__ __forceinline__ bool wait_flag_bounded(const uint64_t* p, uint64_t want, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (ld_acquire_sys(p) >= want) return true;
+    if (i > 64) __nanosleep(40);
+  }
+  return false;
+}
+
+// View of the symmetric heap handed to every fused collective kernel (by value).
+//   data[r]  : rank r's staging area as mapped into this process (data[rank] is local)
+//   flags[r] : rank r's flag words
+//   seq      : local device counter bumped once per forward pass (same value on all ranks)
+//   status   : local status word
+struct FabricView {
+  char* data[IFAB_MAX_RANKS];
+  uint64_t* flags[IFAB_MAX_RANKS];
+  const uint64_t* seq;
+  uint32_t* status;
+  int rank;
+  int world;
+  uint32_t spin_limit;
+  uint32_t data_half_bytes;   // bytes of one parity half of the staging area
+  uint32_t flag_half_words;   // flag words of one parity half
+};
+
+// host: build the by-value device view from the C descriptor
+inline int fabric_view(const IfabFabric* f, FabricView* v) {
+  if (f == nullptr || f->world < 1 || f->world > IFAB_MAX_RANKS || f->rank < 0 || f->rank >= f->world) return -10;
+  for (int i = 0; i < IFAB_MAX_RANKS; ++i) {
+    v->data[i] = (char*)f->data[i];
+    v->flags[i] = (uint64_t*)f->flags[i];
+  }
+  v->seq = f->seq;
+  v->status = f->status;
+  v->rank = f->rank;
+  v->world = f->world;
+  v->spin_limit = f->spin_limit;
+  v->data_half_bytes = f->data_half_bytes;
+  v->flag_half_words = f->flag_half_words;
+  return 0;
+}
+
+}  // namespace ifab

@@ -1,0 +1,364 @@
+// Multi-head latent attention, decode / short-chunk path, for sm_100a.
+//
+// The KV cache keeps ONE row per token shared by all heads: [latent(512) bf16 | rope(64) bf16], in
+// pages of `page_tokens` rows addressed through a per-sequence page table. Queries are "absorbed":
+// q_nope is multiplied by W_UK so scores are taken directly against the latent rows, and the
+// value up-projection W_UV is applied once to the attention output.
+//
+//   mla_kv_write_kernel     RMSNorm(latent) + RoPE(k_pe) + paged scatter (one CTA per token)
+//   mla_q_absorb_kernel     q_lat[h] = [ q_nope[h] W_UK[h] | RoPE(q_rope[h]) ]
+//   mla_split_kernel        split-KV online-softmax attention over the paged cache (+ learned sink
+//                           rows, sliding window); partial (m, l, acc) per split go to scratch
+//   mla_merge_vup_kernel    log-sum-exp merge of the splits + W_UV up-projection -> [T, H*vdim]
+//
+// Every query row carries its own position and sequence slot, so the same kernels serve
+// single-sequence decode, batched decode and short causal prefill chunks (rows of one chunk are
+// written to the cache first; row i then sees keys <= position i).
+//
+// Reference counterparts: cache_norm_rope_append (KvRmsNormRopeCache), mla_query (BatchMatMul +
+// rotary + concat), latent_attention (FusedInferAttentionSink) and mla_value
+// (native/src/token_executor.h:613-909).
+#include "gemv.cuh"
+#include "ifab_kernels.h"
+
+using namespace ifab;
+
+namespace {
+
+constexpr int LATENT = 512;
+constexpr int ROPE = 64;
+constexpr int ROW = LATENT + ROPE;
+
+__device__ __forceinline__ void rope_cos_sin(int pos, int i, int rope_dim, float theta, float* c, float* s) {
+  // angle_i = pos / theta^(2i/rope_dim); cos/sin are rounded to bf16 like the tables of the reference
+  const float inv_freq = exp2f(-(2.f * (float)i / (float)rope_dim) * log2f(theta));
+  float sn, cs;
+  sincosf((float)pos * inv_freq, &sn, &cs);
+  *c = bf16_round(cs);
+  *s = bf16_round(sn);
+}
+
+__device__ __forceinline__ long cache_row_of(int pos, int slot, const int32_t* page_table, int max_pages,
+                                             int page_tokens, int num_pages) {
+  const int lp = pos / page_tokens;
+  if (lp >= max_pages) return -1;
+  const int page = page_table[(long)slot * max_pages + lp];
+  if (page < 0 || page >= num_pages) return -1;
+  return (long)page * page_tokens + (pos % page_tokens);
+}
+
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) mla_kv_write_kernel(const bf16* kv, long ldkv, const bf16* norm_w, float eps,
+                                                           float theta, const int32_t* positions, const int32_t* slots,
+                                                           const int32_t* page_table, int max_pages, int page_tokens,
+                                                           bf16* cache, int num_pages, int latent, int rope,
+                                                           uint32_t* status) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  if (pos < 0) return;
+  const long row = cache_row_of(pos, slots[t], page_table, max_pages, page_tokens, num_pages);
+  if (row < 0) {
+    if (threadIdx.x == 0 && status) atomicOr(status, IFAB_STATUS_BAD_INDEX);
+    return;
+  }
+  __shared__ float red[4];
+  const bf16* src = kv + (long)t * ldkv;
+  bf16* dst = cache + row * (latent + rope);
+  const int tid = threadIdx.x;
+  float f[8];
+  float ss = 0.f;
+  const bool has = tid < latent / 8;
+  if (has) {
+    unpack8(*reinterpret_cast<const uint4*>(src + tid * 8), f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  const float inv = rsqrtf((red[0] + red[1] + red[2] + red[3]) / (float)latent + eps);
+  if (has) {
+    float g[8];
+    unpack8(*reinterpret_cast<const uint4*>(norm_w + tid * 8), g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f[i] * inv * g[i];
+    *reinterpret_cast<uint4*>(dst + tid * 8) = pack8(f);
+  }
+  const int half = rope / 2;
+  if (tid < half) {
+    float c, s;
+    rope_cos_sin(pos, tid, rope, theta, &c, &s);
+    const float a = __bfloat162float(src[latent + tid]), b = __bfloat162float(src[latent + tid + half]);
+    dst[latent + tid] = __float2bfloat16_rn(a * c - b * s);
+    dst[latent + tid + half] = __float2bfloat16_rn(b * c + a * s);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// grid (H, T), 256 threads: thread i owns latent columns 2i, 2i+1
+__global__ void __launch_bounds__(256) mla_q_absorb_kernel(const bf16* q, long ldq, const bf16* w_kvb, float theta,
+                                                           const int32_t* positions, bf16* q_lat, int H, int nope,
+                                                           int rope, int latent, int vdim) {
+  const int h = blockIdx.x, t = blockIdx.y;
+  const int pos = positions[t];
+  __shared__ float qs[256];
+  const bf16* qrow = q + (long)t * ldq + (long)h * (nope + rope);
+  for (int i = threadIdx.x; i < nope; i += blockDim.x) qs[i] = __bfloat162float(qrow[i]);
+  __syncthreads();
+  bf16* out = q_lat + ((long)t * H + h) * (latent + rope);
+  const bf16* W = w_kvb + (long)h * (nope + vdim) * latent;
+  for (int c2 = threadIdx.x; c2 < latent / 2; c2 += blockDim.x) {
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll 8
+    for (int d = 0; d < nope; ++d) {
+      const float2 w = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(W + (long)d * latent + 2 * c2));
+      a0 = fmaf(qs[d], w.x, a0);
+      a1 = fmaf(qs[d], w.y, a1);
+    }
+    *reinterpret_cast<__nv_bfloat162*>(out + 2 * c2) = __floats2bfloat162_rn(a0, a1);
+  }
+  const int half = rope / 2;
+  if ((int)threadIdx.x < half) {
+    float c, s;
+    rope_cos_sin(pos < 0 ? 0 : pos, threadIdx.x, rope, theta, &c, &s);
+    const float a = __bfloat162float(qrow[nope + threadIdx.x]), b = __bfloat162float(qrow[nope + threadIdx.x + half]);
+    out[latent + threadIdx.x] = __float2bfloat16_rn(a * c - b * s);
+    out[latent + threadIdx.x + half] = __float2bfloat16_rn(b * c + a * s);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+struct AttnParams {
+  const bf16* q_lat; const bf16* cache; const int32_t* positions; const int32_t* slots; const int32_t* page_table;
+  int max_pages, page_tokens, num_pages;
+  const bf16* sinks; int n_sinks, window; float scale;
+  int T, H, kps, max_splits;
+  float* scratch;   // [T][H][max_splits][LATENT + 2]
+  uint32_t* status;
+};
+
+// key-space of one query: sink rows first, then the visible context rows
+__device__ __forceinline__ void visible_range(int pos, int window, int* first, int* count) {
+  int n = pos + 1;
+  if (window > 0 && n > window) n = window;
+  *count = n;
+  *first = pos + 1 - n;
+}
+
+// lane layout of one 576-wide row: latent elements [8l, 8l+8) and [256+8l, 256+8l+8), rope elements 2l, 2l+1
+struct RowFrag {
+  float lat[16];
+  float rp[2];
+};
+__device__ __forceinline__ void load_row(const bf16* row, int lane, RowFrag* f) {
+  const uint4 a = *reinterpret_cast<const uint4*>(row + lane * 8);
+  const uint4 b = *reinterpret_cast<const uint4*>(row + 256 + lane * 8);
+  const __nv_bfloat162 r = *reinterpret_cast<const __nv_bfloat162*>(row + LATENT + lane * 2);
+  unpack8(a, f->lat);
+  unpack8(b, f->lat + 8);
+  const float2 rr = __bfloat1622float2(r);
+  f->rp[0] = rr.x;
+  f->rp[1] = rr.y;
+}
+
+template <int HG>
+__global__ void __launch_bounds__(256) mla_split_kernel(AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* sm_acc = reinterpret_cast<float*>(smem_raw);            // [8][HG][LATENT]
+  float* sm_m = sm_acc + 8 * HG * LATENT;                        // [8][HG]
+  float* sm_l = sm_m + 8 * HG;                                   // [8][HG]
+  const int split = blockIdx.x, hg = blockIdx.y, t = blockIdx.z;
+  const int pos = p.positions[t];
+  if (pos < 0) return;
+  int first, nctx;
+  visible_range(pos, p.window, &first, &nctx);
+  const int total = p.n_sinks + nctx;
+  const int k_begin = split * p.kps;
+  if (k_begin >= total) return;
+  const int k_end = min(total, k_begin + p.kps);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = p.slots[t];
+
+  RowFrag qf[HG];
+#pragma unroll
+  for (int g = 0; g < HG; ++g) load_row(p.q_lat + ((long)t * p.H + hg * HG + g) * ROW, lane, &qf[g]);
+  float m[HG], l[HG], acc[HG][16];
+#pragma unroll
+  for (int g = 0; g < HG; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[g][i] = 0.f;
+  }
+  for (int k = k_begin + warp; k < k_end; k += 8) {
+    const bf16* row;
+    if (k < p.n_sinks) {
+      row = p.sinks + (long)k * ROW;
+    } else {
+      const long r = cache_row_of(first + (k - p.n_sinks), slot, p.page_table, p.max_pages, p.page_tokens, p.num_pages);
+      if (r < 0) {
+        if (lane == 0 && p.status) atomicOr(p.status, IFAB_STATUS_BAD_INDEX);
+        continue;
+      }
+      row = p.cache + r * ROW;
+    }
+    RowFrag kf;
+    load_row(row, lane, &kf);
+#pragma unroll
+    for (int g = 0; g < HG; ++g) {
+      float s = qf[g].rp[0] * kf.rp[0] + qf[g].rp[1] * kf.rp[1];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) s = fmaf(qf[g].lat[i], kf.lat[i], s);
+      s = warp_sum(s) * p.scale;
+      const float mn = fmaxf(m[g], s);
+      const float corr = __expf(m[g] - mn), pe = __expf(s - mn);
+      l[g] = l[g] * corr + pe;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) acc[g][i] = acc[g][i] * corr + pe * kf.lat[i];
+      m[g] = mn;
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < HG; ++g) {
+    if (lane == 0) {
+      sm_m[warp * HG + g] = m[g];
+      sm_l[warp * HG + g] = l[g];
+    }
+    float* dst = sm_acc + ((long)warp * HG + g) * LATENT;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      dst[lane * 8 + i] = acc[g][i];
+      dst[256 + lane * 8 + i] = acc[g][8 + i];
+    }
+  }
+  __syncthreads();
+  // fixed-order merge of the 8 warps
+  for (int g = 0; g < HG; ++g) {
+    float M = -INFINITY;
+    for (int w = 0; w < 8; ++w) M = fmaxf(M, sm_m[w * HG + g]);
+    float wgt[8], L = 0.f;
+    for (int w = 0; w < 8; ++w) {
+      wgt[w] = (sm_m[w * HG + g] == -INFINITY) ? 0.f : __expf(sm_m[w * HG + g] - M);
+      L += wgt[w] * sm_l[w * HG + g];
+    }
+    float* out = p.scratch + (((long)t * p.H + hg * HG + g) * p.max_splits + split) * (LATENT + 2);
+    for (int c = threadIdx.x; c < LATENT; c += blockDim.x) {
+      float v = 0.f;
+      for (int w = 0; w < 8; ++w) v += wgt[w] * sm_acc[((long)w * HG + g) * LATENT + c];
+      out[c] = v;
+    }
+    if (threadIdx.x == 0) {
+      out[LATENT] = M;
+      out[LATENT + 1] = L;
+    }
+  }
+}
+
+// grid (H, T): merge splits, then out[t][h*vdim + j] = sum_c o[c] * W_UV[h][j][c]
+__global__ void __launch_bounds__(256) mla_merge_vup_kernel(AttnParams p, const bf16* w_kvb, int nope, int vdim,
+                                                            bf16* out, long ldo) {
+  __shared__ __align__(16) bf16 os[LATENT];
+  __shared__ float wgt[64];
+  __shared__ float Ls;
+  const int h = blockIdx.x, t = blockIdx.y;
+  const int pos = p.positions[t];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (pos < 0) return;
+  int first, nctx;
+  visible_range(pos, p.window, &first, &nctx);
+  const int total = p.n_sinks + nctx;
+  int ns = (total + p.kps - 1) / p.kps;
+  if (ns > p.max_splits) ns = p.max_splits;
+  const float* base = p.scratch + ((long)t * p.H + h) * p.max_splits * (LATENT + 2);
+  if (threadIdx.x == 0) {
+    float M = -INFINITY;
+    for (int s = 0; s < ns; ++s) M = fmaxf(M, base[(long)s * (LATENT + 2) + LATENT]);
+    float L = 0.f;
+    for (int s = 0; s < ns; ++s) {
+      const float ms = base[(long)s * (LATENT + 2) + LATENT];
+      const float w = (ms == -INFINITY) ? 0.f : __expf(ms - M);
+      wgt[s] = w;
+      L += w * base[(long)s * (LATENT + 2) + LATENT + 1];
+    }
+    Ls = L;
+  }
+  __syncthreads();
+  const float invL = Ls > 0.f ? 1.f / Ls : 0.f;
+  for (int c = threadIdx.x; c < LATENT; c += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < ns; ++s) v += wgt[s] * base[(long)s * (LATENT + 2) + c];
+    os[c] = __float2bfloat16_rn(v * invL);
+  }
+  __syncthreads();
+  const bf16* W = w_kvb + ((long)h * (nope + vdim) + nope) * LATENT;
+  for (int j0 = warp * 4; j0 < vdim; j0 += 32) {
+    const bf16* rows[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) rows[r] = (j0 + r < vdim) ? W + (long)(j0 + r) * LATENT : nullptr;
+    float acc[4][1] = {{0.f}, {0.f}, {0.f}, {0.f}};
+    warp_rows_dot<1, 4>(rows, os, LATENT, acc);
+    warp_reduce_acc<1, 4>(acc);
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+        if (j0 + r < vdim) out[(long)t * ldo + (long)h * vdim + j0 + r] = __float2bfloat16_rn(acc[r][0]);
+    }
+  }
+}
+
+template <int HG>
+int launch_split(const AttnParams& p, cudaStream_t s) {
+  const size_t smem = (size_t)(8 * HG * LATENT + 16 * HG) * sizeof(float);
+  auto k = mla_split_kernel<HG>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dim3 grid(p.max_splits, p.H / HG, p.T);
+  k<<<grid, 256, smem, s>>>(p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" int ifab_mla_kv_write(const void* kv, long ldkv, const void* norm_w, float eps, float theta,
+                                 const int32_t* positions, const int32_t* slots, const int32_t* page_table,
+                                 int max_pages, int page_tokens, void* cache, int num_pages, int T, int latent, int rope,
+                                 uint32_t* status, void* stream) {
+  if (latent % 8 != 0 || latent > 1024 || rope % 2 != 0 || rope > 256 || ldkv % 8 != 0) return -1;
+  mla_kv_write_kernel<<<T, 128, 0, (cudaStream_t)stream>>>((const bf16*)kv, ldkv, (const bf16*)norm_w, eps, theta,
+                                                          positions, slots, page_table, max_pages, page_tokens,
+                                                          (bf16*)cache, num_pages, latent, rope, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ifab_mla_q_absorb(const void* q, long ldq, const void* w_kvb, float theta, const int32_t* positions,
+                                 void* q_lat, int T, int H, int nope, int rope, int latent, int vdim, void* stream) {
+  if (nope > 256 || latent % 2 != 0 || rope % 2 != 0 || rope > 512) return -1;
+  dim3 grid(H, T);
+  mla_q_absorb_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)q, ldq, (const bf16*)w_kvb, theta, positions,
+                                                             (bf16*)q_lat, H, nope, rope, latent, vdim);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ifab_mla_decode_attention(const void* q_lat, const void* cache, const int32_t* positions,
+                                         const int32_t* slots, const int32_t* page_table, int max_pages,
+                                         int page_tokens, int num_pages, const void* sinks, int n_sinks, int window,
+                                         float scale, int T, int H, int latent, int rope, int keys_per_split,
+                                         int max_splits, float* scratch, uint64_t scratch_bytes, const void* w_kvb,
+                                         int nope, int vdim, void* out, long ldo, uint32_t* status, void* stream) {
+  if (latent != LATENT || rope != ROPE) return -1;
+  if (max_splits < 1 || max_splits > 64 || keys_per_split < 8) return -1;
+  if ((uint64_t)T * H * max_splits * (LATENT + 2) * sizeof(float) > scratch_bytes) return -5;
+  AttnParams p{(const bf16*)q_lat, (const bf16*)cache, positions, slots, page_table, max_pages, page_tokens, num_pages,
+               (const bf16*)sinks, sinks ? n_sinks : 0, window, scale, T, H, keys_per_split, max_splits, scratch, status};
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc;
+  if (H % 4 == 0) rc = launch_split<4>(p, s);
+  else if (H % 2 == 0) rc = launch_split<2>(p, s);
+  else rc = launch_split<1>(p, s);
+  if (rc) return rc;
+  dim3 grid(H, T);
+  mla_merge_vup_kernel<<<grid, 256, 0, s>>>(p, (const bf16*)w_kvb, nope, vdim, (bf16*)out, ldo);
+  return (int)cudaGetLastError();
+}

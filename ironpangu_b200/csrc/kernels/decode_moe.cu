@@ -1,0 +1,496 @@
+// MoE decode path for sm_100a with owner-local expert parallelism (tokens and routes replicated on
+// every rank, each rank evaluates the routes that land on its experts, partial outputs are summed
+// by the fused all-reduce of the down projection).
+//
+//   router_topk_kernel        f32 router GEMV (+RMSNorm prologue); the last CTA to finish turns the
+//                             logits into top-k ids and weights (softmax top-k or sigmoid+bias)
+//   moe_gate_up_kernel        one CTA column per route: gate/up rows of the routed expert, SwiGLU
+//   moe_down_allreduce_kernel score-weighted sum of the local experts' down projections (+ the
+//                             tensor-parallel shard of the shared expert) + one-shot all-reduce
+//   lm_head_argmax_kernel     vocabulary-sharded logits + greedy selection; the last CTA exchanges
+//                             (value, index) pairs with the peers so every rank ends with the token
+//
+// Reference counterparts: router_projection/router_select, route_quantize, expert_gmm,
+// expert_reduce and allreduce (native/src/token_executor.h:957-1205) and emit (:1206-1274).
+#include "gemv.cuh"
+#include "oneshot_ar.cuh"
+#include "ifab_kernels.h"
+
+using namespace ifab;
+
+namespace {
+
+constexpr int MAX_TOPK = 16;
+
+// ------------------------------------------------------------------------------------------------
+struct RouterParams {
+  const bf16* x; long ldx; const bf16* norm_w; float eps;
+  const float* w; const float* bias;
+  float* logits; int32_t* ids; float* wts;
+  int T, D, E, topk, scoring, renorm; float scale;
+  uint32_t* ticket;
+};
+
+template <int T>
+__global__ void __launch_bounds__(256) router_topk_kernel(RouterParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* xs = reinterpret_cast<bf16*>(smem_raw);
+  __shared__ float red[T * 33];
+  __shared__ int is_last;
+  stage_x<T>(xs, p.x, p.ldx, 0, p.T, p.D, p.norm_w, p.eps, false, red);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e = blockIdx.x * 8 + warp;
+  if (e < p.E) {
+    float acc[T];
+#pragma unroll
+    for (int t = 0; t < T; ++t) acc[t] = 0.f;
+    const float* wr = p.w + (long)e * p.D;
+    for (int c = lane; c < p.D / 4; c += 32) {
+      const float4 wv = __ldg(reinterpret_cast<const float4*>(wr) + c);
+#pragma unroll
+      for (int t = 0; t < T; ++t) {
+        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(xs + t * p.D + c * 4);
+        const float2 a = __bfloat1622float2(xp[0]), b = __bfloat1622float2(xp[1]);
+        acc[t] += wv.x * a.x + wv.y * a.y + wv.z * b.x + wv.w * b.y;
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+      const float v = warp_sum(acc[t]);
+      if (lane == 0 && t < p.T) p.logits[(long)t * p.E + e] = v;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t tk = atomicAdd(p.ticket, 1u);
+    is_last = (tk == gridDim.x - 1);
+    if (is_last) *p.ticket = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // selection: warp t handles token t; each lane owns experts lane, lane+32, ...
+  if (warp >= p.T) return;
+  const int t = warp;
+  constexpr int PER = 8;  // supports E <= 256
+  float score[PER], sel[PER];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int ei = lane + 32 * i;
+    score[i] = (ei < p.E) ? __ldcg(p.logits + (long)t * p.E + ei) : -INFINITY;
+    mx = fmaxf(mx, score[i]);
+  }
+  mx = warp_max(mx);
+  float denom = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int ei = lane + 32 * i;
+    if (ei < p.E) {
+      if (p.scoring == 0) {
+        score[i] = __expf(score[i] - mx);
+        denom += score[i];
+        sel[i] = score[i];
+      } else {
+        score[i] = 1.f / (1.f + __expf(-score[i]));
+        sel[i] = score[i] + (p.bias ? p.bias[ei] : 0.f);
+      }
+    } else {
+      score[i] = 0.f;
+      sel[i] = -INFINITY;
+    }
+  }
+  denom = warp_sum(denom);
+  float picked_w[MAX_TOPK];
+  int picked_e[MAX_TOPK];
+  float wsum = 0.f;
+  for (int k = 0; k < p.topk; ++k) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int ei = lane + 32 * i;
+      if (sel[i] > bv || (sel[i] == bv && ei < bi)) { bv = sel[i]; bi = ei; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    // owner lane reports the raw score and retires the expert
+    float raw = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      if (lane + 32 * i == bi) { raw = score[i]; sel[i] = -INFINITY; }
+    }
+    raw = warp_sum(raw);
+    picked_e[k] = bi;
+    picked_w[k] = (p.scoring == 0) ? raw / denom : raw;
+    wsum += picked_w[k];
+  }
+  if (lane == 0) {
+    for (int k = 0; k < p.topk; ++k) {
+      float w = picked_w[k];
+      if (p.scoring == 0) { if (p.renorm) w = w / wsum; }
+      else w = w / (wsum + 1e-20f);
+      p.ids[t * p.topk + k] = picked_e[k];
+      p.wts[t * p.topk + k] = w * p.scale;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+struct GateUpParams {
+  const bf16* x; long ldx; const bf16* norm_w; float eps;
+  const int32_t* ids; int T, D, F, topk, e0, e_local;
+  const bf16* w_gu; const bf16* w_sgu; int Fs;
+  bf16* act;
+};
+
+// grid: (ceil(F/16), T*topk + T). Column y < T*topk is route (t, k); columns after that are the shared
+// expert of token t. Routes that belong to other ranks exit at once.
+__global__ void __launch_bounds__(256) moe_gate_up_kernel(GateUpParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* xs = reinterpret_cast<bf16*>(smem_raw);
+  __shared__ float red[33];
+  const int routes = p.T * p.topk;
+  int t, slot, Fcur;
+  const bf16* W;
+  if ((int)blockIdx.y < routes) {
+    t = blockIdx.y / p.topk;
+    slot = blockIdx.y % p.topk;
+    const int e = p.ids[blockIdx.y];
+    if (e < p.e0 || e >= p.e0 + p.e_local) return;
+    W = p.w_gu + (size_t)(e - p.e0) * 2 * p.F * p.D;
+    Fcur = p.F;
+  } else {
+    t = blockIdx.y - routes;
+    slot = p.topk;
+    W = p.w_sgu;
+    Fcur = p.Fs;
+    if (W == nullptr) return;
+  }
+  if ((int)blockIdx.x * 16 >= Fcur) return;
+  stage_x<1>(xs, p.x, p.ldx, t, p.T, p.D, p.norm_w, p.eps, false, red);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j0 = (blockIdx.x * 8 + warp) * 2;
+  if (j0 >= Fcur) return;
+  const bf16* rows[4];
+  rows[0] = W + (size_t)j0 * p.D;
+  rows[1] = (j0 + 1 < Fcur) ? W + (size_t)(j0 + 1) * p.D : nullptr;
+  rows[2] = W + (size_t)(Fcur + j0) * p.D;
+  rows[3] = (j0 + 1 < Fcur) ? W + (size_t)(Fcur + j0 + 1) * p.D : nullptr;
+  float acc[4][1] = {{0.f}, {0.f}, {0.f}, {0.f}};
+  warp_rows_dot<1, 4>(rows, xs, p.D, acc);
+  warp_reduce_acc<1, 4>(acc);
+  if (lane == 0) {
+    bf16* out = p.act + ((size_t)t * (p.topk + 1) + slot) * p.F;
+    out[j0] = __float2bfloat16_rn(silu(bf16_round(acc[0][0])) * bf16_round(acc[2][0]));
+    if (j0 + 1 < Fcur) out[j0 + 1] = __float2bfloat16_rn(silu(bf16_round(acc[1][0])) * bf16_round(acc[3][0]));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+struct DownParams {
+  const bf16* act; const int32_t* ids; const float* wts;
+  int T, D, F, topk, e0, e_local;
+  const bf16* w_down; const bf16* w_sdown; int Fs;
+  const bf16* residual; long ldr; bf16* y; long ldy;
+  FabricView fv; uint64_t* seq; uint32_t* done;
+};
+
+template <int T, int R>
+__global__ void __launch_bounds__(256) moe_down_allreduce_kernel(DownParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* as = reinterpret_cast<bf16*>(smem_raw);   // one activation row [F]
+  constexpr int RPC = 8 * R;
+  __shared__ float slab[T * RPC];
+  __shared__ int timed_out;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nbase = blockIdx.x * RPC, n0 = nbase + warp * R;
+  for (int i = threadIdx.x; i < T * RPC; i += blockDim.x) slab[i] = 0.f;
+  if (threadIdx.x == 0) timed_out = 0;
+  float total[R][T];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int t = 0; t < T; ++t) total[r][t] = 0.f;
+
+#pragma unroll
+  for (int t = 0; t < T; ++t) {
+    if (t >= p.T) break;
+    for (int slot = 0; slot <= p.topk; ++slot) {
+      const bf16* W;
+      int Fcur;
+      float wgt;
+      if (slot < p.topk) {
+        const int e = p.ids[t * p.topk + slot];
+        if (e < p.e0 || e >= p.e0 + p.e_local) continue;   // uniform across the block
+        W = p.w_down + (size_t)(e - p.e0) * p.D * p.F;
+        Fcur = p.F;
+        wgt = p.wts[t * p.topk + slot];
+      } else {
+        if (p.w_sdown == nullptr) continue;
+        W = p.w_sdown;
+        Fcur = p.Fs;
+        wgt = 1.f;
+      }
+      __syncthreads();
+      const bf16* arow = p.act + ((size_t)t * (p.topk + 1) + slot) * p.F;
+      for (int c = threadIdx.x; c < (Fcur >> 3); c += blockDim.x)
+        *reinterpret_cast<uint4*>(as + c * 8) = *reinterpret_cast<const uint4*>(arow + c * 8);
+      __syncthreads();
+      const bf16* rows[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) rows[r] = (n0 + r < p.D) ? W + (size_t)(n0 + r) * Fcur : nullptr;
+      float acc[R][1];
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r][0] = 0.f;
+      warp_rows_dot<1, R>(rows, as, Fcur, acc);
+      warp_reduce_acc<1, R>(acc);
+#pragma unroll
+      for (int r = 0; r < R; ++r) total[r][t] += (slot < p.topk) ? wgt * bf16_round(acc[r][0]) : acc[r][0];
+    }
+  }
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int t = 0; t < T; ++t) slab[t * RPC + warp * R + r] = total[r][t];
+  }
+  __syncthreads();
+  oneshot_allreduce_slab<T, RPC>(slab, p.fv, p.seq, p.done, nbase, p.T, p.D, p.residual, p.ldr, p.y, p.ldy, nullptr,
+                                 &timed_out);
+}
+
+template <int T, int R>
+int launch_down(const DownParams& p, cudaStream_t s) {
+  const size_t smem = (size_t)(p.F > p.Fs ? p.F : p.Fs) * sizeof(bf16);
+  dim3 grid((p.D + 8 * R - 1) / (8 * R));
+  moe_down_allreduce_kernel<T, R><<<grid, 256, smem, s>>>(p);
+  return (int)cudaGetLastError();
+}
+template <int T>
+int dispatch_down(const DownParams& p, cudaStream_t s) {
+  if ((p.D + 7) / 8 <= 296) return launch_down<T, 1>(p, s);
+  if ((p.D + 15) / 16 <= 296) return launch_down<T, 2>(p, s);
+  if ((p.D + 31) / 32 <= 296) return launch_down<T, 4>(p, s);
+  return -2;
+}
+
+// ------------------------------------------------------------------------------------------------
+struct HeadParams {
+  const bf16* x; long ldx; const bf16* norm_w; float eps;
+  const bf16* w; float* logits;
+  int T, V, K, vocab_offset;
+  float2* partial;     // [grid][T] (value, index-as-int-bits)
+  int32_t* out_ids; float* out_vals;
+  FabricView fv; uint64_t* seq; uint32_t* done;
+};
+
+template <int T, int R>
+__global__ void __launch_bounds__(256) lm_head_argmax_kernel(HeadParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* xs = reinterpret_cast<bf16*>(smem_raw);
+  __shared__ float red[T * 33];
+  __shared__ float bestv[8][T];
+  __shared__ int besti[8][T];
+  __shared__ int is_last;
+  stage_x<T>(xs, p.x, p.ldx, 0, p.T, p.K, p.norm_w, p.eps, false, red);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * 8 + warp) * R;
+  {
+    const bf16* rows[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) rows[r] = (n0 + r < p.V) ? p.w + (size_t)(n0 + r) * p.K : nullptr;
+    float acc[R][T];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int t = 0; t < T; ++t) acc[r][t] = 0.f;
+    warp_rows_dot<T, R>(rows, xs, p.K, acc);
+    warp_reduce_acc<T, R>(acc);
+    if (lane == 0) {
+#pragma unroll
+      for (int t = 0; t < T; ++t) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          if (n0 + r >= p.V) continue;
+          if (p.logits && t < p.T) p.logits[(size_t)t * p.V + n0 + r] = acc[r][t];
+          if (acc[r][t] > bv) { bv = acc[r][t]; bi = p.vocab_offset + n0 + r; }
+        }
+        bestv[warp][t] = bv;
+        besti[warp][t] = bi;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < T) {
+    const int t = threadIdx.x;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int w = 0; w < 8; ++w)
+      if (bestv[w][t] > bv || (bestv[w][t] == bv && besti[w][t] < bi)) { bv = bestv[w][t]; bi = besti[w][t]; }
+    p.partial[(size_t)blockIdx.x * T + t] = make_float2(bv, __int_as_float(bi));
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t tk = atomicAdd(p.done, 1u);
+    is_last = (tk == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // final reduction over CTAs: warp t handles token t
+  const uint64_t epoch = *reinterpret_cast<volatile uint64_t*>(p.seq) + 1;
+  const uint32_t par = (uint32_t)(epoch & 1);
+  const int world = p.fv.world, rank = p.fv.rank;
+  if (warp < p.T) {
+    const int t = warp;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int c = lane; c < (int)gridDim.x; c += 32) {
+      const float2 v = __ldcg(p.partial + (size_t)c * T + t);
+      const int vi = __float_as_int(v.y);
+      if (v.x > bv || (v.x == bv && vi < bi)) { bv = v.x; bi = vi; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (world > 1) {
+      // exchange: slot [parity][src rank][t] in every peer's staging area
+      if (lane < world) {
+        float2* dst = reinterpret_cast<float2*>(p.fv.data[lane] + (size_t)par * p.fv.data_half_bytes) + rank * T + t;
+        *dst = make_float2(bv, __int_as_float(bi));
+      }
+    } else if (lane == 0) {
+      p.out_ids[t] = bi;
+      if (p.out_vals) p.out_vals[t] = bv;
+    }
+  }
+  if (world > 1) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < world) {
+      const int q = threadIdx.x;
+      st_release_sys(p.fv.flags[q] + (size_t)par * p.fv.flag_half_words + rank, epoch);
+      if (!wait_flag_bounded(p.fv.flags[rank] + (size_t)par * p.fv.flag_half_words + q, epoch, p.fv.spin_limit))
+        atomicOr(p.fv.status, IFAB_STATUS_PEER_TIMEOUT);
+    }
+    __syncthreads();
+    if (threadIdx.x < p.T) {
+      const int t = threadIdx.x;
+      const float2* src = reinterpret_cast<const float2*>(p.fv.data[rank] + (size_t)par * p.fv.data_half_bytes);
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int q = 0; q < world; ++q) {
+        const float2 v = __ldcg(src + q * T + t);
+        const int vi = __float_as_int(v.y);
+        if (v.x > bv || (v.x == bv && vi < bi)) { bv = v.x; bi = vi; }
+      }
+      p.out_ids[t] = bi;
+      if (p.out_vals) p.out_vals[t] = bv;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *p.done = 0;
+    *p.seq = epoch;
+    __threadfence();
+  }
+}
+
+template <int T, int R>
+int launch_head(const HeadParams& p, uint64_t partial_bytes, cudaStream_t s) {
+  const size_t smem = (size_t)T * p.K * sizeof(bf16);
+  auto k = lm_head_argmax_kernel<T, R>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dim3 grid((p.V + 8 * R - 1) / (8 * R));
+  if ((uint64_t)grid.x * T * sizeof(float2) > partial_bytes) return -5;
+  k<<<grid, 256, smem, s>>>(p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" int ifab_router_topk(const void* x, long ldx, const void* norm_w, float eps, const float* w_router,
+                                const float* bias, float* logits, int32_t* ids, float* wts, int T, int D, int E,
+                                int topk, int scoring, int renorm, float scale, uint32_t* ticket, void* stream) {
+  if (T < 1 || T > 8 || E > 256 || topk > MAX_TOPK || topk > E || D % 8 != 0) return -1;
+  RouterParams p{(const bf16*)x, ldx, (const bf16*)norm_w, eps, w_router, bias, logits, ids, wts,
+                 T, D, E, topk, scoring, renorm, scale, ticket};
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid((E + 7) / 8);
+#define IFAB_ROUTER(TT)                                                                                   \
+  {                                                                                                       \
+    const size_t smem = (size_t)TT * D * sizeof(bf16);                                                    \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(router_topk_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    router_topk_kernel<TT><<<grid, 256, smem, s>>>(p);                                                    \
+  }
+  if (T <= 1) IFAB_ROUTER(1) else if (T <= 2) IFAB_ROUTER(2) else if (T <= 4) IFAB_ROUTER(4) else IFAB_ROUTER(8)
+#undef IFAB_ROUTER
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ifab_moe_gate_up_decode(const void* x, long ldx, const void* norm_w, float eps, const int32_t* ids, int T,
+                                       int D, int F, int topk, int e0, int e_local, const void* w_gu,
+                                       const void* w_shared_gu, int Fs, void* act, void* stream) {
+  if (D % 8 != 0 || F % 8 != 0 || Fs % 8 != 0 || Fs > F) return -1;
+  GateUpParams p{(const bf16*)x, ldx, (const bf16*)norm_w, eps, ids, T, D, F, topk, e0, e_local,
+                 (const bf16*)w_gu, (const bf16*)w_shared_gu, Fs, (bf16*)act};
+  dim3 grid((F + 15) / 16, T * topk + T);
+  const size_t smem = (size_t)D * sizeof(bf16);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(moe_gate_up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  moe_gate_up_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ifab_moe_down_allreduce_decode(const void* act, const int32_t* ids, const float* wts, int T, int D, int F,
+                                              int topk, int e0, int e_local, const void* w_down,
+                                              const void* w_shared_down, int Fs, const void* residual, long ldr,
+                                              void* y, long ldy, const IfabFabric* fab, void* stream) {
+  if (T < 1 || T > 8 || F % 8 != 0 || Fs % 8 != 0) return -1;
+  DownParams p;
+  p.act = (const bf16*)act; p.ids = ids; p.wts = wts;
+  p.T = T; p.D = D; p.F = F; p.topk = topk; p.e0 = e0; p.e_local = e_local;
+  p.w_down = (const bf16*)w_down; p.w_sdown = (const bf16*)w_shared_down; p.Fs = Fs;
+  p.residual = (const bf16*)residual; p.ldr = ldr; p.y = (bf16*)y; p.ldy = ldy;
+  if (int rc = fabric_view(fab, &p.fv)) return rc;
+  p.seq = fab->seq; p.done = fab->done;
+  if ((size_t)fab->world * T * D * sizeof(float) > fab->data_half_bytes) return -3;
+  if ((size_t)fab->world * 296 > fab->flag_half_words) return -4;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (T <= 1) return dispatch_down<1>(p, s);
+  if (T <= 2) return dispatch_down<2>(p, s);
+  if (T <= 4) return dispatch_down<4>(p, s);
+  return dispatch_down<8>(p, s);
+}
+
+extern "C" int ifab_lm_head_argmax(const void* x, long ldx, const void* norm_w, float eps, const void* w, float* logits,
+                                   int T, int V_local, int K, int vocab_offset, void* partial, uint64_t partial_bytes,
+                                   int32_t* out_ids, float* out_vals, const IfabFabric* fab, void* stream) {
+  if (T < 1 || T > 8 || K % 8 != 0) return -1;
+  HeadParams p;
+  p.x = (const bf16*)x; p.ldx = ldx; p.norm_w = (const bf16*)norm_w; p.eps = eps;
+  p.w = (const bf16*)w; p.logits = logits; p.T = T; p.V = V_local; p.K = K; p.vocab_offset = vocab_offset;
+  p.partial = (float2*)partial; p.out_ids = out_ids; p.out_vals = out_vals;
+  if (int rc = fabric_view(fab, &p.fv)) return rc;
+  p.seq = fab->seq; p.done = fab->done;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (T <= 1) return launch_head<1, 4>(p, partial_bytes, s);
+  if (T <= 2) return launch_head<2, 4>(p, partial_bytes, s);
+  if (T <= 4) return launch_head<4, 4>(p, partial_bytes, s);
+  return launch_head<8, 2>(p, partial_bytes, s);
+}

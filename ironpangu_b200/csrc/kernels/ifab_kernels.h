@@ -1,0 +1,100 @@
+/* C ABI of the sm_100a kernel library (libifab_kernels.so).
+ *
+ * Every entry point takes raw device pointers plus a CUDA stream handle and returns 0 on success,
+ * a negative value for a rejected argument, or a positive cudaError_t from the launch. Nothing here
+ * allocates device memory except the functions in the "fabric" group, which own the symmetric heap.
+ * All matrices are row-major; weights are [out_features, in_features] with in_features contiguous.
+ */
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IFAB_MAX_RANKS 8
+
+/* Symmetric-heap descriptor of one rank (host struct, passed by pointer). data[r]/flags[r] are rank
+ * r's staging area and flag words as mapped into this process; entries >= world are ignored. */
+typedef struct IfabFabric {
+  void* data[IFAB_MAX_RANKS];
+  uint64_t* flags[IFAB_MAX_RANKS];
+  uint64_t* seq;      /* local: number of fused-collective launches completed */
+  uint32_t* done;     /* local: CTA ticket counter of the running launch */
+  uint32_t* status;   /* local: IFAB_STATUS_* bits, sticky until the host clears them */
+  int32_t rank;
+  int32_t world;
+  uint32_t spin_limit;
+  uint32_t data_half_bytes;
+  uint32_t flag_half_words;
+} IfabFabric;
+
+/* ---- fabric: symmetric heap over CUDA IPC (one process per GPU) ---- */
+int ifab_device_alloc(void** out, uint64_t bytes);           /* cudaMalloc + zero fill */
+int ifab_device_free(void* p);
+int ifab_ipc_export(void* p, unsigned char handle[64]);      /* cudaIpcGetMemHandle */
+int ifab_ipc_import(const unsigned char handle[64], void** out);
+int ifab_ipc_close(void* p);
+int ifab_set_device(int device);
+int ifab_peek(void* dst_host, const void* src_device, uint64_t bytes);   /* synchronous small copies of */
+int ifab_poke(void* dst_device, const void* src_host, uint64_t bytes);   /* control words               */
+const char* ifab_error_string(int code);
+
+/* ---- elementwise / layout ---- */
+int ifab_embedding_bf16(const int32_t* ids, const void* table, void* out, int T, int D, int vocab, uint32_t* status,
+                        void* stream);
+int ifab_rmsnorm_bf16(const void* x, long ldx, const void* w, void* y, long ldy, int T, int D, float eps,
+                      int zero_centered, void* stream);
+
+/* ---- decode linears (T <= 8 per tile; larger T loops over tiles) ---- */
+int ifab_gemv_bf16(const void* x, long ldx, const void* w, const void* norm_w, float eps, int zero_centered,
+                   const void* residual, long ldr, void* y, long ldy, int out_f32, int T, int N, int K, int mode,
+                   void* stream);
+int ifab_gemv_allreduce_bf16(const void* x, long ldx, const void* w, const void* residual, long ldr, void* y, long ldy,
+                             void* y_f32, int T, int N, int K, const IfabFabric* fab, void* stream);
+
+/* ---- MoE decode path (owner-local expert parallelism) ---- */
+int ifab_router_topk(const void* x, long ldx, const void* norm_w, float eps, const float* w_router, const float* bias,
+                     float* logits, int32_t* ids, float* wts, int T, int D, int E, int topk, int scoring, int renorm,
+                     float scale, uint32_t* ticket, void* stream);
+int ifab_moe_gate_up_decode(const void* x, long ldx, const void* norm_w, float eps, const int32_t* ids, int T, int D,
+                            int F, int topk, int e0, int e_local, const void* w_gu, const void* w_shared_gu, int Fs,
+                            void* act, void* stream);
+int ifab_moe_down_allreduce_decode(const void* act, const int32_t* ids, const float* wts, int T, int D, int F, int topk,
+                                   int e0, int e_local, const void* w_down, const void* w_shared_down, int Fs,
+                                   const void* residual, long ldr, void* y, long ldy, const IfabFabric* fab,
+                                   void* stream);
+
+/* ---- lm_head + vocab-sharded greedy sampling ---- */
+int ifab_lm_head_argmax(const void* x, long ldx, const void* norm_w, float eps, const void* w, float* logits,
+                        int T, int V_local, int K, int vocab_offset, void* partial /* >= grid*T*8 bytes */,
+                        uint64_t partial_bytes, int32_t* out_ids, float* out_vals, const IfabFabric* fab,
+                        void* stream);
+
+/* ---- MLA (multi-head latent attention) decode path ---- */
+int ifab_mla_kv_write(const void* kv, long ldkv, const void* norm_w, float eps, float theta, const int32_t* positions,
+                      const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens, void* cache,
+                      int num_pages, int T, int latent, int rope, uint32_t* status, void* stream);
+int ifab_mla_q_absorb(const void* q, long ldq, const void* w_kvb, float theta, const int32_t* positions, void* q_lat,
+                      int T, int H, int nope, int rope, int latent, int vdim, void* stream);
+int ifab_mla_decode_attention(const void* q_lat, const void* cache, const int32_t* positions, const int32_t* slots,
+                              const int32_t* page_table, int max_pages, int page_tokens, int num_pages,
+                              const void* sinks, int n_sinks, int window, float scale, int T, int H, int latent,
+                              int rope, int keys_per_split, int max_splits, float* scratch, uint64_t scratch_bytes,
+                              const void* w_kvb, int nope, int vdim, void* out, long ldo, uint32_t* status,
+                              void* stream);
+
+/* ---- GQA decode path (dense models) ---- */
+int ifab_gqa_rope_kv_write(void* qkv, long ld, const int32_t* positions, const int32_t* slots,
+                           const int32_t* page_table, int max_pages, int page_tokens, void* k_cache, void* v_cache,
+                           int num_pages, int T, int Hq, int Hkv, int head_dim, int rotary_dim, float theta,
+                           uint32_t* status, void* stream);
+int ifab_gqa_decode_attention(const void* q, long ldq, const void* k_cache, const void* v_cache,
+                              const int32_t* positions, const int32_t* slots, const int32_t* page_table, int max_pages,
+                              int page_tokens, int num_pages, float scale, int T, int Hq, int Hkv, int head_dim,
+                              int keys_per_split, int max_splits, float* scratch, uint64_t scratch_bytes, void* out,
+                              long ldo, uint32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

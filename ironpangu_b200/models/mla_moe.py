@@ -1,0 +1,287 @@
+"""MLA + MoE decoder (the 92B-class flagship family) on the sm_100a decode kernels.
+
+Layer structure (pre-norm residual blocks)::
+
+    x += o_proj( MLA( norm(x) ) )          q_a|kv_a paired, q_b tp_rows, o_proj tp_columns + all-reduce
+    x += MoE( norm(x) ) + Shared( norm(x) ) routed experts owner-local (EP = TP group), shared expert
+                                            sharded along its intermediate dim; one fused all-reduce
+
+The reference's OpenPangu module set has the same skeleton (paired q_a/kv_a projection, absorbed
+``mla_query``, ``latent_attention``, ``mla_value``, K-sharded ``o_proj`` + ``allreduce``, ``router`` +
+``expert_linear``/``expert_swiglu_down``/``expert_reduce`` + ``allreduce``:
+examples/openpangu/92b-tp8-ep8.inferfabric:29-75); dims here are attributes of :class:`MlaMoeConfig`,
+not constants.
+
+Per decode step and layer this path launches 10 kernels and no stand-alone collective: both
+all-reduces live inside the o_proj / expert-down kernels, and greedy sampling is fused with the
+vocabulary-sharded lm_head.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..ops import decode as K
+from ..parallel.fabric import Fabric
+
+BF16 = torch.bfloat16
+
+
+@dataclass
+class MlaMoeConfig:
+    layers: int = 46
+    hidden: int = 4096
+    vocab: int = 153600
+    heads: int = 32
+    q_lora: int = 1536
+    kv_lora: int = 512
+    nope: int = 128
+    rope: int = 64
+    vdim: int = 128
+    experts: int = 96
+    expert_ffn: int = 1536
+    topk: int = 8
+    shared_ffn: int = 1536
+    theta: float = 6400000.0
+    eps: float = 1e-5
+    window: int = 0
+    scoring: str = "softmax"
+    route_scale: float = 1.0
+    eos: int = -1
+    page_tokens: int = 16
+
+    @staticmethod
+    def flagship() -> "MlaMoeConfig":
+        """The 92B-class configuration: 46 layers, hidden 4096, 32 heads, 96 experts x 1536, top-8 + 1 shared."""
+        return MlaMoeConfig()
+
+    @staticmethod
+    def tiny(layers: int = 2) -> "MlaMoeConfig":
+        return MlaMoeConfig(layers=layers, hidden=256, vocab=1024, heads=8, q_lora=128, kv_lora=512, nope=32, rope=64,
+                            vdim=32, experts=16, expert_ffn=64, topk=4, shared_ffn=64)
+
+    @property
+    def qk_dim(self) -> int:
+        return self.nope + self.rope
+
+    @property
+    def scale(self) -> float:
+        return 1.0 / math.sqrt(self.qk_dim)
+
+    def param_count(self) -> int:
+        c = self
+        per = (c.hidden * (c.q_lora + c.kv_lora + c.rope) + c.q_lora * c.heads * c.qk_dim +
+               c.heads * (c.nope + c.vdim) * c.kv_lora + c.hidden * c.heads * c.vdim + c.experts * c.hidden +
+               c.experts * 3 * c.hidden * c.expert_ffn + 3 * c.hidden * c.shared_ffn + 2 * c.hidden + c.q_lora + c.kv_lora)
+        return per * c.layers + 2 * c.vocab * c.hidden + c.hidden
+
+
+# ---------------------------------------------------------------------------------------------------
+# Weights
+# ---------------------------------------------------------------------------------------------------
+def full_weight_shapes(cfg: MlaMoeConfig) -> Dict[str, tuple]:
+    """Names and shapes of the unsharded checkpoint tensors."""
+    c = cfg
+    s: Dict[str, tuple] = {"embed": (c.vocab, c.hidden), "final_norm": (c.hidden,), "lm_head": (c.vocab, c.hidden)}
+    for l in range(c.layers):
+        p = f"layers.{l}."
+        s[p + "attn_norm"] = (c.hidden,)
+        s[p + "qkv_a"] = (c.q_lora + c.kv_lora + c.rope, c.hidden)
+        s[p + "q_a_norm"] = (c.q_lora,)
+        s[p + "kv_a_norm"] = (c.kv_lora,)
+        s[p + "q_b"] = (c.heads * c.qk_dim, c.q_lora)
+        s[p + "kv_b"] = (c.heads, c.nope + c.vdim, c.kv_lora)
+        s[p + "o_proj"] = (c.hidden, c.heads * c.vdim)
+        s[p + "ffn_norm"] = (c.hidden,)
+        s[p + "router"] = (c.experts, c.hidden)
+        s[p + "gate_up"] = (c.experts, 2 * c.expert_ffn, c.hidden)
+        s[p + "down"] = (c.experts, c.hidden, c.expert_ffn)
+        s[p + "shared_gate_up"] = (2 * c.shared_ffn, c.hidden)
+        s[p + "shared_down"] = (c.hidden, c.shared_ffn)
+    return s
+
+
+def random_full_weights(cfg: MlaMoeConfig, seed: int = 0, device="cpu") -> Dict[str, torch.Tensor]:
+    """N(0, 0.02) weights (norm gains 1 + N(0, 0.02)), bf16 except the f32 router. For small configs / tests."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    out = {}
+    for name, shape in full_weight_shapes(cfg).items():
+        t = torch.randn(shape, generator=g, dtype=torch.float32) * 0.02
+        if name.endswith("norm"):
+            t = t + 1.0
+        out[name] = (t if name.endswith("router") else t.to(BF16)).to(device)
+    return out
+
+
+def shard_weights(cfg: MlaMoeConfig, full: Dict[str, torch.Tensor], rank: int, world: int, device) -> Dict[str, torch.Tensor]:
+    """Slice an unsharded checkpoint for one rank (TP = EP = world)."""
+    c = cfg
+    hl, el, fs = c.heads // world, c.experts // world, c.shared_ffn // world
+    out = {}
+    for name, t in full.items():
+        base = name.split(".")[-1]
+        if base == "q_b":
+            t = t.view(c.heads, c.qk_dim, c.q_lora)[rank * hl:(rank + 1) * hl].reshape(hl * c.qk_dim, c.q_lora)
+        elif base == "kv_b":
+            t = t[rank * hl:(rank + 1) * hl]
+        elif base == "o_proj":
+            t = t[:, rank * hl * c.vdim:(rank + 1) * hl * c.vdim]
+        elif base in ("gate_up", "down"):
+            t = t[rank * el:(rank + 1) * el]
+        elif base == "shared_gate_up":
+            t = torch.cat([t[rank * fs:(rank + 1) * fs], t[c.shared_ffn + rank * fs:c.shared_ffn + (rank + 1) * fs]], 0)
+        elif base == "shared_down":
+            t = t[:, rank * fs:(rank + 1) * fs]
+        elif base == "lm_head":
+            vl = c.vocab // world
+            t = t[rank * vl:(rank + 1) * vl]
+        out[name] = t.contiguous().to(device)
+    return out
+
+
+def random_rank_weights(cfg: MlaMoeConfig, rank: int, world: int, device, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random-init this rank's shard directly on the device (benchmarks: no host copy of a 175 GB model).
+
+    Replicated tensors use a seed shared by all ranks so every rank holds identical values."""
+    c = cfg
+    hl, el, fs, vl = c.heads // world, c.experts // world, c.shared_ffn // world, c.vocab // world
+    shapes = {
+        "q_b": (hl * c.qk_dim, c.q_lora), "kv_b": (hl, c.nope + c.vdim, c.kv_lora), "o_proj": (c.hidden, hl * c.vdim),
+        "gate_up": (el, 2 * c.expert_ffn, c.hidden), "down": (el, c.hidden, c.expert_ffn),
+        "shared_gate_up": (2 * fs, c.hidden), "shared_down": (c.hidden, fs), "lm_head": (vl, c.hidden),
+    }
+    shared_gen = torch.Generator(device=device).manual_seed(seed)
+    local_gen = torch.Generator(device=device).manual_seed(seed * 1000 + 17 + rank)
+    out = {}
+    for name, shape in full_weight_shapes(cfg).items():
+        base = name.split(".")[-1]
+        sharded = base in shapes
+        shp = shapes.get(base, shape)
+        gen = local_gen if sharded else shared_gen
+        dt = torch.float32 if base == "router" else BF16
+        t = torch.empty(shp, dtype=dt, device=device)
+        t.normal_(0.0, 0.02, generator=gen)
+        if base.endswith("norm"):
+            t += 1.0
+        out[name] = t
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# Decoder
+# ---------------------------------------------------------------------------------------------------
+class MlaMoeDecoder:
+    """Per-rank executor for up to ``max_tokens`` (<= 8) query rows per step.
+
+    State: a paged latent KV cache per layer ``[pages, page_tokens, kv_lora + rope]`` and a page table
+    ``[slots, max_pages]``. ``forward`` consumes device-resident ``tokens/positions/slots`` (int32) and
+    leaves the greedy next token of every row in ``self.next_ids``; nothing crosses the host boundary.
+    """
+
+    def __init__(self, cfg: MlaMoeConfig, weights: Dict[str, torch.Tensor], fabric: Fabric, *, max_tokens: int = 1,
+                 max_context: int = 1024, num_slots: int = 1, keys_per_split: int = 64, keep_logits: bool = False):
+        assert 1 <= max_tokens <= 8
+        self.cfg, self.w, self.fabric = cfg, weights, fabric
+        self.rank, self.world = fabric.rank, fabric.world
+        c, dev = cfg, fabric.device
+        assert c.heads % self.world == 0 and c.experts % self.world == 0 and c.vocab % self.world == 0
+        assert c.shared_ffn % (8 * self.world) == 0
+        self.hl, self.el, self.vl = c.heads // self.world, c.experts // self.world, c.vocab // self.world
+        self.T = max_tokens
+        self.max_context = max_context
+        self.max_pages = (max_context + c.page_tokens - 1) // c.page_tokens
+        self.num_slots = num_slots
+        self.num_pages = self.max_pages * num_slots
+        self.kps = keys_per_split
+        self.max_splits = max(1, min(64, (max_context + keys_per_split - 1) // keys_per_split))
+        while self.max_splits * self.kps < max_context:
+            self.kps *= 2
+        T = self.T
+        # static inputs (CUDA-graph friendly)
+        self.tokens = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.positions = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.slots = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.page_table = torch.arange(self.num_pages, dtype=torch.int32, device=dev).view(num_slots, self.max_pages).contiguous()
+        self.caches = [torch.zeros(self.num_pages, c.page_tokens, c.kv_lora + c.rope, dtype=BF16, device=dev)
+                       for _ in range(c.layers)]
+        # activations
+        e = lambda *s, dt=BF16: torch.empty(*s, dtype=dt, device=dev)
+        self.x = e(T, c.hidden)
+        self.qkv = e(T, c.q_lora + c.kv_lora + c.rope)
+        self.q = e(T, self.hl * c.qk_dim)
+        self.q_lat = e(T, self.hl, c.kv_lora + c.rope)
+        self.attn = e(T, self.hl * c.vdim)
+        self.scratch = e(T * self.hl * self.max_splits * (c.kv_lora + 2), dt=torch.float32)
+        self.logits_r = e(T, c.experts, dt=torch.float32)
+        self.route_ids = e(T, c.topk, dt=torch.int32)
+        self.route_w = e(T, c.topk, dt=torch.float32)
+        self.act = torch.zeros(T, c.topk + 1, c.expert_ffn, dtype=BF16, device=dev)
+        self.partial = e(((self.vl + 7) // 8) * 8 * 2, dt=torch.float32)
+        self.next_ids = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.next_vals = torch.zeros(T, dtype=torch.float32, device=dev)
+        self.logits = e(T, self.vl, dt=torch.float32) if keep_logits else None
+        self.launches_per_forward = 3 + 10 * c.layers - 1  # embedding + layers + lm_head (kernel count)
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+
+    # -- one step ----------------------------------------------------------------------------------
+    def forward(self, T: Optional[int] = None) -> torch.Tensor:
+        c, w, fab = self.cfg, self.w, self.fabric
+        T = self.T if T is None else T
+        tok, pos, slot = self.tokens[:T], self.positions[:T], self.slots[:T]
+        x = self.x[:T]
+        st = fab.desc.status
+        K.embedding(tok, w["embed"], out=x, status_ptr=st)
+        for l in range(c.layers):
+            p = f"layers.{l}."
+            qkv = self.qkv[:T]
+            K.gemv(x, w[p + "qkv_a"], norm_w=w[p + "attn_norm"], eps=c.eps, out=qkv)
+            K.mla_kv_write(qkv[:, c.q_lora:], w[p + "kv_a_norm"], pos, slot, self.page_table, self.caches[l],
+                           latent=c.kv_lora, rope=c.rope, eps=c.eps, theta=c.theta, status_ptr=st)
+            q = self.q[:T]
+            K.gemv(qkv[:, :c.q_lora], w[p + "q_b"], norm_w=w[p + "q_a_norm"], eps=c.eps, out=q)
+            q_lat = self.q_lat[:T]
+            K.mla_q_absorb(q, w[p + "kv_b"], pos, nope=c.nope, rope=c.rope, theta=c.theta, out=q_lat)
+            attn = self.attn[:T]
+            K.mla_decode_attention(q_lat, self.caches[l], pos, slot, self.page_table, w[p + "kv_b"], nope=c.nope,
+                                   scale=c.scale, window=c.window, keys_per_split=self.kps, max_splits=self.max_splits,
+                                   scratch=self.scratch, out=attn, status_ptr=st)
+            K.gemv_allreduce(attn, w[p + "o_proj"], fab, residual=x, out=x)
+            K.router_topk(x, w[p + "router"], c.topk, norm_w=w[p + "ffn_norm"], eps=c.eps, scoring=c.scoring,
+                          scale=c.route_scale, ticket_ptr=fab.ticket_ptr, logits=self.logits_r[:T],
+                          ids=self.route_ids[:T], wts=self.route_w[:T])
+            K.moe_gate_up(x, self.route_ids[:T], w[p + "gate_up"], self.rank * self.el, norm_w=w[p + "ffn_norm"],
+                          eps=c.eps, w_shared_gu=w[p + "shared_gate_up"], act=self.act[:T])
+            K.moe_down_allreduce(self.act[:T], self.route_ids[:T], self.route_w[:T], w[p + "down"], self.rank * self.el,
+                                 fab, w_shared_down=w[p + "shared_down"], residual=x, out=x)
+        K.lm_head_argmax(x, w["lm_head"], fab, norm_w=w["final_norm"], eps=c.eps, vocab_offset=self.rank * self.vl,
+                         partial=self.partial, logits=None if self.logits is None else self.logits[:T],
+                         out_ids=self.next_ids[:T], out_vals=self.next_vals[:T])
+        return self.next_ids[:T]
+
+    # -- CUDA graph ----------------------------------------------------------------------------------
+    def capture(self, T: Optional[int] = None, feedback: bool = False) -> torch.cuda.CUDAGraph:
+        """Capture one decode step. With ``feedback`` the graph also copies the sampled token into the
+        input buffer and advances the positions, so back-to-back replays decode autoregressively with
+        no host involvement."""
+        T = self.T if T is None else T
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self.forward(T)  # warm-up outside capture (module loading, attribute setting)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.forward(T)
+            if feedback:
+                self.tokens[:T].copy_(self.next_ids[:T])
+                self.positions[:T].add_(1)
+        self._graph = g
+        return g
+
+    def reset(self) -> None:
+        for cch in self.caches:
+            cch.zero_()

@@ -1,0 +1,104 @@
+"""ctypes binding of ``libifab_kernels.so`` (the sm_100a kernel library).
+
+The library is built in-tree by :mod:`ironpangu_b200._build`. Loading never falls back to another
+implementation: on a machine with a GPU a missing or unbuildable library is an error.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from pathlib import Path
+
+from .. import _build
+
+_lock = threading.Lock()
+_lib = None
+
+c_void_p, c_int, c_long, c_float, c_u64 = C.c_void_p, C.c_int, C.c_long, C.c_float, C.c_uint64
+MAX_RANKS = 8
+
+
+class IfabFabric(C.Structure):
+    """Mirror of ``struct IfabFabric`` in ``csrc/kernels/ifab_kernels.h``."""
+
+    _fields_ = [
+        ("data", c_void_p * MAX_RANKS),
+        ("flags", c_void_p * MAX_RANKS),
+        ("seq", c_void_p),
+        ("done", c_void_p),
+        ("status", c_void_p),
+        ("rank", C.c_int32),
+        ("world", C.c_int32),
+        ("spin_limit", C.c_uint32),
+        ("data_half_bytes", C.c_uint32),
+        ("flag_half_words", C.c_uint32),
+    ]
+
+
+_P = c_void_p
+_SIGS = {
+    "ifab_device_alloc": [C.POINTER(c_void_p), c_u64],
+    "ifab_device_free": [_P],
+    "ifab_ipc_export": [_P, C.c_char_p],
+    "ifab_ipc_import": [C.c_char_p, C.POINTER(c_void_p)],
+    "ifab_ipc_close": [_P],
+    "ifab_set_device": [c_int],
+    "ifab_peek": [_P, _P, c_u64],
+    "ifab_poke": [_P, _P, c_u64],
+    "ifab_embedding_bf16": [_P, _P, _P, c_int, c_int, c_int, _P, _P],
+    "ifab_rmsnorm_bf16": [_P, c_long, _P, _P, c_long, c_int, c_int, c_float, c_int, _P],
+    "ifab_gemv_bf16": [_P, c_long, _P, _P, c_float, c_int, _P, c_long, _P, c_long, c_int, c_int, c_int, c_int, c_int, _P],
+    "ifab_gemv_allreduce_bf16": [_P, c_long, _P, _P, c_long, _P, c_long, _P, c_int, c_int, c_int, C.POINTER(IfabFabric), _P],
+    "ifab_router_topk": [_P, c_long, _P, c_float, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P],
+    "ifab_moe_gate_up_decode": [_P, c_long, _P, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P],
+    "ifab_moe_down_allreduce_decode": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, c_long, _P,
+                                       c_long, C.POINTER(IfabFabric), _P],
+    "ifab_lm_head_argmax": [_P, c_long, _P, c_float, _P, _P, c_int, c_int, c_int, c_int, _P, c_u64, _P, _P,
+                            C.POINTER(IfabFabric), _P],
+    "ifab_mla_kv_write": [_P, c_long, _P, c_float, c_float, _P, _P, _P, c_int, c_int, _P, c_int, c_int, c_int, c_int, _P, _P],
+    "ifab_mla_q_absorb": [_P, c_long, _P, c_float, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "ifab_mla_decode_attention": [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_float, c_int, c_int, c_int,
+                                  c_int, c_int, c_int, _P, c_u64, _P, c_int, c_int, _P, c_long, _P, _P],
+    "ifab_gqa_rope_kv_write": [_P, c_long, _P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
+                               c_float, _P, _P],
+    "ifab_gqa_decode_attention": [_P, c_long, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
+                                  c_int, c_int, _P, c_u64, _P, c_long, _P, _P],
+}
+
+
+def lib_path() -> Path:
+    return _build.KERNEL_LIB
+
+
+def load(build: bool = True):
+    """Return the loaded kernel library, building it first when the sources changed."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = _build.KERNEL_LIB
+        if build:
+            try:
+                path = _build.build_kernels()
+            except Exception:
+                if not path.exists():
+                    raise
+        if not path.exists():
+            raise RuntimeError(f"{path} is missing: run `python -m ironpangu_b200._build`")
+        lib = C.CDLL(str(path))
+        lib.ifab_error_string.restype = C.c_char_p
+        lib.ifab_error_string.argtypes = [c_int]
+        for name, sig in _SIGS.items():
+            fn = getattr(lib, name, None)
+            if fn is None:
+                continue
+            fn.argtypes = sig
+            fn.restype = c_int
+        _lib = lib
+        return lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = load().ifab_error_string(rc).decode()
+        raise RuntimeError(f"{what} failed: {msg} (code {rc})")

@@ -1,0 +1,208 @@
+"""Python entry points of the decode-path kernels (thin wrappers over the C ABI).
+
+All functions launch on the current CUDA stream, never synchronise and never fall back to PyTorch
+math; outputs can be passed in (``out=``) so that an engine can run allocation-free under CUDA
+graph capture.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import check
+
+BF16 = torch.bfloat16
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _rows(x: torch.Tensor) -> int:
+    assert x.dim() == 2 and x.stride(1) == 1
+    return x.stride(0)
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None,
+              status_ptr: Optional[int] = None) -> torch.Tensor:
+    T, (V, D) = ids.numel(), table.shape
+    assert ids.dtype == torch.int32 and table.dtype == BF16 and table.is_contiguous()
+    if out is None:
+        out = torch.empty(T, D, dtype=BF16, device=table.device)
+    check(_lib.load().ifab_embedding_bf16(ids.data_ptr(), table.data_ptr(), out.data_ptr(), T, D, V, status_ptr,
+                                          _stream()), "embedding")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5, zero_centered: bool = False,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    T, D = x.shape
+    if out is None:
+        out = torch.empty(T, D, dtype=BF16, device=x.device)
+    check(_lib.load().ifab_rmsnorm_bf16(x.data_ptr(), _rows(x), w.data_ptr(), out.data_ptr(), _rows(out), T, D, eps,
+                                        int(zero_centered), _stream()), "rmsnorm")
+    return out
+
+
+def gemv(x: torch.Tensor, w: torch.Tensor, *, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-5,
+         zero_centered: bool = False, residual: Optional[torch.Tensor] = None, swiglu: bool = False,
+         out_f32: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y = act(norm(x) @ w.T) (+ residual)`` for a few tokens (decode).
+
+    ``w`` is ``[N, K]`` (or ``[2N, K]`` = gate rows then up rows when ``swiglu``). ``norm_w`` fuses an
+    RMSNorm of ``x`` into the prologue."""
+    T, K = x.shape
+    rows = w.shape[0]
+    assert w.shape[1] == K and w.is_contiguous() and w.dtype == BF16 and x.dtype == BF16
+    N = rows // 2 if swiglu else rows
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.float32 if out_f32 else BF16, device=x.device)
+    check(_lib.load().ifab_gemv_bf16(x.data_ptr(), _rows(x), w.data_ptr(), _ptr(norm_w), eps, int(zero_centered),
+                                     _ptr(residual), _rows(residual) if residual is not None else 0, out.data_ptr(),
+                                     _rows(out), int(out.dtype == torch.float32), T, N, K, int(swiglu), _stream()), "gemv")
+    return out
+
+
+def gemv_allreduce(x: torch.Tensor, w: torch.Tensor, fabric, *, residual: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None, out_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-parallel linear fused with a one-shot all-reduce: ``y = sum_r x_r @ w_r.T (+ residual)``."""
+    T, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and w.is_contiguous()
+    if out is None:
+        out = torch.empty(T, N, dtype=BF16, device=x.device)
+    check(_lib.load().ifab_gemv_allreduce_bf16(x.data_ptr(), _rows(x), w.data_ptr(), _ptr(residual),
+                                               _rows(residual) if residual is not None else 0, out.data_ptr(),
+                                               _rows(out), _ptr(out_f32), T, N, K, C.byref(fabric.desc), _stream()),
+          "gemv_allreduce")
+    return out
+
+
+def router_topk(x: torch.Tensor, w_router: torch.Tensor, topk: int, *, norm_w: Optional[torch.Tensor] = None,
+                eps: float = 1e-5, bias: Optional[torch.Tensor] = None, scoring: str = "softmax", renorm: bool = True,
+                scale: float = 1.0, ticket_ptr: int = 0, logits: Optional[torch.Tensor] = None,
+                ids: Optional[torch.Tensor] = None, wts: Optional[torch.Tensor] = None):
+    """f32 router projection + top-k selection in one launch. Returns (ids int32 [T,k], weights f32 [T,k], logits)."""
+    T, D = x.shape
+    E = w_router.shape[0]
+    assert w_router.dtype == torch.float32 and w_router.is_contiguous()
+    dev = x.device
+    logits = logits if logits is not None else torch.empty(T, E, dtype=torch.float32, device=dev)
+    ids = ids if ids is not None else torch.empty(T, topk, dtype=torch.int32, device=dev)
+    wts = wts if wts is not None else torch.empty(T, topk, dtype=torch.float32, device=dev)
+    mode = {"softmax": 0, "sigmoid_bias_group_topk": 1}[scoring]
+    check(_lib.load().ifab_router_topk(x.data_ptr(), _rows(x), _ptr(norm_w), eps, w_router.data_ptr(), _ptr(bias),
+                                       logits.data_ptr(), ids.data_ptr(), wts.data_ptr(), T, D, E, topk, mode,
+                                       int(renorm), scale, ticket_ptr, _stream()), "router_topk")
+    return ids, wts, logits
+
+
+def moe_gate_up(x: torch.Tensor, ids: torch.Tensor, w_gu: torch.Tensor, e0: int, *,
+                norm_w: Optional[torch.Tensor] = None, eps: float = 1e-5, w_shared_gu: Optional[torch.Tensor] = None,
+                act: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gate/up projections + SwiGLU of the routes owned by this rank (and of the shared-expert shard).
+
+    ``w_gu``: ``[E_local, 2F, D]``; ``act``: ``[T, topk+1, F]`` (slot ``topk`` is the shared expert)."""
+    T, D = x.shape
+    topk = ids.shape[1]
+    e_local, twoF, _ = w_gu.shape
+    F = twoF // 2
+    Fs = 0 if w_shared_gu is None else w_shared_gu.shape[0] // 2
+    if act is None:
+        act = torch.zeros(T, topk + 1, F, dtype=BF16, device=x.device)
+    check(_lib.load().ifab_moe_gate_up_decode(x.data_ptr(), _rows(x), _ptr(norm_w), eps, ids.data_ptr(), T, D, F, topk,
+                                              e0, e_local, w_gu.data_ptr(), _ptr(w_shared_gu), Fs, act.data_ptr(),
+                                              _stream()), "moe_gate_up")
+    return act
+
+
+def moe_down_allreduce(act: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_down: torch.Tensor, e0: int, fabric,
+                       *, w_shared_down: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Score-weighted sum of the local experts' down projections (+ shared shard) fused with the all-reduce."""
+    T, slots, F = act.shape
+    topk = slots - 1
+    e_local, D, _ = w_down.shape
+    Fs = 0 if w_shared_down is None else w_shared_down.shape[1]
+    if out is None:
+        out = torch.empty(T, D, dtype=BF16, device=act.device)
+    check(_lib.load().ifab_moe_down_allreduce_decode(act.data_ptr(), ids.data_ptr(), wts.data_ptr(), T, D, F, topk, e0,
+                                                     e_local, w_down.data_ptr(), _ptr(w_shared_down), Fs,
+                                                     _ptr(residual), _rows(residual) if residual is not None else 0,
+                                                     out.data_ptr(), _rows(out), C.byref(fabric.desc), _stream()),
+          "moe_down_allreduce")
+    return out
+
+
+def lm_head_argmax(x: torch.Tensor, w: torch.Tensor, fabric, *, norm_w: Optional[torch.Tensor] = None,
+                   eps: float = 1e-5, vocab_offset: int = 0, partial: Optional[torch.Tensor] = None,
+                   logits: Optional[torch.Tensor] = None, out_ids: Optional[torch.Tensor] = None,
+                   out_vals: Optional[torch.Tensor] = None):
+    """Vocabulary-sharded lm_head + greedy token selection (cross-rank exchange inside the kernel)."""
+    T, K = x.shape
+    V = w.shape[0]
+    dev = x.device
+    if partial is None:
+        partial = torch.empty(((V + 7) // 8) * 8 * 2, dtype=torch.float32, device=dev)
+    if out_ids is None:
+        out_ids = torch.empty(T, dtype=torch.int32, device=dev)
+    check(_lib.load().ifab_lm_head_argmax(x.data_ptr(), _rows(x), _ptr(norm_w), eps, w.data_ptr(), _ptr(logits), T, V, K,
+                                          vocab_offset, partial.data_ptr(), partial.numel() * partial.element_size(),
+                                          out_ids.data_ptr(), _ptr(out_vals), C.byref(fabric.desc), _stream()),
+          "lm_head_argmax")
+    return out_ids
+
+
+def mla_kv_write(kv: torch.Tensor, norm_w: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                 page_table: torch.Tensor, cache: torch.Tensor, *, latent: int, rope: int, eps: float, theta: float,
+                 status_ptr: Optional[int] = None) -> None:
+    """RMSNorm(latent) + RoPE(k_pe) + scatter into the paged latent cache ``[pages, page_tokens, latent+rope]``."""
+    T = kv.shape[0]
+    num_pages, page_tokens, _ = cache.shape
+    check(_lib.load().ifab_mla_kv_write(kv.data_ptr(), _rows(kv), norm_w.data_ptr(), eps, theta, positions.data_ptr(),
+                                        slots.data_ptr(), page_table.data_ptr(), page_table.shape[1], page_tokens,
+                                        cache.data_ptr(), num_pages, T, latent, rope, status_ptr, _stream()),
+          "mla_kv_write")
+
+
+def mla_q_absorb(q: torch.Tensor, w_kvb: torch.Tensor, positions: torch.Tensor, *, nope: int, rope: int, theta: float,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``q_lat[t,h] = [q_nope[t,h] @ W_UK[h] | RoPE(q_rope[t,h])]`` with ``w_kvb`` = ``[H, nope+vdim, latent]``."""
+    T = q.shape[0]
+    H, rows, latent = w_kvb.shape
+    vdim = rows - nope
+    if out is None:
+        out = torch.empty(T, H, latent + rope, dtype=BF16, device=q.device)
+    check(_lib.load().ifab_mla_q_absorb(q.data_ptr(), _rows(q), w_kvb.data_ptr(), theta, positions.data_ptr(),
+                                        out.data_ptr(), T, H, nope, rope, latent, vdim, _stream()), "mla_q_absorb")
+    return out
+
+
+def mla_decode_attention(q_lat: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                         page_table: torch.Tensor, w_kvb: torch.Tensor, *, nope: int, scale: float, window: int = 0,
+                         sinks: Optional[torch.Tensor] = None, keys_per_split: int = 64, max_splits: int = 16,
+                         scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                         status_ptr: Optional[int] = None) -> torch.Tensor:
+    """Split-KV paged MLA attention + value up-projection. Returns ``[T, H*vdim]`` bf16."""
+    T, H, row = q_lat.shape
+    num_pages, page_tokens, _ = cache.shape
+    latent = w_kvb.shape[2]
+    rope = row - latent
+    vdim = w_kvb.shape[1] - nope
+    if scratch is None:
+        scratch = torch.empty(T * H * max_splits * (latent + 2), dtype=torch.float32, device=q_lat.device)
+    if out is None:
+        out = torch.empty(T, H * vdim, dtype=BF16, device=q_lat.device)
+    check(_lib.load().ifab_mla_decode_attention(
+        q_lat.data_ptr(), cache.data_ptr(), positions.data_ptr(), slots.data_ptr(), page_table.data_ptr(),
+        page_table.shape[1], page_tokens, num_pages, _ptr(sinks), 0 if sinks is None else sinks.shape[0], window, scale,
+        T, H, latent, rope, keys_per_split, max_splits, scratch.data_ptr(), scratch.numel() * 4, w_kvb.data_ptr(), nope,
+        vdim, out.data_ptr(), _rows(out), status_ptr, _stream()), "mla_decode_attention")
+    return out

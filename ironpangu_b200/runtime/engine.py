@@ -1,0 +1,107 @@
+"""Single-sequence generation engine: the public call path a user makes (``prefill`` / ``step`` /
+``generate``) on top of a per-rank decoder and its captured CUDA graphs.
+
+Each ``step`` uploads the step's control inputs (token id, position) from pinned host memory, replays
+the decode graph and reads the sampled token back - the same host/device contract as the reference's
+``set_input_rows`` -> graph replay -> ``emit`` (native/src/token_executor.h:1323-1448). Activations
+never cross the host boundary.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+
+class DecodeEngine:
+    def __init__(self, decoder, chunk: Optional[int] = None):
+        self.dec = decoder
+        self.chunk = chunk or decoder.T
+        self.pos = 0
+        self._ctl_host = torch.zeros(2, dtype=torch.int32).pin_memory()
+        self._ctl_dev = torch.zeros(2, dtype=torch.int32, device=decoder.tokens.device)
+        self._out_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._graph = None
+        self._feedback_graph = None
+        self.h2d_bytes_per_step = 8
+        self.d2h_bytes_per_step = 4
+
+    # -- graphs ------------------------------------------------------------------------------------
+    def _capture(self):
+        d = self.dec
+        d.tokens[:1].copy_(self._ctl_dev[0:1])
+        d.positions[:1].copy_(self._ctl_dev[1:2])
+        d.forward(1)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            d.tokens[:1].copy_(self._ctl_dev[0:1])
+            d.positions[:1].copy_(self._ctl_dev[1:2])
+            d.forward(1)
+        self._graph = g
+
+    def _capture_feedback(self):
+        d = self.dec
+        d.forward(1)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            d.forward(1)
+            d.tokens[:1].copy_(d.next_ids[:1])
+            d.positions[:1].add_(1)
+        self._feedback_graph = g
+
+    # -- public API --------------------------------------------------------------------------------
+    def reset(self) -> None:
+        self.pos = 0
+
+    def prefill(self, tokens: List[int]) -> int:
+        """Run the prompt through the model in chunks; returns the greedy token after the last prompt token."""
+        d = self.dec
+        n = len(tokens)
+        host = torch.tensor(tokens, dtype=torch.int32).pin_memory()
+        last = None
+        for s in range(0, n, self.chunk):
+            m = min(self.chunk, n - s)
+            d.tokens[:m].copy_(host[s:s + m], non_blocking=True)
+            d.positions[:m].copy_(torch.arange(self.pos + s, self.pos + s + m, dtype=torch.int32), non_blocking=False)
+            d.slots[:m].zero_()
+            d.forward(m)
+            last = d.next_ids[m - 1:m]
+        self.pos += n
+        self._out_host.copy_(last)
+        return int(self._out_host[0])
+
+    def step(self, token: int) -> int:
+        """One decode step through the captured graph: H2D control inputs, replay, D2H sampled token."""
+        if self._graph is None:
+            self._capture()
+        self._ctl_host[0] = token
+        self._ctl_host[1] = self.pos
+        self._ctl_dev.copy_(self._ctl_host, non_blocking=True)
+        self._graph.replay()
+        self._out_host.copy_(self.dec.next_ids[:1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.pos += 1
+        return int(self._out_host[0])
+
+    def generate(self, prompt: List[int], max_new_tokens: int, eos: int = -1) -> List[int]:
+        self.reset()
+        tok = self.prefill(prompt)
+        out = [tok]
+        while len(out) < max_new_tokens and tok != eos:
+            tok = self.step(tok)
+            out.append(tok)
+        return out
+
+    def run_device_loop(self, first_token: Optional[int], steps: int) -> None:
+        """Decode ``steps`` tokens with the sampled token fed back on the device (no host round trips)."""
+        d = self.dec
+        if self._feedback_graph is None:
+            self._capture_feedback()
+        if first_token is not None:
+            d.tokens[:1].fill_(first_token)
+            d.positions[:1].fill_(self.pos)
+        for _ in range(steps):
+            self._feedback_graph.replay()
+        self.pos += steps

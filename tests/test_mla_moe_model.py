@@ -1,0 +1,119 @@
+"""Tiny MLA+MoE decoder on the CUDA decode path against the PyTorch fp32 oracle (single GPU)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(max_tokens=1, layers=2, keep_logits=True, window=0):
+    from ironpangu_b200.models.mla_moe import MlaMoeConfig, MlaMoeDecoder, random_full_weights, shard_weights
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    cfg = MlaMoeConfig.tiny(layers)
+    cfg.window = window
+    full = random_full_weights(cfg, seed=0)
+    fab = Fabric(0, 1)
+    dec = MlaMoeDecoder(cfg, shard_weights(cfg, full, 0, 1, "cuda"), fab, max_tokens=max_tokens, max_context=128,
+                        num_slots=2, keep_logits=keep_logits)
+    return cfg, full, fab, dec
+
+
+def _feed(dec, toks, start, slot=0):
+    n = len(toks)
+    dec.tokens[:n].copy_(torch.tensor(toks, dtype=torch.int32))
+    dec.positions[:n].copy_(torch.arange(start, start + n, dtype=torch.int32))
+    dec.slots[:n].fill_(slot)
+    dec.forward(n)
+    return dec.logits[:n].clone(), dec.next_ids[:n].clone()
+
+
+@pytest.mark.parametrize("window", [0, 8])
+def test_token_by_token_matches_oracle(window):
+    from ironpangu_b200.models.mla_moe_ref import forward_ref
+
+    cfg, full, fab, dec = _setup(1, window=window)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab, (16,), generator=g).tolist()
+    ref = forward_ref(cfg, full, torch.tensor(prompt, device="cuda"))
+    for i, t in enumerate(prompt):
+        logits, nid = _feed(dec, [t], i, slot=1)
+        torch.testing.assert_close(logits[0], ref[i], rtol=2e-2, atol=2e-2)
+        assert int(nid[0]) == int(logits[0].argmax())
+    assert fab.status() == 0
+    fab.close()
+
+
+def test_chunked_prefill_then_greedy_decode_matches_oracle():
+    """8-token chunks through the same kernels (causal via per-row positions), then greedy decode."""
+    from ironpangu_b200.models.mla_moe_ref import forward_ref
+
+    cfg, full, fab, dec = _setup(8)
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, cfg.vocab, (19,), generator=g).tolist()
+    seq = list(prompt)
+    nxt = None
+    for s in range(0, len(prompt), 8):
+        chunk = prompt[s:s + 8]
+        logits, ids = _feed(dec, chunk, s)
+        nxt = int(ids[len(chunk) - 1])
+    generated = []
+    for i in range(8):
+        generated.append(nxt)
+        seq.append(nxt)
+        logits, ids = _feed(dec, [nxt], len(seq) - 1)
+        nxt = int(ids[0])
+    ref = forward_ref(cfg, full, torch.tensor(seq, device="cuda"))
+    ref_ids = ref.argmax(-1).tolist()
+    # oracle greedy continuation at every generated position (teacher-forced on our own tokens)
+    mismatches = 0
+    for i, tok in enumerate(generated):
+        p = len(prompt) - 1 + i
+        if ref_ids[p] != tok:
+            top2 = ref[p].topk(2).values
+            assert float(top2[0] - top2[1]) < 5e-3, "greedy token differs beyond a near-tie"
+            mismatches += 1
+    assert mismatches <= 1
+    fab.close()
+
+
+def test_graph_replay_equals_eager_bitwise():
+    cfg, full, fab, dec = _setup(1)
+    prompt = [3, 99, 512, 7, 1000, 42]
+    eager = []
+    for i, t in enumerate(prompt):
+        logits, _ = _feed(dec, [t], i)
+        eager.append(logits.clone())
+    dec.reset()
+    dec.capture(1)
+    for i, t in enumerate(prompt):
+        dec.tokens[:1].fill_(t)
+        dec.positions[:1].fill_(i)
+        dec.slots[:1].fill_(0)
+        if i == 0:
+            # the capture's warm-up wrote position-0 rows of whatever token was in the buffer; replay rewrites them
+            pass
+        dec._graph.replay()
+        assert torch.equal(dec.logits[:1], eager[i]), f"graph replay differs from eager at step {i}"
+    fab.close()
+
+
+def test_feedback_graph_decodes_autoregressively():
+    cfg, full, fab, dec = _setup(1, keep_logits=False)
+    ids_eager = []
+    tok = 11
+    for i in range(6):
+        dec.tokens[:1].fill_(tok)
+        dec.positions[:1].fill_(i)
+        dec.forward(1)
+        tok = int(dec.next_ids[0])
+        ids_eager.append(tok)
+    dec.reset()
+    dec.capture(1, feedback=True)
+    dec.tokens[:1].fill_(11)
+    dec.positions[:1].fill_(0)
+    ids_graph = []
+    for i in range(6):
+        dec._graph.replay()
+        ids_graph.append(int(dec.next_ids[0]))
+    assert ids_graph == ids_eager
+    fab.close()
