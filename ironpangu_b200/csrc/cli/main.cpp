@@ -1,0 +1,262 @@
+// `ifab` command line: offline compiler, inspectors and the CPU oracle.
+//
+//   ifab compile-token MODEL.inferfabric CHECKPOINT|- OUTPUT_DIR [--resident-sequences N]
+//        [--prefill-tokens N | --prefill-variants 2,4,8] [--uncaptured-prefill] [--shared-pages]
+//        [--output-rows] [--bulk-collectives] [--kernel-dir DIR]
+//   ifab explain MODEL.inferfabric            graph / program summary as JSON
+//   ifab model-source MODEL.inferfabric       expanded primitive list (one node per line)
+//   ifab synth-checkpoint MODEL.inferfabric OUT_DIR [--seed N]   random N(0,0.02) safetensors for the model
+//   ifab interpret MODEL.inferfabric CHECKPOINT_DIR NEW_TOKENS TOKEN_ID...   greedy decode on the CPU oracle
+//   ifab inspect FILE                         decode execution.bin / logical.bin / rank-N.bin / arena-rank-N.txt
+//   ifab plan|execute|explain-plan ...        CPU f32 graph planner (see cpu_plan.h)
+//   ifab compile SPEC.json OUT.bin            structural rank plans for TP/SP/CP/PD meshes
+//   ifab demo                                 compile + run the built-in two-layer slice
+//
+// Verbs follow the reference CLI (crates/inferfabric-cli/src/main.rs:17-293).
+#include <cstdio>
+#include <cstring>
+#include <iostream>
+
+#include "bundle.h"
+#include "cpu_plan.h"
+#include "interp.h"
+#include "rankplan.h"
+
+using namespace ifab;
+
+namespace {
+
+int usage() {
+  std::fprintf(stderr,
+               "usage: ifab <command> ...\n"
+               "  compile-token MODEL CHECKPOINT|- OUTPUT_DIR [flags]\n  explain MODEL\n  model-source MODEL\n"
+               "  synth-checkpoint MODEL OUT_DIR [--seed N]\n  interpret MODEL CHECKPOINT_DIR NEW_TOKENS TOKEN...\n"
+               "  inspect FILE\n  plan GRAPH.json|MODEL.inferfabric [OUT.bin]\n  execute GRAPH.json|MODEL.inferfabric INPUTS.json\n"
+               "  compile SPEC.json OUT.bin\n  demo\n");
+  return 2;
+}
+
+std::vector<uint32_t> parse_list(const std::string& s) {
+  std::vector<uint32_t> v;
+  size_t b = 0;
+  while (b < s.size()) {
+    size_t e = s.find(',', b);
+    if (e == std::string::npos) e = s.size();
+    v.push_back((uint32_t)std::stoul(s.substr(b, e - b)));
+    b = e + 1;
+  }
+  return v;
+}
+
+int compile_token(int argc, char** argv) {
+  if (argc < 5) return usage();
+  bundle::BundleInputs in;
+  in.source_path = argv[2];
+  in.source_text = read_file(argv[2], 1 << 20);
+  in.checkpoint_dir = std::string(argv[3]) == "-" ? "" : argv[3];
+  std::string out = argv[4];
+  bool tokens_set = false, variants_set = false;
+  for (int i = 5; i < argc; ++i) {
+    std::string a = argv[i];
+    auto next = [&]() -> std::string {
+      if (i + 1 >= argc) invalid("flag " + a + " needs a value");
+      return argv[++i];
+    };
+    if (a == "--resident-sequences") in.options.resident_sequences = (uint32_t)std::stoul(next());
+    else if (a == "--prefill-tokens") { in.options.prefill_tokens = (uint32_t)std::stoul(next()); tokens_set = true; }
+    else if (a == "--prefill-variants") { in.options.prefill_variants = parse_list(next()); variants_set = true; }
+    else if (a == "--uncaptured-prefill") in.options.uncaptured_prefill = true;
+    else if (a == "--shared-pages") in.options.shared_pages = true;
+    else if (a == "--output-rows") in.options.output_rows = true;
+    else if (a == "--bulk-collectives") in.options.bulk_collectives = true;
+    else if (a == "--allow-stale-index-size") in.allow_stale_index_size = true;
+    else if (a == "--kernel-dir") in.kernel_source_dir = next();
+    else invalid("unknown flag " + a);
+  }
+  if (tokens_set && variants_set) invalid("--prefill-tokens and --prefill-variants are exclusive");
+  if (variants_set) in.options.prefill_tokens = in.options.prefill_variants.back();
+  if (in.options.prefill_tokens >= 4096) in.options.uncaptured_prefill = true;  // the long-chunk envelope runs eagerly
+  auto s = bundle::write_bundle(in, out);
+  std::cout << s.to_json().dump(1) << "\n";
+  return 0;
+}
+
+int explain(const char* path) {
+  graph::Graph g = graph::compile_source(read_file(path, 1 << 20));
+  program::Program p = program::lower(g);
+  Json j = Json::object();
+  j.set("model", g.name);
+  j.set("logical_nodes", (int64_t)g.nodes.size());
+  Json oh = Json::object();
+  for (auto& kv : g.op_histogram()) oh.set(kv.first, (int64_t)kv.second);
+  j.set("logical_ops", oh);
+  j.set("instructions", (int64_t)p.instructions.size());
+  Json ph = Json::object();
+  for (auto& kv : p.op_histogram()) ph.set(kv.first, (int64_t)kv.second);
+  j.set("physical_ops", ph);
+  j.set("launches_per_token", (int64_t)p.launches_per_token());
+  j.set("collectives_per_token", (int64_t)p.collectives_per_token());
+  j.set("parallel", g.parallel.to_json());
+  auto need = init::required_tensors(p);
+  uint64_t bytes = 0;
+  for (auto& kv : need) {
+    uint64_t n = init::dtype_bytes(kv.second.first);
+    for (auto d : kv.second.second) n *= d;
+    bytes += n;
+  }
+  j.set("checkpoint_tensors", (int64_t)need.size());
+  j.set("checkpoint_bytes", bytes);
+  std::cout << j.dump(1) << "\n";
+  return 0;
+}
+
+int interpret(int argc, char** argv) {
+  if (argc < 6) return usage();
+  graph::Graph g = graph::compile_source(read_file(argv[2], 1 << 20));
+  interp::Weights w = interp::Weights::from_checkpoint(init::Checkpoint::inspect(argv[3]));
+  interp::Interpreter it(g, w);
+  uint32_t steps = (uint32_t)std::stoul(argv[4]);
+  uint32_t next = 0, pos = 0;
+  for (int i = 5; i < argc; ++i) next = it.step((uint32_t)std::stoul(argv[i]), pos++);
+  Json gen = Json::array();
+  for (uint32_t s = 0; s < steps; ++s) {
+    gen.push((int64_t)next);
+    if (next == g.eos) break;
+    next = it.step(next, pos++);
+  }
+  Json j = Json::object();
+  j.set("generated", gen);
+  std::cout << j.dump() << "\n";
+  return 0;
+}
+
+int inspect(const char* path) {
+  std::string bytes = read_file(path);
+  if (bytes.compare(0, 8, "IFTOKN01") == 0) std::cout << graph::Graph::decode(bytes).to_json().dump(1) << "\n";
+  else if (bytes.compare(0, 7, "IFTOKN0") == 0) std::cout << program::Program::decode(bytes).to_json().dump(1) << "\n";
+  else if (bytes.compare(0, 8, "IFINIT01") == 0) std::cout << init::Plan::decode(bytes).to_json().dump(1) << "\n";
+  else if (bytes.compare(0, 7, "IFARENA") == 0) {
+    uint64_t pf = 0, bf = 0;
+    bundle::Arena a = bundle::Arena::decode(bytes, &pf, &bf);
+    Json j = Json::object();
+    j.set("bytes", a.bytes);
+    j.set("slots", (int64_t)a.slots.size());
+    j.set("tokens", a.tokens);
+    j.set("program_fingerprint", hex64(pf));
+    j.set("backend_fingerprint", hex64(bf));
+    std::cout << j.dump(1) << "\n";
+  } else if (bytes.compare(0, 8, "IFPLAN01") == 0) std::cout << cpu::decode_plan(bytes).to_json().dump(1) << "\n";
+  else if (bytes.compare(0, 5, "PANGU") == 0) std::cout << rankplan::decode(bytes).to_json().dump(1) << "\n";
+  else invalid("unrecognised file format");
+  return 0;
+}
+
+cpu::LogicalGraph load_cpu_graph(const std::string& path) {
+  std::string text = read_file(path, 16 << 20);
+  if (path.size() > 12 && path.compare(path.size() - 12, 12, ".inferfabric") == 0) return cpu::from_dsl(text);
+  return cpu::LogicalGraph::from_json(Json::parse(text));
+}
+
+int demo() {
+  const char* src = R"(language inferfabric 1;
+model Residual { input x: tensor<f32>[2, 2]; const weight: tensor<f32>[2, 2] = [1, 0, 0, 1];
+  let projected = matmul(x, weight); let summed = add(projected, x); let output = relu(summed); yield output; }
+plan Cpu for Residual { target = cpu_f32_v1; })";
+  cpu::LogicalGraph lg = cpu::from_dsl(src);
+  cpu::PhysicalPlan plan = cpu::compile(lg);
+  cpu::verify(plan);
+  cpu::Executor ex(plan);
+  auto rep = ex.run({{"x", {1, -2, 3, 4}}});
+  std::cout << rep.to_json().dump(1) << "\n";
+  return 0;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  if (argc < 2) return usage();
+  std::string cmd = argv[1];
+  try {
+    if (cmd == "compile-token") return compile_token(argc, argv);
+    if (cmd == "explain" || cmd == "explain-model") return argc < 3 ? usage() : explain(argv[2]);
+    if (cmd == "model-source") {
+      if (argc < 3) return usage();
+      auto ex = lang::expand(lang::parse(read_file(argv[2], 1 << 20)));
+      for (auto& n : ex.nodes) {
+        std::cout << n.name << " = " << n.op << "(";
+        for (size_t i = 0; i < n.inputs.size(); ++i) std::cout << (i ? ", " : "") << n.inputs[i];
+        for (auto& kv : n.attrs) std::cout << ", " << kv.first << "=" << kv.second;
+        std::cout << ")\n";
+      }
+      return 0;
+    }
+    if (cmd == "synth-checkpoint") {
+      if (argc < 4) return usage();
+      uint64_t seed = 0;
+      for (int i = 4; i + 1 < argc; ++i)
+        if (std::string(argv[i]) == "--seed") seed = std::stoull(argv[i + 1]);
+      graph::Graph g = graph::compile_source(read_file(argv[2], 1 << 20));
+      program::Program p = program::lower(g);
+      auto need = init::required_tensors(p);
+      uint64_t bytes = 0;
+      for (auto& kv : need) {
+        uint64_t n = 2;
+        for (auto d : kv.second.second) n *= d;
+        bytes += n;
+      }
+      if (bytes > ((uint64_t)8 << 30)) fail(ErrorKind::Capacity, "refusing to synthesize more than 8 GiB of weights on the host");
+      interp::Weights::random(need, seed).save(argv[3]);
+      std::cout << "{\"tensors\": " << need.size() << ", \"bytes\": " << bytes << "}\n";
+      return 0;
+    }
+    if (cmd == "interpret") return interpret(argc, argv);
+    if (cmd == "inspect") return argc < 3 ? usage() : inspect(argv[2]);
+    if (cmd == "plan" || cmd == "plan-debug" || cmd == "tune-plan" || cmd == "explain-plan") {
+      if (argc < 3) return usage();
+      cpu::Options o;
+      o.debug_names = cmd == "plan-debug";
+      cpu::PhysicalPlan plan = cpu::compile(load_cpu_graph(argv[2]), o);
+      cpu::verify(plan);
+      if (argc >= 4) write_file_atomic(argv[3], cpu::encode_plan(plan));
+      std::cout << plan.to_json().dump(1) << "\n";
+      return 0;
+    }
+    if (cmd == "execute") {
+      if (argc < 4) return usage();
+      cpu::PhysicalPlan plan = cpu::compile(load_cpu_graph(argv[2]));
+      cpu::verify(plan);
+      cpu::Executor ex(plan);
+      Json inputs = Json::parse(read_file(argv[3], 16 << 20));
+      Json reports = Json::array();
+      auto run_one = [&](const Json& step) {
+        std::map<std::string, std::vector<float>> in;
+        for (auto& kv : step.as_object()) {
+          std::vector<float> v;
+          for (auto& x : kv.second.as_array()) v.push_back((float)x.as_double());
+          in[kv.first] = std::move(v);
+        }
+        reports.push(ex.run(in).to_json());
+      };
+      if (inputs.is_array()) for (auto& s : inputs.as_array()) run_one(s);
+      else run_one(inputs);
+      std::cout << reports.dump(1) << "\n";
+      return 0;
+    }
+    if (cmd == "compile") {
+      if (argc < 4) return usage();
+      rankplan::Spec spec = rankplan::Spec::from_json(Json::parse(read_file(argv[2], 16 << 20)));
+      rankplan::Artifact art = rankplan::compile(spec);
+      write_file_atomic(argv[3], rankplan::encode(art));
+      std::cout << art.to_json().dump(1) << "\n";
+      return 0;
+    }
+    if (cmd == "demo") return demo();
+    return usage();
+  } catch (const Error& e) {
+    std::fprintf(stderr, "ifab: %s\n", e.describe().c_str());
+    return 1;
+  } catch (const std::exception& e) {
+    std::fprintf(stderr, "ifab: %s\n", e.what());
+    return 1;
+  }
+}

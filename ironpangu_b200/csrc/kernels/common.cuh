@@ -57,6 +57,44 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch. Every kernel of the decode chain is launched with the
+// programmatic-stream-serialization attribute: it may start while its predecessor is still
+// running. `grid_dep_launch` lets the successor start; `grid_dep_wait` blocks until the predecessor
+// grid has completed and its writes are visible. Before the wait a kernel may only read data that
+// no kernel writes (weights) and must not write global memory; every kernel of the chain executes
+// the wait, so completion order stays transitive.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline int& pdl_enabled() {
+  static int on = 1;
+  return on;
+}
+
+// Launch `kernel` on `s`, with programmatic dependent launch unless it was switched off.
+template <typename... KArgs, typename... Args>
+inline int launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename KernelT>
+inline int opt_in_smem(KernelT kernel, size_t smem) {
+  if (smem <= 48 * 1024) return 0;
+  return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Cross-GPU flag protocol. Flags are 64-bit epochs in memory that every rank maps. A writer
 // publishes its data with plain stores, then one thread issues a system-scope release store of
 // the epoch; a reader spins (bounded) with system-scope acquire loads. The spin never exceeds

@@ -29,22 +29,25 @@ __global__ void __launch_bounds__(256) gemv_kernel(GemvParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* xs = reinterpret_cast<bf16*>(smem_raw);
   __shared__ float red[T * 33];
+  grid_dep_launch();
   const int t0 = blockIdx.y * T;
-  stage_x<T>(xs, p.x, p.ldx, t0, p.T, p.K, p.norm_w, p.eps, p.zero_centered != 0, red);
-
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = (blockIdx.x * 8 + warp) * R;
-  if (n0 >= p.N) return;
   if (p.mode == 0) {
     const bf16* rows[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) rows[r] = (n0 + r < p.N) ? p.w + (long)(n0 + r) * p.K : nullptr;
+    RowBatch<R> pf;
+    prefetch_rows<R>(rows, p.K, pf);
+    grid_dep_wait();
+    stage_x<T>(xs, p.x, p.ldx, t0, p.T, p.K, p.norm_w, p.eps, p.zero_centered != 0, red);
+    if (n0 >= p.N) return;
     float acc[R][T];
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int t = 0; t < T; ++t) acc[r][t] = 0.f;
-    warp_rows_dot<T, R>(rows, xs, p.K, acc);
+    warp_rows_dot<T, R>(rows, xs, p.K, acc, pf);
     warp_reduce_acc<T, R>(acc);
     if (lane == 0) {
 #pragma unroll
@@ -69,12 +72,17 @@ __global__ void __launch_bounds__(256) gemv_kernel(GemvParams p) {
       rows[r] = ok ? p.w + (long)(n0 + r) * p.K : nullptr;
       rows[R + r] = ok ? p.w + (long)(p.N + n0 + r) * p.K : nullptr;
     }
+    RowBatch<2 * R> pf;
+    prefetch_rows<2 * R>(rows, p.K, pf);
+    grid_dep_wait();
+    stage_x<T>(xs, p.x, p.ldx, t0, p.T, p.K, p.norm_w, p.eps, p.zero_centered != 0, red);
+    if (n0 >= p.N) return;
     float acc[2 * R][T];
 #pragma unroll
     for (int r = 0; r < 2 * R; ++r)
 #pragma unroll
       for (int t = 0; t < T; ++t) acc[r][t] = 0.f;
-    warp_rows_dot<T, 2 * R>(rows, xs, p.K, acc);
+    warp_rows_dot<T, 2 * R>(rows, xs, p.K, acc, pf);
     warp_reduce_acc<T, 2 * R>(acc);
     if (lane == 0) {
 #pragma unroll
@@ -95,13 +103,9 @@ template <int T, int R>
 int launch_gemv(const GemvParams& p, cudaStream_t s) {
   const size_t smem = (size_t)T * p.K * sizeof(bf16);
   auto k = gemv_kernel<T, R>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int rc = opt_in_smem(k, smem)) return rc;
   dim3 grid((p.N + 8 * R - 1) / (8 * R), (p.T + T - 1) / T);
-  k<<<grid, 256, smem, s>>>(p);
-  return (int)cudaGetLastError();
+  return launch_chain(k, grid, dim3(256), smem, s, p);
 }
 
 template <int T>
@@ -118,18 +122,9 @@ int dispatch_rows(const GemvParams& p, cudaStream_t s) {
 }
 
 // ----------------------------------------------------------------------------------------------
-// Row-parallel linear + one-shot all-reduce.
-// Every CTA owns a slab of `rows_per_cta` output columns for all T tokens. After the local dot
-// products the CTA pushes its f32 partial slab into the same slot of every peer's staging area
-// (slot index = my rank), publishes one flag per (peer, cta) with a system-scope release, waits
-// (bounded) for the flags of the other ranks' CTAs with the same index and sums the `world`
-// partials in rank order. Only same-index CTAs synchronise, so no grid-wide barrier is needed and
-// the transfer of early slabs overlaps the math of late ones.
-//
-// Calls are numbered by a device-resident counter (`seq`) that the last CTA of each launch
-// advances, so a captured CUDA graph replays with fresh epochs. Staging and flags are double
-// buffered on the parity of the call number: a rank can be at most one call ahead of its slowest
-// peer, because finishing call n needs every peer's push of call n.
+// Row-parallel linear + one-shot all-reduce (protocol in oneshot_ar.cuh).
+// Every CTA owns a slab of 8*R output columns for all T tokens; only same-index CTAs of the ranks
+// synchronise, so the transfer of early slabs overlaps the math of late ones.
 // ----------------------------------------------------------------------------------------------
 struct ArParams {
   GemvParams g;
@@ -147,23 +142,26 @@ __global__ void __launch_bounds__(256) gemv_allreduce_kernel(ArParams a) {
   __shared__ float red[T * 33];
   __shared__ float slab[T * 8 * R];
   __shared__ int timed_out;
-  if (threadIdx.x == 0) timed_out = 0;
-  stage_x<T>(xs, p.x, p.ldx, 0, p.T, p.K, p.norm_w, p.eps, p.zero_centered != 0, red);
-
+  grid_dep_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int RPC = 8 * R;
   const int nbase = blockIdx.x * RPC;
   const int n0 = nbase + warp * R;
-  {
-    const bf16* rows[R];
+  const bf16* rows[R];
 #pragma unroll
-    for (int r = 0; r < R; ++r) rows[r] = (n0 + r < p.N) ? p.w + (long)(n0 + r) * p.K : nullptr;
+  for (int r = 0; r < R; ++r) rows[r] = (n0 + r < p.N) ? p.w + (long)(n0 + r) * p.K : nullptr;
+  RowBatch<R> pf;
+  prefetch_rows<R>(rows, p.K, pf);
+  grid_dep_wait();
+  if (threadIdx.x == 0) timed_out = 0;
+  stage_x<T>(xs, p.x, p.ldx, 0, p.T, p.K, p.norm_w, p.eps, p.zero_centered != 0, red);
+  {
     float acc[R][T];
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int t = 0; t < T; ++t) acc[r][t] = 0.f;
-    warp_rows_dot<T, R>(rows, xs, p.K, acc);
+    warp_rows_dot<T, R>(rows, xs, p.K, acc, pf);
     warp_reduce_acc<T, R>(acc);
     if (lane == 0) {
 #pragma unroll
@@ -173,7 +171,6 @@ __global__ void __launch_bounds__(256) gemv_allreduce_kernel(ArParams a) {
     }
   }
   __syncthreads();
-
   oneshot_allreduce_slab<T, RPC>(slab, a.fv, a.seq, a.done, nbase, p.T, p.N, p.residual, p.ldr,
                                  reinterpret_cast<bf16*>(p.y), p.ldy, a.y_f32, &timed_out);
 }
@@ -182,13 +179,9 @@ template <int T, int R>
 int launch_ar(const ArParams& a, cudaStream_t s) {
   const size_t smem = (size_t)T * a.g.K * sizeof(bf16);
   auto k = gemv_allreduce_kernel<T, R>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int rc = opt_in_smem(k, smem)) return rc;
   dim3 grid((a.g.N + 8 * R - 1) / (8 * R));
-  k<<<grid, 256, smem, s>>>(a);
-  return (int)cudaGetLastError();
+  return launch_chain(k, grid, dim3(256), smem, s, a);
 }
 
 template <int T>

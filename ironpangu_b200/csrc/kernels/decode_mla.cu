@@ -53,6 +53,8 @@ __global__ void __launch_bounds__(128) mla_kv_write_kernel(const bf16* kv, long 
                                                            const int32_t* page_table, int max_pages, int page_tokens,
                                                            bf16* cache, int num_pages, int latent, int rope,
                                                            uint32_t* status) {
+  grid_dep_launch();
+  grid_dep_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   if (pos < 0) return;
@@ -95,35 +97,63 @@ __global__ void __launch_bounds__(128) mla_kv_write_kernel(const bf16* kv, long 
 }
 
 // ------------------------------------------------------------------------------------------------
-// grid (H, T), 256 threads: thread i owns latent columns 2i, 2i+1
+// grid (H, T, latent/128), 256 threads. A CTA produces 128 latent columns of one head: thread
+// (ds, cg) = (tid / 16, tid % 16) owns 8 columns [cg*8, cg*8+8) and the 8 q_nope elements
+// [ds*8, ds*8+8); its 8 weight loads (16 bytes each) are issued before the dependency wait, the 16
+// d-slices are then summed through shared memory. CTA z == 0 also rotates the rope part.
 __global__ void __launch_bounds__(256) mla_q_absorb_kernel(const bf16* q, long ldq, const bf16* w_kvb, float theta,
                                                            const int32_t* positions, bf16* q_lat, int H, int nope,
                                                            int rope, int latent, int vdim) {
-  const int h = blockIdx.x, t = blockIdx.y;
-  const int pos = positions[t];
   __shared__ float qs[256];
+  __shared__ float part[16][129];
+  grid_dep_launch();
+  const int h = blockIdx.x, t = blockIdx.y, cbase = blockIdx.z * 128;
+  const int cg = threadIdx.x & 15, ds = threadIdx.x >> 4;
+  const bf16* W = w_kvb + (long)h * (nope + vdim) * latent + cbase + cg * 8;
+  uint4 wv[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int d = ds * 8 + j;
+    wv[j] = d < nope ? ld_stream16(W + (long)d * latent) : make_uint4(0, 0, 0, 0);
+  }
+  grid_dep_wait();
+  const int pos = positions[t];
   const bf16* qrow = q + (long)t * ldq + (long)h * (nope + rope);
   for (int i = threadIdx.x; i < nope; i += blockDim.x) qs[i] = __bfloat162float(qrow[i]);
   __syncthreads();
-  bf16* out = q_lat + ((long)t * H + h) * (latent + rope);
-  const bf16* W = w_kvb + (long)h * (nope + vdim) * latent;
-  for (int c2 = threadIdx.x; c2 < latent / 2; c2 += blockDim.x) {
-    float a0 = 0.f, a1 = 0.f;
-#pragma unroll 8
-    for (int d = 0; d < nope; ++d) {
-      const float2 w = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(W + (long)d * latent + 2 * c2));
-      a0 = fmaf(qs[d], w.x, a0);
-      a1 = fmaf(qs[d], w.y, a1);
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int d0 = ds * 8; d0 < nope; d0 += 128) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int d = d0 + j;
+      if (d >= nope) break;
+      float wf[8];
+      unpack8(d0 == ds * 8 ? wv[j] : ld_stream16(W + (long)d * latent), wf);
+      const float qd = qs[d];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = fmaf(qd, wf[i], acc[i]);
     }
-    *reinterpret_cast<__nv_bfloat162*>(out + 2 * c2) = __floats2bfloat162_rn(a0, a1);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) part[ds][cg * 8 + i] = acc[i];
+  __syncthreads();
+  bf16* out = q_lat + ((long)t * H + h) * (latent + rope);
+  if (threadIdx.x < 128) {
+    float v = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) v += part[k][threadIdx.x];
+    out[cbase + threadIdx.x] = __float2bfloat16_rn(v);
   }
   const int half = rope / 2;
-  if ((int)threadIdx.x < half) {
-    float c, s;
-    rope_cos_sin(pos < 0 ? 0 : pos, threadIdx.x, rope, theta, &c, &s);
-    const float a = __bfloat162float(qrow[nope + threadIdx.x]), b = __bfloat162float(qrow[nope + threadIdx.x + half]);
-    out[latent + threadIdx.x] = __float2bfloat16_rn(a * c - b * s);
-    out[latent + threadIdx.x + half] = __float2bfloat16_rn(b * c + a * s);
+  if (blockIdx.z == 0 && (int)threadIdx.x >= 128 && (int)threadIdx.x - 128 < half) {
+    const int i = threadIdx.x - 128;
+    float c, sn;
+    rope_cos_sin(pos < 0 ? 0 : pos, i, rope, theta, &c, &sn);
+    const float a = __bfloat162float(qrow[nope + i]), b2 = __bfloat162float(qrow[nope + i + half]);
+    out[latent + i] = __float2bfloat16_rn(a * c - b2 * sn);
+    out[latent + i + half] = __float2bfloat16_rn(b2 * c + a * sn);
   }
 }
 
@@ -167,6 +197,8 @@ __global__ void __launch_bounds__(256) mla_split_kernel(AttnParams p) {
   float* sm_acc = reinterpret_cast<float*>(smem_raw);            // [8][HG][LATENT]
   float* sm_m = sm_acc + 8 * HG * LATENT;                        // [8][HG]
   float* sm_l = sm_m + 8 * HG;                                   // [8][HG]
+  grid_dep_launch();
+  grid_dep_wait();
   const int split = blockIdx.x, hg = blockIdx.y, t = blockIdx.z;
   const int pos = p.positions[t];
   if (pos < 0) return;
@@ -190,32 +222,59 @@ __global__ void __launch_bounds__(256) mla_split_kernel(AttnParams p) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[g][i] = 0.f;
   }
-  for (int k = k_begin + warp; k < k_end; k += 8) {
-    const bf16* row;
-    if (k < p.n_sinks) {
-      row = p.sinks + (long)k * ROW;
-    } else {
-      const long r = cache_row_of(first + (k - p.n_sinks), slot, p.page_table, p.max_pages, p.page_tokens, p.num_pages);
-      if (r < 0) {
-        if (lane == 0 && p.status) atomicOr(p.status, IFAB_STATUS_BAD_INDEX);
-        continue;
+  // Each warp owns keys k_begin + warp, +8, ...; the rows of a batch of KB keys are all requested
+  // before the first score is computed, so their latencies overlap.
+  constexpr int KB = 4;
+  for (int kb = k_begin + warp; kb < k_end; kb += 8 * KB) {
+    uint4 ra[KB], rb[KB];
+    __nv_bfloat162 rr[KB];
+    bool ok[KB];
+#pragma unroll
+    for (int j = 0; j < KB; ++j) {
+      const int k = kb + 8 * j;
+      ok[j] = k < k_end;
+      const bf16* row = nullptr;
+      if (ok[j]) {
+        if (k < p.n_sinks) {
+          row = p.sinks + (long)k * ROW;
+        } else {
+          const long r = cache_row_of(first + (k - p.n_sinks), slot, p.page_table, p.max_pages, p.page_tokens, p.num_pages);
+          if (r < 0) {
+            if (lane == 0 && p.status) atomicOr(p.status, IFAB_STATUS_BAD_INDEX);
+            ok[j] = false;
+          } else {
+            row = p.cache + r * ROW;
+          }
+        }
       }
-      row = p.cache + r * ROW;
+      if (ok[j]) {
+        ra[j] = *reinterpret_cast<const uint4*>(row + lane * 8);
+        rb[j] = *reinterpret_cast<const uint4*>(row + 256 + lane * 8);
+        rr[j] = *reinterpret_cast<const __nv_bfloat162*>(row + LATENT + lane * 2);
+      }
     }
-    RowFrag kf;
-    load_row(row, lane, &kf);
 #pragma unroll
-    for (int g = 0; g < HG; ++g) {
-      float s = qf[g].rp[0] * kf.rp[0] + qf[g].rp[1] * kf.rp[1];
+    for (int j = 0; j < KB; ++j) {
+      if (!ok[j]) continue;
+      RowFrag kf;
+      unpack8(ra[j], kf.lat);
+      unpack8(rb[j], kf.lat + 8);
+      const float2 r2 = __bfloat1622float2(rr[j]);
+      kf.rp[0] = r2.x;
+      kf.rp[1] = r2.y;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) s = fmaf(qf[g].lat[i], kf.lat[i], s);
-      s = warp_sum(s) * p.scale;
-      const float mn = fmaxf(m[g], s);
-      const float corr = __expf(m[g] - mn), pe = __expf(s - mn);
-      l[g] = l[g] * corr + pe;
+      for (int g = 0; g < HG; ++g) {
+        float s = qf[g].rp[0] * kf.rp[0] + qf[g].rp[1] * kf.rp[1];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) acc[g][i] = acc[g][i] * corr + pe * kf.lat[i];
-      m[g] = mn;
+        for (int i = 0; i < 16; ++i) s = fmaf(qf[g].lat[i], kf.lat[i], s);
+        s = warp_sum(s) * p.scale;
+        const float mn = fmaxf(m[g], s);
+        const float corr = __expf(m[g] - mn), pe = __expf(s - mn);
+        l[g] = l[g] * corr + pe;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[g][i] = acc[g][i] * corr + pe * kf.lat[i];
+        m[g] = mn;
+      }
     }
   }
 #pragma unroll
@@ -260,9 +319,18 @@ __global__ void __launch_bounds__(256) mla_merge_vup_kernel(AttnParams p, const 
   __shared__ __align__(16) bf16 os[LATENT];
   __shared__ float wgt[64];
   __shared__ float Ls;
+  grid_dep_launch();
   const int h = blockIdx.x, t = blockIdx.y;
-  const int pos = p.positions[t];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int RV = 8;
+  const bf16* W = w_kvb + ((long)h * (nope + vdim) + nope) * LATENT;
+  const bf16* rows[RV];
+#pragma unroll
+  for (int r = 0; r < RV; ++r) rows[r] = (warp * RV + r < vdim) ? W + (long)(warp * RV + r) * LATENT : nullptr;
+  RowBatch<RV> pf;
+  prefetch_rows<RV>(rows, LATENT, pf);
+  grid_dep_wait();
+  const int pos = p.positions[t];
   if (pos < 0) return;
   int first, nctx;
   visible_range(pos, p.window, &first, &nctx);
@@ -290,17 +358,20 @@ __global__ void __launch_bounds__(256) mla_merge_vup_kernel(AttnParams p, const 
     os[c] = __float2bfloat16_rn(v * invL);
   }
   __syncthreads();
-  const bf16* W = w_kvb + ((long)h * (nope + vdim) + nope) * LATENT;
-  for (int j0 = warp * 4; j0 < vdim; j0 += 32) {
-    const bf16* rows[4];
+  for (int j0 = warp * RV, it = 0; j0 < vdim; j0 += 8 * RV, ++it) {
+    if (it > 0) {
 #pragma unroll
-    for (int r = 0; r < 4; ++r) rows[r] = (j0 + r < vdim) ? W + (long)(j0 + r) * LATENT : nullptr;
-    float acc[4][1] = {{0.f}, {0.f}, {0.f}, {0.f}};
-    warp_rows_dot<1, 4>(rows, os, LATENT, acc);
-    warp_reduce_acc<1, 4>(acc);
+      for (int r = 0; r < RV; ++r) rows[r] = (j0 + r < vdim) ? W + (long)(j0 + r) * LATENT : nullptr;
+      prefetch_rows<RV>(rows, LATENT, pf);
+    }
+    float acc[RV][1];
+#pragma unroll
+    for (int r = 0; r < RV; ++r) acc[r][0] = 0.f;
+    warp_rows_dot<1, RV>(rows, os, LATENT, acc, pf);
+    warp_reduce_acc<1, RV>(acc);
     if (lane == 0) {
 #pragma unroll
-      for (int r = 0; r < 4; ++r)
+      for (int r = 0; r < RV; ++r)
         if (j0 + r < vdim) out[(long)t * ldo + (long)h * vdim + j0 + r] = __float2bfloat16_rn(acc[r][0]);
     }
   }
@@ -310,13 +381,9 @@ template <int HG>
 int launch_split(const AttnParams& p, cudaStream_t s) {
   const size_t smem = (size_t)(8 * HG * LATENT + 16 * HG) * sizeof(float);
   auto k = mla_split_kernel<HG>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int rc = opt_in_smem(k, smem)) return rc;
   dim3 grid(p.max_splits, p.H / HG, p.T);
-  k<<<grid, 256, smem, s>>>(p);
-  return (int)cudaGetLastError();
+  return launch_chain(k, grid, dim3(256), smem, s, p);
 }
 
 }  // namespace
@@ -326,19 +393,17 @@ extern "C" int ifab_mla_kv_write(const void* kv, long ldkv, const void* norm_w, 
                                  int max_pages, int page_tokens, void* cache, int num_pages, int T, int latent, int rope,
                                  uint32_t* status, void* stream) {
   if (latent % 8 != 0 || latent > 1024 || rope % 2 != 0 || rope > 256 || ldkv % 8 != 0) return -1;
-  mla_kv_write_kernel<<<T, 128, 0, (cudaStream_t)stream>>>((const bf16*)kv, ldkv, (const bf16*)norm_w, eps, theta,
-                                                          positions, slots, page_table, max_pages, page_tokens,
-                                                          (bf16*)cache, num_pages, latent, rope, status);
-  return (int)cudaGetLastError();
+  return launch_chain(mla_kv_write_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream, (const bf16*)kv, ldkv,
+                      (const bf16*)norm_w, eps, theta, positions, slots, page_table, max_pages, page_tokens,
+                      (bf16*)cache, num_pages, latent, rope, status);
 }
 
 extern "C" int ifab_mla_q_absorb(const void* q, long ldq, const void* w_kvb, float theta, const int32_t* positions,
                                  void* q_lat, int T, int H, int nope, int rope, int latent, int vdim, void* stream) {
-  if (nope > 256 || latent % 2 != 0 || rope % 2 != 0 || rope > 512) return -1;
-  dim3 grid(H, T);
-  mla_q_absorb_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)q, ldq, (const bf16*)w_kvb, theta, positions,
-                                                             (bf16*)q_lat, H, nope, rope, latent, vdim);
-  return (int)cudaGetLastError();
+  if (nope > 256 || nope % 8 != 0 || latent % 128 != 0 || rope % 2 != 0 || rope > 256) return -1;
+  dim3 grid(H, T, latent / 128);
+  return launch_chain(mla_q_absorb_kernel, grid, dim3(256), 0, (cudaStream_t)stream, (const bf16*)q, ldq,
+                      (const bf16*)w_kvb, theta, positions, (bf16*)q_lat, H, nope, rope, latent, vdim);
 }
 
 extern "C" int ifab_mla_decode_attention(const void* q_lat, const void* cache, const int32_t* positions,
@@ -359,6 +424,5 @@ extern "C" int ifab_mla_decode_attention(const void* q_lat, const void* cache, c
   else rc = launch_split<1>(p, s);
   if (rc) return rc;
   dim3 grid(H, T);
-  mla_merge_vup_kernel<<<grid, 256, 0, s>>>(p, (const bf16*)w_kvb, nope, vdim, (bf16*)out, ldo);
-  return (int)cudaGetLastError();
+  return launch_chain(mla_merge_vup_kernel, grid, dim3(256), 0, s, p, (const bf16*)w_kvb, nope, vdim, (bf16*)out, ldo);
 }

@@ -2,8 +2,9 @@
 // every rank, each rank evaluates the routes that land on its experts, partial outputs are summed
 // by the fused all-reduce of the down projection).
 //
-//   router_topk_kernel        f32 router GEMV (+RMSNorm prologue); the last CTA to finish turns the
-//                             logits into top-k ids and weights (softmax top-k or sigmoid+bias)
+//   router_topk_kernel        f32 router projection, one CTA per expert (+RMSNorm prologue); the
+//                             last CTA to finish turns the logits into top-k ids and weights
+//                             (softmax top-k or sigmoid+bias)
 //   moe_gate_up_kernel        one CTA column per route: gate/up rows of the routed expert, SwiGLU
 //   moe_down_allreduce_kernel score-weighted sum of the local experts' down projections (+ the
 //                             tensor-parallel shard of the shared expert) + one-shot all-reduce
@@ -31,34 +32,55 @@ struct RouterParams {
   uint32_t* ticket;
 };
 
+// grid = E CTAs of 256 threads; thread i owns float4 columns i, i+256, ... of its expert's row
 template <int T>
 __global__ void __launch_bounds__(256) router_topk_kernel(RouterParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* xs = reinterpret_cast<bf16*>(smem_raw);
   __shared__ float red[T * 33];
+  __shared__ float part[8][T];
   __shared__ int is_last;
-  stage_x<T>(xs, p.x, p.ldx, 0, p.T, p.D, p.norm_w, p.eps, false, red);
+  grid_dep_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int e = blockIdx.x * 8 + warp;
-  if (e < p.E) {
-    float acc[T];
+  const int e = blockIdx.x;
+  const float4* wr = reinterpret_cast<const float4*>(p.w + (long)e * p.D);
+  const int quads = p.D >> 2;
+  constexpr int PFQ = 4;
+  float4 pf[PFQ];
 #pragma unroll
-    for (int t = 0; t < T; ++t) acc[t] = 0.f;
-    const float* wr = p.w + (long)e * p.D;
-    for (int c = lane; c < p.D / 4; c += 32) {
-      const float4 wv = __ldg(reinterpret_cast<const float4*>(wr) + c);
+  for (int j = 0; j < PFQ; ++j) {
+    const int c = threadIdx.x + j * 256;
+    pf[j] = c < quads ? __ldg(wr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  grid_dep_wait();
+  stage_x<T>(xs, p.x, p.ldx, 0, p.T, p.D, p.norm_w, p.eps, false, red);
+  float acc[T];
 #pragma unroll
-      for (int t = 0; t < T; ++t) {
-        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(xs + t * p.D + c * 4);
-        const float2 a = __bfloat1622float2(xp[0]), b = __bfloat1622float2(xp[1]);
-        acc[t] += wv.x * a.x + wv.y * a.y + wv.z * b.x + wv.w * b.y;
-      }
-    }
+  for (int t = 0; t < T; ++t) acc[t] = 0.f;
+  auto fma_quad = [&](const float4& wv, int c) {
 #pragma unroll
     for (int t = 0; t < T; ++t) {
-      const float v = warp_sum(acc[t]);
-      if (lane == 0 && t < p.T) p.logits[(long)t * p.E + e] = v;
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(xs + t * p.D + c * 4);
+      const float2 a = __bfloat1622float2(xp[0]), b = __bfloat1622float2(xp[1]);
+      acc[t] += wv.x * a.x + wv.y * a.y + wv.z * b.x + wv.w * b.y;
     }
+  };
+#pragma unroll
+  for (int j = 0; j < PFQ; ++j) {
+    const int c = threadIdx.x + j * 256;
+    if (c < quads) fma_quad(pf[j], c);
+  }
+  for (int c = threadIdx.x + PFQ * 256; c < quads; c += 256) fma_quad(__ldg(wr + c), c);
+#pragma unroll
+  for (int t = 0; t < T; ++t) {
+    const float v = warp_sum(acc[t]);
+    if (lane == 0) part[warp][t] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < T && (int)threadIdx.x < p.T) {
+    float v = 0.f;
+    for (int w = 0; w < 8; ++w) v += part[w][threadIdx.x];
+    p.logits[(long)threadIdx.x * p.E + e] = v;
   }
   __threadfence();
   __syncthreads();
@@ -150,40 +172,55 @@ struct GateUpParams {
 };
 
 // grid: (ceil(F/16), T*topk + T). Column y < T*topk is route (t, k); columns after that are the shared
-// expert of token t. Routes that belong to other ranks exit at once.
+// expert of token t. Routes that belong to other ranks exit at once (after the dependency wait).
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(GateUpParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* xs = reinterpret_cast<bf16*>(smem_raw);
   __shared__ float red[33];
+  grid_dep_launch();
   const int routes = p.T * p.topk;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j0 = (blockIdx.x * 8 + warp) * 2;
+  const bool shared_col = (int)blockIdx.y >= routes;
+  const bf16* rows[4] = {nullptr, nullptr, nullptr, nullptr};
+  RowBatch<4> pf;
   int t, slot, Fcur;
   const bf16* W;
-  if ((int)blockIdx.y < routes) {
+  if (shared_col) {
+    // the shared expert does not depend on the routes: its weight rows are prefetched before the wait
+    t = blockIdx.y - routes;
+    slot = p.topk;
+    W = p.w_sgu;
+    Fcur = W ? p.Fs : 0;
+    if (j0 < Fcur) {
+      rows[0] = W + (size_t)j0 * p.D;
+      rows[1] = (j0 + 1 < Fcur) ? W + (size_t)(j0 + 1) * p.D : nullptr;
+      rows[2] = W + (size_t)(Fcur + j0) * p.D;
+      rows[3] = (j0 + 1 < Fcur) ? W + (size_t)(Fcur + j0 + 1) * p.D : nullptr;
+    }
+    prefetch_rows<4>(rows, p.D, pf);
+    grid_dep_wait();
+  } else {
+    grid_dep_wait();
     t = blockIdx.y / p.topk;
     slot = blockIdx.y % p.topk;
     const int e = p.ids[blockIdx.y];
     if (e < p.e0 || e >= p.e0 + p.e_local) return;
     W = p.w_gu + (size_t)(e - p.e0) * 2 * p.F * p.D;
     Fcur = p.F;
-  } else {
-    t = blockIdx.y - routes;
-    slot = p.topk;
-    W = p.w_sgu;
-    Fcur = p.Fs;
-    if (W == nullptr) return;
+    if (j0 < Fcur) {
+      rows[0] = W + (size_t)j0 * p.D;
+      rows[1] = (j0 + 1 < Fcur) ? W + (size_t)(j0 + 1) * p.D : nullptr;
+      rows[2] = W + (size_t)(Fcur + j0) * p.D;
+      rows[3] = (j0 + 1 < Fcur) ? W + (size_t)(Fcur + j0 + 1) * p.D : nullptr;
+    }
+    prefetch_rows<4>(rows, p.D, pf);
   }
   if ((int)blockIdx.x * 16 >= Fcur) return;
   stage_x<1>(xs, p.x, p.ldx, t, p.T, p.D, p.norm_w, p.eps, false, red);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int j0 = (blockIdx.x * 8 + warp) * 2;
   if (j0 >= Fcur) return;
-  const bf16* rows[4];
-  rows[0] = W + (size_t)j0 * p.D;
-  rows[1] = (j0 + 1 < Fcur) ? W + (size_t)(j0 + 1) * p.D : nullptr;
-  rows[2] = W + (size_t)(Fcur + j0) * p.D;
-  rows[3] = (j0 + 1 < Fcur) ? W + (size_t)(Fcur + j0 + 1) * p.D : nullptr;
   float acc[4][1] = {{0.f}, {0.f}, {0.f}, {0.f}};
-  warp_rows_dot<1, 4>(rows, xs, p.D, acc);
+  warp_rows_dot<1, 4>(rows, xs, p.D, acc, pf);
   warp_reduce_acc<1, 4>(acc);
   if (lane == 0) {
     bf16* out = p.act + ((size_t)t * (p.topk + 1) + slot) * p.F;
@@ -201,65 +238,113 @@ struct DownParams {
   FabricView fv; uint64_t* seq; uint32_t* done;
 };
 
+// Every warp owns R output columns. The K dimension of all local routes of a token is flattened into
+// one chunk space (route s contributes F/8 chunks, the shared shard Fs/8), so a lane keeps 16 loads
+// in flight across route boundaries instead of draining per expert:
+//   y[t][n] = sum_s wgt_s * dot(W_s[n, :], act[t][s][:])
 template <int T, int R>
 __global__ void __launch_bounds__(256) moe_down_allreduce_kernel(DownParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* as = reinterpret_cast<bf16*>(smem_raw);   // one activation row [F]
+  bf16* as = reinterpret_cast<bf16*>(smem_raw);   // [(topk+1)][F] activation rows of the current token
   constexpr int RPC = 8 * R;
+  constexpr int MAXS = MAX_TOPK + 1;
   __shared__ float slab[T * RPC];
   __shared__ int timed_out;
+  __shared__ const bf16* s_w[MAXS];   // weight base of local route i
+  __shared__ float s_g[MAXS];         // its score
+  __shared__ int s_k[MAXS];           // its K extent
+  __shared__ int s_cbeg[MAXS + 1];    // first flattened chunk of route i
+  __shared__ int s_slot[MAXS];
+  __shared__ int s_n;
+  grid_dep_launch();
+  grid_dep_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nbase = blockIdx.x * RPC, n0 = nbase + warp * R;
-  for (int i = threadIdx.x; i < T * RPC; i += blockDim.x) slab[i] = 0.f;
   if (threadIdx.x == 0) timed_out = 0;
-  float total[R][T];
-#pragma unroll
-  for (int r = 0; r < R; ++r)
-#pragma unroll
-    for (int t = 0; t < T; ++t) total[r][t] = 0.f;
-
-#pragma unroll
   for (int t = 0; t < T; ++t) {
-    if (t >= p.T) break;
-    for (int slot = 0; slot <= p.topk; ++slot) {
-      const bf16* W;
-      int Fcur;
-      float wgt;
-      if (slot < p.topk) {
-        const int e = p.ids[t * p.topk + slot];
-        if (e < p.e0 || e >= p.e0 + p.e_local) continue;   // uniform across the block
-        W = p.w_down + (size_t)(e - p.e0) * p.D * p.F;
-        Fcur = p.F;
-        wgt = p.wts[t * p.topk + slot];
-      } else {
-        if (p.w_sdown == nullptr) continue;
-        W = p.w_sdown;
-        Fcur = p.Fs;
-        wgt = 1.f;
+    if (t < p.T) {
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int n = 0, c = 0;
+        for (int slot = 0; slot <= p.topk; ++slot) {
+          if (slot < p.topk) {
+            const int e = p.ids[t * p.topk + slot];
+            if (e < p.e0 || e >= p.e0 + p.e_local) continue;
+            s_w[n] = p.w_down + (size_t)(e - p.e0) * p.D * p.F;
+            s_g[n] = p.wts[t * p.topk + slot];
+            s_k[n] = p.F;
+          } else {
+            if (p.w_sdown == nullptr) continue;
+            s_w[n] = p.w_sdown;
+            s_g[n] = 1.f;
+            s_k[n] = p.Fs;
+          }
+          s_slot[n] = slot;
+          s_cbeg[n] = c;
+          c += s_k[n] >> 3;
+          ++n;
+        }
+        s_cbeg[n] = c;
+        s_n = n;
       }
       __syncthreads();
-      const bf16* arow = p.act + ((size_t)t * (p.topk + 1) + slot) * p.F;
-      for (int c = threadIdx.x; c < (Fcur >> 3); c += blockDim.x)
-        *reinterpret_cast<uint4*>(as + c * 8) = *reinterpret_cast<const uint4*>(arow + c * 8);
+      const int n_routes = s_n;
+      for (int i = 0; i < n_routes; ++i) {
+        const bf16* arow = p.act + ((size_t)t * (p.topk + 1) + s_slot[i]) * p.F;
+        for (int c = threadIdx.x; c < (s_k[i] >> 3); c += blockDim.x)
+          *reinterpret_cast<uint4*>(as + (size_t)i * p.F + c * 8) = *reinterpret_cast<const uint4*>(arow + c * 8);
+      }
       __syncthreads();
-      const bf16* rows[R];
+      float total[R];
 #pragma unroll
-      for (int r = 0; r < R; ++r) rows[r] = (n0 + r < p.D) ? W + (size_t)(n0 + r) * Fcur : nullptr;
-      float acc[R][1];
+      for (int r = 0; r < R; ++r) total[r] = 0.f;
+      const int chunks = s_cbeg[n_routes];
+      // all routed experts span cpr chunks; only a trailing shared-expert shard may differ
+      const int cpr = p.F >> 3;
+      const int n_exp_chunks = (n_routes > 0 && s_slot[n_routes - 1] == p.topk) ? s_cbeg[n_routes - 1] : chunks;
+      constexpr int U = 16 / R;
+      for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
+        uint4 wv[U][R];
+        int route[U], cc[U];
 #pragma unroll
-      for (int r = 0; r < R; ++r) acc[r][0] = 0.f;
-      warp_rows_dot<1, R>(rows, as, Fcur, acc);
-      warp_reduce_acc<1, R>(acc);
+        for (int u = 0; u < U; ++u) {
+          const int c = c0 + u * 32;
+          const int i = c < n_exp_chunks ? c / cpr : n_routes - 1;
+          route[u] = i;
+          cc[u] = c < n_exp_chunks ? c - i * cpr : c - n_exp_chunks;
+          if (c < chunks) {
+            const bf16* wb = s_w[i] + (size_t)n0 * s_k[i] + cc[u] * 8;
 #pragma unroll
-      for (int r = 0; r < R; ++r) total[r][t] += (slot < p.topk) ? wgt * bf16_round(acc[r][0]) : acc[r][0];
+            for (int r = 0; r < R; ++r)
+              wv[u][r] = (n0 + r < p.D) ? ld_stream16(wb + (size_t)r * s_k[i]) : make_uint4(0, 0, 0, 0);
+          } else {
+#pragma unroll
+            for (int r = 0; r < R; ++r) wv[u][r] = make_uint4(0, 0, 0, 0);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (c0 + u * 32 < chunks) {
+            float xf[8];
+            unpack8(*reinterpret_cast<const uint4*>(as + (size_t)route[u] * p.F + cc[u] * 8), xf);
+            const float g = s_g[route[u]];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              float wf[8], d = 0.f;
+              unpack8(wv[u][r], wf);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) d = fmaf(wf[k], xf[k], d);
+              total[r] = fmaf(g, d, total[r]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float v = warp_sum(total[r]);
+        if (lane == 0) slab[t * RPC + warp * R + r] = v;
+      }
     }
-  }
-  __syncthreads();
-  if (lane == 0) {
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-      for (int t = 0; t < T; ++t) slab[t * RPC + warp * R + r] = total[r][t];
   }
   __syncthreads();
   oneshot_allreduce_slab<T, RPC>(slab, p.fv, p.seq, p.done, nbase, p.T, p.D, p.residual, p.ldr, p.y, p.ldy, nullptr,
@@ -268,10 +353,11 @@ __global__ void __launch_bounds__(256) moe_down_allreduce_kernel(DownParams p) {
 
 template <int T, int R>
 int launch_down(const DownParams& p, cudaStream_t s) {
-  const size_t smem = (size_t)(p.F > p.Fs ? p.F : p.Fs) * sizeof(bf16);
+  const size_t smem = (size_t)(p.topk + 1) * p.F * sizeof(bf16);
+  auto k = moe_down_allreduce_kernel<T, R>;
+  if (int rc = opt_in_smem(k, smem)) return rc;
   dim3 grid((p.D + 8 * R - 1) / (8 * R));
-  moe_down_allreduce_kernel<T, R><<<grid, 256, smem, s>>>(p);
-  return (int)cudaGetLastError();
+  return launch_chain(k, grid, dim3(256), smem, s, p);
 }
 template <int T>
 int dispatch_down(const DownParams& p, cudaStream_t s) {
@@ -299,19 +385,23 @@ __global__ void __launch_bounds__(256) lm_head_argmax_kernel(HeadParams p) {
   __shared__ float bestv[8][T];
   __shared__ int besti[8][T];
   __shared__ int is_last;
-  stage_x<T>(xs, p.x, p.ldx, 0, p.T, p.K, p.norm_w, p.eps, false, red);
+  grid_dep_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = (blockIdx.x * 8 + warp) * R;
-  {
-    const bf16* rows[R];
+  const bf16* rows[R];
 #pragma unroll
-    for (int r = 0; r < R; ++r) rows[r] = (n0 + r < p.V) ? p.w + (size_t)(n0 + r) * p.K : nullptr;
+  for (int r = 0; r < R; ++r) rows[r] = (n0 + r < p.V) ? p.w + (size_t)(n0 + r) * p.K : nullptr;
+  RowBatch<R> pf;
+  prefetch_rows<R>(rows, p.K, pf);
+  grid_dep_wait();
+  stage_x<T>(xs, p.x, p.ldx, 0, p.T, p.K, p.norm_w, p.eps, false, red);
+  {
     float acc[R][T];
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int t = 0; t < T; ++t) acc[r][t] = 0.f;
-    warp_rows_dot<T, R>(rows, xs, p.K, acc);
+    warp_rows_dot<T, R>(rows, xs, p.K, acc, pf);
     warp_reduce_acc<T, R>(acc);
     if (lane == 0) {
 #pragma unroll
@@ -413,14 +503,10 @@ template <int T, int R>
 int launch_head(const HeadParams& p, uint64_t partial_bytes, cudaStream_t s) {
   const size_t smem = (size_t)T * p.K * sizeof(bf16);
   auto k = lm_head_argmax_kernel<T, R>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int rc = opt_in_smem(k, smem)) return rc;
   dim3 grid((p.V + 8 * R - 1) / (8 * R));
   if ((uint64_t)grid.x * T * sizeof(float2) > partial_bytes) return -5;
-  k<<<grid, 256, smem, s>>>(p);
-  return (int)cudaGetLastError();
+  return launch_chain(k, grid, dim3(256), smem, s, p);
 }
 
 }  // namespace
@@ -432,16 +518,15 @@ extern "C" int ifab_router_topk(const void* x, long ldx, const void* norm_w, flo
   RouterParams p{(const bf16*)x, ldx, (const bf16*)norm_w, eps, w_router, bias, logits, ids, wts,
                  T, D, E, topk, scoring, renorm, scale, ticket};
   cudaStream_t s = (cudaStream_t)stream;
-  dim3 grid((E + 7) / 8);
-#define IFAB_ROUTER(TT)                                                                                   \
-  {                                                                                                       \
-    const size_t smem = (size_t)TT * D * sizeof(bf16);                                                    \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(router_topk_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    router_topk_kernel<TT><<<grid, 256, smem, s>>>(p);                                                    \
+  dim3 grid(E);
+#define IFAB_ROUTER(TT)                                                      \
+  {                                                                          \
+    const size_t smem = (size_t)TT * D * sizeof(bf16);                       \
+    if (int rc = opt_in_smem(router_topk_kernel<TT>, smem)) return rc;       \
+    return launch_chain(router_topk_kernel<TT>, grid, dim3(256), smem, s, p); \
   }
   if (T <= 1) IFAB_ROUTER(1) else if (T <= 2) IFAB_ROUTER(2) else if (T <= 4) IFAB_ROUTER(4) else IFAB_ROUTER(8)
 #undef IFAB_ROUTER
-  return (int)cudaGetLastError();
 }
 
 extern "C" int ifab_moe_gate_up_decode(const void* x, long ldx, const void* norm_w, float eps, const int32_t* ids, int T,
@@ -452,16 +537,15 @@ extern "C" int ifab_moe_gate_up_decode(const void* x, long ldx, const void* norm
                  (const bf16*)w_gu, (const bf16*)w_shared_gu, Fs, (bf16*)act};
   dim3 grid((F + 15) / 16, T * topk + T);
   const size_t smem = (size_t)D * sizeof(bf16);
-  if (smem > 48 * 1024) cudaFuncSetAttribute(moe_gate_up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  moe_gate_up_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(p);
-  return (int)cudaGetLastError();
+  if (int rc = opt_in_smem(moe_gate_up_kernel, smem)) return rc;
+  return launch_chain(moe_gate_up_kernel, grid, dim3(256), smem, (cudaStream_t)stream, p);
 }
 
 extern "C" int ifab_moe_down_allreduce_decode(const void* act, const int32_t* ids, const float* wts, int T, int D, int F,
                                               int topk, int e0, int e_local, const void* w_down,
                                               const void* w_shared_down, int Fs, const void* residual, long ldr,
                                               void* y, long ldy, const IfabFabric* fab, void* stream) {
-  if (T < 1 || T > 8 || F % 8 != 0 || Fs % 8 != 0) return -1;
+  if (T < 1 || T > 8 || F % 8 != 0 || Fs % 8 != 0 || topk > MAX_TOPK || Fs > F) return -1;
   DownParams p;
   p.act = (const bf16*)act; p.ids = ids; p.wts = wts;
   p.T = T; p.D = D; p.F = F; p.topk = topk; p.e0 = e0; p.e_local = e_local;

@@ -2,13 +2,44 @@
 //
 // Decode-time linears have M = 1..8 tokens and are bound by the HBM stream of the weight matrix,
 // so the design goal is bytes in flight, not tensor-core issue: every warp owns R weight rows,
-// every lane issues 16-byte streaming loads that bypass L1, and U*R loads are outstanding per lane
+// every lane issues 16-byte streaming loads that bypass L1, and 16 loads are outstanding per lane
 // before the first FMA. Activations sit in shared memory as bf16 (optionally RMS-normalised while
 // they are staged) and are re-read conflict-free by consecutive lanes.
+//
+// Weights never depend on the previous kernel, activations do. Every kernel is launched with
+// programmatic dependent launch: it first releases its own dependents, issues the first batch of
+// weight loads into registers (`prefetch_rows`), and only then waits for the producer of its
+// activations (`grid_dep_wait`). The weight stream of kernel n+1 therefore overlaps the tail,
+// drain and launch latency of kernel n.
 #pragma once
 #include "common.cuh"
 
 namespace ifab {
+
+// number of 16-byte chunks a lane keeps in flight per batch, split over the R rows of its warp
+template <int R>
+struct Pf {
+  static constexpr int U = 16 / R;
+};
+
+template <int R>
+struct RowBatch {
+  uint4 v[Pf<R>::U][R];
+};
+
+// issue the loads of the first batch (chunks lane, lane+32, ...) of R rows; rows may be nullptr
+template <int R>
+__device__ __forceinline__ void prefetch_rows(const bf16* const (&wrow)[R], int K, RowBatch<R>& pf) {
+  const int lane = threadIdx.x & 31;
+  const int chunks = K >> 3;
+#pragma unroll
+  for (int u = 0; u < Pf<R>::U; ++u) {
+    const int c = lane + u * 32;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      pf.v[u][r] = (c < chunks && wrow[r] != nullptr) ? ld_stream16(wrow[r] + c * 8) : make_uint4(0, 0, 0, 0);
+  }
+}
 
 // Stage T rows of x (bf16, K columns, row stride ldx) into shared memory. When norm_w != nullptr the
 // rows are RMS-normalised on the way: y = bf16(x * rsqrt(mean(x^2) + eps) * (w or 1+w)).
@@ -62,21 +93,23 @@ __device__ __forceinline__ void stage_x(bf16* xs, const bf16* __restrict__ x, lo
   __syncthreads();
 }
 
-// acc[r][t] += dot(w_row[r][0..K), xs[t][0..K)) over this lane's share of K. Rows whose pointer is
+// acc[r][t] += dot(w_row[r][0..K), xs[t][0..K)) over this lane's share of K. `pf` holds the first
+// batch (already loaded by prefetch_rows); later batches are loaded here. Rows whose pointer is
 // nullptr are skipped. Caller reduces across the warp afterwards.
 template <int T, int R>
-__device__ __forceinline__ void warp_rows_dot(const bf16* const (&wrow)[R], const bf16* xs, int K, float (&acc)[R][T]) {
+__device__ __forceinline__ void warp_rows_dot(const bf16* const (&wrow)[R], const bf16* xs, int K, float (&acc)[R][T],
+                                              RowBatch<R>& pf) {
   const int lane = threadIdx.x & 31;
   const int chunks = K >> 3;
-  constexpr int U = (R >= 4) ? 2 : (R == 2 ? 4 : 8);
+  constexpr int U = Pf<R>::U;
   for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
-    uint4 wv[U][R];
+    if (c0 != lane) {
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int c = c0 + u * 32;
+      for (int u = 0; u < U; ++u) {
+        const int c = c0 + u * 32;
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        wv[u][r] = (c < chunks && wrow[r] != nullptr) ? ld_stream16(wrow[r] + c * 8) : make_uint4(0, 0, 0, 0);
+        for (int r = 0; r < R; ++r)
+          pf.v[u][r] = (c < chunks && wrow[r] != nullptr) ? ld_stream16(wrow[r] + c * 8) : make_uint4(0, 0, 0, 0);
       }
     }
 #pragma unroll
@@ -89,7 +122,7 @@ __device__ __forceinline__ void warp_rows_dot(const bf16* const (&wrow)[R], cons
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           float wf[8];
-          unpack8(wv[u][r], wf);
+          unpack8(pf.v[u][r], wf);
 #pragma unroll
           for (int t = 0; t < T; ++t) {
 #pragma unroll
@@ -99,6 +132,14 @@ __device__ __forceinline__ void warp_rows_dot(const bf16* const (&wrow)[R], cons
       }
     }
   }
+}
+
+// convenience: prefetch + dot in one go (no overlap with a prologue)
+template <int T, int R>
+__device__ __forceinline__ void warp_rows_dot(const bf16* const (&wrow)[R], const bf16* xs, int K, float (&acc)[R][T]) {
+  RowBatch<R> pf;
+  prefetch_rows<R>(wrow, K, pf);
+  warp_rows_dot<T, R>(wrow, xs, K, acc, pf);
 }
 
 template <int T, int R>

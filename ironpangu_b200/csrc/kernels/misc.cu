@@ -34,6 +34,10 @@ extern "C" int ifab_ipc_import(const unsigned char handle[64], void** out) {
 }
 extern "C" int ifab_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 
+extern "C" int ifab_set_pdl(int on) {
+  pdl_enabled() = on ? 1 : 0;
+  return 0;
+}
 extern "C" int ifab_set_device(int device) { return (int)cudaSetDevice(device); }
 extern "C" int ifab_peek(void* dst_host, const void* src_device, uint64_t bytes) {
   return (int)cudaMemcpy(dst_host, src_device, bytes, cudaMemcpyDeviceToHost);
@@ -60,6 +64,8 @@ extern "C" const char* ifab_error_string(int code) {
 namespace {
 
 __global__ void embedding_kernel(const int32_t* ids, const bf16* table, bf16* out, int D, int vocab, uint32_t* status) {
+  grid_dep_launch();
+  grid_dep_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) {
@@ -75,6 +81,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const bf16* x, long ldx, c
                                                       float eps, int zero_centered) {
   __shared__ float red[8];
   __shared__ float inv_s;
+  grid_dep_launch();
+  grid_dep_wait();
   const int t = blockIdx.x;
   const bf16* xr = x + (long)t * ldx;
   float ss = 0.f;
@@ -109,14 +117,13 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const bf16* x, long ldx, c
 extern "C" int ifab_embedding_bf16(const int32_t* ids, const void* table, void* out, int T, int D, int vocab,
                                    uint32_t* status, void* stream) {
   if (D % 8 != 0) return -1;
-  embedding_kernel<<<T, 128, 0, (cudaStream_t)stream>>>(ids, (const bf16*)table, (bf16*)out, D, vocab, status);
-  return (int)cudaGetLastError();
+  return launch_chain(embedding_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream, ids, (const bf16*)table, (bf16*)out,
+                      D, vocab, status);
 }
 
 extern "C" int ifab_rmsnorm_bf16(const void* x, long ldx, const void* w, void* y, long ldy, int T, int D, float eps,
                                  int zero_centered, void* stream) {
   if (D % 8 != 0 || ldx % 8 != 0 || ldy % 8 != 0) return -1;
-  rmsnorm_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, ldx, (const bf16*)w, (bf16*)y, ldy, D, eps,
-                                                     zero_centered);
-  return (int)cudaGetLastError();
+  return launch_chain(rmsnorm_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x, ldx, (const bf16*)w,
+                      (bf16*)y, ldy, D, eps, zero_centered);
 }

@@ -114,7 +114,7 @@ def forward_ref(cfg: MlaMoeConfig, W: Dict[str, torch.Tensor], tokens: torch.Ten
                         continue
                     g_u = _r(h2[t] @ gu[e].T)
                     a = _r(torch.nn.functional.silu(g_u[:c.expert_ffn]) * g_u[c.expert_ffn:])
-                    part[t] += wts[t, k] * _r(a @ dn[e].T)
+                    part[t] += wts[t, k] * (a @ dn[e].T)
             # tensor-parallel shard of the shared expert
             fs = c.shared_ffn // tp
             sgu, sdn = f(p + "shared_gate_up"), f(p + "shared_down")

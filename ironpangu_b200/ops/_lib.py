@@ -43,6 +43,7 @@ _SIGS = {
     "ifab_ipc_import": [C.c_char_p, C.POINTER(c_void_p)],
     "ifab_ipc_close": [_P],
     "ifab_set_device": [c_int],
+    "ifab_set_pdl": [c_int],
     "ifab_peek": [_P, _P, c_u64],
     "ifab_poke": [_P, _P, c_u64],
     "ifab_embedding_bf16": [_P, _P, _P, c_int, c_int, c_int, _P, _P],
@@ -94,6 +95,9 @@ def load(build: bool = True):
                 continue
             fn.argtypes = sig
             fn.restype = c_int
+        import os
+        if os.environ.get("IFAB_PDL", "1") == "0":  # A/B switch: plain stream-ordered launches
+            lib.ifab_set_pdl(0)
         _lib = lib
         return lib
 

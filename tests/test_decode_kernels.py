@@ -121,7 +121,7 @@ def test_moe_decode_single_rank(env):
             gu = (h[t] @ wgu[e].float().T).to(BF16).float()
             a = (torch.nn.functional.silu(gu[:F]) * gu[F:]).to(BF16).float()
             torch.testing.assert_close(act[t, k].float(), a, rtol=2e-2, atol=1e-3)
-            ref[t] += wts[t, k] * (a @ wd[e].float().T).to(BF16).float()
+            ref[t] += wts[t, k] * (a @ wd[e].float().T)
         gu = (h[t] @ sgu.float().T).to(BF16).float()
         a = (torch.nn.functional.silu(gu[:Fs]) * gu[Fs:]).to(BF16).float()
         ref[t] += a @ sd.float().T
