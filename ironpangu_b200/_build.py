@@ -30,7 +30,7 @@ SERVER_BIN = SERVER_DIR / "ifab-server"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall",
 ]
 CXX_FLAGS = ["-std=c++20", "-O2", "-fPIC", "-Wall", "-Wextra", "-pthread"]
 

@@ -172,6 +172,10 @@ Interpreter::Interpreter(const graph::Graph& g, const Weights& w) : g_(g), w_(w)
     }
     if (n.op == "embedding") vocab_ = (uint32_t)n.int_attr("vocab");
   }
+  // the vocabulary projection keeps f32 logits (the device lm_head kernel never rounds them)
+  const Node& out = g.nodes[g.output];
+  if (out.op == "gather" && g.nodes[out.inputs[0]].op == "linear") logits_linear_ = (int64_t)out.inputs[0];
+  else if (out.op == "linear") logits_linear_ = (int64_t)g.output;
 }
 
 void Interpreter::reset() {
@@ -239,14 +243,17 @@ void Interpreter::run_node(uint32_t idx, uint32_t token, uint32_t position) {
     const Tensor& w0 = W("weight");
     const Tensor* w1 = n.has("paired_weight") ? &W("paired_weight") : nullptr;
     const uint32_t pwidth = w1 ? (n.has("paired_width") ? (uint32_t)n.int_attr("paired_width") : width) : 0;
+    const bool keep_f32 = (int64_t)idx == logits_linear_;
+    auto rnd = [&](float v) { return keep_f32 ? v : bf16_round(v); };
+    out.f32 = keep_f32;
     if (pl == "replicated") {
       if (!x.replicated) invalid(n.name + ": replicated linear over a rank-local input");
       std::vector<float> xv = as_bf16(x, 0);
       const size_t K = xv.size();
       if (w0.shape != std::vector<uint64_t>{width, K}) invalid(n.name + ": weight shape mismatch");
       std::vector<float> y(width + pwidth);
-      for (uint32_t j = 0; j < width; ++j) y[j] = bf16_round(dotf(&w0.data[(size_t)j * K], xv.data(), K));
-      for (uint32_t j = 0; j < pwidth; ++j) y[width + j] = bf16_round(dotf(&w1->data[(size_t)j * K], xv.data(), K));
+      for (uint32_t j = 0; j < width; ++j) y[j] = rnd(dotf(&w0.data[(size_t)j * K], xv.data(), K));
+      for (uint32_t j = 0; j < pwidth; ++j) y[width + j] = rnd(dotf(&w1->data[(size_t)j * K], xv.data(), K));
       out.r = {std::move(y)};
     } else if (pl == "tp_rows") {
       per_rank(false, [&](uint32_t r) {
@@ -254,8 +261,8 @@ void Interpreter::run_node(uint32_t idx, uint32_t token, uint32_t position) {
         const size_t K = xv.size();
         if (w0.shape != std::vector<uint64_t>{(uint64_t)width * tp, K}) invalid(n.name + ": weight shape mismatch");
         std::vector<float> y(width + pwidth);
-        for (uint32_t j = 0; j < width; ++j) y[j] = bf16_round(dotf(&w0.data[((size_t)r * width + j) * K], xv.data(), K));
-        for (uint32_t j = 0; j < pwidth; ++j) y[width + j] = bf16_round(dotf(&w1->data[((size_t)r * pwidth + j) * K], xv.data(), K));
+        for (uint32_t j = 0; j < width; ++j) y[j] = rnd(dotf(&w0.data[((size_t)r * width + j) * K], xv.data(), K));
+        for (uint32_t j = 0; j < pwidth; ++j) y[width + j] = rnd(dotf(&w1->data[((size_t)r * pwidth + j) * K], xv.data(), K));
         return y;
       });
       if (tp == 1) out.replicated = true;

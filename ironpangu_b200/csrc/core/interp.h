@@ -76,6 +76,7 @@ class Interpreter {
   std::map<uint32_t, int> cache_of_node_;
   std::map<uint32_t, ConvState> conv_;
   uint32_t expected_pos_ = 0;
+  int64_t logits_linear_ = -1;
 };
 
 }  // namespace ifab::interp

@@ -285,3 +285,38 @@ class MlaMoeDecoder:
     def reset(self) -> None:
         for cch in self.caches:
             cch.zero_()
+
+
+def weights_from_checkpoint(cfg: MlaMoeConfig, checkpoint_dir: str, prefix: str = "model") -> Dict[str, torch.Tensor]:
+    """Unsharded weights of this module's naming from a safetensors checkpoint that uses the scoped names
+    of the DSL examples (``model.layers.N.self_attn.q_a_proj.weight`` ...)."""
+    from ..runtime.plan_engine import SafetensorsDir
+
+    st = SafetensorsDir(checkpoint_dir)
+
+    def get(name: str) -> torch.Tensor:
+        mm, off, n, dtype, shape = st.tensors[name + ".weight"]
+        import numpy as np
+        raw = torch.from_numpy(np.frombuffer(mm, dtype=np.uint8, count=n, offset=off).copy())
+        t = raw.view(torch.bfloat16 if dtype == "BF16" else torch.float32)
+        return t.view(*shape)
+
+    c = cfg
+    out = {"embed": get(f"{prefix}.embed_tokens"), "final_norm": get(f"{prefix}.norm"), "lm_head": get("lm_head")}
+    for l in range(c.layers):
+        p, q = f"layers.{l}.", f"{prefix}.layers.{l}."
+        out[p + "attn_norm"] = get(q + "input_layernorm")
+        out[p + "qkv_a"] = torch.cat([get(q + "self_attn.q_a_proj"), get(q + "self_attn.kv_a_proj_with_mqa")], 0)
+        out[p + "q_a_norm"] = get(q + "self_attn.q_a_layernorm")
+        out[p + "kv_a_norm"] = get(q + "self_attn.kv_a_layernorm")
+        out[p + "q_b"] = get(q + "self_attn.q_b_proj")
+        out[p + "kv_b"] = get(q + "self_attn.kv_b_proj").view(c.heads, c.nope + c.vdim, c.kv_lora)
+        out[p + "o_proj"] = get(q + "self_attn.o_proj")
+        out[p + "ffn_norm"] = get(q + "post_attention_layernorm")
+        out[p + "router"] = get(q + "mlp.gate").float()
+        out[p + "gate_up"] = torch.stack([torch.cat([get(q + f"mlp.experts.{e}.gate_proj"), get(q + f"mlp.experts.{e}.up_proj")], 0)
+                                          for e in range(c.experts)])
+        out[p + "down"] = torch.stack([get(q + f"mlp.experts.{e}.down_proj") for e in range(c.experts)])
+        out[p + "shared_gate_up"] = torch.cat([get(q + "mlp.shared_experts.gate_proj"), get(q + "mlp.shared_experts.up_proj")], 0)
+        out[p + "shared_down"] = get(q + "mlp.shared_experts.down_proj")
+    return out

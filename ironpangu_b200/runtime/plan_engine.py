@@ -1,0 +1,249 @@
+"""Executor of a compiled bundle on one rank.
+
+``PlanEngine`` reads ``device-program.json`` and this rank's IFINIT01 plan from a bundle directory,
+streams the weight slices from the safetensors checkpoint into device parameters (row shards,
+strided column shards, local experts, packed pairs - exactly as the plan says) and then runs the
+physical instructions by dispatching each one to its sm_100a kernel. The instruction loop is only
+walked eagerly for prefill chunks and once during CUDA-graph capture; steady-state decode replays
+the captured graph.
+
+Reference counterparts: the init-plan executor (native/src/initialization_plan.cpp:192-278) and the
+token dispatcher (native/src/token_dispatch.inc:19-294).
+"""
+from __future__ import annotations
+
+import json
+import math
+import mmap
+import os
+import struct
+from pathlib import Path
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..ops import decode as K
+from ..parallel.fabric import Fabric
+
+BF16 = torch.bfloat16
+_DT = {"bf16": (torch.bfloat16, 2), "f32": (torch.float32, 4), "int8": (torch.int8, 1), "fp8_e4m3": (torch.float8_e4m3fn, 1)}
+
+
+class SafetensorsDir:
+    """Read-only view of every ``*.safetensors`` file of a directory (headers parsed, data mmapped)."""
+
+    def __init__(self, path: str):
+        self.tensors: Dict[str, tuple] = {}
+        self._maps = []
+        for f in sorted(Path(path).glob("*.safetensors")):
+            fh = open(f, "rb")
+            mm = mmap.mmap(fh.fileno(), 0, access=mmap.ACCESS_READ)
+            self._maps.append((fh, mm))
+            (hlen,) = struct.unpack("<Q", mm[:8])
+            hdr = json.loads(mm[8:8 + hlen])
+            for name, info in hdr.items():
+                if name == "__metadata__":
+                    continue
+                b, e = info["data_offsets"]
+                self.tensors[name] = (mm, 8 + hlen + b, e - b, info["dtype"], info["shape"])
+
+    def bytes_of(self, name: str) -> np.ndarray:
+        mm, off, n, _, _ = self.tensors[name]
+        return np.frombuffer(mm, dtype=np.uint8, count=n, offset=off)
+
+
+def load_parameters(init_plan: dict, ckpt: SafetensorsDir, device) -> Dict[str, torch.Tensor]:
+    """Execute one rank's initialization plan: returns ``{parameter name: device tensor}``."""
+    params, cursors, raw = {}, {}, {}
+    for p in init_plan["parameters"]:
+        dt, eb = _DT[p["dtype"]]
+        n = int(np.prod(p["dims"])) * eb
+        raw[p["id"]] = torch.empty(n, dtype=torch.uint8, device=device)
+        cursors[p["id"]] = 0
+    meta = {p["id"]: p for p in init_plan["parameters"]}
+    for l in init_plan["loads"]:
+        src = ckpt.bytes_of(l["tensor"])
+        if l["kind"] == "slice":
+            chunk = src[l["offset"]:l["offset"] + l["bytes"]]
+        else:
+            rows = l["bytes"] // l["row_bytes"]
+            view = np.lib.stride_tricks.as_strided(src[l["offset"]:], shape=(rows, l["row_bytes"]), strides=(l["stride_bytes"], 1))
+            chunk = np.ascontiguousarray(view).reshape(-1)
+        t = torch.from_numpy(np.array(chunk, copy=True))
+        dst_dt = meta[l["dest"]]["dtype"]
+        if l["src_dtype"] == "bf16" and dst_dt == "f32":
+            t = t.view(torch.bfloat16).to(torch.float32).view(torch.uint8)
+        elif l["src_dtype"] != dst_dt:
+            raise ValueError(f"no conversion {l['src_dtype']} -> {dst_dt} for {l['tensor']}")
+        c = cursors[l["dest"]]
+        raw[l["dest"]][c:c + t.numel()].copy_(t, non_blocking=False)
+        cursors[l["dest"]] = c + t.numel()
+    for pid, p in meta.items():
+        if cursors[pid] != raw[pid].numel():
+            raise ValueError(f"parameter {p['name']} was filled with {cursors[pid]} of {raw[pid].numel()} bytes")
+        params[p["name"]] = raw[pid].view(_DT[p["dtype"]][0]).view(*p["dims"])
+    return params
+
+
+class PlanEngine:
+    """Runs a bundle's physical program for up to ``max_tokens`` (<= 8) query rows per step."""
+
+    def __init__(self, bundle_dir: str, checkpoint_dir: str, fabric: Fabric, *, max_tokens: int = 8,
+                 num_slots: int = 1, keep_logits: bool = False):
+        self.fabric, self.rank, self.world = fabric, fabric.rank, fabric.world
+        b = Path(bundle_dir)
+        self.program = json.loads((b / "device-program.json").read_text())
+        self.manifest = json.loads((b / "serving.json").read_text())
+        if self.program["parallel"]["tp"] != self.world:
+            raise ValueError(f"bundle was compiled for tp={self.program['parallel']['tp']}, running on {self.world} ranks")
+        init_plan = json.loads((b / f"rank-{self.rank}.init.json").read_text())
+        dev = fabric.device
+        self.P = load_parameters(init_plan, SafetensorsDir(checkpoint_dir), dev)
+        self.ins = self.program["instructions"]
+        self.T = max_tokens
+        self.max_context = self.program["max_context"]
+        self.page_tokens = 16
+        self.max_pages = (self.max_context + self.page_tokens - 1) // self.page_tokens
+        self.num_slots = num_slots
+        self.num_pages = self.max_pages * num_slots
+        T = self.T
+        self.tokens = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.positions = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.slots = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.page_table = torch.arange(self.num_pages, dtype=torch.int32, device=dev).view(num_slots, self.max_pages).contiguous()
+        self.next_ids = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.next_vals = torch.zeros(T, dtype=torch.float32, device=dev)
+        self.kps = 64
+        self.max_splits = max(1, min(64, (self.max_context + self.kps - 1) // self.kps))
+        while self.max_splits * self.kps < self.max_context:
+            self.kps *= 2
+        self.keep_logits = keep_logits
+        self.logits = None
+        self.vals: List[object] = [None] * len(self.ins)
+        self.caches: Dict[int, torch.Tensor] = {}
+        self._alloc(dev)
+        self.launches_per_forward = self.program["launches_per_token"] + sum(1 for i in self.ins if i["op"] == "mla_attention")
+        self._graph = None
+
+    # -- buffers -------------------------------------------------------------------------------------
+    def _alloc(self, dev) -> None:
+        T = self.T
+        max_heads = 1
+        for k, i in enumerate(self.ins):
+            op, w = i["op"], i["width"]
+            if op == "view":
+                continue
+            if op == "mla_kv_write":
+                self.caches[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
+            elif op == "router_topk":
+                a = i["attrs"]
+                self.vals[k] = (torch.empty(T, w, dtype=torch.int32, device=dev), torch.empty(T, w, dtype=torch.float32, device=dev),
+                                torch.empty(T, int(a["experts"]), dtype=torch.float32, device=dev))
+            elif op == "moe_gate_up":
+                topk = self.ins[i["inputs"][1]]["width"]
+                self.vals[k] = torch.zeros(T, topk + 1, w, dtype=BF16, device=dev)
+            elif op == "mla_q_absorb":
+                a = i["attrs"]
+                hl = int(a["heads"]) // self.world
+                max_heads = max(max_heads, hl)
+                self.vals[k] = torch.empty(T, hl, int(a["latent"]) + int(a["rope"]), dtype=BF16, device=dev)
+            elif op == "lm_head":
+                vl = int(i["attrs"]["width"])
+                self.partial = torch.empty(((vl + 7) // 8) * 8 * 2, dtype=torch.float32, device=dev)
+                if self.keep_logits:
+                    self.logits = torch.empty(T, vl, dtype=torch.float32, device=dev)
+                self.vals[k] = self.next_ids
+            else:
+                dt = torch.float32 if i["dtype"] == "f32" else BF16
+                self.vals[k] = torch.empty(T, w, dtype=dt, device=dev)
+        self.scratch = torch.empty(T * max_heads * self.max_splits * (512 + 2), dtype=torch.float32, device=dev)
+
+    def _param(self, name: str, optional: bool = False):
+        if name in self.P:
+            return self.P[name]
+        if optional:
+            return None
+        raise KeyError(f"bundle has no parameter {name}")
+
+    # -- one step --------------------------------------------------------------------------------------
+    def forward(self, T: Optional[int] = None) -> torch.Tensor:
+        T = self.T if T is None else T
+        fab, st = self.fabric, self.fabric.desc.status
+        tok, pos, slot = self.tokens[:T], self.positions[:T], self.slots[:T]
+        V = self.vals
+
+        def val(idx):
+            v = V[idx]
+            return v[:T] if isinstance(v, torch.Tensor) else v
+
+        for k, i in enumerate(self.ins):
+            op, a, ins = i["op"], i["attrs"], i["inputs"]
+            norm_w = self._param(a["norm_weight"], "norm_optional" in a) if "norm_weight" in a else None
+            eps = float(a.get("norm_eps", 1e-5))
+            if op == "embedding":
+                K.embedding(tok, self._param(a["weight"]), out=val(k), status_ptr=st)
+            elif op == "view":
+                src = V[ins[0]]
+                s, w = int(a["start"]), int(a["width"])
+                V[k] = src[:, s:s + w]
+            elif op == "linear":
+                name = a["weight"] + ("|" + a["paired_weight"] if "paired_weight" in a else "")
+                K.gemv(val(ins[0]), self._param(name), norm_w=norm_w, eps=eps, swiglu=a.get("activation") == "swiglu", out=val(k))
+            elif op == "linear_allreduce":
+                res = val(ins[1]) if len(ins) > 1 else None
+                K.gemv_allreduce(val(ins[0]), self._param(a["weight"]), fab, residual=res, out=val(k))
+            elif op == "norm":
+                K.rmsnorm(val(ins[0]), self._param(a["weight"]), float(a["eps"]), out=val(k))
+            elif op == "mla_kv_write":
+                lat, kr = val(ins[0]), val(ins[1])
+                if kr.data_ptr() != lat.data_ptr() + lat.shape[1] * 2 or kr.stride(0) != lat.stride(0):
+                    raise NotImplementedError("latent and rope columns must be adjacent slices of one projection")
+                kv = torch.as_strided(lat, (T, lat.shape[1] + kr.shape[1]), (lat.stride(0), 1))
+                K.mla_kv_write(kv, self._param(a["weight"]), pos, slot, self.page_table, self.caches[k], latent=lat.shape[1],
+                               rope=kr.shape[1], eps=float(a["eps"]), theta=float(a["theta"]), status_ptr=st)
+                V[k] = k
+            elif op == "mla_q_absorb":
+                H, nope, rope, latent = int(a["heads"]), int(a["nope"]), int(a["rope"]), int(a["latent"])
+                vdim = int(a.get("value", nope))
+                w = self._param(a["weight"]).view(H // self.world, nope + vdim, latent)
+                K.mla_q_absorb(val(ins[0]), w, pos, nope=nope, rope=rope, theta=float(a["theta"]), out=val(k))
+            elif op == "mla_attention":
+                H, latent, vdim = int(a["heads"]), int(a["latent"]), int(a["value"])
+                nope = int(a.get("nope", vdim))
+                w = self._param(a["weight"]).view(H // self.world, nope + vdim, latent)
+                cache = self.caches[V[ins[1]]]
+                K.mla_decode_attention(val(ins[0]), cache, pos, slot, self.page_table, w, nope=nope,
+                                       scale=1.0 / math.sqrt(float(a["scale_dim"])), window=int(a["window"]),
+                                       keys_per_split=self.kps, max_splits=self.max_splits, scratch=self.scratch,
+                                       out=val(k), status_ptr=st)
+            elif op == "router_topk":
+                ids, wts, logits = V[k]
+                K.router_topk(val(ins[0]), self._param(a["weight"]), int(a["topk"]), norm_w=norm_w, eps=eps,
+                              scoring=a["scoring"], scale=float(a["scale"]), renorm=a.get("renorm", "true") != "false",
+                              bias=self._param(a["weight"] + ".e_score_correction_bias", True), ticket_ptr=fab.ticket_ptr,
+                              logits=logits[:T], ids=ids[:T], wts=wts[:T])
+            elif op == "moe_gate_up":
+                ids = V[ins[1]][0][:T]
+                wgu = self._param(a["weight"] + "|" + a["paired_weight"])
+                sh = self._param(a["shared_weight"] + "|" + a["shared_paired_weight"]) if "shared_weight" in a else None
+                K.moe_gate_up(val(ins[0]), ids, wgu, self.rank * wgu.shape[0], norm_w=norm_w, eps=eps, w_shared_gu=sh, act=V[k][:T])
+            elif op == "moe_down_allreduce":
+                ids, wts, _ = V[ins[1]]
+                wd = self._param(a["weight"])
+                sh = self._param(a["shared_weight"]) if "shared_weight" in a else None
+                res = val(ins[2]) if len(ins) > 2 else None
+                K.moe_down_allreduce(V[ins[0]][:T], ids[:T], wts[:T], wd, self.rank * wd.shape[0], fab, w_shared_down=sh,
+                                     residual=res, out=val(k))
+            elif op == "lm_head":
+                w = self._param(a["weight"])
+                K.lm_head_argmax(val(ins[0]), w, fab, norm_w=norm_w, eps=eps, vocab_offset=self.rank * w.shape[0],
+                                 partial=self.partial, logits=None if self.logits is None else self.logits[:T],
+                                 out_ids=self.next_ids[:T], out_vals=self.next_vals[:T])
+            else:
+                raise NotImplementedError(f"no device kernel bound for instruction '{op}' ({i['name']})")
+        return self.next_ids[:T]
+
+    def reset(self) -> None:
+        for c in self.caches.values():
+            c.zero_()
