@@ -60,9 +60,12 @@ def write_bundle(source_path: str, out_dir: str, checkpoint_dir: Optional[str] =
                  json.dumps(options))
 
 
-def interpret(source: str, checkpoint_dir: str, tokens: List[int], steps: int = 0, logits: bool = False) -> Dict[str, Any]:
-    """Run the CPU oracle: feed ``tokens`` then decode ``steps`` greedy tokens."""
-    return _call("ifab_core_interpret", source, str(checkpoint_dir), json.dumps({"tokens": tokens, "steps": steps, "logits": logits}))
+def interpret(source: str, checkpoint_dir: str, tokens: List[int], steps: int = 0, logits: bool = False,
+              all_logits: bool = False) -> Dict[str, Any]:
+    """Run the CPU oracle: feed ``tokens`` then decode ``steps`` greedy tokens. ``all_logits`` also returns the
+    f32 logits after every fed token (``prompt_logits``)."""
+    return _call("ifab_core_interpret", source, str(checkpoint_dir),
+                 json.dumps({"tokens": tokens, "steps": steps, "logits": logits, "all_logits": all_logits}))
 
 
 def read_init_plan(path: str) -> Dict[str, Any]:

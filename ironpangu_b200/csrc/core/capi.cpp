@@ -104,10 +104,18 @@ char* ifab_core_interpret(const char* source, const char* checkpoint_dir, const 
     Json gen = Json::array(), pl = Json::array();
     std::vector<float> logits;
     uint32_t next = 0;
+    const bool all_logits = req.find("all_logits") && req.at("all_logits").as_bool();
+    Json every = Json::array();
     for (size_t i = 0; i < toks.size(); ++i) {
       next = it.step(toks[i], (uint32_t)i, &logits);
       pl.push((int64_t)next);
+      if (all_logits) {
+        Json l = Json::array();
+        for (float v : logits) l.push((double)v);
+        every.push(std::move(l));
+      }
     }
+    if (all_logits) out.set("prompt_logits", every);
     out.set("prompt_argmax", pl);
     uint32_t pos = (uint32_t)toks.size();
     for (uint32_t s = 0; s < steps; ++s) {

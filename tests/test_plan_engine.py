@@ -21,14 +21,15 @@ def test_bundle_executes_token_exact_against_cpu_interpreter(tmp_path):
     compiler.write_bundle(SLICE, bundle, checkpoint_dir=str(ck))
     g = torch.Generator().manual_seed(3)
     prompt = torch.randint(0, 1024, (16,), generator=g).tolist()
-    oracle = compiler.interpret(SLICE.read_text(), str(ck), prompt, steps=8, logits=True)
+    first = compiler.interpret(SLICE.read_text(), str(ck), prompt, steps=8)
+    seq = prompt + first["generated"]
+    oracle = compiler.interpret(SLICE.read_text(), str(ck), seq, all_logits=True)
+    ref = torch.tensor(oracle["prompt_logits"])
 
     fab = Fabric(0, 1)
     eng = PlanEngine(str(bundle), str(ck), fab, max_tokens=8, keep_logits=True)
     drv = DecodeEngine(eng)
-    # teacher-forced on the oracle's tokens so one near-tie cannot derail the comparison
-    seq = prompt + oracle["generated"]
-    got = []
+    # teacher-forced on the oracle's tokens; logits must agree everywhere, tokens wherever the oracle has no near-tie
     for s in range(0, len(seq), 8):
         chunk = seq[s:s + 8]
         n = len(chunk)
@@ -36,14 +37,18 @@ def test_bundle_executes_token_exact_against_cpu_interpreter(tmp_path):
         eng.positions[:n].copy_(torch.arange(s, s + n, dtype=torch.int32))
         eng.slots[:n].zero_()
         eng.forward(n)
-        got += eng.next_ids[:n].tolist()
-        last_logits = eng.logits[n - 1].clone()
-    want = oracle["prompt_argmax"][:15] + oracle["generated"]
-    mism = [i for i, (a, b) in enumerate(zip(got[:len(want)], want)) if a != b]
-    assert len(mism) <= 1, (mism, got, want)
+        got, logits = eng.next_ids[:n].tolist(), eng.logits[:n].cpu()
+        torch.testing.assert_close(logits, ref[s:s + n], rtol=2e-2, atol=1e-2)
+        for i in range(n):
+            top2 = ref[s + i].topk(2).values
+            if float(top2[0] - top2[1]) > 1e-2:
+                assert got[i] == int(ref[s + i].argmax()), (s + i, got[i])
+            assert got[i] == int(logits[i].argmax())
     # engine API: greedy generation through prefill chunks + captured decode graph
     eng.reset()
     out = drv.generate(prompt, 8)
-    assert sum(a != b for a, b in zip(out, oracle["generated"])) <= 1
+    assert len(out) == 8 and all(0 <= t < 1024 for t in out)
+    if all(float(ref[15 + i].topk(2).values.diff().abs()) > 1e-2 for i in range(8)):
+        assert out == first["generated"]
     assert fab.status() == 0
     fab.close()
