@@ -1,0 +1,51 @@
+"""Time the tcgen05 GEMM against torch.matmul (cuBLAS) on a few shapes; CUDA events, L2 flushed between runs.
+
+    python -m ironpangu_b200.utils.bench_gemm [--shapes 4096x4096x4096,...]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def time_fn(fn, flush, iters=10):
+    for _ in range(3):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default="4096x4096x4096,4096x2112x4096,4096x3072x4096,4096x4096x1536,8192x8192x8192,128x3072x4096")
+    args = ap.parse_args()
+    from ironpangu_b200.ops.gemm import gemm
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    out = []
+    for s in args.shapes.split(","):
+        M, N, K = map(int, s.split("x"))
+        a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+        c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        t_ours = time_fn(lambda: gemm(a, b, out=c), flush)
+        t_lib = time_fn(lambda: torch.matmul(a, b.T, out=c), flush)
+        fl = 2.0 * M * N * K
+        out.append({"shape": s, "ours_ms": round(t_ours, 4), "ours_tflops": round(fl / t_ours / 1e9, 1),
+                    "cublas_ms": round(t_lib, 4), "cublas_tflops": round(fl / t_lib / 1e9, 1)})
+        print(json.dumps(out[-1]), flush=True)
+
+
+if __name__ == "__main__":
+    main()
