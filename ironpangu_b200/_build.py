@@ -27,6 +27,8 @@ KERNEL_LIB = KERNEL_DIR / "libifab_kernels.so"
 CORE_LIB = CORE_DIR / "libifab_core.so"
 CLI_BIN = CLI_DIR / "ifab"
 SERVER_BIN = SERVER_DIR / "ifab-server"
+TESTS_DIR = ROOT / "csrc" / "tests"
+TESTS_BIN = TESTS_DIR / "core_tests"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -115,7 +117,7 @@ def build_core(force: bool = False) -> Path:
             objs = list(ex.map(one, srcs))
         _run(["g++", "-shared", "-o", str(CORE_LIB), *objs, "-pthread"], cwd=CORE_DIR)
         _mark(CORE_LIB, deps)
-    for bindir, binary in ((CLI_DIR, CLI_BIN), (SERVER_DIR, SERVER_BIN)):
+    for bindir, binary in ((CLI_DIR, CLI_BIN), (SERVER_DIR, SERVER_BIN), (TESTS_DIR, TESTS_BIN)):
         bsrcs = sorted(bindir.glob("*.cpp"))
         if not bsrcs:
             continue

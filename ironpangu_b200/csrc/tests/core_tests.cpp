@@ -1,0 +1,443 @@
+// Unit tests of the host runtime services (no device needed). Exit code 0 = all passed.
+#include <cstdio>
+#include <functional>
+#include <iostream>
+
+#include "cpu_plan.h"
+#include "paging.h"
+#include "prefix_index.h"
+#include "rankplan.h"
+#include "runtime.h"
+#include "scheduler.h"
+#include "state_pool.h"
+
+using namespace ifab;
+
+static int failures = 0, checks = 0;
+#define CHECK(cond)                                                            \
+  do {                                                                         \
+    ++checks;                                                                  \
+    if (!(cond)) {                                                             \
+      ++failures;                                                              \
+      std::printf("FAIL %s:%d: %s\n", __FILE__, __LINE__, #cond);              \
+    }                                                                          \
+  } while (0)
+template <typename F>
+static bool throws(F&& f, ErrorKind kind) {
+  try {
+    f();
+  } catch (const Error& e) {
+    return e.kind() == kind;
+  } catch (...) {
+    return false;
+  }
+  return false;
+}
+#define CHECK_THROWS(kind, expr) CHECK(throws([&] { expr; }, ErrorKind::kind))
+
+static serving::Manifest manifest(bool sliding) {
+  serving::Manifest m;
+  m.identity = {"m", std::string(64, 'a'), "b200_token_v1", 2};
+  m.max_context = 4096;
+  m.vocab = 1000;
+  m.eos = 1;
+  m.resident_sequences = 4;
+  m.max_batched_tokens = 64;
+  serving::Variant d;
+  d.name = "decode";
+  d.numerics = "gemv";
+  m.variants.push_back(d);
+  serving::Variant p;
+  p.name = "prefill_chunk";
+  p.phase = serving::Phase::Prefill;
+  p.max_query_tokens = 64;
+  p.captured = false;
+  p.numerics = "tc";
+  m.variants.push_back(p);
+  serving::State kv;
+  kv.name = "kv16";
+  kv.component = 0;
+  kv.dtype = "bf16";
+  kv.storage = {serving::Storage::Kind::Pages, 16, 1152, 0};
+  if (sliding) kv.retention = {serving::Retention::Kind::SlidingWindow, 512};
+  m.states.push_back(kv);
+  serving::State slot;
+  slot.name = "conv";
+  slot.component = 1;
+  slot.dtype = "bf16";
+  slot.storage = {serving::Storage::Kind::Slot, 0, 0, 4096};
+  m.states.push_back(slot);
+  m.validate();
+  return m;
+}
+
+static void test_state_pool() {
+  using namespace runtime;
+  auto m = manifest(false);
+  std::map<StatePool::Key, uint32_t> cap;
+  for (uint32_t r = 0; r < 2; ++r) {
+    cap[{"kv16", r}] = 8;
+    cap[{"conv", r}] = 2;
+  }
+  StatePool p(m, 7, 2, cap);
+  auto baseline = p.usage();
+  Lease a = p.reserve(7, 1, 32);
+  CHECK(p.bindings(7, a).size() == 4);
+  CHECK(p.page_address(7, a, "kv16", 1, 17).row == 1);
+  CHECK(p.page_address(7, a, "kv16", 0, 17).byte_offset == (uint64_t)p.bindings(7, a)[0].units[1] * 16 * 1152 + 1152);
+  CHECK_THROWS(Capacity, p.page_address(7, a, "kv16", 0, 32));
+  CHECK_THROWS(Stale, p.reserve(8, 2, 16));
+  Ticket t = p.submit(7, {a}, {});
+  CHECK_THROWS(Invalid, p.seal(7, a));
+  p.complete(7, t, 0);
+  CHECK_THROWS(Invalid, p.seal(7, a));      // every rank must complete
+  CHECK_THROWS(Invalid, p.complete(7, t, 0));
+  p.complete(7, t, 1);
+  SealedLease s = p.seal(7, a);
+  CHECK_THROWS(Invalid, p.submit(7, {a}, {}));   // sealed = read-only
+  Borrow pin = p.borrow_sealed(7, s);
+  p.retire(7, a);
+  Borrow reader = p.borrow_sealed(7, s);          // snapshot survives the owner's retirement
+  Ticket restore = p.submit(7, {}, {reader});
+  p.release(7, pin);
+  p.release(7, reader);
+  p.complete(7, restore, 1);
+  bool occupied = false;
+  for (auto& u : p.usage()) occupied |= u.occupied_units > 0;
+  CHECK(occupied);                                 // still in flight on rank 0
+  p.complete(7, restore, 0);
+  CHECK(p.usage() == baseline);                    // deferred reclaim happened
+  CHECK_THROWS(Stale, p.borrow_sealed(7, s));
+  // all-or-nothing reservation
+  Lease big = p.reserve(7, 3, 8 * 16);
+  auto before = p.usage();
+  CHECK_THROWS(Capacity, p.reserve(7, 4, 16));
+  CHECK(p.usage() == before);
+  p.retire(7, big);
+  // slot pinning
+  Lease s1 = p.reserve_at_slot(7, 5, 16, 1);
+  for (auto& b : p.bindings(7, s1))
+    if (b.component == "conv") CHECK(b.units[0] == 1);
+  CHECK_THROWS(Capacity, p.reserve_at_slot(7, 6, 16, 1));
+  p.poison();
+  CHECK_THROWS(Backend, p.reserve(7, 9, 16));
+  // sliding window ring
+  auto ms = manifest(true);
+  std::map<StatePool::Key, uint32_t> cap2;
+  for (uint32_t r = 0; r < 2; ++r) {
+    cap2[{"kv16", r}] = 80;
+    cap2[{"conv", r}] = 2;
+  }
+  StatePool q(ms, 1, 2, cap2);
+  Lease lg = q.reserve(1, 1, 4096);
+  const auto& bs = q.bindings(1, lg);
+  CHECK(bs[0].ring_tokens == 544 && bs[0].units.size() == 34);
+  std::set<uint64_t> live;
+  for (uint32_t pos = 2000; pos < 2000 + 512; ++pos) CHECK(live.insert(q.page_address(1, lg, "kv16", 0, pos).byte_offset).second);
+  Lease sh = q.reserve(1, 2, 17);
+  CHECK(q.bindings(1, sh)[0].units.size() == 2 && q.bindings(1, sh)[0].ring_tokens == 0);
+}
+
+static void test_prefix_index() {
+  using namespace runtime;
+  serving::PrefixIdentity id{"p", "w", "ns", "", 16};
+  PrefixIndex ix(id, 4);
+  std::vector<uint32_t> a{1, 2, 3, 4, 5, 6, 7, 8}, b{1, 2, 3, 4, 9, 9, 9, 9}, c{1, 2, 3, 4};
+  CHECK(ix.insert(id, a, {1}));
+  CHECK(ix.insert(id, b, {2}));
+  CHECK(ix.insert(id, c, {3}));
+  CHECK(!ix.insert(id, c, {4}));
+  CHECK_THROWS(Invalid, ix.insert(id, {1, 2, 3}, {5}));
+  CHECK(ix.size() == 3);
+  auto m = ix.lookup(id, {1, 2, 3, 4, 5, 6, 7, 8, 10});
+  CHECK(m && m->id.value == 1 && m->tokens == 8);
+  m = ix.lookup(id, {1, 2, 3, 4, 5, 6, 7, 8});     // must leave one token to compute
+  CHECK(m && m->id.value == 3 && m->tokens == 4);
+  m = ix.lookup(id, {1, 2, 3, 4, 9, 9, 0});
+  CHECK(m && m->id.value == 3);
+  CHECK(!ix.lookup(id, {2, 2, 3, 4, 5}));
+  serving::PrefixIdentity other = id;
+  other.salt = "x";
+  CHECK(!ix.lookup(other, {1, 2, 3, 4, 5, 6, 7, 8, 10}));
+  CHECK(ix.remove({3}));
+  CHECK(!ix.remove({3}));
+  m = ix.lookup(id, {1, 2, 3, 4, 5, 6, 7, 8, 10});
+  CHECK(m && m->id.value == 1);
+  CHECK(ix.remove({1}) && ix.remove({2}) && ix.empty() && ix.token_units() == 0);
+  // LRU cache
+  PrefixCache cache(id, 4, 2);
+  serving::ArithmeticHistory h4, h8;
+  h4.append_completed(0, 4, "tc");
+  h8.append_completed(0, 8, "tc");
+  std::vector<SealedLease> ev;
+  auto i1 = cache.publish(c, {1, 1}, h4, &ev);
+  auto i2 = cache.publish(a, {2, 2}, h8, &ev);
+  CHECK(i1 && i2 && ev.empty());
+  const auto* hit = cache.restore({1, 2, 3, 4, 5, 6, 7, 8, 9});
+  CHECK(hit && hit->tokens.size() == 8);
+  auto i3 = cache.publish(b, {3, 3}, h8, &ev);       // evicts the LRU unpinned entry (prefix c)
+  CHECK(i3 && ev.size() == 1 && ev[0].lease == 1);
+  cache.unpin(hit->id);
+  serving::ArithmeticHistory other_hist;
+  other_hist.append_completed(0, 8, "gemv");
+  CHECK(cache.restore({1, 2, 3, 4, 9, 9, 9, 9, 1}, &other_hist) == nullptr);   // different numerics: no reuse
+  CHECK(cache.clear().size() == 2);
+}
+
+static void test_paging() {
+  using namespace paging;
+  auto sp = page_spans(14, 20, 16);
+  CHECK(sp.size() == 3 && sp[0].page == 0 && sp[0].first_row == 14 && sp[0].rows == 2 && sp[1].rows == 16 && sp[2].rows == 2);
+  ResidentPages rp({16, 1152, 8, 4}, 2);
+  rp.bind(0, {5, 2, 7});       // permuted, non-contiguous pages
+  rp.bind(1, {0, 1, 3});
+  CHECK_THROWS(Invalid, rp.bind(1, {5}));
+  CHECK(rp.row_offset(0, 17) == ((uint64_t)2 * 16 + 1) * 1152);
+  auto t = rp.batch_table();
+  CHECK(t.size() == 8 && t[0] == 5 && t[3] == -1 && t[4] == 0);
+  auto cp = rp.copy_plan(0, 1, 40);
+  CHECK(cp.size() == 3 && cp[2].bytes == 8 * 1152);
+  CHECK_THROWS(Capacity, rp.copy_plan(0, 1, 64));
+  rp.release(0);
+  rp.append(0, 5);
+  CHECK_THROWS(Invalid, rp.append(0, 0));
+  auto b = SequenceBatch::make({{1, 10, 3, true}, {0, 0, 2, false}}, {7, 8, 9, 1, 2}, 8, 2, 64);
+  CHECK(b.tokens.size() == 5 && b.positions[2] == 12 && b.slots[3] == 0 && b.sample_rows[0] == 2 && b.sample_rows[1] == -1);
+  CHECK_THROWS(Invalid, SequenceBatch::make({{1, 0, 1, true}, {1, 1, 1, true}}, {1, 2}, 8, 2, 64));
+  CHECK_THROWS(Capacity, SequenceBatch::make({{0, 62, 4, true}}, {1, 2, 3, 4}, 8, 2, 64));
+  auto w = SlidingWindowLayout::make(65536, 512, 4, 16);
+  CHECK(w.capacity == 544 && w.ring_row(544) == 0 && w.first_visible(1000) == 489);
+  CHECK(w.append_is_safe(5000, 4) && w.append_is_safe(5000, 32) && !w.append_is_safe(5000, 64));
+  BoundedBuffers bb(1024, 2);
+  uint32_t x = bb.acquire(1000);
+  bb.acquire(8);
+  CHECK_THROWS(Capacity, bb.acquire(8));
+  CHECK_THROWS(Capacity, BoundedBuffers(16, 1).acquire(32));
+  bb.release(x);
+  CHECK_THROWS(Invalid, bb.release(x));
+}
+
+static rankplan::Spec spec(uint32_t tp, uint32_t cp, bool sp) {
+  rankplan::Spec s;
+  s.model = {"hybrid", 2048, 6144, 248320, 8, 2, 256, 16, 128, 4, {rankplan::Layer::Delta, rankplan::Layer::Delta, rankplan::Layer::Delta, rankplan::Layer::Full}};
+  s.prefill = {tp, cp, sp};
+  s.decode = {tp, 1, false};
+  s.page_tokens = 128;
+  s.token_budget = 1024;
+  s.batch_buckets = {1, 2, 4, 8};
+  s.context_buckets = {128, 512, 2048, 8192};
+  return s;
+}
+
+static void test_rankplan_and_runtime() {
+  using namespace rankplan;
+  using namespace runtime;
+  Artifact a = compile(spec(2, 2, true));
+  size_t n_prefill = 0, n_decode = 0;
+  for (auto& p : a.plans) (p.role == Role::Prefill ? n_prefill : n_decode)++;
+  CHECK(n_prefill == 4 && n_decode == 2 && a.buckets.size() == 16);
+  auto count = [&](const RankPlan& p, CommKind k, const std::string& g) {
+    size_t n = 0;
+    for (auto& i : p.instructions) n += i.kind == Instruction::Kind::Communication && i.comm == k && i.group == g;
+    return n;
+  };
+  const RankPlan& p0 = a.plans[0];
+  CHECK(count(p0, CommKind::ReduceScatter, "tp") == 8 && count(p0, CommKind::AllReduce, "tp") == 0);   // SP: RS instead of AR
+  CHECK(count(p0, CommKind::AllGather, "tp") == 8 + 1 + 1);
+  CHECK(count(p0, CommKind::Send, "cp") == 1 + 3 && count(p0, CommKind::Receive, "cp") == 1);           // ring on the full layer; delta hand-off
+  const RankPlan& dec = a.plans[4];
+  CHECK(dec.role == Role::Decode && count(dec, CommKind::AllReduce, "tp") == 8 && count(dec, CommKind::Send, "cp") == 0);
+  CHECK(dec.states.size() == 3 * 2 + 1);
+  Artifact back = decode(encode(a));
+  CHECK(back.key == a.key && back.plans.size() == a.plans.size());
+  std::string bytes = encode(a);
+  bytes[100] ^= 1;
+  CHECK_THROWS(Stale, decode(bytes));
+  auto bad = spec(2, 1, false);
+  bad.decode.cp = 2;
+  CHECK_THROWS(Invalid, bad.validate());
+  bad = spec(1, 1, true);
+  CHECK_THROWS(Invalid, bad.validate());
+  bad = spec(2, 1, false);
+  bad.batch_buckets = {4, 2};
+  CHECK_THROWS(Invalid, bad.validate());
+  // every start-up stage failure prevents readiness
+  for (Stage st : {Stage::Validate, Stage::Compile, Stage::Prepare, Stage::Warmup, Stage::Capture, Stage::ValidateReplay, Stage::Reset, Stage::Ready}) {
+    auto tr = std::make_shared<Trace>();
+    Runtime rt(compile(spec(2, 1, false)), Role::Decode, 0, std::make_unique<MockBackend>(tr));
+    CHECK_THROWS(Backend, rt.start("w", st));
+    CHECK(rt.stage() == Stage::Failed && !rt.ready());
+    CHECK_THROWS(Backend, rt.step({{1, {1}, 0}}));
+  }
+  auto tr = std::make_shared<Trace>();
+  Runtime rt(compile(spec(2, 1, false)), Role::Decode, 1, std::make_unique<MockBackend>(tr, 1));
+  rt.start("w");
+  CHECK(rt.ready() && tr->count("capture") == 16);
+  auto out = rt.step({{5, {3}, 100}, {6, {4}, 600}});
+  CHECK(out.size() == 2 && out[0].token == MockBackend::token_for(5, 101, 248320));
+  CHECK(tr->count("comm all_reduce tp") == 8);
+  CHECK_THROWS(Capacity, rt.step({{5, {3}, 9000}}));
+  rt.close();
+  CHECK(rt.stage() == Stage::Closed);
+  // thread-per-rank worker group: a failing rank fails the group for good
+  std::atomic<int> ran{0};
+  {
+    WorkerGroup g(4, [&](uint32_t rank, uint64_t gen) {
+      ++ran;
+      if (gen == 2 && rank == 3) throw std::runtime_error("boom");
+    });
+    g.step();
+    CHECK(ran == 4 && g.healthy());
+    CHECK_THROWS(Backend, g.step());
+    CHECK(!g.healthy() && g.failure().find("rank 3") != std::string::npos);
+    CHECK_THROWS(Backend, g.step());
+  }
+  HealthGuard hg;
+  hg.fail("first");
+  hg.fail("second");
+  CHECK(!hg.healthy() && hg.reason() == "first");
+}
+
+static void test_transfer() {
+  using namespace runtime;
+  InMemoryTransport t("key", 8, 2, 16);
+  TransferLease l = t.reserve(1, 5, 40);
+  CHECK(l.pages.size() == 3);
+  TransferManifest m{1, 5, "key", 40, 77, {1, 2}, 0, 0};
+  CHECK_THROWS(Invalid, t.commit(l));
+  t.transfer(m);
+  t.transfer(m);                                   // idempotent duplicate
+  TransferManifest other = m;
+  other.next_token = 78;
+  CHECK_THROWS(Invalid, t.transfer(other));
+  TransferManifest stale = m;
+  stale.epoch = 4;
+  CHECK_THROWS(Stale, t.transfer(stale));
+  t.complete(l);
+  CHECK(t.commit(l).next_token == 77 && t.commit(l).next_token == 77);
+  CHECK_THROWS(Invalid, t.finish(l));
+  t.acknowledge(l);
+  t.acknowledge(l);
+  t.finish(l);
+  CHECK(t.pending() == 0 && t.pool().retired() == 3 && t.pool().free_pages() == 5);
+  TransferLease old = l;
+  CHECK_THROWS(Stale, t.complete(old));
+  t.completion_fence();
+  CHECK(t.pool().free_pages() == 8);
+  TransferLease l2 = t.reserve(1, 5, 16);
+  CHECK(l2.generation != l.generation);
+  CHECK_THROWS(Stale, t.pool().check(l));
+  TransferLease grown = t.pool().ensure(l2, 50);
+  CHECK(grown.pages.size() == 4);
+  CHECK_THROWS(NotImplemented, UnavailableTransport().poll(1));
+}
+
+static void test_scheduler() {
+  using namespace sched;
+  size_t cur = 0;
+  auto pick = select_round({4, 4, 4, 4}, &cur, 10);
+  CHECK(pick.size() == 2 && pick[0] == 0 && cur == 2);
+  pick = select_round({4, 4, 4, 4}, &cur, 10);
+  CHECK(pick[0] == 2 && pick[1] == 3 && cur == 0);
+  LiveScheduler s({2, 8, 4, 64, 3, 100});
+  s.submit({1, {1, 2, 3, 4, 5, 6}, 3, {99}});
+  s.submit({2, {7, 8}, 2, {}});
+  s.submit({3, {9}, 1, {}});
+  CHECK_THROWS(Invalid, s.submit({3, {9}, 1, {}}));
+  CHECK_THROWS(Invalid, s.submit({4, {1000}, 1, {}}));
+  CHECK_THROWS(Capacity, s.submit({5, std::vector<uint32_t>(63, 1), 4, {}}));
+  auto p = s.plan();                                 // seq1 chunk of 4, seq2 whole prompt (2)
+  CHECK(p.batch.slices.size() == 2 && p.batch.slices[0].token_count == 4 && !p.batch.slices[0].sample && p.batch.slices[1].sample);
+  CHECK(s.queued() == 1 && s.running() == 2);
+  auto ev = s.commit(p, {0, 50});
+  CHECK(ev.size() == 1 && ev[0].request == 2 && *ev[0].token == 50 && !ev[0].finish);
+  p = s.plan();                                      // seq1 rest of prompt (2 rows), seq2 decode (service order rotates)
+  CHECK(p.batch.tokens.size() == 3);
+  std::vector<uint32_t> sampled;
+  for (size_t k = 0; k < p.batch.slices.size(); ++k) {
+    if (p.requests[k] == 1) CHECK(p.batch.slices[k].position == 4 && p.batch.slices[k].token_count == 2 && p.batch.slices[k].sample);
+    sampled.push_back(p.requests[k] == 1 ? 60 : 51);
+  }
+  ev = s.commit(p, sampled);
+  CHECK(ev.size() == 2);
+  for (auto& e : ev) CHECK(e.request == 1 ? (!e.finish && *e.token == 60) : (e.finish && *e.finish == Finish::Length));
+  p = s.plan();                                      // resident of seq2 is reused by request 3
+  CHECK(p.released.size() == 1 && p.requests.size() == 2);
+  s.set_backpressure(1, true);
+  sampled.clear();
+  for (auto r : p.requests) sampled.push_back(r == 1 ? 99 : 5);
+  ev = s.commit(p, sampled);                         // seq1 hits its stop token
+  bool stop_seen = false;
+  for (auto& e : ev) stop_seen |= e.request == 1 && e.finish && *e.finish == Finish::Stop;
+  CHECK(stop_seen);
+  p = s.plan();
+  CHECK(s.idle() || !p.empty());
+  // cancellation while a step is in flight
+  LiveScheduler c({1, 4, 4, 64, 4, 0});
+  c.submit({9, {1, 2}, 5, {}});
+  auto pc = c.plan();
+  auto ce = c.cancel(9);
+  CHECK(ce && *ce->finish == Finish::Cancelled && c.running() == 1);
+  CHECK(c.commit(pc, {3}).empty() && c.running() == 0 && c.idle());
+  c.submit({10, {1}, 2, {}});
+  c.plan();
+  CHECK(c.fail_all().size() == 1 && c.idle());
+  // PD simulation over the mock runtime
+  auto tr = std::make_shared<runtime::Trace>();
+  auto rep = run_mock(rankplan::compile(spec(1, 1, false)), {{1, 300, 4, 0, std::nullopt}, {2, 2000, 3, 0, std::nullopt}, {3, 50, 5, 2, 4u}}, {4, 64, 128}, tr);
+  CHECK(rep.completed == 2 && rep.cancelled == 1 && rep.transfers == 3 && rep.leaked_allocations == 0);
+  CHECK(rep.outputs.at(1).size() == 4 && rep.prefill_steps >= 3);
+  auto rep2 = run_mock(rankplan::compile(spec(1, 1, false)), {{1, 300, 4, 0, std::nullopt}, {2, 2000, 3, 0, std::nullopt}}, {4, 64, 128});
+  CHECK(rep2.outputs.at(1) == rep.outputs.at(1));     // repeatable
+}
+
+static void test_cpu_plan() {
+  using namespace cpu;
+  LogicalGraph g = from_dsl(R"(language inferfabric 1;
+model Acc { input x: tensor<f32>[2, 2]; const w: tensor<f32>[2, 2] = [1, 2, 3, 4]; const one: tensor<f32>[2, 2] = [1, 1, 1, 1];
+  state hist: tensor<f32>[2, 2] = [0, 0, 0, 0];
+  let scale = add(one, one); let p = matmul(x, w); let q = mul(p, scale); let r = relu(q); let dead = mul(p, p);
+  let out = add(r, hist); update hist = out; yield out; }
+plan Cpu for Acc { target = cpu_f32_v1; })");
+  PhysicalPlan plan = compile(g);
+  verify(plan);
+  CHECK(plan.folded_constants == 1 && plan.eliminated_nodes == 1 && plan.steps.size() == 4);
+  Executor ex(plan);
+  auto r1 = ex.run({{"x", {1, 0, 0, 1}}});
+  CHECK(r1.outputs.at("out") == (std::vector<float>{2, 4, 6, 8}));
+  auto r2 = ex.run({{"x", {1, 0, 0, 1}}});
+  CHECK(r2.outputs.at("out") == (std::vector<float>{4, 8, 12, 16}));   // state committed after the first run
+  PhysicalPlan back = decode_plan(encode_plan(plan));
+  CHECK(back.steps.size() == plan.steps.size() && back.arena_bytes == plan.arena_bytes);
+  PhysicalPlan broken = plan;
+  broken.steps[1].dependencies.clear();
+  CHECK_THROWS(Invalid, verify(broken));
+  broken = plan;
+  for (auto& b : broken.buffers)
+    if (b.storage == Storage::Temporary) b.offset = 0;   // everything aliased
+  CHECK_THROWS(Invalid, verify(broken));
+  Options o;
+  o.override_kernels["p"] = Kernel::MatmulBlockedF32V1;
+  CHECK(compile(g, o).steps[0].selection_reason == "forced by override");
+  o.override_kernels["p"] = Kernel::AddF32V1;
+  CHECK_THROWS(Invalid, compile(g, o));
+  CHECK_THROWS(Invalid, ex.run({{"y", {1}}}));
+}
+
+int main() {
+  std::pair<const char*, std::function<void()>> tests[] = {
+      {"state_pool", test_state_pool}, {"prefix_index", test_prefix_index}, {"paging", test_paging},
+      {"rankplan_runtime", test_rankplan_and_runtime}, {"transfer", test_transfer}, {"scheduler", test_scheduler}, {"cpu_plan", test_cpu_plan}};
+  for (auto& t : tests) {
+    int before = failures;
+    try {
+      t.second();
+    } catch (const std::exception& e) {
+      ++failures;
+      std::printf("FAIL %s: unexpected exception: %s\n", t.first, e.what());
+    }
+    std::printf("%s %s\n", failures == before ? "ok  " : "FAIL", t.first);
+  }
+  std::printf("%d checks, %d failures\n", checks, failures);
+  return failures ? 1 : 0;
+}
