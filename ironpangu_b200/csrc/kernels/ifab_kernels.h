@@ -75,6 +75,12 @@ int ifab_lm_head_argmax(const void* x, long ldx, const void* norm_w, float eps, 
                         uint64_t partial_bytes, int32_t* out_ids, float* out_vals, const IfabFabric* fab,
                         void* stream);
 
+/* ---- sampling on vocabulary-sharded logits: temperature, penalties, top-k <= 64, min-p, top-p, counter-based draw ---- */
+int ifab_sample_topk(const float* logits, long ld, int T, int V_local, int vocab_offset, int top_k,
+                     const float* inv_temperature, const float* top_p, const float* min_p, const int16_t* counts, long ldc,
+                     const float* penalties, const uint64_t* seeds, uint64_t* counters, void* scratch, uint64_t scratch_bytes,
+                     int32_t* out_ids, float* out_probs, const IfabFabric* fab, void* stream);
+
 /* ---- MLA (multi-head latent attention) decode path ---- */
 int ifab_mla_kv_write(const void* kv, long ldkv, const void* norm_w, float eps, float theta, const int32_t* positions,
                       const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens, void* cache,

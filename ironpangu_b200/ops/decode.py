@@ -206,3 +206,57 @@ def mla_decode_attention(q_lat: torch.Tensor, cache: torch.Tensor, positions: to
         T, H, latent, rope, keys_per_split, max_splits, scratch.data_ptr(), scratch.numel() * 4, w_kvb.data_ptr(), nope,
         vdim, out.data_ptr(), _rows(out), status_ptr, _stream()), "mla_decode_attention")
     return out
+
+
+def gqa_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
+                      k_cache: torch.Tensor, v_cache: torch.Tensor, *, heads: int, kv_heads: int, head_dim: int,
+                      rotary_dim: Optional[int] = None, theta: float = 1e6, status_ptr: Optional[int] = None) -> None:
+    """Rotate q and k of ``qkv`` = ``[T, (heads + 2*kv_heads) * head_dim]`` in place and append k / v to the paged caches
+    ``[pages, page_tokens, kv_heads, head_dim]``."""
+    T = qkv.shape[0]
+    num_pages, page_tokens = k_cache.shape[0], k_cache.shape[1]
+    check(_lib.load().ifab_gqa_rope_kv_write(qkv.data_ptr(), _rows(qkv), positions.data_ptr(), slots.data_ptr(),
+                                             page_table.data_ptr(), page_table.shape[1], page_tokens, k_cache.data_ptr(),
+                                             v_cache.data_ptr(), num_pages, T, heads, kv_heads, head_dim,
+                                             rotary_dim or head_dim, theta, status_ptr, _stream()), "gqa_rope_kv_write")
+
+
+def gqa_decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
+                         slots: torch.Tensor, page_table: torch.Tensor, *, heads: int, kv_heads: int, head_dim: int,
+                         scale: float, keys_per_split: int = 64, max_splits: int = 16, scratch: Optional[torch.Tensor] = None,
+                         out: Optional[torch.Tensor] = None, status_ptr: Optional[int] = None) -> torch.Tensor:
+    """Split-KV paged GQA attention; ``q`` is ``[T, >= heads*head_dim]`` (the q columns of the qkv buffer)."""
+    T = q.shape[0]
+    num_pages, page_tokens = k_cache.shape[0], k_cache.shape[1]
+    if scratch is None:
+        scratch = torch.empty(T * heads * max_splits * (head_dim + 2), dtype=torch.float32, device=q.device)
+    if out is None:
+        out = torch.empty(T, heads * head_dim, dtype=BF16, device=q.device)
+    check(_lib.load().ifab_gqa_decode_attention(q.data_ptr(), _rows(q), k_cache.data_ptr(), v_cache.data_ptr(),
+                                                positions.data_ptr(), slots.data_ptr(), page_table.data_ptr(),
+                                                page_table.shape[1], page_tokens, num_pages, scale, T, heads, kv_heads,
+                                                head_dim, keys_per_split, max_splits, scratch.data_ptr(), scratch.numel() * 4,
+                                                out.data_ptr(), _rows(out), status_ptr, _stream()), "gqa_decode_attention")
+    return out
+
+
+def sample_topk(logits: torch.Tensor, fabric, *, top_k: int = 50, inv_temperature: Optional[torch.Tensor] = None,
+                top_p: Optional[torch.Tensor] = None, min_p: Optional[torch.Tensor] = None,
+                counts: Optional[torch.Tensor] = None, penalties: Optional[torch.Tensor] = None,
+                seeds: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None, vocab_offset: int = 0,
+                scratch: Optional[torch.Tensor] = None, out_ids: Optional[torch.Tensor] = None,
+                out_probs: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Exact top-k / min-p / top-p sampling on vocabulary-sharded f32 logits ``[T, V_local]`` (cross-rank candidate
+    exchange inside the kernel). ``seeds``/``counters`` are int64 ``[T]``; counters advance on the device."""
+    T, V = logits.shape
+    nblocks = (V + 4095) // 4096
+    dev = logits.device
+    if scratch is None:
+        scratch = torch.empty(T * nblocks * 64 * 2, dtype=torch.float32, device=dev)
+    if out_ids is None:
+        out_ids = torch.empty(T, dtype=torch.int32, device=dev)
+    check(_lib.load().ifab_sample_topk(logits.data_ptr(), logits.stride(0), T, V, vocab_offset, top_k, _ptr(inv_temperature),
+                                       _ptr(top_p), _ptr(min_p), _ptr(counts), 0 if counts is None else counts.stride(0),
+                                       _ptr(penalties), _ptr(seeds), _ptr(counters), scratch.data_ptr(), scratch.numel() * 4,
+                                       out_ids.data_ptr(), _ptr(out_probs), C.byref(fabric.desc), _stream()), "sample_topk")
+    return out_ids

@@ -94,6 +94,34 @@ def main():
     assert all(a == all_ids[0] for a in all_ids), "ranks disagree on the sampled tokens"
     assert fab.status() == 0
     print(f"rank {rank}: ok tiny model tp={world}", flush=True)
+    # 4. dense GQA model (TP = world when the tiny model's kv heads divide) + cross-rank top-k sampling
+    from ironpangu_b200.models import dense_gqa as D
+    dcfg = D.DenseConfig.tiny(2)
+    if dcfg.kv_heads % world == 0:
+        dfull = D.random_full_weights(dcfg, 0)
+        ddec = D.DenseDecoder(dcfg, D.shard_weights(dcfg, dfull, rank, world, "cuda"), fab, max_tokens=8, max_context=64, keep_logits=True)
+        dref = D.forward_ref(dcfg, dfull, torch.tensor(prompt, device="cuda"), tp=world)
+        n = len(prompt)
+        ddec.tokens[:n].copy_(torch.tensor(prompt, dtype=torch.int32))
+        ddec.positions[:n].copy_(torch.arange(n, dtype=torch.int32))
+        ddec.slots[:n].zero_()
+        ddec.forward(n)
+        dvl = dcfg.vocab // world
+        torch.testing.assert_close(ddec.logits[:n], dref[:, rank * dvl:(rank + 1) * dvl], rtol=2e-2, atol=2e-2)
+        seeds = torch.full((n,), 5, dtype=torch.int64, device="cuda")
+        counters = torch.zeros(n, dtype=torch.int64, device="cuda")
+        invt = torch.full((n,), 1 / 0.7, device="cuda")
+        ids = K.sample_topk(ddec.logits[:n], fab, top_k=50, inv_temperature=invt, seeds=seeds, counters=counters, vocab_offset=rank * dvl)
+        full_logits = [torch.empty_like(ddec.logits[:n]) for _ in range(world)]
+        dist.all_gather(full_logits, ddec.logits[:n].contiguous())
+        allowed = torch.cat(full_logits, 1).topk(50, -1).indices
+        for t in range(n):
+            assert int(ids[t]) in allowed[t].tolist()
+        got = [torch.empty_like(ids) for _ in range(world)]
+        dist.all_gather(got, ids)
+        assert all(torch.equal(got[0], x) for x in got), "ranks drew different tokens"
+        print(f"rank {rank}: ok dense gqa + sampling tp={world}", flush=True)
+    assert fab.status() == 0
     torch.cuda.synchronize()
     dist.barrier()
     fab.close()

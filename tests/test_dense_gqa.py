@@ -1,0 +1,127 @@
+"""Dense GQA decoder + device sampling against PyTorch fp32 references (single GPU)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BF16 = torch.bfloat16
+
+
+def _setup(max_tokens=8, num_slots=2):
+    from ironpangu_b200.models.dense_gqa import DenseConfig, DenseDecoder, random_full_weights, shard_weights
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    cfg = DenseConfig.tiny(2)
+    full = random_full_weights(cfg, 0)
+    fab = Fabric(0, 1)
+    dec = DenseDecoder(cfg, shard_weights(cfg, full, 0, 1, "cuda"), fab, max_tokens=max_tokens, max_context=128,
+                       num_slots=num_slots, keep_logits=True)
+    return cfg, full, fab, dec
+
+
+def test_two_interleaved_sequences_match_oracle():
+    """Rows of two sequences at different positions share every launch (continuous batching)."""
+    from ironpangu_b200.models.dense_gqa import forward_ref
+
+    cfg, full, fab, dec = _setup()
+    g = torch.Generator().manual_seed(4)
+    a = torch.randint(0, cfg.vocab, (21,), generator=g).tolist()
+    b = torch.randint(0, cfg.vocab, (9,), generator=g).tolist()
+    ra, rb = forward_ref(cfg, full, torch.tensor(a, device="cuda")), forward_ref(cfg, full, torch.tensor(b, device="cuda"))
+    pa = pb = 0
+    while pa < len(a) or pb < len(b):
+        na, nb = min(5, len(a) - pa), min(3, len(b) - pb)     # chunk of A + chunk of B in one step
+        toks = a[pa:pa + na] + b[pb:pb + nb]
+        pos = list(range(pa, pa + na)) + list(range(pb, pb + nb))
+        slot = [0] * na + [1] * nb
+        n = len(toks)
+        dec.tokens[:n].copy_(torch.tensor(toks, dtype=torch.int32))
+        dec.positions[:n].copy_(torch.tensor(pos, dtype=torch.int32))
+        dec.slots[:n].copy_(torch.tensor(slot, dtype=torch.int32))
+        dec.forward(n)
+        lg = dec.logits[:n]
+        torch.testing.assert_close(lg[:na], ra[pa:pa + na], rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(lg[na:], rb[pb:pb + nb], rtol=2e-2, atol=2e-2)
+        assert torch.equal(dec.next_ids[:n].long(), lg.argmax(-1))
+        pa, pb = pa + na, pb + nb
+    assert fab.status() == 0
+    fab.close()
+
+
+def test_graph_replay_equals_eager():
+    cfg, full, fab, dec = _setup(1, 1)
+    outs = []
+    for i, t in enumerate([3, 77, 500, 9]):
+        dec.tokens.fill_(t); dec.positions.fill_(i); dec.slots.zero_()
+        dec.forward(1)
+        outs.append(dec.logits[:1].clone())
+    dec.reset()
+    dec.capture(1)
+    for i, t in enumerate([3, 77, 500, 9]):
+        dec.tokens.fill_(t); dec.positions.fill_(i)
+        dec._graph.replay()
+        assert torch.equal(dec.logits[:1], outs[i])
+    fab.close()
+
+
+def test_sampling_topk_topp_minp_exact():
+    from ironpangu_b200.ops import decode as K
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    fab = Fabric(0, 1)
+    T, V, k = 4, 151936, 50
+    g = torch.Generator(device="cuda").manual_seed(1)
+    logits = torch.randn(T, V, generator=g, device="cuda") * 3
+    invt = torch.tensor([1 / 0.7, 0.0, 1.0, 2.0], device="cuda")
+    topp = torch.tensor([1.0, 1.0, 0.8, 1.0], device="cuda")
+    minp = torch.tensor([0.0, 0.0, 0.0, 0.3], device="cuda")
+    seeds = torch.arange(T, dtype=torch.int64, device="cuda") + 11
+    counters = torch.zeros(T, dtype=torch.int64, device="cuda")
+    probs = torch.empty(T, device="cuda")
+    draws = torch.stack([K.sample_topk(logits, fab, top_k=k, inv_temperature=invt, top_p=topp, min_p=minp, seeds=seeds,
+                                       counters=counters, out_probs=probs).clone() for _ in range(400)])
+    assert int(counters[0]) == 400                       # the counter advances on the device
+    # allowed sets from a plain PyTorch restatement
+    for t in range(T):
+        scaled = logits[t] * (invt[t] if invt[t] > 0 else 1.0)
+        vals, idx = scaled.topk(k)
+        p = torch.softmax(vals, -1)
+        keep = torch.ones(k, dtype=torch.bool, device="cuda")
+        if minp[t] > 0:
+            keep &= p >= minp[t] * p[0]
+        if topp[t] < 1:
+            pk = p * keep
+            excl = torch.cumsum(pk, 0) - pk
+            keep &= excl < topp[t] * pk.sum()
+        allowed = set(idx[keep].tolist())
+        seen = set(draws[:, t].tolist())
+        if invt[t] <= 0:
+            assert seen == {int(logits[t].argmax())}
+        else:
+            assert seen <= allowed, (t, seen - allowed)
+            assert len(seen) > 1 or len(allowed) == 1
+    # empirical frequencies of row 0 follow the renormalised top-k distribution
+    vals, idx = (logits[0] / 0.7).topk(k)
+    p = torch.softmax(vals, -1)
+    top = int(idx[0])
+    freq = (draws[:, 0] == top).float().mean().item()
+    assert abs(freq - float(p[0])) < 0.08
+    assert fab.status() == 0
+    fab.close()
+
+
+def test_sampling_penalties():
+    from ironpangu_b200.ops import decode as K
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    fab = Fabric(0, 1)
+    V = 5000
+    logits = torch.zeros(1, V, device="cuda")
+    logits[0, 7] = 5.0
+    logits[0, 9] = 4.0
+    counts = torch.zeros(1, V, dtype=torch.int16, device="cuda")
+    counts[0, 7] = 3
+    pen = torch.tensor([[1.0, 0.5, 0.1]], device="cuda")     # repetition, frequency, presence
+    invt = torch.zeros(1, device="cuda")                       # greedy on penalised logits: 5 - 1.5 - 0.1 = 3.4 < 4
+    out = K.sample_topk(logits, fab, top_k=8, inv_temperature=invt, counts=counts, penalties=pen)
+    assert int(out[0]) == 9
+    fab.close()
