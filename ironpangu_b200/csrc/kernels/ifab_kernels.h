@@ -57,6 +57,9 @@ int ifab_gemv_allreduce_bf16(const void* x, long ldx, const void* w, const void*
 int ifab_gemm_bf16(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int out_f32, const void* residual,
                    long ldr, int M, int N, int K, uint32_t* status, void* stream);
 
+int ifab_gemm_allreduce_bf16(const void* a, long lda, const void* b, long ldb, void* const* out_peers, long ldc, const void* residual,
+                             long ldr, int M, int N, int K, const IfabFabric* fab, void* stream);
+
 /* ---- MoE decode path (owner-local expert parallelism) ---- */
 int ifab_router_topk(const void* x, long ldx, const void* norm_w, float eps, const float* w_router, const float* bias,
                      float* logits, int32_t* ids, float* wts, int T, int D, int E, int topk, int scoring, int renorm,

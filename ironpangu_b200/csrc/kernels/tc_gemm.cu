@@ -11,15 +11,13 @@
 // stored everywhere in this library, so no transposes are needed. M, N and K tails are handled by
 // TMA zero fill plus masked stores. Used for prefill chunks and batched decode (M >= 16); the
 // reference's counterpart is aclnnMatmul on [T<=4096, K] activations (token_executor.h:387-456).
-#include "tc_common.cuh"
+#include "tc_gemm_core.cuh"
 #include "ifab_kernels.h"
 
 using namespace ifab;
 using namespace ifab::tc;
 
 namespace {
-
-constexpr int BM = 128, BK = 64, UMMA_K = 16;
 
 struct GemmParams {
   void* c; long ldc; int out_f32;
@@ -29,140 +27,62 @@ struct GemmParams {
   uint32_t spin_limit;
 };
 
-template <int BN>
-struct Cfg {
-  static constexpr int STAGES = BN == 256 ? 4 : 6;
-  static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-};
+// store 32 consecutive columns of one row (values already final)
+__device__ __forceinline__ void store_row32(const GemmParams& p, int row, int col, float* v) {
+  if (row >= p.M || col >= p.N) return;
+  const int nvalid = min(32, p.N - col);
+  if (p.residual) {
+    const bf16* r = p.residual + (long)row * p.ldr + col;
+    for (int i = 0; i < nvalid; ++i) v[i] = bf16_round(v[i]) + __bfloat162float(r[i]);
+  }
+  if (p.out_f32) {
+    float* out = reinterpret_cast<float*>(p.c) + (long)row * p.ldc + col;
+    if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) reinterpret_cast<float4*>(out)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+      for (int i = 0; i < nvalid; ++i) out[i] = v[i];
+    }
+  } else {
+    bf16* out = reinterpret_cast<bf16*>(p.c) + (long)row * p.ldc + col;
+    if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(out)[i] = pack8(v + 8 * i);
+    } else {
+      for (int i = 0; i < nvalid; ++i) out[i] = __float2bfloat16_rn(v[i]);
+    }
+  }
+}
 
 template <int BN>
 __global__ void __launch_bounds__(192) tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                       const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
-  using C = Cfg<BN>;
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
-  uint64_t* empty = full + C::STAGES;
-  uint64_t* acc_full = empty + C::STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
+  Pipe<BN> pipe;
+  pipe.setup(smem_raw, &tmap_a, &tmap_b);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int num_kb = (p.K + BK - 1) / BK;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
-    }
-    mbar_init(acc_full, 1);
-    *abort_flag = 0;
-    mbar_fence_init();
-    tma_prefetch_desc(&tmap_a);
-    tma_prefetch_desc(&tmap_b);
-  }
-  if (warp == 1) tmem_alloc(tmem_slot, BN);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
   grid_dep_launch();
   grid_dep_wait();
-
   if (warp == 0 && lane == 0) {
-    // ---------------- producer ----------------
-    int issued = 0;
-    for (int kb = 0; kb < num_kb; ++kb) {
-      const int s = kb % C::STAGES;
-      const uint32_t round = kb / C::STAGES;
-      if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, p.spin_limit)) { *abort_flag = 1; break; }
-      if (*abort_flag) break;
-      unsigned char* a_dst = smem + s * C::STAGE_BYTES;
-      mbar_expect_tx(&full[s], C::STAGE_BYTES);
-      tma_load_2d(a_dst, &tmap_a, &full[s], kb * BK, m0);
-      tma_load_2d(a_dst + C::A_BYTES, &tmap_b, &full[s], kb * BK, n0);
-      issued = kb + 1;
-    }
-    if (*abort_flag) {
-      // drain: every copy this thread issued must land before the CTA may exit
-      for (int kb = max(0, issued - C::STAGES); kb < issued; ++kb) mbar_wait(&full[kb % C::STAGES], (kb / C::STAGES) & 1, p.spin_limit);
-      if (p.status) atomicOr(p.status, IFAB_STATUS_MBAR_TIMEOUT);
-    }
+    pipe.produce(&tmap_a, &tmap_b, num_kb, m0, n0, -1, p.spin_limit, p.status);
   } else if (warp == 1 && lane == 0) {
-    // ---------------- MMA issuer ----------------
-    constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
-    bool ok = true;
-    for (int kb = 0; kb < num_kb && ok; ++kb) {
-      const int s = kb % C::STAGES;
-      if (!mbar_wait(&full[s], (kb / C::STAGES) & 1, p.spin_limit) || *abort_flag) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
-      const uint64_t da = umma_desc_sw128(a_addr), db = umma_desc_sw128(a_addr + C::A_BYTES);
-#pragma unroll
-      for (int k = 0; k < BK / UMMA_K; ++k) {
-        // advancing 16 bf16 = 32 bytes along K inside the swizzle atom = +2 in 16-byte units
-        umma_bf16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, kb > 0 || k > 0);
-      }
-      umma_commit(&empty[s]);   // frees the stage once these MMAs have read it
-    }
-    if (!ok) {
-      *abort_flag = 1;
-      if (p.status) atomicOr(p.status, IFAB_STATUS_MBAR_TIMEOUT);
-    }
-    umma_commit(acc_full);      // accumulator complete (or abandoned: the epilogue checks the flag)
+    pipe.mma(num_kb, p.spin_limit, p.status);
   } else if (warp >= 2) {
-    // ---------------- epilogue ----------------
-    const bool ready = mbar_wait(acc_full, 0, p.spin_limit);
-    tc_fence_after();
-    if (!ready) {
-      *abort_flag = 1;
-      if (lane == 0 && p.status) atomicOr(p.status, IFAB_STATUS_MBAR_TIMEOUT);
-    }
-    const int q = warp & 3;                       // TMEM lane quarter this warp may read
-    const int row = m0 + q * 32 + lane;
-    if (ready && !*abort_flag) {
+    if (pipe.wait_accumulator(p.spin_limit, p.status)) {
+      const int q = warp & 3;                       // TMEM lane quarter this warp may read
+      const int row = m0 + q * 32 + lane;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld_32x32(pipe.tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
         tmem_ld_wait();
-        const int col = n0 + c0;
-        if (row < p.M && col < p.N) {
-          const int nvalid = min(32, p.N - col);
-          if (p.residual) {
-            const bf16* r = p.residual + (long)row * p.ldr + col;
-            for (int i = 0; i < nvalid; ++i) v[i] = bf16_round(v[i]) + __bfloat162float(r[i]);
-          }
-          if (p.out_f32) {
-            float* out = reinterpret_cast<float*>(p.c) + (long)row * p.ldc + col;
-            if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) reinterpret_cast<float4*>(out)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            } else {
-              for (int i = 0; i < nvalid; ++i) out[i] = v[i];
-            }
-          } else {
-            bf16* out = reinterpret_cast<bf16*>(p.c) + (long)row * p.ldc + col;
-            if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(out)[i] = pack8(v + 8 * i);
-            } else {
-              for (int i = 0; i < nvalid; ++i) out[i] = __float2bfloat16_rn(v[i]);
-            }
-          }
-        }
+        store_row32(p, row, n0 + c0, v);
       }
     }
   }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, BN);
-  }
+  pipe.teardown();
 }
 
 template <int BN>
@@ -234,3 +154,4 @@ extern "C" int ifab_gemm_bf16(const void* a, long lda, const void* b, long ldb, 
   cudaStream_t s = (cudaStream_t)stream;
   return BN == 256 ? launch<256>(ta, tb, p, s) : launch<128>(ta, tb, p, s);
 }
+

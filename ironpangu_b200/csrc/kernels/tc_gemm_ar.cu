@@ -1,0 +1,200 @@
+// Row-parallel bf16 GEMM fused with a two-shot all-reduce (reduce-scatter + all-gather) over NVLink peer
+// memory:  Y = sum_ranks A_r[M,K_r] * B_r[N,K_r]^T (+ residual), every rank ends with the full result.
+//
+// Every rank runs the same grid of 128 x BN tiles over its K shard (tcgen05 main loop of
+// tc_gemm_core.cuh). Tile t is owned by rank t % world.
+//   non-owner  accumulator -> bf16 tile in shared memory (the drained TMA ring) -> coalesced 512-byte row
+//              stores into slot (t, rank) of the OWNER's staging area -> system fence -> flag; the CTA
+//              then exits, it never waits
+//   owner      waits - bounded - for the other ranks' flags of its tile, sums the `world` partials in rank
+//              order (its own partial rounded to bf16 like the others, so the result does not depend on
+//              who owns a tile), adds the residual, rounds, and stores the finished rows into the output
+//              buffer of EVERY rank (the output lives in symmetric memory: out_peers[r] is rank r's
+//              buffer), then raises each peer's "final" flag of the tile
+//   last CTA   (by ticket) waits for the final flags of the tiles this rank does not own, so when the
+//              kernel completes on a rank its output is complete, then advances the call counter
+// Bytes crossing NVLink per rank: 2 * (world-1)/world * M*N*2 - the minimum of a bf16 reduce-scatter +
+// all-gather - and they move tile by tile underneath the main loops of later tiles. Only same-index tiles
+// synchronise across ranks; CTAs are dispatched in index order on every rank, so waits are short and
+// cannot form a cycle. No TMA multicast and no TMA access to peer memory is used: peers are written with
+// plain coalesced stores. Reference: linear(tp_columns) + allreduce on the bulk collective domain
+// (native/src/token_executor.h:374-404, docs/validation/2026-10-18-bulk-domains).
+#include "tc_gemm_core.cuh"
+#include "ifab_kernels.h"
+
+using namespace ifab;
+using namespace ifab::tc;
+
+namespace {
+
+struct ArParams {
+  bf16* out_peers[IFAB_MAX_RANKS];   // out_peers[rank] is the local output; same shape / ldc on every rank
+  long ldc;
+  const bf16* residual; long ldr;
+  int M, N, K;
+  FabricView fv;
+  uint64_t* seq; uint32_t* done;
+  int tiles_n, ntiles;
+  uint32_t spin_limit;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(192) tc_gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                const __grid_constant__ CUtensorMap tmap_b, ArParams a) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ int s_flag_ok, s_last;
+  Pipe<BN> pipe;
+  pipe.setup(smem_raw, &tmap_a, &tmap_b);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x;
+  const int m0 = (tile / a.tiles_n) * BM, n0 = (tile % a.tiles_n) * BN;
+  const int num_kb = (a.K + BK - 1) / BK;
+  const int world = a.fv.world, rank = a.fv.rank, owner = tile % world;
+  grid_dep_launch();
+  grid_dep_wait();
+  const uint64_t epoch = *reinterpret_cast<volatile uint64_t*>(a.seq) + 1;
+  const uint32_t par = (uint32_t)(epoch & 1);
+  constexpr size_t TILE_BYTES = (size_t)BM * BN * 2;
+  constexpr int ROW_PAD = BN + 8;                       // bf16 elements per padded shared-memory row
+  auto half = [&](int r) { return a.fv.data[r] + (size_t)par * a.fv.data_half_bytes; };
+  auto flags = [&](int r) { return a.fv.flags[r] + (size_t)par * a.fv.flag_half_words; };
+  if (warp == 0 && lane == 0) {
+    pipe.produce(&tmap_a, &tmap_b, num_kb, m0, n0, -1, a.spin_limit, a.fv.status);
+  } else if (warp == 1 && lane == 0) {
+    pipe.mma(num_kb, a.spin_limit, a.fv.status);
+  } else if (warp >= 2) {
+    const bool ok = pipe.wait_accumulator(a.spin_limit, a.fv.status);
+    const int q = warp & 3, trow = q * 32 + lane, et = threadIdx.x - 64, ew = warp - 2;   // epilogue thread / warp ids
+    const uint32_t tm = pipe.tmem_base + ((uint32_t)(q * 32) << 16);
+    bf16* tile_s = reinterpret_cast<bf16*>(pipe.smem);   // the stage ring is drained once the accumulator is complete
+    // accumulator -> bf16 rows in shared memory
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        tmem_ld_32x32(tm + (uint32_t)c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(tile_s + (size_t)trow * ROW_PAD + c0 + 8 * i) = pack8(v + 8 * i);
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    constexpr int CPR = BN / 8;                          // 16-byte chunks per row
+    if (world > 1 && rank != owner) {
+      // ---- push the partial tile: warp-per-row, 512 contiguous bytes per store instruction ----
+      bf16* dst = reinterpret_cast<bf16*>(half(owner) + ((size_t)(tile / world) * world + rank) * TILE_BYTES);
+      for (int r = ew; r < BM; r += 4)
+        for (int c = lane; c < CPR; c += 32)
+          *reinterpret_cast<uint4*>(dst + (size_t)r * BN + c * 8) = *reinterpret_cast<const uint4*>(tile_s + (size_t)r * ROW_PAD + c * 8);
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et == 0) st_release_sys(flags(owner) + (size_t)tile * world + rank, epoch);
+    } else {
+      // ---- owner (or single rank): reduce in rank order, add the residual, publish to every rank ----
+      if (et == 0) s_flag_ok = 1;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (world > 1 && et < world && et != rank) {
+        if (!wait_flag_bounded(flags(rank) + (size_t)tile * world + et, epoch, a.fv.spin_limit)) {
+          s_flag_ok = 0;
+          atomicOr(a.fv.status, IFAB_STATUS_PEER_TIMEOUT);
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ok && s_flag_ok) {
+        const bf16* stage = reinterpret_cast<const bf16*>(half(rank) + (size_t)(tile / world) * world * TILE_BYTES);
+        for (int r = ew; r < BM; r += 4) {
+          const int row = m0 + r;
+          if (row >= a.M) break;
+          for (int c = lane; c < CPR; c += 32) {
+            const int col = n0 + c * 8;
+            if (col >= a.N) continue;
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int src = 0; src < world; ++src) {
+              float f[8];
+              if (src == rank) unpack8(*reinterpret_cast<const uint4*>(tile_s + (size_t)r * ROW_PAD + c * 8), f);
+              else unpack8(__ldcg(reinterpret_cast<const uint4*>(stage + (size_t)src * BM * BN + (size_t)r * BN + c * 8)), f);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) v[k] += f[k];
+            }
+            if (a.residual) {
+              float f[8];
+              unpack8(*reinterpret_cast<const uint4*>(a.residual + (long)row * a.ldr + col), f);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) v[k] = bf16_round(v[k]) + f[k];
+            }
+            const uint4 packed = pack8(v);
+            for (int dst = 0; dst < world; ++dst) *reinterpret_cast<uint4*>(a.out_peers[dst] + (long)row * a.ldc + col) = packed;
+          }
+        }
+      }
+      if (world > 1) {
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et < world && et != rank) st_release_sys(flags(et) + (size_t)a.ntiles * world + tile, epoch);
+      }
+    }
+  }
+  pipe.teardown();
+  // ---- the last CTA of this rank collects the final flags of the tiles owned by peers ----
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = (atomicAdd(a.done, 1u) == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (world > 1) {
+    for (int t = threadIdx.x; t < a.ntiles; t += blockDim.x) {
+      if (t % world == rank) continue;
+      if (!wait_flag_bounded(flags(rank) + (size_t)a.ntiles * world + t, epoch, a.fv.spin_limit)) atomicOr(a.fv.status, IFAB_STATUS_PEER_TIMEOUT);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *a.done = 0;
+    *a.seq = epoch;
+    __threadfence();
+  }
+}
+
+template <int BN>
+int launch_ar(const CUtensorMap& ta, const CUtensorMap& tb, ArParams& a, cudaStream_t s) {
+  auto k = tc_gemm_allreduce_kernel<BN>;
+  if (int rc = opt_in_smem(k, Cfg<BN>::SMEM)) return rc;
+  static_assert((size_t)BM * (BN + 8) * 2 <= (size_t)Cfg<BN>::STAGES * Cfg<BN>::STAGE_BYTES, "tile must fit the drained ring");
+  a.tiles_n = (a.N + BN - 1) / BN;
+  a.ntiles = a.tiles_n * ((a.M + BM - 1) / BM);
+  if (a.fv.world > 1) {
+    const size_t owned = (a.ntiles + a.fv.world - 1) / a.fv.world;
+    if (owned * a.fv.world * (size_t)BM * BN * 2 > a.fv.data_half_bytes) return -3;
+    if ((size_t)a.ntiles * (a.fv.world + 1) > a.fv.flag_half_words) return -4;
+  }
+  return launch_chain(k, dim3(a.ntiles), dim3(192), (size_t)Cfg<BN>::SMEM, s, ta, tb, a);
+}
+
+}  // namespace
+
+// `out_peers`: world pointers to the output buffer of every rank as mapped into this process (entry `rank` is
+// the local one). With world == 1 only entry 0 is used. N and ldc must be multiples of 8.
+extern "C" int ifab_gemm_allreduce_bf16(const void* a, long lda, const void* b, long ldb, void* const* out_peers, long ldc,
+                                        const void* residual, long ldr, int M, int N, int K, const IfabFabric* fab,
+                                        void* stream) {
+  if (M < 1 || N < 1 || K < 8 || K % 8 || lda % 8 || ldb % 8 || ldc % 8 || N % 8 || (residual && ldr % 8)) return -1;
+  CUtensorMap ta, tb;
+  const int BN = N > 128 ? 256 : 128;
+  if (int rc = make_tmap_bf16_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)BN)) return rc;
+  ArParams p;
+  if (int rc = fabric_view(fab, &p.fv)) return rc;
+  for (int r = 0; r < IFAB_MAX_RANKS; ++r) p.out_peers[r] = r < fab->world ? (bf16*)out_peers[r] : nullptr;
+  for (int r = 0; r < fab->world; ++r)
+    if (p.out_peers[r] == nullptr || (reinterpret_cast<uintptr_t>(p.out_peers[r]) & 15)) return -1;
+  p.ldc = ldc;
+  p.residual = (const bf16*)residual;
+  p.ldr = ldr;
+  p.M = M; p.N = N; p.K = K;
+  p.seq = fab->seq;
+  p.done = fab->done;
+  p.spin_limit = 4000000u;
+  cudaStream_t s = (cudaStream_t)stream;
+  return BN == 256 ? launch_ar<256>(ta, tb, p, s) : launch_ar<128>(ta, tb, p, s);
+}

@@ -25,3 +25,23 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, residual: Optional[torch.Tensor] =
                                      0 if residual is None else residual.stride(0), M, N, K, status_ptr,
                                      torch.cuda.current_stream().cuda_stream), "gemm")
     return out
+
+
+def gemm_allreduce(a: torch.Tensor, b: torch.Tensor, fabric, out, *, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-parallel GEMM fused with a two-shot all-reduce over NVLink peer memory:
+    ``C = sum_ranks A_r @ B_r.T (+ residual)``; ``A_r`` = ``[M, K_local]``, ``B_r`` = ``[N, K_local]``.
+
+    ``out`` is a :class:`~ironpangu_b200.parallel.fabric.SymmetricTensor` ``[M, N]`` (tile owners store finished rows
+    into every rank's buffer). ``residual`` may be ``out.tensor`` itself (in-place residual update). The fabric staging
+    area must hold ``ceil(tiles/world)*world * 128*BN*2`` bytes per half and ``tiles*(world+1)`` flag words."""
+    import ctypes as C
+    M, K = a.shape
+    N = b.shape[0]
+    y = out.tensor
+    assert y.shape == (M, N) and y.dtype == BF16 and y.is_contiguous()
+    check(_lib.load().ifab_gemm_allreduce_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.peer_ptrs, y.stride(0),
+                                               None if residual is None else residual.data_ptr(),
+                                               0 if residual is None else residual.stride(0), M, N, K,
+                                               C.byref(fabric.desc), torch.cuda.current_stream().cuda_stream),
+          "gemm_allreduce")
+    return y

@@ -106,6 +106,12 @@ class Fabric:
         """Number of fused-collective launches completed on this rank."""
         return self._peek(self.desc.seq, C.c_uint64)
 
+    # -- symmetric tensors ---------------------------------------------------------------------------
+    def symmetric_empty(self, shape, dtype=torch.bfloat16) -> "SymmetricTensor":
+        """Collective: allocate one zero-filled buffer of this shape on every rank and map all of them into every
+        process. Kernels that publish results to all ranks (fused GEMM + all-reduce) write through ``peer_ptrs``."""
+        return SymmetricTensor(self, tuple(int(d) for d in shape), dtype)
+
     def close(self) -> None:
         if getattr(self, "base", None) is None:
             return
@@ -127,3 +133,57 @@ class Fabric:
             self.close()
         except Exception:
             pass
+
+
+class _CudaBuffer:
+    """Minimal ``__cuda_array_interface__`` holder so torch can view memory this library allocated."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class SymmetricTensor:
+    """One buffer per rank, each mapped into every process. ``tensor`` is the local view; ``peer_ptrs`` is a
+    ``void*[8]`` with every rank's base address as seen from this process (entry ``rank`` is the local one)."""
+
+    def __init__(self, fabric: "Fabric", shape, dtype):
+        self.fabric, self.shape, self.dtype = fabric, shape, dtype
+        n = 1
+        for d in shape:
+            n *= d
+        self.nbytes = max(256, (n * torch.empty((), dtype=dtype).element_size() + 255) // 256 * 256)
+        lib = fabric.lib
+        base = C.c_void_p()
+        with torch.cuda.device(fabric.device):
+            _lib.check(lib.ifab_device_alloc(C.byref(base), self.nbytes), "symmetric alloc")
+        self.base = base.value
+        self._imported = []
+        ptrs = [0] * _lib.MAX_RANKS
+        ptrs[fabric.rank] = self.base
+        if fabric.world > 1:
+            import torch.distributed as dist
+            handle = C.create_string_buffer(64)
+            _lib.check(lib.ifab_ipc_export(self.base, handle), "ipc export")
+            handles = [None] * fabric.world
+            dist.all_gather_object(handles, bytes(handle.raw), group=fabric.group)
+            for r, h in enumerate(handles):
+                if r == fabric.rank:
+                    continue
+                out = C.c_void_p()
+                with torch.cuda.device(fabric.device):
+                    _lib.check(lib.ifab_ipc_import(h, C.byref(out)), f"ipc import from rank {r}")
+                ptrs[r] = out.value
+                self._imported.append(out.value)
+            dist.barrier(group=fabric.group)
+        self.peer_ptrs = (C.c_void_p * _lib.MAX_RANKS)(*[p or None for p in ptrs])
+        raw = torch.as_tensor(_CudaBuffer(self.base, self.nbytes), device=fabric.device)
+        self.tensor = raw[: n * torch.empty((), dtype=dtype).element_size()].view(dtype).view(*shape)
+
+    def close(self) -> None:
+        if self.base is None:
+            return
+        torch.cuda.synchronize()
+        for p in self._imported:
+            self.fabric.lib.ifab_ipc_close(p)
+        self.fabric.lib.ifab_device_free(self.base)
+        self.base = None

@@ -1,0 +1,93 @@
+"""Worker for the bulk (prefill-sized) fused kernels: tcgen05 GEMM + two-shot all-reduce over peer memory.
+Run under torch.distributed.run; prints timing of the fused kernel vs cuBLAS + NCCL when BULK_BENCH=1."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+BF16 = torch.bfloat16
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    from ironpangu_b200.ops.gemm import gemm_allreduce
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    fab = Fabric(rank, world, data_half_bytes=80 << 20, flag_half_words=8192, spin_limit=4_000_000)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    for M, N, Kl in [(128, 256, 64), (512, 1024, 256), (300, 520, 128), (2048, 4096, 512)]:
+        a = torch.randn(M, Kl * world, generator=g, device="cuda").to(BF16)
+        b = (torch.randn(N, Kl * world, generator=g, device="cuda") * 0.05).to(BF16)
+        res = torch.randn(M, N, generator=g, device="cuda").to(BF16)
+        al, bl = a[:, rank * Kl:(rank + 1) * Kl].contiguous(), b[:, rank * Kl:(rank + 1) * Kl].contiguous()
+        ref = torch.zeros(M, N, device="cuda")
+        for r in range(world):
+            ref += (a[:, r * Kl:(r + 1) * Kl].float() @ b[:, r * Kl:(r + 1) * Kl].float().T).to(BF16).float()
+        ref = ref.to(BF16).float() + res.float()
+        sym = fab.symmetric_empty((M, N))
+        for _ in range(3):   # repeated calls exercise the parity double buffering
+            y = gemm_allreduce(al, bl, fab, sym, residual=res)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=3e-2)
+        ys = [torch.empty_like(y) for _ in range(world)]
+        dist.all_gather(ys, y)
+        assert all(torch.equal(ys[0], t) for t in ys), "ranks hold different results"
+    assert fab.status() == 0
+    print(f"rank {rank}: ok gemm_allreduce bulk", flush=True)
+
+    if os.environ.get("BULK_BENCH") == "1":
+        M, N, Kl = 4096, 4096, 4096 // world
+        a = torch.randn(M, Kl, device="cuda").to(BF16)
+        b = torch.randn(N, Kl, device="cuda").to(BF16)
+        res = torch.randn(M, N, device="cuda").to(BF16)
+        out = torch.empty(M, N, dtype=BF16, device="cuda")
+        sym = fab.symmetric_empty((M, N))
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+        def timed(fn, iters=10):
+            for _ in range(3):
+                fn()
+            ts = []
+            for _ in range(iters):
+                flush.zero_()
+                dist.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ts.append(float(t))
+            ts.sort()
+            return ts[len(ts) // 2]
+
+        def baseline():
+            torch.matmul(a, b.T, out=out)
+            dist.all_reduce(out)
+            out.add_(res)
+
+        t_f = timed(lambda: gemm_allreduce(a, b, fab, sym, residual=res))
+        t_b = timed(baseline)
+        link_bytes = 2 * (world - 1) / world * M * N * 2
+        t_link = link_bytes / 770e9 * 1e3
+        t_mma = 2.0 * M * N * Kl / 1.6705e15 * 1e3
+        if rank == 0:
+            print(json.dumps({"shape": f"{M}x{N}x{Kl}*{world}", "fused_ms": round(t_f, 4), "cublas_nccl_ms": round(t_b, 4),
+                              "roofline_ms": round(max(t_link, t_mma), 4), "link_ms": round(t_link, 4), "mma_ms": round(t_mma, 4),
+                              "fraction_of_roofline": round(max(t_link, t_mma) / t_f, 3)}), flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    fab.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

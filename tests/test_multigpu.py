@@ -33,3 +33,11 @@ def test_fused_collectives_and_tiny_model(world):
         pytest.skip(f"needs {world} GPUs")
     out = _run(world, "multigpu_worker.py")
     assert out.count("ok tiny model") == world
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_bulk_gemm_allreduce(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    out = _run(world, "multigpu_bulk_worker.py")
+    assert out.count("ok gemm_allreduce bulk") == world
