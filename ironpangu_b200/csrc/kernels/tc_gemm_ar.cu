@@ -1,11 +1,12 @@
 // Row-parallel bf16 GEMM fused with a two-shot all-reduce (reduce-scatter + all-gather) over NVLink peer
 // memory:  Y = sum_ranks A_r[M,K_r] * B_r[N,K_r]^T (+ residual), every rank ends with the full result.
 //
-// Every rank runs the same grid of 128 x BN tiles over its K shard (tcgen05 main loop of
-// tc_gemm_core.cuh). Tile t is owned by rank t % world.
-//   non-owner  accumulator -> bf16 tile in shared memory (the drained TMA ring) -> coalesced 512-byte row
-//              stores into slot (t, rank) of the OWNER's staging area -> system fence -> flag; the CTA
-//              then exits, it never waits
+// Every rank runs the same grid of 128 x 128 tiles over its K shard (tcgen05 main loop of
+// tc_gemm_core.cuh, 3-stage ring so that two CTAs share an SM and one tile's exchange overlaps another
+// tile's main loop). Tile t is owned by rank t % world.
+//   non-owner  accumulator -> bf16 tile in shared memory (the drained TMA ring) -> one bulk copy per row
+//              (cp.async.bulk shared -> global) into slot (t, rank) of the OWNER's staging area -> system
+//              fence -> flag; the CTA then exits, it never waits
 //   owner      waits - bounded - for the other ranks' flags of its tile, sums the `world` partials in rank
 //              order (its own partial rounded to bf16 like the others, so the result does not depend on
 //              who owns a tile), adds the residual, rounds, and stores the finished rows into the output
@@ -16,8 +17,8 @@
 // Bytes crossing NVLink per rank: 2 * (world-1)/world * M*N*2 - the minimum of a bf16 reduce-scatter +
 // all-gather - and they move tile by tile underneath the main loops of later tiles. Only same-index tiles
 // synchronise across ranks; CTAs are dispatched in index order on every rank, so waits are short and
-// cannot form a cycle. No TMA multicast and no TMA access to peer memory is used: peers are written with
-// plain coalesced stores. Reference: linear(tp_columns) + allreduce on the bulk collective domain
+// cannot form a cycle. No TMA multicast and no TMA load from peer memory is used: peers are written with
+// non-tensor bulk stores from shared memory and staged partials are read back locally. Reference: linear(tp_columns) + allreduce on the bulk collective domain
 // (native/src/token_executor.h:374-404, docs/validation/2026-10-18-bulk-domains).
 #include "tc_gemm_core.cuh"
 #include "ifab_kernels.h"
@@ -38,12 +39,12 @@ struct ArParams {
   uint32_t spin_limit;
 };
 
-template <int BN>
+template <int BN, int NSTAGES>
 __global__ void __launch_bounds__(192) tc_gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                 const __grid_constant__ CUtensorMap tmap_b, ArParams a) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ int s_flag_ok, s_last;
-  Pipe<BN> pipe;
+  Pipe<BN, NSTAGES> pipe;
   pipe.setup(smem_raw, &tmap_a, &tmap_b);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x;
@@ -78,14 +79,17 @@ __global__ void __launch_bounds__(192) tc_gemm_allreduce_kernel(const __grid_con
         for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(tile_s + (size_t)trow * ROW_PAD + c0 + 8 * i) = pack8(v + 8 * i);
       }
     }
+    fence_proxy_async_smem();
     asm volatile("bar.sync 1, 128;" ::: "memory");
     constexpr int CPR = BN / 8;                          // 16-byte chunks per row
+    const int nvalid = min(BN, a.N - n0);                // valid columns of this tile (multiple of 8)
     if (world > 1 && rank != owner) {
-      // ---- push the partial tile: warp-per-row, 512 contiguous bytes per store instruction ----
+      // ---- push the partial tile: one bulk copy per row (thread et owns row et) ----
       bf16* dst = reinterpret_cast<bf16*>(half(owner) + ((size_t)(tile / world) * world + rank) * TILE_BYTES);
-      for (int r = ew; r < BM; r += 4)
-        for (int c = lane; c < CPR; c += 32)
-          *reinterpret_cast<uint4*>(dst + (size_t)r * BN + c * 8) = *reinterpret_cast<const uint4*>(tile_s + (size_t)r * ROW_PAD + c * 8);
+      if (ok) bulk_store(dst + (size_t)et * BN, tile_s + (size_t)et * ROW_PAD, BN * 2);
+      bulk_commit();
+      bulk_wait_all();
+      fence_proxy_async();
       __threadfence_system();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (et == 0) st_release_sys(flags(owner) + (size_t)tile * world + rank, epoch);
@@ -100,7 +104,8 @@ __global__ void __launch_bounds__(192) tc_gemm_allreduce_kernel(const __grid_con
         }
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (ok && s_flag_ok) {
+      const bool good = ok && s_flag_ok;
+      if (good) {
         const bf16* stage = reinterpret_cast<const bf16*>(half(rank) + (size_t)(tile / world) * world * TILE_BYTES);
         for (int r = ew; r < BM; r += 4) {
           const int row = m0 + r;
@@ -122,12 +127,20 @@ __global__ void __launch_bounds__(192) tc_gemm_allreduce_kernel(const __grid_con
 #pragma unroll
               for (int k = 0; k < 8; ++k) v[k] = bf16_round(v[k]) + f[k];
             }
-            const uint4 packed = pack8(v);
-            for (int dst = 0; dst < world; ++dst) *reinterpret_cast<uint4*>(a.out_peers[dst] + (long)row * a.ldc + col) = packed;
+            *reinterpret_cast<uint4*>(tile_s + (size_t)r * ROW_PAD + c * 8) = pack8(v);
           }
         }
       }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (good && m0 + et < a.M) {
+        for (int dst = 0; dst < world; ++dst)
+          bulk_store(a.out_peers[dst] + (long)(m0 + et) * a.ldc + n0, tile_s + (size_t)et * ROW_PAD, (uint32_t)nvalid * 2);
+      }
+      bulk_commit();
+      bulk_wait_all();
       if (world > 1) {
+        fence_proxy_async();
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (et < world && et != rank) st_release_sys(flags(et) + (size_t)a.ntiles * world + tile, epoch);
@@ -156,19 +169,23 @@ __global__ void __launch_bounds__(192) tc_gemm_allreduce_kernel(const __grid_con
   }
 }
 
-template <int BN>
+// 128 x 128 tiles with a 3-stage ring (97 KB of shared memory): two CTAs share an SM, so the exchange of one
+// tile overlaps the tensor-core main loop of another.
+constexpr int AR_BN = 128, AR_STAGES = 3;
+
 int launch_ar(const CUtensorMap& ta, const CUtensorMap& tb, ArParams& a, cudaStream_t s) {
-  auto k = tc_gemm_allreduce_kernel<BN>;
-  if (int rc = opt_in_smem(k, Cfg<BN>::SMEM)) return rc;
-  static_assert((size_t)BM * (BN + 8) * 2 <= (size_t)Cfg<BN>::STAGES * Cfg<BN>::STAGE_BYTES, "tile must fit the drained ring");
-  a.tiles_n = (a.N + BN - 1) / BN;
+  using C = Cfg<AR_BN, AR_STAGES>;
+  auto k = tc_gemm_allreduce_kernel<AR_BN, AR_STAGES>;
+  if (int rc = opt_in_smem(k, C::SMEM)) return rc;
+  static_assert((size_t)BM * (AR_BN + 8) * 2 <= (size_t)C::STAGES * C::STAGE_BYTES, "tile must fit the drained ring");
+  a.tiles_n = (a.N + AR_BN - 1) / AR_BN;
   a.ntiles = a.tiles_n * ((a.M + BM - 1) / BM);
   if (a.fv.world > 1) {
     const size_t owned = (a.ntiles + a.fv.world - 1) / a.fv.world;
-    if (owned * a.fv.world * (size_t)BM * BN * 2 > a.fv.data_half_bytes) return -3;
+    if (owned * a.fv.world * (size_t)BM * AR_BN * 2 > a.fv.data_half_bytes) return -3;
     if ((size_t)a.ntiles * (a.fv.world + 1) > a.fv.flag_half_words) return -4;
   }
-  return launch_chain(k, dim3(a.ntiles), dim3(192), (size_t)Cfg<BN>::SMEM, s, ta, tb, a);
+  return launch_chain(k, dim3(a.ntiles), dim3(192), (size_t)C::SMEM, s, ta, tb, a);
 }
 
 }  // namespace
@@ -180,9 +197,8 @@ extern "C" int ifab_gemm_allreduce_bf16(const void* a, long lda, const void* b, 
                                         void* stream) {
   if (M < 1 || N < 1 || K < 8 || K % 8 || lda % 8 || ldb % 8 || ldc % 8 || N % 8 || (residual && ldr % 8)) return -1;
   CUtensorMap ta, tb;
-  const int BN = N > 128 ? 256 : 128;
   if (int rc = make_tmap_bf16_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return rc;
-  if (int rc = make_tmap_bf16_2d(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)BN)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)AR_BN)) return rc;
   ArParams p;
   if (int rc = fabric_view(fab, &p.fv)) return rc;
   for (int r = 0; r < IFAB_MAX_RANKS; ++r) p.out_peers[r] = r < fab->world ? (bf16*)out_peers[r] : nullptr;
@@ -196,5 +212,5 @@ extern "C" int ifab_gemm_allreduce_bf16(const void* a, long lda, const void* b, 
   p.done = fab->done;
   p.spin_limit = 4000000u;
   cudaStream_t s = (cudaStream_t)stream;
-  return BN == 256 ? launch_ar<256>(ta, tb, p, s) : launch_ar<128>(ta, tb, p, s);
+  return launch_ar(ta, tb, p, s);
 }

@@ -8,15 +8,15 @@ namespace ifab::tc {
 
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 
-template <int BN>
+template <int BN, int NSTAGES = (BN == 256 ? 4 : 6)>
 struct Cfg {
-  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int STAGES = NSTAGES;
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <int BN>
+template <int BN, int NSTAGES = (BN == 256 ? 4 : 6)>
 struct Pipe {
   unsigned char* smem;        // 1024-byte aligned stage ring
   uint64_t *full, *empty, *acc_full;
@@ -26,7 +26,7 @@ struct Pipe {
 
   // all threads; allocates TMEM (warp 1), initialises barriers, ends with a CTA barrier
   __device__ __forceinline__ void setup(unsigned char* smem_raw, const CUtensorMap* ta, const CUtensorMap* tb) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, NSTAGES>;
     smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
     empty = full + C::STAGES;
@@ -54,7 +54,7 @@ struct Pipe {
   // one thread. (ax, ay[, az]) / (bx, by[, bz]) = tile origins; k advances along x.
   __device__ __forceinline__ void produce(const CUtensorMap* ta, const CUtensorMap* tb, int num_kb, int a_row, int b_row, int b_batch,
                                           uint32_t spin_limit, uint32_t* status) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, NSTAGES>;
     int issued = 0;
     for (int kb = 0; kb < num_kb; ++kb) {
       const int s = kb % C::STAGES;
@@ -77,7 +77,7 @@ struct Pipe {
 
   // one thread
   __device__ __forceinline__ void mma(int num_kb, uint32_t spin_limit, uint32_t* status) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, NSTAGES>;
     constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
     bool ok = true;
     for (int kb = 0; kb < num_kb && ok; ++kb) {

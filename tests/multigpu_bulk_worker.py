@@ -18,7 +18,7 @@ def main():
     from ironpangu_b200.ops.gemm import gemm_allreduce
     from ironpangu_b200.parallel.fabric import Fabric
 
-    fab = Fabric(rank, world, data_half_bytes=80 << 20, flag_half_words=8192, spin_limit=4_000_000)
+    fab = Fabric(rank, world, data_half_bytes=80 << 20, flag_half_words=16384, spin_limit=4_000_000)
     g = torch.Generator(device="cuda").manual_seed(9)
     for M, N, Kl in [(128, 256, 64), (512, 1024, 256), (300, 520, 128), (2048, 4096, 512)]:
         a = torch.randn(M, Kl * world, generator=g, device="cuda").to(BF16)
