@@ -108,6 +108,28 @@ int ifab_gqa_decode_attention(const void* q, long ldq, const void* k_cache, cons
                               int keys_per_split, int max_splits, float* scratch, uint64_t scratch_bytes, void* out,
                               long ldo, uint32_t* status, void* stream);
 
+/* ---- GQA decode attention without any allocation (this entry point has no counterpart in the reference) ----
+ * Same computation and same results as ifab_gqa_decode_attention, but the split-partials workspace is a
+ * fixed array inside the library, so neither the caller nor the library calls cudaMalloc / cudaFree or any
+ * allocating routine. Meant for C / C++ hosts that link the library without a tensor framework and cannot
+ * allocate where they call it: all free device memory already belongs to their KV cache, they run under an
+ * allocator lock, or an allocation could stall the device in a latency-critical loop.
+ *   - limit: T * Hq * max_splits * (head_dim + 2) * 4 bytes must not exceed IFAB_GQA_STATIC_SCRATCH_BYTES;
+ *     a larger call returns IFAB_ERR_STATIC_SCRATCH, launches nothing and explains itself in `err`
+ *   - the first call made with a given device current looks up the array's address on that device
+ *     (cudaGetSymbolAddress); make that first call before any stream capture begins
+ *   - all calls on a device share the one array: calls that may overlap on the GPU race on it, so keep them
+ *     on one stream or order them. The array keeps the previous call's contents; each call overwrites
+ *     everything it reads, so nothing has to be cleared
+ *   - `err` (optional, `err_len` bytes) receives a NUL-terminated message when the result is not 0 */
+#define IFAB_GQA_STATIC_SCRATCH_BYTES (8u << 20)
+#define IFAB_ERR_STATIC_SCRATCH (-6)
+int ifab_gqa_decode_attention_static(const void* q, long ldq, const void* k_cache, const void* v_cache,
+                                     const int32_t* positions, const int32_t* slots, const int32_t* page_table,
+                                     int max_pages, int page_tokens, int num_pages, float scale, int T, int Hq, int Hkv,
+                                     int head_dim, int keys_per_split, int max_splits, void* out, long ldo,
+                                     uint32_t* status, void* stream, char* err, uint64_t err_len);
+
 #ifdef __cplusplus
 }
 #endif
