@@ -109,6 +109,9 @@ __device__ __forceinline__ uint64_t ld_acquire_sys(const uint64_t* p) {
   asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ void st_relaxed_sys(uint64_t* p, uint64_t v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 __device__ __forceinline__ uint64_t ld_relaxed_sys(const uint64_t* p) {
   uint64_t v;
   asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -138,6 +141,8 @@ struct FabricView {
   uint32_t spin_limit;
   uint32_t data_half_bytes;   // bytes of one parity half of the staging area
   uint32_t flag_half_words;   // flag words of one parity half
+  uint32_t ll_half_bytes;     // one parity half of the tagged-store area (used only by oneshot_ar.cuh)
+  uint64_t ll_offset;         // its byte offset from data[r]
 };
 
 // host: build the by-value device view from the C descriptor
@@ -154,6 +159,8 @@ inline int fabric_view(const IfabFabric* f, FabricView* v) {
   v->spin_limit = f->spin_limit;
   v->data_half_bytes = f->data_half_bytes;
   v->flag_half_words = f->flag_half_words;
+  v->ll_half_bytes = f->ll_half_bytes;
+  v->ll_offset = f->ll_offset;
   return 0;
 }
 

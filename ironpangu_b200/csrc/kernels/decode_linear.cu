@@ -220,7 +220,7 @@ extern "C" int ifab_gemv_allreduce_bf16(const void* x, long ldx, const void* w, 
   a.seq = fab->seq;
   a.done = fab->done;
   a.y_f32 = (float*)y_f32;
-  if ((size_t)fab->world * T * N * sizeof(float) > fab->data_half_bytes) return -3;
+  if ((size_t)fab->world * T * N * sizeof(uint64_t) > fab->ll_half_bytes) return -3;
   if ((size_t)fab->world * 296 > fab->flag_half_words) return -4;
   cudaStream_t s = (cudaStream_t)stream;
   if (T <= 1) return dispatch_ar<1>(a, s);

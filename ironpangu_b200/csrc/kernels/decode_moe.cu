@@ -553,7 +553,7 @@ extern "C" int ifab_moe_down_allreduce_decode(const void* act, const int32_t* id
   p.residual = (const bf16*)residual; p.ldr = ldr; p.y = (bf16*)y; p.ldy = ldy;
   if (int rc = fabric_view(fab, &p.fv)) return rc;
   p.seq = fab->seq; p.done = fab->done;
-  if ((size_t)fab->world * T * D * sizeof(float) > fab->data_half_bytes) return -3;
+  if ((size_t)fab->world * T * D * sizeof(uint64_t) > fab->ll_half_bytes) return -3;
   if ((size_t)fab->world * 296 > fab->flag_half_words) return -4;
   cudaStream_t s = (cudaStream_t)stream;
   if (T <= 1) return dispatch_down<1>(p, s);

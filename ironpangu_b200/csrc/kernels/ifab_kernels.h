@@ -27,6 +27,9 @@ typedef struct IfabFabric {
   uint32_t spin_limit;
   uint32_t data_half_bytes;
   uint32_t flag_half_words;
+  uint32_t ll_half_bytes;  /* one parity half of the tagged-store area (8 bytes per exchanged f32) */
+  uint64_t ll_offset;      /* byte offset of that area from data[r]; it is used by nothing else, because a
+                              reader takes any 8-byte word whose high half equals the call number as valid */
 } IfabFabric;
 
 /* ---- fabric: symmetric heap over CUDA IPC (one process per GPU) ---- */

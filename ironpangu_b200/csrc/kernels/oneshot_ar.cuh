@@ -1,16 +1,21 @@
 // One-shot all-reduce epilogue used inside compute kernels (row-parallel linears, MoE combine).
 //
 // The calling CTA holds an f32 slab [T][RPC] of partial outputs for columns [nbase, nbase+RPC).
-// It pushes the slab into slot `rank` of every peer's staging area, publishes one flag per
-// (peer, cta), waits - bounded - for the same-index CTAs of the other ranks, sums the `world`
-// partials in rank order (deterministic, independent of arrival order), adds the residual and
-// stores bf16. Peer memory is written with plain stores and read back locally; the only remote
-// traffic is T*RPC*4 bytes per peer per CTA.
+// Every value is pushed to every peer as ONE 8-byte store that carries the f32 payload in its low
+// half and the low 32 bits of the call number in its high half. An aligned 8-byte store becomes
+// visible as a unit, so the receiver needs neither a fence nor a separate flag: it polls the slot
+// itself until the tag matches the call it is in (bounded), which makes the cost of the exchange one
+// one-way NVLink store latency instead of two fenced round trips. The `world` partials are then summed
+// in rank order (deterministic, independent of arrival order), the residual is added and bf16 stored.
+// The only remote traffic is T*RPC*8 bytes per peer per CTA.
 //
 // Protocol state: `seq` numbers the fused-collective launches of this rank (all ranks run the same
-// sequence); the last CTA of a launch advances it, so CUDA-graph replays get fresh epochs. The
-// staging area and the flags are double buffered on the parity of the call number; a rank cannot
-// be more than one call ahead of a peer because finishing call n needs that peer's push of call n.
+// sequence); the last CTA of a launch advances it, so CUDA-graph replays get fresh tags. The tagged-store
+// area (its own region of the symmetric block: no other protocol may write arbitrary bits there)
+// is double buffered on the parity of the call number; a rank cannot be more than one call ahead
+// of a peer because finishing call n needs that peer's push of call n, so a slot is never overwritten
+// before its reader consumed it. A slot left over from an earlier call carries an older tag and is
+// ignored (a false match would need exactly 2^32 calls between two uses of one slot).
 #pragma once
 #include "common.cuh"
 
@@ -24,27 +29,16 @@ __device__ __forceinline__ void oneshot_allreduce_slab(const float* slab, const 
   const int world = fv.world, rank = fv.rank;
   const uint64_t epoch = *reinterpret_cast<volatile uint64_t*>(seq) + 1;
   const uint32_t par = (uint32_t)(epoch & 1);
+  const uint32_t tag = (uint32_t)epoch;
   if (world > 1) {
     for (int i = threadIdx.x; i < world * T * RPC; i += blockDim.x) {
       const int q = i / (T * RPC), rem = i % (T * RPC), t = rem / RPC, c = rem % RPC;
-      if (t < t_live && nbase + c < N) {
-        float* dst = reinterpret_cast<float*>(fv.data[q] + (size_t)par * fv.data_half_bytes) +
-                     ((size_t)rank * t_live + t) * N + nbase + c;
-        *dst = slab[t * RPC + c];
+      if (q != rank && t < t_live && nbase + c < N) {
+        uint64_t* dst = reinterpret_cast<uint64_t*>(fv.data[q] + fv.ll_offset + (size_t)par * fv.ll_half_bytes) +
+                        ((size_t)rank * t_live + t) * N + nbase + c;
+        st_relaxed_sys(dst, ((uint64_t)tag << 32) | (uint64_t)__float_as_uint(slab[t * RPC + c]));
       }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < world) {
-      const int q = threadIdx.x;
-      st_release_sys(fv.flags[q] + (size_t)par * fv.flag_half_words + (size_t)rank * gridDim.x + blockIdx.x, epoch);
-      const uint64_t* f = fv.flags[rank] + (size_t)par * fv.flag_half_words + (size_t)q * gridDim.x + blockIdx.x;
-      if (!wait_flag_bounded(f, epoch, fv.spin_limit)) {
-        *timed_out_smem = 1;
-        atomicOr(fv.status, IFAB_STATUS_PEER_TIMEOUT);
-      }
-    }
-    __syncthreads();
   }
   for (int i = threadIdx.x; i < T * RPC; i += blockDim.x) {
     const int t = i / RPC, c = i % RPC;
@@ -52,8 +46,27 @@ __device__ __forceinline__ void oneshot_allreduce_slab(const float* slab, const 
     float v;
     if (world > 1) {
       v = 0.f;
-      const float* src = reinterpret_cast<const float*>(fv.data[rank] + (size_t)par * fv.data_half_bytes);
-      for (int q = 0; q < world; ++q) v += __ldcg(src + ((size_t)q * t_live + t) * N + nbase + c);
+      const uint64_t* src = reinterpret_cast<const uint64_t*>(fv.data[rank] + fv.ll_offset + (size_t)par * fv.ll_half_bytes);
+      for (int q = 0; q < world; ++q) {
+        if (q == rank) {
+          v += slab[t * RPC + c];
+          continue;
+        }
+        const uint64_t* slot = src + ((size_t)q * t_live + t) * N + nbase + c;
+        uint64_t got = 0;
+        bool ok = false;
+        for (uint32_t spin = 0; spin < fv.spin_limit; ++spin) {
+          got = ld_relaxed_sys(slot);
+          if ((uint32_t)(got >> 32) == tag) { ok = true; break; }
+          if (spin > 256) __nanosleep(32);
+        }
+        if (!ok) {
+          *timed_out_smem = 1;
+          atomicOr(fv.status, IFAB_STATUS_PEER_TIMEOUT);
+          break;
+        }
+        v += __uint_as_float((uint32_t)got);
+      }
     } else {
       v = slab[t * RPC + c];
     }

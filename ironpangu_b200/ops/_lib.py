@@ -32,6 +32,8 @@ class IfabFabric(C.Structure):
         ("spin_limit", C.c_uint32),
         ("data_half_bytes", C.c_uint32),
         ("flag_half_words", C.c_uint32),
+        ("ll_half_bytes", C.c_uint32),
+        ("ll_offset", C.c_uint64),
     ]
 
 

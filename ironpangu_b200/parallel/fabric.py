@@ -32,7 +32,7 @@ class Fabric:
     """Owner of this rank's symmetric block and of the peer mappings."""
 
     def __init__(self, rank: int = 0, world: int = 1, group=None, data_half_bytes: int = 4 << 20,
-                 flag_half_words: int = 8 * 296, spin_limit: int = 4_000_000, device: Optional[torch.device] = None):
+                 flag_half_words: int = 8 * 296, ll_half_bytes: int = 2 << 20, spin_limit: int = 4_000_000, device: Optional[torch.device] = None):
         if world < 1 or world > _lib.MAX_RANKS:
             raise ValueError("world must be 1..8")
         self.rank, self.world, self.group = rank, world, group
@@ -43,7 +43,9 @@ class Fabric:
         flag_bytes = _align(2 * flag_half_words * 8, 256)
         self._off_flags = 2 * self.data_half_bytes
         self._off_ctl = self._off_flags + flag_bytes
-        self.bytes = self._off_ctl + 256
+        self.ll_half_bytes = _align(ll_half_bytes, 256)
+        self._off_ll = self._off_ctl + 256          # tagged-store area of the one-shot all-reduce (two parity halves)
+        self.bytes = self._off_ll + 2 * self.ll_half_bytes
         base = C.c_void_p()
         with torch.cuda.device(self.device):
             _lib.check(self.lib.ifab_set_device(self.device.index or 0), "set device")
@@ -65,6 +67,8 @@ class Fabric:
         f.spin_limit = spin_limit
         f.data_half_bytes = self.data_half_bytes
         f.flag_half_words = flag_half_words
+        f.ll_half_bytes = self.ll_half_bytes
+        f.ll_offset = self._off_ll
         self.desc = f
         # a scratch ticket area for kernels that use a "last CTA finishes" pattern without a fabric
         self.ticket_ptr = self.base + self._off_ctl + 32
