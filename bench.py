@@ -34,6 +34,7 @@ def parse():
     ap.add_argument("--impl", default="native", choices=["native", "reference", "nccl_cublas"])
     ap.add_argument("--model", default="flagship", choices=["flagship", "tiny"])
     ap.add_argument("--context", type=int, default=512)
+    ap.add_argument("--persistent", type=int, default=0, help="1: one persistent cooperative launch per decode step")
     ap.add_argument("--layers", type=int, default=0, help="override layer count (marks the run as a reduced config)")
     return ap.parse_args()
 
@@ -124,7 +125,8 @@ def main():
     torch.cuda.synchronize()
     weight_bytes = sum(t.numel() * t.element_size() for t in weights.values())
     if args.impl == "native":
-        dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1)
+        dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1,
+                            persistent=bool(args.persistent))
     else:
         from baseline.nccl_cublas import NcclCublasDecoder
         dec = NcclCublasDecoder(cfg, weights, rank, world, max_tokens=8, max_context=max_context)
@@ -208,7 +210,7 @@ def main():
                                  "v 128, 96 experts x 1536 top-8 softmax + 1 shared, vocab 153600") if args.model == "flagship"
                        and not args.layers else f"{args.model} layers={cfg.layers} (reduced config)",
                        "params_b": round(cfg.param_count() / 1e9, 2), "global_batch": 1, "seq_len": args.context,
-                       "decode_tokens": K, "parallelism": f"tp{world}ep{world}",
+                       "decode_tokens": K, "parallelism": f"tp{world}ep{world}", "decode_step": "single persistent launch" if args.persistent else "operator chain",
                        "l2": "per-step weight stream (>= 2.5 GB per rank) exceeds the 126 MB L2; no explicit flush",
                        "baseline_ref": "17.7293 ms TPOT on 8x Ascend (docs/validation/2026-10-17-packed-c8/README.md:20-23)",
                        "weight_bytes_per_rank": weight_bytes},

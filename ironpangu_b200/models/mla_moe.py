@@ -182,7 +182,8 @@ class MlaMoeDecoder:
     """
 
     def __init__(self, cfg: MlaMoeConfig, weights: Dict[str, torch.Tensor], fabric: Fabric, *, max_tokens: int = 1,
-                 max_context: int = 1024, num_slots: int = 1, keys_per_split: int = 64, keep_logits: bool = False):
+                 max_context: int = 1024, num_slots: int = 1, keys_per_split: int = 64, keep_logits: bool = False,
+                 persistent: bool = False):
         assert 1 <= max_tokens <= 8
         self.cfg, self.w, self.fabric = cfg, weights, fabric
         self.rank, self.world = fabric.rank, fabric.world
@@ -225,11 +226,76 @@ class MlaMoeDecoder:
         self.logits = e(T, self.vl, dt=torch.float32) if keep_logits else None
         self.launches_per_forward = 3 + 10 * c.layers - 1  # embedding + layers + lm_head (kernel count)
         self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self.persistent = persistent
+        if persistent:
+            self._build_step_descriptor()
+            self.launches_per_forward = 1
+
+    def _build_step_descriptor(self) -> None:
+        """Descriptor of the single-launch decode step (``ops.decode.mla_moe_decode_step``): a device table with the
+        16 pointers of every layer plus the activation buffers; written once, reused by every step."""
+        from ..ops import _lib
+
+        c, w, dev = self.cfg, self.w, self.fabric.device
+        names = {"attn_norm": "attn_norm", "qkv_a": "qkv_a", "kv_a_norm": "kv_a_norm", "q_a_norm": "q_a_norm", "q_b": "q_b",
+                 "kv_b": "kv_b", "o_proj": "o_proj", "ffn_norm": "ffn_norm", "router": "router", "gate_up": "gate_up",
+                 "down": "down", "shared_gate_up": "shared_gate_up", "shared_down": "shared_down"}
+        rows = []
+        for l in range(c.layers):
+            row = []
+            for f in _lib.IfabMlaMoeLayer.FIELDS:
+                if f == "cache":
+                    row.append(self.caches[l].data_ptr())
+                elif f in names:
+                    t = w.get(f"layers.{l}.{names[f]}")
+                    row.append(0 if t is None else t.data_ptr())
+                else:
+                    row.append(0)          # router_bias, sinks: not used by this configuration
+            rows.append(row)
+        self._layer_table = torch.tensor(rows, dtype=torch.int64).to(dev)
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self._step_partial = torch.empty(2 * sms * 8 * 2, dtype=torch.float32, device=dev)
+        self._step_bar = torch.zeros(4, dtype=torch.int32, device=dev)
+        s = _lib.IfabMlaMoeStep()
+        s.layers = self._layer_table.data_ptr()
+        s.n_layers, s.hidden, s.heads_local, s.q_lora, s.nope, s.rope, s.vdim = c.layers, c.hidden, self.hl, c.q_lora, c.nope, c.rope, c.vdim
+        s.experts, s.experts_local, s.expert0, s.topk, s.expert_ffn = c.experts, self.el, self.rank * self.el, c.topk, c.expert_ffn
+        s.shared_ffn_local = c.shared_ffn // self.world
+        s.vocab_local, s.vocab_offset, s.vocab = self.vl, self.rank * self.vl, c.vocab
+        s.scoring = {"softmax": 0, "sigmoid_bias_group_topk": 1}[c.scoring]
+        s.renorm, s.window, s.n_sinks, s.page_tokens = 1, c.window, 0, c.page_tokens
+        s.max_pages, s.num_pages, s.keys_per_split, s.max_splits = self.max_pages, self.num_pages, self.kps, self.max_splits
+        s.route_scale, s.eps, s.theta, s.attn_scale = c.route_scale, c.eps, c.theta, c.scale
+        s.embed, s.final_norm, s.lm_head = w["embed"].data_ptr(), w["final_norm"].data_ptr(), w["lm_head"].data_ptr()
+        s.tokens, s.positions, s.slots, s.page_table = (self.tokens.data_ptr(), self.positions.data_ptr(), self.slots.data_ptr(),
+                                                        self.page_table.data_ptr())
+        s.x, s.qkv, s.q, s.q_lat, s.attn, s.act = (self.x.data_ptr(), self.qkv.data_ptr(), self.q.data_ptr(), self.q_lat.data_ptr(),
+                                                   self.attn.data_ptr(), self.act.data_ptr())
+        s.scratch, s.router_logits, s.route_ids, s.route_w = (self.scratch.data_ptr(), self.logits_r.data_ptr(),
+                                                              self.route_ids.data_ptr(), self.route_w.data_ptr())
+        s.partial, s.next_ids, s.next_vals = self._step_partial.data_ptr(), self.next_ids.data_ptr(), self.next_vals.data_ptr()
+        s.logits = 0 if self.logits is None else self.logits.data_ptr()
+        s.bar = self._step_bar.data_ptr()
+        self._step = s
+
+    def forward_feedback(self, T: Optional[int] = None) -> torch.Tensor:
+        """One step whose sampled token and position + 1 become the inputs of the next step (device-side feedback)."""
+        T = self.T if T is None else T
+        if self.persistent:
+            K.mla_moe_decode_step(self._step, T, self.fabric, feedback=True)
+            return self.next_ids[:T]
+        self.forward(T)
+        self.tokens[:T].copy_(self.next_ids[:T])
+        self.positions[:T].add_(1)
+        return self.next_ids[:T]
 
     # -- one step ----------------------------------------------------------------------------------
     def forward(self, T: Optional[int] = None) -> torch.Tensor:
         c, w, fab = self.cfg, self.w, self.fabric
         T = self.T if T is None else T
+        if self.persistent:
+            K.mla_moe_decode_step(self._step, T, fab)
+            return self.next_ids[:T]
         tok, pos, slot = self.tokens[:T], self.positions[:T], self.slots[:T]
         x = self.x[:T]
         st = fab.desc.status
@@ -275,10 +341,10 @@ class MlaMoeDecoder:
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            self.forward(T)
             if feedback:
-                self.tokens[:T].copy_(self.next_ids[:T])
-                self.positions[:T].add_(1)
+                self.forward_feedback(T)
+            else:
+                self.forward(T)
         self._graph = g
         return g
 

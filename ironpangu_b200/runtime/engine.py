@@ -46,9 +46,12 @@ class DecodeEngine:
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            d.forward(1)
-            d.tokens[:1].copy_(d.next_ids[:1])
-            d.positions[:1].add_(1)
+            if hasattr(d, "forward_feedback"):
+                d.forward_feedback(1)
+            else:
+                d.forward(1)
+                d.tokens[:1].copy_(d.next_ids[:1])
+                d.positions[:1].add_(1)
         self._feedback_graph = g
 
     # -- public API --------------------------------------------------------------------------------
@@ -74,11 +77,11 @@ class DecodeEngine:
 
     def step(self, token: int) -> int:
         """One decode step through the captured graph: H2D control inputs, replay, D2H sampled token."""
-        if self._graph is None:
-            self._capture()
         self._ctl_host[0] = token
         self._ctl_host[1] = self.pos
         self._ctl_dev.copy_(self._ctl_host, non_blocking=True)
+        if self._graph is None:
+            self._capture()     # its warm-up run executes this very step (same token, same position), never a stale one
         self._graph.replay()
         self._out_host.copy_(self.dec.next_ids[:1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
@@ -97,11 +100,12 @@ class DecodeEngine:
     def run_device_loop(self, first_token: Optional[int], steps: int) -> None:
         """Decode ``steps`` tokens with the sampled token fed back on the device (no host round trips)."""
         d = self.dec
-        if self._feedback_graph is None:
-            self._capture_feedback()
         if first_token is not None:
             d.tokens[:1].fill_(first_token)
             d.positions[:1].fill_(self.pos)
+            d.slots[:1].zero_()
+        if self._feedback_graph is None:
+            self._capture_feedback()    # warm-up = the step about to be replayed (same inputs), so it changes no state
         for _ in range(steps):
             self._feedback_graph.replay()
         self.pos += steps
