@@ -5,13 +5,9 @@
 #include "decode_mega_kernel.cuh"
 
 namespace ifab::mega {
-extern template int launch_step<1, 4>(Params&, cudaStream_t);
 extern template int launch_step<1, 1>(Params&, cudaStream_t);
-extern template int launch_step<2, 4>(Params&, cudaStream_t);
 extern template int launch_step<2, 1>(Params&, cudaStream_t);
-extern template int launch_step<4, 4>(Params&, cudaStream_t);
 extern template int launch_step<4, 1>(Params&, cudaStream_t);
-extern template int launch_step<8, 4>(Params&, cudaStream_t);
 extern template int launch_step<8, 1>(Params&, cudaStream_t);
 }  // namespace ifab::mega
 
@@ -39,15 +35,14 @@ extern "C" int ifab_mla_moe_decode_step(const IfabMlaMoeStep* s, int T, const If
   p.x = (bf16*)s->x; p.qkv = (bf16*)s->qkv; p.q = (bf16*)s->q; p.q_lat = (bf16*)s->q_lat; p.attn = (bf16*)s->attn;
   p.act = (bf16*)s->act; p.scratch = s->scratch; p.router_logits = s->router_logits; p.route_ids = s->route_ids;
   p.route_w = s->route_w; p.partial = (float2*)s->partial; p.next_ids = s->next_ids; p.next_vals = s->next_vals;
-  p.logits = s->logits; p.bar = s->bar; p.T_live = T; p.feedback = s->feedback;
+  p.logits = s->logits; p.bar = s->bar; p.trace = (unsigned long long*)s->trace; p.T_live = T; p.feedback = s->feedback;
   if (int rc = fabric_view(fab, &p.fv)) return rc;
   p.seq = fab->seq;
   p.spin_limit = fab->spin_limit;
   if ((size_t)fab->world * T * s->hidden * sizeof(uint64_t) > fab->ll_half_bytes) return -3;
   if ((size_t)fab->world > fab->flag_half_words) return -4;
   cudaStream_t st = (cudaStream_t)stream;
-  const bool hg4 = s->heads_local % 4 == 0;
-#define IFAB_STEP(TT) return hg4 ? launch_step<TT, 4>(p, st) : launch_step<TT, 1>(p, st);
+#define IFAB_STEP(TT) return launch_step<TT, 1>(p, st);
   if (T <= 1) IFAB_STEP(1)
   if (T <= 2) IFAB_STEP(2)
   if (T <= 4) IFAB_STEP(4)

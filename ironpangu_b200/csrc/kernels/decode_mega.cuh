@@ -37,6 +37,7 @@ namespace ifab::mega {
 using namespace ifab::mla;
 
 constexpr int THREADS = 256, WARPS = 8;
+constexpr int MD = 16;                     // 16-byte weight loads a lane keeps in flight per batch (see gemv.cuh)
 constexpr int MAX_TOPK = 16;
 constexpr int MAX_ROUTES = 8 * MAX_TOPK;   // T * topk
 constexpr int AR_ROWS = 8;                 // output rows one warp may own in an all-reduce phase
@@ -65,6 +66,7 @@ struct Params {
   int32_t* next_ids;
   float *next_vals, *logits;
   uint32_t* bar;        // [0] arrivals  [1] base of this launch  [2] exit tickets  [3] abort
+  unsigned long long* trace;   // optional: CTA 0 stores the global timer (ns) at kernel entry and after every barrier
   int T_live, feedback;
   FabricView fv;
   uint64_t* seq;
@@ -85,8 +87,15 @@ __device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) {
   return v;
 }
 
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
 // Grid-wide barrier state of one CTA. `count` advances identically in every thread of every CTA.
 struct GridBar {
+  unsigned long long* trace;
   uint32_t* bar;
   uint32_t base, count, nblocks, limit;
   uint32_t* status;
@@ -112,6 +121,7 @@ __device__ __forceinline__ bool grid_sync(GridBar& g) {
     }
   }
   __syncthreads();
+  if (g.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) g.trace[g.count] = global_timer_ns();
   return *g.s_ok != 0;
 }
 
@@ -171,8 +181,12 @@ __device__ __forceinline__ void stage_act(bf16* xs, const bf16* x, long ld, int 
 
 // y[t][r] = dot(W[r, :], xs[t, :]) for the rows this warp owns (units of R rows, interleaved over all warps of the
 // grid so that neighbouring warps stream neighbouring rows). epi(first_row, acc) runs on every lane with full sums.
+// `first` holds the first weight batch of this warp's first unit when the caller issued it ahead of time
+// (prefetch_first, before the grid barrier that publishes the activations: weights never change, so their loads may
+// overlap the barrier and the staging of the activations).
 template <int T, int R, class Epi>
-__device__ __forceinline__ void gemv_phase(const bf16* W, int rows, int K, const bf16* xs, int gw, int GW, Epi epi) {
+__device__ __forceinline__ void gemv_phase(const bf16* W, int rows, int K, const bf16* xs, int gw, int GW, RowBatch<R, MD>& first,
+                                           bool have_first, Epi epi) {
   const int units = (rows + R - 1) / R;
   for (int u = gw; u < units; u += GW) {
     const bf16* wrow[R];
@@ -183,10 +197,26 @@ __device__ __forceinline__ void gemv_phase(const bf16* W, int rows, int K, const
     for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int t = 0; t < T; ++t) acc[r][t] = 0.f;
-    warp_rows_dot<T, R>(wrow, xs, K, acc);
+    if (have_first && u == gw) warp_rows_dot<T, R, MD>(wrow, xs, K, acc, first);
+    else warp_rows_dot<T, R, MD>(wrow, xs, K, acc);
     warp_reduce_acc<T, R>(acc);
     epi(u * R, acc);
   }
+}
+
+template <int T, int R, class Epi>
+__device__ __forceinline__ void gemv_phase(const bf16* W, int rows, int K, const bf16* xs, int gw, int GW, Epi epi) {
+  RowBatch<R, MD> none;
+  gemv_phase<T, R>(W, rows, K, xs, gw, GW, none, false, epi);
+}
+
+// issue the first weight batch of unit `gw` (rows gw*R .. gw*R+R-1) of a GEMV phase
+template <int R>
+__device__ __forceinline__ void prefetch_first(const bf16* W, int rows, int K, int gw, RowBatch<R, MD>& pf) {
+  const bf16* wrow[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) wrow[r] = (gw * R + r < rows) ? W + (size_t)(gw * R + r) * K : nullptr;
+  prefetch_rows<R, MD>(wrow, K, pf);
 }
 
 // ---- all-reduce of row partials (tagged 8-byte stores, see oneshot_ar.cuh) ------------------------------------

@@ -289,33 +289,45 @@ __device__ __forceinline__ void phase_down(const Params& p, const Layer& L, cons
         *reinterpret_cast<uint4*>(as + (size_t)i * F + c * 8) = ld_act16(arow + c * 8);
     }
     __syncthreads();
+    // The K ranges of all local routes form one flattened chunk space (16-byte chunks; routed experts own F/8 of
+    // them each, a trailing shared-expert shard Fs/8), so a lane keeps U loads in flight across route boundaries.
+    // The (route, chunk) pair of a load advances incrementally in registers - no division - and is remembered as
+    // one packed word: route << 20 | chunk index in `as`.
     const int chunks = st.dcbeg[n_routes];
-    const int cpr = F >> 3;
-    const int n_exp_chunks = (n_routes > 0 && st.dslot[n_routes - 1] == p.topk) ? st.dcbeg[n_routes - 1] : chunks;
-    constexpr int U = 16;
+    const int as_cpr = F >> 3;
+    const int last = n_routes - 1;
+    const int last_cpr = n_routes > 0 ? (st.dk[last] >> 3) : 0;
+    constexpr int U = 8;
     int k = 0;
     for (int n0 = gw; n0 < D && k < AR_ROWS; n0 += GW, ++k) {
       float total = 0.f;
+      int route = 0, cc = lane;
+      int cur = (route == last) ? last_cpr : as_cpr;
+      while (route < n_routes && cc >= cur) { cc -= cur; ++route; cur = (route == last) ? last_cpr : as_cpr; }
       for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
         uint4 wv[U];
-        int route[U], cc[U];
+        int where[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          const int c = c0 + u * 32;
-          const int i = c < n_exp_chunks ? c / cpr : n_routes - 1;
-          route[u] = i;
-          cc[u] = c < n_exp_chunks ? c - i * cpr : c - n_exp_chunks;
-          wv[u] = (c < chunks) ? ld_stream16(st.dw[i] + (size_t)n0 * st.dk[i] + cc[u] * 8) : make_uint4(0, 0, 0, 0);
+          if (route < n_routes) {
+            where[u] = (route << 20) | (route * as_cpr + cc);
+            wv[u] = ld_stream16(st.dw[route] + ((size_t)n0 * cur + cc) * 8);
+            cc += 32;
+            while (route < n_routes && cc >= cur) { cc -= cur; ++route; cur = (route == last) ? last_cpr : as_cpr; }
+          } else {
+            where[u] = -1;
+            wv[u] = make_uint4(0, 0, 0, 0);
+          }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          if (c0 + u * 32 < chunks) {
+          if (where[u] >= 0) {
             float xf[8], wf[8], d = 0.f;
-            unpack8(*reinterpret_cast<const uint4*>(as + (size_t)route[u] * F + cc[u] * 8), xf);
+            unpack8(*reinterpret_cast<const uint4*>(as + (size_t)(where[u] & 0xfffff) * 8), xf);
             unpack8(wv[u], wf);
 #pragma unroll
             for (int q = 0; q < 8; ++q) d = fmaf(wf[q], xf[q], d);
-            total = fmaf(st.dg[route[u]], d, total);
+            total = fmaf(st.dg[where[u] >> 20], d, total);
           }
         }
       }
@@ -531,7 +543,8 @@ __global__ void __launch_bounds__(THREADS, 2) decode_step_kernel(const __grid_co
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ CtaState<T> st;
   if (threadIdx.x == 0) st.ok = 1;
-  GridBar gb{p.bar, ld_volatile_u32(p.bar + 1), 0u, gridDim.x, p.spin_limit, p.fv.status, &st.ok};
+  GridBar gb{p.trace, p.bar, ld_volatile_u32(p.bar + 1), 0u, gridDim.x, p.spin_limit, p.fv.status, &st.ok};
+  if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[0] = global_timer_ns();
   const uint64_t seq0 = *reinterpret_cast<volatile uint64_t*>(p.seq);
   __syncthreads();
   run_step<T, HG>(p, smem, st, gb, seq0);

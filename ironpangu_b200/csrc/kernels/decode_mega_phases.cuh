@@ -272,8 +272,8 @@ __device__ __forceinline__ void phase_merge_vup(const Params& p, const Layer& L,
     const bf16* rows[RV];
 #pragma unroll
     for (int r = 0; r < RV; ++r) rows[r] = (j0 + r < p.vdim) ? W + (long)(j0 + r) * LATENT : nullptr;
-    RowBatch<RV> pf;
-    prefetch_rows<RV>(rows, LATENT, pf);
+    RowBatch<RV, MD> pf;
+    prefetch_rows<RV, MD>(rows, LATENT, pf);
     int first, nctx;
     visible_range(pos, p.window, &first, &nctx);
     const int total = p.n_sinks + nctx;
@@ -304,7 +304,7 @@ __device__ __forceinline__ void phase_merge_vup(const Params& p, const Layer& L,
     float acc[RV][1];
 #pragma unroll
     for (int r = 0; r < RV; ++r) acc[r][0] = 0.f;
-    warp_rows_dot<1, RV>(rows, os, LATENT, acc, pf);
+    warp_rows_dot<1, RV, MD>(rows, os, LATENT, acc, pf);
     warp_reduce_acc<1, RV>(acc);
     if (lane == 0) {
 #pragma unroll

@@ -5,6 +5,5 @@
 #include "decode_mega_kernel.cuh"
 
 namespace ifab::mega {
-template int launch_step<4, 4>(Params&, cudaStream_t);
 template int launch_step<4, 1>(Params&, cudaStream_t);
 }  // namespace ifab::mega

@@ -16,24 +16,26 @@
 
 namespace ifab {
 
-// number of 16-byte chunks a lane keeps in flight per batch, split over the R rows of its warp
-template <int R>
+// number of 16-byte chunks a lane keeps in flight per batch (DEPTH), split over the R rows of its warp. The
+// operator-per-launch kernels use 16; the persistent decode-step kernel, which lives on 128 registers per thread
+// with 16 resident warps per SM, uses 8.
+template <int R, int DEPTH = 16>
 struct Pf {
-  static constexpr int U = 16 / R;
+  static constexpr int U = DEPTH / R;
 };
 
-template <int R>
+template <int R, int DEPTH = 16>
 struct RowBatch {
-  uint4 v[Pf<R>::U][R];
+  uint4 v[Pf<R, DEPTH>::U][R];
 };
 
 // issue the loads of the first batch (chunks lane, lane+32, ...) of R rows; rows may be nullptr
-template <int R>
-__device__ __forceinline__ void prefetch_rows(const bf16* const (&wrow)[R], int K, RowBatch<R>& pf) {
+template <int R, int DEPTH = 16>
+__device__ __forceinline__ void prefetch_rows(const bf16* const (&wrow)[R], int K, RowBatch<R, DEPTH>& pf) {
   const int lane = threadIdx.x & 31;
   const int chunks = K >> 3;
 #pragma unroll
-  for (int u = 0; u < Pf<R>::U; ++u) {
+  for (int u = 0; u < Pf<R, DEPTH>::U; ++u) {
     const int c = lane + u * 32;
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -96,12 +98,12 @@ __device__ __forceinline__ void stage_x(bf16* xs, const bf16* __restrict__ x, lo
 // acc[r][t] += dot(w_row[r][0..K), xs[t][0..K)) over this lane's share of K. `pf` holds the first
 // batch (already loaded by prefetch_rows); later batches are loaded here. Rows whose pointer is
 // nullptr are skipped. Caller reduces across the warp afterwards.
-template <int T, int R>
+template <int T, int R, int DEPTH = 16>
 __device__ __forceinline__ void warp_rows_dot(const bf16* const (&wrow)[R], const bf16* xs, int K, float (&acc)[R][T],
-                                              RowBatch<R>& pf) {
+                                              RowBatch<R, DEPTH>& pf) {
   const int lane = threadIdx.x & 31;
   const int chunks = K >> 3;
-  constexpr int U = Pf<R>::U;
+  constexpr int U = Pf<R, DEPTH>::U;
   for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
     if (c0 != lane) {
 #pragma unroll
@@ -135,11 +137,11 @@ __device__ __forceinline__ void warp_rows_dot(const bf16* const (&wrow)[R], cons
 }
 
 // convenience: prefetch + dot in one go (no overlap with a prologue)
-template <int T, int R>
+template <int T, int R, int DEPTH = 16>
 __device__ __forceinline__ void warp_rows_dot(const bf16* const (&wrow)[R], const bf16* xs, int K, float (&acc)[R][T]) {
-  RowBatch<R> pf;
-  prefetch_rows<R>(wrow, K, pf);
-  warp_rows_dot<T, R>(wrow, xs, K, acc, pf);
+  RowBatch<R, DEPTH> pf;
+  prefetch_rows<R, DEPTH>(wrow, K, pf);
+  warp_rows_dot<T, R, DEPTH>(wrow, xs, K, acc, pf);
 }
 
 template <int T, int R>

@@ -132,6 +132,7 @@ typedef struct IfabMlaMoeStep {
   int32_t* next_ids;
   float *next_vals, *logits;                /* logits may be NULL; [T, vocab_local] f32 */
   uint32_t* bar;
+  uint64_t* trace;    /* optional (NULL = off): 3 + 9 * n_layers global-timer stamps in ns, one per barrier, written by CTA 0 */
   int32_t feedback;
 } IfabMlaMoeStep;
 

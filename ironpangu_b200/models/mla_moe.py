@@ -276,7 +276,32 @@ class MlaMoeDecoder:
         s.partial, s.next_ids, s.next_vals = self._step_partial.data_ptr(), self.next_ids.data_ptr(), self.next_vals.data_ptr()
         s.logits = 0 if self.logits is None else self.logits.data_ptr()
         s.bar = self._step_bar.data_ptr()
+        s.trace = 0
         self._step = s
+
+    PHASES = ("qkv_a", "q_b+kv_write", "absorb", "attn_split", "merge+v_up", "o_proj+ar", "router", "gate_up", "down+ar")
+
+    def trace_step(self, T: int = 1) -> Dict[str, float]:
+        """Run one single-launch step with the in-kernel timer on; returns microseconds per phase (summed over the
+        layers, barrier included), plus ``embedding``, ``head`` and ``total``. Profiling aid: costs one sync."""
+        assert self.persistent
+        n = 3 + 9 * self.cfg.layers
+        buf = torch.zeros(n, dtype=torch.int64, device=self.fabric.device)
+        self._step.trace = buf.data_ptr()
+        try:
+            K.mla_moe_decode_step(self._step, T, self.fabric)
+            torch.cuda.synchronize()
+        finally:
+            self._step.trace = 0
+        t = buf.cpu().double()
+        d = (t[1:] - t[:-1]) / 1e3
+        out = {"embedding": float(d[0])}
+        per = d[1:1 + 9 * self.cfg.layers].view(self.cfg.layers, 9).sum(0)
+        for i, name in enumerate(self.PHASES):
+            out[name] = float(per[i])
+        out["head"] = float(d[1 + 9 * self.cfg.layers])
+        out["total"] = float((t[-1] - t[0]) / 1e3)
+        return out
 
     def forward_feedback(self, T: Optional[int] = None) -> torch.Tensor:
         """One step whose sampled token and position + 1 become the inputs of the next step (device-side feedback)."""

@@ -28,7 +28,7 @@ class IfabMlaMoeStep(C.Structure):
              "n_sinks", "page_tokens", "max_pages", "num_pages", "keys_per_split", "max_splits")
     _FLOATS = ("route_scale", "eps", "theta", "attn_scale")
     _PTRS = ("embed", "final_norm", "lm_head", "tokens", "positions", "slots", "page_table", "x", "qkv", "q", "q_lat", "attn",
-             "act", "scratch", "router_logits", "route_ids", "route_w", "partial", "next_ids", "next_vals", "logits", "bar")
+             "act", "scratch", "router_logits", "route_ids", "route_w", "partial", "next_ids", "next_vals", "logits", "bar", "trace")
     _fields_ = ([("layers", C.c_void_p)] + [(n, C.c_int32) for n in _INTS] + [(n, C.c_float) for n in _FLOATS]
                 + [(n, C.c_void_p) for n in _PTRS] + [("feedback", C.c_int32)])
 
