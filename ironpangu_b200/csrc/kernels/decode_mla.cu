@@ -379,6 +379,7 @@ extern "C" int ifab_mla_decode_attention(const void* q_lat, const void* cache, c
   else if (H % 2 == 0) rc = launch_split<2>(p, s);
   else rc = launch_split<1>(p, s);
   if (rc) return rc;
+  if (w_kvb == nullptr) return 0;   // split partials only: the caller merges (ifab_mla_merge) and up-projects with a GEMM
   dim3 grid(H, T);
   return launch_chain(mla_merge_vup_kernel, grid, dim3(256), 0, s, p, (const bf16*)w_kvb, nope, vdim, (bf16*)out, ldo);
 }

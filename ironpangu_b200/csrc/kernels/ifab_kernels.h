@@ -63,6 +63,33 @@ int ifab_gemm_bf16(const void* a, long lda, const void* b, long ldb, void* c, lo
 int ifab_gemm_allreduce_bf16(const void* a, long lda, const void* b, long ldb, void* const* out_peers, long ldc, const void* residual,
                              long ldr, int M, int N, int K, const IfabFabric* fab, void* stream);
 
+/* ---- prefill path: grouped expert GEMM (tcgen05) and its routing plumbing; all sizes are device-side counts ---- */
+/* mode 0: C[rows, N] = A . B[e]^T; mode 1: N = 2F (gate rows then up rows), C[rows, F] = silu(gate) * up.
+ * tiles: max_tiles x int4 {expert, first row, valid rows, 0}; *num_tiles of them are valid (written by ifab_moe_dispatch). */
+int ifab_grouped_gemm_bf16(const void* a, long lda, int rows_max, const void* b, int experts, int N, int K,
+                           const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* c, long ldc, int mode,
+                           uint32_t* status, void* stream);
+/* router for any number of rows (blocks of 8 per CTA); xn (optional) receives the RMS-normalised rows */
+int ifab_router_block(const void* x, long ldx, const void* norm_w, float eps, const float* w_router, const float* bias,
+                      float* logits, int32_t* ids, float* wts, void* xn, long ldxn, int M, int D, int E, int topk,
+                      int scoring, int renorm, float scale, void* stream);
+int ifab_moe_dispatch(const int32_t* ids, int M, int topk, int e0, int e_local, int32_t* counts, int32_t* route_row,
+                      int32_t* perm_token, int32_t* tiles, int32_t* num_tiles, int32_t* total_rows, int max_tiles,
+                      void* stream);
+int ifab_moe_gather(const void* xn, long ldxn, const int32_t* perm_token, const int32_t* total_rows, void* xp, long ldxp,
+                    int D, int rows_max, void* stream);
+int ifab_moe_combine(const void* y, long ldy, const int32_t* route_row, const float* wts, int M, int topk, int D,
+                     const void* shared, long lds, const void* residual, long ldr, float* out_f32, void* out, long ldo,
+                     void* stream);
+int ifab_mla_q_rope(const void* q, long ldq, const int32_t* positions, void* q_lat, int T, int H, int nope, int rope,
+                    float theta, void* stream);
+int ifab_mla_merge(const float* scratch, const int32_t* positions, int n_sinks, int window, int keys_per_split,
+                   int max_splits, int T, int H, void* o_lat, void* stream);
+/* one-shot pull all-reduce of f32 [rows, D] partials held in symmetric memory (parts[r] = rank r's buffer as mapped here),
+ * + residual, bf16 out. The caller alternates two sets of partial buffers between consecutive calls. */
+int ifab_allreduce_rows(const void* const* parts, const void* residual, long ldr, void* out, long ldo, long rows, int D,
+                        const IfabFabric* fab, void* stream);
+
 /* ---- MoE decode path (owner-local expert parallelism) ---- */
 int ifab_router_topk(const void* x, long ldx, const void* norm_w, float eps, const float* w_router, const float* bias,
                      float* logits, int32_t* ids, float* wts, int T, int D, int E, int topk, int scoring, int renorm,

@@ -1,0 +1,179 @@
+// Small kernels of the prefill path that have no decode counterpart:
+//
+//   mla_q_rope_kernel     rotary part of the absorbed query: q[t, h, nope:] -> q_lat[t, h, 512:576]
+//                         (the latent part comes from a per-head tensor-core GEMM with W_uk)
+//   mla_merge_kernel      log-sum-exp merge of the split-KV partials -> o_lat [T, H, 512] bf16
+//                         (the value up-projection is a per-head tensor-core GEMM with W_uv afterwards)
+//   allreduce_rows_kernel one-shot pull all-reduce of an f32 [rows, D] partial held in symmetric memory by every
+//                         rank: every rank reads all partials through its peer mappings (plain loads), sums them in
+//                         rank order, adds the residual and stores bf16. Used after the MoE combine of a prefill chunk.
+#include <algorithm>
+
+#include "mla_common.cuh"
+#include "ifab_kernels.h"
+
+using namespace ifab;
+using namespace ifab::mla;
+
+namespace {
+
+__global__ void __launch_bounds__(64) mla_q_rope_kernel(const bf16* q, long ldq, const int32_t* positions, bf16* q_lat, int H,
+                                                        int nope, int rope, float theta) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int h = blockIdx.x, t = blockIdx.y;
+  const int half = rope / 2;
+  const int i = threadIdx.x;
+  if (i >= half) return;
+  const int pos = positions[t];
+  const bf16* qr = q + (long)t * ldq + (long)h * (nope + rope) + nope;
+  bf16* out = q_lat + ((long)t * H + h) * ROW + LATENT;
+  float c, s;
+  rope_cos_sin(pos < 0 ? 0 : pos, i, rope, theta, &c, &s);
+  const float a = __bfloat162float(qr[i]), b = __bfloat162float(qr[i + half]);
+  out[i] = __float2bfloat16_rn(a * c - b * s);
+  out[i + half] = __float2bfloat16_rn(b * c + a * s);
+}
+
+struct MergeParams {
+  const float* scratch;   // [T][H][max_splits][LATENT + 2]
+  const int32_t* positions;
+  int n_sinks, window, kps, max_splits, H;
+  bf16* o_lat;            // [T][H][LATENT]
+};
+
+__global__ void __launch_bounds__(256) mla_merge_kernel(MergeParams p) {
+  __shared__ float wgt[64];
+  __shared__ float Ls;
+  grid_dep_launch();
+  grid_dep_wait();
+  const int h = blockIdx.x, t = blockIdx.y;
+  const int pos = p.positions[t];
+  bf16* out = p.o_lat + ((long)t * p.H + h) * LATENT;
+  if (pos < 0) {
+    for (int c = threadIdx.x; c < LATENT; c += blockDim.x) out[c] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  int first, nctx;
+  visible_range(pos, p.window, &first, &nctx);
+  const int total = p.n_sinks + nctx;
+  int ns = (total + p.kps - 1) / p.kps;
+  if (ns > p.max_splits) ns = p.max_splits;
+  const float* base = p.scratch + ((long)t * p.H + h) * p.max_splits * (LATENT + 2);
+  if (threadIdx.x == 0) {
+    float M = -INFINITY;
+    for (int s = 0; s < ns; ++s) M = fmaxf(M, base[(long)s * (LATENT + 2) + LATENT]);
+    float L = 0.f;
+    for (int s = 0; s < ns; ++s) {
+      const float ms = base[(long)s * (LATENT + 2) + LATENT];
+      const float w = (ms == -INFINITY) ? 0.f : __expf(ms - M);
+      wgt[s] = w;
+      L += w * base[(long)s * (LATENT + 2) + LATENT + 1];
+    }
+    Ls = L;
+  }
+  __syncthreads();
+  const float invL = Ls > 0.f ? 1.f / Ls : 0.f;
+  for (int c = threadIdx.x; c < LATENT; c += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < ns; ++s) v += wgt[s] * base[(long)s * (LATENT + 2) + c];
+    out[c] = __float2bfloat16_rn(v * invL);
+  }
+}
+
+struct ArRowsParams {
+  const float* parts[IFAB_MAX_RANKS];   // parts[r]: rank r's partial as mapped here (parts[rank] is local)
+  const bf16* residual; long ldr;
+  bf16* out; long ldo;
+  long rows; int D;
+  FabricView fv; uint64_t* seq; uint32_t* done;
+};
+
+__global__ void __launch_bounds__(256) allreduce_rows_kernel(ArRowsParams p) {
+  __shared__ int s_ok, s_last;
+  grid_dep_launch();
+  grid_dep_wait();
+  const uint64_t epoch = *reinterpret_cast<volatile uint64_t*>(p.seq) + 1;
+  const uint32_t par = (uint32_t)(epoch & 1);
+  const int world = p.fv.world, rank = p.fv.rank;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (world > 1) {
+    // this rank's partial was written by the previous kernel of the stream: tell every peer, then wait for theirs
+    if (blockIdx.x == 0 && (int)threadIdx.x < world && (int)threadIdx.x != rank) {
+      __threadfence_system();
+      st_release_sys(p.fv.flags[threadIdx.x] + (size_t)par * p.fv.flag_half_words + rank, epoch);
+    }
+    if ((int)threadIdx.x < world && (int)threadIdx.x != rank) {
+      if (!wait_flag_bounded(p.fv.flags[rank] + (size_t)par * p.fv.flag_half_words + threadIdx.x, epoch, p.fv.spin_limit)) {
+        s_ok = 0;
+        atomicOr(p.fv.status, IFAB_STATUS_PEER_TIMEOUT);
+      }
+    }
+    __syncthreads();
+  }
+  if (s_ok) {
+    const long chunks = p.rows * (p.D >> 2);   // float4 chunks
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += (long)gridDim.x * blockDim.x) {
+      const long row = i / (p.D >> 2);
+      const int c = (int)(i % (p.D >> 2)) * 4;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < world; ++r) {
+        const float4 v = *reinterpret_cast<const float4*>(p.parts[r] + row * p.D + c);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      float o[4] = {acc.x, acc.y, acc.z, acc.w};
+      if (p.residual) {
+        const bf16* rr = p.residual + row * p.ldr + c;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[k] = bf16_round(o[k]) + __bfloat162float(rr[k]);
+      }
+      __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(p.out + row * p.ldo + c);
+      dst[0] = __floats2bfloat162_rn(o[0], o[1]);
+      dst[1] = __floats2bfloat162_rn(o[2], o[3]);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = (atomicAdd(p.done, 1u) == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x == 0) {
+    *p.done = 0;
+    *p.seq = epoch;
+    __threadfence();
+  }
+}
+
+}  // namespace
+
+extern "C" int ifab_mla_q_rope(const void* q, long ldq, const int32_t* positions, void* q_lat, int T, int H, int nope, int rope,
+                               float theta, void* stream) {
+  if (rope != ROPE || T < 1 || H < 1) return -1;
+  return launch_chain(mla_q_rope_kernel, dim3(H, T), dim3(64), 0, (cudaStream_t)stream, (const bf16*)q, ldq, positions, (bf16*)q_lat, H,
+                      nope, rope, theta);
+}
+
+extern "C" int ifab_mla_merge(const float* scratch, const int32_t* positions, int n_sinks, int window, int keys_per_split,
+                              int max_splits, int T, int H, void* o_lat, void* stream) {
+  if (max_splits < 1 || max_splits > 64 || T < 1 || H < 1) return -1;
+  MergeParams p{scratch, positions, n_sinks, window, keys_per_split, max_splits, H, (bf16*)o_lat};
+  return launch_chain(mla_merge_kernel, dim3(H, T), dim3(256), 0, (cudaStream_t)stream, p);
+}
+
+// parts[r] (r < world): rank r's f32 [rows, D] partial in symmetric memory as mapped into this process. Partials must be
+// double buffered by the caller (alternate two symmetric buffers between consecutive calls).
+extern "C" int ifab_allreduce_rows(const void* const* parts, const void* residual, long ldr, void* out, long ldo, long rows, int D,
+                                   const IfabFabric* fab, void* stream) {
+  if (rows < 1 || D % 4 || (residual && ldr % 4) || ldo % 4) return -1;
+  ArRowsParams p;
+  if (int rc = fabric_view(fab, &p.fv)) return rc;
+  for (int r = 0; r < IFAB_MAX_RANKS; ++r) p.parts[r] = r < fab->world ? (const float*)parts[r] : nullptr;
+  p.residual = (const bf16*)residual; p.ldr = ldr; p.out = (bf16*)out; p.ldo = ldo; p.rows = rows; p.D = D;
+  p.seq = fab->seq; p.done = fab->done;
+  if ((size_t)fab->world > fab->flag_half_words) return -4;
+  const long chunks = rows * (D >> 2);
+  const int grid = (int)std::min<long>(2 * 148, (chunks + 255) / 256);
+  return launch_chain(allreduce_rows_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p);
+}

@@ -52,8 +52,10 @@ struct Pipe {
   }
 
   // one thread. (ax, ay[, az]) / (bx, by[, bz]) = tile origins; k advances along x.
+  // b_row_hi >= 0: the B tile is two boxes of BN/2 rows (tb's box is BN/2 rows): rows b_row.. fill the first half of
+  // the stage's B area and rows b_row_hi.. the second half (paired gate / up projections under one accumulator).
   __device__ __forceinline__ void produce(const CUtensorMap* ta, const CUtensorMap* tb, int num_kb, int a_row, int b_row, int b_batch,
-                                          uint32_t spin_limit, uint32_t* status) {
+                                          uint32_t spin_limit, uint32_t* status, int b_row_hi = -1) {
     using C = Cfg<BN, NSTAGES>;
     int issued = 0;
     for (int kb = 0; kb < num_kb; ++kb) {
@@ -66,6 +68,10 @@ struct Pipe {
       tma_load_2d(a_dst, ta, &full[s], kb * BK, a_row);
       if (b_batch >= 0) tma_load_3d(a_dst + C::A_BYTES, tb, &full[s], kb * BK, b_row, b_batch);
       else tma_load_2d(a_dst + C::A_BYTES, tb, &full[s], kb * BK, b_row);
+      if (b_row_hi >= 0) {
+        if (b_batch >= 0) tma_load_3d(a_dst + C::A_BYTES + C::B_BYTES / 2, tb, &full[s], kb * BK, b_row_hi, b_batch);
+        else tma_load_2d(a_dst + C::A_BYTES + C::B_BYTES / 2, tb, &full[s], kb * BK, b_row_hi);
+      }
       issued = kb + 1;
     }
     if (*abort_flag) {

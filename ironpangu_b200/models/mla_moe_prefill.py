@@ -1,0 +1,148 @@
+"""Tensor-core prefill path of the MLA + MoE decoder (chunks of up to ``max_rows`` prompt tokens).
+
+The decode path streams every weight matrix once per step; pushing a long prompt through it 8 tokens at a time
+re-reads the whole model 64 times per 512 tokens. This path runs a chunk as matrix-matrix work instead:
+
+* dense linears (qkv_a, q_b, shared expert down) on the tcgen05 GEMM, the row-parallel o_proj on the fused
+  GEMM + all-reduce kernel when the model is tensor parallel;
+* the absorbed-MLA projections (q_nope @ W_uk, o_lat @ W_uv) as one small GEMM per head;
+* attention through the split-KV kernels of the decode path with one query row per token (causality comes from
+  the per-row positions), 64 query rows per launch;
+* the MoE through a device-side dispatch (routes sorted by expert, 128-row tile table), the grouped expert GEMM
+  with the SwiGLU epilogue, the grouped down GEMM and a score-weighted combine; the shared expert rides on the same
+  grouped kernel with a single "expert"; across ranks the partial outputs are summed by a pull all-reduce.
+
+It shares the KV cache, the page table and the weights with ``MlaMoeDecoder`` and leaves the cache exactly as
+token-by-token decoding would (same normalisation and rotary kernel), so decode continues from it.
+Rounding differs from the decode path in one place: expert outputs are stored as bf16 rows before the
+combine (the decode kernels keep them in f32), which stays inside the tolerance of the oracle tests.
+Reference: the uncaptured 4096-token prefill envelope (native/src/token_executor.h:1449-1587).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops import decode as K
+from ..ops import gemm as G
+from ..ops import prefill as P
+from .mla_moe import BF16, MlaMoeDecoder
+
+
+class MlaMoePrefill:
+    def __init__(self, dec: MlaMoeDecoder, max_rows: int = 512, attn_rows: int = 64):
+        self.dec, self.M, self.QC = dec, max_rows, attn_rows
+        c, dev, fab = dec.cfg, dec.fabric.device, dec.fabric
+        hl, el, M = dec.hl, dec.el, max_rows
+        e = lambda *s, dt=BF16: torch.empty(*s, dtype=dt, device=dev)
+        self.tokens = torch.zeros(M, dtype=torch.int32, device=dev)
+        self.positions = torch.zeros(M, dtype=torch.int32, device=dev)
+        self.slots = torch.zeros(M, dtype=torch.int32, device=dev)
+        self.x_sym = fab.symmetric_empty((M, c.hidden)) if fab.world > 1 else None
+        self.x = self.x_sym.tensor if self.x_sym is not None else e(M, c.hidden)
+        Mpad = (M + 127) // 128 * 128     # whole 128-row tiles of the one-expert group are stored
+        self.h = torch.zeros(Mpad, c.hidden, dtype=BF16, device=dev)
+        self.qkv = e(M, c.q_lora + c.kv_lora + c.rope)
+        self.qn = e(M, c.q_lora)
+        self.q = e(M, hl * c.qk_dim)
+        self.q_lat = e(M, hl, c.kv_lora + c.rope)
+        self.o_lat = e(M, hl, c.kv_lora)
+        self.attn = e(M, hl * c.vdim)
+        self.scratch = e(self.QC * hl * dec.max_splits * (c.kv_lora + 2), dt=torch.float32)
+        self.ids = torch.zeros(M, c.topk, dtype=torch.int32, device=dev)
+        self.wts = e(M, c.topk, dt=torch.float32)
+        self.route = P.DispatchBuffers(M, c.topk, el, dev)
+        R = self.route.max_routes
+        self.xp = torch.zeros(R, c.hidden, dtype=BF16, device=dev)
+        self.act = e(R, c.expert_ffn)
+        self.y = e(R, c.hidden)
+        fs = c.shared_ffn // fab.world
+        self.sact = e(Mpad, fs)
+        self.sd = e(Mpad, c.hidden)
+        # the shared expert as a one-expert group over all rows of the chunk (static tile table)
+        nt = (M + 127) // 128
+        st = torch.zeros(nt, 4, dtype=torch.int32)
+        for i in range(nt):
+            st[i, 1], st[i, 2] = i * 128, 128
+        self.shared_tiles = st.to(dev)
+        self.shared_ntiles = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.parts = [fab.symmetric_empty((M, c.hidden), torch.float32) for _ in range(2)] if fab.world > 1 else None
+        self._calls = 0
+        # W_uk^T per head: [hl, latent, nope], the [N, K] operand of the absorb GEMM
+        self.w_uk_t = [dec.w[f"layers.{l}.kv_b"][:, :c.nope, :].transpose(1, 2).contiguous() for l in range(c.layers)]
+        self.launches = 0
+
+    def forward(self, tokens: torch.Tensor, pos0: int, slot: int = 0) -> torch.Tensor:
+        """Run ``tokens`` (int32 ``[m]``, ``m <= max_rows``, already on the device) at positions ``pos0 .. pos0+m-1``
+        of sequence slot ``slot``; returns the greedy next token after the last row (device tensor ``[1]``)."""
+        d, c, fab = self.dec, self.dec.cfg, self.dec.fabric
+        w, st, hl = d.w, fab.desc.status, d.hl
+        m = tokens.numel()
+        assert 1 <= m <= self.M
+        self.tokens[:m].copy_(tokens)
+        self.positions[:m].copy_(torch.arange(pos0, pos0 + m, dtype=torch.int32, device=tokens.device))
+        self.slots[:m].fill_(slot)
+        tok, pos, sl = self.tokens[:m], self.positions[:m], self.slots[:m]
+        x, h = self.x[:m], self.h[:m]
+        n_launch = 0
+        K.embedding(tok, w["embed"], out=x, status_ptr=st)
+        self.shared_ntiles.fill_((m + 127) // 128)
+        for l in range(c.layers):
+            p = f"layers.{l}."
+            # ---- attention ----
+            K.rmsnorm(x, w[p + "attn_norm"], c.eps, out=h)
+            qkv = G.gemm(h, w[p + "qkv_a"], out=self.qkv[:m], status_ptr=st)
+            K.mla_kv_write(qkv[:, c.q_lora:], w[p + "kv_a_norm"], pos, sl, d.page_table, d.caches[l], latent=c.kv_lora,
+                           rope=c.rope, eps=c.eps, theta=c.theta, status_ptr=st)
+            K.rmsnorm(qkv[:, :c.q_lora], w[p + "q_a_norm"], c.eps, out=self.qn[:m])
+            q = G.gemm(self.qn[:m], w[p + "q_b"], out=self.q[:m], status_ptr=st)
+            q_lat, o_lat, attn = self.q_lat[:m], self.o_lat[:m], self.attn[:m]
+            for hh in range(hl):
+                G.gemm(q[:, hh * c.qk_dim: hh * c.qk_dim + c.nope], self.w_uk_t[l][hh], out=q_lat[:, hh, :c.kv_lora], status_ptr=st)
+            P.mla_q_rope(q, pos, q_lat, nope=c.nope, rope=c.rope, theta=c.theta)
+            for q0 in range(0, m, self.QC):
+                q1 = min(m, q0 + self.QC)
+                P.mla_split(q_lat[q0:q1], d.caches[l], pos[q0:q1], sl[q0:q1], d.page_table, self.scratch, scale=c.scale,
+                            window=c.window, keys_per_split=d.kps, max_splits=d.max_splits, status_ptr=st)
+                P.mla_merge(self.scratch, pos[q0:q1], o_lat[q0:q1], window=c.window, keys_per_split=d.kps, max_splits=d.max_splits)
+            kvb = w[p + "kv_b"]
+            for hh in range(hl):
+                G.gemm(o_lat[:, hh, :], kvb[hh, c.nope:, :], out=attn[:, hh * c.vdim:(hh + 1) * c.vdim], status_ptr=st)
+            if fab.world > 1:
+                G.gemm_allreduce(attn, w[p + "o_proj"], fab, self._sym_rows(m), residual=x)
+            else:
+                G.gemm(attn, w[p + "o_proj"], residual=x, out=x, status_ptr=st)
+            # ---- MoE ----
+            P.router_block(x, w[p + "router"], c.topk, self.ids[:m], self.wts[:m], norm_w=w[p + "ffn_norm"], eps=c.eps,
+                           scoring=c.scoring, scale=c.route_scale, xn=h)
+            P.moe_dispatch(self.ids[:m], d.rank * d.el, d.el, self.route)
+            P.moe_gather(h, self.route, self.xp)
+            P.grouped_gemm(self.xp, w[p + "gate_up"], self.route.tiles, self.route.num_tiles, self.act, swiglu=True, status_ptr=st)
+            P.grouped_gemm(self.act, w[p + "down"], self.route.tiles, self.route.num_tiles, self.y, status_ptr=st)
+            sgu, sdn = w[p + "shared_gate_up"], w[p + "shared_down"]
+            P.grouped_gemm(h, sgu.unsqueeze(0), self.shared_tiles, self.shared_ntiles, self.sact[:m], swiglu=True, status_ptr=st)
+            G.gemm(self.sact[:m], sdn, out=self.sd[:m], status_ptr=st)
+            if fab.world > 1:
+                part = self.parts[self._calls & 1]
+                self._calls += 1
+                P.moe_combine(self.y, self.route, self.wts[:m], shared=self.sd[:m], out_f32=part.tensor[:m])
+                P.allreduce_rows(part, fab, x, residual=x)
+            else:
+                P.moe_combine(self.y, self.route, self.wts[:m], shared=self.sd[:m], residual=x, out=x)
+            n_launch += 17 + 2 * hl + 2 * ((m + self.QC - 1) // self.QC)
+        # greedy token after the last row through the decode head (vocabulary-sharded argmax exchange included)
+        K.lm_head_argmax(x[m - 1:m], w["lm_head"], fab, norm_w=w["final_norm"], eps=c.eps, vocab_offset=d.rank * d.vl,
+                         partial=d.partial, logits=None if d.logits is None else d.logits[:1], out_ids=d.next_ids[:1],
+                         out_vals=d.next_vals[:1])
+        self.launches = n_launch + 2
+        return d.next_ids[:1]
+
+    def _sym_rows(self, m: int):
+        """The symmetric activation buffer restricted to ``m`` rows (same peer pointers, smaller shape)."""
+        if m == self.M:
+            return self.x_sym
+        v = object.__new__(type(self.x_sym))
+        v.__dict__.update(self.x_sym.__dict__)
+        v.tensor = self.x_sym.tensor[:m]
+        return v

@@ -91,6 +91,15 @@ _SIGS = {
     "ifab_gqa_rope_kv_write": [_P, c_long, _P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_float, _P, _P],
     "ifab_mla_moe_decode_step": [_P, c_int, _P, _P],
+    "ifab_grouped_gemm_bf16": [_P, c_long, c_int, _P, c_int, c_int, c_int, _P, _P, c_int, _P, c_long, c_int, _P, _P],
+    "ifab_router_block": [_P, c_long, _P, c_float, _P, _P, _P, _P, _P, _P, c_long, c_int, c_int, c_int, c_int, c_int, c_int,
+                          c_float, _P],
+    "ifab_moe_dispatch": [_P, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, c_int, _P],
+    "ifab_moe_gather": [_P, c_long, _P, _P, _P, c_long, c_int, c_int, _P],
+    "ifab_moe_combine": [_P, c_long, _P, _P, c_int, c_int, c_int, _P, c_long, _P, c_long, _P, _P, c_long, _P],
+    "ifab_mla_q_rope": [_P, c_long, _P, _P, c_int, c_int, c_int, c_int, c_float, _P],
+    "ifab_mla_merge": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
+    "ifab_allreduce_rows": [_P, _P, c_long, _P, c_long, c_long, c_int, C.POINTER(IfabFabric), _P],
     "ifab_gqa_decode_attention": [_P, c_long, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
                                   c_int, c_int, _P, c_u64, _P, c_long, _P, _P],
 }

@@ -1,0 +1,119 @@
+"""ctypes wrappers of the prefill-side kernels: grouped expert GEMM (tcgen05), block router, MoE dispatch / gather /
+combine, MLA query rotary + split merge, pull all-reduce of row partials. All of them take pre-allocated outputs
+(prefill runs on persistent buffers) and launch on the current stream."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import check
+
+BF16 = torch.bfloat16
+
+
+def _s() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def grouped_gemm(a: torch.Tensor, b: torch.Tensor, tiles: torch.Tensor, num_tiles: torch.Tensor, out: torch.Tensor, *,
+                 swiglu: bool = False, status_ptr: Optional[int] = None) -> torch.Tensor:
+    """``out[r] = a[r] @ b[expert(r)].T`` over the 128-row tiles listed in ``tiles`` (int32 ``[max_tiles, 4]``:
+    expert, first row, valid rows, 0); with ``swiglu`` ``b`` is ``[E, 2F, K]`` and ``out`` is ``[rows, F]``."""
+    rows, K = a.shape
+    E, N, Kb = b.shape
+    assert Kb == K and a.stride(1) == 1 and b.is_contiguous() and out.stride(1) == 1 and tiles.dtype == torch.int32
+    check(_lib.load().ifab_grouped_gemm_bf16(a.data_ptr(), a.stride(0), rows, b.data_ptr(), E, N, K, tiles.data_ptr(),
+                                             num_tiles.data_ptr(), tiles.shape[0], out.data_ptr(), out.stride(0), int(swiglu),
+                                             status_ptr, _s()), "grouped_gemm")
+    return out
+
+
+def router_block(x: torch.Tensor, w_router: torch.Tensor, topk: int, ids: torch.Tensor, wts: torch.Tensor, *,
+                 norm_w: Optional[torch.Tensor] = None, eps: float = 1e-5, bias: Optional[torch.Tensor] = None,
+                 scoring: str = "softmax", renorm: bool = True, scale: float = 1.0, logits: Optional[torch.Tensor] = None,
+                 xn: Optional[torch.Tensor] = None) -> None:
+    """Router projection (f32) + top-k for any number of rows; ``xn`` receives the normalised rows."""
+    M, D = x.shape
+    E = w_router.shape[0]
+    mode = {"softmax": 0, "sigmoid_bias_group_topk": 1}[scoring]
+    check(_lib.load().ifab_router_block(x.data_ptr(), x.stride(0), _p(norm_w), eps, w_router.data_ptr(), _p(bias), _p(logits),
+                                        ids.data_ptr(), wts.data_ptr(), _p(xn), 0 if xn is None else xn.stride(0), M, D, E, topk,
+                                        mode, int(renorm), scale, _s()), "router_block")
+
+
+class DispatchBuffers:
+    """Device-side routing state of one prefill chunk (allocated once for ``max_rows`` tokens)."""
+
+    def __init__(self, max_rows: int, topk: int, e_local: int, device):
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=device)
+        self.max_routes = max_rows * topk
+        self.max_tiles = (self.max_routes + 127) // 128 + e_local
+        self.counts = i32(e_local)
+        self.route_row = i32(self.max_routes)
+        self.perm_token = i32(self.max_routes)
+        self.tiles = i32(self.max_tiles, 4)
+        self.num_tiles = i32(1)
+        self.total_rows = i32(1)
+
+
+def moe_dispatch(ids: torch.Tensor, e0: int, e_local: int, buf: DispatchBuffers) -> None:
+    M, topk = ids.shape
+    assert M * topk <= buf.max_routes and ids.is_contiguous()
+    check(_lib.load().ifab_moe_dispatch(ids.data_ptr(), M, topk, e0, e_local, buf.counts.data_ptr(), buf.route_row.data_ptr(),
+                                        buf.perm_token.data_ptr(), buf.tiles.data_ptr(), buf.num_tiles.data_ptr(),
+                                        buf.total_rows.data_ptr(), buf.max_tiles, _s()), "moe_dispatch")
+
+
+def moe_gather(xn: torch.Tensor, buf: DispatchBuffers, xp: torch.Tensor) -> None:
+    check(_lib.load().ifab_moe_gather(xn.data_ptr(), xn.stride(0), buf.perm_token.data_ptr(), buf.total_rows.data_ptr(),
+                                      xp.data_ptr(), xp.stride(0), xn.shape[1], xp.shape[0], _s()), "moe_gather")
+
+
+def moe_combine(y: torch.Tensor, buf: DispatchBuffers, wts: torch.Tensor, *, shared: Optional[torch.Tensor] = None,
+                residual: Optional[torch.Tensor] = None, out_f32: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> None:
+    M, topk = wts.shape
+    D = y.shape[1]
+    check(_lib.load().ifab_moe_combine(y.data_ptr(), y.stride(0), buf.route_row.data_ptr(), wts.data_ptr(), M, topk, D,
+                                       _p(shared), 0 if shared is None else shared.stride(0), _p(residual),
+                                       0 if residual is None else residual.stride(0), _p(out_f32), _p(out),
+                                       0 if out is None else out.stride(0), _s()), "moe_combine")
+
+
+def mla_q_rope(q: torch.Tensor, positions: torch.Tensor, q_lat: torch.Tensor, *, nope: int, rope: int, theta: float) -> None:
+    T, H, _ = q_lat.shape
+    check(_lib.load().ifab_mla_q_rope(q.data_ptr(), q.stride(0), positions.data_ptr(), q_lat.data_ptr(), T, H, nope, rope, theta,
+                                      _s()), "mla_q_rope")
+
+
+def mla_split(q_lat: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
+              scratch: torch.Tensor, *, scale: float, window: int, keys_per_split: int, max_splits: int,
+              status_ptr: Optional[int] = None) -> None:
+    """Split-KV partials only (no value up-projection): ``scratch`` = f32 ``[T, H, max_splits, 514]``."""
+    T, H, row = q_lat.shape
+    num_pages, page_tokens, _ = cache.shape
+    check(_lib.load().ifab_mla_decode_attention(
+        q_lat.data_ptr(), cache.data_ptr(), positions.data_ptr(), slots.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+        page_tokens, num_pages, None, 0, window, scale, T, H, 512, row - 512, keys_per_split, max_splits, scratch.data_ptr(),
+        scratch.numel() * 4, None, 0, 0, None, 0, status_ptr, _s()), "mla_split")
+
+
+def mla_merge(scratch: torch.Tensor, positions: torch.Tensor, o_lat: torch.Tensor, *, window: int, keys_per_split: int,
+              max_splits: int) -> None:
+    T, H, _ = o_lat.shape
+    check(_lib.load().ifab_mla_merge(scratch.data_ptr(), positions.data_ptr(), 0, window, keys_per_split, max_splits, T, H,
+                                     o_lat.data_ptr(), _s()), "mla_merge")
+
+
+def allreduce_rows(parts, fabric, out: torch.Tensor, *, residual: Optional[torch.Tensor] = None) -> None:
+    """``parts``: SymmetricTensor f32 ``[rows, D]`` (this call's parity buffer); ``out = bf16(sum_ranks parts) + residual``."""
+    rows, D = out.shape
+    check(_lib.load().ifab_allreduce_rows(parts.peer_ptrs, _p(residual), 0 if residual is None else residual.stride(0),
+                                          out.data_ptr(), out.stride(0), rows, D, C.byref(fabric.desc), _s()), "allreduce_rows")
