@@ -34,6 +34,8 @@ def parse():
     ap.add_argument("--impl", default="native", choices=["native", "reference", "nccl_cublas"])
     ap.add_argument("--model", default="flagship", choices=["flagship", "tiny"])
     ap.add_argument("--context", type=int, default=512)
+    ap.add_argument("--prefill", default="gemm", choices=["gemm", "decode"],
+                    help="gemm: tensor-core prefill path (native impl only); decode: prompt through the decode kernels, 8 rows a time")
     ap.add_argument("--persistent", type=int, default=0, help="1: one persistent cooperative launch per decode step")
     ap.add_argument("--layers", type=int, default=0, help="override layer count (marks the run as a reduced config)")
     return ap.parse_args()
@@ -130,7 +132,11 @@ def main():
     else:
         from baseline.nccl_cublas import NcclCublasDecoder
         dec = NcclCublasDecoder(cfg, weights, rank, world, max_tokens=8, max_context=max_context)
-    eng = DecodeEngine(dec)
+    pre = None
+    if args.impl == "native" and args.prefill == "gemm":
+        from ironpangu_b200.models.mla_moe_prefill import MlaMoePrefill
+        pre = MlaMoePrefill(dec, max_rows=min(512, args.context))
+    eng = DecodeEngine(dec, prefill=pre)
     init_s = time.time() - t0
 
     def barrier():
@@ -211,6 +217,7 @@ def main():
                        and not args.layers else f"{args.model} layers={cfg.layers} (reduced config)",
                        "params_b": round(cfg.param_count() / 1e9, 2), "global_batch": 1, "seq_len": args.context,
                        "decode_tokens": K, "parallelism": f"tp{world}ep{world}", "decode_step": "single persistent launch" if args.persistent else "operator chain",
+                       "prefill": args.prefill if args.impl == "native" else "library",
                        "l2": "per-step weight stream (>= 2.5 GB per rank) exceeds the 126 MB L2; no explicit flush",
                        "baseline_ref": "17.7293 ms TPOT on 8x Ascend (docs/validation/2026-10-17-packed-c8/README.md:20-23)",
                        "weight_bytes_per_rank": weight_bytes},

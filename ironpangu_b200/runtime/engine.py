@@ -14,8 +14,12 @@ import torch
 
 
 class DecodeEngine:
-    def __init__(self, decoder, chunk: Optional[int] = None):
+    def __init__(self, decoder, chunk: Optional[int] = None, prefill=None):
+        """``prefill``: optional tensor-core prefill object (``models.mla_moe_prefill.MlaMoePrefill``) with
+        ``forward(tokens, pos0, slot)`` and ``M`` (rows per chunk); without it prompts go through the decode kernels in
+        chunks of ``chunk`` rows."""
         self.dec = decoder
+        self.prefill_path = prefill
         self.chunk = chunk or decoder.T
         self.pos = 0
         self._ctl_host = torch.zeros(2, dtype=torch.int32).pin_memory()
@@ -64,6 +68,14 @@ class DecodeEngine:
         n = len(tokens)
         host = torch.tensor(tokens, dtype=torch.int32).pin_memory()
         last = None
+        if self.prefill_path is not None:
+            pp = self.prefill_path
+            dev_tokens = host.to(d.tokens.device, non_blocking=True)
+            for s in range(0, n, pp.M):
+                last = pp.forward(dev_tokens[s:s + pp.M], self.pos + s, 0)
+            self.pos += n
+            self._out_host.copy_(last)
+            return int(self._out_host[0])
         for s in range(0, n, self.chunk):
             m = min(self.chunk, n - s)
             d.tokens[:m].copy_(host[s:s + m], non_blocking=True)

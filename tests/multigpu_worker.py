@@ -112,6 +112,18 @@ def main():
     torch.testing.assert_close(one.logits[:n], ref[:n, rank * vl:(rank + 1) * vl], rtol=2e-2, atol=2e-2)
     assert fab.status() == 0
     print(f"rank {rank}: ok persistent step tp={world}", flush=True)
+    # tensor-core prefill path (fused GEMM + all-reduce for o_proj, pull all-reduce after the MoE), then decode on its cache
+    from ironpangu_b200.models.mla_moe_prefill import MlaMoePrefill
+    pdec = MlaMoeDecoder(cfg, shard_weights(cfg, full, rank, world, "cuda"), fab, max_tokens=1, max_context=64, keep_logits=True)
+    pre = MlaMoePrefill(pdec, max_rows=8, attn_rows=8)
+    nxt = pre.forward(torch.tensor(prompt[:7], dtype=torch.int32, device="cuda"), 0)
+    torch.testing.assert_close(pdec.logits[0], ref[6, rank * vl:(rank + 1) * vl], rtol=3e-2, atol=3e-2)
+    pdec.tokens.fill_(prompt[7])
+    pdec.positions.fill_(7)
+    pdec.forward(1)
+    torch.testing.assert_close(pdec.logits[0], ref[7, rank * vl:(rank + 1) * vl], rtol=3e-2, atol=3e-2)
+    assert fab.status() == 0
+    print(f"rank {rank}: ok prefill path tp={world}", flush=True)
     print(f"rank {rank}: ok tiny model tp={world}", flush=True)
     # 4. dense GQA model (TP = world when the tiny model's kv heads divide) + cross-rank top-k sampling
     from ironpangu_b200.models import dense_gqa as D
