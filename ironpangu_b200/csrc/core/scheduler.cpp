@@ -94,6 +94,7 @@ LiveScheduler::Plan LiveScheduler::plan() {
     queue_.pop_front();
     s.fed = s.req.prefix_hit;
     ++running_;
+    p.admitted.push_back({(uint32_t)i, s.req.id});
   }
   // quanta
   std::vector<uint32_t> costs(seqs_.size(), 0);

@@ -66,6 +66,7 @@ class LiveScheduler {
     paging::SequenceBatch batch;
     std::vector<uint64_t> requests;     // request of each slice
     std::vector<uint32_t> released;     // residents freed since the previous plan (their state may be dropped)
+    std::vector<std::pair<uint32_t, uint64_t>> admitted;   // (resident, request) admitted by this plan
     bool empty() const { return batch.slices.empty(); }
   };
   Plan plan();

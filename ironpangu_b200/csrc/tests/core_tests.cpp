@@ -424,8 +424,13 @@ plan Cpu for Acc { target = cpu_f32_v1; })");
   CHECK_THROWS(Invalid, ex.run({{"y", {1}}}));
 }
 
+#include "serve_tests.h"
+
 int main() {
   std::pair<const char*, std::function<void()>> tests[] = {
+      {"serve_batching", test_serve_batching_matches_sequential}, {"serve_admission", test_serve_validation_and_admission},
+      {"serve_backpressure_cancel", test_serve_backpressure_cancel_and_eos}, {"serve_failure_shutdown", test_serve_engine_failure_and_shutdown},
+      {"api_tokenizer", test_api_tokenizer_and_sampling_json},
       {"state_pool", test_state_pool}, {"prefix_index", test_prefix_index}, {"paging", test_paging},
       {"rankplan_runtime", test_rankplan_and_runtime}, {"transfer", test_transfer}, {"scheduler", test_scheduler}, {"cpu_plan", test_cpu_plan}};
   for (auto& t : tests) {
