@@ -145,7 +145,10 @@ struct AttnParams {
   int T, H, kps, max_splits;
   float* scratch;   // [T][H][max_splits][LATENT + 2]
   uint32_t* status;
+  int q8;           // cache rows are packed: 512 int8 | 64 bf16 rope | 4 f32 scales (one per 128 latent columns) = 656 bytes
 };
+
+constexpr int ROW_Q8 = LATENT + ROPE * 2 + 16;
 
 template <int HG>
 __global__ void __launch_bounds__(256) mla_split_kernel(AttnParams p) {
@@ -184,12 +187,13 @@ __global__ void __launch_bounds__(256) mla_split_kernel(AttnParams p) {
   for (int kb = k_begin + warp; kb < k_end; kb += 8 * KB) {
     uint4 ra[KB], rb[KB];
     __nv_bfloat162 rr[KB];
-    bool ok[KB];
+    bool ok[KB], packed[KB];
 #pragma unroll
     for (int j = 0; j < KB; ++j) {
       const int k = kb + 8 * j;
       ok[j] = k < k_end;
       const bf16* row = nullptr;
+      packed[j] = false;
       if (ok[j]) {
         if (k < p.n_sinks) {
           row = p.sinks + (long)k * ROW;
@@ -198,12 +202,22 @@ __global__ void __launch_bounds__(256) mla_split_kernel(AttnParams p) {
           if (r < 0) {
             if (lane == 0 && p.status) atomicOr(p.status, IFAB_STATUS_BAD_INDEX);
             ok[j] = false;
+          } else if (p.q8) {
+            // packed row: this lane's 8 + 8 int8 latents travel in ra, the two tile scales in rb
+            const unsigned char* r8 = reinterpret_cast<const unsigned char*>(p.cache) + r * ROW_Q8;
+            const uint2 a8 = *reinterpret_cast<const uint2*>(r8 + lane * 8);
+            const uint2 b8 = *reinterpret_cast<const uint2*>(r8 + 256 + lane * 8);
+            ra[j] = make_uint4(a8.x, a8.y, b8.x, b8.y);
+            rb[j].x = *reinterpret_cast<const uint32_t*>(r8 + LATENT + ROPE * 2 + 4 * (lane >> 4));
+            rb[j].y = *reinterpret_cast<const uint32_t*>(r8 + LATENT + ROPE * 2 + 4 * (2 + (lane >> 4)));
+            rr[j] = *reinterpret_cast<const __nv_bfloat162*>(r8 + LATENT + lane * 4);
+            packed[j] = true;
           } else {
             row = p.cache + r * ROW;
           }
         }
       }
-      if (ok[j]) {
+      if (ok[j] && !packed[j]) {
         ra[j] = *reinterpret_cast<const uint4*>(row + lane * 8);
         rb[j] = *reinterpret_cast<const uint4*>(row + 256 + lane * 8);
         rr[j] = *reinterpret_cast<const __nv_bfloat162*>(row + LATENT + lane * 2);
@@ -213,8 +227,18 @@ __global__ void __launch_bounds__(256) mla_split_kernel(AttnParams p) {
     for (int j = 0; j < KB; ++j) {
       if (!ok[j]) continue;
       RowFrag kf;
-      unpack8(ra[j], kf.lat);
-      unpack8(rb[j], kf.lat + 8);
+      if (packed[j]) {
+        const float sa = __uint_as_float(rb[j].x), sb = __uint_as_float(rb[j].y);
+        const uint32_t w[4] = {ra[j].x, ra[j].y, ra[j].z, ra[j].w};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int q = (int)(signed char)((w[i >> 2] >> (8 * (i & 3))) & 0xff);
+          kf.lat[i] = (float)q * (i < 8 ? sa : sb);
+        }
+      } else {
+        unpack8(ra[j], kf.lat);
+        unpack8(rb[j], kf.lat + 8);
+      }
       const float2 r2 = __bfloat1622float2(rr[j]);
       kf.rp[0] = r2.x;
       kf.rp[1] = r2.y;
@@ -368,11 +392,14 @@ extern "C" int ifab_mla_decode_attention(const void* q_lat, const void* cache, c
                                          float scale, int T, int H, int latent, int rope, int keys_per_split,
                                          int max_splits, float* scratch, uint64_t scratch_bytes, const void* w_kvb,
                                          int nope, int vdim, void* out, long ldo, uint32_t* status, void* stream) {
-  if (latent != LATENT || rope != ROPE) return -1;
+  if (latent != LATENT || (rope != ROPE && rope != -ROPE)) return -1;
   if (max_splits < 1 || max_splits > 64 || keys_per_split < 8) return -1;
   if ((uint64_t)T * H * max_splits * (LATENT + 2) * sizeof(float) > scratch_bytes) return -5;
+  // a negative `rope` selects the packed int8 cache layout (656-byte rows written by ifab_mla_kv_write_q8)
+  const int q8 = rope < 0 ? 1 : 0;
+  if (q8) rope = -rope;
   AttnParams p{(const bf16*)q_lat, (const bf16*)cache, positions, slots, page_table, max_pages, page_tokens, num_pages,
-               (const bf16*)sinks, sinks ? n_sinks : 0, window, scale, T, H, keys_per_split, max_splits, scratch, status};
+               (const bf16*)sinks, sinks ? n_sinks : 0, window, scale, T, H, keys_per_split, max_splits, scratch, status, q8};
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
   if (H % 4 == 0) rc = launch_split<4>(p, s);

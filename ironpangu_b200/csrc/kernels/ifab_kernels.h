@@ -127,6 +127,16 @@ int ifab_mla_decode_attention(const void* q_lat, const void* cache, const int32_
                               const void* w_kvb, int nope, int vdim, void* out, long ldo, uint32_t* status,
                               void* stream);
 
+/* ---- packed int8 latent cache (656-byte rows: 512 int8 | 64 bf16 rope | 4 f32 tile scales) and activation quantisation ----
+ * Attention over a packed cache: ifab_mla_decode_attention with rope = -64 and `cache` pointing at the packed rows. */
+int ifab_mla_kv_write_q8(const void* kv, long ldkv, const void* norm_w, float eps, float theta, const int32_t* positions,
+                         const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens, void* cache,
+                         int num_pages, int T, uint32_t* status, void* stream);
+int ifab_kv_dequantize_q8(const void* cache, void* out /* bf16 [rows, 576] */, long rows, void* stream);
+/* symmetric int8, ties away from zero; group_cols = K: per-row scale, 128: per-tile scales [T, ceil(K/128)] */
+int ifab_quantize_int8(const void* x, long ldx, void* q, long ldq, float* scales, long lds, int T, int K, int group_cols,
+                       void* stream);
+
 /* ---- whole decode step of the MLA + MoE decoder as one persistent cooperative kernel ----
  * All pointers are device pointers. `layers` points to an array of `n_layers` IfabMlaMoeLayer in device memory
  * (written once when the model is loaded). The launch computes exactly what the operator-by-operator chain

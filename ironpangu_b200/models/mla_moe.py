@@ -183,8 +183,11 @@ class MlaMoeDecoder:
 
     def __init__(self, cfg: MlaMoeConfig, weights: Dict[str, torch.Tensor], fabric: Fabric, *, max_tokens: int = 1,
                  max_context: int = 1024, num_slots: int = 1, keys_per_split: int = 64, keep_logits: bool = False,
-                 persistent: bool = False):
+                 persistent: bool = False, kv_int8: bool = False):
+        """``kv_int8``: keep the latent cache as packed int8 rows (656 bytes per token instead of 1152)."""
         assert 1 <= max_tokens <= 8
+        assert not (persistent and kv_int8), "the single-launch step reads bf16 cache rows"
+        self.kv_int8 = kv_int8
         self.cfg, self.w, self.fabric = cfg, weights, fabric
         self.rank, self.world = fabric.rank, fabric.world
         c, dev = cfg, fabric.device
@@ -206,8 +209,11 @@ class MlaMoeDecoder:
         self.positions = torch.zeros(T, dtype=torch.int32, device=dev)
         self.slots = torch.zeros(T, dtype=torch.int32, device=dev)
         self.page_table = torch.arange(self.num_pages, dtype=torch.int32, device=dev).view(num_slots, self.max_pages).contiguous()
-        self.caches = [torch.zeros(self.num_pages, c.page_tokens, c.kv_lora + c.rope, dtype=BF16, device=dev)
-                       for _ in range(c.layers)]
+        if kv_int8:
+            self.caches = [torch.zeros(self.num_pages, c.page_tokens, 656, dtype=torch.uint8, device=dev) for _ in range(c.layers)]
+        else:
+            self.caches = [torch.zeros(self.num_pages, c.page_tokens, c.kv_lora + c.rope, dtype=BF16, device=dev)
+                           for _ in range(c.layers)]
         # activations
         e = lambda *s, dt=BF16: torch.empty(*s, dtype=dt, device=dev)
         self.x = e(T, c.hidden)
@@ -329,8 +335,12 @@ class MlaMoeDecoder:
             p = f"layers.{l}."
             qkv = self.qkv[:T]
             K.gemv(x, w[p + "qkv_a"], norm_w=w[p + "attn_norm"], eps=c.eps, out=qkv)
-            K.mla_kv_write(qkv[:, c.q_lora:], w[p + "kv_a_norm"], pos, slot, self.page_table, self.caches[l],
-                           latent=c.kv_lora, rope=c.rope, eps=c.eps, theta=c.theta, status_ptr=st)
+            if self.kv_int8:
+                K.mla_kv_write_q8(qkv[:, c.q_lora:], w[p + "kv_a_norm"], pos, slot, self.page_table, self.caches[l], eps=c.eps,
+                                  theta=c.theta, status_ptr=st)
+            else:
+                K.mla_kv_write(qkv[:, c.q_lora:], w[p + "kv_a_norm"], pos, slot, self.page_table, self.caches[l],
+                               latent=c.kv_lora, rope=c.rope, eps=c.eps, theta=c.theta, status_ptr=st)
             q = self.q[:T]
             K.gemv(qkv[:, :c.q_lora], w[p + "q_b"], norm_w=w[p + "q_a_norm"], eps=c.eps, out=q)
             q_lat = self.q_lat[:T]
@@ -338,7 +348,7 @@ class MlaMoeDecoder:
             attn = self.attn[:T]
             K.mla_decode_attention(q_lat, self.caches[l], pos, slot, self.page_table, w[p + "kv_b"], nope=c.nope,
                                    scale=c.scale, window=c.window, keys_per_split=self.kps, max_splits=self.max_splits,
-                                   scratch=self.scratch, out=attn, status_ptr=st)
+                                   scratch=self.scratch, out=attn, status_ptr=st, packed=self.kv_int8)
             K.gemv_allreduce(attn, w[p + "o_proj"], fab, residual=x, out=x)
             K.router_topk(x, w[p + "router"], c.topk, norm_w=w[p + "ffn_norm"], eps=c.eps, scoring=c.scoring,
                           scale=c.route_scale, ticket_ptr=fab.ticket_ptr, logits=self.logits_r[:T],

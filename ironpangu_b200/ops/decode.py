@@ -172,6 +172,39 @@ def mla_kv_write(kv: torch.Tensor, norm_w: torch.Tensor, positions: torch.Tensor
           "mla_kv_write")
 
 
+def mla_kv_write_q8(kv: torch.Tensor, norm_w: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                    page_table: torch.Tensor, cache: torch.Tensor, *, eps: float, theta: float,
+                    status_ptr: Optional[int] = None) -> None:
+    """RMSNorm(latent) + RoPE(k_pe) + per-128-column int8 quantisation into the packed cache ``uint8 [pages, page_tokens, 656]``."""
+    T = kv.shape[0]
+    num_pages, page_tokens, row = cache.shape
+    assert cache.dtype == torch.uint8 and row == 656
+    check(_lib.load().ifab_mla_kv_write_q8(kv.data_ptr(), _rows(kv), norm_w.data_ptr(), eps, theta, positions.data_ptr(),
+                                           slots.data_ptr(), page_table.data_ptr(), page_table.shape[1], page_tokens, cache.data_ptr(),
+                                           num_pages, T, status_ptr, _stream()), "mla_kv_write_q8")
+
+
+def kv_dequantize_q8(cache: torch.Tensor) -> torch.Tensor:
+    """Packed int8 cache -> bf16 ``[pages, page_tokens, 576]`` (test utility)."""
+    num_pages, page_tokens, _ = cache.shape
+    out = torch.empty(num_pages, page_tokens, 576, dtype=BF16, device=cache.device)
+    check(_lib.load().ifab_kv_dequantize_q8(cache.data_ptr(), out.data_ptr(), num_pages * page_tokens, _stream()), "kv_dequantize_q8")
+    return out
+
+
+def quantize_int8(x: torch.Tensor, group_cols: Optional[int] = None):
+    """Symmetric int8 quantisation of ``[T, K]`` bf16 (ties away from zero): per row, or per ``group_cols`` columns.
+    Returns ``(q int8 [T, K], scales f32 [T, groups])``."""
+    T, Kc = x.shape
+    gc = Kc if group_cols is None else group_cols
+    groups = (Kc + gc - 1) // gc
+    q = torch.empty(T, Kc, dtype=torch.int8, device=x.device)
+    scales = torch.empty(T, groups, dtype=torch.float32, device=x.device)
+    check(_lib.load().ifab_quantize_int8(x.data_ptr(), _rows(x), q.data_ptr(), Kc, scales.data_ptr(), groups, T, Kc, gc, _stream()),
+          "quantize_int8")
+    return q, scales
+
+
 def mla_q_absorb(q: torch.Tensor, w_kvb: torch.Tensor, positions: torch.Tensor, *, nope: int, rope: int, theta: float,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``q_lat[t,h] = [q_nope[t,h] @ W_UK[h] | RoPE(q_rope[t,h])]`` with ``w_kvb`` = ``[H, nope+vdim, latent]``."""
@@ -189,8 +222,9 @@ def mla_decode_attention(q_lat: torch.Tensor, cache: torch.Tensor, positions: to
                          page_table: torch.Tensor, w_kvb: torch.Tensor, *, nope: int, scale: float, window: int = 0,
                          sinks: Optional[torch.Tensor] = None, keys_per_split: int = 64, max_splits: int = 16,
                          scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                         status_ptr: Optional[int] = None) -> torch.Tensor:
-    """Split-KV paged MLA attention + value up-projection. Returns ``[T, H*vdim]`` bf16."""
+                         status_ptr: Optional[int] = None, packed: bool = False) -> torch.Tensor:
+    """Split-KV paged MLA attention + value up-projection. Returns ``[T, H*vdim]`` bf16. With ``packed`` the cache
+    holds 656-byte int8 rows (``uint8 [pages, page_tokens, 656]``, written by :func:`mla_kv_write_q8`)."""
     T, H, row = q_lat.shape
     num_pages, page_tokens, _ = cache.shape
     latent = w_kvb.shape[2]
@@ -203,7 +237,7 @@ def mla_decode_attention(q_lat: torch.Tensor, cache: torch.Tensor, positions: to
     check(_lib.load().ifab_mla_decode_attention(
         q_lat.data_ptr(), cache.data_ptr(), positions.data_ptr(), slots.data_ptr(), page_table.data_ptr(),
         page_table.shape[1], page_tokens, num_pages, _ptr(sinks), 0 if sinks is None else sinks.shape[0], window, scale,
-        T, H, latent, rope, keys_per_split, max_splits, scratch.data_ptr(), scratch.numel() * 4, w_kvb.data_ptr(), nope,
+        T, H, latent, -rope if packed else rope, keys_per_split, max_splits, scratch.data_ptr(), scratch.numel() * 4, w_kvb.data_ptr(), nope,
         vdim, out.data_ptr(), _rows(out), status_ptr, _stream()), "mla_decode_attention")
     return out
 

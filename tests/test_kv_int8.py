@@ -1,0 +1,92 @@
+"""Packed int8 latent KV cache: write kernel, dequantise utility, attention over packed rows, activation quantisation."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BF16 = torch.bfloat16
+
+
+def _quant_ref(v, group):
+    """Symmetric int8 per `group` columns, ties away from zero, scale 1 for an all-zero group."""
+    T, K = v.shape
+    g = v.view(T, K // group, group)
+    amax = g.abs().amax(-1, keepdim=True)
+    # tensor / tensor is an exact IEEE division (tensor / python-scalar multiplies by a rounded reciprocal on CUDA)
+    scale = torch.where(amax > 0, amax / torch.full_like(amax, 127.0), torch.ones_like(amax))
+    q = g / scale
+    q = torch.where(q >= 0, torch.floor(q + 0.5), torch.ceil(q - 0.5)).clamp(-127, 127)
+    return q.view(T, K).to(torch.int8), scale.view(T, K // group)
+
+
+def test_quantize_int8_matches_reference():
+    from ironpangu_b200.ops import decode as K
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(9, 512, generator=g, device="cuda").to(BF16)
+    x[3] = 0
+    for group in (None, 128):
+        q, s = K.quantize_int8(x, group)
+        rq, rs = _quant_ref(x.float(), 512 if group is None else group)
+        assert torch.equal(s, rs)
+        assert torch.equal(q, rq)
+
+
+def test_kv_write_q8_and_attention_over_packed_rows():
+    from ironpangu_b200.models.mla_moe_ref import rmsnorm_ref, rope_ref
+    from ironpangu_b200.ops import decode as K
+
+    g = torch.Generator(device="cuda").manual_seed(1)
+    T, pages, pt, H, theta = 40, 6, 16, 4, 10000.0
+    kv = torch.randn(T, 576, generator=g, device="cuda").to(BF16)
+    nw = (1 + 0.1 * torch.randn(512, generator=g, device="cuda")).to(BF16)
+    pos = torch.arange(T, dtype=torch.int32, device="cuda")
+    slots = torch.zeros(T, dtype=torch.int32, device="cuda")
+    table = torch.tensor([[4, 1, 5, 0, 2, 3]], dtype=torch.int32, device="cuda")
+    packed = torch.zeros(pages, pt, 656, dtype=torch.uint8, device="cuda")
+    plain = torch.zeros(pages, pt, 576, dtype=BF16, device="cuda")
+    K.mla_kv_write_q8(kv, nw, pos, slots, table, packed, eps=1e-5, theta=theta)
+    K.mla_kv_write(kv, nw, pos, slots, table, plain, latent=512, rope=64, eps=1e-5, theta=theta)
+    deq = K.kv_dequantize_q8(packed)
+    rows = [int(table[0, p // pt]) * pt + p % pt for p in range(T)]
+    lat_ref = rmsnorm_ref(kv[:, :512], nw, 1e-5)
+    got = deq.view(-1, 576)[rows].float()
+    want_plain = plain.view(-1, 576)[rows].float()
+    assert torch.equal(got[:, 512:], want_plain[:, 512:])                                # rotary part is stored exactly
+    torch.testing.assert_close(got[:, 512:], rope_ref(kv[:, 512:], pos, theta), rtol=2e-2, atol=2e-2)
+    step = lat_ref.view(T, 4, 128).abs().amax(-1, keepdim=True) / 127.0
+    assert bool(((got[:, :512] - lat_ref).view(T, 4, 128).abs() <= 0.51 * step + 0.02).all())   # half a quantisation step + bf16 rounding of the dequantised copy
+    # attention over the packed rows equals attention over their dequantised copy and is close to the bf16 cache
+    q_lat = (torch.randn(3, H, 576, generator=g, device="cuda") * 0.3).to(BF16)
+    w_kvb = (torch.randn(H, 32 + 16, 512, generator=g, device="cuda") * 0.05).to(BF16)
+    qpos = torch.tensor([39, 7, 20], dtype=torch.int32, device="cuda")
+    qslot = torch.zeros(3, dtype=torch.int32, device="cuda")
+    kw = dict(nope=32, scale=1 / math.sqrt(192), keys_per_split=16, max_splits=4)
+    a_packed = K.mla_decode_attention(q_lat, packed, qpos, qslot, table, w_kvb, packed=True, **kw)
+    a_deq = K.mla_decode_attention(q_lat, deq, qpos, qslot, table, w_kvb, **kw)
+    a_plain = K.mla_decode_attention(q_lat, plain, qpos, qslot, table, w_kvb, **kw)
+    torch.testing.assert_close(a_packed.float(), a_deq.float(), rtol=2e-2, atol=5e-3)   # the bf16 copy rounds the dequantised values
+    torch.testing.assert_close(a_packed.float(), a_plain.float(), rtol=5e-2, atol=5e-3)
+
+
+def test_model_with_int8_cache_tracks_the_oracle():
+    from ironpangu_b200.models.mla_moe import MlaMoeConfig, MlaMoeDecoder, random_full_weights, shard_weights
+    from ironpangu_b200.models.mla_moe_ref import forward_ref
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    cfg = MlaMoeConfig.tiny(2)
+    full = random_full_weights(cfg, seed=0)
+    fab = Fabric(0, 1)
+    dec = MlaMoeDecoder(cfg, shard_weights(cfg, full, 0, 1, "cuda"), fab, max_tokens=8, max_context=64, keep_logits=True, kv_int8=True)
+    toks = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(3))
+    ref = forward_ref(cfg, full, toks.cuda())
+    for s in range(0, 24, 8):
+        dec.tokens[:8].copy_(toks[s:s + 8].to(torch.int32))
+        dec.positions[:8].copy_(torch.arange(s, s + 8, dtype=torch.int32))
+        dec.slots[:8].zero_()
+        dec.forward(8)
+        torch.testing.assert_close(dec.logits[:8], ref[s:s + 8], rtol=5e-2, atol=5e-2)
+    assert dec.caches[0].element_size() * dec.caches[0][0, 0].numel() == 656
+    assert fab.status() == 0
+    fab.close()
