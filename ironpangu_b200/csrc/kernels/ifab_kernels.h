@@ -127,6 +127,24 @@ int ifab_mla_decode_attention(const void* q_lat, const void* cache, const int32_
                               const void* w_kvb, int nope, int vdim, void* out, long ldo, uint32_t* status,
                               void* stream);
 
+/* ---- hyper-connection / hybrid-model operators (hc_ops.cu); all mixing arithmetic in f32 ---- */
+/* causal depthwise conv with residual; w f32 [C_total, taps] (this rank's channels start at c_offset); state bf16 [slots, taps-1, C] */
+int ifab_mome(const void* x, long ldx, const float* w, void* state, const int32_t* positions, const int32_t* slots, void* y,
+              long ldy, int T, int C, int taps, int c_offset, void* stream);
+/* X bf16 [T, S, W]; phi f32 [S*S+2S, S*W]; gamma [S*W]; alpha [3]; beta [S*S+2S] -> y bf16 [T, W], post f32 [T, S], comb f32 [T, S, S] */
+int ifab_mhc_pre(const void* X, const float* phi, const float* gamma, const float* alpha, const float* beta, void* y, float* post,
+                 float* comb, int T, int S, int W, int sinkhorn_iters, float eps, void* stream);
+int ifab_mhc_post(const void* X, const void* branch, long ldb, const float* post, const float* comb, void* Y, int T, int S, int W,
+                  void* stream);
+/* gated delta rule, one token per row: q, k bf16 [rows, H, dk]; v bf16 [rows, H, dv]; g, beta f32 [rows, H]; state f32 [slots, H, dk, dv] */
+int ifab_delta_rule_decode(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state,
+                           const int32_t* slots, void* out, int rows, int H, int dk, int dv, void* stream);
+/* indexer: q bf16 [T, heads, dim], w f32 [T, heads], keys paged bf16 [pages, page_tokens, dim]; scores = scratch f32 [T, ctx];
+ * out int32 [T, topk]: the top-k key positions (<= the query position) in ascending order, -1 padded */
+int ifab_sparse_index(const void* q, const float* w, const void* keys, const int32_t* positions, const int32_t* slots,
+                      const int32_t* page_table, int max_pages, int page_tokens, int num_pages, float* scores, int ctx, int T,
+                      int heads, int dim, int topk, int32_t* out, uint32_t* status, void* stream);
+
 /* ---- packed int8 latent cache (656-byte rows: 512 int8 | 64 bf16 rope | 4 f32 tile scales) and activation quantisation ----
  * Attention over a packed cache: ifab_mla_decode_attention with rope = -64 and `cache` pointing at the packed rows. */
 int ifab_mla_kv_write_q8(const void* kv, long ldkv, const void* norm_w, float eps, float theta, const int32_t* positions,

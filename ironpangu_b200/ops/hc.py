@@ -1,0 +1,71 @@
+"""Wrappers of the hyper-connection / hybrid-model kernels (``csrc/kernels/hc_ops.cu``): MoME causal conv, mHC pre / post,
+gated delta rule, sparse-attention indexer."""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import check
+
+BF16 = torch.bfloat16
+
+
+def _s() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def mome(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, *,
+         c_offset: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y = x + [pos + 1 >= taps] * causal_conv(x)``; ``w`` f32 ``[C_total, taps]``, ``state`` bf16 ``[slots, taps-1, C]``."""
+    T, Cn = x.shape
+    taps = w.shape[-1]
+    out = torch.empty(T, Cn, dtype=BF16, device=x.device) if out is None else out
+    check(_lib.load().ifab_mome(x.data_ptr(), x.stride(0), w.data_ptr(), state.data_ptr(), positions.data_ptr(), slots.data_ptr(),
+                                out.data_ptr(), out.stride(0), T, Cn, taps, c_offset, _s()), "mome")
+    return out
+
+
+def mhc_pre(X: torch.Tensor, phi: torch.Tensor, gamma: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor, *, sinkhorn: int = 20,
+            eps: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Returns ``(y bf16 [T, W], post f32 [T, S], comb f32 [T, S, S])`` for residual streams ``X`` bf16 ``[T, S, W]``."""
+    T, S, W = X.shape
+    y = torch.empty(T, W, dtype=BF16, device=X.device)
+    post = torch.empty(T, S, dtype=torch.float32, device=X.device)
+    comb = torch.empty(T, S, S, dtype=torch.float32, device=X.device)
+    check(_lib.load().ifab_mhc_pre(X.data_ptr(), phi.data_ptr(), gamma.data_ptr(), alpha.data_ptr(), beta.data_ptr(), y.data_ptr(),
+                                   post.data_ptr(), comb.data_ptr(), T, S, W, sinkhorn, eps, _s()), "mhc_pre")
+    return y, post, comb
+
+
+def mhc_post(X: torch.Tensor, branch: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
+    T, S, W = X.shape
+    Y = torch.empty(T, S, W, dtype=BF16, device=X.device)
+    check(_lib.load().ifab_mhc_post(X.data_ptr(), branch.data_ptr(), branch.stride(0), post.data_ptr(), comb.data_ptr(), Y.data_ptr(), T, S, W,
+                                    _s()), "mhc_post")
+    return Y
+
+
+def delta_rule_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
+                      slots: torch.Tensor) -> torch.Tensor:
+    """One gated delta-rule step per row; ``state`` f32 ``[slots, H, dk, dv]`` is updated in place."""
+    rows, H, dk = q.shape
+    dv = v.shape[-1]
+    out = torch.empty(rows, H, dv, dtype=BF16, device=q.device)
+    check(_lib.load().ifab_delta_rule_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), state.data_ptr(),
+                                             slots.data_ptr(), out.data_ptr(), rows, H, dk, dv, _s()), "delta_rule_decode")
+    return out
+
+
+def sparse_index(q: torch.Tensor, w: torch.Tensor, keys: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                 page_table: torch.Tensor, *, ctx: int, topk: int, status_ptr: Optional[int] = None) -> torch.Tensor:
+    """Top-``topk`` key positions per query by ``sum_h w_h * relu(q_h . key)``; ``keys`` paged bf16 ``[pages, page_tokens, dim]``."""
+    T, H, dim = q.shape
+    num_pages, page_tokens, _ = keys.shape
+    scores = torch.empty(T, ctx, dtype=torch.float32, device=q.device)
+    out = torch.empty(T, topk, dtype=torch.int32, device=q.device)
+    check(_lib.load().ifab_sparse_index(q.data_ptr(), w.data_ptr(), keys.data_ptr(), positions.data_ptr(), slots.data_ptr(),
+                                        page_table.data_ptr(), page_table.shape[1], page_tokens, num_pages, scores.data_ptr(), ctx, T, H,
+                                        dim, topk, out.data_ptr(), status_ptr, _s()), "sparse_index")
+    return out
