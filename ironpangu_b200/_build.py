@@ -130,9 +130,29 @@ def build_core(force: bool = False) -> Path:
     return CORE_LIB
 
 
+PLUGIN_DIR = ROOT / "csrc" / "plugins"
+
+
+def build_plugins(force: bool = False) -> list:
+    """Compile every example kernel plugin (``csrc/plugins/*.cpp`` with g++, ``*.cu`` with nvcc) into its own shared object."""
+    out = []
+    hdr = [CORE_DIR / "kernel_plugin.h"]
+    for src in sorted(PLUGIN_DIR.glob("*.cpp")) + sorted(PLUGIN_DIR.glob("*.cu")):
+        so = PLUGIN_DIR / f"libifab_plugin_{src.stem}.so"
+        if force or _stale(so, [src] + hdr):
+            if src.suffix == ".cu":
+                _run([_nvcc(), *NVCC_FLAGS, "-shared", "-Xcompiler", "-fPIC", str(src), "-o", str(so), "-lcudart"], cwd=PLUGIN_DIR)
+            else:
+                _run(["g++", *CXX_FLAGS, "-shared", str(src), "-o", str(so)], cwd=PLUGIN_DIR)
+            _mark(so, [src] + hdr)
+        out.append(so)
+    return out
+
+
 def build_all(force: bool = False) -> None:
     build_kernels(force)
     build_core(force)
+    build_plugins(force)
 
 
 if __name__ == "__main__":

@@ -6,6 +6,7 @@
 
 #include "bundle.h"
 #include "interp.h"
+#include "kernel_plugin.h"
 
 using namespace ifab;
 
@@ -138,6 +139,27 @@ char* ifab_core_read_init_plan(const char* path) {
 }
 char* ifab_core_read_program(const char* path) {
   return guarded([&] { return program::Program::decode(read_file(path)).to_json(); });
+}
+
+// Load a kernel plugin that implements "inferfabric.swiglu.bf16.v1" for `target` and run it once on x [T, 2F] -> y [T, F]
+// (bf16, row strides in elements). The pointers are host memory for target "cpu" and device memory for the CUDA target;
+// `stream` is handed to the plugin unchanged and synchronising it is the caller's job. The plugin's prepared state only
+// holds launch arguments, so releasing it right after the enqueue is safe.
+char* ifab_core_plugin_swiglu(const char* path, const char* target, void* x, void* y, long T, long F, long ldx, long ldy, void* stream) {
+  return guarded([&] {
+    plugin::PluginKernel k(path, "inferfabric.swiglu.bf16.v1", target);
+    IFKernelTensorV1 in = plugin::make_tensor(x, 2, {T, 2 * F}, 1), out = plugin::make_tensor(y, 2, {T, F}, 2);
+    in.strides[0] = ldx;
+    out.strides[0] = ldy;
+    in.allocation_bytes = plugin::tensor_span_bytes(in);
+    out.allocation_bytes = plugin::tensor_span_bytes(out);
+    k.prepare({in}, {out});
+    k.enqueue(nullptr, 0, stream);
+    Json j = Json::object();
+    j.set("contract", k.contract());
+    j.set("workspace_bytes", k.workspace_bytes());
+    return j;
+  });
 }
 
 }  // extern "C"

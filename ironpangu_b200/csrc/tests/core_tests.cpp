@@ -425,12 +425,51 @@ plan Cpu for Acc { target = cpu_f32_v1; })");
 }
 
 #include "serve_tests.h"
+#include "kernel_plugin.h"
+
+static void test_kernel_plugin_loader() {
+  using namespace ifab::plugin;
+  const char* dir = std::getenv("IFAB_PLUGIN_DIR");
+  if (!dir) {
+    std::printf("skip kernel_plugin (IFAB_PLUGIN_DIR not set)\n");
+    return;
+  }
+  const std::string so = std::string(dir) + "/libifab_plugin_swiglu_cpu.so";
+  CHECK_THROWS(Io, PluginKernel("/nonexistent/plugin.so", "inferfabric.swiglu.bf16.v1", "cpu"));
+  CHECK_THROWS(Stale, PluginKernel(so, "inferfabric.other.v1", "cpu"));
+  CHECK_THROWS(Stale, PluginKernel(so, "inferfabric.swiglu.bf16.v1", kCudaTarget));      // built for another target
+  std::vector<uint16_t> x(3 * 8, 0x3f80), y(3 * 4, 0);                                  // bf16 1.0 everywhere
+  {
+    PluginKernel k(so, "inferfabric.swiglu.bf16.v1", "cpu");
+    CHECK_THROWS(Invalid, k.enqueue(nullptr, 0, nullptr));                               // before prepare
+    IFKernelTensorV1 in = make_tensor(x.data(), 2, {3, 8}, 1), out = make_tensor(y.data(), 2, {3, 4}, 2);
+    IFKernelTensorV1 ro = out;
+    ro.access = 1;
+    CHECK_THROWS(Invalid, k.prepare({in}, {ro}));                                        // output not writable
+    IFKernelTensorV1 alias = make_tensor(x.data() + 4, 2, {3, 4}, 2);
+    CHECK_THROWS(Invalid, k.prepare({in}, {alias}));                                     // output overlaps the input
+    IFKernelTensorV1 small = in;
+    small.allocation_bytes = 8;
+    CHECK_THROWS(Invalid, k.prepare({small}, {out}));                                    // view larger than its allocation
+    IFKernelTensorV1 wrong = make_tensor(y.data(), 2, {3, 5}, 2, 64);
+    CHECK_THROWS(Backend, k.prepare({in}, {wrong}));                                     // the plugin itself refuses the shapes
+    k.prepare({in}, {out});
+    CHECK_THROWS(Invalid, k.prepare({in}, {out}));                                       // only once
+    k.enqueue(nullptr, 0, nullptr);
+    CHECK_THROWS(Invalid, k.enqueue(nullptr, 0, nullptr));                               // single-enqueue guard
+    k.completed();
+    k.enqueue(nullptr, 0, nullptr);
+    k.completed();
+  }
+  // silu(1) * 1 = 0.7310586 -> bf16 0x3f3b
+  CHECK(y[0] == 0x3f3b && y[11] == 0x3f3b);
+}
 
 int main() {
   std::pair<const char*, std::function<void()>> tests[] = {
       {"serve_batching", test_serve_batching_matches_sequential}, {"serve_admission", test_serve_validation_and_admission},
       {"serve_backpressure_cancel", test_serve_backpressure_cancel_and_eos}, {"serve_failure_shutdown", test_serve_engine_failure_and_shutdown},
-      {"api_tokenizer", test_api_tokenizer_and_sampling_json},
+      {"api_tokenizer", test_api_tokenizer_and_sampling_json}, {"kernel_plugin", test_kernel_plugin_loader},
       {"state_pool", test_state_pool}, {"prefix_index", test_prefix_index}, {"paging", test_paging},
       {"rankplan_runtime", test_rankplan_and_runtime}, {"transfer", test_transfer}, {"scheduler", test_scheduler}, {"cpu_plan", test_cpu_plan}};
   for (auto& t : tests) {
