@@ -299,6 +299,7 @@ BundleSummary write_bundle(const BundleInputs& in, const std::string& out_dir) {
   try {
     put("execution.bin", exec);
     put("logical.bin", g.encode());
+    put("model.inferfabric", in.source_text);   // the checked source travels with the bundle: host executors recompile it
     put("execution.json", g.to_json().dump(1));
     put("execution.dot", g.dot());
     put("execution.html", html_view(g, p, arena));

@@ -5,6 +5,7 @@
 //   ifab-server --spawn "CMD" [options]               start CMD with IFAB_ENGINE_SOCKET set, wait for it to connect
 //   ifab-server --program BUNDLE CHECKPOINT [--gpus N] [options]
 //                                                     sugar for --spawn of the Python engine worker on a compiled bundle
+//   ifab-server --program BUNDLE CHECKPOINT --cpu     run the bundle on the host with the CPU interpreter (no device needed)
 // Options: --port P (0 = pick one, printed), --max-num-seqs N, --max-num-batched-tokens B, --max-model-len C,
 //          --vocab V, --max-queue Q, --stream-capacity S, --step-micros U (mock), --accept-seconds S, --temperature T,
 //          --top-k K, --presence-penalty X (server-side sampling defaults).
@@ -20,6 +21,7 @@
 #include <iostream>
 
 #include "api.h"
+#include "program_engine.h"
 
 using namespace ifab;
 
@@ -28,6 +30,7 @@ namespace {
 struct Args {
   std::string mode, socket, spawn, bundle, checkpoint;
   int port = 8000, gpus = 1;
+  bool cpu = false, seqs_given = false, len_given = false;
   serve::EngineInfo info;
   serve::ServiceOptions opt;
   uint32_t step_micros = 0;
@@ -61,10 +64,11 @@ Args parse(int argc, char** argv) {
     else if (f == "--spawn") { a.mode = "spawn"; a.spawn = need(i); }
     else if (f == "--program") { a.mode = "program"; a.bundle = need(i); a.checkpoint = need(i); }
     else if (f == "--gpus") a.gpus = std::atoi(need(i));
+    else if (f == "--cpu") a.cpu = true;
     else if (f == "--port") a.port = std::atoi(need(i));
-    else if (f == "--max-num-seqs") a.info.residents = (uint32_t)std::atoi(need(i));
+    else if (f == "--max-num-seqs") { a.info.residents = (uint32_t)std::atoi(need(i)); a.seqs_given = true; }
     else if (f == "--max-num-batched-tokens") a.info.token_budget = a.info.chunk = (uint32_t)std::atoi(need(i));
-    else if (f == "--max-model-len") a.info.context = (uint32_t)std::atoi(need(i));
+    else if (f == "--max-model-len") { a.info.context = (uint32_t)std::atoi(need(i)); a.len_given = true; }
     else if (f == "--vocab") a.info.vocab = (uint32_t)std::atoi(need(i));
     else if (f == "--max-queue") a.opt.queue = (uint32_t)std::atoi(need(i));
     else if (f == "--stream-capacity") a.opt.stream_capacity = (uint32_t)std::atoi(need(i));
@@ -109,6 +113,8 @@ int main(int argc, char** argv) {
   try {
     if (a.mode == "mock") {
       engine = std::make_shared<serve::MockEngine>(a.info, a.step_micros);
+    } else if (a.mode == "program" && a.cpu) {
+      engine = serve::make_cpu_program_engine(a.bundle, a.checkpoint, a.seqs_given ? a.info.residents : 0, a.len_given ? a.info.context : 0);
     } else {
       if (a.socket.empty()) a.socket = "/tmp/ifab-engine-" + std::to_string((long)::getpid()) + ".sock";
       if (a.mode == "program") {

@@ -188,3 +188,58 @@ def test_gpu_engine_worker_serves_the_tiny_model():
         fab.close()
     finally:
         s.close()
+
+
+def test_program_engine_abi_and_cpu_server(tmp_path):
+    """A compiled bundle + synthetic checkpoint served on the host: the program-engine C ABI and `--program ... --cpu` agree
+    with the interpreter, token for token."""
+    import ctypes as C
+
+    from ironpangu_b200 import _build, compiler
+
+    src = os.path.join(ROOT, "examples", "mla_moe_slice_tp1.inferfabric")
+    ckpt, bundle = tmp_path / "ckpt", tmp_path / "bundle"
+    r = compiler.cli("synth-checkpoint", src, str(ckpt))
+    assert r.returncode == 0, r.stderr
+    r = compiler.cli("compile-token", src, str(ckpt), str(bundle), "--resident-sequences", "2")
+    assert r.returncode == 0, r.stderr
+    prompt = [5, 77, 300, 12, 9]
+    want = compiler.interpret(open(src).read(), str(ckpt), prompt, steps=4)["generated"]
+    lib = C.CDLL(str(_build.build_core()))
+    lib.ifab_program_error.restype = C.c_char_p
+    h = C.c_void_p()
+    assert lib.ifab_program_open(str(bundle).encode(), str(ckpt).encode(), 0, C.byref(h)) == 0, lib.ifab_program_error()
+    assert lib.ifab_program_abi_version() == 1
+    ctx, vocab, eos, cap = C.c_uint32(), C.c_uint32(), C.c_uint32(), C.c_uint32()
+    assert lib.ifab_program_info(h, C.byref(ctx), C.byref(vocab), C.byref(eos)) == 0 and vocab.value > 300
+    assert lib.ifab_program_resident_capacity(h, C.byref(cap)) == 0 and cap.value == 2
+    out = C.c_uint32()
+    arr = (C.c_uint32 * len(prompt))(*prompt)
+    assert lib.ifab_program_select_resident(h, 1) == 0
+    assert lib.ifab_program_prefill(h, arr, len(prompt), 0, 1, C.byref(out)) == 0, lib.ifab_program_error()
+    got = [out.value]
+    for i in range(3):
+        assert lib.ifab_program_token(h, got[-1], len(prompt) + i, 1, C.byref(out)) == 0
+        got.append(out.value)
+    assert got == want
+    # wrong position, unknown slot, copy rules
+    assert lib.ifab_program_token(h, 1, 3, 1, C.byref(out)) != 0 and b"stands at position" in lib.ifab_program_error()
+    assert lib.ifab_program_select_resident(h, 7) != 0
+    assert lib.ifab_program_copy_resident(h, 1, 0, len(prompt) + 3) == 0
+    assert lib.ifab_program_copy_resident(h, 1, 0, len(prompt) + 3) != 0                 # destination no longer reset
+    # batch: resident 0 continues the copied sequence, resident 1 too; both produce the same next token
+    Seq = C.c_uint32 * 4
+    seqs = (Seq * 2)(Seq(0, len(prompt) + 3, 1, 1), Seq(1, len(prompt) + 3, 1, 1))
+    toks = (C.c_uint32 * 2)(got[-1], got[-1])
+    outs, n = (C.c_uint32 * 2)(), C.c_uint32()
+    assert lib.ifab_program_batch(h, seqs, 2, toks, 2, outs, 2, C.byref(n)) == 0, lib.ifab_program_error()
+    assert n.value == 2 and outs[0] == outs[1]
+    assert lib.ifab_program_close(h) == 0
+    s = Server("--program", str(bundle), str(ckpt), "--cpu")
+    try:
+        st, g = s.post("/inference/v1/generate", {"token_ids": prompt, "sampling_params": {"max_tokens": 4}}, timeout=120)
+        assert st == 200 and g["token_ids"] == want
+        st, e = s.post("/v1/completions", {"prompt": "x", "temperature": 0.9})
+        assert st == 400 and "greedy" in e["error"]["message"]
+    finally:
+        s.close()
