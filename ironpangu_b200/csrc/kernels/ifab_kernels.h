@@ -90,6 +90,21 @@ int ifab_mla_merge(const float* scratch, const int32_t* positions, int n_sinks, 
 int ifab_allreduce_rows(const void* const* parts, const void* residual, long ldr, void* out, long ldo, long rows, int D,
                         const IfabFabric* fab, void* stream);
 
+/* ---- expert parallelism with sharded tokens: dispatch / combine all-to-all over peer memory (ep_a2a.cu) ----
+ * `*_peers` arrays hold `world` pointers into the symmetric buffers of every rank as mapped here: recv / ret bf16 [W*cap, D],
+ * meta int32 [W*cap, 2], ctl = 2 x 8 u64 flags + 8 i32 counts. `epoch` grows by one per exchange, identically on all ranks. */
+int ifab_ep_dispatch(const void* xn, long ldxn, const int32_t* ids, int M, int topk, int D, int e_local, int world, int rank, int cap,
+                     int32_t* send_idx, void* const* recv_peers, void* const* meta_peers, void* const* ctl_peers, uint32_t* ticket,
+                     int32_t* dst_count, uint64_t epoch, uint32_t* status, void* stream);
+int ifab_ep_plan(const void* meta, void* ctl, int world, int cap, int e_local, int32_t* perm, int32_t* tiles, int32_t* num_tiles,
+                 int32_t* total_rows, int max_tiles, uint64_t epoch, uint32_t spin_limit, uint32_t* status, void* stream);
+int ifab_ep_gather(const void* recv, const int32_t* perm, const int32_t* total_rows, void* xp, long ldxp, int D, int rows_max, void* stream);
+int ifab_ep_return(const void* y, long ldy, const int32_t* perm, const int32_t* total_rows, int D, int cap, int world, int rank, int rows_max,
+                   void* const* ret_peers, void* const* ctl_peers, uint32_t* ticket, uint64_t epoch, void* stream);
+int ifab_ep_combine(const void* ret, void* ctl, const int32_t* ids, const int32_t* send_idx, const float* wts, int M, int topk, int D,
+                    int e_local, int world, int cap, const void* shared, long lds, const void* residual, long ldr, void* out, long ldo,
+                    uint64_t epoch, uint32_t spin_limit, uint32_t* status, void* stream);
+
 /* ---- MoE decode path (owner-local expert parallelism) ---- */
 int ifab_router_topk(const void* x, long ldx, const void* norm_w, float eps, const float* w_router, const float* bias,
                      float* logits, int32_t* ids, float* wts, int T, int D, int E, int topk, int scoring, int renorm,

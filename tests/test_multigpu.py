@@ -41,3 +41,21 @@ def test_bulk_gemm_allreduce(world):
         pytest.skip(f"needs {world} GPUs")
     out = _run(world, "multigpu_bulk_worker.py")
     assert out.count("ok gemm_allreduce bulk") == world
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ep_dispatch_combine_all_to_all(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    out = _run(world, "ep_worker.py")
+    assert out.count("ok ep all-to-all") == world
+
+
+def test_ep_dispatch_combine_single_rank():
+    """World 1: the same kernels with every peer pointer local (plan, gather, grouped GEMMs, return, combine)."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("ep_worker", os.path.join(HERE, "ep_worker.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.run(0, 1)
