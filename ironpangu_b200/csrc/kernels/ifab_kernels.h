@@ -63,6 +63,14 @@ int ifab_gemm_bf16(const void* a, long lda, const void* b, long ldb, void* c, lo
 int ifab_gemm_allreduce_bf16(const void* a, long lda, const void* b, long ldb, void* const* out_peers, long ldc, const void* residual,
                              long ldr, int M, int N, int K, const IfabFabric* fab, void* stream);
 
+/* column-parallel GEMM fused with the all-gather of its row-sharded activations: C[world*rows_local, N] = gather(A_r) * B^T.
+ * a_peers[r] = rank r's [rows_local, K] shard in symmetric memory as mapped here (remote tiles are copied once with peer
+ * loads into `staged` [M, K] and then read by TMA; no multicast); flag_peers[r] = rank r's u64[8] flag row; tile_count =
+ * local u64 [M / 128], zeroed once; `epoch` starts at 1 and grows by one per call; alternate two A buffers. */
+int ifab_allgather_gemm_bf16(void* const* a_peers, long lda, const void* b, long ldb, void* c, long ldc, int rows_local, int N,
+                             int K, int world, int rank, void* const* flag_peers, void* staged, long lds, void* tile_count,
+                             uint64_t epoch, uint32_t* status, void* stream);
+
 /* ---- prefill path: grouped expert GEMM (tcgen05) and its routing plumbing; all sizes are device-side counts ---- */
 /* mode 0: C[rows, N] = A . B[e]^T; mode 1: N = 2F (gate rows then up rows), C[rows, F] = silu(gate) * up.
  * tiles: max_tiles x int4 {expert, first row, valid rows, 0}; *num_tiles of them are valid (written by ifab_moe_dispatch). */

@@ -45,3 +45,39 @@ def gemm_allreduce(a: torch.Tensor, b: torch.Tensor, fabric, out, *, residual: O
                                                C.byref(fabric.desc), torch.cuda.current_stream().cuda_stream),
           "gemm_allreduce")
     return y
+
+
+class AllGatherGemmState:
+    """Per-shape scratch of :func:`allgather_gemm`: flags (symmetric), the local staging matrix and its tile counters."""
+
+    def __init__(self, fabric, rows_local: int, K: int):
+        self.flags = fabric.symmetric_empty((8,), torch.int64)
+        M = rows_local * fabric.world
+        self.staged = torch.empty(M, K, dtype=BF16, device=fabric.device)
+        self.tile_count = torch.zeros((M + 127) // 128, dtype=torch.int64, device=fabric.device)
+        self.epoch = 0
+
+
+def allgather_gemm(a_shard, b: torch.Tensor, state: "AllGatherGemmState", fabric, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Column-parallel GEMM fused with the all-gather of its activations: ``C = concat_ranks(A_r) @ B.T``.
+
+    ``a_shard`` is a :class:`~ironpangu_b200.parallel.fabric.SymmetricTensor` ``[rows_local, K]`` (bf16) that every rank
+    has just written; remote 128-row tiles are brought over NVLink once, inside the GEMM kernel, while the tiles of the
+    local shard are already being multiplied. Alternate two ``a_shard`` buffers between consecutive calls; every rank
+    must make the same sequence of calls with the same ``state``."""
+    import ctypes as C
+    a = a_shard.tensor
+    rows_local, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty(rows_local * fabric.world, N, dtype=BF16, device=a.device)
+    lib = _lib.load()
+    fn = lib.ifab_allgather_gemm_bf16
+    fn.argtypes = [C.c_void_p, C.c_long, C.c_void_p, C.c_long, C.c_void_p, C.c_long, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                   C.c_void_p, C.c_void_p, C.c_long, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]
+    fn.restype = C.c_int
+    state.epoch += 1
+    check(fn(a_shard.peer_ptrs, a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0), rows_local, N, K, fabric.world,
+             fabric.rank, state.flags.peer_ptrs, state.staged.data_ptr(), state.staged.stride(0), state.tile_count.data_ptr(), state.epoch,
+             fabric.desc.status, torch.cuda.current_stream().cuda_stream), "allgather_gemm")
+    return out

@@ -1,0 +1,90 @@
+"""All-gather fused into the column-parallel tcgen05 GEMM (remote activation tiles read with TMA from peer memory)."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+BF16 = torch.bfloat16
+
+
+def main():
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    from ironpangu_b200.ops.gemm import AllGatherGemmState, allgather_gemm
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    fab = Fabric(rank, world)
+    for rows_local, N, K in [(128, 256, 64), (256, 520, 192), (384, 96, 1024)]:
+        bufs = [fab.symmetric_empty((rows_local, K)) for _ in range(2)]
+        state = AllGatherGemmState(fab, rows_local, K)
+        g = torch.Generator(device="cuda").manual_seed(5)
+        b = (torch.randn(N, K, generator=g, device="cuda") * 0.05).to(BF16)            # same on all ranks here; any local weight works
+        for call in range(3):                                                            # alternate the two shard buffers
+            gl = torch.Generator(device="cuda").manual_seed(1000 * call + rank)
+            shard = bufs[call & 1]
+            shard.tensor.copy_(torch.randn(rows_local, K, generator=gl, device="cuda").to(BF16))
+            c = allgather_gemm(shard, b, state, fab)
+            torch.cuda.synchronize()
+            if world > 1:
+                parts = [torch.empty_like(shard.tensor) for _ in range(world)]
+                dist.all_gather(parts, shard.tensor)
+                full = torch.cat(parts)
+            else:
+                full = shard.tensor
+            ref = full.float() @ b.float().T
+            torch.testing.assert_close(c.float(), ref, rtol=2e-2, atol=2e-2)
+    assert fab.status() == 0
+    print(f"rank {rank}: ok allgather gemm", flush=True)
+    if os.environ.get("AG_BENCH") == "1" and world > 1:
+        rows_local, N, K = 4096 // world * 2, 4096, 4096
+        bufs = [fab.symmetric_empty((rows_local, K)) for _ in range(2)]
+        state = AllGatherGemmState(fab, rows_local, K)
+        for bb in bufs:
+            bb.tensor.normal_()
+        b = torch.randn(N, K, device="cuda").to(BF16)
+        gathered = torch.empty(rows_local * world, K, dtype=BF16, device="cuda")
+        out = torch.empty(rows_local * world, N, dtype=BF16, device="cuda")
+
+        def timed(fn, calls=8):
+            for i in range(3):
+                fn(i)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(calls):
+                fn(i)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / calls], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t)
+
+        def fused(i):
+            allgather_gemm(bufs[i & 1], b, state, fab, out=out)
+
+        def baseline(i):
+            dist.all_gather_into_tensor(gathered, bufs[i & 1].tensor)
+            torch.matmul(gathered, b.T, out=out)
+
+        tf, tb = timed(fused), timed(baseline)
+        if rank == 0:
+            M = rows_local * world
+            print(json.dumps({"shape": f"{M}x{N}x{K}", "world": world, "fused_ms": round(tf, 4), "nccl_cublas_ms": round(tb, 4),
+                              "mma_ms_at_measured_peak": round(2.0 * M * N * K / 1.6705e15 * 1e3, 4),
+                              "link_ms": round((world - 1) * rows_local * K * 2 / 770e9 * 1e3, 4)}), flush=True)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    fab.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

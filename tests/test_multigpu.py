@@ -59,3 +59,11 @@ def test_ep_dispatch_combine_single_rank():
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     mod.run(0, 1)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_allgather_fused_into_gemm(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    out = _run(world, "ag_gemm_worker.py")
+    assert out.count("ok allgather gemm") == world
