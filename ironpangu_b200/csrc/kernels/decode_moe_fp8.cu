@@ -1,0 +1,350 @@
+// Decode-time expert FFN over block-scaled fp8 (e4m3) expert weights.
+//
+// Storage: a weight matrix [rows, K] is kept as one byte per element plus one f32 scale per 1 x 128 block of a row
+// (scales[row][ceil(K / 128)]); the represented value is fp8(w[row][k]) * scale[row][k / 128]. Decode linears are bound
+// by the HBM stream of the weights, so halving the bytes of the expert matrices - 3/4 of the bytes a token touches in a
+// mixture-of-experts layer - is what this buys; the arithmetic stays f32: every lane converts its 16-byte chunk (16
+// weights) to f32, forms the chunk's dot product with the bf16 activations staged in shared memory, and scales it once.
+// The kernels mirror the bf16 ones of decode_moe.cu (same grids, same routing inputs, same fused all-reduce), only the
+// chunk geometry differs: 16 elements per 16-byte load instead of 8.
+// Reference: W8A8 expert matrices of the 92B program (dequantising grouped matmul, native/src/token_executor.h:640-700).
+#include <cuda_fp8.h>
+
+#include "gemv.cuh"
+#include "ifab_kernels.h"
+#include "oneshot_ar.cuh"
+
+using namespace ifab;
+
+namespace {
+
+constexpr int QBLOCK = 128;
+constexpr int MAX_TOPK8 = 16;
+
+__device__ __forceinline__ void unpack16_e4m3(const uint4& v, float* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __nv_fp8x2_storage_t pair = (__nv_fp8x2_storage_t)((w[i] >> (16 * h)) & 0xffffu);
+      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
+      const float2 ff = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+      f[i * 4 + h * 2] = ff.x;
+      f[i * 4 + h * 2 + 1] = ff.y;
+    }
+  }
+}
+
+// ---- quantiser: one warp per (row, block) ------------------------------------------------------------
+__global__ void __launch_bounds__(256) quantize_fp8_block_kernel(const bf16* __restrict__ w, long ldw, long rows, int K, uint8_t* q,
+                                                                 float* scales) {
+  const int nb = (K + QBLOCK - 1) / QBLOCK;
+  const long item = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (item >= rows * nb) return;
+  const long row = item / nb;
+  const int b = (int)(item % nb), lane = threadIdx.x & 31;
+  float v[4];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int k = b * QBLOCK + lane * 4 + i;
+    v[i] = k < K ? __bfloat162float(w[row * ldw + k]) : 0.f;
+    amax = fmaxf(amax, fabsf(v[i]));
+  }
+  amax = warp_max(amax);
+  const float scale = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
+  if (lane == 0) scales[row * nb + b] = scale;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int k = b * QBLOCK + lane * 4 + i;
+    if (k < K) q[row * (long)K + k] = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(v[i], scale), __NV_SATFINITE, __NV_E4M3);
+  }
+}
+
+// ---- gate/up -------------------------------------------------------------------------------------------
+struct GateUp8Params {
+  const bf16* x; long ldx; const bf16* norm_w; float eps;
+  const int32_t* ids; int T, D, F, topk, e0, e_local;
+  const uint8_t* w_gu; const float* s_gu; const uint8_t* w_sgu; const float* s_sgu; int Fs;
+  bf16* act;
+};
+
+// grid: (ceil(F/16), T*topk + T), the layout of the bf16 kernel: a warp owns gate rows j0, j0+1 and up rows j0, j0+1.
+__global__ void __launch_bounds__(256) moe_gate_up_fp8_kernel(GateUp8Params p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* xs = reinterpret_cast<bf16*>(smem_raw);
+  __shared__ float red[33];
+  grid_dep_launch();
+  const int routes = p.T * p.topk;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j0 = (blockIdx.x * 8 + warp) * 2;
+  const bool shared_col = (int)blockIdx.y >= routes;
+  const int nb = (p.D + QBLOCK - 1) / QBLOCK, chunks = p.D >> 4;
+  const uint8_t* rows[4] = {nullptr, nullptr, nullptr, nullptr};
+  const float* srow[4] = {nullptr, nullptr, nullptr, nullptr};
+  int t, slot, Fcur;
+  const uint8_t* W;
+  const float* S;
+  if (shared_col) {
+    t = blockIdx.y - routes;
+    slot = p.topk;
+    W = p.w_sgu;
+    S = p.s_sgu;
+    Fcur = W ? p.Fs : 0;
+  } else {
+    grid_dep_wait();
+    t = blockIdx.y / p.topk;
+    slot = blockIdx.y % p.topk;
+    const int e = p.ids[blockIdx.y];
+    if (e < p.e0 || e >= p.e0 + p.e_local) return;
+    W = p.w_gu + (size_t)(e - p.e0) * 2 * p.F * p.D;
+    S = p.s_gu + (size_t)(e - p.e0) * 2 * p.F * nb;
+    Fcur = p.F;
+  }
+  if (j0 < Fcur) {
+    const int r[4] = {j0, j0 + 1, Fcur + j0, Fcur + j0 + 1};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if ((i & 1) && j0 + 1 >= Fcur) continue;
+      rows[i] = W + (size_t)r[i] * p.D;
+      srow[i] = S + (size_t)r[i] * nb;
+    }
+  }
+  constexpr int U = 4;   // 16 chunks of 16 bytes in flight per lane, over 4 rows
+  uint4 pf[U][4];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int c = lane + u * 32;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pf[u][i] = (c < chunks && rows[i]) ? ld_stream16(rows[i] + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
+  }
+  if (shared_col) grid_dep_wait();
+  if ((int)blockIdx.x * 16 >= Fcur) return;
+  stage_x<1>(xs, p.x, p.ldx, t, p.T, p.D, p.norm_w, p.eps, false, red);
+  if (j0 >= Fcur) return;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
+    if (c0 != lane) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int c = c0 + u * 32;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pf[u][i] = (c < chunks && rows[i]) ? ld_stream16(rows[i] + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int c = c0 + u * 32;
+      if (c < chunks) {
+        float xf[16];
+        unpack8(*reinterpret_cast<const uint4*>(xs + c * 16), xf);
+        unpack8(*reinterpret_cast<const uint4*>(xs + c * 16 + 8), xf + 8);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (rows[i] == nullptr) continue;
+          float wf[16], d = 0.f;
+          unpack16_e4m3(pf[u][i], wf);
+#pragma unroll
+          for (int k = 0; k < 16; ++k) d = fmaf(wf[k], xf[k], d);
+          acc[i] = fmaf(__ldg(srow[i] + (c >> 3)), d, acc[i]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i] = warp_sum(acc[i]);
+  if (lane == 0) {
+    bf16* out = p.act + ((size_t)t * (p.topk + 1) + slot) * p.F;
+    out[j0] = __float2bfloat16_rn(silu(bf16_round(acc[0])) * bf16_round(acc[2]));
+    if (j0 + 1 < Fcur) out[j0 + 1] = __float2bfloat16_rn(silu(bf16_round(acc[1])) * bf16_round(acc[3]));
+  }
+}
+
+// ---- down + all-reduce ---------------------------------------------------------------------------------
+struct Down8Params {
+  const bf16* act; const int32_t* ids; const float* wts;
+  int T, D, F, topk, e0, e_local;
+  const uint8_t* w_down; const float* s_down; const uint8_t* w_sdown; const float* s_sdown; int Fs;
+  const bf16* residual; long ldr; bf16* y; long ldy;
+  FabricView fv; uint64_t* seq; uint32_t* done;
+};
+
+// The K dimension of all local routes of a token is flattened into one space of 16-element chunks, as in the bf16 kernel:
+//   y[t][n] = sum_s wgt_s * sum_blocks scale_s[n][b] * dot(W8_s[n, block b], act[t][s][block b])
+template <int T, int R>
+__global__ void __launch_bounds__(256) moe_down_fp8_allreduce_kernel(Down8Params p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* as = reinterpret_cast<bf16*>(smem_raw);   // [(topk+1)][F] activation rows of the current token
+  constexpr int RPC = 8 * R;
+  constexpr int MAXS = MAX_TOPK8 + 1;
+  __shared__ float slab[T * RPC];
+  __shared__ int timed_out;
+  __shared__ const uint8_t* s_w[MAXS];
+  __shared__ const float* s_sc[MAXS];
+  __shared__ float s_g[MAXS];
+  __shared__ int s_k[MAXS];
+  __shared__ int s_cbeg[MAXS + 1];
+  __shared__ int s_slot[MAXS];
+  __shared__ int s_n;
+  grid_dep_launch();
+  grid_dep_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nbase = blockIdx.x * RPC, n0 = nbase + warp * R;
+  if (threadIdx.x == 0) timed_out = 0;
+  for (int t = 0; t < T; ++t) {
+    if (t < p.T) {
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int n = 0, c = 0;
+        for (int slot = 0; slot <= p.topk; ++slot) {
+          if (slot < p.topk) {
+            const int e = p.ids[t * p.topk + slot];
+            if (e < p.e0 || e >= p.e0 + p.e_local) continue;
+            s_w[n] = p.w_down + (size_t)(e - p.e0) * p.D * p.F;
+            s_sc[n] = p.s_down + (size_t)(e - p.e0) * p.D * ((p.F + QBLOCK - 1) / QBLOCK);
+            s_g[n] = p.wts[t * p.topk + slot];
+            s_k[n] = p.F;
+          } else {
+            if (p.w_sdown == nullptr) continue;
+            s_w[n] = p.w_sdown;
+            s_sc[n] = p.s_sdown;
+            s_g[n] = 1.f;
+            s_k[n] = p.Fs;
+          }
+          s_slot[n] = slot;
+          s_cbeg[n] = c;
+          c += s_k[n] >> 4;
+          ++n;
+        }
+        s_cbeg[n] = c;
+        s_n = n;
+      }
+      __syncthreads();
+      const int n_routes = s_n;
+      for (int i = 0; i < n_routes; ++i) {
+        const bf16* arow = p.act + ((size_t)t * (p.topk + 1) + s_slot[i]) * p.F;
+        for (int c = threadIdx.x; c < (s_k[i] >> 3); c += blockDim.x)
+          *reinterpret_cast<uint4*>(as + (size_t)i * p.F + c * 8) = *reinterpret_cast<const uint4*>(arow + c * 8);
+      }
+      __syncthreads();
+      float total[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) total[r] = 0.f;
+      const int chunks = s_cbeg[n_routes];
+      const int cpr = p.F >> 4;
+      const int n_exp_chunks = (n_routes > 0 && s_slot[n_routes - 1] == p.topk) ? s_cbeg[n_routes - 1] : chunks;
+      constexpr int U = 16 / R;
+      for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
+        uint4 wv[U][R];
+        float sv[U][R];
+        int route[U], cc[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int c = c0 + u * 32;
+          const int i = c < n_exp_chunks ? c / cpr : n_routes - 1;
+          route[u] = i;
+          cc[u] = c < n_exp_chunks ? c - i * cpr : c - n_exp_chunks;
+          if (c < chunks) {
+            const int k = s_k[i], nbk = (k + QBLOCK - 1) / QBLOCK;
+            const uint8_t* wb = s_w[i] + (size_t)n0 * k + (size_t)cc[u] * 16;
+            const float* sb = s_sc[i] + (size_t)n0 * nbk + (cc[u] >> 3);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              const bool in = n0 + r < p.D;
+              wv[u][r] = in ? ld_stream16(wb + (size_t)r * k) : make_uint4(0, 0, 0, 0);
+              sv[u][r] = in ? __ldg(sb + (size_t)r * nbk) : 0.f;
+            }
+          } else {
+#pragma unroll
+            for (int r = 0; r < R; ++r) { wv[u][r] = make_uint4(0, 0, 0, 0); sv[u][r] = 0.f; }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (c0 + u * 32 < chunks) {
+            float xf[16];
+            const bf16* ar = as + (size_t)route[u] * p.F + cc[u] * 16;
+            unpack8(*reinterpret_cast<const uint4*>(ar), xf);
+            unpack8(*reinterpret_cast<const uint4*>(ar + 8), xf + 8);
+            const float g = s_g[route[u]];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              float wf[16], d = 0.f;
+              unpack16_e4m3(wv[u][r], wf);
+#pragma unroll
+              for (int k = 0; k < 16; ++k) d = fmaf(wf[k], xf[k], d);
+              total[r] = fmaf(g * sv[u][r], d, total[r]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float v = warp_sum(total[r]);
+        if (lane == 0) slab[t * RPC + warp * R + r] = v;
+      }
+    }
+  }
+  __syncthreads();
+  oneshot_allreduce_slab<T, RPC>(slab, p.fv, p.seq, p.done, nbase, p.T, p.D, p.residual, p.ldr, p.y, p.ldy, nullptr, &timed_out);
+}
+
+template <int T, int R>
+int launch_down8(const Down8Params& p, cudaStream_t s) {
+  const size_t smem = (size_t)(p.topk + 1) * p.F * sizeof(bf16);
+  auto k = moe_down_fp8_allreduce_kernel<T, R>;
+  if (int rc = opt_in_smem(k, smem)) return rc;
+  dim3 grid((p.D + 8 * R - 1) / (8 * R));
+  return launch_chain(k, grid, dim3(256), smem, s, p);
+}
+template <int T>
+int dispatch_down8(const Down8Params& p, cudaStream_t s) {
+  if ((p.D + 7) / 8 <= 296) return launch_down8<T, 1>(p, s);
+  if ((p.D + 15) / 16 <= 296) return launch_down8<T, 2>(p, s);
+  if ((p.D + 31) / 32 <= 296) return launch_down8<T, 4>(p, s);
+  return -2;
+}
+
+}  // namespace
+
+// w: bf16 [rows, K] (row stride ldw); q: u8 [rows, K]; scales: f32 [rows, ceil(K / 128)]
+extern "C" int ifab_quantize_fp8_block(const void* w, long ldw, long rows, int K, void* q, float* scales, void* stream) {
+  if (rows < 1 || K < 1) return -1;
+  const long items = rows * ((K + QBLOCK - 1) / QBLOCK);
+  quantize_fp8_block_kernel<<<(unsigned)((items + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)w, ldw, rows, K, (uint8_t*)q, scales);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ifab_moe_gate_up_decode_fp8(const void* x, long ldx, const void* norm_w, float eps, const int32_t* ids, int T, int D, int F,
+                                           int topk, int e0, int e_local, const void* w_gu, const float* s_gu, const void* w_shared_gu,
+                                           const float* s_shared_gu, int Fs, void* act, void* stream) {
+  if (D % 16 != 0 || F % 16 != 0 || Fs % 16 != 0 || Fs > F) return -1;
+  GateUp8Params p{(const bf16*)x, ldx, (const bf16*)norm_w, eps, ids, T, D, F, topk, e0, e_local,
+                  (const uint8_t*)w_gu, s_gu, (const uint8_t*)w_shared_gu, s_shared_gu, Fs, (bf16*)act};
+  dim3 grid((F + 15) / 16, T * topk + T);
+  const size_t smem = (size_t)D * sizeof(bf16);
+  if (int rc = opt_in_smem(moe_gate_up_fp8_kernel, smem)) return rc;
+  return launch_chain(moe_gate_up_fp8_kernel, grid, dim3(256), smem, (cudaStream_t)stream, p);
+}
+
+extern "C" int ifab_moe_down_allreduce_decode_fp8(const void* act, const int32_t* ids, const float* wts, int T, int D, int F, int topk,
+                                                  int e0, int e_local, const void* w_down, const float* s_down, const void* w_shared_down,
+                                                  const float* s_shared_down, int Fs, const void* residual, long ldr, void* y, long ldy,
+                                                  const IfabFabric* fab, void* stream) {
+  if (T < 1 || T > 8 || F % 16 != 0 || Fs % 16 != 0 || topk > MAX_TOPK8 || Fs > F) return -1;
+  Down8Params p;
+  p.act = (const bf16*)act; p.ids = ids; p.wts = wts;
+  p.T = T; p.D = D; p.F = F; p.topk = topk; p.e0 = e0; p.e_local = e_local;
+  p.w_down = (const uint8_t*)w_down; p.s_down = s_down; p.w_sdown = (const uint8_t*)w_shared_down; p.s_sdown = s_shared_down; p.Fs = Fs;
+  p.residual = (const bf16*)residual; p.ldr = ldr; p.y = (bf16*)y; p.ldy = ldy;
+  if (int rc = fabric_view(fab, &p.fv)) return rc;
+  p.seq = fab->seq; p.done = fab->done;
+  if ((size_t)fab->world * T * D * sizeof(uint64_t) > fab->ll_half_bytes) return -3;
+  if ((size_t)fab->world * 296 > fab->flag_half_words) return -4;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (T <= 1) return dispatch_down8<1>(p, s);
+  if (T <= 2) return dispatch_down8<2>(p, s);
+  if (T <= 4) return dispatch_down8<4>(p, s);
+  return dispatch_down8<8>(p, s);
+}

@@ -3,10 +3,12 @@
 //
 // The activations are sharded by rows (sequence parallel): rank r produced rows [r * Ml, (r + 1) * Ml) into a buffer in
 // symmetric memory. There is no separate gather: the GEMM grid starts with the tiles of this rank's own shard (TMA from
-// local memory) while the CTAs of every remote 128-row tile first bring that tile over NVLink - each of the N/BN CTAs of
-// the row copies its slice of the K columns with plain peer loads into a local staging matrix, exactly once per tile -
-// and then feed their main loop from the local copy with ordinary tiled TMA loads (no multicast, no TMA from peer
-// memory). The transfer of the remote shards therefore hides under the tensor-core work on the local one.
+// local memory). While the tensor cores work on a local tile, the four epilogue warps of that CTA - idle until the
+// accumulator is complete - bring the same tile row of every remote shard over NVLink with plain peer loads (this CTA's
+// slice of the K columns, exactly once per remote element) into a local staging matrix and count the tile row complete.
+// The CTAs of the remote tiles, later in the grid, wait for that count and feed their main loop from the local copy with
+// ordinary tiled TMA loads (no multicast, no TMA from peer memory). The transfer of the remote shards therefore hides
+// under the tensor-core work on the local one.
 //
 // Readiness: the shard of a rank is written by the kernel that precedes this one in that rank's stream. At kernel start
 // CTA 0 publishes "my shard of call `epoch` is complete" to every peer (system fence + release store); a CTA whose rows
@@ -64,29 +66,6 @@ __global__ void __launch_bounds__(192) tc_gemm_ag_kernel(const __grid_constant__
   const bool remote = src != p.rank;
   const CUtensorMap* ta = remote ? &map_s : &maps.a[p.rank];
   __shared__ int s_ready;
-  if (remote) {
-    // bring this CTA's slice of the K columns of the tile over NVLink (all rows), once
-    if (threadIdx.x == 0) {
-      s_ready = wait_flag_bounded(p.flags[p.rank] + src, p.epoch, p.spin_limit) ? 1 : 0;
-      if (!s_ready && p.status) atomicOr(p.status, IFAB_STATUS_PEER_TIMEOUT);
-    }
-    __syncthreads();
-    if (s_ready) {
-      const int chunks = p.K >> 3, per = (chunks + gridDim.x - 1) / gridDim.x;
-      const int c_lo = blockIdx.x * per, c_hi = min(chunks, c_lo + per);
-      const int width = max(0, c_hi - c_lo);
-      const bf16* from = p.a_peer[src] + (long)(m0 - src * p.rows_local) * p.lda;
-      bf16* to = p.staged + (long)m0 * p.lds;
-      const int rows = min(BM, p.rows_local - (m0 - src * p.rows_local));
-      for (int i = threadIdx.x; i < rows * width; i += blockDim.x) {
-        const int r = i / width, c = c_lo + i % width;
-        *reinterpret_cast<uint4*>(to + (long)r * p.lds + c * 8) = *reinterpret_cast<const uint4*>(from + (long)r * p.lda + c * 8);
-      }
-    }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) atomicAdd(p.tile_count + ty, 1ull);
-  }
   Pipe<BN> pipe;
   pipe.setup(smem_raw, ta, &tmap_b);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -100,8 +79,7 @@ __global__ void __launch_bounds__(192) tc_gemm_ag_kernel(const __grid_constant__
         if (ld_acquire_gpu_u64(p.tile_count + ty) >= target) { ready = true; break; }
         if (i > 64) __nanosleep(40);
       }
-      ready = ready && s_ready;
-      fence_proxy_async();   // the copied rows (generic-proxy stores of this and other CTAs) must be visible to the TMA engine
+      fence_proxy_async();   // the copied rows (generic-proxy stores of other CTAs) must be visible to the TMA engine
     }
     if (!ready) {
       if (p.status) atomicOr(p.status, IFAB_STATUS_PEER_TIMEOUT);
@@ -111,6 +89,46 @@ __global__ void __launch_bounds__(192) tc_gemm_ag_kernel(const __grid_constant__
   } else if (warp == 1 && lane == 0) {
     pipe.mma(num_kb, p.spin_limit, p.status);
   } else if (warp >= 2) {
+    if (!remote && p.world > 1) {
+      // While the tensor cores work on this local tile, the four epilogue warps bring the same tile row of every
+      // remote shard over NVLink: this CTA's slice of the K columns, eight 16-byte loads in flight per thread.
+      const int et = threadIdx.x - 64;
+      const int chunks = p.K >> 3, per = (chunks + gridDim.x - 1) / gridDim.x;
+      const int c_lo = blockIdx.x * per, width = max(0, min(chunks, c_lo + per) - c_lo);
+      const int r0 = m0 - p.rank * p.rows_local;          // first row of the tile inside a shard
+      const int rows = min(BM, p.rows_local - r0);
+      const int total = rows * width;
+      for (int j = 1; j < p.world; ++j) {
+        const int s = (p.rank + j) % p.world;
+        if (et == 0) {
+          s_ready = wait_flag_bounded(p.flags[p.rank] + s, p.epoch, p.spin_limit) ? 1 : 0;
+          if (!s_ready && p.status) atomicOr(p.status, IFAB_STATUS_PEER_TIMEOUT);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (s_ready) {
+          const bf16* from = p.a_peer[s] + (long)r0 * p.lda;
+          bf16* to = p.staged + (long)(s * p.rows_local + r0) * p.lds;
+          constexpr int G = 8;
+          for (int i0 = et; i0 < total; i0 += 128 * G) {
+            uint4 buf[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              const int i = i0 + 128 * g;
+              buf[g] = make_uint4(0u, 0u, 0u, 0u);
+              if (i < total) buf[g] = __ldcg(reinterpret_cast<const uint4*>(from + (long)(i / width) * p.lda + (c_lo + i % width) * 8));
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              const int i = i0 + 128 * g;
+              if (i < total) *reinterpret_cast<uint4*>(to + (long)(i / width) * p.lds + (c_lo + i % width) * 8) = buf[g];
+            }
+          }
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) atomicAdd(p.tile_count + (s * (p.rows_local / BM) + r0 / BM), 1ull);
+      }
+    }
     if (pipe.wait_accumulator(p.spin_limit, p.status)) {
       const int q = warp & 3;
       const int row = m0 + q * 32 + lane;

@@ -3,21 +3,22 @@
 //
 // Every rank runs the same grid of 128 x 128 tiles over its K shard (tcgen05 main loop of
 // tc_gemm_core.cuh, 3-stage ring so that two CTAs share an SM and one tile's exchange overlaps another
-// tile's main loop). Tile t is owned by rank t % world.
+// tile's main loop). Tile t is owned by rank t % world. A rank computes the tiles it does NOT own first (in
+// index order) and its own tiles last, so by the time an owner reaches a tile the partials of the other ranks -
+// pushed from the front of their grids - have normally arrived and the bounded wait falls through.
 //   non-owner  accumulator -> bf16 tile in shared memory (the drained TMA ring) -> one bulk copy per row
-//              (cp.async.bulk shared -> global) into slot (t, rank) of the OWNER's staging area -> system
-//              fence -> flag; the CTA then exits, it never waits
+//              (cp.async.bulk shared -> global) into slot (t, rank) of the OWNER's staging area -> one
+//              system fence by one thread behind a CTA barrier -> flag; the CTA then exits, it never waits
 //   owner      waits - bounded - for the other ranks' flags of its tile, sums the `world` partials in rank
 //              order (its own partial rounded to bf16 like the others, so the result does not depend on
-//              who owns a tile), adds the residual, rounds, and stores the finished rows into the output
-//              buffer of EVERY rank (the output lives in symmetric memory: out_peers[r] is rank r's
-//              buffer), then raises each peer's "final" flag of the tile
+//              who owns a tile; eight 16-byte loads in flight per thread), adds the residual, rounds, and
+//              stores the finished rows into the output buffer of EVERY rank (the output lives in symmetric
+//              memory: out_peers[r] is rank r's buffer), then raises each peer's "final" flag of the tile
 //   last CTA   (by ticket) waits for the final flags of the tiles this rank does not own, so when the
 //              kernel completes on a rank its output is complete, then advances the call counter
 // Bytes crossing NVLink per rank: 2 * (world-1)/world * M*N*2 - the minimum of a bf16 reduce-scatter +
-// all-gather - and they move tile by tile underneath the main loops of later tiles. Only same-index tiles
-// synchronise across ranks; CTAs are dispatched in index order on every rank, so waits are short and
-// cannot form a cycle. No TMA multicast and no TMA load from peer memory is used: peers are written with
+// all-gather - and they move tile by tile underneath the main loops of later tiles. Owners wait only for
+// non-owner CTAs, which never wait, so no cycle can form. No TMA multicast and no TMA load from peer memory is used: peers are written with
 // non-tensor bulk stores from shared memory and staged partials are read back locally. Reference: linear(tp_columns) + allreduce on the bulk collective domain
 // (native/src/token_executor.h:374-404, docs/validation/2026-10-18-bulk-domains).
 #include "tc_gemm_core.cuh"
@@ -47,10 +48,22 @@ __global__ void __launch_bounds__(192) tc_gemm_allreduce_kernel(const __grid_con
   Pipe<BN, NSTAGES> pipe;
   pipe.setup(smem_raw, &tmap_a, &tmap_b);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x;
+  const int world = a.fv.world, rank = a.fv.rank;
+  // block order: the tiles of the other owners in increasing index, then this rank's own tiles
+  int tile = blockIdx.x;
+  if (world > 1) {
+    const int owned = (a.ntiles - rank + world - 1) / world, foreign = a.ntiles - owned;
+    const int b = blockIdx.x;
+    if (b < foreign) {
+      const int g = b / (world - 1), i = b % (world - 1);
+      tile = g * world + (i < rank ? i : i + 1);
+    } else {
+      tile = (b - foreign) * world + rank;
+    }
+  }
   const int m0 = (tile / a.tiles_n) * BM, n0 = (tile % a.tiles_n) * BN;
   const int num_kb = (a.K + BK - 1) / BK;
-  const int world = a.fv.world, rank = a.fv.rank, owner = tile % world;
+  const int owner = tile % world;
   grid_dep_launch();
   grid_dep_wait();
   const uint64_t epoch = *reinterpret_cast<volatile uint64_t*>(a.seq) + 1;
@@ -90,9 +103,11 @@ __global__ void __launch_bounds__(192) tc_gemm_allreduce_kernel(const __grid_con
       bulk_commit();
       bulk_wait_all();
       fence_proxy_async();
-      __threadfence_system();
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et == 0) st_release_sys(flags(owner) + (size_t)tile * world + rank, epoch);
+      if (et == 0) {
+        __threadfence_system();
+        st_release_sys(flags(owner) + (size_t)tile * world + rank, epoch);
+      }
     } else {
       // ---- owner (or single rank): reduce in rank order, add the residual, publish to every rank ----
       if (et == 0) s_flag_ok = 1;
@@ -107,27 +122,50 @@ __global__ void __launch_bounds__(192) tc_gemm_allreduce_kernel(const __grid_con
       const bool good = ok && s_flag_ok;
       if (good) {
         const bf16* stage = reinterpret_cast<const bf16*>(half(rank) + (size_t)(tile / world) * world * TILE_BYTES);
-        for (int r = ew; r < BM; r += 4) {
-          const int row = m0 + r;
-          if (row >= a.M) break;
-          for (int c = lane; c < CPR; c += 32) {
-            const int col = n0 + c * 8;
-            if (col >= a.N) continue;
-            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int src = 0; src < world; ++src) {
-              float f[8];
-              if (src == rank) unpack8(*reinterpret_cast<const uint4*>(tile_s + (size_t)r * ROW_PAD + c * 8), f);
-              else unpack8(__ldcg(reinterpret_cast<const uint4*>(stage + (size_t)src * BM * BN + (size_t)r * BN + c * 8)), f);
+        // item i = 16-byte chunk (i % CPR) of row (i / CPR); a thread owns items et + 128 * k and keeps G of them in flight
+        constexpr int G = 8, ITEMS = BM * CPR / 128;
+        static_assert(ITEMS % G == 0, "items per thread must split into groups");
+#pragma unroll 1
+        for (int k0 = 0; k0 < ITEMS; k0 += G) {
+          float v[G][8];
 #pragma unroll
-              for (int k = 0; k < 8; ++k) v[k] += f[k];
+          for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[g][k] = 0.f;
+#pragma unroll 1
+          for (int src = 0; src < world; ++src) {
+            uint4 raw[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              const int i = et + 128 * (k0 + g), r = i / CPR, c = i % CPR;
+              raw[g] = src == rank ? *reinterpret_cast<const uint4*>(tile_s + (size_t)r * ROW_PAD + c * 8)
+                                   : __ldcg(reinterpret_cast<const uint4*>(stage + (size_t)src * BM * BN + (size_t)r * BN + c * 8));
             }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              float f[8];
+              unpack8(raw[g], f);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) v[g][k] += f[k];
+            }
+          }
+          uint4 res[G];
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const int i = et + 128 * (k0 + g), r = i / CPR, c = i % CPR;
+            const bool in = m0 + r < a.M && n0 + c * 8 < a.N;
+            res[g] = (a.residual && in) ? *reinterpret_cast<const uint4*>(a.residual + (long)(m0 + r) * a.ldr + n0 + c * 8) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const int i = et + 128 * (k0 + g), r = i / CPR, c = i % CPR;
             if (a.residual) {
               float f[8];
-              unpack8(*reinterpret_cast<const uint4*>(a.residual + (long)row * a.ldr + col), f);
+              unpack8(res[g], f);
 #pragma unroll
-              for (int k = 0; k < 8; ++k) v[k] = bf16_round(v[k]) + f[k];
+              for (int k = 0; k < 8; ++k) v[g][k] = bf16_round(v[g][k]) + f[k];
             }
-            *reinterpret_cast<uint4*>(tile_s + (size_t)r * ROW_PAD + c * 8) = pack8(v);
+            *reinterpret_cast<uint4*>(tile_s + (size_t)r * ROW_PAD + c * 8) = pack8(v[g]);
           }
         }
       }
@@ -141,9 +179,12 @@ __global__ void __launch_bounds__(192) tc_gemm_allreduce_kernel(const __grid_con
       bulk_wait_all();
       if (world > 1) {
         fence_proxy_async();
-        __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (et < world && et != rank) st_release_sys(flags(et) + (size_t)a.ntiles * world + tile, epoch);
+        if (et == 0) {
+          __threadfence_system();
+          for (int dst = 0; dst < world; ++dst)
+            if (dst != rank) st_release_sys(flags(dst) + (size_t)a.ntiles * world + tile, epoch);
+        }
       }
     }
   }

@@ -183,12 +183,24 @@ class MlaMoeDecoder:
 
     def __init__(self, cfg: MlaMoeConfig, weights: Dict[str, torch.Tensor], fabric: Fabric, *, max_tokens: int = 1,
                  max_context: int = 1024, num_slots: int = 1, keys_per_split: int = 64, keep_logits: bool = False,
-                 persistent: bool = False, kv_int8: bool = False):
-        """``kv_int8``: keep the latent cache as packed int8 rows (656 bytes per token instead of 1152)."""
+                 persistent: bool = False, kv_int8: bool = False, expert_fp8: bool = False, drop_bf16_experts: bool = True):
+        """``kv_int8``: keep the latent cache as packed int8 rows (656 bytes per token instead of 1152).
+        ``expert_fp8``: quantise the routed and shared expert matrices to block-scaled fp8 (1 x 128 scale blocks) at
+        construction and decode over them; with ``drop_bf16_experts`` the bf16 originals leave ``weights``."""
         assert 1 <= max_tokens <= 8
-        assert not (persistent and kv_int8), "the single-launch step reads bf16 cache rows"
+        assert not (persistent and (kv_int8 or expert_fp8)), "the single-launch step reads bf16 cache rows and bf16 experts"
         self.kv_int8 = kv_int8
+        self.expert_fp8 = expert_fp8
         self.cfg, self.w, self.fabric = cfg, weights, fabric
+        if expert_fp8:
+            assert cfg.shared_ffn % (16 * fabric.world) == 0 and cfg.expert_ffn % 16 == 0 and cfg.hidden % 16 == 0
+            self.w8: Dict[str, tuple] = {}
+            for l in range(cfg.layers):
+                for name in ("gate_up", "down", "shared_gate_up", "shared_down"):
+                    key = f"layers.{l}.{name}"
+                    self.w8[key] = K.quantize_fp8_block(weights[key].contiguous())
+                    if drop_bf16_experts:
+                        del weights[key]
         self.rank, self.world = fabric.rank, fabric.world
         c, dev = cfg, fabric.device
         assert c.heads % self.world == 0 and c.experts % self.world == 0 and c.vocab % self.world == 0
@@ -353,6 +365,13 @@ class MlaMoeDecoder:
             K.router_topk(x, w[p + "router"], c.topk, norm_w=w[p + "ffn_norm"], eps=c.eps, scoring=c.scoring,
                           scale=c.route_scale, ticket_ptr=fab.ticket_ptr, logits=self.logits_r[:T],
                           ids=self.route_ids[:T], wts=self.route_w[:T])
+            if self.expert_fp8:
+                w8 = self.w8
+                K.moe_gate_up_fp8(x, self.route_ids[:T], w8[p + "gate_up"], self.rank * self.el, norm_w=w[p + "ffn_norm"],
+                                  eps=c.eps, w_shared_gu=w8[p + "shared_gate_up"], act=self.act[:T])
+                K.moe_down_allreduce_fp8(self.act[:T], self.route_ids[:T], self.route_w[:T], w8[p + "down"], self.rank * self.el,
+                                         fab, w_shared_down=w8[p + "shared_down"], residual=x, out=x)
+                continue
             K.moe_gate_up(x, self.route_ids[:T], w[p + "gate_up"], self.rank * self.el, norm_w=w[p + "ffn_norm"],
                           eps=c.eps, w_shared_gu=w[p + "shared_gate_up"], act=self.act[:T])
             K.moe_down_allreduce(self.act[:T], self.route_ids[:T], self.route_w[:T], w[p + "down"], self.rank * self.el,

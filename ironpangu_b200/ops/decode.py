@@ -141,6 +141,54 @@ def moe_down_allreduce(act: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, 
     return out
 
 
+def quantize_fp8_block(w: torch.Tensor):
+    """Block-scaled fp8 (e4m3) form of a bf16 matrix ``[..., rows, K]``: ``(q uint8 [..., rows, K], scales f32 [..., rows,
+    ceil(K/128)])`` with ``w ~= fp8(q) * scale`` per 1 x 128 block of a row."""
+    assert w.dtype == BF16 and w.is_contiguous()
+    K = w.shape[-1]
+    rows = w.numel() // K
+    q = torch.empty(w.shape, dtype=torch.uint8, device=w.device)
+    scales = torch.empty(*w.shape[:-1], (K + 127) // 128, dtype=torch.float32, device=w.device)
+    check(_lib.load().ifab_quantize_fp8_block(w.data_ptr(), K, rows, K, q.data_ptr(), scales.data_ptr(), _stream()), "quantize_fp8_block")
+    return q, scales
+
+
+def moe_gate_up_fp8(x: torch.Tensor, ids: torch.Tensor, w_gu, e0: int, *, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-5,
+                    w_shared_gu=None, act: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``moe_gate_up`` over block-scaled fp8 weights: ``w_gu`` and ``w_shared_gu`` are ``(q, scales)`` pairs."""
+    T, D = x.shape
+    topk = ids.shape[1]
+    q, sc = w_gu
+    e_local, twoF, _ = q.shape
+    F = twoF // 2
+    sq, ss = w_shared_gu if w_shared_gu is not None else (None, None)
+    Fs = 0 if sq is None else sq.shape[0] // 2
+    if act is None:
+        act = torch.zeros(T, topk + 1, F, dtype=BF16, device=x.device)
+    check(_lib.load().ifab_moe_gate_up_decode_fp8(x.data_ptr(), _rows(x), _ptr(norm_w), eps, ids.data_ptr(), T, D, F, topk, e0, e_local,
+                                                  q.data_ptr(), sc.data_ptr(), _ptr(sq), _ptr(ss), Fs, act.data_ptr(), _stream()),
+          "moe_gate_up_fp8")
+    return act
+
+
+def moe_down_allreduce_fp8(act: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_down, e0: int, fabric, *, w_shared_down=None,
+                           residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``moe_down_allreduce`` over block-scaled fp8 weights (``(q, scales)`` pairs)."""
+    T, slots, F = act.shape
+    topk = slots - 1
+    q, sc = w_down
+    e_local, D, _ = q.shape
+    sq, ss = w_shared_down if w_shared_down is not None else (None, None)
+    Fs = 0 if sq is None else sq.shape[1]
+    if out is None:
+        out = torch.empty(T, D, dtype=BF16, device=act.device)
+    check(_lib.load().ifab_moe_down_allreduce_decode_fp8(act.data_ptr(), ids.data_ptr(), wts.data_ptr(), T, D, F, topk, e0, e_local,
+                                                         q.data_ptr(), sc.data_ptr(), _ptr(sq), _ptr(ss), Fs, _ptr(residual),
+                                                         _rows(residual) if residual is not None else 0, out.data_ptr(), _rows(out),
+                                                         C.byref(fabric.desc), _stream()), "moe_down_allreduce_fp8")
+    return out
+
+
 def lm_head_argmax(x: torch.Tensor, w: torch.Tensor, fabric, *, norm_w: Optional[torch.Tensor] = None,
                    eps: float = 1e-5, vocab_offset: int = 0, partial: Optional[torch.Tensor] = None,
                    logits: Optional[torch.Tensor] = None, out_ids: Optional[torch.Tensor] = None,

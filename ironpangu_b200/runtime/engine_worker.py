@@ -2,15 +2,21 @@
 
 One worker process per GPU (plain ``python -m ...`` for one GPU, under ``torch.distributed.run`` for tensor /
 expert parallel models). Rank 0 connects to the Unix socket in ``IFAB_ENGINE_SOCKET`` and answers the server's
-newline-delimited JSON requests (``info`` / ``admit`` / ``step`` / ``release`` / ``shutdown``); every request is
-broadcast to the other ranks so that all of them launch the same kernels (the collectives live inside those
-kernels). A ``step`` carries slices ``[resident, position, count, sample]`` of several sequences: prompt chunks and
-decode rows are packed into launches of up to ``max_tokens`` rows (continuous batching); one token per sampling
+newline-delimited JSON requests (``info`` / ``admit`` / ``step`` / ``release`` / ``audit`` / ``shutdown``); every
+request is broadcast to the other ranks so that all of them launch the same kernels (the collectives live inside
+those kernels). A ``step`` carries slices ``[resident, position, count, sample]`` of several sequences: prompt chunks
+and decode rows are packed into launches of up to ``max_tokens`` rows (continuous batching); one token per sampling
 slice goes back. Sequence slot ``resident`` owns the pages ``resident * max_pages ...`` of the KV cache.
+
+Besides greedy decoding the engine samples on the device (temperature, top-k <= 64, top-p, min-p, repetition /
+frequency / presence penalties, per-request seed) with the vocabulary-sharded sampling kernel, and it keeps a prefix
+cache of device snapshots: when a prompt starts with tokens whose KV rows were snapshotted before, the matching
+prefill chunks are served by copying those rows into the sequence's pages instead of running the model.
 
     IFAB_ENGINE_SOCKET=/tmp/e.sock python -m ironpangu_b200.runtime.engine_worker --model tiny --max-num-seqs 4
 
-Reference: the ResidentEngine trait and its packed batch path (frontend/src/program_worker.rs:22-61,279-317).
+Reference: the ResidentEngine trait and its packed batch path (frontend/src/program_worker.rs:22-61,279-317), the
+prefix cache (native/src/prefix_cache.rs), the transfer audit (native/src/resident_transfer.h).
 """
 from __future__ import annotations
 
@@ -19,41 +25,145 @@ import json
 import os
 import socket
 import sys
-from typing import Dict, List
+from collections import OrderedDict
+from typing import Dict, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
 
 
-class BatchEngine:
-    """Packs the slices of one scheduler step into decoder launches; greedy sampling on the device."""
+class PrefixSnapshots:
+    """LRU of device snapshots keyed by token prefixes (multiples of ``block`` tokens). A snapshot is the KV rows of every
+    layer for positions ``[0, n)``, cloned out of the paged cache, so it survives the release of the slot it came from."""
 
-    def __init__(self, decoder, model_name: str, context: int, vocab: int, eos: int = -1, greedy_only: bool = True):
+    def __init__(self, capacity: int, block: int):
+        self.capacity, self.block = capacity, block
+        self.entries: "OrderedDict[Tuple[int, ...], List[torch.Tensor]]" = OrderedDict()
+        self.hits = self.misses = self.published = self.evicted = 0
+
+    def lookup(self, tokens: List[int]) -> Optional[Tuple[Tuple[int, ...], List[torch.Tensor]]]:
+        """A stored snapshot whose tokens start with all of ``tokens``, or None."""
+        want = tuple(tokens)
+        for key in reversed(self.entries):
+            if len(key) >= len(want) and key[:len(want)] == want:
+                self.entries.move_to_end(key)
+                return key, self.entries[key]
+        return None
+
+    def publish(self, tokens: List[int], rows_of) -> None:
+        """``rows_of(n)`` -> list of per-layer tensors with the first ``n`` KV rows of the sequence."""
+        n = len(tokens) // self.block * self.block
+        if n == 0 or self.capacity == 0:
+            return
+        key = tuple(tokens[:n])
+        if key in self.entries:
+            self.entries.move_to_end(key)
+            return
+        self.entries[key] = rows_of(n)
+        self.published += 1
+        while len(self.entries) > self.capacity:
+            self.entries.popitem(last=False)
+            self.evicted += 1
+
+
+class BatchEngine:
+    """Packs the slices of one scheduler step into decoder launches; greedy or sampled tokens come from the device."""
+
+    TOPK_CAP = 64   # candidates the sampling kernel keeps per row
+
+    def __init__(self, decoder, model_name: str, context: int, vocab: int, eos: int = -1, greedy_only: bool = False,
+                 prefix_slots: int = 0):
         self.dec, self.name, self.context, self.eos, self.vocab = decoder, model_name, context, eos, vocab
-        self.greedy_only = greedy_only
         self.residents = decoder.num_slots
         self.rows = decoder.T
+        self.can_sample = getattr(decoder, "logits", None) is not None
+        self.greedy_only = greedy_only or not self.can_sample
+        dev = decoder.tokens.device
         self._host = torch.zeros(3, self.rows, dtype=torch.int32).pin_memory()
         self._out = torch.zeros(self.rows, dtype=torch.int32).pin_memory()
         self.next_pos = [0] * self.residents
+        self.history: List[List[int]] = [[] for _ in range(self.residents)]
+        self.sampling: List[Dict] = [{} for _ in range(self.residents)]
+        self.prompt_done = [False] * self.residents
+        R = self.residents
+        if self.can_sample:
+            vl = decoder.logits.shape[1]
+            self.inv_temp = torch.ones(R, device=dev)
+            self.top_p = torch.ones(R, device=dev)
+            self.min_p = torch.zeros(R, device=dev)
+            self.pen = torch.tensor([[1.0, 0.0, 0.0]] * R, device=dev)
+            self.seeds = torch.zeros(R, dtype=torch.int64, device=dev)
+            self.counters = torch.zeros(R, dtype=torch.int64, device=dev)
+            self.counts = torch.zeros(R, vl, dtype=torch.int16, device=dev)
+            self.vocab_offset = decoder.rank * vl
+        self.prefix = PrefixSnapshots(prefix_slots, self.rows) if prefix_slots > 0 and hasattr(decoder, "caches") else None
+        self.audit_counters = {"steps": 0, "launch_groups": 0, "rows": 0, "h2d_bytes": 0, "d2h_bytes": 0, "prefix_rows_copied": 0,
+                               "sampled_rows": 0}
 
+    # -- contract ------------------------------------------------------------------------------------
     def info(self) -> Dict:
         return {"model": self.name, "residents": self.residents, "token_budget": self.rows, "chunk": self.rows,
                 "context": self.context, "vocab": self.vocab, "eos": max(self.eos, 0), "has_eos": self.eos >= 0,
                 "world": self.dec.world, "greedy_only": self.greedy_only}
+
+    def audit(self) -> Dict:
+        a = dict(self.audit_counters)
+        if self.prefix is not None:
+            a.update({"prefix_hits": self.prefix.hits, "prefix_misses": self.prefix.misses, "prefix_published": self.prefix.published,
+                      "prefix_evicted": self.prefix.evicted, "prefix_entries": len(self.prefix.entries)})
+        a["fabric_status"] = self.dec.fabric.status()
+        return a
 
     def admit(self, resident: int, sampling: Dict, reserve: int) -> None:
         if not 0 <= resident < self.residents:
             raise ValueError("resident out of range")
         if reserve > self.context:
             raise OverflowError("request does not fit the sequence slot")
-        if self.greedy_only and float(sampling.get("temperature", 0.0)) > 0.0 and int(sampling.get("top_k", 0)) != 1:
+        temp, top_k = float(sampling.get("temperature", 0.0)), int(sampling.get("top_k", 0))
+        greedy = temp <= 0.0 or top_k == 1
+        if not greedy and self.greedy_only:
             raise ValueError("this engine samples greedily only")
+        if top_k > self.TOPK_CAP:
+            raise ValueError(f"top_k above {self.TOPK_CAP} is not supported")
         self.next_pos[resident] = 0
+        self.history[resident] = []
+        self.prompt_done[resident] = False
+        self.sampling[resident] = {"greedy": greedy, "top_k": top_k}
+        if self.can_sample:
+            self.inv_temp[resident] = 1.0 / temp if temp > 0 else 1.0
+            self.top_p[resident] = float(sampling.get("top_p", 1.0))
+            self.min_p[resident] = float(sampling.get("min_p", 0.0))
+            self.pen[resident] = torch.tensor([float(sampling.get("repetition_penalty", 1.0)), float(sampling.get("frequency_penalty", 0.0)),
+                                               float(sampling.get("presence_penalty", 0.0))], device=self.pen.device)
+            seed = sampling.get("seed")
+            self.seeds[resident] = int(seed) if seed is not None else (resident + 1) * 0x9E3779B1
+            self.counters[resident] = 0
+            self.counts[resident].zero_()
 
     def release(self, resident: int) -> None:
         self.next_pos[resident] = 0
+        self.history[resident] = []
 
+    # -- prefix snapshots ----------------------------------------------------------------------------
+    def _kv_rows(self, resident: int, lo: int, hi: int) -> torch.Tensor:
+        """Flat row indices of positions [lo, hi) of a resident in the paged cache."""
+        d = self.dec
+        pt = d.caches[0].shape[1]
+        pos = torch.arange(lo, hi, device=d.tokens.device)
+        pages = d.page_table[resident].long()[pos // pt]
+        return pages * pt + pos % pt
+
+    def _snapshot(self, resident: int, n: int) -> List[torch.Tensor]:
+        rows = self._kv_rows(resident, 0, n)
+        return [c.view(-1, c.shape[-1])[rows].clone() for c in self.dec.caches]
+
+    def _restore(self, resident: int, snap: List[torch.Tensor], lo: int, hi: int) -> None:
+        rows = self._kv_rows(resident, lo, hi)
+        for c, s in zip(self.dec.caches, snap):
+            c.view(-1, c.shape[-1])[rows] = s[lo:hi]
+        self.audit_counters["prefix_rows_copied"] += (hi - lo) * len(snap)
+
+    # -- one scheduler step ----------------------------------------------------------------------------
     def step(self, slices: List[List[int]], tokens: List[int]) -> List[int]:
         d = self.dec
         rows = []                     # (token, position, slot, slice index or -1 when the row does not sample)
@@ -63,11 +173,21 @@ class BatchEngine:
                 raise RuntimeError(f"slice of resident {resident} starts at {position}, expected {self.next_pos[resident]}")
             if position + count > self.context:
                 raise RuntimeError("slice runs past the context")
-            for k in range(count):
-                last = k == count - 1
-                rows.append((tokens[off + k], position + k, resident, i if (sample and last) else -1))
+            toks = tokens[off:off + count]
+            hist = self.history[resident]
+            hist.extend(toks)
             off += count
             self.next_pos[resident] = position + count
+            # a whole non-sampling prefill chunk that a snapshot covers is served by a copy
+            if self.prefix is not None and not sample and position + count == len(hist):
+                hit = self.prefix.lookup(hist)
+                if hit is not None and len(hit[0]) >= position + count:
+                    self._restore(resident, hit[1], position, position + count)
+                    self.prefix.hits += 1
+                    continue
+                self.prefix.misses += 1
+            for k in range(count):
+                rows.append((toks[k], position + k, resident, i if (sample and k == count - 1) else -1))
         out = [0] * len(slices)
         for r0 in range(0, len(rows), self.rows):
             part = rows[r0:r0 + self.rows]
@@ -78,36 +198,78 @@ class BatchEngine:
             d.positions[:n].copy_(self._host[1, :n], non_blocking=True)
             d.slots[:n].copy_(self._host[2, :n], non_blocking=True)
             d.forward(n)
-            self._out[:n].copy_(d.next_ids[:n], non_blocking=True)
+            ids = d.next_ids[:n]
+            if self.can_sample:
+                slots = d.slots[:n].long()
+                local = (d.tokens[:n].long() - self.vocab_offset)          # count the fed tokens (repetition / frequency / presence)
+                ok = (local >= 0) & (local < self.counts.shape[1])
+                self.counts[slots[ok], local[ok]] += 1                      # a token repeated inside one chunk counts once
+                hot = [j for j, (_, _, slot, si) in enumerate(part) if si >= 0 and not self.sampling[slot].get("greedy", True)]
+                if hot:
+                    from ..ops import decode as K
+                    sel = torch.tensor(hot, device=slots.device)
+                    rs = slots[sel]
+                    kmax = max(self.sampling[part[j][2]]["top_k"] or self.TOPK_CAP for j in hot)
+                    counters = self.counters[rs].contiguous()
+                    sampled = K.sample_topk(d.logits[:n][sel].contiguous(), d.fabric, top_k=kmax, inv_temperature=self.inv_temp[rs].contiguous(),
+                                            top_p=self.top_p[rs].contiguous(), min_p=self.min_p[rs].contiguous(),
+                                            counts=self.counts[rs].contiguous(), penalties=self.pen[rs].contiguous(),
+                                            seeds=self.seeds[rs].contiguous(), counters=counters, vocab_offset=self.vocab_offset)
+                    self.counters[rs] = counters
+                    ids = ids.clone()
+                    ids[sel] = sampled
+                    self.audit_counters["sampled_rows"] += len(hot)
+            self._out[:n].copy_(ids, non_blocking=True)
             torch.cuda.current_stream().synchronize()
             for j, (_, _, _, si) in enumerate(part):
                 if si >= 0:
                     out[si] = int(self._out[j])
+            self.audit_counters["launch_groups"] += 1
+            self.audit_counters["rows"] += n
+            self.audit_counters["h2d_bytes"] += 12 * n
+            self.audit_counters["d2h_bytes"] += 4 * n
+        # publish the prompt of every sequence that just finished its prefill
+        if self.prefix is not None:
+            for resident, position, count, sample in slices:
+                if sample and not self.prompt_done[resident]:      # the first sampling slice of a sequence ends its prompt
+                    self.prompt_done[resident] = True
+                    self.prefix.publish(list(self.history[resident]), lambda n, r=resident: self._snapshot(r, n))
+        self.audit_counters["steps"] += 1
         if d.fabric.status() != 0:
             raise RuntimeError(f"kernel status word = {d.fabric.status()}")
         return out
 
 
-def build_engine(args, rank: int, world: int) -> BatchEngine:
+def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
     from ironpangu_b200.models.mla_moe import MlaMoeConfig, MlaMoeDecoder, random_rank_weights
     from ironpangu_b200.parallel.fabric import Fabric
 
     dev = torch.device("cuda", torch.cuda.current_device())
     fab = Fabric(rank, world)
+    mark = (lambda name, note="": rec.stage(name, note)) if rec is not None else (lambda name, note="": None)
+    mark("fabric", "symmetric-memory block and peer mappings")
     if args.bundle:
         # a compiled bundle + its checkpoint: the physical program is executed instruction by instruction
         from ironpangu_b200.runtime.plan_engine import PlanEngine
 
         eng = PlanEngine(args.bundle, args.checkpoint, fab, max_tokens=8, num_slots=args.max_num_seqs)
+        mark("program", "parameters, KV state and workspace of the compiled program")
         head = [i for i in eng.ins if i["op"] == "lm_head"][-1]
         vocab = int(eng._param(head["attrs"]["weight"]).shape[0]) * world
-        return BatchEngine(eng, os.path.basename(os.path.normpath(args.bundle)), min(args.max_model_len, eng.max_context), vocab)
+        return BatchEngine(eng, os.path.basename(os.path.normpath(args.bundle)), min(args.max_model_len, eng.max_context), vocab,
+                           greedy_only=True)
     cfg = MlaMoeConfig.tiny(args.layers or 2) if args.model == "tiny" else MlaMoeConfig.flagship()
     if args.model != "tiny" and args.layers:
         cfg.layers = args.layers
     weights = random_rank_weights(cfg, rank, world, dev, seed=args.seed)
-    dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs)
-    return BatchEngine(dec, f"ifab-{args.model}", args.max_model_len, cfg.vocab, eos=cfg.eos)
+    mark("weights")
+    dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs,
+                        keep_logits=not args.greedy_only, kv_int8=args.kv_int8)
+    mark("state", "KV cache, recurrent state and step workspace")
+    eng = BatchEngine(dec, f"ifab-{args.model}", args.max_model_len, cfg.vocab, eos=cfg.eos, greedy_only=args.greedy_only,
+                      prefix_slots=args.prefix_cache_slots)
+    mark("sampling", "per-slot sampling state and prefix snapshots")
+    return eng
 
 
 def serve(engine: BatchEngine, rank: int, world: int, sock_path: str) -> None:
@@ -144,6 +306,8 @@ def serve(engine: BatchEngine, rank: int, world: int, sock_path: str) -> None:
             elif op == "release":
                 engine.release(int(req["resident"]))
                 resp = {"ok": True}
+            elif op == "audit":
+                resp = {"ok": True, "audit": engine.audit()}
             elif op == "shutdown":
                 resp = {"ok": True}
             else:
@@ -174,15 +338,33 @@ def main() -> None:
     ap.add_argument("--checkpoint", default="")
     ap.add_argument("--max-num-seqs", type=int, default=4)
     ap.add_argument("--max-model-len", type=int, default=256)
+    ap.add_argument("--prefix-cache-slots", type=int, default=0, help="device snapshots kept by the prefix cache (0 = off)")
+    ap.add_argument("--kv-int8", action="store_true", help="packed int8 latent KV cache")
+    ap.add_argument("--greedy-only", action="store_true", help="skip the logits buffer; refuse sampled requests")
+    ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
+    ap.add_argument("--memory-profile", default="", help="write the staged start-up memory profile (JSON) here")
+    ap.add_argument("--profile-only", action="store_true", help="build the engine, write the memory profile and exit")
     ap.add_argument("--socket", default=os.environ.get("IFAB_ENGINE_SOCKET", ""))
     args = ap.parse_args()
-    if not args.socket:
+    if not args.socket and not args.profile_only:
         raise SystemExit("no engine socket: set IFAB_ENGINE_SOCKET or pass --socket")
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
-    engine = build_engine(args, rank, world)
+    from ironpangu_b200.runtime.memory import MemoryProfile, StartupOptions
+
+    opts = StartupOptions(args.max_model_len, args.max_num_seqs, 8, args.gpu_memory_utilization,
+                          (args.memory_profile + (f".rank{rank}" if rank else "")) if args.memory_profile else None, args.profile_only)
+    rec = MemoryProfile.start(opts)
+    engine = build_engine(args, rank, world, rec)
+    rec.finish()
+    if args.profile_only:
+        torch.cuda.synchronize()
+        engine.dec.fabric.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return
     try:
         serve(engine, rank, world, args.socket)
     finally:

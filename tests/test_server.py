@@ -163,7 +163,7 @@ def test_gpu_engine_worker_serves_the_tiny_model():
     from ironpangu_b200.parallel.fabric import Fabric
     from ironpangu_b200.runtime.engine import DecodeEngine
 
-    s = Server("--spawn", f"{sys.executable} -m ironpangu_b200.runtime.engine_worker --model tiny --max-num-seqs 3 --max-model-len 128",
+    s = Server("--spawn", f"{sys.executable} -m ironpangu_b200.runtime.engine_worker --model tiny --max-num-seqs 3 --max-model-len 128 --greedy-only",
                "--accept-seconds", "300", timeout=400)
     try:
         prompts = [[5, 77, 300, 12, 999, 41, 8, 650, 3, 17, 256], [9], [100, 200, 300]]
@@ -243,3 +243,49 @@ def test_program_engine_abi_and_cpu_server(tmp_path):
         assert st == 400 and "greedy" in e["error"]["message"]
     finally:
         s.close()
+
+
+@pytest.mark.gpu
+def test_gpu_engine_sampling_prefix_cache_and_int8_kv():
+    """The engine worker with device sampling, the prefix cache of device snapshots and the packed int8 KV cache."""
+    s = Server("--spawn", f"{sys.executable} -m ironpangu_b200.runtime.engine_worker --model tiny --max-num-seqs 2 --max-model-len 128 "
+               "--prefix-cache-slots 4", "--accept-seconds", "300", timeout=400)
+    try:
+        prompt = list(range(10, 10 + 27))
+        body = {"token_ids": prompt, "sampling_params": {"max_tokens": 8}}
+        st, first = s.post("/inference/v1/generate", body, timeout=120)
+        st, again = s.post("/inference/v1/generate", body, timeout=120)          # 24 of the 27 prompt rows come from the snapshot
+        assert st == 200 and again["token_ids"] == first["token_ids"]
+        st, longer = s.post("/inference/v1/generate", {"token_ids": prompt + [5, 6], "sampling_params": {"max_tokens": 4}}, timeout=120)
+        assert st == 200 and len(longer["token_ids"]) == 4
+        # seeded sampling is reproducible, different seeds diverge, temperature 0 equals greedy
+        samp = lambda seed: s.post("/inference/v1/generate", {"token_ids": prompt, "sampling_params": {
+            "max_tokens": 12, "temperature": 1.5, "top_k": 40, "top_p": 0.95, "seed": seed, "presence_penalty": 0.5}}, timeout=120)[1]["token_ids"]
+        a, b, c = samp(1), samp(1), samp(2)
+        assert a == b and a != c and a != first["token_ids"][:12]
+        st, bad = s.post("/inference/v1/generate", {"token_ids": prompt, "sampling_params": {"temperature": 1.0, "top_k": 500}}, timeout=60)
+        assert st == 503 or st == 400
+    finally:
+        s.close()
+    s = Server("--spawn", f"{sys.executable} -m ironpangu_b200.runtime.engine_worker --model tiny --max-num-seqs 2 --max-model-len 128 --kv-int8",
+               "--accept-seconds", "300", timeout=400)
+    try:
+        st, q8 = s.post("/inference/v1/generate", {"token_ids": list(range(10, 37)), "sampling_params": {"max_tokens": 8}}, timeout=120)
+        assert st == 200 and len(q8["token_ids"]) == 8
+    finally:
+        s.close()
+
+
+@pytest.mark.gpu
+def test_gpu_engine_worker_profile_only_writes_the_memory_profile(tmp_path):
+    import json
+    import subprocess
+
+    path = tmp_path / "mem.json"
+    r = subprocess.run([sys.executable, "-m", "ironpangu_b200.runtime.engine_worker", "--model", "tiny", "--max-num-seqs", "2",
+                        "--max-model-len", "128", "--memory-profile", str(path), "--profile-only"],
+                       capture_output=True, text=True, timeout=300, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0, r.stderr[-2000:]
+    d = json.loads(path.read_text())
+    assert [s["name"] for s in d["stages"]] == ["fabric", "weights", "state", "sampling"]
+    assert d["failed_stage"] is None and d["headroom_bytes"] > 0 and d["stages"][1]["delta_bytes"] > 0
