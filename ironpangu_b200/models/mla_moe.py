@@ -12,7 +12,8 @@ The reference's OpenPangu module set has the same skeleton (paired q_a/kv_a proj
 examples/openpangu/92b-tp8-ep8.inferfabric:29-75); dims here are attributes of :class:`MlaMoeConfig`,
 not constants.
 
-Per decode step and layer this path launches 10 kernels and no stand-alone collective: both
+Per decode step and layer this path launches 6 kernels (qkv_a, the cluster-per-head attention kernel, o_proj, router,
+expert gate/up, expert down; 10 with the attention steps as separate kernels) and no stand-alone collective: both
 all-reduces live inside the o_proj / expert-down kernels, and greedy sampling is fused with the
 vocabulary-sharded lm_head.
 """
@@ -183,14 +184,22 @@ class MlaMoeDecoder:
 
     def __init__(self, cfg: MlaMoeConfig, weights: Dict[str, torch.Tensor], fabric: Fabric, *, max_tokens: int = 1,
                  max_context: int = 1024, num_slots: int = 1, keys_per_split: int = 64, keep_logits: bool = False,
-                 persistent: bool = False, kv_int8: bool = False, expert_fp8: bool = False, drop_bf16_experts: bool = True):
+                 persistent: bool = False, kv_int8: bool = False, expert_fp8: bool = False, drop_bf16_experts: bool = True,
+                 fused_head: Optional[bool] = None):
         """``kv_int8``: keep the latent cache as packed int8 rows (656 bytes per token instead of 1152).
         ``expert_fp8``: quantise the routed and shared expert matrices to block-scaled fp8 (1 x 128 scale blocks) at
-        construction and decode over them; with ``drop_bf16_experts`` the bf16 originals leave ``weights``."""
+        construction and decode over them; with ``drop_bf16_experts`` the bf16 originals leave ``weights``.
+        ``fused_head``: run cache write, q_b, absorb, attention and value up-projection as one cluster-per-head launch
+        (default: on for bf16 caches with contexts up to 4096 keys, where 64 warps per head cover the keys; longer contexts
+        keep the split-KV kernels, which spread one head over up to 64 CTAs)."""
         assert 1 <= max_tokens <= 8
         assert not (persistent and (kv_int8 or expert_fp8)), "the single-launch step reads bf16 cache rows and bf16 experts"
         self.kv_int8 = kv_int8
         self.expert_fp8 = expert_fp8
+        can_fuse = (not kv_int8 and cfg.kv_lora == 512 and cfg.rope == 64 and cfg.nope % 32 == 0 and cfg.nope <= 128 and
+                    cfg.vdim <= 128 and cfg.q_lora % 8 == 0)
+        self.fused_head = (can_fuse and max_context <= 4096) if fused_head is None else bool(fused_head)
+        assert not self.fused_head or can_fuse, "the fused head kernel needs a bf16 cache and 512 + 64 latent rows"
         self.cfg, self.w, self.fabric = cfg, weights, fabric
         if expert_fp8:
             assert cfg.shared_ffn % (16 * fabric.world) == 0 and cfg.expert_ffn % 16 == 0 and cfg.hidden % 16 == 0
@@ -242,7 +251,8 @@ class MlaMoeDecoder:
         self.next_ids = torch.zeros(T, dtype=torch.int32, device=dev)
         self.next_vals = torch.zeros(T, dtype=torch.float32, device=dev)
         self.logits = e(T, self.vl, dt=torch.float32) if keep_logits else None
-        self.launches_per_forward = 3 + 10 * c.layers - 1  # embedding + layers + lm_head (kernel count)
+        # embedding + lm_head + per layer: qkv_a, [cache write, q_b, absorb, split, merge+v_up | fused head], o_proj, router, gate_up, down
+        self.launches_per_forward = 2 + (6 if self.fused_head else 10) * c.layers
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self.persistent = persistent
         if persistent:
@@ -333,6 +343,27 @@ class MlaMoeDecoder:
         return self.next_ids[:T]
 
     # -- one step ----------------------------------------------------------------------------------
+    def _ffn(self, l: int, T: int) -> None:
+        """o_proj + all-reduce, router, expert FFN + all-reduce of layer ``l`` (consumes ``self.attn``, updates ``self.x``)."""
+        c, w, fab = self.cfg, self.w, self.fabric
+        p = f"layers.{l}."
+        x, attn = self.x[:T], self.attn[:T]
+        K.gemv_allreduce(attn, w[p + "o_proj"], fab, residual=x, out=x)
+        K.router_topk(x, w[p + "router"], c.topk, norm_w=w[p + "ffn_norm"], eps=c.eps, scoring=c.scoring,
+                      scale=c.route_scale, ticket_ptr=fab.ticket_ptr, logits=self.logits_r[:T],
+                      ids=self.route_ids[:T], wts=self.route_w[:T])
+        if self.expert_fp8:
+            w8 = self.w8
+            K.moe_gate_up_fp8(x, self.route_ids[:T], w8[p + "gate_up"], self.rank * self.el, norm_w=w[p + "ffn_norm"],
+                              eps=c.eps, w_shared_gu=w8[p + "shared_gate_up"], act=self.act[:T])
+            K.moe_down_allreduce_fp8(self.act[:T], self.route_ids[:T], self.route_w[:T], w8[p + "down"], self.rank * self.el,
+                                     fab, w_shared_down=w8[p + "shared_down"], residual=x, out=x)
+            return
+        K.moe_gate_up(x, self.route_ids[:T], w[p + "gate_up"], self.rank * self.el, norm_w=w[p + "ffn_norm"],
+                      eps=c.eps, w_shared_gu=w[p + "shared_gate_up"], act=self.act[:T])
+        K.moe_down_allreduce(self.act[:T], self.route_ids[:T], self.route_w[:T], w[p + "down"], self.rank * self.el,
+                             fab, w_shared_down=w[p + "shared_down"], residual=x, out=x)
+
     def forward(self, T: Optional[int] = None) -> torch.Tensor:
         c, w, fab = self.cfg, self.w, self.fabric
         T = self.T if T is None else T
@@ -347,6 +378,12 @@ class MlaMoeDecoder:
             p = f"layers.{l}."
             qkv = self.qkv[:T]
             K.gemv(x, w[p + "qkv_a"], norm_w=w[p + "attn_norm"], eps=c.eps, out=qkv)
+            if self.fused_head:
+                K.mla_head_decode(qkv, w[p + "q_a_norm"], w[p + "kv_a_norm"], w[p + "q_b"], w[p + "kv_b"], self.caches[l], pos, slot,
+                                  self.page_table, q_lora=c.q_lora, nope=c.nope, scale=c.scale, eps=c.eps, theta=c.theta,
+                                  window=c.window, out=self.attn[:T], status_ptr=st)
+                self._ffn(l, T)
+                continue
             if self.kv_int8:
                 K.mla_kv_write_q8(qkv[:, c.q_lora:], w[p + "kv_a_norm"], pos, slot, self.page_table, self.caches[l], eps=c.eps,
                                   theta=c.theta, status_ptr=st)
@@ -361,21 +398,7 @@ class MlaMoeDecoder:
             K.mla_decode_attention(q_lat, self.caches[l], pos, slot, self.page_table, w[p + "kv_b"], nope=c.nope,
                                    scale=c.scale, window=c.window, keys_per_split=self.kps, max_splits=self.max_splits,
                                    scratch=self.scratch, out=attn, status_ptr=st, packed=self.kv_int8)
-            K.gemv_allreduce(attn, w[p + "o_proj"], fab, residual=x, out=x)
-            K.router_topk(x, w[p + "router"], c.topk, norm_w=w[p + "ffn_norm"], eps=c.eps, scoring=c.scoring,
-                          scale=c.route_scale, ticket_ptr=fab.ticket_ptr, logits=self.logits_r[:T],
-                          ids=self.route_ids[:T], wts=self.route_w[:T])
-            if self.expert_fp8:
-                w8 = self.w8
-                K.moe_gate_up_fp8(x, self.route_ids[:T], w8[p + "gate_up"], self.rank * self.el, norm_w=w[p + "ffn_norm"],
-                                  eps=c.eps, w_shared_gu=w8[p + "shared_gate_up"], act=self.act[:T])
-                K.moe_down_allreduce_fp8(self.act[:T], self.route_ids[:T], self.route_w[:T], w8[p + "down"], self.rank * self.el,
-                                         fab, w_shared_down=w8[p + "shared_down"], residual=x, out=x)
-                continue
-            K.moe_gate_up(x, self.route_ids[:T], w[p + "gate_up"], self.rank * self.el, norm_w=w[p + "ffn_norm"],
-                          eps=c.eps, w_shared_gu=w[p + "shared_gate_up"], act=self.act[:T])
-            K.moe_down_allreduce(self.act[:T], self.route_ids[:T], self.route_w[:T], w[p + "down"], self.rank * self.el,
-                                 fab, w_shared_down=w[p + "shared_down"], residual=x, out=x)
+            self._ffn(l, T)
         K.lm_head_argmax(x, w["lm_head"], fab, norm_w=w["final_norm"], eps=c.eps, vocab_offset=self.rank * self.vl,
                          partial=self.partial, logits=None if self.logits is None else self.logits[:T],
                          out_ids=self.next_ids[:T], out_vals=self.next_vals[:T])

@@ -72,10 +72,14 @@ class BatchEngine:
     TOPK_CAP = 64   # candidates the sampling kernel keeps per row
 
     def __init__(self, decoder, model_name: str, context: int, vocab: int, eos: int = -1, greedy_only: bool = False,
-                 prefix_slots: int = 0):
+                 prefix_slots: int = 0, prefill=None):
+        """``prefill``: optional tensor-core chunk executor (``forward(tokens, pos0, slot)``, attribute ``M`` = rows per call);
+        prompt slices longer than one decode launch group run through it, and the engine advertises ``M`` as its token budget."""
         self.dec, self.name, self.context, self.eos, self.vocab = decoder, model_name, context, eos, vocab
         self.residents = decoder.num_slots
         self.rows = decoder.T
+        self.prefill = prefill
+        self.budget = max(self.rows, prefill.M) if prefill is not None else self.rows
         self.can_sample = getattr(decoder, "logits", None) is not None
         self.greedy_only = greedy_only or not self.can_sample
         dev = decoder.tokens.device
@@ -98,11 +102,11 @@ class BatchEngine:
             self.vocab_offset = decoder.rank * vl
         self.prefix = PrefixSnapshots(prefix_slots, self.rows) if prefix_slots > 0 and hasattr(decoder, "caches") else None
         self.audit_counters = {"steps": 0, "launch_groups": 0, "rows": 0, "h2d_bytes": 0, "d2h_bytes": 0, "prefix_rows_copied": 0,
-                               "sampled_rows": 0}
+                               "sampled_rows": 0, "prefill_chunks": 0, "prefill_rows": 0}
 
     # -- contract ------------------------------------------------------------------------------------
     def info(self) -> Dict:
-        return {"model": self.name, "residents": self.residents, "token_budget": self.rows, "chunk": self.rows,
+        return {"model": self.name, "residents": self.residents, "token_budget": self.budget, "chunk": self.budget,
                 "context": self.context, "vocab": self.vocab, "eos": max(self.eos, 0), "has_eos": self.eos >= 0,
                 "world": self.dec.world, "greedy_only": self.greedy_only}
 
@@ -167,6 +171,7 @@ class BatchEngine:
     def step(self, slices: List[List[int]], tokens: List[int]) -> List[int]:
         d = self.dec
         rows = []                     # (token, position, slot, slice index or -1 when the row does not sample)
+        long_slices = []              # prompt slices that go through the matrix-matrix prefill path
         off = 0
         for i, (resident, position, count, sample) in enumerate(slices):
             if position != self.next_pos[resident]:
@@ -186,9 +191,29 @@ class BatchEngine:
                     self.prefix.hits += 1
                     continue
                 self.prefix.misses += 1
+            if self.prefill is not None and count > self.rows:
+                long_slices.append((i, resident, position, toks, sample))
+                continue
             for k in range(count):
                 rows.append((toks[k], position + k, resident, i if (sample and k == count - 1) else -1))
         out = [0] * len(slices)
+        # prompt chunks: matrix-matrix path, one call per chunk; the row after the chunk's last token is the one that samples
+        for i, resident, position, toks, sample in long_slices:
+            for c0 in range(0, len(toks), self.prefill.M):
+                chunk = toks[c0:c0 + self.prefill.M]
+                host = torch.tensor(chunk, dtype=torch.int32).pin_memory()
+                dev_toks = host.to(d.tokens.device, non_blocking=True)
+                self.prefill.forward(dev_toks, position + c0, resident)
+                if self.can_sample:
+                    local = dev_toks.long() - self.vocab_offset
+                    ok = (local >= 0) & (local < self.counts.shape[1])
+                    self.counts[resident, local[ok]] += 1
+                self.audit_counters["prefill_chunks"] += 1
+                self.audit_counters["prefill_rows"] += len(chunk)
+                self.audit_counters["h2d_bytes"] += 4 * len(chunk)
+            if sample:
+                d.slots[:1].fill_(resident)
+                out[i] = self._emit([(toks[-1], position + len(toks) - 1, resident, i)], 1, counted=True)[0][1]
         for r0 in range(0, len(rows), self.rows):
             part = rows[r0:r0 + self.rows]
             n = len(part)
@@ -198,32 +223,8 @@ class BatchEngine:
             d.positions[:n].copy_(self._host[1, :n], non_blocking=True)
             d.slots[:n].copy_(self._host[2, :n], non_blocking=True)
             d.forward(n)
-            ids = d.next_ids[:n]
-            if self.can_sample:
-                slots = d.slots[:n].long()
-                local = (d.tokens[:n].long() - self.vocab_offset)          # count the fed tokens (repetition / frequency / presence)
-                ok = (local >= 0) & (local < self.counts.shape[1])
-                self.counts[slots[ok], local[ok]] += 1                      # a token repeated inside one chunk counts once
-                hot = [j for j, (_, _, slot, si) in enumerate(part) if si >= 0 and not self.sampling[slot].get("greedy", True)]
-                if hot:
-                    from ..ops import decode as K
-                    sel = torch.tensor(hot, device=slots.device)
-                    rs = slots[sel]
-                    kmax = max(self.sampling[part[j][2]]["top_k"] or self.TOPK_CAP for j in hot)
-                    counters = self.counters[rs].contiguous()
-                    sampled = K.sample_topk(d.logits[:n][sel].contiguous(), d.fabric, top_k=kmax, inv_temperature=self.inv_temp[rs].contiguous(),
-                                            top_p=self.top_p[rs].contiguous(), min_p=self.min_p[rs].contiguous(),
-                                            counts=self.counts[rs].contiguous(), penalties=self.pen[rs].contiguous(),
-                                            seeds=self.seeds[rs].contiguous(), counters=counters, vocab_offset=self.vocab_offset)
-                    self.counters[rs] = counters
-                    ids = ids.clone()
-                    ids[sel] = sampled
-                    self.audit_counters["sampled_rows"] += len(hot)
-            self._out[:n].copy_(ids, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            for j, (_, _, _, si) in enumerate(part):
-                if si >= 0:
-                    out[si] = int(self._out[j])
+            for si, tok in self._emit(part, n):
+                out[si] = tok
             self.audit_counters["launch_groups"] += 1
             self.audit_counters["rows"] += n
             self.audit_counters["h2d_bytes"] += 12 * n
@@ -238,6 +239,36 @@ class BatchEngine:
         if d.fabric.status() != 0:
             raise RuntimeError(f"kernel status word = {d.fabric.status()}")
         return out
+
+    def _emit(self, part, n: int, counted: bool = False):
+        """Tokens of the sampling rows among the ``n`` rows the decoder just produced (``next_ids`` / ``logits`` rows 0..n-1,
+        ``slots`` rows 0..n-1 valid): greedy ids as they are, sampled rows through the sampling kernel. Returns ``[(slice, token)]``."""
+        d = self.dec
+        ids = d.next_ids[:n]
+        if self.can_sample:
+            slots = d.slots[:n].long()
+            if not counted:
+                local = (d.tokens[:n].long() - self.vocab_offset)      # count the fed tokens (repetition / frequency / presence)
+                ok = (local >= 0) & (local < self.counts.shape[1])
+                self.counts[slots[ok], local[ok]] += 1                  # a token repeated inside one chunk counts once
+            hot = [j for j, (_, _, slot, si) in enumerate(part) if si >= 0 and not self.sampling[slot].get("greedy", True)]
+            if hot:
+                from ..ops import decode as K
+                sel = torch.tensor(hot, device=slots.device)
+                rs = slots[sel]
+                kmax = max(self.sampling[part[j][2]]["top_k"] or self.TOPK_CAP for j in hot)
+                counters = self.counters[rs].contiguous()
+                sampled = K.sample_topk(d.logits[:n][sel].contiguous(), d.fabric, top_k=kmax, inv_temperature=self.inv_temp[rs].contiguous(),
+                                        top_p=self.top_p[rs].contiguous(), min_p=self.min_p[rs].contiguous(),
+                                        counts=self.counts[rs].contiguous(), penalties=self.pen[rs].contiguous(),
+                                        seeds=self.seeds[rs].contiguous(), counters=counters, vocab_offset=self.vocab_offset)
+                self.counters[rs] = counters
+                ids = ids.clone()
+                ids[sel] = sampled
+                self.audit_counters["sampled_rows"] += len(hot)
+        self._out[:n].copy_(ids, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return [(si, int(self._out[j])) for j, (_, _, _, si) in enumerate(part) if si >= 0]
 
 
 def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
@@ -258,16 +289,38 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
         vocab = int(eng._param(head["attrs"]["weight"]).shape[0]) * world
         return BatchEngine(eng, os.path.basename(os.path.normpath(args.bundle)), min(args.max_model_len, eng.max_context), vocab,
                            greedy_only=True)
+    if args.model.startswith("dense"):
+        # Qwen-style dense GQA decoder (tensor parallel over the fabric): same batch contract, K/V page caches
+        from ironpangu_b200.models import dense_gqa as G
+
+        dcfg = G.DenseConfig.tiny(args.layers or 2) if args.model == "dense-tiny" else G.DenseConfig.qwen2b()
+        if args.model == "dense2b" and args.layers:
+            dcfg.layers = args.layers
+        dweights = G.random_rank_weights(dcfg, rank, world, dev, seed=args.seed)
+        mark("weights")
+        ddec = G.DenseDecoder(dcfg, dweights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs,
+                              keep_logits=not args.greedy_only)
+        mark("state", "K/V page caches and step workspace")
+        eng = BatchEngine(ddec, f"ifab-{args.model}", args.max_model_len, dcfg.vocab, eos=-1, greedy_only=args.greedy_only)
+        mark("sampling", "per-slot sampling state")
+        return eng
     cfg = MlaMoeConfig.tiny(args.layers or 2) if args.model == "tiny" else MlaMoeConfig.flagship()
     if args.model != "tiny" and args.layers:
         cfg.layers = args.layers
     weights = random_rank_weights(cfg, rank, world, dev, seed=args.seed)
     mark("weights")
     dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs,
-                        keep_logits=not args.greedy_only, kv_int8=args.kv_int8)
+                        keep_logits=not args.greedy_only, kv_int8=args.kv_int8, expert_fp8=args.expert_fp8)
     mark("state", "KV cache, recurrent state and step workspace")
+    prefill = None
+    if args.prefill_chunk > 8 and not args.kv_int8 and not args.expert_fp8:
+        # prompt chunks on the tensor cores (bf16 cache and bf16 experts; the quantised layouts prefill through the decode kernels)
+        from ironpangu_b200.models.mla_moe_prefill import MlaMoePrefill
+
+        prefill = MlaMoePrefill(dec, max_rows=args.prefill_chunk)
+        mark("prefill", "activation buffers of the matrix-matrix prompt path")
     eng = BatchEngine(dec, f"ifab-{args.model}", args.max_model_len, cfg.vocab, eos=cfg.eos, greedy_only=args.greedy_only,
-                      prefix_slots=args.prefix_cache_slots)
+                      prefix_slots=args.prefix_cache_slots, prefill=prefill)
     mark("sampling", "per-slot sampling state and prefix snapshots")
     return eng
 
@@ -331,7 +384,7 @@ def serve(engine: BatchEngine, rank: int, world: int, sock_path: str) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model", default="tiny", choices=["tiny", "flagship"])
+    ap.add_argument("--model", default="tiny", choices=["tiny", "flagship", "dense-tiny", "dense2b"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--bundle", default="")
@@ -340,6 +393,8 @@ def main() -> None:
     ap.add_argument("--max-model-len", type=int, default=256)
     ap.add_argument("--prefix-cache-slots", type=int, default=0, help="device snapshots kept by the prefix cache (0 = off)")
     ap.add_argument("--kv-int8", action="store_true", help="packed int8 latent KV cache")
+    ap.add_argument("--expert-fp8", action="store_true", help="block-scaled fp8 expert weights (1 x 128 scale blocks)")
+    ap.add_argument("--prefill-chunk", type=int, default=0, help="rows per tensor-core prefill call (0 = prompts go through the decode kernels)")
     ap.add_argument("--greedy-only", action="store_true", help="skip the logits buffer; refuse sampled requests")
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--memory-profile", default="", help="write the staged start-up memory profile (JSON) here")

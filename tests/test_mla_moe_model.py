@@ -117,3 +117,67 @@ def test_feedback_graph_decodes_autoregressively():
         ids_graph.append(int(dec.next_ids[0]))
     assert ids_graph == ids_eager
     fab.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T", [1, 2, 4, 8])
+def test_fused_head_kernel_matches_the_operator_chain(T):
+    """Cluster-per-head launch (cache write + q_b + absorb + attention + value up-projection) against the five separate kernels,
+    on a chunk whose rows see each other (same slot, consecutive positions) and on rows of different sequences."""
+    import math
+
+    from ironpangu_b200.ops import decode as K
+
+    g = torch.Generator(device="cuda").manual_seed(T)
+    rnd = lambda *s, scale=1.0: (torch.randn(*s, generator=g, device="cuda") * scale).to(torch.bfloat16)
+    for H, q_lora, nope, vdim in ((4, 1536, 128, 128), (8, 128, 32, 32)):
+        pt, pages_per_slot, slots_n = 16, 4, 3
+        qkv = rnd(T, q_lora + 576)
+        qn, kn = rnd(q_lora, scale=0.1) + 1, rnd(512, scale=0.1) + 1
+        w_qb, w_kvb = rnd(H * (nope + 64), q_lora, scale=0.03), rnd(H, nope + vdim, 512, scale=0.05)
+        table = torch.randperm(slots_n * pages_per_slot, generator=torch.Generator().manual_seed(1)).to(torch.int32).cuda().view(slots_n, pages_per_slot)
+        base = rnd(slots_n * pages_per_slot, pt, 576, scale=0.5)
+        # rows 0..T/2 continue slot 1 from position 37 (a chunk), the rest sit on other slots / positions
+        pos = torch.tensor([37 + i if i < max(1, T // 2) else 5 + 7 * i for i in range(T)], dtype=torch.int32, device="cuda")
+        slot = torch.tensor([1 if i < max(1, T // 2) else (0 if i % 2 else 2) for i in range(T)], dtype=torch.int32, device="cuda")
+        scale = 1 / math.sqrt(nope + 64)
+        # operator chain
+        c1 = base.clone()
+        K.mla_kv_write(qkv[:, q_lora:], kn, pos, slot, table, c1, latent=512, rope=64, eps=1e-5, theta=1e4)
+        q = K.gemv(qkv[:, :q_lora], w_qb, norm_w=qn, eps=1e-5)
+        q_lat = K.mla_q_absorb(q, w_kvb, pos, nope=nope, rope=64, theta=1e4)
+        want = K.mla_decode_attention(q_lat, c1, pos, slot, table, w_kvb, nope=nope, scale=scale, keys_per_split=16, max_splits=4)
+        # one launch
+        c2 = base.clone()
+        got = K.mla_head_decode(qkv, qn, kn, w_qb, w_kvb, c2, pos, slot, table, q_lora=q_lora, nope=nope, scale=scale, eps=1e-5, theta=1e4)
+        torch.cuda.synchronize()
+        assert torch.equal(c1, c2)                      # same cache rows, bit for bit
+        torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-3)
+
+
+@pytest.mark.gpu
+def test_fused_head_decoder_tracks_the_oracle_and_the_chain():
+    from ironpangu_b200.models.mla_moe import MlaMoeConfig, MlaMoeDecoder, random_full_weights, shard_weights
+    from ironpangu_b200.models.mla_moe_ref import forward_ref
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    cfg = MlaMoeConfig.tiny(2)
+    full = random_full_weights(cfg, seed=0)
+    fab = Fabric(0, 1)
+    decs = [MlaMoeDecoder(cfg, shard_weights(cfg, full, 0, 1, "cuda"), fab, max_tokens=8, max_context=64, keep_logits=True, fused_head=f)
+            for f in (True, False)]
+    assert decs[0].fused_head and not decs[1].fused_head
+    toks = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(3))
+    ref = forward_ref(cfg, full, toks.cuda())
+    for s in range(0, 24, 8):
+        outs = []
+        for dec in decs:
+            dec.tokens[:8].copy_(toks[s:s + 8].to(torch.int32))
+            dec.positions[:8].copy_(torch.arange(s, s + 8, dtype=torch.int32))
+            dec.slots[:8].zero_()
+            dec.forward(8)
+            outs.append(dec.logits[:8].clone())
+            torch.testing.assert_close(dec.logits[:8], ref[s:s + 8], rtol=3e-2, atol=3e-2)
+        torch.testing.assert_close(outs[0], outs[1], rtol=2e-2, atol=2e-2)
+    assert fab.status() == 0
+    fab.close()

@@ -289,3 +289,30 @@ def test_gpu_engine_worker_profile_only_writes_the_memory_profile(tmp_path):
     d = json.loads(path.read_text())
     assert [s["name"] for s in d["stages"]] == ["fabric", "weights", "state", "sampling"]
     assert d["failed_stage"] is None and d["headroom_bytes"] > 0 and d["stages"][1]["delta_bytes"] > 0
+
+
+def test_serving_load_generator_against_the_mock_server():
+    from ironpangu_b200.utils import bench_serving
+
+    res = bench_serving.main(["--mode", "mock", "--requests", "12", "--rate", "400", "--max-model-len", "128", "--vocab", "300",
+                              "--prompt-len", "4,20", "--output-len", "3,9", "--max-num-seqs", "3"])
+    assert res["completed"] == 12 and res["statuses"] == {"200": 12} and res["server_exit"] == 0
+    assert res["output_tokens"] >= 36 and res["ttft_ms"]["p50"] > 0 and res["tpot_ms"]["p50"] > 0
+
+
+@pytest.mark.gpu
+def test_gpu_engine_prefills_long_prompts_on_the_tensor_cores():
+    """With --prefill-chunk the worker advertises a larger token budget and runs prompt slices through the matrix-matrix path;
+    the first generated token equals the one of the decode-kernel prefill."""
+    cmd = f"{sys.executable} -m ironpangu_b200.runtime.engine_worker --model tiny --max-num-seqs 2 --max-model-len 256 --greedy-only"
+    prompt = [(7 * i + 3) % 1000 for i in range(150)]
+    outs = []
+    for extra in ("", " --prefill-chunk 64"):
+        s = Server("--spawn", cmd + extra, "--accept-seconds", "300", timeout=400)
+        try:
+            st, r = s.post("/inference/v1/generate", {"token_ids": prompt, "sampling_params": {"max_tokens": 6}}, timeout=120)
+            assert st == 200 and len(r["token_ids"]) == 6
+            outs.append(r["token_ids"])
+        finally:
+            s.close()
+    assert outs[0][0] == outs[1][0]
