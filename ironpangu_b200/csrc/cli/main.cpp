@@ -31,6 +31,7 @@ int usage() {
                "usage: ifab <command> ...\n"
                "  compile-token MODEL CHECKPOINT|- OUTPUT_DIR [flags]\n  explain MODEL\n  model-source MODEL\n"
                "  synth-checkpoint MODEL OUT_DIR [--seed N]\n  interpret MODEL CHECKPOINT_DIR NEW_TOKENS TOKEN...\n"
+               "  inspect-checkpoint DIR [OUT.json]\n  bind-checkpoint MODEL DIR [OUT.json]\n  plan-placement MODEL [DIR|-] [OUT.json]\n"
                "  inspect FILE\n  plan GRAPH.json|MODEL.inferfabric [OUT.bin]\n  execute GRAPH.json|MODEL.inferfabric INPUTS.json\n"
                "  compile SPEC.json OUT.bin\n  demo\n");
   return 2;
@@ -151,6 +152,133 @@ int inspect(const char* path) {
   return 0;
 }
 
+// ---- checkpoint metadata verbs (no tensor data is read) ------------------------------------------------------------
+uint64_t tensor_bytes(const init::TensorInfo& t) { return t.end - t.begin; }
+
+void write_or_print(const Json& j, const char* out) {
+  if (out) write_file_atomic(out, j.dump(1) + "\n");
+  else std::cout << j.dump(1) << "\n";
+}
+
+// inspect-checkpoint DIR [OUT.json]: every tensor of every *.safetensors header, totals per dtype and per layer
+int inspect_checkpoint(int argc, char** argv) {
+  if (argc < 3) return usage();
+  init::Checkpoint ck = init::Checkpoint::inspect(argv[2]);
+  Json j = Json::object(), tensors = Json::array(), by_dtype = Json::object();
+  std::map<std::string, uint64_t> dt_bytes, layer_bytes;
+  uint64_t total = 0;
+  for (auto& kv : ck.tensors) {
+    const init::TensorInfo& t = kv.second;
+    Json e = Json::object(), shape = Json::array();
+    for (auto d : t.shape) shape.push((int64_t)d);
+    e.set("name", t.name);
+    e.set("dtype", init::dtype_name(t.dtype));
+    e.set("shape", shape);
+    e.set("bytes", tensor_bytes(t));
+    e.set("file", t.file);
+    tensors.push(e);
+    dt_bytes[init::dtype_name(t.dtype)] += tensor_bytes(t);
+    total += tensor_bytes(t);
+    size_t at = t.name.find("layers.");
+    if (at != std::string::npos) {
+      size_t end = t.name.find('.', at + 7);
+      layer_bytes[t.name.substr(at + 7, end == std::string::npos ? std::string::npos : end - at - 7)] += tensor_bytes(t);
+    }
+  }
+  for (auto& kv : dt_bytes) by_dtype.set(kv.first, kv.second);
+  j.set("directory", ck.dir);
+  j.set("fingerprint", ck.fingerprint);
+  j.set("tensors", (int64_t)ck.tensors.size());
+  j.set("bytes", total);
+  j.set("bytes_by_dtype", by_dtype);
+  j.set("layers", (int64_t)layer_bytes.size());
+  j.set("executable", false);
+  j.set("tensor_list", tensors);
+  write_or_print(j, argc > 3 ? argv[3] : nullptr);
+  std::cerr << "checkpoint metadata audit: " << ck.tensors.size() << " tensors, " << layer_bytes.size() << " layers, " << total << " bytes\n";
+  return 0;
+}
+
+// bind-checkpoint MODEL DIR [OUT.json]: which checkpoint tensor feeds which model parameter; shape / dtype agreement;
+// tensors of the checkpoint the model does not use (multi-token-prediction heads and the like) are listed as excluded
+int bind_checkpoint(int argc, char** argv) {
+  if (argc < 4) return usage();
+  graph::Graph g = graph::compile_source(read_file(argv[2], 1 << 20));
+  program::Program p = program::lower(g);
+  init::Checkpoint ck = init::Checkpoint::inspect(argv[3]);
+  auto need = init::required_tensors(p);
+  Json j = Json::object(), bound = Json::array(), missing = Json::array(), mismatched = Json::array(), excluded = Json::array();
+  uint64_t bound_bytes = 0, excluded_bytes = 0;
+  for (auto& kv : need) {
+    if (!ck.has(kv.first)) { missing.push(kv.first); continue; }
+    const init::TensorInfo& t = ck.need(kv.first);
+    if (t.shape != kv.second.second) {
+      Json e = Json::object(), want = Json::array(), got = Json::array();
+      for (auto d : kv.second.second) want.push((int64_t)d);
+      for (auto d : t.shape) got.push((int64_t)d);
+      e.set("name", kv.first);
+      e.set("model_shape", want);
+      e.set("checkpoint_shape", got);
+      mismatched.push(e);
+      continue;
+    }
+    Json e = Json::object();
+    e.set("name", kv.first);
+    e.set("checkpoint_dtype", init::dtype_name(t.dtype));
+    e.set("device_dtype", init::dtype_name(kv.second.first));
+    e.set("bytes", tensor_bytes(t));
+    e.set("file", t.file);
+    bound.push(e);
+    bound_bytes += tensor_bytes(t);
+  }
+  for (auto& kv : ck.tensors)
+    if (!need.count(kv.first)) { excluded.push(kv.first); excluded_bytes += tensor_bytes(kv.second); }
+  j.set("model", g.name);
+  j.set("checkpoint_fingerprint", ck.fingerprint);
+  j.set("bound", (int64_t)bound.size());
+  j.set("bound_bytes", bound_bytes);
+  j.set("excluded_bytes", excluded_bytes);
+  j.set("complete", missing.size() == 0 && mismatched.size() == 0);
+  j.set("bindings", bound);
+  j.set("missing", missing);
+  j.set("mismatched", mismatched);
+  j.set("excluded", excluded);
+  write_or_print(j, argc > 4 ? argv[4] : nullptr);
+  std::cerr << "bound " << bound.size() << " tensors (" << bound_bytes << " bytes); missing " << missing.size() << ", mismatched "
+            << mismatched.size() << ", excluded " << excluded_bytes << " bytes\n";
+  return (missing.size() || mismatched.size()) ? 1 : 0;
+}
+
+// plan-placement MODEL [DIR] [OUT.json]: per-rank placement summary of the parallel plan (parameters, bytes, load slices);
+// without a checkpoint directory the shapes come from the model alone
+int plan_placement(int argc, char** argv) {
+  if (argc < 3) return usage();
+  graph::Graph g = graph::compile_source(read_file(argv[2], 1 << 20));
+  program::Program p = program::lower(g);
+  const bool have_dir = argc > 3 && std::string(argv[3]) != "-";
+  init::Checkpoint ck = have_dir ? init::Checkpoint::inspect(argv[3]) : init::Checkpoint::synthetic(init::required_tensors(p));
+  std::vector<init::Plan> plans = init::plan_all(p, ck);
+  Json j = Json::object(), ranks = Json::array();
+  for (auto& pl : plans) {
+    Json r = Json::object();
+    uint64_t strided = 0, src = 0;
+    for (auto& l : pl.loads) { src += l.bytes; if (l.tag == 2) ++strided; }
+    r.set("rank", (int64_t)pl.rank);
+    r.set("parameters", (int64_t)pl.parameters.size());
+    r.set("device_bytes", pl.device_bytes());
+    r.set("load_slices", (int64_t)pl.loads.size());
+    r.set("strided_slices", (int64_t)strided);
+    r.set("source_bytes", src);
+    ranks.push(r);
+  }
+  j.set("model", g.name);
+  j.set("parallel", g.parallel.to_json());
+  j.set("ranks", ranks);
+  j.set("executable", have_dir);
+  write_or_print(j, argc > 4 ? argv[4] : nullptr);
+  return 0;
+}
+
 cpu::LogicalGraph load_cpu_graph(const std::string& path) {
   std::string text = read_file(path, 16 << 20);
   if (path.size() > 12 && path.compare(path.size() - 12, 12, ".inferfabric") == 0) return cpu::from_dsl(text);
@@ -211,6 +339,9 @@ int main(int argc, char** argv) {
     }
     if (cmd == "interpret") return interpret(argc, argv);
     if (cmd == "inspect") return argc < 3 ? usage() : inspect(argv[2]);
+    if (cmd == "inspect-checkpoint") return inspect_checkpoint(argc, argv);
+    if (cmd == "bind-checkpoint") return bind_checkpoint(argc, argv);
+    if (cmd == "plan-placement") return plan_placement(argc, argv);
     if (cmd == "plan" || cmd == "plan-debug" || cmd == "tune-plan" || cmd == "explain-plan") {
       if (argc < 3) return usage();
       cpu::Options o;

@@ -157,3 +157,29 @@ def test_interpreter_matches_pytorch_oracle(tmp_path):
             top2 = ref[i].topk(2).values
             assert float(top2[0] - top2[1]) < 2e-3, (i, a, b)
     torch.testing.assert_close(torch.tensor(out["logits_last"]), ref[19], rtol=2e-2, atol=5e-3)
+
+
+def test_cli_checkpoint_metadata_verbs(tmp_path):
+    """inspect-checkpoint / bind-checkpoint / plan-placement: metadata audits that read no tensor data."""
+    ck = tmp_path / "ck"
+    assert compiler.cli("synth-checkpoint", str(SLICE), str(ck), "--seed", "0").returncode == 0
+    r = compiler.cli("inspect-checkpoint", str(ck), str(tmp_path / "audit.json"))
+    assert r.returncode == 0, r.stderr
+    audit = json.loads((tmp_path / "audit.json").read_text())
+    assert audit["layers"] == 2 and audit["tensors"] == len(audit["tensor_list"]) and audit["bytes"] == sum(t["bytes"] for t in audit["tensor_list"])
+    r = compiler.cli("bind-checkpoint", str(SLICE), str(ck))
+    bound = json.loads(r.stdout)
+    assert r.returncode == 0 and bound["complete"] and bound["bound"] == audit["tensors"] and bound["excluded"] == []
+    # a checkpoint that lacks a tensor binds incompletely and says which one
+    victim = next(p for p in ck.iterdir() if p.suffix == ".safetensors")
+    other = tmp_path / "ck2"
+    other.mkdir()
+    for p in ck.iterdir():
+        if p != victim:
+            (other / p.name).write_bytes(p.read_bytes())
+    if any(other.iterdir()):
+        r = compiler.cli("bind-checkpoint", str(SLICE), str(other))
+        assert r.returncode == 1 and json.loads(r.stdout)["missing"]
+    place = json.loads(compiler.cli("plan-placement", str(ROOT / "examples" / "mla_moe_92b_tp8.inferfabric"), "-").stdout)
+    assert len(place["ranks"]) == 8 and place["executable"] is False
+    assert len({r["device_bytes"] for r in place["ranks"]}) == 1 and place["ranks"][0]["strided_slices"] > 0
