@@ -363,6 +363,19 @@ void Api::handle(const http::Request& req, http::ResponseWriter& w) {
     j.set("residents", info.residents);
     return w.send(200, "application/json", j.dump());
   }
+  if (req.path == "/audit" && get) {
+    // engine-side transfer / execution audit plus the service counters, one JSON document
+    const auto c = svc_.counters();
+    Json j = Json::object(), svc = Json::object();
+    svc.set("requests_finished", c.requests_finished);
+    svc.set("requests_failed", c.requests_failed);
+    svc.set("requests_cancelled", c.requests_cancelled);
+    svc.set("running", c.running);
+    svc.set("waiting", c.queued);
+    j.set("service", svc);
+    j.set("engine", svc_.engine_audit());
+    return w.send(200, "application/json", j.dump());
+  }
   if (req.path == "/v1/models" && get) {
     Json m = Json::object();
     m.set("id", info.model);

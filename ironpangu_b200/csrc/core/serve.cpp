@@ -115,9 +115,17 @@ uint32_t MockEngine::next_token(const std::vector<uint32_t>& seq, uint32_t vocab
   return 3 + (uint32_t)(h % (vocab - 3));
 }
 
+Json MockEngine::audit() {
+  Json j = Json::object();
+  j.set("steps", steps_);
+  j.set("rows", rows_);
+  return j;
+}
+
 std::vector<uint32_t> MockEngine::step(const paging::SequenceBatch& batch) {
   if (fail_after_ && steps_ >= *fail_after_) fail(ErrorKind::Backend, "mock engine: injected step failure");
   ++steps_;
+  rows_ += batch.tokens.size();
   if (step_micros_) std::this_thread::sleep_for(std::chrono::microseconds(step_micros_));
   std::vector<uint32_t> out;
   size_t row = 0;
@@ -245,6 +253,14 @@ void PipeEngine::release(uint32_t resident) {
   call(r);
 }
 
+Json PipeEngine::audit() {
+  Json r = Json::object();
+  r.set("op", "audit");
+  const Json resp = call(r);
+  const Json* a = resp.find("audit");
+  return a ? *a : Json::object();
+}
+
 void PipeEngine::shutdown() {
   if (fd_ < 0) return;
   try {
@@ -370,6 +386,19 @@ std::string Service::metrics_text() const {
   return s;
 }
 
+Json Service::engine_audit(double timeout_seconds) {
+  if (stop_.load() || !health_.healthy()) fail(ErrorKind::Backend, "engine is not serving");
+  auto p = std::make_shared<std::promise<Json>>();
+  auto f = p->get_future();
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    audit_waiters_.push_back(p);
+  }
+  if (f.wait_for(std::chrono::duration<double>(timeout_seconds)) != std::future_status::ready)
+    fail(ErrorKind::Backend, "engine audit timed out");
+  return f.get();
+}
+
 void Service::run() {
   sched::Capacity cap;
   cap.residents = info_.residents;
@@ -401,12 +430,21 @@ void Service::run() {
   for (;;) {
     std::deque<std::pair<sched::Request, Live>> fresh;
     std::vector<uint64_t> aborts;
+    std::vector<std::shared_ptr<std::promise<Json>>> audits;
     {
       std::lock_guard<std::mutex> lk(mu_);
       fresh.swap(inbox_);
       aborts.swap(aborts_);
+      audits.swap(audit_waiters_);
       counters_.queued = (uint32_t)sch.queued();
       counters_.running = (uint32_t)sch.running();
+    }
+    for (auto& w : audits) {
+      try {
+        w->set_value(engine_->audit());
+      } catch (...) {
+        w->set_exception(std::current_exception());
+      }
     }
     for (auto& [req, lv] : fresh) {
       const uint64_t id = req.id;

@@ -13,6 +13,7 @@
 // Reference: frontend/src/{native_backend.rs,program_worker.rs,backend.rs}, vendor/rust/src/llm/src/backend.rs:13-21.
 #pragma once
 #include <condition_variable>
+#include <future>
 #include <thread>
 #include <unordered_map>
 
@@ -53,6 +54,8 @@ class ResidentEngine {
   // one engine step; returns one token per slice (ignored where slice.sample is false). Throws Backend on failure.
   virtual std::vector<uint32_t> step(const paging::SequenceBatch& batch) = 0;
   virtual void release(uint32_t resident) { (void)resident; }
+  // transfer / execution audit of the engine (bytes moved each way, launch groups, prefix-cache traffic ...); engine thread only
+  virtual Json audit() { return Json::object(); }
   virtual void shutdown() {}
 };
 
@@ -63,6 +66,7 @@ class MockEngine : public ResidentEngine {
   void admit(uint32_t resident, const SamplingParams&, uint32_t) override { history_.at(resident).clear(); }
   std::vector<uint32_t> step(const paging::SequenceBatch& batch) override;
   void release(uint32_t resident) override { history_.at(resident).clear(); }
+  Json audit() override;
   void fail_after(uint64_t steps) { fail_after_ = steps; }      // the step with this ordinal throws Backend
   uint64_t steps() const { return steps_; }
   // the token the mock produces after `sequence`
@@ -72,7 +76,7 @@ class MockEngine : public ResidentEngine {
   EngineInfo info_;
   uint32_t step_micros_;
   std::vector<std::vector<uint32_t>> history_;
-  uint64_t steps_ = 0;
+  uint64_t steps_ = 0, rows_ = 0;
   std::optional<uint64_t> fail_after_;
 };
 
@@ -91,6 +95,7 @@ class PipeEngine : public ResidentEngine {
   void admit(uint32_t resident, const SamplingParams& params, uint32_t reserve_tokens) override;
   std::vector<uint32_t> step(const paging::SequenceBatch& batch) override;
   void release(uint32_t resident) override;
+  Json audit() override;
   void shutdown() override;
 
  private:
@@ -158,6 +163,9 @@ class Service {
   std::string unhealthy_reason() const { return health_.reason(); }
   Counters counters() const;
   std::string metrics_text() const;     // Prometheus exposition format
+  // The engine's audit record, fetched by the engine thread between two steps (throws Backend when the engine is down or
+  // does not answer within `timeout_seconds`).
+  Json engine_audit(double timeout_seconds = 10.0);
 
  private:
   void run();
@@ -172,6 +180,7 @@ class Service {
   std::unordered_map<std::string, uint64_t> ids_;
   uint64_t next_id_ = 1;
   std::atomic<bool> stop_{false};
+  std::vector<std::shared_ptr<std::promise<Json>>> audit_waiters_;
   Counters counters_;
   std::thread worker_;
 };

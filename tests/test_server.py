@@ -99,6 +99,14 @@ def test_routes_and_openai_shapes(mock_server):
     assert all(e["object"] == "chat.completion.chunk" for e in ch)
 
 
+def test_audit_route_reports_engine_and_service_counters(mock_server):
+    st, _ = mock_server.post("/v1/completions", {"prompt": "abc", "max_tokens": 4})
+    assert st == 200
+    st, body = mock_server.request("GET", "/audit")
+    a = json.loads(body)
+    assert st == 200 and a["service"]["requests_finished"] == 1 and a["engine"]["steps"] >= 4 and a["engine"]["rows"] >= 6
+
+
 def test_errors_are_openai_errors(mock_server):
     s = mock_server
     for body, needle in [({"prompt": "x", "max_tokens": 5000}, "exceeds the context"), ({"prompt": "x", "n": 2}, "'n'"),
