@@ -28,7 +28,7 @@ def _load():
         path = _build.build_core()
         lib = C.CDLL(str(path))
         for name, nargs in (("ifab_core_compile", 2), ("ifab_core_write_bundle", 5), ("ifab_core_interpret", 3),
-                            ("ifab_core_read_init_plan", 1), ("ifab_core_read_program", 1)):
+                            ("ifab_core_read_init_plan", 1), ("ifab_core_read_program", 1), ("ifab_core_validate_bundle", 1)):
             fn = getattr(lib, name)
             fn.restype = C.c_void_p
             fn.argtypes = [C.c_char_p] * nargs
@@ -70,6 +70,12 @@ def interpret(source: str, checkpoint_dir: str, tokens: List[int], steps: int = 
 
 def read_init_plan(path: str) -> Dict[str, Any]:
     return _call("ifab_core_read_init_plan", str(path))
+
+
+def validate_bundle(bundle_dir: str) -> Dict[str, Any]:
+    """Engine-side contract check of a bundle: kernel contracts of the program, binding contracts of every rank's
+    initialization plan. Raises :class:`CompileError` naming the instruction or parameter that breaks a rule."""
+    return _call("ifab_core_validate_bundle", str(bundle_dir))
 
 
 def read_program(path: str) -> Dict[str, Any]:

@@ -17,6 +17,7 @@
 #include <cstring>
 #include <iostream>
 
+#include "contract.h"
 #include "bundle.h"
 #include "cpu_plan.h"
 #include "interp.h"
@@ -31,7 +32,7 @@ int usage() {
                "usage: ifab <command> ...\n"
                "  compile-token MODEL CHECKPOINT|- OUTPUT_DIR [flags]\n  explain MODEL\n  model-source MODEL\n"
                "  synth-checkpoint MODEL OUT_DIR [--seed N]\n  interpret MODEL CHECKPOINT_DIR NEW_TOKENS TOKEN...\n"
-               "  inspect-checkpoint DIR [OUT.json]\n  bind-checkpoint MODEL DIR [OUT.json]\n  plan-placement MODEL [DIR|-] [OUT.json]\n"
+               "  validate-bundle BUNDLE_DIR\n  inspect-checkpoint DIR [OUT.json]\n  bind-checkpoint MODEL DIR [OUT.json]\n  plan-placement MODEL [DIR|-] [OUT.json]\n"
                "  inspect FILE\n  plan GRAPH.json|MODEL.inferfabric [OUT.bin]\n  execute GRAPH.json|MODEL.inferfabric INPUTS.json\n"
                "  compile SPEC.json OUT.bin\n  demo\n");
   return 2;
@@ -339,6 +340,11 @@ int main(int argc, char** argv) {
     }
     if (cmd == "interpret") return interpret(argc, argv);
     if (cmd == "inspect") return argc < 3 ? usage() : inspect(argv[2]);
+    if (cmd == "validate-bundle") {
+      if (argc < 3) return usage();
+      std::cout << contract::validate_bundle(argv[2]).dump(1) << "\n";
+      return 0;
+    }
     if (cmd == "inspect-checkpoint") return inspect_checkpoint(argc, argv);
     if (cmd == "bind-checkpoint") return bind_checkpoint(argc, argv);
     if (cmd == "plan-placement") return plan_placement(argc, argv);

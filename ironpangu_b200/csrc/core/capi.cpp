@@ -4,6 +4,7 @@
 #include <cstdlib>
 #include <cstring>
 
+#include "contract.h"
 #include "bundle.h"
 #include "interp.h"
 #include "kernel_plugin.h"
@@ -136,6 +137,10 @@ char* ifab_core_interpret(const char* source, const char* checkpoint_dir, const 
 // Read back a bundle's IFINIT01 plan as JSON (for loaders written in other languages).
 char* ifab_core_read_init_plan(const char* path) {
   return guarded([&] { return init::Plan::decode(read_file(path)).to_json(); });
+}
+// Engine-side contract check of a bundle (kernel contracts of execution.bin, binding contracts of every rank-N.bin).
+char* ifab_core_validate_bundle(const char* dir) {
+  return guarded([&] { return contract::validate_bundle(dir); });
 }
 char* ifab_core_read_program(const char* path) {
   return guarded([&] { return program::Program::decode(read_file(path)).to_json(); });

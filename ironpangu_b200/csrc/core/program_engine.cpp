@@ -1,3 +1,4 @@
+#include "contract.h"
 #include "program_engine.h"
 
 #include <map>
@@ -156,6 +157,7 @@ class CpuResidentEngine : public serve::ResidentEngine {
 namespace serve {
 std::shared_ptr<ResidentEngine> make_cpu_program_engine(const std::string& bundle, const std::string& checkpoint, uint32_t residents,
                                                         uint32_t context) {
+  contract::validate_bundle(bundle);
   return std::make_shared<CpuResidentEngine>(bundle, checkpoint, residents, context);
 }
 }  // namespace serve
@@ -172,6 +174,7 @@ int ifab_program_open(const char* bundle, const char* checkpoint, uint32_t prepa
   return guard([&] {
     if (!bundle || !checkpoint || !out) invalid("program engine: null argument");
     *out = nullptr;
+    contract::validate_bundle(bundle);   // kernel and binding contracts of the serialized program, before anything is loaded
     *out = new CpuProgram(bundle, checkpoint, preparation);
   });
 }

@@ -98,7 +98,7 @@ __device__ __forceinline__ void warp_reduce_scatter(float (&v)[NV], int lane) {
 }
 
 template <int T>
-__global__ void __launch_bounds__(256, 1) mla_head_decode_kernel(HeadParams p) {
+__global__ void __launch_bounds__(256, (T <= 2 ? 2 : 1)) mla_head_decode_kernel(HeadParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const Layout L = layout_for(T, p.q_lora);
@@ -143,6 +143,19 @@ __global__ void __launch_bounds__(256, 1) mla_head_decode_kernel(HeadParams p) {
     s_slot[threadIdx.x] = live ? p.slots[threadIdx.x] : -1;
   }
   stage_x<T>(xs, p.qkv, p.ldqkv, 0, p.T, p.q_lora, p.q_norm, p.eps, false, red);
+  // Ask for the cache rows this warp will score in step 3 now (L2 prefetch, nine 128-byte lines per row), so that their
+  // HBM latency passes under steps 1 and 2; the page-table reads on the way also warm L1 for step 3.
+  for (int t = 0; t < T; ++t) {
+    const int pos = s_pos[t];
+    if (pos < 0) continue;
+    int first, nctx;
+    visible_range(pos, p.window, &first, &nctx);
+    for (int k = gw; k < nctx; k += NW) {
+      const long r = cache_row_of(first + k, s_slot[t], p.page_table, p.max_pages, p.page_tokens, p.num_pages);
+      if (r >= 0 && lane < (ROW * 2 + 127) / 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.cache + r * ROW) + lane * 128));
+    }
+  }
   if (warp < T && warp < p.T && s_pos[warp] >= 0) {
     const int t = warp, pos = s_pos[t];
     const bf16* src = p.qkv + (long)t * p.ldqkv + p.q_lora;

@@ -3,6 +3,7 @@
 #include <functional>
 #include <iostream>
 
+#include "contract.h"
 #include "cpu_plan.h"
 #include "paging.h"
 #include "prefix_index.h"
@@ -465,13 +466,55 @@ static void test_kernel_plugin_loader() {
   CHECK(y[0] == 0x3f3b && y[11] == 0x3f3b);
 }
 
+// ---- engine-side contract validator: a correct program passes, each tampering is refused -----------------------
+static void test_contract_validator() {
+  // path of a model source (the two-layer example of the repository), handed over by the harness
+  const char* src_path = std::getenv("IFAB_EXAMPLE_MODEL");
+  if (!src_path) { std::printf("skip contract_validator (IFAB_EXAMPLE_MODEL not set)\n"); return; }
+  graph::Graph g = graph::compile_source(read_file(src_path, 1 << 20));
+  program::Program p = program::lower(g);
+  init::Checkpoint ck = init::Checkpoint::synthetic(init::required_tensors(p));
+  std::vector<init::Plan> plans = init::plan_all(p, ck);
+  contract::validate_kernels(p);
+  contract::validate_bindings(p, plans.at(0));
+  auto find = [&](const char* op) -> size_t {
+    for (size_t i = 0; i < p.instructions.size(); ++i) if (p.instructions[i].op == op) return i;
+    return p.instructions.size();
+  };
+  auto drop_attr = [](program::Instruction& i, const char* key) {
+    for (size_t k = 0; k < i.attrs.size(); ++k) if (i.attrs[k].first == key) { i.attrs.erase(i.attrs.begin() + (long)k); return; }
+  };
+  auto set_attr = [](program::Instruction& i, const char* key, const char* value) {
+    for (auto& a : i.attrs) if (a.first == key) a.second = value;
+  };
+  { program::Program q = p; q.instructions[find("linear")].kernel = "cublasGemmEx"; CHECK_THROWS(Invalid, contract::validate_kernels(q)); }
+  { program::Program q = p; q.instructions[find("router_topk")].kernel = "unsupported"; CHECK_THROWS(Invalid, contract::validate_kernels(q)); }
+  { program::Program q = p; drop_attr(q.instructions[find("mla_q_absorb")], "theta"); CHECK_THROWS(Invalid, contract::validate_kernels(q)); }
+  { program::Program q = p; set_attr(q.instructions[find("router_topk")], "topk", "4096"); CHECK_THROWS(Invalid, contract::validate_kernels(q)); }
+  { program::Program q = p; set_attr(q.instructions[find("mla_attention")], "latent", "256"); CHECK_THROWS(Invalid, contract::validate_kernels(q)); }
+  { program::Program q = p; set_attr(q.instructions[find("view")], "start", "100000"); CHECK_THROWS(Invalid, contract::validate_kernels(q)); }
+  { program::Program q = p; q.instructions[find("moe_gate_up")].inputs.pop_back(); CHECK_THROWS(Invalid, contract::validate_kernels(q)); }
+  { program::Program q = p; q.instructions[find("lm_head")].kind = 2; CHECK_THROWS(Invalid, contract::validate_kernels(q)); }
+  { program::Program q = p; q.instructions[find("linear")].op = "conv3d"; CHECK_THROWS(Invalid, contract::validate_kernels(q)); }
+  // bindings: a weight the rank does not load, a parameter nobody reads, a wrong leading dimension, a short load
+  { program::Program q = p; set_attr(q.instructions[find("lm_head")], "weight", "lm_tail"); CHECK_THROWS(Invalid, contract::validate_bindings(q, plans[0])); }
+  { init::Plan b = plans[0]; b.parameters.push_back(b.parameters[0]); b.parameters.back().name = "orphan"; CHECK_THROWS(Invalid, contract::validate_bindings(p, b)); }
+  { init::Plan b = plans[0];
+    const std::string head = *p.instructions[find("lm_head")].attr("weight");
+    for (auto& prm : b.parameters) if (prm.name == head) prm.dims[0] += 8;
+    CHECK_THROWS(Invalid, contract::validate_bindings(p, b)); }
+  { init::Plan b = plans[0]; b.loads.pop_back(); CHECK_THROWS(Invalid, contract::validate_bindings(p, b)); }
+  { init::Plan b = plans[0]; b.loads[0].dest = 100000; CHECK_THROWS(Invalid, contract::validate_bindings(p, b)); }
+}
+
 int main() {
   std::pair<const char*, std::function<void()>> tests[] = {
       {"serve_batching", test_serve_batching_matches_sequential}, {"serve_admission", test_serve_validation_and_admission},
       {"serve_backpressure_cancel", test_serve_backpressure_cancel_and_eos}, {"serve_failure_shutdown", test_serve_engine_failure_and_shutdown},
       {"api_tokenizer", test_api_tokenizer_and_sampling_json}, {"kernel_plugin", test_kernel_plugin_loader},
       {"state_pool", test_state_pool}, {"prefix_index", test_prefix_index}, {"paging", test_paging},
-      {"rankplan_runtime", test_rankplan_and_runtime}, {"transfer", test_transfer}, {"scheduler", test_scheduler}, {"cpu_plan", test_cpu_plan}};
+      {"rankplan_runtime", test_rankplan_and_runtime}, {"transfer", test_transfer}, {"scheduler", test_scheduler}, {"cpu_plan", test_cpu_plan},
+      {"contract_validator", test_contract_validator}};
   for (auto& t : tests) {
     int before = failures;
     try {

@@ -93,6 +93,9 @@ class PlanEngine:
                  num_slots: int = 1, keep_logits: bool = False):
         self.fabric, self.rank, self.world = fabric, fabric.rank, fabric.world
         b = Path(bundle_dir)
+        from .. import compiler
+
+        compiler.validate_bundle(str(b))     # kernel / binding contracts of the serialized program, before any allocation
         self.program = json.loads((b / "device-program.json").read_text())
         self.manifest = json.loads((b / "serving.json").read_text())
         if self.program["parallel"]["tp"] != self.world:

@@ -12,7 +12,8 @@ def test_core_services_cpp():
 
     _build.build_core()
     _build.build_plugins()
-    env = dict(os.environ, IFAB_PLUGIN_DIR=str(_build.PLUGIN_DIR))
+    env = dict(os.environ, IFAB_PLUGIN_DIR=str(_build.PLUGIN_DIR),
+               IFAB_EXAMPLE_MODEL=os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "mla_moe_slice_tp1.inferfabric"))
     r = subprocess.run([str(_build.TESTS_BIN)], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-2000:]
     assert "0 failures" in r.stdout and "ok   kernel_plugin" in r.stdout and "skip kernel_plugin" not in r.stdout
