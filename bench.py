@@ -32,7 +32,8 @@ def parse():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="native", choices=["native", "reference", "nccl_cublas"])
-    ap.add_argument("--model", default="flagship", choices=["flagship", "tiny"])
+    ap.add_argument("--model", default="flagship", choices=["flagship", "tiny", "dense2b"],
+                    help="flagship: the 92B-class MLA+MoE model of the headline metric; dense2b: the Qwen-style 2B dense GQA decoder")
     ap.add_argument("--context", type=int, default=512)
     ap.add_argument("--prefill", default="gemm", choices=["gemm", "decode"],
                     help="gemm: tensor-core prefill path (native impl only); decode: prompt through the decode kernels, 8 rows a time")
@@ -116,17 +117,27 @@ def main():
     from ironpangu_b200.parallel.fabric import Fabric
     from ironpangu_b200.runtime.engine import DecodeEngine
 
-    cfg = MlaMoeConfig.flagship() if args.model == "flagship" else MlaMoeConfig.tiny(4)
+    dense = args.model == "dense2b"
+    if dense:
+        from ironpangu_b200.models import dense_gqa as G
+        cfg = G.DenseConfig.qwen2b()
+    else:
+        cfg = MlaMoeConfig.flagship() if args.model == "flagship" else MlaMoeConfig.tiny(4)
     if args.layers:
         cfg.layers = args.layers
     K, W = args.steps, max(args.warmup, 3)
     max_context = args.context + 3 * K + 2 * W + 64
     fab = Fabric(rank, world)
     t0 = time.time()
-    weights = random_rank_weights(cfg, rank, world, dev, seed=0)
+    weights = (G.random_rank_weights if dense else random_rank_weights)(cfg, rank, world, dev, seed=0)
     torch.cuda.synchronize()
     weight_bytes = sum(t.numel() * t.element_size() for t in weights.values())
-    if args.impl == "native":
+    if dense:
+        if args.impl != "native":
+            raise SystemExit("--model dense2b runs on the native path only")
+        dec = G.DenseDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1)
+        args.prefill = "decode"
+    elif args.impl == "native":
         dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1,
                             persistent=bool(args.persistent))
     else:
@@ -210,13 +221,15 @@ def main():
         line = {
             "metric": "decode_tokens_per_s_per_box", "value": round(value, 3), "unit": "tokens/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / BASELINE_TOK_S, 3), "dtype": "bf16", "impl": args.impl,
+            "vs_baseline": None if dense else round(value / BASELINE_TOK_S, 3), "dtype": "bf16", "impl": args.impl,
             "data": "synthetic (uniform random prompt ids; N(0,0.02) random-init weights generated on device)",
             "config": {"model": ("92B-class MLA+MoE: 46L hidden 4096, 32 heads, q_lora 1536, kv_lora 512, nope 128, rope 64, "
                                  "v 128, 96 experts x 1536 top-8 softmax + 1 shared, vocab 153600") if args.model == "flagship"
-                       and not args.layers else f"{args.model} layers={cfg.layers} (reduced config)",
+                       and not args.layers else ("Qwen-style 2B dense: 24L hidden 2048, 16 q / 4 kv heads x 128, SwiGLU 6144, vocab 151936 "
+                                                 "(not the headline model)") if dense and not args.layers
+                       else f"{args.model} layers={cfg.layers} (reduced config)",
                        "params_b": round(cfg.param_count() / 1e9, 2), "global_batch": 1, "seq_len": args.context,
-                       "decode_tokens": K, "parallelism": f"tp{world}ep{world}", "decode_step": "single persistent launch" if args.persistent else "operator chain",
+                       "decode_tokens": K, "parallelism": f"tp{world}" if dense else f"tp{world}ep{world}", "decode_step": "single persistent launch" if args.persistent else "operator chain",
                        "prefill": args.prefill if args.impl == "native" else "library",
                        "l2": "per-step weight stream (>= 2.5 GB per rank) exceeds the 126 MB L2; no explicit flush",
                        "baseline_ref": "17.7293 ms TPOT on 8x Ascend (docs/validation/2026-10-17-packed-c8/README.md:20-23)",

@@ -27,6 +27,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=46)
     ap.add_argument("--q-lora", type=int, default=1536)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--eager", action="store_true", help="plain launches instead of graph replays (for profilers)")
     a = ap.parse_args()
     dev = torch.device("cuda")
     H, T, L, ql, nope, vdim, pt = a.heads, a.tokens, a.layers, a.q_lora, 128, 128, 16
@@ -65,9 +66,14 @@ def main() -> None:
     for name, fn in (("chain_us_per_layer", chain), ("fused_us_per_layer", fused)):
         fn()
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            fn()
+        if a.eager:
+            class _Eager:
+                replay = staticmethod(fn)
+            graph = _Eager()
+        else:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn()
         for _ in range(3):
             graph.replay()
         torch.cuda.synchronize()
