@@ -1,25 +1,27 @@
 // Row-parallel bf16 GEMM fused with a two-shot all-reduce (reduce-scatter + all-gather) over NVLink peer
 // memory:  Y = sum_ranks A_r[M,K_r] * B_r[N,K_r]^T (+ residual), every rank ends with the full result.
 //
-// Every rank runs the same grid of 128 x 128 tiles over its K shard (tcgen05 main loop of
-// tc_gemm_core.cuh, 3-stage ring so that two CTAs share an SM and one tile's exchange overlaps another
-// tile's main loop). Tile t is owned by rank t % world. A rank computes the tiles it does NOT own first (in
-// index order) and its own tiles last, so by the time an owner reaches a tile the partials of the other ranks -
-// pushed from the front of their grids - have normally arrived and the bounded wait falls through.
-//   non-owner  accumulator -> bf16 tile in shared memory (the drained TMA ring) -> one bulk copy per row
-//              (cp.async.bulk shared -> global) into slot (t, rank) of the OWNER's staging area -> one
-//              system fence by one thread behind a CTA barrier -> flag; the CTA then exits, it never waits
-//   owner      waits - bounded - for the other ranks' flags of its tile, sums the `world` partials in rank
-//              order (its own partial rounded to bf16 like the others, so the result does not depend on
-//              who owns a tile; eight 16-byte loads in flight per thread), adds the residual, rounds, and
-//              stores the finished rows into the output buffer of EVERY rank (the output lives in symmetric
-//              memory: out_peers[r] is rank r's buffer), then raises each peer's "final" flag of the tile
+// A persistent kernel, one CTA per SM, 128 x 256 tiles over this rank's K shard. Tensor memory holds TWO accumulators
+// (2 x 256 columns): while the four epilogue warps exchange tile i with the other GPUs, the TMA producer and the MMA
+// issuer are already running the main loop of tile i + 1 into the other accumulator, so the NVLink traffic of a tile
+// moves underneath the tensor-core work of the next one. Tile t is owned by rank t % world; a rank works through the
+// tiles it does NOT own first (in index order, strided over its CTAs) and its own tiles last, so by the time an owner
+// reaches a tile the partials of the other ranks - pushed from the front of their schedules - have normally arrived.
+//   non-owner  accumulator -> bf16 tile in shared memory -> accumulator released -> one bulk copy per row
+//              (cp.async.bulk shared -> global) into slot (t, rank) of the OWNER's staging area -> one system
+//              fence by one thread behind a barrier -> flag; the epilogue never waits for a peer
+//   owner      accumulator -> bf16 tile in shared memory -> accumulator released -> bounded wait for the other
+//              ranks' flags of the tile -> sum of the `world` partials in rank order (the own partial rounded to
+//              bf16 like the others, so the result does not depend on who owns a tile; eight 16-byte loads in
+//              flight per thread) + residual -> rows stored into the output buffer of EVERY rank (the output lives
+//              in symmetric memory: out_peers[r] is rank r's buffer) -> each peer's "final" flag of the tile
 //   last CTA   (by ticket) waits for the final flags of the tiles this rank does not own, so when the
 //              kernel completes on a rank its output is complete, then advances the call counter
 // Bytes crossing NVLink per rank: 2 * (world-1)/world * M*N*2 - the minimum of a bf16 reduce-scatter +
-// all-gather - and they move tile by tile underneath the main loops of later tiles. Owners wait only for
-// non-owner CTAs, which never wait, so no cycle can form. No TMA multicast and no TMA load from peer memory is used: peers are written with
-// non-tensor bulk stores from shared memory and staged partials are read back locally. Reference: linear(tp_columns) + allreduce on the bulk collective domain
+// all-gather. Owners wait only for non-owner epilogues, which never wait, so no cycle can form; every wait (mbarrier
+// or flag) is bounded and reports through the status word. No TMA multicast and no TMA load from peer memory is
+// used: peers are written with non-tensor bulk stores from shared memory and staged partials are read back locally.
+// Reference: linear(tp_columns) + allreduce on the bulk collective domain
 // (native/src/token_executor.h:374-404, docs/validation/2026-10-18-bulk-domains).
 #include "tc_gemm_core.cuh"
 #include "ifab_kernels.h"
@@ -28,6 +30,13 @@ using namespace ifab;
 using namespace ifab::tc;
 
 namespace {
+
+constexpr int AR_BN = 256, AR_STAGES = 3;
+constexpr int AR_A_BYTES = BM * BK * 2, AR_B_BYTES = AR_BN * BK * 2, AR_STAGE_BYTES = AR_A_BYTES + AR_B_BYTES;
+constexpr int AR_ROW_PAD = AR_BN + 8;                       // bf16 elements per padded row of the exchange tile
+constexpr int AR_TILE_SMEM = BM * AR_ROW_PAD * 2;
+constexpr size_t AR_TILE_BYTES = (size_t)BM * AR_BN * 2;    // one staged partial tile in global memory
+constexpr int AR_SMEM = AR_STAGES * AR_STAGE_BYTES + AR_TILE_SMEM + 1024 /*align*/ + 256 /*barriers*/;
 
 struct ArParams {
   bf16* out_peers[IFAB_MAX_RANKS];   // out_peers[rank] is the local output; same shape / ldc on every rank
@@ -40,156 +49,252 @@ struct ArParams {
   uint32_t spin_limit;
 };
 
-template <int BN, int NSTAGES>
-__global__ void __launch_bounds__(192) tc_gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                                                                const __grid_constant__ CUtensorMap tmap_b, ArParams a) {
+// barrier 1 over the 128 epilogue threads that also ANDs a predicate, so that every warp takes the same branch
+__device__ __forceinline__ bool epilogue_all(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r) : "r"((uint32_t)pred) : "memory");
+  return r != 0;
+}
+
+// schedule position -> tile: the tiles of the other owners in increasing index, then this rank's own tiles
+__device__ __forceinline__ int tile_at(int pos, int ntiles, int world, int rank) {
+  if (world == 1) return pos;
+  const int owned = (ntiles - rank + world - 1) / world, foreign = ntiles - owned;
+  if (pos < foreign) {
+    const int g = pos / (world - 1), i = pos % (world - 1);
+    return g * world + (i < rank ? i : i + 1);
+  }
+  return (pos - foreign) * world + rank;
+}
+
+__global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                   const __grid_constant__ CUtensorMap tmap_b, ArParams a) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ int s_flag_ok, s_last;
-  Pipe<BN, NSTAGES> pipe;
-  pipe.setup(smem_raw, &tmap_a, &tmap_b);
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  bf16* tile_s = reinterpret_cast<bf16*>(smem + AR_STAGES * AR_STAGE_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + AR_STAGES * AR_STAGE_BYTES + AR_TILE_SMEM);
+  uint64_t* empty = full + AR_STAGES;
+  uint64_t* acc_full = empty + AR_STAGES;    // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int world = a.fv.world, rank = a.fv.rank;
-  // block order: the tiles of the other owners in increasing index, then this rank's own tiles
-  int tile = blockIdx.x;
-  if (world > 1) {
-    const int owned = (a.ntiles - rank + world - 1) / world, foreign = a.ntiles - owned;
-    const int b = blockIdx.x;
-    if (b < foreign) {
-      const int g = b / (world - 1), i = b % (world - 1);
-      tile = g * world + (i < rank ? i : i + 1);
-    } else {
-      tile = (b - foreign) * world + rank;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < AR_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
     }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
   }
-  const int m0 = (tile / a.tiles_n) * BM, n0 = (tile % a.tiles_n) * BN;
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * AR_BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int world = a.fv.world, rank = a.fv.rank;
   const int num_kb = (a.K + BK - 1) / BK;
-  const int owner = tile % world;
+  // this CTA's tiles: schedule positions blockIdx.x, + gridDim.x, ...
+  const int my_tiles = (a.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
   grid_dep_launch();
   grid_dep_wait();
   const uint64_t epoch = *reinterpret_cast<volatile uint64_t*>(a.seq) + 1;
   const uint32_t par = (uint32_t)(epoch & 1);
-  constexpr size_t TILE_BYTES = (size_t)BM * BN * 2;
-  constexpr int ROW_PAD = BN + 8;                       // bf16 elements per padded shared-memory row
   auto half = [&](int r) { return a.fv.data[r] + (size_t)par * a.fv.data_half_bytes; };
   auto flags = [&](int r) { return a.fv.flags[r] + (size_t)par * a.fv.flag_half_words; };
+
   if (warp == 0 && lane == 0) {
-    pipe.produce(&tmap_a, &tmap_b, num_kb, m0, n0, -1, a.spin_limit, a.fv.status);
+    // ---- TMA producer: one continuous ring of stages over all tiles of this CTA ----
+    int it = 0, issued = 0;
+    for (int i = 0; i < my_tiles && !*abort_flag; ++i) {
+      const int tile = tile_at(blockIdx.x + i * gridDim.x, a.ntiles, world, rank);
+      const int m0 = (tile / a.tiles_n) * BM, n0 = (tile % a.tiles_n) * AR_BN;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % AR_STAGES;
+        const uint32_t round = it / AR_STAGES;
+        if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, a.spin_limit)) { *abort_flag = 1; break; }
+        if (*abort_flag) break;
+        unsigned char* dst = smem + s * AR_STAGE_BYTES;
+        mbar_expect_tx(&full[s], AR_STAGE_BYTES);
+        tma_load_2d(dst, &tmap_a, &full[s], kb * BK, m0);
+        tma_load_2d(dst + AR_A_BYTES, &tmap_b, &full[s], kb * BK, n0);
+        issued = it + 1;
+      }
+    }
+    if (*abort_flag) {
+      // drain: every copy this thread issued must land before the CTA may exit
+      for (int k = max(0, issued - AR_STAGES); k < issued; ++k) mbar_wait(&full[k % AR_STAGES], (k / AR_STAGES) & 1, a.spin_limit);
+      atomicOr(a.fv.status, IFAB_STATUS_MBAR_TIMEOUT);
+    }
   } else if (warp == 1 && lane == 0) {
-    pipe.mma(num_kb, a.spin_limit, a.fv.status);
+    // ---- MMA issuer: tile i accumulates into accumulator i & 1 ----
+    constexpr uint32_t idesc = umma_idesc_bf16(BM, AR_BN);
+    int it = 0;
+    bool ok = true;
+    for (int i = 0; i < my_tiles && ok; ++i) {
+      const int acc = i & 1, use = i >> 1;
+      if (use > 0 && !mbar_wait(&acc_empty[acc], (use - 1) & 1, a.spin_limit)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d = tmem_base + (uint32_t)(acc * AR_BN);
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % AR_STAGES;
+        if (!mbar_wait(&full[s], (it / AR_STAGES) & 1, a.spin_limit) || *abort_flag) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * AR_STAGE_BYTES);
+        const uint64_t da = umma_desc_sw128(a_addr), db = umma_desc_sw128(a_addr + AR_A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, kb > 0 || k > 0);
+        umma_commit(&empty[s]);
+      }
+      if (ok) umma_commit(&acc_full[acc]);
+    }
+    if (!ok) {
+      *abort_flag = 1;
+      atomicOr(a.fv.status, IFAB_STATUS_MBAR_TIMEOUT);
+    }
   } else if (warp >= 2) {
-    const bool ok = pipe.wait_accumulator(a.spin_limit, a.fv.status);
-    const int q = warp & 3, trow = q * 32 + lane, et = threadIdx.x - 64, ew = warp - 2;   // epilogue thread / warp ids
-    const uint32_t tm = pipe.tmem_base + ((uint32_t)(q * 32) << 16);
-    bf16* tile_s = reinterpret_cast<bf16*>(pipe.smem);   // the stage ring is drained once the accumulator is complete
-    // accumulator -> bf16 rows in shared memory
-    if (ok) {
+    // ---- epilogue warps: exchange tile i while the main loop of tile i + 1 runs ----
+    const int q = warp & 3, trow = q * 32 + lane, et = threadIdx.x - 64;
+    constexpr int CPR = AR_BN / 8;                        // 16-byte chunks per row
+    for (int i = 0; i < my_tiles; ++i) {
+      const int acc = i & 1, use = i >> 1;
+      const int tile = tile_at(blockIdx.x + i * gridDim.x, a.ntiles, world, rank);
+      const int m0 = (tile / a.tiles_n) * BM, n0 = (tile % a.tiles_n) * AR_BN;
+      const int owner = tile % world;
+      const bool ok = epilogue_all(mbar_wait(&acc_full[acc], use & 1, a.spin_limit) && !*abort_flag);
+      tc_fence_after();
+      if (!ok) {
+        *abort_flag = 1;
+        if (lane == 0) atomicOr(a.fv.status, IFAB_STATUS_MBAR_TIMEOUT);
+        break;
+      }
+      // accumulator -> bf16 rows in shared memory, then hand the accumulator back to the MMA issuer
+      const uint32_t tm = tmem_base + (uint32_t)(acc * AR_BN) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < AR_BN; c0 += 32) {
         float v[32];
         tmem_ld_32x32(tm + (uint32_t)c0, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(tile_s + (size_t)trow * ROW_PAD + c0 + 8 * i) = pack8(v + 8 * i);
+        for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4*>(tile_s + (size_t)trow * AR_ROW_PAD + c0 + 8 * k) = pack8(v + 8 * k);
       }
-    }
-    fence_proxy_async_smem();
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    constexpr int CPR = BN / 8;                          // 16-byte chunks per row
-    const int nvalid = min(BN, a.N - n0);                // valid columns of this tile (multiple of 8)
-    if (world > 1 && rank != owner) {
-      // ---- push the partial tile: one bulk copy per row (thread et owns row et) ----
-      bf16* dst = reinterpret_cast<bf16*>(half(owner) + ((size_t)(tile / world) * world + rank) * TILE_BYTES);
-      if (ok) bulk_store(dst + (size_t)et * BN, tile_s + (size_t)et * ROW_PAD, BN * 2);
-      bulk_commit();
-      bulk_wait_all();
-      fence_proxy_async();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et == 0) {
-        __threadfence_system();
-        st_release_sys(flags(owner) + (size_t)tile * world + rank, epoch);
-      }
-    } else {
-      // ---- owner (or single rank): reduce in rank order, add the residual, publish to every rank ----
-      if (et == 0) s_flag_ok = 1;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (world > 1 && et < world && et != rank) {
-        if (!wait_flag_bounded(flags(rank) + (size_t)tile * world + et, epoch, a.fv.spin_limit)) {
-          s_flag_ok = 0;
-          atomicOr(a.fv.status, IFAB_STATUS_PEER_TIMEOUT);
-        }
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      const bool good = ok && s_flag_ok;
-      if (good) {
-        const bf16* stage = reinterpret_cast<const bf16*>(half(rank) + (size_t)(tile / world) * world * TILE_BYTES);
-        // item i = 16-byte chunk (i % CPR) of row (i / CPR); a thread owns items et + 128 * k and keeps G of them in flight
-        constexpr int G = 8, ITEMS = BM * CPR / 128;
-        static_assert(ITEMS % G == 0, "items per thread must split into groups");
-#pragma unroll 1
-        for (int k0 = 0; k0 < ITEMS; k0 += G) {
-          float v[G][8];
-#pragma unroll
-          for (int g = 0; g < G; ++g)
-#pragma unroll
-            for (int k = 0; k < 8; ++k) v[g][k] = 0.f;
-#pragma unroll 1
-          for (int src = 0; src < world; ++src) {
-            uint4 raw[G];
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-              const int i = et + 128 * (k0 + g), r = i / CPR, c = i % CPR;
-              raw[g] = src == rank ? *reinterpret_cast<const uint4*>(tile_s + (size_t)r * ROW_PAD + c * 8)
-                                   : __ldcg(reinterpret_cast<const uint4*>(stage + (size_t)src * BM * BN + (size_t)r * BN + c * 8));
-            }
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-              float f[8];
-              unpack8(raw[g], f);
-#pragma unroll
-              for (int k = 0; k < 8; ++k) v[g][k] += f[k];
-            }
-          }
-          uint4 res[G];
-#pragma unroll
-          for (int g = 0; g < G; ++g) {
-            const int i = et + 128 * (k0 + g), r = i / CPR, c = i % CPR;
-            const bool in = m0 + r < a.M && n0 + c * 8 < a.N;
-            res[g] = (a.residual && in) ? *reinterpret_cast<const uint4*>(a.residual + (long)(m0 + r) * a.ldr + n0 + c * 8) : make_uint4(0, 0, 0, 0);
-          }
-#pragma unroll
-          for (int g = 0; g < G; ++g) {
-            const int i = et + 128 * (k0 + g), r = i / CPR, c = i % CPR;
-            if (a.residual) {
-              float f[8];
-              unpack8(res[g], f);
-#pragma unroll
-              for (int k = 0; k < 8; ++k) v[g][k] = bf16_round(v[g][k]) + f[k];
-            }
-            *reinterpret_cast<uint4*>(tile_s + (size_t)r * ROW_PAD + c * 8) = pack8(v[g]);
-          }
-        }
-      }
+      tc_fence_before();
       fence_proxy_async_smem();
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (good && m0 + et < a.M) {
-        for (int dst = 0; dst < world; ++dst)
-          bulk_store(a.out_peers[dst] + (long)(m0 + et) * a.ldc + n0, tile_s + (size_t)et * ROW_PAD, (uint32_t)nvalid * 2);
-      }
-      bulk_commit();
-      bulk_wait_all();
-      if (world > 1) {
+      if (et == 0) mbar_arrive(&acc_empty[acc]);
+      const int nvalid = min(AR_BN, a.N - n0);            // valid columns of this tile (multiple of 8)
+      if (world > 1 && rank != owner) {
+        // ---- push the partial tile: one bulk copy per row (thread et owns row et) ----
+        bf16* dst = reinterpret_cast<bf16*>(half(owner) + ((size_t)(tile / world) * world + rank) * AR_TILE_BYTES);
+        bulk_store(dst + (size_t)et * AR_BN, tile_s + (size_t)et * AR_ROW_PAD, AR_BN * 2);
+        bulk_commit();
+        bulk_wait_all();
         fence_proxy_async();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (et == 0) {
           __threadfence_system();
+          st_release_sys(flags(owner) + (size_t)tile * world + rank, epoch);
+        }
+      } else {
+        // ---- owner (or single rank): reduce in rank order, add the residual, publish to every rank ----
+        if (et == 0) s_flag_ok = 1;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (world > 1 && et < world && et != rank) {
+          if (!wait_flag_bounded(flags(rank) + (size_t)tile * world + et, epoch, a.fv.spin_limit)) {
+            s_flag_ok = 0;
+            atomicOr(a.fv.status, IFAB_STATUS_PEER_TIMEOUT);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool good = s_flag_ok != 0;
+        if (good) {
+          const bf16* stage = reinterpret_cast<const bf16*>(half(rank) + (size_t)(tile / world) * world * AR_TILE_BYTES);
+          // item j = 16-byte chunk (j % CPR) of row (j / CPR); a thread owns items et + 128 * k and keeps G of them in flight
+          constexpr int G = 8, ITEMS = BM * CPR / 128;
+          static_assert(ITEMS % G == 0, "items per thread must split into groups");
+#pragma unroll 1
+          for (int k0 = 0; k0 < ITEMS; k0 += G) {
+            float v[G][8];
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+#pragma unroll
+              for (int k = 0; k < 8; ++k) v[g][k] = 0.f;
+#pragma unroll 1
+            for (int src = 0; src < world; ++src) {
+              uint4 raw[G];
+#pragma unroll
+              for (int g = 0; g < G; ++g) {
+                const int j = et + 128 * (k0 + g), r = j / CPR, c = j % CPR;
+                raw[g] = src == rank ? *reinterpret_cast<const uint4*>(tile_s + (size_t)r * AR_ROW_PAD + c * 8)
+                                     : __ldcg(reinterpret_cast<const uint4*>(stage + (size_t)src * BM * AR_BN + (size_t)r * AR_BN + c * 8));
+              }
+#pragma unroll
+              for (int g = 0; g < G; ++g) {
+                float f[8];
+                unpack8(raw[g], f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[g][k] += f[k];
+              }
+            }
+            uint4 res[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              const int j = et + 128 * (k0 + g), r = j / CPR, c = j % CPR;
+              const bool in = m0 + r < a.M && n0 + c * 8 < a.N;
+              res[g] = (a.residual && in) ? *reinterpret_cast<const uint4*>(a.residual + (long)(m0 + r) * a.ldr + n0 + c * 8) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              const int j = et + 128 * (k0 + g), r = j / CPR, c = j % CPR;
+              if (a.residual) {
+                float f[8];
+                unpack8(res[g], f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[g][k] = bf16_round(v[g][k]) + f[k];
+              }
+              *reinterpret_cast<uint4*>(tile_s + (size_t)r * AR_ROW_PAD + c * 8) = pack8(v[g]);
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (good && m0 + et < a.M && nvalid > 0) {
           for (int dst = 0; dst < world; ++dst)
-            if (dst != rank) st_release_sys(flags(dst) + (size_t)a.ntiles * world + tile, epoch);
+            bulk_store(a.out_peers[dst] + (long)(m0 + et) * a.ldc + n0, tile_s + (size_t)et * AR_ROW_PAD, (uint32_t)nvalid * 2);
+        }
+        bulk_commit();
+        bulk_wait_all();
+        if (world > 1) {
+          fence_proxy_async();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (et == 0) {
+            __threadfence_system();
+            for (int dst = 0; dst < world; ++dst)
+              if (dst != rank) st_release_sys(flags(dst) + (size_t)a.ntiles * world + tile, epoch);
+          }
         }
       }
+      // the exchange tile in shared memory is rewritten by the next iteration: every bulk copy has completed (wait above)
+      asm volatile("bar.sync 1, 128;" ::: "memory");
     }
   }
-  pipe.teardown();
-  // ---- the last CTA of this rank collects the final flags of the tiles owned by peers ----
+  // ---- teardown: free tensor memory, then the last CTA of this rank collects the final flags ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * AR_BN);
+  }
   if (threadIdx.x == 0) {
     __threadfence();
     s_last = (atomicAdd(a.done, 1u) == gridDim.x - 1) ? 1 : 0;
@@ -210,23 +315,25 @@ __global__ void __launch_bounds__(192) tc_gemm_allreduce_kernel(const __grid_con
   }
 }
 
-// 128 x 128 tiles with a 3-stage ring (97 KB of shared memory): two CTAs share an SM, so the exchange of one
-// tile overlaps the tensor-core main loop of another.
-constexpr int AR_BN = 128, AR_STAGES = 3;
-
 int launch_ar(const CUtensorMap& ta, const CUtensorMap& tb, ArParams& a, cudaStream_t s) {
-  using C = Cfg<AR_BN, AR_STAGES>;
-  auto k = tc_gemm_allreduce_kernel<AR_BN, AR_STAGES>;
-  if (int rc = opt_in_smem(k, C::SMEM)) return rc;
-  static_assert((size_t)BM * (AR_BN + 8) * 2 <= (size_t)C::STAGES * C::STAGE_BYTES, "tile must fit the drained ring");
+  auto k = tc_gemm_allreduce_kernel;
+  if (int rc = opt_in_smem(k, AR_SMEM)) return rc;
   a.tiles_n = (a.N + AR_BN - 1) / AR_BN;
   a.ntiles = a.tiles_n * ((a.M + BM - 1) / BM);
   if (a.fv.world > 1) {
     const size_t owned = (a.ntiles + a.fv.world - 1) / a.fv.world;
-    if (owned * a.fv.world * (size_t)BM * AR_BN * 2 > a.fv.data_half_bytes) return -3;
+    if (owned * a.fv.world * AR_TILE_BYTES > a.fv.data_half_bytes) return -3;
     if ((size_t)a.ntiles * (a.fv.world + 1) > a.fv.flag_half_words) return -4;
   }
-  return launch_chain(k, dim3(a.ntiles), dim3(192), (size_t)C::SMEM, s, ta, tb, a);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const int grid = a.ntiles < sms ? a.ntiles : sms;
+  return launch_chain(k, dim3(grid), dim3(192), (size_t)AR_SMEM, s, ta, tb, a);
 }
 
 }  // namespace
