@@ -7,14 +7,16 @@
 // moves underneath the tensor-core work of the next one. Tile t is owned by rank t % world; a rank works through the
 // tiles it does NOT own first (in index order, strided over its CTAs) and its own tiles last, so by the time an owner
 // reaches a tile the partials of the other ranks - pushed from the front of their schedules - have normally arrived.
-//   non-owner  accumulator -> bf16 tile in shared memory -> accumulator released -> one bulk copy per row
-//              (cp.async.bulk shared -> global) into slot (t, rank) of the OWNER's staging area -> one system
-//              fence by one thread behind a barrier -> flag; the epilogue never waits for a peer
-//   owner      accumulator -> bf16 tile in shared memory -> accumulator released -> bounded wait for the other
-//              ranks' flags of the tile -> sum of the `world` partials in rank order (the own partial rounded to
-//              bf16 like the others, so the result does not depend on who owns a tile; eight 16-byte loads in
-//              flight per thread) + residual -> rows stored into the output buffer of EVERY rank (the output lives
-//              in symmetric memory: out_peers[r] is rank r's buffer) -> each peer's "final" flag of the tile
+// A tile is exchanged in four passes of 64 columns through one 18 KB shared-memory buffer, which leaves room for a
+// 4-stage operand ring beside it:
+//   non-owner  accumulator columns -> bf16 rows in shared memory -> one bulk copy per row (cp.async.bulk shared ->
+//              global) into slot (t, rank) of the OWNER's staging area; after the last pass: completion of all copies
+//              -> one system fence by one thread behind a barrier -> flag; the epilogue never waits for a peer
+//   owner      bounded wait for the other ranks' flags of the tile, then per pass: accumulator columns -> bf16 -> sum of
+//              the `world` partials in rank order (the own partial rounded to bf16 like the others, so the result does
+//              not depend on who owns a tile; eight 16-byte loads in flight per thread) + residual -> rows stored into
+//              the output buffer of EVERY rank (the output lives in symmetric memory: out_peers[r] is rank r's
+//              buffer); after the last pass each peer's "final" flag of the tile
 //   last CTA   (by ticket) waits for the final flags of the tiles this rank does not own, so when the
 //              kernel completes on a rank its output is complete, then advances the call counter
 // Bytes crossing NVLink per rank: 2 * (world-1)/world * M*N*2 - the minimum of a bf16 reduce-scatter +
@@ -31,9 +33,10 @@ using namespace ifab::tc;
 
 namespace {
 
-constexpr int AR_BN = 256, AR_STAGES = 3;
+constexpr int AR_BN = 256, AR_STAGES = 4;
+constexpr int AR_QN = 64;                                   // columns exchanged per epilogue pass (a quarter of the tile)
 constexpr int AR_A_BYTES = BM * BK * 2, AR_B_BYTES = AR_BN * BK * 2, AR_STAGE_BYTES = AR_A_BYTES + AR_B_BYTES;
-constexpr int AR_ROW_PAD = AR_BN + 8;                       // bf16 elements per padded row of the exchange tile
+constexpr int AR_ROW_PAD = AR_QN + 8;                       // bf16 elements per padded row of the exchange buffer
 constexpr int AR_TILE_SMEM = BM * AR_ROW_PAD * 2;
 constexpr size_t AR_TILE_BYTES = (size_t)BM * AR_BN * 2;    // one staged partial tile in global memory
 constexpr int AR_SMEM = AR_STAGES * AR_STAGE_BYTES + AR_TILE_SMEM + 1024 /*align*/ + 256 /*barriers*/;
@@ -165,7 +168,6 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
   } else if (warp >= 2) {
     // ---- epilogue warps: exchange tile i while the main loop of tile i + 1 runs ----
     const int q = warp & 3, trow = q * 32 + lane, et = threadIdx.x - 64;
-    constexpr int CPR = AR_BN / 8;                        // 16-byte chunks per row
     for (int i = 0; i < my_tiles; ++i) {
       const int acc = i & 1, use = i >> 1;
       const int tile = tile_at(blockIdx.x + i * gridDim.x, a.ntiles, world, rank);
@@ -178,35 +180,12 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
         if (lane == 0) atomicOr(a.fv.status, IFAB_STATUS_MBAR_TIMEOUT);
         break;
       }
-      // accumulator -> bf16 rows in shared memory, then hand the accumulator back to the MMA issuer
+      // The tile is exchanged in four passes of 64 columns through one small shared-memory buffer (which leaves room
+      // for a 4-stage operand ring); the accumulator goes back to the MMA issuer after the last pass has read it.
       const uint32_t tm = tmem_base + (uint32_t)(acc * AR_BN) + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < AR_BN; c0 += 32) {
-        float v[32];
-        tmem_ld_32x32(tm + (uint32_t)c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4*>(tile_s + (size_t)trow * AR_ROW_PAD + c0 + 8 * k) = pack8(v + 8 * k);
-      }
-      tc_fence_before();
-      fence_proxy_async_smem();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et == 0) mbar_arrive(&acc_empty[acc]);
-      const int nvalid = min(AR_BN, a.N - n0);            // valid columns of this tile (multiple of 8)
-      if (world > 1 && rank != owner) {
-        // ---- push the partial tile: one bulk copy per row (thread et owns row et) ----
-        bf16* dst = reinterpret_cast<bf16*>(half(owner) + ((size_t)(tile / world) * world + rank) * AR_TILE_BYTES);
-        bulk_store(dst + (size_t)et * AR_BN, tile_s + (size_t)et * AR_ROW_PAD, AR_BN * 2);
-        bulk_commit();
-        bulk_wait_all();
-        fence_proxy_async();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (et == 0) {
-          __threadfence_system();
-          st_release_sys(flags(owner) + (size_t)tile * world + rank, epoch);
-        }
-      } else {
-        // ---- owner (or single rank): reduce in rank order, add the residual, publish to every rank ----
+      const bool pusher = world > 1 && rank != owner;
+      bool good = true;
+      if (!pusher) {
         if (et == 0) s_flag_ok = 1;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (world > 1 && et < world && et != rank) {
@@ -216,14 +195,48 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        const bool good = s_flag_ok != 0;
-        if (good) {
-          const bf16* stage = reinterpret_cast<const bf16*>(half(rank) + (size_t)(tile / world) * world * AR_TILE_BYTES);
-          // item j = 16-byte chunk (j % CPR) of row (j / CPR); a thread owns items et + 128 * k and keeps G of them in flight
-          constexpr int G = 8, ITEMS = BM * CPR / 128;
-          static_assert(ITEMS % G == 0, "items per thread must split into groups");
+        good = s_flag_ok != 0;
+      }
+      bf16* push_dst = reinterpret_cast<bf16*>(half(owner) + ((size_t)(tile / world) * world + rank) * AR_TILE_BYTES);
+      const bf16* stage = reinterpret_cast<const bf16*>(half(rank) + (size_t)(tile / world) * world * AR_TILE_BYTES);
 #pragma unroll 1
-          for (int k0 = 0; k0 < ITEMS; k0 += G) {
+      for (int qc = 0; qc < AR_BN; qc += AR_QN) {
+        // the previous pass's bulk copies have finished READING the buffer
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int c0 = 0; c0 < AR_QN; c0 += 32) {
+          float v[32];
+          tmem_ld_32x32(tm + (uint32_t)(qc + c0), v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4*>(tile_s + (size_t)trow * AR_ROW_PAD + c0 + 8 * k) = pack8(v + 8 * k);
+        }
+        if (qc + AR_QN == AR_BN) {
+          tc_fence_before();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (et == 0) mbar_arrive(&acc_empty[acc]);
+        } else {
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        const int ncols = min(AR_QN, a.N - (n0 + qc));     // valid columns of this pass (multiple of 8, may be <= 0)
+        if (pusher) {
+          // ---- push the partial rows: one bulk copy per row (thread et owns row et) ----
+          fence_proxy_async_smem();   // thread et wrote row et itself
+          bulk_store(push_dst + (size_t)et * AR_BN + qc, tile_s + (size_t)et * AR_ROW_PAD, AR_QN * 2);
+          bulk_commit();
+        } else {
+          // ---- owner (or single rank): reduce in rank order, add the residual, publish to every rank ----
+          if (good) {
+            // item j = 16-byte chunk (j % CPQ) of row (j / CPQ); a thread owns items et + 128 * g, all G in flight at once
+            constexpr int CPQ = AR_QN / 8, G = BM * CPQ / 128;
+            uint4 res[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              const int j = et + 128 * g, r = j / CPQ, c = j % CPQ;
+              const bool in = m0 + r < a.M && n0 + qc + c * 8 < a.N;
+              res[g] = (a.residual && in) ? *reinterpret_cast<const uint4*>(a.residual + (long)(m0 + r) * a.ldr + n0 + qc + c * 8) : make_uint4(0, 0, 0, 0);
+            }
             float v[G][8];
 #pragma unroll
             for (int g = 0; g < G; ++g)
@@ -234,9 +247,9 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
               uint4 raw[G];
 #pragma unroll
               for (int g = 0; g < G; ++g) {
-                const int j = et + 128 * (k0 + g), r = j / CPR, c = j % CPR;
+                const int j = et + 128 * g, r = j / CPQ, c = j % CPQ;
                 raw[g] = src == rank ? *reinterpret_cast<const uint4*>(tile_s + (size_t)r * AR_ROW_PAD + c * 8)
-                                     : __ldcg(reinterpret_cast<const uint4*>(stage + (size_t)src * BM * AR_BN + (size_t)r * AR_BN + c * 8));
+                                     : __ldcg(reinterpret_cast<const uint4*>(stage + (size_t)src * BM * AR_BN + (size_t)r * AR_BN + qc + c * 8));
               }
 #pragma unroll
               for (int g = 0; g < G; ++g) {
@@ -246,16 +259,9 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
                 for (int k = 0; k < 8; ++k) v[g][k] += f[k];
               }
             }
-            uint4 res[G];
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-              const int j = et + 128 * (k0 + g), r = j / CPR, c = j % CPR;
-              const bool in = m0 + r < a.M && n0 + c * 8 < a.N;
-              res[g] = (a.residual && in) ? *reinterpret_cast<const uint4*>(a.residual + (long)(m0 + r) * a.ldr + n0 + c * 8) : make_uint4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-              const int j = et + 128 * (k0 + g), r = j / CPR, c = j % CPR;
+              const int j = et + 128 * g, r = j / CPQ, c = j % CPQ;
               if (a.residual) {
                 float f[8];
                 unpack8(res[g], f);
@@ -265,27 +271,30 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
               *reinterpret_cast<uint4*>(tile_s + (size_t)r * AR_ROW_PAD + c * 8) = pack8(v[g]);
             }
           }
-        }
-        fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (good && m0 + et < a.M && nvalid > 0) {
-          for (int dst = 0; dst < world; ++dst)
-            bulk_store(a.out_peers[dst] + (long)(m0 + et) * a.ldc + n0, tile_s + (size_t)et * AR_ROW_PAD, (uint32_t)nvalid * 2);
-        }
-        bulk_commit();
-        bulk_wait_all();
-        if (world > 1) {
-          fence_proxy_async();
+          fence_proxy_async_smem();
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (et == 0) {
-            __threadfence_system();
+          if (good && m0 + et < a.M && ncols > 0) {
+            for (int dst = 0; dst < world; ++dst)
+              bulk_store(a.out_peers[dst] + (long)(m0 + et) * a.ldc + n0 + qc, tile_s + (size_t)et * AR_ROW_PAD, (uint32_t)ncols * 2);
+          }
+          bulk_commit();
+        }
+      }
+      // every copy of the tile has landed: publish
+      bulk_wait_all();
+      if (world > 1) {
+        fence_proxy_async();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) {
+          __threadfence_system();
+          if (pusher) {
+            st_release_sys(flags(owner) + (size_t)tile * world + rank, epoch);
+          } else {
             for (int dst = 0; dst < world; ++dst)
               if (dst != rank) st_release_sys(flags(dst) + (size_t)a.ntiles * world + tile, epoch);
           }
         }
       }
-      // the exchange tile in shared memory is rewritten by the next iteration: every bulk copy has completed (wait above)
-      asm volatile("bar.sync 1, 128;" ::: "memory");
     }
   }
   // ---- teardown: free tensor memory, then the last CTA of this rank collects the final flags ----

@@ -29,8 +29,15 @@ def time_fn(fn, flush, iters=10):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shapes", default="4096x4096x4096,4096x2112x4096,4096x3072x4096,4096x4096x1536,8192x8192x8192,128x3072x4096")
+    ap.add_argument("--persistent-ar", action="store_true",
+                    help="also time the persistent GEMM + all-reduce kernel at world 1 (its main loop and epilogue without any exchange)")
     args = ap.parse_args()
-    from ironpangu_b200.ops.gemm import gemm
+    from ironpangu_b200.ops.gemm import gemm, gemm_allreduce
+
+    fab = None
+    if args.persistent_ar:
+        from ironpangu_b200.parallel.fabric import Fabric
+        fab = Fabric(0, 1)
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     out = []
@@ -44,6 +51,13 @@ def main():
         fl = 2.0 * M * N * K
         out.append({"shape": s, "ours_ms": round(t_ours, 4), "ours_tflops": round(fl / t_ours / 1e9, 1),
                     "cublas_ms": round(t_lib, 4), "cublas_tflops": round(fl / t_lib / 1e9, 1)})
+        if fab is not None:
+            sym = fab.symmetric_empty((M, N))
+            res = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+            t_p = time_fn(lambda: gemm_allreduce(a, b, fab, sym, residual=res), flush)
+            t_pn = time_fn(lambda: gemm_allreduce(a, b, fab, sym), flush)
+            out[-1].update({"persistent_ar_world1_ms": round(t_p, 4), "persistent_ar_world1_tflops": round(fl / t_p / 1e9, 1),
+                            "persistent_ar_world1_no_residual_ms": round(t_pn, 4)})
         print(json.dumps(out[-1]), flush=True)
 
 
