@@ -111,7 +111,8 @@ inline int launch_chain_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block,
 
 template <typename KernelT>
 inline int opt_in_smem(KernelT kernel, size_t smem) {
-  if (smem <= 48 * 1024) return 0;
+  // the 48 KB default covers static + dynamic shared memory together, so opt in well below it
+  if (smem <= 32 * 1024) return 0;
   return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
 }
 

@@ -72,18 +72,20 @@ class BatchEngine:
     TOPK_CAP = 64   # candidates the sampling kernel keeps per row
 
     def __init__(self, decoder, model_name: str, context: int, vocab: int, eos: int = -1, greedy_only: bool = False,
-                 prefix_slots: int = 0, prefill=None):
+                 prefix_slots: int = 0, prefill=None, token_budget: int = 0):
         """``prefill``: optional tensor-core chunk executor (``forward(tokens, pos0, slot)``, attribute ``M`` = rows per call);
         prompt slices longer than one decode launch group run through it, and the engine advertises ``M`` as its token budget."""
         self.dec, self.name, self.context, self.eos, self.vocab = decoder, model_name, context, eos, vocab
         self.residents = decoder.num_slots
         self.rows = decoder.T
         self.prefill = prefill
-        self.budget = max(self.rows, prefill.M) if prefill is not None else self.rows
+        # tokens the scheduler may hand over per step: more than one launch group (``rows``) is fine, they run back to back
+        self.budget = max(self.rows, prefill.M if prefill is not None else 0, token_budget)
         self.can_sample = getattr(decoder, "logits", None) is not None
         self.greedy_only = greedy_only or not self.can_sample
         dev = decoder.tokens.device
-        self._host = torch.zeros(3, self.rows, dtype=torch.int32).pin_memory()
+        # one pinned control block per launch group of a step: the copies are asynchronous and a step synchronises once
+        self._host = torch.zeros((self.budget + self.rows - 1) // self.rows + 1, 3, self.rows, dtype=torch.int32).pin_memory()
         self._out = torch.zeros(self.rows, dtype=torch.int32).pin_memory()
         self.next_pos = [0] * self.residents
         self.history: List[List[int]] = [[] for _ in range(self.residents)]
@@ -197,6 +199,7 @@ class BatchEngine:
             for k in range(count):
                 rows.append((toks[k], position + k, resident, i if (sample and k == count - 1) else -1))
         out = [0] * len(slices)
+        pending = []                  # (slice indices, device ids) of every launch group, read back once per step
         # prompt chunks: matrix-matrix path, one call per chunk; the row after the chunk's last token is the one that samples
         for i, resident, position, toks, sample in long_slices:
             for c0 in range(0, len(toks), self.prefill.M):
@@ -213,22 +216,24 @@ class BatchEngine:
                 self.audit_counters["h2d_bytes"] += 4 * len(chunk)
             if sample:
                 d.slots[:1].fill_(resident)
-                out[i] = self._emit([(toks[-1], position + len(toks) - 1, resident, i)], 1, counted=True)[0][1]
+                pending += self._emit([(toks[-1], position + len(toks) - 1, resident, i)], 1, counted=True)
         for r0 in range(0, len(rows), self.rows):
             part = rows[r0:r0 + self.rows]
             n = len(part)
+            hb = self._host[(r0 // self.rows) % self._host.shape[0]]
+            if r0 // self.rows >= self._host.shape[0]:
+                torch.cuda.current_stream().synchronize()     # more groups than control blocks: drain before reuse
             for j, (tok, pos, slot, _) in enumerate(part):
-                self._host[0, j], self._host[1, j], self._host[2, j] = tok, pos, slot
-            d.tokens[:n].copy_(self._host[0, :n], non_blocking=True)
-            d.positions[:n].copy_(self._host[1, :n], non_blocking=True)
-            d.slots[:n].copy_(self._host[2, :n], non_blocking=True)
+                hb[0, j], hb[1, j], hb[2, j] = tok, pos, slot
+            d.tokens[:n].copy_(hb[0, :n], non_blocking=True)
+            d.positions[:n].copy_(hb[1, :n], non_blocking=True)
+            d.slots[:n].copy_(hb[2, :n], non_blocking=True)
             d.forward(n)
-            for si, tok in self._emit(part, n):
-                out[si] = tok
+            pending += self._emit(part, n)
             self.audit_counters["launch_groups"] += 1
             self.audit_counters["rows"] += n
             self.audit_counters["h2d_bytes"] += 12 * n
-            self.audit_counters["d2h_bytes"] += 4 * n
+        self._collect(pending, out)
         # publish the prompt of every sequence that just finished its prefill
         if self.prefix is not None:
             for resident, position, count, sample in slices:
@@ -242,7 +247,8 @@ class BatchEngine:
 
     def _emit(self, part, n: int, counted: bool = False):
         """Tokens of the sampling rows among the ``n`` rows the decoder just produced (``next_ids`` / ``logits`` rows 0..n-1,
-        ``slots`` rows 0..n-1 valid): greedy ids as they are, sampled rows through the sampling kernel. Returns ``[(slice, token)]``."""
+        ``slots`` rows 0..n-1 valid): greedy ids as they are, sampled rows through the sampling kernel. Returns at most one
+        ``(slice indices, device ids)`` pair; nothing is copied to the host here."""
         d = self.dec
         ids = d.next_ids[:n]
         if self.can_sample:
@@ -266,9 +272,28 @@ class BatchEngine:
                 ids = ids.clone()
                 ids[sel] = sampled
                 self.audit_counters["sampled_rows"] += len(hot)
-        self._out[:n].copy_(ids, non_blocking=True)
+        pick = [j for j, (_, _, _, si) in enumerate(part) if si >= 0]
+        if not pick:
+            return []
+        sel_ids = ids[torch.tensor(pick, device=ids.device)] if len(pick) != n else ids.clone()
+        return [([part[j][3] for j in pick], sel_ids)]
+
+    def _collect(self, pending, out: List[int]) -> None:
+        """One device-to-host copy and one synchronisation for all launch groups of a step."""
+        if not pending:
+            return
+        dev = torch.cat([ids for _, ids in pending])
+        if dev.numel() > self._out.numel():
+            self._out = torch.zeros(dev.numel(), dtype=torch.int32).pin_memory()
+        host = self._out[:dev.numel()]
+        host.copy_(dev, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        return [(si, int(self._out[j])) for j, (_, _, _, si) in enumerate(part) if si >= 0]
+        k = 0
+        for slice_ids, ids in pending:
+            for si in slice_ids:
+                out[si] = int(host[k])
+                k += 1
+        self.audit_counters["d2h_bytes"] += 4 * dev.numel()
 
 
 def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
@@ -301,7 +326,8 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
         ddec = G.DenseDecoder(dcfg, dweights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs,
                               keep_logits=not args.greedy_only)
         mark("state", "K/V page caches and step workspace")
-        eng = BatchEngine(ddec, f"ifab-{args.model}", args.max_model_len, dcfg.vocab, eos=-1, greedy_only=args.greedy_only)
+        eng = BatchEngine(ddec, f"ifab-{args.model}", args.max_model_len, dcfg.vocab, eos=-1, greedy_only=args.greedy_only,
+                          token_budget=args.max_num_batched_tokens)
         mark("sampling", "per-slot sampling state")
         return eng
     cfg = MlaMoeConfig.tiny(args.layers or 2) if args.model == "tiny" else MlaMoeConfig.flagship()
@@ -320,7 +346,7 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
         prefill = MlaMoePrefill(dec, max_rows=args.prefill_chunk)
         mark("prefill", "activation buffers of the matrix-matrix prompt path")
     eng = BatchEngine(dec, f"ifab-{args.model}", args.max_model_len, cfg.vocab, eos=cfg.eos, greedy_only=args.greedy_only,
-                      prefix_slots=args.prefix_cache_slots, prefill=prefill)
+                      prefix_slots=args.prefix_cache_slots, prefill=prefill, token_budget=args.max_num_batched_tokens)
     mark("sampling", "per-slot sampling state and prefix snapshots")
     return eng
 
@@ -391,6 +417,7 @@ def main() -> None:
     ap.add_argument("--checkpoint", default="")
     ap.add_argument("--max-num-seqs", type=int, default=4)
     ap.add_argument("--max-model-len", type=int, default=256)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=0, help="tokens per scheduler step (0 = one launch group of 8 rows)")
     ap.add_argument("--prefix-cache-slots", type=int, default=0, help="device snapshots kept by the prefix cache (0 = off)")
     ap.add_argument("--kv-int8", action="store_true", help="packed int8 latent KV cache")
     ap.add_argument("--expert-fp8", action="store_true", help="block-scaled fp8 expert weights (1 x 128 scale blocks)")
@@ -409,7 +436,7 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     from ironpangu_b200.runtime.memory import MemoryProfile, StartupOptions
 
-    opts = StartupOptions(args.max_model_len, args.max_num_seqs, 8, args.gpu_memory_utilization,
+    opts = StartupOptions(args.max_model_len, args.max_num_seqs, max(8, args.max_num_batched_tokens), args.gpu_memory_utilization,
                           (args.memory_profile + (f".rank{rank}" if rank else "")) if args.memory_profile else None, args.profile_only)
     rec = MemoryProfile.start(opts)
     engine = build_engine(args, rank, world, rec)

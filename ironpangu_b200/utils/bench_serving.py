@@ -195,12 +195,12 @@ def get_json(host: str, port: int, path: str) -> Optional[Dict]:
 
 def server_args(a) -> List[str]:
     common = ["--max-num-seqs", str(a.max_num_seqs), "--max-num-batched-tokens", str(a.max_num_batched_tokens), "--max-model-len",
-              str(a.max_model_len)]
+              str(a.max_model_len), "--max-queue", str(max(64, 2 * a.requests))]
     if a.mode == "mock":
         return ["--mock", "--vocab", str(a.vocab), "--step-micros", str(a.step_micros), *common]
     if a.mode == "worker":
         worker = (f"{sys.executable} -m ironpangu_b200.runtime.engine_worker --model {a.model} --max-num-seqs {a.max_num_seqs} "
-                  f"--max-model-len {a.max_model_len}")
+                  f"--max-model-len {a.max_model_len} --max-num-batched-tokens {a.max_num_batched_tokens}")
         if a.layers:
             worker += f" --layers {a.layers}"
         if a.kv_int8:
@@ -210,7 +210,7 @@ def server_args(a) -> List[str]:
         if a.gpus > 1:
             worker = (f"{sys.executable} -m torch.distributed.run --nnodes=1 --nproc-per-node {a.gpus} --master-addr 127.0.0.1 "
                       f"--master-port {a.master_port} -m ironpangu_b200.runtime.engine_worker" + worker.split("engine_worker", 1)[1])
-        return ["--spawn", worker, *common]
+        return ["--spawn", worker, "--accept-seconds", "900", *common]
     if a.mode == "program":
         return ["--program", a.bundle, a.checkpoint, *(["--cpu"] if a.cpu else ["--gpus", str(a.gpus)]), *common]
     raise SystemExit(f"unknown mode {a.mode}")
