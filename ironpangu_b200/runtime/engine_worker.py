@@ -72,13 +72,17 @@ class BatchEngine:
     TOPK_CAP = 64   # candidates the sampling kernel keeps per row
 
     def __init__(self, decoder, model_name: str, context: int, vocab: int, eos: int = -1, greedy_only: bool = False,
-                 prefix_slots: int = 0, prefill=None, token_budget: int = 0):
+                 prefix_slots: int = 0, prefill=None, token_budget: int = 0, use_graphs: bool = True):
         """``prefill``: optional tensor-core chunk executor (``forward(tokens, pos0, slot)``, attribute ``M`` = rows per call);
         prompt slices longer than one decode launch group run through it, and the engine advertises ``M`` as its token budget."""
         self.dec, self.name, self.context, self.eos, self.vocab = decoder, model_name, context, eos, vocab
         self.residents = decoder.num_slots
         self.rows = decoder.T
         self.prefill = prefill
+        # one CUDA graph per launch-group width: a decoder step is a few hundred launches, which cost more host time through
+        # Python than the kernels take on the device
+        self.use_graphs = use_graphs and hasattr(decoder, "capture")
+        self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         # tokens the scheduler may hand over per step: more than one launch group (``rows``) is fine, they run back to back
         self.budget = max(self.rows, prefill.M if prefill is not None else 0, token_budget)
         self.can_sample = getattr(decoder, "logits", None) is not None
@@ -228,7 +232,7 @@ class BatchEngine:
             d.tokens[:n].copy_(hb[0, :n], non_blocking=True)
             d.positions[:n].copy_(hb[1, :n], non_blocking=True)
             d.slots[:n].copy_(hb[2, :n], non_blocking=True)
-            d.forward(n)
+            self._run_group(n)
             pending += self._emit(part, n)
             self.audit_counters["launch_groups"] += 1
             self.audit_counters["rows"] += n
@@ -244,6 +248,25 @@ class BatchEngine:
         if d.fabric.status() != 0:
             raise RuntimeError(f"kernel status word = {d.fabric.status()}")
         return out
+
+    def _run_group(self, n: int) -> None:
+        """Decoder forward over the ``n`` rows staged in its static input buffers: eager the first time a width is seen
+        (that run also warms the capture), a graph replay afterwards."""
+        d = self.dec
+        if not self.use_graphs:
+            d.forward(n)
+            return
+        g = self._graphs.get(n)
+        if g is not None:
+            g.replay()
+            return
+        d.forward(n)                              # the real run of this step
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):                 # capture only records: it does not execute
+            d.forward(n)
+        self._graphs[n] = g
+        self.audit_counters["graphs_captured"] = len(self._graphs)
 
     def _emit(self, part, n: int, counted: bool = False):
         """Tokens of the sampling rows among the ``n`` rows the decoder just produced (``next_ids`` / ``logits`` rows 0..n-1,
@@ -326,8 +349,14 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
         ddec = G.DenseDecoder(dcfg, dweights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs,
                               keep_logits=not args.greedy_only)
         mark("state", "K/V page caches and step workspace")
-        eng = BatchEngine(ddec, f"ifab-{args.model}", args.max_model_len, dcfg.vocab, eos=-1, greedy_only=args.greedy_only,
-                          token_budget=args.max_num_batched_tokens)
+        dprefill = None
+        if args.prefill_chunk > 8:
+            from ironpangu_b200.models.dense_prefill import DensePrefill
+
+            dprefill = DensePrefill(ddec, max_rows=args.prefill_chunk)
+            mark("prefill", "activation buffers of the matrix-matrix prompt path")
+        eng = BatchEngine(ddec, f"ifab-{args.model}", args.max_model_len, dcfg.vocab, eos=-1, greedy_only=args.greedy_only, prefill=dprefill,
+                          token_budget=args.max_num_batched_tokens, use_graphs=not args.no_graphs)
         mark("sampling", "per-slot sampling state")
         return eng
     cfg = MlaMoeConfig.tiny(args.layers or 2) if args.model == "tiny" else MlaMoeConfig.flagship()
@@ -346,7 +375,8 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
         prefill = MlaMoePrefill(dec, max_rows=args.prefill_chunk)
         mark("prefill", "activation buffers of the matrix-matrix prompt path")
     eng = BatchEngine(dec, f"ifab-{args.model}", args.max_model_len, cfg.vocab, eos=cfg.eos, greedy_only=args.greedy_only,
-                      prefix_slots=args.prefix_cache_slots, prefill=prefill, token_budget=args.max_num_batched_tokens)
+                      prefix_slots=args.prefix_cache_slots, prefill=prefill, token_budget=args.max_num_batched_tokens,
+                      use_graphs=not args.no_graphs)
     mark("sampling", "per-slot sampling state and prefix snapshots")
     return eng
 
@@ -422,6 +452,7 @@ def main() -> None:
     ap.add_argument("--kv-int8", action="store_true", help="packed int8 latent KV cache")
     ap.add_argument("--expert-fp8", action="store_true", help="block-scaled fp8 expert weights (1 x 128 scale blocks)")
     ap.add_argument("--prefill-chunk", type=int, default=0, help="rows per tensor-core prefill call (0 = prompts go through the decode kernels)")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host instead of replaying CUDA graphs")
     ap.add_argument("--greedy-only", action="store_true", help="skip the logits buffer; refuse sampled requests")
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--memory-profile", default="", help="write the staged start-up memory profile (JSON) here")

@@ -203,6 +203,8 @@ def server_args(a) -> List[str]:
                   f"--max-model-len {a.max_model_len} --max-num-batched-tokens {a.max_num_batched_tokens}")
         if a.layers:
             worker += f" --layers {a.layers}"
+        if a.prefill_chunk:
+            worker += f" --prefill-chunk {a.prefill_chunk}"
         if a.kv_int8:
             worker += " --kv-int8"
         if a.prefix_cache_slots:
@@ -228,6 +230,7 @@ def main(argv: Optional[List[str]] = None) -> Dict:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--master-port", type=int, default=29611)
     ap.add_argument("--kv-int8", action="store_true")
+    ap.add_argument("--prefill-chunk", type=int, default=0, help="rows per tensor-core prefill call of the worker (0 = decode kernels)")
     ap.add_argument("--prefix-cache-slots", type=int, default=0)
     ap.add_argument("--max-num-seqs", type=int, default=8)
     ap.add_argument("--max-num-batched-tokens", type=int, default=8)

@@ -125,3 +125,37 @@ def test_sampling_penalties():
     out = K.sample_topk(logits, fab, top_k=8, inv_temperature=invt, counts=counts, penalties=pen)
     assert int(out[0]) == 9
     fab.close()
+
+
+@pytest.mark.gpu
+def test_tensor_core_prefill_matches_the_decode_path_and_the_oracle():
+    """A 150-token prompt through DensePrefill (chunks of 64) leaves the same caches and last-row logits as the decode kernels."""
+    from ironpangu_b200.models import dense_gqa as G
+    from ironpangu_b200.models.dense_prefill import DensePrefill
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    cfg = G.DenseConfig.tiny(2)
+    full = G.random_full_weights(cfg, seed=0)
+    fab = Fabric(0, 1)
+    mk = lambda: G.DenseDecoder(cfg, G.shard_weights(cfg, full, 0, 1, "cuda"), fab, max_tokens=8, max_context=256, keep_logits=True)
+    a, b = mk(), mk()
+    toks = torch.randint(0, cfg.vocab, (150,), generator=torch.Generator().manual_seed(5)).to(torch.int32).cuda()
+    pre = DensePrefill(a, max_rows=64, attn_rows=32)
+    for s in range(0, 150, 64):
+        nxt = pre.forward(toks[s:s + 64], s, 0)
+    for s in range(0, 150, 8):
+        n = min(8, 150 - s)
+        b.tokens[:n].copy_(toks[s:s + n])
+        b.positions[:n].copy_(torch.arange(s, s + n, dtype=torch.int32))
+        b.slots[:n].zero_()
+        b.forward(n)
+    torch.cuda.synchronize()
+    ref = G.forward_ref(cfg, full, toks.long())       # on the device of the tokens
+    torch.testing.assert_close(a.logits[0], ref[149], rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(a.logits[0], b.logits[(150 - 1) % 8], rtol=3e-2, atol=3e-2)
+    for l in range(cfg.layers):
+        torch.testing.assert_close(a.k_cache[l].float(), b.k_cache[l].float(), rtol=3e-2, atol=3e-2)
+    top2 = ref[149].topk(2).values
+    assert int(nxt[0]) == int(ref[149].argmax()) or float(top2[0] - top2[1]) < 5e-2
+    assert fab.status() == 0
+    fab.close()
