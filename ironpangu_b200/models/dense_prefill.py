@@ -59,12 +59,38 @@ class DensePrefill:
         ``slot``; returns the greedy next token after the last row (device tensor ``[1]``; its logits land in row 0 of the
         decoder's logits buffer when that exists)."""
         d, c, fab = self.dec, self.dec.cfg, self.dec.fabric
-        w, st = d.w, fab.desc.status
         m = tokens.numel()
         assert 1 <= m <= self.M
         self.tokens[:m].copy_(tokens)
         self.positions[:m].copy_(torch.arange(pos0, pos0 + m, dtype=torch.int32, device=tokens.device))
         self.slots[:m].fill_(slot)
+        x = self._layers(m)
+        K.lm_head_argmax(x[m - 1:m], d.w["lm_head"], fab, norm_w=d.w["final_norm"], eps=c.eps, vocab_offset=d.rank * d.vl,
+                         partial=d.partial, logits=None if d.logits is None else d.logits[:1], out_ids=d.next_ids[:1],
+                         out_vals=d.next_vals[:1])
+        self.launches += 1
+        return d.next_ids[:1]
+
+    def forward_rows(self, tokens: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, select: torch.Tensor) -> torch.Tensor:
+        """Batched step over ``m`` independent rows (each with its own position and sequence slot, e.g. one decode row per
+        running sequence): the layers run as matrix-matrix work, then the vocabulary shard of the logits of rows ``select``
+        (int64 indices) comes from one GEMM. Returns f32 logits ``[len(select), vocab_local]``."""
+        d, c = self.dec, self.dec.cfg
+        m = tokens.numel()
+        assert 1 <= m <= self.M
+        self.tokens[:m].copy_(tokens)
+        self.positions[:m].copy_(positions)
+        self.slots[:m].copy_(slots)
+        x = self._layers(m)
+        xs = x.index_select(0, select)
+        xn = K.rmsnorm(xs, d.w["final_norm"], c.eps)
+        self.launches += 2
+        return G.gemm(xn, d.w["lm_head"], out_f32=True, status_ptr=d.fabric.desc.status)
+
+    def _layers(self, m: int) -> torch.Tensor:
+        """Embedding + all layers over the ``m`` rows staged in ``tokens / positions / slots``; returns the hidden rows."""
+        d, c, fab = self.dec, self.dec.cfg, self.dec.fabric
+        w, st = d.w, fab.desc.status
         tok, pos, sl = self.tokens[:m], self.positions[:m], self.slots[:m]
         x, h = self.x[:m], self.h[:m]
         K.embedding(tok, w["embed"], out=x, status_ptr=st)
@@ -91,8 +117,5 @@ class DensePrefill:
                 G.gemm_allreduce(self.act[:m], w[p + "down"], fab, self._sym_rows(m), residual=x)
             else:
                 G.gemm(self.act[:m], w[p + "down"], residual=x, out=x, status_ptr=st)
-        K.lm_head_argmax(x[m - 1:m], w["lm_head"], fab, norm_w=w["final_norm"], eps=c.eps, vocab_offset=d.rank * d.vl,
-                         partial=d.partial, logits=None if d.logits is None else d.logits[:1], out_ids=d.next_ids[:1],
-                         out_vals=d.next_vals[:1])
-        self.launches = 2 + c.layers * (8 + 2 * ((m + self.QC - 1) // self.QC))
-        return d.next_ids[:1]
+        self.launches = 1 + c.layers * (8 + 2 * ((m + self.QC - 1) // self.QC))
+        return x

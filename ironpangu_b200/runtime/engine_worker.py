@@ -221,6 +221,12 @@ class BatchEngine:
             if sample:
                 d.slots[:1].fill_(resident)
                 pending += self._emit([(toks[-1], position + len(toks) - 1, resident, i)], 1, counted=True)
+        batched = (self.prefill is not None and hasattr(self.prefill, "forward_rows") and self.can_sample and len(rows) > self.rows)
+        if batched:
+            # more rows than one decode launch group: all of them as one matrix-matrix pass per `M` rows
+            for r0 in range(0, len(rows), self.prefill.M):
+                pending += self._run_rows_batched(rows[r0:r0 + self.prefill.M])
+            rows = []
         for r0 in range(0, len(rows), self.rows):
             part = rows[r0:r0 + self.rows]
             n = len(part)
@@ -247,6 +253,46 @@ class BatchEngine:
         self.audit_counters["steps"] += 1
         if d.fabric.status() != 0:
             raise RuntimeError(f"kernel status word = {d.fabric.status()}")
+        return out
+
+    def _run_rows_batched(self, part):
+        """Rows of many sequences (one decode row each, short prompt pieces) through the matrix-matrix path of the prefill
+        executor; the sampling rows get their logits from one GEMM and their tokens from the sampling kernel (greedy rows as
+        a draw at vanishing temperature). Returns ``[(slice indices, device ids)]`` like :meth:`_emit`."""
+        from ..ops import decode as K
+
+        d, n = self.dec, len(part)
+        host = torch.tensor([[r[0] for r in part], [r[1] for r in part], [r[2] for r in part]], dtype=torch.int32).pin_memory()
+        dev = host.to(d.tokens.device, non_blocking=True)
+        pick = [j for j, r in enumerate(part) if r[3] >= 0]
+        sel = torch.tensor(pick or [n - 1], device=dev.device)
+        logits = self.prefill.forward_rows(dev[0], dev[1], dev[2], sel)
+        slots = dev[2].long()
+        local = dev[0].long() - self.vocab_offset
+        ok = (local >= 0) & (local < self.counts.shape[1])
+        self.counts[slots[ok], local[ok]] += 1
+        self.audit_counters["launch_groups"] += 1
+        self.audit_counters["rows"] += n
+        self.audit_counters["batched_rows"] = self.audit_counters.get("batched_rows", 0) + n
+        self.audit_counters["h2d_bytes"] += 12 * n
+        if not pick:
+            return []
+        out = []
+        for c0 in range(0, len(pick), 64):            # the sampling kernel takes up to 64 rows a call
+            sub = pick[c0:c0 + 64]
+            rs = slots[sel[c0:c0 + 64]]
+            greedy = torch.tensor([self.sampling[part[j][2]].get("greedy", True) for j in sub], device=dev.device)
+            inv_t = torch.where(greedy, torch.full_like(self.inv_temp[rs], 1e4), self.inv_temp[rs]).contiguous()
+            top_p = torch.where(greedy, torch.ones_like(self.top_p[rs]), self.top_p[rs]).contiguous()
+            min_p = torch.where(greedy, torch.zeros_like(self.min_p[rs]), self.min_p[rs]).contiguous()
+            ks = [self.sampling[part[j][2]]["top_k"] or self.TOPK_CAP for j in sub if not self.sampling[part[j][2]].get("greedy", True)]
+            counters = self.counters[rs].contiguous()
+            ids = K.sample_topk(logits[c0:c0 + 64].contiguous(), d.fabric, top_k=max(ks) if ks else 1, inv_temperature=inv_t, top_p=top_p,
+                                min_p=min_p, counts=self.counts[rs].contiguous(), penalties=self.pen[rs].contiguous(),
+                                seeds=self.seeds[rs].contiguous(), counters=counters, vocab_offset=self.vocab_offset)
+            self.counters[rs] = counters
+            self.audit_counters["sampled_rows"] += sum(1 for j in sub if not self.sampling[part[j][2]].get("greedy", True))
+            out.append(([part[j][3] for j in sub], ids))
         return out
 
     def _run_group(self, n: int) -> None:

@@ -324,3 +324,34 @@ def test_gpu_engine_prefills_long_prompts_on_the_tensor_cores():
         finally:
             s.close()
     assert outs[0][0] == outs[1][0]
+
+
+@pytest.mark.gpu
+def test_gpu_dense_worker_batches_decode_rows_on_the_tensor_cores():
+    """Dense model behind the server with a tensor-core prompt path: many concurrent sampled requests complete, and the
+    decode rows of a step run as one matrix-matrix pass (audit counter)."""
+    from ironpangu_b200.utils import bench_serving
+
+    res = bench_serving.main(["--mode", "worker", "--model", "dense-tiny", "--requests", "12", "--max-model-len", "256", "--vocab", "1024",
+                              "--prompt-len", "20,90", "--output-len", "6,14", "--max-num-seqs", "12", "--max-num-batched-tokens", "96",
+                              "--prefill-chunk", "64", "--temperature", "0.8", "--top-k", "20", "--timeout", "300"])
+    assert res["completed"] == 12 and res["server_exit"] == 0, res
+    assert res["output_tokens"] >= 72
+
+    cmd = (f"{sys.executable} -m ironpangu_b200.runtime.engine_worker --model dense-tiny --max-num-seqs 4 --max-model-len 256 "
+           "--max-num-batched-tokens 64 --prefill-chunk 32")
+    s = Server("--spawn", cmd, "--accept-seconds", "300", timeout=400)
+    try:
+        prompt = [(5 * i + 1) % 1000 for i in range(70)]
+        outs = [None] * 3
+        def go(i):
+            outs[i] = s.post("/inference/v1/generate", {"token_ids": prompt[: 40 + 10 * i], "sampling_params": {"max_tokens": 8}}, timeout=120)
+        ths = [threading.Thread(target=go, args=(i,)) for i in range(3)]
+        [t.start() for t in ths]
+        [t.join() for t in ths]
+        assert all(o[0] == 200 and len(o[1]["token_ids"]) == 8 for o in outs)
+        st, body = s.request("GET", "/audit")
+        a = json.loads(body)["engine"]
+        assert st == 200 and a["prefill_chunks"] >= 3 and a["fabric_status"] == 0
+    finally:
+        s.close()
