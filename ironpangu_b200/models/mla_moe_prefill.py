@@ -83,6 +83,33 @@ class MlaMoePrefill:
         self.tokens[:m].copy_(tokens)
         self.positions[:m].copy_(torch.arange(pos0, pos0 + m, dtype=torch.int32, device=tokens.device))
         self.slots[:m].fill_(slot)
+        x = self._layers(m)
+        # greedy token after the last row through the decode head (vocabulary-sharded argmax exchange included)
+        K.lm_head_argmax(x[m - 1:m], w["lm_head"], fab, norm_w=w["final_norm"], eps=c.eps, vocab_offset=d.rank * d.vl,
+                         partial=d.partial, logits=None if d.logits is None else d.logits[:1], out_ids=d.next_ids[:1],
+                         out_vals=d.next_vals[:1])
+        self.launches += 1
+        return d.next_ids[:1]
+
+    def forward_rows(self, tokens: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, select: torch.Tensor) -> torch.Tensor:
+        """Batched step over ``m`` independent rows (own position and sequence slot per row, e.g. one decode row per running
+        sequence): attention per row over its own cache pages, the experts through the device-side dispatch and the grouped
+        GEMM, then the vocabulary shard of the logits of rows ``select`` (int64 indices) from one GEMM (f32 ``[k, vocab_local]``)."""
+        d, c = self.dec, self.dec.cfg
+        m = tokens.numel()
+        assert 1 <= m <= self.M
+        self.tokens[:m].copy_(tokens)
+        self.positions[:m].copy_(positions)
+        self.slots[:m].copy_(slots)
+        x = self._layers(m)
+        xn = K.rmsnorm(x.index_select(0, select), d.w["final_norm"], c.eps)
+        self.launches += 2
+        return G.gemm(xn, d.w["lm_head"], out_f32=True, status_ptr=d.fabric.desc.status)
+
+    def _layers(self, m: int) -> torch.Tensor:
+        """Embedding + all layers over the ``m`` rows staged in ``tokens / positions / slots``; returns the hidden rows."""
+        d, c, fab = self.dec, self.dec.cfg, self.dec.fabric
+        w, st, hl = d.w, fab.desc.status, d.hl
         tok, pos, sl = self.tokens[:m], self.positions[:m], self.slots[:m]
         x, h = self.x[:m], self.h[:m]
         n_launch = 0
@@ -131,12 +158,8 @@ class MlaMoePrefill:
             else:
                 P.moe_combine(self.y, self.route, self.wts[:m], shared=self.sd[:m], residual=x, out=x)
             n_launch += 17 + 2 * hl + 2 * ((m + self.QC - 1) // self.QC)
-        # greedy token after the last row through the decode head (vocabulary-sharded argmax exchange included)
-        K.lm_head_argmax(x[m - 1:m], w["lm_head"], fab, norm_w=w["final_norm"], eps=c.eps, vocab_offset=d.rank * d.vl,
-                         partial=d.partial, logits=None if d.logits is None else d.logits[:1], out_ids=d.next_ids[:1],
-                         out_vals=d.next_vals[:1])
-        self.launches = n_launch + 2
-        return d.next_ids[:1]
+        self.launches = n_launch + 1
+        return x
 
     def _sym_rows(self, m: int):
         """The symmetric activation buffer restricted to ``m`` rows (same peer pointers, smaller shape)."""

@@ -135,3 +135,44 @@ def test_prefill_matches_oracle_and_decode_continues(m, window):
         torch.testing.assert_close(dec.logits[0], ref[i], rtol=3e-2, atol=3e-2)
     assert fab.status() == 0
     fab.close()
+
+
+def test_forward_rows_matches_the_decode_kernels_on_independent_sequences():
+    """One decode row per sequence (three sequences at different positions) through the matrix-matrix path against the
+    decode kernels: same logits, same cache rows."""
+    from ironpangu_b200.models.mla_moe import MlaMoeConfig, MlaMoeDecoder, random_full_weights, shard_weights
+    from ironpangu_b200.models.mla_moe_prefill import MlaMoePrefill
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    cfg = MlaMoeConfig.tiny(2)
+    full = random_full_weights(cfg, seed=0)
+    fab = Fabric(0, 1)
+    mk = lambda: MlaMoeDecoder(cfg, shard_weights(cfg, full, 0, 1, "cuda"), fab, max_tokens=8, max_context=128, num_slots=3,
+                               keep_logits=True, fused_head=False)
+    a, b = mk(), mk()
+    g = torch.Generator().manual_seed(11)
+    lens = [37, 5, 64]
+    for dec in (a, b):
+        for slot, n in enumerate(lens):
+            toks = torch.randint(0, cfg.vocab, (n,), generator=torch.Generator().manual_seed(slot)).to(torch.int32)
+            for s in range(0, n, 8):
+                k = min(8, n - s)
+                dec.tokens[:k].copy_(toks[s:s + k])
+                dec.positions[:k].copy_(torch.arange(s, s + k, dtype=torch.int32))
+                dec.slots[:k].fill_(slot)
+                dec.forward(k)
+    step = torch.randint(0, cfg.vocab, (3,), generator=g).to(torch.int32).cuda()
+    pos = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    slots = torch.arange(3, dtype=torch.int32, device="cuda")
+    pre = MlaMoePrefill(a, max_rows=64, attn_rows=16)
+    got = pre.forward_rows(step, pos, slots, torch.tensor([0, 2], device="cuda"))
+    b.tokens[:3].copy_(step)
+    b.positions[:3].copy_(pos)
+    b.slots[:3].copy_(slots)
+    b.forward(3)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(got, b.logits[:3][[0, 2]], rtol=3e-2, atol=3e-2)
+    for l in range(cfg.layers):
+        torch.testing.assert_close(a.caches[l].float(), b.caches[l].float(), rtol=2e-2, atol=2e-2)
+    assert fab.status() == 0
+    fab.close()
