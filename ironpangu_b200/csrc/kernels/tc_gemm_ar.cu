@@ -49,8 +49,22 @@ struct ArParams {
   FabricView fv;
   uint64_t* seq; uint32_t* done;
   int tiles_n, ntiles;
+  // reduce-scatter mode: rank r owns the row block [r * rows_per_rank, (r + 1) * rows_per_rank) and keeps the finished rows
+  // in its own [rows_per_rank, N] shard (out_peers[rank], residual addressed shard-relative); nothing is gathered
+  int scatter, rows_per_rank, tiles_per_rank;
   uint32_t spin_limit;
 };
+
+// owner of a tile and the index of the tile among its owner's tiles
+__device__ __forceinline__ int owner_of(const ArParams& a, int tile, int* local) {
+  if (!a.scatter) {
+    *local = tile / a.fv.world;
+    return tile % a.fv.world;
+  }
+  const int o = min(tile / a.tiles_per_rank, a.fv.world - 1);
+  *local = tile - o * a.tiles_per_rank;
+  return o;
+}
 
 // barrier 1 over the 128 epilogue threads that also ANDs a predicate, so that every warp takes the same branch
 __device__ __forceinline__ bool epilogue_all(bool pred) {
@@ -62,8 +76,17 @@ __device__ __forceinline__ bool epilogue_all(bool pred) {
 }
 
 // schedule position -> tile: the tiles of the other owners in increasing index, then this rank's own tiles
-__device__ __forceinline__ int tile_at(int pos, int ntiles, int world, int rank) {
+__device__ __forceinline__ int tile_at(const ArParams& a, int pos) {
+  const int ntiles = a.ntiles, world = a.fv.world, rank = a.fv.rank;
   if (world == 1) return pos;
+  if (a.scatter) {
+    // row-block ownership: the other owners in ring order starting at rank + 1 (so that at any moment every GPU receives
+    // from one sender), each owner's tiles in index order, then this rank's own block
+    const int own = a.tiles_per_rank, foreign = ntiles - own;
+    if (pos >= foreign) return rank * own + (pos - foreign);
+    const int j = pos / own;
+    return ((rank + 1 + j) % world) * own + pos % own;
+  }
   const int owned = (ntiles - rank + world - 1) / world, foreign = ntiles - owned;
   if (pos < foreign) {
     const int g = pos / (world - 1), i = pos % (world - 1);
@@ -120,7 +143,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
     // ---- TMA producer: one continuous ring of stages over all tiles of this CTA ----
     int it = 0, issued = 0;
     for (int i = 0; i < my_tiles && !*abort_flag; ++i) {
-      const int tile = tile_at(blockIdx.x + i * gridDim.x, a.ntiles, world, rank);
+      const int tile = tile_at(a, blockIdx.x + i * gridDim.x);
       const int m0 = (tile / a.tiles_n) * BM, n0 = (tile % a.tiles_n) * AR_BN;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % AR_STAGES;
@@ -168,11 +191,22 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
   } else if (warp >= 2) {
     // ---- epilogue warps: exchange tile i while the main loop of tile i + 1 runs ----
     const int q = warp & 3, trow = q * 32 + lane, et = threadIdx.x - 64;
+    if (a.scatter && epoch > 2) {
+      // Reduce-scatter calls do not end with a gather, so nothing else keeps a fast rank from running two calls ahead and
+      // overwriting staging slots (same parity half) that a slow owner is still reducing: wait until every peer has
+      // finished the call that last used this half.
+      if (et < world && et != rank &&
+          !wait_flag_bounded(flags(rank) + (size_t)a.fv.flag_half_words - world + et, epoch - 2, a.fv.spin_limit))
+        atomicOr(a.fv.status, IFAB_STATUS_PEER_TIMEOUT);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     for (int i = 0; i < my_tiles; ++i) {
       const int acc = i & 1, use = i >> 1;
-      const int tile = tile_at(blockIdx.x + i * gridDim.x, a.ntiles, world, rank);
+      const int tile = tile_at(a, blockIdx.x + i * gridDim.x);
       const int m0 = (tile / a.tiles_n) * BM, n0 = (tile % a.tiles_n) * AR_BN;
-      const int owner = tile % world;
+      int local_idx;
+      const int owner = owner_of(a, tile, &local_idx);
+      const int out_row0 = a.scatter ? m0 - rank * a.rows_per_rank : m0;   // first row of the tile in the local output / residual
       const bool ok = epilogue_all(mbar_wait(&acc_full[acc], use & 1, a.spin_limit) && !*abort_flag);
       tc_fence_after();
       if (!ok) {
@@ -197,8 +231,8 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
         asm volatile("bar.sync 1, 128;" ::: "memory");
         good = s_flag_ok != 0;
       }
-      bf16* push_dst = reinterpret_cast<bf16*>(half(owner) + ((size_t)(tile / world) * world + rank) * AR_TILE_BYTES);
-      const bf16* stage = reinterpret_cast<const bf16*>(half(rank) + (size_t)(tile / world) * world * AR_TILE_BYTES);
+      bf16* push_dst = reinterpret_cast<bf16*>(half(owner) + ((size_t)local_idx * world + rank) * AR_TILE_BYTES);
+      const bf16* stage = reinterpret_cast<const bf16*>(half(rank) + (size_t)local_idx * world * AR_TILE_BYTES);
 #pragma unroll 1
       for (int qc = 0; qc < AR_BN; qc += AR_QN) {
         // the previous pass's bulk copies have finished READING the buffer
@@ -235,7 +269,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
             for (int g = 0; g < G; ++g) {
               const int j = et + 128 * g, r = j / CPQ, c = j % CPQ;
               const bool in = m0 + r < a.M && n0 + qc + c * 8 < a.N;
-              res[g] = (a.residual && in) ? *reinterpret_cast<const uint4*>(a.residual + (long)(m0 + r) * a.ldr + n0 + qc + c * 8) : make_uint4(0, 0, 0, 0);
+              res[g] = (a.residual && in) ? *reinterpret_cast<const uint4*>(a.residual + (long)(out_row0 + r) * a.ldr + n0 + qc + c * 8) : make_uint4(0, 0, 0, 0);
             }
             float v[G][8];
 #pragma unroll
@@ -274,8 +308,12 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
           fence_proxy_async_smem();
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (good && m0 + et < a.M && ncols > 0) {
-            for (int dst = 0; dst < world; ++dst)
-              bulk_store(a.out_peers[dst] + (long)(m0 + et) * a.ldc + n0 + qc, tile_s + (size_t)et * AR_ROW_PAD, (uint32_t)ncols * 2);
+            if (a.scatter) {
+              bulk_store(a.out_peers[rank] + (long)(out_row0 + et) * a.ldc + n0 + qc, tile_s + (size_t)et * AR_ROW_PAD, (uint32_t)ncols * 2);
+            } else {
+              for (int dst = 0; dst < world; ++dst)
+                bulk_store(a.out_peers[dst] + (long)(m0 + et) * a.ldc + n0 + qc, tile_s + (size_t)et * AR_ROW_PAD, (uint32_t)ncols * 2);
+            }
           }
           bulk_commit();
         }
@@ -289,7 +327,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
           __threadfence_system();
           if (pusher) {
             st_release_sys(flags(owner) + (size_t)tile * world + rank, epoch);
-          } else {
+          } else if (!a.scatter) {
             for (int dst = 0; dst < world; ++dst)
               if (dst != rank) st_release_sys(flags(dst) + (size_t)a.ntiles * world + tile, epoch);
           }
@@ -310,13 +348,18 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
   }
   __syncthreads();
   if (!s_last) return;
-  if (world > 1) {
+  if (world > 1 && !a.scatter) {
     for (int t = threadIdx.x; t < a.ntiles; t += blockDim.x) {
       if (t % world == rank) continue;
       if (!wait_flag_bounded(flags(rank) + (size_t)a.ntiles * world + t, epoch, a.fv.spin_limit)) atomicOr(a.fv.status, IFAB_STATUS_PEER_TIMEOUT);
     }
   }
   __syncthreads();
+  // "this rank has finished call `epoch`" (it no longer reads the staging slots of this parity half), for the guard above
+  if (world > 1 && (int)threadIdx.x < world && (int)threadIdx.x != rank) {
+    __threadfence_system();
+    st_release_sys(flags(threadIdx.x) + (size_t)a.fv.flag_half_words - world + rank, epoch);
+  }
   if (threadIdx.x == 0) {
     *a.done = 0;
     *a.seq = epoch;
@@ -330,9 +373,9 @@ int launch_ar(const CUtensorMap& ta, const CUtensorMap& tb, ArParams& a, cudaStr
   a.tiles_n = (a.N + AR_BN - 1) / AR_BN;
   a.ntiles = a.tiles_n * ((a.M + BM - 1) / BM);
   if (a.fv.world > 1) {
-    const size_t owned = (a.ntiles + a.fv.world - 1) / a.fv.world;
+    const size_t owned = a.scatter ? (size_t)a.tiles_per_rank : (size_t)(a.ntiles + a.fv.world - 1) / a.fv.world;
     if (owned * a.fv.world * AR_TILE_BYTES > a.fv.data_half_bytes) return -3;
-    if ((size_t)a.ntiles * (a.fv.world + 1) > a.fv.flag_half_words) return -4;
+    if ((size_t)a.ntiles * (a.fv.world + 1) + a.fv.world > a.fv.flag_half_words) return -4;
   }
   static int sms = 0;
   if (sms == 0) {
@@ -365,9 +408,38 @@ extern "C" int ifab_gemm_allreduce_bf16(const void* a, long lda, const void* b, 
   p.residual = (const bf16*)residual;
   p.ldr = ldr;
   p.M = M; p.N = N; p.K = K;
+  p.scatter = 0; p.rows_per_rank = 0; p.tiles_per_rank = 0;
   p.seq = fab->seq;
   p.done = fab->done;
   p.spin_limit = 4000000u;
   cudaStream_t s = (cudaStream_t)stream;
   return launch_ar(ta, tb, p, s);
+}
+
+// Reduce-scatter form: rank r ends with rows [r * M / world, (r + 1) * M / world) of sum_ranks A_r B_r^T (+ residual) in its
+// own `out` shard [M / world, N] (row stride ldc); `residual` is the matching [M / world, N] shard. M / world must be a
+// multiple of 128. Same staging / flag protocol as the all-reduce form; no gather, no final flags.
+extern "C" int ifab_gemm_reduce_scatter_bf16(const void* a, long lda, const void* b, long ldb, void* out, long ldc, const void* residual,
+                                             long ldr, int M, int N, int K, const IfabFabric* fab, void* stream) {
+  if (M < 1 || N < 1 || K < 8 || K % 8 || lda % 8 || ldb % 8 || ldc % 8 || N % 8 || (residual && ldr % 8)) return -1;
+  if (M % fab->world || (fab->world > 1 && (M / fab->world) % BM)) return -1;
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_bf16_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)AR_BN)) return rc;
+  ArParams p;
+  if (int rc = fabric_view(fab, &p.fv)) return rc;
+  for (int r = 0; r < IFAB_MAX_RANKS; ++r) p.out_peers[r] = nullptr;
+  if (out == nullptr || (reinterpret_cast<uintptr_t>(out) & 15)) return -1;
+  p.out_peers[fab->rank] = (bf16*)out;
+  p.ldc = ldc;
+  p.residual = (const bf16*)residual;
+  p.ldr = ldr;
+  p.M = M; p.N = N; p.K = K;
+  p.scatter = fab->world > 1 ? 1 : 0;
+  p.rows_per_rank = M / fab->world;
+  p.tiles_per_rank = ((M / fab->world + BM - 1) / BM) * ((N + AR_BN - 1) / AR_BN);
+  p.seq = fab->seq;
+  p.done = fab->done;
+  p.spin_limit = 4000000u;
+  return launch_ar(ta, tb, p, (cudaStream_t)stream);
 }

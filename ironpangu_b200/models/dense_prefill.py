@@ -22,6 +22,10 @@ from .dense_gqa import BF16, DenseDecoder
 
 
 class DensePrefill:
+    # steps with more rows than this go through `forward_rows`: past two rows the CUDA-core GEMV kernels are FMA-bound
+    # (4.9 ms per 8-row pass of the 2B model), the GEMM path streams the weights at tensor-core speed whatever the row count
+    batch_threshold = 2
+
     def __init__(self, dec: DenseDecoder, max_rows: int = 512, attn_rows: int = 64):
         self.dec, self.M, self.QC = dec, max_rows, attn_rows
         c, fab, dev = dec.cfg, dec.fabric, dec.fabric.device

@@ -31,6 +31,10 @@ from .mla_moe import BF16, MlaMoeDecoder
 
 
 class MlaMoePrefill:
+    # steps with more rows than this go through `forward_rows` (the path launches ~100 kernels per layer, so it only pays
+    # beyond one decode launch group)
+    batch_threshold = 8
+
     def __init__(self, dec: MlaMoeDecoder, max_rows: int = 512, attn_rows: int = 64):
         self.dec, self.M, self.QC = dec, max_rows, attn_rows
         c, dev, fab = dec.cfg, dec.fabric.device, dec.fabric

@@ -47,6 +47,27 @@ def gemm_allreduce(a: torch.Tensor, b: torch.Tensor, fabric, out, *, residual: O
     return y
 
 
+def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, fabric, out: Optional[torch.Tensor] = None, *,
+                        residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-parallel GEMM fused with a reduce-scatter over NVLink peer memory: rank ``r`` ends with rows
+    ``[r * M / world, (r + 1) * M / world)`` of ``sum_ranks A_r @ B_r.T (+ residual)`` in ``out`` ``[M / world, N]``
+    (``residual`` is the matching row shard). ``M / world`` must be a multiple of 128 when ``world > 1``. The sequence-parallel
+    counterpart of :func:`gemm_allreduce`; together with :func:`allgather_gemm` it brackets a tensor-parallel block whose
+    activations stay sharded by rows."""
+    import ctypes as C
+    M, K = a.shape
+    N = b.shape[0]
+    rows = M // fabric.world
+    if out is None:
+        out = torch.empty(rows, N, dtype=BF16, device=a.device)
+    assert out.shape == (rows, N) and out.dtype == BF16 and out.stride(1) == 1
+    check(_lib.load().ifab_gemm_reduce_scatter_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0),
+                                                    None if residual is None else residual.data_ptr(),
+                                                    0 if residual is None else residual.stride(0), M, N, K, C.byref(fabric.desc),
+                                                    torch.cuda.current_stream().cuda_stream), "gemm_reduce_scatter")
+    return out
+
+
 class AllGatherGemmState:
     """Per-shape scratch of :func:`allgather_gemm`: flags (symmetric), the local staging matrix and its tile counters."""
 

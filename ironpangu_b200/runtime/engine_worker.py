@@ -221,7 +221,8 @@ class BatchEngine:
             if sample:
                 d.slots[:1].fill_(resident)
                 pending += self._emit([(toks[-1], position + len(toks) - 1, resident, i)], 1, counted=True)
-        batched = (self.prefill is not None and hasattr(self.prefill, "forward_rows") and self.can_sample and len(rows) > self.rows)
+        batched = (self.prefill is not None and hasattr(self.prefill, "forward_rows") and self.can_sample and
+                   len(rows) > getattr(self.prefill, "batch_threshold", self.rows))
         if batched:
             # more rows than one decode launch group: all of them as one matrix-matrix pass per `M` rows
             for r0 in range(0, len(rows), self.prefill.M):

@@ -15,12 +15,12 @@ def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
-    from ironpangu_b200.ops.gemm import gemm_allreduce
+    from ironpangu_b200.ops.gemm import gemm_allreduce, gemm_reduce_scatter
     from ironpangu_b200.parallel.fabric import Fabric
 
     fab = Fabric(rank, world, data_half_bytes=80 << 20, flag_half_words=16384, spin_limit=4_000_000)
     g = torch.Generator(device="cuda").manual_seed(9)
-    for M, N, Kl in [(128, 256, 64), (512, 1024, 256), (300, 520, 128), (2048, 4096, 512)]:
+    for M, N, Kl in [(128, 256, 64), (512, 1024, 256), (300, 520, 128), (2048, 4096, 512), (1024, 776, 192)]:
         a = torch.randn(M, Kl * world, generator=g, device="cuda").to(BF16)
         b = (torch.randn(N, Kl * world, generator=g, device="cuda") * 0.05).to(BF16)
         res = torch.randn(M, N, generator=g, device="cuda").to(BF16)
@@ -38,6 +38,16 @@ def main():
         ys = [torch.empty_like(y) for _ in range(world)]
         dist.all_gather(ys, y)
         assert all(torch.equal(ys[0], t) for t in ys), "ranks hold different results"
+        if M % (128 * world) == 0:
+            # reduce-scatter form: every rank keeps its own row block (three calls: parity halves and the run-ahead guard)
+            rows = M // world
+            shard_res = res[rank * rows:(rank + 1) * rows].contiguous()
+            for _ in range(3):
+                ysh = gemm_reduce_scatter(al, bl, fab, residual=shard_res)
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.testing.assert_close(ysh.float(), ref[rank * rows:(rank + 1) * rows], rtol=2e-2, atol=3e-2)
+            assert torch.equal(ysh, y[rank * rows:(rank + 1) * rows]), "reduce-scatter and all-reduce forms disagree"
     assert fab.status() == 0
     print(f"rank {rank}: ok gemm_allreduce bulk", flush=True)
 
