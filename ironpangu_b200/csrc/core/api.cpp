@@ -1,3 +1,4 @@
+#include "chat_parse.h"
 #include "api.h"
 
 #include <chrono>
@@ -107,6 +108,8 @@ std::vector<uint32_t> Api::prompt_of(const Json& body, bool chat) const {
     const Json& msgs = body.at("messages");
     if (!msgs.is_array() || msgs.size() == 0) invalid("'messages' must be a non-empty array");
     std::string text;
+    if (const Json* tools = body.find("tools"); tools && !tools->is_null() && tools->size() > 0)
+      text += "<|system|>\n" + chat::render_tools(*tools) + "\n";
     for (const auto& m : msgs.as_array()) {
       const Json& content = m.at("content");
       std::string c;
@@ -263,7 +266,17 @@ void Api::completions(const http::Request& req, http::ResponseWriter& w, bool ch
   }
   text += ts.flush();
   if (fin == sched::Finish::Error) return send_error(w, Error(ErrorKind::Backend, error.empty() ? "generation failed" : error));
-  Json j = envelope(choice(text, Json(finish_reason(fin)), true));
+  Json one = choice(text, Json(finish_reason(fin)), true);
+  if (chat) {
+    // reasoning sections and tool calls leave the content; a request may switch either parser off
+    bool want_reasoning = true, want_tools = body.find("tools") != nullptr;
+    if (const Json* k = body.find("chat_template_kwargs"); k && k->is_object())
+      if (const Json* t = k->find("parse_reasoning"); t && !t->is_null()) want_reasoning = t->as_bool();
+    const chat::Parsed parsed = chat::parse_assistant(text, want_reasoning, want_tools);
+    one.set("message", chat::message_json(parsed, id));
+    if (!parsed.tool_calls.empty() && fin != sched::Finish::Length) one.set("finish_reason", "tool_calls");
+  }
+  Json j = envelope(std::move(one));
   Json usage = Json::object();
   usage.set("prompt_tokens", (int64_t)prompt_tokens);
   usage.set("completion_tokens", (int64_t)completion_tokens);

@@ -3,6 +3,7 @@
 #include <functional>
 #include <iostream>
 
+#include "chat_parse.h"
 #include "contract.h"
 #include "cpu_plan.h"
 #include "paging.h"
@@ -507,6 +508,37 @@ static void test_contract_validator() {
   { init::Plan b = plans[0]; b.loads[0].dest = 100000; CHECK_THROWS(Invalid, contract::validate_bindings(p, b)); }
 }
 
+// ---- chat post-processing: reasoning sections and tool calls ---------------------------------------------------------
+static void test_chat_parsers() {
+  using namespace ifab::chat;
+  Parsed a = parse_assistant("<think>\nadd the numbers\n</think>\n\nThe sum is 4.");
+  CHECK(a.has_reasoning && a.reasoning == "add the numbers" && a.content == "The sum is 4." && a.tool_calls.empty());
+  Parsed b = parse_assistant("plan first</think>answer");          // the template opened the section in the prompt
+  CHECK(b.has_reasoning && b.reasoning == "plan first" && b.content == "answer");
+  Parsed c = parse_assistant("no sections here");
+  CHECK(!c.has_reasoning && c.content == "no sections here");
+  Parsed d = parse_assistant("Let me look.\n<tool_call>\n{\"name\": \"get_weather\", \"arguments\": {\"city\": \"Oslo\", \"days\": 2}}\n</tool_call>\n"
+                             "<tool_call>{\"name\":\"now\"}</tool_call>");
+  CHECK(d.tool_calls.size() == 2 && d.tool_calls[0].name == "get_weather" && d.tool_calls[1].name == "now" && d.tool_calls[1].arguments == "{}");
+  CHECK(Json::parse(d.tool_calls[0].arguments).at("days").as_int() == 2 && d.content == "Let me look.");
+  Parsed e = parse_assistant("<tool_call>{\"name\": 7}</tool_call> and <tool_call>{broken</tool_call> <tool_call>{\"name\":\"x\"}");
+  CHECK(e.tool_calls.empty() && e.content.find("{broken") != std::string::npos && e.content.find("<tool_call>{\"name\":\"x\"}") != std::string::npos);
+  Parsed f = parse_assistant("<tool_call>{\"name\":\"f\",\"arguments\":\"{\\\"k\\\": 1}\"}</tool_call>");   // arguments as a JSON string
+  CHECK(f.tool_calls.size() == 1 && Json::parse(f.tool_calls[0].arguments).at("k").as_int() == 1);
+  Parsed g = parse_assistant("<think>x</think><tool_call>{\"name\":\"f\"}</tool_call>", false, false);     // both parsers off: verbatim
+  CHECK(!g.has_reasoning && g.tool_calls.empty() && g.content.find("<think>") == 0);
+  Json m = message_json(d, "chatcmpl-9");
+  CHECK(m.at("tool_calls").size() == 2 && m.at("tool_calls").as_array()[0].at("id").as_string() == "chatcmpl-9-call-0");
+  CHECK(m.at("tool_calls").as_array()[0].at("function").at("arguments").is_string() && m.at("content").as_string() == "Let me look.");
+  Json only_calls = message_json(parse_assistant("<tool_call>{\"name\":\"f\"}</tool_call>"), "id");
+  CHECK(only_calls.at("content").is_null());
+  Json tools = Json::parse("[{\"type\":\"function\",\"function\":{\"name\":\"get_weather\",\"parameters\":{\"type\":\"object\"}}}]");
+  const std::string block = render_tools(tools);
+  CHECK(block.find("\"get_weather\"") != std::string::npos && block.find("<tool_call>") != std::string::npos);
+  CHECK_THROWS(Invalid, render_tools(Json::parse("[{\"type\":\"retrieval\"}]")));
+  CHECK_THROWS(Invalid, render_tools(Json::parse("{}")));
+}
+
 int main() {
   std::pair<const char*, std::function<void()>> tests[] = {
       {"serve_batching", test_serve_batching_matches_sequential}, {"serve_admission", test_serve_validation_and_admission},
@@ -514,7 +546,7 @@ int main() {
       {"api_tokenizer", test_api_tokenizer_and_sampling_json}, {"kernel_plugin", test_kernel_plugin_loader},
       {"state_pool", test_state_pool}, {"prefix_index", test_prefix_index}, {"paging", test_paging},
       {"rankplan_runtime", test_rankplan_and_runtime}, {"transfer", test_transfer}, {"scheduler", test_scheduler}, {"cpu_plan", test_cpu_plan},
-      {"contract_validator", test_contract_validator}};
+      {"contract_validator", test_contract_validator}, {"chat_parsers", test_chat_parsers}};
   for (auto& t : tests) {
     int before = failures;
     try {

@@ -107,6 +107,24 @@ def test_audit_route_reports_engine_and_service_counters(mock_server):
     assert st == 200 and a["service"]["requests_finished"] == 1 and a["engine"]["steps"] >= 4 and a["engine"]["rows"] >= 6
 
 
+def test_chat_route_accepts_tools_and_returns_a_parsed_message():
+    mock_server = Server("--mock", "--max-num-seqs", "2", "--max-num-batched-tokens", "64", "--vocab", "300", "--max-model-len", "2048")
+    try:
+        _chat_tools_checks(mock_server)
+    finally:
+        mock_server.close()
+
+
+def _chat_tools_checks(mock_server):
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object", "properties": {"city": {"type": "string"}}}}}]
+    st, r = mock_server.post("/v1/chat/completions", {"messages": [{"role": "user", "content": "weather?"}], "tools": tools, "max_tokens": 6})
+    assert st == 200
+    msg = r["choices"][0]["message"]
+    assert msg["role"] == "assistant" and "content" in msg and r["usage"]["prompt_tokens"] > 200     # the tool block is part of the prompt
+    st, r = mock_server.post("/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "tools": [{"type": "retrieval"}]})
+    assert st == 400 and "function" in r["error"]["message"]
+
+
 def test_errors_are_openai_errors(mock_server):
     s = mock_server
     for body, needle in [({"prompt": "x", "max_tokens": 5000}, "exceeds the context"), ({"prompt": "x", "n": 2}, "'n'"),
