@@ -67,3 +67,11 @@ def test_allgather_fused_into_gemm(world):
         pytest.skip(f"needs {world} GPUs")
     out = _run(world, "ag_gemm_worker.py")
     assert out.count("ok allgather gemm") == world
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_dense_decoder_tensor_parallel_decode_prefill_and_batched_rows(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    out = _run(world, "dense_worker.py")
+    assert out.count("ok dense tensor parallel") == world
