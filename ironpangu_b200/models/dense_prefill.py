@@ -49,6 +49,10 @@ class DensePrefill:
         self.tiles = st.to(dev)
         self.ntiles = torch.zeros(1, dtype=torch.int32, device=dev)
         self.launches = 0
+        # CUDA graphs of the layer stack for small batched steps (one graph per row count): a 64-row decode step is ~250
+        # launches, which cost more host time through Python than device time
+        self.graph_rows_max = 64
+        self._graphs = {}
 
     def _sym_rows(self, m: int):
         if m == self.M:
@@ -85,11 +89,26 @@ class DensePrefill:
         self.tokens[:m].copy_(tokens)
         self.positions[:m].copy_(positions)
         self.slots[:m].copy_(slots)
-        x = self._layers(m)
+        x = self._layers_graphed(m)
         xs = x.index_select(0, select)
         xn = K.rmsnorm(xs, d.w["final_norm"], c.eps)
         self.launches += 2
         return G.gemm(xn, d.w["lm_head"], out_f32=True, status_ptr=d.fabric.desc.status)
+
+    def _layers_graphed(self, m: int) -> torch.Tensor:
+        if m > self.graph_rows_max:
+            return self._layers(m)
+        g = self._graphs.get(m)
+        if g is not None:
+            g.replay()
+            return self.x[:m]
+        x = self._layers(m)                         # the real run of this step (and the warm-up of the capture)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):                   # records only: the caches are not touched a second time
+            self._layers(m)
+        self._graphs[m] = g
+        return x
 
     def _layers(self, m: int) -> torch.Tensor:
         """Embedding + all layers over the ``m`` rows staged in ``tokens / positions / slots``; returns the hidden rows."""

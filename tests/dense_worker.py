@@ -57,6 +57,9 @@ def main():
     b.forward(3)
     torch.cuda.synchronize()
     torch.testing.assert_close(got, b.logits[:3], rtol=3e-2, atol=3e-2)
+    again = pre.forward_rows(step, pos, slots, torch.tensor([0, 1, 2], device="cuda"))      # same rows: replay of the captured graph
+    torch.cuda.synchronize()
+    assert torch.equal(again, got)
     assert fab.status() == 0
     print(f"rank {rank}: ok dense tensor parallel", flush=True)
     fab.close()
