@@ -45,6 +45,7 @@ struct DispatchParams {
   bf16* recv[IFAB_MAX_RANKS]; int2* meta[IFAB_MAX_RANKS]; EpCtl* ctl[IFAB_MAX_RANKS];
   uint32_t* ticket; int32_t* dst_count;      // local scratch: [1], [W]
   uint64_t epoch; uint32_t* status;
+  int smem_routes;                           // routes whose destinations fit the dynamic shared memory of the launch
 };
 
 // grid = any; CTA 0 ranks the routes first (other CTAs wait on a local flag), then all warps copy rows
@@ -55,12 +56,22 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchParams p) {
   const int R = p.M * p.topk;
   __shared__ int s_last;
   if (blockIdx.x == 0) {
-    // stable ranking of the routes inside every destination: warp w handles destinations w, w + 8, ...
+    // stable ranking of the routes inside every destination: warp w handles destinations w, w + 8, ...; the destination of
+    // every route is staged in shared memory first (one coalesced pass), so the ballot scans do not wait on global loads
+    extern __shared__ unsigned char s_dst[];
+    const bool staged = R <= p.smem_routes;
+    if (staged) {
+      for (int i = threadIdx.x; i < R; i += blockDim.x) {
+        const int d = p.ids[i] / p.el;
+        s_dst[i] = (unsigned char)((d >= 0 && d < p.world) ? d : 255);
+      }
+      __syncthreads();
+    }
     for (int dst = warp; dst < p.world; dst += 8) {
       int base = 0;
       for (int i0 = 0; i0 < R; i0 += 32) {
         const int i = i0 + lane;
-        const bool hit = i < R && p.ids[i] / p.el == dst;
+        const bool hit = i < R && (staged ? (int)s_dst[i] == dst : p.ids[i] / p.el == dst);
         const unsigned m = __ballot_sync(0xffffffffu, hit);
         if (hit) p.send_idx[i] = base + __popc(m & ((1u << lane) - 1));
         base += __popc(m);
@@ -92,6 +103,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchParams p) {
     if (dst < 0 || dst >= p.world || idx >= p.cap) continue;
     const bf16* src = p.xn + (long)(i / p.topk) * p.ldxn;
     bf16* out = p.recv[dst] + ((long)p.rank * p.cap + idx) * p.D;
+#pragma unroll 4
     for (int c = lane; c < (p.D >> 3); c += 32) *reinterpret_cast<uint4*>(out + c * 8) = *reinterpret_cast<const uint4*>(src + c * 8);
     if (lane == 0) p.meta[dst][(long)p.rank * p.cap + idx] = make_int2(e - dst * p.el, idx);
   }
@@ -120,6 +132,7 @@ struct PlanParams {
   int32_t* perm;          // [W * cap]: receive-buffer row of sorted row r
   int4* tiles; int32_t* num_tiles; int32_t* total_rows;
   uint64_t epoch; uint32_t spin_limit; uint32_t* status;
+  int smem_rows;          // received rows whose expert ids fit the dynamic shared memory of the launch
 };
 
 // single CTA of 1024 threads
@@ -147,13 +160,23 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(PlanParams p) {
     }
     return;
   }
+  // the local expert of every received row, staged once in shared memory (source-major): the scans below read it twice per
+  // expert and would otherwise wait on a global load per ballot
+  extern __shared__ short s_exp[];
+  const bool staged = p.world * p.cap <= p.smem_rows;
+  if (staged) {
+    for (int src = 0; src < p.world; ++src)
+      for (int i = threadIdx.x; i < s_cnt[src]; i += blockDim.x) s_exp[src * p.cap + i] = (short)__ldcg(&p.meta[(long)src * p.cap + i]).x;
+    __syncthreads();
+  }
+  auto expert_of = [&](int src, int i) -> int { return staged ? (int)s_exp[src * p.cap + i] : __ldcg(&p.meta[(long)src * p.cap + i]).x; };
   // counts per local expert, then stable placement (source-major, then arrival index)
   for (int e = warp; e < p.el; e += 32) {
     int n = 0;
     for (int src = 0; src < p.world; ++src)
       for (int i0 = 0; i0 < s_cnt[src]; i0 += 32) {
         const int i = i0 + lane;
-        const bool hit = i < s_cnt[src] && __ldcg(&p.meta[(long)src * p.cap + i]).x == e;
+        const bool hit = i < s_cnt[src] && expert_of(src, i) == e;
         n += __popc(__ballot_sync(0xffffffffu, hit));
       }
     if (lane == 0) s_count[e] = n;
@@ -178,7 +201,7 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(PlanParams p) {
     for (int src = 0; src < p.world; ++src)
       for (int i0 = 0; i0 < s_cnt[src]; i0 += 32) {
         const int i = i0 + lane;
-        const bool hit = i < s_cnt[src] && __ldcg(&p.meta[(long)src * p.cap + i]).x == e;
+        const bool hit = i < s_cnt[src] && expert_of(src, i) == e;
         const unsigned m = __ballot_sync(0xffffffffu, hit);
         if (hit) p.perm[base + __popc(m & ((1u << lane) - 1))] = src * p.cap + i;
         base += __popc(m);
@@ -216,6 +239,7 @@ __global__ void __launch_bounds__(256) ep_return_kernel(ReturnParams p) {
     const int row = p.perm[r], src = row / p.cap, idx = row % p.cap;
     bf16* out = p.ret[src] + ((long)p.rank * p.cap + idx) * p.D;
     const bf16* in = p.y + (long)r * p.ldy;
+#pragma unroll 4
     for (int c = lane; c < (p.D >> 3); c += 32) *reinterpret_cast<uint4*>(out + c * 8) = *reinterpret_cast<const uint4*>(in + c * 8);
   }
   __threadfence_system();
@@ -239,9 +263,10 @@ struct CombineParams {
   int M, topk, D, el, world, cap;
   const bf16* shared; long lds; const bf16* residual; long ldr; bf16* out; long ldo;
   uint64_t epoch; uint32_t spin_limit; uint32_t* status;
+  int col_splits;
 };
 
-// one warp per token
+// one warp per (token, column range)
 __global__ void __launch_bounds__(256) ep_combine_kernel(CombineParams p) {
   __shared__ int s_ok;
   grid_dep_launch();
@@ -257,23 +282,38 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(CombineParams p) {
   }
   __syncthreads();
   if (!s_ok) return;
-  const int m = blockIdx.x * 8 + warp;
+  // a warp owns one token and one of `p.col_splits` column ranges, so that small batches still fill the GPU
+  const int unit = blockIdx.x * 8 + warp, m = unit / p.col_splits, part = unit % p.col_splits;
   if (m >= p.M) return;
+  const int chunks = p.D >> 3, per = (chunks + p.col_splits - 1) / p.col_splits;
+  const int c_lo = part * per, c_hi = min(chunks, c_lo + per);
   long rows[MAX_TOPK];
   float w[MAX_TOPK];
-  for (int k = 0; k < p.topk; ++k) {
-    const int i = m * p.topk + k, owner = p.ids[i] / p.el, idx = p.send_idx[i];
-    rows[k] = (owner >= 0 && owner < p.world && idx < p.cap) ? (long)owner * p.cap + idx : -1;
-    w[k] = p.wts[i];
-  }
-  for (int c = lane; c < (p.D >> 3); c += 32) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int k = 0; k < p.topk; ++k) {
-      if (rows[k] < 0) continue;
-      float f[8];
-      unpack8(__ldcg(reinterpret_cast<const uint4*>(p.ret + rows[k] * p.D + c * 8)), f);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[k], f[i], acc[i]);
+  for (int k = 0; k < MAX_TOPK; ++k) {
+    rows[k] = -1;
+    w[k] = 0.f;
+    if (k < p.topk) {
+      const int i = m * p.topk + k, owner = p.ids[i] / p.el, idx = p.send_idx[i];
+      rows[k] = (owner >= 0 && owner < p.world && idx < p.cap) ? (long)owner * p.cap + idx : -1;
+      w[k] = p.wts[i];
+    }
+  }
+  for (int c = c_lo + lane; c < c_hi; c += 32) {
+    // all rows of the token are requested before the first one is used
+    uint4 raw[MAX_TOPK];
+#pragma unroll
+    for (int k = 0; k < MAX_TOPK; ++k)
+      raw[k] = (k < p.topk && rows[k] >= 0) ? __ldcg(reinterpret_cast<const uint4*>(p.ret + rows[k] * p.D + c * 8)) : make_uint4(0, 0, 0, 0);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int k = 0; k < MAX_TOPK; ++k) {
+      if (k < p.topk) {
+        float f[8];
+        unpack8(raw[k], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[k], f[i], acc[i]);
+      }
     }
     if (p.shared) {
       float f[8];
@@ -308,15 +348,21 @@ int ifab_ep_dispatch(const void* xn, long ldxn, const int32_t* ids, int M, int t
     p.meta[r] = r < world ? (int2*)meta_peers[r] : nullptr;
     p.ctl[r] = r < world ? (EpCtl*)ctl_peers[r] : nullptr;
   }
-  const int grid = std::max(1, std::min(148, (M * topk + 7) / 8));
-  return launch_chain(ep_dispatch_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p);
+  const int grid = std::max(1, std::min(2 * 148, (M * topk + 7) / 8));
+  const size_t smem = (size_t)std::min(M * topk, 40 * 1024);
+  p.smem_routes = (int)smem;
+  return launch_chain(ep_dispatch_kernel, dim3(grid), dim3(256), smem, (cudaStream_t)stream, p);
 }
 
 int ifab_ep_plan(const void* meta, void* ctl, int world, int cap, int e_local, int32_t* perm, int32_t* tiles, int32_t* num_tiles,
                  int32_t* total_rows, int max_tiles, uint64_t epoch, uint32_t spin_limit, uint32_t* status, void* stream) {
   if (world < 1 || world > IFAB_MAX_RANKS || e_local < 1 || e_local > 256 || max_tiles < 1) return -1;
-  PlanParams p{(const int2*)meta, (EpCtl*)ctl, world, cap, e_local, max_tiles, perm, (int4*)tiles, num_tiles, total_rows, epoch, spin_limit, status};
-  return launch_chain(ep_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, p);
+  PlanParams p{(const int2*)meta, (EpCtl*)ctl, world, cap, e_local, max_tiles, perm, (int4*)tiles, num_tiles, total_rows, epoch, spin_limit, status, 0};
+  const size_t want = (size_t)world * cap * sizeof(short);
+  const size_t smem = want <= 160 * 1024 ? want : 0;
+  p.smem_rows = (int)(smem / sizeof(short));
+  if (int rc = opt_in_smem(ep_plan_kernel, smem)) return rc;
+  return launch_chain(ep_plan_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)stream, p);
 }
 
 int ifab_ep_gather(const void* recv, const int32_t* perm, const int32_t* total_rows, void* xp, long ldxp, int D, int rows_max, void* stream) {
@@ -336,7 +382,7 @@ int ifab_ep_return(const void* y, long ldy, const int32_t* perm, const int32_t* 
     p.ret[r] = r < world ? (bf16*)ret_peers[r] : nullptr;
     p.ctl[r] = r < world ? (EpCtl*)ctl_peers[r] : nullptr;
   }
-  const int grid = std::max(1, std::min(148, (rows_max + 7) / 8));
+  const int grid = std::max(1, std::min(4 * 148, (rows_max + 7) / 8));
   return launch_chain(ep_return_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p);
 }
 
@@ -345,8 +391,12 @@ int ifab_ep_combine(const void* ret, void* ctl, const int32_t* ids, const int32_
                     uint64_t epoch, uint32_t spin_limit, uint32_t* status, void* stream) {
   if (D % 8 || topk > MAX_TOPK || ldo % 8 || world < 1 || world > IFAB_MAX_RANKS) return -1;
   CombineParams p{(const bf16*)ret, (EpCtl*)ctl, ids, send_idx, wts, M, topk, D, e_local, world, cap, (const bf16*)shared, lds,
-                  (const bf16*)residual, ldr, (bf16*)out, ldo, epoch, spin_limit, status};
-  return launch_chain(ep_combine_kernel, dim3((M + 7) / 8), dim3(256), 0, (cudaStream_t)stream, p);
+                  (const bf16*)residual, ldr, (bf16*)out, ldo, epoch, spin_limit, status, 1};
+  // column ranges per token so that at least ~2 CTAs per SM exist; a range keeps at least one 512-byte warp row
+  int splits = 1;
+  while (splits < 8 && (long)M * splits < 8L * 2 * 148 && (D >> 3) / (splits * 2) >= 32) splits *= 2;
+  p.col_splits = splits;
+  return launch_chain(ep_combine_kernel, dim3((M * splits + 7) / 8), dim3(256), 0, (cudaStream_t)stream, p);
 }
 
 }  // extern "C"
