@@ -97,6 +97,45 @@ __device__ __forceinline__ void warp_reduce_scatter(float (&v)[NV], int lane) {
   }
 }
 
+// RMS-normalised rows of x into shared memory in ONE pass when a row fits one 16-byte chunk per thread (K <= 8 * blockDim):
+// every thread keeps its chunk of every row in registers between the sum of squares and the scaling, so the rows are read
+// once and two block barriers suffice. Same arithmetic and rounding as stage_x.
+template <int T>
+__device__ __forceinline__ void stage_q(bf16* xs, const bf16* __restrict__ x, long ldx, int t_total, int K, const bf16* __restrict__ norm_w,
+                                        float eps, float* red) {
+  const int chunks = K >> 3, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
+  if (chunks > (int)blockDim.x) {
+    stage_x<T>(xs, x, ldx, 0, t_total, K, norm_w, eps, false, red);
+    return;
+  }
+  float f[T][8], g[8];
+  const bool has = tid < chunks;
+  if (has) unpack8(*reinterpret_cast<const uint4*>(norm_w + tid * 8), g);
+#pragma unroll
+  for (int t = 0; t < T; ++t) {
+    const uint4 v = (has && t < t_total) ? *reinterpret_cast<const uint4*>(x + (long)t * ldx + tid * 8) : make_uint4(0, 0, 0, 0);
+    unpack8(v, f[t]);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[t][i] * f[t][i];
+    ss = warp_sum(ss);
+    if (lane == 0) red[t * 33 + warp] = ss;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int t = 0; t < T; ++t) {
+    float s = 0.f;
+    for (int w = 0; w < nwarp; ++w) s += red[t * 33 + w];
+    const float inv = rsqrtf(s / (float)K + eps);
+    if (has) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[t][i] = f[t][i] * inv * g[i];
+      *reinterpret_cast<uint4*>(xs + t * K + tid * 8) = pack8(f[t]);
+    }
+  }
+  __syncthreads();
+}
+
 template <int T>
 __global__ void __launch_bounds__(256, (T <= 2 ? 2 : 1)) mla_head_decode_kernel(HeadParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
@@ -142,18 +181,22 @@ __global__ void __launch_bounds__(256, (T <= 2 ? 2 : 1)) mla_head_decode_kernel(
     s_pos[threadIdx.x] = live ? p.positions[threadIdx.x] : -1;
     s_slot[threadIdx.x] = live ? p.slots[threadIdx.x] : -1;
   }
-  stage_x<T>(xs, p.qkv, p.ldqkv, 0, p.T, p.q_lora, p.q_norm, p.eps, false, red);
+  stage_q<T>(xs, p.qkv, p.ldqkv, p.T, p.q_lora, p.q_norm, p.eps, red);
   // Ask for the cache rows this warp will score in step 3 now (L2 prefetch, nine 128-byte lines per row), so that their
-  // HBM latency passes under steps 1 and 2; the page-table reads on the way also warm L1 for step 3.
+  // HBM latency passes under steps 1 and 2. Lane j looks up the j-th key of the warp, so the page-table loads of a warp
+  // are in flight together (one latency, not one per key); they also warm L1 for the lookups of step 3.
   for (int t = 0; t < T; ++t) {
     const int pos = s_pos[t];
     if (pos < 0) continue;
     int first, nctx;
     visible_range(pos, p.window, &first, &nctx);
-    for (int k = gw; k < nctx; k += NW) {
+    for (int k = gw + NW * lane; k < nctx; k += NW * 32) {
       const long r = cache_row_of(first + k, s_slot[t], p.page_table, p.max_pages, p.page_tokens, p.num_pages);
-      if (r >= 0 && lane < (ROW * 2 + 127) / 128)
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.cache + r * ROW) + lane * 128));
+      if (r >= 0) {
+        const char* row = reinterpret_cast<const char*>(p.cache + r * ROW);
+#pragma unroll
+        for (int i = 0; i < (ROW * 2 + 127) / 128; ++i) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + i * 128));
+      }
     }
   }
   if (warp < T && warp < p.T && s_pos[warp] >= 0) {
