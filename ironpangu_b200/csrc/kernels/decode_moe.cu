@@ -298,43 +298,84 @@ __global__ void __launch_bounds__(256) moe_down_allreduce_kernel(DownParams p) {
       float total[R];
 #pragma unroll
       for (int r = 0; r < R; ++r) total[r] = 0.f;
-      const int chunks = s_cbeg[n_routes];
-      // all routed experts span cpr chunks; only a trailing shared-expert shard may differ
-      const int cpr = p.F >> 3;
-      const int n_exp_chunks = (n_routes > 0 && s_slot[n_routes - 1] == p.topk) ? s_cbeg[n_routes - 1] : chunks;
-      constexpr int U = 16 / R;
-      for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
-        uint4 wv[U][R];
-        int route[U], cc[U];
+      constexpr int MAXC = 6;   // 16-byte chunks per lane and route the per-route form holds in registers (K <= 1536)
+      if ((p.F >> 3) <= 32 * MAXC) {
+        // One route at a time: weight base, score and activation row are loop invariants, a lane requests its (at most
+        // MAXC) chunks of all R rows at once and the chunk loop is straight-line code. The flattened form below spends
+        // three times the instructions per chunk on finding out which route a chunk belongs to.
+        for (int i = 0; i < n_routes; ++i) {
+          const int k = s_k[i], kch = k >> 3;
+          const bf16* wb = s_w[i] + (size_t)n0 * k;
+          uint4 wv[MAXC][R];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int c = c0 + u * 32;
-          const int i = c < n_exp_chunks ? c / cpr : n_routes - 1;
-          route[u] = i;
-          cc[u] = c < n_exp_chunks ? c - i * cpr : c - n_exp_chunks;
-          if (c < chunks) {
-            const bf16* wb = s_w[i] + (size_t)n0 * s_k[i] + cc[u] * 8;
+          for (int u = 0; u < MAXC; ++u) {
+            const int c = lane + 32 * u;
 #pragma unroll
             for (int r = 0; r < R; ++r)
-              wv[u][r] = (n0 + r < p.D) ? ld_stream16(wb + (size_t)r * s_k[i]) : make_uint4(0, 0, 0, 0);
-          } else {
-#pragma unroll
-            for (int r = 0; r < R; ++r) wv[u][r] = make_uint4(0, 0, 0, 0);
+              wv[u][r] = (c < kch && n0 + r < p.D) ? ld_stream16(wb + (size_t)r * k + c * 8) : make_uint4(0, 0, 0, 0);
           }
+          const float g = s_g[i];
+          const bf16* arow_s = as + (size_t)i * p.F;
+          float d[R];
+#pragma unroll
+          for (int r = 0; r < R; ++r) d[r] = 0.f;
+#pragma unroll
+          for (int u = 0; u < MAXC; ++u) {
+            const int c = lane + 32 * u;
+            if (c < kch) {
+              float xf[8];
+              unpack8(*reinterpret_cast<const uint4*>(arow_s + c * 8), xf);
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                float wf[8];
+                unpack8(wv[u][r], wf);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) d[r] = fmaf(wf[q], xf[q], d[r]);
+              }
+            }
+          }
+#pragma unroll
+          for (int r = 0; r < R; ++r) total[r] = fmaf(g, d[r], total[r]);
         }
+      } else {
+      const int chunks = s_cbeg[n_routes];
+        // all routed experts span cpr chunks; only a trailing shared-expert shard may differ
+        const int cpr = p.F >> 3;
+        const int n_exp_chunks = (n_routes > 0 && s_slot[n_routes - 1] == p.topk) ? s_cbeg[n_routes - 1] : chunks;
+        constexpr int U = 16 / R;
+        for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
+          uint4 wv[U][R];
+          int route[U], cc[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if (c0 + u * 32 < chunks) {
-            float xf[8];
-            unpack8(*reinterpret_cast<const uint4*>(as + (size_t)route[u] * p.F + cc[u] * 8), xf);
-            const float g = s_g[route[u]];
+          for (int u = 0; u < U; ++u) {
+            const int c = c0 + u * 32;
+            const int i = c < n_exp_chunks ? c / cpr : n_routes - 1;
+            route[u] = i;
+            cc[u] = c < n_exp_chunks ? c - i * cpr : c - n_exp_chunks;
+            if (c < chunks) {
+              const bf16* wb = s_w[i] + (size_t)n0 * s_k[i] + cc[u] * 8;
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-              float wf[8], d = 0.f;
-              unpack8(wv[u][r], wf);
+              for (int r = 0; r < R; ++r)
+                wv[u][r] = (n0 + r < p.D) ? ld_stream16(wb + (size_t)r * s_k[i]) : make_uint4(0, 0, 0, 0);
+            } else {
 #pragma unroll
-              for (int k = 0; k < 8; ++k) d = fmaf(wf[k], xf[k], d);
-              total[r] = fmaf(g, d, total[r]);
+              for (int r = 0; r < R; ++r) wv[u][r] = make_uint4(0, 0, 0, 0);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (c0 + u * 32 < chunks) {
+              float xf[8];
+              unpack8(*reinterpret_cast<const uint4*>(as + (size_t)route[u] * p.F + cc[u] * 8), xf);
+              const float g = s_g[route[u]];
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                float wf[8], d = 0.f;
+                unpack8(wv[u][r], wf);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) d = fmaf(wf[k], xf[k], d);
+                total[r] = fmaf(g, d, total[r]);
+              }
             }
           }
         }

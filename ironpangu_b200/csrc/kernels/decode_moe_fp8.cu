@@ -231,50 +231,96 @@ __global__ void __launch_bounds__(256) moe_down_fp8_allreduce_kernel(Down8Params
       float total[R];
 #pragma unroll
       for (int r = 0; r < R; ++r) total[r] = 0.f;
-      const int chunks = s_cbeg[n_routes];
-      const int cpr = p.F >> 4;
-      const int n_exp_chunks = (n_routes > 0 && s_slot[n_routes - 1] == p.topk) ? s_cbeg[n_routes - 1] : chunks;
-      constexpr int U = 16 / R;
-      for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
-        uint4 wv[U][R];
-        float sv[U][R];
-        int route[U], cc[U];
+      constexpr int MAXC = 4;   // 16-byte chunks (16 weights) per lane and route held in registers (K <= 2048)
+      if ((p.F >> 4) <= 32 * MAXC) {
+        // one route at a time, as in the bf16 kernel: base pointers, score and activation row are loop invariants
+        for (int i = 0; i < n_routes; ++i) {
+          const int k = s_k[i], kch = k >> 4, nbk = (k + QBLOCK - 1) / QBLOCK;
+          const uint8_t* wb = s_w[i] + (size_t)n0 * k;
+          const float* sb = s_sc[i] + (size_t)n0 * nbk;
+          uint4 wv[MAXC][R];
+          float sv[MAXC][R];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int c = c0 + u * 32;
-          const int i = c < n_exp_chunks ? c / cpr : n_routes - 1;
-          route[u] = i;
-          cc[u] = c < n_exp_chunks ? c - i * cpr : c - n_exp_chunks;
-          if (c < chunks) {
-            const int k = s_k[i], nbk = (k + QBLOCK - 1) / QBLOCK;
-            const uint8_t* wb = s_w[i] + (size_t)n0 * k + (size_t)cc[u] * 16;
-            const float* sb = s_sc[i] + (size_t)n0 * nbk + (cc[u] >> 3);
+          for (int u = 0; u < MAXC; ++u) {
+            const int c = lane + 32 * u;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-              const bool in = n0 + r < p.D;
-              wv[u][r] = in ? ld_stream16(wb + (size_t)r * k) : make_uint4(0, 0, 0, 0);
-              sv[u][r] = in ? __ldg(sb + (size_t)r * nbk) : 0.f;
+              const bool in = c < kch && n0 + r < p.D;
+              wv[u][r] = in ? ld_stream16(wb + (size_t)r * k + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
+              sv[u][r] = in ? __ldg(sb + (size_t)r * nbk + (c >> 3)) : 0.f;
             }
-          } else {
-#pragma unroll
-            for (int r = 0; r < R; ++r) { wv[u][r] = make_uint4(0, 0, 0, 0); sv[u][r] = 0.f; }
           }
+          const float g = s_g[i];
+          const bf16* arow_s = as + (size_t)i * p.F;
+          float acc[R];
+#pragma unroll
+          for (int r = 0; r < R; ++r) acc[r] = 0.f;
+#pragma unroll
+          for (int u = 0; u < MAXC; ++u) {
+            const int c = lane + 32 * u;
+            if (c < kch) {
+              float xf[16];
+              unpack8(*reinterpret_cast<const uint4*>(arow_s + c * 16), xf);
+              unpack8(*reinterpret_cast<const uint4*>(arow_s + c * 16 + 8), xf + 8);
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                float wf[16], d = 0.f;
+                unpack16_e4m3(wv[u][r], wf);
+#pragma unroll
+                for (int q = 0; q < 16; ++q) d = fmaf(wf[q], xf[q], d);
+                acc[r] = fmaf(sv[u][r], d, acc[r]);
+              }
+            }
+          }
+#pragma unroll
+          for (int r = 0; r < R; ++r) total[r] = fmaf(g, acc[r], total[r]);
         }
+      } else {
+      const int chunks = s_cbeg[n_routes];
+        const int cpr = p.F >> 4;
+        const int n_exp_chunks = (n_routes > 0 && s_slot[n_routes - 1] == p.topk) ? s_cbeg[n_routes - 1] : chunks;
+        constexpr int U = 16 / R;
+        for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
+          uint4 wv[U][R];
+          float sv[U][R];
+          int route[U], cc[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if (c0 + u * 32 < chunks) {
-            float xf[16];
-            const bf16* ar = as + (size_t)route[u] * p.F + cc[u] * 16;
-            unpack8(*reinterpret_cast<const uint4*>(ar), xf);
-            unpack8(*reinterpret_cast<const uint4*>(ar + 8), xf + 8);
-            const float g = s_g[route[u]];
+          for (int u = 0; u < U; ++u) {
+            const int c = c0 + u * 32;
+            const int i = c < n_exp_chunks ? c / cpr : n_routes - 1;
+            route[u] = i;
+            cc[u] = c < n_exp_chunks ? c - i * cpr : c - n_exp_chunks;
+            if (c < chunks) {
+              const int k = s_k[i], nbk = (k + QBLOCK - 1) / QBLOCK;
+              const uint8_t* wb = s_w[i] + (size_t)n0 * k + (size_t)cc[u] * 16;
+              const float* sb = s_sc[i] + (size_t)n0 * nbk + (cc[u] >> 3);
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-              float wf[16], d = 0.f;
-              unpack16_e4m3(wv[u][r], wf);
+              for (int r = 0; r < R; ++r) {
+                const bool in = n0 + r < p.D;
+                wv[u][r] = in ? ld_stream16(wb + (size_t)r * k) : make_uint4(0, 0, 0, 0);
+                sv[u][r] = in ? __ldg(sb + (size_t)r * nbk) : 0.f;
+              }
+            } else {
 #pragma unroll
-              for (int k = 0; k < 16; ++k) d = fmaf(wf[k], xf[k], d);
-              total[r] = fmaf(g * sv[u][r], d, total[r]);
+              for (int r = 0; r < R; ++r) { wv[u][r] = make_uint4(0, 0, 0, 0); sv[u][r] = 0.f; }
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (c0 + u * 32 < chunks) {
+              float xf[16];
+              const bf16* ar = as + (size_t)route[u] * p.F + cc[u] * 16;
+              unpack8(*reinterpret_cast<const uint4*>(ar), xf);
+              unpack8(*reinterpret_cast<const uint4*>(ar + 8), xf + 8);
+              const float g = s_g[route[u]];
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                float wf[16], d = 0.f;
+                unpack16_e4m3(wv[u][r], wf);
+#pragma unroll
+                for (int k = 0; k < 16; ++k) d = fmaf(wf[k], xf[k], d);
+                total[r] = fmaf(g * sv[u][r], d, total[r]);
+              }
             }
           }
         }
