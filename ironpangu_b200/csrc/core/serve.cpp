@@ -2,6 +2,7 @@
 
 #include <poll.h>
 #include <sys/socket.h>
+#include <sys/wait.h>
 #include <sys/un.h>
 #include <unistd.h>
 
@@ -139,7 +140,8 @@ std::vector<uint32_t> MockEngine::step(const paging::SequenceBatch& batch) {
 }
 
 // ---- pipe engine ----------------------------------------------------------------------------------------------------
-PipeEngine::PipeEngine(const std::string& socket_path, double accept_seconds, double io_seconds) : path_(socket_path), io_seconds_(io_seconds) {
+PipeEngine::PipeEngine(const std::string& socket_path, double accept_seconds, double io_seconds, long watch_pid)
+    : path_(socket_path), io_seconds_(io_seconds) {
   sockaddr_un addr{};
   if (socket_path.size() >= sizeof(addr.sun_path)) invalid("engine socket path is too long");
   listen_fd_ = ::socket(AF_UNIX, SOCK_STREAM, 0);
@@ -152,8 +154,18 @@ PipeEngine::PipeEngine(const std::string& socket_path, double accept_seconds, do
     listen_fd_ = -1;
     fail(ErrorKind::Io, "engine socket: cannot bind " + socket_path);
   }
-  pollfd p{listen_fd_, POLLIN, 0};
-  if (::poll(&p, 1, (int)(accept_seconds * 1000)) <= 0) fail(ErrorKind::Backend, "engine worker did not connect in time");
+  const double deadline = now_seconds() + accept_seconds;
+  for (;;) {
+    pollfd p{listen_fd_, POLLIN, 0};
+    const double left = deadline - now_seconds();
+    if (left <= 0) fail(ErrorKind::Backend, "engine worker did not connect in time");
+    if (::poll(&p, 1, (int)(std::min(left, 0.5) * 1000)) > 0) break;
+    if (watch_pid > 0) {
+      int status = 0;
+      if (::waitpid((pid_t)watch_pid, &status, WNOHANG) == (pid_t)watch_pid)
+        fail(ErrorKind::Backend, "engine worker exited before connecting (status " + std::to_string(status) + ")");
+    }
+  }
   fd_ = ::accept(listen_fd_, nullptr, nullptr);
   if (fd_ < 0) fail(ErrorKind::Backend, "engine socket: accept failed");
   Json req = Json::object();

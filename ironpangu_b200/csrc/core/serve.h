@@ -89,7 +89,8 @@ class MockEngine : public ResidentEngine {
 class PipeEngine : public ResidentEngine {
  public:
   // listens on `socket_path` and waits up to `accept_seconds` for the worker to connect
-  PipeEngine(const std::string& socket_path, double accept_seconds, double io_seconds = 120.0);
+  // `watch_pid`: a child process expected to connect; when it exits first the wait ends at once with a Backend error
+  PipeEngine(const std::string& socket_path, double accept_seconds, double io_seconds = 120.0, long watch_pid = 0);
   ~PipeEngine() override;
   EngineInfo info() const override { return info_; }
   void admit(uint32_t resident, const SamplingParams& params, uint32_t reserve_tokens) override;

@@ -128,7 +128,7 @@ int main(int argc, char** argv) {
         child = spawn_shell(a.spawn, a.socket);
         if (child < 0) throw Error(ErrorKind::Io, "cannot start the engine worker");
       }
-      engine = std::make_shared<serve::PipeEngine>(a.socket, a.accept_seconds);
+      engine = std::make_shared<serve::PipeEngine>(a.socket, a.accept_seconds, 120.0, (long)child);
     }
   } catch (const std::exception& e) {
     std::fprintf(stderr, "ifab-server: engine start-up failed: %s\n", e.what());

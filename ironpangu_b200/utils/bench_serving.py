@@ -52,23 +52,21 @@ class Launched:
                                      text=True, cwd=ROOT, env=env)
         self.port = None
         self.log: List[str] = []
-        t0 = time.time()
-        while time.time() - t0 < timeout:
-            line = self.proc.stdout.readline()
-            if not line:
-                break
-            self.log.append(line)
-            if line.startswith("listening on"):
-                self.port = int(line.rsplit(":", 1)[1])
-                break
+        ready = threading.Event()
+
+        def reader() -> None:
+            for line in self.proc.stdout:
+                self.log.append(line)
+                if self.port is None and line.startswith("listening on"):
+                    self.port = int(line.rsplit(":", 1)[1])
+                    ready.set()
+            ready.set()                     # the server exited
+
+        threading.Thread(target=reader, daemon=True).start()
+        ready.wait(timeout)
         if not self.port:
             self.close()
             raise RuntimeError("server did not come up:\n" + "".join(self.log[-40:]))
-        threading.Thread(target=self._drain, daemon=True).start()
-
-    def _drain(self) -> None:
-        for line in self.proc.stdout:
-            self.log.append(line)
 
     def close(self) -> int:
         if self.proc.poll() is None:
@@ -205,8 +203,12 @@ def server_args(a) -> List[str]:
             worker += f" --layers {a.layers}"
         if a.prefill_chunk:
             worker += f" --prefill-chunk {a.prefill_chunk}"
+        if a.gpu_memory_utilization != 0.9:
+            worker += f" --gpu-memory-utilization {a.gpu_memory_utilization}"
         if a.kv_int8:
             worker += " --kv-int8"
+        if a.expert_fp8:
+            worker += " --expert-fp8"
         if a.prefix_cache_slots:
             worker += f" --prefix-cache-slots {a.prefix_cache_slots}"
         if a.gpus > 1:
@@ -229,7 +231,9 @@ def main(argv: Optional[List[str]] = None) -> Dict:
     ap.add_argument("--cpu", action="store_true")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--master-port", type=int, default=29611)
+    ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--kv-int8", action="store_true")
+    ap.add_argument("--expert-fp8", action="store_true")
     ap.add_argument("--prefill-chunk", type=int, default=0, help="rows per tensor-core prefill call of the worker (0 = decode kernels)")
     ap.add_argument("--prefix-cache-slots", type=int, default=0)
     ap.add_argument("--max-num-seqs", type=int, default=8)

@@ -373,3 +373,15 @@ def test_gpu_dense_worker_batches_decode_rows_on_the_tensor_cores():
         assert st == 200 and a["prefill_chunks"] >= 3 and a["fabric_status"] == 0
     finally:
         s.close()
+
+
+def test_server_fails_fast_when_the_spawned_engine_dies():
+    """A worker that exits before connecting ends the wait at once instead of after the whole accept window."""
+    from ironpangu_b200 import _build
+
+    _build.build_core()
+    t0 = time.time()
+    r = subprocess.run([str(_build.SERVER_BIN), "--port", "0", "--spawn", "exit 3", "--accept-seconds", "120"], capture_output=True, text=True,
+                       timeout=60)
+    assert r.returncode != 0 and time.time() - t0 < 20
+    assert "exited before connecting" in (r.stdout + r.stderr)
