@@ -38,6 +38,8 @@ def parse():
     ap.add_argument("--prefill", default="gemm", choices=["gemm", "decode"],
                     help="gemm: tensor-core prefill path (native impl only); decode: prompt through the decode kernels, 8 rows a time")
     ap.add_argument("--persistent", type=int, default=0, help="1: one persistent cooperative launch per decode step")
+    ap.add_argument("--expert-fp8", action="store_true", help="block-scaled fp8 expert weights (the serving configuration; NOT the bf16 headline)")
+    ap.add_argument("--kv-int8", action="store_true", help="packed int8 latent KV cache (the serving configuration; NOT the bf16 headline)")
     ap.add_argument("--layers", type=int, default=0, help="override layer count (marks the run as a reduced config)")
     return ap.parse_args()
 
@@ -139,7 +141,9 @@ def main():
         args.prefill = "decode"
     elif args.impl == "native":
         dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1,
-                            persistent=bool(args.persistent))
+                            persistent=bool(args.persistent), expert_fp8=args.expert_fp8, kv_int8=args.kv_int8)
+        if args.expert_fp8 or args.kv_int8:
+            args.prefill = "decode"        # the quantised layouts prefill through the decode kernels
     else:
         from baseline.nccl_cublas import NcclCublasDecoder
         dec = NcclCublasDecoder(cfg, weights, rank, world, max_tokens=8, max_context=max_context)
@@ -221,7 +225,8 @@ def main():
         line = {
             "metric": "decode_tokens_per_s_per_box", "value": round(value, 3), "unit": "tokens/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None if dense else round(value / BASELINE_TOK_S, 3), "dtype": "bf16", "impl": args.impl,
+            "vs_baseline": None if dense else round(value / BASELINE_TOK_S, 3),
+            "dtype": "bf16" + (" activations, fp8 block-scaled experts" if args.expert_fp8 else "") + (", int8 KV" if args.kv_int8 else ""), "impl": args.impl,
             "data": "synthetic (uniform random prompt ids; N(0,0.02) random-init weights generated on device)",
             "config": {"model": ("92B-class MLA+MoE: 46L hidden 4096, 32 heads, q_lora 1536, kv_lora 512, nope 128, rope 64, "
                                  "v 128, 96 experts x 1536 top-8 softmax + 1 shared, vocab 153600") if args.model == "flagship"
