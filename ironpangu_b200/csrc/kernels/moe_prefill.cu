@@ -55,13 +55,23 @@ __global__ void __launch_bounds__(256) router_block_kernel(RouterBlockParams p) 
     float acc[T];
 #pragma unroll
     for (int t = 0; t < T; ++t) acc[t] = 0.f;
-    for (int c = lane; c < quads; c += 32) {
-      const float4 wv = __ldg(wr + c);
+    // eight 16-byte weight loads in flight per lane: issued one at a time the loop waits for L2 on every iteration
+    constexpr int G = 8;
+    for (int c0 = lane; c0 < quads; c0 += 32 * G) {
+      float4 wv[G];
 #pragma unroll
-      for (int t = 0; t < T; ++t) {
-        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(xs + (size_t)t * p.D + c * 4);
-        const float2 a = __bfloat1622float2(xp[0]), b = __bfloat1622float2(xp[1]);
-        acc[t] += wv.x * a.x + wv.y * a.y + wv.z * b.x + wv.w * b.y;
+      for (int g = 0; g < G; ++g) wv[g] = (c0 + 32 * g < quads) ? __ldg(wr + c0 + 32 * g) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const int c = c0 + 32 * g;
+        if (c < quads) {
+#pragma unroll
+          for (int t = 0; t < T; ++t) {
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(xs + (size_t)t * p.D + c * 4);
+            const float2 a = __bfloat1622float2(xp[0]), b = __bfloat1622float2(xp[1]);
+            acc[t] += wv[g].x * a.x + wv[g].y * a.y + wv[g].z * b.x + wv[g].w * b.y;
+          }
+        }
       }
     }
 #pragma unroll
@@ -150,6 +160,7 @@ struct DispatchParams {
   int32_t* route_row;   // [M * topk]: row in the permuted matrix, -1 when the expert lives on another rank
   int32_t* perm_token;  // [M * topk]: token of permuted row r
   int4* tiles; int32_t* num_tiles; int32_t* total_rows; int max_tiles;
+  int smem_routes;      // routes whose local expert ids fit the dynamic shared memory of the launch
 };
 
 // single CTA of 1024 threads: warp w ranks the routes of experts w, w + 32, ... with ballot prefix sums, so the order
@@ -161,12 +172,23 @@ __global__ void __launch_bounds__(1024) moe_dispatch_kernel(DispatchParams p) {
   grid_dep_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int R = p.M * p.topk;
+  // the local expert of every route (or -1), staged once: the ballot scans below would otherwise wait on a global load each
+  extern __shared__ short s_loc[];
+  const bool staged = R <= p.smem_routes;
+  if (staged) {
+    for (int i = threadIdx.x; i < R; i += blockDim.x) {
+      const int e = p.ids[i] - p.e0;
+      s_loc[i] = (short)((e >= 0 && e < p.el) ? e : -1);
+    }
+    __syncthreads();
+  }
+  auto local_of = [&](int i) -> int { return staged ? (int)s_loc[i] : p.ids[i] - p.e0; };
   // pass 1: counts
   for (int e = warp; e < p.el; e += 32) {
     int n = 0;
     for (int i0 = 0; i0 < R; i0 += 32) {
       const int i = i0 + lane;
-      const bool hit = i < R && p.ids[i] == p.e0 + e;
+      const bool hit = i < R && local_of(i) == e;
       n += __popc(__ballot_sync(0xffffffffu, hit));
     }
     if (lane == 0) s_count[e] = n;
@@ -198,7 +220,7 @@ __global__ void __launch_bounds__(1024) moe_dispatch_kernel(DispatchParams p) {
     int base = s_off[e];
     for (int i0 = 0; i0 < R; i0 += 32) {
       const int i = i0 + lane;
-      const bool hit = i < R && p.ids[i] == p.e0 + e;
+      const bool hit = i < R && local_of(i) == e;
       const unsigned m = __ballot_sync(0xffffffffu, hit);
       if (hit) {
         const int r = base + __popc(m & ((1u << lane) - 1));
@@ -295,8 +317,12 @@ extern "C" int ifab_moe_dispatch(const int32_t* ids, int M, int topk, int e0, in
                                  void* stream) {
   if (M < 1 || topk < 1 || topk > MAX_TOPK || e_local < 1 || e_local > MAX_LOCAL || max_tiles < 1) return -1;
   DispatchParams p{ids, M, topk, e0, e_local, counts, route_row, perm_token, reinterpret_cast<int4*>(tiles), num_tiles, total_rows,
-                   max_tiles};
-  return launch_chain(moe_dispatch_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, p);
+                   max_tiles, 0};
+  const size_t want = (size_t)M * topk * sizeof(short);
+  const size_t smem = want <= 160 * 1024 ? want : 0;
+  p.smem_routes = (int)(smem / sizeof(short));
+  if (int rc = opt_in_smem(moe_dispatch_kernel, smem)) return rc;
+  return launch_chain(moe_dispatch_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)stream, p);
 }
 
 extern "C" int ifab_moe_gather(const void* xn, long ldxn, const int32_t* perm_token, const int32_t* total_rows, void* xp, long ldxp,
