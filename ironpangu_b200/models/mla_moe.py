@@ -199,7 +199,11 @@ class MlaMoeDecoder:
         self.expert_fp8 = expert_fp8
         can_fuse = (not kv_int8 and cfg.kv_lora == 512 and cfg.rope == 64 and cfg.nope % 32 == 0 and cfg.nope <= 128 and
                     cfg.vdim <= 128 and cfg.q_lora % 8 == 0)
-        self.fused_head = (can_fuse and max_context <= 2048) if fused_head is None else bool(fused_head)
+        self.can_fuse_head = can_fuse
+        self.fused_ctx_limit = 2048
+        self.fused_auto = fused_head is None      # engines that know the position may pick the kernel per step (fuse_override)
+        self.fuse_override: Optional[bool] = None
+        self.fused_head = (can_fuse and max_context <= self.fused_ctx_limit) if fused_head is None else bool(fused_head)
         self.fused_head_rows = 2 if fused_head is None else 8     # an explicit request fuses every step width
         assert not self.fused_head or can_fuse, "the fused head kernel needs a bf16 cache and 512 + 64 latent rows"
         self.cfg, self.w, self.fabric = cfg, weights, fabric
@@ -380,7 +384,8 @@ class MlaMoeDecoder:
             p = f"layers.{l}."
             qkv = self.qkv[:T]
             K.gemv(x, w[p + "qkv_a"], norm_w=w[p + "attn_norm"], eps=c.eps, out=qkv)
-            if self.fused_head and T <= self.fused_head_rows:
+            fuse = self.fused_head if self.fuse_override is None else (self.fuse_override and self.can_fuse_head)
+            if fuse and T <= self.fused_head_rows:
                 K.mla_head_decode(qkv, w[p + "q_a_norm"], w[p + "kv_a_norm"], w[p + "q_b"], w[p + "kv_b"], self.caches[l], pos, slot,
                                   self.page_table, q_lora=c.q_lora, nope=c.nope, scale=c.scale, eps=c.eps, theta=c.theta,
                                   window=c.window, out=self.attn[:T], status_ptr=st)

@@ -27,10 +27,31 @@ class DecodeEngine:
         self._out_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._graph = None
         self._feedback_graph = None
+        # decoders whose attention has two forms (one fused launch for short contexts, split-KV kernels for long ones) get one
+        # graph per form; the engine knows the position on the host and replays the matching one
+        self._graphs = {}
+        self._feedback_graphs = {}
         self.h2d_bytes_per_step = 8
         self.d2h_bytes_per_step = 4
 
     # -- graphs ------------------------------------------------------------------------------------
+    def _variant(self, last_pos: int):
+        d = self.dec
+        if getattr(d, "can_fuse_head", False) and getattr(d, "fused_auto", False) and not getattr(d, "persistent", False):
+            return last_pos < d.fused_ctx_limit
+        return None
+
+    def _select(self, table, variant, capture):
+        d = self.dec
+        if variant not in table:
+            if variant is not None:
+                d.fuse_override = variant
+            capture()
+            table[variant] = self._graph if table is self._graphs else self._feedback_graph
+            if variant is not None:
+                d.fuse_override = None
+        return table[variant]
+
     def _capture(self):
         d = self.dec
         d.tokens[:1].copy_(self._ctl_dev[0:1])
@@ -92,8 +113,8 @@ class DecodeEngine:
         self._ctl_host[0] = token
         self._ctl_host[1] = self.pos
         self._ctl_dev.copy_(self._ctl_host, non_blocking=True)
-        if self._graph is None:
-            self._capture()     # its warm-up run executes this very step (same token, same position), never a stale one
+        # a capture's warm-up run executes this very step (same token, same position), never a stale one
+        self._graph = self._select(self._graphs, self._variant(self.pos), self._capture)
         self._graph.replay()
         self._out_host.copy_(self.dec.next_ids[:1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
@@ -116,8 +137,8 @@ class DecodeEngine:
             d.tokens[:1].fill_(first_token)
             d.positions[:1].fill_(self.pos)
             d.slots[:1].zero_()
-        if self._feedback_graph is None:
-            self._capture_feedback()    # warm-up = the step about to be replayed (same inputs), so it changes no state
+        # warm-up of a capture = the step about to be replayed (same inputs), so it changes no state
+        self._feedback_graph = self._select(self._feedback_graphs, self._variant(self.pos + steps - 1), self._capture_feedback)
         for _ in range(steps):
             self._feedback_graph.replay()
         self.pos += steps

@@ -181,3 +181,29 @@ def test_fused_head_decoder_tracks_the_oracle_and_the_chain():
         torch.testing.assert_close(outs[0], outs[1], rtol=2e-2, atol=2e-2)
     assert fab.status() == 0
     fab.close()
+
+
+@pytest.mark.gpu
+def test_engine_switches_attention_kernels_at_the_context_limit():
+    """A decoder built for long contexts decodes through the fused attention kernel while the position is below the limit and
+    through the split-KV kernels after it: two graphs, one token stream."""
+    from ironpangu_b200.models.mla_moe import MlaMoeConfig, MlaMoeDecoder, random_full_weights, shard_weights
+    from ironpangu_b200.parallel.fabric import Fabric
+    from ironpangu_b200.runtime.engine import DecodeEngine
+
+    cfg = MlaMoeConfig.tiny(2)
+    full = random_full_weights(cfg, seed=0)
+    fab = Fabric(0, 1)
+    outs = []
+    for auto in (True, False):
+        dec = MlaMoeDecoder(cfg, shard_weights(cfg, full, 0, 1, "cuda"), fab, max_tokens=8, max_context=4096,
+                            fused_head=None if auto else False)
+        assert not dec.fused_head
+        dec.fused_ctx_limit = 24
+        eng = DecodeEngine(dec)
+        outs.append(eng.generate(list(range(5, 17)), 30))
+        assert len(eng._graphs) == (2 if auto else 1)
+    same = sum(a == b for a, b in zip(*outs))
+    assert same >= 28, outs          # the two kernels agree to f32 summation order; a near-tie may flip late in the stream
+    assert fab.status() == 0
+    fab.close()
