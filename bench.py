@@ -94,7 +94,7 @@ def main():
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "reference is a Rust + CANN/HCCL stack for Ascend NPUs: no Python package, no CUDA build, "
-                          "no Rust toolchain in this image (pip install of /root/reference fails: no setup.py/pyproject)"}))
+                          "no Rust toolchain in this image (pip install of the reference tree fails: no setup.py/pyproject)"}))
         return 0
 
     import torch
