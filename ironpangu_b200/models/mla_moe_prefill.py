@@ -76,6 +76,30 @@ class MlaMoePrefill:
         # W_uk^T per head: [hl, latent, nope], the [N, K] operand of the absorb GEMM
         self.w_uk_t = [dec.w[f"layers.{l}.kv_b"][:, :c.nope, :].transpose(1, 2).contiguous() for l in range(c.layers)]
         self.launches = 0
+        # CUDA graphs of the layer stack, one per row count (the few most recent): a chunk is ~100 launches per layer and at
+        # 4-8 GPUs the host cannot issue them as fast as the devices finish them. The all-reduce staging buffers alternate per
+        # layer from host state, so a recorded pass replays correctly only if a pass leaves that state as it found it.
+        self.use_graphs = fab.world == 1 or c.layers % 2 == 0
+        self._graphs = {}
+
+    def _layers_graphed(self, m: int) -> torch.Tensor:
+        if not self.use_graphs:
+            return self._layers(m)
+        g = self._graphs.get(m)
+        if g is not None:
+            g.replay()
+            return self.x[:m]
+        x = self._layers(m)                         # the real run of this chunk (and the warm-up of the capture)
+        torch.cuda.synchronize()
+        calls = self._calls
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):                   # records only: caches and counters are not touched a second time
+            self._layers(m)
+        self._calls = calls
+        if len(self._graphs) >= 4:
+            self._graphs.pop(next(iter(self._graphs)))
+        self._graphs[m] = g
+        return x
 
     def forward(self, tokens: torch.Tensor, pos0: int, slot: int = 0) -> torch.Tensor:
         """Run ``tokens`` (int32 ``[m]``, ``m <= max_rows``, already on the device) at positions ``pos0 .. pos0+m-1``
@@ -87,7 +111,7 @@ class MlaMoePrefill:
         self.tokens[:m].copy_(tokens)
         self.positions[:m].copy_(torch.arange(pos0, pos0 + m, dtype=torch.int32, device=tokens.device))
         self.slots[:m].fill_(slot)
-        x = self._layers(m)
+        x = self._layers_graphed(m)
         # greedy token after the last row through the decode head (vocabulary-sharded argmax exchange included)
         K.lm_head_argmax(x[m - 1:m], w["lm_head"], fab, norm_w=w["final_norm"], eps=c.eps, vocab_offset=d.rank * d.vl,
                          partial=d.partial, logits=None if d.logits is None else d.logits[:1], out_ids=d.next_ids[:1],
@@ -105,7 +129,7 @@ class MlaMoePrefill:
         self.tokens[:m].copy_(tokens)
         self.positions[:m].copy_(positions)
         self.slots[:m].copy_(slots)
-        x = self._layers(m)
+        x = self._layers_graphed(m)
         xn = K.rmsnorm(x.index_select(0, select), d.w["final_norm"], c.eps)
         self.launches += 2
         return G.gemm(xn, d.w["lm_head"], out_f32=True, status_ptr=d.fabric.desc.status)
