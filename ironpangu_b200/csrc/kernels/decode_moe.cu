@@ -30,6 +30,7 @@ struct RouterParams {
   float* logits; int32_t* ids; float* wts;
   int T, D, E, topk, scoring, renorm; float scale;
   uint32_t* ticket;
+  bf16* xn; long ldxn;     // optional: the normalised rows, for the expert kernels that follow (CTA 0 writes them)
 };
 
 // grid = E CTAs of 256 threads; thread i owns float4 columns i, i+256, ... of its expert's row
@@ -54,6 +55,12 @@ __global__ void __launch_bounds__(256) router_topk_kernel(RouterParams p) {
   }
   grid_dep_wait();
   stage_x<T>(xs, p.x, p.ldx, 0, p.T, p.D, p.norm_w, p.eps, false, red);
+  if (p.xn && blockIdx.x == 0) {
+    for (int i = threadIdx.x; i < p.T * (p.D >> 3); i += blockDim.x) {
+      const int t = i / (p.D >> 3), c = i % (p.D >> 3);
+      *reinterpret_cast<uint4*>(p.xn + (long)t * p.ldxn + c * 8) = *reinterpret_cast<const uint4*>(xs + (size_t)t * p.D + c * 8);
+    }
+  }
   float acc[T];
 #pragma unroll
   for (int t = 0; t < T; ++t) acc[t] = 0.f;
@@ -554,10 +561,10 @@ int launch_head(const HeadParams& p, uint64_t partial_bytes, cudaStream_t s) {
 
 extern "C" int ifab_router_topk(const void* x, long ldx, const void* norm_w, float eps, const float* w_router,
                                 const float* bias, float* logits, int32_t* ids, float* wts, int T, int D, int E,
-                                int topk, int scoring, int renorm, float scale, uint32_t* ticket, void* stream) {
-  if (T < 1 || T > 8 || E > 256 || topk > MAX_TOPK || topk > E || D % 8 != 0) return -1;
+                                int topk, int scoring, int renorm, float scale, uint32_t* ticket, void* xn, long ldxn, void* stream) {
+  if (T < 1 || T > 8 || E > 256 || topk > MAX_TOPK || topk > E || D % 8 != 0 || (xn && ldxn % 8 != 0)) return -1;
   RouterParams p{(const bf16*)x, ldx, (const bf16*)norm_w, eps, w_router, bias, logits, ids, wts,
-                 T, D, E, topk, scoring, renorm, scale, ticket};
+                 T, D, E, topk, scoring, renorm, scale, ticket, (bf16*)xn, ldxn};
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(E);
 #define IFAB_ROUTER(TT)                                                      \

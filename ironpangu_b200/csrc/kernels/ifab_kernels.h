@@ -116,7 +116,7 @@ int ifab_ep_combine(const void* ret, void* ctl, const int32_t* ids, const int32_
 /* ---- MoE decode path (owner-local expert parallelism) ---- */
 int ifab_router_topk(const void* x, long ldx, const void* norm_w, float eps, const float* w_router, const float* bias,
                      float* logits, int32_t* ids, float* wts, int T, int D, int E, int topk, int scoring, int renorm,
-                     float scale, uint32_t* ticket, void* stream);
+                     float scale, uint32_t* ticket, void* xn, long ldxn, void* stream);
 int ifab_moe_gate_up_decode(const void* x, long ldx, const void* norm_w, float eps, const int32_t* ids, int T, int D,
                             int F, int topk, int e0, int e_local, const void* w_gu, const void* w_shared_gu, int Fs,
                             void* act, void* stream);

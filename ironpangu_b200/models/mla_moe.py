@@ -251,6 +251,7 @@ class MlaMoeDecoder:
         self.scratch = e(T * self.hl * self.max_splits * (c.kv_lora + 2), dt=torch.float32)
         self.logits_r = e(T, c.experts, dt=torch.float32)
         self.route_ids = e(T, c.topk, dt=torch.int32)
+        self.xn = e(T, c.hidden)
         self.route_w = e(T, c.topk, dt=torch.float32)
         self.act = torch.zeros(T, c.topk + 1, c.expert_ffn, dtype=BF16, device=dev)
         self.partial = e(((self.vl + 7) // 8) * 8 * 2, dt=torch.float32)
@@ -357,16 +358,17 @@ class MlaMoeDecoder:
         K.gemv_allreduce(attn, w[p + "o_proj"], fab, residual=x, out=x)
         K.router_topk(x, w[p + "router"], c.topk, norm_w=w[p + "ffn_norm"], eps=c.eps, scoring=c.scoring,
                       scale=c.route_scale, ticket_ptr=fab.ticket_ptr, logits=self.logits_r[:T],
-                      ids=self.route_ids[:T], wts=self.route_w[:T])
+                      ids=self.route_ids[:T], wts=self.route_w[:T], xn=self.xn[:T])
+        xn = self.xn[:T]      # normalised once by the router; the expert kernels skip their own RMSNorm prologue
         if self.expert_fp8:
             w8 = self.w8
-            K.moe_gate_up_fp8(x, self.route_ids[:T], w8[p + "gate_up"], self.rank * self.el, norm_w=w[p + "ffn_norm"],
-                              eps=c.eps, w_shared_gu=w8[p + "shared_gate_up"], act=self.act[:T])
+            K.moe_gate_up_fp8(xn, self.route_ids[:T], w8[p + "gate_up"], self.rank * self.el,
+                              w_shared_gu=w8[p + "shared_gate_up"], act=self.act[:T])
             K.moe_down_allreduce_fp8(self.act[:T], self.route_ids[:T], self.route_w[:T], w8[p + "down"], self.rank * self.el,
                                      fab, w_shared_down=w8[p + "shared_down"], residual=x, out=x)
             return
-        K.moe_gate_up(x, self.route_ids[:T], w[p + "gate_up"], self.rank * self.el, norm_w=w[p + "ffn_norm"],
-                      eps=c.eps, w_shared_gu=w[p + "shared_gate_up"], act=self.act[:T])
+        K.moe_gate_up(xn, self.route_ids[:T], w[p + "gate_up"], self.rank * self.el, w_shared_gu=w[p + "shared_gate_up"],
+                      act=self.act[:T])
         K.moe_down_allreduce(self.act[:T], self.route_ids[:T], self.route_w[:T], w[p + "down"], self.rank * self.el,
                              fab, w_shared_down=w[p + "shared_down"], residual=x, out=x)
 

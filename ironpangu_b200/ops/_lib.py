@@ -77,7 +77,7 @@ _SIGS = {
     "ifab_gemm_bf16": [_P, c_long, _P, c_long, _P, c_long, c_int, _P, c_long, c_int, c_int, c_int, _P, _P],
     "ifab_gemm_allreduce_bf16": [_P, c_long, _P, c_long, _P, c_long, _P, c_long, c_int, c_int, c_int, C.POINTER(IfabFabric), _P],
     "ifab_gemm_reduce_scatter_bf16": [_P, c_long, _P, c_long, _P, c_long, _P, c_long, c_int, c_int, c_int, C.POINTER(IfabFabric), _P],
-    "ifab_router_topk": [_P, c_long, _P, c_float, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P],
+    "ifab_router_topk": [_P, c_long, _P, c_float, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, c_long, _P],
     "ifab_moe_gate_up_decode": [_P, c_long, _P, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P],
     "ifab_moe_down_allreduce_decode": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, c_long, _P,
                                        c_long, C.POINTER(IfabFabric), _P],

@@ -88,8 +88,9 @@ def gemv_allreduce(x: torch.Tensor, w: torch.Tensor, fabric, *, residual: Option
 def router_topk(x: torch.Tensor, w_router: torch.Tensor, topk: int, *, norm_w: Optional[torch.Tensor] = None,
                 eps: float = 1e-5, bias: Optional[torch.Tensor] = None, scoring: str = "softmax", renorm: bool = True,
                 scale: float = 1.0, ticket_ptr: int = 0, logits: Optional[torch.Tensor] = None,
-                ids: Optional[torch.Tensor] = None, wts: Optional[torch.Tensor] = None):
-    """f32 router projection + top-k selection in one launch. Returns (ids int32 [T,k], weights f32 [T,k], logits)."""
+                ids: Optional[torch.Tensor] = None, wts: Optional[torch.Tensor] = None, xn: Optional[torch.Tensor] = None):
+    """f32 router projection + top-k selection in one launch. Returns (ids int32 [T,k], weights f32 [T,k], logits).
+    ``xn`` (bf16 ``[T, D]``) receives the normalised rows, which the expert kernels can then take as they are."""
     T, D = x.shape
     E = w_router.shape[0]
     assert w_router.dtype == torch.float32 and w_router.is_contiguous()
@@ -100,7 +101,7 @@ def router_topk(x: torch.Tensor, w_router: torch.Tensor, topk: int, *, norm_w: O
     mode = {"softmax": 0, "sigmoid_bias_group_topk": 1}[scoring]
     check(_lib.load().ifab_router_topk(x.data_ptr(), _rows(x), _ptr(norm_w), eps, w_router.data_ptr(), _ptr(bias),
                                        logits.data_ptr(), ids.data_ptr(), wts.data_ptr(), T, D, E, topk, mode,
-                                       int(renorm), scale, ticket_ptr, _stream()), "router_topk")
+                                       int(renorm), scale, ticket_ptr, _ptr(xn), 0 if xn is None else _rows(xn), _stream()), "router_topk")
     return ids, wts, logits
 
 
