@@ -130,6 +130,32 @@ def build_core(force: bool = False) -> Path:
     return CORE_LIB
 
 
+def build_core_tests_sanitized(kind: str, force: bool = False) -> Path:
+    """The C++ unit-test binary with the whole host core compiled under a sanitizer: ``"address"`` (AddressSanitizer +
+    UndefinedBehaviorSanitizer) or ``"thread"`` (ThreadSanitizer, for the scheduler / state-pool / service threads). One
+    statically linked binary per kind under ``csrc/tests/``; the regular libraries are not touched."""
+    flags = {"address": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"], "thread": ["-fsanitize=thread"]}[kind]
+    out = TESTS_DIR / f"core_tests_{kind}"
+    srcs = sorted(CORE_DIR.glob("*.cpp"))
+    tsrcs = sorted(TESTS_DIR.glob("*.cpp"))
+    deps = srcs + tsrcs + sorted(CORE_DIR.glob("*.h")) + sorted(TESTS_DIR.glob("*.h"))
+    if force or _stale(out, deps):
+        objdir = CORE_DIR / "build" / kind
+        objdir.mkdir(parents=True, exist_ok=True)
+        cxx = [f for f in CXX_FLAGS if not f.startswith("-O")] + ["-O1", "-g", "-fno-omit-frame-pointer", *flags]
+
+        def one(src: Path):
+            obj = objdir / (src.stem + ".o")
+            _run(["g++", *cxx, "-I", str(CORE_DIR), "-c", str(src), "-o", str(obj)], cwd=src.parent)
+            return str(obj)
+
+        with ThreadPoolExecutor(max_workers=8) as ex:
+            objs = list(ex.map(one, srcs + tsrcs))
+        _run(["g++", *flags, "-o", str(out), *objs, "-pthread", "-ldl"], cwd=TESTS_DIR)
+        _mark(out, deps)
+    return out
+
+
 PLUGIN_DIR = ROOT / "csrc" / "plugins"
 
 

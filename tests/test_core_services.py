@@ -1,5 +1,6 @@
 """Runs the C++ unit tests of the host runtime services (state pool, prefix index and cache, paging, rank plans,
 staged start-up with fault injection, worker group, PD transfer protocol, continuous-batching scheduler, CPU planner)."""
+import os
 import subprocess
 
 import pytest
@@ -48,3 +49,18 @@ def test_cuda_kernel_plugin_through_the_loader():
     want = torch.nn.functional.silu(x[:, :96].float()) * x[:, 96:].float()
     torch.testing.assert_close(y.float(), want, rtol=1e-2, atol=1e-2)
     assert call(b"cpu", x, y)["error"]["kind"] == "stale"
+
+
+@pytest.mark.parametrize("kind", ["address", "thread"])
+def test_cpp_unit_tests_under_sanitizers(kind):
+    """The whole host core (compiler, planner, state pool, scheduler, service threads, HTTP pieces) compiled under
+    AddressSanitizer + UBSan, and under ThreadSanitizer: the C++ unit tests must pass without a single report."""
+    binary = _build.build_core_tests_sanitized(kind)
+    _build.build_plugins()
+    env = dict(os.environ, IFAB_PLUGIN_DIR=str(_build.PLUGIN_DIR),
+               IFAB_EXAMPLE_MODEL=os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "mla_moe_slice_tp1.inferfabric"),
+               ASAN_OPTIONS="detect_leaks=1:abort_on_error=0", TSAN_OPTIONS="halt_on_error=0")
+    r = subprocess.run([str(binary)], capture_output=True, text=True, timeout=600, env=env)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-3000:]
+    assert "0 failures" in out and "Sanitizer" not in out and "runtime error" not in out, out[-3000:]
