@@ -32,7 +32,11 @@ class Fabric:
     """Owner of this rank's symmetric block and of the peer mappings."""
 
     def __init__(self, rank: int = 0, world: int = 1, group=None, data_half_bytes: int = 4 << 20,
-                 flag_half_words: int = 8 * 296, ll_half_bytes: int = 2 << 20, spin_limit: int = 4_000_000, device: Optional[torch.device] = None):
+                 flag_half_words: int = 8 * 296, ll_half_bytes: int = 2 << 20, spin_limit: int = 4_000_000, device: Optional[torch.device] = None,
+                 silent_peers: bool = False):
+        """``silent_peers``: the other ``world - 1`` ranks are blocks on THIS device that nothing ever writes - a one-process
+        stand-in for peers that never arrive, used to exercise the bounded waits (with a small ``spin_limit``) without a
+        second GPU and without hanging one: every kernel gives up after ``spin_limit`` polls and reports through the status word."""
         if world < 1 or world > _lib.MAX_RANKS:
             raise ValueError("world must be 1..8")
         self.rank, self.world, self.group = rank, world, group
@@ -54,7 +58,17 @@ class Fabric:
         self.peer_bases = [0] * _lib.MAX_RANKS
         self.peer_bases[rank] = self.base
         self._imported = []
-        if world > 1:
+        self._silent = []
+        if world > 1 and silent_peers:
+            for r in range(world):
+                if r == rank:
+                    continue
+                blk = C.c_void_p()
+                with torch.cuda.device(self.device):
+                    _lib.check(self.lib.ifab_device_alloc(C.byref(blk), self.bytes), "fabric alloc (silent peer)")
+                self.peer_bases[r] = blk.value
+                self._silent.append(blk.value)
+        elif world > 1:
             self._exchange()
         f = _lib.IfabFabric()
         for r in range(world):
@@ -120,7 +134,10 @@ class Fabric:
         if getattr(self, "base", None) is None:
             return
         torch.cuda.synchronize()
-        if self.world > 1:
+        for blk in self._silent:
+            self.lib.ifab_device_free(blk)
+        self._silent = []
+        if self.world > 1 and self._imported:
             import torch.distributed as dist
             try:
                 dist.barrier(group=self.group)
