@@ -355,6 +355,7 @@ std::shared_ptr<Stream> Service::generate(GenerateRequest req) {
   live.stream = std::make_shared<Stream>(opt_.stream_capacity);
   live.sampling = req.sampling;
   live.reserve = (uint32_t)r.prompt.size() + r.max_new_tokens;
+  live.t_submit = now_seconds();
   ids_[live.name] = r.id;
   ++counters_.requests_total;
   counters_.prompt_tokens += r.prompt.size();
@@ -395,6 +396,15 @@ std::string Service::metrics_text() const {
   line("ifab_requests_running", "Requests holding a resident slot.", "gauge", (double)c.running);
   line("ifab_requests_waiting", "Requests in the admission queue.", "gauge", (double)c.queued);
   line("ifab_healthy", "1 while the engine is healthy.", "gauge", healthy() ? 1.0 : 0.0);
+  auto histogram = [&](const char* name, const char* help, const Histogram& h) {
+    s += std::string("# HELP ") + name + " " + help + "\n# TYPE " + name + " histogram\n";
+    for (int i = 0; i < Histogram::N; ++i)
+      s += std::string(name) + "_bucket{le=\"" + format_double(Histogram::kBounds[i]) + "\"} " + std::to_string(h.bucket[i]) + "\n";
+    s += std::string(name) + "_bucket{le=\"+Inf\"} " + std::to_string(h.count) + "\n";
+    s += std::string(name) + "_sum " + format_double(h.sum) + "\n" + name + "_count " + std::to_string(h.count) + "\n";
+  };
+  histogram("ifab_time_to_first_token_seconds", "Time from submission to the first generated token.", c.ttft);
+  histogram("ifab_inter_token_latency_seconds", "Time between consecutive tokens of a request.", c.inter_token);
   return s;
 }
 
@@ -531,11 +541,16 @@ void Service::run() {
       continue;
     }
     uint64_t generated = 0;
+    Histogram ttft_now, itl_now;
+    const double t_emit = now_seconds();
     for (auto& ev : events) {
       auto it = live.find(ev.request);
       if (it == live.end()) continue;
       if (ev.token) {
         ++generated;
+        if (it->second.t_last == 0.0) ttft_now.observe(t_emit - it->second.t_submit);
+        else itl_now.observe(t_emit - it->second.t_last);
+        it->second.t_last = t_emit;
         if (ev.finish) {
           finish(ev.request, StreamItem{ev.token, ev.finish, ""});
           continue;
@@ -552,6 +567,12 @@ void Service::run() {
       counters_.step_seconds += dt;
       counters_.generated_tokens += generated;
       counters_.backpressure_skips += skipped;
+      for (const auto* pair : {&ttft_now, &itl_now}) {
+        Histogram& dst = pair == &ttft_now ? counters_.ttft : counters_.inter_token;
+        for (int i = 0; i < Histogram::N; ++i) dst.bucket[i] += pair->bucket[i];
+        dst.count += pair->count;
+        dst.sum += pair->sum;
+      }
     }
   }
   // drain: free every resident, stop the engine

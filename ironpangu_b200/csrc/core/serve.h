@@ -144,11 +144,27 @@ struct ServiceOptions {
   uint32_t idle_micros = 2000;
 };
 
+// cumulative latency histogram (Prometheus style): count of observations <= each bound, sum and total count
+struct Histogram {
+  static constexpr int N = 14;
+  static constexpr double kBounds[N] = {0.001, 0.002, 0.005, 0.01, 0.02, 0.05, 0.1, 0.2, 0.5, 1.0, 2.0, 5.0, 10.0, 30.0};
+  uint64_t bucket[N] = {};
+  uint64_t count = 0;
+  double sum = 0.0;
+  void observe(double seconds) {
+    for (int i = 0; i < N; ++i)
+      if (seconds <= kBounds[i]) ++bucket[i];
+    ++count;
+    sum += seconds;
+  }
+};
+
 struct Counters {
   uint64_t requests_total = 0, requests_finished = 0, requests_failed = 0, requests_cancelled = 0, rejected_overloaded = 0,
            rejected_unavailable = 0, prompt_tokens = 0, generated_tokens = 0, engine_steps = 0, batched_rows = 0, backpressure_skips = 0;
   double step_seconds = 0.0;
   uint32_t running = 0, queued = 0;
+  Histogram ttft, inter_token;   // seconds from submission to the first token / between consecutive tokens of a request
 };
 
 class Service {
@@ -170,7 +186,10 @@ class Service {
 
  private:
   void run();
-  struct Live { std::string name; std::shared_ptr<Stream> stream; SamplingParams sampling; uint32_t reserve = 0; };
+  struct Live {
+    std::string name; std::shared_ptr<Stream> stream; SamplingParams sampling; uint32_t reserve = 0;
+    double t_submit = 0.0, t_last = 0.0;   // for the latency histograms
+  };
   std::shared_ptr<ResidentEngine> engine_;
   EngineInfo info_;
   ServiceOptions opt_;

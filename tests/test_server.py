@@ -160,6 +160,11 @@ def test_continuous_batching_many_clients_and_metrics(mock_server):
     assert float(metrics["ifab_requests_finished_total"]) == 13
     assert float(metrics["ifab_engine_rows_total"]) > float(metrics["ifab_engine_steps_total"])   # rows shared steps
     assert float(metrics["ifab_healthy"]) == 1
+    # latency histograms: one first-token observation per finished request, one inter-token observation per later token
+    assert float(metrics["ifab_time_to_first_token_seconds_count"]) == 13
+    assert float(metrics["ifab_inter_token_latency_seconds_count"]) == float(metrics["ifab_generation_tokens_total"]) - 13
+    assert float(metrics['ifab_time_to_first_token_seconds_bucket{le="+Inf"}']) == 13
+    assert float(metrics["ifab_time_to_first_token_seconds_sum"]) > 0
 
 
 def test_disconnect_cancels_and_server_keeps_serving(mock_server):
