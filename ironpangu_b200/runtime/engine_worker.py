@@ -122,6 +122,9 @@ class BatchEngine:
             a.update({"prefix_hits": self.prefix.hits, "prefix_misses": self.prefix.misses, "prefix_published": self.prefix.published,
                       "prefix_evicted": self.prefix.evicted, "prefix_entries": len(self.prefix.entries)})
         a["fabric_status"] = self.dec.fabric.status()
+        opts = getattr(self, "runtime_options", None)
+        if opts is not None:
+            a["runtime_options"] = opts.to_dict()
         return a
 
     def admit(self, resident: int, sampling: Dict, reserve: int) -> None:
@@ -371,7 +374,8 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
     from ironpangu_b200.parallel.fabric import Fabric
 
     dev = torch.device("cuda", torch.cuda.current_device())
-    fab = Fabric(rank, world)
+    ro = getattr(args, "runtime_options", None)
+    fab = Fabric(rank, world, spin_limit=ro.spin_limit) if ro is not None else Fabric(rank, world)
     mark = (lambda name, note="": rec.stage(name, note)) if rec is not None else (lambda name, note="": None)
     mark("fabric", "symmetric-memory block and peer mappings")
     if args.bundle:
@@ -412,7 +416,8 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
     weights = random_rank_weights(cfg, rank, world, dev, seed=args.seed)
     mark("weights")
     dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs,
-                        keep_logits=not args.greedy_only, kv_int8=args.kv_int8, expert_fp8=args.expert_fp8)
+                        keep_logits=not args.greedy_only, kv_int8=args.kv_int8, expert_fp8=args.expert_fp8,
+                        fused_head=ro.fused_head if ro is not None else None)
     mark("state", "KV cache, recurrent state and step workspace")
     prefill = None
     if args.prefill_chunk > 8 and not args.kv_int8 and not args.expert_fp8:
@@ -505,7 +510,24 @@ def main() -> None:
     ap.add_argument("--memory-profile", default="", help="write the staged start-up memory profile (JSON) here")
     ap.add_argument("--profile-only", action="store_true", help="build the engine, write the memory profile and exit")
     ap.add_argument("--socket", default=os.environ.get("IFAB_ENGINE_SOCKET", ""))
+    ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE",
+                    help="runtime option (see runtime/options.py); also read from IFAB_<NAME> environment variables")
     args = ap.parse_args()
+    # typed runtime options: environment first, then --set, then the dedicated flags of this command line
+    from ironpangu_b200.runtime.options import RuntimeOptions
+
+    ropts = RuntimeOptions.from_env(os.environ, args.set)
+    args.kv_int8 = args.kv_int8 or ropts.kv_int8
+    args.expert_fp8 = args.expert_fp8 or ropts.expert_fp8
+    args.prefill_chunk = args.prefill_chunk or ropts.prefill_chunk
+    args.prefix_cache_slots = args.prefix_cache_slots or ropts.prefix_cache_slots
+    args.no_graphs = args.no_graphs or not ropts.decode_graph
+    ropts.kv_int8, ropts.expert_fp8, ropts.prefill_chunk = args.kv_int8, args.expert_fp8, args.prefill_chunk
+    ropts.prefix_cache_slots, ropts.decode_graph = args.prefix_cache_slots, not args.no_graphs
+    ropts.validate()
+    if not ropts.pdl:
+        os.environ["IFAB_PDL"] = "0"           # read by the kernel library when it is loaded
+    args.runtime_options = ropts
     if not args.socket and not args.profile_only:
         raise SystemExit("no engine socket: set IFAB_ENGINE_SOCKET or pass --socket")
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -518,6 +540,7 @@ def main() -> None:
                           (args.memory_profile + (f".rank{rank}" if rank else "")) if args.memory_profile else None, args.profile_only)
     rec = MemoryProfile.start(opts)
     engine = build_engine(args, rank, world, rec)
+    engine.runtime_options = ropts
     rec.finish()
     if args.profile_only:
         torch.cuda.synchronize()
@@ -529,6 +552,11 @@ def main() -> None:
         serve(engine, rank, world, args.socket)
     finally:
         torch.cuda.synchronize()
+        if ropts.audit_dir:
+            # the audit record of this rank (counters, options), for runs that are compared later
+            os.makedirs(ropts.audit_dir, exist_ok=True)
+            with open(os.path.join(ropts.audit_dir, f"engine-audit-rank{rank}.json"), "w") as f:
+                json.dump(engine.audit(), f, indent=1)
         engine.dec.fabric.close()
         if world > 1:
             dist.destroy_process_group()

@@ -362,7 +362,7 @@ def test_gpu_dense_worker_batches_decode_rows_on_the_tensor_cores():
     assert res["output_tokens"] >= 72
 
     cmd = (f"{sys.executable} -m ironpangu_b200.runtime.engine_worker --model dense-tiny --max-num-seqs 4 --max-model-len 256 "
-           "--max-num-batched-tokens 64 --prefill-chunk 32")
+           "--max-num-batched-tokens 64 --set prefill_chunk=32 --set spin_limit=2000000")
     s = Server("--spawn", cmd, "--accept-seconds", "300", timeout=400)
     try:
         prompt = [(5 * i + 1) % 1000 for i in range(70)]
@@ -376,6 +376,7 @@ def test_gpu_dense_worker_batches_decode_rows_on_the_tensor_cores():
         st, body = s.request("GET", "/audit")
         a = json.loads(body)["engine"]
         assert st == 200 and a["prefill_chunks"] >= 3 and a["fabric_status"] == 0
+        assert a["runtime_options"]["prefill_chunk"] == 32 and a["runtime_options"]["spin_limit"] == 2000000
     finally:
         s.close()
 
