@@ -122,6 +122,15 @@ def main():
     pdec.positions.fill_(7)
     pdec.forward(1)
     torch.testing.assert_close(pdec.logits[0], ref[7, rank * vl:(rank + 1) * vl], rtol=3e-2, atol=3e-2)
+    # rows with their own positions through the matrix-matrix path (the batched decode step of the serving engine); the
+    # second call has the same row count and replays the recorded graph
+    ext = prompt + [3, 9, 27, 81]
+    ref = forward_ref(cfg, full, torch.tensor(ext, device="cuda"), tp=world)
+    for lo in (8, 10):
+        rows = torch.tensor(ext[lo:lo + 2], dtype=torch.int32, device="cuda")
+        got = pre.forward_rows(rows, torch.tensor([lo, lo + 1], dtype=torch.int32, device="cuda"),
+                               torch.zeros(2, dtype=torch.int32, device="cuda"), torch.tensor([0, 1], device="cuda"))
+        torch.testing.assert_close(got, ref[lo:lo + 2, rank * vl:(rank + 1) * vl], rtol=3e-2, atol=3e-2)
     assert fab.status() == 0
     print(f"rank {rank}: ok prefill path tp={world}", flush=True)
     print(f"rank {rank}: ok tiny model tp={world}", flush=True)
