@@ -117,7 +117,7 @@ class BatchEngine:
                 "world": self.dec.world, "greedy_only": self.greedy_only}
 
     def audit(self) -> Dict:
-        a = dict(self.audit_counters)
+        a = {"format": "ifab.engine-audit.v1", **self.audit_counters}
         if self.prefix is not None:
             a.update({"prefix_hits": self.prefix.hits, "prefix_misses": self.prefix.misses, "prefix_published": self.prefix.published,
                       "prefix_evicted": self.prefix.evicted, "prefix_entries": len(self.prefix.entries)})
