@@ -183,3 +183,25 @@ def test_cli_checkpoint_metadata_verbs(tmp_path):
     place = json.loads(compiler.cli("plan-placement", str(ROOT / "examples" / "mla_moe_92b_tp8.inferfabric"), "-").stdout)
     assert len(place["ranks"]) == 8 and place["executable"] is False
     assert len({r["device_bytes"] for r in place["ranks"]}) == 1 and place["ranks"][0]["strided_slices"] > 0
+
+
+def test_bundles_pass_the_engine_side_contract_check(tmp_path):
+    """validate-bundle / compiler.validate_bundle: kernel contracts of execution.bin and binding contracts of every rank-N.bin;
+    a bundle whose program was altered after compilation is refused with the instruction named."""
+    out = tmp_path / "b"
+    assert compiler.cli("compile-token", str(SLICE), "-", str(out)).returncode == 0
+    ok = compiler.validate_bundle(str(out))
+    assert ok["valid"] and ok["ranks"] == 1 and ok["instructions"] > 10
+    r = compiler.cli("validate-bundle", str(out))
+    assert r.returncode == 0 and json.loads(r.stdout)["valid"]
+    big = tmp_path / "b8"
+    assert compiler.cli("compile-token", str(ROOT / "examples" / "mla_moe_92b_tp8.inferfabric"), "-", str(big)).returncode == 0
+    assert compiler.validate_bundle(str(big))["ranks"] == 8
+    # swap a kernel name for another of the same length inside the serialized program
+    raw = (out / "execution.bin").read_bytes()
+    assert b"ifab_router_topk" in raw
+    (out / "execution.bin").write_bytes(raw.replace(b"ifab_router_topk", b"ifab_router_topX", 1))
+    with pytest.raises(compiler.CompileError, match="router"):
+        compiler.validate_bundle(str(out))
+    r = compiler.cli("validate-bundle", str(out))
+    assert r.returncode == 1 and "kernel contract" in r.stderr
