@@ -433,7 +433,29 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
     return eng
 
 
-def serve(engine: BatchEngine, rank: int, world: int, sock_path: str) -> None:
+def agree(resp: Dict, op: str, rank: int, world: int, group) -> Dict:
+    """Cross-rank agreement on the outcome of one request. Every rank executes every request; rank 0 answers the server, so a
+    rank that failed or sampled a different token must not go unnoticed: the ranks exchange (ok, tokens, error) and any
+    failure, or any difference between the token lists of a step, becomes a backend error on rank 0 (which makes the server
+    fail closed). Returns the response rank 0 should send."""
+    mine = (bool(resp.get("ok")), resp.get("tokens"), resp.get("kind"), resp.get("error"))
+    every = [None] * world
+    dist.all_gather_object(every, mine, group=group)
+    for r, (ok, _, kind, err) in enumerate(every):
+        if not ok:
+            if r == rank:
+                return resp
+            return {"ok": False, "kind": kind or "backend", "error": f"rank {r}: {err}"}
+    if op == "step":
+        for r, (_, toks, _, _) in enumerate(every):
+            if toks != every[0][1]:
+                return {"ok": False, "kind": "backend", "error": f"token consensus mismatch: rank 0 produced {every[0][1]}, rank {r} produced {toks}"}
+    return resp
+
+
+def serve(engine, rank: int, world: int, sock_path: str, group=None) -> None:
+    """Request loop of one rank. ``group``: process group for the control traffic (request broadcast and agreement); a gloo
+    group keeps it off the GPU streams."""
     conn = None
     buf = b""
     if rank == 0:
@@ -453,7 +475,7 @@ def serve(engine: BatchEngine, rank: int, world: int, sock_path: str) -> None:
                 req = json.loads(line)
         if world > 1:
             box = [req]
-            dist.broadcast_object_list(box, src=0)
+            dist.broadcast_object_list(box, src=0, group=group)
             req = box[0]
         op = req.get("op")
         try:
@@ -479,6 +501,8 @@ def serve(engine: BatchEngine, rank: int, world: int, sock_path: str) -> None:
             resp = {"ok": False, "kind": "invalid", "error": str(e)}
         except Exception as e:  # noqa: BLE001 - every failure must reach the server as a backend error
             resp = {"ok": False, "kind": "backend", "error": f"{type(e).__name__}: {e}"}
+        if world > 1 and op in ("info", "admit", "step", "release"):
+            resp = agree(resp, op, rank, world, group)
         if rank == 0 and conn is not None:
             try:
                 conn.sendall(json.dumps(resp).encode() + b"\n")
@@ -548,8 +572,9 @@ def main() -> None:
         if world > 1:
             dist.destroy_process_group()
         return
+    ctl = dist.new_group(backend="gloo") if world > 1 else None     # control traffic stays on the CPU
     try:
-        serve(engine, rank, world, args.socket)
+        serve(engine, rank, world, args.socket, ctl)
     finally:
         torch.cuda.synchronize()
         if ropts.audit_dir:
