@@ -572,6 +572,8 @@ def main() -> None:
         if world > 1:
             dist.destroy_process_group()
         return
+    if world > 1:
+        os.environ.setdefault("GLOO_SOCKET_IFNAME", "lo")              # ranks of one node: no host-name lookup for the CPU group
     ctl = dist.new_group(backend="gloo") if world > 1 else None     # control traffic stays on the CPU
     try:
         serve(engine, rank, world, args.socket, ctl)
