@@ -439,6 +439,14 @@ def agree(resp: Dict, op: str, rank: int, world: int, group) -> Dict:
     failure, or any difference between the token lists of a step, becomes a backend error on rank 0 (which makes the server
     fail closed). Returns the response rank 0 should send."""
     mine = (bool(resp.get("ok")), resp.get("tokens"), resp.get("kind"), resp.get("error"))
+    # fast path: one small all-reduce over a digest of (ok, tokens); the details are exchanged only when the digests differ
+    import zlib
+
+    h = zlib.crc32(json.dumps([mine[0], mine[1]]).encode()) if mine[0] else -1 - rank
+    t = torch.tensor([h, -h], dtype=torch.int64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    if mine[0] and int(t[0]) == h and int(t[1]) == -h:
+        return resp
     every = [None] * world
     dist.all_gather_object(every, mine, group=group)
     for r, (ok, _, kind, err) in enumerate(every):
