@@ -461,7 +461,7 @@ def agree(resp: Dict, op: str, rank: int, world: int, group) -> Dict:
     return resp
 
 
-def serve(engine, rank: int, world: int, sock_path: str, group=None) -> None:
+def serve(engine, rank: int, world: int, sock_path: str, group=None, agreement: bool = True) -> None:
     """Request loop of one rank. ``group``: process group for the control traffic (request broadcast and agreement); a gloo
     group keeps it off the GPU streams."""
     conn = None
@@ -509,7 +509,7 @@ def serve(engine, rank: int, world: int, sock_path: str, group=None) -> None:
             resp = {"ok": False, "kind": "invalid", "error": str(e)}
         except Exception as e:  # noqa: BLE001 - every failure must reach the server as a backend error
             resp = {"ok": False, "kind": "backend", "error": f"{type(e).__name__}: {e}"}
-        if world > 1 and op in ("info", "admit", "step", "release"):
+        if world > 1 and agreement and op in ("info", "admit", "step", "release"):
             resp = agree(resp, op, rank, world, group)
         if rank == 0 and conn is not None:
             try:
@@ -584,7 +584,7 @@ def main() -> None:
         os.environ.setdefault("GLOO_SOCKET_IFNAME", "lo")              # ranks of one node: no host-name lookup for the CPU group
     ctl = dist.new_group(backend="gloo") if world > 1 else None     # control traffic stays on the CPU
     try:
-        serve(engine, rank, world, args.socket, ctl)
+        serve(engine, rank, world, args.socket, ctl, ropts.rank_agreement)
     finally:
         torch.cuda.synchronize()
         if ropts.audit_dir:
