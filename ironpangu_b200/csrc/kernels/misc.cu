@@ -112,7 +112,29 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const bf16* x, long ldx, c
   }
 }
 
+// act[t, c] = silu(gu[t, c]) * gu[t, F + c]: the activation of a gate/up projection whose GEMM has no SwiGLU epilogue
+// (the all-gather GEMM of the sequence-parallel block)
+__global__ void __launch_bounds__(256) swiglu_rows_kernel(const bf16* gu, long ldg, bf16* act, long lda, int F) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int t = blockIdx.x;
+  const bf16* g = gu + (long)t * ldg;
+  for (int c = threadIdx.x; c < F / 8; c += blockDim.x) {
+    float a[8], b[8];
+    unpack8(*reinterpret_cast<const uint4*>(g + c * 8), a);
+    unpack8(*reinterpret_cast<const uint4*>(g + F + c * 8), b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = a[i] / (1.f + __expf(-a[i])) * b[i];
+    *reinterpret_cast<uint4*>(act + (long)t * lda + c * 8) = pack8(a);
+  }
+}
+
 }  // namespace
+
+extern "C" int ifab_swiglu_rows_bf16(const void* gu, long ldg, void* act, long lda, int T, int F, void* stream) {
+  if (F % 8 != 0 || ldg % 8 != 0 || lda % 8 != 0) return -1;
+  return launch_chain(swiglu_rows_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)gu, ldg, (bf16*)act, lda, F);
+}
 
 extern "C" int ifab_embedding_bf16(const int32_t* ids, const void* table, void* out, int T, int D, int vocab,
                                    uint32_t* status, void* stream) {

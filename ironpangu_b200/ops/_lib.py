@@ -71,6 +71,7 @@ _SIGS = {
     "ifab_peek": [_P, _P, c_u64],
     "ifab_poke": [_P, _P, c_u64],
     "ifab_embedding_bf16": [_P, _P, _P, c_int, c_int, c_int, _P, _P],
+    "ifab_swiglu_rows_bf16": [_P, c_long, _P, c_long, c_int, c_int, _P],
     "ifab_rmsnorm_bf16": [_P, c_long, _P, _P, c_long, c_int, c_int, c_float, c_int, _P],
     "ifab_gemv_bf16": [_P, c_long, _P, _P, c_float, c_int, _P, c_long, _P, c_long, c_int, c_int, c_int, c_int, c_int, _P],
     "ifab_gemv_allreduce_bf16": [_P, c_long, _P, _P, c_long, _P, c_long, _P, c_int, c_int, c_int, C.POINTER(IfabFabric), _P],

@@ -51,6 +51,16 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5, zero_centered: 
     return out
 
 
+def swiglu_rows(gu: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gu[:, :F]) * gu[:, F:]`` for a gate/up projection ``[T, 2F]`` (gate columns first)."""
+    T, F2 = gu.shape
+    F = F2 // 2
+    if out is None:
+        out = torch.empty(T, F, dtype=BF16, device=gu.device)
+    check(_lib.load().ifab_swiglu_rows_bf16(gu.data_ptr(), _rows(gu), out.data_ptr(), _rows(out), T, F, _stream()), "swiglu_rows")
+    return out
+
+
 def gemv(x: torch.Tensor, w: torch.Tensor, *, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-5,
          zero_centered: bool = False, residual: Optional[torch.Tensor] = None, swiglu: bool = False,
          out_f32: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:

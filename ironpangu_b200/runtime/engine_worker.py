@@ -405,6 +405,7 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
             from ironpangu_b200.models.dense_prefill import DensePrefill
 
             dprefill = DensePrefill(ddec, max_rows=args.prefill_chunk)
+            dprefill.sequence_parallel = bool(ro is not None and ro.sequence_parallel)
             mark("prefill", "activation buffers of the matrix-matrix prompt path")
         eng = BatchEngine(ddec, f"ifab-{args.model}", args.max_model_len, dcfg.vocab, eos=-1, greedy_only=args.greedy_only, prefill=dprefill,
                           token_budget=args.max_num_batched_tokens, use_graphs=not args.no_graphs)

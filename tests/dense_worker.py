@@ -60,11 +60,54 @@ def main():
     again = pre.forward_rows(step, pos, slots, torch.tensor([0, 1, 2], device="cuda"))      # same rows: replay of the captured graph
     torch.cuda.synchronize()
     assert torch.equal(again, got)
+    if world > 1:
+        sequence_parallel_check(cfg, full, fab, rank, world)
     assert fab.status() == 0
     print(f"rank {rank}: ok dense tensor parallel", flush=True)
     fab.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def sequence_parallel_check(cfg, full, fab, rank, world):
+    """One chunk of 128 rows per rank through the sequence-parallel layer stack (all-gather GEMM -> attention -> GEMM +
+    reduce-scatter, residual sharded by rows) against the all-reduce path: same next token, logits and caches."""
+    from ironpangu_b200.models import dense_gqa as G
+    from ironpangu_b200.models.dense_prefill import DensePrefill
+
+    m = 128 * world
+    mk = lambda: G.DenseDecoder(cfg, G.shard_weights(cfg, full, rank, world, "cuda"), fab, max_tokens=8, max_context=m,
+                                num_slots=1, keep_logits=True)
+    c1, c2 = mk(), mk()
+    toks = torch.randint(0, cfg.vocab, (m,), generator=torch.Generator().manual_seed(9)).to(torch.int32).cuda()
+    p1, p2 = DensePrefill(c1, max_rows=m, attn_rows=32), DensePrefill(c2, max_rows=m, attn_rows=32)
+    assert p2.can_sequence_parallel(m) and not p2.can_sequence_parallel(m - 1)
+    id1 = p1.forward(toks, 0, 0).clone()
+    want = c1.logits[0].clone()
+    for _ in range(2):                                  # the second call reuses shards, flags and counters one epoch later
+        id2 = p2.forward(toks, 0, 0, sequence_parallel=True).clone()
+        torch.cuda.synchronize()
+        torch.testing.assert_close(c2.logits[0], want, rtol=3e-2, atol=3e-2)
+        assert int(id1) == int(id2)
+    for l in range(cfg.layers):
+        torch.testing.assert_close(c2.k_cache[l].float(), c1.k_cache[l].float(), rtol=3e-2, atol=3e-2)
+        torch.testing.assert_close(c2.v_cache[l].float(), c1.v_cache[l].float(), rtol=3e-2, atol=3e-2)
+    if os.environ.get("DENSE_SP_BENCH"):
+        for name, run in (("all-reduce", lambda: p1.forward(toks, 0, 0)), ("sequence-parallel", lambda: p2.forward(toks, 0, 0, sequence_parallel=True))):
+            for _ in range(3):
+                run()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(10):
+                run()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / 10], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if rank == 0:
+                print(f"prefill chunk of {m} rows, {name}: {t.item():.3f} ms (max over ranks)", flush=True)
 
 
 if __name__ == "__main__":

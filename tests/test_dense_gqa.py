@@ -159,3 +159,17 @@ def test_tensor_core_prefill_matches_the_decode_path_and_the_oracle():
     assert int(nxt[0]) == int(ref[149].argmax()) or float(top2[0] - top2[1]) < 5e-2
     assert fab.status() == 0
     fab.close()
+
+
+@pytest.mark.gpu
+def test_swiglu_rows_matches_torch():
+    from ironpangu_b200.ops import decode as K
+    torch.manual_seed(3)
+    gu = (torch.randn(37, 2 * 264, device="cuda") * 2).to(torch.bfloat16)
+    got = K.swiglu_rows(gu)
+    g, u = gu[:, :264].float(), gu[:, 264:].float()
+    torch.testing.assert_close(got.float(), (torch.nn.functional.silu(g) * u).to(torch.bfloat16).float(), rtol=2e-2, atol=2e-2)
+    # a strided view (columns of a wider buffer) goes through the row strides
+    wide = torch.zeros(5, 1024, dtype=torch.bfloat16, device="cuda")
+    wide[:, :528] = gu[:5]
+    torch.testing.assert_close(K.swiglu_rows(wide[:, :528]).float(), got[:5].float(), rtol=0, atol=0)
