@@ -191,12 +191,15 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
   } else if (warp >= 2) {
     // ---- epilogue warps: exchange tile i while the main loop of tile i + 1 runs ----
     const int q = warp & 3, trow = q * 32 + lane, et = threadIdx.x - 64;
-    if (a.scatter && epoch > 2) {
-      // Reduce-scatter calls do not end with a gather, so nothing else keeps a fast rank from running two calls ahead and
-      // overwriting staging slots (same parity half) that a slow owner is still reducing: wait until every peer has
-      // finished the call that last used this half.
-      if (et < world && et != rank &&
-          !wait_flag_bounded(flags(rank) + (size_t)a.fv.flag_half_words - world + et, epoch - 2, a.fv.spin_limit))
+    if (a.scatter) {
+      // Reduce-scatter calls do not end with a gather, so nothing else keeps a fast rank from overwriting staging slots of
+      // this parity half that a slow owner is still reducing. Every rank leaves, per half, the epoch of the last call of this
+      // kernel it finished there (its own copy in slot `rank`, one in every peer's slot table); all ranks make the same
+      // calls, so the previous user of this half has the same epoch everywhere: wait until every peer has finished it.
+      // (Other fused kernels advance the shared call counter too, so that call is not simply "two epochs ago".)
+      const uint64_t* slots = flags(rank) + (size_t)a.fv.flag_half_words - world;
+      const uint64_t prev = *reinterpret_cast<const volatile uint64_t*>(slots + rank);
+      if (prev > 0 && et < world && et != rank && !wait_flag_bounded(slots + et, prev, a.fv.spin_limit))
         atomicOr(a.fv.status, IFAB_STATUS_PEER_TIMEOUT);
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
@@ -355,8 +358,9 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
     }
   }
   __syncthreads();
-  // "this rank has finished call `epoch`" (it no longer reads the staging slots of this parity half), for the guard above
-  if (world > 1 && (int)threadIdx.x < world && (int)threadIdx.x != rank) {
+  // "this rank has finished call `epoch`" (it no longer reads the staging slots of this parity half), for the guard above:
+  // to every peer, and to the own slot table (the next call on this half reads which epoch to wait for)
+  if (world > 1 && (int)threadIdx.x < world) {
     __threadfence_system();
     st_release_sys(flags(threadIdx.x) + (size_t)a.fv.flag_half_words - world + rank, epoch);
   }

@@ -62,7 +62,7 @@ def main():
     assert torch.equal(again, got)
     if world > 1:
         sequence_parallel_check(cfg, full, fab, rank, world)
-    assert fab.status() == 0
+    assert fab.status() == 0, hex(fab.status())
     print(f"rank {rank}: ok dense tensor parallel", flush=True)
     fab.close()
     if world > 1:

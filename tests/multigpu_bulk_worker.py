@@ -48,6 +48,18 @@ def main():
             dist.barrier()
             torch.testing.assert_close(ysh.float(), ref[rank * rows:(rank + 1) * rows], rtol=2e-2, atol=3e-2)
             assert torch.equal(ysh, y[rank * rows:(rank + 1) * rows]), "reduce-scatter and all-reduce forms disagree"
+            # other fused kernels advance the fabric's call counter between reduce-scatter calls (the head of a decoder
+            # does): consecutive reduce-scatters then land on the same staging half or skip one, and the guard against a
+            # rank running ahead must still find the previous user of the half (no peer timeout, same result)
+            from ironpangu_b200.ops.decode import gemv_allreduce
+            xs, ws = torch.randn(2, 64, device="cuda").to(BF16), torch.randn(128, 64, device="cuda").to(BF16)
+            for k in (1, 2, 1, 3):
+                for _ in range(k):
+                    gemv_allreduce(xs, ws, fab)
+                ysh2 = gemm_reduce_scatter(al, bl, fab, residual=shard_res)
+            torch.cuda.synchronize()
+            dist.barrier()
+            assert torch.equal(ysh2, ysh) and fab.status() == 0
     assert fab.status() == 0
     print(f"rank {rank}: ok gemm_allreduce bulk", flush=True)
 
