@@ -434,37 +434,86 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
     return eng
 
 
-def agree(resp: Dict, op: str, rank: int, world: int, group) -> Dict:
-    """Cross-rank agreement on the outcome of one request. Every rank executes every request; rank 0 answers the server, so a
-    rank that failed or sampled a different token must not go unnoticed: the ranks exchange (ok, tokens, error) and any
-    failure, or any difference between the token lists of a step, becomes a backend error on rank 0 (which makes the server
-    fail closed). Returns the response rank 0 should send."""
-    mine = (bool(resp.get("ok")), resp.get("tokens"), resp.get("kind"), resp.get("error"))
-    # fast path: one small all-reduce over a digest of (ok, tokens); the details are exchanged only when the digests differ
-    import zlib
+class Agreement:
+    """Cross-rank agreement on the outcome of every request. Every rank executes every request; rank 0 answers the server, so
+    a rank that failed or sampled a different token must not go unnoticed: any failure, or any difference between the token
+    lists of a step, becomes a backend error on rank 0 (which makes the server fail closed).
 
-    h = zlib.crc32(json.dumps([mine[0], mine[1]]).encode()) if mine[0] else -1 - rank
-    t = torch.tensor([h, -h], dtype=torch.int64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
-    if mine[0] and int(t[0]) == h and int(t[1]) == -h:
+    The common case costs one small all-reduce over a digest of (ok, tokens); the details (who failed, which tokens) are
+    exchanged only when the digests differ. Modes:
+      strict    the ranks agree BEFORE rank 0 answers: nothing a rank disagreed on ever reaches a client, and the slowest
+                rank's host work plus one CPU all-reduce sit on the critical path of every step;
+      deferred  the all-reduce of request k is started asynchronously and checked when request k + 1 has been executed, so
+                it overlaps the next step; a disagreement on request k turns the answer to request k + 1 (and every later
+                one) into the backend error - at most one answer leaves before the failure is reported."""
+
+    def __init__(self, rank: int, world: int, group, mode: str = "strict"):
+        assert mode in ("strict", "deferred")
+        self.rank, self.world, self.group, self.mode = rank, world, group, mode
+        self.pending = None            # (work, tensor, digest, mine, op, resp) of the request whose all-reduce is in flight
+        self.failed: Optional[Dict] = None
+
+    def _start(self, mine, async_op: bool):
+        import zlib
+
+        h = zlib.crc32(json.dumps([mine[0], mine[1]]).encode()) if mine[0] else -1 - self.rank
+        t = torch.tensor([h, -h], dtype=torch.int64)
+        work = dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group, async_op=async_op)
+        return work, t, h
+
+    def _verdict(self, t, h, mine, op: str, resp: Dict) -> Dict:
+        """``resp`` when all digests were equal, else the error every rank derives from the exchanged details."""
+        if mine[0] and int(t[0]) == h and int(t[1]) == -h:
+            return resp
+        every = [None] * self.world
+        dist.all_gather_object(every, mine, group=self.group)
+        for r, (ok, _, kind, err) in enumerate(every):
+            if not ok:
+                if r == self.rank:
+                    return resp
+                return {"ok": False, "kind": kind or "backend", "error": f"rank {r}: {err}"}
+        if op == "step":
+            for r, (_, toks, _, _) in enumerate(every):
+                if toks != every[0][1]:
+                    return {"ok": False, "kind": "backend",
+                            "error": f"token consensus mismatch: rank 0 produced {every[0][1]}, rank {r} produced {toks}"}
         return resp
-    every = [None] * world
-    dist.all_gather_object(every, mine, group=group)
-    for r, (ok, _, kind, err) in enumerate(every):
-        if not ok:
-            if r == rank:
-                return resp
-            return {"ok": False, "kind": kind or "backend", "error": f"rank {r}: {err}"}
-    if op == "step":
-        for r, (_, toks, _, _) in enumerate(every):
-            if toks != every[0][1]:
-                return {"ok": False, "kind": "backend", "error": f"token consensus mismatch: rank 0 produced {every[0][1]}, rank {r} produced {toks}"}
-    return resp
+
+    def check(self, resp: Dict, op: str) -> Dict:
+        """The response rank 0 should send for this request."""
+        mine = (bool(resp.get("ok")), resp.get("tokens"), resp.get("kind"), resp.get("error"))
+        if self.mode == "strict":
+            _, t, h = self._start(mine, False)
+            return self._verdict(t, h, mine, op, resp)
+        if self.failed is not None:                 # every rank reached this state at the same request: no more collectives
+            return self.failed
+        late = self.finish()
+        if late is not None:                        # the digests of the previous request differed: every rank sees that here
+            self.failed = late
+            return late
+        self.pending = self._start(mine, True) + (mine, op, resp)
+        return resp
+
+    def finish(self) -> Optional[Dict]:
+        """Wait for the all-reduce in flight (deferred mode); returns the error it revealed, if any."""
+        if self.pending is None:
+            return None
+        work, t, h, mine, op, resp = self.pending
+        self.pending = None
+        work.wait()
+        v = self._verdict(t, h, mine, op, resp)
+        if v is resp and resp.get("ok"):
+            return None
+        if v is resp:                               # this rank's own failure: rank 0 already answered with it
+            v = {"ok": False, "kind": resp.get("kind") or "backend", "error": f"rank {self.rank}: {resp.get('error')}"}
+        return {"ok": False, "kind": v.get("kind") or "backend", "error": "an earlier request: " + str(v.get("error"))}
 
 
-def serve(engine, rank: int, world: int, sock_path: str, group=None, agreement: bool = True) -> None:
+def serve(engine, rank: int, world: int, sock_path: str, group=None, agreement="strict") -> None:
     """Request loop of one rank. ``group``: process group for the control traffic (request broadcast and agreement); a gloo
-    group keeps it off the GPU streams."""
+    group keeps it off the GPU streams. ``agreement``: "strict", "deferred" or "off" (see :class:`Agreement`)."""
+    agreement = {True: "strict", False: "off"}.get(agreement, agreement)
+    agreeing = Agreement(rank, world, group, agreement) if world > 1 and agreement != "off" else None
     conn = None
     buf = b""
     if rank == 0:
@@ -510,8 +559,12 @@ def serve(engine, rank: int, world: int, sock_path: str, group=None, agreement: 
             resp = {"ok": False, "kind": "invalid", "error": str(e)}
         except Exception as e:  # noqa: BLE001 - every failure must reach the server as a backend error
             resp = {"ok": False, "kind": "backend", "error": f"{type(e).__name__}: {e}"}
-        if world > 1 and agreement and op in ("info", "admit", "step", "release"):
-            resp = agree(resp, op, rank, world, group)
+        if agreeing is not None and op in ("info", "admit", "step", "release"):
+            resp = agreeing.check(resp, op)
+        elif agreeing is not None and op == "shutdown":
+            late = agreeing.finish()
+            if late is not None:
+                resp = late
         if rank == 0 and conn is not None:
             try:
                 conn.sendall(json.dumps(resp).encode() + b"\n")

@@ -27,7 +27,7 @@ class RuntimeOptions:
     spin_limit: int = 4_000_000          # polls a kernel waits for a peer before it reports a timeout
     bulk_collectives: bool = True        # fused GEMM + all-reduce for prompt chunks (off: GEMM, then pull all-reduce)
     sequence_parallel: bool = False      # dense prompt chunks keep the residual stream sharded by rows (all-gather GEMM / GEMM + reduce-scatter)
-    rank_agreement: bool = True          # ranks of an engine worker compare the outcome of every request before rank 0 answers
+    rank_agreement: str = "strict"       # ranks of an engine worker compare the outcome of every request: strict (before rank 0 answers), deferred (overlapped with the next request), off
     audit_dir: str = ""                  # where engines write their audit JSON at shutdown ("" = nowhere)
     trace_dir: str = ""                  # where step traces go ("" = off)
 
@@ -88,6 +88,11 @@ class RuntimeOptions:
             raise ValueError("prefix_cache_slots must be in [0, 4096]")
         if not 1000 <= self.spin_limit <= 1 << 31:
             raise ValueError("spin_limit must be in [1000, 2^31]")
+        mode = {"1": "strict", "true": "strict", "on": "strict", "yes": "strict", "0": "off", "false": "off", "no": "off"}.get(
+            str(self.rank_agreement).strip().lower(), str(self.rank_agreement).strip().lower())
+        if mode not in ("strict", "deferred", "off"):
+            raise ValueError("rank_agreement must be strict, deferred or off")
+        self.rank_agreement = mode
         if self.kv_int8 and self.fused_head:
             raise ValueError("fused_head reads bf16 cache rows: it cannot be forced together with kv_int8")
         return self

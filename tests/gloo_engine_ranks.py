@@ -1,5 +1,5 @@
 """Two CPU ranks (gloo) run the engine worker's request loop over a fake engine; rank 0 talks to the test through a Unix
-socket. Scenario from argv: agree | mismatch | raise. Run under torch.distributed.run."""
+socket. Scenario from argv: agree | mismatch | raise, then the agreement mode (strict | deferred). Run under torch.distributed.run."""
 import os
 import sys
 
@@ -41,7 +41,8 @@ def main():
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dist.init_process_group("gloo")
-    serve(FakeEngine(rank, sys.argv[1]), rank, world, os.environ["IFAB_ENGINE_SOCKET"], None)
+    mode = sys.argv[2] if len(sys.argv) > 2 else "strict"
+    serve(FakeEngine(rank, sys.argv[1]), rank, world, os.environ["IFAB_ENGINE_SOCKET"], None, mode)
     dist.destroy_process_group()
     print(f"rank {rank} left the loop", flush=True)
 

@@ -18,7 +18,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _session(tmp_path, scenario, requests):
+def _session(tmp_path, scenario, requests, mode="strict"):
     path = str(tmp_path / "engine.sock")
     srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
     srv.bind(path)
@@ -26,7 +26,7 @@ def _session(tmp_path, scenario, requests):
     srv.settimeout(120)
     env = dict(os.environ, IFAB_ENGINE_SOCKET=path)
     proc = subprocess.Popen([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-                             "--master-port", str(_free_port()), os.path.join(HERE, "gloo_engine_ranks.py"), scenario],
+                             "--master-port", str(_free_port()), os.path.join(HERE, "gloo_engine_ranks.py"), scenario, mode],
                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
     try:
         conn, _ = srv.accept()
@@ -43,6 +43,8 @@ def _session(tmp_path, scenario, requests):
         if proc.poll() is None:
             proc.kill()
         srv.close()
+        if os.path.exists(path):
+            os.unlink(path)
     assert proc.returncode == 0, out[-3000:]
     assert out.count("left the loop") == 2          # both ranks saw the shutdown
     return answers
@@ -69,3 +71,16 @@ def test_a_rank_that_samples_another_token_is_reported(tmp_path):
 def test_a_rank_that_fails_is_reported_by_rank_zero(tmp_path):
     a = _session(tmp_path, "raise", SCRIPT)
     assert a[2]["ok"] and a[3]["ok"] is False and a[3]["kind"] == "backend" and "rank 1" in a[3]["error"] and "rank-local failure" in a[3]["error"]
+
+
+def test_deferred_agreement_reports_one_request_later_and_stays_failed(tmp_path):
+    """Deferred mode overlaps the comparison of request k with request k + 1: the answer of the step the ranks disagreed on
+    has left already, the next answer (and every later one) is the backend error."""
+    script = SCRIPT[:4] + [STEP, STEP, {"op": "shutdown"}]
+    a = _session(tmp_path, "agree", script, "deferred")
+    assert all(x["ok"] for x in a)
+    for scenario, needle in (("mismatch", "consensus"), ("raise", "rank-local failure")):
+        a = _session(tmp_path, scenario, script, "deferred")
+        assert a[2]["ok"] and a[3]["ok"]                       # the second step is the one rank 1 spoils; rank 0 has answered it
+        assert a[4]["ok"] is False and a[4]["kind"] == "backend" and "earlier request" in a[4]["error"] and needle in a[4]["error"]
+        assert a[5]["ok"] is False and a[5]["error"] == a[4]["error"]
