@@ -27,7 +27,7 @@ class RuntimeOptions:
     spin_limit: int = 4_000_000          # polls a kernel waits for a peer before it reports a timeout
     bulk_collectives: bool = True        # fused GEMM + all-reduce for prompt chunks (off: GEMM, then pull all-reduce)
     sequence_parallel: bool = False      # dense prompt chunks keep the residual stream sharded by rows (all-gather GEMM / GEMM + reduce-scatter)
-    rank_agreement: str = "strict"       # ranks of an engine worker compare the outcome of every request: strict (before rank 0 answers), deferred (overlapped with the next request), off
+    rank_agreement: str = "deferred"     # ranks of an engine worker compare the outcome of every request: strict (before rank 0 answers), deferred (overlapped with the next request), off
     audit_dir: str = ""                  # where engines write their audit JSON at shutdown ("" = nowhere)
     trace_dir: str = ""                  # where step traces go ("" = off)
 
