@@ -215,37 +215,70 @@ __global__ void __launch_bounds__(256) moe_down_fp8_allreduce_kernel(Down8Params
   for (int t = 0; t < T; ++t) {
     if (t < p.T) {
       __syncthreads();
-      if (threadIdx.x == 0) {
-        int n = 0, c = 0;
-        for (int slot = 0; slot <= p.topk; ++slot) {
-          if (slot < p.topk) {
-            const int e = p.ids[t * p.topk + slot];
-            if (e < p.e0 || e >= p.e0 + p.e_local) continue;
-            s_w[n] = p.w_down + (size_t)(e - p.e0) * p.D * p.F;
-            s_sc[n] = p.s_down + (size_t)(e - p.e0) * p.D * ((p.F + QBLOCK - 1) / QBLOCK);
-            s_g[n] = p.wts[t * p.topk + slot];
-            s_k[n] = p.F;
-          } else {
-            if (p.w_sdown == nullptr) continue;
-            s_w[n] = p.w_sdown;
-            s_sc[n] = p.s_sdown;
-            s_g[n] = 1.f;
-            s_k[n] = p.Fs;
-          }
-          s_slot[n] = slot;
-          s_cbeg[n] = c;
-          c += s_k[n] >> 4;
-          ++n;
+      if (warp == 0) {
+        // route table, one slot per lane (ids and scores of all slots requested at once), compacted with a ballot
+        const int slot = lane;
+        bool local = false;
+        const uint8_t* w = nullptr;
+        const float* sc = nullptr;
+        float g = 0.f;
+        int k = 0;
+        if (slot < p.topk) {
+          const int e = p.ids[t * p.topk + slot];
+          local = e >= p.e0 && e < p.e0 + p.e_local;
+          const size_t el = local ? (size_t)(e - p.e0) : 0;
+          w = p.w_down + el * p.D * p.F;
+          sc = p.s_down + el * p.D * ((p.F + QBLOCK - 1) / QBLOCK);
+          g = p.wts[t * p.topk + slot];
+          k = p.F;
+        } else if (slot == p.topk && p.w_sdown != nullptr) {
+          local = true;
+          w = p.w_sdown;
+          sc = p.s_sdown;
+          g = 1.f;
+          k = p.Fs;
         }
-        s_cbeg[n] = c;
-        s_n = n;
+        const unsigned m = __ballot_sync(0xffffffffu, local);
+        const int n = __popc(m & ((1u << lane) - 1u));
+        if (local) {
+          s_w[n] = w;
+          s_sc[n] = sc;
+          s_g[n] = g;
+          s_k[n] = k;
+          s_slot[n] = slot;
+          s_cbeg[n] = n * (p.F >> 4);              // every route before the shared expert spans F
+        }
+        if (lane == 0) {
+          const int total_n = __popc(m), shared = (int)((m >> p.topk) & 1u);
+          s_cbeg[total_n] = (total_n - shared) * (p.F >> 4) + shared * (p.Fs >> 4);
+          s_n = total_n;
+        }
       }
       __syncthreads();
       const int n_routes = s_n;
-      for (int i = 0; i < n_routes; ++i) {
-        const bf16* arow = p.act + ((size_t)t * (p.topk + 1) + s_slot[i]) * p.F;
-        for (int c = threadIdx.x; c < (s_k[i] >> 3); c += blockDim.x)
-          *reinterpret_cast<uint4*>(as + (size_t)i * p.F + c * 8) = bf16x8_to_scaled_f16(*reinterpret_cast<const uint4*>(arow + c * 8));
+      {
+        // activation rows of the local routes -> scaled f16 in shared memory: eight loads in flight per thread
+        const int kch0 = max(1, p.F >> 3);
+        const int shared_last = (n_routes > 0 && s_slot[n_routes - 1] == p.topk) ? 1 : 0;
+        const int total_c = (n_routes - shared_last) * kch0 + shared_last * (p.Fs >> 3);
+        constexpr int SB = 8;
+        for (int q0 = threadIdx.x; q0 < total_c; q0 += (int)blockDim.x * SB) {
+          uint4 v[SB];
+          int dst[SB];
+#pragma unroll
+          for (int j = 0; j < SB; ++j) {
+            const int q = q0 + (int)blockDim.x * j;
+            dst[j] = -1;
+            if (q < total_c) {
+              const int i = min(q / kch0, n_routes - 1), c = q - i * kch0;
+              v[j] = *reinterpret_cast<const uint4*>(p.act + ((size_t)t * (p.topk + 1) + s_slot[i]) * p.F + c * 8);
+              dst[j] = i * p.F + c * 8;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < SB; ++j)
+            if (dst[j] >= 0) *reinterpret_cast<uint4*>(as + dst[j]) = bf16x8_to_scaled_f16(v[j]);
+        }
       }
       __syncthreads();
       float total[R];
