@@ -29,3 +29,13 @@ def test_unknown_names_and_bad_values_are_errors():
         RuntimeOptions.from_env({}, ["spin_limit=5"])
     with pytest.raises(ValueError, match="kv_int8"):
         RuntimeOptions.from_env({}, ["kv_int8=1", "fused_head=1"])
+
+
+def test_rank_agreement_modes_and_boolean_spellings():
+    from ironpangu_b200.runtime.options import RuntimeOptions
+    assert RuntimeOptions().validate().rank_agreement == "deferred"
+    for text, want in (("0", "off"), ("false", "off"), ("1", "strict"), ("on", "strict"), ("Strict", "strict"), ("deferred", "deferred")):
+        assert RuntimeOptions.from_env({"IFAB_RANK_AGREEMENT": text}).rank_agreement == want
+    with pytest.raises(ValueError):
+        RuntimeOptions.from_env({}, ["rank_agreement=sometimes"])
+    assert RuntimeOptions.from_env({}, ["sequence_parallel=1"]).sequence_parallel is True
