@@ -138,7 +138,6 @@ def main():
         if args.impl != "native":
             raise SystemExit("--model dense2b runs on the native path only")
         dec = G.DenseDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1)
-        args.prefill = "decode"
     elif args.impl == "native":
         dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1,
                             persistent=bool(args.persistent), expert_fp8=args.expert_fp8, kv_int8=args.kv_int8)
@@ -148,7 +147,10 @@ def main():
         from baseline.nccl_cublas import NcclCublasDecoder
         dec = NcclCublasDecoder(cfg, weights, rank, world, max_tokens=8, max_context=max_context)
     pre = None
-    if args.impl == "native" and args.prefill == "gemm":
+    if dense and args.prefill == "gemm":
+        from ironpangu_b200.models.dense_prefill import DensePrefill
+        pre = DensePrefill(dec, max_rows=min(512, args.context))
+    elif args.impl == "native" and args.prefill == "gemm":
         from ironpangu_b200.models.mla_moe_prefill import MlaMoePrefill
         pre = MlaMoePrefill(dec, max_rows=min(512, args.context))
     eng = DecodeEngine(dec, prefill=pre)
