@@ -84,3 +84,10 @@ def test_deferred_agreement_reports_one_request_later_and_stays_failed(tmp_path)
         assert a[2]["ok"] and a[3]["ok"]                       # the second step is the one rank 1 spoils; rank 0 has answered it
         assert a[4]["ok"] is False and a[4]["kind"] == "backend" and "earlier request" in a[4]["error"] and needle in a[4]["error"]
         assert a[5]["ok"] is False and a[5]["error"] == a[4]["error"]
+
+
+def test_deferred_agreement_reports_at_shutdown_when_no_request_follows(tmp_path):
+    """The comparison still in flight when the server says goodbye is waited for: its error rides on the shutdown answer."""
+    a = _session(tmp_path, "mismatch", SCRIPT[:4] + [{"op": "shutdown"}], "deferred")
+    assert a[2]["ok"] and a[3]["ok"]
+    assert a[4]["ok"] is False and "earlier request" in a[4]["error"] and "consensus" in a[4]["error"]
