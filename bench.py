@@ -113,6 +113,10 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # NCCL only carries the bootstrap, the barriers and the max-over-ranks of the timing here (the model's collectives are
+        # the fabric kernels over peer memory), so its in-switch reduction buys nothing: keep it off, as in every measured run
+        if args.impl == "native":               # the NCCL + cuBLAS arm keeps NCCL's defaults: its collectives are NCCL's
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
 
     from ironpangu_b200.models.mla_moe import MlaMoeConfig, MlaMoeDecoder, random_rank_weights
