@@ -53,3 +53,71 @@ def test_reduce_scatter_schedule_visits_owners_in_ring_order(world, per_rank):
             at_step.setdefault(j, []).append(block[0])
     for j, targets in at_step.items():
         assert sorted(targets) == list(range(world))   # one sender per destination at every step of the ring
+
+
+# ---- the reduce-scatter form's guard against a rank running ahead, restated as a small state machine -------------------------
+# Calls are numbered by one counter that every fused kernel of the fabric advances ("S" = GEMM + reduce-scatter, "O" = any other
+# fused kernel, e.g. the head's cross-rank argmax). An S call of epoch e pushes partial tiles into the owners' staging half
+# e & 1, so before it starts every peer must have finished the PREVIOUS S call that used that half. Each rank leaves, per half,
+# the epoch of the last S call it finished, in its own slot table and in every peer's, and an S call waits until every peer
+# reports the epoch the rank itself last finished on that half. In this model (as in the kernels) finishing ANY fused call needs
+# a push from every peer, which already keeps ranks within one call of each other: the invariant holds with or without the
+# guard, so what the guard owes is that it never blocks - whatever other kernels advance the counter in between.
+import random
+
+
+def _simulate(kinds, world, rule, seed):
+    rng = random.Random(seed)
+    n = len(kinds)
+    pc = [0] * world                     # index of the call a rank is in
+    started = [False] * world
+    slot = [[[0] * world for _ in range(2)] for _ in range(world)]        # slot[r][half][q]
+    prev_same_half = {}
+    last = {0: None, 1: None}
+    for i, k in enumerate(kinds):
+        if k == "S":
+            prev_same_half[i] = last[(i + 1) & 1]
+            last[(i + 1) & 1] = i
+    for _ in range(200 * n * world):
+        if all(p == n for p in pc):
+            return True
+        r = rng.randrange(world)
+        i = pc[r]
+        if i == n:
+            continue
+        e, h = i + 1, (i + 1) & 1
+        if not started[r]:
+            if kinds[i] == "S":
+                if rule == "none":
+                    ok = True
+                elif rule == "two_epochs_ago":
+                    ok = e <= 2 or all(slot[r][h][q] >= e - 2 for q in range(world) if q != r)
+                else:
+                    ok = all(slot[r][h][q] >= slot[r][h][r] for q in range(world) if q != r)
+                if not ok:
+                    continue
+                j = prev_same_half[i]
+                if j is not None:            # the invariant the guard exists for
+                    assert all(pc[q] > j for q in range(world)), f"rank {r} started call {i} while a peer still reduces call {j}"
+            started[r] = True
+        elif all(pc[q] > i or (pc[q] == i and started[q]) for q in range(world)):      # finishing needs every peer's push
+            if kinds[i] == "S":
+                for q in range(world):
+                    slot[q][h][r] = e
+            pc[r], started[r] = i + 1, False
+    return False
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_reduce_scatter_guard_holds_its_invariant_and_never_blocks(world):
+    rng = random.Random(7)
+    for trial in range(30):
+        kinds = [rng.choice("SSO") for _ in range(rng.randrange(4, 24))]
+        assert _simulate(kinds, world, "previous_user", trial), kinds
+        assert _simulate(kinds, world, "none", trial), kinds          # the exchange itself keeps the staging halves safe
+
+
+def test_waiting_for_the_call_two_epochs_ago_blocks_once_other_kernels_interleave():
+    assert _simulate(list("SSSSSS"), 2, "two_epochs_ago", 0)               # back-to-back calls: the old rule was enough
+    assert not _simulate(list("SSOSS"), 2, "two_epochs_ago", 0)            # call 5 waits for an epoch-3 report nobody makes
+    assert _simulate(list("SSOSS"), 2, "previous_user", 0)
