@@ -192,8 +192,9 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_allreduce_kernel(const __grid_
     // ---- epilogue warps: exchange tile i while the main loop of tile i + 1 runs ----
     const int q = warp & 3, trow = q * 32 + lane, et = threadIdx.x - 64;
     if (a.scatter) {
-      // Reduce-scatter calls do not end with a gather, so nothing else keeps a fast rank from overwriting staging slots of
-      // this parity half that a slow owner is still reducing. Every rank leaves, per half, the epoch of the last call of this
+      // Reduce-scatter calls do not end with a gather; what keeps a fast rank from overwriting staging slots of this parity
+      // half that a slow owner is still reducing is that finishing any call needs a push from every peer. This explicit check
+      // states that condition instead of relying on it. Every rank leaves, per half, the epoch of the last call of this
       // kernel it finished there (its own copy in slot `rank`, one in every peer's slot table); all ranks make the same
       // calls, so the previous user of this half has the same epoch everywhere: wait until every peer has finished it.
       // (Other fused kernels advance the shared call counter too, so that call is not simply "two epochs ago".)
