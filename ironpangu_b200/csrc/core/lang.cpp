@@ -522,7 +522,18 @@ class Expander {
         if (v.kind != Value::Kind::Tensor) err_at(a.second->pos, "expected tensor/graph handle as positional argument of " + f);
         n.inputs.push_back(v.text);
       } else {
-        Value v = literal(eval(*a.second, env, prefix, hint, site), site);
+        // an attribute value that is a bare word no binding claims (a dtype, a cache layout, a selection mode) is the
+        // word itself; the checker decides whether the operator knows it
+        const Expr& ae = *a.second;
+        Value v;
+        if (ae.kind == Expr::Kind::Name && !env.count(ae.text) && ae.text.find('.') == std::string::npos &&
+            ae.text != "true" && ae.text != "false") {
+          tick(ae.pos);
+          v.kind = Value::Kind::String;
+          v.text = ae.text;
+        } else {
+          v = literal(eval(ae, env, prefix, hint, site), site);
+        }
         for (auto& kv : n.attrs)
           if (kv.first == a.first) err_at(a.second->pos, "duplicate attribute " + a.first);
         n.attrs.emplace_back(a.first, render(v));

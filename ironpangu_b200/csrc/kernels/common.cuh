@@ -165,7 +165,26 @@ struct FabricView {
   uint32_t flag_half_words;   // flag words of one parity half
   uint32_t ll_half_bytes;     // one parity half of the tagged-store area (used only by oneshot_ar.cuh)
   uint64_t ll_offset;         // its byte offset from data[r]
+  char* mc;                   // multicast mapping of the block (NVLS), or nullptr
 };
+
+// NVLink multicast (NVLS): one store that the switch delivers to the same offset of every rank's block
+__device__ __forceinline__ void multimem_st_u64(uint64_t* mc_addr, uint64_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.u64 [%0], %1;" ::"l"(mc_addr), "l"(v) : "memory");
+}
+// the sum over all ranks of the four floats at this offset, reduced inside the switch
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc_addr) {
+  float4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w)
+               : "l"(mc_addr)
+               : "memory");
+  return r;
+}
+__device__ __forceinline__ void multimem_st_f32x4(float* mc_addr, const float4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
 
 // host: build the by-value device view from the C descriptor
 inline int fabric_view(const IfabFabric* f, FabricView* v) {
@@ -183,6 +202,7 @@ inline int fabric_view(const IfabFabric* f, FabricView* v) {
   v->flag_half_words = f->flag_half_words;
   v->ll_half_bytes = f->ll_half_bytes;
   v->ll_offset = f->ll_offset;
+  v->mc = (char*)f->mc;
   return 0;
 }
 

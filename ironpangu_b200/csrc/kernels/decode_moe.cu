@@ -15,13 +15,13 @@
 // expert_reduce and allreduce (native/src/token_executor.h:957-1205) and emit (:1206-1274).
 #include "gemv.cuh"
 #include "oneshot_ar.cuh"
+#include "moe_select.cuh"
 #include "ifab_kernels.h"
 
 using namespace ifab;
 
 namespace {
 
-constexpr int MAX_TOPK = 16;
 
 // ------------------------------------------------------------------------------------------------
 struct RouterParams {
@@ -99,75 +99,10 @@ __global__ void __launch_bounds__(256) router_topk_kernel(RouterParams p) {
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // selection: warp t handles token t; each lane owns experts lane, lane+32, ...
+  // selection: warp t handles token t
   if (warp >= p.T) return;
-  const int t = warp;
-  constexpr int PER = 8;  // supports E <= 256
-  float score[PER], sel[PER];
-  float mx = -INFINITY;
-#pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    const int ei = lane + 32 * i;
-    score[i] = (ei < p.E) ? __ldcg(p.logits + (long)t * p.E + ei) : -INFINITY;
-    mx = fmaxf(mx, score[i]);
-  }
-  mx = warp_max(mx);
-  float denom = 0.f;
-#pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    const int ei = lane + 32 * i;
-    if (ei < p.E) {
-      if (p.scoring == 0) {
-        score[i] = __expf(score[i] - mx);
-        denom += score[i];
-        sel[i] = score[i];
-      } else {
-        score[i] = 1.f / (1.f + __expf(-score[i]));
-        sel[i] = score[i] + (p.bias ? p.bias[ei] : 0.f);
-      }
-    } else {
-      score[i] = 0.f;
-      sel[i] = -INFINITY;
-    }
-  }
-  denom = warp_sum(denom);
-  float picked_w[MAX_TOPK];
-  int picked_e[MAX_TOPK];
-  float wsum = 0.f;
-  for (int k = 0; k < p.topk; ++k) {
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-#pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      const int ei = lane + 32 * i;
-      if (sel[i] > bv || (sel[i] == bv && ei < bi)) { bv = sel[i]; bi = ei; }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
-    // owner lane reports the raw score and retires the expert
-    float raw = 0.f;
-#pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      if (lane + 32 * i == bi) { raw = score[i]; sel[i] = -INFINITY; }
-    }
-    raw = warp_sum(raw);
-    picked_e[k] = bi;
-    picked_w[k] = (p.scoring == 0) ? raw / denom : raw;
-    wsum += picked_w[k];
-  }
-  if (lane == 0) {
-    for (int k = 0; k < p.topk; ++k) {
-      float w = picked_w[k];
-      if (p.scoring == 0) { if (p.renorm) w = w / wsum; }
-      else w = w / (wsum + 1e-20f);
-      p.ids[t * p.topk + k] = picked_e[k];
-      p.wts[t * p.topk + k] = w * p.scale;
-    }
-  }
+  select_topk_row(p.logits + (long)warp * p.E, p.bias, p.E, p.topk, p.scoring, p.renorm, p.scale, p.ids + warp * p.topk,
+                  p.wts + warp * p.topk);
 }
 
 // ------------------------------------------------------------------------------------------------

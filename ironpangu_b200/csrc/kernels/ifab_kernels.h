@@ -30,6 +30,8 @@ typedef struct IfabFabric {
   uint32_t ll_half_bytes;  /* one parity half of the tagged-store area (8 bytes per exchanged f32) */
   uint64_t ll_offset;      /* byte offset of that area from data[r]; it is used by nothing else, because a
                               reader takes any 8-byte word whose high half equals the call number as valid */
+  void* mc;                /* NVLink multicast address of the same block (a store to it lands in every rank's copy, a
+                              multimem.ld_reduce returns the sum over the ranks), or NULL: plain peer loads / stores */
 } IfabFabric;
 
 /* ---- fabric: symmetric heap over CUDA IPC (one process per GPU) ---- */
@@ -97,6 +99,10 @@ int ifab_mla_merge(const float* scratch, const int32_t* positions, int n_sinks, 
  * + residual, bf16 out. The caller alternates two sets of partial buffers between consecutive calls. */
 int ifab_allreduce_rows(const void* const* parts, const void* residual, long ldr, void* out, long ldo, long rows, int D,
                         const IfabFabric* fab, void* stream);
+/* NVLS (NVLink multicast) form: two-shot - each rank reduces 1/world of the buffer with multimem.ld_reduce and writes the
+ * sums back to every copy with multimem.st; the buffer holds this rank's partial on entry and the sums on exit. */
+int ifab_allreduce_rows_nvls(void* part_local, void* part_mc, const void* residual, long ldr, void* out, long ldo, long rows, int D,
+                             uint32_t* arrive, const IfabFabric* fab, void* stream);
 
 /* ---- expert parallelism with sharded tokens: dispatch / combine all-to-all over peer memory (ep_a2a.cu) ----
  * `*_peers` arrays hold `world` pointers into the symmetric buffers of every rank as mapped here: recv / ret bf16 [W*cap, D],
@@ -124,6 +130,18 @@ int ifab_moe_down_allreduce_decode(const void* act, const int32_t* ids, const fl
                                    int e0, int e_local, const void* w_down, const void* w_shared_down, int Fs,
                                    const void* residual, long ldr, void* y, long ldy, const IfabFabric* fab,
                                    void* stream);
+
+/* Router + shared and routed gate/up + down + all-reduce of one decode layer as ONE launch (T = 1 or 2 rows, F <= 1536).
+ * The grid is sized to be resident at once; two in-grid signals (bounded waits) stand where the three kernels above
+ * have kernel boundaries. Results are bit-identical to ifab_router_topk -> ifab_moe_gate_up_decode ->
+ * ifab_moe_down_allreduce_decode. sync_words: 16 + 8 * T * E zero-initialised bytes (8-byte aligned) owned by the caller,
+ * one set per stream;
+ * y = x + reduced expert output, y may alias x. logits / ids / wts receive the router's outputs. */
+int ifab_moe_block_decode(const void* x, long ldx, const void* norm_w, float eps, const float* w_router, const float* bias,
+                          int E, int topk, int scoring, int renorm, float route_scale, const void* w_gu,
+                          const void* w_shared_gu, const void* w_down, const void* w_shared_down, int T, int D, int F,
+                          int Fs, int e0, int e_local, float* logits, int32_t* ids, float* wts, void* act, void* y,
+                          long ldy, uint32_t* sync_words, const IfabFabric* fab, void* stream);
 
 /* ---- lm_head + vocab-sharded greedy sampling ---- */
 int ifab_lm_head_argmax(const void* x, long ldx, const void* norm_w, float eps, const void* w, float* logits,

@@ -146,6 +146,125 @@ __global__ void __launch_bounds__(256) allreduce_rows_kernel(ArRowsParams p) {
   }
 }
 
+// Two-shot all-reduce through the NVLink switch (NVLS). Rank r owns the float4 chunks i with i % world == r:
+//   1. flag exchange: every rank's partial is in its own memory and visible;
+//   2. the owner reads the sum of a chunk over all ranks with ONE multimem.ld_reduce (the switch adds the eight copies)
+//      and writes it back to all eight copies with ONE multimem.st: a rank receives and sends 1/world of what the
+//      pull form above moves;
+//   3. second flag exchange: every rank's copy now holds the complete sums; each rank converts its own copy
+//      (bf16, + residual) with local loads only.
+// Every element is reduced by exactly one rank, so all ranks end with bit-identical rows.
+struct ArNvlsParams {
+  float* part_local;      // this rank's copy of the partial / result buffer [rows, D]
+  float* part_mc;         // multicast address of the same buffer
+  const bf16* residual; long ldr;
+  bf16* out; long ldo;
+  long rows; int D;
+  FabricView fv; uint64_t* seq; uint32_t* done;
+  uint32_t* arrive;       // local counter for the in-grid barrier between steps 2 and 3
+};
+
+// all CTAs of the grid are resident (grid <= 2 per SM); CTA 0 talks to the peers
+__device__ __forceinline__ bool nvls_rank_barrier(const ArNvlsParams& p, uint64_t want, int slot_base, uint32_t par) {
+  // called by threads < world of CTA 0
+  const int q = threadIdx.x, rank = p.fv.rank;
+  if (q == rank) return true;
+  st_release_sys(p.fv.flags[q] + (size_t)par * p.fv.flag_half_words + slot_base + rank, want);
+  return wait_flag_bounded(p.fv.flags[rank] + (size_t)par * p.fv.flag_half_words + slot_base + q, want, p.fv.spin_limit);
+}
+
+__global__ void __launch_bounds__(256) allreduce_rows_nvls_kernel(ArNvlsParams p) {
+  __shared__ int s_ok, s_last;
+  grid_dep_launch();
+  grid_dep_wait();
+  const uint64_t epoch = *reinterpret_cast<volatile uint64_t*>(p.seq) + 1;
+  const uint32_t par = (uint32_t)(epoch & 1);
+  const int world = p.fv.world, rank = p.fv.rank;
+  const uint32_t G = gridDim.x;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  // in-grid barrier: CTA 0 does the cross-rank part, publishes `phase` in arrive[1]; the others wait for it
+  auto grid_phase = [&](uint32_t phase, int slot_base) {
+    __syncthreads();
+    if (blockIdx.x == 0) {
+      // wait until every CTA of this rank has finished the step before (its stores fenced)
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        bool ok = false;
+        for (uint32_t i = 0; i < p.fv.spin_limit; ++i) {
+          if (*reinterpret_cast<volatile uint32_t*>(p.arrive) == (G - 1) * phase) { ok = true; break; }
+          if (i > 64) __nanosleep(40);
+        }
+        if (!ok) { s_ok = 0; atomicOr(p.fv.status, IFAB_STATUS_PEER_TIMEOUT); }
+        __threadfence_system();
+      }
+      __syncthreads();
+      if ((int)threadIdx.x < world && !nvls_rank_barrier(p, epoch, slot_base, par)) {
+        s_ok = 0;
+        atomicOr(p.fv.status, IFAB_STATUS_PEER_TIMEOUT);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(p.arrive + 1) = s_ok ? (uint32_t)epoch * 4u + phase : 0xffffffffu;
+      }
+    } else {
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        atomicAdd(p.arrive, 1u);
+        bool ok = false;
+        const uint32_t want = (uint32_t)epoch * 4u + phase;
+        for (uint32_t i = 0; i < p.fv.spin_limit; ++i) {
+          const uint32_t v = *reinterpret_cast<volatile uint32_t*>(p.arrive + 1);
+          if (v == want) { ok = true; break; }
+          if (v == 0xffffffffu) break;
+          if (i > 64) __nanosleep(40);
+        }
+        if (!ok) s_ok = 0;
+        __threadfence();
+      }
+    }
+    __syncthreads();
+  };
+  const long chunks = p.rows * (p.D >> 2);   // float4 chunks
+  grid_phase(1, 0);                          // every rank's partial is complete
+  if (s_ok) {
+    for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * world + rank; i < chunks; i += (long)G * blockDim.x * world) {
+      const float4 v = multimem_ld_reduce_f32x4(p.part_mc + i * 4);
+      multimem_st_f32x4(p.part_mc + i * 4, v);
+    }
+  }
+  grid_phase(2, world);                      // every owner's sums have reached every copy
+  if (s_ok) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += (long)G * blockDim.x) {
+      const long row = i / (p.D >> 2);
+      const int c = (int)(i % (p.D >> 2)) * 4;
+      const float4 acc = __ldcg(reinterpret_cast<const float4*>(p.part_local + row * p.D + c));
+      float o[4] = {acc.x, acc.y, acc.z, acc.w};
+      if (p.residual) {
+        const bf16* rr = p.residual + row * p.ldr + c;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[k] = bf16_round(o[k]) + __bfloat162float(rr[k]);
+      }
+      __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(p.out + row * p.ldo + c);
+      dst[0] = __floats2bfloat162_rn(o[0], o[1]);
+      dst[1] = __floats2bfloat162_rn(o[2], o[3]);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = (atomicAdd(p.done, 1u) == G - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x == 0) {
+    *p.done = 0;
+    p.arrive[0] = 0;
+    *p.seq = epoch;
+    __threadfence();
+  }
+}
+
 }  // namespace
 
 extern "C" int ifab_mla_q_rope(const void* q, long ldq, const int32_t* positions, void* q_lat, int T, int H, int nope, int rope,
@@ -176,4 +295,27 @@ extern "C" int ifab_allreduce_rows(const void* const* parts, const void* residua
   const long chunks = rows * (D >> 2);
   const int grid = (int)std::min<long>(2 * 148, (chunks + 255) / 256);
   return launch_chain(allreduce_rows_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p);
+}
+
+// NVLS form of ifab_allreduce_rows: part_local / part_mc are this rank's mapping and the multicast mapping of ONE f32
+// [rows, D] buffer in symmetric memory that holds this rank's partial on entry and the complete sums on exit (alternate two
+// buffers between consecutive calls). arrive: 2 zeroed uint32 words on this device, used only by this kernel.
+extern "C" int ifab_allreduce_rows_nvls(void* part_local, void* part_mc, const void* residual, long ldr, void* out, long ldo, long rows,
+                                        int D, uint32_t* arrive, const IfabFabric* fab, void* stream) {
+  if (rows < 1 || D % 4 || (residual && ldr % 4) || ldo % 4 || part_mc == nullptr || arrive == nullptr) return -1;
+  ArNvlsParams p;
+  if (int rc = fabric_view(fab, &p.fv)) return rc;
+  p.part_local = (float*)part_local; p.part_mc = (float*)part_mc;
+  p.residual = (const bf16*)residual; p.ldr = ldr; p.out = (bf16*)out; p.ldo = ldo; p.rows = rows; p.D = D;
+  p.seq = fab->seq; p.done = fab->done; p.arrive = arrive;
+  if ((size_t)2 * fab->world > fab->flag_half_words) return -4;
+  const long chunks = rows * (D >> 2);
+  // the CTAs wait on one another: never more than are resident at once (one per SM is enough to saturate the links)
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -6;
+  }
+  const int grid = (int)std::min<long>(sms, (chunks + 255) / 256);
+  return launch_chain(allreduce_rows_nvls_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p);
 }

@@ -185,14 +185,18 @@ class MlaMoeDecoder:
     def __init__(self, cfg: MlaMoeConfig, weights: Dict[str, torch.Tensor], fabric: Fabric, *, max_tokens: int = 1,
                  max_context: int = 1024, num_slots: int = 1, keys_per_split: int = 64, keep_logits: bool = False,
                  persistent: bool = False, kv_int8: bool = False, expert_fp8: bool = False, drop_bf16_experts: bool = True,
-                 fused_head: Optional[bool] = None):
+                 fused_head: Optional[bool] = None, shard: Optional[tuple] = None, fused_moe: Optional[bool] = None):
         """``kv_int8``: keep the latent cache as packed int8 rows (656 bytes per token instead of 1152).
         ``expert_fp8``: quantise the routed and shared expert matrices to block-scaled fp8 (1 x 128 scale blocks) at
         construction and decode over them; with ``drop_bf16_experts`` the bf16 originals leave ``weights``.
         ``fused_head``: run cache write, q_b, absorb, attention and value up-projection as one cluster-per-head launch
         (default: on for bf16 caches with contexts up to 2048 keys, and used for steps of one or two rows: measured on a
         B200 it takes 25 us against 38 us per layer at 32 heads and 19 against 29 us at 4 heads with 512 keys, while at 4096
-        keys or 8 rows the split-KV kernels, which spread a head over up to 64 CTAs, are faster)."""
+        keys or 8 rows the split-KV kernels, which spread a head over up to 64 CTAs, are faster).
+        ``fused_moe``: router, expert gate/up and expert down + all-reduce of a layer as one launch for steps of one or two
+        rows (default: on for bf16 experts up to 1536 wide; bit-identical to the three-kernel chain).
+        ``shard``: ``(rank, world)`` of the weight shard when it differs from the fabric's (a profiling aid: one GPU runs the
+        kernels of rank r of an N-rank job at their real shapes, without the peers; the sums it computes are partial)."""
         assert 1 <= max_tokens <= 8
         assert not (persistent and (kv_int8 or expert_fp8)), "the single-launch step reads bf16 cache rows and bf16 experts"
         self.kv_int8 = kv_int8
@@ -208,7 +212,7 @@ class MlaMoeDecoder:
         assert not self.fused_head or can_fuse, "the fused head kernel needs a bf16 cache and 512 + 64 latent rows"
         self.cfg, self.w, self.fabric = cfg, weights, fabric
         if expert_fp8:
-            assert cfg.shared_ffn % (16 * fabric.world) == 0 and cfg.expert_ffn % 16 == 0 and cfg.hidden % 16 == 0
+            assert cfg.shared_ffn % (16 * (fabric.world if shard is None else int(shard[1]))) == 0 and cfg.expert_ffn % 16 == 0 and cfg.hidden % 16 == 0
             self.w8: Dict[str, tuple] = {}
             for l in range(cfg.layers):
                 for name in ("gate_up", "down", "shared_gate_up", "shared_down"):
@@ -216,7 +220,7 @@ class MlaMoeDecoder:
                     self.w8[key] = K.quantize_fp8_block(weights[key].contiguous())
                     if drop_bf16_experts:
                         del weights[key]
-        self.rank, self.world = fabric.rank, fabric.world
+        self.rank, self.world = (fabric.rank, fabric.world) if shard is None else (int(shard[0]), int(shard[1]))
         c, dev = cfg, fabric.device
         assert c.heads % self.world == 0 and c.experts % self.world == 0 and c.vocab % self.world == 0
         assert c.shared_ffn % (8 * self.world) == 0
@@ -255,11 +259,16 @@ class MlaMoeDecoder:
         self.route_w = e(T, c.topk, dt=torch.float32)
         self.act = torch.zeros(T, c.topk + 1, c.expert_ffn, dtype=BF16, device=dev)
         self.partial = e(((self.vl + 7) // 8) * 8 * 2, dt=torch.float32)
+        can_fuse_moe = (not expert_fp8 and c.expert_ffn <= 1536 and c.expert_ffn % 8 == 0 and (c.shared_ffn // self.world) % 8 == 0
+                        and c.experts <= 256 and c.topk <= 16 and not persistent)
+        self.fused_moe = can_fuse_moe if fused_moe is None else bool(fused_moe)
+        assert not self.fused_moe or can_fuse_moe, "the one-launch MoE block needs bf16 experts of at most 1536 columns"
+        self.moe_sync = torch.zeros(K.moe_block_sync_words(2, c.experts), dtype=torch.int32, device=dev)
         self.next_ids = torch.zeros(T, dtype=torch.int32, device=dev)
         self.next_vals = torch.zeros(T, dtype=torch.float32, device=dev)
         self.logits = e(T, self.vl, dt=torch.float32) if keep_logits else None
         # embedding + lm_head + per layer: qkv_a, [cache write, q_b, absorb, split, merge+v_up | fused head], o_proj, router, gate_up, down
-        self.launches_per_forward = 2 + (6 if self.fused_head else 10) * c.layers
+        self.launches_per_forward = 2 + ((6 if self.fused_head else 10) - (2 if self.fused_moe else 0)) * c.layers
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self.persistent = persistent
         if persistent:
@@ -356,6 +365,12 @@ class MlaMoeDecoder:
         p = f"layers.{l}."
         x, attn = self.x[:T], self.attn[:T]
         K.gemv_allreduce(attn, w[p + "o_proj"], fab, residual=x, out=x)
+        if self.fused_moe and T <= 2:
+            K.moe_block(x, w[p + "router"], w[p + "gate_up"], w[p + "down"], self.rank * self.el, c.topk, fab, sync=self.moe_sync,
+                        norm_w=w[p + "ffn_norm"], eps=c.eps, scoring=c.scoring, scale=c.route_scale,
+                        w_shared_gu=w[p + "shared_gate_up"], w_shared_down=w[p + "shared_down"], logits=self.logits_r[:T],
+                        ids=self.route_ids[:T], wts=self.route_w[:T], act=self.act[:T], out=x)
+            return
         K.router_topk(x, w[p + "router"], c.topk, norm_w=w[p + "ffn_norm"], eps=c.eps, scoring=c.scoring,
                       scale=c.route_scale, ticket_ptr=fab.ticket_ptr, logits=self.logits_r[:T],
                       ids=self.route_ids[:T], wts=self.route_w[:T], xn=self.xn[:T])

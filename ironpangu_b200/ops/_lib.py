@@ -56,6 +56,7 @@ class IfabFabric(C.Structure):
         ("flag_half_words", C.c_uint32),
         ("ll_half_bytes", C.c_uint32),
         ("ll_offset", C.c_uint64),
+        ("mc", c_void_p),
     ]
 
 
@@ -82,6 +83,8 @@ _SIGS = {
     "ifab_moe_gate_up_decode": [_P, c_long, _P, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, _P],
     "ifab_moe_down_allreduce_decode": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, c_long, _P,
                                        c_long, C.POINTER(IfabFabric), _P],
+    "ifab_moe_block_decode": [_P, c_long, _P, c_float, _P, _P, c_int, c_int, c_int, c_int, c_float, _P, _P, _P, _P, c_int, c_int,
+                              c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_long, _P, C.POINTER(IfabFabric), _P],
     "ifab_mla_head_decode": [_P, c_long, _P, _P, c_float, c_float, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_float,
                              c_int, c_int, c_int, c_int, c_int, _P, c_long, _P, _P],
     "ifab_quantize_fp8_block": [_P, c_long, c_long, c_int, _P, _P, _P],
@@ -116,6 +119,7 @@ _SIGS = {
     "ifab_mla_q_rope": [_P, c_long, _P, _P, c_int, c_int, c_int, c_int, c_float, _P],
     "ifab_mla_merge": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "ifab_allreduce_rows": [_P, _P, c_long, _P, c_long, c_long, c_int, C.POINTER(IfabFabric), _P],
+    "ifab_allreduce_rows_nvls": [_P, _P, _P, c_long, _P, c_long, c_long, c_int, _P, C.POINTER(IfabFabric), _P],
     "ifab_gqa_decode_attention": [_P, c_long, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
                                   c_int, c_int, _P, c_u64, _P, c_long, _P, _P],
 }

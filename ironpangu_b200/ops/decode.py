@@ -152,6 +152,41 @@ def moe_down_allreduce(act: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, 
     return out
 
 
+def moe_block_sync_words(T: int, E: int) -> int:
+    return 4 + 2 * T * E
+
+
+def moe_block(x: torch.Tensor, w_router: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, e0: int, topk: int, fabric, *,
+              sync: torch.Tensor, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-5, bias: Optional[torch.Tensor] = None,
+              scoring: str = "softmax", renorm: bool = True, scale: float = 1.0, w_shared_gu: Optional[torch.Tensor] = None,
+              w_shared_down: Optional[torch.Tensor] = None, logits: Optional[torch.Tensor] = None,
+              ids: Optional[torch.Tensor] = None, wts: Optional[torch.Tensor] = None, act: Optional[torch.Tensor] = None,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The MoE half of a decode layer in one launch (one or two rows): router + top-k, shared and routed gate/up with SwiGLU,
+    down projections, score-weighted sum and the fused all-reduce; ``out = x + reduced`` (``out`` may be ``x``).
+    Bit-identical to ``router_topk`` -> ``moe_gate_up`` -> ``moe_down_allreduce``. ``sync``: zeroed int32 words that only
+    this op uses (in-grid signals and tagged router logits): at least ``moe_block_sync_words(T, E)`` of them."""
+    T, D = x.shape
+    E = w_router.shape[0]
+    e_local, twoF, _ = w_gu.shape
+    F = twoF // 2
+    Fs = 0 if w_shared_gu is None else w_shared_gu.shape[0] // 2
+    assert T <= 2 and w_router.dtype == torch.float32 and w_router.is_contiguous() and sync.numel() >= moe_block_sync_words(T, E) and sync.dtype == torch.int32
+    dev = x.device
+    logits = logits if logits is not None else torch.empty(T, E, dtype=torch.float32, device=dev)
+    ids = ids if ids is not None else torch.empty(T, topk, dtype=torch.int32, device=dev)
+    wts = wts if wts is not None else torch.empty(T, topk, dtype=torch.float32, device=dev)
+    act = act if act is not None else torch.zeros(T, topk + 1, F, dtype=BF16, device=dev)
+    out = out if out is not None else torch.empty(T, D, dtype=BF16, device=dev)
+    mode = {"softmax": 0, "sigmoid_bias_group_topk": 1}[scoring]
+    check(_lib.load().ifab_moe_block_decode(x.data_ptr(), _rows(x), _ptr(norm_w), eps, w_router.data_ptr(), _ptr(bias), E, topk, mode,
+                                            int(renorm), scale, w_gu.data_ptr(), _ptr(w_shared_gu), w_down.data_ptr(),
+                                            _ptr(w_shared_down), T, D, F, Fs, e0, e_local, logits.data_ptr(), ids.data_ptr(),
+                                            wts.data_ptr(), act.data_ptr(), out.data_ptr(), _rows(out), sync.data_ptr(),
+                                            C.byref(fabric.desc), _stream()), "moe_block")
+    return out
+
+
 def mla_head_decode(qkv: torch.Tensor, q_norm: torch.Tensor, kv_norm: torch.Tensor, w_qb: torch.Tensor, w_kvb: torch.Tensor,
                     cache: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor, *, q_lora: int,
                     nope: int, scale: float, eps: float = 1e-5, theta: float = 10000.0, window: int = 0,

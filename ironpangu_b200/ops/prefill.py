@@ -113,7 +113,18 @@ def mla_merge(scratch: torch.Tensor, positions: torch.Tensor, o_lat: torch.Tenso
 
 
 def allreduce_rows(parts, fabric, out: torch.Tensor, *, residual: Optional[torch.Tensor] = None) -> None:
-    """``parts``: SymmetricTensor f32 ``[rows, D]`` (this call's parity buffer); ``out = bf16(sum_ranks parts) + residual``."""
+    """``parts``: SymmetricTensor f32 ``[rows, D]`` (this call's parity buffer); ``out = bf16(sum_ranks parts) + residual``.
+    With an NVLink multicast mapping of ``parts`` the sum is taken inside the switch (two-shot ``multimem.ld_reduce`` /
+    ``multimem.st``; ``parts`` then holds the sums afterwards), otherwise every rank pulls every peer's rows."""
     rows, D = out.shape
-    check(_lib.load().ifab_allreduce_rows(parts.peer_ptrs, _p(residual), 0 if residual is None else residual.stride(0),
-                                          out.data_ptr(), out.stride(0), rows, D, C.byref(fabric.desc), _s()), "allreduce_rows")
+    lib = _lib.load()
+    if getattr(parts, "mc_ptr", 0) and fabric.world > 1:
+        arrive = getattr(fabric, "_nvls_arrive", None)
+        if arrive is None:
+            arrive = fabric._nvls_arrive = torch.zeros(2, dtype=torch.int32, device=out.device)
+        check(lib.ifab_allreduce_rows_nvls(parts.base, parts.mc_ptr, _p(residual), 0 if residual is None else residual.stride(0),
+                                           out.data_ptr(), out.stride(0), rows, D, arrive.data_ptr(), C.byref(fabric.desc), _s()),
+              "allreduce_rows_nvls")
+        return
+    check(lib.ifab_allreduce_rows(parts.peer_ptrs, _p(residual), 0 if residual is None else residual.stride(0),
+                                  out.data_ptr(), out.stride(0), rows, D, C.byref(fabric.desc), _s()), "allreduce_rows")

@@ -28,6 +28,7 @@ def main():
     from ironpangu_b200.models.mla_moe_ref import forward_ref, rmsnorm_ref
 
     fab = Fabric(rank, world, spin_limit=2_000_000)
+    print(f"rank {rank}: nvls {'on' if fab.mc else 'off'}", flush=True)
 
     # 1. fused GEMV + all-reduce -------------------------------------------------------------------
     g = torch.Generator(device="cuda").manual_seed(5)

@@ -129,6 +129,52 @@ def test_moe_decode_single_rank(env):
     torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("T,D,F,E,topk,Fs,e0,el", [(1, 256, 64, 16, 4, 32, 0, 16), (2, 256, 64, 16, 4, 32, 4, 4),
+                                                   (1, 4096, 1536, 96, 8, 192, 12, 12), (2, 4096, 1536, 96, 8, 1536, 0, 96),
+                                                   (1, 512, 72, 24, 6, 0, 0, 24)])
+def test_moe_block_one_launch_equals_chain(env, T, D, F, E, topk, Fs, e0, el):
+    """Router + gate/up + down + all-reduce as one launch against the three-kernel chain (bit-identical) and against the
+    fp32 reference; run twice so that the in-grid signal words are reused, with a shard of the experts as on one of N ranks."""
+    K, fab, R = env
+    x, nw = rnd(T, D), rnd(D, scale=0.1) + 1
+    wgu, wd = rnd(el, 2 * F, D, scale=0.05), rnd(el, D, F, scale=0.05)
+    sgu, sd = (rnd(2 * Fs, D, scale=0.05), rnd(D, Fs, scale=0.05)) if Fs else (None, None)
+    wr = rnd(E, D, scale=0.2, dtype=torch.float32)
+    ids, wts, logits = K.router_topk(x, wr, topk, norm_w=nw, ticket_ptr=fab.ticket_ptr)
+    act = K.moe_gate_up(x, ids, wgu, e0, norm_w=nw, w_shared_gu=sgu)
+    y = K.moe_down_allreduce(act, ids, wts, wd, e0, fab, w_shared_down=sd, residual=x)
+    sync = torch.zeros(K.moe_block_sync_words(T, E), dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        ids2 = torch.full_like(ids, -1)
+        wts2, logits2 = torch.zeros_like(wts), torch.zeros_like(logits)
+        y2 = K.moe_block(x, wr, wgu, wd, e0, topk, fab, sync=sync, norm_w=nw, w_shared_gu=sgu, w_shared_down=sd, ids=ids2,
+                         wts=wts2, logits=logits2)
+        torch.cuda.synchronize()
+        assert fab.status() == 0
+        assert torch.equal(ids2, ids) and torch.equal(wts2, wts) and torch.equal(logits2, logits)
+        assert torch.equal(y2, y)
+    h = R.rmsnorm_ref(x, nw, 1e-5)
+    ref = torch.zeros(T, D, device="cuda")
+    for t in range(T):
+        for k in range(topk):
+            e = int(ids[t, k]) - e0
+            if not 0 <= e < el:
+                continue
+            gu = (h[t] @ wgu[e].float().T).to(BF16).float()
+            a = (torch.nn.functional.silu(gu[:F]) * gu[F:]).to(BF16).float()
+            ref[t] += wts[t, k] * (a @ wd[e].float().T)
+        if Fs:
+            gu = (h[t] @ sgu.float().T).to(BF16).float()
+            a = (torch.nn.functional.silu(gu[:Fs]) * gu[Fs:]).to(BF16).float()
+            ref[t] += a @ sd.float().T
+    ref = ref.to(BF16).float() + x.float()
+    torch.testing.assert_close(y2.float(), ref, rtol=2e-2, atol=2e-2)
+    # x may be updated in place (the residual stream of the decoder)
+    x3 = x.clone()
+    K.moe_block(x3, wr, wgu, wd, e0, topk, fab, sync=sync, norm_w=nw, w_shared_gu=sgu, w_shared_down=sd, out=x3)
+    assert torch.equal(x3, y)
+
+
 @pytest.mark.parametrize("T,V", [(1, 19200), (4, 1000), (8, 153600)])
 def test_lm_head_argmax(env, T, V):
     K, fab, R = env

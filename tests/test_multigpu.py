@@ -18,8 +18,8 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _run(world: int, script: str, timeout: int = 600):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+def _run(world: int, script: str, timeout: int = 600, **extra_env):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, script)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
@@ -27,12 +27,18 @@ def _run(world: int, script: str, timeout: int = 600):
     return r.stdout
 
 
+@pytest.mark.parametrize("nvls", ["0", "1"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_fused_collectives_and_tiny_model(world):
+def test_fused_collectives_and_tiny_model(world, nvls):
+    """``nvls`` = 1: the symmetric blocks are bound to an NVLink multicast object when the machine offers one (the one-shot
+    all-reduce pushes with multimem.st, the bulk all-reduce of the prompt path reduces in the switch); 0: plain peer
+    loads and stores. Both must give the same tokens and bit-identical rows on every rank."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    out = _run(world, "multigpu_worker.py")
+    out = _run(world, "multigpu_worker.py", IFAB_NVLS=nvls)
     assert out.count("ok tiny model") == world
+    if nvls == "0":
+        assert "nvls on" not in out
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
