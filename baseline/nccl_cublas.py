@@ -11,9 +11,12 @@ all shapes are static and nothing synchronises with the host.
 Design notes (what a careful user of the libraries would write, not a strawman):
   * the KV cache is a dense ``[max_context, latent + rope]`` tensor per layer; attention runs in the
     absorbed MLA form over the whole cache with a position mask, as two batched GEMMs
-  * routed experts: the ``topk`` selected experts of every row are gathered from this rank's expert
-    bank with ``index_select`` and applied with ``torch.bmm``; routes owned by other ranks are
-    clamped to expert 0 and weighted by zero (static shapes for graph capture)
+  * routed experts: the routes of all rows are sorted by local expert and applied with the library's grouped GEMM
+    (``torch._grouped_mm``: one call for gate/up, one for down, reading each selected expert's weights once and no
+    others); routes owned by other ranks sort behind the last group and contribute zero. Where the installed
+    library has no grouped GEMM for this device the selected experts are gathered with ``index_select`` and applied with
+    ``torch.bmm`` (the gather triples the expert traffic); ``expert_path`` says which ran
+  * RMSNorm is the fused ``torch.nn.functional.rms_norm``
   * one NCCL all-reduce after the attention output projection, one after the MoE, one all-gather-free
     argmax exchange (max of values, then min of the matching index) for the vocabulary-sharded head
 """
@@ -51,12 +54,28 @@ class NcclCublasDecoder:
         self.logits = torch.empty(T, self.vl, dtype=torch.float32, device=dev) if keep_logits else None
         # library launches per forward, counted from the operator list below (for the bench record only)
         self.launches_per_forward = 0
+        self.expert_arange = torch.arange(self.el, device=dev)
+        self.expert_path = "grouped_mm" if self._grouped_mm_works() else "index_select+bmm"
+
+    def _grouped_mm_works(self) -> bool:
+        """One tiny call decides: the grouped GEMM of the installed library either supports this device and layout or not."""
+        if not hasattr(torch, "_grouped_mm"):
+            return False
+        try:
+            dev = self.tokens.device
+            a = torch.zeros(8, 64, dtype=BF16, device=dev)
+            b = torch.zeros(2, 32, 64, dtype=BF16, device=dev)
+            offs = torch.tensor([3, 8], dtype=torch.int32, device=dev)
+            torch._grouped_mm(a, b.transpose(1, 2), offs=offs)
+            torch.cuda.synchronize()
+            return True
+        except Exception:
+            return False
 
     # -- helpers -----------------------------------------------------------------------------------
     @staticmethod
     def _norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-        xf = x.float()
-        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(BF16)
+        return F.rms_norm(x, (x.shape[-1],), w, eps)
 
     def _rope(self, x: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
         """Half-rotation RoPE, bf16-rounded tables; x [T, ..., d]."""
@@ -117,17 +136,20 @@ class NcclCublasDecoder:
             mine = (local >= 0) & (local < self.el)
             local = torch.where(mine, local, torch.zeros_like(local)).reshape(-1)
             wts = torch.where(mine, wts, torch.zeros_like(wts))
-            moe = torch.empty(T, c.hidden, dtype=torch.float32, device=x.device)
-            for r0 in range(0, T, 2):                                          # two rows at a time bounds the gather buffers
-                r1 = min(T, r0 + 2)
-                sel = local[r0 * c.topk:r1 * c.topk]
-                gu = w[p + "gate_up"].index_select(0, sel)                     # [rows*topk, 2F, D]
-                dn = w[p + "down"].index_select(0, sel)                        # [rows*topk, D, F]
-                hx = h2[r0:r1].repeat_interleave(c.topk, 0).unsqueeze(2)       # [rows*topk, D, 1]
-                g_u = torch.bmm(gu, hx).squeeze(2)
-                act = (F.silu(g_u[:, :c.expert_ffn].float()) * g_u[:, c.expert_ffn:].float()).to(BF16)
-                y = torch.bmm(dn, act.unsqueeze(2)).squeeze(2).float().view(r1 - r0, c.topk, c.hidden)
-                moe[r0:r1] = (y * wts[r0:r1, :, None]).sum(1)
+            if self.expert_path == "grouped_mm":
+                moe = self._experts_grouped(h2, local, mine.reshape(-1), wts.reshape(-1), w[p + "gate_up"], w[p + "down"], T)
+            else:
+                moe = torch.empty(T, c.hidden, dtype=torch.float32, device=x.device)
+                for r0 in range(0, T, 2):                                      # two rows at a time bounds the gather buffers
+                    r1 = min(T, r0 + 2)
+                    sel = local[r0 * c.topk:r1 * c.topk]
+                    gu = w[p + "gate_up"].index_select(0, sel)                 # [rows*topk, 2F, D]
+                    dn = w[p + "down"].index_select(0, sel)                    # [rows*topk, D, F]
+                    hx = h2[r0:r1].repeat_interleave(c.topk, 0).unsqueeze(2)   # [rows*topk, D, 1]
+                    g_u = torch.bmm(gu, hx).squeeze(2)
+                    act = (F.silu(g_u[:, :c.expert_ffn].float()) * g_u[:, c.expert_ffn:].float()).to(BF16)
+                    y = torch.bmm(dn, act.unsqueeze(2)).squeeze(2).float().view(r1 - r0, c.topk, c.hidden)
+                    moe[r0:r1] = (y * wts[r0:r1, :, None]).sum(1)
             sg = h2 @ w[p + "shared_gate_up"].T
             fs = sg.shape[1] // 2
             sact = (F.silu(sg[:, :fs].float()) * sg[:, fs:].float()).to(BF16)
@@ -148,6 +170,23 @@ class NcclCublasDecoder:
         self.next_ids[:T].copy_(idx.to(torch.int32))
         self.next_vals[:T].copy_(val)
         return self.next_ids[:T]
+
+    def _experts_grouped(self, h2, local, mine, wts, w_gu, w_down, T: int) -> torch.Tensor:
+        """Routed experts through the library's grouped GEMM. Routes are sorted by local expert (foreign routes behind the
+        last group, outside every offset, never computed); all shapes are static, nothing synchronises with the host."""
+        c = self.cfg
+        key = torch.where(mine, local, torch.full_like(local, self.el))
+        order = torch.argsort(key, stable=True)
+        skey = key[order]
+        counts = (skey[:, None] == self.expert_arange[None, :]).sum(0)
+        offs = torch.cumsum(counts, 0).to(torch.int32)
+        token = torch.div(order, c.topk, rounding_mode="floor")
+        xs = h2[token]                                                        # [R, D]
+        g_u = torch._grouped_mm(xs, w_gu.transpose(1, 2), offs=offs)          # [R, 2F]
+        act = (F.silu(g_u[:, :c.expert_ffn].float()) * g_u[:, c.expert_ffn:].float()).to(BF16)
+        y = torch._grouped_mm(act, w_down.transpose(1, 2), offs=offs).float()   # [R, D]
+        y = torch.where(mine[order][:, None], y * wts[order][:, None], torch.zeros_like(y))
+        return torch.zeros(T, c.hidden, dtype=torch.float32, device=h2.device).index_add_(0, token, y)
 
     def reset(self) -> None:
         for cch in self.caches:

@@ -41,6 +41,11 @@ def parse():
     ap.add_argument("--expert-fp8", action="store_true", help="block-scaled fp8 expert weights (the serving configuration; NOT the bf16 headline)")
     ap.add_argument("--kv-int8", action="store_true", help="packed int8 latent KV cache (the serving configuration; NOT the bf16 headline)")
     ap.add_argument("--layers", type=int, default=0, help="override layer count (marks the run as a reduced config)")
+    ap.add_argument("--repeats", type=int, default=5, help="the timed loop of --steps steps runs this many times; the median is reported")
+    ap.add_argument("--baseline-steps", type=int, default=16,
+                    help="native arm, MLA+MoE models: also run the cuBLAS + NCCL decoder on the same weights in this process - compare "
+                         "its first greedy tokens with the native arm's and time this many of its decode steps (0: skip)")
+    ap.add_argument("--fused-moe", type=int, default=-1, help="-1: decoder default; 0/1: MoE half of a layer as three launches / one")
     return ap.parse_args()
 
 
@@ -89,6 +94,69 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def library_arm(cfg, weights, rank, world, max_context, prompt, native_tokens, native_logits, steps, dev, barrier, max_over_ranks):
+    """The cuBLAS + NCCL decoder on the same weight tensors.
+
+    (1) Greedy tokens: the library arm reads the same prompt and then the native arm's own tokens (teacher forcing, so that
+    one early difference does not end the comparison); after every token its prediction is compared with the native arm's.
+    Two correct bf16 implementations differ in summation order, so their logits differ by a measurable noise: eps = RMS over the
+    vocabulary of (native logits - library logits) at that step. A differing token counts as agreeing when the library arm
+    scores the native arm's token within 4.5 eps of its own best (a top-2 flip inside the noise); ``tokens_match`` is true when
+    every compared position agrees in that sense. (2) Its decode step time over ``steps`` graph replays."""
+    import torch
+    import torch.distributed as dist
+
+    from baseline.nccl_cublas import NcclCublasDecoder
+    from ironpangu_b200.runtime.engine import DecodeEngine
+
+    bdec = NcclCublasDecoder(cfg, weights, rank, world, max_tokens=8, max_context=max_context, keep_logits=True)
+    beng = DecodeEngine(bdec)
+    vl = bdec.vl
+
+    def allreduce(t, op):
+        if world > 1:
+            dist.all_reduce(t, op=op)
+        return t
+
+    def judge(native_tok: int, ln):
+        lb = bdec.logits[0]
+        best = allreduce(lb.max().reshape(1).clone(), dist.ReduceOp.MAX)
+        local = native_tok - rank * vl
+        mine = lb[local].reshape(1).clone() if 0 <= local < vl else torch.full((1,), float("-inf"), device=dev)
+        mine = allreduce(mine, dist.ReduceOp.MAX)
+        eps = None
+        if ln is not None:
+            sq = allreduce(((ln.float() - lb) ** 2).sum().reshape(1), dist.ReduceOp.SUM)
+            eps = float(torch.sqrt(sq / (vl * world)))
+        return float(best - mine), eps
+
+    rows = []
+    pred = beng.prefill(prompt)
+    for i, tok in enumerate(native_tokens):
+        margin, eps = judge(tok, native_logits[i])
+        rows.append((pred == tok, margin, eps))
+        if i + 1 < len(native_tokens):
+            pred = beng.step(tok)
+    eps_seen = [e for _, _, e in rows if e is not None]
+    eps_max = max(eps_seen) if eps_seen else 0.0
+    agree = [same or margin <= 4.5 * (eps if eps is not None else eps_max) for same, margin, eps in rows]
+    out = {"tokens_match": bool(all(agree)), "tokens_compared": len(rows), "tokens_identical": sum(1 for same, _, _ in rows if same),
+           "largest_margin_of_a_differing_token": round(max([m for same, m, _ in rows if not same], default=0.0), 5),
+           "logit_noise_rms": round(eps_max, 5), "expert_path": bdec.expert_path}
+    beng.run_device_loop(native_tokens[-1], 3)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    beng.run_device_loop(None, steps)
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    out.update({"steps": steps, "ms_per_step": round(ms / steps, 4), "tokens_s": round(steps / (ms / 1e3), 3)})
+    del beng, bdec
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -113,10 +181,8 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # NCCL only carries the bootstrap, the barriers and the max-over-ranks of the timing here (the model's collectives are
-        # the fabric kernels over peer memory), so its in-switch reduction buys nothing: keep it off, as in every measured run
-        if args.impl == "native":               # the NCCL + cuBLAS arm keeps NCCL's defaults: its collectives are NCCL's
-            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        # NCCL carries the bootstrap, the barriers and the max-over-ranks of the timing for the native arm (the model's
+        # collectives are the fabric kernels over peer memory) and every collective of the cuBLAS + NCCL arm: library defaults
         dist.init_process_group("nccl", device_id=dev)
 
     from ironpangu_b200.models.mla_moe import MlaMoeConfig, MlaMoeDecoder, random_rank_weights
@@ -132,7 +198,9 @@ def main():
     if args.layers:
         cfg.layers = args.layers
     K, W = args.steps, max(args.warmup, 3)
-    max_context = args.context + 3 * K + 2 * W + 64
+    R = max(1, args.repeats)
+    CHECK = 16                                   # greedy tokens compared between the native and the library arm
+    max_context = args.context + (R + 2) * K + 2 * W + CHECK + 64
     fab = Fabric(rank, world)
     t0 = time.time()
     weights = (G.random_rank_weights if dense else random_rank_weights)(cfg, rank, world, dev, seed=0)
@@ -144,7 +212,8 @@ def main():
         dec = G.DenseDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1)
     elif args.impl == "native":
         dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1,
-                            persistent=bool(args.persistent), expert_fp8=args.expert_fp8, kv_int8=args.kv_int8)
+                            persistent=bool(args.persistent), expert_fp8=args.expert_fp8, kv_int8=args.kv_int8,
+                            fused_moe=None if args.fused_moe < 0 else bool(args.fused_moe))
         if args.expert_fp8 or args.kv_int8:
             args.prefill = "decode"        # the quantised layouts prefill through the decode kernels
     else:
@@ -187,18 +256,42 @@ def main():
     torch.cuda.synchronize()
     ttft_ms = max_over_ranks(e0.elapsed_time(e1))
 
-    # ---- device-timed decode: feedback graph, no host round trips ----------------------------------
+    # ---- greedy tokens of the native arm against the cuBLAS + NCCL decoder on the same weights, and that decoder's step time ----
+    native_tokens = [first]
+    lib_arm = None
+    if args.impl == "native" and not dense and args.baseline_steps > 0 and not (args.expert_fp8 or args.kv_int8):
+        from ironpangu_b200.ops import decode as KK
+        tok = first
+        native_logits = [None]                 # the prompt's last row lives in the prefill path's buffers: no logits kept for it
+        for _ in range(CHECK):
+            tok = eng.step(tok)
+            native_tokens.append(tok)
+            # this step's logits of the local vocabulary shard, from the final hidden row (outside the step's own graph)
+            native_logits.append(KK.gemv(dec.x[:1], weights["lm_head"], norm_w=weights["final_norm"], eps=cfg.eps, out_f32=True)[0])
+        try:
+            lib_arm = library_arm(cfg, weights, rank, world, max_context, prompt, native_tokens, native_logits,
+                                  args.baseline_steps, dev, barrier, max_over_ranks)
+        except Exception as exc:          # e.g. no memory left beside a one-GPU shard of 175 GB: the native numbers still stand
+            lib_arm = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+            if world > 1:
+                raise
+        first = native_tokens[-1]
+
+    # ---- device-timed decode: feedback graph, no host round trips; median of R runs of K steps -------
     eng.run_device_loop(first, W)
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    barrier()
-    e0.record()
-    eng.run_device_loop(None, K)
-    e1.record()
-    barrier()
-    dev_ms = max_over_ranks(e0.elapsed_time(e1))
+    runs = []
+    for _ in range(R):
+        barrier()
+        e0.record()
+        eng.run_device_loop(None, K)
+        e1.record()
+        barrier()
+        runs.append(max_over_ranks(e0.elapsed_time(e1)))
+    dev_ms = statistics.median(runs)
 
     # ---- per-step TPOT distribution (events around every replay) -----------------------------------
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(K + 1)]
@@ -226,8 +319,16 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     status = fab.status()
 
+    # launches of this package's kernels in one step, counted at the entry points (one eager step after the timing)
+    launches_counted = None
+    if args.impl == "native":
+        from ironpangu_b200.ops import _lib as native_lib
+        n0 = native_lib.launch_count
+        dec.forward(1)
+        torch.cuda.synchronize()
+        launches_counted = native_lib.launch_count - n0
     if rank == 0:
-        per_step_launches = getattr(dec, "launches_per_forward", 0)
+        per_step_launches = launches_counted if launches_counted is not None else getattr(dec, "launches_per_forward", 0)
         value = K / (dev_ms / 1e3)
         line = {
             "metric": "decode_tokens_per_s_per_box", "value": round(value, 3), "unit": "tokens/s", "n_gpus": world,
@@ -249,9 +350,15 @@ def main():
             "tpot_p50_ms": round(tpot_p50, 4), "ttft_ms": round(ttft_ms, 3),
             "e2e": {"value": round(K / (e2e_ms / 1e3), 3), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 4),
                     "h2d_bytes_per_step": eng.h2d_bytes_per_step, "d2h_bytes_per_step": eng.d2h_bytes_per_step},
-            "gpu_launches": per_step_launches * K, "clocks": clocks, "fabric_status": status,
-            "init_s": round(init_s, 1),
+            "gpu_launches": per_step_launches * K, "launches_per_step": per_step_launches, "clocks": clocks, "fabric_status": status,
+            "timed_runs_ms": [round(v, 3) for v in runs], "init_s": round(init_s, 1),
         }
+        if args.impl == "native" and not dense:
+            line["config"]["moe_block"] = "one launch" if getattr(dec, "fused_moe", False) else "router, gate/up, down"
+            line["config"]["nvls"] = bool(getattr(fab, "mc", 0))
+        if lib_arm is not None:
+            line["tokens_match"] = lib_arm.pop("tokens_match", None)
+            line["nccl_cublas"] = lib_arm
         print(json.dumps(line))
     barrier()
     if hasattr(fab, "close"):

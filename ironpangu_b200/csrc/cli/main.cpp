@@ -136,7 +136,7 @@ int inspect(const char* path) {
   std::string bytes = read_file(path);
   if (bytes.compare(0, 8, "IFTOKN01") == 0) std::cout << graph::Graph::decode(bytes).to_json().dump(1) << "\n";
   else if (bytes.compare(0, 7, "IFTOKN0") == 0) std::cout << program::Program::decode(bytes).to_json().dump(1) << "\n";
-  else if (bytes.compare(0, 8, "IFINIT01") == 0) std::cout << init::Plan::decode(bytes).to_json().dump(1) << "\n";
+  else if (bytes.compare(0, 7, "IFINIT0") == 0) std::cout << init::Plan::decode(bytes).to_json().dump(1) << "\n";
   else if (bytes.compare(0, 7, "IFARENA") == 0) {
     uint64_t pf = 0, bf = 0;
     bundle::Arena a = bundle::Arena::decode(bytes, &pf, &bf);

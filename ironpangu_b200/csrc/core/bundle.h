@@ -3,7 +3,7 @@
 //   execution.bin         physical program (IFTOKN02-09)        logical.bin       logical graph (IFTOKN01)
 //   execution.json/.dot   logical graph, JSON and Graphviz       execution.html    self-contained viewer
 //   device-program.json   instructions + kernel recipes          physical.json     inspection plan (costs, collectives)
-//   rank-N.bin/.init.json per-rank weight plans (IFINIT01)       serving.json      serving manifest
+//   rank-N.bin/.init.json per-rank weight plans (IFINIT01/02)     serving.json      serving manifest
 //   arena-rank-N.txt      frozen activation arena (IFARENA2)     workspace-rank-N.txt  kernel scratch (IFWORKSPACE1)
 //   arena.json            arena summary                           plan.json         bundle index (token-bundle.v1)
 //

@@ -40,9 +40,16 @@ uint64_t Plan::device_bytes() const {
 }
 
 // ---------------------------------------------------------------------------------------------
+bool Plan::reference_form() const {
+  if (loads.size() != parameters.size()) return false;
+  for (size_t i = 0; i < loads.size(); ++i)
+    if (loads[i].dest != i || (uint32_t)loads[i].src_dtype > 3 || (uint32_t)parameters[i].dtype > 3) return false;
+  return true;
+}
+
 std::string Plan::encode() const {
   ByteWriter w;
-  w.raw("IFINIT01");
+  w.raw(reference_form() ? "IFINIT01" : "IFINIT02");
   w.u32(rank);
   w.u32(device);
   w.str(provenance);
@@ -58,7 +65,7 @@ std::string Plan::encode() const {
   for (auto& l : loads) {
     w.u32(l.tag);
     w.u32(l.dest);
-    w.str(l.tensor);
+    w.str(l.shard);
     w.u64(l.offset);
     w.u64(l.bytes);
     w.u32((uint32_t)l.src_dtype);
@@ -72,7 +79,9 @@ std::string Plan::encode() const {
 
 Plan Plan::decode(std::string_view bytes) {
   ByteReader r(bytes);
-  if (r.raw(8) != "IFINIT01") invalid("not an IFINIT01 plan");
+  const std::string magic(r.raw(8));
+  if (magic != "IFINIT01" && magic != "IFINIT02") invalid("not an initialization plan (IFINIT01 / IFINIT02)");
+  const bool extended = magic == "IFINIT02";
   Plan p;
   p.rank = r.u32();
   p.device = r.u32();
@@ -85,7 +94,7 @@ Plan Plan::decode(std::string_view bytes) {
     if (q.id != i) invalid("parameter ids must be dense and ordered");
     q.name = r.str(4096);
     uint32_t dt = r.u32();
-    if (dt < 1 || dt > 4) invalid("unknown parameter dtype");
+    if (dt < 1 || dt > (extended ? 4u : 3u)) invalid("unknown parameter dtype");
     q.dtype = (DType)dt;
     uint32_t rank = r.u32();
     if (rank == 0 || rank > 6) invalid("parameter rank out of range");
@@ -104,11 +113,12 @@ Plan Plan::decode(std::string_view bytes) {
     if (l.tag != 1 && l.tag != 2) invalid("unknown load tag");
     l.dest = r.u32();
     if (l.dest >= np) invalid("load destination out of range");
-    l.tensor = r.str(4096);
+    l.shard = r.str(4096);
+    if (l.shard.empty() || l.shard.find('/') != std::string::npos || l.shard.find("..") != std::string::npos) invalid("load names a shard outside the checkpoint directory");
     l.offset = r.u64();
     l.bytes = r.u64();
     uint32_t dt = r.u32();
-    if (dt < 1 || dt > 4) invalid("unknown source dtype");
+    if (dt < 1 || dt > (extended ? 4u : 3u)) invalid("unknown source dtype");
     l.src_dtype = (DType)dt;
     if (l.tag == 2) {
       l.row_bytes = r.u64();
@@ -118,6 +128,7 @@ Plan Plan::decode(std::string_view bytes) {
     p.loads.push_back(std::move(l));
   }
   if (!r.done()) invalid("trailing bytes after the plan");
+  if (!extended && !p.reference_form()) invalid("an IFINIT01 plan carries exactly one load per parameter, in parameter order");
   return p;
 }
 
@@ -145,8 +156,9 @@ Json Plan::to_json() const {
     Json o = Json::object();
     o.set("kind", l.tag == 1 ? "slice" : "strided_rows");
     o.set("dest", l.dest);
-    o.set("tensor", l.tensor);
+    o.set("shard", l.shard);
     o.set("offset", l.offset);
+    if (!l.tensor.empty()) o.set("tensor", l.tensor);
     o.set("bytes", l.bytes);
     o.set("src_dtype", dtype_name(l.src_dtype));
     if (l.tag == 2) {
@@ -250,11 +262,20 @@ Checkpoint Checkpoint::inspect(const std::string& dir) {
 Checkpoint Checkpoint::synthetic(const std::map<std::string, std::pair<DType, std::vector<uint64_t>>>& shapes) {
   Checkpoint c;
   Sha256 h;
+  uint64_t cursor = 0;
   for (auto& kv : shapes) {
     TensorInfo t;
     t.name = kv.first;
     t.dtype = kv.second.first;
     t.shape = kv.second.second;
+    // a virtual single shard, tensors back to back in name order after an 8-byte-aligned header stand-in
+    t.file = "model.safetensors";
+    t.data_start = 0;
+    t.begin = cursor;
+    uint64_t n = dtype_bytes(t.dtype);
+    for (auto d : t.shape) n *= d;
+    t.end = t.begin + n;
+    cursor = t.end;
     c.tensors[t.name] = t;
     std::string line = kv.first + ":" + dtype_name(t.dtype);
     for (auto d : t.shape) line += "," + std::to_string(d);
@@ -517,13 +538,14 @@ std::vector<Plan> plan_all(const Program& p, const Checkpoint& ckpt) {
           LoadSlice l;
           l.dest = prm.id;
           l.tensor = tname;
+          l.shard = t.file;
           l.src_dtype = t.dtype;
           const uint64_t R = n.full.size() == 1 ? 1 : n.full[0], C = n.full.size() == 1 ? n.full[0] : n.full[1];
           uint64_t r_local = R, c_local = C;
           switch (n.shard) {
             case Need::Full:
               l.tag = 1;
-              l.offset = 0;
+              l.offset = t.file_offset();
               l.bytes = R * C * eb;
               break;
             case Need::Rows:
@@ -531,14 +553,14 @@ std::vector<Plan> plan_all(const Program& p, const Checkpoint& ckpt) {
               if (R % tp) invalid("tensor " + tname + ": rows not divisible by tp");
               r_local = R / tp;
               l.tag = 1;
-              l.offset = rank * r_local * C * eb;
+              l.offset = t.file_offset() + rank * r_local * C * eb;
               l.bytes = r_local * C * eb;
               break;
             case Need::Cols:
               if (C % tp) invalid("tensor " + tname + ": columns not divisible by tp");
               c_local = C / tp;
               l.tag = 2;
-              l.offset = rank * c_local * eb;
+              l.offset = t.file_offset() + rank * c_local * eb;
               l.row_bytes = c_local * eb;
               l.stride_bytes = C * eb;
               l.bytes = R * c_local * eb;
@@ -584,17 +606,21 @@ uint64_t execute(const Plan& plan, const Checkpoint& ckpt, DeviceMemory& mem, co
   std::vector<char> stage(opt.staging_bytes), conv;
   std::map<std::string, std::unique_ptr<std::ifstream>> files;
   uint64_t written = 0;
+  std::map<std::string, uint64_t> sizes;
   for (auto& l : plan.loads) {
-    const TensorInfo& t = ckpt.need(l.tensor);
     const Parameter& prm = plan.parameters.at(l.dest);
-    auto& f = files[t.file];
+    const std::string what = l.tensor.empty() ? l.shard + "@" + std::to_string(l.offset) : l.tensor;
+    auto& f = files[l.shard];
     if (!f) {
-      f = std::make_unique<std::ifstream>(ckpt.dir + "/" + t.file, std::ios::binary);
-      if (!*f) fail(ErrorKind::Io, "cannot open " + ckpt.dir + "/" + t.file);
+      const std::string path = ckpt.dir + "/" + l.shard;
+      f = std::make_unique<std::ifstream>(path, std::ios::binary);
+      if (!*f) fail(ErrorKind::Io, "cannot open " + path);
+      f->seekg(0, std::ios::end);
+      sizes[l.shard] = (uint64_t)f->tellg();
     }
-    const uint64_t tensor_bytes = t.end - t.begin;
+    const uint64_t file_bytes = sizes[l.shard];
     const bool widen = l.src_dtype == DType::Bf16 && prm.dtype == DType::F32;
-    if (!widen && l.src_dtype != prm.dtype) invalid("load of " + l.tensor + ": no conversion from " + dtype_name(l.src_dtype) + " to " + dtype_name(prm.dtype));
+    if (!widen && l.src_dtype != prm.dtype) invalid("load of " + what + ": no conversion from " + dtype_name(l.src_dtype) + " to " + dtype_name(prm.dtype));
     auto push = [&](const char* data, uint64_t n) {
       if (widen) {
         conv.resize(n * 2);
@@ -605,7 +631,7 @@ uint64_t execute(const Plan& plan, const Checkpoint& ckpt, DeviceMemory& mem, co
         if (opt.verify_upload) {
           std::vector<char> back(n * 2);
           mem.read(l.dest, cursor[l.dest], back.data(), n * 2);
-          if (memcmp(back.data(), conv.data(), n * 2) != 0) fail(ErrorKind::Backend, "upload verification failed for " + l.tensor);
+          if (memcmp(back.data(), conv.data(), n * 2) != 0) fail(ErrorKind::Backend, "upload verification failed for " + what);
         }
         cursor[l.dest] += n * 2;
         written += n * 2;
@@ -614,35 +640,35 @@ uint64_t execute(const Plan& plan, const Checkpoint& ckpt, DeviceMemory& mem, co
         if (opt.verify_upload) {
           std::vector<char> back(n);
           mem.read(l.dest, cursor[l.dest], back.data(), n);
-          if (memcmp(back.data(), data, n) != 0) fail(ErrorKind::Backend, "upload verification failed for " + l.tensor);
+          if (memcmp(back.data(), data, n) != 0) fail(ErrorKind::Backend, "upload verification failed for " + what);
         }
         cursor[l.dest] += n;
         written += n;
       }
     };
     if (l.tag == 1) {
-      if (l.offset + l.bytes > tensor_bytes) invalid("load of " + l.tensor + " exceeds the tensor");
+      if (l.offset + l.bytes > file_bytes) invalid("load of " + what + " runs past the end of " + l.shard);
       uint64_t done = 0;
       while (done < l.bytes) {
         uint64_t n = std::min<uint64_t>(stage.size(), l.bytes - done);
-        f->seekg((std::streamoff)(t.data_start + t.begin + l.offset + done));
+        f->seekg((std::streamoff)(l.offset + done));
         f->read(stage.data(), (std::streamsize)n);
-        if (!*f) fail(ErrorKind::Io, "short read of " + l.tensor);
+        if (!*f) fail(ErrorKind::Io, "short read of " + what);
         push(stage.data(), n);
         done += n;
       }
     } else {
       const uint64_t rows = l.bytes / l.row_bytes;
-      if (l.offset + (rows - 1) * l.stride_bytes + l.row_bytes > tensor_bytes) invalid("strided load of " + l.tensor + " exceeds the tensor");
+      if (l.offset + (rows - 1) * l.stride_bytes + l.row_bytes > file_bytes) invalid("strided load of " + what + " runs past the end of " + l.shard);
       // pack as many rows as fit the staging buffer, then write once
       const uint64_t per = std::max<uint64_t>(1, stage.size() / l.row_bytes);
       if (l.row_bytes > stage.size()) stage.resize(l.row_bytes);
       for (uint64_t r0 = 0; r0 < rows; r0 += per) {
         uint64_t n = std::min(per, rows - r0);
         for (uint64_t r = 0; r < n; ++r) {
-          f->seekg((std::streamoff)(t.data_start + t.begin + l.offset + (r0 + r) * l.stride_bytes));
+          f->seekg((std::streamoff)(l.offset + (r0 + r) * l.stride_bytes));
           f->read(stage.data() + r * l.row_bytes, (std::streamsize)l.row_bytes);
-          if (!*f) fail(ErrorKind::Io, "short read of " + l.tensor);
+          if (!*f) fail(ErrorKind::Io, "short read of " + what);
         }
         push(stage.data(), n * l.row_bytes);
       }

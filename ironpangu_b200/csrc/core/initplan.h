@@ -28,14 +28,19 @@ struct Parameter {
 
 // Append `bytes` (after conversion) to parameter `dest`. tag 1 = contiguous range, tag 2 = strided
 // rows (`row_bytes` taken every `stride_bytes`, starting at `offset`, until `bytes` source bytes).
+// `shard` is the checkpoint FILE the bytes come from and `offset` an absolute offset in that file (the
+// safetensors header included), as in the reference's LoadSlice (crates/inferfabric-ir/src/initialization.rs:
+// 52-66): a plan is executable with nothing but the shard files. `tensor` names the checkpoint tensor for
+// diagnostics and the JSON view; it is not part of the binary form.
 struct LoadSlice {
   uint32_t tag = 1;
   uint32_t dest = 0;
-  std::string tensor;        // checkpoint tensor name
-  uint64_t offset = 0;       // byte offset inside the tensor's data
+  std::string shard;         // file name inside the checkpoint directory
+  uint64_t offset = 0;       // absolute byte offset inside that file
   uint64_t bytes = 0;        // source bytes to move
   DType src_dtype = DType::Bf16;
   uint64_t row_bytes = 0, stride_bytes = 0;
+  std::string tensor;        // informational: the checkpoint tensor the range lies in
 };
 
 struct Plan {
@@ -44,7 +49,11 @@ struct Plan {
   std::vector<Parameter> parameters;
   std::vector<LoadSlice> loads;
 
-  std::string encode() const;            // IFINIT01
+  // IFINIT01 when the plan has the reference's form (exactly one load per parameter, in parameter order, dtypes 1-3):
+  // byte-for-byte what the reference's encoder writes for the same plan. Otherwise IFINIT02: the same layout, but
+  // several loads may append to one parameter (expert stacks, packed pairs) and dtype 4 (fp8 e4m3) may appear.
+  std::string encode() const;
+  bool reference_form() const;
   static Plan decode(std::string_view bytes);
   Json to_json() const;
   uint64_t device_bytes() const;
@@ -57,6 +66,7 @@ struct TensorInfo {
   std::vector<uint64_t> shape;
   uint64_t begin = 0, end = 0;   // byte range inside the file's data section
   uint64_t data_start = 0;       // file offset of the data section
+  uint64_t file_offset() const { return data_start + begin; }
 };
 struct Checkpoint {
   std::string dir;

@@ -160,7 +160,12 @@ def load(build: bool = True):
         return lib
 
 
+launch_count = 0          # launches of this library's kernels since the process started (every entry point reports here)
+
+
 def check(rc: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if rc != 0:
         msg = load().ifab_error_string(rc).decode()
         raise RuntimeError(f"{what} failed: {msg} (code {rc})")

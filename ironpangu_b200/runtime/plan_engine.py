@@ -35,11 +35,13 @@ class SafetensorsDir:
 
     def __init__(self, path: str):
         self.tensors: Dict[str, tuple] = {}
+        self.files: Dict[str, mmap.mmap] = {}
         self._maps = []
         for f in sorted(Path(path).glob("*.safetensors")):
             fh = open(f, "rb")
             mm = mmap.mmap(fh.fileno(), 0, access=mmap.ACCESS_READ)
             self._maps.append((fh, mm))
+            self.files[f.name] = mm
             (hlen,) = struct.unpack("<Q", mm[:8])
             hdr = json.loads(mm[8:8 + hlen])
             for name, info in hdr.items():
@@ -52,6 +54,13 @@ class SafetensorsDir:
         mm, off, n, _, _ = self.tensors[name]
         return np.frombuffer(mm, dtype=np.uint8, count=n, offset=off)
 
+    def shard_from(self, shard: str, offset: int) -> np.ndarray:
+        """The bytes of shard file ``shard`` from absolute file offset ``offset`` to its end."""
+        mm = self.files[shard]
+        if offset < 0 or offset > len(mm):
+            raise ValueError(f"offset {offset} is outside {shard} ({len(mm)} bytes)")
+        return np.frombuffer(mm, dtype=np.uint8, count=len(mm) - offset, offset=offset)
+
 
 def load_parameters(init_plan: dict, ckpt: SafetensorsDir, device) -> Dict[str, torch.Tensor]:
     """Execute one rank's initialization plan: returns ``{parameter name: device tensor}``."""
@@ -63,19 +72,24 @@ def load_parameters(init_plan: dict, ckpt: SafetensorsDir, device) -> Dict[str, 
         cursors[p["id"]] = 0
     meta = {p["id"]: p for p in init_plan["parameters"]}
     for l in init_plan["loads"]:
-        src = ckpt.bytes_of(l["tensor"])
+        # a load names the shard FILE and an absolute offset inside it (the safetensors header included)
+        src = ckpt.shard_from(l["shard"], l["offset"])
         if l["kind"] == "slice":
-            chunk = src[l["offset"]:l["offset"] + l["bytes"]]
+            if l["bytes"] > src.size:
+                raise ValueError(f"load of {l.get('tensor', l['shard'])} runs past the end of {l['shard']}")
+            chunk = src[:l["bytes"]]
         else:
             rows = l["bytes"] // l["row_bytes"]
-            view = np.lib.stride_tricks.as_strided(src[l["offset"]:], shape=(rows, l["row_bytes"]), strides=(l["stride_bytes"], 1))
+            if (rows - 1) * l["stride_bytes"] + l["row_bytes"] > src.size:
+                raise ValueError(f"strided load of {l.get('tensor', l['shard'])} runs past the end of {l['shard']}")
+            view = np.lib.stride_tricks.as_strided(src, shape=(rows, l["row_bytes"]), strides=(l["stride_bytes"], 1))
             chunk = np.ascontiguousarray(view).reshape(-1)
         t = torch.from_numpy(np.array(chunk, copy=True))
         dst_dt = meta[l["dest"]]["dtype"]
         if l["src_dtype"] == "bf16" and dst_dt == "f32":
             t = t.view(torch.bfloat16).to(torch.float32).view(torch.uint8)
         elif l["src_dtype"] != dst_dt:
-            raise ValueError(f"no conversion {l['src_dtype']} -> {dst_dt} for {l['tensor']}")
+            raise ValueError(f"no conversion {l['src_dtype']} -> {dst_dt} for {l.get('tensor', l['shard'])}")
         c = cursors[l["dest"]]
         raw[l["dest"]][c:c + t.numel()].copy_(t, non_blocking=False)
         cursors[l["dest"]] = c + t.numel()

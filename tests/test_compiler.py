@@ -64,7 +64,8 @@ def test_bundle_files_init_plans_and_no_overwrite(tmp_path):
         assert f in names, f
     assert json.loads((out / "plan.json").read_text())["format"] == "inferfabric.token-bundle.v1"
     assert (out / "execution.bin").read_bytes()[:8] == b"IFTOKN02"
-    assert (out / "rank-3.bin").read_bytes()[:8] == b"IFINIT01"
+    # expert stacks and packed pairs take several loads per parameter: the extended container, not the reference's form
+    assert (out / "rank-3.bin").read_bytes()[:8] == b"IFINIT02"
     plan = json.loads((out / "rank-3.init.json").read_text())
     by = {p["name"]: p for p in plan["parameters"]}
     loads = {}
@@ -74,11 +75,16 @@ def test_bundle_files_init_plans_and_no_overwrite(tmp_path):
     o = by["model.layers.0.self_attn.o_proj"]
     assert o["dims"] == [4096, 512]
     (l,) = loads[o["id"]]
-    assert l["kind"] == "strided_rows" and l["row_bytes"] == 1024 and l["stride_bytes"] == 8192 and l["offset"] == 3 * 1024
+    assert l["kind"] == "strided_rows" and l["row_bytes"] == 1024 and l["stride_bytes"] == 8192
+    assert l["shard"] == "model.safetensors" and (l["offset"] - 3 * 1024) % 2 == 0
+    base_o = l["offset"] - 3 * 1024            # file offset of the tensor: every rank's slice starts rank * 1024 bytes in
+    assert json.loads((out / "rank-5.init.json").read_text())["loads"][plan["loads"].index(l)]["offset"] == base_o + 5 * 1024
     # row-sharded q_b: one contiguous slice at rank * rows
     qb = by["model.layers.0.self_attn.q_b_proj"]
     (l,) = loads[qb["id"]]
-    assert qb["dims"] == [768, 1536] and l["kind"] == "slice" and l["offset"] == 3 * 768 * 1536 * 2
+    assert qb["dims"] == [768, 1536] and l["kind"] == "slice" and l["bytes"] == 768 * 1536 * 2
+    l0 = json.loads((out / "rank-0.init.json").read_text())["loads"][plan["loads"].index(l)]
+    assert l["offset"] - l0["offset"] == 3 * 768 * 1536 * 2
     # local experts 36..47 of 96, gate and up packed per expert
     gu = by["model.layers.5.mlp.experts.{expert}.gate_proj|model.layers.5.mlp.experts.{expert}.up_proj"]
     assert gu["dims"] == [12, 3072, 4096]
