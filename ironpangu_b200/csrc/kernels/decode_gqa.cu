@@ -99,7 +99,8 @@ __global__ void __launch_bounds__(256) gqa_split_kernel(GqaParams p) {
   const int first = pos + 1 - n;
   const int k_begin = split * p.kps;
   if (k_begin >= n) return;
-  const int k_end = min(n, k_begin + p.kps);
+  // the last split also takes every key beyond max_splits * keys_per_split, so a long context is slower, never clipped
+  const int k_end = (split == p.max_splits - 1) ? n : min(n, k_begin + p.kps);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = p.slots[t];
   float qf[G][EPL];

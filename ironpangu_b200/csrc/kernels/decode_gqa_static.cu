@@ -11,9 +11,9 @@
 // Consequences of that choice, all of which a caller has to know:
 //   * the workspace has a fixed size (IFAB_GQA_STATIC_SCRATCH_BYTES); a call that needs more is
 //     refused with IFAB_ERR_STATIC_SCRATCH and a message, nothing is launched
-//   * the address of the array is looked up once per device, on the first call made while that
-//     device is current. That first call should be made outside any stream capture; later calls only
-//     launch kernels
+//   * the address of the array on the current device is looked up on every call (cudaGetSymbolAddress, a
+//     host-side query that allocates nothing), so it stays right across a device reset or a new context.
+//     The first call on a device may load the module: make it outside any stream capture
 //   * every call on a device uses the same array, so two calls that can overlap on the GPU (different
 //     streams without an ordering between them) race on it. Issue calls on one stream, or order them
 //   * the array keeps whatever the previous call left in it. Nothing here needs it zeroed: each call
@@ -21,7 +21,6 @@
 //     holds at least one key, and exactly those splits are written by the same call)
 // The arithmetic is the one of ifab_gqa_decode_attention - this entry point forwards to it with the
 // built-in workspace - so results are bit-identical to a call with a caller-provided buffer.
-#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -30,13 +29,8 @@
 
 namespace {
 
-constexpr int kMaxDevices = 64;
-
 // the workspace: [T][Hq][max_splits][head_dim + 2] f32 partials (accumulator, running max, running sum)
 static __device__ __align__(256) unsigned char g_gqa_static_scratch[IFAB_GQA_STATIC_SCRATCH_BYTES];
-
-// device ordinal -> address of the array on that device (each device has its own copy of a __device__ variable)
-std::atomic<float*> g_scratch_addr[kMaxDevices];
 
 // formats into the caller's buffer (if any); snprintf does not allocate
 void explain(char* err, uint64_t err_len, const char* fmt, ...) {
@@ -47,30 +41,19 @@ void explain(char* err, uint64_t err_len, const char* fmt, ...) {
   va_end(ap);
 }
 
-// Looks the address up on first use for the current device; no allocation, the array is part of the module.
+// The array's address on the current device (each device has its own copy of a __device__ variable). In host code the
+// array's name is only a handle for this query, never a device pointer. Nothing is cached: the query is cheap and a cached
+// pointer would be stale after a device reset.
 int static_scratch(float** out, char* err, uint64_t err_len) {
-  int dev = -1;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) {
-    explain(err, err_len, "cudaGetDevice failed (CUDA error %d)", (int)e);
-    return (int)e;
+  void* sym = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(&sym, g_gqa_static_scratch);
+  if (e != cudaSuccess || !sym) {
+    int dev = -1;
+    (void)cudaGetDevice(&dev);
+    explain(err, err_len, "cudaGetSymbolAddress of the built-in workspace failed on device %d (CUDA error %d)", dev, (int)e);
+    return e != cudaSuccess ? (int)e : -1;
   }
-  if (dev < 0 || dev >= kMaxDevices) {
-    explain(err, err_len, "device ordinal %d is outside the %d supported", dev, kMaxDevices);
-    return -1;
-  }
-  float* p = g_scratch_addr[dev].load(std::memory_order_acquire);
-  if (!p) {
-    void* sym = nullptr;
-    e = cudaGetSymbolAddress(&sym, g_gqa_static_scratch);
-    if (e != cudaSuccess || !sym) {
-      explain(err, err_len, "cudaGetSymbolAddress of the built-in workspace failed on device %d (CUDA error %d)", dev, (int)e);
-      return e != cudaSuccess ? (int)e : -1;
-    }
-    p = static_cast<float*>(sym);
-    g_scratch_addr[dev].store(p, std::memory_order_release);   // concurrent first calls store the same value
-  }
-  *out = p;
+  *out = static_cast<float*>(sym);
   return 0;
 }
 
@@ -91,7 +74,8 @@ extern "C" int ifab_gqa_decode_attention_static(const void* q, long ldq, const v
   if (need > (uint64_t)IFAB_GQA_STATIC_SCRATCH_BYTES) {
     explain(err, err_len,
             "this call needs %llu bytes of split workspace (T*Hq*max_splits*(head_dim+2)*4) but the built-in array holds %llu; "
-            "lower max_splits or T, or use ifab_gqa_decode_attention with your own buffer",
+            "raise keys_per_split (the last split covers the tail of any context) together with a lower max_splits, or lower T, "
+            "or use ifab_gqa_decode_attention with your own buffer",
             (unsigned long long)need, (unsigned long long)IFAB_GQA_STATIC_SCRATCH_BYTES);
     return IFAB_ERR_STATIC_SCRATCH;
   }
@@ -103,3 +87,6 @@ extern "C" int ifab_gqa_decode_attention_static(const void* q, long ldq, const v
   if (rc) explain(err, err_len, "ifab_gqa_decode_attention refused the call or a launch failed (code %d)", rc);
   return rc;
 }
+
+extern "C" uint64_t ifab_gqa_static_scratch_bytes(void) { return (uint64_t)IFAB_GQA_STATIC_SCRATCH_BYTES; }
+extern "C" int ifab_err_static_scratch(void) { return IFAB_ERR_STATIC_SCRATCH; }

@@ -153,7 +153,7 @@ __device__ __forceinline__ void phase_split(const Params& p, const Layer& L, flo
     const int total = p.n_sinks + nctx;
     const int k_begin = split * p.kps;
     if (k_begin >= total) continue;
-    const int k_end = min(total, k_begin + p.kps);
+    const int k_end = (split == p.max_splits - 1) ? total : min(total, k_begin + p.kps);   // the last split takes the tail
     const int slot = p.slots[t];
     RowFrag qf[HG];
 #pragma unroll

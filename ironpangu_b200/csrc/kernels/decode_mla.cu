@@ -166,7 +166,8 @@ __global__ void __launch_bounds__(256) mla_split_kernel(AttnParams p) {
   const int total = p.n_sinks + nctx;
   const int k_begin = split * p.kps;
   if (k_begin >= total) return;
-  const int k_end = min(total, k_begin + p.kps);
+  // the last split also takes every key beyond max_splits * keys_per_split, so a long context is slower, never clipped
+  const int k_end = (split == p.max_splits - 1) ? total : min(total, k_begin + p.kps);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = p.slots[t];
 

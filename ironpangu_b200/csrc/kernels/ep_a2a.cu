@@ -55,6 +55,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int R = p.M * p.topk;
   __shared__ int s_last;
+  bool ranking_missing = false;
   if (blockIdx.x == 0) {
     // stable ranking of the routes inside every destination: warp w handles destinations w, w + 8, ...; the destination of
     // every route is staged in shared memory first (one coalesced pass), so the ballot scans do not wait on global loads
@@ -89,16 +90,25 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchParams p) {
     if (threadIdx.x == 0) atomicExch(p.ticket + 1, 1u);   // ranking done
   } else {
     if (threadIdx.x == 0) {
+      s_last = 0;                                 // reused below; here: 1 = the ranking never arrived
+      bool ranked = false;
       for (uint32_t spin = 0; spin < 4000000u; ++spin) {
-        if (atomicAdd(p.ticket + 1, 0u) != 0) break;
+        if (atomicAdd(p.ticket + 1, 0u) != 0) { ranked = true; break; }
         __nanosleep(64);
+      }
+      if (!ranked) {
+        s_last = 1;
+        if (p.status) atomicOr(p.status, IFAB_STATUS_PEER_TIMEOUT);
       }
     }
     __syncthreads();
     __threadfence();
+    ranking_missing = s_last != 0;
+    __syncthreads();
   }
   // copy rows: one warp per route
-  for (int i = blockIdx.x * 8 + warp; i < R; i += gridDim.x * 8) {
+  // without the ranking the send indices are stale: copy nothing (the status word says why) and only take the ticket
+  for (int i = blockIdx.x * 8 + warp; i < R && !ranking_missing; i += gridDim.x * 8) {
     const int e = p.ids[i], dst = e / p.el, idx = __ldcg(p.send_idx + i);
     if (dst < 0 || dst >= p.world || idx >= p.cap) continue;
     const bf16* src = p.xn + (long)(i / p.topk) * p.ldxn;

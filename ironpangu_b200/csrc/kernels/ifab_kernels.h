@@ -151,6 +151,7 @@ int ifab_lm_head_argmax(const void* x, long ldx, const void* norm_w, float eps, 
 
 /* ---- sampling on vocabulary-sharded logits: temperature, penalties, top-k <= 64, min-p, top-p, counter-based draw ---- */
 int ifab_sample_topk(const float* logits, long ld, int T, int V_local, int vocab_offset, int top_k,
+                     const int32_t* top_k_rows /* optional [T]: per-row k <= top_k */,
                      const float* inv_temperature, const float* top_p, const float* min_p, const int16_t* counts, long ldc,
                      const float* penalties, const uint64_t* seeds, uint64_t* counters, void* scratch, uint64_t scratch_bytes,
                      int32_t* out_ids, float* out_probs, const IfabFabric* fab, void* stream);
@@ -239,6 +240,9 @@ int ifab_gqa_rope_kv_write(void* qkv, long ld, const int32_t* positions, const i
                            const int32_t* page_table, int max_pages, int page_tokens, void* k_cache, void* v_cache,
                            int num_pages, int T, int Hq, int Hkv, int head_dim, int rotary_dim, float theta,
                            uint32_t* status, void* stream);
+/* Split-KV decode attention. Split s covers keys [s * keys_per_split, (s + 1) * keys_per_split); the LAST split also covers
+ * every key beyond max_splits * keys_per_split, so any context is attended in full (contexts longer than that product
+ * only lose parallelism). scratch: T * Hq * max_splits * (head_dim + 2) floats. */
 int ifab_gqa_decode_attention(const void* q, long ldq, const void* k_cache, const void* v_cache,
                               const int32_t* positions, const int32_t* slots, const int32_t* page_table, int max_pages,
                               int page_tokens, int num_pages, float scale, int T, int Hq, int Hkv, int head_dim,
@@ -253,14 +257,19 @@ int ifab_gqa_decode_attention(const void* q, long ldq, const void* k_cache, cons
  * allocator lock, or an allocation could stall the device in a latency-critical loop.
  *   - limit: T * Hq * max_splits * (head_dim + 2) * 4 bytes must not exceed IFAB_GQA_STATIC_SCRATCH_BYTES;
  *     a larger call returns IFAB_ERR_STATIC_SCRATCH, launches nothing and explains itself in `err`
- *   - the first call made with a given device current looks up the array's address on that device
- *     (cudaGetSymbolAddress); make that first call before any stream capture begins
+ *   - every call looks up the array's address on the current device (cudaGetSymbolAddress: a host-side query that
+ *     allocates nothing, and is right again after a device reset); the first call on a device may load the module, so
+ *     make that first call before any stream capture begins
  *   - all calls on a device share the one array: calls that may overlap on the GPU race on it, so keep them
  *     on one stream or order them. The array keeps the previous call's contents; each call overwrites
  *     everything it reads, so nothing has to be cleared
- *   - `err` (optional, `err_len` bytes) receives a NUL-terminated message when the result is not 0 */
+ *   - `err` (optional, `err_len` bytes) receives a NUL-terminated message when the result is not 0
+ *   - ifab_gqa_static_scratch_bytes() / ifab_err_static_scratch() return the two constants below to callers that do not
+ *     include this header (bindings) */
 #define IFAB_GQA_STATIC_SCRATCH_BYTES (8u << 20)
 #define IFAB_ERR_STATIC_SCRATCH (-6)
+uint64_t ifab_gqa_static_scratch_bytes(void);
+int ifab_err_static_scratch(void);
 int ifab_gqa_decode_attention_static(const void* q, long ldq, const void* k_cache, const void* v_cache,
                                      const int32_t* positions, const int32_t* slots, const int32_t* page_table,
                                      int max_pages, int page_tokens, int num_pages, float scale, int T, int Hq, int Hkv,

@@ -54,6 +54,8 @@ extern "C" const char* ifab_error_string(int code) {
     case -3: return "fabric staging area too small for this call";
     case -4: return "fabric flag area too small for this call";
     case -5: return "scratch buffer too small";
+    case -6: return "the call needs more split workspace than the library's built-in array holds (ifab_gqa_decode_attention_static)";
+    case -7: return "the kernel's co-resident grid does not fit this device";
     case -10: return "invalid fabric descriptor";
     default: break;
   }

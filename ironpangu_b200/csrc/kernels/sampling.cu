@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(256) sample_block_topk_kernel(SampleParams p) 
 
 struct FinishParams {
   const Cand* cand; int nblocks, T, K;
+  const int32_t* k_rows;   // optional [T]: top-k of each row (values outside 1..K mean K)
   const float* inv_temperature; const float* top_p; const float* min_p;   // [T] each (nullptr = disabled)
   const uint64_t* seeds; uint64_t* counters;                              // [T]: draw = hash(seed, counter++)
   int32_t* out_ids; float* out_probs;
@@ -165,6 +166,10 @@ __global__ void __launch_bounds__(256) sample_finish_kernel(FinishParams p) {
     if (threadIdx.x == 0) {
       const float it = p.inv_temperature ? p.inv_temperature[t] : 1.f;
       int K = p.K;
+      if (p.k_rows) {          // rows of different requests share a launch: each keeps its own k
+        const int kr = p.k_rows[t];
+        if (kr >= 1 && kr < K) K = kr;
+      }
       if (it <= 0.f) K = 1;   // greedy
       while (K > 1 && fin[K - 1].v == -INFINITY) --K;
       // softmax over the K survivors
@@ -216,7 +221,7 @@ __global__ void __launch_bounds__(256) sample_finish_kernel(FinishParams p) {
 
 // scratch: T * nblocks * 64 * 8 bytes with nblocks = ceil(V_local / 4096) (must be <= 64)
 extern "C" int ifab_sample_topk(const float* logits, long ld, int T, int V_local, int vocab_offset, int top_k,
-                                const float* inv_temperature, const float* top_p, const float* min_p, const int16_t* counts,
+                                const int32_t* top_k_rows, const float* inv_temperature, const float* top_p, const float* min_p, const int16_t* counts,
                                 long ldc, const float* penalties, const uint64_t* seeds, uint64_t* counters, void* scratch,
                                 uint64_t scratch_bytes, int32_t* out_ids, float* out_probs, const IfabFabric* fab, void* stream) {
   if (T < 1 || T > 64 || top_k < 1 || top_k > KMAX || V_local < 1) return -1;
@@ -227,7 +232,7 @@ extern "C" int ifab_sample_topk(const float* logits, long ld, int T, int V_local
   SampleParams a{logits, ld, T, V_local, vocab_offset, top_k, inv_temperature, counts, ldc, penalties, (Cand*)scratch, nblocks};
   if (int rc = launch_chain(sample_block_topk_kernel, dim3(nblocks, T), dim3(256), 0, s, a)) return rc;
   FinishParams f;
-  f.cand = (const Cand*)scratch; f.nblocks = nblocks; f.T = T; f.K = top_k;
+  f.cand = (const Cand*)scratch; f.nblocks = nblocks; f.T = T; f.K = top_k; f.k_rows = top_k_rows;
   f.inv_temperature = inv_temperature; f.top_p = top_p; f.min_p = min_p; f.seeds = seeds; f.counters = counters;
   f.out_ids = out_ids; f.out_probs = out_probs;
   if (int rc = fabric_view(fab, &f.fv)) return rc;

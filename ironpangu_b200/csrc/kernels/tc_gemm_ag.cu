@@ -10,6 +10,12 @@
 // ordinary tiled TMA loads (no multicast, no TMA from peer memory). The transfer of the remote shards therefore hides
 // under the tensor-core work on the local one.
 //
+// Forward progress: a remote-tile CTA spins (bounded) on a count that local-tile CTAs of the SAME grid bump. The local tiles
+// have the lower block indices, and the hardware hands out CTAs of a grid in block-index order, so by the time a remote-tile
+// CTA is resident every local-tile CTA is resident or done. CUDA does not document that order; if it ever changed, a grid
+// larger than the device holds could fill the SMs with waiting CTAs - the waits would then run out, the status word would
+// carry IFAB_STATUS_PEER_TIMEOUT and the output of those tiles would be missing, without a hang.
+//
 // Readiness: the shard of a rank is written by the kernel that precedes this one in that rank's stream. At kernel start
 // CTA 0 publishes "my shard of call `epoch` is complete" to every peer (system fence + release store); a CTA whose rows
 // live on rank s waits - bounded - for s's flag, then issues a cross-proxy fence before its first TMA load. The caller

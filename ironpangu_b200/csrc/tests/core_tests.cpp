@@ -1,11 +1,15 @@
 // Unit tests of the host runtime services (no device needed). Exit code 0 = all passed.
 #include <cstdio>
+#include <cstring>
+#include <filesystem>
+#include <unistd.h>
 #include <functional>
 #include <iostream>
 
 #include "chat_parse.h"
 #include "contract.h"
 #include "cpu_plan.h"
+#include "initplan.h"
 #include "paging.h"
 #include "prefix_index.h"
 #include "rankplan.h"
@@ -539,8 +543,84 @@ static void test_chat_parsers() {
   CHECK_THROWS(Invalid, render_tools(Json::parse("{}")));
 }
 
+// An initialization plan laid out byte for byte as the reference's encoder writes it (crates/inferfabric-compiler/src/
+// initialization.rs:8-49): magic, rank, device, length-prefixed sha256 text, parameters {id, name, dtype, rank, dims},
+// instructions {tag, destination, shard FILE name, absolute file offset, bytes, source dtype [, row_bytes, stride_bytes]}.
+// Built here by hand, decoded by the library, executed against a shard file, and re-encoded to the same bytes.
+static void test_init_plan_reference_layout() {
+  namespace fs = std::filesystem;
+  const fs::path dir = fs::temp_directory_path() / ("ifab_init_" + std::to_string((unsigned long)::getpid()));
+  fs::create_directories(dir);
+  // one shard with a [4, 6] bf16 matrix (values 0..23 as raw u16) and a [3] bf16 vector (100..102)
+  init::TensorInfo a, b;
+  a.name = "w"; a.dtype = init::DType::Bf16; a.shape = {4, 6};
+  b.name = "v"; b.dtype = init::DType::Bf16; b.shape = {3};
+  std::string da, db;
+  for (uint16_t i = 0; i < 24; ++i) { da.push_back((char)(i & 0xff)); da.push_back((char)(i >> 8)); }
+  for (uint16_t i = 100; i < 103; ++i) { db.push_back((char)(i & 0xff)); db.push_back((char)(i >> 8)); }
+  init::write_safetensors((dir / "model-00001-of-00001.safetensors").string(), {{a, da}, {b, db}});
+  const init::Checkpoint ck = init::Checkpoint::inspect(dir.string());
+  const uint64_t w_at = ck.need("w").file_offset(), v_at = ck.need("v").file_offset();
+  CHECK(w_at >= 8 && v_at == w_at + 48);
+
+  std::string bytes = "IFINIT01";
+  auto u32 = [&](uint32_t v) { for (int i = 0; i < 4; ++i) bytes.push_back((char)((v >> (8 * i)) & 0xff)); };
+  auto u64 = [&](uint64_t v) { for (int i = 0; i < 8; ++i) bytes.push_back((char)((v >> (8 * i)) & 0xff)); };
+  auto str = [&](const std::string& t) { u32((uint32_t)t.size()); bytes += t; };
+  u32(1);                          // rank
+  u32(1);                          // device
+  str(std::string(64, 'c'));       // checkpoint metadata sha256 (provenance text)
+  u32(3);                          // parameters
+  u32(0); str("w.cols"); u32(2); u32(2); u64(4); u64(3);   // columns 3..5 of every row: strided source rows
+  u32(1); str("v");      u32(3); u32(1); u64(3);           // bf16 source widened to f32
+  u32(2); str("w.rows"); u32(2); u32(2); u64(2); u64(6);   // rows 2..3: one contiguous range
+  u32(3);                          // instructions, one per parameter, in parameter order
+  u32(2); u32(0); str("model-00001-of-00001.safetensors"); u64(w_at + 6); u64(24); u32(2); u64(6); u64(12);
+  u32(1); u32(1); str("model-00001-of-00001.safetensors"); u64(v_at); u64(6); u32(2);
+  u32(1); u32(2); str("model-00001-of-00001.safetensors"); u64(w_at + 24); u64(24); u32(2);
+
+  init::Plan plan = init::Plan::decode(bytes);
+  CHECK(plan.rank == 1 && plan.parameters.size() == 3 && plan.loads.size() == 3 && plan.reference_form());
+  CHECK(plan.loads[0].shard == "model-00001-of-00001.safetensors" && plan.loads[0].offset == w_at + 6 && plan.loads[0].stride_bytes == 12);
+  CHECK(plan.encode() == bytes);   // the same bytes come back
+  init::Checkpoint files;          // execution needs the directory only: no tensor table, no fingerprint
+  files.dir = dir.string();
+  init::HostMemory mem;
+  init::ExecuteOptions opt;
+  opt.staging_bytes = 4096;
+  opt.verify_upload = true;
+  CHECK(init::execute(plan, files, mem, opt) == 24 + 12 + 24);
+  auto u16_at = [&](uint32_t param, size_t i) { return (uint16_t)((uint8_t)mem.store[param][2 * i] | ((uint8_t)mem.store[param][2 * i + 1] << 8)); };
+  const uint16_t want_cols[12] = {3, 4, 5, 9, 10, 11, 15, 16, 17, 21, 22, 23};
+  for (size_t i = 0; i < 12; ++i) CHECK(u16_at(0, i) == want_cols[i]);
+  for (size_t i = 0; i < 12; ++i) CHECK(u16_at(2, i) == 12 + i);
+  uint32_t f0;
+  memcpy(&f0, mem.store[1].data(), 4);
+  CHECK(f0 == (100u << 16));       // bf16 bits moved to the upper half of the f32
+  // what the reference's validate() refuses is refused here too under the IFINIT01 magic
+  {
+    std::string two = bytes;       // claim a second load for parameter 0 by rewriting the destination of the last load
+    init::Plan bad = plan;
+    bad.loads[2].dest = 0;
+    CHECK(!bad.reference_form() && bad.encode().compare(0, 8, "IFINIT02") == 0);
+    std::string forged = bad.encode();
+    forged.replace(0, 8, "IFINIT01");
+    CHECK_THROWS(Invalid, init::Plan::decode(forged));
+  }
+  {
+    init::Plan bad = plan;
+    bad.loads[1].shard = "../outside.safetensors";
+    CHECK_THROWS(Invalid, init::Plan::decode(bad.encode()));
+    bad = plan;
+    bad.loads[2].offset = w_at + 1000;   // past the end of the shard
+    CHECK_THROWS(Invalid, init::execute(bad, files, mem, opt));
+  }
+  fs::remove_all(dir);
+}
+
 int main() {
   std::pair<const char*, std::function<void()>> tests[] = {
+      {"init_plan_reference_layout", test_init_plan_reference_layout},
       {"serve_batching", test_serve_batching_matches_sequential}, {"serve_admission", test_serve_validation_and_admission},
       {"serve_backpressure_cancel", test_serve_backpressure_cancel_and_eos}, {"serve_failure_shutdown", test_serve_engine_failure_and_shutdown},
       {"api_tokenizer", test_api_tokenizer_and_sampling_json}, {"kernel_plugin", test_kernel_plugin_loader},

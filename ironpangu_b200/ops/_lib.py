@@ -93,7 +93,7 @@ _SIGS = {
                                            c_long, C.POINTER(IfabFabric), _P],
     "ifab_lm_head_argmax": [_P, c_long, _P, c_float, _P, _P, c_int, c_int, c_int, c_int, _P, c_u64, _P, _P,
                             C.POINTER(IfabFabric), _P],
-    "ifab_sample_topk": [_P, c_long, c_int, c_int, c_int, c_int, _P, _P, _P, _P, c_long, _P, _P, _P, _P, c_u64, _P, _P,
+    "ifab_sample_topk": [_P, c_long, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_long, _P, _P, _P, _P, c_u64, _P, _P,
                          C.POINTER(IfabFabric), _P],
     "ifab_mla_kv_write": [_P, c_long, _P, c_float, c_float, _P, _P, _P, c_int, c_int, _P, c_int, c_int, c_int, c_int, _P, _P],
     "ifab_mla_q_absorb": [_P, c_long, _P, c_float, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],

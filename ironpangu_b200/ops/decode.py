@@ -400,9 +400,11 @@ def sample_topk(logits: torch.Tensor, fabric, *, top_k: int = 50, inv_temperatur
                 counts: Optional[torch.Tensor] = None, penalties: Optional[torch.Tensor] = None,
                 seeds: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None, vocab_offset: int = 0,
                 scratch: Optional[torch.Tensor] = None, out_ids: Optional[torch.Tensor] = None,
-                out_probs: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out_probs: Optional[torch.Tensor] = None, top_k_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Exact top-k / min-p / top-p sampling on vocabulary-sharded f32 logits ``[T, V_local]`` (cross-rank candidate
-    exchange inside the kernel). ``seeds``/``counters`` are int64 ``[T]``; counters advance on the device."""
+    exchange inside the kernel). ``seeds``/``counters`` are int64 ``[T]``; counters advance on the device.
+    ``top_k_rows`` (int32 ``[T]``): the k of every row when rows of different requests share the call; ``top_k`` is then
+    the largest of them (the number of candidates the ranks exchange)."""
     T, V = logits.shape
     nblocks = (V + 4095) // 4096
     dev = logits.device
@@ -410,7 +412,8 @@ def sample_topk(logits: torch.Tensor, fabric, *, top_k: int = 50, inv_temperatur
         scratch = torch.empty(T * nblocks * 64 * 2, dtype=torch.float32, device=dev)
     if out_ids is None:
         out_ids = torch.empty(T, dtype=torch.int32, device=dev)
-    check(_lib.load().ifab_sample_topk(logits.data_ptr(), logits.stride(0), T, V, vocab_offset, top_k, _ptr(inv_temperature),
+    assert top_k_rows is None or (top_k_rows.dtype == torch.int32 and top_k_rows.numel() == T and top_k_rows.is_contiguous())
+    check(_lib.load().ifab_sample_topk(logits.data_ptr(), logits.stride(0), T, V, vocab_offset, top_k, _ptr(top_k_rows), _ptr(inv_temperature),
                                        _ptr(top_p), _ptr(min_p), _ptr(counts), 0 if counts is None else counts.stride(0),
                                        _ptr(penalties), _ptr(seeds), _ptr(counters), scratch.data_ptr(), scratch.numel() * 4,
                                        out_ids.data_ptr(), _ptr(out_probs), C.byref(fabric.desc), _stream()), "sample_topk")

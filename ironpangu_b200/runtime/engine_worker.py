@@ -198,6 +198,11 @@ class BatchEngine:
                 if hit is not None and len(hit[0]) >= position + count:
                     self._restore(resident, hit[1], position, position + count)
                     self.prefix.hits += 1
+                    if self.can_sample:
+                        # the restored tokens count towards the penalties exactly as if they had been run
+                        local = torch.tensor(toks, dtype=torch.long, device=self.counts.device) - self.vocab_offset
+                        ok = (local >= 0) & (local < self.counts.shape[1])
+                        self.counts[resident, local[ok]] += 1
                     continue
                 self.prefix.misses += 1
             if self.prefill is not None and count > self.rows:
@@ -289,9 +294,11 @@ class BatchEngine:
             inv_t = torch.where(greedy, torch.full_like(self.inv_temp[rs], 1e4), self.inv_temp[rs]).contiguous()
             top_p = torch.where(greedy, torch.ones_like(self.top_p[rs]), self.top_p[rs]).contiguous()
             min_p = torch.where(greedy, torch.zeros_like(self.min_p[rs]), self.min_p[rs]).contiguous()
-            ks = [self.sampling[part[j][2]]["top_k"] or self.TOPK_CAP for j in sub if not self.sampling[part[j][2]].get("greedy", True)]
+            # every row samples with its own request's k (greedy rows: 1), whatever else shares the launch
+            k_rows = [1 if self.sampling[part[j][2]].get("greedy", True) else (self.sampling[part[j][2]]["top_k"] or self.TOPK_CAP) for j in sub]
             counters = self.counters[rs].contiguous()
-            ids = K.sample_topk(logits[c0:c0 + 64].contiguous(), d.fabric, top_k=max(ks) if ks else 1, inv_temperature=inv_t, top_p=top_p,
+            ids = K.sample_topk(logits[c0:c0 + 64].contiguous(), d.fabric, top_k=max(k_rows), inv_temperature=inv_t, top_p=top_p,
+                                top_k_rows=torch.tensor(k_rows, dtype=torch.int32, device=dev.device),
                                 min_p=min_p, counts=self.counts[rs].contiguous(), penalties=self.pen[rs].contiguous(),
                                 seeds=self.seeds[rs].contiguous(), counters=counters, vocab_offset=self.vocab_offset)
             self.counters[rs] = counters
@@ -335,9 +342,10 @@ class BatchEngine:
                 from ..ops import decode as K
                 sel = torch.tensor(hot, device=slots.device)
                 rs = slots[sel]
-                kmax = max(self.sampling[part[j][2]]["top_k"] or self.TOPK_CAP for j in hot)
+                k_rows = [self.sampling[part[j][2]]["top_k"] or self.TOPK_CAP for j in hot]     # each row keeps its own request's k
                 counters = self.counters[rs].contiguous()
-                sampled = K.sample_topk(d.logits[:n][sel].contiguous(), d.fabric, top_k=kmax, inv_temperature=self.inv_temp[rs].contiguous(),
+                sampled = K.sample_topk(d.logits[:n][sel].contiguous(), d.fabric, top_k=max(k_rows), inv_temperature=self.inv_temp[rs].contiguous(),
+                                        top_k_rows=torch.tensor(k_rows, dtype=torch.int32, device=slots.device),
                                         top_p=self.top_p[rs].contiguous(), min_p=self.min_p[rs].contiguous(),
                                         counts=self.counts[rs].contiguous(), penalties=self.pen[rs].contiguous(),
                                         seeds=self.seeds[rs].contiguous(), counters=counters, vocab_offset=self.vocab_offset)

@@ -63,6 +63,35 @@ def test_graph_replay_equals_eager():
     fab.close()
 
 
+def test_sampling_rows_keep_their_own_top_k():
+    """Rows of requests with different top_k in one call draw exactly what each draws alone (same seed, same counter)."""
+    from ironpangu_b200.ops import decode as K
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    fab = Fabric(0, 1)
+    T, V = 4, 20000
+    g = torch.Generator(device="cuda").manual_seed(3)
+    logits = torch.randn(T, V, generator=g, device="cuda") * 2
+    ks = [5, 50, 1, 64]
+    invt = torch.full((T,), 1 / 0.9, device="cuda")
+    seeds = torch.arange(T, dtype=torch.int64, device="cuda") + 101
+    together, alone = [], []
+    counters = torch.zeros(T, dtype=torch.int64, device="cuda")
+    k_rows = torch.tensor(ks, dtype=torch.int32, device="cuda")
+    for _ in range(60):
+        together.append(K.sample_topk(logits, fab, top_k=max(ks), top_k_rows=k_rows, inv_temperature=invt, seeds=seeds, counters=counters).clone())
+    for t in range(T):
+        c = torch.zeros(1, dtype=torch.int64, device="cuda")
+        alone.append(torch.stack([K.sample_topk(logits[t:t + 1], fab, top_k=ks[t], inv_temperature=invt[t:t + 1], seeds=seeds[t:t + 1],
+                                                counters=c).clone() for _ in range(60)])[:, 0])
+    together = torch.stack(together)
+    for t in range(T):
+        assert torch.equal(together[:, t], alone[t]), t
+        assert set(together[:, t].tolist()) <= set(logits[t].topk(ks[t]).indices.tolist())
+    assert len(set(together[:, 2].tolist())) == 1            # k = 1 is greedy
+    fab.close()
+
+
 def test_sampling_topk_topp_minp_exact():
     from ironpangu_b200.ops import decode as K
     from ironpangu_b200.parallel.fabric import Fabric

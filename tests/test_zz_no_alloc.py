@@ -13,8 +13,16 @@ import torch
 pytestmark = pytest.mark.gpu
 BF16 = torch.bfloat16
 
-STATIC_BYTES = 8 << 20          # IFAB_GQA_STATIC_SCRATCH_BYTES
-ERR_STATIC_SCRATCH = -6         # IFAB_ERR_STATIC_SCRATCH
+def _constants():
+    """The workspace size and the refusal code, asked of the library itself so that this file cannot drift from the header."""
+    from ironpangu_b200.ops import _lib
+
+    lib = _lib.load()
+    lib.ifab_gqa_static_scratch_bytes.restype = C.c_uint64
+    lib.ifab_gqa_static_scratch_bytes.argtypes = []
+    lib.ifab_err_static_scratch.restype = C.c_int
+    lib.ifab_err_static_scratch.argtypes = []
+    return int(lib.ifab_gqa_static_scratch_bytes()), int(lib.ifab_err_static_scratch())
 
 
 def _symbol():
@@ -88,6 +96,7 @@ def test_static_entry_refuses_what_does_not_fit():
     hq, hkv, hd = 64, 8, 256
     q, k, v, pos, slots, table = _case(3, 8, hq, hkv, hd, [5] * 8, max_pages=2)
     out = torch.zeros(8, hq * hd, dtype=BF16, device="cuda")
+    STATIC_BYTES, ERR_STATIC_SCRATCH = _constants()
     need = 8 * hq * 64 * (hd + 2) * 4
     assert need > STATIC_BYTES
     rc, msg = _call_static(fn, q, k, v, pos, slots, table, hq, hkv, hd, 64, 64, out)
@@ -95,3 +104,17 @@ def test_static_entry_refuses_what_does_not_fit():
     assert str(need) in msg and str(STATIC_BYTES) in msg
     torch.cuda.synchronize()
     assert float(out.float().abs().sum()) == 0.0      # nothing was launched
+    lib_msg = __import__("ironpangu_b200.ops._lib", fromlist=["load"]).load().ifab_error_string(ERR_STATIC_SCRATCH).decode()
+    assert "built-in" in lib_msg
+
+
+def test_context_longer_than_the_split_grid_is_attended_in_full():
+    """keys_per_split * max_splits is smaller than the context: the last split takes the tail, nothing is clipped."""
+    fn = _symbol()
+    hq, hkv, hd, kps, max_splits = 8, 2, 128, 16, 3          # 48 keys of split grid against up to 341 keys of context
+    q, k, v, pos, slots, table = _case(4, 4, hq, hkv, hd, [340, 47, 48, 200])
+    got = torch.full((4, hq * hd), float("nan"), dtype=BF16, device="cuda")
+    rc, msg = _call_static(fn, q, k, v, pos, slots, table, hq, hkv, hd, kps, max_splits, got)
+    assert rc == 0, msg
+    torch.cuda.synchronize()
+    torch.testing.assert_close(got.float(), _reference_fp32(q, k, v, pos, slots, table, hq, hkv, hd), rtol=2e-2, atol=2e-2)
