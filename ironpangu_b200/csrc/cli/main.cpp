@@ -20,6 +20,7 @@
 #include "contract.h"
 #include "bundle.h"
 #include "cpu_plan.h"
+#include "definition.h"
 #include "interp.h"
 #include "rankplan.h"
 
@@ -34,7 +35,7 @@ int usage() {
                "  synth-checkpoint MODEL OUT_DIR [--seed N]\n  interpret MODEL CHECKPOINT_DIR NEW_TOKENS TOKEN...\n"
                "  validate-bundle BUNDLE_DIR\n  inspect-checkpoint DIR [OUT.json]\n  bind-checkpoint MODEL DIR [OUT.json]\n  plan-placement MODEL [DIR|-] [OUT.json]\n"
                "  inspect FILE\n  plan GRAPH.json|MODEL.inferfabric [OUT.bin]\n  execute GRAPH.json|MODEL.inferfabric INPUTS.json\n"
-               "  compile SPEC.json OUT.bin\n  demo\n");
+               "  compile SPEC.json|MODEL.inferfabric OUT.bin\n  compile-model MODEL.inferfabric|MODEL.json [OUT.json]\n  demo\n");
   return 2;
 }
 
@@ -84,7 +85,35 @@ int compile_token(int argc, char** argv) {
 }
 
 int explain(const char* path) {
-  graph::Graph g = graph::compile_source(read_file(path, 1 << 20));
+  // a document or a model artifact of any kind: contracts and CPU graphs are summarised, token graphs also lowered
+  definition::ModelDefinition def = definition::definition(read_file(path, definition::kMaxArtifactBytes));
+  if (def.kind != definition::Kind::Execution) {
+    Json j = Json::object();
+    j.set("kind", definition::kind_name(def.kind));
+    if (def.kind == definition::Kind::Qwen) {
+      j.set("checkpoint", def.checkpoint);
+      j.set("model", def.spec.model.name);
+      size_t full = 0;
+      for (auto l : def.spec.model.layers) full += l == rankplan::Layer::Full;
+      j.set("layers", (int64_t)def.spec.model.layers.size());
+      j.set("full_attention_layers", (int64_t)full);
+      j.set("delta_layers", (int64_t)(def.spec.model.layers.size() - full));
+      j.set("prefill_ranks", def.spec.prefill.ranks());
+      j.set("decode_ranks", def.spec.decode.ranks());
+      j.set("max_context", def.spec.max_context());
+    } else if (def.kind == definition::Kind::OpenPangu) {
+      j.set("parallel", def.parallel.to_json());
+    } else {
+      j.set("model", def.logical.name);
+      j.set("nodes", (int64_t)def.logical.nodes.size());
+      cpu::PhysicalPlan plan = cpu::compile(def.logical);
+      j.set("steps", (int64_t)plan.steps.size());
+      j.set("arena_bytes", (int64_t)plan.arena_bytes);
+    }
+    std::cout << j.dump(1) << "\n";
+    return 0;
+  }
+  graph::Graph g = std::move(def.execution);
   program::Program p = program::lower(g);
   Json j = Json::object();
   j.set("model", g.name);
@@ -379,9 +408,20 @@ int main(int argc, char** argv) {
       std::cout << reports.dump(1) << "\n";
       return 0;
     }
+    if (cmd == "compile-model") {
+      // any document -> the versioned JSON artifact (inferfabric.model); an artifact is re-validated and re-written
+      if (argc < 3) return usage();
+      const std::string out = definition::encode(definition::definition(read_file(argv[2], definition::kMaxArtifactBytes)));
+      if (argc >= 4) write_file_atomic(argv[3], out);
+      else std::cout << out << "\n";
+      return 0;
+    }
     if (cmd == "compile") {
       if (argc < 4) return usage();
-      rankplan::Spec spec = rankplan::Spec::from_json(Json::parse(read_file(argv[2], 16 << 20)));
+      const std::string text = read_file(argv[2], 16 << 20);
+      const std::string path = argv[2];
+      const bool dsl = path.size() > 12 && path.compare(path.size() - 12, 12, ".inferfabric") == 0;
+      rankplan::Spec spec = dsl ? definition::parse_spec(text) : rankplan::Spec::from_json(Json::parse(text));
       rankplan::Artifact art = rankplan::compile(spec);
       write_file_atomic(argv[3], rankplan::encode(art));
       std::cout << art.to_json().dump(1) << "\n";

@@ -194,8 +194,9 @@ static std::vector<float> parse_floats(const std::string& s) {
   return d;
 }
 
-LogicalGraph from_dsl(std::string_view source) {
-  lang::Expanded ex = lang::expand(lang::parse(source));
+LogicalGraph from_dsl(std::string_view source) { return from_expanded(lang::expand(lang::parse(source))); }
+
+LogicalGraph from_expanded(const lang::Expanded& ex) {
   auto t = ex.plan.find("target");
   if (t == ex.plan.end() || t->second != "cpu_f32_v1") invalid("plan target must be cpu_f32_v1");
   LogicalGraph g;

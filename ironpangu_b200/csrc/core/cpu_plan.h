@@ -9,6 +9,7 @@
 #include <functional>
 
 #include "base.h"
+#include "lang.h"
 
 namespace ifab::cpu {
 
@@ -32,6 +33,7 @@ struct LogicalGraph {
 };
 // cpu_f32_v1 model written in the DSL (input / const / state / update members, ops add mul relu matmul).
 LogicalGraph from_dsl(std::string_view source);
+LogicalGraph from_expanded(const lang::Expanded& ex);
 
 enum class Storage { Input, Constant, State, Temporary };
 enum class Kernel { AddF32V1, MulF32V1, ReluF32V1, MatmulNaiveF32V1, MatmulBlockedF32V1 };

@@ -725,6 +725,53 @@ Json Graph::to_json() const {
   return j;
 }
 
+Graph Graph::from_json(const Json& j) {
+  if (j.at("format").as_string() != "inferfabric.token-graph.v1") invalid("not a token graph (inferfabric.token-graph.v1)");
+  Graph g;
+  g.name = j.at("name").as_string();
+  g.max_context = (uint32_t)j.at("max_context").as_int();
+  g.eos = (uint32_t)j.at("eos").as_int();
+  const Json& par = j.at("parallel");
+  g.parallel.target = par.at("target").as_string();
+  g.parallel.tp = (uint32_t)par.at("tp").as_int();
+  g.parallel.ep = (uint32_t)par.at("ep").as_int();
+  g.parallel.devices.clear();
+  for (auto& d : par.at("devices").as_array()) g.parallel.devices.push_back((uint32_t)d.as_int());
+  g.parallel.max_num_seqs = (uint32_t)par.at("max_num_seqs").as_int();
+  g.parallel.max_num_batched_tokens = (uint32_t)par.at("max_num_batched_tokens").as_int();
+  g.parallel.max_model_len = (uint32_t)par.at("max_model_len").as_int();
+  g.parallel.validate();
+  const JsonArray& nodes = j.at("nodes").as_array();
+  if (nodes.size() > 10000) fail(ErrorKind::Capacity, "graph exceeds 10000 nodes");
+  std::vector<Type> types;
+  for (auto& o : nodes) {
+    Node n;
+    n.name = o.at("name").as_string();
+    n.op = o.at("op").as_string();
+    if (!lang::primitives().count(n.op)) invalid("node " + n.name + ": unknown operator " + n.op);
+    std::vector<Type> in;
+    for (auto& i : o.at("inputs").as_array()) {
+      const int64_t k = i.as_int();
+      if (k < 0 || (size_t)k >= g.nodes.size()) invalid("node " + n.name + " reads a node that is not defined earlier");
+      n.inputs.push_back((uint32_t)k);
+      in.push_back(types[(size_t)k]);
+    }
+    for (auto& kv : o.at("attrs").as_object()) n.attrs.emplace_back(kv.first, kv.second.as_string());
+    std::sort(n.attrs.begin(), n.attrs.end());
+    if (auto b = o.find("byte")) n.byte = (size_t)b->as_int();
+    if (auto fr = o.find("frames"))
+      for (auto& f : fr->as_array()) n.frames.push_back({f.at("what").as_string(), (size_t)f.at("byte").as_int()});
+    n.type = infer(n, in, g.parallel);
+    types.push_back(n.type);
+    g.nodes.push_back(std::move(n));
+  }
+  const int64_t out = j.at("output").as_int();
+  if (out < 0 || (size_t)out >= g.nodes.size()) invalid("output index out of range");
+  g.output = (uint32_t)out;
+  g.validate();
+  return g;
+}
+
 std::map<std::string, size_t> Graph::op_histogram() const {
   std::map<std::string, size_t> h;
   for (auto& n : nodes) ++h[n.op];

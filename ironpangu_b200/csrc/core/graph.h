@@ -55,6 +55,7 @@ struct Graph {
   static Graph decode(std::string_view bytes);
   std::string dot() const;          // Graphviz
   Json to_json() const;
+  static Graph from_json(const Json& j);   // types are inferred again and the graph is validated: nothing is trusted
   std::map<std::string, size_t> op_histogram() const;
 };
 
