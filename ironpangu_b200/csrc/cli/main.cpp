@@ -21,6 +21,7 @@
 #include "bundle.h"
 #include "cpu_plan.h"
 #include "definition.h"
+#include "hybrid.h"
 #include "interp.h"
 #include "rankplan.h"
 
@@ -35,7 +36,8 @@ int usage() {
                "  synth-checkpoint MODEL OUT_DIR [--seed N]\n  interpret MODEL CHECKPOINT_DIR NEW_TOKENS TOKEN...\n"
                "  validate-bundle BUNDLE_DIR\n  inspect-checkpoint DIR [OUT.json]\n  bind-checkpoint MODEL DIR [OUT.json]\n  plan-placement MODEL [DIR|-] [OUT.json]\n"
                "  inspect FILE\n  plan GRAPH.json|MODEL.inferfabric [OUT.bin]\n  execute GRAPH.json|MODEL.inferfabric INPUTS.json\n"
-               "  compile SPEC.json|MODEL.inferfabric OUT.bin\n  compile-model MODEL.inferfabric|MODEL.json [OUT.json]\n  demo\n");
+               "  compile SPEC.json|MODEL.inferfabric OUT.bin\n  compile-model MODEL.inferfabric|MODEL.json [OUT.json]\n"
+               "  inspect-hybrid-checkpoint MODEL DIR [OUT.json]\n  compile-checkpoint MODEL DIR [OUT.json]\n  lower-checkpoint MODEL DIR CONTEXT [BATCH] [OUT.json]\n  demo\n");
   return 2;
 }
 
@@ -406,6 +408,32 @@ int main(int argc, char** argv) {
       if (inputs.is_array()) for (auto& s : inputs.as_array()) run_one(s);
       else run_one(inputs);
       std::cout << reports.dump(1) << "\n";
+      return 0;
+    }
+    if (cmd == "inspect-hybrid-checkpoint" || cmd == "compile-checkpoint" || cmd == "lower-checkpoint") {
+      // the checkpoint-bound path of the hybrid decoder family: MODEL must carry the qwen35_text_v1 contract
+      if (argc < 4) return usage();
+      const rankplan::Spec spec = definition::parse_checkpoint_spec(read_file(argv[2], definition::kMaxArtifactBytes));
+      const hybrid::Checkpoint ck = hybrid::inspect(argv[3], spec.model);
+      Json out;
+      int next = 4;
+      if (cmd == "inspect-hybrid-checkpoint") {
+        out = ck.to_json();
+      } else {
+        const hybrid::Plan plan = hybrid::compile(spec, ck);
+        if (cmd == "compile-checkpoint") {
+          out = plan.to_json();
+        } else {
+          if (argc < 5) return usage();
+          const uint32_t context = (uint32_t)std::stoul(argv[4]);
+          uint32_t batch = 1;
+          next = 5;
+          if (argc > 5 && std::string(argv[5]).find_first_not_of("0123456789") == std::string::npos) { batch = (uint32_t)std::stoul(argv[5]); next = 6; }
+          out = hybrid::lower_batch(plan, context, batch).to_json();
+        }
+      }
+      if (argc > next) write_file_atomic(argv[next], out.dump(1));
+      else std::cout << out.dump(1) << "\n";
       return 0;
     }
     if (cmd == "compile-model") {
