@@ -1,4 +1,5 @@
 #include "bundle.h"
+#include "physical.h"
 
 #include <algorithm>
 #include <cstdio>
@@ -170,65 +171,90 @@ std::string backend_fingerprint(const std::string& dir) {
   return h.hex();
 }
 
-Json physical_plan(const Program& p, const std::string& backend_fp) {
-  Json j = Json::object();
-  j.set("format", "inferfabric.physical.v1");
-  j.set("backend", "b200_sm100a");
-  j.set("backend_fingerprint", backend_fp);
-  Json steps = Json::array(), colls = Json::array(), bounds = Json::array();
+// The program as a physical inspection plan (physical.h): one operation per instruction, each with the kernel the lowering
+// selected and, where the library has another implementation of the same contract, that one as a second candidate with
+// the reason it is not eligible in a decode program. Costs are a stream model (bytes the kernel must read at the measured
+// copy rate of a B200 plus a fixed cost per launch), marked analytical with the model's name as evidence. "Logical nodes"
+// are instruction numbers of the physical program: fused kernels cover several graph nodes, instructions are unique.
+physical::Plan physical_plan(const Program& p, const std::string& backend_fp) {
+  using namespace physical;
   const uint64_t tp = p.parallel.tp;
-  uint64_t weight_bytes = 0;
+  const std::string revision = "ifab_kernels@" + (backend_fp.empty() ? std::string("unfingerprinted") : backend_fp.substr(0, 16));
+  auto stream_cost = [](uint64_t bytes) {
+    Cost c;
+    c.source = CostSource::Analytical;
+    c.estimate_ns = 2000 + bytes / 6400;       // 6.4 TB/s = 6400 bytes per ns
+    c.upper_ns = 6000 + bytes / 3200;          // half that rate, and a cold launch
+    c.evidence = "stream-model-1: weight bytes at 6.4 TB/s + 2 us per dependent launch";
+    return c;
+  };
+  std::vector<Operation> ops;
+  std::vector<Value> values;
+  size_t sequence = 0;
   for (uint32_t k = 0; k < p.instructions.size(); ++k) {
     const Instruction& i = p.instructions[k];
-    Json s = Json::object();
-    s.set("instruction", k);
-    s.set("op", i.op);
-    s.set("candidate", i.kernel);
-    s.set("location", i.kernel == "view" ? "alias" : "device");
-    uint64_t K = i.inputs.empty() ? 0 : p.instructions[i.inputs[0]].width;
+    Operation op;
+    op.name = i.name.empty() ? i.op : i.name;
+    op.logical_nodes = {k};
+    for (auto in : i.inputs) op.inputs.push_back(in);
+    const bool launches = i.kernel != "view" && i.kernel != "none";
+    const uint64_t K = i.inputs.empty() ? 0 : p.instructions[i.inputs[0]].width;
     uint64_t wbytes = 0;
     if (i.op == "linear" || i.op == "linear_allreduce" || i.op == "lm_head") wbytes = K * i.width * 2 * (i.attr("activation") ? 2 : 1) / (i.op == "lm_head" ? tp : 1);
     if (i.op == "embedding") wbytes = (uint64_t)i.width * 2;
-    Json cost = Json::object();
-    cost.set("weight_bytes_per_token", wbytes);
-    cost.set("flops_per_token", wbytes);  // one MAC per bf16 weight element = bytes
-    s.set("cost", cost);
-    weight_bytes += wbytes;
-    steps.push(s);
-    if (i.op == "linear_allreduce" || i.op == "moe_down_allreduce" || i.op == "allreduce") {
-      Json c = Json::object();
-      c.set("instruction", k);
-      c.set("collective", "all_reduce_sum");
-      c.set("fused_into", i.kernel);
-      c.set("payload_bytes_per_token", (uint64_t)i.width * 4);
-      c.set("ranks", tp);
-      c.set("algorithm", i.attr("bulk") ? "two_shot_reduce_scatter_all_gather" : "one_shot_push");
-      colls.push(c);
-    } else if (i.op == "lm_head") {
-      Json c = Json::object();
-      c.set("instruction", k);
-      c.set("collective", "argmax_exchange");
-      c.set("fused_into", i.kernel);
-      c.set("payload_bytes_per_token", 8);
-      c.set("ranks", tp);
-      colls.push(c);
-    } else if (i.op == "gather") {
-      Json c = Json::object();
-      c.set("instruction", k);
-      c.set("collective", "all_gather");
-      c.set("payload_bytes_per_token", (uint64_t)i.width * 2 / tp);
-      c.set("ranks", tp);
-      colls.push(c);
+    // the kernel field names the decode kernel and, after '|', the kernel that takes the same instruction for bulk rows
+    const size_t bar = i.kernel.find('|');
+    const std::string decode_kernel = i.kernel.substr(0, bar), bulk_kernel = bar == std::string::npos ? "" : i.kernel.substr(bar + 1);
+    Candidate c;
+    c.id = launches ? decode_kernel : "view";
+    c.contract_revision = revision;
+    c.numerical_contract = launches ? (i.dtype.empty() ? "none" : i.dtype) + std::string(" storage, f32 accumulation, sums in rank order") : "alias of its input";
+    c.capture_qualified = true;
+    c.workspace_bound_bytes = 0;
+    if (i.op == "mla_attention" || i.op == "paged_attention") {
+      c.workspace_bound_bytes.reset();
+      c.unresolved.push_back("split-KV partials: sized from max_context when the engine prepares the program");
     }
+    if (i.op == "moe_gate_up" || i.op == "moe_down_allreduce") c.unresolved.push_back("expert bytes depend on the routes of the step: the cost counts the launch only");
+    if (launches) {
+      c.cost = stream_cost(wbytes);
+    } else {
+      c.cost.source = CostSource::Analytical;
+      c.cost.estimate_ns = c.cost.upper_ns = 0;
+      c.cost.evidence = "no launch";
+    }
+    if (i.op == "embedding") c.boundaries.push_back({BoundaryKind::ControlUpload, "token ids, positions, slots and the page table are written by the engine before the step"});
+    if (i.op == "lm_head") c.boundaries.push_back({BoundaryKind::RequestOutput, "the sampled token id (4 bytes per row) is what the engine reads after the step"});
+    if (i.op == "kv_cache_append" || i.op == "mla_attention" || i.op == "paged_attention" || i.op == "mome") c.boundaries.push_back({BoundaryKind::PersistentState, "reads or writes a resident sequence state"});
+    op.candidates.push_back(std::move(c));
+    if (!bulk_kernel.empty()) {
+      Candidate g = op.candidates[0];
+      g.id = bulk_kernel;
+      g.eligible = false;
+      g.rejection = "the bulk-row kernel of this instruction (tensor cores): takes 9 or more rows per step, a decode step has at most 8";
+      g.boundaries.clear();
+      op.candidates.push_back(std::move(g));
+    }
+    if (i.op == "linear_allreduce" || i.op == "moe_down_allreduce" || i.op == "allreduce") {
+      op.collective = Collective{"all_ranks", i.attr("bulk") ? "all_reduce_sum (reduce-scatter + all-gather in the GEMM epilogue)" : "all_reduce_sum (one-shot push in the kernel epilogue)", "f32", i.width, sequence++};
+    } else if (i.op == "lm_head") {
+      op.collective = Collective{"all_ranks", "argmax_exchange", "f32+i32", 2, sequence++};
+    } else if (i.op == "gather") {
+      op.collective = Collective{"all_ranks", "all_gather", "bf16", std::max<uint64_t>(1, i.width / tp), sequence++};
+    }
+    ops.push_back(std::move(op));
+    Value v;
+    v.logical_node = k;
+    const std::string dt = i.dtype == "int8" ? "i8" : i.dtype;
+    if ((dt == "bf16" || dt == "f32" || dt == "i8" || dt == "i32") && i.width > 0 && i.kind <= 3) {
+      v.dtype = dt;
+      v.shape = {1, i.width};
+      v.payload_bytes = (uint64_t)i.width * (dt == "bf16" ? 2 : dt == "i8" ? 1 : 4);
+      v.alignment = 512;
+    }
+    values.push_back(std::move(v));
   }
-  for (auto role : {"ControlInput: token ids, positions, slots, page table (host -> device)",
-                    "RequestOutput: sampled token ids (device -> host)",
-                    "ParameterPreparation: weights at start-up only (host -> device)"}) bounds.push(role);
-  j.set("steps", steps);
-  j.set("collectives", colls);
-  j.set("boundaries", bounds);
-  j.set("weight_bytes_streamed_per_token_dense_part", weight_bytes);
-  return j;
+  return serial_plan(p.name, p.parallel.target, Sha256::of(p.encode()), p.parallel.devices, std::move(ops), std::move(values), {p.output});
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -304,7 +330,7 @@ BundleSummary write_bundle(const BundleInputs& in, const std::string& out_dir) {
     put("execution.dot", g.dot());
     put("execution.html", html_view(g, p, arena));
     put("device-program.json", p.to_json().dump(1));
-    put("physical.json", physical_plan(p, bfp).dump(1));
+    put("physical.json", physical_plan(p, bfp).to_json().dump(1));
     put("serving.json", man.to_json().dump(1));
     for (auto& pl : plans) {
       put("rank-" + std::to_string(pl.rank) + ".bin", pl.encode());

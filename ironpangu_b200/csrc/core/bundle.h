@@ -12,6 +12,7 @@
 // native/include/frozen_arena.h:14-99, token_physical.rs:14-273.
 #pragma once
 #include "initplan.h"
+#include "physical.h"
 #include "serving.h"
 
 namespace ifab::bundle {
@@ -37,7 +38,7 @@ Arena plan_arena(const program::Program& p, uint32_t tokens);
 uint64_t value_bytes(const program::Program& p, const program::Instruction& ins, uint32_t tokens);
 
 // ---- inspection plan -------------------------------------------------------------------------------
-Json physical_plan(const program::Program& p, const std::string& backend_fingerprint);
+physical::Plan physical_plan(const program::Program& p, const std::string& backend_fingerprint);
 // SHA-256 over the kernel sources that execute the program (sorted by file name); "" if dir is empty.
 std::string backend_fingerprint(const std::string& kernel_source_dir);
 

@@ -9,6 +9,8 @@
 #include "chat_parse.h"
 #include "contract.h"
 #include "cpu_plan.h"
+#include "device_buffer.h"
+#include "physical.h"
 #include "initplan.h"
 #include "paging.h"
 #include "prefix_index.h"
@@ -618,8 +620,152 @@ static void test_init_plan_reference_layout() {
   fs::remove_all(dir);
 }
 
+static physical::Candidate device_candidate(const std::string& id, std::optional<uint64_t> est = std::nullopt, std::optional<uint64_t> upper = std::nullopt) {
+  physical::Candidate c;
+  c.id = id;
+  c.contract_revision = "kernels@1";
+  c.numerical_contract = "bf16 in, f32 accumulate, bf16 out";
+  if (est) {
+    c.cost.source = physical::CostSource::Analytical;
+    c.cost.estimate_ns = est;
+    c.cost.upper_ns = upper ? upper : est;
+    c.cost.evidence = "stream-model-1";
+  }
+  return c;
+}
+
+static void test_physical_inspection_plan() {
+  using namespace physical;
+  // choice: complete costs -> cheapest conservative bound; any unknown cost -> stable baseline, never "unknown = free"
+  std::vector<Candidate> cs = {device_candidate("b_fast", 900, 1000), device_candidate("a_slow", 800, 2000)};
+  Choice c = choose(cs);
+  CHECK(c.index == 0 && c.reason.find("cheapest") != std::string::npos);
+  cs.push_back(device_candidate("c_unknown"));
+  c = choose(cs);
+  CHECK(cs[c.index].id == "a_slow" && c.reason.find("no latency is compared") != std::string::npos);
+  // an ineligible candidate is skipped but must say why
+  cs[1].eligible = false;
+  CHECK_THROWS(Invalid, choose(cs));
+  cs[1].rejection = "needs at least 9 rows";
+  CHECK(cs[choose(cs).index].id == "b_fast");
+  // residency is checked before cost: a host candidate, or one that copies through the host, is refused even if rejected
+  auto host = cs;
+  host[2].location = Location::Host;
+  host[2].eligible = false;
+  host[2].rejection = "cpu fallback";
+  CHECK_THROWS(Invalid, choose(host));
+  auto copy = cs;
+  copy[0].boundaries.push_back({BoundaryKind::DeviceToHost, "reads the routing table back"});
+  CHECK_THROWS(Invalid, choose(copy));
+  auto numerics = cs;
+  numerics[2].numerical_contract = "fp8";
+  CHECK_THROWS(Invalid, choose(numerics));
+  auto cost = cs;
+  cost[0].cost.upper_ns = 100;   // bound below the estimate
+  CHECK_THROWS(Invalid, choose(cost));
+  CHECK_THROWS(Invalid, choose({}));
+
+  // a three-step plan: embedding -> linear (+ all-reduce) -> head; one value per step
+  auto op = [&](const char* name, size_t node, std::vector<size_t> in, std::vector<Candidate> cand) {
+    Operation o;
+    o.name = name;
+    o.logical_nodes = {node};
+    o.inputs = std::move(in);
+    o.candidates = std::move(cand);
+    return o;
+  };
+  auto val = [&](size_t node, uint64_t cols) {
+    Value v;
+    v.logical_node = node;
+    v.dtype = "bf16";
+    v.shape = {1, cols};
+    v.payload_bytes = 2 * cols;
+    v.alignment = 256;
+    return v;
+  };
+  std::vector<Operation> ops = {op("embed", 0, {}, {device_candidate("ifab_embedding_bf16", 2000)}),
+                                op("o_proj", 3, {0}, {device_candidate("ifab_gemv_allreduce_bf16", 8000, 9000)}),
+                                op("head", 7, {1}, {device_candidate("ifab_lm_head_argmax", 60000)})};
+  ops[1].collective = Collective{"all_ranks", "all_reduce_sum", "f32", 4096, 0};
+  Plan p = serial_plan("toy", "b200_token_v1", std::string(64, 'd'), {0, 1}, ops, {val(0, 4096), val(3, 4096), val(7, 8)}, {2});
+  CHECK(p.schedule.estimated_serial_ns && *p.schedule.estimated_serial_ns == 70000 && p.schedule.cost_complete && !p.executable);
+  CHECK(p.schedule.values[0].last == 1 && p.schedule.values[1].last == 2 && p.schedule.values[2].last == 3);
+  CHECK(p.schedule.steps[2].order_dependencies == std::vector<size_t>{1});
+  // JSON round trip, then tampering: every derived fact is recomputed by verify
+  Plan q = Plan::from_json(Json::parse(p.to_json().dump()));
+  verify(q);
+  CHECK(q.to_json().dump() == p.to_json().dump());
+  { Plan t = q; t.schedule.steps[1].selected = 5; CHECK_THROWS(Invalid, verify(t)); }
+  { Plan t = q; t.schedule.values[0].last = 2; CHECK_THROWS(Invalid, verify(t)); }
+  { Plan t = q; t.schedule.values[1].payload_bytes = 9000; CHECK_THROWS(Invalid, verify(t)); }
+  { Plan t = q; t.schedule.estimated_serial_ns = 1; CHECK_THROWS(Invalid, verify(t)); }
+  { Plan t = q; t.schedule.steps[1].operation.collective->sequence = 1; CHECK_THROWS(Invalid, verify(t)); }
+  { Plan t = q; t.executable = true; CHECK_THROWS(Invalid, verify(t)); }
+  { Plan t = q; t.devices = {3, 3}; CHECK_THROWS(Invalid, verify(t)); }
+  { Plan t = q; t.schedule.steps[2].operation.logical_nodes = {3}; CHECK_THROWS(Invalid, verify(t)); }
+  { Plan t = q; t.schedule.steps[1].stream = 1; CHECK_THROWS(Invalid, verify(t)); }
+  // a cost of unknown source makes the summary incomplete rather than smaller
+  ops[2].candidates = {device_candidate("ifab_lm_head_argmax")};
+  Plan u = serial_plan("toy", "b200_token_v1", std::string(64, 'd'), {0}, ops, {val(0, 4096), val(3, 4096), val(7, 8)}, {2});
+  CHECK(!u.schedule.cost_complete && !u.schedule.estimated_serial_ns);
+  ops[1].inputs = {2};
+  CHECK_THROWS(Invalid, serial_plan("toy", "t", "d", {0}, ops, {val(0, 4096), val(3, 4096), val(7, 8)}, {2}));
+}
+
+static void test_device_buffer_contract() {
+  using namespace device_buffer;
+  Invocation call;
+  call.implementation = "swiglu_cuda";
+  call.binary_sha256 = std::string(64, 'a');
+  call.numerical_contract = "inferfabric.swiglu.bf16.v1";
+  call.rank = 1;
+  call.device = 1;
+  call.allocations = {{7, 1, 1, 1 << 20, 256, MemoryClass::Activation, false}, {9, 1, 1, 4096, 256, MemoryClass::Workspace, false},
+                      {3, 1, 1, 1 << 16, 256, MemoryClass::Weight, true}};
+  TensorView x{7, 0, DType::Bf16, {4, 256}, {256, 1}, 16, Access::Read};
+  TensorView w{3, 512, DType::Bf16, {128}, {1}, 16, Access::Read};
+  TensorView y{7, 4096, DType::Bf16, {4, 128}, {128, 1}, 16, Access::Write};
+  call.inputs = {x, w};
+  call.outputs = {y};
+  call.workspace = Workspace{9, 0, 2048, 256};
+  call.verify();
+  CHECK(x.byte_span() == 2048);
+  Invocation again = Invocation::from_json(Json::parse(call.to_json().dump()));
+  again.verify();
+  CHECK(again.to_json().dump() == call.to_json().dump());
+  { Invocation c = call; c.outputs[0].offset = 1024; CHECK_THROWS(Invalid, c.verify()); }                       // output overlaps an input
+  { Invocation c = call; c.outputs.push_back(y); CHECK_THROWS(Invalid, c.verify()); }                            // two outputs overlap
+  { Invocation c = call; c.inputs[0].strides = {512, 1}; CHECK_THROWS(Invalid, c.verify()); }                    // not contiguous
+  { Invocation c = call; c.outputs[0].allocation = 3; c.outputs[0].offset = 0; CHECK_THROWS(Invalid, c.verify()); }   // write into weights
+  { Invocation c = call; c.allocations[2].read_only = false; CHECK_THROWS(Invalid, c.verify()); }                // writable weight
+  { Invocation c = call; c.inputs[1].offset = 513; CHECK_THROWS(Invalid, c.verify()); }                          // misaligned
+  { Invocation c = call; c.inputs[0].shape = {4096, 256}; c.inputs[0].strides = {256, 1}; CHECK_THROWS(Invalid, c.verify()); }   // outside
+  { Invocation c = call; c.allocations.push_back({11, 1, 1, 64, 64, MemoryClass::State, false}); CHECK_THROWS(Invalid, c.verify()); }   // unused
+  { Invocation c = call; c.allocations[0].device = 2; CHECK_THROWS(Invalid, c.verify()); }                       // other device
+  { Invocation c = call; c.workspace->allocation = 7; c.workspace->offset = 4096; CHECK_THROWS(Invalid, c.verify()); }   // workspace on a tensor
+  { Invocation c = call; c.binary_sha256 = "xyz"; CHECK_THROWS(Invalid, c.verify()); }
+  call.verify_prepared(std::string(64, 'a'), "inferfabric.swiglu.bf16.v1", 1024, 128);
+  CHECK_THROWS(Invalid, call.verify_prepared(std::string(64, 'a'), "inferfabric.swiglu.bf16.v1", 4096, 128));   // larger than frozen
+  CHECK_THROWS(Invalid, call.verify_prepared(std::string(64, 'b'), "inferfabric.swiglu.bf16.v1", 0, 1));        // another binary
+  { Invocation c = call; c.workspace.reset(); c.allocations.erase(c.allocations.begin() + 1); c.verify_prepared(std::string(64, 'a'), "inferfabric.swiglu.bf16.v1", 0, 1);
+    CHECK_THROWS(Invalid, c.verify_prepared(std::string(64, 'a'), "inferfabric.swiglu.bf16.v1", 16, 16)); }
+  // binding: descriptors carry absolute addresses (simulated here: they are never dereferenced)
+  char* base = (char*)(uintptr_t)0x7f0000000000ull;
+  std::vector<ResidentAllocation> res = {{7, base, 1 << 20, 1, 1}, {9, base + (2 << 20), 4096, 1, 1}, {3, base + (4 << 20), 1 << 16, 1, 1}};
+  BoundInvocation b = device_buffer::bind(call, res);
+  CHECK(b.inputs.size() == 2 && b.outputs.size() == 1 && b.outputs[0].data == base + 4096 && b.outputs[0].access == 2 && b.outputs[0].dtype == 2);
+  CHECK(b.inputs[0].shape[1] == 256 && b.inputs[0].strides[0] == 256 && b.inputs[0].allocation_bytes == (1u << 20) && b.workspace == base + (2 << 20) && b.workspace_bytes == 2048);
+  { auto r = res; r[1].base = base + 4096; CHECK_THROWS(Invalid, device_buffer::bind(call, r)); }          // another id, same memory as the output
+  { auto r = res; r[0].bytes = 1 << 10; CHECK_THROWS(Invalid, device_buffer::bind(call, r)); }             // smaller than recorded
+  { auto r = res; r[2].device = 0; CHECK_THROWS(Invalid, device_buffer::bind(call, r)); }
+  { auto r = res; r[0].base = base + 8; CHECK_THROWS(Invalid, device_buffer::bind(call, r)); }             // misaligned base
+  { auto r = res; r.pop_back(); CHECK_THROWS(Invalid, device_buffer::bind(call, r)); }
+  CHECK(support().at("kernel_abi").as_string() == "IFKernelTensorV1");
+}
+
 int main() {
   std::pair<const char*, std::function<void()>> tests[] = {
+      {"physical_inspection_plan", test_physical_inspection_plan}, {"device_buffer_contract", test_device_buffer_contract},
       {"init_plan_reference_layout", test_init_plan_reference_layout},
       {"serve_batching", test_serve_batching_matches_sequential}, {"serve_admission", test_serve_validation_and_admission},
       {"serve_backpressure_cancel", test_serve_backpressure_cancel_and_eos}, {"serve_failure_shutdown", test_serve_engine_failure_and_shutdown},

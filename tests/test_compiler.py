@@ -93,6 +93,16 @@ def test_bundle_files_init_plans_and_no_overwrite(tmp_path):
     assert ts[-1] == "model.layers.5.mlp.experts.47.up_proj.weight" and len(ts) == 24
     # router weights are widened bf16 -> f32 only if the checkpoint stores bf16; here the synthetic metadata is f32
     assert by["model.layers.0.mlp.gate"]["dtype"] == "f32"
+    # the physical inspection plan: one step per instruction, the selected kernel first among its candidates, every
+    # all-reduce / gather / argmax exchange numbered in order, a complete analytical cost, nothing executable claimed
+    phys = json.loads((out / "physical.json").read_text())
+    sched = phys["schedules"][0]
+    assert phys["format"] == "inferfabric.physical.v1" and phys["executable"] is False and len(phys["ranks"]) == 8
+    assert len(sched["steps"]) == s["instructions"] and sched["cost_complete"] and sched["estimated_serial_ns"] > 500_000
+    colls = [st["operation"]["collective"] for st in sched["steps"] if st["operation"]["collective"]]
+    assert [c["sequence"] for c in colls] == list(range(len(colls))) and len(colls) == s["collectives_per_token"]
+    lin = next(st for st in sched["steps"] if st["operation"]["candidates"][0]["id"] == "ifab_gemv_allreduce_bf16")
+    assert lin["selected"] == 0 and lin["operation"]["candidates"][1]["eligible"] is False and "9 or more rows" in lin["operation"]["candidates"][1]["rejection"]
     man = json.loads((out / "serving.json").read_text())
     assert len(man["states"]) == 46 and man["states"][0]["storage"] == {"kind": "pages", "page_tokens": 16, "row_bytes": 1152}
     arena = (out / "arena-rank-0.txt").read_text().split("\n")[0].split()
