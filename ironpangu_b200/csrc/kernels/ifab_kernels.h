@@ -97,6 +97,17 @@ int ifab_mla_merge(const float* scratch, const int32_t* positions, int n_sinks, 
                    int max_splits, int T, int H, void* o_lat, void* stream);
 /* one-shot pull all-reduce of f32 [rows, D] partials held in symmetric memory (parts[r] = rank r's buffer as mapped here),
  * + residual, bf16 out. The caller alternates two sets of partial buffers between consecutive calls. */
+/* ---- prompt attention on the tensor cores (tcgen05): one sequence, consecutive positions, causal (+ sliding window) ----
+ * q: [m, ...] head h at columns h * q_head_stride + [0, d1 + d2); k: [ctx, ...] key head g = h / kv_group at columns
+ * g * k_head_stride + [0, d1); k2: [ctx, d2] key columns shared by all heads (NULL when d2 = 0); vt: transposed values, key head g
+ * at rows g * vt_head_stride + vt_row0 + [0, 128), one column per key (ldvt >= ctx); out: [m, H * 128].
+ * d1 in {64, 128}, d2 in {0, 64}; rows of q are positions pos0 .. pos0 + m - 1 and pos0 + m <= ctx. */
+int ifab_fa_prefill_bf16(const void* q, long ldq, int q_head_stride, const void* k, long ldk, int k_head_stride, const void* k2, long ldk2,
+                         const void* vt, long ldvt, int vt_head_stride, int vt_row0, int vt_rows, void* out, long ldo, int m, int ctx, int H,
+                         int kv_group, int d1, int d2, int pos0, int window, float scale, uint32_t* status, void* stream);
+int ifab_mla_q_rope_inplace(void* q, long ldq, const int32_t* positions, int T, int H, int nope, int rope, float theta, void* stream);
+int ifab_mla_ctx_gather(const void* cache, const int32_t* page_table, int slot, int max_pages, int page_tokens, int num_pages, int ctx,
+                        int rows, void* lat, void* pe, uint32_t* status, void* stream);
 int ifab_allreduce_rows(const void* const* parts, const void* residual, long ldr, void* out, long ldo, long rows, int D,
                         const IfabFabric* fab, void* stream);
 /* NVLS (NVLink multicast) form: two-shot - each rank reduces 1/world of the buffer with multimem.ld_reduce and writes the

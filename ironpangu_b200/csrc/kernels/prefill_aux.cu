@@ -35,6 +35,44 @@ __global__ void __launch_bounds__(64) mla_q_rope_kernel(const bf16* q, long ldq,
   out[i + half] = __float2bfloat16_rn(b * c + a * s);
 }
 
+// rotary columns of every head of a [T, H * (nope + rope)] query matrix, rotated in place (thread i owns the pair i, i + rope / 2)
+__global__ void __launch_bounds__(64) mla_q_rope_inplace_kernel(bf16* q, long ldq, const int32_t* positions, int nope, int rope, float theta) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int h = blockIdx.x, t = blockIdx.y;
+  const int half = rope / 2;
+  const int i = threadIdx.x;
+  if (i >= half) return;
+  const int pos = positions[t];
+  bf16* qr = q + (long)t * ldq + (long)h * (nope + rope) + nope;
+  float c, s;
+  rope_cos_sin(pos < 0 ? 0 : pos, i, rope, theta, &c, &s);
+  const float a = __bfloat162float(qr[i]), b = __bfloat162float(qr[i + half]);
+  qr[i] = __float2bfloat16_rn(a * c - b * s);
+  qr[i + half] = __float2bfloat16_rn(b * c + a * s);
+}
+
+// The latent cache rows of keys 0 .. ctx - 1 of one sequence slot, copied out of their pages into two dense matrices: the
+// latent part [rows, 512] and the rotary part [rows, 64]; rows from ctx up to `rows` are zero. One CTA per row, one
+// 16-byte chunk per thread.
+__global__ void __launch_bounds__(72) mla_ctx_gather_kernel(const bf16* cache, const int32_t* page_table, int slot, int max_pages, int page_tokens,
+                                                            int num_pages, int ctx, bf16* lat, bf16* pe, uint32_t* status) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int r = blockIdx.x, c = threadIdx.x;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (r < ctx) {
+    const long row = cache_row_of(r, slot, page_table, max_pages, page_tokens, num_pages);
+    if (row < 0) {
+      if (c == 0 && status) atomicOr(status, IFAB_STATUS_BAD_INDEX);
+    } else {
+      v = *reinterpret_cast<const uint4*>(cache + row * ROW + c * 8);
+    }
+  }
+  if (c < LATENT / 8) *reinterpret_cast<uint4*>(lat + (long)r * LATENT + c * 8) = v;
+  else *reinterpret_cast<uint4*>(pe + (long)r * ROPE + (c - LATENT / 8) * 8) = v;
+}
+
 struct MergeParams {
   const float* scratch;   // [T][H][max_splits][LATENT + 2]
   const int32_t* positions;
@@ -318,4 +356,17 @@ extern "C" int ifab_allreduce_rows_nvls(void* part_local, void* part_mc, const v
   }
   const int grid = (int)std::min<long>(sms, (chunks + 255) / 256);
   return launch_chain(allreduce_rows_nvls_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p);
+}
+
+extern "C" int ifab_mla_q_rope_inplace(void* q, long ldq, const int32_t* positions, int T, int H, int nope, int rope, float theta, void* stream) {
+  if (rope != ROPE || T < 1 || H < 1) return -1;
+  return launch_chain(mla_q_rope_inplace_kernel, dim3(H, T), dim3(64), 0, (cudaStream_t)stream, (bf16*)q, ldq, positions, nope, rope, theta);
+}
+
+// lat: [rows, 512], pe: [rows, 64] (rows >= ctx; the tail is zeroed)
+extern "C" int ifab_mla_ctx_gather(const void* cache, const int32_t* page_table, int slot, int max_pages, int page_tokens, int num_pages, int ctx,
+                                   int rows, void* lat, void* pe, uint32_t* status, void* stream) {
+  if (ctx < 1 || rows < ctx || slot < 0) return -1;
+  return launch_chain(mla_ctx_gather_kernel, dim3(rows), dim3(72), 0, (cudaStream_t)stream, (const bf16*)cache, page_table, slot, max_pages,
+                      page_tokens, num_pages, ctx, (bf16*)lat, (bf16*)pe, status);
 }

@@ -75,6 +75,18 @@ class MlaMoePrefill:
         self._calls = 0
         # W_uk^T per head: [hl, latent, nope], the [N, K] operand of the absorb GEMM
         self.w_uk_t = [dec.w[f"layers.{l}.kv_b"][:, :c.nope, :].transpose(1, 2).contiguous() for l in range(c.layers)]
+        # Prompt attention on the tensor cores (chunks of consecutive positions of one sequence): the context's latent rows are
+        # gathered out of their pages, up-projected for all local heads by two GEMMs (keys as [ctx, heads x 256], values
+        # transposed as [heads x 256, ctx]) and attended by the tcgen05 attention kernel in the per-head form - a third of the
+        # arithmetic of attention over the 576-wide latent rows, no per-head projection launches, no split / merge passes.
+        self.tc_attention = (not dec.kv_int8 and c.kv_lora == 512 and c.rope == 64 and c.nope == 128 and c.vdim == 128)
+        if self.tc_attention:
+            cap = (dec.max_context + 127) // 128 * 128
+            self.ctx_lat = torch.zeros(cap, c.kv_lora, dtype=BF16, device=dev)
+            self.ctx_pe = torch.zeros(cap, c.rope, dtype=BF16, device=dev)
+            self.kv_up = e(cap, hl * (c.nope + c.vdim))
+            self.kvt = e(hl * (c.nope + c.vdim), cap)
+        self._contig = None            # (first position, slot) of the chunk being run, None for rows of many sequences
         self.launches = 0
         # CUDA graphs of the layer stack, one per row count (the few most recent): a chunk is ~100 launches per layer and at
         # 4-8 GPUs the host cannot issue them as fast as the devices finish them. The all-reduce staging buffers alternate per
@@ -85,7 +97,8 @@ class MlaMoePrefill:
     def _layers_graphed(self, m: int) -> torch.Tensor:
         if not self.use_graphs:
             return self._layers(m)
-        g = self._graphs.get(m)
+        key = (m, self._contig if self.tc_attention else None)       # the tensor-core attention bakes positions into its launches
+        g = self._graphs.get(key)
         if g is not None:
             g.replay()
             return self.x[:m]
@@ -98,7 +111,7 @@ class MlaMoePrefill:
         self._calls = calls
         if len(self._graphs) >= 4:
             self._graphs.pop(next(iter(self._graphs)))
-        self._graphs[m] = g
+        self._graphs[key] = g
         return x
 
     def forward(self, tokens: torch.Tensor, pos0: int, slot: int = 0) -> torch.Tensor:
@@ -111,6 +124,7 @@ class MlaMoePrefill:
         self.tokens[:m].copy_(tokens)
         self.positions[:m].copy_(torch.arange(pos0, pos0 + m, dtype=torch.int32, device=tokens.device))
         self.slots[:m].fill_(slot)
+        self._contig = (int(pos0), int(slot))
         x = self._layers_graphed(m)
         # greedy token after the last row through the decode head (vocabulary-sharded argmax exchange included)
         K.lm_head_argmax(x[m - 1:m], w["lm_head"], fab, norm_w=w["final_norm"], eps=c.eps, vocab_offset=d.rank * d.vl,
@@ -129,6 +143,7 @@ class MlaMoePrefill:
         self.tokens[:m].copy_(tokens)
         self.positions[:m].copy_(positions)
         self.slots[:m].copy_(slots)
+        self._contig = None
         x = self._layers_graphed(m)
         xn = K.rmsnorm(x.index_select(0, select), d.w["final_norm"], c.eps)
         self.launches += 2
@@ -153,17 +168,21 @@ class MlaMoePrefill:
             K.rmsnorm(qkv[:, :c.q_lora], w[p + "q_a_norm"], c.eps, out=self.qn[:m])
             q = G.gemm(self.qn[:m], w[p + "q_b"], out=self.q[:m], status_ptr=st)
             q_lat, o_lat, attn = self.q_lat[:m], self.o_lat[:m], self.attn[:m]
-            for hh in range(hl):
-                G.gemm(q[:, hh * c.qk_dim: hh * c.qk_dim + c.nope], self.w_uk_t[l][hh], out=q_lat[:, hh, :c.kv_lora], status_ptr=st)
-            P.mla_q_rope(q, pos, q_lat, nope=c.nope, rope=c.rope, theta=c.theta)
-            for q0 in range(0, m, self.QC):
-                q1 = min(m, q0 + self.QC)
-                P.mla_split(q_lat[q0:q1], d.caches[l], pos[q0:q1], sl[q0:q1], d.page_table, self.scratch, scale=c.scale,
-                            window=c.window, keys_per_split=d.kps, max_splits=d.max_splits, status_ptr=st)
-                P.mla_merge(self.scratch, pos[q0:q1], o_lat[q0:q1], window=c.window, keys_per_split=d.kps, max_splits=d.max_splits)
-            kvb = w[p + "kv_b"]
-            for hh in range(hl):
-                G.gemm(o_lat[:, hh, :], kvb[hh, c.nope:, :], out=attn[:, hh * c.vdim:(hh + 1) * c.vdim], status_ptr=st)
+            if self.tc_attention and self._contig is not None:
+                pos0, slot = self._contig
+                ctx = pos0 + m
+                rows = (ctx + 63) // 64 * 64
+                kvb = w[p + "kv_b"].view(hl * (c.nope + c.vdim), c.kv_lora)
+                P.mla_ctx_gather(d.caches[l], d.page_table, slot, ctx, self.ctx_lat[:rows], self.ctx_pe[:rows], status_ptr=st)
+                G.gemm(self.ctx_lat[:rows], kvb, out=self.kv_up[:rows], status_ptr=st)
+                G.gemm(kvb, self.ctx_lat[:rows], out=self.kvt[:, :rows], status_ptr=st)
+                P.mla_q_rope_inplace(q, pos, heads=hl, nope=c.nope, rope=c.rope, theta=c.theta)
+                P.fa_prefill(q, self.kv_up, self.kvt, attn, heads=hl, q_head_stride=c.qk_dim, k_head_stride=c.nope + c.vdim,
+                             vt_head_stride=c.nope + c.vdim, vt_row0=c.nope, d1=c.nope, d2=c.rope, k2=self.ctx_pe, ctx=ctx, pos0=pos0,
+                             scale=c.scale, window=c.window, status_ptr=st)
+                n_launch += 5 - 2 * hl - 1 - 2 * ((m + self.QC - 1) // self.QC)
+            else:
+                self._latent_attention(l, m, q, q_lat, o_lat, attn)
             if fab.world > 1:
                 G.gemm_allreduce(attn, w[p + "o_proj"], fab, self._sym_rows(m), residual=x)
             else:
@@ -188,6 +207,26 @@ class MlaMoePrefill:
             n_launch += 17 + 2 * hl + 2 * ((m + self.QC - 1) // self.QC)
         self.launches = n_launch + 1
         return x
+
+    def _latent_attention(self, l: int, m: int, q, q_lat, o_lat, attn) -> None:
+        """Attention of layer ``l`` in the absorbed (latent) form on the split-KV kernels, one query row per token with its own
+        position and sequence slot: the form for rows of many sequences, quantised caches and head shapes the tensor-core
+        kernel does not take."""
+        d, c = self.dec, self.dec.cfg
+        w, st, hl = d.w, d.fabric.desc.status, d.hl
+        p = f"layers.{l}."
+        pos, sl = self.positions[:m], self.slots[:m]
+        for hh in range(hl):
+            G.gemm(q[:, hh * c.qk_dim: hh * c.qk_dim + c.nope], self.w_uk_t[l][hh], out=q_lat[:, hh, :c.kv_lora], status_ptr=st)
+        P.mla_q_rope(q, pos, q_lat, nope=c.nope, rope=c.rope, theta=c.theta)
+        for q0 in range(0, m, self.QC):
+            q1 = min(m, q0 + self.QC)
+            P.mla_split(q_lat[q0:q1], d.caches[l], pos[q0:q1], sl[q0:q1], d.page_table, self.scratch, scale=c.scale,
+                        window=c.window, keys_per_split=d.kps, max_splits=d.max_splits, status_ptr=st)
+            P.mla_merge(self.scratch, pos[q0:q1], o_lat[q0:q1], window=c.window, keys_per_split=d.kps, max_splits=d.max_splits)
+        kvb = w[p + "kv_b"]
+        for hh in range(hl):
+            G.gemm(o_lat[:, hh, :], kvb[hh, c.nope:, :], out=attn[:, hh * c.vdim:(hh + 1) * c.vdim], status_ptr=st)
 
     def _sym_rows(self, m: int):
         """The symmetric activation buffer restricted to ``m`` rows (same peer pointers, smaller shape)."""

@@ -128,3 +128,34 @@ def allreduce_rows(parts, fabric, out: torch.Tensor, *, residual: Optional[torch
         return
     check(lib.ifab_allreduce_rows(parts.peer_ptrs, _p(residual), 0 if residual is None else residual.stride(0),
                                   out.data_ptr(), out.stride(0), rows, D, C.byref(fabric.desc), _s()), "allreduce_rows")
+
+
+def fa_prefill(q: torch.Tensor, k: torch.Tensor, vt: torch.Tensor, out: torch.Tensor, *, heads: int, q_head_stride: int, k_head_stride: int,
+               vt_head_stride: int, vt_row0: int = 0, d1: int = 128, d2: int = 0, k2: Optional[torch.Tensor] = None, kv_group: int = 1,
+               ctx: int, pos0: int, scale: float, window: int = 0, status_ptr=None) -> torch.Tensor:
+    """Prompt attention on the tensor cores for ``m = q.shape[0]`` consecutive positions ``pos0 ..`` of one sequence against keys
+    ``0 .. ctx - 1`` (causal, optional sliding window). ``q``: ``[m, ...]``; ``k``: ``[>= ctx, ...]`` per-head key columns;
+    ``k2``: ``[>= ctx, d2]`` key columns shared by all heads; ``vt``: transposed values ``[rows, >= ctx]``; ``out``: ``[m, heads * 128]``."""
+    m = q.shape[0]
+    assert q.dtype == BF16 and k.dtype == BF16 and vt.dtype == BF16 and out.dtype == BF16 and q.stride(1) == 1 and k.stride(1) == 1
+    assert vt.stride(1) == 1 and out.stride(1) == 1 and k.shape[0] >= ctx and vt.shape[1] >= ctx and (k2 is None or k2.shape[0] >= ctx)
+    check(_lib.load().ifab_fa_prefill_bf16(q.data_ptr(), q.stride(0), q_head_stride, k.data_ptr(), k.stride(0), k_head_stride, _p(k2),
+                                           0 if k2 is None else k2.stride(0), vt.data_ptr(), vt.stride(0), vt_head_stride, vt_row0,
+                                           vt.shape[0], out.data_ptr(), out.stride(0), m, ctx, heads, kv_group, d1, d2, pos0, window, scale,
+                                           status_ptr, _s()), "fa_prefill")
+    return out
+
+
+def mla_q_rope_inplace(q: torch.Tensor, positions: torch.Tensor, *, heads: int, nope: int, rope: int, theta: float) -> None:
+    """Rotate the last ``rope`` columns of every head of ``q`` (``[T, heads * (nope + rope)]``) in place."""
+    check(_lib.load().ifab_mla_q_rope_inplace(q.data_ptr(), q.stride(0), positions.data_ptr(), q.shape[0], heads, nope, rope, theta, _s()),
+          "mla_q_rope_inplace")
+
+
+def mla_ctx_gather(cache: torch.Tensor, page_table: torch.Tensor, slot: int, ctx: int, lat: torch.Tensor, pe: torch.Tensor, status_ptr=None) -> None:
+    """Keys ``0 .. ctx - 1`` of sequence slot ``slot`` out of the paged latent cache into dense ``lat [rows, 512]`` and ``pe [rows, 64]``
+    (``rows >= ctx``; the tail rows are zeroed)."""
+    rows = lat.shape[0]
+    assert pe.shape[0] == rows and lat.is_contiguous() and pe.is_contiguous() and lat.shape[1] == 512 and pe.shape[1] == 64
+    check(_lib.load().ifab_mla_ctx_gather(cache.data_ptr(), page_table.data_ptr(), slot, page_table.shape[1], cache.shape[1], cache.shape[0],
+                                          ctx, rows, lat.data_ptr(), pe.data_ptr(), status_ptr, _s()), "mla_ctx_gather")

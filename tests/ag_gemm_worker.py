@@ -40,44 +40,6 @@ def main():
             torch.testing.assert_close(c.float(), ref, rtol=2e-2, atol=2e-2)
     assert fab.status() == 0
     print(f"rank {rank}: ok allgather gemm", flush=True)
-    if os.environ.get("AG_BENCH") == "1" and world > 1:
-        rows_local, N, K = 4096 // world * 2, 4096, 4096
-        bufs = [fab.symmetric_empty((rows_local, K)) for _ in range(2)]
-        state = AllGatherGemmState(fab, rows_local, K)
-        for bb in bufs:
-            bb.tensor.normal_()
-        b = torch.randn(N, K, device="cuda").to(BF16)
-        gathered = torch.empty(rows_local * world, K, dtype=BF16, device="cuda")
-        out = torch.empty(rows_local * world, N, dtype=BF16, device="cuda")
-
-        def timed(fn, calls=8):
-            for i in range(3):
-                fn(i)
-            dist.barrier()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for i in range(calls):
-                fn(i)
-            e1.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) / calls], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t)
-
-        def fused(i):
-            allgather_gemm(bufs[i & 1], b, state, fab, out=out)
-
-        def baseline(i):
-            dist.all_gather_into_tensor(gathered, bufs[i & 1].tensor)
-            torch.matmul(gathered, b.T, out=out)
-
-        tf, tb = timed(fused), timed(baseline)
-        if rank == 0:
-            M = rows_local * world
-            print(json.dumps({"shape": f"{M}x{N}x{K}", "world": world, "fused_ms": round(tf, 4), "nccl_cublas_ms": round(tb, 4),
-                              "mma_ms_at_measured_peak": round(2.0 * M * N * K / 1.6705e15 * 1e3, 4),
-                              "link_ms": round((world - 1) * rows_local * K * 2 / 770e9 * 1e3, 4)}), flush=True)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()

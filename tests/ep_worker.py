@@ -73,107 +73,12 @@ def run(rank: int, world: int) -> None:
     fab.close()
 
 
-def bench(rank: int, world: int) -> None:
-    """Dispatch and combine exchange of one flagship MoE layer (hidden 4096, top-8 of 96 experts, 512 tokens per rank), device
-    time per call, max over ranks, against the same payload through NCCL all_to_all_single with equal splits (routing built
-    so that every destination receives the same number of rows, which spares the library path its size exchange)."""
-    import json
-
-    from ironpangu_b200.parallel.ep import EpExchange
-    from ironpangu_b200.parallel.fabric import Fabric
-
-    fab = Fabric(rank, world)
-    E, topk, D, M = 96, 8, 4096, 512
-    el = E // world
-    ex = EpExchange(fab, M, topk, D, el)
-    g = torch.Generator(device="cuda").manual_seed(3 + rank)
-    h = torch.randn(M, D, generator=g, device="cuda").to(BF16)
-    # token t picks expert (t + k * E / topk) % E for k = 0..7: uniform over experts, hence over ranks
-    ids = ((torch.arange(M, device="cuda")[:, None] + torch.arange(topk, device="cuda")[None, :] * (E // topk)) % E).to(torch.int32).contiguous()
-    wts = torch.rand(M, topk, generator=g, device="cuda")
-    res = torch.randn(M, D, generator=g, device="cuda").to(BF16)
-    out = torch.empty(M, D, dtype=BF16, device="cuda")
-    xp = torch.zeros(ex.rows_max, D, dtype=BF16, device="cuda")
-    y = torch.zeros(ex.rows_max, D, dtype=BF16, device="cuda")
-
-    def fused_dispatch():
-        ex.dispatch(h, ids)
-        ex.plan()
-        ex.gather(xp)
-
-    def fused_combine():
-        ex.send_back(y)
-        ex.combine(ids, wts, out, residual=res)
-
-    rows = M * topk
-    dest = (ids.view(-1).long() // el)
-    order = torch.argsort(dest, stable=True)
-    send = torch.empty(rows, D, dtype=BF16, device="cuda")
-    recv = torch.empty(rows, D, dtype=BF16, device="cuda")
-    back = torch.empty(rows, D, dtype=BF16, device="cuda")
-    perm = torch.randperm(rows, device="cuda")
-    inv = torch.argsort(order)
-
-    def nccl_dispatch():
-        torch.index_select(h, 0, order // topk, out=send)          # rows grouped by destination
-        dist.all_to_all_single(recv, send)
-        torch.index_select(recv, 0, perm, out=xp[:rows])            # owner: expert-sorted matrix
-
-    def nccl_combine():
-        torch.index_select(y[:rows], 0, perm, out=send)
-        dist.all_to_all_single(back, send)
-        r = torch.index_select(back, 0, inv).view(M, topk, D).float()
-        out.copy_(((r * wts[:, :, None]).sum(1).to(BF16).float() + res.float()).to(BF16))
-
-    def timed(pair, iters=10, calls=8):
-        # `calls` layers (dispatch + combine) back to back between one pair of events: a single call timed after a host
-        # synchronisation mostly measures host launch latency
-        for _ in range(3):
-            for fn in pair:
-                fn()
-        torch.cuda.synchronize()
-        ts = []
-        for _ in range(iters):
-            if world > 1:
-                dist.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(calls):
-                for fn in pair:
-                    fn()
-            e1.record()
-            torch.cuda.synchronize()
-            ts.append(e0.elapsed_time(e1) / calls)
-        ts.sort()
-        v = torch.tensor([ts[len(ts) // 2]], device="cuda", dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(v, op=dist.ReduceOp.MAX)
-        return float(v[0])
-
-    f = timed([fused_dispatch, fused_combine])
-    n = timed([nccl_dispatch, nccl_combine]) if world > 1 else float("nan")
-    link_ms = 2 * rows * D * 2 * (world - 1) / world / 770e9 * 1e3
-    if rank == 0:
-        print(json.dumps({"world": world, "tokens_per_rank": M, "topk": topk, "hidden": D,
-                          "bytes_per_rank_both_directions": 2 * rows * D * 2 * (world - 1) // world,
-                          "fused_dispatch_plus_combine_ms": round(f, 4), "nccl_dispatch_plus_combine_ms": round(n, 4),
-                          "link_ms_at_770GBs": round(link_ms, 4), "fraction_of_link": round(link_ms / f, 3) if world > 1 else None}), flush=True)
-    assert fab.status() == 0
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    ex.close()
-    fab.close()
-
-
 def main():
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     run(rank, world)
-    if os.environ.get("EP_BENCH") == "1":
-        bench(rank, world)
     if world > 1:
         dist.destroy_process_group()
 

@@ -1,5 +1,5 @@
 """Worker for the bulk (prefill-sized) fused kernels: tcgen05 GEMM + two-shot all-reduce over peer memory.
-Run under torch.distributed.run; prints timing of the fused kernel vs cuBLAS + NCCL when BULK_BENCH=1."""
+Run under torch.distributed.run. (Timings of the same kernels: ``python -m ironpangu_b200.utils.bench_fused gemm_ar``.)"""
 import json
 import os
 import sys
@@ -63,56 +63,6 @@ def main():
     assert fab.status() == 0
     print(f"rank {rank}: ok gemm_allreduce bulk", flush=True)
 
-    if os.environ.get("BULK_BENCH") == "1":
-        # A single call timed after a host barrier mostly measures how far apart the two processes launch, so
-        # each sample times CALLS back-to-back calls that rotate over SETS operand sets (together larger than L2)
-        M, N, Kl = 4096, 4096, 4096 // world
-        SETS, CALLS = 4, 8
-        a = [torch.randn(M, Kl, device="cuda").to(BF16) for _ in range(SETS)]
-        b = [torch.randn(N, Kl, device="cuda").to(BF16) for _ in range(SETS)]
-        res = [torch.randn(M, N, device="cuda").to(BF16) for _ in range(SETS)]
-        out = [torch.empty(M, N, dtype=BF16, device="cuda") for _ in range(SETS)]
-        sym = [fab.symmetric_empty((M, N)) for _ in range(SETS)]
-
-        def timed(fn, iters=7):
-            for i in range(3):
-                fn(i % SETS)
-            ts = []
-            for _ in range(iters):
-                dist.barrier()
-                torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                for i in range(CALLS):
-                    fn(i % SETS)
-                e1.record()
-                torch.cuda.synchronize()
-                t = torch.tensor([e0.elapsed_time(e1) / CALLS], device="cuda")
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                ts.append(float(t))
-            ts.sort()
-            return ts[len(ts) // 2]
-
-        def baseline(i):
-            torch.matmul(a[i], b[i].T, out=out[i])
-            dist.all_reduce(out[i])
-            out[i].add_(res[i])
-
-        def gemm_only(i):
-            torch.matmul(a[i], b[i].T, out=out[i])
-
-        t_f = timed(lambda i: gemm_allreduce(a[i], b[i], fab, sym[i], residual=res[i]))
-        t_b = timed(baseline)
-        t_g = timed(gemm_only)
-        assert fab.status() == 0
-        link_bytes = 2 * (world - 1) / world * M * N * 2
-        t_link = link_bytes / 770e9 * 1e3
-        t_mma = 2.0 * M * N * Kl / 1.6705e15 * 1e3
-        if rank == 0:
-            print(json.dumps({"shape": f"{M}x{N}x{Kl}*{world}", "calls_per_sample": CALLS, "operand_sets": SETS,
-                              "fused_ms": round(t_f, 4), "cublas_nccl_ms": round(t_b, 4), "cublas_gemm_only_ms": round(t_g, 4),
-                              "roofline_ms": round(max(t_link, t_mma), 4), "link_ms": round(t_link, 4), "mma_ms": round(t_mma, 4),
-                              "fraction_of_roofline": round(max(t_link, t_mma) / t_f, 3)}), flush=True)
     torch.cuda.synchronize()
     dist.barrier()
     fab.close()
