@@ -24,6 +24,7 @@
 #include "hybrid.h"
 #include "interp.h"
 #include "rankplan.h"
+#include "tokenizer.h"
 
 using namespace ifab;
 
@@ -37,6 +38,7 @@ int usage() {
                "  validate-bundle BUNDLE_DIR\n  inspect-checkpoint DIR [OUT.json]\n  bind-checkpoint MODEL DIR [OUT.json]\n  plan-placement MODEL [DIR|-] [OUT.json]\n"
                "  inspect FILE\n  plan GRAPH.json|MODEL.inferfabric [OUT.bin]\n  execute GRAPH.json|MODEL.inferfabric INPUTS.json\n"
                "  compile SPEC.json|MODEL.inferfabric OUT.bin\n  compile-model MODEL.inferfabric|MODEL.json [OUT.json]\n"
+               "  tokenize TOKENIZER TEXT_FILE\n  detokenize TOKENIZER IDS.json\n  render-chat TOKENIZER MESSAGES.json [auto|chatml|plain]\n"
                "  inspect-hybrid-checkpoint MODEL DIR [OUT.json]\n  compile-checkpoint MODEL DIR [OUT.json]\n  lower-checkpoint MODEL DIR CONTEXT [BATCH] [OUT.json]\n  demo\n");
   return 2;
 }
@@ -434,6 +436,46 @@ int main(int argc, char** argv) {
       }
       if (argc > next) write_file_atomic(argv[next], out.dump(1));
       else std::cout << out.dump(1) << "\n";
+      return 0;
+    }
+    if (cmd == "tokenize" || cmd == "detokenize" || cmd == "render-chat") {
+      // TOKENIZER = "bytes" or a tokenizer.json; tokenize TEXT_FILE -> ids (+ the words they came from); detokenize IDS.json -> text;
+      // render-chat MESSAGES.json [STYLE] -> the prompt text and its ids
+      if (argc < 4) return usage();
+      std::shared_ptr<tok::Tokenizer> t = tok::load_tokenizer(argv[2]);
+      Json out = Json::object();
+      out.set("tokenizer", t->name());
+      out.set("vocab_size", t->vocab_size());
+      if (cmd == "tokenize") {
+        const std::string text = read_file(argv[3], 64 << 20);
+        Json ids = Json::array(), words = Json::array();
+        for (auto id : t->encode(text)) ids.push((int64_t)id);
+        if (t->name() == "bpe")
+          for (auto w : tok::BpeTokenizer::split_words(text)) words.push(std::string(w));
+        out.set("ids", ids);
+        out.set("words", words);
+      } else if (cmd == "detokenize") {
+        std::vector<uint32_t> ids;
+        const Json list = Json::parse(read_file(argv[3], 64 << 20));
+        for (auto& x : list.as_array()) ids.push_back((uint32_t)x.as_int());
+        out.set("text", t->decode(ids));
+        out.set("text_without_special", t->decode(ids, true));
+        tok::Detokenizer stream(t, false);
+        Json parts = Json::array();
+        for (auto id : ids) parts.push(stream.feed(id));
+        parts.push(stream.flush());
+        out.set("stream", parts);
+      } else {
+        std::vector<tok::ChatMessage> msgs;
+        const Json list = Json::parse(read_file(argv[3], 16 << 20));
+        for (auto& m : list.as_array()) msgs.push_back({m.at("role").as_string(), m.at("content").as_string()});
+        const std::string text = tok::render_chat(msgs, *t, argc > 4 ? argv[4] : "auto");
+        out.set("text", text);
+        Json ids = Json::array();
+        for (auto id : t->encode(text)) ids.push((int64_t)id);
+        out.set("ids", ids);
+      }
+      std::cout << out.dump() << "\n";
       return 0;
     }
     if (cmd == "compile-model") {

@@ -19,37 +19,6 @@ int utf8_len(unsigned char b) {
 }
 
 // moves every complete, valid sequence from `in` to the result; replaces invalid bytes; leaves an incomplete tail in `in`
-std::string drain_utf8(std::string& in, bool final) {
-  std::string out;
-  size_t i = 0;
-  while (i < in.size()) {
-    const unsigned char b = (unsigned char)in[i];
-    const int n = utf8_len(b);
-    if (n == 0) {
-      out += "\xEF\xBF\xBD";
-      ++i;
-      continue;
-    }
-    if (i + n > in.size()) {
-      if (!final) break;
-      out += "\xEF\xBF\xBD";
-      i = in.size();
-      break;
-    }
-    bool ok = true;
-    for (int k = 1; k < n; ++k)
-      if (((unsigned char)in[i + k] & 0xC0) != 0x80) ok = false;
-    if (ok) {
-      out.append(in, i, n);
-      i += n;
-    } else {
-      out += "\xEF\xBF\xBD";
-      ++i;
-    }
-  }
-  in.erase(0, i);
-  return out;
-}
 
 Json error_body(const std::string& message, const char* type, int code) {
   Json e = Json::object();
@@ -81,35 +50,13 @@ const char* finish_reason(sched::Finish f) {
 
 }  // namespace
 
-std::vector<uint32_t> ByteTokenizer::encode(std::string_view text) const {
-  std::vector<uint32_t> ids;
-  ids.reserve(text.size());
-  for (unsigned char c : text) ids.push_back(kFirstByte + c);
-  return ids;
-}
-
-std::string ByteTokenizer::decode(const std::vector<uint32_t>& ids) const {
-  TextStream ts;
-  std::string out;
-  for (uint32_t id : ids) out += ts.feed(id);
-  return out + ts.flush();
-}
-
-std::string TextStream::feed(uint32_t id) {
-  if (id < ByteTokenizer::kFirstByte) return "";
-  if (id >= ByteTokenizer::kVocab) return drain_utf8(pending_, true) + "<|" + std::to_string(id) + "|>";
-  pending_.push_back((char)(id - ByteTokenizer::kFirstByte));
-  return drain_utf8(pending_, false);
-}
-std::string TextStream::flush() { return drain_utf8(pending_, true); }
-
 std::vector<uint32_t> Api::prompt_of(const Json& body, bool chat) const {
   if (chat) {
     const Json& msgs = body.at("messages");
     if (!msgs.is_array() || msgs.size() == 0) invalid("'messages' must be a non-empty array");
-    std::string text;
+    std::vector<tok::ChatMessage> rendered;
     if (const Json* tools = body.find("tools"); tools && !tools->is_null() && tools->size() > 0)
-      text += "<|system|>\n" + chat::render_tools(*tools) + "\n";
+      rendered.push_back({"system", chat::render_tools(*tools)});
     for (const auto& m : msgs.as_array()) {
       const Json& content = m.at("content");
       std::string c;
@@ -123,15 +70,16 @@ std::vector<uint32_t> Api::prompt_of(const Json& body, bool chat) const {
       } else {
         invalid("message content must be a string or an array of text parts");
       }
-      text += "<|" + m.at("role").as_string() + "|>\n" + c + "\n";
+      rendered.push_back({m.at("role").as_string(), std::move(c)});
     }
-    text += "<|assistant|>\n";
-    std::vector<uint32_t> ids{ByteTokenizer::kBos};
-    for (uint32_t t : tok_.encode(text)) ids.push_back(t);
+    const std::string text = tok::render_chat(rendered, *tok_, chat_style_);
+    std::vector<uint32_t> ids;
+    if (tok_->bos() >= 0) ids.push_back((uint32_t)tok_->bos());
+    for (uint32_t t : tok_->encode(text)) ids.push_back(t);
     return ids;
   }
   const Json& p = body.at("prompt");
-  if (p.is_string()) return tok_.encode(p.as_string());
+  if (p.is_string()) return tok_->encode(p.as_string());
   if (p.is_array() && p.size() > 0) {
     const Json& first = p.as_array()[0];
     if (first.is_int()) {
@@ -206,7 +154,7 @@ void Api::completions(const http::Request& req, http::ResponseWriter& w, bool ch
     j.set("choices", arr);
     return j;
   };
-  TextStream ts;
+  tok::Detokenizer ts(tok_);
   size_t completion_tokens = 0;
   if (stream) {
     if (!w.begin_stream("text/event-stream")) {
@@ -425,7 +373,7 @@ void Api::handle(const http::Request& req, http::ResponseWriter& w) {
       } else {
         std::vector<uint32_t> ids;
         for (const auto& t : body.at("tokens").as_array()) ids.push_back((uint32_t)t.as_int());
-        j.set("prompt", tok_.decode(ids));
+        j.set("prompt", tok_->decode(ids));
       }
       return w.send(200, "application/json", j.dump());
     } catch (const Error& e) {

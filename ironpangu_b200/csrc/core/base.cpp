@@ -267,9 +267,28 @@ struct JsonParser {
               else if (h >= 'A' && h <= 'F') cp |= (unsigned)(h - 'A' + 10);
               else err("bad hex digit");
             }
+            if (cp >= 0xD800 && cp <= 0xDBFF && i + 6 <= s.size() && s[i] == '\\' && s[i + 1] == 'u') {
+              // a surrogate pair: two \u escapes name one code point beyond U+FFFF
+              unsigned lo = 0;
+              bool hex = true;
+              for (int k = 0; k < 4; ++k) {
+                const char h = s[i + 2 + k];
+                lo <<= 4;
+                if (h >= '0' && h <= '9') lo |= (unsigned)(h - '0');
+                else if (h >= 'a' && h <= 'f') lo |= (unsigned)(h - 'a' + 10);
+                else if (h >= 'A' && h <= 'F') lo |= (unsigned)(h - 'A' + 10);
+                else hex = false;
+              }
+              if (hex && lo >= 0xDC00 && lo <= 0xDFFF) {
+                cp = 0x10000 + ((cp - 0xD800) << 10) + (lo - 0xDC00);
+                i += 6;
+              }
+            }
+            if (cp >= 0xD800 && cp <= 0xDFFF) cp = 0xFFFD;   // a lone surrogate is not a character
             if (cp < 0x80) out += (char)cp;
             else if (cp < 0x800) { out += (char)(0xc0 | (cp >> 6)); out += (char)(0x80 | (cp & 0x3f)); }
-            else { out += (char)(0xe0 | (cp >> 12)); out += (char)(0x80 | ((cp >> 6) & 0x3f)); out += (char)(0x80 | (cp & 0x3f)); }
+            else if (cp < 0x10000) { out += (char)(0xe0 | (cp >> 12)); out += (char)(0x80 | ((cp >> 6) & 0x3f)); out += (char)(0x80 | (cp & 0x3f)); }
+            else { out += (char)(0xf0 | (cp >> 18)); out += (char)(0x80 | ((cp >> 12) & 0x3f)); out += (char)(0x80 | ((cp >> 6) & 0x3f)); out += (char)(0x80 | (cp & 0x3f)); }
             break;
           }
           default: err("bad escape");

@@ -28,7 +28,7 @@ using namespace ifab;
 namespace {
 
 struct Args {
-  std::string mode, socket, spawn, bundle, checkpoint;
+  std::string mode, socket, spawn, bundle, checkpoint, tokenizer = "bytes", chat_template = "auto";
   int port = 8000, gpus = 1;
   bool cpu = false, seqs_given = false, len_given = false;
   serve::EngineInfo info;
@@ -65,6 +65,8 @@ Args parse(int argc, char** argv) {
     else if (f == "--program") { a.mode = "program"; a.bundle = need(i); a.checkpoint = need(i); }
     else if (f == "--gpus") a.gpus = std::atoi(need(i));
     else if (f == "--cpu") a.cpu = true;
+    else if (f == "--tokenizer") a.tokenizer = need(i);            // "bytes" or the path of a tokenizer.json (byte-level BPE)
+    else if (f == "--chat-template") a.chat_template = need(i);    // auto | chatml | plain
     else if (f == "--port") a.port = std::atoi(need(i));
     else if (f == "--max-num-seqs") { a.info.residents = (uint32_t)std::atoi(need(i)); a.seqs_given = true; }
     else if (f == "--max-num-batched-tokens") a.info.token_budget = a.info.chunk = (uint32_t)std::atoi(need(i));
@@ -110,6 +112,18 @@ int main(int argc, char** argv) {
 
   pid_t child = -1;
   std::shared_ptr<serve::ResidentEngine> engine;
+  std::shared_ptr<tok::Tokenizer> tokenizer;
+  try {
+    tokenizer = tok::load_tokenizer(a.tokenizer);
+    if (a.mode == "mock" && a.tokenizer != "bytes") {
+      // the stand-in engine speaks the tokenizer's vocabulary: its end-of-sequence id and width come from the file
+      if (tokenizer->eos() >= 0) a.info.eos = (uint32_t)tokenizer->eos();
+      a.info.vocab = std::max<uint32_t>(a.info.vocab, tokenizer->vocab_size());
+    }
+  } catch (const std::exception& e) {
+    std::fprintf(stderr, "ifab-server: cannot load the tokenizer: %s\n", e.what());
+    return 1;
+  }
   try {
     if (a.mode == "mock") {
       engine = std::make_shared<serve::MockEngine>(a.info, a.step_micros);
@@ -137,7 +151,7 @@ int main(int argc, char** argv) {
   }
   serve::Service service(engine, a.opt);
   if (service.info().greedy_only) a.defaults.temperature = 0.0;
-  api::Api api(service, a.defaults);
+  api::Api api(service, a.defaults, tokenizer, a.chat_template);
   std::unique_ptr<http::Server> server;
   try {
     server = std::make_unique<http::Server>((uint16_t)a.port, [&](const http::Request& r, http::ResponseWriter& w) { api.handle(r, w); });
