@@ -37,7 +37,6 @@ def parse():
     ap.add_argument("--context", type=int, default=512)
     ap.add_argument("--prefill", default="gemm", choices=["gemm", "decode"],
                     help="gemm: tensor-core prefill path (native impl only); decode: prompt through the decode kernels, 8 rows a time")
-    ap.add_argument("--persistent", type=int, default=0, help="1: one persistent cooperative launch per decode step")
     ap.add_argument("--expert-fp8", action="store_true", help="block-scaled fp8 expert weights (the serving configuration; NOT the bf16 headline)")
     ap.add_argument("--kv-int8", action="store_true", help="packed int8 latent KV cache (the serving configuration; NOT the bf16 headline)")
     ap.add_argument("--layers", type=int, default=0, help="override layer count (marks the run as a reduced config)")
@@ -212,7 +211,7 @@ def main():
         dec = G.DenseDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1)
     elif args.impl == "native":
         dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1,
-                            persistent=bool(args.persistent), expert_fp8=args.expert_fp8, kv_int8=args.kv_int8,
+                            expert_fp8=args.expert_fp8, kv_int8=args.kv_int8,
                             fused_moe=None if args.fused_moe < 0 else bool(args.fused_moe))
         if args.expert_fp8 or args.kv_int8:
             args.prefill = "decode"        # the quantised layouts prefill through the decode kernels
@@ -342,7 +341,7 @@ def main():
                                                  "(not the headline model)") if dense and not args.layers
                        else f"{args.model} layers={cfg.layers} (reduced config)",
                        "params_b": round(cfg.param_count() / 1e9, 2), "global_batch": 1, "seq_len": args.context,
-                       "decode_tokens": K, "parallelism": f"tp{world}" if dense else f"tp{world}ep{world}", "decode_step": "single persistent launch" if args.persistent else "operator chain",
+                       "decode_tokens": K, "parallelism": f"tp{world}" if dense else f"tp{world}ep{world}", "decode_step": "operator chain",
                        "prefill": args.prefill if args.impl == "native" else "library",
                        "l2": "per-step weight stream (>= 2.5 GB per rank) exceeds the 126 MB L2; no explicit flush",
                        "baseline_ref": "17.7293 ms TPOT on 8x Ascend (docs/validation/2026-10-17-packed-c8/README.md:20-23)",

@@ -208,44 +208,6 @@ int ifab_kv_dequantize_q8(const void* cache, void* out /* bf16 [rows, 576] */, l
 int ifab_quantize_int8(const void* x, long ldx, void* q, long ldq, float* scales, long lds, int T, int K, int group_cols,
                        void* stream);
 
-/* ---- whole decode step of the MLA + MoE decoder as one persistent cooperative kernel ----
- * All pointers are device pointers. `layers` points to an array of `n_layers` IfabMlaMoeLayer in device memory
- * (written once when the model is loaded). The launch computes exactly what the operator-by-operator chain
- * (embedding, ifab_gemv_bf16, ifab_mla_*, ifab_gemv_allreduce_bf16, ifab_router_topk, ifab_moe_*,
- * ifab_lm_head_argmax) computes for `T` rows, and advances the fabric's call counter by the same amount, so the
- * two forms can be mixed from step to step. `bar` = 4 zero-initialised uint32 words owned by this entry point.
- * With `feedback` != 0 the sampled token and position + 1 are written back into tokens / positions. */
-typedef struct IfabMlaMoeLayer {
-  const void *attn_norm, *qkv_a, *kv_a_norm, *q_a_norm, *q_b, *kv_b, *o_proj, *ffn_norm;
-  const float *router, *router_bias;
-  const void *gate_up, *down, *shared_gate_up, *shared_down;
-  void* cache;        /* [pages, page_tokens, 576] bf16 */
-  const void* sinks;  /* [n_sinks, 576] or NULL */
-} IfabMlaMoeLayer;
-
-typedef struct IfabMlaMoeStep {
-  const IfabMlaMoeLayer* layers;
-  int32_t n_layers, hidden, heads_local, q_lora, nope, rope, vdim, experts, experts_local, expert0, topk, expert_ffn,
-      shared_ffn_local, vocab_local, vocab_offset, vocab;
-  int32_t scoring, renorm, window, n_sinks, page_tokens, max_pages, num_pages, keys_per_split, max_splits;
-  float route_scale, eps, theta, attn_scale;
-  const void *embed, *final_norm, *lm_head;
-  int32_t *tokens, *positions;
-  const int32_t *slots, *page_table;
-  void *x, *qkv, *q, *q_lat, *attn, *act;   /* [T, hidden], [T, q_lora+576], [T, hl*192], [T, hl, 576], [T, hl*vdim], [T, topk+1, F] */
-  float *scratch, *router_logits;           /* [T, hl, max_splits, 514], [T, experts] */
-  int32_t* route_ids;                       /* [T, topk] */
-  float* route_w;
-  void* partial;                            /* >= 8 * T * (2 * SM count) bytes */
-  int32_t* next_ids;
-  float *next_vals, *logits;                /* logits may be NULL; [T, vocab_local] f32 */
-  uint32_t* bar;
-  uint64_t* trace;    /* optional (NULL = off): 3 + 9 * n_layers global-timer stamps in ns, one per barrier, written by CTA 0 */
-  int32_t feedback;
-} IfabMlaMoeStep;
-
-int ifab_mla_moe_decode_step(const IfabMlaMoeStep* step, int T, const IfabFabric* fab, void* stream);
-
 /* ---- GQA decode path (dense models) ---- */
 int ifab_gqa_rope_kv_write(void* qkv, long ld, const int32_t* positions, const int32_t* slots,
                            const int32_t* page_table, int max_pages, int page_tokens, void* k_cache, void* v_cache,

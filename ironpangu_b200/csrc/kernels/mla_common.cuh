@@ -1,4 +1,4 @@
-// Helpers shared by the MLA decode kernels and the persistent decode-step kernel: row geometry of the latent
+// Helpers shared by the MLA decode and prompt kernels: row geometry of the latent
 // cache (512 latent + 64 rope columns per token), RoPE angles, page-table lookup, visible key range.
 #pragma once
 #include "common.cuh"

@@ -184,7 +184,7 @@ class MlaMoeDecoder:
 
     def __init__(self, cfg: MlaMoeConfig, weights: Dict[str, torch.Tensor], fabric: Fabric, *, max_tokens: int = 1,
                  max_context: int = 1024, num_slots: int = 1, keys_per_split: int = 64, keep_logits: bool = False,
-                 persistent: bool = False, kv_int8: bool = False, expert_fp8: bool = False, drop_bf16_experts: bool = True,
+                 kv_int8: bool = False, expert_fp8: bool = False, drop_bf16_experts: bool = True,
                  fused_head: Optional[bool] = None, shard: Optional[tuple] = None, fused_moe: Optional[bool] = None):
         """``kv_int8``: keep the latent cache as packed int8 rows (656 bytes per token instead of 1152).
         ``expert_fp8``: quantise the routed and shared expert matrices to block-scaled fp8 (1 x 128 scale blocks) at
@@ -198,7 +198,6 @@ class MlaMoeDecoder:
         ``shard``: ``(rank, world)`` of the weight shard when it differs from the fabric's (a profiling aid: one GPU runs the
         kernels of rank r of an N-rank job at their real shapes, without the peers; the sums it computes are partial)."""
         assert 1 <= max_tokens <= 8
-        assert not (persistent and (kv_int8 or expert_fp8)), "the single-launch step reads bf16 cache rows and bf16 experts"
         self.kv_int8 = kv_int8
         self.expert_fp8 = expert_fp8
         can_fuse = (not kv_int8 and cfg.kv_lora == 512 and cfg.rope == 64 and cfg.nope % 32 == 0 and cfg.nope <= 128 and
@@ -260,7 +259,7 @@ class MlaMoeDecoder:
         self.act = torch.zeros(T, c.topk + 1, c.expert_ffn, dtype=BF16, device=dev)
         self.partial = e(((self.vl + 7) // 8) * 8 * 2, dt=torch.float32)
         can_fuse_moe = (not expert_fp8 and c.expert_ffn <= 1536 and c.expert_ffn % 8 == 0 and (c.shared_ffn // self.world) % 8 == 0
-                        and c.experts <= 256 and c.topk <= 16 and not persistent)
+                        and c.experts <= 256 and c.topk <= 16)
         # measured: the one-launch block loses 2-3 % per layer to the three-kernel chain when a rank holds many routes (1 or 2
         # GPUs) and wins once the per-rank expert work is small against the fixed cost of a kernel boundary
         self.fused_moe = (can_fuse_moe and self.world >= 4) if fused_moe is None else bool(fused_moe)
@@ -272,89 +271,10 @@ class MlaMoeDecoder:
         # embedding + lm_head + per layer: qkv_a, [cache write, q_b, absorb, split, merge+v_up | fused head], o_proj, router, gate_up, down
         self.launches_per_forward = 2 + ((6 if self.fused_head else 10) - (2 if self.fused_moe else 0)) * c.layers
         self._graph: Optional[torch.cuda.CUDAGraph] = None
-        self.persistent = persistent
-        if persistent:
-            self._build_step_descriptor()
-            self.launches_per_forward = 1
-
-    def _build_step_descriptor(self) -> None:
-        """Descriptor of the single-launch decode step (``ops.decode.mla_moe_decode_step``): a device table with the
-        16 pointers of every layer plus the activation buffers; written once, reused by every step."""
-        from ..ops import _lib
-
-        c, w, dev = self.cfg, self.w, self.fabric.device
-        names = {"attn_norm": "attn_norm", "qkv_a": "qkv_a", "kv_a_norm": "kv_a_norm", "q_a_norm": "q_a_norm", "q_b": "q_b",
-                 "kv_b": "kv_b", "o_proj": "o_proj", "ffn_norm": "ffn_norm", "router": "router", "gate_up": "gate_up",
-                 "down": "down", "shared_gate_up": "shared_gate_up", "shared_down": "shared_down"}
-        rows = []
-        for l in range(c.layers):
-            row = []
-            for f in _lib.IfabMlaMoeLayer.FIELDS:
-                if f == "cache":
-                    row.append(self.caches[l].data_ptr())
-                elif f in names:
-                    t = w.get(f"layers.{l}.{names[f]}")
-                    row.append(0 if t is None else t.data_ptr())
-                else:
-                    row.append(0)          # router_bias, sinks: not used by this configuration
-            rows.append(row)
-        self._layer_table = torch.tensor(rows, dtype=torch.int64).to(dev)
-        sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        self._step_partial = torch.empty(2 * sms * 8 * 2, dtype=torch.float32, device=dev)
-        self._step_bar = torch.zeros(4, dtype=torch.int32, device=dev)
-        s = _lib.IfabMlaMoeStep()
-        s.layers = self._layer_table.data_ptr()
-        s.n_layers, s.hidden, s.heads_local, s.q_lora, s.nope, s.rope, s.vdim = c.layers, c.hidden, self.hl, c.q_lora, c.nope, c.rope, c.vdim
-        s.experts, s.experts_local, s.expert0, s.topk, s.expert_ffn = c.experts, self.el, self.rank * self.el, c.topk, c.expert_ffn
-        s.shared_ffn_local = c.shared_ffn // self.world
-        s.vocab_local, s.vocab_offset, s.vocab = self.vl, self.rank * self.vl, c.vocab
-        s.scoring = {"softmax": 0, "sigmoid_bias_group_topk": 1}[c.scoring]
-        s.renorm, s.window, s.n_sinks, s.page_tokens = 1, c.window, 0, c.page_tokens
-        s.max_pages, s.num_pages, s.keys_per_split, s.max_splits = self.max_pages, self.num_pages, self.kps, self.max_splits
-        s.route_scale, s.eps, s.theta, s.attn_scale = c.route_scale, c.eps, c.theta, c.scale
-        s.embed, s.final_norm, s.lm_head = w["embed"].data_ptr(), w["final_norm"].data_ptr(), w["lm_head"].data_ptr()
-        s.tokens, s.positions, s.slots, s.page_table = (self.tokens.data_ptr(), self.positions.data_ptr(), self.slots.data_ptr(),
-                                                        self.page_table.data_ptr())
-        s.x, s.qkv, s.q, s.q_lat, s.attn, s.act = (self.x.data_ptr(), self.qkv.data_ptr(), self.q.data_ptr(), self.q_lat.data_ptr(),
-                                                   self.attn.data_ptr(), self.act.data_ptr())
-        s.scratch, s.router_logits, s.route_ids, s.route_w = (self.scratch.data_ptr(), self.logits_r.data_ptr(),
-                                                              self.route_ids.data_ptr(), self.route_w.data_ptr())
-        s.partial, s.next_ids, s.next_vals = self._step_partial.data_ptr(), self.next_ids.data_ptr(), self.next_vals.data_ptr()
-        s.logits = 0 if self.logits is None else self.logits.data_ptr()
-        s.bar = self._step_bar.data_ptr()
-        s.trace = 0
-        self._step = s
-
-    PHASES = ("qkv_a", "q_b+kv_write", "absorb", "attn_split", "merge+v_up", "o_proj+ar", "router", "gate_up", "down+ar")
-
-    def trace_step(self, T: int = 1) -> Dict[str, float]:
-        """Run one single-launch step with the in-kernel timer on; returns microseconds per phase (summed over the
-        layers, barrier included), plus ``embedding``, ``head`` and ``total``. Profiling aid: costs one sync."""
-        assert self.persistent
-        n = 3 + 9 * self.cfg.layers
-        buf = torch.zeros(n, dtype=torch.int64, device=self.fabric.device)
-        self._step.trace = buf.data_ptr()
-        try:
-            K.mla_moe_decode_step(self._step, T, self.fabric)
-            torch.cuda.synchronize()
-        finally:
-            self._step.trace = 0
-        t = buf.cpu().double()
-        d = (t[1:] - t[:-1]) / 1e3
-        out = {"embedding": float(d[0])}
-        per = d[1:1 + 9 * self.cfg.layers].view(self.cfg.layers, 9).sum(0)
-        for i, name in enumerate(self.PHASES):
-            out[name] = float(per[i])
-        out["head"] = float(d[1 + 9 * self.cfg.layers])
-        out["total"] = float((t[-1] - t[0]) / 1e3)
-        return out
 
     def forward_feedback(self, T: Optional[int] = None) -> torch.Tensor:
         """One step whose sampled token and position + 1 become the inputs of the next step (device-side feedback)."""
         T = self.T if T is None else T
-        if self.persistent:
-            K.mla_moe_decode_step(self._step, T, self.fabric, feedback=True)
-            return self.next_ids[:T]
         self.forward(T)
         self.tokens[:T].copy_(self.next_ids[:T])
         self.positions[:T].add_(1)
@@ -392,9 +312,6 @@ class MlaMoeDecoder:
     def forward(self, T: Optional[int] = None) -> torch.Tensor:
         c, w, fab = self.cfg, self.w, self.fabric
         T = self.T if T is None else T
-        if self.persistent:
-            K.mla_moe_decode_step(self._step, T, fab)
-            return self.next_ids[:T]
         tok, pos, slot = self.tokens[:T], self.positions[:T], self.slots[:T]
         x = self.x[:T]
         st = fab.desc.status

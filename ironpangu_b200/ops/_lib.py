@@ -12,27 +12,6 @@ from pathlib import Path
 from .. import _build
 
 
-class IfabMlaMoeLayer(C.Structure):
-    """Mirror of ``struct IfabMlaMoeLayer``: 16 device pointers of one decoder layer."""
-
-    FIELDS = ("attn_norm", "qkv_a", "kv_a_norm", "q_a_norm", "q_b", "kv_b", "o_proj", "ffn_norm", "router", "router_bias",
-              "gate_up", "down", "shared_gate_up", "shared_down", "cache", "sinks")
-    _fields_ = [(n, C.c_void_p) for n in FIELDS]
-
-
-class IfabMlaMoeStep(C.Structure):
-    """Mirror of ``struct IfabMlaMoeStep`` (arguments of the persistent decode-step kernel)."""
-
-    _INTS = ("n_layers", "hidden", "heads_local", "q_lora", "nope", "rope", "vdim", "experts", "experts_local", "expert0",
-             "topk", "expert_ffn", "shared_ffn_local", "vocab_local", "vocab_offset", "vocab", "scoring", "renorm", "window",
-             "n_sinks", "page_tokens", "max_pages", "num_pages", "keys_per_split", "max_splits")
-    _FLOATS = ("route_scale", "eps", "theta", "attn_scale")
-    _PTRS = ("embed", "final_norm", "lm_head", "tokens", "positions", "slots", "page_table", "x", "qkv", "q", "q_lat", "attn",
-             "act", "scratch", "router_logits", "route_ids", "route_w", "partial", "next_ids", "next_vals", "logits", "bar", "trace")
-    _fields_ = ([("layers", C.c_void_p)] + [(n, C.c_int32) for n in _INTS] + [(n, C.c_float) for n in _FLOATS]
-                + [(n, C.c_void_p) for n in _PTRS] + [("feedback", C.c_int32)])
-
-
 _lock = threading.Lock()
 _lib = None
 
@@ -101,7 +80,6 @@ _SIGS = {
                                   c_int, c_int, c_int, _P, c_u64, _P, c_int, c_int, _P, c_long, _P, _P],
     "ifab_gqa_rope_kv_write": [_P, c_long, _P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_float, _P, _P],
-    "ifab_mla_moe_decode_step": [_P, c_int, _P, _P],
     "ifab_mome": [_P, c_long, _P, _P, _P, _P, _P, c_long, c_int, c_int, c_int, c_int, _P],
     "ifab_mhc_pre": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P],
     "ifab_mhc_post": [_P, _P, c_long, _P, _P, _P, c_int, c_int, c_int, _P],

@@ -357,12 +357,6 @@ def mla_decode_attention(q_lat: torch.Tensor, cache: torch.Tensor, positions: to
     return out
 
 
-def mla_moe_decode_step(step: "_lib.IfabMlaMoeStep", T: int, fabric, feedback: bool = False) -> None:
-    """One whole decode step of the MLA + MoE decoder as a single persistent cooperative launch."""
-    step.feedback = int(feedback)
-    check(_lib.load().ifab_mla_moe_decode_step(C.byref(step), T, C.byref(fabric.desc), _stream()), "mla_moe_decode_step")
-
-
 def gqa_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
                       k_cache: torch.Tensor, v_cache: torch.Tensor, *, heads: int, kv_heads: int, head_dim: int,
                       rotary_dim: Optional[int] = None, theta: float = 1e6, status_ptr: Optional[int] = None) -> None:

@@ -37,7 +37,7 @@ class DecodeEngine:
     # -- graphs ------------------------------------------------------------------------------------
     def _variant(self, last_pos: int):
         d = self.dec
-        if getattr(d, "can_fuse_head", False) and getattr(d, "fused_auto", False) and not getattr(d, "persistent", False):
+        if getattr(d, "can_fuse_head", False) and getattr(d, "fused_auto", False):
             return last_pos < d.fused_ctx_limit
         return None
 

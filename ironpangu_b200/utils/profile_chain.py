@@ -37,7 +37,6 @@ def main() -> None:
     ap.add_argument("--shard-world", type=int, default=0)
     ap.add_argument("--shard-rank", type=int, default=0)
     ap.add_argument("--replays", type=int, default=30)
-    ap.add_argument("--persistent", type=int, default=0)
     ap.add_argument("--skip-knockouts", action="store_true")
     ap.add_argument("--fused-moe", type=int, default=1, help="0: router, gate/up and down as three launches")
     args = ap.parse_args()
@@ -61,8 +60,7 @@ def main() -> None:
     shard = (args.shard_rank, args.shard_world) if args.shard_world else None
     srank, sworld = shard if shard else (rank, world)
     w = random_rank_weights(cfg, srank, sworld, dev)
-    dec = MlaMoeDecoder(cfg, w, fab, max_tokens=1, max_context=args.context + 64, shard=shard, persistent=bool(args.persistent),
-                        fused_moe=bool(args.fused_moe) and not args.persistent)
+    dec = MlaMoeDecoder(cfg, w, fab, max_tokens=1, max_context=args.context + 64, shard=shard, fused_moe=bool(args.fused_moe))
     dec.tokens.fill_(17)
     dec.slots.zero_()
     dec.positions.fill_(args.context)
@@ -86,7 +84,7 @@ def main() -> None:
     out = {"world": world, "shard": list(shard) if shard else None, "layers": args.layers, "context": args.context}
 
     # ---- eager, events around every launch -----------------------------------------------------------------------------
-    if not args.persistent:
+    if True:   # eager pass
         names = [n for n in dir(K) if not n.startswith("_") and callable(getattr(K, n)) and
                  getattr(getattr(K, n), "__module__", "") == K.__name__]
         orig = {n: getattr(K, n) for n in names}
@@ -157,7 +155,7 @@ def main() -> None:
     torch.cuda.synchronize()
     hi, lo, _ = gather_max(e0.elapsed_time(e1) * 1e3 / args.replays)
     out["graph_back_to_back_us"] = {"max": round(hi, 1), "per_layer": round(hi / args.layers, 2)}
-    if not args.persistent and not args.skip_knockouts and world == 1:
+    if not args.skip_knockouts and world == 1:
         # leaving a kernel out is only done in one process: with peers, every rank would have to leave out the same
         # exchange, and the single-process shard run already isolates the compute side
         full = out["graph_step_us"]["max"]

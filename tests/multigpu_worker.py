@@ -94,25 +94,6 @@ def main():
     dist.all_gather_object(all_ids, graph_ids)
     assert all(a == all_ids[0] for a in all_ids), "ranks disagree on the sampled tokens"
     assert fab.status() == 0
-    # the same model as ONE persistent launch per step (both all-reduces and the argmax exchange inside it)
-    one = MlaMoeDecoder(cfg, shard_weights(cfg, full, rank, world, "cuda"), fab, max_tokens=4, max_context=64,
-                        keep_logits=True, persistent=True)
-    one_ids = []
-    for i, t in enumerate(prompt):
-        one.tokens[:1].fill_(t)
-        one.positions[:1].fill_(i)
-        one.forward(1)
-        torch.testing.assert_close(one.logits[0], ref[i, rank * vl:(rank + 1) * vl], rtol=2e-2, atol=2e-2)
-        one_ids.append(int(one.next_ids[0]))
-    assert one_ids == eager_ids, (one_ids, eager_ids)
-    one.reset()
-    n = 4
-    one.tokens[:n].copy_(torch.tensor(prompt[:n], dtype=torch.int32))
-    one.positions[:n].copy_(torch.arange(n, dtype=torch.int32))
-    one.forward(n)
-    torch.testing.assert_close(one.logits[:n], ref[:n, rank * vl:(rank + 1) * vl], rtol=2e-2, atol=2e-2)
-    assert fab.status() == 0
-    print(f"rank {rank}: ok persistent step tp={world}", flush=True)
     # tensor-core prefill path (fused GEMM + all-reduce for o_proj, pull all-reduce after the MoE), then decode on its cache
     from ironpangu_b200.models.mla_moe_prefill import MlaMoePrefill
     pdec = MlaMoeDecoder(cfg, shard_weights(cfg, full, rank, world, "cuda"), fab, max_tokens=1, max_context=64, keep_logits=True)
