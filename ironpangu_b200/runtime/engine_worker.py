@@ -390,7 +390,7 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
         # a compiled bundle + its checkpoint: the physical program is executed instruction by instruction
         from ironpangu_b200.runtime.plan_engine import PlanEngine
 
-        eng = PlanEngine(args.bundle, args.checkpoint, fab, max_tokens=8, num_slots=args.max_num_seqs)
+        eng = PlanEngine(args.bundle, args.checkpoint, fab, max_tokens=None, num_slots=args.max_num_seqs)   # rows per step: as planned
         mark("program", "parameters, KV state and workspace of the compiled program")
         head = [i for i in eng.ins if i["op"] == "lm_head"][-1]
         vocab = int(eng._param(head["attrs"]["weight"]).shape[0]) * world

@@ -100,11 +100,79 @@ def load_parameters(init_plan: dict, ckpt: SafetensorsDir, device) -> Dict[str, 
     return params
 
 
-class PlanEngine:
-    """Runs a bundle's physical program for up to ``max_tokens`` (<= 8) query rows per step."""
+def _fnv1a64(data: bytes) -> int:
+    h = 0xcbf29ce484222325
+    for b in data:
+        h = ((h ^ b) * 0x100000001b3) & 0xFFFFFFFFFFFFFFFF
+    return h
 
-    def __init__(self, bundle_dir: str, checkpoint_dir: str, fabric: Fabric, *, max_tokens: int = 8,
+
+class FrozenArena:
+    """The activation arena a bundle was compiled with (``arena-rank-N.txt``, IFARENA2, and ``workspace-rank-N.txt``,
+    IFWORKSPACE1): ONE device block, every instruction result a view at the offset the compiler planned for it.
+
+    Rules (the reference's frozen arena: native/include/frozen_arena.h:26-54, native/src/prepared_execution.h:189-239):
+    the files' program fingerprint must be that of the bundle's ``execution.bin`` (a plan made for another program is
+    refused), the plan must cover at least as many query rows as the engine runs, a lease must fit its slot exactly or
+    leave room (never grow it), every instruction leases at most once, and nothing is allocated after construction."""
+
+    def __init__(self, bundle: Path, rank: int, rows: int, device):
+        text = (bundle / f"arena-rank-{rank}.txt").read_text().split("\n")
+        head = text[0].split()
+        if len(head) != 5 or head[0] != "IFARENA2":
+            raise ValueError("arena file is not IFARENA2")
+        want = _fnv1a64((bundle / "execution.bin").read_bytes())
+        if int(head[1], 16) != want:
+            raise ValueError(f"arena was planned for another program (fingerprint {head[1]}, this bundle's program has {want:016x})")
+        self.bytes, n = int(head[3]), int(head[4])
+        sizes = [tuple(int(x) for x in text[1 + i].split()) for i in range(n)]
+        if text[1 + n].strip() != "pool":
+            raise ValueError("arena file lacks its pool section")
+        owners = [tuple(int(x) for x in text[2 + n + i].split()) for i in range(n)]
+        tokens_line = text[2 + 2 * n].split()
+        self.tokens = int(tokens_line[1]) if len(tokens_line) == 2 and tokens_line[0] == "tokens" else 1
+        if self.tokens < rows:
+            raise ValueError(f"arena was planned for {self.tokens} query rows, the engine runs {rows}: compile the bundle with "
+                             f"prefill_tokens >= {rows}")
+        self.slots: Dict[int, tuple] = {}
+        for (off, size), (ins, first, last) in zip(sizes, owners):
+            if off % 512 or size % 512 or off + size > self.bytes:
+                raise ValueError(f"arena slot of instruction {ins} is misaligned or outside the arena")
+            self.slots[ins] = (off, size)
+        ws = (bundle / f"workspace-rank-{rank}.txt").read_text().split()
+        if len(ws) != 4 or ws[0] != "IFWORKSPACE1" or int(ws[1], 16) != want:
+            raise ValueError("workspace file does not belong to this bundle's program")
+        self.workspace_bytes = int(ws[3])
+        self.block = torch.zeros(self.bytes + self.workspace_bytes, dtype=torch.uint8, device=device)   # the one allocation
+        self.leased: Dict[int, int] = {}
+
+    def lease(self, instruction: int, nbytes: int) -> torch.Tensor:
+        """The planned slot of ``instruction`` as a byte tensor of ``nbytes``; raises when there is no slot, when it is smaller
+        than asked (the plan and the engine disagree on a shape) or when it was leased before."""
+        if instruction not in self.slots:
+            raise RuntimeError(f"the arena has no slot for instruction {instruction}")
+        if instruction in self.leased:
+            raise RuntimeError(f"instruction {instruction} leased its arena slot twice")
+        off, size = self.slots[instruction]
+        if nbytes > size:
+            raise RuntimeError(f"instruction {instruction} needs {nbytes} bytes, its arena slot holds {size}")
+        self.leased[instruction] = nbytes
+        return self.block[off:off + nbytes]
+
+    def workspace(self, nbytes: int) -> torch.Tensor:
+        if nbytes > self.workspace_bytes:
+            raise RuntimeError(f"a kernel needs {nbytes} bytes of workspace, the plan froze {self.workspace_bytes}")
+        return self.block[self.bytes:self.bytes + nbytes]
+
+
+class PlanEngine:
+    """Runs a bundle's physical program for up to ``max_tokens`` (<= 8) query rows per step. Activations live in the bundle's
+    frozen arena (one device block laid out by the compiler); sequence state (KV pages) and the step's control tensors are the
+    only other device memory, all of it allocated before the first step."""
+
+    def __init__(self, bundle_dir: str, checkpoint_dir: str, fabric: Fabric, *, max_tokens: Optional[int] = 8,
                  num_slots: int = 1, keep_logits: bool = False):
+        """``max_tokens``: query rows per step (at most 8); ``None`` takes what the bundle's arena was planned for."""
         self.fabric, self.rank, self.world = fabric, fabric.rank, fabric.world
         b = Path(bundle_dir)
         from .. import compiler
@@ -118,6 +186,9 @@ class PlanEngine:
         dev = fabric.device
         self.P = load_parameters(init_plan, SafetensorsDir(checkpoint_dir), dev)
         self.ins = self.program["instructions"]
+        if max_tokens is None:
+            planned = json.loads((b / "arena.json").read_text()).get("tokens", 1)
+            max_tokens = max(1, min(8, int(planned)))
         self.T = max_tokens
         self.max_context = self.program["max_context"]
         self.page_tokens = 16
@@ -139,14 +210,26 @@ class PlanEngine:
         self.logits = None
         self.vals: List[object] = [None] * len(self.ins)
         self.caches: Dict[int, torch.Tensor] = {}
+        self.arena = FrozenArena(b, self.rank, T, dev)
         self._alloc(dev)
+        self.bundle_sha256 = json.loads((b / "plan.json").read_text()).get("program_sha256", "")
         self.launches_per_forward = self.program["launches_per_token"] + sum(1 for i in self.ins if i["op"] == "mla_attention")
         self._graph = None
 
     # -- buffers -------------------------------------------------------------------------------------
     def _alloc(self, dev) -> None:
+        """Views into the frozen arena for every instruction result; KV pages as sequence state beside it."""
         T = self.T
         max_heads = 1
+        f32, i32 = torch.float32, torch.int32
+
+        def view(k: int, shape, dtype) -> torch.Tensor:
+            n = 1
+            for d in shape:
+                n *= d
+            esize = torch.empty((), dtype=dtype).element_size()
+            return self.arena.lease(k, n * esize).view(dtype).view(*shape)
+
         for k, i in enumerate(self.ins):
             op, w = i["op"], i["width"]
             if op == "view":
@@ -154,27 +237,32 @@ class PlanEngine:
             if op == "mla_kv_write":
                 self.caches[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
             elif op == "router_topk":
-                a = i["attrs"]
-                self.vals[k] = (torch.empty(T, w, dtype=torch.int32, device=dev), torch.empty(T, w, dtype=torch.float32, device=dev),
-                                torch.empty(T, int(a["experts"]), dtype=torch.float32, device=dev))
+                E = int(i["attrs"]["experts"])
+                raw = self.arena.lease(k, T * w * 8 + T * E * 4)           # ids | weights | logits, one slot
+                ids = raw[:T * w * 4].view(i32).view(T, w)
+                wts = raw[T * w * 4:T * w * 8].view(f32).view(T, w)
+                logits = raw[T * w * 8:].view(f32).view(T, E)
+                self.vals[k] = (ids, wts, logits)
             elif op == "moe_gate_up":
                 topk = self.ins[i["inputs"][1]]["width"]
-                self.vals[k] = torch.zeros(T, topk + 1, w, dtype=BF16, device=dev)
+                self.vals[k] = view(k, (T, topk + 1, w), BF16)
+                self.vals[k].zero_()
             elif op == "mla_q_absorb":
                 a = i["attrs"]
                 hl = int(a["heads"]) // self.world
                 max_heads = max(max_heads, hl)
-                self.vals[k] = torch.empty(T, hl, int(a["latent"]) + int(a["rope"]), dtype=BF16, device=dev)
+                self.vals[k] = view(k, (T, hl, int(a["latent"]) + int(a["rope"])), BF16)
             elif op == "lm_head":
                 vl = int(i["attrs"]["width"])
-                self.partial = torch.empty(((vl + 7) // 8) * 8 * 2, dtype=torch.float32, device=dev)
+                self._partial_floats = ((vl + 7) // 8) * 8 * 2
                 if self.keep_logits:
                     self.logits = torch.empty(T, vl, dtype=torch.float32, device=dev)
                 self.vals[k] = self.next_ids
             else:
-                dt = torch.float32 if i["dtype"] == "f32" else BF16
-                self.vals[k] = torch.empty(T, w, dtype=dt, device=dev)
-        self.scratch = torch.empty(T * max_heads * self.max_splits * (512 + 2), dtype=torch.float32, device=dev)
+                self.vals[k] = view(k, (T, w), f32 if i["dtype"] == "f32" else BF16)
+        # kernel scratch comes out of the frozen workspace: the attention splits and the argmax partials never live at once
+        self.scratch = self.arena.workspace(T * max_heads * self.max_splits * (512 + 2) * 4).view(f32)
+        self.partial = self.arena.workspace(self._partial_floats * 4).view(f32)
 
     def _param(self, name: str, optional: bool = False):
         if name in self.P:

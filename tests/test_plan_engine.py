@@ -18,7 +18,7 @@ def test_bundle_executes_token_exact_against_cpu_interpreter(tmp_path):
 
     ck, bundle = tmp_path / "ck", tmp_path / "bundle"
     assert compiler.cli("synth-checkpoint", str(SLICE), str(ck), "--seed", "3").returncode == 0
-    compiler.write_bundle(SLICE, bundle, checkpoint_dir=str(ck))
+    compiler.write_bundle(SLICE, bundle, checkpoint_dir=str(ck), prefill_tokens=8)      # the arena is planned for 8 query rows
     g = torch.Generator().manual_seed(3)
     prompt = torch.randint(0, 1024, (16,), generator=g).tolist()
     first = compiler.interpret(SLICE.read_text(), str(ck), prompt, steps=8)
@@ -29,6 +29,14 @@ def test_bundle_executes_token_exact_against_cpu_interpreter(tmp_path):
     fab = Fabric(0, 1)
     eng = PlanEngine(str(bundle), str(ck), fab, max_tokens=8, keep_logits=True)
     drv = DecodeEngine(eng)
+    # activations live in the bundle's frozen arena: one block of the planned size, every result a view at its planned offset
+    assert eng.arena.tokens == 8 and eng.arena.block.numel() == eng.arena.bytes + eng.arena.workspace_bytes
+    base, end = eng.arena.block.data_ptr(), eng.arena.block.data_ptr() + eng.arena.block.numel()
+    for k, v in enumerate(eng.vals):
+        for t in (v if isinstance(v, tuple) else (v,)):
+            if isinstance(t, torch.Tensor) and t is not eng.next_ids:
+                assert base <= t.data_ptr() < end and (t.data_ptr() - base) % 4 == 0, k
+    assert base + eng.arena.bytes <= eng.scratch.data_ptr() < end
     # teacher-forced on the oracle's tokens; logits must agree everywhere, tokens wherever the oracle has no near-tie
     for s in range(0, len(seq), 8):
         chunk = seq[s:s + 8]
@@ -44,11 +52,45 @@ def test_bundle_executes_token_exact_against_cpu_interpreter(tmp_path):
             if float(top2[0] - top2[1]) > 1e-2:
                 assert got[i] == int(ref[s + i].argmax()), (s + i, got[i])
             assert got[i] == int(logits[i].argmax())
-    # engine API: greedy generation through prefill chunks + captured decode graph
+    # engine API: greedy generation through prefill chunks + captured decode graph; once the graph exists a step allocates nothing
     eng.reset()
     out = drv.generate(prompt, 8)
+    before = torch.cuda.memory_stats()["allocation.all.allocated"]
+    tok = out[-1]
+    for _ in range(4):
+        tok = drv.step(tok)
+    assert torch.cuda.memory_stats()["allocation.all.allocated"] == before
     assert len(out) == 8 and all(0 <= t < 1024 for t in out)
     if all(float(ref[15 + i].topk(2).values.diff().abs()) > 1e-2 for i in range(8)):
         assert out == first["generated"]
     assert fab.status() == 0
+    fab.close()
+
+
+def test_arena_is_enforced(tmp_path):
+    """A bundle whose arena was planned for fewer rows than the engine runs, or whose arena file belongs to another program, is
+    refused before anything runs; a lease larger than its slot is refused too."""
+    from ironpangu_b200 import compiler
+    from ironpangu_b200.parallel.fabric import Fabric
+    from ironpangu_b200.runtime.plan_engine import FrozenArena, PlanEngine
+
+    ck, small, other = tmp_path / "ck", tmp_path / "small", tmp_path / "other"
+    assert compiler.cli("synth-checkpoint", str(SLICE), str(ck), "--seed", "3").returncode == 0
+    compiler.write_bundle(SLICE, small, checkpoint_dir=str(ck))                     # one query row
+    fab = Fabric(0, 1)
+    with pytest.raises(ValueError, match="planned for 1 query rows"):
+        PlanEngine(str(small), str(ck), fab, max_tokens=8)
+    eng = PlanEngine(str(small), str(ck), fab, max_tokens=1)
+    with pytest.raises(RuntimeError, match="leased its arena slot twice"):
+        eng.arena.lease(next(iter(eng.arena.leased)), 16)
+    free = [k for k in eng.arena.slots if k not in eng.arena.leased]
+    if free:
+        with pytest.raises(RuntimeError, match="arena slot holds"):
+            eng.arena.lease(free[0], eng.arena.slots[free[0]][1] + 512)
+    with pytest.raises(RuntimeError, match="workspace"):
+        eng.arena.workspace(eng.arena.workspace_bytes + 1)
+    compiler.write_bundle(SLICE, other, checkpoint_dir=str(ck), resident_sequences=2)   # another program variant
+    (small / "arena-rank-0.txt").write_text((other / "arena-rank-0.txt").read_text())
+    with pytest.raises(ValueError, match="another program"):
+        FrozenArena(small, 0, 1, "cuda")
     fab.close()

@@ -232,7 +232,7 @@ def test_program_engine_abi_and_cpu_server(tmp_path):
     ckpt, bundle = tmp_path / "ckpt", tmp_path / "bundle"
     r = compiler.cli("synth-checkpoint", src, str(ckpt))
     assert r.returncode == 0, r.stderr
-    r = compiler.cli("compile-token", src, str(ckpt), str(bundle), "--resident-sequences", "2")
+    r = compiler.cli("compile-token", src, str(ckpt), str(bundle), "--resident-sequences", "2", "--prefill-tokens", "8")
     assert r.returncode == 0, r.stderr
     prompt = [5, 77, 300, 12, 9]
     want = compiler.interpret(open(src).read(), str(ckpt), prompt, steps=4)["generated"]
