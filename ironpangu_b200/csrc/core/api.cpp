@@ -192,6 +192,7 @@ void Api::completions(const http::Request& req, http::ResponseWriter& w, bool ch
     return;
   }
   std::string text, error;
+  ErrorKind error_kind = ErrorKind::Backend;
   sched::Finish fin = sched::Finish::Error;
   for (;;) {
     auto item = out->pop(0.25);
@@ -209,11 +210,12 @@ void Api::completions(const http::Request& req, http::ResponseWriter& w, bool ch
     if (item->finish) {
       fin = *item->finish;
       error = item->error;
+      error_kind = item->error_kind;
       break;
     }
   }
   text += ts.flush();
-  if (fin == sched::Finish::Error) return send_error(w, Error(ErrorKind::Backend, error.empty() ? "generation failed" : error));
+  if (fin == sched::Finish::Error) return send_error(w, Error(error_kind, error.empty() ? "generation failed" : error));
   Json one = choice(text, Json(finish_reason(fin)), true);
   if (chat) {
     // reasoning sections and tool calls leave the content; a request may switch either parser off
@@ -290,7 +292,7 @@ void Api::generate_tokens(const http::Request& req, http::ResponseWriter& w) {
         w.write_chunk("data: [DONE]\n\n");
         w.end_stream();
       } else if (*item->finish == sched::Finish::Error) {
-        send_error(w, Error(ErrorKind::Backend, item->error.empty() ? "generation failed" : item->error));
+        send_error(w, Error(item->error_kind, item->error.empty() ? "generation failed" : item->error));
       } else {
         Json j = Json::object();
         j.set("request_id", id);

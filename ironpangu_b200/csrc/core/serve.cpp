@@ -474,7 +474,13 @@ void Service::run() {
       try {
         sch.submit(std::move(req));
       } catch (const Error& e) {
-        finish(id, StreamItem{std::nullopt, sched::Finish::Error, e.what()});
+        // the submit-side check races with requests still in the inbox; a request the scheduler's queue cannot take is
+        // refused as overloaded (429), like one refused at the door
+        if (e.kind() == ErrorKind::Capacity) {
+          std::lock_guard<std::mutex> lk(mu_);
+          ++counters_.rejected_overloaded;
+        }
+        finish(id, StreamItem{std::nullopt, sched::Finish::Error, e.what(), e.kind()});
       }
     }
     for (auto& [id, lv] : live)

@@ -112,6 +112,7 @@ struct StreamItem {
   std::optional<uint32_t> token;
   std::optional<sched::Finish> finish;
   std::string error;
+  ErrorKind error_kind = ErrorKind::Backend;   // of a terminal Finish::Error: Capacity when admission refused the request after all
 };
 
 class Stream {
