@@ -138,83 +138,98 @@ class Parser {
     return m;
   }
 
-  std::vector<size_t> shape(size_t depth) {
+  // A bracketed list of numeric literals, read straight from the tokens: `[` number (`,` number)* `]`. `what` names the
+  // list in diagnostics ("shape", "initializer"); each literal goes through `take` with its position for the message.
+  template <class F>
+  size_t literal_list(const char* what, F&& take) {
+    if (!is("[")) err(std::string(what) + ": expected '[' and a list of numbers");
+    ++p_;
+    size_t n = 0;
+    while (!is("]")) {
+      const Token& t = peek();
+      if (t.kind != Token::Kind::Number) err(std::string(what) + ": entry " + std::to_string(n) + " is not a number literal");
+      take(t.text, n);
+      ++p_;
+      ++n;
+      if (!is(",")) break;
+      ++p_;
+    }
+    expect("]");
+    return n;
+  }
+
+  // what follows the keyword of a graph-body declaration
+  struct DeclForm {
+    const char* keyword;
+    Member::Kind kind;
+    bool named, typed, initialised, valued;   // NAME / ": tensor<f32>[dims]" / "= [floats]" / "= expr" (or bare expr when unnamed)
+  };
+  static const DeclForm* decl_form(const std::string& key) {
+    static const DeclForm forms[] = {
+        {"input", Member::Kind::Input, true, true, false, false},   {"const", Member::Kind::Constant, true, true, true, false},
+        {"state", Member::Kind::State, true, true, true, false},    {"update", Member::Kind::Update, true, false, false, true},
+        {"let", Member::Kind::Let, true, false, false, true},       {"yield", Member::Kind::Yield, false, false, false, true},
+    };
+    for (const auto& f : forms)
+      if (key == f.keyword) return &f;
+    return nullptr;
+  }
+
+  void tensor_type(Member& m) {
     expect(":");
     expect_ident("tensor");
     expect("<");
     expect_ident("f32");
     expect(">");
-    ExprPtr e = expr(depth + 1);
-    if (e->kind != Expr::Kind::List) err("expected shape list");
-    std::vector<size_t> dims;
-    for (auto& a : e->args) {
-      if (a.second->kind != Expr::Kind::Number) err("dimension must be an integer");
-      char* end = nullptr;
-      long long v = strtoll(a.second->text.c_str(), &end, 10);
-      if (!end || *end || v <= 0) err("invalid dimension");
-      dims.push_back((size_t)v);
-    }
-    return dims;
+    literal_list("shape", [&](const std::string& text, size_t i) {
+      size_t v = 0;
+      for (char c : text) {
+        if (c < '0' || c > '9') err("shape: dimension " + std::to_string(i) + " ('" + text + "') is not a positive integer");
+        if (v > (SIZE_MAX - 9) / 10) err("shape: dimension " + std::to_string(i) + " overflows");
+        v = v * 10 + (size_t)(c - '0');
+      }
+      if (v == 0) err("shape: dimension " + std::to_string(i) + " is zero");
+      m.dims.push_back(v);
+    });
   }
-  std::vector<float> floats(size_t depth) {
-    ExprPtr e = expr(depth + 1);
-    if (e->kind != Expr::Kind::List) err("expected initializer list");
-    std::vector<float> v;
-    for (auto& a : e->args) {
-      if (a.second->kind != Expr::Kind::Number) err("initializer must be numeric");
+
+  void initialiser(Member& m) {
+    size_t want = 1;
+    for (size_t d : m.dims) want *= d;
+    const size_t got = literal_list("initializer", [&](const std::string& text, size_t i) {
       char* end = nullptr;
-      float f = strtof(a.second->text.c_str(), &end);
-      if (!end || *end) err("invalid float");
-      v.push_back(f);
-    }
-    return v;
+      const float f = strtof(text.c_str(), &end);
+      if (end == text.c_str() || *end) err("initializer: entry " + std::to_string(i) + " ('" + text + "') is not a float");
+      m.values.push_back(f);
+    });
+    if (got != want)
+      err("initializer of " + m.name + " has " + std::to_string(got) + " values, its shape holds " + std::to_string(want));
   }
 
   std::vector<Member> members(bool graph_allowed, size_t depth) {
     if (depth > kMaxNesting) fail(ErrorKind::Capacity, "declaration nesting limit (64)");
     expect("{");
     std::vector<Member> out;
-    while (!is("}")) {
+    for (; !is("}"); expect(";"), out.back().end = t_[p_ - 1].end) {
       if (peek().kind == Token::Kind::End) err("unclosed declaration");
-      Member m;
+      Member& m = out.emplace_back();
       m.start = peek().start;
-      std::string key = ident();
-      if (graph_allowed && key == "input") {
-        m.kind = Member::Kind::Input;
-        m.name = ident();
-        m.dims = shape(depth);
-      } else if (graph_allowed && (key == "const" || key == "state")) {
-        m.kind = key == "const" ? Member::Kind::Constant : Member::Kind::State;
-        m.name = ident();
-        m.dims = shape(depth);
-        expect("=");
-        m.values = floats(depth);
-        size_t n = 1;
-        for (size_t d : m.dims) n *= d;
-        if (n != m.values.size()) err("initializer length does not match the shape");
-      } else if (graph_allowed && key == "update") {
-        m.kind = Member::Kind::Update;
-        m.name = ident();
-        expect("=");
-        m.expr = expr(depth + 1);
-      } else if (graph_allowed && key == "let") {
-        m.kind = Member::Kind::Let;
-        m.name = ident();
-        if (m.name.find('.') != std::string::npos) err("binding name cannot contain '.'");
-        expect("=");
-        m.expr = expr(depth + 1);
-      } else if (graph_allowed && key == "yield") {
-        m.kind = Member::Kind::Yield;
-        m.expr = expr(depth + 1);
-      } else {
+      const std::string key = ident();
+      const DeclForm* form = graph_allowed ? decl_form(key) : nullptr;
+      if (!form) {                       // `name = expr`: a field of a record / weights scope
         m.kind = Member::Kind::Field;
         m.name = key;
         expect("=");
         m.expr = expr(depth + 1);
+        continue;
       }
-      expect(";");
-      m.end = t_[p_ - 1].end;
-      out.push_back(std::move(m));
+      m.kind = form->kind;
+      if (form->named) m.name = ident();
+      if (form->kind == Member::Kind::Let && m.name.find('.') != std::string::npos) err("binding name cannot contain '.'");
+      if (form->typed) tensor_type(m);
+      if (form->initialised || (form->valued && form->named)) expect("=");
+      if (form->initialised) initialiser(m);
+      if (form->valued) m.expr = expr(depth + 1);
     }
     expect("}");
     return out;
