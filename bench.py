@@ -117,8 +117,8 @@ def library_arm(cfg, weights, rank, world, max_context, prompt, native_tokens, n
             dist.all_reduce(t, op=op)
         return t
 
-    def judge(native_tok: int, ln):
-        lb = bdec.logits[0]
+    def judge(native_tok: int, ln, row: int = 0):
+        lb = bdec.logits[row]
         best = allreduce(lb.max().reshape(1).clone(), dist.ReduceOp.MAX)
         local = native_tok - rank * vl
         mine = lb[local].reshape(1).clone() if 0 <= local < vl else torch.full((1,), float("-inf"), device=dev)
@@ -131,8 +131,9 @@ def library_arm(cfg, weights, rank, world, max_context, prompt, native_tokens, n
 
     rows = []
     pred = beng.prefill(prompt)
+    last_row = (len(prompt) - 1) % beng.chunk        # the prompt's last token is this row of the library arm's last chunk
     for i, tok in enumerate(native_tokens):
-        margin, eps = judge(tok, native_logits[i])
+        margin, eps = judge(tok, native_logits[i], last_row if i == 0 else 0)
         rows.append((pred == tok, margin, eps))
         if i + 1 < len(native_tokens):
             pred = beng.step(tok)
@@ -141,7 +142,9 @@ def library_arm(cfg, weights, rank, world, max_context, prompt, native_tokens, n
     agree = [same or margin <= 4.5 * (eps if eps is not None else eps_max) for same, margin, eps in rows]
     out = {"tokens_match": bool(all(agree)), "tokens_compared": len(rows), "tokens_identical": sum(1 for same, _, _ in rows if same),
            "largest_margin_of_a_differing_token": round(max([m for same, m, _ in rows if not same], default=0.0), 5),
-           "logit_noise_rms": round(eps_max, 5), "expert_path": bdec.expert_path}
+           "logit_noise_rms": round(eps_max, 5), "expert_path": bdec.expert_path,
+           # per compared position: identical?, the library arm's margin against the native token, the logit noise there
+           "rows": [[int(same), round(margin, 4), None if eps is None else round(eps, 4)] for same, margin, eps in rows]}
     beng.run_device_loop(native_tokens[-1], 3)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

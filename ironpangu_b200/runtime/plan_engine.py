@@ -170,9 +170,16 @@ class PlanEngine:
     frozen arena (one device block laid out by the compiler); sequence state (KV pages) and the step's control tensors are the
     only other device memory, all of it allocated before the first step."""
 
-    def __init__(self, bundle_dir: str, checkpoint_dir: str, fabric: Fabric, *, max_tokens: Optional[int] = 8,
-                 num_slots: int = 1, keep_logits: bool = False):
-        """``max_tokens``: query rows per step (at most 8); ``None`` takes what the bundle's arena was planned for."""
+    def __init__(self, bundle_dir: str, checkpoint_dir: Optional[str], fabric: Fabric, *, max_tokens: Optional[int] = 8,
+                 num_slots: int = 1, keep_logits: bool = False, parameters: Optional[Dict[str, torch.Tensor]] = None,
+                 fused_head: Optional[bool] = None, fused_moe: Optional[bool] = None):
+        """``max_tokens``: query rows per step (at most 8); ``None`` takes what the bundle's arena was planned for.
+        ``parameters``: device tensors by the init plan's parameter names, used instead of a checkpoint (random-init
+        benchmarks, weights another engine already holds); every parameter of the plan must be there with the plan's
+        shape and dtype. ``fused_head`` / ``fused_moe``: let the dispatcher replace the instruction groups
+        {q_b linear, cache write, absorb, attention} and {router, expert gate/up, expert down + all-reduce} by their
+        one-launch kernels where the shapes allow (defaults: the head kernel for contexts up to 2048 keys, the expert block
+        from 4 ranks up, both only for steps of one or two rows - the measured crossovers of the kernels)."""
         self.fabric, self.rank, self.world = fabric, fabric.rank, fabric.world
         b = Path(bundle_dir)
         from .. import compiler
@@ -184,7 +191,8 @@ class PlanEngine:
             raise ValueError(f"bundle was compiled for tp={self.program['parallel']['tp']}, running on {self.world} ranks")
         init_plan = json.loads((b / f"rank-{self.rank}.init.json").read_text())
         dev = fabric.device
-        self.P = load_parameters(init_plan, SafetensorsDir(checkpoint_dir), dev)
+        self.P = (self._adopt(init_plan, parameters) if parameters is not None
+                  else load_parameters(init_plan, SafetensorsDir(checkpoint_dir), dev))
         self.ins = self.program["instructions"]
         if max_tokens is None:
             planned = json.loads((b / "arena.json").read_text()).get("tokens", 1)
@@ -213,8 +221,98 @@ class PlanEngine:
         self.arena = FrozenArena(b, self.rank, T, dev)
         self._alloc(dev)
         self.bundle_sha256 = json.loads((b / "plan.json").read_text()).get("program_sha256", "")
-        self.launches_per_forward = self.program["launches_per_token"] + sum(1 for i in self.ins if i["op"] == "mla_attention")
+        self._prepare(fused_head, fused_moe)
         self._graph = None
+
+    @staticmethod
+    def _adopt(init_plan: dict, given: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        """The caller's tensors as this rank's parameters, checked against the init plan (name, shape, dtype)."""
+        out = {}
+        for p in init_plan["parameters"]:
+            t = given.get(p["name"])
+            if t is None:
+                raise KeyError(f"no tensor was given for parameter {p['name']}")
+            want = {"bf16": BF16, "f32": torch.float32}.get(p["dtype"])
+            if want is None or t.dtype != want or list(t.shape) != list(p["dims"]) or not t.is_contiguous():
+                raise ValueError(f"parameter {p['name']}: the plan wants {p['dtype']} {p['dims']}, got {t.dtype} {list(t.shape)}")
+            out[p["name"]] = t
+        return out
+
+    # -- dispatcher: instruction groups -> kernels -------------------------------------------------------
+    def _prepare(self, fused_head: Optional[bool], fused_moe: Optional[bool]) -> None:
+        """Finds the instruction groups that have a one-launch kernel and records them at the group's last member (the
+        anchor); ``forward`` runs the anchor's kernel and skips the other members when the step is narrow enough.
+        Reference: the native dispatcher that picks a kernel per instruction (native/src/token_dispatch.inc:19-294)."""
+        ins = self.ins
+        users: Dict[int, List[int]] = {}
+        for k, i in enumerate(ins):
+            for j in i["inputs"]:
+                users.setdefault(j, []).append(k)
+
+        def through_views(k: int) -> List[int]:
+            out = []
+            for u in users.get(k, []):
+                out += through_views(u) if ins[u]["op"] == "view" else [u]
+            return out
+
+        self.head_groups: Dict[int, dict] = {}
+        self.moe_groups: Dict[int, dict] = {}
+        self.layer_weights: List[dict] = []       # per decoder layer, in program order: the parameter names of its kernels
+        for k, i in enumerate(ins):
+            if i["op"] == "mla_attention":
+                kabs, kw = i["inputs"]
+                if ins[kabs]["op"] != "mla_q_absorb" or ins[kw]["op"] != "mla_kv_write":
+                    continue
+                kqb = ins[kabs]["inputs"][0]
+                qb = ins[kqb]
+                if qb["op"] != "linear" or "norm_weight" not in qb["attrs"] or "paired_weight" in qb["attrs"]:
+                    continue
+                vq, vlat, vr = ins[qb["inputs"][0]], ins[ins[kw]["inputs"][0]], ins[ins[kw]["inputs"][1]]
+                if not all(v["op"] == "view" for v in (vq, vlat, vr)) or len({v["inputs"][0] for v in (vq, vlat, vr)}) != 1:
+                    continue
+                a, aa = i["attrs"], ins[kabs]["attrs"]
+                q_lora, latent, rope, nope = int(vq["attrs"]["width"]), int(aa["latent"]), int(aa["rope"]), int(aa["nope"])
+                vdim = int(a["value"])
+                if (int(vq["attrs"]["start"]), int(vlat["attrs"]["start"]), int(vr["attrs"]["start"])) != (0, q_lora, q_lora + latent):
+                    continue
+                private = users.get(kqb, []) == [kabs] and users.get(kabs, []) == [k] and users.get(kw, []) == [k]
+                shapes_ok = latent == 512 and rope == 64 and nope % 32 == 0 and nope <= 128 and vdim <= 128 and q_lora % 8 == 0
+                self.head_groups[k] = {"members": (kqb, kw, kabs), "qkv": vq["inputs"][0], "q_lora": q_lora, "nope": nope, "vdim": vdim,
+                                       "q_norm": qb["attrs"]["norm_weight"], "kv_norm": ins[kw]["attrs"]["weight"], "w_qb": qb["attrs"]["weight"],
+                                       "w_kvb": a["weight"], "eps": float(qb["attrs"].get("norm_eps", 1e-5)), "theta": float(aa["theta"]),
+                                       "scale": 1.0 / math.sqrt(float(a["scale_dim"])), "window": int(a["window"]), "cache": kw,
+                                       "ok": private and shapes_ok and aa["weight"] == a["weight"]}
+            elif i["op"] == "moe_down_allreduce" and len(i["inputs"]) > 2:
+                kgu, kr, kres = i["inputs"][:3]
+                if ins[kgu]["op"] != "moe_gate_up" or ins[kr]["op"] != "router_topk":
+                    continue
+                r, g, a = ins[kr]["attrs"], ins[kgu]["attrs"], i["attrs"]
+                kx = ins[kr]["inputs"][0]
+                same_x = ins[kgu]["inputs"][0] == kx and kres == kx and r.get("norm_weight") == g.get("norm_weight")
+                private = sorted(users.get(kr, [])) == sorted([kgu, k]) and users.get(kgu, []) == [k]
+                self.moe_groups[k] = {"members": (kr, kgu), "router": kr, "gate_up": kgu, "x": kx,
+                                      "ok": same_x and private and "shared_weight" in g and "shared_weight" in a}
+        self.fused_ctx_limit = 2048
+        can_head = bool(self.head_groups) and all(g["ok"] for g in self.head_groups.values())
+        self.fused_head = (can_head and self.max_context <= self.fused_ctx_limit) if fused_head is None else (bool(fused_head) and can_head)
+        self.fuse_override: Optional[bool] = None          # engines that know the position pick the head kernel per step
+        self.can_fuse_head = can_head
+        can_moe = bool(self.moe_groups) and all(g["ok"] for g in self.moe_groups.values())
+        for g in self.moe_groups.values():
+            wgu = self.P.get(self.ins[g["gate_up"]]["attrs"]["weight"] + "|" + self.ins[g["gate_up"]]["attrs"]["paired_weight"])
+            E = int(self.ins[g["router"]]["attrs"]["experts"])
+            can_moe = can_moe and wgu is not None and wgu.shape[1] // 2 <= 1536 and E <= 256 and self.ins[g["router"]]["width"] <= 16
+        self.fused_moe = (can_moe and self.world >= 4) if fused_moe is None else (bool(fused_moe) and can_moe)
+        self.moe_sync = None
+        if can_moe:
+            E = max(int(self.ins[g["router"]]["attrs"]["experts"]) for g in self.moe_groups.values())
+            self.moe_sync = torch.zeros(K.moe_block_sync_words(2, E), dtype=torch.int32, device=self.fabric.device)
+        # members of a group that the anchor's kernel covers
+        self._head_members = {m: k for k, g in self.head_groups.items() for m in g["members"]}
+        self._moe_members = {m: k for k, g in self.moe_groups.items() for m in g["members"]}
+        per_token = self.program["launches_per_token"] + sum(1 for i in self.ins if i["op"] == "mla_attention")
+        self.launches_per_forward = (per_token - (4 * len(self.head_groups) if self.fused_head else 0)
+                                     - (2 * len(self.moe_groups) if self.fused_moe else 0))
 
     # -- buffers -------------------------------------------------------------------------------------
     def _alloc(self, dev) -> None:
@@ -282,11 +380,37 @@ class PlanEngine:
             v = V[idx]
             return v[:T] if isinstance(v, torch.Tensor) else v
 
+        narrow = T <= 2
+        head = (self.fused_head if self.fuse_override is None else (self.fuse_override and self.can_fuse_head)) and narrow
+        moe = self.fused_moe and narrow
         for k, i in enumerate(self.ins):
             op, a, ins = i["op"], i["attrs"], i["inputs"]
+            if (head and k in self._head_members) or (moe and k in self._moe_members):
+                if op == "mla_kv_write":
+                    V[k] = k                  # the cache of this write, for whoever reads it
+                continue
             norm_w = self._param(a["norm_weight"], "norm_optional" in a) if "norm_weight" in a else None
             eps = float(a.get("norm_eps", 1e-5))
-            if op == "embedding":
+            if head and k in self.head_groups:
+                g = self.head_groups[k]
+                hl = int(a["heads"]) // self.world
+                K.mla_head_decode(val(g["qkv"]), self._param(g["q_norm"]), self._param(g["kv_norm"]), self._param(g["w_qb"]),
+                                  self._param(g["w_kvb"]).view(hl, g["nope"] + g["vdim"], 512), self.caches[g["cache"]], pos, slot,
+                                  self.page_table, q_lora=g["q_lora"], nope=g["nope"], scale=g["scale"], eps=g["eps"], theta=g["theta"],
+                                  window=g["window"], out=val(k), status_ptr=st)
+            elif moe and k in self.moe_groups:
+                g = self.moe_groups[k]
+                r, gu = self.ins[g["router"]]["attrs"], self.ins[g["gate_up"]]["attrs"]
+                ids, wts, logits = V[g["router"]]
+                wgu, wd = self._param(gu["weight"] + "|" + gu["paired_weight"]), self._param(a["weight"])
+                K.moe_block(val(g["x"]), self._param(r["weight"]), wgu, wd, self.rank * wgu.shape[0], int(r["topk"]), fab, sync=self.moe_sync,
+                            norm_w=self._param(r["norm_weight"]) if "norm_weight" in r else None, eps=float(r.get("norm_eps", 1e-5)),
+                            bias=self._param(r["weight"] + ".e_score_correction_bias", True), scoring=r["scoring"],
+                            renorm=r.get("renorm", "true") != "false", scale=float(r["scale"]),
+                            w_shared_gu=self._param(gu["shared_weight"] + "|" + gu["shared_paired_weight"]),
+                            w_shared_down=self._param(a["shared_weight"]), logits=logits[:T], ids=ids[:T], wts=wts[:T],
+                            act=V[g["gate_up"]][:T], out=val(k))
+            elif op == "embedding":
                 K.embedding(tok, self._param(a["weight"]), out=val(k), status_ptr=st)
             elif op == "view":
                 src = V[ins[0]]
