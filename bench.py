@@ -44,6 +44,9 @@ def parse():
     ap.add_argument("--baseline-steps", type=int, default=16,
                     help="native arm, MLA+MoE models: also run the cuBLAS + NCCL decoder on the same weights in this process - compare "
                          "its first greedy tokens with the native arm's and time this many of its decode steps (0: skip)")
+    ap.add_argument("--executor", default="bundle", choices=["bundle", "model"],
+                    help="native arm, bf16 MLA+MoE models: 'bundle' compiles the model's .inferfabric source and runs the bundle's "
+                         "program (runtime/plan_engine.py); 'model' runs the hand-wired decoder class (models/mla_moe.py)")
     ap.add_argument("--fused-moe", type=int, default=-1, help="-1: decoder default; 0/1: MoE half of a layer as three launches / one")
     return ap.parse_args()
 
@@ -205,6 +208,7 @@ def main():
     max_context = args.context + (R + 2) * K + 2 * W + CHECK + 64
     fab = Fabric(rank, world)
     t0 = time.time()
+    bundle_sha = ""
     weights = (G.random_rank_weights if dense else random_rank_weights)(cfg, rank, world, dev, seed=0)
     torch.cuda.synchronize()
     weight_bytes = sum(t.numel() * t.element_size() for t in weights.values())
@@ -212,6 +216,22 @@ def main():
         if args.impl != "native":
             raise SystemExit("--model dense2b runs on the native path only")
         dec = G.DenseDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1)
+    elif args.impl == "native" and args.executor == "bundle" and not (args.expert_fp8 or args.kv_int8):
+        # compile the model's source for this tensor-parallel width and run the bundle's program: the dispatcher of the plan
+        # engine picks the kernels, the activations live in the bundle's frozen arena, the weights are the tensors above
+        import tempfile
+        from ironpangu_b200 import compiler
+        from ironpangu_b200.compiler.sources import mla_moe_source
+        from ironpangu_b200.models.mla_moe import bundle_parameters
+        from ironpangu_b200.runtime.plan_engine import PlanEngine
+        work = tempfile.mkdtemp(prefix=f"ifab-bench-r{rank}-")
+        src = os.path.join(work, "model.inferfabric")
+        with open(src, "w") as f:
+            f.write(mla_moe_source(cfg, world, context=max_context))
+        compiled = compiler.write_bundle(src, os.path.join(work, "bundle"), prefill_tokens=8)
+        dec = PlanEngine(compiled["dir"], None, fab, max_tokens=8, num_slots=1, parameters=bundle_parameters(cfg, weights),
+                         fused_moe=None if args.fused_moe < 0 else bool(args.fused_moe))
+        bundle_sha = compiled["program_sha256"]
     elif args.impl == "native":
         dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1,
                             expert_fp8=args.expert_fp8, kv_int8=args.kv_int8,
@@ -344,7 +364,7 @@ def main():
                                                  "(not the headline model)") if dense and not args.layers
                        else f"{args.model} layers={cfg.layers} (reduced config)",
                        "params_b": round(cfg.param_count() / 1e9, 2), "global_batch": 1, "seq_len": args.context,
-                       "decode_tokens": K, "parallelism": f"tp{world}" if dense else f"tp{world}ep{world}", "decode_step": "operator chain",
+                       "decode_tokens": K, "parallelism": f"tp{world}" if dense else f"tp{world}ep{world}", "decode_step": (f"compiled bundle {bundle_sha[:16]}: plan engine, {dec.launches_per_forward} launches" if bundle_sha else "operator chain"),
                        "prefill": args.prefill if args.impl == "native" else "library",
                        "l2": "per-step weight stream (>= 2.5 GB per rank) exceeds the 126 MB L2; no explicit flush",
                        "baseline_ref": "17.7293 ms TPOT on 8x Ascend (docs/validation/2026-10-17-packed-c8/README.md:20-23)",

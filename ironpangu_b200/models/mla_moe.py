@@ -373,6 +373,32 @@ class MlaMoeDecoder:
             cch.zero_()
 
 
+def bundle_parameters(cfg: MlaMoeConfig, weights: Dict[str, torch.Tensor], prefix: str = "model") -> Dict[str, torch.Tensor]:
+    """This module's per-rank weight tensors under the parameter names of a bundle compiled from
+    ``compiler.sources.mla_moe_source`` (``model.layers.N.self_attn.q_b_proj`` ..., pairs joined by ``|``); the same storage,
+    so a bundle's engine and the library baseline can run on one copy of the weights."""
+    c = cfg
+    out = {f"{prefix}.embed_tokens": weights["embed"], f"{prefix}.norm": weights["final_norm"], "lm_head": weights["lm_head"]}
+    for l in range(c.layers):
+        p, q = f"layers.{l}.", f"{prefix}.layers.{l}."
+        a, m = q + "self_attn.", q + "mlp."
+        out[q + "input_layernorm"] = weights[p + "attn_norm"]
+        out[a + "q_a_proj|" + a + "kv_a_proj_with_mqa"] = weights[p + "qkv_a"]
+        out[a + "q_a_layernorm"], out[a + "kv_a_layernorm"] = weights[p + "q_a_norm"], weights[p + "kv_a_norm"]
+        out[a + "q_b_proj"] = weights[p + "q_b"]
+        kvb = weights[p + "kv_b"]
+        out[a + "kv_b_proj"] = kvb.view(kvb.shape[0] * kvb.shape[1], kvb.shape[2])
+        out[a + "o_proj"] = weights[p + "o_proj"]
+        out[q + "post_attention_layernorm"] = weights[p + "ffn_norm"]
+        out[m + "gate"] = weights[p + "router"]
+        e = m + "experts.{expert}."
+        out[e + "gate_proj|" + e + "up_proj"] = weights[p + "gate_up"]
+        out[e + "down_proj"] = weights[p + "down"]
+        out[m + "shared_experts.gate_proj|" + m + "shared_experts.up_proj"] = weights[p + "shared_gate_up"]
+        out[m + "shared_experts.down_proj"] = weights[p + "shared_down"]
+    return out
+
+
 def weights_from_checkpoint(cfg: MlaMoeConfig, checkpoint_dir: str, prefix: str = "model") -> Dict[str, torch.Tensor]:
     """Unsharded weights of this module's naming from a safetensors checkpoint that uses the scoped names
     of the DSL examples (``model.layers.N.self_attn.q_a_proj.weight`` ...)."""

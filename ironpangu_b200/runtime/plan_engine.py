@@ -217,7 +217,8 @@ class PlanEngine:
         self.keep_logits = keep_logits
         self.logits = None
         self.vals: List[object] = [None] * len(self.ins)
-        self.caches: Dict[int, torch.Tensor] = {}
+        self._cache_of: Dict[int, torch.Tensor] = {}     # cache-write instruction -> its pages
+        self.caches: List[torch.Tensor] = []              # the same tensors in program order (one per attention layer)
         self.arena = FrozenArena(b, self.rank, T, dev)
         self._alloc(dev)
         self.bundle_sha256 = json.loads((b / "plan.json").read_text()).get("program_sha256", "")
@@ -296,6 +297,7 @@ class PlanEngine:
         can_head = bool(self.head_groups) and all(g["ok"] for g in self.head_groups.values())
         self.fused_head = (can_head and self.max_context <= self.fused_ctx_limit) if fused_head is None else (bool(fused_head) and can_head)
         self.fuse_override: Optional[bool] = None          # engines that know the position pick the head kernel per step
+        self.fused_auto = fused_head is None
         self.can_fuse_head = can_head
         can_moe = bool(self.moe_groups) and all(g["ok"] for g in self.moe_groups.values())
         for g in self.moe_groups.values():
@@ -307,12 +309,65 @@ class PlanEngine:
         if can_moe:
             E = max(int(self.ins[g["router"]]["attrs"]["experts"]) for g in self.moe_groups.values())
             self.moe_sync = torch.zeros(K.moe_block_sync_words(2, E), dtype=torch.int32, device=self.fabric.device)
+        self._router_shares_norm = {g["router"] for g in self.moe_groups.values() if g["ok"] and "norm_weight" in self.ins[g["router"]]["attrs"]}
+        hidden = max((self.ins[self.ins[r]["inputs"][0]]["width"] for r in self._router_shares_norm), default=0)
+        self.xn = self.arena.workspace(self.T * hidden * 2).view(BF16).view(self.T, hidden) if hidden else None
         # members of a group that the anchor's kernel covers
         self._head_members = {m: k for k, g in self.head_groups.items() for m in g["members"]}
         self._moe_members = {m: k for k, g in self.moe_groups.items() for m in g["members"]}
         per_token = self.program["launches_per_token"] + sum(1 for i in self.ins if i["op"] == "mla_attention")
         self.launches_per_forward = (per_token - (4 * len(self.head_groups) if self.fused_head else 0)
                                      - (2 * len(self.moe_groups) if self.fused_moe else 0))
+        self._describe()
+
+    def _describe(self) -> None:
+        """What the program says about the model, in the vocabulary of the hand-wired decoder (``models/mla_moe.py``): a
+        configuration record and the parameters by role. The prompt executor (``models/mla_moe_prefill.py``) and the batch
+        engine read a decoder through these attributes, so they run on a bundle's engine as they do on ``MlaMoeDecoder``.
+        Left undefined (``cfg is None``) for programs that are not a stack of {latent attention, routed experts} layers."""
+        self.cfg, self.w, self.kv_int8 = None, {}, False
+        ins = self.ins
+        heads, moes = sorted(self.head_groups), sorted(self.moe_groups)
+        emb = next((i for i in ins if i["op"] == "embedding"), None)
+        head = next((i for i in ins if i["op"] == "lm_head"), None)
+        if not heads or len(heads) != len(moes) or emb is None or head is None:
+            return
+        from ..models.mla_moe import MlaMoeConfig
+
+        g0, m0 = self.head_groups[heads[0]], self.moe_groups[moes[0]]
+        a0, r0, gu0 = ins[heads[0]]["attrs"], ins[m0["router"]]["attrs"], ins[m0["gate_up"]]["attrs"]
+        self.cfg = MlaMoeConfig(layers=len(heads), hidden=emb["width"], vocab=int(emb["attrs"]["vocab"]), heads=int(a0["heads"]),
+                                q_lora=g0["q_lora"], kv_lora=int(a0["latent"]), nope=g0["nope"], rope=int(ins[g0["members"][2]]["attrs"]["rope"]),
+                                vdim=g0["vdim"], experts=int(r0["experts"]), expert_ffn=ins[m0["gate_up"]]["width"], topk=int(r0["topk"]),
+                                shared_ffn=int(gu0["shared_width"]) * self.world, theta=g0["theta"], eps=g0["eps"], window=g0["window"],
+                                scoring=r0["scoring"], route_scale=float(r0["scale"]), eos=int(self.program.get("eos", -1)),
+                                page_tokens=self.page_tokens)
+        c = self.cfg
+        self.hl, self.el, self.vl = c.heads // self.world, c.experts // self.world, c.vocab // self.world
+        w = self.w
+        w["embed"], w["final_norm"], w["lm_head"] = self._param(emb["attrs"]["weight"]), self._param(head["attrs"]["norm_weight"]), self._param(head["attrs"]["weight"])
+        for l, (kh, km) in enumerate(zip(heads, moes)):
+            g, m = self.head_groups[kh], self.moe_groups[km]
+            qkv = ins[g["qkv"]]["attrs"]
+            o = next(ins[u] for u in range(kh + 1, km) if ins[u]["op"] == "linear_allreduce" and ins[u]["inputs"][0] == kh)
+            r, gu, dn = ins[m["router"]]["attrs"], ins[m["gate_up"]]["attrs"], ins[km]["attrs"]
+            p = f"layers.{l}."
+            w[p + "attn_norm"], w[p + "qkv_a"] = self._param(qkv["norm_weight"]), self._param(qkv["weight"] + "|" + qkv["paired_weight"])
+            w[p + "q_a_norm"], w[p + "kv_a_norm"], w[p + "q_b"] = self._param(g["q_norm"]), self._param(g["kv_norm"]), self._param(g["w_qb"])
+            w[p + "kv_b"] = self._param(g["w_kvb"]).view(self.hl, c.nope + c.vdim, c.kv_lora)
+            w[p + "o_proj"] = self._param(o["attrs"]["weight"])
+            w[p + "ffn_norm"], w[p + "router"] = self._param(r["norm_weight"]), self._param(r["weight"])
+            w[p + "gate_up"], w[p + "down"] = self._param(gu["weight"] + "|" + gu["paired_weight"]), self._param(dn["weight"])
+            w[p + "shared_gate_up"] = self._param(gu["shared_weight"] + "|" + gu["shared_paired_weight"])
+            w[p + "shared_down"] = self._param(dn["shared_weight"])
+
+    def forward_feedback(self, T: Optional[int] = None) -> torch.Tensor:
+        """One step whose sampled token and position + 1 become the inputs of the next step (device-side feedback)."""
+        T = self.T if T is None else T
+        self.forward(T)
+        self.tokens[:T].copy_(self.next_ids[:T])
+        self.positions[:T].add_(1)
+        return self.next_ids[:T]
 
     # -- buffers -------------------------------------------------------------------------------------
     def _alloc(self, dev) -> None:
@@ -333,7 +388,8 @@ class PlanEngine:
             if op == "view":
                 continue
             if op == "mla_kv_write":
-                self.caches[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
+                self._cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
+                self.caches.append(self._cache_of[k])
             elif op == "router_topk":
                 E = int(i["attrs"]["experts"])
                 raw = self.arena.lease(k, T * w * 8 + T * E * 4)           # ids | weights | logits, one slot
@@ -358,6 +414,8 @@ class PlanEngine:
                 self.vals[k] = self.next_ids
             else:
                 self.vals[k] = view(k, (T, w), f32 if i["dtype"] == "f32" else BF16)
+        head = next((i for i in self.ins if i["op"] == "lm_head"), None)
+        self.x = self.vals[head["inputs"][0]] if head is not None else None      # the final hidden rows (before the last norm)
         # kernel scratch comes out of the frozen workspace: the attention splits and the argmax partials never live at once
         self.scratch = self.arena.workspace(T * max_heads * self.max_splits * (512 + 2) * 4).view(f32)
         self.partial = self.arena.workspace(self._partial_floats * 4).view(f32)
@@ -395,7 +453,7 @@ class PlanEngine:
                 g = self.head_groups[k]
                 hl = int(a["heads"]) // self.world
                 K.mla_head_decode(val(g["qkv"]), self._param(g["q_norm"]), self._param(g["kv_norm"]), self._param(g["w_qb"]),
-                                  self._param(g["w_kvb"]).view(hl, g["nope"] + g["vdim"], 512), self.caches[g["cache"]], pos, slot,
+                                  self._param(g["w_kvb"]).view(hl, g["nope"] + g["vdim"], 512), self._cache_of[g["cache"]], pos, slot,
                                   self.page_table, q_lora=g["q_lora"], nope=g["nope"], scale=g["scale"], eps=g["eps"], theta=g["theta"],
                                   window=g["window"], out=val(k), status_ptr=st)
             elif moe and k in self.moe_groups:
@@ -429,7 +487,7 @@ class PlanEngine:
                 if kr.data_ptr() != lat.data_ptr() + lat.shape[1] * 2 or kr.stride(0) != lat.stride(0):
                     raise NotImplementedError("latent and rope columns must be adjacent slices of one projection")
                 kv = torch.as_strided(lat, (T, lat.shape[1] + kr.shape[1]), (lat.stride(0), 1))
-                K.mla_kv_write(kv, self._param(a["weight"]), pos, slot, self.page_table, self.caches[k], latent=lat.shape[1],
+                K.mla_kv_write(kv, self._param(a["weight"]), pos, slot, self.page_table, self._cache_of[k], latent=lat.shape[1],
                                rope=kr.shape[1], eps=float(a["eps"]), theta=float(a["theta"]), status_ptr=st)
                 V[k] = k
             elif op == "mla_q_absorb":
@@ -441,22 +499,28 @@ class PlanEngine:
                 H, latent, vdim = int(a["heads"]), int(a["latent"]), int(a["value"])
                 nope = int(a.get("nope", vdim))
                 w = self._param(a["weight"]).view(H // self.world, nope + vdim, latent)
-                cache = self.caches[V[ins[1]]]
+                cache = self._cache_of[V[ins[1]]]
                 K.mla_decode_attention(val(ins[0]), cache, pos, slot, self.page_table, w, nope=nope,
                                        scale=1.0 / math.sqrt(float(a["scale_dim"])), window=int(a["window"]),
                                        keys_per_split=self.kps, max_splits=self.max_splits, scratch=self.scratch,
                                        out=val(k), status_ptr=st)
             elif op == "router_topk":
                 ids, wts, logits = V[k]
+                # when the expert kernels read the same rows under the same norm, the router leaves the normalised rows in the
+                # workspace and they skip their own RMSNorm prologue
+                shares = k in self._router_shares_norm
                 K.router_topk(val(ins[0]), self._param(a["weight"]), int(a["topk"]), norm_w=norm_w, eps=eps,
                               scoring=a["scoring"], scale=float(a["scale"]), renorm=a.get("renorm", "true") != "false",
                               bias=self._param(a["weight"] + ".e_score_correction_bias", True), ticket_ptr=fab.ticket_ptr,
-                              logits=logits[:T], ids=ids[:T], wts=wts[:T])
+                              logits=logits[:T], ids=ids[:T], wts=wts[:T], xn=self.xn[:T] if shares else None)
             elif op == "moe_gate_up":
                 ids = V[ins[1]][0][:T]
                 wgu = self._param(a["weight"] + "|" + a["paired_weight"])
                 sh = self._param(a["shared_weight"] + "|" + a["shared_paired_weight"]) if "shared_weight" in a else None
-                K.moe_gate_up(val(ins[0]), ids, wgu, self.rank * wgu.shape[0], norm_w=norm_w, eps=eps, w_shared_gu=sh, act=V[k][:T])
+                if ins[1] in self._router_shares_norm:
+                    K.moe_gate_up(self.xn[:T], ids, wgu, self.rank * wgu.shape[0], w_shared_gu=sh, act=V[k][:T])
+                else:
+                    K.moe_gate_up(val(ins[0]), ids, wgu, self.rank * wgu.shape[0], norm_w=norm_w, eps=eps, w_shared_gu=sh, act=V[k][:T])
             elif op == "moe_down_allreduce":
                 ids, wts, _ = V[ins[1]]
                 wd = self._param(a["weight"])
@@ -474,5 +538,5 @@ class PlanEngine:
         return self.next_ids[:T]
 
     def reset(self) -> None:
-        for c in self.caches.values():
+        for c in self.caches:
             c.zero_()

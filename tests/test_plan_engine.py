@@ -94,3 +94,62 @@ def test_arena_is_enforced(tmp_path):
     with pytest.raises(ValueError, match="another program"):
         FrozenArena(small, 0, 1, "cuda")
     fab.close()
+
+
+@pytest.mark.parametrize("fused_head,fused_moe", [(None, None), (False, False), (True, True)])
+def test_bundle_engine_equals_the_hand_wired_decoder(tmp_path, fused_head, fused_moe):
+    """The generated source, compiled, run by the plan engine on adopted weights: bit-identical logits and tokens to the
+    decoder class that wires the same kernels by hand, for every dispatcher choice; the prompt executor and the single-sequence
+    engine run on the bundle's engine through its decoder attributes."""
+    from ironpangu_b200 import compiler
+    from ironpangu_b200.compiler.sources import mla_moe_source
+    from ironpangu_b200.models.mla_moe import MlaMoeConfig, MlaMoeDecoder, bundle_parameters, random_rank_weights
+    from ironpangu_b200.models.mla_moe_prefill import MlaMoePrefill
+    from ironpangu_b200.parallel.fabric import Fabric
+    from ironpangu_b200.runtime.engine import DecodeEngine
+    from ironpangu_b200.runtime.plan_engine import PlanEngine
+
+    cfg = MlaMoeConfig.tiny(layers=3)
+    dev = torch.device("cuda", 0)
+    weights = random_rank_weights(cfg, 0, 1, dev, seed=5)
+    src = tmp_path / "m.inferfabric"
+    src.write_text(mla_moe_source(cfg, 1, context=256))
+    out = compiler.write_bundle(str(src), str(tmp_path / "b"), prefill_tokens=8)
+    fab = Fabric(0, 1)
+    eng = PlanEngine(out["dir"], None, fab, max_tokens=8, keep_logits=True, parameters=bundle_parameters(cfg, weights),
+                     fused_head=fused_head, fused_moe=fused_moe)
+    ref = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=256, keep_logits=True, fused_head=fused_head, fused_moe=fused_moe)
+    assert eng.cfg == cfg and eng.hl == ref.hl and eng.el == ref.el and len(eng.caches) == cfg.layers
+    assert eng.launches_per_forward == ref.launches_per_forward
+    assert eng.fused_head == ref.fused_head and eng.fused_moe == ref.fused_moe
+    g = torch.Generator().manual_seed(11)
+    seq = torch.randint(0, cfg.vocab, (40,), generator=g).to(torch.int32)
+    for width in (8, 1, 2):
+        eng.reset(); ref.reset()
+        for s in range(0, len(seq), width):
+            n = min(width, len(seq) - s)
+            for d in (eng, ref):
+                d.tokens[:n].copy_(seq[s:s + n])
+                d.positions[:n].copy_(torch.arange(s, s + n, dtype=torch.int32))
+                d.slots[:n].zero_()
+                d.forward(n)
+            assert torch.equal(eng.logits[:n], ref.logits[:n]), (width, s)
+            assert torch.equal(eng.next_ids[:n], ref.next_ids[:n])
+        for a, b in zip(eng.caches, ref.caches):
+            assert torch.equal(a, b)
+    # prompt executor + single-sequence engine over the bundle's engine
+    eng.reset(); ref.reset()
+    prompt = seq[:33].tolist()
+    got = DecodeEngine(eng, prefill=MlaMoePrefill(eng, max_rows=32)).generate(prompt, 6)
+    want = DecodeEngine(ref, prefill=MlaMoePrefill(ref, max_rows=32)).generate(prompt, 6)
+    assert got == want
+    # a parameter with the wrong shape, or a missing one, is refused before anything runs
+    bad = dict(bundle_parameters(cfg, weights))
+    bad["lm_head"] = bad["lm_head"][:-1]
+    with pytest.raises(ValueError, match="lm_head"):
+        PlanEngine(out["dir"], None, fab, parameters=bad)
+    del bad["lm_head"]
+    with pytest.raises(KeyError, match="lm_head"):
+        PlanEngine(out["dir"], None, fab, parameters=bad)
+    assert fab.status() == 0
+    fab.close()
