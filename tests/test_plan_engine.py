@@ -119,7 +119,8 @@ def test_bundle_engine_equals_the_hand_wired_decoder(tmp_path, fused_head, fused
     eng = PlanEngine(out["dir"], None, fab, max_tokens=8, keep_logits=True, parameters=bundle_parameters(cfg, weights),
                      fused_head=fused_head, fused_moe=fused_moe)
     ref = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=256, keep_logits=True, fused_head=fused_head, fused_moe=fused_moe)
-    assert eng.cfg == cfg and eng.hl == ref.hl and eng.el == ref.el and len(eng.caches) == cfg.layers
+    import dataclasses
+    assert eng.cfg == dataclasses.replace(cfg, eos=2) and eng.hl == ref.hl and eng.el == ref.el and len(eng.caches) == cfg.layers
     assert eng.launches_per_forward == ref.launches_per_forward
     assert eng.fused_head == ref.fused_head and eng.fused_moe == ref.fused_moe
     g = torch.Generator().manual_seed(11)
