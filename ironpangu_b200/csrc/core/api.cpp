@@ -34,6 +34,7 @@ void send_error(http::ResponseWriter& w, const Error& e) {
   switch (e.kind()) {
     case ErrorKind::Invalid: w.send(400, "application/json", error_body(e.what(), "invalid_request_error", 400).dump()); break;
     case ErrorKind::Capacity: w.send(429, "application/json", error_body(e.what(), "overloaded", 429).dump()); break;
+    case ErrorKind::NotImplemented: w.send(501, "application/json", error_body(e.what(), "unsupported", 501).dump()); break;
     case ErrorKind::Backend: w.send(503, "application/json", error_body(e.what(), "unavailable", 503).dump()); break;
     default: w.send(500, "application/json", error_body(e.what(), "internal_error", 500).dump()); break;
   }
@@ -113,6 +114,7 @@ void Api::completions(const http::Request& req, http::ResponseWriter& w, bool ch
     if (const Json* s = body.find("stream"); s && !s->is_null()) stream = s->as_bool();
     if (const Json* m = body.find("model"); m && m->is_string()) model = m->as_string();
     gen.prompt = prompt_of(body, chat);
+    serve::SamplingParams::refuse_unsupported(body);
     gen.sampling = serve::SamplingParams::from_json(body, defaults_);
     if (const Json* r = body.find("request_id"); r && r->is_string()) gen.request_id = r->as_string();
   } catch (const Error& e) {
@@ -245,6 +247,7 @@ void Api::generate_tokens(const http::Request& req, http::ResponseWriter& w) {
       gen.prompt.push_back((uint32_t)t.as_int());
     }
     const Json* sp = body.find("sampling_params");
+    serve::SamplingParams::refuse_unsupported(body);
     gen.sampling = sp && !sp->is_null() ? serve::SamplingParams::from_json(*sp, defaults_) : defaults_;
     if (const Json* s = body.find("stream"); s && !s->is_null()) stream = s->as_bool();
     if (const Json* r = body.find("request_id"); r && r->is_string()) gen.request_id = r->as_string();

@@ -1,5 +1,7 @@
 #include "serve.h"
 
+#include <sys/stat.h>
+
 #include <poll.h>
 #include <sys/socket.h>
 #include <sys/wait.h>
@@ -75,6 +77,53 @@ SamplingParams SamplingParams::from_json(const Json& j, const SamplingParams& d)
     for (auto& t : v->as_array()) s.stop_token_ids.push_back((uint32_t)t.as_int());
   if (const Json* v = j.find("logprobs"); v && !v->is_null()) s.logprobs = v->is_bool() ? (v->as_bool() ? 1 : -1) : (int32_t)v->as_int();
   return s;
+}
+
+SamplingParams SamplingParams::model_card() {
+  SamplingParams s;
+  s.temperature = 1.0;
+  s.top_k = 20;
+  s.presence_penalty = 2.0;
+  return s;
+}
+
+SamplingParams SamplingParams::deployment_defaults(const std::string& dir_or_file) {
+  SamplingParams s = model_card();
+  std::string path = dir_or_file;
+  struct stat st {};
+  if (!path.empty() && ::stat(path.c_str(), &st) == 0 && S_ISDIR(st.st_mode)) path += "/generation_config.json";
+  if (!path.empty() && ::stat(path.c_str(), &st) == 0) {
+    const Json cfg = Json::parse(read_file(path, 1 << 20));
+    if (!cfg.is_object()) invalid("generation config: " + path + " is not a JSON object");
+    Json only = Json::object();
+    for (const char* key : {"temperature", "top_k", "top_p", "min_p", "presence_penalty", "frequency_penalty", "repetition_penalty"})
+      if (const Json* v = cfg.find(key); v && !v->is_null()) only.set(key, *v);
+    const uint32_t keep = s.max_tokens;
+    s = from_json(only, s);
+    s.max_tokens = keep;
+  } else if (!dir_or_file.empty() && ::stat(dir_or_file.c_str(), &st) != 0) {
+    invalid("generation config: " + dir_or_file + " does not exist");
+  }
+  s.validate();
+  return s;
+}
+
+void SamplingParams::refuse_unsupported(const Json& request) {
+  static const char* const kUnsupported[] = {"logit_bias", "allowed_token_ids", "bad_words", "bad_words_token_ids", "structured_outputs",
+                                             "guided_json", "guided_regex", "guided_choice", "guided_grammar", "response_format",
+                                             "prompt_logprobs", "logprob_token_ids", "repetition_detection", "thinking_token_budget",
+                                             "lora_request", "mm_features", "data_parallel_rank", "best_of", "use_beam_search"};
+  auto scan = [](const Json& o) {
+    if (!o.is_object()) return;
+    for (const char* key : kUnsupported)
+      if (const Json* v = o.find(key); v && !v->is_null())
+        fail(ErrorKind::NotImplemented, std::string("sampling: '") + key + "' is not supported by this engine (supported: temperature, top_k, "
+             "top_p, min_p, seed, repetition / presence / frequency penalties, min_tokens, stop_token_ids)");
+  };
+  scan(request);
+  if (const Json* sp = request.find("sampling_params")) scan(*sp);
+  if (const Json* n = request.find("n"); n && !n->is_null() && n->as_int() != 1) fail(ErrorKind::NotImplemented, "sampling: n != 1 is not supported");
+  if (const Json* p = request.find("priority"); p && !p->is_null() && p->as_int() != 0) fail(ErrorKind::NotImplemented, "sampling: priority is not supported");
 }
 
 Json EngineInfo::to_json() const {

@@ -35,6 +35,14 @@ struct SamplingParams {
   void validate() const;             // throws Invalid
   Json to_json() const;
   static SamplingParams from_json(const Json& j, const SamplingParams& defaults);
+  // Defaults of a deployment: the model-card recommendation (temperature 1, top-k 20, presence penalty 2, the rest neutral),
+  // then every sampling key of `generation_config.json` in `dir_or_file` that is present and not null, then validation.
+  // Reference: frontend/src/native_sampling.rs:16-39.
+  static SamplingParams model_card();
+  static SamplingParams deployment_defaults(const std::string& dir_or_file);
+  // Request fields this engine does not implement (logit_bias, allowed_token_ids, structured outputs, prompt_logprobs ...):
+  // a request carrying one is refused instead of being served without it. Reference: native_sampling.rs:44-67.
+  static void refuse_unsupported(const Json& request);
 };
 
 struct EngineInfo {

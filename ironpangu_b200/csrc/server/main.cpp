@@ -8,7 +8,8 @@
 //   ifab-server --program BUNDLE CHECKPOINT --cpu     run the bundle on the host with the CPU interpreter (no device needed)
 // Options: --port P (0 = pick one, printed), --max-num-seqs N, --max-num-batched-tokens B, --max-model-len C,
 //          --vocab V, --max-queue Q, --stream-capacity S, --step-micros U (mock), --accept-seconds S, --temperature T,
-//          --top-k K, --presence-penalty X (server-side sampling defaults).
+//          --top-k K, --presence-penalty X (server-side sampling defaults), --sampling-defaults model-card|DIR|FILE (the
+//          model-card recommendation, overridden by DIR/generation_config.json).
 // Prints "listening on 127.0.0.1:PORT" once ready; SIGINT / SIGTERM drain and exit.
 // Reference: frontend/src/main.rs (modes --mock / --program / --native), frontend/src/shutdown.rs.
 #include <signal.h>
@@ -76,6 +77,11 @@ Args parse(int argc, char** argv) {
     else if (f == "--stream-capacity") a.opt.stream_capacity = (uint32_t)std::atoi(need(i));
     else if (f == "--step-micros") a.step_micros = (uint32_t)std::atoi(need(i));
     else if (f == "--accept-seconds") a.accept_seconds = std::atof(need(i));
+    else if (f == "--sampling-defaults") {
+      // "model-card": temperature 1, top-k 20, presence penalty 2; a directory or file: those, overridden by its generation_config.json
+      const std::string v = need(i);
+      a.defaults = v == "model-card" ? serve::SamplingParams::model_card() : serve::SamplingParams::deployment_defaults(v);
+    }
     else if (f == "--temperature") a.defaults.temperature = std::atof(need(i));
     else if (f == "--top-k") a.defaults.top_k = std::atoi(need(i));
     else if (f == "--presence-penalty") a.defaults.presence_penalty = std::atof(need(i));

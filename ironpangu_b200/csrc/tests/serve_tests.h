@@ -204,4 +204,20 @@ static void test_api_tokenizer_and_sampling_json() {
   CHECK_THROWS(Invalid, serve::SamplingParams::from_json(Json::parse("{\"top_p\":0}"), d).validate());
   CHECK_THROWS(Invalid, serve::SamplingParams::from_json(Json::parse("{\"max_tokens\":0}"), d));
   CHECK_THROWS(Invalid, serve::SamplingParams::from_json(Json::parse("{\"temperature\":\"hot\"}"), d));
+  // deployment defaults: the model-card recommendation, then the checkpoint's generation_config.json (null keys keep the default)
+  const auto card = serve::SamplingParams::model_card();
+  CHECK(card.temperature == 1.0 && card.top_k == 20 && card.top_p == 1.0 && card.presence_penalty == 2.0 && card.repetition_penalty == 1.0);
+  char tmpl[] = "/tmp/ifab-gencfg-XXXXXX";
+  const std::string dir = ::mkdtemp(tmpl);
+  CHECK(serve::SamplingParams::deployment_defaults(dir).top_k == 20);                       // no file in the directory: the card
+  write_file(dir + "/generation_config.json", "{\"temperature\":0.7,\"top_k\":null,\"top_p\":0.8,\"presence_penalty\":0,\"eos_token_id\":7,\"max_tokens\":999}");
+  const auto dep = serve::SamplingParams::deployment_defaults(dir);
+  CHECK(dep.temperature == 0.7 && dep.top_k == 20 && dep.top_p == 0.8 && dep.presence_penalty == 0.0 && dep.max_tokens == card.max_tokens);
+  write_file(dir + "/generation_config.json", "{\"top_p\":0}");
+  CHECK_THROWS(Invalid, serve::SamplingParams::deployment_defaults(dir));                   // defaults are validated like requests
+  CHECK_THROWS(Invalid, serve::SamplingParams::deployment_defaults(dir + "/nothing-here"));
+  // fields the engine does not implement are refused, at the top level and inside sampling_params
+  CHECK_THROWS(NotImplemented, serve::SamplingParams::refuse_unsupported(Json::parse("{\"prompt\":\"x\",\"logit_bias\":{\"5\":1}}")));
+  CHECK_THROWS(NotImplemented, serve::SamplingParams::refuse_unsupported(Json::parse("{\"token_ids\":[1],\"sampling_params\":{\"allowed_token_ids\":[1]}}")));
+  serve::SamplingParams::refuse_unsupported(Json::parse("{\"prompt\":\"x\",\"logit_bias\":null,\"temperature\":0.2}"));
 }

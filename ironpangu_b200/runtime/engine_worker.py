@@ -424,9 +424,28 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
         cfg.layers = args.layers
     weights = random_rank_weights(cfg, rank, world, dev, seed=args.seed)
     mark("weights")
-    dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs,
-                        keep_logits=not args.greedy_only, kv_int8=args.kv_int8, expert_fp8=args.expert_fp8,
-                        fused_head=ro.fused_head if ro is not None else None)
+    if args.executor == "bundle" and not (args.kv_int8 or args.expert_fp8):
+        # the model's .inferfabric source, compiled for this job's width; the plan engine's dispatcher picks the kernels, the
+        # activations live in the bundle's frozen arena (the quantised layouts are not in the language yet: hand-wired class)
+        import tempfile
+
+        from ironpangu_b200 import compiler
+        from ironpangu_b200.compiler.sources import mla_moe_source
+        from ironpangu_b200.models.mla_moe import bundle_parameters
+        from ironpangu_b200.runtime.plan_engine import PlanEngine
+
+        work = tempfile.mkdtemp(prefix=f"ifab-worker-r{rank}-")
+        src = os.path.join(work, "model.inferfabric")
+        with open(src, "w") as f:
+            f.write(mla_moe_source(cfg, world, context=args.max_model_len))
+        compiled = compiler.write_bundle(src, os.path.join(work, "bundle"), prefill_tokens=8)
+        dec = PlanEngine(compiled["dir"], None, fab, max_tokens=8, num_slots=args.max_num_seqs, keep_logits=not args.greedy_only,
+                         parameters=bundle_parameters(cfg, weights), fused_head=ro.fused_head if ro is not None else None)
+        mark("bundle", f"program {compiled['program_sha256'][:16]}, arena {dec.arena.bytes + dec.arena.workspace_bytes} bytes")
+    else:
+        dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs,
+                            keep_logits=not args.greedy_only, kv_int8=args.kv_int8, expert_fp8=args.expert_fp8,
+                            fused_head=ro.fused_head if ro is not None else None)
     mark("state", "KV cache, recurrent state and step workspace")
     prefill = None
     if args.prefill_chunk > 8 and not args.kv_int8 and not args.expert_fp8:
@@ -594,6 +613,8 @@ def main() -> None:
     ap.add_argument("--max-num-seqs", type=int, default=4)
     ap.add_argument("--max-model-len", type=int, default=256)
     ap.add_argument("--max-num-batched-tokens", type=int, default=0, help="tokens per scheduler step (0 = one launch group of 8 rows)")
+    ap.add_argument("--executor", default="bundle", choices=["bundle", "model"],
+                    help="bf16 MLA+MoE models: run the compiled bundle of the model's generated source (plan engine) or the hand-wired decoder class")
     ap.add_argument("--prefix-cache-slots", type=int, default=0, help="device snapshots kept by the prefix cache (0 = off)")
     ap.add_argument("--kv-int8", action="store_true", help="packed int8 latent KV cache")
     ap.add_argument("--expert-fp8", action="store_true", help="block-scaled fp8 expert weights (1 x 128 scale blocks)")

@@ -537,6 +537,21 @@ class PlanEngine:
                 raise NotImplementedError(f"no device kernel bound for instruction '{op}' ({i['name']})")
         return self.next_ids[:T]
 
+    def capture(self, T: Optional[int] = None, feedback: bool = False) -> torch.cuda.CUDAGraph:
+        """One step as a CUDA graph (after an eager warm-up run of the same step); with ``feedback`` the graph also feeds the
+        sampled token and position + 1 back into the input buffers."""
+        T = self.T if T is None else T
+        self.forward(T)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            if feedback:
+                self.forward_feedback(T)
+            else:
+                self.forward(T)
+        self._graph = g
+        return g
+
     def reset(self) -> None:
         for c in self.caches:
             c.zero_()

@@ -134,6 +134,11 @@ def test_errors_are_openai_errors(mock_server):
         assert st == 400 and e["error"]["type"] == "invalid_request_error" and needle in e["error"]["message"], (body, e)
     st, raw = s.request("POST", "/v1/completions", None)
     assert st == 400
+    # request fields the engine does not implement are refused (501), not silently dropped
+    for path, body in [("/v1/completions", {"prompt": "x", "logit_bias": {"5": 1.0}}),
+                       ("/inference/v1/generate", {"token_ids": [5], "sampling_params": {"allowed_token_ids": [1, 2]}})]:
+        st, e = s.post(path, body)
+        assert st == 501 and e["error"]["type"] == "unsupported", (body, e)
 
 
 def test_continuous_batching_many_clients_and_metrics(mock_server):
