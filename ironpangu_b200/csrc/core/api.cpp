@@ -118,7 +118,8 @@ void Api::completions(const http::Request& req, http::ResponseWriter& w, bool ch
     gen.sampling = serve::SamplingParams::from_json(body, defaults_);
     if (const Json* r = body.find("request_id"); r && r->is_string()) gen.request_id = r->as_string();
   } catch (const Error& e) {
-    return send_error(w, Error(ErrorKind::Invalid, e.what()));
+    // anything wrong with the request body is the client's error, except a well-formed field this engine does not implement
+    return send_error(w, Error(e.kind() == ErrorKind::NotImplemented ? ErrorKind::NotImplemented : ErrorKind::Invalid, e.what()));
   }
   const size_t prompt_tokens = gen.prompt.size();
   const std::string id = std::string(chat ? "chatcmpl-" : "cmpl-") + std::to_string(++counter_);
@@ -252,7 +253,8 @@ void Api::generate_tokens(const http::Request& req, http::ResponseWriter& w) {
     if (const Json* s = body.find("stream"); s && !s->is_null()) stream = s->as_bool();
     if (const Json* r = body.find("request_id"); r && r->is_string()) gen.request_id = r->as_string();
   } catch (const Error& e) {
-    return send_error(w, Error(ErrorKind::Invalid, e.what()));
+    // anything wrong with the request body is the client's error, except a well-formed field this engine does not implement
+    return send_error(w, Error(e.kind() == ErrorKind::NotImplemented ? ErrorKind::NotImplemented : ErrorKind::Invalid, e.what()));
   }
   if (gen.request_id.empty()) gen.request_id = "gen-" + std::to_string(++counter_);
   const std::string id = gen.request_id;
