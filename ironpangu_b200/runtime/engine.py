@@ -12,6 +12,8 @@ from typing import List, Optional
 
 import torch
 
+from .transfers import TransferAudit
+
 
 class DecodeEngine:
     def __init__(self, decoder, chunk: Optional[int] = None, prefill=None):
@@ -31,6 +33,7 @@ class DecodeEngine:
         # graph per form; the engine knows the position on the host and replays the matching one
         self._graphs = {}
         self._feedback_graphs = {}
+        self.transfers = TransferAudit()      # every host <-> device copy of this engine, by role
         self.h2d_bytes_per_step = 8
         self.d2h_bytes_per_step = 4
 
@@ -112,11 +115,13 @@ class DecodeEngine:
         """One decode step through the captured graph: H2D control inputs, replay, D2H sampled token."""
         self._ctl_host[0] = token
         self._ctl_host[1] = self.pos
-        self._ctl_dev.copy_(self._ctl_host, non_blocking=True)
+        with self.transfers.scope("control_input"):
+            self.transfers.h2d(self._ctl_dev, self._ctl_host)
         # a capture's warm-up run executes this very step (same token, same position), never a stale one
         self._graph = self._select(self._graphs, self._variant(self.pos), self._capture)
         self._graph.replay()
-        self._out_host.copy_(self.dec.next_ids[:1], non_blocking=True)
+        with self.transfers.scope("request_output"):
+            self.transfers.d2h(self._out_host, self.dec.next_ids[:1])
         torch.cuda.current_stream().synchronize()
         self.pos += 1
         return int(self._out_host[0])

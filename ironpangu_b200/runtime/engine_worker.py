@@ -31,6 +31,8 @@ from typing import Dict, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
+from .transfers import TransferAudit, prepared_execution_report, state_copy_report
+
 
 class PrefixSnapshots:
     """LRU of device snapshots keyed by token prefixes (multiples of ``block`` tokens). A snapshot is the KV rows of every
@@ -107,6 +109,8 @@ class BatchEngine:
             self.counts = torch.zeros(R, vl, dtype=torch.int16, device=dev)
             self.vocab_offset = decoder.rank * vl
         self.prefix = PrefixSnapshots(prefix_slots, self.rows) if prefix_slots > 0 and hasattr(decoder, "caches") else None
+        self.transfers = TransferAudit()
+        self.allocations_at_ready: Optional[int] = None      # set once the engine has served its first step of every width it will see
         self.audit_counters = {"steps": 0, "launch_groups": 0, "rows": 0, "h2d_bytes": 0, "d2h_bytes": 0, "prefix_rows_copied": 0,
                                "sampled_rows": 0, "prefill_chunks": 0, "prefill_rows": 0}
 
@@ -122,6 +126,9 @@ class BatchEngine:
             a.update({"prefix_hits": self.prefix.hits, "prefix_misses": self.prefix.misses, "prefix_published": self.prefix.published,
                       "prefix_evicted": self.prefix.evicted, "prefix_entries": len(self.prefix.entries)})
         a["fabric_status"] = self.dec.fabric.status()
+        a["transfers"] = self.transfers.report()
+        a["prepared_execution"] = prepared_execution_report(self)
+        a["state_copies"] = state_copy_report(self)
         opts = getattr(self, "runtime_options", None)
         if opts is not None:
             a["runtime_options"] = opts.to_dict()
@@ -168,6 +175,7 @@ class BatchEngine:
 
     def _snapshot(self, resident: int, n: int) -> List[torch.Tensor]:
         rows = self._kv_rows(resident, 0, n)
+        self.audit_counters["prefix_rows_published"] = self.audit_counters.get("prefix_rows_published", 0) + n * len(self.dec.caches)
         return [c.view(-1, c.shape[-1])[rows].clone() for c in self.dec.caches]
 
     def _restore(self, resident: int, snap: List[torch.Tensor], lo: int, hi: int) -> None:
@@ -217,7 +225,8 @@ class BatchEngine:
             for c0 in range(0, len(toks), self.prefill.M):
                 chunk = toks[c0:c0 + self.prefill.M]
                 host = torch.tensor(chunk, dtype=torch.int32).pin_memory()
-                dev_toks = host.to(d.tokens.device, non_blocking=True)
+                with self.transfers.scope("control_input"):
+                    dev_toks = self.transfers.upload(host, d.tokens.device)
                 self.prefill.forward(dev_toks, position + c0, resident)
                 if self.can_sample:
                     local = dev_toks.long() - self.vocab_offset
@@ -244,9 +253,10 @@ class BatchEngine:
                 torch.cuda.current_stream().synchronize()     # more groups than control blocks: drain before reuse
             for j, (tok, pos, slot, _) in enumerate(part):
                 hb[0, j], hb[1, j], hb[2, j] = tok, pos, slot
-            d.tokens[:n].copy_(hb[0, :n], non_blocking=True)
-            d.positions[:n].copy_(hb[1, :n], non_blocking=True)
-            d.slots[:n].copy_(hb[2, :n], non_blocking=True)
+            with self.transfers.scope("control_input") as tr:
+                tr.h2d(d.tokens[:n], hb[0, :n])
+                tr.h2d(d.positions[:n], hb[1, :n])
+                tr.h2d(d.slots[:n], hb[2, :n])
             self._run_group(n)
             pending += self._emit(part, n)
             self.audit_counters["launch_groups"] += 1
@@ -272,7 +282,8 @@ class BatchEngine:
 
         d, n = self.dec, len(part)
         host = torch.tensor([[r[0] for r in part], [r[1] for r in part], [r[2] for r in part]], dtype=torch.int32).pin_memory()
-        dev = host.to(d.tokens.device, non_blocking=True)
+        with self.transfers.scope("control_input"):
+            dev = self.transfers.upload(host, d.tokens.device)
         pick = [j for j, r in enumerate(part) if r[3] >= 0]
         sel = torch.tensor(pick or [n - 1], device=dev.device)
         logits = self.prefill.forward_rows(dev[0], dev[1], dev[2], sel)
@@ -367,7 +378,8 @@ class BatchEngine:
         if dev.numel() > self._out.numel():
             self._out = torch.zeros(dev.numel(), dtype=torch.int32).pin_memory()
         host = self._out[:dev.numel()]
-        host.copy_(dev, non_blocking=True)
+        with self.transfers.scope("request_output"):
+            self.transfers.d2h(host, dev)
         torch.cuda.current_stream().synchronize()
         k = 0
         for slice_ids, ids in pending:
