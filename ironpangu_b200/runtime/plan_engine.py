@@ -62,8 +62,22 @@ class SafetensorsDir:
         return np.frombuffer(mm, dtype=np.uint8, count=len(mm) - offset, offset=offset)
 
 
-def load_parameters(init_plan: dict, ckpt: SafetensorsDir, device) -> Dict[str, torch.Tensor]:
-    """Execute one rank's initialization plan: returns ``{parameter name: device tensor}``."""
+def load_parameters(init_plan: dict, ckpt: SafetensorsDir, device, *, staging_bytes: int = 64 << 20, transfers=None) -> Dict[str, torch.Tensor]:
+    """Execute one rank's initialization plan: returns ``{parameter name: device tensor}``.
+
+    Bytes travel through ONE staging buffer of ``staging_bytes`` (pinned when the destination is a GPU), so loading a shard of
+    any size costs a bounded amount of host memory; strided loads (column shards) are gathered row block by row block into
+    the same buffer. Every upload is recorded under the ``parameter_preparation`` role of ``transfers`` (a
+    ``runtime.transfers.TransferAudit``) when one is given.
+    Reference: bounded staging + verify of the native init executor (crates/inferfabric-native/src/initialization.rs)."""
+    from .transfers import TransferAudit
+
+    tr = transfers if transfers is not None else TransferAudit()
+    on_gpu = torch.device(device).type == "cuda"
+    stage = torch.empty(max(4096, int(staging_bytes)), dtype=torch.uint8)
+    if on_gpu:
+        stage = stage.pin_memory()
+    stage_np = stage.numpy()
     params, cursors, raw = {}, {}, {}
     for p in init_plan["parameters"]:
         dt, eb = _DT[p["dtype"]]
@@ -71,28 +85,47 @@ def load_parameters(init_plan: dict, ckpt: SafetensorsDir, device) -> Dict[str, 
         raw[p["id"]] = torch.empty(n, dtype=torch.uint8, device=device)
         cursors[p["id"]] = 0
     meta = {p["id"]: p for p in init_plan["parameters"]}
+
+    def upload(dest: int, nbytes: int, widen: bool) -> None:
+        """``stage[:nbytes]`` -> the next bytes of parameter ``dest`` (bf16 -> f32 widening on the device when asked)."""
+        c = cursors[dest]
+        with tr.scope("parameter_preparation"):
+            if widen:
+                tmp = tr.upload(stage[:nbytes], device, non_blocking=False)
+                raw[dest][c:c + 2 * nbytes].copy_(tmp.view(torch.bfloat16).to(torch.float32).view(torch.uint8))
+                cursors[dest] = c + 2 * nbytes
+            else:
+                tr.h2d(raw[dest][c:c + nbytes], stage[:nbytes], non_blocking=False)     # the buffer is reused at once
+                cursors[dest] = c + nbytes
+
     for l in init_plan["loads"]:
         # a load names the shard FILE and an absolute offset inside it (the safetensors header included)
         src = ckpt.shard_from(l["shard"], l["offset"])
+        dst_dt = meta[l["dest"]]["dtype"]
+        widen = l["src_dtype"] == "bf16" and dst_dt == "f32"
+        if not widen and l["src_dtype"] != dst_dt:
+            raise ValueError(f"no conversion {l['src_dtype']} -> {dst_dt} for {l.get('tensor', l['shard'])}")
         if l["kind"] == "slice":
             if l["bytes"] > src.size:
                 raise ValueError(f"load of {l.get('tensor', l['shard'])} runs past the end of {l['shard']}")
-            chunk = src[:l["bytes"]]
+            step = stage.numel() // 4 * 4
+            for b in range(0, l["bytes"], step):
+                n = min(step, l["bytes"] - b)
+                stage_np[:n] = src[b:b + n]
+                upload(l["dest"], n, widen)
         else:
-            rows = l["bytes"] // l["row_bytes"]
-            if (rows - 1) * l["stride_bytes"] + l["row_bytes"] > src.size:
+            rb, sb = l["row_bytes"], l["stride_bytes"]
+            rows = l["bytes"] // rb
+            if (rows - 1) * sb + rb > src.size:
                 raise ValueError(f"strided load of {l.get('tensor', l['shard'])} runs past the end of {l['shard']}")
-            view = np.lib.stride_tricks.as_strided(src, shape=(rows, l["row_bytes"]), strides=(l["stride_bytes"], 1))
-            chunk = np.ascontiguousarray(view).reshape(-1)
-        t = torch.from_numpy(np.array(chunk, copy=True))
-        dst_dt = meta[l["dest"]]["dtype"]
-        if l["src_dtype"] == "bf16" and dst_dt == "f32":
-            t = t.view(torch.bfloat16).to(torch.float32).view(torch.uint8)
-        elif l["src_dtype"] != dst_dt:
-            raise ValueError(f"no conversion {l['src_dtype']} -> {dst_dt} for {l.get('tensor', l['shard'])}")
-        c = cursors[l["dest"]]
-        raw[l["dest"]][c:c + t.numel()].copy_(t, non_blocking=False)
-        cursors[l["dest"]] = c + t.numel()
+            if rb > stage.numel():
+                raise ValueError(f"a row of {l.get('tensor', l['shard'])} ({rb} bytes) does not fit the staging buffer")
+            per = max(1, stage.numel() // rb)
+            for r0 in range(0, rows, per):
+                nr = min(per, rows - r0)
+                view = np.lib.stride_tricks.as_strided(src[r0 * sb:], shape=(nr, rb), strides=(sb, 1))
+                stage_np[:nr * rb].reshape(nr, rb)[:] = view
+                upload(l["dest"], nr * rb, widen)
     for pid, p in meta.items():
         if cursors[pid] != raw[pid].numel():
             raise ValueError(f"parameter {p['name']} was filled with {cursors[pid]} of {raw[pid].numel()} bytes")

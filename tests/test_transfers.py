@@ -55,3 +55,37 @@ def test_engine_reports_have_their_formats():
     s = state_copy_report(Eng())
     assert s == {"format": "ifab.state-copy-audit.v1", "host_bytes": 0, "rows_restored": 64, "rows_published": 32, "snapshots": 1,
                  "hits": 3, "misses": 2, "evicted": 1}
+
+
+def test_init_plan_loader_stages_through_a_bounded_buffer(tmp_path):
+    """Row shards, strided column shards and expert stacks of a two-rank plan: the same bytes whatever the staging size, every
+    upload recorded as parameter preparation, a column shard equal to the slice of the checkpoint tensor."""
+    import json
+
+    from ironpangu_b200 import compiler
+    from ironpangu_b200.compiler.sources import mla_moe_source
+    from ironpangu_b200.models.mla_moe import MlaMoeConfig
+    from ironpangu_b200.runtime.plan_engine import SafetensorsDir, load_parameters
+
+    cfg = MlaMoeConfig.tiny(layers=1)
+    src = tmp_path / "m.inferfabric"
+    src.write_text(mla_moe_source(cfg, 2, context=64))
+    assert compiler.cli("synth-checkpoint", str(src), str(tmp_path / "ck"), "--seed", "1").returncode == 0
+    out = compiler.write_bundle(str(src), str(tmp_path / "b"), checkpoint_dir=str(tmp_path / "ck"))
+    ck = SafetensorsDir(str(tmp_path / "ck"))
+    for rank in (0, 1):
+        plan = json.loads((tmp_path / "b" / f"rank-{rank}.init.json").read_text())
+        assert any(l["kind"] != "slice" for l in plan["loads"])          # the o_proj / down column shards are strided
+        big = load_parameters(plan, ck, "cpu")
+        tr = TransferAudit()
+        small = load_parameters(plan, ck, "cpu", staging_bytes=4096, transfers=tr)
+        total = sum(t.numel() * t.element_size() for t in big.values())
+        assert set(big) == set(small) and all(torch.equal(big[k].view(torch.uint8), small[k].view(torch.uint8)) for k in big)
+        b = {x["role"]: x for x in tr.report()["boundaries"]}["parameter_preparation"]
+        assert b["h2d_calls"] > len(plan["loads"]) and b["d2h_calls"] == 0 and tr.rejected == 0
+        assert b["h2d_bytes"] <= total
+        mm, off, n, dtype, shape = ck.tensors["model.layers.0.self_attn.o_proj.weight"]
+        full = torch.frombuffer(bytearray(mm[off:off + n]), dtype=torch.bfloat16).view(*shape)
+        half = shape[1] // 2
+        assert torch.equal(big["model.layers.0.self_attn.o_proj"], full[:, rank * half:(rank + 1) * half])
+    assert out["instructions"] > 0
