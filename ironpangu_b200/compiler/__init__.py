@@ -61,11 +61,12 @@ def write_bundle(source_path: str, out_dir: str, checkpoint_dir: Optional[str] =
 
 
 def interpret(source: str, checkpoint_dir: str, tokens: List[int], steps: int = 0, logits: bool = False,
-              all_logits: bool = False) -> Dict[str, Any]:
+              all_logits: bool = False, watch: Optional[List[str]] = None) -> Dict[str, Any]:
     """Run the CPU oracle: feed ``tokens`` then decode ``steps`` greedy tokens. ``all_logits`` also returns the
-    f32 logits after every fed token (``prompt_logits``)."""
+    f32 logits after every fed token (``prompt_logits``); ``watch`` names graph nodes whose values are returned after every
+    fed token (``watched``: one ``{name: value}`` object per token)."""
     return _call("ifab_core_interpret", source, str(checkpoint_dir),
-                 json.dumps({"tokens": tokens, "steps": steps, "logits": logits, "all_logits": all_logits}))
+                 json.dumps({"tokens": tokens, "steps": steps, "logits": logits, "all_logits": all_logits, "watch": watch or []}))
 
 
 def read_init_plan(path: str) -> Dict[str, Any]:

@@ -108,9 +108,19 @@ char* ifab_core_interpret(const char* source, const char* checkpoint_dir, const 
     uint32_t next = 0;
     const bool all_logits = req.find("all_logits") && req.at("all_logits").as_bool();
     Json every = Json::array();
+    // "watch": node names whose values are reported after every fed token (`watched`: one object per token)
+    std::vector<std::string> watch;
+    if (const Json* wj = req.find("watch"))
+      for (auto& nm : wj->as_array()) watch.push_back(nm.as_string());
+    Json watched = Json::array();
     for (size_t i = 0; i < toks.size(); ++i) {
       next = it.step(toks[i], (uint32_t)i, &logits);
       pl.push((int64_t)next);
+      if (!watch.empty()) {
+        Json at = Json::object();
+        for (auto& nm : watch) at.set(nm, it.watch(nm));
+        watched.push(std::move(at));
+      }
       if (all_logits) {
         Json l = Json::array();
         for (float v : logits) l.push((double)v);
@@ -118,6 +128,7 @@ char* ifab_core_interpret(const char* source, const char* checkpoint_dir, const 
       }
     }
     if (all_logits) out.set("prompt_logits", every);
+    if (!watch.empty()) out.set("watched", watched);
     out.set("prompt_argmax", pl);
     uint32_t pos = (uint32_t)toks.size();
     for (uint32_t s = 0; s < steps; ++s) {

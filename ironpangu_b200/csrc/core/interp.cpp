@@ -10,6 +10,25 @@ namespace ifab::interp {
 using graph::Kind;
 using graph::Node;
 
+// x -> rint(x / s) * s with s = max|x| / 127 kept in half precision (one scale per row)
+static void quantize_row_int8(float* x, size_t n) {
+  float mx = 0.f;
+  for (size_t i = 0; i < n; ++i) mx = std::max(mx, std::fabs(x[i]));
+  if (mx == 0.f) return;
+  float s = mx / 127.f;
+  {  // round the scale to half precision, ties to even: 11 significant bits, or multiples of 2^-24 below 2^-14 (subnormals)
+    if (s < std::ldexp(1.f, -14)) {
+      s = std::ldexp(std::nearbyint(std::ldexp(s, 24)), -24);
+    } else {
+      int e;
+      const float m = std::frexp(s, &e);
+      s = std::ldexp(std::nearbyint(std::ldexp(m, 11)), e - 11);
+    }
+    if (s == 0.f) return;
+  }
+  for (size_t i = 0; i < n; ++i) x[i] = std::max(-127.f, std::min(127.f, std::nearbyint(x[i] / s))) * s;
+}
+
 float bf16_round(float v) {
   uint32_t u;
   memcpy(&u, &v, 4);
@@ -176,6 +195,40 @@ Interpreter::Interpreter(const graph::Graph& g, const Weights& w) : g_(g), w_(w)
   const Node& out = g.nodes[g.output];
   if (out.op == "gather" && g.nodes[out.inputs[0]].op == "linear") logits_linear_ = (int64_t)out.inputs[0];
   else if (out.op == "linear") logits_linear_ = (int64_t)g.output;
+}
+
+Json Interpreter::watch(const std::string& name) const {
+  for (size_t i = 0; i < g_.nodes.size(); ++i) {
+    if (g_.nodes[i].name != name) continue;
+    const Value& v = vals_[i];
+    Json j = Json::object();
+    if (v.cache >= 0) {
+      j.set("cache_rows", (int64_t)caches_[v.cache].rows.size());
+      if (!caches_[v.cache].rows.empty()) {
+        Json last = Json::array();
+        for (float x : caches_[v.cache].rows.back()) last.push((double)x);
+        j.set("last_row", last);
+      }
+      return j;
+    }
+    if (!v.ids.empty() || !v.wts.empty()) {
+      Json ids = Json::array(), wts = Json::array();
+      for (uint32_t x : v.ids) ids.push((int64_t)x);
+      for (float x : v.wts) wts.push((double)x);
+      j.set("ids", ids);
+      j.set("weights", wts);
+      return j;
+    }
+    Json ranks = Json::array();
+    for (const auto& r : v.r) {
+      Json row = Json::array();
+      for (float x : r) row.push((double)x);
+      ranks.push(std::move(row));
+    }
+    j.set("ranks", ranks);
+    return j;
+  }
+  invalid("watch: the graph has no node named " + name);
 }
 
 void Interpreter::reset() {
@@ -494,6 +547,37 @@ void Interpreter::run_node(uint32_t idx, uint32_t token, uint32_t position) {
     if (c.rows.size() != position) invalid(n.name + ": cache rows out of step with positions");
     c.rows.push_back(std::move(row));
     out.cache = cache_of_node_.at(idx);
+  } else if (op == "index_cache_append") {
+    // one index key per position; an int8 index cache keeps rint(x / s) * s with one scale per row (s = max|x| / 127, the
+    // scale itself held in half precision), which is what the selector later scores against
+    CacheState& c = caches_[cache_of_node_.at(idx)];
+    std::vector<float> row = as_bf16(in(0), 0);
+    if (n.has("cache_dtype") && n.need("cache_dtype") == "int8") quantize_row_int8(row.data(), row.size());
+    if (c.rows.size() != position) invalid(n.name + ": index cache rows out of step with positions");
+    c.rows.push_back(std::move(row));
+    out.cache = cache_of_node_.at(idx);
+  } else if (op == "sparse_index") {
+    // score(p) = sum_h w_h * relu(q_h . key_p) over the causal positions; the `topk` best positions (ties to the earlier
+    // one), reported in ascending order. With an int8 index cache the query heads are quantised row-wise like the keys.
+    const uint32_t H = (uint32_t)n.int_attr("heads"), D = (uint32_t)n.int_attr("head_dim"), K = (uint32_t)n.int_attr("topk");
+    std::vector<float> q = as_bf16(in(0), 0), w = as_bf16(in(1), 0);
+    const CacheState& c = caches_[in(2).cache];
+    const Node& cn = g_.nodes[n.inputs[2]];
+    if (cn.has("cache_dtype") && cn.need("cache_dtype") == "int8")
+      for (uint32_t h = 0; h < H; ++h) quantize_row_int8(&q[(size_t)h * D], D);
+    if (c.rows.size() != position + 1) invalid(n.name + ": the index cache must hold the current position before it is searched");
+    std::vector<std::pair<float, uint32_t>> scored(position + 1);
+    for (uint32_t p = 0; p <= position; ++p) {
+      float sc = 0.f;
+      for (uint32_t h = 0; h < H; ++h) sc += w[h] * std::max(0.f, dotf(&q[(size_t)h * D], c.rows[p].data(), D));
+      scored[p] = {sc, p};
+    }
+    const size_t keep = std::min<size_t>(K, scored.size());
+    std::partial_sort(scored.begin(), scored.begin() + keep, scored.end(),
+                      [](const auto& a, const auto& b) { return a.first != b.first ? a.first > b.first : a.second < b.second; });
+    out.ids.clear();
+    for (size_t i = 0; i < keep; ++i) out.ids.push_back(scored[i].second);
+    std::sort(out.ids.begin(), out.ids.end());
   } else if (op == "sink_normalize") {
     const std::string base = n.need("weight");
     const Tensor& kv = w_.need(base + ".param_sink_compressed_kv");
@@ -541,15 +625,23 @@ void Interpreter::run_node(uint32_t idx, uint32_t token, uint32_t position) {
     const uint32_t roww = c.width, rp = g_.nodes[n.inputs[1]].type.aux, lat = roww - rp;
     const float scale = 1.f / std::sqrt((float)n.int_attr("scale_dim"));
     const int64_t window = n.int_attr("window");
-    if (n.need("selection") != "all_causal_within_window") fail(ErrorKind::NotImplemented, "interpreter: learned index selection");
+    const bool learned = n.need("selection") == "learned_indices";
     const size_t lo = window > 0 && (int64_t)position + 1 > window ? position + 1 - (size_t)window : 0;
+    // learned selection: the positions the indexer chose (always causal), further limited by the window when there is one
+    std::vector<uint32_t> chosen;
+    if (learned)
+      for (uint32_t p : in(2).ids)
+        if (p >= lo && p <= position) chosen.push_back(p);
     per_rank(q.replicated, [&](uint32_t r) {
       std::vector<float> qv = as_bf16(q, r);
       const size_t hl = qv.size() / roww;
       std::vector<float> y(hl * lat);
       std::vector<const std::vector<float>*> keys;
       for (auto& s : c.sinks) keys.push_back(&s);
-      for (size_t p = lo; p <= position; ++p) keys.push_back(&c.rows[p]);
+      if (learned)
+        for (uint32_t p : chosen) keys.push_back(&c.rows[p]);
+      else
+        for (size_t p = lo; p <= position; ++p) keys.push_back(&c.rows[p]);
       std::vector<float> sc(keys.size());
       for (size_t h = 0; h < hl; ++h) {
         float mx = -INFINITY;

@@ -41,6 +41,10 @@ class Interpreter {
   uint32_t step(uint32_t token, uint32_t position, std::vector<float>* logits = nullptr);
   void reset();
   uint32_t vocab() const { return vocab_; }
+  // The value node `name` produced in the last step, as JSON: {"ranks": [[...]]} for tensors (one row when replicated),
+  // {"ids": [...], "weights": [...]} for routes and index selections, {"cache_rows": n} for caches. A probe for tests and
+  // for debugging a device kernel against the oracle (the reference's probes: crates/inferfabric-cli/src/npu_probe.rs).
+  Json watch(const std::string& name) const;
 
  private:
   struct Value {
