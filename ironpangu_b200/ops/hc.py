@@ -48,11 +48,12 @@ def mhc_post(X: torch.Tensor, branch: torch.Tensor, post: torch.Tensor, comb: to
 
 
 def delta_rule_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
-                      slots: torch.Tensor) -> torch.Tensor:
-    """One gated delta-rule step per row; ``state`` f32 ``[slots, H, dk, dv]`` is updated in place."""
+                      slots: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One gated delta-rule step per row; ``state`` f32 ``[slots, H, dk, dv]`` is updated in place. Rows of one launch must
+    belong to different sequence slots (rows of one sequence go in separate launches, in order)."""
     rows, H, dk = q.shape
     dv = v.shape[-1]
-    out = torch.empty(rows, H, dv, dtype=BF16, device=q.device)
+    out = torch.empty(rows, H, dv, dtype=BF16, device=q.device) if out is None else out
     check(_lib.load().ifab_delta_rule_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), state.data_ptr(),
                                              slots.data_ptr(), out.data_ptr(), rows, H, dk, dv, _s()), "delta_rule_decode")
     return out
