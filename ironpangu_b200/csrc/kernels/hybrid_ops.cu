@@ -10,7 +10,8 @@
 //                          state = the previous width - 1 inputs per slot and channel, oldest first; a thread owns a channel
 //                          and walks the rows in order, so rows of one sequence inside a chunk see one another
 //   delta_prepare_kernel   per (row, head): q, k L2-normalised (sum of squares rounded to bf16 before eps is added),
-//                          g = -exp(A_log) * softplus(a + dt_bias) in f32, beta = sigmoid(b) rounded to bf16
+//                          g = -exp(A_log) * softplus(a + dt_bias) in f32, beta = sigmoid(b) rounded to bf16; a row at
+//                          position 0 clears the recurrent state of its sequence slot
 //   gated_rms_kernel       y = (x * rsqrt(mean(x^2) + eps) * w) * silu(z) per head, f32 gain w (not 1 + w)
 //
 // All of them are launched with programmatic dependent launch like the rest of the decode chain. The recurrence itself is
@@ -114,13 +115,17 @@ __global__ void __launch_bounds__(256) conv_silu_kernel(const bf16* x, long ldx,
 
 // grid = ceil(T * H / 8): one warp per (row, head). conv [T, 3 * H * d] (q | k | v), ab [T, 2 * H] (a | b) bf16.
 __global__ void __launch_bounds__(256) delta_prepare_kernel(const bf16* conv, long ldc, const bf16* ab, long ldab, const float* a_log,
-                                                           const float* dt_bias, float eps, bf16* q, bf16* k, float* g, float* beta, int T, int H,
-                                                           int d) {
+                                                           const float* dt_bias, float eps, bf16* q, bf16* k, float* g, float* beta,
+                                                           const int32_t* positions, const int32_t* slots, float* state, int T, int H, int d) {
   grid_dep_launch();
   grid_dep_wait();
   const int item = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (item >= T * H) return;
   const int t = item / H, h = item % H;
+  if (state != nullptr && positions[t] == 0) {      // a new sequence starts from an empty state
+    float* S = state + ((long)slots[t] * H + h) * d * d;
+    for (int i = lane; i < d * d; i += 32) S[i] = 0.f;
+  }
   for (int which = 0; which < 2; ++which) {
     const bf16* src = conv + (long)t * ldc + ((long)which * H + h) * d;
     bf16* dst = (which == 0 ? q : k) + ((long)t * H + h) * d;
@@ -193,10 +198,11 @@ extern "C" int ifab_conv_silu(const void* x, long ldx, const void* w, void* stat
 }
 
 extern "C" int ifab_delta_prepare(const void* conv, long ldc, const void* ab, long ldab, const float* a_log, const float* dt_bias, float eps,
-                                  void* q, void* k, float* g, float* beta, int T, int H, int d, void* stream) {
-  if (T < 1 || H < 1 || d < 1) return -1;
+                                  void* q, void* k, float* g, float* beta, const int32_t* positions, const int32_t* slots, float* state, int T,
+                                  int H, int d, void* stream) {
+  if (T < 1 || H < 1 || d < 1 || (state != nullptr && (positions == nullptr || slots == nullptr))) return -1;
   return launch_chain(delta_prepare_kernel, dim3((T * H + 7) / 8), dim3(256), 0, (cudaStream_t)stream, (const bf16*)conv, ldc, (const bf16*)ab,
-                      ldab, a_log, dt_bias, eps, (bf16*)q, (bf16*)k, g, beta, T, H, d);
+                      ldab, a_log, dt_bias, eps, (bf16*)q, (bf16*)k, g, beta, positions, slots, state, T, H, d);
 }
 
 extern "C" int ifab_gated_rmsnorm(const void* x, const void* z, long ldz, const float* w, float eps, void* y, long ldy, int T, int H, int d,

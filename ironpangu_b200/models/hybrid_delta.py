@@ -210,7 +210,7 @@ class HybridDecoder:
                 proj = K.gemv(xn, L["proj"], out=self.proj_delta[:T])
                 HY.conv_silu(proj[:, :C], L["conv"], L["history"], pos, slot, out=self.conv_out[:T])
                 HY.delta_prepare(self.conv_out[:T], proj[:, C + D:], L["a_log"], L["dt_bias"], c.eps, heads=dh, dim=dd, q=self.dq[:T], k=self.dk[:T],
-                                 g=self.dg[:T], beta=self.dbeta[:T])
+                                 g=self.dg[:T], beta=self.dbeta[:T], positions=pos, slots=slot, state=L["state"])
                 for t in range(T):      # rows of one sequence must update its state in order: one launch per row
                     vt = self.conv_out[t:t + 1, 2 * D:].view(1, dh, dd)
                     HC.delta_rule_decode(self.dq[t:t + 1], self.dk[t:t + 1], vt, self.dg[t:t + 1], self.dbeta[t:t + 1], L["state"], slot[t:t + 1],

@@ -87,7 +87,7 @@ _SIGS = {
     "ifab_hybrid_qk_prepare": [_P, c_long, _P, c_long, _P, _P, c_float, _P, c_long, _P, c_long, c_int, c_int, c_int, c_int, _P],
     "ifab_sigmoid_mul": [_P, c_long, _P, c_long, _P, c_long, c_int, c_int, _P],
     "ifab_conv_silu": [_P, c_long, _P, _P, _P, _P, _P, c_long, c_int, c_int, c_int, _P],
-    "ifab_delta_prepare": [_P, c_long, _P, c_long, _P, _P, c_float, _P, _P, _P, _P, c_int, c_int, c_int, _P],
+    "ifab_delta_prepare": [_P, c_long, _P, c_long, _P, _P, c_float, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P],
     "ifab_gated_rmsnorm": [_P, _P, c_long, _P, c_float, _P, c_long, c_int, c_int, c_int, _P],
     "ifab_delta_rule_decode": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "ifab_sparse_index": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],

@@ -56,12 +56,16 @@ def conv_silu(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, positions: 
 
 
 def delta_prepare(conv: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, eps: float, *, heads: int, dim: int,
-                  q: torch.Tensor, k: torch.Tensor, g: torch.Tensor, beta: torch.Tensor) -> None:
+                  q: torch.Tensor, k: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, positions: Optional[torch.Tensor] = None,
+                  slots: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None) -> None:
     """``conv``: ``[T, 3 * heads * dim]`` (q | k | v after the convolution); ``ab``: ``[T, 2 * heads]`` (a | b). Fills L2-normalised
-    ``q``, ``k`` (bf16 ``[T, heads, dim]``), the log decay ``g`` and the write strength ``beta`` (f32 ``[T, heads]``)."""
+    ``q``, ``k`` (bf16 ``[T, heads, dim]``), the log decay ``g`` and the write strength ``beta`` (f32 ``[T, heads]``). With ``state``
+    (f32 ``[slots, heads, dim, dim]``), a row at position 0 clears the state of its slot: a new sequence starts empty."""
     T = conv.shape[0]
     check(_lib.load().ifab_delta_prepare(conv.data_ptr(), conv.stride(0), ab.data_ptr(), ab.stride(0), a_log.data_ptr(), dt_bias.data_ptr(), eps,
-                                         q.data_ptr(), k.data_ptr(), g.data_ptr(), beta.data_ptr(), T, heads, dim, _s()), "delta_prepare")
+                                         q.data_ptr(), k.data_ptr(), g.data_ptr(), beta.data_ptr(),
+                                         None if state is None else positions.data_ptr(), None if state is None else slots.data_ptr(),
+                                         None if state is None else state.data_ptr(), T, heads, dim, _s()), "delta_prepare")
 
 
 def gated_rmsnorm(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -408,6 +408,24 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
         vocab = int(eng._param(head["attrs"]["weight"]).shape[0]) * world
         return BatchEngine(eng, os.path.basename(os.path.normpath(args.bundle)), min(args.max_model_len, eng.max_context), vocab,
                            greedy_only=True)
+    if args.model.startswith("hybrid"):
+        # gated delta-rule + gated full-attention family (one GPU): K / V pages, f32 delta state and conv history per sequence slot
+        from ironpangu_b200.models import hybrid_delta as H
+
+        if world != 1:
+            raise SystemExit("the hybrid decoder runs on one GPU")
+        hcfg = H.HybridConfig.tiny(args.layers or 1) if args.model == "hybrid-tiny" else H.HybridConfig.text2b()
+        if args.model == "hybrid2b" and args.layers:
+            hcfg.layers = hcfg.layers[:args.layers]
+        hweights = H.random_weights(hcfg, dev, seed=args.seed)
+        mark("weights")
+        hdec = H.HybridDecoder(hcfg, hweights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs,
+                               keep_logits=not args.greedy_only)
+        mark("state", "K/V pages, delta state, conv history and step workspace")
+        eng = BatchEngine(hdec, f"ifab-{args.model}", args.max_model_len, hcfg.vocab, eos=-1, greedy_only=args.greedy_only,
+                          token_budget=args.max_num_batched_tokens, use_graphs=not args.no_graphs)
+        mark("sampling", "per-slot sampling state")
+        return eng
     if args.model.startswith("dense"):
         # Qwen-style dense GQA decoder (tensor parallel over the fabric): same batch contract, K/V page caches
         from ironpangu_b200.models import dense_gqa as G
@@ -617,7 +635,7 @@ def serve(engine, rank: int, world: int, sock_path: str, group=None, agreement="
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model", default="tiny", choices=["tiny", "flagship", "dense-tiny", "dense2b"])
+    ap.add_argument("--model", default="tiny", choices=["tiny", "flagship", "dense-tiny", "dense2b", "hybrid-tiny", "hybrid2b"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--bundle", default="")
