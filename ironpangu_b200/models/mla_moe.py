@@ -194,7 +194,8 @@ class MlaMoeDecoder:
         B200 it takes 25 us against 38 us per layer at 32 heads and 19 against 29 us at 4 heads with 512 keys, while at 4096
         keys or 8 rows the split-KV kernels, which spread a head over up to 64 CTAs, are faster).
         ``fused_moe``: router, expert gate/up and expert down + all-reduce of a layer as one launch for steps of one or two
-        rows (default: on from 4 ranks up, for bf16 experts up to 1536 wide; bit-identical to the three-kernel chain).
+        rows (default: off - measured slower than the chain at 1, 2 and 8 GPUs; for bf16 experts up to 1536 wide; bit-identical to the
+        three-kernel chain).
         ``shard``: ``(rank, world)`` of the weight shard when it differs from the fabric's (a profiling aid: one GPU runs the
         kernels of rank r of an N-rank job at their real shapes, without the peers; the sums it computes are partial)."""
         assert 1 <= max_tokens <= 8
@@ -260,9 +261,9 @@ class MlaMoeDecoder:
         self.partial = e(((self.vl + 7) // 8) * 8 * 2, dt=torch.float32)
         can_fuse_moe = (not expert_fp8 and c.expert_ffn <= 1536 and c.expert_ffn % 8 == 0 and (c.shared_ffn // self.world) % 8 == 0
                         and c.experts <= 256 and c.topk <= 16)
-        # measured: the one-launch block loses 2-3 % per layer to the three-kernel chain when a rank holds many routes (1 or 2
-        # GPUs) and wins once the per-rank expert work is small against the fixed cost of a kernel boundary
-        self.fused_moe = (can_fuse_moe and self.world >= 4) if fused_moe is None else bool(fused_moe)
+        # measured: the one-launch block loses 2-5 % per layer to the three-kernel chain at 1 and 2 GPUs and 1 % at 8 GPUs
+        # (3.66 against 3.63 ms per step): its in-grid barrier costs what the two kernel boundaries it replaces cost. Off by default.
+        self.fused_moe = False if fused_moe is None else bool(fused_moe)
         assert not self.fused_moe or can_fuse_moe, "the one-launch MoE block needs bf16 experts of at most 1536 columns"
         self.moe_sync = torch.zeros(K.moe_block_sync_words(2, c.experts), dtype=torch.int32, device=dev)
         self.next_ids = torch.zeros(T, dtype=torch.int32, device=dev)

@@ -211,8 +211,8 @@ class PlanEngine:
         benchmarks, weights another engine already holds); every parameter of the plan must be there with the plan's
         shape and dtype. ``fused_head`` / ``fused_moe``: let the dispatcher replace the instruction groups
         {q_b linear, cache write, absorb, attention} and {router, expert gate/up, expert down + all-reduce} by their
-        one-launch kernels where the shapes allow (defaults: the head kernel for contexts up to 2048 keys, the expert block
-        from 4 ranks up, both only for steps of one or two rows - the measured crossovers of the kernels)."""
+        one-launch kernels where the shapes allow, for steps of one or two rows (defaults: the head kernel for contexts up to
+        2048 keys - its measured crossover; the expert block off - it measured slower than its three kernels at 1, 2 and 8 GPUs)."""
         self.fabric, self.rank, self.world = fabric, fabric.rank, fabric.world
         b = Path(bundle_dir)
         from .. import compiler
@@ -337,7 +337,7 @@ class PlanEngine:
             wgu = self.P.get(self.ins[g["gate_up"]]["attrs"]["weight"] + "|" + self.ins[g["gate_up"]]["attrs"]["paired_weight"])
             E = int(self.ins[g["router"]]["attrs"]["experts"])
             can_moe = can_moe and wgu is not None and wgu.shape[1] // 2 <= 1536 and E <= 256 and self.ins[g["router"]]["width"] <= 16
-        self.fused_moe = (can_moe and self.world >= 4) if fused_moe is None else (bool(fused_moe) and can_moe)
+        self.fused_moe = False if fused_moe is None else (bool(fused_moe) and can_moe)
         self.moe_sync = None
         if can_moe:
             E = max(int(self.ins[g["router"]]["attrs"]["experts"]) for g in self.moe_groups.values())

@@ -38,7 +38,7 @@ def main() -> None:
     ap.add_argument("--shard-rank", type=int, default=0)
     ap.add_argument("--replays", type=int, default=30)
     ap.add_argument("--skip-knockouts", action="store_true")
-    ap.add_argument("--fused-moe", type=int, default=1, help="0: router, gate/up and down as three launches")
+    ap.add_argument("--fused-moe", type=int, default=0, help="0: router, gate/up and down as three launches")
     args = ap.parse_args()
 
     import torch.distributed as dist
