@@ -331,6 +331,7 @@ class PlanEngine:
         self.fused_head = (can_head and self.max_context <= self.fused_ctx_limit) if fused_head is None else (bool(fused_head) and can_head)
         self.fuse_override: Optional[bool] = None          # engines that know the position pick the head kernel per step
         self.fused_auto = fused_head is None
+        self.fused_head_rows = 2 if fused_head is None else 8      # an explicit request fuses every step width
         self.can_fuse_head = can_head
         can_moe = bool(self.moe_groups) and all(g["ok"] for g in self.moe_groups.values())
         for g in self.moe_groups.values():
@@ -471,9 +472,8 @@ class PlanEngine:
             v = V[idx]
             return v[:T] if isinstance(v, torch.Tensor) else v
 
-        narrow = T <= 2
-        head = (self.fused_head if self.fuse_override is None else (self.fuse_override and self.can_fuse_head)) and narrow
-        moe = self.fused_moe and narrow
+        head = (self.fused_head if self.fuse_override is None else (self.fuse_override and self.can_fuse_head)) and T <= self.fused_head_rows
+        moe = self.fused_moe and T <= 2
         for k, i in enumerate(self.ins):
             op, a, ins = i["op"], i["attrs"], i["inputs"]
             if (head and k in self._head_members) or (moe and k in self._moe_members):
