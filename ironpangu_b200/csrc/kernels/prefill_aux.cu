@@ -73,6 +73,47 @@ __global__ void __launch_bounds__(72) mla_ctx_gather_kernel(const bf16* cache, c
   else *reinterpret_cast<uint4*>(pe + (long)r * ROPE + (c - LATENT / 8) * 8) = v;
 }
 
+// Keys and values 0 .. ctx - 1 of one sequence slot out of the paged GQA caches [pages, page_tokens, kv_heads * hd]: the keys as
+// dense rows k[rows, W] (W = kv_heads * hd), the values TRANSPOSED as vt[W, ld] with one column per key - the operand layouts of
+// the tensor-core prompt attention. Rows / columns from ctx up to `rows` are zero. One CTA per 32 keys: the values go through a
+// shared-memory tile so that both the reads (along a cache row) and the writes (32 consecutive keys of one column) coalesce.
+__global__ void __launch_bounds__(256) gqa_ctx_gather_kernel(const bf16* k_cache, const bf16* v_cache, const int32_t* page_table, int slot,
+                                                             int max_pages, int page_tokens, int num_pages, int ctx, int W, bf16* k, bf16* vt,
+                                                             long ldvt, uint32_t* status) {
+  __shared__ bf16 tile[32][256 + 2];
+  __shared__ long src_row[32];
+  grid_dep_launch();
+  grid_dep_wait();
+  const int j0 = blockIdx.x * 32, t = threadIdx.x;
+  if (t < 32) {
+    const int j = j0 + t;
+    long row = -1;
+    if (j < ctx) {
+      row = cache_row_of(j, slot, page_table, max_pages, page_tokens, num_pages);
+      if (row < 0 && status) atomicOr(status, IFAB_STATUS_BAD_INDEX);
+    }
+    src_row[t] = row;
+  }
+  __syncthreads();
+  for (int c0 = 0; c0 < W; c0 += 256) {
+    const int c = c0 + t;
+    for (int kk = 0; kk < 32; ++kk) {
+      const long row = src_row[kk];
+      bf16 kv = __float2bfloat16_rn(0.f), vv = kv;
+      if (row >= 0 && c < W) {
+        kv = k_cache[row * W + c];
+        vv = v_cache[row * W + c];
+      }
+      if (c < W) k[(long)(j0 + kk) * W + c] = kv;
+      tile[kk][t] = vv;
+    }
+    __syncthreads();
+    const int key = t & 31;
+    for (int cc = t >> 5; cc < 256 && c0 + cc < W; cc += 8) vt[(long)(c0 + cc) * ldvt + j0 + key] = tile[key][cc];
+    __syncthreads();
+  }
+}
+
 struct MergeParams {
   const float* scratch;   // [T][H][max_splits][LATENT + 2]
   const int32_t* positions;
@@ -364,6 +405,13 @@ extern "C" int ifab_mla_q_rope_inplace(void* q, long ldq, const int32_t* positio
 }
 
 // lat: [rows, 512], pe: [rows, 64] (rows >= ctx; the tail is zeroed)
+extern "C" int ifab_gqa_ctx_gather(const void* k_cache, const void* v_cache, const int32_t* page_table, int slot, int max_pages, int page_tokens,
+                                   int num_pages, int ctx, int rows, int width, void* k, void* vt, long ldvt, uint32_t* status, void* stream) {
+  if (ctx < 1 || rows < ctx || rows % 32 || slot < 0 || width < 1 || ldvt < rows) return -1;
+  return launch_chain(gqa_ctx_gather_kernel, dim3(rows / 32), dim3(256), 0, (cudaStream_t)stream, (const bf16*)k_cache, (const bf16*)v_cache,
+                      page_table, slot, max_pages, page_tokens, num_pages, ctx, width, (bf16*)k, (bf16*)vt, ldvt, status);
+}
+
 extern "C" int ifab_mla_ctx_gather(const void* cache, const int32_t* page_table, int slot, int max_pages, int page_tokens, int num_pages, int ctx,
                                    int rows, void* lat, void* pe, uint32_t* status, void* stream) {
   if (ctx < 1 || rows < ctx || slot < 0) return -1;

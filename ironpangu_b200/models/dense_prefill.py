@@ -56,6 +56,15 @@ class DensePrefill:
         self.tiles = st.to(dev)
         self.ntiles = torch.zeros(1, dtype=torch.int32, device=dev)
         self.launches = 0
+        # Prompt attention on the tensor cores for chunks of consecutive positions of one sequence (heads of 128 columns): keys and
+        # values of the context are gathered out of their pages (values transposed) and attended by the tcgen05 attention kernel
+        # in its grouped-query form, instead of one split-KV pass per 64 query rows.
+        self.tc_attention = c.head_dim == 128
+        if self.tc_attention:
+            cap = (dec.max_context + 127) // 128 * 128
+            self.ctx_k = torch.zeros(cap, dec.hk * c.head_dim, dtype=BF16, device=dev)
+            self.ctx_vt = torch.zeros(dec.hk * c.head_dim, cap, dtype=BF16, device=dev)
+        self._contig = None            # (first position, slot) of the chunk being run, None for rows of many sequences
         # CUDA graphs of the layer stack for small batched steps (one graph per row count): a 64-row decode step is ~250
         # launches, which cost more host time through Python than device time
         self.graph_rows_max = 64
@@ -88,10 +97,14 @@ class DensePrefill:
         self.slots[:m].fill_(slot)
         if sequence_parallel is None:
             sequence_parallel = self.sequence_parallel
-        if sequence_parallel and self.can_sequence_parallel(m):
-            x = self._layers_sp(m)
-        else:
-            x = self._layers(m)
+        self._contig = (pos0, slot)
+        try:
+            if sequence_parallel and self.can_sequence_parallel(m):
+                x = self._layers_sp(m)
+            else:
+                x = self._layers(m)
+        finally:
+            self._contig = None
         K.lm_head_argmax(x[m - 1:m], d.w["lm_head"], fab, norm_w=d.w["final_norm"], eps=c.eps, vocab_offset=d.rank * d.vl,
                          partial=d.partial, logits=None if d.logits is None else d.logits[:1], out_ids=d.next_ids[:1],
                          out_vals=d.next_vals[:1])
@@ -129,6 +142,24 @@ class DensePrefill:
         self._graphs[m] = g
         return x
 
+    def _attention(self, l: int, m: int, qkv: torch.Tensor, pos: torch.Tensor, sl: torch.Tensor, scale: float, st) -> None:
+        """Attention of layer ``l`` for the ``m`` rows of ``qkv`` (rotated, keys / values already in the cache) into ``self.attn``."""
+        d, c = self.dec, self.dec.cfg
+        if self.tc_attention and self._contig is not None:
+            pos0, slot = self._contig
+            ctx = pos0 + m
+            rows = (ctx + 63) // 64 * 64
+            P.gqa_ctx_gather(d.k_cache[l], d.v_cache[l], d.page_table, slot, ctx, self.ctx_k[:rows], self.ctx_vt, status_ptr=st)
+            P.fa_prefill(qkv[:, :d.hq * c.head_dim], self.ctx_k, self.ctx_vt, self.attn[:m], heads=d.hq, q_head_stride=c.head_dim,
+                         k_head_stride=c.head_dim, vt_head_stride=c.head_dim, vt_row0=0, d1=c.head_dim, d2=0, kv_group=d.hq // d.hk, ctx=ctx,
+                         pos0=pos0, scale=scale, status_ptr=st)
+            return
+        for q0 in range(0, m, self.QC):
+            q1 = min(m, q0 + self.QC)
+            K.gqa_decode_attention(qkv[q0:q1], d.k_cache[l], d.v_cache[l], pos[q0:q1], sl[q0:q1], d.page_table, heads=d.hq,
+                                   kv_heads=d.hk, head_dim=c.head_dim, scale=scale, keys_per_split=d.kps, max_splits=d.max_splits,
+                                   scratch=self.scratch, out=self.attn[q0:q1], status_ptr=st)
+
     def _layers(self, m: int) -> torch.Tensor:
         """Embedding + all layers over the ``m`` rows staged in ``tokens / positions / slots``; returns the hidden rows."""
         d, c, fab = self.dec, self.dec.cfg, self.dec.fabric
@@ -144,11 +175,7 @@ class DensePrefill:
             qkv = G.gemm(h, w[p + "qkv"], out=self.qkv[:m], status_ptr=st)
             K.gqa_rope_kv_write(qkv, pos, sl, d.page_table, d.k_cache[l], d.v_cache[l], heads=d.hq, kv_heads=d.hk,
                                 head_dim=c.head_dim, theta=c.theta, status_ptr=st)
-            for q0 in range(0, m, self.QC):
-                q1 = min(m, q0 + self.QC)
-                K.gqa_decode_attention(qkv[q0:q1], d.k_cache[l], d.v_cache[l], pos[q0:q1], sl[q0:q1], d.page_table, heads=d.hq,
-                                       kv_heads=d.hk, head_dim=c.head_dim, scale=scale, keys_per_split=d.kps, max_splits=d.max_splits,
-                                       scratch=self.scratch, out=self.attn[q0:q1], status_ptr=st)
+            self._attention(l, m, qkv, pos, sl, scale, st)
             if fab.world > 1:
                 G.gemm_allreduce(self.attn[:m], w[p + "o_proj"], fab, self._sym_rows(m), residual=x)
             else:
@@ -203,11 +230,7 @@ class DensePrefill:
             qkv = G.allgather_gemm(sp["h_attn"], w[p + "qkv"], sp["ag_qkv"], fab, out=self.qkv[:m])
             K.gqa_rope_kv_write(qkv, pos, sl, d.page_table, d.k_cache[l], d.v_cache[l], heads=d.hq, kv_heads=d.hk,
                                 head_dim=c.head_dim, theta=c.theta, status_ptr=stt)
-            for q0 in range(0, m, self.QC):
-                q1 = min(m, q0 + self.QC)
-                K.gqa_decode_attention(qkv[q0:q1], d.k_cache[l], d.v_cache[l], pos[q0:q1], sl[q0:q1], d.page_table, heads=d.hq,
-                                       kv_heads=d.hk, head_dim=c.head_dim, scale=scale, keys_per_split=d.kps, max_splits=d.max_splits,
-                                       scratch=self.scratch, out=self.attn[q0:q1], status_ptr=stt)
+            self._attention(l, m, qkv, pos, sl, scale, stt)
             G.gemm_reduce_scatter(self.attn[:m], w[p + "o_proj"], fab, out=xl, residual=xl)
             K.rmsnorm(xl, w[p + "ffn_norm"], c.eps, out=sp["h_ffn"].tensor)
             gu = G.allgather_gemm(sp["h_ffn"], w[p + "gate_up"], sp["ag_ffn"], fab, out=sp["gu"])

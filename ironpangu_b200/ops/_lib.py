@@ -107,6 +107,7 @@ _SIGS = {
                              c_int, c_int, c_int, c_int, c_int, c_float, _P, _P],
     "ifab_mla_q_rope_inplace": [_P, c_long, _P, c_int, c_int, c_int, c_int, c_float, _P],
     "ifab_mla_ctx_gather": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P],
+    "ifab_gqa_ctx_gather": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, c_long, _P, _P],
     "ifab_allreduce_rows_nvls": [_P, _P, _P, c_long, _P, c_long, c_long, c_int, _P, C.POINTER(IfabFabric), _P],
     "ifab_gqa_decode_attention": [_P, c_long, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
                                   c_int, c_int, _P, c_u64, _P, c_long, _P, _P],

@@ -159,3 +159,15 @@ def mla_ctx_gather(cache: torch.Tensor, page_table: torch.Tensor, slot: int, ctx
     assert pe.shape[0] == rows and lat.is_contiguous() and pe.is_contiguous() and lat.shape[1] == 512 and pe.shape[1] == 64
     check(_lib.load().ifab_mla_ctx_gather(cache.data_ptr(), page_table.data_ptr(), slot, page_table.shape[1], cache.shape[1], cache.shape[0],
                                           ctx, rows, lat.data_ptr(), pe.data_ptr(), status_ptr, _s()), "mla_ctx_gather")
+
+
+def gqa_ctx_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor, slot: int, ctx: int, k: torch.Tensor,
+                   vt: torch.Tensor, status_ptr=None) -> None:
+    """Keys / values ``0 .. ctx - 1`` of sequence slot ``slot`` out of the paged caches ``[pages, page_tokens, kv_heads, hd]`` into dense
+    keys ``k [rows, kv_heads * hd]`` and transposed values ``vt [kv_heads * hd, >= rows]`` (``rows`` a multiple of 32, the tail zeroed)."""
+    rows, W = k.shape
+    assert k.is_contiguous() and vt.stride(1) == 1 and vt.shape[0] == W and vt.shape[1] >= rows and rows % 32 == 0
+    assert W == k_cache.shape[2] * k_cache.shape[3]
+    check(_lib.load().ifab_gqa_ctx_gather(k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(), slot, page_table.shape[1],
+                                          k_cache.shape[1], k_cache.shape[0], ctx, rows, W, k.data_ptr(), vt.data_ptr(), vt.stride(0), status_ptr,
+                                          _s()), "gqa_ctx_gather")

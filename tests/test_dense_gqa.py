@@ -191,6 +191,52 @@ def test_tensor_core_prefill_matches_the_decode_path_and_the_oracle():
 
 
 @pytest.mark.gpu
+def test_prompt_attention_on_the_tensor_cores_for_128_wide_heads():
+    """Heads of 128 columns: prompt chunks gather the context (values transposed) and run the tcgen05 attention kernel in its
+    grouped-query form. Same last-row logits as the oracle and the decode kernels, same caches; decode continues from it."""
+    from ironpangu_b200.models import dense_gqa as G
+    from ironpangu_b200.models.dense_prefill import DensePrefill
+    from ironpangu_b200.ops import prefill as P
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    cfg = G.DenseConfig(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=128, ffn=512, vocab=1024, theta=1e4)
+    full = G.random_full_weights(cfg, seed=1)
+    fab = Fabric(0, 1)
+    mk = lambda: G.DenseDecoder(cfg, G.shard_weights(cfg, full, 0, 1, "cuda"), fab, max_tokens=8, max_context=512, keep_logits=True)
+    a, b = mk(), mk()
+    n = 300
+    toks = torch.randint(0, cfg.vocab, (n + 3,), generator=torch.Generator().manual_seed(6)).to(torch.int32).cuda()
+    pre = DensePrefill(a, max_rows=192, attn_rows=32)
+    assert pre.tc_attention
+    for s in range(0, n, 192):
+        nxt = pre.forward(toks[s:min(n, s + 192)], s, 0)
+    for s in range(0, n, 8):
+        m = min(8, n - s)
+        b.tokens[:m].copy_(toks[s:s + m]); b.positions[:m].copy_(torch.arange(s, s + m, dtype=torch.int32)); b.slots[:m].zero_()
+        b.forward(m)
+    ref = G.forward_ref(cfg, full, toks.long())
+    torch.testing.assert_close(a.logits[0], ref[n - 1], rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(a.logits[0], b.logits[(n - 1) % 8], rtol=3e-2, atol=3e-2)
+    for l in range(cfg.layers):
+        torch.testing.assert_close(a.k_cache[l].float(), b.k_cache[l].float(), rtol=3e-2, atol=3e-2)
+    # the gather itself: dense keys and transposed values of the first layer, zero tail
+    rows = 320
+    k = torch.full((rows, cfg.kv_heads * 128), 5.0, dtype=torch.bfloat16, device="cuda")
+    vt = torch.full((cfg.kv_heads * 128, 384), 5.0, dtype=torch.bfloat16, device="cuda")
+    P.gqa_ctx_gather(a.k_cache[0], a.v_cache[0], a.page_table, 0, n, k, vt, status_ptr=fab.desc.status)
+    flat_k, flat_v = a.k_cache[0].view(-1, cfg.kv_heads * 128), a.v_cache[0].view(-1, cfg.kv_heads * 128)
+    assert torch.equal(k[:n], flat_k[:n]) and bool((k[n:] == 0).all())
+    assert torch.equal(vt[:, :n], flat_v[:n].T) and bool((vt[:, n:rows] == 0).all()) and bool((vt[:, rows:] == 5.0).all())
+    # decode continues on the cache the prompt path left
+    for i in range(n, n + 3):
+        a.tokens[:1].copy_(toks[i:i + 1]); a.positions[:1].fill_(i); a.slots[:1].zero_()
+        a.forward(1)
+        torch.testing.assert_close(a.logits[0], ref[i], rtol=3e-2, atol=3e-2)
+    assert fab.status() == 0
+    fab.close()
+
+
+@pytest.mark.gpu
 def test_swiglu_rows_matches_torch():
     from ironpangu_b200.ops import decode as K
     torch.manual_seed(3)
