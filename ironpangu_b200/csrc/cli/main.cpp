@@ -17,6 +17,8 @@
 #include <cstring>
 #include <iostream>
 
+#include <sys/stat.h>
+
 #include "contract.h"
 #include "bundle.h"
 #include "cpu_plan.h"
@@ -36,7 +38,8 @@ int usage() {
                "  compile-token MODEL CHECKPOINT|- OUTPUT_DIR [flags]\n  explain MODEL\n  model-source MODEL\n"
                "  synth-checkpoint MODEL OUT_DIR [--seed N]\n  interpret MODEL CHECKPOINT_DIR NEW_TOKENS TOKEN...\n"
                "  validate-bundle BUNDLE_DIR\n  inspect-checkpoint DIR [OUT.json]\n  bind-checkpoint MODEL DIR [OUT.json]\n  plan-placement MODEL [DIR|-] [OUT.json]\n"
-               "  inspect FILE\n  plan GRAPH.json|MODEL.inferfabric [OUT.bin]\n  execute GRAPH.json|MODEL.inferfabric INPUTS.json\n"
+               "  inspect FILE\n  plan|plan-debug GRAPH.json|MODEL.inferfabric [OUT.ifplan] [--dump-ir DIR]\n  tune-plan PLAN.ifplan OVERRIDES.json OUT.ifplan\n"
+               "  explain-plan PLAN.ifplan|GRAPH [--html OUT.html]\n  explain-model TYPED-PLAN.json --html OUT.html\n  execute GRAPH.json|MODEL.inferfabric INPUTS.json\n"
                "  compile SPEC.json|MODEL.inferfabric OUT.bin\n  compile-model MODEL.inferfabric|MODEL.json [OUT.json]\n"
                "  tokenize TOKENIZER TEXT_FILE\n  detokenize TOKENIZER IDS.json\n  render-chat TOKENIZER MESSAGES.json [auto|chatml|plain]\n"
                "  inspect-hybrid-checkpoint MODEL DIR [OUT.json]\n  compile-checkpoint MODEL DIR [OUT.json]\n  lower-checkpoint MODEL DIR CONTEXT [BATCH] [OUT.json]\n  demo\n");
@@ -340,6 +343,14 @@ int main(int argc, char** argv) {
   std::string cmd = argv[1];
   try {
     if (cmd == "compile-token") return compile_token(argc, argv);
+    if (cmd == "explain-model" && argc >= 5 && std::string(argv[3]) == "--html") {
+      // explain-model TYPED-PLAN.json --html MODEL.html: the typed plan of the checkpoint-bound path as a page
+      const Json doc = Json::parse(read_file(argv[2], 64 << 20));
+      write_file_atomic(argv[4], hybrid::html_view(doc));
+      std::cout << doc.at("spec").at("model").at("layers").size() << " layers, " << doc.at("nodes").size() << " operators, "
+                << doc.at("checkpoint").at("weights").size() << " weights, " << doc.at("states").size() << " state tensors; " << argv[4] << "\n";
+      return 0;
+    }
     if (cmd == "explain" || cmd == "explain-model") return argc < 3 ? usage() : explain(argv[2]);
     if (cmd == "model-source") {
       if (argc < 3) return usage();
@@ -381,13 +392,52 @@ int main(int argc, char** argv) {
     if (cmd == "inspect-checkpoint") return inspect_checkpoint(argc, argv);
     if (cmd == "bind-checkpoint") return bind_checkpoint(argc, argv);
     if (cmd == "plan-placement") return plan_placement(argc, argv);
-    if (cmd == "plan" || cmd == "plan-debug" || cmd == "tune-plan" || cmd == "explain-plan") {
+    if (cmd == "plan" || cmd == "plan-debug") {
+      // plan GRAPH.json|MODEL.inferfabric [OUT.ifplan] [--dump-ir DIR]: compile for the CPU f32 target; DIR receives the pipeline's stages
       if (argc < 3) return usage();
       cpu::Options o;
       o.debug_names = cmd == "plan-debug";
-      cpu::PhysicalPlan plan = cpu::compile(load_cpu_graph(argv[2]), o);
+      std::string out_path, dump_dir;
+      for (int i = 3; i < argc; ++i) {
+        if (std::string(argv[i]) == "--dump-ir" && i + 1 < argc) dump_dir = argv[++i];
+        else out_path = argv[i];
+      }
+      const cpu::LogicalGraph g = load_cpu_graph(argv[2]);
+      cpu::Stages stages;
+      cpu::PhysicalPlan plan = cpu::compile(g, o, &stages);
       cpu::verify(plan);
-      if (argc >= 4) write_file_atomic(argv[3], cpu::encode_plan(plan));
+      const std::string binary = cpu::encode_plan(plan);
+      if (!out_path.empty()) write_file_atomic(out_path, binary);
+      if (!dump_dir.empty()) {
+        ::mkdir(dump_dir.c_str(), 0755);
+        write_file_atomic(dump_dir + "/00-logical.json", g.to_json().dump(1) + "\n");
+        write_file_atomic(dump_dir + "/01-typed.json", stages.typed.dump(1) + "\n");
+        write_file_atomic(dump_dir + "/02-optimized.json", stages.optimized.dump(1) + "\n");
+        write_file_atomic(dump_dir + "/03-physical.json", plan.to_json().dump(1) + "\n");
+        write_file_atomic(dump_dir + "/04-bundle-manifest.json", cpu::manifest(binary).dump(1) + "\n");
+      }
+      std::cout << plan.to_json().dump(1) << "\n";
+      return 0;
+    }
+    if (cmd == "tune-plan") {
+      // tune-plan PLAN.ifplan OVERRIDES.json OUT.ifplan: {"step name": "kernel name", ...}
+      if (argc < 5) return usage();
+      const cpu::PhysicalPlan plan = cpu::decode_plan(read_file(argv[2], 64 << 20));
+      std::map<std::string, std::string> overrides;
+      const Json wanted = Json::parse(read_file(argv[3], 1 << 20));
+      for (auto& kv : wanted.as_object()) overrides[kv.first] = kv.second.as_string();
+      const cpu::PhysicalPlan tuned = cpu::tune(plan, overrides);
+      write_file_atomic(argv[4], cpu::encode_plan(tuned));
+      std::cout << tuned.to_json().dump(1) << "\n";
+      return 0;
+    }
+    if (cmd == "explain-plan") {
+      // explain-plan PLAN.ifplan|GRAPH [--html OUT.html]
+      if (argc < 3) return usage();
+      const std::string bytes = read_file(argv[2], 64 << 20);
+      cpu::PhysicalPlan plan = bytes.rfind("IFPLAN01", 0) == 0 ? cpu::decode_plan(bytes) : cpu::compile(load_cpu_graph(argv[2]));
+      cpu::verify(plan);
+      if (argc >= 5 && std::string(argv[3]) == "--html") write_file_atomic(argv[4], cpu::html_view(plan));
       std::cout << plan.to_json().dump(1) << "\n";
       return 0;
     }

@@ -301,7 +301,7 @@ size_t work_of(Op op, const std::vector<std::vector<size_t>>& in) {
 
 }  // namespace
 
-PhysicalPlan compile(const LogicalGraph& g, const Options& opt) {
+PhysicalPlan compile(const LogicalGraph& g, const Options& opt, Stages* stages) {
   struct V { std::string name; std::vector<size_t> shape; Storage st; std::vector<float> data; bool is_const = false; };
   std::vector<V> values;
   std::map<std::string, size_t> index;
@@ -334,6 +334,30 @@ PhysicalPlan compile(const LogicalGraph& g, const Options& opt) {
     outs.push_back(it->second);
   }
   if (outs.empty()) invalid("graph has no outputs");
+  auto dump_nodes = [&](const std::vector<TN>& list) {
+    Json vals = Json::array(), ns = Json::array();
+    for (auto& v : values) {
+      Json j = Json::object(), shp = Json::array();
+      for (size_t d : v.shape) shp.push((int64_t)d);
+      j.set("name", v.name);
+      j.set("shape", shp);
+      j.set("storage", v.st == Storage::Input ? "input" : v.st == Storage::Constant ? "constant" : v.st == Storage::State ? "state" : "temporary");
+      vals.push(std::move(j));
+    }
+    for (auto& n : list) {
+      Json j = Json::object(), in = Json::array();
+      for (size_t i : n.in) in.push(values[i].name);
+      j.set("name", n.name);
+      j.set("op", op_name(n.op));
+      j.set("inputs", in);
+      ns.push(std::move(j));
+    }
+    Json out = Json::object();
+    out.set("values", vals);
+    out.set("nodes", ns);
+    return out;
+  };
+  if (stages) stages->typed = dump_nodes(nodes);
   std::map<size_t, size_t> updates;
   for (auto& kv : g.updates) {
     auto s = index.find(kv.first), v = index.find(kv.second);
@@ -388,6 +412,11 @@ PhysicalPlan compile(const LogicalGraph& g, const Options& opt) {
       continue;
     }
     kept.push_back(n);
+  }
+  if (stages) {
+    stages->optimized = dump_nodes(kept);
+    stages->optimized.set("folded_constants", (int64_t)plan.folded_constants);
+    stages->optimized.set("eliminated_nodes", (int64_t)eliminated);
   }
   // constants that only fed folded nodes may now be dead: recompute liveness over kept nodes
   std::fill(live.begin(), live.end(), 0);
@@ -661,6 +690,78 @@ PhysicalPlan PhysicalPlan::from_json(const Json& j) {
   for (auto& o : j.at("outputs").as_array()) p.outputs.push_back((size_t)o.as_int());
   for (auto& kv : j.at("updates").as_object()) p.updates[(size_t)std::stoul(kv.first)] = (size_t)kv.second.as_int();
   return p;
+}
+
+PhysicalPlan tune(const PhysicalPlan& plan, const std::map<std::string, std::string>& overrides) {
+  PhysicalPlan out = plan;
+  std::map<std::string, size_t> by_name;
+  for (size_t i = 0; i < out.steps.size(); ++i) by_name[out.steps[i].name] = i;
+  static const Kernel kAll[] = {Kernel::AddF32V1, Kernel::MulF32V1, Kernel::ReluF32V1, Kernel::MatmulNaiveF32V1, Kernel::MatmulBlockedF32V1};
+  for (auto& kv : overrides) {
+    auto it = by_name.find(kv.first);
+    if (it == by_name.end()) invalid("tune: the plan has no step named " + kv.first);
+    const Kernel* chosen = nullptr;
+    for (const Kernel& k : kAll)
+      if (kv.second == kernel_name(k)) chosen = &k;
+    if (!chosen) invalid("tune: unknown kernel " + kv.second);
+    Step& s = out.steps[it->second];
+    if (kernel_op(*chosen) != kernel_op(s.kernel))
+      invalid("tune: " + kv.second + " does not implement the operation of step " + kv.first + " (" + op_name(kernel_op(s.kernel)) + ")");
+    s.kernel = *chosen;
+    s.selection_reason = "forced by override";
+  }
+  verify(out);
+  return out;
+}
+
+std::string html_view(const PhysicalPlan& plan) {
+  auto esc = [](const std::string& t) {
+    std::string o;
+    for (char c : t) {
+      if (c == '<') o += "&lt;";
+      else if (c == '>') o += "&gt;";
+      else if (c == '&') o += "&amp;";
+      else if (c == '"') o += "&quot;";
+      else o += c;
+    }
+    return o;
+  };
+  auto shape = [](const std::vector<size_t>& s) {
+    std::string o = "[";
+    for (size_t i = 0; i < s.size(); ++i) o += (i ? ", " : "") + std::to_string(s[i]);
+    return o + "]";
+  };
+  std::string h = "<!doctype html><html><head><meta charset=\"utf-8\"><title>" + esc(plan.name) + " - " + esc(plan.target) +
+                  "</title><style>body{font:13px monospace;margin:1.5em}table{border-collapse:collapse;margin:1em 0}td,th{border:1px solid #999;"
+                  "padding:2px 8px;text-align:left}th{background:#eee}.bar{background:#48a;height:10px;display:inline-block}</style></head><body>";
+  h += "<h1>" + esc(plan.name) + "</h1><p>target " + esc(plan.target) + ", policy " + esc(plan.policy) + ", " + std::to_string(plan.steps.size()) +
+       " steps, arena " + std::to_string(plan.arena_bytes) + " bytes, " + std::to_string(plan.folded_constants) + " constants folded, " +
+       std::to_string(plan.eliminated_nodes) + " nodes eliminated</p>";
+  h += "<h2>Steps</h2><table id=\"steps\"><tr><th>#</th><th>name</th><th>kernel</th><th>inputs</th><th>output</th><th>depends on</th><th>reuse after</th><th>why</th></tr>";
+  for (size_t i = 0; i < plan.steps.size(); ++i) {
+    const Step& s = plan.steps[i];
+    std::string in, dep, reuse;
+    for (size_t b : s.inputs) in += (in.empty() ? "" : ", ") + esc(plan.buffers[b].name);
+    for (size_t d : s.dependencies) dep += (dep.empty() ? "" : ", ") + std::to_string(d);
+    for (size_t d : s.reuse_dependencies) reuse += (reuse.empty() ? "" : ", ") + std::to_string(d);
+    h += "<tr><td>" + std::to_string(i) + "</td><td>" + esc(s.name) + "</td><td>" + kernel_name(s.kernel) + "</td><td>" + in + "</td><td>" +
+         esc(plan.buffers[s.output].name) + "</td><td>" + dep + "</td><td>" + reuse + "</td><td>" + esc(s.selection_reason) + "</td></tr>";
+  }
+  h += "</table><h2>Buffers</h2><table id=\"buffers\"><tr><th>name</th><th>shape</th><th>storage</th><th>bytes</th><th>arena offset</th><th>live steps</th><th></th></tr>";
+  const size_t n = std::max<size_t>(1, plan.steps.size());
+  for (auto& b : plan.buffers) {
+    const char* st = b.storage == Storage::Input ? "input" : b.storage == Storage::Constant ? "constant" : b.storage == Storage::State ? "state" : "temporary";
+    std::string life, bar;
+    if (b.has_lifetime) {
+      life = std::to_string(b.first) + " - " + std::to_string(b.last);
+      bar = "<span style=\"display:inline-block;width:" + std::to_string(200 * b.first / n) + "px\"></span><span class=\"bar\" style=\"width:" +
+            std::to_string(std::max<size_t>(2, 200 * (std::min(b.last, n) - b.first + 1) / n)) + "px\"></span>";
+    }
+    h += "<tr><td>" + esc(b.name) + "</td><td>" + shape(b.shape) + "</td><td>" + st + "</td><td>" + std::to_string(b.bytes()) + "</td><td>" +
+         (b.has_offset ? std::to_string(b.offset) : "") + "</td><td>" + life + "</td><td>" + bar + "</td></tr>";
+  }
+  h += "</table></body></html>\n";
+  return h;
 }
 
 std::string encode_plan(const PhysicalPlan& p) {

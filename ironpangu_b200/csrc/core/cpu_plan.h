@@ -80,7 +80,18 @@ struct Options {
   std::map<std::string, Kernel> override_kernels;   // node name -> forced kernel (must implement the node's op)
   size_t fold_work_limit = 4096;
 };
-PhysicalPlan compile(const LogicalGraph& g, const Options& opt = {});
+// What the pipeline looked like between its passes, for `plan --dump-ir`: the typed graph (every value with its inferred
+// shape) and the optimised graph (dead nodes gone, constants folded), each as JSON.
+struct Stages {
+  Json typed, optimized;
+};
+PhysicalPlan compile(const LogicalGraph& g, const Options& opt = {}, Stages* stages = nullptr);
+// A plan with some steps' kernels replaced: `overrides` maps step names to kernel names; a kernel must implement the step's
+// operation and exist; offsets, lifetimes and dependencies are kept and the result is verified. (Reference: override_kernels
+// behind `tune-plan`, crates/inferfabric-cli/src/physical.rs:70-76.)
+PhysicalPlan tune(const PhysicalPlan& plan, const std::map<std::string, std::string>& overrides);
+// A self-contained HTML page of a plan: steps with kernels and reasons, buffers with arena offsets and lifetimes.
+std::string html_view(const PhysicalPlan& plan);
 void verify(const PhysicalPlan& p);   // throws Error(Invalid) naming the violated rule
 
 std::string encode_plan(const PhysicalPlan& p);      // IFPLAN01: magic, u64 length, sha256, JSON

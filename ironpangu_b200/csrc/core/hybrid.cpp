@@ -1,5 +1,7 @@
 #include "hybrid.h"
 
+#include <cstring>
+
 #include <algorithm>
 #include <cmath>
 #include <filesystem>
@@ -493,6 +495,80 @@ Plan compile(const rankplan::Spec& spec, const Checkpoint& checkpoint) {
   validate(plan);
   plan.key = Sha256::of(plan.to_json().dump());
   return plan;
+}
+
+std::string html_view(const Json& doc) {
+  if (!doc.is_object() || !doc.find("format") || doc.at("format").as_string() != "inferfabric.typed-plan.v1") invalid("explain-model: not a typed plan document");
+  auto esc = [](const std::string& t) {
+    std::string o;
+    for (char c : t) {
+      if (c == '<') o += "&lt;";
+      else if (c == '>') o += "&gt;";
+      else if (c == '&') o += "&amp;";
+      else if (c == '"') o += "&quot;";
+      else o += c;
+    }
+    return o;
+  };
+  auto tensor = [&](const Json& t) {
+    std::string s = esc(t.at("name").as_string()) + " : " + t.at("dtype").as_string() + "[";
+    bool first = true;
+    for (auto& d : t.at("shape").as_array()) {
+      s += std::string(first ? "" : ", ") + (d.is_string() ? d.as_string() : std::to_string(d.as_int()));
+      first = false;
+    }
+    return s + "]";
+  };
+  // the layer an operator belongs to: the number after "layers." in any of its weight / state attributes
+  auto layer_of = [](const Json& n) -> int64_t {
+    const Json* a = n.find("attrs");
+    if (!a) return -1;
+    for (auto& kv : a->as_object()) {
+      if (!kv.second.is_string()) continue;
+      const std::string& v = kv.second.as_string();
+      for (const char* tag : {"layers.", "layer."}) {
+        const size_t p = v.find(tag);
+        if (p != std::string::npos) return std::atoll(v.c_str() + p + std::strlen(tag));
+      }
+    }
+    return -1;
+  };
+  const Json& model = doc.at("spec").at("model");
+  const auto& nodes = doc.at("nodes").as_array();
+  std::string h = "<!doctype html><html><head><meta charset=\"utf-8\"><title>typed plan</title><style>body{font:13px monospace;margin:1.5em}"
+                  "table{border-collapse:collapse;margin:.5em 0 1.5em}td,th{border:1px solid #999;padding:2px 8px;text-align:left;vertical-align:top}"
+                  "th{background:#eee}h3{margin:.2em 0}.attr{color:#555}</style></head><body>";
+  h += "<h1>" + esc(model.find("name") && model.at("name").is_string() ? model.at("name").as_string() : std::string("model")) + "</h1>";
+  h += "<p>contract " + esc(doc.at("contract").as_string()) + ", key " + esc(doc.at("key").as_string()).substr(0, 16) + ", " + std::to_string(nodes.size()) +
+       " operators, " + std::to_string(doc.at("states").size()) + " state tensors, " + std::to_string(doc.at("checkpoint").at("weights").size()) +
+       " weights (" + std::to_string(doc.at("text_weight_bytes").as_int()) + " bytes); state per request " +
+       std::to_string(doc.at("recurrent_and_conv_bytes_per_request").as_int()) + " bytes, KV per page " + std::to_string(doc.at("kv_bytes_per_page").as_int()) + " bytes</p>";
+  h += "<h2>States</h2><table id=\"states\"><tr><th>tensor</th><th>kind</th><th>starts at zero</th></tr>";
+  for (auto& s : doc.at("states").as_array())
+    h += "<tr><td>" + tensor(s) + "</td><td>" + esc(s.at("kind").as_string()) + "</td><td>" + (s.at("initially_zero").as_bool() ? "yes" : "") + "</td></tr>";
+  h += "</table><h2>Operators</h2>";
+  int64_t current = -2;
+  bool open = false;
+  for (auto& n : nodes) {
+    int64_t layer = layer_of(n);
+    if (layer < 0) layer = current < 0 ? -1 : current;      // glue operators stay with the layer around them
+    if (layer != current) {
+      if (open) h += "</table>";
+      h += layer < 0 ? "<h3>input</h3>" : "<h3>layer " + std::to_string(layer) + "</h3>";
+      h += "<table class=\"layer\"><tr><th>operator</th><th>inputs</th><th>outputs</th><th>attributes</th></tr>";
+      current = layer;
+      open = true;
+    }
+    std::string in, out, attrs;
+    for (auto& i : n.at("inputs").as_array()) in += (in.empty() ? "" : ", ") + esc(i.as_string());
+    for (auto& o : n.at("outputs").as_array()) out += (out.empty() ? "" : "<br>") + tensor(o);
+    if (const Json* a = n.find("attrs"))
+      for (auto& kv : a->as_object()) attrs += (attrs.empty() ? "" : "<br>") + esc(kv.first) + " = " + esc(kv.second.is_string() ? kv.second.as_string() : kv.second.dump());
+    h += "<tr><td>" + esc(n.at("op").as_string()) + "</td><td>" + in + "</td><td>" + out + "</td><td class=\"attr\">" + attrs + "</td></tr>";
+  }
+  if (open) h += "</table>";
+  h += "<p>output: " + esc(doc.at("output").as_string()) + "</p></body></html>\n";
+  return h;
 }
 
 void validate(const Plan& plan) {

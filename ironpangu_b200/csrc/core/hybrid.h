@@ -95,6 +95,10 @@ struct Plan {
   Json to_json() const;
 };
 Plan compile(const rankplan::Spec& spec, const Checkpoint& checkpoint);
+// A self-contained HTML page of a typed plan document (the JSON `Plan::to_json` writes): model facts, states, and the operators
+// grouped by layer with their shapes, weights and numerics attributes. Refuses documents of another format.
+// Reference: crates/inferfabric-compiler/src/model_inspect.rs behind `explain-model`.
+std::string html_view(const Json& typed_plan);
 void validate(const Plan& plan);
 
 // ---- lowering ----------------------------------------------------------------------------------------

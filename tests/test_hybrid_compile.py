@@ -199,3 +199,24 @@ def test_contract_and_parallel_limits(tmp_path):
     # another layer schedule in the document than in the checkpoint's config
     r = compiler.cli("compile-checkpoint", doc(tmp_path, layers=["full"] * 8), str(ck))
     assert r.returncode == 1
+
+
+def test_typed_plan_viewer(tmp_path):
+    """`explain-model PLAN.json --html OUT.html`: one table per layer, every operator and state of the plan on the page."""
+    ck = make_checkpoint(tmp_path / "ck")
+    plan_path, page = tmp_path / "plan.json", tmp_path / "model.html"
+    assert compiler.cli("compile-checkpoint", doc(tmp_path), str(ck), str(plan_path)).returncode == 0
+    r = compiler.cli("explain-model", str(plan_path), "--html", str(page))
+    assert r.returncode == 0, r.stderr
+    plan = json.loads(plan_path.read_text())
+    assert f"{len(plan['nodes'])} operators" in r.stdout and "8 layers" in r.stdout
+    html = page.read_text()
+    assert html.startswith("<!doctype html>") and html.count('<table class="layer">') == 9          # the input + 8 layers
+    for op in ("DeltaRecurrence", "PagedAttention", "GatedRms", "CausalConvSilu", "SelectFrontier"):
+        assert html.count(f"<td>{op}</td>") == sum(1 for n in plan["nodes"] if n["op"] == op)
+    assert "layer.3.keys" in html and "S *= exp(g)" in html and "&lt;" not in plan["key"]
+    # a document of another format is refused
+    other = tmp_path / "other.json"
+    other.write_text(json.dumps({"format": "something.else"}))
+    r = compiler.cli("explain-model", str(other), "--html", str(tmp_path / "x.html"))
+    assert r.returncode != 0 and "not a typed plan" in r.stderr
