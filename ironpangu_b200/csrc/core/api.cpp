@@ -252,6 +252,7 @@ void Api::generate_tokens(const http::Request& req, http::ResponseWriter& w) {
     gen.sampling = sp && !sp->is_null() ? serve::SamplingParams::from_json(*sp, defaults_) : defaults_;
     if (const Json* s = body.find("stream"); s && !s->is_null()) stream = s->as_bool();
     if (const Json* r = body.find("request_id"); r && r->is_string()) gen.request_id = r->as_string();
+    if (const Json* c = body.find("cache_salt"); c && c->is_string() && gen.sampling.cache_salt.empty()) gen.sampling.cache_salt = c->as_string();
   } catch (const Error& e) {
     // anything wrong with the request body is the client's error, except a well-formed field this engine does not implement
     return send_error(w, Error(e.kind() == ErrorKind::NotImplemented ? ErrorKind::NotImplemented : ErrorKind::Invalid, e.what()));

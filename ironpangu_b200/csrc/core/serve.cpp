@@ -51,6 +51,7 @@ Json SamplingParams::to_json() const {
   j.set("repetition_penalty", repetition_penalty);
   if (seed) j.set("seed", (int64_t)*seed);
   j.set("max_tokens", (int64_t)max_tokens);
+  if (!cache_salt.empty()) j.set("cache_salt", cache_salt);
   return j;
 }
 
@@ -75,6 +76,10 @@ SamplingParams SamplingParams::from_json(const Json& j, const SamplingParams& d)
   if (const Json* v = j.find("ignore_eos"); v && !v->is_null()) s.ignore_eos = v->as_bool();
   if (const Json* v = j.find("stop_token_ids"); v && !v->is_null())
     for (auto& t : v->as_array()) s.stop_token_ids.push_back((uint32_t)t.as_int());
+  if (const Json* v = j.find("cache_salt"); v && !v->is_null()) {
+    if (!v->is_string() || v->as_string().size() > 256) invalid("sampling: cache_salt must be a string of at most 256 bytes");
+    s.cache_salt = v->as_string();
+  }
   if (const Json* v = j.find("logprobs"); v && !v->is_null()) s.logprobs = v->is_bool() ? (v->as_bool() ? 1 : -1) : (int32_t)v->as_int();
   return s;
 }

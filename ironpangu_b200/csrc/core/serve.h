@@ -31,6 +31,7 @@ struct SamplingParams {
   std::vector<uint32_t> stop_token_ids;
   bool ignore_eos = false;
   int32_t logprobs = -1;             // -1 = none
+  std::string cache_salt;            // prefix-cache isolation: requests share cached prefixes only with requests of the same salt
   bool greedy() const { return temperature <= 0.0 || top_k == 1; }
   void validate() const;             // throws Invalid
   Json to_json() const;

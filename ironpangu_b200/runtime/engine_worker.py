@@ -22,6 +22,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import socket
 import sys
@@ -34,30 +35,41 @@ import torch.distributed as dist
 from .transfers import TransferAudit, prepared_execution_report, state_copy_report
 
 
-class PrefixSnapshots:
-    """LRU of device snapshots keyed by token prefixes (multiples of ``block`` tokens). A snapshot is the KV rows of every
-    layer for positions ``[0, n)``, cloned out of the paged cache, so it survives the release of the slot it came from."""
+def checkpoint_boundary(tokens: int, alignment: int, chunk: int) -> int:
+    """The longest prefix of a ``tokens``-token prompt that may be published or restored: a whole number of cache blocks
+    (``alignment``) AND of prefill chunks (``chunk``) - so a restore lands where an uninterrupted prefill would have a chunk
+    boundary - and strictly shorter than the prompt, so at least one prompt token is left to run and produce logits.
+    Reference: frontend/src/program_cached.rs:10-15."""
+    step = alignment // math.gcd(alignment, chunk) * chunk
+    return max(0, tokens - 1) // step * step
 
-    def __init__(self, capacity: int, block: int):
-        self.capacity, self.block = capacity, block
-        self.entries: "OrderedDict[Tuple[int, ...], List[torch.Tensor]]" = OrderedDict()
+
+class PrefixSnapshots:
+    """LRU of device snapshots keyed by (salt, token prefix), prefixes being multiples of ``block`` tokens. A snapshot is the KV
+    rows of every layer for positions ``[0, n)``, cloned out of the paged cache, so it survives the release of the slot it came
+    from. The salt (the deployment's namespace plus the request's ``cache_salt``) isolates tenants: a prefix is only ever
+    found by requests that carry the salt it was published under."""
+
+    def __init__(self, capacity: int, block: int, chunk: int = 0, namespace: str = ""):
+        self.capacity, self.block, self.chunk, self.namespace = capacity, block, chunk or block, namespace
+        self.entries: "OrderedDict[Tuple, List[torch.Tensor]]" = OrderedDict()
         self.hits = self.misses = self.published = self.evicted = 0
 
-    def lookup(self, tokens: List[int]) -> Optional[Tuple[Tuple[int, ...], List[torch.Tensor]]]:
-        """A stored snapshot whose tokens start with all of ``tokens``, or None."""
-        want = tuple(tokens)
+    def lookup(self, tokens: List[int], salt: str = "") -> Optional[Tuple[Tuple[int, ...], List[torch.Tensor]]]:
+        """A stored snapshot of the same salt whose tokens start with all of ``tokens``, or None."""
+        want, ns = tuple(tokens), (self.namespace, salt)
         for key in reversed(self.entries):
-            if len(key) >= len(want) and key[:len(want)] == want:
+            if key[0] == ns and len(key[1]) >= len(want) and key[1][:len(want)] == want:
                 self.entries.move_to_end(key)
-                return key, self.entries[key]
+                return key[1], self.entries[key]
         return None
 
-    def publish(self, tokens: List[int], rows_of) -> None:
+    def publish(self, tokens: List[int], rows_of, salt: str = "") -> None:
         """``rows_of(n)`` -> list of per-layer tensors with the first ``n`` KV rows of the sequence."""
-        n = len(tokens) // self.block * self.block
+        n = checkpoint_boundary(len(tokens), self.block, self.chunk)
         if n == 0 or self.capacity == 0:
             return
-        key = tuple(tokens[:n])
+        key = ((self.namespace, salt), tuple(tokens[:n]))
         if key in self.entries:
             self.entries.move_to_end(key)
             return
@@ -74,7 +86,7 @@ class BatchEngine:
     TOPK_CAP = 64   # candidates the sampling kernel keeps per row
 
     def __init__(self, decoder, model_name: str, context: int, vocab: int, eos: int = -1, greedy_only: bool = False,
-                 prefix_slots: int = 0, prefill=None, token_budget: int = 0, use_graphs: bool = True):
+                 prefix_slots: int = 0, prefill=None, token_budget: int = 0, use_graphs: bool = True, prefix_namespace: str = ""):
         """``prefill``: optional tensor-core chunk executor (``forward(tokens, pos0, slot)``, attribute ``M`` = rows per call);
         prompt slices longer than one decode launch group run through it, and the engine advertises ``M`` as its token budget."""
         self.dec, self.name, self.context, self.eos, self.vocab = decoder, model_name, context, eos, vocab
@@ -97,6 +109,7 @@ class BatchEngine:
         self.history: List[List[int]] = [[] for _ in range(self.residents)]
         self.sampling: List[Dict] = [{} for _ in range(self.residents)]
         self.prompt_done = [False] * self.residents
+        self.salt = [""] * self.residents
         R = self.residents
         if self.can_sample:
             vl = decoder.logits.shape[1]
@@ -108,7 +121,10 @@ class BatchEngine:
             self.counters = torch.zeros(R, dtype=torch.int64, device=dev)
             self.counts = torch.zeros(R, vl, dtype=torch.int16, device=dev)
             self.vocab_offset = decoder.rank * vl
-        self.prefix = PrefixSnapshots(prefix_slots, self.rows) if prefix_slots > 0 and hasattr(decoder, "caches") else None
+        # snapshots end where the scheduler's prompt slices end (it hands out slices of `budget` tokens): other lengths could
+        # never be restored whole
+        self.prefix = (PrefixSnapshots(prefix_slots, self.rows, chunk=self.budget, namespace=prefix_namespace)
+                       if prefix_slots > 0 and hasattr(decoder, "caches") else None)
         self.transfers = TransferAudit()
         self.allocations_at_ready: Optional[int] = None      # set once the engine has served its first step of every width it will see
         self.audit_counters = {"steps": 0, "launch_groups": 0, "rows": 0, "h2d_bytes": 0, "d2h_bytes": 0, "prefix_rows_copied": 0,
@@ -149,6 +165,7 @@ class BatchEngine:
         self.history[resident] = []
         self.prompt_done[resident] = False
         self.sampling[resident] = {"greedy": greedy, "top_k": top_k}
+        self.salt[resident] = str(sampling.get("cache_salt", ""))
         if self.can_sample:
             self.inv_temp[resident] = 1.0 / temp if temp > 0 else 1.0
             self.top_p[resident] = float(sampling.get("top_p", 1.0))
@@ -202,7 +219,7 @@ class BatchEngine:
             self.next_pos[resident] = position + count
             # a whole non-sampling prefill chunk that a snapshot covers is served by a copy
             if self.prefix is not None and not sample and position + count == len(hist):
-                hit = self.prefix.lookup(hist)
+                hit = self.prefix.lookup(hist, self.salt[resident])
                 if hit is not None and len(hit[0]) >= position + count:
                     self._restore(resident, hit[1], position, position + count)
                     self.prefix.hits += 1
@@ -268,7 +285,7 @@ class BatchEngine:
             for resident, position, count, sample in slices:
                 if sample and not self.prompt_done[resident]:      # the first sampling slice of a sequence ends its prompt
                     self.prompt_done[resident] = True
-                    self.prefix.publish(list(self.history[resident]), lambda n, r=resident: self._snapshot(r, n))
+                    self.prefix.publish(list(self.history[resident]), lambda n, r=resident: self._snapshot(r, n), self.salt[resident])
         self.audit_counters["steps"] += 1
         if d.fabric.status() != 0:
             raise RuntimeError(f"kernel status word = {d.fabric.status()}")
@@ -486,7 +503,7 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
         mark("prefill", "activation buffers of the matrix-matrix prompt path")
     eng = BatchEngine(dec, f"ifab-{args.model}", args.max_model_len, cfg.vocab, eos=cfg.eos, greedy_only=args.greedy_only,
                       prefix_slots=args.prefix_cache_slots, prefill=prefill, token_budget=args.max_num_batched_tokens,
-                      use_graphs=not args.no_graphs)
+                      use_graphs=not args.no_graphs, prefix_namespace=args.prefix_cache_namespace)
     mark("sampling", "per-slot sampling state and prefix snapshots")
     return eng
 
@@ -645,6 +662,7 @@ def main() -> None:
     ap.add_argument("--max-num-batched-tokens", type=int, default=0, help="tokens per scheduler step (0 = one launch group of 8 rows)")
     ap.add_argument("--executor", default="bundle", choices=["bundle", "model"],
                     help="bf16 MLA+MoE models: run the compiled bundle of the model's generated source (plan engine) or the hand-wired decoder class")
+    ap.add_argument("--prefix-cache-namespace", default="", help="tenant namespace of the prefix cache: part of every key")
     ap.add_argument("--prefix-cache-slots", type=int, default=0, help="device snapshots kept by the prefix cache (0 = off)")
     ap.add_argument("--kv-int8", action="store_true", help="packed int8 latent KV cache")
     ap.add_argument("--expert-fp8", action="store_true", help="block-scaled fp8 expert weights (1 x 128 scale blocks)")

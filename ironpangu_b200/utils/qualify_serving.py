@@ -10,7 +10,8 @@ Scenarios (each reports ``passed`` and what it measured):
 * ``repeatability``     the same greedy request twice gives the same tokens; a request alone equals the same request among peers
 * ``cancellation``      a streamed request is abandoned in the middle while peers run: the peers finish, the cancellation is counted,
                         the slot is reused
-* ``prefix_cache``      cold prompt (misses) -> same prompt again (hits, same tokens) -> a prompt that shares only the first blocks
+* ``prefix_cache``      cold prompt (misses) -> same prompt again (hits, same tokens) -> same prompt under another ``cache_salt``
+                        (misses: tenants share nothing) -> a prompt that shares only the first blocks
                         (partial reuse) -> enough distinct prompts to evict the first -> the first again (misses again: LRU)
 * ``overload``          a burst larger than the admission queue: the excess is refused with 429 and a JSON error, nothing hangs,
                         and a request after the burst succeeds (recovery)
@@ -30,6 +31,7 @@ import argparse
 import hashlib
 import http.client
 import json
+import math
 import os
 import signal
 import socket
@@ -54,6 +56,7 @@ class StandInEngine:
         self.residents, self.context, self.vocab, self.budget = residents, context, vocab, budget
         self.history: List[List[int]] = [[] for _ in range(residents)]
         self.prompt_done = [False] * residents
+        self.salt = [""] * residents
         self.prefix: "OrderedDict[tuple, int]" = OrderedDict()
         self.prefix_slots = prefix_slots
         self.counters = {"steps": 0, "rows": 0, "prefix_hits": 0, "prefix_misses": 0, "prefix_published": 0, "prefix_evicted": 0}
@@ -63,13 +66,14 @@ class StandInEngine:
         return {"model": "standin", "residents": self.residents, "token_budget": self.budget, "chunk": self.budget, "context": self.context,
                 "vocab": self.vocab, "eos": 0, "has_eos": False, "world": 1, "greedy_only": True}
 
-    def admit(self, resident: int, reserve: int) -> None:
+    def admit(self, resident: int, reserve: int, salt: str = "") -> None:
         if not 0 <= resident < self.residents:
             raise ValueError("resident out of range")
         if reserve > self.context:
             raise OverflowError("request does not fit the sequence slot")
         self.history[resident] = []
         self.prompt_done[resident] = False
+        self.salt[resident] = salt
 
     def _token(self, hist: List[int]) -> int:
         h = hashlib.blake2b(repr(hist).encode(), digest_size=8).digest()
@@ -91,8 +95,8 @@ class StandInEngine:
             off += count
             self.counters["rows"] += count
             if self.prefix_slots and not sample:
-                want = tuple(hist)
-                hit = next((k for k in reversed(self.prefix) if len(k) >= len(want) and k[:len(want)] == want), None)
+                want, salt = tuple(hist), self.salt[resident]
+                hit = next((k for k in reversed(self.prefix) if k[0] == salt and len(k[1]) >= len(want) and k[1][:len(want)] == want), None)
                 if hit is not None:
                     self.prefix.move_to_end(hit)
                     self.counters["prefix_hits"] += 1
@@ -102,8 +106,9 @@ class StandInEngine:
                 out[i] = self._token(hist)
                 if self.prefix_slots and not self.prompt_done[resident]:
                     self.prompt_done[resident] = True
-                    n = len(hist) // self.BLOCK * self.BLOCK
-                    key = tuple(hist[:n])
+                    step = self.BLOCK // math.gcd(self.BLOCK, self.budget) * self.budget
+                    n = (len(hist) - 1) // step * step       # whole blocks and whole prompt slices, one prompt token left over
+                    key = (self.salt[resident], tuple(hist[:n]))
                     if n and key in self.prefix:
                         self.prefix.move_to_end(key)
                     elif n:
@@ -136,7 +141,7 @@ def serve_standin(sock_path: str, args) -> None:
             if op == "info":
                 resp = {"ok": True, "info": eng.info()}
             elif op == "admit":
-                eng.admit(int(req["resident"]), int(req.get("reserve", 0)))
+                eng.admit(int(req["resident"]), int(req.get("reserve", 0)), str(req.get("sampling", {}).get("cache_salt", "")))
                 resp = {"ok": True}
             elif op == "step":
                 steps += 1
@@ -211,8 +216,11 @@ class ServerUnderTest:
         c.close()
         return r.status, data
 
-    def generate(self, ids: List[int], n: int, timeout: float = 300):
-        st, data = self.request("POST", "/inference/v1/generate", {"token_ids": ids, "sampling_params": {"max_tokens": n, "temperature": 0}}, timeout)
+    def generate(self, ids: List[int], n: int, timeout: float = 300, salt: str = ""):
+        sp = {"max_tokens": n, "temperature": 0}
+        if salt:
+            sp["cache_salt"] = salt
+        st, data = self.request("POST", "/inference/v1/generate", {"token_ids": ids, "sampling_params": sp}, timeout)
         try:
             return st, json.loads(data)
         except ValueError:
@@ -340,6 +348,8 @@ def scenario_prefix_cache(s: ServerUnderTest, args) -> Dict:
     h1 = hits()
     warm = s.generate(base, 6)
     h2 = hits()
+    salted = s.generate(base, 6, salt="tenant-b")          # the same prompt under another salt shares nothing
+    hs = hits()
     branch = s.generate(base[:n // 2] + prompt(6, n - n // 2, args.vocab), 6)
     h3 = hits()
     for i in range(args.prefix_cache_slots + 2):        # distinct prompts until the first one's snapshots are evicted
@@ -350,10 +360,11 @@ def scenario_prefix_cache(s: ServerUnderTest, args) -> Dict:
     ok = (cold[0] == warm[0] == branch[0] == again[0] == 200 and cold[1]["token_ids"] == warm[1]["token_ids"] == again[1]["token_ids"]
           and h1[0] == h0[0] and h1[1] > h0[1]            # cold: only misses
           and h2[0] > h1[0]                              # warm: hits
-          and h3[0] > h2[0] and h3[1] > h2[1]            # shared first half hits, the new second half misses
+          and salted[0] == 200 and salted[1]["token_ids"] == cold[1]["token_ids"] and hs[0] == h2[0] and hs[1] > h2[1]   # salt isolation
+          and h3[0] > hs[0] and h3[1] > hs[1]            # shared first half hits, the new second half misses
           and h4[2] > h3[2]                              # the flood evicted something
           and h5[1] > h4[1])                             # the first prompt misses again: least recently used went first
-    return {"passed": bool(ok), "counters_hits_misses_evicted": [h0, h1, h2, h3, h4, h5]}
+    return {"passed": bool(ok), "counters_hits_misses_evicted": [h0, h1, h2, h3, h4, h5], "after_salted_request": hs}
 
 
 def scenario_overload(args) -> Dict:

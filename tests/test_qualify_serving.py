@@ -41,3 +41,22 @@ def test_stand_in_engine_follows_the_worker_protocol():
         raise AssertionError("a reservation beyond the context must be refused")
     except OverflowError:
         pass
+
+
+def test_prefix_snapshot_keys_boundaries_and_salts():
+    from ironpangu_b200.runtime.engine_worker import PrefixSnapshots, checkpoint_boundary
+
+    # whole cache blocks and whole prompt slices, and always at least one prompt token left to run
+    assert checkpoint_boundary(100, 16, 16) == 96 and checkpoint_boundary(96, 16, 16) == 80 and checkpoint_boundary(16, 16, 16) == 0
+    assert checkpoint_boundary(100, 16, 24) == 96 and checkpoint_boundary(95, 16, 24) == 48      # lcm(16, 24) = 48
+    assert checkpoint_boundary(1000, 8, 512) == 512 and checkpoint_boundary(0, 8, 8) == 0
+    p = PrefixSnapshots(2, block=8, chunk=8, namespace="prod")
+    toks = list(range(20))
+    p.publish(toks, lambda n: [n], salt="a")
+    assert len(p.entries) == 1 and next(iter(p.entries)) == (("prod", "a"), tuple(range(16)))
+    assert p.lookup(toks[:8], "a")[0] == tuple(range(16)) and p.lookup(toks[:8], "b") is None and p.lookup(toks[:8]) is None
+    assert p.lookup(toks[:17], "a") is None                     # longer than what was stored
+    p.publish(toks, lambda n: [n], salt="a")                    # again: refreshed, not duplicated
+    p.publish(toks, lambda n: [n], salt="b")
+    p.publish(list(range(50, 70)), lambda n: [n], salt="a")     # third entry: the least recently used one goes
+    assert p.published == 3 and p.evicted == 1 and p.lookup(toks[:8], "a") is None and p.lookup(toks[:8], "b") is not None
