@@ -19,6 +19,7 @@
 
 #include <sys/stat.h>
 
+#include "config_audit.h"
 #include "contract.h"
 #include "bundle.h"
 #include "cpu_plan.h"
@@ -37,7 +38,7 @@ int usage() {
                "usage: ifab <command> ...\n"
                "  compile-token MODEL CHECKPOINT|- OUTPUT_DIR [flags]\n  explain MODEL\n  model-source MODEL\n"
                "  synth-checkpoint MODEL OUT_DIR [--seed N]\n  interpret MODEL CHECKPOINT_DIR NEW_TOKENS TOKEN...\n"
-               "  validate-bundle BUNDLE_DIR\n  inspect-checkpoint DIR [OUT.json]\n  bind-checkpoint MODEL DIR [OUT.json]\n  plan-placement MODEL [DIR|-] [OUT.json]\n"
+               "  validate-bundle BUNDLE_DIR\n  inspect-config CONFIG.json [OUT.json]\n  inspect-checkpoint DIR [OUT.json]\n  bind-checkpoint MODEL DIR [OUT.json]\n  plan-placement MODEL [DIR|-] [OUT.json]\n"
                "  inspect FILE\n  plan|plan-debug GRAPH.json|MODEL.inferfabric [OUT.ifplan] [--dump-ir DIR]\n  tune-plan PLAN.ifplan OVERRIDES.json OUT.ifplan\n"
                "  explain-plan PLAN.ifplan|GRAPH [--html OUT.html]\n  explain-model TYPED-PLAN.json --html OUT.html\n  execute GRAPH.json|MODEL.inferfabric INPUTS.json\n"
                "  compile SPEC.json|MODEL.inferfabric OUT.bin\n  compile-model MODEL.inferfabric|MODEL.json [OUT.json]\n"
@@ -231,6 +232,18 @@ int inspect_checkpoint(int argc, char** argv) {
   j.set("layers", (int64_t)layer_bytes.size());
   j.set("executable", false);
   j.set("tensor_list", tensors);
+  // the directory's config.json, when it is of the audited family, is summarised beside the inventory
+  {
+    struct stat st {};
+    const std::string cfg = std::string(argv[2]) + "/config.json";
+    if (::stat(cfg.c_str(), &st) == 0) {
+      try {
+        j.set("config_audit", config_audit::audit(read_file(cfg, config_audit::kMaxConfigBytes)));
+      } catch (const Error& e) {
+        j.set("config_audit_error", std::string(e.what()));
+      }
+    }
+  }
   write_or_print(j, argc > 3 ? argv[3] : nullptr);
   std::cerr << "checkpoint metadata audit: " << ck.tensors.size() << " tensors, " << layer_bytes.size() << " layers, " << total << " bytes\n";
   return 0;
@@ -387,6 +400,12 @@ int main(int argc, char** argv) {
     if (cmd == "validate-bundle") {
       if (argc < 3) return usage();
       std::cout << contract::validate_bundle(argv[2]).dump(1) << "\n";
+      return 0;
+    }
+    if (cmd == "inspect-config") {
+      // inspect-config CONFIG.json [OUT.json]: layer forms, features, required operations and kernels of an MLA + MoE config
+      if (argc < 3) return usage();
+      write_or_print(config_audit::audit(read_file(argv[2], config_audit::kMaxConfigBytes)), argc > 3 ? argv[3] : nullptr);
       return 0;
     }
     if (cmd == "inspect-checkpoint") return inspect_checkpoint(argc, argv);
