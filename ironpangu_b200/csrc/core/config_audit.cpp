@@ -45,6 +45,67 @@ struct OpRow {
   const char* kernel;     // entry point of libifab_kernels that implements it ("" = none)
 };
 
+// The one weight-quantisation scheme the family ships: compressed-tensors, int8 weights with one static symmetric scale per
+// output channel, int8 activations with one dynamic symmetric scale per token, applied to Linear modules except those named
+// (exactly, no patterns) under `ignore`. Anything else - groups, block structures, activation ordering, quantised outputs
+// or caches, several groups - is refused: a different scheme needs its own kernels.
+Json quantization_map(const Json& c) {
+  Json out = Json::object();
+  const Json* q = c.find("quantization_config");
+  if (!q || q->is_null()) {
+    out.set("declared", false);
+    return out;
+  }
+  if (!q->is_object()) invalid("config: quantization_config must be an object");
+  auto want = [](const Json& o, const char* key, const Json& value, const char* where) {
+    const Json* v = o.find(key);
+    if (!v || v->dump() != value.dump()) invalid(std::string("config: quantization ") + where + key + " must be " + value.dump());
+  };
+  want(*q, "quant_method", Json("compressed-tensors"), "");
+  want(*q, "quantize", Json("w8a8_dynamic"), "");
+  want(*q, "format", Json("int-quantized"), "");
+  want(*q, "quantization_status", Json("compressed"), "");
+  const Json* groups = q->find("config_groups");
+  if (!groups || !groups->is_object() || groups->size() != 1) invalid("config: quantization needs exactly one config group (W8A8 over Linear)");
+  const Json& g = groups->as_object().front().second;
+  Json linear = Json::array();
+  linear.push("Linear");
+  want(g, "targets", linear, "group ");
+  for (const char* side : {"weights", "input_activations"}) {
+    const Json* o = g.find(side);
+    if (!o || !o->is_object()) invalid(std::string("config: quantization group lacks ") + side);
+    const std::string where = std::string(side) + ".";
+    want(*o, "num_bits", Json((int64_t)8), where.c_str());
+    want(*o, "type", Json("int"), where.c_str());
+    want(*o, "symmetric", Json(true), where.c_str());
+    for (const char* key : {"actorder", "group_size", "block_structure"})
+      if (const Json* v = o->find(key); v && !v->is_null()) invalid(std::string("config: quantization ") + where + key + " is not supported");
+  }
+  want(g.at("weights"), "strategy", Json("channel"), "weights.");
+  want(g.at("weights"), "dynamic", Json(false), "weights.");
+  want(g.at("input_activations"), "strategy", Json("token"), "input_activations.");
+  want(g.at("input_activations"), "dynamic", Json(true), "input_activations.");
+  if (const Json* v = g.find("output_activations"); v && !v->is_null()) invalid("config: quantised output activations need their own contract");
+  if (const Json* v = q->find("kv_cache_scheme"); v && !v->is_null()) invalid("config: a quantised cache scheme needs its own contract");
+  Json ignore = Json::array();
+  if (const Json* ig = q->find("ignore"); ig && !ig->is_null()) {
+    if (!ig->is_array()) invalid("config: quantization ignore must be a list of module names");
+    std::set<std::string> seen;
+    for (auto& e : ig->as_array()) {
+      if (!e.is_string() || e.as_string().empty() || e.as_string().find_first_of("*?[") != std::string::npos)
+        invalid("config: quantization ignore entries must be exact module names (no patterns)");
+      if (seen.insert(e.as_string()).second) ignore.push(e.as_string());
+    }
+  }
+  out.set("declared", true);
+  out.set("scheme", "w8a8_dynamic");
+  out.set("weights", "int8, symmetric, one static scale per output channel (<module>.weight_scale)");
+  out.set("activations", "int8, symmetric, one dynamic scale per token");
+  out.set("applies_to", "every Linear module not listed under ignore");
+  out.set("ignore", ignore);
+  return out;
+}
+
 }  // namespace
 
 Json audit(std::string_view bytes) {
@@ -210,6 +271,7 @@ Json audit(std::string_view bytes) {
   out.set("config", c);
   out.set("layers", summary);
   out.set("features", features);
+  out.set("quantization", quantization_map(c));
   out.set("required_operations", required);
   out.set("operations_without_a_kernel", gaps);
   out.set("warnings", warnings);

@@ -14,7 +14,13 @@ BASE = {
     "swa_layers": [1, 3], "sliding_window_list": [2048, 512], "index_topk": 2048, "index_n_heads": 24, "index_head_dim": 128,
     "use_mome": True, "router_sliding_window": 3, "mhc_num_stream": 4, "mhc_recur_norm": 1, "mhc_use_gamma": True, "use_mhc": False,
     "cla_explicit_mapping": {"4": 2}, "indexer_types": ["full", "full", "shared", "full", "shared", "full"], "param_sink_number": 16,
-    "quantization_config": {"weights": "w8a8"}, "some_future_field": [1, 2, 3],
+    "quantization_config": {
+        "quant_method": "compressed-tensors", "quantize": "w8a8_dynamic", "format": "int-quantized", "quantization_status": "compressed",
+        "config_groups": {"group_0": {"targets": ["Linear"],
+                                      "weights": {"num_bits": 8, "type": "int", "symmetric": True, "strategy": "channel", "dynamic": False, "group_size": None},
+                                      "input_activations": {"num_bits": 8, "type": "int", "symmetric": True, "strategy": "token", "dynamic": True}}},
+        "ignore": ["lm_head", "model.layers.0.mlp.gate", "lm_head"], "kv_cache_scheme": None},
+    "some_future_field": [1, 2, 3],
 }
 
 
@@ -41,11 +47,12 @@ def test_layer_forms_features_and_operations(tmp_path):
     assert ops["mhc_pre"] == "ifab_mhc_pre" and ops["sparse_topk"] == "ifab_sparse_index" and ops["causal_channel_convolution"] == "ifab_mome"
     assert set(a["operations_without_a_kernel"]) == {"shared_layer_cache_views", "shared_sparse_indices", "indexer_cache_append", "sparse_attention"}
     assert any("use_mhc disagrees" in w for w in a["warnings"]) and len(a["unresolved"]) == 5
+    assert a["quantization"]["declared"] and a["quantization"]["scheme"] == "w8a8_dynamic" and a["quantization"]["ignore"] == ["lm_head", "model.layers.0.mlp.gate"]
     # a plain dense config: no optional mechanism, no optional operation
     plain = {k: BASE[k] for k in ("model_type", "hidden_size", "intermediate_size", "vocab_size", "num_attention_heads", "kv_lora_rank",
                                   "qk_nope_head_dim", "qk_rope_head_dim", "v_head_dim", "max_position_embeddings", "num_hidden_layers")}
     b = json.loads(audit(tmp_path, plain).stdout)
-    assert not any(b["features"].values()) and all(l["attention"] == "full_mla" and l["feed_forward"] == "dense" for l in b["layers"])
+    assert b["quantization"] == {"declared": False} and not any(b["features"].values()) and all(l["attention"] == "full_mla" and l["feed_forward"] == "dense" for l in b["layers"])
     assert len(b["required_operations"]) == 10 and b["operations_without_a_kernel"] == []
 
 
@@ -64,6 +71,10 @@ def test_layer_forms_features_and_operations(tmp_path):
     ({"mhc_num_stream": 0}, "between 1 and 1024"),
     ({"index_n_heads": None}, "index_n_heads is missing"),
     ({"use_mome": "yes"}, "true or false"),
+    ({"quantization_config": {"quant_method": "awq"}}, "quant_method must be"),
+    ({"quantization_config": {**BASE["quantization_config"], "ignore": ["model.layers.*.mlp"]}}, "no patterns"),
+    ({"quantization_config": {**BASE["quantization_config"], "kv_cache_scheme": {"num_bits": 8}}}, "quantised cache scheme"),
+    ({"quantization_config": {**BASE["quantization_config"], "config_groups": {}}}, "exactly one config group"),
 ])
 def test_malformed_configs_are_refused(tmp_path, change, message):
     r = audit(tmp_path, {**BASE, **change})
