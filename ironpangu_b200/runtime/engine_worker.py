@@ -126,6 +126,7 @@ class BatchEngine:
         self.prefix = (PrefixSnapshots(prefix_slots, self.rows, chunk=self.budget, namespace=prefix_namespace)
                        if prefix_slots > 0 and hasattr(decoder, "caches") else None)
         self.transfers = TransferAudit()
+        self.trace = None                     # runtime.trace.StepTrace when the runtime option trace_dir is set
         self.allocations_at_ready: Optional[int] = None      # set once the engine has served its first step of every width it will see
         self.audit_counters = {"steps": 0, "launch_groups": 0, "rows": 0, "h2d_bytes": 0, "d2h_bytes": 0, "prefix_rows_copied": 0,
                                "sampled_rows": 0, "prefill_chunks": 0, "prefill_rows": 0}
@@ -203,6 +204,16 @@ class BatchEngine:
 
     # -- one scheduler step ----------------------------------------------------------------------------
     def step(self, slices: List[List[int]], tokens: List[int]) -> List[int]:
+        """One scheduler step; with a step trace switched on (runtime option ``trace_dir``) the step is timed and recorded."""
+        if self.trace is None:
+            return self._step(slices, tokens)
+        rec = self.trace.begin(self.audit_counters, len(slices))
+        try:
+            return self._step(slices, tokens)
+        finally:
+            self.trace.end(rec, self.audit_counters)
+
+    def _step(self, slices: List[List[int]], tokens: List[int]) -> List[int]:
         d = self.dec
         rows = []                     # (token, position, slot, slice index or -1 when the row does not sample)
         long_slices = []              # prompt slices that go through the matrix-matrix prefill path
@@ -704,6 +715,10 @@ def main() -> None:
     rec = MemoryProfile.start(opts)
     engine = build_engine(args, rank, world, rec)
     engine.runtime_options = ropts
+    if ropts.trace_dir:
+        from .trace import StepTrace
+
+        engine.trace = StepTrace(ropts.trace_dir, rank)
     rec.finish()
     if args.profile_only:
         torch.cuda.synchronize()
@@ -718,6 +733,8 @@ def main() -> None:
         serve(engine, rank, world, args.socket, ctl, ropts.rank_agreement)
     finally:
         torch.cuda.synchronize()
+        if engine.trace is not None:
+            engine.trace.close()
         if ropts.audit_dir:
             # the audit record of this rank (counters, options), for runs that are compared later
             os.makedirs(ropts.audit_dir, exist_ok=True)

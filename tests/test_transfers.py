@@ -89,3 +89,30 @@ def test_init_plan_loader_stages_through_a_bounded_buffer(tmp_path):
         half = shape[1] // 2
         assert torch.equal(big["model.layers.0.self_attn.o_proj"], full[:, rank * half:(rank + 1) * half])
     assert out["instructions"] > 0
+
+
+def test_step_traces_line_up_across_ranks(tmp_path):
+    from ironpangu_b200.runtime.trace import COLUMNS, StepTrace, merge
+
+    counters = [{"rows": 0, "prefill_rows": 0, "launch_groups": 0, "sampled_rows": 0, "h2d_bytes": 0, "d2h_bytes": 0} for _ in range(2)]
+    traces = [StepTrace(str(tmp_path), rank=r, use_cuda=False, flush_every=2) for r in range(2)]
+    for step in range(5):
+        for r, t in enumerate(traces):
+            rec = t.begin(counters[r], slices=step + 1)
+            counters[r]["rows"] += 3
+            counters[r]["prefill_rows"] += 16 if step == 0 else 0
+            counters[r]["launch_groups"] += 1
+            counters[r]["h2d_bytes"] += 36
+            t.end(rec, counters[r])
+    for t in traces:
+        t.close()
+    lines = (tmp_path / "steps-rank1.csv").read_text().strip().split("\\n")
+    assert lines[0].split(",") == COLUMNS and len(lines) == 6
+    first = dict(zip(COLUMNS, lines[1].split(",")))
+    assert first["rows"] == "19" and first["prompt_rows"] == "16" and first["slices"] == "1" and first["h2d_bytes"] == "36" and first["device_ms"] == ""
+    m = merge(str(tmp_path))
+    assert [x["step"] for x in m] == list(range(5)) and all(x["ranks"] == 2 and x["device_ms_max"] is None and x["host_ms_max"] >= 0 for x in m)
+    # a rank that recorded fewer steps is reported, not papered over
+    (tmp_path / "steps-rank1.csv").write_text("\\n".join(lines[:4]) + "\\n")
+    with pytest.raises(ValueError, match="do not line up"):
+        merge(str(tmp_path))
