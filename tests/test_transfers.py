@@ -106,13 +106,13 @@ def test_step_traces_line_up_across_ranks(tmp_path):
             t.end(rec, counters[r])
     for t in traces:
         t.close()
-    lines = (tmp_path / "steps-rank1.csv").read_text().strip().split("\\n")
+    lines = (tmp_path / "steps-rank1.csv").read_text().splitlines()
     assert lines[0].split(",") == COLUMNS and len(lines) == 6
     first = dict(zip(COLUMNS, lines[1].split(",")))
     assert first["rows"] == "19" and first["prompt_rows"] == "16" and first["slices"] == "1" and first["h2d_bytes"] == "36" and first["device_ms"] == ""
     m = merge(str(tmp_path))
     assert [x["step"] for x in m] == list(range(5)) and all(x["ranks"] == 2 and x["device_ms_max"] is None and x["host_ms_max"] >= 0 for x in m)
     # a rank that recorded fewer steps is reported, not papered over
-    (tmp_path / "steps-rank1.csv").write_text("\\n".join(lines[:4]) + "\\n")
+    (tmp_path / "steps-rank1.csv").write_text("\n".join(lines[:4]) + "\n")
     with pytest.raises(ValueError, match="do not line up"):
         merge(str(tmp_path))
