@@ -26,7 +26,8 @@ def gemm_ar(rank: int, world: int) -> None:
     from ironpangu_b200.ops.gemm import gemm_allreduce
     from ironpangu_b200.parallel.fabric import Fabric
 
-    fab = Fabric(rank, world)
+    # staging: every rank holds world partial copies of the tiles it owns (32 MB per parity half for a 4096 x 4096 output)
+    fab = Fabric(rank, world, data_half_bytes=80 << 20, flag_half_words=16384)
     # A single call timed after a host barrier mostly measures how far apart the two processes launch, so
     # each sample times CALLS back-to-back calls that rotate over SETS operand sets (together larger than L2)
     M, N, Kl = 4096, 4096, 4096 // world
