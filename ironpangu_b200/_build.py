@@ -27,6 +27,8 @@ KERNEL_LIB = KERNEL_DIR / "libifab_kernels.so"
 CORE_LIB = CORE_DIR / "libifab_core.so"
 CLI_BIN = CLI_DIR / "ifab"
 SERVER_BIN = SERVER_DIR / "ifab-server"
+DEVICE_DIR = ROOT / "csrc" / "device"
+DEVICE_LIB = DEVICE_DIR / "libifab_device.so"
 TESTS_DIR = ROOT / "csrc" / "tests"
 TESTS_BIN = TESTS_DIR / "core_tests"
 
@@ -175,10 +177,27 @@ def build_plugins(force: bool = False) -> list:
     return out
 
 
+def build_device(force: bool = False) -> Path:
+    """The native device executor (``csrc/device``): C++ against the CUDA runtime, the kernel library and the host core. The
+    server loads it on demand (``ifab-server --program BUNDLE CHECKPOINT --native``), so the server itself needs no CUDA."""
+    srcs = sorted(DEVICE_DIR.glob("*.cpp"))
+    deps = srcs + sorted(DEVICE_DIR.glob("*.h")) + sorted(CORE_DIR.glob("*.h")) + [KERNEL_DIR / "ifab_kernels.h"]
+    if srcs and (force or _stale(DEVICE_LIB, deps)):
+        build_kernels()
+        build_core()
+        cuda = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+        _run(["g++", *CXX_FLAGS, "-shared", "-I", str(cuda / "include"), *map(str, srcs), "-o", str(DEVICE_LIB),
+              "-L", str(CORE_DIR), "-lifab_core", "-L", str(KERNEL_DIR), "-lifab_kernels", "-L", str(cuda / "lib64"), "-lcudart",
+              "-Wl,-rpath,$ORIGIN/../core", "-Wl,-rpath,$ORIGIN/../kernels", f"-Wl,-rpath,{cuda / 'lib64'}"], cwd=DEVICE_DIR)
+        _mark(DEVICE_LIB, deps)
+    return DEVICE_LIB
+
+
 def build_all(force: bool = False) -> None:
     build_kernels(force)
     build_core(force)
     build_plugins(force)
+    build_device(force)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,703 @@
+#include "device_program.h"
+
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <set>
+
+#include "../core/contract.h"
+#include "../core/initplan.h"
+#include "../kernels/ifab_kernels.h"
+
+namespace ifab::device {
+namespace {
+
+void cu(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) fail(ErrorKind::Backend, std::string("device program: ") + what + ": " + cudaGetErrorString(e));
+}
+void kernel(int rc, const std::string& what) {
+  if (rc != 0) fail(ErrorKind::Backend, "device program: " + what + " failed: " + ifab_error_string(rc) + " (code " + std::to_string(rc) + ")");
+}
+uint64_t fnv1a64(std::string_view s) {
+  uint64_t h = 0xcbf29ce484222325ull;
+  for (unsigned char c : s) h = (h ^ c) * 0x100000001b3ull;
+  return h;
+}
+std::vector<std::string> words(const std::string& line) {
+  std::vector<std::string> out;
+  size_t b = 0;
+  while (b < line.size()) {
+    while (b < line.size() && (line[b] == ' ' || line[b] == '\r')) ++b;
+    size_t e = b;
+    while (e < line.size() && line[e] != ' ' && line[e] != '\r') ++e;
+    if (e > b) out.push_back(line.substr(b, e - b));
+    b = e;
+  }
+  return out;
+}
+std::vector<std::string> lines(const std::string& text) {
+  std::vector<std::string> out;
+  size_t b = 0;
+  while (b <= text.size()) {
+    size_t e = text.find('\n', b);
+    if (e == std::string::npos) e = text.size();
+    out.push_back(text.substr(b, e - b));
+    b = e + 1;
+  }
+  return out;
+}
+
+// Parameters of one rank in device memory, filled by the init-plan executor through a bounded pinned staging buffer.
+class CudaMemory : public init::DeviceMemory {
+ public:
+  explicit CudaMemory(size_t staging_bytes) : staging_bytes_(staging_bytes) { cu(cudaMallocHost(&stage_, staging_bytes_), "pinned staging buffer"); }
+  ~CudaMemory() override {
+    if (stage_) cudaFreeHost(stage_);
+    for (auto& kv : ptr) cudaFree(kv.second);
+  }
+  void allocate(const init::Parameter& p) override {
+    void* d = nullptr;
+    cu(cudaMalloc(&d, std::max<uint64_t>(p.bytes(), 16)), "parameter allocation");
+    ptr[p.id] = d;
+    size[p.id] = p.bytes();
+  }
+  void write(uint32_t param, uint64_t offset, const void* data, uint64_t bytes) override {
+    if (offset + bytes > size.at(param)) invalid("device program: a load runs past the end of its parameter");
+    const char* src = static_cast<const char*>(data);
+    for (uint64_t done = 0; done < bytes;) {
+      const uint64_t n = std::min<uint64_t>(staging_bytes_, bytes - done);
+      std::memcpy(stage_, src + done, n);
+      cu(cudaMemcpy(static_cast<char*>(ptr.at(param)) + offset + done, stage_, n, cudaMemcpyHostToDevice), "parameter upload");
+      done += n;
+      uploaded += n;
+    }
+  }
+  void read(uint32_t param, uint64_t offset, void* out, uint64_t bytes) override {
+    cu(cudaMemcpy(out, static_cast<char*>(ptr.at(param)) + offset, bytes, cudaMemcpyDeviceToHost), "parameter read-back");
+  }
+  std::map<uint32_t, void*> ptr;
+  std::map<uint32_t, uint64_t> size;
+  uint64_t uploaded = 0;
+
+ private:
+  size_t staging_bytes_;
+  void* stage_ = nullptr;
+};
+
+struct Ins {
+  std::string op, name, dtype;
+  uint32_t width = 0;
+  std::vector<uint32_t> in;
+  std::map<std::string, std::string> a;
+  bool has(const char* k) const { return a.count(k) != 0; }
+  const std::string& s(const char* k) const {
+    auto it = a.find(k);
+    if (it == a.end()) invalid("device program: instruction " + name + " lacks attribute " + k);
+    return it->second;
+  }
+  int i(const char* k) const { return std::stoi(s(k)); }
+  float f(const char* k, float fallback) const { return has(k) ? std::stof(a.at(k)) : fallback; }
+};
+// a value: a strided row view into the arena (or into a parameter-free state)
+struct Val {
+  char* ptr = nullptr;     // row 0
+  long ld = 0;             // elements per row
+  int esize = 2;
+};
+struct HeadGroup {
+  uint32_t qb = 0, write = 0, absorb = 0, qkv = 0;
+  bool ok = false;
+};
+
+}  // namespace
+
+struct DeviceProgram::Impl {
+  Options opt;
+  std::string name;
+  std::vector<Ins> ins;
+  uint32_t context = 0, vocab = 0, eos = 0, residents = 1, rows = 1;
+  int page_tokens = 16, max_pages = 0, num_pages = 0;
+  int kps = 64, max_splits = 1;
+  std::unique_ptr<CudaMemory> params;
+  std::map<std::string, uint32_t> param_id;
+  std::map<std::string, std::vector<uint64_t>> param_dims;
+  // one device block: [arena | workspace | control]
+  char* block = nullptr;
+  uint64_t arena_bytes = 0, workspace_bytes = 0, block_bytes = 0;
+  std::map<uint32_t, std::pair<uint64_t, uint64_t>> slot_of;   // instruction -> (offset, size)
+  std::vector<Val> val;
+  std::map<uint32_t, void*> cache_of;                           // cache-write instruction -> pages
+  std::map<uint32_t, HeadGroup> heads;                          // attention instruction -> its group
+  std::set<uint32_t> head_members;
+  bool fused_head = false;
+  // control block (device): tokens | positions | slots | next ids | next values, page table; pinned mirror on the host
+  int32_t *d_tokens = nullptr, *d_positions = nullptr, *d_slots = nullptr, *d_next = nullptr, *d_page_table = nullptr;
+  float* d_next_vals = nullptr;
+  int32_t *h_ctl = nullptr, *h_out = nullptr;
+  char* fabric_block = nullptr;
+  IfabFabric fab{};
+  uint32_t* ticket = nullptr;
+  cudaStream_t stream = nullptr;
+  std::map<int, cudaGraphExec_t> graphs;
+  uint64_t launches = 0, steps = 0, h2d = 0, d2h = 0;
+  uint64_t launches_per_step_last = 0;
+  size_t free_at_ready = 0;
+  bool ready = false;
+
+  ~Impl() {
+    for (auto& g : graphs) cudaGraphExecDestroy(g.second);
+    for (auto& c : cache_of) cudaFree(c.second);
+    if (block) cudaFree(block);
+    if (fabric_block) cudaFree(fabric_block);
+    if (d_page_table) cudaFree(d_page_table);
+    if (h_ctl) cudaFreeHost(h_ctl);
+    if (h_out) cudaFreeHost(h_out);
+    if (stream) cudaStreamDestroy(stream);
+  }
+
+  void* P(const std::string& pname) const {
+    auto it = param_id.find(pname);
+    if (it == param_id.end()) invalid("device program: the bundle has no parameter " + pname);
+    return params->ptr.at(it->second);
+  }
+  void* P_optional(const std::string& pname) const {
+    auto it = param_id.find(pname);
+    return it == param_id.end() ? nullptr : params->ptr.at(it->second);
+  }
+  const std::vector<uint64_t>& dims(const std::string& pname) const { return param_dims.at(pname); }
+
+  Val lease(uint32_t k, uint64_t bytes, long ld, int esize) {
+    auto it = slot_of.find(k);
+    if (it == slot_of.end()) fail(ErrorKind::Backend, "device program: the arena has no slot for instruction " + std::to_string(k));
+    if (bytes > it->second.second)
+      fail(ErrorKind::Backend, "device program: instruction " + std::to_string(k) + " needs " + std::to_string(bytes) + " bytes, its arena slot holds " +
+                                   std::to_string(it->second.second));
+    return Val{block + it->second.first, ld, esize};
+  }
+  char* workspace(uint64_t bytes) const {
+    if (bytes > workspace_bytes) fail(ErrorKind::Backend, "device program: a kernel needs " + std::to_string(bytes) + " bytes of workspace, the plan froze " + std::to_string(workspace_bytes));
+    return block + arena_bytes;
+  }
+
+  void load(const std::string& bundle, const std::string& checkpoint);
+  void dispatch(int T);
+  void step(const int32_t* tokens, const int32_t* positions, const int32_t* slots, int T, int32_t* out);
+};
+
+void DeviceProgram::Impl::load(const std::string& bundle, const std::string& checkpoint) {
+  cu(cudaSetDevice(opt.device), "cudaSetDevice");
+  contract::validate_bundle(bundle);                      // kernel and binding contracts of the serialized program, before any allocation
+  const Json prog = Json::parse(read_file(bundle + "/device-program.json", 256 << 20));
+  const Json man = Json::parse(read_file(bundle + "/serving.json", 16 << 20));
+  if (prog.at("parallel").at("tp").as_int() != 1) fail(ErrorKind::NotImplemented, "device program: this executor runs bundles compiled for tp = 1");
+  name = prog.at("name").as_string();
+  context = (uint32_t)prog.at("max_context").as_int();
+  if (opt.context && opt.context < context) context = opt.context;
+  eos = (uint32_t)prog.at("eos").as_int();
+  vocab = (uint32_t)man.at("vocab").as_int();
+  residents = opt.residents ? opt.residents : std::max<uint32_t>(1, (uint32_t)man.at("resident_sequences").as_int());
+  for (auto& j : prog.at("instructions").as_array()) {
+    Ins x;
+    x.op = j.at("op").as_string();
+    x.name = j.at("name").as_string();
+    x.dtype = j.at("dtype").as_string();
+    x.width = (uint32_t)j.at("width").as_int();
+    for (auto& i : j.at("inputs").as_array()) x.in.push_back((uint32_t)i.as_int());
+    for (auto& kv : j.at("attrs").as_object()) x.a[kv.first] = kv.second.is_string() ? kv.second.as_string() : kv.second.dump();
+    ins.push_back(std::move(x));
+  }
+  // ---- parameters: the rank's init plan, executed into device memory ----
+  const init::Plan plan = init::Plan::decode(read_file(bundle + "/rank-0.bin", 64 << 20));
+  const init::Checkpoint ck = init::Checkpoint::inspect(checkpoint);
+  params = std::make_unique<CudaMemory>(opt.staging_bytes);
+  init::ExecuteOptions eo;
+  eo.staging_bytes = opt.staging_bytes;
+  for (auto& p : plan.parameters) {
+    param_id[p.name] = p.id;
+    param_dims[p.name] = p.dims;
+  }
+  init::execute(plan, ck, *params, eo);
+  // ---- arena + workspace: one block, the compiler's offsets ----
+  const std::string exec_bin = read_file(bundle + "/execution.bin", 256 << 20);
+  const uint64_t fingerprint = fnv1a64(exec_bin);
+  const auto al = lines(read_file(bundle + "/arena-rank-0.txt", 64 << 20));
+  const auto head = words(al.at(0));
+  if (head.size() != 5 || head[0] != "IFARENA2") invalid("device program: arena file is not IFARENA2");
+  if (std::stoull(head[1], nullptr, 16) != fingerprint) invalid("device program: the arena was planned for another program");
+  arena_bytes = std::stoull(head[3]);
+  const size_t n = std::stoull(head[4]);
+  if (al.size() < 2 * n + 3 || words(al[1 + n]).at(0) != "pool") invalid("device program: arena file is truncated");
+  for (size_t i = 0; i < n; ++i) {
+    const auto sz = words(al[1 + i]), own = words(al[2 + n + i]);
+    const uint64_t off = std::stoull(sz.at(0)), size = std::stoull(sz.at(1));
+    if (off % 512 || size % 512 || off + size > arena_bytes) invalid("device program: an arena slot is misaligned or outside the arena");
+    slot_of[(uint32_t)std::stoul(own.at(0))] = {off, size};
+  }
+  const auto tok = words(al[2 + 2 * n]);
+  rows = tok.size() == 2 && tok[0] == "tokens" ? (uint32_t)std::stoul(tok[1]) : 1;
+  rows = std::max<uint32_t>(1, std::min<uint32_t>(8, rows));
+  const auto ws = words(read_file(bundle + "/workspace-rank-0.txt", 1 << 20));
+  if (ws.size() != 4 || ws[0] != "IFWORKSPACE1" || std::stoull(ws[1], nullptr, 16) != fingerprint) invalid("device program: the workspace file does not belong to this program");
+  workspace_bytes = std::stoull(ws[3]);
+  const uint64_t ctl_bytes = 4096;
+  block_bytes = arena_bytes + workspace_bytes + ctl_bytes;
+  cu(cudaMalloc((void**)&block, block_bytes), "arena block");
+  cu(cudaMemset(block, 0, block_bytes), "arena clear");
+  char* ctl = block + arena_bytes + workspace_bytes;
+  d_tokens = (int32_t*)ctl;
+  d_positions = d_tokens + 8;
+  d_slots = d_positions + 8;
+  d_next = d_slots + 8;
+  d_next_vals = (float*)(d_next + 8);
+  cu(cudaMallocHost((void**)&h_ctl, 3 * 8 * sizeof(int32_t)), "pinned control block");
+  cu(cudaMallocHost((void**)&h_out, 8 * sizeof(int32_t)), "pinned output block");
+  cu(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "stream");
+  // ---- sequence state: latent KV pages per resident, identity page table ----
+  max_pages = (int)((context + page_tokens - 1) / page_tokens);
+  num_pages = max_pages * (int)residents;
+  std::vector<int32_t> table((size_t)num_pages);
+  for (int i = 0; i < num_pages; ++i) table[(size_t)i] = i;
+  cu(cudaMalloc((void**)&d_page_table, table.size() * 4), "page table");
+  cu(cudaMemcpy(d_page_table, table.data(), table.size() * 4, cudaMemcpyHostToDevice), "page table upload");
+  max_splits = std::max(1, std::min(64, ((int)context + kps - 1) / kps));
+  while ((long)max_splits * kps < (long)context) kps *= 2;
+  // ---- a one-rank fabric: staging halves, flags, control words (the fused all-reduce kernels take the descriptor at any width) ----
+  {
+    const uint64_t data_half = 4 << 20, flag_half_words = 8 * 296, ll_half = 2 << 20;
+    const uint64_t flag_bytes = (2 * flag_half_words * 8 + 255) / 256 * 256;
+    const uint64_t off_flags = 2 * data_half, off_ctl = off_flags + flag_bytes, off_ll = off_ctl + 256, total = off_ll + 2 * ll_half;
+    cu(cudaMalloc((void**)&fabric_block, total), "fabric block");
+    cu(cudaMemset(fabric_block, 0, total), "fabric clear");
+    fab.data[0] = fabric_block;
+    fab.flags[0] = (uint64_t*)(fabric_block + off_flags);
+    fab.seq = (uint64_t*)(fabric_block + off_ctl);
+    fab.done = (uint32_t*)(fabric_block + off_ctl + 8);
+    fab.status = (uint32_t*)(fabric_block + off_ctl + 16);
+    ticket = (uint32_t*)(fabric_block + off_ctl + 32);
+    fab.rank = 0;
+    fab.world = 1;
+    fab.spin_limit = 4000000;
+    fab.data_half_bytes = (uint32_t)data_half;
+    fab.flag_half_words = (uint32_t)flag_half_words;
+    fab.ll_half_bytes = (uint32_t)ll_half;
+    fab.ll_offset = off_ll;
+    fab.mc = nullptr;
+  }
+  // ---- values: views into the arena ----
+  val.assign(ins.size(), Val{});
+  const int T = (int)rows;
+  for (uint32_t k = 0; k < ins.size(); ++k) {
+    const Ins& x = ins[k];
+    if (x.op == "view") continue;
+    if (x.op == "mla_kv_write") {
+      void* pages = nullptr;
+      const uint64_t bytes = (uint64_t)num_pages * page_tokens * x.width * 2;
+      cu(cudaMalloc(&pages, bytes), "KV pages");
+      cu(cudaMemset(pages, 0, bytes), "KV clear");
+      cache_of[k] = pages;
+    } else if (x.op == "router_topk") {
+      const int E = x.i("experts");
+      val[k] = lease(k, (uint64_t)T * x.width * 8 + (uint64_t)T * E * 4, x.width, 4);
+    } else if (x.op == "moe_gate_up") {
+      const uint32_t topk = ins[x.in.at(1)].width;
+      val[k] = lease(k, (uint64_t)T * (topk + 1) * x.width * 2, (long)(topk + 1) * x.width, 2);
+    } else if (x.op == "mla_q_absorb") {
+      const long w = (long)x.i("heads") * (x.i("latent") + x.i("rope"));
+      val[k] = lease(k, (uint64_t)T * w * 2, w, 2);
+    } else if (x.op == "lm_head") {
+      val[k] = Val{(char*)d_next, 1, 4};
+    } else {
+      const int es = x.dtype == "f32" ? 4 : 2;
+      val[k] = lease(k, (uint64_t)T * x.width * es, x.width, es);
+    }
+  }
+  for (uint32_t k = 0; k < ins.size(); ++k) {          // views: a column range of their source (sources precede them)
+    const Ins& x = ins[k];
+    if (x.op != "view") continue;
+    const Val& src = val[x.in.at(0)];
+    val[k] = Val{src.ptr + (long)x.i("start") * src.esize, src.ld, src.esize};
+  }
+  // ---- dispatcher: the attention group as one launch ----
+  std::map<uint32_t, std::vector<uint32_t>> users;
+  for (uint32_t k = 0; k < ins.size(); ++k)
+    for (uint32_t j : ins[k].in) users[j].push_back(k);
+  auto only_user = [&](uint32_t v, uint32_t u) { return users[v].size() == 1 && users[v][0] == u; };
+  bool all_ok = true, any = false;
+  for (uint32_t k = 0; k < ins.size(); ++k) {
+    const Ins& x = ins[k];
+    if (x.op != "mla_attention") continue;
+    HeadGroup g;
+    g.absorb = x.in.at(0);
+    g.write = x.in.at(1);
+    if (ins[g.absorb].op != "mla_q_absorb" || ins[g.write].op != "mla_kv_write") continue;
+    g.qb = ins[g.absorb].in.at(0);
+    const Ins &qb = ins[g.qb], &ab = ins[g.absorb];
+    if (qb.op != "linear" || !qb.has("norm_weight") || qb.has("paired_weight")) continue;
+    const Ins &vq = ins[qb.in.at(0)], &vl = ins[ins[g.write].in.at(0)], &vr = ins[ins[g.write].in.at(1)];
+    if (vq.op != "view" || vl.op != "view" || vr.op != "view" || vq.in[0] != vl.in[0] || vq.in[0] != vr.in[0]) continue;
+    g.qkv = vq.in[0];
+    const int q_lora = vq.i("width"), latent = ab.i("latent"), rope = ab.i("rope"), nope = ab.i("nope"), vdim = x.i("value");
+    const bool layout = vq.i("start") == 0 && vl.i("start") == q_lora && vr.i("start") == q_lora + latent;
+    const bool priv = only_user(g.qb, g.absorb) && only_user(g.absorb, k) && only_user(g.write, k);
+    g.ok = layout && priv && latent == 512 && rope == 64 && nope % 32 == 0 && nope <= 128 && vdim <= 128 && q_lora % 8 == 0 && ab.s("weight") == x.s("weight");
+    heads[k] = g;
+    any = true;
+    all_ok = all_ok && g.ok;
+  }
+  const bool can = any && all_ok;
+  fused_head = opt.fused_head < 0 ? (can && context <= 2048) : (opt.fused_head != 0 && can);
+  if (fused_head)
+    for (auto& kv : heads) {
+      head_members.insert(kv.second.qb);
+      head_members.insert(kv.second.write);
+      head_members.insert(kv.second.absorb);
+    }
+  size_t total = 0;
+  cu(cudaMemGetInfo(&free_at_ready, &total), "cudaMemGetInfo");
+  ready = true;
+}
+
+// Enqueue the program for T rows on `stream` (eagerly or under capture).
+void DeviceProgram::Impl::dispatch(int T) {
+  void* st = stream;
+  uint32_t* status = fab.status;
+  const bool head = fused_head && T <= 2;
+  uint64_t count = 0;
+  auto V = [&](uint32_t k) -> const Val& { return val[k]; };
+  for (uint32_t k = 0; k < ins.size(); ++k) {
+    const Ins& x = ins[k];
+    if (x.op == "view") continue;
+    if (head && head_members.count(k)) continue;
+    const void* norm_w = x.has("norm_weight") ? (x.has("norm_optional") ? P_optional(x.s("norm_weight")) : P(x.s("norm_weight"))) : nullptr;
+    const float eps = x.f("norm_eps", 1e-5f);
+    ++count;
+    if (head && heads.count(k)) {
+      const HeadGroup& g = heads[k];
+      const Ins &qb = ins[g.qb], &ab = ins[g.absorb], &wr = ins[g.write];
+      const Val& qkv = V(g.qkv);
+      kernel(ifab_mla_head_decode(qkv.ptr, qkv.ld, P(qb.s("norm_weight")), P(wr.s("weight")), qb.f("norm_eps", 1e-5f), ab.f("theta", 10000.f),
+                                  P(qb.s("weight")), P(x.s("weight")), cache_of.at(g.write), d_positions, d_slots, d_page_table, max_pages, page_tokens,
+                                  num_pages, nullptr, 0, x.i("window"), 1.f / std::sqrt((float)x.i("scale_dim")), T, x.i("heads"), ins[qb.in[0]].i("width"),
+                                  ab.i("nope"), x.i("value"), V(k).ptr, V(k).ld, status, st),
+             x.name);
+    } else if (x.op == "embedding") {
+      kernel(ifab_embedding_bf16(d_tokens, P(x.s("weight")), V(k).ptr, T, (int)x.width, x.i("vocab"), status, st), x.name);
+    } else if (x.op == "linear") {
+      const std::string pname = x.s("weight") + (x.has("paired_weight") ? "|" + x.s("paired_weight") : "");
+      const bool swiglu = x.has("activation") && x.s("activation") == "swiglu";
+      const auto& d = dims(pname);
+      const Val& in = V(x.in.at(0));
+      kernel(ifab_gemv_bf16(in.ptr, in.ld, P(pname), norm_w, eps, 0, nullptr, 0, V(k).ptr, V(k).ld, 0, T, (int)(swiglu ? d[0] / 2 : d[0]), (int)d[1],
+                            swiglu ? 1 : 0, st),
+             x.name);
+    } else if (x.op == "linear_allreduce") {
+      const auto& d = dims(x.s("weight"));
+      const Val& in = V(x.in.at(0));
+      const Val* res = x.in.size() > 1 ? &V(x.in[1]) : nullptr;
+      kernel(ifab_gemv_allreduce_bf16(in.ptr, in.ld, P(x.s("weight")), res ? res->ptr : nullptr, res ? res->ld : 0, V(k).ptr, V(k).ld, nullptr, T, (int)d[0],
+                                      (int)d[1], &fab, st),
+             x.name);
+    } else if (x.op == "norm") {
+      const Val& in = V(x.in.at(0));
+      kernel(ifab_rmsnorm_bf16(in.ptr, in.ld, P(x.s("weight")), V(k).ptr, V(k).ld, T, (int)x.width, x.f("eps", 1e-5f), 0, st), x.name);
+    } else if (x.op == "mla_kv_write") {
+      const Val &lat = V(x.in.at(0)), &kr = V(x.in.at(1));
+      const int latent = (int)ins[x.in[0]].width, rope = (int)ins[x.in[1]].width;
+      if (kr.ptr != lat.ptr + (long)latent * 2 || kr.ld != lat.ld) fail(ErrorKind::NotImplemented, "device program: latent and rotary columns must be adjacent slices of one projection");
+      kernel(ifab_mla_kv_write(lat.ptr, lat.ld, P(x.s("weight")), x.f("eps", 1e-5f), x.f("theta", 10000.f), d_positions, d_slots, d_page_table, max_pages,
+                               page_tokens, cache_of.at(k), num_pages, T, latent, rope, status, st),
+             x.name);
+    } else if (x.op == "mla_q_absorb") {
+      const Val& q = V(x.in.at(0));
+      const int nope = x.i("nope"), vdim = x.has("value") ? x.i("value") : nope;
+      kernel(ifab_mla_q_absorb(q.ptr, q.ld, P(x.s("weight")), x.f("theta", 10000.f), d_positions, V(k).ptr, T, x.i("heads"), nope, x.i("rope"), x.i("latent"),
+                               vdim, st),
+             x.name);
+    } else if (x.op == "mla_attention") {
+      const int H = x.i("heads"), latent = x.i("latent"), vdim = x.i("value"), nope = x.has("nope") ? x.i("nope") : vdim;
+      const uint64_t scratch = (uint64_t)T * H * max_splits * (latent + 2) * 4;
+      ++count;                                                         // split + merge
+      kernel(ifab_mla_decode_attention(V(x.in.at(0)).ptr, cache_of.at(x.in.at(1)), d_positions, d_slots, d_page_table, max_pages, page_tokens, num_pages, nullptr,
+                                       0, x.i("window"), 1.f / std::sqrt((float)x.i("scale_dim")), T, H, latent, 64, kps, max_splits,
+                                       (float*)workspace(scratch), scratch, P(x.s("weight")), nope, vdim, V(k).ptr, V(k).ld, status, st),
+             x.name);
+    } else if (x.op == "router_topk") {
+      const int E = x.i("experts"), topk = x.i("topk");
+      char* raw = V(k).ptr;
+      int32_t* ids = (int32_t*)raw;
+      float* wts = (float*)(raw + (uint64_t)rows * topk * 4);
+      float* logits = (float*)(raw + (uint64_t)rows * topk * 8);
+      const Val& in = V(x.in.at(0));
+      const int scoring = x.s("scoring") == "softmax" ? 0 : 1;
+      const int renorm = !(x.has("renorm") && x.s("renorm") == "false");
+      kernel(ifab_router_topk(in.ptr, in.ld, norm_w, eps, (const float*)P(x.s("weight")), (const float*)P_optional(x.s("weight") + ".e_score_correction_bias"),
+                              logits, ids, wts, T, (int)ins[x.in[0]].width, E, topk, scoring, renorm, x.f("scale", 1.f), ticket, nullptr, 0, st),
+             x.name);
+    } else if (x.op == "moe_gate_up") {
+      const Ins& r = ins[x.in.at(1)];
+      const std::string pname = x.s("weight") + "|" + x.s("paired_weight");
+      const auto& d = dims(pname);        // [experts, 2F, D]
+      const void* shared = x.has("shared_weight") ? P(x.s("shared_weight") + "|" + x.s("shared_paired_weight")) : nullptr;
+      const int Fs = x.has("shared_weight") ? (int)(dims(x.s("shared_weight") + "|" + x.s("shared_paired_weight"))[0] / 2) : 0;
+      const Val& in = V(x.in.at(0));
+      kernel(ifab_moe_gate_up_decode(in.ptr, in.ld, norm_w, eps, (const int32_t*)V(x.in[1]).ptr, T, (int)d[2], (int)(d[1] / 2), r.i("topk"), 0, (int)d[0], P(pname),
+                                     shared, Fs, V(k).ptr, st),
+             x.name);
+    } else if (x.op == "moe_down_allreduce") {
+      const Ins& r = ins[x.in.at(1)];
+      const auto& d = dims(x.s("weight"));   // [experts, D, F]
+      const int topk = r.i("topk");
+      char* raw = V(x.in[1]).ptr;
+      const void* shared = x.has("shared_weight") ? P(x.s("shared_weight")) : nullptr;
+      const int Fs = x.has("shared_weight") ? (int)dims(x.s("shared_weight"))[1] : 0;
+      const Val* res = x.in.size() > 2 ? &V(x.in[2]) : nullptr;
+      kernel(ifab_moe_down_allreduce_decode(V(x.in[0]).ptr, (const int32_t*)raw, (const float*)(raw + (uint64_t)rows * topk * 4), T, (int)d[1], (int)d[2], topk, 0,
+                                            (int)d[0], P(x.s("weight")), shared, Fs, res ? res->ptr : nullptr, res ? res->ld : 0, V(k).ptr, V(k).ld, &fab, st),
+             x.name);
+    } else if (x.op == "lm_head") {
+      const auto& d = dims(x.s("weight"));
+      const uint64_t partial = ((d[0] + 7) / 8) * 8 * 2 * 4;
+      const Val& in = V(x.in.at(0));
+      kernel(ifab_lm_head_argmax(in.ptr, in.ld, norm_w, eps, P(x.s("weight")), nullptr, T, (int)d[0], (int)d[1], 0, workspace(partial), partial, d_next, d_next_vals, &fab,
+                                 st),
+             x.name);
+    } else {
+      fail(ErrorKind::NotImplemented, "device program: no kernel bound for instruction '" + x.op + "' (" + x.name + ")");
+    }
+  }
+  launches_per_step_last = count;
+}
+
+void DeviceProgram::Impl::step(const int32_t* tokens, const int32_t* positions, const int32_t* slots, int T, int32_t* out) {
+  if (T < 1 || T > (int)rows) invalid("device program: a launch group holds 1.." + std::to_string(rows) + " rows");
+  for (int i = 0; i < T; ++i) {
+    if (tokens[i] < 0 || (uint32_t)tokens[i] >= vocab) invalid("device program: token id outside the vocabulary");
+    if (positions[i] < 0 || (uint32_t)positions[i] >= context) fail(ErrorKind::Capacity, "device program: a row lies beyond the context");
+    if (slots[i] < 0 || (uint32_t)slots[i] >= residents) invalid("device program: resident slot out of range");
+    h_ctl[i] = tokens[i];
+    h_ctl[8 + i] = positions[i];
+    h_ctl[16 + i] = slots[i];
+  }
+  cu(cudaMemcpyAsync(d_tokens, h_ctl, 3 * 8 * sizeof(int32_t), cudaMemcpyHostToDevice, stream), "control upload");
+  h2d += 3 * 8 * sizeof(int32_t);
+  auto it = graphs.find(T);
+  if (it != graphs.end()) {
+    cu(cudaGraphLaunch(it->second, stream), "graph launch");
+  } else {
+    dispatch(T);                                                  // the real run of this step, and the warm-up of the capture
+    if (opt.graphs) {
+      cu(cudaStreamSynchronize(stream), "synchronise before capture");
+      cudaGraph_t g = nullptr;
+      cu(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal), "begin capture");
+      try {
+        dispatch(T);                                              // records only
+      } catch (...) {
+        cudaStreamEndCapture(stream, &g);
+        if (g) cudaGraphDestroy(g);
+        throw;
+      }
+      cu(cudaStreamEndCapture(stream, &g), "end capture");
+      cudaGraphExec_t exec = nullptr;
+      cu(cudaGraphInstantiate(&exec, g, 0), "graph instantiate");
+      cudaGraphDestroy(g);
+      graphs[T] = exec;
+    }
+  }
+  launches += launches_per_step_last;
+  cu(cudaMemcpyAsync(h_out, d_next, 8 * sizeof(int32_t), cudaMemcpyDeviceToHost, stream), "token download");
+  uint32_t status = 0;
+  cu(cudaMemcpyAsync(&h_out[0] + 0, d_next, T * sizeof(int32_t), cudaMemcpyDeviceToHost, stream), "token download");
+  cu(cudaStreamSynchronize(stream), "step synchronise");
+  cu(cudaMemcpy(&status, fab.status, 4, cudaMemcpyDeviceToHost), "status read");
+  d2h += T * sizeof(int32_t) + 4;
+  if (status != 0) fail(ErrorKind::Backend, "device program: kernel status word = " + std::to_string(status));
+  for (int i = 0; i < T; ++i) out[i] = h_out[i];
+  ++steps;
+}
+
+DeviceProgram::DeviceProgram(const std::string& bundle_dir, const std::string& checkpoint_dir, const Options& opt) : p_(std::make_unique<Impl>()) {
+  p_->opt = opt;
+  p_->load(bundle_dir, checkpoint_dir);
+}
+DeviceProgram::~DeviceProgram() = default;
+uint32_t DeviceProgram::context() const { return p_->context; }
+uint32_t DeviceProgram::vocab() const { return p_->vocab; }
+uint32_t DeviceProgram::eos() const { return p_->eos; }
+uint32_t DeviceProgram::residents() const { return p_->residents; }
+uint32_t DeviceProgram::max_rows() const { return p_->rows; }
+const std::string& DeviceProgram::name() const { return p_->name; }
+void DeviceProgram::run_rows(const int32_t* tokens, const int32_t* positions, const int32_t* slots, int rows, int32_t* next_tokens) {
+  cu(cudaSetDevice(p_->opt.device), "cudaSetDevice");
+  p_->step(tokens, positions, slots, rows, next_tokens);
+}
+void DeviceProgram::reset() {
+  for (auto& c : p_->cache_of) {
+    const Ins& x = p_->ins[c.first];
+    cu(cudaMemset(c.second, 0, (uint64_t)p_->num_pages * p_->page_tokens * x.width * 2), "KV clear");
+  }
+}
+Json DeviceProgram::audit() const {
+  Json j = Json::object();
+  j.set("format", "ifab.device-program-audit.v1");
+  j.set("program", p_->name);
+  j.set("steps", p_->steps);
+  j.set("launches", p_->launches);
+  j.set("launches_per_step", p_->launches_per_step_last);
+  j.set("fused_head", p_->fused_head);
+  Json widths = Json::array();
+  for (auto& g : p_->graphs) widths.push((int64_t)g.first);
+  j.set("graph_widths", widths);
+  Json arena = Json::object();
+  arena.set("bytes", p_->arena_bytes);
+  arena.set("workspace_bytes", p_->workspace_bytes);
+  arena.set("slots", (int64_t)p_->slot_of.size());
+  arena.set("planned_rows", p_->rows);
+  j.set("arena", arena);
+  j.set("parameter_bytes_uploaded", p_->params ? p_->params->uploaded : 0);
+  j.set("h2d_bytes", p_->h2d);
+  j.set("d2h_bytes", p_->d2h);
+  size_t free_now = 0, total = 0;
+  if (cudaMemGetInfo(&free_now, &total) == cudaSuccess) j.set("device_bytes_allocated_after_ready", (int64_t)p_->free_at_ready - (int64_t)free_now);
+  return j;
+}
+
+// ---- the executor as a server engine ----------------------------------------------------------------------------------------
+namespace {
+class DeviceResidentEngine : public serve::ResidentEngine {
+ public:
+  DeviceResidentEngine(const std::string& bundle, const std::string& checkpoint, const Options& opt) : p_(bundle, checkpoint, opt), next_(p_.residents(), 0) {}
+  serve::EngineInfo info() const override {
+    serve::EngineInfo e;
+    e.model = p_.name().empty() ? "ifab-program" : p_.name();
+    e.residents = p_.residents();
+    e.token_budget = e.chunk = std::max<uint32_t>(8, p_.max_rows());
+    e.context = p_.context();
+    e.vocab = p_.vocab();
+    e.eos = p_.eos();
+    e.has_eos = false;
+    e.greedy_only = true;
+    return e;
+  }
+  void admit(uint32_t resident, const serve::SamplingParams& s, uint32_t reserve) override {
+    if (!s.greedy()) invalid("the device program engine samples greedily only");
+    if (reserve > p_.context()) fail(ErrorKind::Capacity, "request does not fit the sequence slot");
+    next_.at(resident) = 0;
+  }
+  std::vector<uint32_t> step(const paging::SequenceBatch& batch) override {
+    // rows in slice order, cut into launch groups of at most max_rows; the token of a slice is that of its last row
+    struct Row { int32_t token, position, slot; int slice; };
+    std::vector<Row> rows;
+    size_t off = 0;
+    for (size_t s = 0; s < batch.slices.size(); ++s) {
+      const auto& sl = batch.slices[s];
+      if (sl.position != next_.at(sl.resident)) invalid("device program engine: resident " + std::to_string(sl.resident) + " stands at position " + std::to_string(next_[sl.resident]));
+      for (uint32_t i = 0; i < sl.token_count; ++i)
+        rows.push_back({batch.tokens[off + i], (int32_t)(sl.position + i), (int32_t)sl.resident, i + 1 == sl.token_count ? (int)s : -1});
+      off += sl.token_count;
+      next_[sl.resident] = sl.position + sl.token_count;
+    }
+    std::vector<uint32_t> out(batch.slices.size(), 0);
+    const int G = (int)p_.max_rows();
+    int32_t t[8], p[8], sl[8], nx[8];
+    for (size_t r0 = 0; r0 < rows.size(); r0 += (size_t)G) {
+      const int n = (int)std::min<size_t>((size_t)G, rows.size() - r0);
+      for (int i = 0; i < n; ++i) {
+        t[i] = rows[r0 + i].token;
+        p[i] = rows[r0 + i].position;
+        sl[i] = rows[r0 + i].slot;
+      }
+      p_.run_rows(t, p, sl, n, nx);
+      for (int i = 0; i < n; ++i)
+        if (rows[r0 + i].slice >= 0) out[(size_t)rows[r0 + i].slice] = (uint32_t)nx[i];
+    }
+    return out;
+  }
+  void release(uint32_t resident) override { next_.at(resident) = 0; }
+  Json audit() override { return p_.audit(); }
+
+ private:
+  DeviceProgram p_;
+  std::vector<uint32_t> next_;
+};
+}  // namespace
+
+std::shared_ptr<serve::ResidentEngine> make_device_program_engine(const std::string& bundle, const std::string& checkpoint, const Options& opt) {
+  return std::make_shared<DeviceResidentEngine>(bundle, checkpoint, opt);
+}
+
+}  // namespace ifab::device
+
+// ---- C ABI --------------------------------------------------------------------------------------------------------------------
+namespace {
+thread_local std::string g_device_error;
+template <typename F>
+int guarded(F&& f) {
+  try {
+    f();
+    return 0;
+  } catch (const ifab::Error& e) {
+    g_device_error = e.what();
+    return 1 + (int)e.kind();
+  } catch (const std::exception& e) {
+    g_device_error = e.what();
+    return 100;
+  }
+}
+ifab::device::DeviceProgram* D(void* e) {
+  if (!e) ifab::invalid("device program: null handle");
+  return static_cast<ifab::device::DeviceProgram*>(e);
+}
+}  // namespace
+
+extern "C" {
+const char* ifab_device_program_error(void) { return g_device_error.c_str(); }
+int ifab_device_program_open(const char* bundle, const char* checkpoint, int device, uint32_t residents, void** out) {
+  return guarded([&] {
+    ifab::device::Options o;
+    o.device = device;
+    o.residents = residents;
+    *out = new ifab::device::DeviceProgram(bundle, checkpoint, o);
+  });
+}
+int ifab_device_program_info(void* e, uint32_t* context, uint32_t* vocabulary, uint32_t* eos, uint32_t* residents, uint32_t* max_rows) {
+  return guarded([&] {
+    auto* p = D(e);
+    if (context) *context = p->context();
+    if (vocabulary) *vocabulary = p->vocab();
+    if (eos) *eos = p->eos();
+    if (residents) *residents = p->residents();
+    if (max_rows) *max_rows = p->max_rows();
+  });
+}
+int ifab_device_program_rows(void* e, const int32_t* tokens, const int32_t* positions, const int32_t* slots, uint32_t rows, int32_t* next_tokens) {
+  return guarded([&] { D(e)->run_rows(tokens, positions, slots, (int)rows, next_tokens); });
+}
+int ifab_device_program_reset(void* e) {
+  return guarded([&] { D(e)->reset(); });
+}
+int ifab_device_program_audit(void* e, char* out_json, uint64_t capacity) {
+  return guarded([&] {
+    const std::string s = D(e)->audit().dump();
+    if (s.size() + 1 > capacity) ifab::fail(ifab::ErrorKind::Capacity, "device program: audit buffer too small");
+    std::memcpy(out_json, s.c_str(), s.size() + 1);
+  });
+}
+int ifab_device_program_close(void* e) {
+  return guarded([&] { delete D(e); });
+}
+// For the server, which loads this library on demand: the executor as a ResidentEngine (a C++ object of the host core's type;
+// both sides are built from the same headers). Returns null and leaves the reason in ifab_device_program_error().
+void* ifab_device_program_engine_new(const char* bundle, const char* checkpoint, int device, uint32_t residents, uint32_t context) {
+  void* out = nullptr;
+  guarded([&] {
+    ifab::device::Options o;
+    o.device = device;
+    o.residents = residents;
+    o.context = context;
+    out = new std::shared_ptr<ifab::serve::ResidentEngine>(ifab::device::make_device_program_engine(bundle, checkpoint, o));
+  });
+  return out;
+}
+}

@@ -180,6 +180,15 @@ int ifab_mla_decode_attention(const void* q_lat, const void* cache, const int32_
                               const void* w_kvb, int nope, int vdim, void* out, long ldo, uint32_t* status,
                               void* stream);
 
+/* The attention half of an MLA decode layer as one launch (a cluster of 8 CTAs per head): cache write, q_b, absorb, attention
+ * over the paged latent cache and value up-projection. qkv: [T, q_lora + 576] (output of the qkv_a linear); w_qb: [H * (nope + 64),
+ * q_lora]; w_kvb: [H, nope + vdim, 512]; out: [T, H * vdim]. T <= 8, bf16 cache. */
+int ifab_mla_head_decode(const void* qkv, long ldqkv, const void* q_norm, const void* kv_norm, float eps, float theta,
+                         const void* w_qb, const void* w_kvb, void* cache, const int32_t* positions, const int32_t* slots,
+                         const int32_t* page_table, int max_pages, int page_tokens, int num_pages, const void* sinks,
+                         int n_sinks, int window, float scale, int T, int H, int q_lora, int nope, int vdim, void* out,
+                         long ldo, uint32_t* status, void* stream);
+
 /* ---- hyper-connection / hybrid-model operators (hc_ops.cu); all mixing arithmetic in f32 ---- */
 /* causal depthwise conv with residual; w f32 [C_total, taps] (this rank's channels start at c_offset); state bf16 [slots, taps-1, C] */
 int ifab_mome(const void* x, long ldx, const float* w, void* state, const int32_t* positions, const int32_t* slots, void* y,

@@ -6,12 +6,15 @@
 //   ifab-server --program BUNDLE CHECKPOINT [--gpus N] [options]
 //                                                     sugar for --spawn of the Python engine worker on a compiled bundle
 //   ifab-server --program BUNDLE CHECKPOINT --cpu     run the bundle on the host with the CPU interpreter (no device needed)
+//   ifab-server --program BUNDLE CHECKPOINT --native [--device N]   run a tp = 1 bundle on GPU N through the native device
+//                                                     executor (csrc/device, loaded on demand): no Python in the serving path
 // Options: --port P (0 = pick one, printed), --max-num-seqs N, --max-num-batched-tokens B, --max-model-len C,
 //          --vocab V, --max-queue Q, --stream-capacity S, --step-micros U (mock), --accept-seconds S, --temperature T,
 //          --top-k K, --presence-penalty X (server-side sampling defaults), --sampling-defaults model-card|DIR|FILE (the
 //          model-card recommendation, overridden by DIR/generation_config.json).
 // Prints "listening on 127.0.0.1:PORT" once ready; SIGINT / SIGTERM drain and exit.
 // Reference: frontend/src/main.rs (modes --mock / --program / --native), frontend/src/shutdown.rs.
+#include <dlfcn.h>
 #include <signal.h>
 #include <sys/wait.h>
 #include <unistd.h>
@@ -29,9 +32,9 @@ using namespace ifab;
 namespace {
 
 struct Args {
-  std::string mode, socket, spawn, bundle, checkpoint, tokenizer = "bytes", chat_template = "auto";
-  int port = 8000, gpus = 1;
-  bool cpu = false, seqs_given = false, len_given = false;
+  std::string mode, socket, spawn, bundle, checkpoint, tokenizer = "bytes", chat_template = "auto", device_lib;
+  int port = 8000, gpus = 1, device = 0;
+  bool cpu = false, native = false, seqs_given = false, len_given = false;
   serve::EngineInfo info;
   serve::ServiceOptions opt;
   uint32_t step_micros = 0;
@@ -66,6 +69,9 @@ Args parse(int argc, char** argv) {
     else if (f == "--program") { a.mode = "program"; a.bundle = need(i); a.checkpoint = need(i); }
     else if (f == "--gpus") a.gpus = std::atoi(need(i));
     else if (f == "--cpu") a.cpu = true;
+    else if (f == "--native") a.native = true;                     // --program on the GPU through libifab_device.so (tp = 1 bundles)
+    else if (f == "--device") a.device = std::atoi(need(i));
+    else if (f == "--device-lib") a.device_lib = need(i);
     else if (f == "--tokenizer") a.tokenizer = need(i);            // "bytes" or the path of a tokenizer.json (byte-level BPE)
     else if (f == "--chat-template") a.chat_template = need(i);    // auto | chatml | plain
     else if (f == "--port") a.port = std::atoi(need(i));
@@ -90,6 +96,15 @@ Args parse(int argc, char** argv) {
   }
   if (a.mode.empty()) usage("no mode given");
   return a;
+}
+
+// libifab_device.so next to this binary's directory: <dir>/../device/libifab_device.so
+std::string default_device_lib(const char* argv0) {
+  char buf[4096];
+  const ssize_t n = ::readlink("/proc/self/exe", buf, sizeof buf - 1);
+  std::string exe = n > 0 ? std::string(buf, (size_t)n) : std::string(argv0);
+  const size_t slash = exe.find_last_of('/');
+  return (slash == std::string::npos ? std::string(".") : exe.substr(0, slash)) + "/../device/libifab_device.so";
 }
 
 pid_t spawn_shell(const std::string& cmd, const std::string& socket_path) {
@@ -135,6 +150,21 @@ int main(int argc, char** argv) {
       engine = std::make_shared<serve::MockEngine>(a.info, a.step_micros);
     } else if (a.mode == "program" && a.cpu) {
       engine = serve::make_cpu_program_engine(a.bundle, a.checkpoint, a.seqs_given ? a.info.residents : 0, a.len_given ? a.info.context : 0);
+    } else if (a.mode == "program" && a.native) {
+      // the native device executor, loaded on demand so that this binary needs no CUDA: no Python, no worker process
+      const std::string lib = a.device_lib.empty() ? default_device_lib(argv[0]) : a.device_lib;
+      void* h = ::dlopen(lib.c_str(), RTLD_NOW | RTLD_GLOBAL);
+      if (!h) throw Error(ErrorKind::Io, std::string("cannot load the device executor: ") + ::dlerror());
+      using New = void* (*)(const char*, const char*, int, uint32_t, uint32_t);
+      using Err = const char* (*)();
+      auto make = reinterpret_cast<New>(::dlsym(h, "ifab_device_program_engine_new"));
+      auto why = reinterpret_cast<Err>(::dlsym(h, "ifab_device_program_error"));
+      if (!make || !why) throw Error(ErrorKind::Io, "the device executor library lacks its entry points");
+      void* made = make(a.bundle.c_str(), a.checkpoint.c_str(), a.device, a.seqs_given ? a.info.residents : 0, a.len_given ? a.info.context : 0);
+      if (!made) throw Error(ErrorKind::Backend, why());
+      auto* holder = static_cast<std::shared_ptr<serve::ResidentEngine>*>(made);
+      engine = std::move(*holder);
+      delete holder;
     } else {
       if (a.socket.empty()) a.socket = "/tmp/ifab-engine-" + std::to_string((long)::getpid()) + ".sock";
       if (a.mode == "program") {

@@ -1,0 +1,149 @@
+"""The native device executor (csrc/device): a compiled bundle run on the GPU from C++ - through its C ABI and as the engine of
+`ifab-server --program ... --native` - against the CPU interpreter of the same program and against the Python plan engine."""
+import ctypes as C
+import json
+import os
+import signal
+import subprocess
+import http.client
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+SLICE = ROOT / "examples" / "mla_moe_slice_tp1.inferfabric"
+
+
+def _bundle(tmp_path, residents=2):
+    from ironpangu_b200 import compiler
+
+    ck, bundle = tmp_path / "ck", tmp_path / "bundle"
+    assert compiler.cli("synth-checkpoint", str(SLICE), str(ck), "--seed", "3").returncode == 0
+    r = compiler.cli("compile-token", str(SLICE), str(ck), str(bundle), "--resident-sequences", str(residents), "--prefill-tokens", "8")
+    assert r.returncode == 0, r.stderr
+    return ck, bundle
+
+
+def test_c_abi_matches_the_interpreter_and_the_plan_engine(tmp_path):
+    from ironpangu_b200 import _build, compiler
+    from ironpangu_b200.parallel.fabric import Fabric
+    from ironpangu_b200.runtime.plan_engine import PlanEngine
+
+    ck, bundle = _bundle(tmp_path)
+    lib = C.CDLL(str(_build.build_device()))
+    lib.ifab_device_program_error.restype = C.c_char_p
+    h = C.c_void_p()
+    assert lib.ifab_device_program_open(str(bundle).encode(), str(ck).encode(), 0, 2, C.byref(h)) == 0, lib.ifab_device_program_error()
+    ctx, vocab, eos, res, rows = (C.c_uint32() for _ in range(5))
+    assert lib.ifab_device_program_info(h, C.byref(ctx), C.byref(vocab), C.byref(eos), C.byref(res), C.byref(rows)) == 0
+    assert (vocab.value, res.value, rows.value) == (1024, 2, 8) and ctx.value >= 64
+
+    def run(tokens, positions, slots):
+        n = len(tokens)
+        arr = lambda v: (C.c_int32 * n)(*v)
+        out = (C.c_int32 * n)()
+        assert lib.ifab_device_program_rows(h, arr(tokens), arr(positions), arr(slots), n, out) == 0, lib.ifab_device_program_error()
+        return list(out)
+
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, 1024, (16,), generator=g).tolist()
+    first = compiler.interpret(SLICE.read_text(), str(ck), prompt, steps=8)
+    oracle = compiler.interpret(SLICE.read_text(), str(ck), prompt + first["generated"], all_logits=True)
+    ref = torch.tensor(oracle["prompt_logits"])
+    seq = prompt + first["generated"]
+    # teacher-forced on the oracle's tokens, eight rows per launch group, in resident slot 1
+    got = []
+    for s in range(0, len(seq), 8):
+        got += run(seq[s:s + 8], list(range(s, min(len(seq), s + 8))), [1] * len(seq[s:s + 8]))
+    for i, t in enumerate(got):
+        top2 = ref[i].topk(2).values
+        if float(top2[0] - top2[1]) > 1e-2:
+            assert t == int(ref[i].argmax()), (i, t)
+    # the Python plan engine runs the same kernels on the same bundle: identical tokens, row for row
+    fab = Fabric(0, 1)
+    eng = PlanEngine(str(bundle), str(ck), fab, max_tokens=8, num_slots=2)
+    same = []
+    for s in range(0, len(seq), 8):
+        n = len(seq[s:s + 8])
+        eng.tokens[:n].copy_(torch.tensor(seq[s:s + n], dtype=torch.int32))
+        eng.positions[:n].copy_(torch.arange(s, s + n, dtype=torch.int32))
+        eng.slots[:n].fill_(1)
+        eng.forward(n)
+        same += eng.next_ids[:n].tolist()
+    assert got == same
+    fab.close()
+    # single-row decode in the other slot replays a graph; the two residents do not disturb each other
+    tok, dec = prompt[0], []
+    for i in range(12):
+        tok = run([tok], [i], [0])[0]
+        dec.append(tok)
+    again = run(seq[:8], list(range(8)), [1] * 8)
+    assert again == got[:8]
+    buf = C.create_string_buffer(1 << 16)
+    assert lib.ifab_device_program_audit(h, buf, len(buf)) == 0
+    audit = json.loads(buf.value)
+    assert audit["format"] == "ifab.device-program-audit.v1" and audit["graph_widths"] == [1, 8] and audit["steps"] == 3 + 12 + 1
+    assert audit["arena"]["planned_rows"] == 8 and audit["parameter_bytes_uploaded"] > 0
+    assert audit["device_bytes_allocated_after_ready"] <= 64 << 20          # graphs only: no buffer is allocated by a step
+    # misuse is refused with a message, the engine stays usable
+    assert lib.ifab_device_program_rows(h, (C.c_int32 * 1)(5000), (C.c_int32 * 1)(0), (C.c_int32 * 1)(0), 1, (C.c_int32 * 1)()) != 0
+    assert b"vocabulary" in lib.ifab_device_program_error()
+    assert lib.ifab_device_program_rows(h, (C.c_int32 * 1)(5), (C.c_int32 * 1)(0), (C.c_int32 * 1)(7), 1, (C.c_int32 * 1)()) != 0
+    assert run([prompt[0]], [0], [0])[0] == dec[0]
+    assert lib.ifab_device_program_close(h) == 0
+
+
+def test_server_runs_the_bundle_natively(tmp_path):
+    from ironpangu_b200 import _build, compiler
+
+    ck, bundle = _bundle(tmp_path)
+    _build.build_device()
+    prompt = [5, 77, 300, 12, 9, 41, 8, 100, 3, 250, 17]
+    want = compiler.interpret(SLICE.read_text(), str(ck), prompt, steps=6)["generated"]
+    proc = subprocess.Popen([str(_build.SERVER_BIN), "--port", "0", "--program", str(bundle), str(ck), "--native"], stdout=subprocess.PIPE,
+                            stderr=subprocess.STDOUT, text=True)
+    try:
+        port, lines = None, []
+        for line in proc.stdout:
+            lines.append(line)
+            if line.startswith("listening on"):
+                port = int(line.rsplit(":", 1)[1])
+                break
+        assert port, "".join(lines)
+
+        def post(path, body):
+            c = http.client.HTTPConnection("127.0.0.1", port, timeout=120)
+            c.request("POST", path, json.dumps(body), {"Content-Type": "application/json"})
+            r = c.getresponse()
+            data = r.read().decode()
+            c.close()
+            return r.status, json.loads(data)
+
+        st, g = post("/inference/v1/generate", {"token_ids": prompt, "sampling_params": {"max_tokens": 6}})
+        assert st == 200 and len(g["token_ids"]) == 6
+        oracle = compiler.interpret(SLICE.read_text(), str(ck), prompt + want, all_logits=True)["prompt_logits"]
+        for i, (a, b) in enumerate(zip(g["token_ids"], want)):
+            if a != b:
+                top2 = torch.tensor(oracle[len(prompt) - 1 + i]).topk(2).values
+                assert float(top2[0] - top2[1]) < 1e-2
+                break
+        # two requests at once share the engine's launch groups
+        import threading
+        out = {}
+        ts = [threading.Thread(target=lambda i=i: out.__setitem__(i, post("/inference/v1/generate", {"token_ids": prompt[:4 + i], "sampling_params": {"max_tokens": 5}})))
+              for i in range(2)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        assert all(v[0] == 200 and len(v[1]["token_ids"]) == 5 for v in out.values())
+        c = http.client.HTTPConnection("127.0.0.1", port, timeout=30)
+        c.request("GET", "/audit")
+        audit = json.loads(c.getresponse().read())
+        assert audit["engine"]["format"] == "ifab.device-program-audit.v1" and audit["engine"]["fused_head"] is True
+        st, e = post("/v1/completions", {"prompt": "x", "temperature": 0.9})
+        assert st == 400 and "greedy" in e["error"]["message"]
+    finally:
+        proc.send_signal(signal.SIGTERM)
+        proc.wait(timeout=60)
+    assert proc.returncode == 0

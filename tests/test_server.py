@@ -323,7 +323,7 @@ def test_gpu_engine_worker_profile_only_writes_the_memory_profile(tmp_path):
                        capture_output=True, text=True, timeout=300, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     assert r.returncode == 0, r.stderr[-2000:]
     d = json.loads(path.read_text())
-    assert [s["name"] for s in d["stages"]] == ["fabric", "weights", "state", "sampling"]
+    assert [s["name"] for s in d["stages"]] == ["fabric", "weights", "bundle", "state", "sampling"]
     assert d["failed_stage"] is None and d["headroom_bytes"] > 0 and d["stages"][1]["delta_bytes"] > 0
 
 
