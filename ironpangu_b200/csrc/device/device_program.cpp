@@ -20,6 +20,12 @@ void cu(cudaError_t e, const char* what) {
 void kernel(int rc, const std::string& what) {
   if (rc != 0) fail(ErrorKind::Backend, "device program: " + what + " failed: " + ifab_error_string(rc) + " (code " + std::to_string(rc) + ")");
 }
+// every device allocation of the executor goes through here, so "nothing is allocated after readiness" is a counted fact
+uint64_t g_device_allocations = 0;
+void dmalloc(void** out, uint64_t bytes, const char* what) {
+  cu(cudaMalloc(out, std::max<uint64_t>(bytes, 16)), what);
+  ++g_device_allocations;
+}
 uint64_t fnv1a64(std::string_view s) {
   uint64_t h = 0xcbf29ce484222325ull;
   for (unsigned char c : s) h = (h ^ c) * 0x100000001b3ull;
@@ -59,7 +65,7 @@ class CudaMemory : public init::DeviceMemory {
   }
   void allocate(const init::Parameter& p) override {
     void* d = nullptr;
-    cu(cudaMalloc(&d, std::max<uint64_t>(p.bytes(), 16)), "parameter allocation");
+    dmalloc(&d, p.bytes(), "parameter allocation");
     ptr[p.id] = d;
     size[p.id] = p.bytes();
   }
@@ -143,7 +149,7 @@ struct DeviceProgram::Impl {
   std::map<int, cudaGraphExec_t> graphs;
   uint64_t launches = 0, steps = 0, h2d = 0, d2h = 0;
   uint64_t launches_per_step_last = 0;
-  size_t free_at_ready = 0;
+  uint64_t allocations_at_ready = 0;
   bool ready = false;
 
   ~Impl() {
@@ -243,7 +249,7 @@ void DeviceProgram::Impl::load(const std::string& bundle, const std::string& che
   workspace_bytes = std::stoull(ws[3]);
   const uint64_t ctl_bytes = 4096;
   block_bytes = arena_bytes + workspace_bytes + ctl_bytes;
-  cu(cudaMalloc((void**)&block, block_bytes), "arena block");
+  dmalloc((void**)&block, block_bytes, "arena block");
   cu(cudaMemset(block, 0, block_bytes), "arena clear");
   char* ctl = block + arena_bytes + workspace_bytes;
   d_tokens = (int32_t*)ctl;
@@ -259,7 +265,7 @@ void DeviceProgram::Impl::load(const std::string& bundle, const std::string& che
   num_pages = max_pages * (int)residents;
   std::vector<int32_t> table((size_t)num_pages);
   for (int i = 0; i < num_pages; ++i) table[(size_t)i] = i;
-  cu(cudaMalloc((void**)&d_page_table, table.size() * 4), "page table");
+  dmalloc((void**)&d_page_table, table.size() * 4, "page table");
   cu(cudaMemcpy(d_page_table, table.data(), table.size() * 4, cudaMemcpyHostToDevice), "page table upload");
   max_splits = std::max(1, std::min(64, ((int)context + kps - 1) / kps));
   while ((long)max_splits * kps < (long)context) kps *= 2;
@@ -268,7 +274,7 @@ void DeviceProgram::Impl::load(const std::string& bundle, const std::string& che
     const uint64_t data_half = 4 << 20, flag_half_words = 8 * 296, ll_half = 2 << 20;
     const uint64_t flag_bytes = (2 * flag_half_words * 8 + 255) / 256 * 256;
     const uint64_t off_flags = 2 * data_half, off_ctl = off_flags + flag_bytes, off_ll = off_ctl + 256, total = off_ll + 2 * ll_half;
-    cu(cudaMalloc((void**)&fabric_block, total), "fabric block");
+    dmalloc((void**)&fabric_block, total, "fabric block");
     cu(cudaMemset(fabric_block, 0, total), "fabric clear");
     fab.data[0] = fabric_block;
     fab.flags[0] = (uint64_t*)(fabric_block + off_flags);
@@ -294,7 +300,7 @@ void DeviceProgram::Impl::load(const std::string& bundle, const std::string& che
     if (x.op == "mla_kv_write") {
       void* pages = nullptr;
       const uint64_t bytes = (uint64_t)num_pages * page_tokens * x.width * 2;
-      cu(cudaMalloc(&pages, bytes), "KV pages");
+      dmalloc(&pages, bytes, "KV pages");
       cu(cudaMemset(pages, 0, bytes), "KV clear");
       cache_of[k] = pages;
     } else if (x.op == "router_topk") {
@@ -354,8 +360,7 @@ void DeviceProgram::Impl::load(const std::string& bundle, const std::string& che
       head_members.insert(kv.second.write);
       head_members.insert(kv.second.absorb);
     }
-  size_t total = 0;
-  cu(cudaMemGetInfo(&free_at_ready, &total), "cudaMemGetInfo");
+  allocations_at_ready = g_device_allocations;
   ready = true;
 }
 
@@ -558,8 +563,7 @@ Json DeviceProgram::audit() const {
   j.set("parameter_bytes_uploaded", p_->params ? p_->params->uploaded : 0);
   j.set("h2d_bytes", p_->h2d);
   j.set("d2h_bytes", p_->d2h);
-  size_t free_now = 0, total = 0;
-  if (cudaMemGetInfo(&free_now, &total) == cudaSuccess) j.set("device_bytes_allocated_after_ready", (int64_t)p_->free_at_ready - (int64_t)free_now);
+  j.set("device_allocations_after_ready", g_device_allocations - p_->allocations_at_ready);   // this executor's own cudaMalloc calls
   return j;
 }
 
