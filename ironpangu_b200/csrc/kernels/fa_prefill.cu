@@ -5,10 +5,11 @@
 //               panels (one stage), all 128-byte-swizzled [128 rows x 64 columns] boxes, never multicast
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma: S_j = Q K_j^T into one of two TMEM score buffers (so
 //               S_{j+1} is computed while the softmax warps work on S_j), then O_j = P_j V_j once P_j is in shared memory
-//   warps 4-7   one query row per thread: tcgen05.ld the scores, mask, running max / sum in base 2, write P_j (bf16) into
-//               shared memory in the swizzled operand layout, and fold the per-tile product O_j (read back from TMEM) into
-//               a register accumulator with the usual correction factor. Keeping the running output in registers means no
-//               tcgen05.st and no read-modify-write of TMEM when the row maximum moves.
+//   warps 4-7   one query row per thread: ONE tcgen05.ld pass over the row's 128 scores (kept in registers), mask, exp2 against
+//               the row's reference maximum, running sum, P_j (bf16) into shared memory in the swizzled operand layout. The
+//               output accumulates in TMEM (O += P_j V_j by the MMA itself); the reference maximum of a row only moves when a
+//               tile's maximum exceeds it by more than 8 (a factor 256 of headroom in the f32 accumulator and in bf16 P), and
+//               only then is the row of O rescaled in place (tcgen05.ld, multiply, tcgen05.st) - rarely after the first tiles.
 //
 // Operands are what the multi-head-latent prompt path has at hand: the per-head key part (up-projected latent, D1 columns)
 // and a second key part shared by all heads (the rotary columns, D2), so S = Q1 K1^T + Q2 K2^T accumulates over 64-column
@@ -164,7 +165,7 @@ __global__ void __launch_bounds__(256, 1) fa_prefill_kernel(const __grid_constan
       for (int pp = 0; pp < PV_PANELS; ++pp) {
         const uint64_t da = umma_desc_sw128(pa + pp * PANEL_BYTES), db = umma_desc_sw128(va + pp * PANEL_BYTES);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_bf16(tmem + O_COL, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, pp > 0 || k > 0);
+        for (int k = 0; k < 4; ++k) umma_bf16(tmem + O_COL, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, j > 0 || pp > 0 || k > 0);
       }
       umma_commit(&B->o_full);
       umma_commit(&B->v_empty);
@@ -176,86 +177,84 @@ __global__ void __launch_bounds__(256, 1) fa_prefill_kernel(const __grid_constan
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int q_pos = p.pos0 + q0 + r;
     const int lo = p.window > 0 ? q_pos - p.window + 1 : 0;     // first visible key
-    float o[DV];
-#pragma unroll
-    for (int i = 0; i < DV; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
+    float m_ref = -INFINITY, l_run = 0.f;     // reference maximum (base-2 domain, may lag the true maximum by up to 8) and running sum
     bool ok = true;
     unsigned char* prow = Ps + (r >> 3) * 1024 + (r & 7) * 128;
+    const uint32_t o_addr = tmem + lane_addr + O_COL;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int key0 = (t_begin + j) * BKEY, s = j & 1;
-      if (!mbar_wait(&B->s_full[s], (j >> 1) & 1, p.spin_limit) || *abort_flag) { ok = false; break; }
+      // the warp leaves the loop together: the TMEM accesses and the vote below are warp-wide
+      if (!__all_sync(0xffffffffu, mbar_wait(&B->s_full[s], (j >> 1) & 1, p.spin_limit) && !*abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t s_addr = tmem + lane_addr + S_COL + (uint32_t)s * 128u;
+      float sv[BKEY];
+#pragma unroll
+      for (int c0 = 0; c0 < BKEY; c0 += 32) tmem_ld_32x32(s_addr + (uint32_t)c0, sv + c0);
+      tmem_ld_wait();
       float tile_max = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BKEY; c0 += 32) {
-        float v[32];
-        tmem_ld_32x32(s_addr + (uint32_t)c0, v);
-        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + c0 + i;
-          if (key <= q_pos && key >= lo) tile_max = fmaxf(tile_max, v[i] * p.scale_log2);
-        }
+      for (int i = 0; i < BKEY; ++i) {
+        const int key = key0 + i;
+        sv[i] = (key <= q_pos && key >= lo) ? sv[i] * p.scale_log2 : -INFINITY;
+        tile_max = fmaxf(tile_max, sv[i]);
       }
-      const float m_new = fmaxf(m_run, tile_max);
-      const float corr = (m_new == -INFINITY) ? 1.f : exp2f(m_run - m_new);
-      if (j > 0) {
-        // O_{j-1} = P_{j-1} V_{j-1} is complete (which also frees the P buffer): fold it in with the factor of ITS tile
-        if (!mbar_wait(&B->o_full, (j - 1) & 1, p.spin_limit) || *abort_flag) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int c0 = 0; c0 < DV; c0 += 32) {
-          float v[32];
-          tmem_ld_32x32(tmem + lane_addr + O_COL + (uint32_t)c0, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], corr_prev, v[i]);
-        }
-      }
+      const bool moved = tile_max > m_ref + 8.f;                 // also true for the first visible key (m_ref = -inf)
+      const float m_new = moved ? tile_max : m_ref;
+      const float corr = (moved && m_ref != -INFINITY) ? exp2f(m_ref - m_new) : 1.f;
       float row_sum = 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BKEY; c0 += 32) {
-        float v[32];
-        tmem_ld_32x32(s_addr + (uint32_t)c0, v);
-        tmem_ld_wait();
+      uint4 packed[BKEY / 8];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + c0 + i;
-          const bool visible = key <= q_pos && key >= lo;
-          v[i] = visible ? exp2f(v[i] * p.scale_log2 - m_new) : 0.f;
-          row_sum += v[i];
-        }
-        // 32 keys = four 16-byte chunks of this row's 128-byte line in panel c0 / 64; chunk c sits at position c ^ (row % 8)
-        unsigned char* panel = prow + (c0 >> 6) * PANEL_BYTES;
+      for (int g = 0; g < BKEY / 8; ++g) {
+        float e[8];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int chunk = ((c0 & 63) >> 3) + g;
-          *reinterpret_cast<uint4*>(panel + ((chunk ^ (r & 7)) << 4)) = pack8(v + 8 * g);
+        for (int i = 0; i < 8; ++i) {
+          e[i] = sv[8 * g + i] == -INFINITY ? 0.f : exp2f(sv[8 * g + i] - m_new);
+          row_sum += e[i];
         }
+        packed[g] = pack8(e);
+      }
+      if (j > 0) {
+        // P_{j-1} V_{j-1} has completed: the P buffer is free and O is at rest until the next product is issued
+        if (!__all_sync(0xffffffffu, mbar_wait(&B->o_full, (j - 1) & 1, p.spin_limit) && !*abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, corr != 1.f)) {              // tcgen05.ld / st are warp-wide: rows that did not move scale by 1
+#pragma unroll
+          for (int c0 = 0; c0 < DV; c0 += 32) {
+            float v[32];
+            tmem_ld_32x32(o_addr + (uint32_t)c0, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= corr;
+            tmem_st_32x32(o_addr + (uint32_t)c0, v);
+          }
+          tmem_st_wait();
+        }
+      }
+      // 8 keys = one 16-byte chunk of this row's 128-byte line in panel key / 64; chunk c sits at position c ^ (row % 8)
+#pragma unroll
+      for (int g = 0; g < BKEY / 8; ++g) {
+        unsigned char* panel = prow + (g >> 3) * PANEL_BYTES;
+        *reinterpret_cast<uint4*>(panel + (((g & 7) ^ (r & 7)) << 4)) = packed[g];
       }
       l_run = l_run * corr + row_sum;
-      m_run = m_new;
-      corr_prev = corr;
+      m_ref = m_new;
       fence_proxy_async_smem();       // the tensor core reads P through the async proxy
-      tc_fence_before();              // and this thread's TMEM loads of S_j and O_{j-1} are done
+      tc_fence_before();              // and this thread's TMEM accesses (S_j, the rescale of O) are done
       mbar_arrive(&B->p_ready);
     }
+    float o[DV];
     if (ok && n_tiles > 0) {
-      if (mbar_wait(&B->o_full, (n_tiles - 1) & 1, p.spin_limit) && !*abort_flag) {
+      if (__all_sync(0xffffffffu, mbar_wait(&B->o_full, (n_tiles - 1) & 1, p.spin_limit) && !*abort_flag)) {
         tc_fence_after();
 #pragma unroll
-        for (int c0 = 0; c0 < DV; c0 += 32) {
-          float v[32];
-          tmem_ld_32x32(tmem + lane_addr + O_COL + (uint32_t)c0, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], corr_prev, v[i]);
-        }
+        for (int c0 = 0; c0 < DV; c0 += 32) tmem_ld_32x32(o_addr + (uint32_t)c0, o + c0);
+        tmem_ld_wait();
       } else {
         ok = false;
       }
+    } else {
+#pragma unroll
+      for (int i = 0; i < DV; ++i) o[i] = 0.f;
     }
     if (!ok) {
       if (lane == 0) fail();
