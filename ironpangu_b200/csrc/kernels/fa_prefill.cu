@@ -5,7 +5,9 @@
 //               panels (one stage), all 128-byte-swizzled [128 rows x 64 columns] boxes, never multicast
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma: S_j = Q K_j^T into one of two TMEM score buffers (so
 //               S_{j+1} is computed while the softmax warps work on S_j), then O_j = P_j V_j once P_j is in shared memory
-//   warps 4-7   one query row per thread: ONE tcgen05.ld pass over the row's 128 scores (kept in registers), mask, exp2 against
+//   warps 4-11  two threads per query row (warps w and w + 4 share a TMEM lane quarter; each owns half of the tile's key
+//               columns and half of the output columns; they agree on the tile maximum through shared memory and a 64-thread
+//               named barrier): ONE tcgen05.ld pass over the scores (kept in registers), mask, exp2 against
 //               the row's reference maximum, running sum, P_j (bf16) into shared memory in the swizzled operand layout. The
 //               output accumulates in TMEM (O += P_j V_j by the MMA itself); the reference maximum of a row only moves when a
 //               tile's maximum exceeds it by more than 8 (a factor 256 of headroom in the f32 accumulator and in bf16 P), and
@@ -55,11 +57,12 @@ struct Layout {
   static constexpr int V_OFF = K_OFF + 2 * NQ * PANEL_BYTES;
   static constexpr int P_OFF = V_OFF + PV_PANELS * PANEL_BYTES;
   static constexpr int BAR_OFF = P_OFF + PV_PANELS * PANEL_BYTES;
-  static constexpr int SMEM = BAR_OFF + 256 + 1024;
+  static constexpr int XCH_OFF = BAR_OFF + 256;            // [2 parities][2 column halves][128 rows] tagged 8-byte words: the two threads of a row
+  static constexpr int SMEM = XCH_OFF + 4096 + 1024;
 };
 
 template <int P1, int P2>
-__global__ void __launch_bounds__(256, 1) fa_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+__global__ void __launch_bounds__(384, 1) fa_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                                                             const __grid_constant__ CUtensorMap tmap_k2, const __grid_constant__ CUtensorMap tmap_vt,
                                                             FaParams p) {
   using L = Layout<P1, P2>;
@@ -71,6 +74,7 @@ __global__ void __launch_bounds__(256, 1) fa_prefill_kernel(const __grid_constan
   unsigned char* Vs = smem + L::V_OFF;
   unsigned char* Ps = smem + L::P_OFF;
   Bars* B = reinterpret_cast<Bars*>(smem + L::BAR_OFF);
+  volatile unsigned long long* xch = reinterpret_cast<volatile unsigned long long*>(smem + L::XCH_OFF);
   volatile int* abort_flag = &B->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * BQ, h = blockIdx.y, kvh = h / p.kv_group;
@@ -89,7 +93,7 @@ __global__ void __launch_bounds__(256, 1) fa_prefill_kernel(const __grid_constan
     }
     mbar_init(&B->v_full, 1);
     mbar_init(&B->v_empty, 1);
-    mbar_init(&B->p_ready, 128);
+    mbar_init(&B->p_ready, 256);
     mbar_init(&B->o_full, 1);
     B->abort_flag = 0;
     mbar_fence_init();
@@ -98,6 +102,7 @@ __global__ void __launch_bounds__(256, 1) fa_prefill_kernel(const __grid_constan
     tma_prefetch_desc(&tmap_k2);
     tma_prefetch_desc(&tmap_vt);
   }
+  for (int i = threadIdx.x; i < 512; i += blockDim.x) xch[i] = 0ull;     // call numbers start at 1: a word left by an earlier CTA must not match
   if (warp == 1) tmem_alloc(&B->tmem_slot, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
@@ -172,44 +177,67 @@ __global__ void __launch_bounds__(256, 1) fa_prefill_kernel(const __grid_constan
     }
     if (!ok) fail();
   } else if (warp >= 4) {
-    // ---------------------------------------------------------------- softmax + output, one query row per thread
-    const int quarter = warp & 3, r = quarter * 32 + lane;
+    // ---------------------------------------------------------------- softmax + output: two threads per query row (warps w and w + 4
+    // share a TMEM lane quarter), each owns 64 of the tile's 128 key columns and 64 of the 128 output columns
+    const int quarter = warp & 3, half = (warp - 4) >> 2, r = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int q_pos = p.pos0 + q0 + r;
     const int lo = p.window > 0 ? q_pos - p.window + 1 : 0;     // first visible key
-    float m_ref = -INFINITY, l_run = 0.f;     // reference maximum (base-2 domain, may lag the true maximum by up to 8) and running sum
+    constexpr int HK = BKEY / 2, HV = DV / 2;
+    float m_ref = -INFINITY, l_run = 0.f;     // reference maximum (base-2 domain, may lag the true maximum by up to 8); sum over this thread's columns
     bool ok = true;
-    unsigned char* prow = Ps + (r >> 3) * 1024 + (r & 7) * 128;
-    const uint32_t o_addr = tmem + lane_addr + O_COL;
+    unsigned char* prow = Ps + half * PANEL_BYTES + (r >> 3) * 1024 + (r & 7) * 128;     // this thread's keys are panel `half` of P
+    const uint32_t o_addr = tmem + lane_addr + O_COL + (uint32_t)(half * HV);
+    // The two threads of a row trade one float per call: each publishes (call number, value) as one 8-byte word and polls its
+    // partner's word for the same call number - a bounded wait, unlike a named barrier, so a pair whose partner has given up
+    // gives up too. Slots alternate with the call parity: a slot is rewritten two calls later, after the partner has passed
+    // the call in between, hence after it has read this one.
+    auto trade = [&](float mine, int call, float* other) -> bool {
+      volatile unsigned long long* slot = xch + (call & 1) * 256;
+      slot[half * 128 + r] = ((unsigned long long)(uint32_t)(call + 1) << 32) | __float_as_uint(mine);
+      for (uint32_t spin = 0; spin < p.spin_limit; ++spin) {
+        const unsigned long long w = slot[(half ^ 1) * 128 + r];
+        if ((uint32_t)(w >> 32) == (uint32_t)(call + 1)) {
+          *other = __uint_as_float((uint32_t)w);
+          return true;
+        }
+        if (*abort_flag) return false;
+      }
+      return false;
+    };
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int key0 = (t_begin + j) * BKEY, s = j & 1;
-      // the warp leaves the loop together: the TMEM accesses and the vote below are warp-wide
+      const int key0 = (t_begin + j) * BKEY + half * HK, s = j & 1;
+      // the warp leaves the loop together: the TMEM accesses and the votes below are warp-wide
       if (!__all_sync(0xffffffffu, mbar_wait(&B->s_full[s], (j >> 1) & 1, p.spin_limit) && !*abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t s_addr = tmem + lane_addr + S_COL + (uint32_t)s * 128u;
-      float sv[BKEY];
+      const uint32_t s_addr = tmem + lane_addr + S_COL + (uint32_t)s * 128u + (uint32_t)(half * HK);
+      float sv[HK];
 #pragma unroll
-      for (int c0 = 0; c0 < BKEY; c0 += 32) tmem_ld_32x32(s_addr + (uint32_t)c0, sv + c0);
+      for (int c0 = 0; c0 < HK; c0 += 32) tmem_ld_32x32(s_addr + (uint32_t)c0, sv + c0);
       tmem_ld_wait();
-      float tile_max = -INFINITY;
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four independent chains
 #pragma unroll
-      for (int i = 0; i < BKEY; ++i) {
+      for (int i = 0; i < HK; ++i) {
         const int key = key0 + i;
         sv[i] = (key <= q_pos && key >= lo) ? sv[i] * p.scale_log2 : -INFINITY;
-        tile_max = fmaxf(tile_max, sv[i]);
+        mx[i & 3] = fmaxf(mx[i & 3], sv[i]);
       }
+      const float my_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      float other_max = -INFINITY;
+      if (!__all_sync(0xffffffffu, trade(my_max, j, &other_max))) { ok = false; break; }
+      const float tile_max = fmaxf(my_max, other_max);
       const bool moved = tile_max > m_ref + 8.f;                 // also true for the first visible key (m_ref = -inf)
       const float m_new = moved ? tile_max : m_ref;
       const float corr = (moved && m_ref != -INFINITY) ? exp2f(m_ref - m_new) : 1.f;
-      float row_sum = 0.f;
-      uint4 packed[BKEY / 8];
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      uint4 packed[HK / 8];
 #pragma unroll
-      for (int g = 0; g < BKEY / 8; ++g) {
+      for (int g = 0; g < HK / 8; ++g) {
         float e[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           e[i] = sv[8 * g + i] == -INFINITY ? 0.f : exp2f(sv[8 * g + i] - m_new);
-          row_sum += e[i];
+          sum[i & 3] += e[i];
         }
         packed[g] = pack8(e);
       }
@@ -219,7 +247,7 @@ __global__ void __launch_bounds__(256, 1) fa_prefill_kernel(const __grid_constan
         tc_fence_after();
         if (__any_sync(0xffffffffu, corr != 1.f)) {              // tcgen05.ld / st are warp-wide: rows that did not move scale by 1
 #pragma unroll
-          for (int c0 = 0; c0 < DV; c0 += 32) {
+          for (int c0 = 0; c0 < HV; c0 += 32) {
             float v[32];
             tmem_ld_32x32(o_addr + (uint32_t)c0, v);
             tmem_ld_wait();
@@ -230,39 +258,42 @@ __global__ void __launch_bounds__(256, 1) fa_prefill_kernel(const __grid_constan
           tmem_st_wait();
         }
       }
-      // 8 keys = one 16-byte chunk of this row's 128-byte line in panel key / 64; chunk c sits at position c ^ (row % 8)
+      // 8 keys = one 16-byte chunk of this row's 128-byte line; chunk c sits at position c ^ (row % 8)
 #pragma unroll
-      for (int g = 0; g < BKEY / 8; ++g) {
-        unsigned char* panel = prow + (g >> 3) * PANEL_BYTES;
-        *reinterpret_cast<uint4*>(panel + (((g & 7) ^ (r & 7)) << 4)) = packed[g];
-      }
-      l_run = l_run * corr + row_sum;
+      for (int g = 0; g < HK / 8; ++g) *reinterpret_cast<uint4*>(prow + ((g ^ (r & 7)) << 4)) = packed[g];
+      l_run = l_run * corr + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
       m_ref = m_new;
       fence_proxy_async_smem();       // the tensor core reads P through the async proxy
       tc_fence_before();              // and this thread's TMEM accesses (S_j, the rescale of O) are done
       mbar_arrive(&B->p_ready);
     }
-    float o[DV];
+    float o[HV];
     if (ok && n_tiles > 0) {
       if (__all_sync(0xffffffffu, mbar_wait(&B->o_full, (n_tiles - 1) & 1, p.spin_limit) && !*abort_flag)) {
         tc_fence_after();
 #pragma unroll
-        for (int c0 = 0; c0 < DV; c0 += 32) tmem_ld_32x32(o_addr + (uint32_t)c0, o + c0);
+        for (int c0 = 0; c0 < HV; c0 += 32) tmem_ld_32x32(o_addr + (uint32_t)c0, o + c0);
         tmem_ld_wait();
       } else {
         ok = false;
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < DV; ++i) o[i] = 0.f;
+      for (int i = 0; i < HV; ++i) o[i] = 0.f;
+    }
+    // the row's sum is the sum of its two threads' partial sums
+    if (ok) {
+      float other_sum = 0.f;
+      if (__all_sync(0xffffffffu, trade(l_run, n_tiles, &other_sum))) l_run += other_sum;
+      else ok = false;
     }
     if (!ok) {
       if (lane == 0) fail();
     } else if (q0 + r < p.m) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      bf16* dst = p.out + (long)(q0 + r) * p.ldo + (long)h * DV;
+      bf16* dst = p.out + (long)(q0 + r) * p.ldo + (long)h * DV + half * HV;
 #pragma unroll
-      for (int c = 0; c < DV; c += 8) {
+      for (int c = 0; c < HV; c += 8) {
         float t8[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) t8[i] = o[c + i] * inv;
@@ -283,7 +314,7 @@ int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& t
   auto k = fa_prefill_kernel<P1, P2>;
   if (int rc = opt_in_smem(k, Layout<P1, P2>::SMEM)) return rc;
   dim3 grid((p.m + BQ - 1) / BQ, H);
-  return launch_chain(k, grid, dim3(256), (size_t)Layout<P1, P2>::SMEM, s, tq, tk, tk2, tv, p);
+  return launch_chain(k, grid, dim3(384), (size_t)Layout<P1, P2>::SMEM, s, tq, tk, tk2, tv, p);
 }
 
 }  // namespace
