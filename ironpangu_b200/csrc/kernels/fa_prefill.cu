@@ -5,9 +5,9 @@
 //               panels (one stage), all 128-byte-swizzled [128 rows x 64 columns] boxes, never multicast
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma: S_j = Q K_j^T into one of two TMEM score buffers (so
 //               S_{j+1} is computed while the softmax warps work on S_j), then O_j = P_j V_j once P_j is in shared memory
-//   warps 4-11  two threads per query row (warps w and w + 4 share a TMEM lane quarter; each owns half of the tile's key
-//               columns and half of the output columns; they agree on the tile maximum through shared memory and a 64-thread
-//               named barrier): ONE tcgen05.ld pass over the scores (kept in registers), mask, exp2 against
+//   warps 4-19  four threads per query row (warps w, w + 4, w + 8, w + 12 share a TMEM lane quarter; each owns a quarter of the
+//               tile's key columns and of the output columns; they agree on the tile maximum through tagged words in shared
+//               memory, a bounded exchange): ONE tcgen05.ld pass over the scores (kept in registers), mask, exp2 against
 //               the row's reference maximum, running sum, P_j (bf16) into shared memory in the swizzled operand layout. The
 //               output accumulates in TMEM (O += P_j V_j by the MMA itself); the reference maximum of a row only moves when a
 //               tile's maximum exceeds it by more than 8 (a factor 256 of headroom in the f32 accumulator and in bf16 P), and
@@ -34,6 +34,8 @@ constexpr int PANEL_BYTES = 128 * 128;      // 128 rows x 64 bf16
 constexpr int PV_PANELS = BKEY / 64;        // panels of P (keys along K) and of V^T
 constexpr uint32_t TMEM_COLS = 512;         // S0 [0,128) S1 [128,256) O [256,384)
 constexpr uint32_t S_COL = 0, O_COL = 256;
+constexpr int PARTS = 4;                    // threads per query row: warps w, w + 4, ... of a TMEM lane quarter split the columns
+constexpr int THREADS = 128 + 128 * PARTS;  // warp 0 producer, warp 1 MMA issuer, warps 2-3 idle, then the softmax warps
 
 struct FaParams {
   bf16* out; long ldo;
@@ -58,11 +60,11 @@ struct Layout {
   static constexpr int P_OFF = V_OFF + PV_PANELS * PANEL_BYTES;
   static constexpr int BAR_OFF = P_OFF + PV_PANELS * PANEL_BYTES;
   static constexpr int XCH_OFF = BAR_OFF + 256;            // [2 parities][2 column halves][128 rows] tagged 8-byte words: the two threads of a row
-  static constexpr int SMEM = XCH_OFF + 4096 + 1024;
+  static constexpr int SMEM = XCH_OFF + 2 * PARTS * 128 * 8 + 1024;
 };
 
 template <int P1, int P2>
-__global__ void __launch_bounds__(384, 1) fa_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+__global__ void __launch_bounds__(THREADS, 1) fa_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                                                             const __grid_constant__ CUtensorMap tmap_k2, const __grid_constant__ CUtensorMap tmap_vt,
                                                             FaParams p) {
   using L = Layout<P1, P2>;
@@ -93,7 +95,7 @@ __global__ void __launch_bounds__(384, 1) fa_prefill_kernel(const __grid_constan
     }
     mbar_init(&B->v_full, 1);
     mbar_init(&B->v_empty, 1);
-    mbar_init(&B->p_ready, 256);
+    mbar_init(&B->p_ready, 128 * PARTS);
     mbar_init(&B->o_full, 1);
     B->abort_flag = 0;
     mbar_fence_init();
@@ -102,7 +104,7 @@ __global__ void __launch_bounds__(384, 1) fa_prefill_kernel(const __grid_constan
     tma_prefetch_desc(&tmap_k2);
     tma_prefetch_desc(&tmap_vt);
   }
-  for (int i = threadIdx.x; i < 512; i += blockDim.x) xch[i] = 0ull;     // call numbers start at 1: a word left by an earlier CTA must not match
+  for (int i = threadIdx.x; i < 2 * PARTS * 128; i += blockDim.x) xch[i] = 0ull;     // call numbers start at 1: a word left by an earlier CTA must not match
   if (warp == 1) tmem_alloc(&B->tmem_slot, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
@@ -179,31 +181,44 @@ __global__ void __launch_bounds__(384, 1) fa_prefill_kernel(const __grid_constan
   } else if (warp >= 4) {
     // ---------------------------------------------------------------- softmax + output: two threads per query row (warps w and w + 4
     // share a TMEM lane quarter), each owns 64 of the tile's 128 key columns and 64 of the 128 output columns
-    const int quarter = warp & 3, half = (warp - 4) >> 2, r = quarter * 32 + lane;
+    const int quarter = warp & 3, half = (warp - 4) >> 2, r = quarter * 32 + lane;     // `half`: which of the PARTS column ranges
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int q_pos = p.pos0 + q0 + r;
     const int lo = p.window > 0 ? q_pos - p.window + 1 : 0;     // first visible key
-    constexpr int HK = BKEY / 2, HV = DV / 2;
+    constexpr int HK = BKEY / PARTS, HV = DV / PARTS;
     float m_ref = -INFINITY, l_run = 0.f;     // reference maximum (base-2 domain, may lag the true maximum by up to 8); sum over this thread's columns
     bool ok = true;
-    unsigned char* prow = Ps + half * PANEL_BYTES + (r >> 3) * 1024 + (r & 7) * 128;     // this thread's keys are panel `half` of P
+    // this thread's keys: panel (half * HK) / 64 of P, 16-byte chunks from ((half * HK) % 64) / 8 on
+    unsigned char* prow = Ps + ((half * HK) >> 6) * PANEL_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+    const int chunk0 = ((half * HK) & 63) >> 3;
     const uint32_t o_addr = tmem + lane_addr + O_COL + (uint32_t)(half * HV);
     // The two threads of a row trade one float per call: each publishes (call number, value) as one 8-byte word and polls its
     // partner's word for the same call number - a bounded wait, unlike a named barrier, so a pair whose partner has given up
     // gives up too. Slots alternate with the call parity: a slot is rewritten two calls later, after the partner has passed
     // the call in between, hence after it has read this one.
-    auto trade = [&](float mine, int call, float* other) -> bool {
-      volatile unsigned long long* slot = xch + (call & 1) * 256;
+    // `combine_max`: the maximum over the partners' values, else their sum
+    auto trade = [&](float mine, int call, bool combine_max, float* result) -> bool {
+      volatile unsigned long long* slot = xch + (call & 1) * (PARTS * 128);
       slot[half * 128 + r] = ((unsigned long long)(uint32_t)(call + 1) << 32) | __float_as_uint(mine);
-      for (uint32_t spin = 0; spin < p.spin_limit; ++spin) {
-        const unsigned long long w = slot[(half ^ 1) * 128 + r];
-        if ((uint32_t)(w >> 32) == (uint32_t)(call + 1)) {
-          *other = __uint_as_float((uint32_t)w);
-          return true;
+      float acc = mine;
+#pragma unroll
+      for (int k = 1; k < PARTS; ++k) {
+        const int other = (half + k) % PARTS;
+        bool got = false;
+        for (uint32_t spin = 0; spin < p.spin_limit; ++spin) {
+          const unsigned long long w = slot[other * 128 + r];
+          if ((uint32_t)(w >> 32) == (uint32_t)(call + 1)) {
+            const float v = __uint_as_float((uint32_t)w);
+            acc = combine_max ? fmaxf(acc, v) : acc + v;
+            got = true;
+            break;
+          }
+          if (*abort_flag) break;
         }
-        if (*abort_flag) return false;
+        if (!got) return false;
       }
-      return false;
+      *result = acc;
+      return true;
     };
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int key0 = (t_begin + j) * BKEY + half * HK, s = j & 1;
@@ -223,9 +238,8 @@ __global__ void __launch_bounds__(384, 1) fa_prefill_kernel(const __grid_constan
         mx[i & 3] = fmaxf(mx[i & 3], sv[i]);
       }
       const float my_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      float other_max = -INFINITY;
-      if (!__all_sync(0xffffffffu, trade(my_max, j, &other_max))) { ok = false; break; }
-      const float tile_max = fmaxf(my_max, other_max);
+      float tile_max = -INFINITY;
+      if (!__all_sync(0xffffffffu, trade(my_max, j, true, &tile_max))) { ok = false; break; }
       const bool moved = tile_max > m_ref + 8.f;                 // also true for the first visible key (m_ref = -inf)
       const float m_new = moved ? tile_max : m_ref;
       const float corr = (moved && m_ref != -INFINITY) ? exp2f(m_ref - m_new) : 1.f;
@@ -260,7 +274,7 @@ __global__ void __launch_bounds__(384, 1) fa_prefill_kernel(const __grid_constan
       }
       // 8 keys = one 16-byte chunk of this row's 128-byte line; chunk c sits at position c ^ (row % 8)
 #pragma unroll
-      for (int g = 0; g < HK / 8; ++g) *reinterpret_cast<uint4*>(prow + ((g ^ (r & 7)) << 4)) = packed[g];
+      for (int g = 0; g < HK / 8; ++g) *reinterpret_cast<uint4*>(prow + (((chunk0 + g) ^ (r & 7)) << 4)) = packed[g];
       l_run = l_run * corr + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
       m_ref = m_new;
       fence_proxy_async_smem();       // the tensor core reads P through the async proxy
@@ -283,8 +297,8 @@ __global__ void __launch_bounds__(384, 1) fa_prefill_kernel(const __grid_constan
     }
     // the row's sum is the sum of its two threads' partial sums
     if (ok) {
-      float other_sum = 0.f;
-      if (__all_sync(0xffffffffu, trade(l_run, n_tiles, &other_sum))) l_run += other_sum;
+      float total = 0.f;
+      if (__all_sync(0xffffffffu, trade(l_run, n_tiles, false, &total))) l_run = total;      // every partner adds in its own order: sums may differ in the last bit between columns
       else ok = false;
     }
     if (!ok) {
@@ -314,7 +328,7 @@ int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& t
   auto k = fa_prefill_kernel<P1, P2>;
   if (int rc = opt_in_smem(k, Layout<P1, P2>::SMEM)) return rc;
   dim3 grid((p.m + BQ - 1) / BQ, H);
-  return launch_chain(k, grid, dim3(384), (size_t)Layout<P1, P2>::SMEM, s, tq, tk, tk2, tv, p);
+  return launch_chain(k, grid, dim3(THREADS), (size_t)Layout<P1, P2>::SMEM, s, tq, tk, tk2, tv, p);
 }
 
 }  // namespace
