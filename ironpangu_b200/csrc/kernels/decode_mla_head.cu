@@ -48,6 +48,8 @@ struct HeadParams {
   int T, H, q_lora, nope, vdim;
   bf16* out; long ldo;
   uint32_t* status;
+  // weight ranges of LATER kernels of the layer, requested into L2 while this kernel (a latency-bound chain that leaves HBM idle) runs
+  const char* pf[3]; unsigned long long pf_bytes[3];
 };
 
 // shared-memory carve-up (bytes), identical in every CTA of the cluster
@@ -154,6 +156,12 @@ __global__ void __launch_bounds__(256, (T <= 2 ? 2 : 1)) mla_head_decode_kernel(
   __shared__ int s_pos[8], s_slot[8];
 
   grid_dep_launch();
+  {
+    const long first = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 128, stride = (long)gridDim.x * blockDim.x * 128;
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+      for (long off = first; off < (long)p.pf_bytes[i]; off += stride) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.pf[i] + off));
+  }
   const int cr = (int)cluster.block_rank(), h = blockIdx.x / C;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gw = cr * 8 + warp;
   const int nq = p.nope + ROPE;
@@ -469,18 +477,31 @@ int launch_head(const HeadParams& p, cudaStream_t s) {
 
 // qkv: [T, q_lora + 576] (q latent | kv latent | k_pe), w_qb: [H * (nope + 64), q_lora], w_kvb: [H, nope + vdim, 512],
 // cache: bf16 paged latent cache; out: [T, H * vdim]. T <= 8.
-extern "C" int ifab_mla_head_decode(const void* qkv, long ldqkv, const void* q_norm, const void* kv_norm, float eps, float theta,
-                                    const void* w_qb, const void* w_kvb, void* cache, const int32_t* positions, const int32_t* slots,
-                                    const int32_t* page_table, int max_pages, int page_tokens, int num_pages, const void* sinks,
-                                    int n_sinks, int window, float scale, int T, int H, int q_lora, int nope, int vdim, void* out,
-                                    long ldo, uint32_t* status, void* stream) {
+extern "C" int ifab_mla_head_decode_pf(const void* qkv, long ldqkv, const void* q_norm, const void* kv_norm, float eps, float theta,
+                                       const void* w_qb, const void* w_kvb, void* cache, const int32_t* positions, const int32_t* slots,
+                                       const int32_t* page_table, int max_pages, int page_tokens, int num_pages, const void* sinks,
+                                       int n_sinks, int window, float scale, int T, int H, int q_lora, int nope, int vdim, void* out,
+                                       long ldo, uint32_t* status, const void* pf0, uint64_t pf0_bytes, const void* pf1, uint64_t pf1_bytes,
+                                       const void* pf2, uint64_t pf2_bytes, void* stream) {
   if (T < 1 || T > 8 || H < 1 || q_lora % 8 != 0 || ldqkv % 8 != 0 || nope % 32 != 0 || nope > 128 || vdim > 128 || vdim < 1) return -1;
   HeadParams p{(const bf16*)qkv, ldqkv, (const bf16*)q_norm, (const bf16*)kv_norm, eps, theta, (const bf16*)w_qb, (const bf16*)w_kvb,
                (bf16*)cache, positions, slots, page_table, max_pages, page_tokens, num_pages, (const bf16*)sinks, sinks ? n_sinks : 0,
-               window, scale, T, H, q_lora, nope, vdim, (bf16*)out, ldo, status};
+               window, scale, T, H, q_lora, nope, vdim, (bf16*)out, ldo, status,
+               {(const char*)pf0, (const char*)pf1, (const char*)pf2},
+               {pf0 ? pf0_bytes : 0, pf1 ? pf1_bytes : 0, pf2 ? pf2_bytes : 0}};
   cudaStream_t s = (cudaStream_t)stream;
   if (T <= 1) return launch_head<1>(p, s);
   if (T <= 2) return launch_head<2>(p, s);
   if (T <= 4) return launch_head<4>(p, s);
   return launch_head<8>(p, s);
+}
+
+extern "C" int ifab_mla_head_decode(const void* qkv, long ldqkv, const void* q_norm, const void* kv_norm, float eps, float theta,
+                                    const void* w_qb, const void* w_kvb, void* cache, const int32_t* positions, const int32_t* slots,
+                                    const int32_t* page_table, int max_pages, int page_tokens, int num_pages, const void* sinks,
+                                    int n_sinks, int window, float scale, int T, int H, int q_lora, int nope, int vdim, void* out,
+                                    long ldo, uint32_t* status, void* stream) {
+  return ifab_mla_head_decode_pf(qkv, ldqkv, q_norm, kv_norm, eps, theta, w_qb, w_kvb, cache, positions, slots, page_table, max_pages, page_tokens,
+                                 num_pages, sinks, n_sinks, window, scale, T, H, q_lora, nope, vdim, out, ldo, status, nullptr, 0, nullptr, 0, nullptr, 0,
+                                 stream);
 }

@@ -189,6 +189,14 @@ int ifab_mla_head_decode(const void* qkv, long ldqkv, const void* q_norm, const 
                          int n_sinks, int window, float scale, int T, int H, int q_lora, int nope, int vdim, void* out,
                          long ldo, uint32_t* status, void* stream);
 
+/* The same, and while it runs its CTAs request up to three byte ranges (weights of the layer's later kernels) into L2. */
+int ifab_mla_head_decode_pf(const void* qkv, long ldqkv, const void* q_norm, const void* kv_norm, float eps, float theta,
+                            const void* w_qb, const void* w_kvb, void* cache, const int32_t* positions, const int32_t* slots,
+                            const int32_t* page_table, int max_pages, int page_tokens, int num_pages, const void* sinks,
+                            int n_sinks, int window, float scale, int T, int H, int q_lora, int nope, int vdim, void* out,
+                            long ldo, uint32_t* status, const void* pf0, uint64_t pf0_bytes, const void* pf1, uint64_t pf1_bytes,
+                            const void* pf2, uint64_t pf2_bytes, void* stream);
+
 /* ---- hyper-connection / hybrid-model operators (hc_ops.cu); all mixing arithmetic in f32 ---- */
 /* causal depthwise conv with residual; w f32 [C_total, taps] (this rank's channels start at c_offset); state bf16 [slots, taps-1, C] */
 int ifab_mome(const void* x, long ldx, const float* w, void* state, const int32_t* positions, const int32_t* slots, void* y,

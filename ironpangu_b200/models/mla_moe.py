@@ -185,7 +185,8 @@ class MlaMoeDecoder:
     def __init__(self, cfg: MlaMoeConfig, weights: Dict[str, torch.Tensor], fabric: Fabric, *, max_tokens: int = 1,
                  max_context: int = 1024, num_slots: int = 1, keys_per_split: int = 64, keep_logits: bool = False,
                  kv_int8: bool = False, expert_fp8: bool = False, drop_bf16_experts: bool = True,
-                 fused_head: Optional[bool] = None, shard: Optional[tuple] = None, fused_moe: Optional[bool] = None):
+                 fused_head: Optional[bool] = None, shard: Optional[tuple] = None, fused_moe: Optional[bool] = None,
+                 l2_prefetch: Optional[bool] = None):
         """``kv_int8``: keep the latent cache as packed int8 rows (656 bytes per token instead of 1152).
         ``expert_fp8``: quantise the routed and shared expert matrices to block-scaled fp8 (1 x 128 scale blocks) at
         construction and decode over them; with ``drop_bf16_experts`` the bf16 originals leave ``weights``.
@@ -199,6 +200,9 @@ class MlaMoeDecoder:
         ``shard``: ``(rank, world)`` of the weight shard when it differs from the fabric's (a profiling aid: one GPU runs the
         kernels of rank r of an N-rank job at their real shapes, without the peers; the sums it computes are partial)."""
         assert 1 <= max_tokens <= 8
+        # the head kernel asks for the weights of the layer's next kernels (o_proj, shared expert) while it runs: it is a
+        # latency-bound chain that leaves HBM idle
+        self.l2_prefetch = True if l2_prefetch is None else bool(l2_prefetch)
         self.kv_int8 = kv_int8
         self.expert_fp8 = expert_fp8
         can_fuse = (not kv_int8 and cfg.kv_lora == 512 and cfg.rope == 64 and cfg.nope % 32 == 0 and cfg.nope <= 128 and
@@ -325,7 +329,8 @@ class MlaMoeDecoder:
             if fuse and T <= self.fused_head_rows:
                 K.mla_head_decode(qkv, w[p + "q_a_norm"], w[p + "kv_a_norm"], w[p + "q_b"], w[p + "kv_b"], self.caches[l], pos, slot,
                                   self.page_table, q_lora=c.q_lora, nope=c.nope, scale=c.scale, eps=c.eps, theta=c.theta,
-                                  window=c.window, out=self.attn[:T], status_ptr=st)
+                                  window=c.window, out=self.attn[:T], status_ptr=st,
+                                  prefetch=(w[p + "o_proj"], w.get(p + "shared_gate_up"), w.get(p + "shared_down")) if self.l2_prefetch else ())
                 self._ffn(l, T)
                 continue
             if self.kv_int8:

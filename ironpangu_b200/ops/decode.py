@@ -190,21 +190,26 @@ def moe_block(x: torch.Tensor, w_router: torch.Tensor, w_gu: torch.Tensor, w_dow
 def mla_head_decode(qkv: torch.Tensor, q_norm: torch.Tensor, kv_norm: torch.Tensor, w_qb: torch.Tensor, w_kvb: torch.Tensor,
                     cache: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor, *, q_lora: int,
                     nope: int, scale: float, eps: float = 1e-5, theta: float = 10000.0, window: int = 0,
-                    sinks: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, status_ptr=None) -> torch.Tensor:
+                    sinks: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, status_ptr=None,
+                    prefetch=()) -> torch.Tensor:
     """The attention half of an MLA decode layer in one launch (a cluster of 8 CTAs per head): cache write, q_b, absorb,
     attention over the paged latent cache and value up-projection. ``qkv``: ``[T, q_lora + 576]`` output of the qkv_a
-    linear; ``w_qb``: ``[H * (nope + 64), q_lora]``; ``w_kvb``: ``[H, nope + vdim, 512]``; returns ``[T, H * vdim]``."""
+    linear; ``w_qb``: ``[H * (nope + 64), q_lora]``; ``w_kvb``: ``[H, nope + vdim, 512]``; returns ``[T, H * vdim]``.
+    ``prefetch``: up to three contiguous tensors (weights of the layer's later kernels) the kernel requests into L2 while it runs."""
     T = qkv.shape[0]
     H, nv, latent = w_kvb.shape
     vdim = nv - nope
     assert latent == 512 and qkv.shape[1] == q_lora + 576 and cache.dtype == BF16
     if out is None:
         out = torch.empty(T, H * vdim, dtype=BF16, device=qkv.device)
-    check(_lib.load().ifab_mla_head_decode(qkv.data_ptr(), _rows(qkv), q_norm.data_ptr(), kv_norm.data_ptr(), eps, theta, w_qb.data_ptr(),
-                                           w_kvb.data_ptr(), cache.data_ptr(), positions.data_ptr(), slots.data_ptr(),
-                                           page_table.data_ptr(), page_table.shape[1], cache.shape[1], cache.shape[0], _ptr(sinks),
-                                           0 if sinks is None else sinks.shape[0], window, scale, T, H, q_lora, nope, vdim,
-                                           out.data_ptr(), _rows(out), status_ptr, _stream()), "mla_head_decode")
+    pf = [(t.data_ptr(), t.numel() * t.element_size()) for t in prefetch if t is not None][:3]
+    pf += [(None, 0)] * (3 - len(pf))
+    check(_lib.load().ifab_mla_head_decode_pf(qkv.data_ptr(), _rows(qkv), q_norm.data_ptr(), kv_norm.data_ptr(), eps, theta, w_qb.data_ptr(),
+                                              w_kvb.data_ptr(), cache.data_ptr(), positions.data_ptr(), slots.data_ptr(),
+                                              page_table.data_ptr(), page_table.shape[1], cache.shape[1], cache.shape[0], _ptr(sinks),
+                                              0 if sinks is None else sinks.shape[0], window, scale, T, H, q_lora, nope, vdim,
+                                              out.data_ptr(), _rows(out), status_ptr, pf[0][0], pf[0][1], pf[1][0], pf[1][1], pf[2][0], pf[2][1],
+                                              _stream()), "mla_head_decode")
     return out
 
 

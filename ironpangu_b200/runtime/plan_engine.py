@@ -205,7 +205,7 @@ class PlanEngine:
 
     def __init__(self, bundle_dir: str, checkpoint_dir: Optional[str], fabric: Fabric, *, max_tokens: Optional[int] = 8,
                  num_slots: int = 1, keep_logits: bool = False, parameters: Optional[Dict[str, torch.Tensor]] = None,
-                 fused_head: Optional[bool] = None, fused_moe: Optional[bool] = None):
+                 fused_head: Optional[bool] = None, fused_moe: Optional[bool] = None, l2_prefetch: Optional[bool] = None):
         """``max_tokens``: query rows per step (at most 8); ``None`` takes what the bundle's arena was planned for.
         ``parameters``: device tensors by the init plan's parameter names, used instead of a checkpoint (random-init
         benchmarks, weights another engine already holds); every parameter of the plan must be there with the plan's
@@ -255,6 +255,7 @@ class PlanEngine:
         self.arena = FrozenArena(b, self.rank, T, dev)
         self._alloc(dev)
         self.bundle_sha256 = json.loads((b / "plan.json").read_text()).get("program_sha256", "")
+        self.l2_prefetch = True if l2_prefetch is None else bool(l2_prefetch)
         self._prepare(fused_head, fused_moe)
         self._graph = None
 
@@ -346,6 +347,18 @@ class PlanEngine:
         self._router_shares_norm = {g["router"] for g in self.moe_groups.values() if g["ok"] and "norm_weight" in self.ins[g["router"]]["attrs"]}
         hidden = max((self.ins[self.ins[r]["inputs"][0]]["width"] for r in self._router_shares_norm), default=0)
         self.xn = self.arena.workspace(self.T * hidden * 2).view(BF16).view(self.T, hidden) if hidden else None
+        # what the head kernel of a layer requests into L2 for the kernels after it: the output projection that consumes the
+        # attention result and the shared expert of the layer's expert block (routed experts are not known yet)
+        self._head_prefetch: Dict[int, tuple] = {}
+        moe_order = sorted(self.moe_groups)
+        for kh in sorted(self.head_groups):
+            o = next((u for u in users.get(kh, []) if ins[u]["op"] == "linear_allreduce"), None)
+            km = next((m for m in moe_order if m > kh), None)
+            pf = [self.P.get(ins[o]["attrs"]["weight"])] if o is not None else []
+            if km is not None and self.moe_groups[km]["ok"]:
+                gu, dn = ins[self.moe_groups[km]["gate_up"]]["attrs"], ins[km]["attrs"]
+                pf += [self.P.get(gu["shared_weight"] + "|" + gu["shared_paired_weight"]), self.P.get(dn["shared_weight"])]
+            self._head_prefetch[kh] = tuple(t for t in pf if t is not None)
         # members of a group that the anchor's kernel covers
         self._head_members = {m: k for k, g in self.head_groups.items() for m in g["members"]}
         self._moe_members = {m: k for k, g in self.moe_groups.items() for m in g["members"]}
@@ -488,7 +501,7 @@ class PlanEngine:
                 K.mla_head_decode(val(g["qkv"]), self._param(g["q_norm"]), self._param(g["kv_norm"]), self._param(g["w_qb"]),
                                   self._param(g["w_kvb"]).view(hl, g["nope"] + g["vdim"], 512), self._cache_of[g["cache"]], pos, slot,
                                   self.page_table, q_lora=g["q_lora"], nope=g["nope"], scale=g["scale"], eps=g["eps"], theta=g["theta"],
-                                  window=g["window"], out=val(k), status_ptr=st)
+                                  window=g["window"], out=val(k), status_ptr=st, prefetch=self._head_prefetch.get(k, ()) if self.l2_prefetch else ())
             elif moe and k in self.moe_groups:
                 g = self.moe_groups[k]
                 r, gu = self.ins[g["router"]]["attrs"], self.ins[g["gate_up"]]["attrs"]
