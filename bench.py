@@ -47,7 +47,7 @@ def parse():
     ap.add_argument("--executor", default="bundle", choices=["bundle", "model"],
                     help="native arm, bf16 MLA+MoE models: 'bundle' compiles the model's .inferfabric source and runs the bundle's "
                          "program (runtime/plan_engine.py); 'model' runs the hand-wired decoder class (models/mla_moe.py)")
-    ap.add_argument("--l2-prefetch", type=int, default=-1, help="-1: default (on); 0/1: the attention kernel requests the layer's next weights into L2")
+    ap.add_argument("--l2-prefetch", type=int, default=-1, help="-1: default (off); 1: the attention kernel requests the layer's next weights (o_proj, shared expert) into L2; 2: o_proj only")
     ap.add_argument("--fused-moe", type=int, default=-1, help="-1: decoder default; 0/1: MoE half of a layer as three launches / one")
     return ap.parse_args()
 
@@ -232,7 +232,7 @@ def main():
         compiled = compiler.write_bundle(src, os.path.join(work, "bundle"), prefill_tokens=8)
         dec = PlanEngine(compiled["dir"], None, fab, max_tokens=8, num_slots=1, parameters=bundle_parameters(cfg, weights),
                          fused_moe=None if args.fused_moe < 0 else bool(args.fused_moe),
-                         l2_prefetch=None if args.l2_prefetch < 0 else bool(args.l2_prefetch))
+                         l2_prefetch=None if args.l2_prefetch < 0 else args.l2_prefetch)
         bundle_sha = compiled["program_sha256"]
     elif args.impl == "native":
         dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1,

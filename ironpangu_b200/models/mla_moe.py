@@ -200,9 +200,9 @@ class MlaMoeDecoder:
         ``shard``: ``(rank, world)`` of the weight shard when it differs from the fabric's (a profiling aid: one GPU runs the
         kernels of rank r of an N-rank job at their real shapes, without the peers; the sums it computes are partial)."""
         assert 1 <= max_tokens <= 8
-        # the head kernel asks for the weights of the layer's next kernels (o_proj, shared expert) while it runs: it is a
-        # latency-bound chain that leaves HBM idle
-        self.l2_prefetch = True if l2_prefetch is None else bool(l2_prefetch)
+        # the head kernel can ask for the weights of the layer's next kernels (o_proj, shared expert) while it runs; measured
+        # 3.4 % slower at one GPU (the requests compete with the kernel's own loads), so off unless asked for
+        self.l2_prefetch = False if l2_prefetch is None else bool(l2_prefetch)
         self.kv_int8 = kv_int8
         self.expert_fp8 = expert_fp8
         can_fuse = (not kv_int8 and cfg.kv_lora == 512 and cfg.rope == 64 and cfg.nope % 32 == 0 and cfg.nope <= 128 and

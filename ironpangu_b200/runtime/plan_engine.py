@@ -255,7 +255,9 @@ class PlanEngine:
         self.arena = FrozenArena(b, self.rank, T, dev)
         self._alloc(dev)
         self.bundle_sha256 = json.loads((b / "plan.json").read_text()).get("program_sha256", "")
-        self.l2_prefetch = True if l2_prefetch is None else bool(l2_prefetch)
+        # measured at one GPU: requesting o_proj + shared expert (72 MB per layer) during the attention kernel costs 3.4 % (5.58 vs
+        # 5.39 ms per step): the requests compete with the kernel's own loads. Off unless asked for; 2 = the output projection only.
+        self.l2_prefetch = 0 if l2_prefetch is None else int(l2_prefetch)
         self._prepare(fused_head, fused_moe)
         self._graph = None
 
@@ -501,7 +503,7 @@ class PlanEngine:
                 K.mla_head_decode(val(g["qkv"]), self._param(g["q_norm"]), self._param(g["kv_norm"]), self._param(g["w_qb"]),
                                   self._param(g["w_kvb"]).view(hl, g["nope"] + g["vdim"], 512), self._cache_of[g["cache"]], pos, slot,
                                   self.page_table, q_lora=g["q_lora"], nope=g["nope"], scale=g["scale"], eps=g["eps"], theta=g["theta"],
-                                  window=g["window"], out=val(k), status_ptr=st, prefetch=self._head_prefetch.get(k, ()) if self.l2_prefetch else ())
+                                  window=g["window"], out=val(k), status_ptr=st, prefetch=self._head_prefetch.get(k, ())[:1 if self.l2_prefetch == 2 else 3] if self.l2_prefetch else ())
             elif moe and k in self.moe_groups:
                 g = self.moe_groups[k]
                 r, gu = self.ins[g["router"]]["attrs"], self.ins[g["gate_up"]]["attrs"]
