@@ -31,9 +31,9 @@ struct RouterBlockParams {
   int M, D, E, topk, scoring, renorm; float scale;
 };
 
-// one CTA per 8 tokens; warps stride over the experts, then warp t selects for token t
+// one CTA per T tokens (8, or 4 when that is what fills the SMs); warps stride over the experts, then warp t selects for token t
+template <int T>
 __global__ void __launch_bounds__(256) router_block_kernel(RouterBlockParams p) {
-  constexpr int T = 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* xs = reinterpret_cast<bf16*>(smem_raw);               // [8][D] normalised
   float* lg = reinterpret_cast<float*>(xs + (size_t)T * p.D); // [8][E]
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(256) router_block_kernel(RouterBlockParams p) 
   }
   __syncthreads();
   const int t = warp;
-  if (t0 + t >= p.M) return;
+  if (t >= T || t0 + t >= p.M) return;
   constexpr int PER = 8;
   float score[PER], sel[PER];
   float mx = -INFINITY;
@@ -160,75 +160,87 @@ struct DispatchParams {
   int32_t* route_row;   // [M * topk]: row in the permuted matrix, -1 when the expert lives on another rank
   int32_t* perm_token;  // [M * topk]: token of permuted row r
   int4* tiles; int32_t* num_tiles; int32_t* total_rows; int max_tiles;
-  int smem_routes;      // routes whose local expert ids fit the dynamic shared memory of the launch
 };
 
-// single CTA of 1024 threads: warp w ranks the routes of experts w, w + 32, ... with ballot prefix sums, so the order
-// inside an expert is the route order (token-major) and the result does not depend on thread timing
+// Single CTA of 1024 threads. Every warp owns a contiguous segment of the routes (route order = token-major), so the order inside
+// an expert is the route order and the result does not depend on thread timing:
+//   1  per warp and expert: how many routes of the segment go to the expert (lanes with the same expert find one another with
+//      match.any; the lowest lane of a group adds the group's size to the warp's histogram in shared memory)
+//   2  per expert: exclusive scan of the warps' counts (one thread per expert), then expert offsets, counts and the tile table
+//   3  per warp: walk the segment again; a route's row = expert offset + routes of earlier warps + routes seen so far in this warp
+//      + its rank inside the 32-route group
+// Work per warp is its segment twice, instead of every route once per expert.
 __global__ void __launch_bounds__(1024) moe_dispatch_kernel(DispatchParams p) {
-  __shared__ int s_count[MAX_LOCAL];
   __shared__ int s_off[MAX_LOCAL + 1];
+  extern __shared__ int s_hist[];          // [32 warps][el]: counts, then running row offsets
   grid_dep_launch();
   grid_dep_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int R = p.M * p.topk;
-  // the local expert of every route (or -1), staged once: the ballot scans below would otherwise wait on a global load each
-  extern __shared__ short s_loc[];
-  const bool staged = R <= p.smem_routes;
-  if (staged) {
-    for (int i = threadIdx.x; i < R; i += blockDim.x) {
-      const int e = p.ids[i] - p.e0;
-      s_loc[i] = (short)((e >= 0 && e < p.el) ? e : -1);
+  const int R = p.M * p.topk, el = p.el;
+  const int per_warp = ((R + 31) / 32 + 31) / 32 * 32;       // segment length, a multiple of 32
+  const int seg0 = warp * per_warp, seg1 = min(R, seg0 + per_warp);
+  for (int i = threadIdx.x; i < 32 * el; i += blockDim.x) s_hist[i] = 0;
+  __syncthreads();
+  int* hist = s_hist + warp * el;
+  for (int i0 = seg0; i0 < seg1; i0 += 32) {
+    const int i = i0 + lane;
+    int e = -1;
+    if (i < seg1) {
+      e = p.ids[i] - p.e0;
+      if (e < 0 || e >= el) {
+        e = -1;
+        p.route_row[i] = -1;                 // the expert lives on another rank
+      }
     }
-    __syncthreads();
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && (same & ((1u << lane) - 1)) == 0) hist[e] += __popc(same);     // one lane per expert per group: no two lanes touch a word
+    __syncwarp();
   }
-  auto local_of = [&](int i) -> int { return staged ? (int)s_loc[i] : p.ids[i] - p.e0; };
-  // pass 1: counts
-  for (int e = warp; e < p.el; e += 32) {
-    int n = 0;
-    for (int i0 = 0; i0 < R; i0 += 32) {
-      const int i = i0 + lane;
-      const bool hit = i < R && local_of(i) == e;
-      n += __popc(__ballot_sync(0xffffffffu, hit));
+  __syncthreads();
+  // exclusive scan over the warps, per expert; the total lands in s_off (as a count for now)
+  for (int e = threadIdx.x; e < el; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = s_hist[w * el + e];
+      s_hist[w * el + e] = run;
+      run += c;
     }
-    if (lane == 0) s_count[e] = n;
+    s_off[e] = run;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     int off = 0, nt = 0;
-    for (int e = 0; e < p.el; ++e) {
+    for (int e = 0; e < el; ++e) {
+      const int c = s_off[e];
       s_off[e] = off;
-      p.counts[e] = s_count[e];
-      for (int r0 = 0; r0 < s_count[e]; r0 += 128) {
-        if (nt < p.max_tiles) p.tiles[nt] = make_int4(e, off + r0, min(128, s_count[e] - r0), 0);
+      p.counts[e] = c;
+      for (int r0 = 0; r0 < c; r0 += 128) {
+        if (nt < p.max_tiles) p.tiles[nt] = make_int4(e, off + r0, min(128, c - r0), 0);
         ++nt;
       }
-      off += s_count[e];
+      off += c;
     }
-    s_off[p.el] = off;
+    s_off[el] = off;
     *p.num_tiles = min(nt, p.max_tiles);
     *p.total_rows = off;
   }
-  // routes of other ranks
-  for (int i = threadIdx.x; i < R; i += blockDim.x) {
-    const int e = p.ids[i] - p.e0;
-    if (e < 0 || e >= p.el) p.route_row[i] = -1;
-  }
   __syncthreads();
-  // pass 2: placement
-  for (int e = warp; e < p.el; e += 32) {
-    int base = s_off[e];
-    for (int i0 = 0; i0 < R; i0 += 32) {
-      const int i = i0 + lane;
-      const bool hit = i < R && local_of(i) == e;
-      const unsigned m = __ballot_sync(0xffffffffu, hit);
-      if (hit) {
-        const int r = base + __popc(m & ((1u << lane) - 1));
-        p.route_row[i] = r;
-        p.perm_token[r] = i / p.topk;
-      }
-      base += __popc(m);
+  for (int i0 = seg0; i0 < seg1; i0 += 32) {
+    const int i = i0 + lane;
+    int e = -1;
+    if (i < seg1) {
+      e = p.ids[i] - p.e0;
+      if (e < 0 || e >= el) e = -1;
     }
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    if (e >= 0) {
+      const int r = s_off[e] + hist[e] + __popc(same & ((1u << lane) - 1));
+      p.route_row[i] = r;
+      p.perm_token[r] = i / p.topk;
+    }
+    __syncwarp();
+    if (e >= 0 && (same & ((1u << lane) - 1)) == 0) hist[e] += __popc(same);
+    __syncwarp();
   }
 }
 
@@ -254,31 +266,44 @@ struct CombineParams {
   float* out_f32; bf16* out; long ldo;
 };
 
-// one warp per token row; f32 accumulation in slot order (deterministic)
-__global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
+// One warp per (token row, column quarter); f32 accumulation in slot order (deterministic). The loads of all routes of a chunk are
+// issued before the first is used: rows of different experts are unrelated addresses, one at a time they cost a memory latency each.
+__global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p, int quarters) {
   grid_dep_launch();
   grid_dep_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m = blockIdx.x * 8 + warp;
+  const int item = blockIdx.x * 8 + warp;
+  const int m = item / quarters, q = item % quarters;
   if (m >= p.M) return;
   int rows[MAX_TOPK];
   float w[MAX_TOPK];
-  for (int k = 0; k < p.topk; ++k) {
-    rows[k] = p.route_row[(long)m * p.topk + k];
-    w[k] = p.wts[(long)m * p.topk + k];
+#pragma unroll
+  for (int k = 0; k < MAX_TOPK; ++k) {
+    rows[k] = k < p.topk ? p.route_row[(long)m * p.topk + k] : -1;
+    w[k] = k < p.topk ? p.wts[(long)m * p.topk + k] : 0.f;
   }
-  for (int c = lane; c < (p.D >> 3); c += 32) {
+  const int per = (p.D >> 3) / quarters;
+  for (int cc = lane; cc < per; cc += 32) {
+    const int c = q * per + cc;
+    uint4 v[MAX_TOPK];
+#pragma unroll
+    for (int k = 0; k < MAX_TOPK; ++k)
+      v[k] = rows[k] >= 0 ? *reinterpret_cast<const uint4*>(p.y + (long)rows[k] * p.ldy + c * 8) : make_uint4(0, 0, 0, 0);
+    uint4 sh = make_uint4(0, 0, 0, 0), rs = make_uint4(0, 0, 0, 0);
+    if (p.shared) sh = *reinterpret_cast<const uint4*>(p.shared + (long)m * p.lds + c * 8);
+    if (p.out && p.residual) rs = *reinterpret_cast<const uint4*>(p.residual + (long)m * p.ldr + c * 8);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int k = 0; k < p.topk; ++k) {
+#pragma unroll
+    for (int k = 0; k < MAX_TOPK; ++k) {
       if (rows[k] < 0) continue;
       float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(p.y + (long)rows[k] * p.ldy + c * 8), f);
+      unpack8(v[k], f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[k], f[i], acc[i]);
     }
     if (p.shared) {
       float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(p.shared + (long)m * p.lds + c * 8), f);
+      unpack8(sh, f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] += f[i];
     }
@@ -290,7 +315,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
     if (p.out) {
       if (p.residual) {
         float f[8];
-        unpack8(*reinterpret_cast<const uint4*>(p.residual + (long)m * p.ldr + c * 8), f);
+        unpack8(rs, f);
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = bf16_round(acc[i]) + f[i];
       }
@@ -307,9 +332,16 @@ extern "C" int ifab_router_block(const void* x, long ldx, const void* norm_w, fl
   if (M < 1 || E > 256 || topk > MAX_TOPK || topk > E || D % 8) return -1;
   RouterBlockParams p{(const bf16*)x, ldx, (const bf16*)norm_w, eps, w_router, bias, logits, ids, wts, (bf16*)xn, ldxn,
                       M, D, E, topk, scoring, renorm, scale};
-  const size_t smem = (size_t)8 * D * sizeof(bf16) + (size_t)8 * E * sizeof(float);
-  if (int rc = opt_in_smem(router_block_kernel, smem)) return rc;
-  return launch_chain(router_block_kernel, dim3((M + 7) / 8), dim3(256), smem, (cudaStream_t)stream, p);
+  // eight tokens per CTA re-read the router matrix least often; with fewer than ~150 such CTAs half the SMs idle, so chunks of
+  // up to ~1200 tokens run four tokens per CTA
+  if ((M + 7) / 8 >= 148) {
+    const size_t smem = (size_t)8 * D * sizeof(bf16) + (size_t)8 * E * sizeof(float);
+    if (int rc = opt_in_smem(router_block_kernel<8>, smem)) return rc;
+    return launch_chain(router_block_kernel<8>, dim3((M + 7) / 8), dim3(256), smem, (cudaStream_t)stream, p);
+  }
+  const size_t smem = (size_t)4 * D * sizeof(bf16) + (size_t)4 * E * sizeof(float);
+  if (int rc = opt_in_smem(router_block_kernel<4>, smem)) return rc;
+  return launch_chain(router_block_kernel<4>, dim3((M + 3) / 4), dim3(256), smem, (cudaStream_t)stream, p);
 }
 
 extern "C" int ifab_moe_dispatch(const int32_t* ids, int M, int topk, int e0, int e_local, int32_t* counts, int32_t* route_row,
@@ -317,10 +349,8 @@ extern "C" int ifab_moe_dispatch(const int32_t* ids, int M, int topk, int e0, in
                                  void* stream) {
   if (M < 1 || topk < 1 || topk > MAX_TOPK || e_local < 1 || e_local > MAX_LOCAL || max_tiles < 1) return -1;
   DispatchParams p{ids, M, topk, e0, e_local, counts, route_row, perm_token, reinterpret_cast<int4*>(tiles), num_tiles, total_rows,
-                   max_tiles, 0};
-  const size_t want = (size_t)M * topk * sizeof(short);
-  const size_t smem = want <= 160 * 1024 ? want : 0;
-  p.smem_routes = (int)(smem / sizeof(short));
+                   max_tiles};
+  const size_t smem = (size_t)32 * e_local * sizeof(int);
   if (int rc = opt_in_smem(moe_dispatch_kernel, smem)) return rc;
   return launch_chain(moe_dispatch_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)stream, p);
 }
@@ -339,5 +369,6 @@ extern "C" int ifab_moe_combine(const void* y, long ldy, const int32_t* route_ro
   if (D % 8 || ldy % 8 || topk > MAX_TOPK || (shared && lds % 8) || (residual && ldr % 8) || (out && ldo % 8)) return -1;
   CombineParams p{(const bf16*)y, ldy, route_row, wts, M, topk, D, (const bf16*)shared, lds, (const bf16*)residual, ldr, out_f32,
                   (bf16*)out, ldo};
-  return launch_chain(moe_combine_kernel, dim3((M + 7) / 8), dim3(256), 0, (cudaStream_t)stream, p);
+  const int quarters = (D % 32 == 0 && D >= 1024) ? 4 : 1;      // four warps share a wide row
+  return launch_chain(moe_combine_kernel, dim3((M * quarters + 7) / 8), dim3(256), 0, (cudaStream_t)stream, p, quarters);
 }
