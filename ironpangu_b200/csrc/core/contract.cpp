@@ -28,7 +28,8 @@ const std::map<std::string, OpRule>& rules() {
       {"view", {{"view"}, {kAny}, false, {"start", "width"}, kView}},
       {"mla_kv_write", {{"ifab_mla_kv_write", "ifab_mla_kv_write_q8"}, {kAny, kAny}, false, {"eps", "theta", "weight"}, kCache}},
       {"mla_q_absorb", {{"ifab_mla_q_absorb"}, {kTensor}, false, {"heads", "latent", "nope", "rope", "theta", "weight"}, kTensor}},
-      {"mla_attention", {{"ifab_mla_decode_attention", "ifab_mla_prefill_attention"}, {kTensor, kCache}, false, {"heads", "latent", "weight"}, kTensor}},
+      // a third input is the sparse indexer's selection (selection = learned_indices)
+      {"mla_attention", {{"ifab_mla_decode_attention", "ifab_mla_prefill_attention"}, {kTensor, kCache}, true, {"heads", "latent", "weight"}, kTensor}},
       {"linear_allreduce", {{"ifab_gemv_allreduce_bf16", "ifab_gemm_reduce_scatter_bf16", "ifab_gemm_allreduce_bf16"}, {kTensor}, true, {"weight", "width"}, kTensor}},
       {"router_topk", {{"ifab_router_topk"}, {kTensor}, false, {"experts", "topk", "weight"}, kRoutes}},
       {"moe_gate_up", {{"ifab_moe_gate_up_decode", "ifab_grouped_gemm_bf16", "ifab_moe_gate_up_decode_fp8"}, {kTensor, kRoutes}, false, {"weight", "width"}, kExperts}},
@@ -124,6 +125,12 @@ void validate_kernels(const Program& p) {
     if (i.attr("width")) {
       const uint64_t w = number(i, "width", 1, 1u << 24);
       if (i.op != "lm_head" && i.op != "embedding" && w % 8 != 0) bad(i, "width is not a multiple of 8 elements");
+    }
+    if (i.op == "mla_attention") {
+      const std::string* sel = i.attr("selection");
+      const bool learned = sel && *sel == "learned_indices";
+      if (i.inputs.size() != (learned ? 3u : 2u)) bad(i, "attention takes (query, cache) or, with learned_indices, (query, cache, selection)");
+      if (learned && p.instructions[i.inputs[2]].op != "sparse_index") bad(i, "the selection must come from a sparse_index instruction");
     }
     if (i.op == "router_topk") {
       const uint64_t e = number(i, "experts", 1, 4096), k = number(i, "topk", 1, 16);

@@ -146,7 +146,15 @@ struct AttnParams {
   float* scratch;   // [T][H][max_splits][LATENT + 2]
   uint32_t* status;
   int q8;           // cache rows are packed: 512 int8 | 64 bf16 rope | 4 f32 scales (one per 128 latent columns) = 656 bytes
+  const int32_t* indices;   // optional learned selection [T][n_index]: the key positions a row attends to, ascending, -1 padded
+  int n_index;
 };
+
+// keys of a query row: sink rows first, then either the window's positions or the selected ones
+__device__ __forceinline__ void key_space(const AttnParams& p, int pos, int* first, int* nctx) {
+  visible_range(pos, p.window, first, nctx);
+  if (p.indices) *nctx = min(p.n_index, pos + 1);       // the selector emits min(topk, pos + 1) positions
+}
 
 constexpr int ROW_Q8 = LATENT + ROPE * 2 + 16;
 
@@ -162,7 +170,7 @@ __global__ void __launch_bounds__(256) mla_split_kernel(AttnParams p) {
   const int pos = p.positions[t];
   if (pos < 0) return;
   int first, nctx;
-  visible_range(pos, p.window, &first, &nctx);
+  key_space(p, pos, &first, &nctx);
   const int total = p.n_sinks + nctx;
   const int k_begin = split * p.kps;
   if (k_begin >= total) return;
@@ -199,8 +207,16 @@ __global__ void __launch_bounds__(256) mla_split_kernel(AttnParams p) {
         if (k < p.n_sinks) {
           row = p.sinks + (long)k * ROW;
         } else {
-          const long r = cache_row_of(first + (k - p.n_sinks), slot, p.page_table, p.max_pages, p.page_tokens, p.num_pages);
-          if (r < 0) {
+          int kp = first + (k - p.n_sinks);
+          bool skip = false;
+          if (p.indices) {
+            kp = p.indices[(long)t * p.n_index + (k - p.n_sinks)];
+            skip = kp < first || kp > pos;                 // padding, or a selected position the window no longer shows
+          }
+          const long r = skip ? 0 : cache_row_of(kp, slot, p.page_table, p.max_pages, p.page_tokens, p.num_pages);
+          if (skip) {
+            ok[j] = false;
+          } else if (r < 0) {
             if (lane == 0 && p.status) atomicOr(p.status, IFAB_STATUS_BAD_INDEX);
             ok[j] = false;
           } else if (p.q8) {
@@ -314,7 +330,7 @@ __global__ void __launch_bounds__(256) mla_merge_vup_kernel(AttnParams p, const 
   const int pos = p.positions[t];
   if (pos < 0) return;
   int first, nctx;
-  visible_range(pos, p.window, &first, &nctx);
+  key_space(p, pos, &first, &nctx);
   const int total = p.n_sinks + nctx;
   int ns = (total + p.kps - 1) / p.kps;
   if (ns > p.max_splits) ns = p.max_splits;
@@ -387,12 +403,14 @@ extern "C" int ifab_mla_q_absorb(const void* q, long ldq, const void* w_kvb, flo
                       (const bf16*)w_kvb, theta, positions, (bf16*)q_lat, H, nope, rope, latent, vdim);
 }
 
-extern "C" int ifab_mla_decode_attention(const void* q_lat, const void* cache, const int32_t* positions,
+extern "C" int ifab_mla_decode_attention_indexed(const void* q_lat, const void* cache, const int32_t* positions,
                                          const int32_t* slots, const int32_t* page_table, int max_pages,
                                          int page_tokens, int num_pages, const void* sinks, int n_sinks, int window,
                                          float scale, int T, int H, int latent, int rope, int keys_per_split,
                                          int max_splits, float* scratch, uint64_t scratch_bytes, const void* w_kvb,
-                                         int nope, int vdim, void* out, long ldo, uint32_t* status, void* stream) {
+                                         int nope, int vdim, void* out, long ldo, uint32_t* status, const int32_t* indices, int n_index,
+                                         void* stream) {
+  if (indices && n_index < 1) return -1;
   if (latent != LATENT || (rope != ROPE && rope != -ROPE)) return -1;
   if (max_splits < 1 || max_splits > 64 || keys_per_split < 8) return -1;
   if ((uint64_t)T * H * max_splits * (LATENT + 2) * sizeof(float) > scratch_bytes) return -5;
@@ -400,7 +418,7 @@ extern "C" int ifab_mla_decode_attention(const void* q_lat, const void* cache, c
   const int q8 = rope < 0 ? 1 : 0;
   if (q8) rope = -rope;
   AttnParams p{(const bf16*)q_lat, (const bf16*)cache, positions, slots, page_table, max_pages, page_tokens, num_pages,
-               (const bf16*)sinks, sinks ? n_sinks : 0, window, scale, T, H, keys_per_split, max_splits, scratch, status, q8};
+               (const bf16*)sinks, sinks ? n_sinks : 0, window, scale, T, H, keys_per_split, max_splits, scratch, status, q8, indices, indices ? n_index : 0};
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
   if (H % 4 == 0) rc = launch_split<4>(p, s);
@@ -410,4 +428,15 @@ extern "C" int ifab_mla_decode_attention(const void* q_lat, const void* cache, c
   if (w_kvb == nullptr) return 0;   // split partials only: the caller merges (ifab_mla_merge) and up-projects with a GEMM
   dim3 grid(H, T);
   return launch_chain(mla_merge_vup_kernel, grid, dim3(256), 0, s, p, (const bf16*)w_kvb, nope, vdim, (bf16*)out, ldo);
+}
+
+extern "C" int ifab_mla_decode_attention(const void* q_lat, const void* cache, const int32_t* positions,
+                                         const int32_t* slots, const int32_t* page_table, int max_pages,
+                                         int page_tokens, int num_pages, const void* sinks, int n_sinks, int window,
+                                         float scale, int T, int H, int latent, int rope, int keys_per_split,
+                                         int max_splits, float* scratch, uint64_t scratch_bytes, const void* w_kvb,
+                                         int nope, int vdim, void* out, long ldo, uint32_t* status, void* stream) {
+  return ifab_mla_decode_attention_indexed(q_lat, cache, positions, slots, page_table, max_pages, page_tokens, num_pages, sinks, n_sinks, window, scale, T, H,
+                                           latent, rope, keys_per_split, max_splits, scratch, scratch_bytes, w_kvb, nope, vdim, out, ldo, status, nullptr, 0,
+                                           stream);
 }

@@ -169,7 +169,83 @@ __global__ void __launch_bounds__(256) gated_rms_kernel(const bf16* x, const bf1
   }
 }
 
+// Half-rotation RoPE over the first `rot` columns of every head of a row (pairs (i, i + rot / 2)), bf16-rounded cos / sin like the
+// cache-write kernels; the other columns are copied. grid T, 256 threads.
+__global__ void __launch_bounds__(256) rope_prefix_kernel(const bf16* x, long ldx, const int32_t* positions, bf16* y, long ldy, int heads, int hd, int rot,
+                                                         float theta) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int t = blockIdx.x, pos = positions[t], half = rot / 2;
+  const bf16* xr = x + (long)t * ldx;
+  bf16* yr = y + (long)t * ldy;
+  for (int i = threadIdx.x; i < heads * hd; i += blockDim.x) {
+    const int h = i / hd, c = i % hd;
+    float v = __bfloat162float(xr[i]);
+    if (c < rot && pos >= 0) {
+      const int j = c < half ? c : c - half;
+      const float inv_freq = exp2f(-(2.f * (float)j / (float)rot) * log2f(theta));
+      float sn, cs;
+      sincosf((float)pos * inv_freq, &sn, &cs);
+      cs = bf16_round(cs);
+      sn = bf16_round(sn);
+      const float a = __bfloat162float(xr[h * hd + j]), b = __bfloat162float(xr[h * hd + j + half]);
+      v = c < half ? a * cs - b * sn : b * cs + a * sn;
+    }
+    yr[i] = __float2bfloat16_rn(v);
+  }
+}
+
+// Index keys of the step's rows into their pages: cache bf16 [pages, page_tokens, dim]. One warp per row.
+__global__ void __launch_bounds__(256) index_cache_append_kernel(const bf16* key, long ldk, const int32_t* positions, const int32_t* slots,
+                                                                const int32_t* page_table, int max_pages, int page_tokens, int num_pages, bf16* cache,
+                                                                int T, int dim, uint32_t* status) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const int pos = positions[t];
+  if (pos < 0) return;
+  const int lp = pos / page_tokens;
+  const int page = lp < max_pages ? page_table[(long)slots[t] * max_pages + lp] : -1;
+  if (page < 0 || page >= num_pages) {
+    if (lane == 0 && status) atomicOr(status, IFAB_STATUS_BAD_INDEX);
+    return;
+  }
+  bf16* dst = cache + ((long)page * page_tokens + pos % page_tokens) * dim;
+  for (int i = lane; i < dim; i += 32) dst[i] = key[(long)t * ldk + i];
+}
+
+// y = a + b, bf16 rows
+__global__ void __launch_bounds__(256) add_rows_kernel(const bf16* a, long lda, const bf16* b, long ldb, bf16* y, long ldy, int rows, int n) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long)rows * n) return;
+  const int r = (int)(i / n), c = (int)(i % n);
+  y[(long)r * ldy + c] = __float2bfloat16_rn(__bfloat162float(a[(long)r * lda + c]) + __bfloat162float(b[(long)r * ldb + c]));
+}
+
 }  // namespace
+
+extern "C" int ifab_rope_prefix(const void* x, long ldx, const int32_t* positions, void* y, long ldy, int T, int heads, int head_dim, int rotary_dim,
+                                float theta, void* stream) {
+  if (T < 1 || heads < 1 || head_dim < 1 || rotary_dim < 2 || rotary_dim % 2 || rotary_dim > head_dim) return -1;
+  return launch_chain(rope_prefix_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x, ldx, positions, (bf16*)y, ldy, heads, head_dim,
+                      rotary_dim, theta);
+}
+
+extern "C" int ifab_index_cache_append(const void* key, long ldk, const int32_t* positions, const int32_t* slots, const int32_t* page_table,
+                                       int max_pages, int page_tokens, int num_pages, void* cache, int T, int dim, uint32_t* status, void* stream) {
+  if (T < 1 || dim < 1) return -1;
+  return launch_chain(index_cache_append_kernel, dim3((T + 7) / 8), dim3(256), 0, (cudaStream_t)stream, (const bf16*)key, ldk, positions, slots, page_table,
+                      max_pages, page_tokens, num_pages, (bf16*)cache, T, dim, status);
+}
+
+extern "C" int ifab_add_rows(const void* a, long lda, const void* b, long ldb, void* y, long ldy, int rows, int n, void* stream) {
+  if (rows < 1 || n < 1) return -1;
+  return launch_chain(add_rows_kernel, dim3((unsigned)(((long)rows * n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, (const bf16*)a, lda,
+                      (const bf16*)b, ldb, (bf16*)y, ldy, rows, n);
+}
 
 extern "C" int ifab_zc_rmsnorm(const void* x, long ldx, const void* w, float eps, void* y, long ldy, int rows, int groups, int d, void* stream) {
   if (rows < 1 || groups < 1 || d < 1) return -1;

@@ -80,11 +80,16 @@ _SIGS = {
     "ifab_mla_q_absorb": [_P, c_long, _P, c_float, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "ifab_mla_decode_attention": [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_float, c_int, c_int, c_int,
                                   c_int, c_int, c_int, _P, c_u64, _P, c_int, c_int, _P, c_long, _P, _P],
+    "ifab_mla_decode_attention_indexed": [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_float, c_int, c_int, c_int,
+                                          c_int, c_int, c_int, _P, c_u64, _P, c_int, c_int, _P, c_long, _P, _P, c_int, _P],
     "ifab_gqa_rope_kv_write": [_P, c_long, _P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_float, _P, _P],
     "ifab_mome": [_P, c_long, _P, _P, _P, _P, _P, c_long, c_int, c_int, c_int, c_int, _P],
     "ifab_mhc_pre": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P],
     "ifab_mhc_post": [_P, _P, c_long, _P, _P, _P, c_int, c_int, c_int, _P],
+    "ifab_rope_prefix": [_P, c_long, _P, _P, c_long, c_int, c_int, c_int, c_int, c_float, _P],
+    "ifab_index_cache_append": [_P, c_long, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, _P, _P],
+    "ifab_add_rows": [_P, c_long, _P, c_long, _P, c_long, c_int, c_int, _P],
     "ifab_zc_rmsnorm": [_P, c_long, _P, c_float, _P, c_long, c_int, c_int, c_int, _P],
     "ifab_hybrid_qk_prepare": [_P, c_long, _P, c_long, _P, _P, c_float, _P, c_long, _P, c_long, c_int, c_int, c_int, c_int, _P],
     "ifab_sigmoid_mul": [_P, c_long, _P, c_long, _P, c_long, c_int, c_int, _P],

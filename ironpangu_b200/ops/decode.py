@@ -342,9 +342,10 @@ def mla_decode_attention(q_lat: torch.Tensor, cache: torch.Tensor, positions: to
                          page_table: torch.Tensor, w_kvb: torch.Tensor, *, nope: int, scale: float, window: int = 0,
                          sinks: Optional[torch.Tensor] = None, keys_per_split: int = 64, max_splits: int = 16,
                          scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                         status_ptr: Optional[int] = None, packed: bool = False) -> torch.Tensor:
+                         status_ptr: Optional[int] = None, packed: bool = False, indices: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Split-KV paged MLA attention + value up-projection. Returns ``[T, H*vdim]`` bf16. With ``packed`` the cache
-    holds 656-byte int8 rows (``uint8 [pages, page_tokens, 656]``, written by :func:`mla_kv_write_q8`)."""
+    holds 656-byte int8 rows (``uint8 [pages, page_tokens, 656]``, written by :func:`mla_kv_write_q8`). ``indices`` (int32
+    ``[T, k]``, ascending key positions padded with -1: the sparse indexer's selection) restricts every row to those keys."""
     T, H, row = q_lat.shape
     num_pages, page_tokens, _ = cache.shape
     latent = w_kvb.shape[2]
@@ -354,11 +355,12 @@ def mla_decode_attention(q_lat: torch.Tensor, cache: torch.Tensor, positions: to
         scratch = torch.empty(T * H * max_splits * (latent + 2), dtype=torch.float32, device=q_lat.device)
     if out is None:
         out = torch.empty(T, H * vdim, dtype=BF16, device=q_lat.device)
-    check(_lib.load().ifab_mla_decode_attention(
+    assert indices is None or (indices.dtype == torch.int32 and indices.is_contiguous() and indices.shape[0] == T)
+    check(_lib.load().ifab_mla_decode_attention_indexed(
         q_lat.data_ptr(), cache.data_ptr(), positions.data_ptr(), slots.data_ptr(), page_table.data_ptr(),
         page_table.shape[1], page_tokens, num_pages, _ptr(sinks), 0 if sinks is None else sinks.shape[0], window, scale,
         T, H, latent, -rope if packed else rope, keys_per_split, max_splits, scratch.data_ptr(), scratch.numel() * 4, w_kvb.data_ptr(), nope,
-        vdim, out.data_ptr(), _rows(out), status_ptr, _stream()), "mla_decode_attention")
+        vdim, out.data_ptr(), _rows(out), status_ptr, _ptr(indices), 0 if indices is None else indices.shape[1], _stream()), "mla_decode_attention")
     return out
 
 

@@ -60,13 +60,42 @@ def delta_rule_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torc
 
 
 def sparse_index(q: torch.Tensor, w: torch.Tensor, keys: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
-                 page_table: torch.Tensor, *, ctx: int, topk: int, status_ptr: Optional[int] = None) -> torch.Tensor:
-    """Top-``topk`` key positions per query by ``sum_h w_h * relu(q_h . key)``; ``keys`` paged bf16 ``[pages, page_tokens, dim]``."""
+                 page_table: torch.Tensor, *, ctx: int, topk: int, status_ptr: Optional[int] = None, scores: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Top-``topk`` key positions per query by ``sum_h w_h * relu(q_h . key)``; ``keys`` paged bf16 ``[pages, page_tokens, dim]``.
+    Positions come out ascending, padded with -1; ``scores`` (f32 ``[T, ctx]``) is scratch."""
     T, H, dim = q.shape
     num_pages, page_tokens, _ = keys.shape
-    scores = torch.empty(T, ctx, dtype=torch.float32, device=q.device)
-    out = torch.empty(T, topk, dtype=torch.int32, device=q.device)
+    scores = torch.empty(T, ctx, dtype=torch.float32, device=q.device) if scores is None else scores
+    out = torch.empty(T, topk, dtype=torch.int32, device=q.device) if out is None else out
+    assert scores.is_contiguous() and scores.shape[1] == ctx and out.is_contiguous() and w.dtype == torch.float32 and w.is_contiguous()
     check(_lib.load().ifab_sparse_index(q.data_ptr(), w.data_ptr(), keys.data_ptr(), positions.data_ptr(), slots.data_ptr(),
                                         page_table.data_ptr(), page_table.shape[1], page_tokens, num_pages, scores.data_ptr(), ctx, T, H,
                                         dim, topk, out.data_ptr(), status_ptr, _s()), "sparse_index")
+    return out
+
+
+def rope_prefix(x: torch.Tensor, positions: torch.Tensor, *, heads: int, head_dim: int, rotary_dim: int, theta: float,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Half-rotation RoPE over the first ``rotary_dim`` columns of every head of ``x`` (``[T, heads * head_dim]``)."""
+    T = x.shape[0]
+    out = torch.empty(T, heads * head_dim, dtype=BF16, device=x.device) if out is None else out
+    check(_lib.load().ifab_rope_prefix(x.data_ptr(), x.stride(0), positions.data_ptr(), out.data_ptr(), out.stride(0), T, heads, head_dim, rotary_dim, theta,
+                                       _s()), "rope_prefix")
+    return out
+
+
+def index_cache_append(key: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
+                       status_ptr: Optional[int] = None) -> None:
+    """Index keys ``[T, dim]`` of the step's rows into the paged index cache ``[pages, page_tokens, dim]`` (bf16)."""
+    T, dim = key.shape
+    check(_lib.load().ifab_index_cache_append(key.data_ptr(), key.stride(0), positions.data_ptr(), slots.data_ptr(), page_table.data_ptr(),
+                                              page_table.shape[1], cache.shape[1], cache.shape[0], cache.data_ptr(), T, dim, status_ptr, _s()),
+          "index_cache_append")
+
+
+def add_rows(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    rows, n = a.shape
+    out = torch.empty(rows, n, dtype=BF16, device=a.device) if out is None else out
+    check(_lib.load().ifab_add_rows(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0), rows, n, _s()), "add_rows")
     return out

@@ -24,6 +24,7 @@ import numpy as np
 import torch
 
 from ..ops import decode as K
+from ..ops import hc as HC
 from ..parallel.fabric import Fabric
 
 BF16 = torch.bfloat16
@@ -250,6 +251,8 @@ class PlanEngine:
         self.keep_logits = keep_logits
         self.logits = None
         self.vals: List[object] = [None] * len(self.ins)
+        self._index_cache_of: Dict[int, torch.Tensor] = {}     # index-cache instruction -> its pages of index keys
+        self._index_scores = None
         self._cache_of: Dict[int, torch.Tensor] = {}     # cache-write instruction -> its pages
         self.caches: List[torch.Tensor] = []              # the same tensors in program order (one per attention layer)
         self.arena = FrozenArena(b, self.rank, T, dev)
@@ -297,7 +300,9 @@ class PlanEngine:
         self.layer_weights: List[dict] = []       # per decoder layer, in program order: the parameter names of its kernels
         for k, i in enumerate(ins):
             if i["op"] == "mla_attention":
-                kabs, kw = i["inputs"]
+                kabs, kw = i["inputs"][:2]
+                if len(i["inputs"]) != 2:
+                    continue              # attention over a learned selection: the split-KV kernel only
                 if ins[kabs]["op"] != "mla_q_absorb" or ins[kw]["op"] != "mla_kv_write":
                     continue
                 kqb = ins[kabs]["inputs"][0]
@@ -439,6 +444,13 @@ class PlanEngine:
             if op == "mla_kv_write":
                 self._cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
                 self.caches.append(self._cache_of[k])
+            elif op == "index_cache_append":
+                if i["attrs"].get("cache_dtype", "bf16") != "bf16":
+                    raise NotImplementedError("the device index cache holds bf16 keys (int8 index keys are an oracle-only layout)")
+                self._index_cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
+            elif op == "sparse_index":
+                self.vals[k] = view(k, (T, w), i32)
+                self._index_scores = torch.empty(T, self.max_context, dtype=f32, device=dev)      # selector scratch: one score per key
             elif op == "router_topk":
                 E = int(i["attrs"]["experts"])
                 raw = self.arena.lease(k, T * w * 8 + T * E * 4)           # ids | weights | logits, one slot
@@ -543,6 +555,21 @@ class PlanEngine:
                 vdim = int(a.get("value", nope))
                 w = self._param(a["weight"]).view(H // self.world, nope + vdim, latent)
                 K.mla_q_absorb(val(ins[0]), w, pos, nope=nope, rope=rope, theta=float(a["theta"]), out=val(k))
+            elif op == "rotary_prefix":
+                HC.rope_prefix(val(ins[0]), pos, heads=int(a["heads"]), head_dim=int(a["head_dim"]), rotary_dim=int(a["rotary_dim"]),
+                               theta=float(a["theta"]), out=val(k))
+            elif op == "index_cache_append":
+                HC.index_cache_append(val(ins[0]), self._index_cache_of[k], pos, slot, self.page_table, status_ptr=st)
+                V[k] = k
+            elif op == "sparse_index":
+                Hi, dim = int(a["heads"]), int(a["head_dim"])
+                q = val(ins[0])
+                if not q.is_contiguous():
+                    raise NotImplementedError("the index query must be a whole instruction result")
+                HC.sparse_index(q.view(T, Hi, dim), val(ins[1]).float(), self._index_cache_of[V[ins[2]]], pos, slot, self.page_table,
+                                ctx=self.max_context, topk=int(a["topk"]), status_ptr=st, scores=self._index_scores[:T], out=val(k))
+            elif op == "add":
+                HC.add_rows(val(ins[0]), val(ins[1]), out=val(k))
             elif op == "mla_attention":
                 H, latent, vdim = int(a["heads"]), int(a["latent"]), int(a["value"])
                 nope = int(a.get("nope", vdim))
@@ -551,7 +578,7 @@ class PlanEngine:
                 K.mla_decode_attention(val(ins[0]), cache, pos, slot, self.page_table, w, nope=nope,
                                        scale=1.0 / math.sqrt(float(a["scale_dim"])), window=int(a["window"]),
                                        keys_per_split=self.kps, max_splits=self.max_splits, scratch=self.scratch,
-                                       out=val(k), status_ptr=st)
+                                       out=val(k), status_ptr=st, indices=val(ins[2]) if len(ins) > 2 else None)
             elif op == "router_topk":
                 ids, wts, logits = V[k]
                 # when the expert kernels read the same rows under the same norm, the router leaves the normalised rows in the
@@ -601,5 +628,5 @@ class PlanEngine:
         return g
 
     def reset(self) -> None:
-        for c in self.caches:
+        for c in list(self.caches) + list(self._index_cache_of.values()):
             c.zero_()

@@ -154,3 +154,42 @@ def test_bundle_engine_equals_the_hand_wired_decoder(tmp_path, fused_head, fused
         PlanEngine(out["dir"], None, fab, parameters=bad)
     assert fab.status() == 0
     fab.close()
+
+
+@pytest.mark.parametrize("topk,window", [(5, 0), (64, 0), (6, 12)])
+def test_sparse_indexer_program_on_the_device_matches_the_interpreter(tmp_path, topk, window):
+    """A program with an index cache, the weighted-ReLU selector and attention over the learned selection: the plan engine binds
+    rotary_prefix, index_cache_append, sparse_index, add and the indexed split-KV attention; selections equal the CPU oracle's
+    and logits agree within bf16 noise."""
+    from indexer_source import source
+
+    from ironpangu_b200 import compiler
+    from ironpangu_b200.parallel.fabric import Fabric
+    from ironpangu_b200.runtime.plan_engine import PlanEngine
+
+    src, ck, bundle = tmp_path / "m.inferfabric", tmp_path / "ck", tmp_path / "b"
+    src.write_text(source(topk, True, window))
+    assert compiler.cli("synth-checkpoint", str(src), str(ck), "--seed", "5").returncode == 0
+    compiler.write_bundle(str(src), str(bundle), checkpoint_dir=str(ck), prefill_tokens=8)
+    toks = torch.randint(1, 512, (40,), generator=torch.Generator().manual_seed(2)).tolist()
+    oracle = compiler.interpret(src.read_text(), str(ck), toks, all_logits=True, watch=["picked"])
+    ref = torch.tensor(oracle["prompt_logits"])
+    fab = Fabric(0, 1)
+    eng = PlanEngine(str(bundle), str(ck), fab, max_tokens=8, keep_logits=True)
+    picked_at = next(k for k, i in enumerate(eng.ins) if i["op"] == "sparse_index")
+    for s in range(0, len(toks), 8):
+        n = min(8, len(toks) - s)
+        eng.tokens[:n].copy_(torch.tensor(toks[s:s + n], dtype=torch.int32))
+        eng.positions[:n].copy_(torch.arange(s, s + n, dtype=torch.int32))
+        eng.slots[:n].zero_()
+        eng.forward(n)
+        sel = eng.vals[picked_at][:n].tolist()
+        for i in range(n):
+            want = oracle["watched"][s + i]["picked"]["ids"]
+            got = [p for p in sel[i] if p >= 0]
+            if got != want:
+                # near-ties of the score may be broken differently by bf16 arithmetic: at most one position differs then
+                assert len(got) == len(want) and len(set(got) ^ set(want)) <= 2, (s + i, got, want)
+        torch.testing.assert_close(eng.logits[:n].cpu(), ref[s:s + n], rtol=3e-2, atol=3e-2)
+    assert fab.status() == 0
+    fab.close()
