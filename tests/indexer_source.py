@@ -15,9 +15,10 @@ model Indexed {{
     let w = weights("model");
     let x = embedding(weight = w.embed, width = 256, vocab = 512);
     let xn = norm(x, weight = w.ln, eps = 1e-5);
-    let q = linear(xn, weight = w.q, width = 384, placement = "replicated");
-    let latent = linear(xn, weight = w.kv, width = 512, placement = "replicated");
-    let kr = linear(xn, weight = w.kr, width = 64, placement = "replicated");
+    let qkv = linear(xn, weight = w.q, paired_weight = w.kva, width = 384, paired_width = 576, placement = "replicated");
+    let q = slice(qkv, start = 0, width = 384);
+    let latent = slice(qkv, start = 384, width = 512);
+    let kr = slice(qkv, start = 896, width = 64);
     let cache = cache_norm_rope_append(latent, kr, weight = w.kv_ln, eps = 1e-5, theta = 10000);{indexer}
     let query = mla_query(q, weight = w.kvb, theta = 10000, heads = 2, nope = 128, rope = 64, latent = 512, value = 128, input_layout = "rank_local");
     let attended = {sel};
