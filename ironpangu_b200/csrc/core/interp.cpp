@@ -651,7 +651,7 @@ void Interpreter::run_node(uint32_t idx, uint32_t token, uint32_t position) {
         for (uint32_t cidx = 0; cidx < lat; ++cidx) {
           float a = 0.f;
           for (size_t k = 0; k < keys.size(); ++k) a += sc[k] * (*keys[k])[cidx];
-          y[h * lat + cidx] = bf16_round(a / sum);
+          y[h * lat + cidx] = keys.empty() ? 0.f : bf16_round(a / sum);     // a selection the window leaves empty attends to nothing
         }
       }
       return y;
