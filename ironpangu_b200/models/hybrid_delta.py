@@ -119,6 +119,116 @@ def random_weights(c: HybridConfig, device, seed: int = 0) -> Dict[str, torch.Te
     return out
 
 
+# ---------------------------------------------------------------------------------------------------------------------------
+# checkpoint-bound construction: definition + checkpoint directory -> typed plan (checked by the host core) -> decoder
+# ---------------------------------------------------------------------------------------------------------------------------
+_ST = {BF16: "BF16", torch.float32: "F32"}
+
+
+def definition_text(c: HybridConfig, *, label: str = "hybrid", context_buckets=(1024,), batch_buckets=(1, 2, 4, 8), token_budget: int = 64) -> str:
+    """The model document (contract ``qwen35_text_v1``) that describes ``c`` on one GPU."""
+    return (f"language inferfabric 1;\nmodel Hybrid {{\n    contract = qwen35_text_v1;\n    label = \"{label}\";\n"
+            f"    hidden = {c.hidden}; intermediate = {c.intermediate}; vocab = {c.vocab};\n"
+            f"    query_heads = {c.query_heads}; kv_heads = {c.kv_heads}; head_dim = {c.head_dim};\n"
+            f"    delta_heads = {c.delta_heads}; delta_dim = {c.delta_dim}; conv_width = {c.conv_width};\n"
+            f"    layers = [{', '.join(c.layers)}];\n}}\nplan OneGpu for Hybrid {{\n"
+            "    prefill = mesh(tp = 1, cp = 1, sp = false);\n    decode = mesh(tp = 1, cp = 1, sp = false);\n"
+            f"    page_tokens = {c.page_tokens}; token_budget = {token_budget};\n"
+            f"    batch_buckets = [{', '.join(map(str, batch_buckets))}];\n    context_buckets = [{', '.join(map(str, context_buckets))}];\n}}\n")
+
+
+def save_checkpoint(path, c: HybridConfig, weights: Dict[str, torch.Tensor], *, shards: int = 2, max_position: int = 4096) -> None:
+    """Write ``weights`` (this module's checkpoint names) as a sharded safetensors directory with the ``config.json`` and the
+    weight index the compile path inspects."""
+    import json
+    import struct
+    from pathlib import Path
+
+    d = Path(path)
+    d.mkdir(parents=True, exist_ok=True)
+    names = list(weights)
+    per = (len(names) + shards - 1) // shards
+    parts = [names[i:i + per] for i in range(0, len(names), per)]
+    wmap, total = {}, 0
+    for i, part in enumerate(parts):
+        fname = f"model-{i + 1:05d}-of-{len(parts):05d}.safetensors"
+        hdr, blobs, cursor = {}, [], 0
+        for n in part:
+            t = weights[n].detach().cpu().contiguous()
+            raw = t.view(torch.uint8).numpy().tobytes() if t.dim() else t.reshape(1).view(torch.uint8).numpy().tobytes()
+            hdr[n] = {"dtype": _ST[t.dtype], "shape": list(t.shape), "data_offsets": [cursor, cursor + len(raw)]}
+            blobs.append(raw)
+            cursor += len(raw)
+            wmap[n] = fname
+        head = json.dumps(hdr).encode()
+        head += b" " * (-len(head) % 8)
+        (d / fname).write_bytes(struct.pack("<Q", len(head)) + head + b"".join(blobs))
+        total += cursor
+    text = {"model_type": "qwen3_5_text", "hidden_size": c.hidden, "intermediate_size": c.intermediate, "vocab_size": c.vocab,
+            "num_hidden_layers": len(c.layers), "num_attention_heads": c.query_heads, "num_key_value_heads": c.kv_heads, "head_dim": c.head_dim,
+            "linear_num_key_heads": c.delta_heads, "linear_num_value_heads": c.delta_heads, "linear_key_head_dim": c.delta_dim,
+            "linear_value_head_dim": c.delta_dim, "linear_conv_kernel_dim": c.conv_width, "attention_bias": False, "attn_output_gate": True,
+            "hidden_act": "silu", "rms_norm_eps": c.eps, "tie_word_embeddings": True, "max_position_embeddings": max_position,
+            "rope_parameters": {"rope_type": "default", "rope_theta": float(c.theta), "partial_rotary_factor": 0.25},
+            "layer_types": ["full_attention" if k == "full" else "linear_attention" for k in c.layers]}
+    (d / "config.json").write_text(json.dumps({"model_type": "qwen3_5", "tie_word_embeddings": True, "text_config": text}))
+    (d / "model.safetensors.index.json").write_text(json.dumps({"metadata": {"total_size": total}, "weight_map": wmap}))
+
+
+def typed_plan(definition_path: str, checkpoint_dir: str) -> dict:
+    """The host core's typed plan of (definition, checkpoint): the checkpoint is inspected against the contract (every tensor
+    present with its dtype and shape, nothing unexpected, config and definition agree) before anything is loaded."""
+    import json
+
+    from .. import compiler
+
+    return json.loads(compiler.cli("compile-checkpoint", str(definition_path), str(checkpoint_dir)).stdout)
+
+
+def config_of(plan: dict, checkpoint_dir: str) -> HybridConfig:
+    """The decoder configuration a typed plan describes (dimensions from the plan, rope base and epsilon from ``config.json``)."""
+    import json
+    from pathlib import Path
+
+    if plan.get("format") != "inferfabric.typed-plan.v1" or plan.get("contract") != "qwen35_text_v1":
+        raise ValueError("not a typed plan of the hybrid decoder contract")
+    spec, m = plan["spec"], plan["spec"]["model"]
+    if spec["decode"]["tp"] != 1 or spec["decode"]["cp"] != 1:
+        raise ValueError("the hybrid decoder executes plans for one GPU (decode mesh tp = 1, cp = 1)")
+    text = json.loads((Path(checkpoint_dir) / "config.json").read_text())
+    text = text.get("text_config", text)
+    return HybridConfig(hidden=m["hidden"], intermediate=m["intermediate"], vocab=m["vocab"], query_heads=m["query_heads"], kv_heads=m["kv_heads"],
+                        head_dim=m["head_dim"], delta_heads=m["delta_heads"], delta_dim=m["delta_dim"], conv_width=m["conv_width"],
+                        layers=[k.lower() for k in m["layers"]], theta=float(text["rope_parameters"]["rope_theta"]),
+                        eps=float(text.get("rms_norm_eps", 1e-6)), page_tokens=spec["page_tokens"])
+
+
+def load_weights(plan: dict, checkpoint_dir: str, device, *, staging_bytes: int = 64 << 20) -> Dict[str, torch.Tensor]:
+    """Every tensor the typed plan binds, read at the (shard, offset, bytes) the plan recorded and uploaded through one bounded
+    staging buffer (pinned when the destination is a GPU)."""
+    from ..runtime.plan_engine import SafetensorsDir
+
+    dts = {"BF16": BF16, "F32": torch.float32}
+    src = SafetensorsDir(checkpoint_dir)
+    on_gpu = torch.device(device).type == "cuda"
+    stage = torch.empty(max(4096, int(staging_bytes)), dtype=torch.uint8)
+    if on_gpu:
+        stage = stage.pin_memory()
+    out = {}
+    for name, info in plan["checkpoint"]["weights"].items():
+        dt, n = dts[info["dtype"]], int(info["bytes"])
+        host = src.shard_from(info["shard"], int(info["offset"]))[:n]
+        if host.size != n:
+            raise ValueError(f"{name}: the shard ends before the tensor does")
+        dst = torch.empty(n, dtype=torch.uint8, device=device)
+        for b in range(0, n, stage.numel()):
+            e = min(n, b + stage.numel())
+            stage[:e - b].copy_(torch.from_numpy(host[b:e].copy()))
+            dst[b:e].copy_(stage[:e - b], non_blocking=False)
+        out[name] = dst.view(dt).view(*info["shape"])
+    return out
+
+
 class HybridDecoder:
     """Up to ``max_tokens`` (<= 8) query rows per step on one GPU; rows carry their own position and sequence slot, rows of one
     sequence inside a step must come in position order. Greedy next tokens land in ``next_ids``."""
@@ -184,6 +294,16 @@ class HybridDecoder:
         self.logits = e(T, c.vocab, dt=torch.float32) if keep_logits else None
         n_full = sum(1 for k in c.layers if k == "full")
         self.launches_per_forward = 3 + n_full * 10 + (len(c.layers) - n_full) * 9      # + one recurrence launch per row and delta layer
+
+    @classmethod
+    def from_checkpoint(cls, definition_path: str, checkpoint_dir: str, fabric: Fabric, **kw) -> "HybridDecoder":
+        """Definition + checkpoint directory -> decoder: the host core inspects and compiles the pair into the typed plan, the
+        plan names the tensors and where their bytes are, and the decoder is built on exactly those. ``self.plan_key`` keeps the
+        plan's content key."""
+        plan = typed_plan(definition_path, checkpoint_dir)
+        dec = cls(config_of(plan, checkpoint_dir), load_weights(plan, checkpoint_dir, fabric.device), fabric, **kw)
+        dec.plan_key = plan["key"]
+        return dec
 
     def forward(self, T: Optional[int] = None) -> torch.Tensor:
         c, fab = self.cfg, self.fabric

@@ -442,10 +442,19 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
 
         if world != 1:
             raise SystemExit("the hybrid decoder runs on one GPU")
-        hcfg = H.HybridConfig.tiny(args.layers or 1) if args.model == "hybrid-tiny" else H.HybridConfig.text2b()
-        if args.model == "hybrid2b" and args.layers:
-            hcfg.layers = hcfg.layers[:args.layers]
-        hweights = H.random_weights(hcfg, dev, seed=args.seed)
+        if args.model == "hybrid":
+            # a model document + a checkpoint directory: inspected and compiled into the typed plan before any byte is loaded
+            if not (args.definition and args.checkpoint):
+                raise SystemExit("--model hybrid needs --definition MODEL.inferfabric and --checkpoint DIR")
+            hplan = H.typed_plan(args.definition, args.checkpoint)
+            hcfg = H.config_of(hplan, args.checkpoint)
+            mark("plan", f"typed plan {hplan['key'][:16]}")
+            hweights = H.load_weights(hplan, args.checkpoint, dev)
+        else:
+            hcfg = H.HybridConfig.tiny(args.layers or 1) if args.model == "hybrid-tiny" else H.HybridConfig.text2b()
+            if args.model == "hybrid2b" and args.layers:
+                hcfg.layers = hcfg.layers[:args.layers]
+            hweights = H.random_weights(hcfg, dev, seed=args.seed)
         mark("weights")
         hdec = H.HybridDecoder(hcfg, hweights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs,
                                keep_logits=not args.greedy_only)
@@ -663,11 +672,12 @@ def serve(engine, rank: int, world: int, sock_path: str, group=None, agreement="
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model", default="tiny", choices=["tiny", "flagship", "dense-tiny", "dense2b", "hybrid-tiny", "hybrid2b"])
+    ap.add_argument("--model", default="tiny", choices=["tiny", "flagship", "dense-tiny", "dense2b", "hybrid-tiny", "hybrid2b", "hybrid"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--bundle", default="")
     ap.add_argument("--checkpoint", default="")
+    ap.add_argument("--definition", default="", help="model document of --model hybrid (contract qwen35_text_v1)")
     ap.add_argument("--max-num-seqs", type=int, default=4)
     ap.add_argument("--max-model-len", type=int, default=256)
     ap.add_argument("--max-num-batched-tokens", type=int, default=0, help="tokens per scheduler step (0 = one launch group of 8 rows)")
