@@ -92,3 +92,74 @@ plan TP{tp}EP{tp} for {name} {{
     max_model_len = {context};
 }}
 """
+
+
+def dense_gqa_source(cfg, tp: int, context: int = 1024, name: str = "DenseGqa", eos: int = 2) -> str:
+    """DSL source of the dense grouped-query-attention decoder ``cfg`` (``models.dense_gqa.DenseConfig``): per layer
+    RMSNorm -> q / k / v projections -> rotary on q and k -> K / V page append -> paged attention -> output projection
+    (all-reduced) + residual; RMSNorm -> SwiGLU MLP (all-reduced) + residual."""
+    c = cfg
+    if c.heads % tp or c.kv_heads % tp or c.ffn % tp or c.vocab % tp:
+        raise ValueError(f"tp={tp} does not divide heads / kv heads / FFN / vocab of the model")
+    hd, theta, eps = c.head_dim, _num(c.theta), repr(c.eps)
+    devices = ", ".join(str(i) for i in range(tp))
+    return f"""language inferfabric 1;
+
+// {c.layers} layers, hidden {c.hidden}, vocab {c.vocab}; GQA: {c.heads} query / {c.kv_heads} KV heads x {hd}; SwiGLU {c.ffn}; tp = {tp}.
+
+module GQAAttention(x, w) {{
+    let q = rotary_prefix(linear(x, weight = w.q_proj, width = div({c.heads * hd}, {tp}), placement = "tp_rows"),
+                          heads = div({c.heads}, {tp}), head_dim = {hd}, rotary_dim = {hd}, theta = {theta});
+    let k = rotary_prefix(linear(x, weight = w.k_proj, width = div({c.kv_heads * hd}, {tp}), placement = "tp_rows"),
+                          heads = div({c.kv_heads}, {tp}), head_dim = {hd}, rotary_dim = {hd}, theta = {theta});
+    let v = linear(x, weight = w.v_proj, width = div({c.kv_heads * hd}, {tp}), placement = "tp_rows");
+    let cache = kv_cache_append(k, v, kv_heads = {c.kv_heads}, head_dim = {hd});
+    let attended = paged_attention(q, cache, heads = {c.heads}, kv_heads = {c.kv_heads}, head_dim = {hd}, scale = {repr(1.0 / (hd ** 0.5))});
+    let partial = linear(attended, weight = w.o_proj, width = {c.hidden}, placement = "tp_columns");
+    let output = allreduce(partial);
+    yield output;
+}}
+
+module SwiGLU(x, w) {{
+    let act = swiglu(linear(x, weight = w.gate_proj, paired_weight = w.up_proj, width = div({c.ffn}, {tp}),
+                            paired_width = div({c.ffn}, {tp}), placement = "tp_rows"));
+    let partial = linear(act, weight = w.down_proj, width = {c.hidden}, placement = "tp_columns");
+    let output = allreduce(partial);
+    yield output;
+}}
+
+module DecoderBlock(x, w) {{
+    let attention = GQAAttention(norm(x, weight = w.input_layernorm, eps = {eps}), w.self_attn);
+    let h = add(x, attention);
+    let ffn = SwiGLU(norm(h, weight = w.post_attention_layernorm, eps = {eps}), w.mlp);
+    let output = add(h, ffn);
+    yield output;
+}}
+
+model {name} {{
+    context = {context};
+    eos = {eos};
+    let w = weights("model");
+    let embedded = embedding(weight = w.embed_tokens, width = {c.hidden}, vocab = {c.vocab});
+
+    let hidden = fold i in range(0, {c.layers}) carry(x = embedded) {{
+        let block = DecoderBlock(x, child(w.layers, i));
+        yield block;
+    }};
+
+    let normalized = norm(hidden, weight = w.norm, eps = {eps});
+    let local_logits = linear(normalized, weight = weights("lm_head"), width = div({c.vocab}, {tp}), placement = "tp_rows");
+    let logits = gather(local_logits);
+    yield logits;
+}}
+
+plan TP{tp} for {name} {{
+    target = b200_token_v1;
+    tp = {tp};
+    ep = {tp};
+    devices = [{devices}];
+    max_num_seqs = 1;
+    max_num_batched_tokens = 1;
+    max_model_len = {context};
+}}
+"""

@@ -710,7 +710,7 @@ const std::set<std::string>& primitives() {
       "sink_normalize", "cache_append", "cache_norm_rope_append", "latent_attention", "index_cache_append", "sparse_index",
       "swiglu", "router", "expert_linear", "expert_swiglu_down", "expert_reduce", "add",
       // dense-attention family (GQA models)
-      "qkv_rope_cache_append", "paged_attention",
+      "kv_cache_append", "paged_attention",
       // cpu_f32_v1 graph ops
       "mul", "relu", "matmul"};
   return p;

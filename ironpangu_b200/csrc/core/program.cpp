@@ -295,6 +295,8 @@ struct Lowering {
     ins.inputs = {s.value};
     ins.attrs = {{"weight", L.need("weight")}, {"paired_weight", L.need("paired_weight")}, {"width", L.need("width")},
                  {"placement", L.need("placement")}, {"activation", "swiglu"}};
+    // the parameter holds both halves: gate rows, then the paired (up) rows
+    ins.attrs.emplace_back("paired_width", L.has("paired_width") ? *L.attr("paired_width") : L.need("width"));
     for (auto& kv : s.norm) ins.attrs.push_back(kv);
     ins.dtype = "bf16";
     ins.logical_node = sw;

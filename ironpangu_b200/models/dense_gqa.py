@@ -113,6 +113,26 @@ def random_rank_weights(c: DenseConfig, rank: int, world: int, device, seed: int
     return out
 
 
+def bundle_parameters(cfg: DenseConfig, weights: Dict[str, torch.Tensor], world: int = 1, prefix: str = "model") -> Dict[str, torch.Tensor]:
+    """This module's per-rank weight tensors under the parameter names of a bundle compiled from
+    ``compiler.sources.dense_gqa_source`` (``model.layers.N.self_attn.q_proj`` ..., pairs joined by ``|``). The q / k / v
+    matrices are row ranges of the packed projection - the same storage, so the bundle's engine finds them back to back and runs
+    one packed projection without copying them."""
+    c = cfg
+    hq, hk, hd = c.heads // world, c.kv_heads // world, c.head_dim
+    out = {f"{prefix}.embed_tokens": weights["embed"], f"{prefix}.norm": weights["final_norm"], "lm_head": weights["lm_head"]}
+    for l in range(c.layers):
+        p, q = f"layers.{l}.", f"{prefix}.layers.{l}."
+        a, m = q + "self_attn.", q + "mlp."
+        qkv = weights[p + "qkv"]
+        out[q + "input_layernorm"], out[q + "post_attention_layernorm"] = weights[p + "attn_norm"], weights[p + "ffn_norm"]
+        out[a + "q_proj"], out[a + "k_proj"], out[a + "v_proj"] = qkv[:hq * hd], qkv[hq * hd:(hq + hk) * hd], qkv[(hq + hk) * hd:]
+        out[a + "o_proj"] = weights[p + "o_proj"]
+        out[m + "gate_proj|" + m + "up_proj"] = weights[p + "gate_up"]
+        out[m + "down_proj"] = weights[p + "down"]
+    return out
+
+
 class DenseDecoder:
     """Per-rank executor for up to ``max_tokens`` (<= 8) query rows per launch group; larger batches are
     processed in tiles of 8 rows by :meth:`forward`."""

@@ -374,7 +374,7 @@ def gqa_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.T
     check(_lib.load().ifab_gqa_rope_kv_write(qkv.data_ptr(), _rows(qkv), positions.data_ptr(), slots.data_ptr(),
                                              page_table.data_ptr(), page_table.shape[1], page_tokens, k_cache.data_ptr(),
                                              v_cache.data_ptr(), num_pages, T, heads, kv_heads, head_dim,
-                                             rotary_dim or head_dim, theta, status_ptr, _stream()), "gqa_rope_kv_write")
+                                             head_dim if rotary_dim is None else rotary_dim, theta, status_ptr, _stream()), "gqa_rope_kv_write")
 
 
 def gqa_decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,

@@ -472,8 +472,25 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
             dcfg.layers = args.layers
         dweights = G.random_rank_weights(dcfg, rank, world, dev, seed=args.seed)
         mark("weights")
-        ddec = G.DenseDecoder(dcfg, dweights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs,
-                              keep_logits=not args.greedy_only)
+        if args.executor == "bundle":
+            # the family's .inferfabric source compiled for this job's width, run by the plan engine on the same tensors
+            import tempfile
+
+            from ironpangu_b200 import compiler
+            from ironpangu_b200.compiler.sources import dense_gqa_source
+            from ironpangu_b200.runtime.plan_engine import PlanEngine
+
+            work = tempfile.mkdtemp(prefix=f"ifab-worker-r{rank}-")
+            src = os.path.join(work, "model.inferfabric")
+            with open(src, "w") as f:
+                f.write(dense_gqa_source(dcfg, world, context=args.max_model_len))
+            compiled = compiler.write_bundle(src, os.path.join(work, "bundle"), prefill_tokens=8)
+            ddec = PlanEngine(compiled["dir"], None, fab, max_tokens=8, num_slots=args.max_num_seqs, keep_logits=not args.greedy_only,
+                              parameters=G.bundle_parameters(dcfg, dweights, world))
+            mark("bundle", f"program {compiled['program_sha256'][:16]}, arena {ddec.arena.bytes + ddec.arena.workspace_bytes} bytes")
+        else:
+            ddec = G.DenseDecoder(dcfg, dweights, fab, max_tokens=8, max_context=args.max_model_len, num_slots=args.max_num_seqs,
+                                  keep_logits=not args.greedy_only)
         mark("state", "K/V page caches and step workspace")
         dprefill = None
         if args.prefill_chunk > 8:

@@ -206,7 +206,8 @@ class PlanEngine:
 
     def __init__(self, bundle_dir: str, checkpoint_dir: Optional[str], fabric: Fabric, *, max_tokens: Optional[int] = 8,
                  num_slots: int = 1, keep_logits: bool = False, parameters: Optional[Dict[str, torch.Tensor]] = None,
-                 fused_head: Optional[bool] = None, fused_moe: Optional[bool] = None, l2_prefetch: Optional[bool] = None):
+                 fused_head: Optional[bool] = None, fused_moe: Optional[bool] = None, l2_prefetch: Optional[bool] = None,
+                 fused_gqa: Optional[bool] = None):
         """``max_tokens``: query rows per step (at most 8); ``None`` takes what the bundle's arena was planned for.
         ``parameters``: device tensors by the init plan's parameter names, used instead of a checkpoint (random-init
         benchmarks, weights another engine already holds); every parameter of the plan must be there with the plan's
@@ -255,12 +256,15 @@ class PlanEngine:
         self._index_scores = None
         self._cache_of: Dict[int, torch.Tensor] = {}     # cache-write instruction -> its pages
         self.caches: List[torch.Tensor] = []              # the same tensors in program order (one per attention layer)
+        self._kv_of: Dict[int, tuple] = {}                # K / V append instruction -> (key pages, value pages)
+        self._kv_pack = None                              # [k | v] rows of a step, for an append outside the fused group
         self.arena = FrozenArena(b, self.rank, T, dev)
         self._alloc(dev)
         self.bundle_sha256 = json.loads((b / "plan.json").read_text()).get("program_sha256", "")
         # measured at one GPU: requesting o_proj + shared expert (72 MB per layer) during the attention kernel costs 3.4 % (5.58 vs
         # 5.39 ms per step): the requests compete with the kernel's own loads. Off unless asked for; 2 = the output projection only.
         self.l2_prefetch = 0 if l2_prefetch is None else int(l2_prefetch)
+        self._fused_gqa_option = fused_gqa
         self._prepare(fused_head, fused_moe)
         self._graph = None
 
@@ -334,6 +338,44 @@ class PlanEngine:
                 private = sorted(users.get(kr, [])) == sorted([kgu, k]) and users.get(kgu, []) == [k]
                 self.moe_groups[k] = {"members": (kr, kgu), "router": kr, "gate_up": kgu, "x": kx,
                                       "ok": same_x and private and "shared_weight" in g and "shared_weight" in a}
+        # grouped-query attention: {q, k, v projections of one normalised input, rotary on q and k, page append, attention} runs
+        # as one packed projection + the rotate-and-append kernel + the split-KV attention (three kernels for seven instructions)
+        self.gqa_groups: Dict[int, dict] = {}
+        for k, i in enumerate(ins):
+            if i["op"] != "paged_attention" or ins[i["inputs"][1]]["op"] != "kv_cache_append":
+                continue
+            kq, kc = i["inputs"]
+            kk, kv = ins[kc]["inputs"]
+            if ins[kq]["op"] != "rotary_prefix" or ins[kk]["op"] != "rotary_prefix" or ins[kv]["op"] != "linear":
+                continue
+            lq, lk = ins[kq]["inputs"][0], ins[kk]["inputs"][0]
+            lins = [ins[lq], ins[lk], ins[kv]]
+            if any(l["op"] != "linear" or "paired_weight" in l["attrs"] or "activation" in l["attrs"] for l in lins):
+                continue
+            same_src = len({l["inputs"][0] for l in lins}) == 1 and len({(l["attrs"].get("norm_weight"), l["attrs"].get("norm_eps")) for l in lins}) == 1
+            rq, rk, a = ins[kq]["attrs"], ins[kk]["attrs"], i["attrs"]
+            same_rope = all(rq[f] == rk[f] for f in ("head_dim", "rotary_dim", "theta")) and rq["head_dim"] == a["head_dim"]
+            private = (users.get(lq, []) == [kq] and users.get(lk, []) == [kk] and users.get(kv, []) == [kc] and users.get(kq, []) == [k]
+                       and users.get(kk, []) == [kc] and users.get(kc, []) == [k])
+            if not (same_src and same_rope and private):
+                continue
+            names = [l["attrs"]["weight"] for l in lins]
+            self.gqa_groups[k] = {"members": (lq, kq, lk, kk, kv, kc), "x": lins[0]["inputs"][0], "cache": kc, "weights": names,
+                                  "norm": lins[0]["attrs"].get("norm_weight"), "norm_optional": "norm_optional" in lins[0]["attrs"],
+                                  "eps": float(lins[0]["attrs"].get("norm_eps", 1e-5)), "rotary_dim": int(rq["rotary_dim"]), "theta": float(rq["theta"])}
+        self._gqa_members = {m: k for k, g in self.gqa_groups.items() for m in g["members"]}
+        self._gqa_packed: Dict[int, torch.Tensor] = {}
+        for k, g in self.gqa_groups.items():
+            ws = [self._param(n) for n in g["weights"]]
+            adjacent = all(ws[j + 1].data_ptr() == ws[j].data_ptr() + ws[j].numel() * 2 for j in range(2)) and \
+                all(w.untyped_storage().data_ptr() == ws[0].untyped_storage().data_ptr() for w in ws)
+            rows = sum(w.shape[0] for w in ws)
+            # the three matrices as one [q | k | v] operand: a view when the caller's tensors already sit back to back
+            self._gqa_packed[k] = torch.as_strided(ws[0], (rows, ws[0].shape[1]), (ws[0].shape[1], 1)) if adjacent else torch.cat(ws, 0).contiguous()
+        if self.gqa_groups:
+            width = max(self._gqa_packed[k].shape[0] for k in self.gqa_groups)
+            self._gqa_qkv = torch.empty(self.T, width, dtype=BF16, device=self.fabric.device)     # read by attention while the workspace holds its splits
+        self.fused_gqa = bool(self.gqa_groups) and self._fused_gqa_option is not False
         self.fused_ctx_limit = 2048
         can_head = bool(self.head_groups) and all(g["ok"] for g in self.head_groups.values())
         self.fused_head = (can_head and self.max_context <= self.fused_ctx_limit) if fused_head is None else (bool(fused_head) and can_head)
@@ -370,8 +412,9 @@ class PlanEngine:
         self._head_members = {m: k for k, g in self.head_groups.items() for m in g["members"]}
         self._moe_members = {m: k for k, g in self.moe_groups.items() for m in g["members"]}
         per_token = self.program["launches_per_token"] + sum(1 for i in self.ins if i["op"] == "mla_attention")
+        per_token += sum(1 for i in self.ins if i["op"] == "paged_attention")        # split + merge
         self.launches_per_forward = (per_token - (4 * len(self.head_groups) if self.fused_head else 0)
-                                     - (2 * len(self.moe_groups) if self.fused_moe else 0))
+                                     - (2 * len(self.moe_groups) if self.fused_moe else 0) - (4 * len(self.gqa_groups) if self.fused_gqa else 0))
         self._describe()
 
     def _describe(self) -> None:
@@ -384,6 +427,9 @@ class PlanEngine:
         heads, moes = sorted(self.head_groups), sorted(self.moe_groups)
         emb = next((i for i in ins if i["op"] == "embedding"), None)
         head = next((i for i in ins if i["op"] == "lm_head"), None)
+        if self.gqa_groups and not heads and not moes and emb is not None and head is not None:
+            self._describe_dense(emb, head)
+            return
         if not heads or len(heads) != len(moes) or emb is None or head is None:
             return
         from ..models.mla_moe import MlaMoeConfig
@@ -415,6 +461,43 @@ class PlanEngine:
             w[p + "shared_gate_up"] = self._param(gu["shared_weight"] + "|" + gu["shared_paired_weight"])
             w[p + "shared_down"] = self._param(dn["shared_weight"])
 
+    def _describe_dense(self, emb: dict, head: dict) -> None:
+        """The same for a stack of {grouped-query attention, SwiGLU} layers, in the vocabulary of ``models/dense_gqa.py``: the
+        dense prompt executor (``models/dense_prefill.py``) runs on a bundle's engine through ``cfg``, ``w``, ``hq`` / ``hk`` /
+        ``vl`` and the K / V pages per layer."""
+        from ..models.dense_gqa import DenseConfig
+
+        ins, groups = self.ins, sorted(self.gqa_groups)
+        a0 = ins[groups[0]]["attrs"]
+        w: Dict[str, torch.Tensor] = {}
+        k_cache, v_cache, ffn = [], [], 0
+        for l, k in enumerate(groups):
+            g, p = self.gqa_groups[k], f"layers.{l}."
+            o = next((ins[u] for u in range(k + 1, len(ins)) if ins[u]["op"] == "linear_allreduce" and ins[u]["inputs"][0] == k), None)
+            if o is None or g["norm"] is None:
+                return
+            ko = ins.index(o)
+            up = next((ins[u] for u in range(ko + 1, len(ins)) if ins[u]["op"] == "linear" and ins[u]["attrs"].get("activation") == "swiglu"
+                       and ins[u]["inputs"][0] == ko and "norm_weight" in ins[u]["attrs"]), None)
+            down = None if up is None else next((ins[u] for u in range(ko + 1, len(ins)) if ins[u]["op"] == "linear_allreduce"
+                                                 and ins[u]["inputs"][0] == ins.index(up)), None)
+            if down is None:
+                return
+            w[p + "attn_norm"], w[p + "qkv"], w[p + "o_proj"] = self._param(g["norm"]), self._gqa_packed[k], self._param(o["attrs"]["weight"])
+            w[p + "ffn_norm"] = self._param(up["attrs"]["norm_weight"])
+            w[p + "gate_up"] = self._param(up["attrs"]["weight"] + "|" + up["attrs"]["paired_weight"])
+            w[p + "down"] = self._param(down["attrs"]["weight"])
+            ffn = int(up["attrs"]["width"]) * self.world
+            kc, vc = self._kv_of[g["cache"]]
+            k_cache.append(kc)
+            v_cache.append(vc)
+        w["embed"], w["final_norm"], w["lm_head"] = self._param(emb["attrs"]["weight"]), self._param(head["attrs"]["norm_weight"]), self._param(head["attrs"]["weight"])
+        g0 = self.gqa_groups[groups[0]]
+        self.cfg = DenseConfig(layers=len(groups), hidden=emb["width"], heads=int(a0["heads"]), kv_heads=int(a0["kv_heads"]), head_dim=int(a0["head_dim"]),
+                               ffn=ffn, vocab=int(emb["attrs"]["vocab"]), theta=g0["theta"], eps=g0["eps"], page_tokens=self.page_tokens)
+        self.w, self.k_cache, self.v_cache = w, k_cache, v_cache
+        self.hq, self.hk, self.vl = self.cfg.heads // self.world, self.cfg.kv_heads // self.world, self.cfg.vocab // self.world
+
     def forward_feedback(self, T: Optional[int] = None) -> torch.Tensor:
         """One step whose sampled token and position + 1 become the inputs of the next step (device-side feedback)."""
         T = self.T if T is None else T
@@ -427,7 +510,7 @@ class PlanEngine:
     def _alloc(self, dev) -> None:
         """Views into the frozen arena for every instruction result; KV pages as sequence state beside it."""
         T = self.T
-        max_heads = 1
+        max_heads, gqa_split_floats = 1, 0
         f32, i32 = torch.float32, torch.int32
 
         def view(k: int, shape, dtype) -> torch.Tensor:
@@ -444,6 +527,20 @@ class PlanEngine:
             if op == "mla_kv_write":
                 self._cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
                 self.caches.append(self._cache_of[k])
+            elif op == "kv_cache_append":
+                if i["attrs"].get("cache_dtype", "bf16") != "bf16":
+                    raise NotImplementedError("a compiled program's K / V pages are bf16")
+                hd = int(i["attrs"]["head_dim"])
+                kvl = w // (2 * hd)
+                pages = [torch.zeros(self.num_pages, self.page_tokens, kvl, hd, dtype=BF16, device=dev) for _ in range(2)]
+                self._kv_of[k] = tuple(pages)
+                if self._kv_pack is None or self._kv_pack.shape[1] < w:
+                    self._kv_pack = torch.empty(T, w, dtype=BF16, device=dev)
+            elif op == "paged_attention":
+                gqa_split_floats = max(gqa_split_floats, (int(i["attrs"]["heads"]) // self.world) * (int(i["attrs"]["head_dim"]) + 2))
+                if int(i["attrs"].get("window", 0)) not in (0,) and int(i["attrs"]["window"]) < self.max_context:
+                    raise NotImplementedError("windowed grouped-query attention has no device kernel")
+                self.vals[k] = view(k, (T, w), BF16)
             elif op == "index_cache_append":
                 if i["attrs"].get("cache_dtype", "bf16") != "bf16":
                     raise NotImplementedError("the device index cache holds bf16 keys (int8 index keys are an oracle-only layout)")
@@ -478,7 +575,8 @@ class PlanEngine:
         head = next((i for i in self.ins if i["op"] == "lm_head"), None)
         self.x = self.vals[head["inputs"][0]] if head is not None else None      # the final hidden rows (before the last norm)
         # kernel scratch comes out of the frozen workspace: the attention splits and the argmax partials never live at once
-        self.scratch = self.arena.workspace(T * max_heads * self.max_splits * (512 + 2) * 4).view(f32)
+        has_latent = any(i["op"] == "mla_attention" for i in self.ins)
+        self.scratch = self.arena.workspace(T * self.max_splits * max(max_heads * (512 + 2) if has_latent else 0, gqa_split_floats, 1) * 4).view(f32)
         self.partial = self.arena.workspace(self._partial_floats * 4).view(f32)
 
     def _param(self, name: str, optional: bool = False):
@@ -501,10 +599,11 @@ class PlanEngine:
 
         head = (self.fused_head if self.fuse_override is None else (self.fuse_override and self.can_fuse_head)) and T <= self.fused_head_rows
         moe = self.fused_moe and T <= 2
+        gqa = self.fused_gqa
         for k, i in enumerate(self.ins):
             op, a, ins = i["op"], i["attrs"], i["inputs"]
-            if (head and k in self._head_members) or (moe and k in self._moe_members):
-                if op == "mla_kv_write":
+            if (head and k in self._head_members) or (moe and k in self._moe_members) or (gqa and k in self._gqa_members):
+                if op in ("mla_kv_write", "kv_cache_append"):
                     V[k] = k                  # the cache of this write, for whoever reads it
                 continue
             norm_w = self._param(a["norm_weight"], "norm_optional" in a) if "norm_weight" in a else None
@@ -528,6 +627,32 @@ class PlanEngine:
                             w_shared_gu=self._param(gu["shared_weight"] + "|" + gu["shared_paired_weight"]),
                             w_shared_down=self._param(a["shared_weight"]), logits=logits[:T], ids=ids[:T], wts=wts[:T],
                             act=V[g["gate_up"]][:T], out=val(k))
+            elif gqa and k in self.gqa_groups:
+                g = self.gqa_groups[k]
+                H, KVH, hd = int(a["heads"]) // self.world, int(a["kv_heads"]) // self.world, int(a["head_dim"])
+                wq = self._gqa_packed[k]
+                qkv = self._gqa_qkv[:T, :wq.shape[0]]
+                kc, vc = self._kv_of[g["cache"]]
+                K.gemv(val(g["x"]), wq, norm_w=self._param(g["norm"], g["norm_optional"]) if g["norm"] else None, eps=g["eps"], out=qkv)
+                K.gqa_rope_kv_write(qkv, pos, slot, self.page_table, kc, vc, heads=H, kv_heads=KVH, head_dim=hd, rotary_dim=g["rotary_dim"],
+                                    theta=g["theta"], status_ptr=st)
+                K.gqa_decode_attention(qkv, kc, vc, pos, slot, self.page_table, heads=H, kv_heads=KVH, head_dim=hd, scale=float(a["scale"]),
+                                       keys_per_split=self.kps, max_splits=self.max_splits, scratch=self.scratch, out=val(k), status_ptr=st)
+            elif op == "kv_cache_append":
+                # k and v rows side by side in the pack buffer, then the append kernel with no query heads and no rotation
+                kr, vr = val(ins[0]), val(ins[1])
+                kc, vc = self._kv_of[k]
+                pack = self._kv_pack[:T, :kr.shape[1] + vr.shape[1]]
+                pack[:, :kr.shape[1]].copy_(kr)
+                pack[:, kr.shape[1]:].copy_(vr)
+                K.gqa_rope_kv_write(pack, pos, slot, self.page_table, kc, vc, heads=0, kv_heads=kc.shape[2], head_dim=kc.shape[3], rotary_dim=0,
+                                    theta=2.0, status_ptr=st)
+                V[k] = k
+            elif op == "paged_attention":
+                kc, vc = self._kv_of[V[ins[1]]]
+                K.gqa_decode_attention(val(ins[0]), kc, vc, pos, slot, self.page_table, heads=int(a["heads"]) // self.world,
+                                       kv_heads=kc.shape[2], head_dim=kc.shape[3], scale=float(a["scale"]), keys_per_split=self.kps,
+                                       max_splits=self.max_splits, scratch=self.scratch, out=val(k), status_ptr=st)
             elif op == "embedding":
                 K.embedding(tok, self._param(a["weight"]), out=val(k), status_ptr=st)
             elif op == "view":
@@ -628,5 +753,5 @@ class PlanEngine:
         return g
 
     def reset(self) -> None:
-        for c in list(self.caches) + list(self._index_cache_of.values()):
+        for c in list(self.caches) + list(self._index_cache_of.values()) + [t for kv in self._kv_of.values() for t in kv]:
             c.zero_()
