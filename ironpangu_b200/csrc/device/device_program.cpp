@@ -116,6 +116,12 @@ struct HeadGroup {
   uint32_t qb = 0, write = 0, absorb = 0, qkv = 0;
   bool ok = false;
 };
+// grouped-query attention: {q, k, v projections of one normalised input, rotary on q and k, page append} feeding one attention
+struct GqaGroup {
+  uint32_t lq = 0, rq = 0, lk = 0, rk = 0, lv = 0, cache = 0, x = 0;
+  void* packed = nullptr;      // [q | k | v] rows of the three matrices, one operand
+  int rows = 0, k = 0;
+};
 
 }  // namespace
 
@@ -138,6 +144,11 @@ struct DeviceProgram::Impl {
   std::map<uint32_t, HeadGroup> heads;                          // attention instruction -> its group
   std::set<uint32_t> head_members;
   bool fused_head = false;
+  std::map<uint32_t, GqaGroup> gqa;                             // paged-attention instruction -> its group
+  std::set<uint32_t> gqa_members;
+  char *gqa_qkv = nullptr, *kv_pack = nullptr;                  // [rows, q | k | v] of a step; [rows, k | v] for an append outside a group
+  long gqa_ld = 0, kv_pack_ld = 0;
+  std::vector<void*> owned;                                     // packed operands and pack buffers
   // control block (device): tokens | positions | slots | next ids | next values, page table; pinned mirror on the host
   int32_t *d_tokens = nullptr, *d_positions = nullptr, *d_slots = nullptr, *d_next = nullptr, *d_page_table = nullptr;
   float* d_next_vals = nullptr;
@@ -155,6 +166,7 @@ struct DeviceProgram::Impl {
   ~Impl() {
     for (auto& g : graphs) cudaGraphExecDestroy(g.second);
     for (auto& c : cache_of) cudaFree(c.second);
+    for (void* o : owned) cudaFree(o);
     if (block) cudaFree(block);
     if (fabric_block) cudaFree(fabric_block);
     if (d_page_table) cudaFree(d_page_table);
@@ -303,6 +315,15 @@ void DeviceProgram::Impl::load(const std::string& bundle, const std::string& che
       dmalloc(&pages, bytes, "KV pages");
       cu(cudaMemset(pages, 0, bytes), "KV clear");
       cache_of[k] = pages;
+    } else if (x.op == "kv_cache_append") {
+      // key pages, then value pages: [pages, page_tokens, local kv heads, head_dim] each
+      if (x.has("cache_dtype") && x.s("cache_dtype") != "bf16") fail(ErrorKind::NotImplemented, "device program: K / V pages are bf16");
+      void* pages = nullptr;
+      const uint64_t bytes = (uint64_t)num_pages * page_tokens * x.width * 2;
+      dmalloc(&pages, bytes, "K/V pages");
+      cu(cudaMemset(pages, 0, bytes), "K/V clear");
+      cache_of[k] = pages;
+      kv_pack_ld = std::max<long>(kv_pack_ld, x.width);
     } else if (x.op == "router_topk") {
       const int E = x.i("experts");
       val[k] = lease(k, (uint64_t)T * x.width * 8 + (uint64_t)T * E * 4, x.width, 4);
@@ -360,6 +381,53 @@ void DeviceProgram::Impl::load(const std::string& bundle, const std::string& che
       head_members.insert(kv.second.write);
       head_members.insert(kv.second.absorb);
     }
+  // ---- dispatcher: the grouped-query attention group as packed projection + rotate-and-append + attention ----
+  for (uint32_t k = 0; k < ins.size(); ++k) {
+    const Ins& x = ins[k];
+    if (x.op != "paged_attention") continue;
+    if (x.has("window") && x.i("window") > 0 && (uint32_t)x.i("window") < context) fail(ErrorKind::NotImplemented, "device program: windowed grouped-query attention has no kernel");
+    GqaGroup g;
+    g.rq = x.in.at(0);
+    g.cache = x.in.at(1);
+    if (ins[g.cache].op != "kv_cache_append" || ins[g.rq].op != "rotary_prefix") continue;
+    g.rk = ins[g.cache].in.at(0);
+    g.lv = ins[g.cache].in.at(1);
+    if (ins[g.rk].op != "rotary_prefix" || ins[g.lv].op != "linear") continue;
+    g.lq = ins[g.rq].in.at(0);
+    g.lk = ins[g.rk].in.at(0);
+    const Ins *L[3] = {&ins[g.lq], &ins[g.lk], &ins[g.lv]};
+    bool ok = true;
+    for (const Ins* l : L) ok = ok && l->op == "linear" && !l->has("paired_weight") && !l->has("activation") && l->in.at(0) == L[0]->in.at(0);
+    for (const char* f : {"norm_weight", "norm_eps", "norm_optional"})
+      for (const Ins* l : L) ok = ok && l->has(f) == L[0]->has(f) && (!l->has(f) || l->s(f) == L[0]->s(f));
+    const Ins &rq = ins[g.rq], &rk = ins[g.rk];
+    for (const char* f : {"head_dim", "rotary_dim", "theta"}) ok = ok && rq.s(f) == rk.s(f);
+    ok = ok && rq.s("head_dim") == x.s("head_dim") && only_user(g.lq, g.rq) && only_user(g.lk, g.rk) && only_user(g.lv, g.cache) && only_user(g.rq, k) &&
+         only_user(g.rk, g.cache) && only_user(g.cache, k);
+    if (!ok) continue;
+    g.x = L[0]->in.at(0);
+    g.k = (int)dims(L[0]->s("weight")).at(1);
+    for (const Ins* l : L) g.rows += (int)dims(l->s("weight")).at(0);
+    dmalloc(&g.packed, (uint64_t)g.rows * g.k * 2, "packed q|k|v operand");
+    owned.push_back(g.packed);
+    uint64_t at = 0;
+    for (const Ins* l : L) {
+      const uint64_t bytes = dims(l->s("weight"))[0] * (uint64_t)g.k * 2;
+      cu(cudaMemcpy((char*)g.packed + at, P(l->s("weight")), bytes, cudaMemcpyDeviceToDevice), "packing q|k|v");
+      at += bytes;
+    }
+    gqa_ld = std::max<long>(gqa_ld, g.rows);
+    for (uint32_t m : {g.lq, g.rq, g.lk, g.rk, g.lv, g.cache}) gqa_members.insert(m);
+    gqa[k] = g;
+  }
+  if (gqa_ld) {
+    dmalloc((void**)&gqa_qkv, (uint64_t)rows * gqa_ld * 2, "q|k|v rows of a step");
+    owned.push_back(gqa_qkv);
+  }
+  if (kv_pack_ld) {
+    dmalloc((void**)&kv_pack, (uint64_t)rows * kv_pack_ld * 2, "k|v rows of a step");
+    owned.push_back(kv_pack);
+  }
   allocations_at_ready = g_device_allocations;
   ready = true;
 }
@@ -375,6 +443,7 @@ void DeviceProgram::Impl::dispatch(int T) {
     const Ins& x = ins[k];
     if (x.op == "view") continue;
     if (head && head_members.count(k)) continue;
+    if (gqa_members.count(k)) continue;
     const void* norm_w = x.has("norm_weight") ? (x.has("norm_optional") ? P_optional(x.s("norm_weight")) : P(x.s("norm_weight"))) : nullptr;
     const float eps = x.f("norm_eps", 1e-5f);
     ++count;
@@ -386,6 +455,52 @@ void DeviceProgram::Impl::dispatch(int T) {
                                   P(qb.s("weight")), P(x.s("weight")), cache_of.at(g.write), d_positions, d_slots, d_page_table, max_pages, page_tokens,
                                   num_pages, nullptr, 0, x.i("window"), 1.f / std::sqrt((float)x.i("scale_dim")), T, x.i("heads"), ins[qb.in[0]].i("width"),
                                   ab.i("nope"), x.i("value"), V(k).ptr, V(k).ld, status, st),
+             x.name);
+    } else if (gqa.count(k)) {
+      const GqaGroup& g = gqa[k];
+      const Ins& lq = ins[g.lq];
+      const int hd = x.i("head_dim"), H = x.i("heads"), KVH = x.i("kv_heads");
+      const Val& in = V(g.x);
+      const void* nw = lq.has("norm_weight") ? (lq.has("norm_optional") ? P_optional(lq.s("norm_weight")) : P(lq.s("norm_weight"))) : nullptr;
+      char* kv = (char*)cache_of.at(g.cache);
+      char* vpages = kv + (uint64_t)num_pages * page_tokens * KVH * hd * 2;
+      const uint64_t scratch = (uint64_t)T * H * max_splits * (hd + 2) * 4;
+      count += 3;                                                      // projection, rotate-and-append, split, merge
+      kernel(ifab_gemv_bf16(in.ptr, in.ld, g.packed, nw, lq.f("norm_eps", 1e-5f), 0, nullptr, 0, gqa_qkv, gqa_ld, 0, T, g.rows, g.k, 0, st), lq.name);
+      kernel(ifab_gqa_rope_kv_write(gqa_qkv, gqa_ld, d_positions, d_slots, d_page_table, max_pages, page_tokens, kv, vpages, num_pages, T, H, KVH, hd,
+                                    ins[g.rq].i("rotary_dim"), ins[g.rq].f("theta", 10000.f), status, st),
+             ins[g.cache].name);
+      kernel(ifab_gqa_decode_attention(gqa_qkv, gqa_ld, kv, vpages, d_positions, d_slots, d_page_table, max_pages, page_tokens, num_pages, x.f("scale", 1.f), T, H,
+                                       KVH, hd, kps, max_splits, (float*)workspace(scratch), scratch, V(k).ptr, V(k).ld, status, st),
+             x.name);
+    } else if (x.op == "rotary_prefix") {
+      const Val& in = V(x.in.at(0));
+      kernel(ifab_rope_prefix(in.ptr, in.ld, d_positions, V(k).ptr, V(k).ld, T, x.i("heads"), x.i("head_dim"), x.i("rotary_dim"), x.f("theta", 10000.f), st), x.name);
+    } else if (x.op == "add") {
+      const Val &a = V(x.in.at(0)), &b = V(x.in.at(1));
+      if (x.dtype != "bf16" || a.esize != 2 || b.esize != 2) fail(ErrorKind::NotImplemented, "device program: add over f32 rows has no kernel");
+      kernel(ifab_add_rows(a.ptr, a.ld, b.ptr, b.ld, V(k).ptr, V(k).ld, T, (int)x.width, st), x.name);
+    } else if (x.op == "kv_cache_append") {
+      // outside a group: k and v rows side by side in the pack buffer, then the append kernel with no query heads and no rotation
+      const Val &kr = V(x.in.at(0)), &vr = V(x.in.at(1));
+      const int hd = x.i("head_dim"), kvl = (int)x.width / (2 * hd);
+      const size_t half = (size_t)kvl * hd * 2;
+      cu(cudaMemcpy2DAsync(kv_pack, kv_pack_ld * 2, kr.ptr, kr.ld * 2, half, T, cudaMemcpyDeviceToDevice, (cudaStream_t)st), "k rows into the pack buffer");
+      cu(cudaMemcpy2DAsync(kv_pack + half, kv_pack_ld * 2, vr.ptr, vr.ld * 2, half, T, cudaMemcpyDeviceToDevice, (cudaStream_t)st), "v rows into the pack buffer");
+      char* kv = (char*)cache_of.at(k);
+      count += 2;
+      kernel(ifab_gqa_rope_kv_write(kv_pack, kv_pack_ld, d_positions, d_slots, d_page_table, max_pages, page_tokens, kv,
+                                    kv + (uint64_t)num_pages * page_tokens * kvl * hd * 2, num_pages, T, 0, kvl, hd, 0, 2.f, status, st),
+             x.name);
+    } else if (x.op == "paged_attention") {
+      const int hd = x.i("head_dim"), H = x.i("heads"), KVH = x.i("kv_heads");
+      char* kv = (char*)cache_of.at(x.in.at(1));
+      const uint64_t scratch = (uint64_t)T * H * max_splits * (hd + 2) * 4;
+      const Val& q = V(x.in.at(0));
+      ++count;
+      kernel(ifab_gqa_decode_attention(q.ptr, q.ld, kv, kv + (uint64_t)num_pages * page_tokens * KVH * hd * 2, d_positions, d_slots, d_page_table, max_pages,
+                                       page_tokens, num_pages, x.f("scale", 1.f), T, H, KVH, hd, kps, max_splits, (float*)workspace(scratch), scratch, V(k).ptr,
+                                       V(k).ld, status, st),
              x.name);
     } else if (x.op == "embedding") {
       kernel(ifab_embedding_bf16(d_tokens, P(x.s("weight")), V(k).ptr, T, (int)x.width, x.i("vocab"), status, st), x.name);

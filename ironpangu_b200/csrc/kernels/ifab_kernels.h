@@ -197,6 +197,13 @@ int ifab_mla_head_decode_pf(const void* qkv, long ldqkv, const void* q_norm, con
                             long ldo, uint32_t* status, const void* pf0, uint64_t pf0_bytes, const void* pf1, uint64_t pf1_bytes,
                             const void* pf2, uint64_t pf2_bytes, void* stream);
 
+/* ---- row operators shared by compiled programs (hybrid_ops.cu) ---- */
+/* Half-rotation RoPE over the first rotary_dim columns of every head of a row; the other columns are copied. */
+int ifab_rope_prefix(const void* x, long ldx, const int32_t* positions, void* y, long ldy, int T, int heads, int head_dim, int rotary_dim,
+                     float theta, void* stream);
+/* y = a + b over [rows, n] bf16 (f32 sum, one rounding). */
+int ifab_add_rows(const void* a, long lda, const void* b, long ldb, void* y, long ldy, int rows, int n, void* stream);
+
 /* ---- hyper-connection / hybrid-model operators (hc_ops.cu); all mixing arithmetic in f32 ---- */
 /* causal depthwise conv with residual; w f32 [C_total, taps] (this rank's channels start at c_offset); state bf16 [slots, taps-1, C] */
 int ifab_mome(const void* x, long ldx, const float* w, void* state, const int32_t* positions, const int32_t* slots, void* y,

@@ -147,3 +147,63 @@ def test_server_runs_the_bundle_natively(tmp_path):
         proc.send_signal(signal.SIGTERM)
         proc.wait(timeout=60)
     assert proc.returncode == 0
+
+
+def test_dense_bundle_runs_natively_like_the_plan_engine(tmp_path):
+    """A grouped-query-attention program: the native executor packs q | k | v, rotates and appends, attends - tokens equal the
+    CPU interpreter's where its logits are decisive, and the Python plan engine's row for row."""
+    from ironpangu_b200 import _build, compiler
+    from ironpangu_b200.compiler.sources import dense_gqa_source
+    from ironpangu_b200.models.dense_gqa import DenseConfig
+    from ironpangu_b200.parallel.fabric import Fabric
+    from ironpangu_b200.runtime.plan_engine import PlanEngine
+
+    cfg = DenseConfig.tiny(2)
+    src, ck, bundle = tmp_path / "dense.inferfabric", tmp_path / "ck", tmp_path / "bundle"
+    src.write_text(dense_gqa_source(cfg, 1, 128))
+    assert compiler.cli("synth-checkpoint", str(src), str(ck), "--seed", "4").returncode == 0
+    r = compiler.cli("compile-token", str(src), str(ck), str(bundle), "--resident-sequences", "2", "--prefill-tokens", "8")
+    assert r.returncode == 0, r.stderr
+    lib = C.CDLL(str(_build.build_device()))
+    lib.ifab_device_program_error.restype = C.c_char_p
+    h = C.c_void_p()
+    assert lib.ifab_device_program_open(str(bundle).encode(), str(ck).encode(), 0, 2, C.byref(h)) == 0, lib.ifab_device_program_error()
+
+    def run(tokens, positions, slots):
+        n = len(tokens)
+        arr = lambda v: (C.c_int32 * n)(*v)
+        out = (C.c_int32 * n)()
+        assert lib.ifab_device_program_rows(h, arr(tokens), arr(positions), arr(slots), n, out) == 0, lib.ifab_device_program_error()
+        return list(out)
+
+    seq = torch.randint(0, cfg.vocab, (27,), generator=torch.Generator().manual_seed(9)).tolist()
+    ref = torch.tensor(compiler.interpret(src.read_text(), str(ck), seq, all_logits=True)["prompt_logits"])
+    got = []
+    for s in range(0, len(seq), 8):
+        got += run(seq[s:s + 8], list(range(s, min(len(seq), s + 8))), [1] * len(seq[s:s + 8]))
+    decisive = 0
+    for i, t in enumerate(got):
+        top2 = ref[i].topk(2).values
+        if float(top2[0] - top2[1]) > 2e-2:
+            decisive += 1
+            assert t == int(ref[i].argmax()), (i, t)
+    assert decisive >= len(seq) // 2
+    fab = Fabric(0, 1)
+    eng = PlanEngine(str(bundle), str(ck), fab, max_tokens=8, num_slots=2)
+    same = []
+    for s in range(0, len(seq), 8):
+        n = len(seq[s:s + 8])
+        eng.tokens[:n].copy_(torch.tensor(seq[s:s + n], dtype=torch.int32))
+        eng.positions[:n].copy_(torch.arange(s, s + n, dtype=torch.int32))
+        eng.slots[:n].fill_(1)
+        eng.forward(n)
+        same += eng.next_ids[:n].tolist()
+    assert got == same
+    fab.close()
+    one = [run([seq[i]], [i], [0])[0] for i in range(10)]            # single rows in the other slot, graph replay after the first
+    assert all(a == b for i, (a, b) in enumerate(zip(one, got)) if float(ref[i].topk(2).values[0] - ref[i].topk(2).values[1]) > 2e-2)
+    buf = C.create_string_buffer(1 << 16)
+    assert lib.ifab_device_program_audit(h, buf, len(buf)) == 0
+    audit = json.loads(buf.value)
+    assert audit["device_allocations_after_ready"] == 0 and audit["launches_per_step"] == 1 + cfg.layers * 7 + 1
+    assert lib.ifab_device_program_close(h) == 0
