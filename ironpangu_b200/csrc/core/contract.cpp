@@ -26,7 +26,8 @@ const std::map<std::string, OpRule>& rules() {
       {"embedding", {{"ifab_embedding_bf16"}, {}, false, {"vocab", "weight", "width"}, kTensor}},
       {"linear", {{"ifab_gemv_bf16", "ifab_gemm_bf16"}, {kTensor}, false, {"weight", "width"}, kTensor}},
       {"view", {{"view"}, {kAny}, false, {"start", "width"}, kView}},
-      {"mla_kv_write", {{"ifab_mla_kv_write", "ifab_mla_kv_write_q8"}, {kAny, kAny}, false, {"eps", "theta", "weight"}, kCache}},
+      // a third input holds the attention-sink rows that every query of the cache also attends to
+      {"mla_kv_write", {{"ifab_mla_kv_write", "ifab_mla_kv_write_q8"}, {kAny, kAny}, true, {"eps", "theta", "weight"}, kCache}},
       {"mla_q_absorb", {{"ifab_mla_q_absorb"}, {kTensor}, false, {"heads", "latent", "nope", "rope", "theta", "weight"}, kTensor}},
       // a third input is the sparse indexer's selection (selection = learned_indices)
       {"mla_attention", {{"ifab_mla_decode_attention", "ifab_mla_prefill_attention"}, {kTensor, kCache}, true, {"heads", "latent", "weight"}, kTensor}},
@@ -112,6 +113,8 @@ void validate_kernels(const Program& p) {
       if (kind == kView) kind = p.instructions[region_of(p, src).root].kind;
       if (kind != r.inputs[k]) bad(i, "input " + std::to_string(k) + " has the wrong kind");
     }
+    if (i.op == "mla_kv_write" && (i.inputs.size() > 3 || (i.inputs.size() == 3 && p.instructions[i.inputs[2]].op != "sink_normalize")))
+      bad(i, "the third input must be the sink rows of a sink_normalize");
     if (r.kind != kAny && i.kind != r.kind) bad(i, "result has the wrong kind");
     for (const auto& a : r.attrs)
       if (!i.attr(a)) bad(i, "missing attribute " + a);
@@ -171,13 +174,26 @@ void validate_bindings(const Program& p, const init::Plan& plan) {
       const std::string* pair = i.attr(pair_key);
       return (pair && !pair->empty()) ? *name + "|" + *pair : *name;
     };
-    const std::string names[3] = {joined("weight", "paired_weight"), joined("shared_weight", "shared_paired_weight"),
-                                  i.attr("norm_weight") ? *i.attr("norm_weight") : std::string()};
+    std::string names[3] = {joined("weight", "paired_weight"), joined("shared_weight", "shared_paired_weight"),
+                            i.attr("norm_weight") ? *i.attr("norm_weight") : std::string()};
+    // operators whose `weight` names a scope: their parameters are the tensors under it
+    std::vector<std::string> scoped;
+    if (i.op == "mhc_pre" || i.op == "mhc_merge") {
+      for (const char* part : {".phi", ".gamma", ".alpha", ".beta"}) scoped.push_back(names[0] + part);
+      names[0].clear();
+    } else if (i.op == "sink_normalize") {
+      scoped = {names[0] + ".param_sink_compressed_kv", names[0] + ".param_sink_k_pe", i.attr("norm") ? *i.attr("norm") : std::string()};
+      names[0].clear();
+    }
+    for (const auto& nm : scoped) {
+      if (nm.empty() || !params.count(nm)) invalid("invalid binding contract: " + i.name + " reads " + nm + ", which rank " + std::to_string(plan.rank) + " does not load");
+      used.insert(nm);
+    }
     for (int k = 0; k < 3; ++k) {
       if (names[k].empty()) continue;
       if (!params.count(names[k])) {
         // optional norms may be absent from a checkpoint; everything else must be bound
-        if (k == 2 && i.attr("norm_optional")) continue;
+        if ((k == 2 && i.attr("norm_optional")) || (k == 0 && i.op == "optional_norm")) continue;
         invalid("invalid binding contract: " + i.name + " reads " + names[k] + ", which rank " + std::to_string(plan.rank) + " does not load");
       }
       used.insert(names[k]);

@@ -401,6 +401,39 @@ std::vector<ParamSpec> specs_of(const Program& p) {
       s.name = *i.attr("weight");
       s.parts.push_back({s.name + ".weight", {in_width(i, 0)}, Need::Full, DType::Bf16});
       out.push_back(s);
+    } else if (op == "mhc_pre" || op == "mhc_merge") {
+      // the mixing module of a hyper-connection: four f32 tensors under the module's scope (no ".weight" suffix)
+      const uint64_t S = attr_u(i, "streams"), total = in_width(i), M = S * S + 2 * S;
+      const std::string base = *i.attr("weight");
+      const std::pair<const char*, std::vector<uint64_t>> parts[4] = {{".phi", {M, total}}, {".gamma", {total}}, {".alpha", {3}}, {".beta", {M}}};
+      for (auto& kv : parts) {
+        ParamSpec s;
+        s.name = base + kv.first;
+        s.dtype = DType::F32;
+        s.parts.push_back({s.name, kv.second, Need::Full, DType::F32});
+        out.push_back(s);
+      }
+    } else if (op == "mome") {
+      // depthwise taps of every channel of the model (a rank convolving its own channel range indexes into them)
+      const bool sharded = i.attr("placement") && *i.attr("placement") == "tp_channels";
+      ParamSpec s;
+      s.name = *i.attr("weight");
+      s.dtype = DType::F32;
+      s.parts.push_back({s.name + ".weight", {(uint64_t)i.width * (sharded ? tp : 1), 1, attr_u(i, "taps")}, Need::Full, DType::F32});
+      out.push_back(s);
+    } else if (op == "sink_normalize") {
+      const uint64_t count = attr_u(i, "count"), latent = attr_u(i, "latent"), rope = attr_u(i, "rope");
+      const std::string base = *i.attr("weight");
+      ParamSpec kv, pe, nw;
+      kv.name = base + ".param_sink_compressed_kv";
+      kv.parts.push_back({kv.name, {count, latent}, Need::Full, DType::Bf16});
+      pe.name = base + ".param_sink_k_pe";
+      pe.parts.push_back({pe.name, {count, rope}, Need::Full, DType::Bf16});
+      nw.name = *i.attr("norm");
+      nw.parts.push_back({nw.name + ".weight", {latent}, Need::Full, DType::Bf16});
+      out.push_back(kv);
+      out.push_back(pe);
+      out.push_back(nw);
     } else if (op == "mla_q_absorb" || op == "mla_attention") {
       ParamSpec s;
       s.name = *i.attr("weight");
@@ -540,7 +573,10 @@ std::vector<Plan> plan_all(const Program& p, const Checkpoint& ckpt) {
           l.tensor = tname;
           l.shard = t.file;
           l.src_dtype = t.dtype;
-          const uint64_t R = n.full.size() == 1 ? 1 : n.full[0], C = n.full.size() == 1 ? n.full[0] : n.full[1];
+          // a tensor of rank three or more is rows x (everything else): [channels, 1, taps] loads as [channels, taps]
+          uint64_t inner = 1;
+          for (size_t d = 1; d < n.full.size(); ++d) inner *= n.full[d];
+          const uint64_t R = n.full.size() == 1 ? 1 : n.full[0], C = n.full.size() == 1 ? n.full[0] : inner;
           uint64_t r_local = R, c_local = C;
           switch (n.shard) {
             case Need::Full:

@@ -418,6 +418,8 @@ struct Lowering {
         ins.dtype = dtype_of(n, ins.inputs);
       } else {
         for (uint32_t in : n.inputs) ins.inputs.push_back(value_of(in));
+        // the streams a hyper-connection mixed are read again when its branch returns: name them, so that they stay alive
+        if (n.op == "mhc_post") ins.inputs.push_back(value_of(N(n.inputs[0]).inputs[0]));
         if (n.op == "cache_norm_rope_append") ins.op = "mla_kv_write";
         if (n.op == "mla_query") ins.op = "mla_q_absorb";
         if (n.op == "add") {

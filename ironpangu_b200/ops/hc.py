@@ -28,20 +28,26 @@ def mome(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, positions: torch
 
 
 def mhc_pre(X: torch.Tensor, phi: torch.Tensor, gamma: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor, *, sinkhorn: int = 20,
-            eps: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Returns ``(y bf16 [T, W], post f32 [T, S], comb f32 [T, S, S])`` for residual streams ``X`` bf16 ``[T, S, W]``."""
+            eps: float = 1e-6, out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Returns ``(y bf16 [T, W], post f32 [T, S], comb f32 [T, S, S])`` for residual streams ``X`` bf16 ``[T, S, W]``; ``out``
+    names three contiguous tensors of those shapes to write into."""
     T, S, W = X.shape
-    y = torch.empty(T, W, dtype=BF16, device=X.device)
-    post = torch.empty(T, S, dtype=torch.float32, device=X.device)
-    comb = torch.empty(T, S, S, dtype=torch.float32, device=X.device)
+    if out is not None:
+        y, post, comb = out
+        assert y.is_contiguous() and post.is_contiguous() and comb.is_contiguous() and X.is_contiguous()
+    else:
+        y = torch.empty(T, W, dtype=BF16, device=X.device)
+        post = torch.empty(T, S, dtype=torch.float32, device=X.device)
+        comb = torch.empty(T, S, S, dtype=torch.float32, device=X.device)
     check(_lib.load().ifab_mhc_pre(X.data_ptr(), phi.data_ptr(), gamma.data_ptr(), alpha.data_ptr(), beta.data_ptr(), y.data_ptr(),
                                    post.data_ptr(), comb.data_ptr(), T, S, W, sinkhorn, eps, _s()), "mhc_pre")
     return y, post, comb
 
 
-def mhc_post(X: torch.Tensor, branch: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
+def mhc_post(X: torch.Tensor, branch: torch.Tensor, post: torch.Tensor, comb: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     T, S, W = X.shape
-    Y = torch.empty(T, S, W, dtype=BF16, device=X.device)
+    Y = torch.empty(T, S, W, dtype=BF16, device=X.device) if out is None else out
+    assert Y.is_contiguous() and X.is_contiguous()
     check(_lib.load().ifab_mhc_post(X.data_ptr(), branch.data_ptr(), branch.stride(0), post.data_ptr(), comb.data_ptr(), Y.data_ptr(), T, S, W,
                                     _s()), "mhc_post")
     return Y

@@ -258,6 +258,10 @@ class PlanEngine:
         self.caches: List[torch.Tensor] = []              # the same tensors in program order (one per attention layer)
         self._kv_of: Dict[int, tuple] = {}                # K / V append instruction -> (key pages, value pages)
         self._kv_pack = None                              # [k | v] rows of a step, for an append outside the fused group
+        self._latent_pack = None                          # [latent | rope] rows of a step, when the two are not adjacent slices
+        self._conv_state: Dict[int, torch.Tensor] = {}    # token-convolution instruction -> the previous taps-1 rows per sequence slot
+        self._sink_rows: Dict[int, torch.Tensor] = {}     # sink_normalize instruction -> its rows [count, latent + rope]
+        self._sinks_of: Dict[int, torch.Tensor] = {}      # cache-write instruction -> the sink rows its readers also attend to
         self.arena = FrozenArena(b, self.rank, T, dev)
         self._alloc(dev)
         self.bundle_sha256 = json.loads((b / "plan.json").read_text()).get("program_sha256", "")
@@ -265,6 +269,9 @@ class PlanEngine:
         # 5.39 ms per step): the requests compete with the kernel's own loads. Off unless asked for; 2 = the output projection only.
         self.l2_prefetch = 0 if l2_prefetch is None else int(l2_prefetch)
         self._fused_gqa_option = fused_gqa
+        # debugging aid, the device-side counterpart of the interpreter's `watch`: called as probe(instruction, rows) right after
+        # each instruction was enqueued (its arena slot is still its own); not for use under graph capture
+        self.probe = None
         self._prepare(fused_head, fused_moe)
         self._graph = None
 
@@ -527,6 +534,31 @@ class PlanEngine:
             if op == "mla_kv_write":
                 self._cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
                 self.caches.append(self._cache_of[k])
+                if self._latent_pack is None or self._latent_pack.shape[1] < w:
+                    self._latent_pack = torch.empty(T, w, dtype=BF16, device=dev)
+            elif op in ("mhc_pre", "mhc_merge"):
+                S = int(i["attrs"]["streams"])
+                if S + S * S > 64:
+                    raise NotImplementedError("a hyper-connection slot holds at most 64 mixing weights per row")
+                raw = self.arena.lease(k, T * w * 2 + T * 64 * 4)          # mixed row | post weights | stream-to-stream weights
+                y = raw[:T * w * 2].view(BF16).view(T, w)
+                post = raw[T * w * 2:T * w * 2 + T * S * 4].view(f32).view(T, S)
+                comb = raw[T * w * 2 + T * S * 4:T * w * 2 + T * (S + S * S) * 4].view(f32).view(T, S, S)
+                self.vals[k] = (y, post, comb)
+            elif op == "mhc_input":
+                continue                                                   # the mixed row of its hyper-connection, no copy
+            elif op == "mome":
+                taps = int(i["attrs"]["taps"])
+                self._conv_state[k] = torch.zeros(self.num_slots, taps - 1, w, dtype=BF16, device=dev)
+                self.vals[k] = view(k, (T, w), BF16)
+            elif op == "sink_normalize":
+                # the sink rows depend on parameters only: normalised once, kept beside the cache they belong to
+                a = i["attrs"]
+                count, lat, rope = int(a["count"]), int(a["latent"]), int(a["rope"])
+                rows = torch.empty(count, lat + rope, dtype=BF16, device=dev)
+                K.rmsnorm(self._param(a["weight"] + ".param_sink_compressed_kv"), self._param(a["norm"]), float(a["eps"]), out=rows[:, :lat])
+                rows[:, lat:].copy_(self._param(a["weight"] + ".param_sink_k_pe"))
+                self._sink_rows[k] = rows
             elif op == "kv_cache_append":
                 if i["attrs"].get("cache_dtype", "bf16") != "bf16":
                     raise NotImplementedError("a compiled program's K / V pages are bf16")
@@ -600,8 +632,11 @@ class PlanEngine:
         head = (self.fused_head if self.fuse_override is None else (self.fuse_override and self.can_fuse_head)) and T <= self.fused_head_rows
         moe = self.fused_moe and T <= 2
         gqa = self.fused_gqa
+        probe = self.probe
         for k, i in enumerate(self.ins):
             op, a, ins = i["op"], i["attrs"], i["inputs"]
+            if probe is not None and k:
+                probe(k - 1, T)
             if (head and k in self._head_members) or (moe and k in self._moe_members) or (gqa and k in self._gqa_members):
                 if op in ("mla_kv_write", "kv_cache_append"):
                     V[k] = k                  # the cache of this write, for whoever reads it
@@ -670,8 +705,14 @@ class PlanEngine:
             elif op == "mla_kv_write":
                 lat, kr = val(ins[0]), val(ins[1])
                 if kr.data_ptr() != lat.data_ptr() + lat.shape[1] * 2 or kr.stride(0) != lat.stride(0):
-                    raise NotImplementedError("latent and rope columns must be adjacent slices of one projection")
-                kv = torch.as_strided(lat, (T, lat.shape[1] + kr.shape[1]), (lat.stride(0), 1))
+                    # e.g. a convolved latent beside the raw rope columns: bring the two side by side first
+                    kv = self._latent_pack[:T, :lat.shape[1] + kr.shape[1]]
+                    kv[:, :lat.shape[1]].copy_(lat)
+                    kv[:, lat.shape[1]:].copy_(kr)
+                else:
+                    kv = torch.as_strided(lat, (T, lat.shape[1] + kr.shape[1]), (lat.stride(0), 1))
+                if len(ins) > 2:
+                    self._sinks_of[k] = self._sink_rows[ins[2]]
                 K.mla_kv_write(kv, self._param(a["weight"]), pos, slot, self.page_table, self._cache_of[k], latent=lat.shape[1],
                                rope=kr.shape[1], eps=float(a["eps"]), theta=float(a["theta"]), status_ptr=st)
                 V[k] = k
@@ -695,6 +736,40 @@ class PlanEngine:
                                 ctx=self.max_context, topk=int(a["topk"]), status_ptr=st, scores=self._index_scores[:T], out=val(k))
             elif op == "add":
                 HC.add_rows(val(ins[0]), val(ins[1]), out=val(k))
+            elif op == "repeat":
+                n = int(a["count"])
+                x = val(ins[0])
+                val(k).view(T, n, x.shape[1]).copy_(x.unsqueeze(1).expand(T, n, x.shape[1]))
+            elif op == "cast":
+                val(k).copy_(val(ins[0]))
+            elif op == "optional_norm":
+                w = self._param(a["weight"], True)
+                if w is None:
+                    val(k).copy_(val(ins[0]))      # the checkpoint has no such gain: the rows pass through (into this instruction's
+                                                   # own slot - the source's slot is free for reuse after this instruction)
+                else:
+                    K.rmsnorm(val(ins[0]), w, float(a["eps"]), out=val(k))
+            elif op in ("mhc_pre", "mhc_merge"):
+                S = int(a["streams"])
+                y, post, comb = V[k]
+                X = val(ins[0])
+                b = a["weight"]
+                HC.mhc_pre(X.view(T, S, X.shape[1] // S), self._param(b + ".phi"), self._param(b + ".gamma"), self._param(b + ".alpha"),
+                           self._param(b + ".beta"), sinkhorn=int(a["sinkhorn"]), eps=float(a["eps"]), out=(y[:T], post[:T], comb[:T]))
+            elif op == "mhc_input":
+                V[k] = V[ins[0]][0]
+            elif op == "mhc_post":
+                _, post, comb = V[ins[0]]
+                S = post.shape[1]
+                X, Y = val(ins[2]), val(k)
+                HC.mhc_post(X.view(T, S, X.shape[1] // S), val(ins[1]), post[:T], comb[:T], out=Y.view(T, S, Y.shape[1] // S))
+            elif op == "mome":
+                w = self._param(a["weight"])
+                x = val(ins[0])
+                HC.mome(x, w, self._conv_state[k], pos, slot, c_offset=self.rank * x.shape[1] if a.get("placement") == "tp_channels" else 0,
+                        out=val(k))
+            elif op == "sink_normalize":
+                V[k] = self._sink_rows[k]
             elif op == "mla_attention":
                 H, latent, vdim = int(a["heads"]), int(a["latent"]), int(a["value"])
                 nope = int(a.get("nope", vdim))
@@ -703,7 +778,8 @@ class PlanEngine:
                 K.mla_decode_attention(val(ins[0]), cache, pos, slot, self.page_table, w, nope=nope,
                                        scale=1.0 / math.sqrt(float(a["scale_dim"])), window=int(a["window"]),
                                        keys_per_split=self.kps, max_splits=self.max_splits, scratch=self.scratch,
-                                       out=val(k), status_ptr=st, indices=val(ins[2]) if len(ins) > 2 else None)
+                                       out=val(k), status_ptr=st, indices=val(ins[2]) if len(ins) > 2 else None,
+                                       sinks=self._sinks_of.get(V[ins[1]]))
             elif op == "router_topk":
                 ids, wts, logits = V[k]
                 # when the expert kernels read the same rows under the same norm, the router leaves the normalised rows in the
@@ -735,6 +811,8 @@ class PlanEngine:
                                  out_ids=self.next_ids[:T], out_vals=self.next_vals[:T])
             else:
                 raise NotImplementedError(f"no device kernel bound for instruction '{op}' ({i['name']})")
+        if probe is not None:
+            probe(len(self.ins) - 1, T)
         return self.next_ids[:T]
 
     def capture(self, T: Optional[int] = None, feedback: bool = False) -> torch.cuda.CUDAGraph:
@@ -753,5 +831,5 @@ class PlanEngine:
         return g
 
     def reset(self) -> None:
-        for c in list(self.caches) + list(self._index_cache_of.values()) + [t for kv in self._kv_of.values() for t in kv]:
+        for c in list(self.caches) + list(self._index_cache_of.values()) + [t for kv in self._kv_of.values() for t in kv] + list(self._conv_state.values()):
             c.zero_()

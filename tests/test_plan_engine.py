@@ -193,3 +193,54 @@ def test_sparse_indexer_program_on_the_device_matches_the_interpreter(tmp_path, 
         torch.testing.assert_close(eng.logits[:n].cpu(), ref[s:s + n], rtol=3e-2, atol=3e-2)
     assert fab.status() == 0
     fab.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("width", [8, 1, 3])
+def test_hyper_connected_program_on_the_device_matches_the_interpreter(tmp_path, width):
+    """Residual streams mixed by mHC modules, token convolutions with per-sequence history on the low-rank query, the latent and
+    the attention value, attention sinks, stand-alone post-norms, an optional norm the checkpoint lacks: the plan engine binds
+    repeat, mhc_pre / mhc_input / mhc_post / mhc_merge, mome, sink_normalize and the cache write with sink rows; logits agree
+    with the CPU oracle at every step width, and a second sequence slot does not disturb the first."""
+    from hyper_source import source
+
+    from ironpangu_b200 import compiler
+    from ironpangu_b200.parallel.fabric import Fabric
+    from ironpangu_b200.runtime.plan_engine import PlanEngine
+
+    src, ck, bundle = tmp_path / "m.inferfabric", tmp_path / "ck", tmp_path / "b"
+    src.write_text(source(layers=2))
+    assert compiler.cli("synth-checkpoint", str(src), str(ck), "--seed", "7").returncode == 0
+    compiler.write_bundle(str(src), str(bundle), checkpoint_dir=str(ck), prefill_tokens=8, resident_sequences=2)
+    toks = torch.randint(1, 512, (21,), generator=torch.Generator().manual_seed(4)).tolist()
+    other = torch.randint(1, 512, (9,), generator=torch.Generator().manual_seed(5)).tolist()
+    ref = torch.tensor(compiler.interpret(src.read_text(), str(ck), toks, all_logits=True)["prompt_logits"])
+    ref_other = torch.tensor(compiler.interpret(src.read_text(), str(ck), other, all_logits=True)["prompt_logits"])
+    fab = Fabric(0, 1)
+    eng = PlanEngine(str(bundle), str(ck), fab, max_tokens=8, num_slots=2, keep_logits=True)
+    ops = {i["op"] for i in eng.ins}
+    assert {"repeat", "mhc_pre", "mhc_input", "mhc_post", "mhc_merge", "mome", "sink_normalize", "optional_norm"} <= ops
+
+    def run(seq, slot, want, step):
+        for s in range(0, len(seq), step):
+            n = min(step, len(seq) - s)
+            eng.tokens[:n].copy_(torch.tensor(seq[s:s + n], dtype=torch.int32))
+            eng.positions[:n].copy_(torch.arange(s, s + n, dtype=torch.int32))
+            eng.slots[:n].fill_(slot)
+            eng.forward(n)
+            torch.testing.assert_close(eng.logits[:n].cpu(), want[s:s + n], rtol=3e-2, atol=3e-2)
+
+    run(toks[:10], 0, ref, width)
+    run(other, 1, ref_other, 8)              # another sequence in between: its convolution history and pages are its own
+    # continue the first sequence where it stopped
+    for s in range(10, len(toks), width):
+        n = min(width, len(toks) - s)
+        eng.tokens[:n].copy_(torch.tensor(toks[s:s + n], dtype=torch.int32))
+        eng.positions[:n].copy_(torch.arange(s, s + n, dtype=torch.int32))
+        eng.slots[:n].zero_()
+        eng.forward(n)
+        torch.testing.assert_close(eng.logits[:n].cpu(), ref[s:s + n], rtol=3e-2, atol=3e-2)
+    assert fab.status() == 0
+    eng.reset()
+    run(toks[:8], 0, ref, 8)                 # after a reset the histories are empty again
+    fab.close()
