@@ -6,6 +6,8 @@ flagship configuration at tp = 8, kept as a file.
 Reference: examples/openpangu/92b-tp8-ep8.inferfabric (the same structure in the reference's vocabulary)."""
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 
 def _num(x: float) -> str:
     return repr(int(x)) if float(x) == int(x) else repr(float(x))
@@ -154,6 +156,150 @@ model {name} {{
 }}
 
 plan TP{tp} for {name} {{
+    target = b200_token_v1;
+    tp = {tp};
+    ep = {tp};
+    devices = [{devices}];
+    max_num_seqs = 1;
+    max_num_batched_tokens = 1;
+    max_model_len = {context};
+}}
+"""
+
+
+@dataclass
+class HyperMlaMoeConfig:
+    """A latent-attention + routed-experts decoder whose residual is ``streams`` parallel streams mixed by hyper-connection
+    modules, with causal token convolutions (``taps`` wide) on the low-rank query, the latent and the attention value,
+    ``sinks`` learned sink rows per attention layer, norms before and after every branch, ``first_dense`` leading layers with
+    a dense FFN, and a long window on every ``long_every``-th layer."""
+    layers: int = 46
+    hidden: int = 2560
+    vocab: int = 151552
+    heads: int = 48
+    q_lora: int = 1024
+    kv_lora: int = 512
+    nope: int = 128
+    rope: int = 64
+    vdim: int = 128
+    experts: int = 256
+    topk: int = 8
+    expert_ffn: int = 1024
+    shared_ffn: int = 1024
+    dense_ffn: int = 9216
+    first_dense: int = 2
+    streams: int = 4
+    sinkhorn: int = 20
+    taps: int = 3
+    sinks: int = 128
+    long_every: int = 3
+    long_window: int = 2048
+    short_window: int = 512
+    theta: float = 6.4e6
+    eps: float = 1e-5
+    route_scale: float = 2.5
+    scoring: str = "sigmoid_bias_group_topk"
+    eos: int = 2
+
+    @staticmethod
+    def pangu92b() -> "HyperMlaMoeConfig":
+        """The published 92B configuration of this family (46 layers, 256 experts of 1024, 48 heads, 4 streams, 128 sinks)."""
+        return HyperMlaMoeConfig()
+
+    @staticmethod
+    def tiny(layers: int = 3) -> "HyperMlaMoeConfig":
+        return HyperMlaMoeConfig(layers=layers, hidden=256, vocab=512, heads=4, q_lora=384, experts=8, topk=2, expert_ffn=128, shared_ffn=128,
+                                 dense_ffn=512, first_dense=1, sinks=5, long_window=64, short_window=16, theta=1e4)
+
+    @property
+    def qk_dim(self) -> int:
+        return self.nope + self.rope
+
+
+def hyper_mla_moe_source(cfg: HyperMlaMoeConfig, tp: int, context: int = 512, name: str = "HyperMlaMoe") -> str:
+    """DSL source of ``cfg`` at tensor / expert parallel width ``tp``. Dense and shared-expert projections are sharded over the
+    ranks and packed (gate | up) so that the lowering fuses them with their activation and their all-reduce."""
+    c = cfg
+    if c.heads % tp or c.experts % tp or c.vocab % tp or c.shared_ffn % tp or c.dense_ffn % tp:
+        raise ValueError(f"tp={tp} does not divide heads / experts / vocab / FFN widths of the model")
+    qw, lat, theta, eps = c.q_lora, c.kv_lora, _num(c.theta), repr(c.eps)
+    H, S = c.hidden, c.streams
+    mhc = f"streams = {S}, sinkhorn = {c.sinkhorn}, eps = 1e-6"
+    devices = ", ".join(str(i) for i in range(tp))
+    return f"""language inferfabric 1;
+
+// {c.layers} layers ({c.first_dense} with a dense FFN), hidden {H} x {S} residual streams, vocab {c.vocab};
+// MLA: {c.heads} heads, q_lora {qw}, kv_lora {lat}, nope {c.nope}, rope {c.rope}, v {c.vdim}, {c.sinks} sink rows, token convolutions of {c.taps} taps;
+// MoE: {c.experts} routed experts (FFN {c.expert_ffn}), top-{c.topk} {c.scoring}, shared expert (FFN {c.shared_ffn}); tp = ep = {tp}.
+
+module Attention(x, w, window) {{
+    let qkv = linear(x, weight = w.q_a_proj, paired_weight = w.kv_a_proj_with_mqa, width = {qw}, paired_width = {lat + c.rope}, placement = "replicated");
+    let qc = mome(slice(qkv, start = 0, width = {qw}), weight = w.qa_conv, taps = {c.taps});
+    let q = linear(norm(qc, weight = w.q_a_layernorm, eps = {eps}), weight = w.q_b_proj, width = div({c.heads * c.qk_dim}, {tp}), placement = "tp_rows");
+    let kc = mome(slice(qkv, start = {qw}, width = {lat}), weight = w.compresskv_conv, taps = {c.taps});
+    let kr = slice(qkv, start = {qw + lat}, width = {c.rope});
+    let sinks = sink_normalize(weight = w, norm = w.kv_a_layernorm, count = {c.sinks}, latent = {lat}, rope = {c.rope}, eps = {eps});
+    let cache = cache_norm_rope_append(kc, kr, sinks, weight = w.kv_a_layernorm, eps = {eps}, theta = {theta});
+    let query = mla_query(q, weight = w.kv_b_proj, theta = {theta}, heads = {c.heads}, nope = {c.nope}, rope = {c.rope}, latent = {lat},
+                          value = {c.vdim}, input_layout = "rank_local");
+    let attended = latent_attention(query, cache, scale_dim = {c.qk_dim}, window = window, selection = "all_causal_within_window");
+    let value = mla_value(attended, weight = w.kv_b_proj, heads = {c.heads}, latent = {lat}, value = {c.vdim}, nope = {c.nope});
+    let oc = mome(value, weight = w.o_conv, taps = {c.taps}, placement = "tp_channels");
+    let output = allreduce(linear(oc, weight = w.o_proj, width = {H}, placement = "tp_columns"));
+    yield output;
+}}
+
+module DenseFFN(x, w) {{
+    let act = swiglu(linear(x, weight = w.gate_proj, paired_weight = w.up_proj, width = div({c.dense_ffn}, {tp}),
+                            paired_width = div({c.dense_ffn}, {tp}), placement = "tp_rows"));
+    let output = allreduce(linear(act, weight = w.down_proj, width = {H}, placement = "tp_columns"));
+    yield output;
+}}
+
+module RoutedMoE(x, w) {{
+    let routes = router(x, weight = w.gate, experts = {c.experts}, topk = {c.topk}, scoring = "{c.scoring}", scale = {repr(float(c.route_scale))});
+    let expert = child(w.experts, "{{expert}}");
+    let gate_up = expert_linear(x, routes, weight = expert.gate_proj, paired_weight = expert.up_proj, width = {c.expert_ffn});
+    let down = expert_swiglu_down(gate_up, routes, weight = expert.down_proj, width = {H});
+    let local = expert_reduce(down, routes);
+    let shared_act = swiglu(linear(x, weight = w.shared_experts.gate_proj, paired_weight = w.shared_experts.up_proj,
+                                   width = div({c.shared_ffn}, {tp}), paired_width = div({c.shared_ffn}, {tp}), placement = "tp_rows"));
+    let shared_partial = linear(shared_act, weight = w.shared_experts.down_proj, width = {H}, placement = "tp_columns");
+    let output = allreduce(add(local, shared_partial));
+    yield output;
+}}
+
+module Block(x, w, index, window) {{
+    let attn_hc = mhc_pre(x, weight = w.attn_mhc_module, {mhc});
+    let attention = Attention(norm(mhc_input(attn_hc), weight = w.input_layernorm, eps = {eps}), w.self_attn, window);
+    let residual = mhc_post(attn_hc, norm(attention, weight = w.post_attention_layernorm, eps = {eps}));
+    let ffn_hc = mhc_pre(residual, weight = w.mlp_mhc_module, {mhc});
+    let ffn_in = norm(mhc_input(ffn_hc), weight = w.pre_mlp_layernorm, eps = {eps});
+    let ffn = choose(lt(index, {c.first_dense}), DenseFFN(ffn_in, w.mlp), RoutedMoE(ffn_in, w.mlp));
+    let mixed = mhc_post(ffn_hc, norm(ffn, weight = w.post_mlp_layernorm, eps = {eps}));
+    let output = optional_norm(mixed, weight = w.block_post_layernorm, eps = {eps});
+    yield output;
+}}
+
+model {name} {{
+    context = {context};
+    eos = {c.eos};
+    let w = weights("model");
+    let embedded = embedding(weight = w.embed_tokens, width = {H}, vocab = {c.vocab});
+
+    let hidden = fold i in range(0, {c.layers}) carry(x = repeat(embedded, count = {S})) {{
+        let window = choose(eq(mod(i, {c.long_every}), 0), {c.long_window}, {c.short_window});
+        let block = Block(x, child(w.layers, i), i, window);
+        yield block;
+    }};
+
+    let merged = mhc_input(mhc_merge(hidden, weight = w.merge_mhc_module, {mhc}));
+    let local_logits = linear(norm(merged, weight = w.norm, eps = {eps}), weight = weights("lm_head"), width = div({c.vocab}, {tp}), placement = "tp_rows");
+    let logits = gather(local_logits);
+    yield logits;
+}}
+
+plan TP{tp}EP{tp} for {name} {{
     target = b200_token_v1;
     tp = {tp};
     ep = {tp};

@@ -59,70 +59,91 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return s;
 }
 
-// one CTA per token. X [T, S, W] bf16; phi [S*S+2S, S*W] f32; gamma [S*W] f32; alpha [3]; beta [S*S+2S].
-// out: y [T, W] bf16, post [T, S] f32, comb [T, S, S] f32.  S <= 8.
-__global__ void __launch_bounds__(256) mhc_pre_kernel(const bf16* X, const float* phi, const float* gamma, const float* alpha, const float* beta,
-                                                      bf16* y, float* post, float* comb, int S, int W, int iters, float eps) {
+// The pre step runs as two launches. The mixing logits are S*S + 2S dot products over all S*W elements of the token's streams
+// (1 MB of phi per token at S = 4, W = 2560): one CTA per (logit, token) streams its row of phi, so the read is spread over
+// S*S + 2S + 1 SMs instead of one. The tail - gates, Sinkhorn, branch input - is one CTA per token.
+//
+// mhc_logits_kernel: grid (M + 1, T), M = S*S + 2S. CTA j < M: raw[t][j] = sum_c phi[j][c] * gamma[c] * X[t][c]; CTA M: the sum of
+// squares. The M + 1 floats land in the first bytes of the token's row of y (the tail kernel reads them before it writes y).
+__global__ void __launch_bounds__(256) mhc_logits_kernel(const bf16* X, const float* phi, const float* gamma, float* raw, long raw_stride, int S, int W) {
   __shared__ float red[8];
-  __shared__ float m[8 * 8 + 16];
+  grid_dep_launch();
+  grid_dep_wait();
+  const int j = blockIdx.x, t = blockIdx.y, M = S * S + 2 * S;
+  const long total = (long)S * W;
+  const bf16* Xt = X + (long)t * total;
+  float s = 0.f;
+  if (j == M) {
+    for (long c = threadIdx.x; c < total; c += blockDim.x) {
+      const float v = __bfloat162float(Xt[c]);
+      s += v * v;
+    }
+  } else {
+    const float* pj = phi + (long)j * total;
+    if ((total & 3) == 0) {
+      const float4* p4 = reinterpret_cast<const float4*>(pj);
+      const float4* g4 = reinterpret_cast<const float4*>(gamma);
+      const uint2* x4 = reinterpret_cast<const uint2*>(Xt);
+      for (long c = threadIdx.x; c < total / 4; c += blockDim.x) {
+        const float4 a = p4[c], g = g4[c];
+        const uint2 xr = x4[c];
+        const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xr.x));
+        const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xr.y));
+        s += a.x * g.x * x01.x + a.y * g.y * x01.y + a.z * g.z * x23.x + a.w * g.w * x23.y;
+      }
+    } else {
+      for (long c = threadIdx.x; c < total; c += blockDim.x) s += pj[c] * gamma[c] * __bfloat162float(Xt[c]);
+    }
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) raw[(long)t * raw_stride + j] = s;
+}
+
+// mhc_mix_kernel: one CTA per token. Reads the M + 1 raw sums, then: sigmoid gates (pre, post), the S x S logits through a row
+// softmax and `iters` rounds of Sinkhorn normalisation (one thread per matrix entry, two buffers, one barrier per pass), and the
+// branch input y = sum_s pre_s * X_s. S <= 8.
+__global__ void __launch_bounds__(256) mhc_mix_kernel(const bf16* X, const float* raw, long raw_stride, const float* alpha, const float* beta, bf16* y,
+                                                      float* post, float* comb, int S, int W, int iters, float eps) {
+  __shared__ float m[8 * 8 + 16 + 1];
+  __shared__ float R[2][64];
   __shared__ float pre_s[8];
   grid_dep_launch();
   grid_dep_wait();
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, M = S * S + 2 * S, n = S * S, tid = threadIdx.x;
   const long total = (long)S * W;
   const bf16* Xt = X + (long)t * total;
-  float ss = 0.f;
-  for (long c = threadIdx.x; c < total; c += blockDim.x) {
-    const float v = __bfloat162float(Xt[c]);
-    ss += v * v;
-  }
-  ss = block_sum(ss, red);
-  const float inv = 1.f / sqrtf(ss / (float)total + eps);
-  const int M = S * S + 2 * S;
-  for (int j = 0; j < M; ++j) {
-    float s = 0.f;
-    const float* pj = phi + (long)j * total;
-    for (long c = threadIdx.x; c < total; c += blockDim.x) s += pj[c] * gamma[c] * __bfloat162float(Xt[c]);
-    s = block_sum(s, red);
-    if (threadIdx.x == 0) m[j] = inv * s;
-  }
+  if (tid <= M) m[tid] = raw[(long)t * raw_stride + tid];
+  __syncthreads();                                   // every raw sum is in shared memory before y (which held them) is written
+  const float inv = 1.f / sqrtf(m[M] / (float)total + eps);
+  if (tid < S) pre_s[tid] = 1.f / (1.f + expf(-(inv * m[tid] * alpha[0] + beta[tid]))) + 1e-6f;
+  else if (tid < 2 * S) post[(long)t * S + (tid - S)] = 2.f / (1.f + expf(-(inv * m[tid] * alpha[1] + beta[tid])));
+  const int a = tid / S, b = tid % S;
+  if (tid < n) R[0][tid] = inv * m[2 * S + tid] * alpha[2] + beta[2 * S + tid];
   __syncthreads();
-  if (threadIdx.x == 0) {
-    float R[64];
-    for (int j = 0; j < S; ++j) pre_s[j] = 1.f / (1.f + expf(-(m[j] * alpha[0] + beta[j]))) + 1e-6f;
-    for (int j = 0; j < S; ++j) post[(long)t * S + j] = 2.f / (1.f + expf(-(m[S + j] * alpha[1] + beta[S + j])));
-    for (int j = 0; j < S * S; ++j) R[j] = m[2 * S + j] * alpha[2] + beta[2 * S + j];
-    for (int a = 0; a < S; ++a) {
-      float mx = -INFINITY, sum = 0.f;
-      for (int b = 0; b < S; ++b) mx = fmaxf(mx, R[a * S + b]);
-      for (int b = 0; b < S; ++b) sum += (R[a * S + b] = expf(R[a * S + b] - mx));
-      for (int b = 0; b < S; ++b) R[a * S + b] = R[a * S + b] / sum + 1e-6f;
-    }
-    auto col_norm = [&] {
-      for (int b = 0; b < S; ++b) {
-        float sum = 0.f;
-        for (int a = 0; a < S; ++a) sum += R[a * S + b];
-        for (int a = 0; a < S; ++a) R[a * S + b] /= (sum + 1e-6f);
-      }
-    };
-    auto row_norm = [&] {
-      for (int a = 0; a < S; ++a) {
-        float sum = 0.f;
-        for (int b = 0; b < S; ++b) sum += R[a * S + b];
-        for (int b = 0; b < S; ++b) R[a * S + b] /= (sum + 1e-6f);
-      }
-    };
-    col_norm();
-    for (int it = 1; it < iters; ++it) {
-      row_norm();
-      col_norm();
-    }
-    for (int j = 0; j < S * S; ++j) comb[(long)t * S * S + j] = R[j];
+  int cur = 0;
+  if (tid < n) {                                     // row softmax
+    float mx = -INFINITY, sum = 0.f;
+    for (int k = 0; k < S; ++k) mx = fmaxf(mx, R[0][a * S + k]);
+    for (int k = 0; k < S; ++k) sum += expf(R[0][a * S + k] - mx);
+    R[1][tid] = expf(R[0][tid] - mx) / sum + 1e-6f;
   }
+  cur = 1;
   __syncthreads();
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+  // column pass, then (iters - 1) x (row pass, column pass)
+  for (int pass = 0; pass < 2 * iters - 1; ++pass) {
+    const bool column = (pass & 1) == 0;
+    if (tid < n) {
+      float sum = 0.f;
+      for (int k = 0; k < S; ++k) sum += column ? R[cur][k * S + b] : R[cur][a * S + k];
+      R[cur ^ 1][tid] = R[cur][tid] / (sum + 1e-6f);
+    }
+    cur ^= 1;
+    __syncthreads();
+  }
+  if (tid < n) comb[(long)t * n + tid] = R[cur][tid];
+  for (int c = tid; c < W; c += blockDim.x) {
     float v = 0.f;
-    for (int s = 0; s < S; ++s) v += pre_s[s] * __bfloat162float(Xt[(long)s * W + c]);
+    for (int k = 0; k < S; ++k) v += pre_s[k] * __bfloat162float(Xt[(long)k * W + c]);
     y[(long)t * W + c] = __float2bfloat16_rn(v);
   }
 }
@@ -289,9 +310,13 @@ extern "C" int ifab_mome(const void* x, long ldx, const float* w, void* state, c
 
 extern "C" int ifab_mhc_pre(const void* X, const float* phi, const float* gamma, const float* alpha, const float* beta, void* y, float* post,
                             float* comb, int T, int S, int W, int sinkhorn_iters, float eps, void* stream) {
-  if (T < 1 || S < 1 || S > 8 || W < 1 || sinkhorn_iters < 1) return -1;
-  return launch_chain(mhc_pre_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)X, phi, gamma, alpha, beta, (bf16*)y, post, comb,
-                      S, W, sinkhorn_iters, eps);
+  const int M = S * S + 2 * S;
+  // the raw sums of a token travel in the first (M + 1) floats of its row of y
+  if (T < 1 || S < 1 || S > 8 || W < 1 || sinkhorn_iters < 1 || (W & 1) || (long)W * 2 < (long)(M + 1) * 4) return -1;
+  if (int rc = launch_chain(mhc_logits_kernel, dim3(M + 1, T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)X, phi, gamma, (float*)y, (long)(W / 2), S, W))
+    return rc;
+  return launch_chain(mhc_mix_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)X, (const float*)y, (long)(W / 2), alpha, beta, (bf16*)y,
+                      post, comb, S, W, sinkhorn_iters, eps);
 }
 
 extern "C" int ifab_mhc_post(const void* X, const void* branch, long ldb, const float* post, const float* comb, void* Y, int T, int S, int W,

@@ -225,7 +225,24 @@ __global__ void __launch_bounds__(256) add_rows_kernel(const bf16* a, long lda, 
   y[(long)r * ldy + c] = __float2bfloat16_rn(__bfloat162float(a[(long)r * lda + c]) + __bfloat162float(b[(long)r * ldb + c]));
 }
 
+// y = silu(gate) * up, bf16 rows (gate and up may be column ranges of one projection or two projections)
+__global__ void __launch_bounds__(256) swiglu_pair_kernel(const bf16* g, long ldg, const bf16* u, long ldu, bf16* y, long ldy, int rows, int n) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long)rows * n) return;
+  const int r = (int)(i / n), c = (int)(i % n);
+  const float a = __bfloat162float(g[(long)r * ldg + c]);
+  y[(long)r * ldy + c] = __float2bfloat16_rn(a / (1.f + __expf(-a)) * __bfloat162float(u[(long)r * ldu + c]));
+}
+
 }  // namespace
+
+extern "C" int ifab_swiglu_pair(const void* gate, long ldg, const void* up, long ldu, void* y, long ldy, int rows, int n, void* stream) {
+  if (rows < 1 || n < 1) return -1;
+  return launch_chain(swiglu_pair_kernel, dim3((unsigned)(((long)rows * n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, (const bf16*)gate, ldg,
+                      (const bf16*)up, ldu, (bf16*)y, ldy, rows, n);
+}
 
 extern "C" int ifab_rope_prefix(const void* x, long ldx, const int32_t* positions, void* y, long ldy, int T, int heads, int head_dim, int rotary_dim,
                                 float theta, void* stream) {

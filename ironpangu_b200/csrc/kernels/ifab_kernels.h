@@ -203,6 +203,8 @@ int ifab_rope_prefix(const void* x, long ldx, const int32_t* positions, void* y,
                      float theta, void* stream);
 /* y = a + b over [rows, n] bf16 (f32 sum, one rounding). */
 int ifab_add_rows(const void* a, long lda, const void* b, long ldb, void* y, long ldy, int rows, int n, void* stream);
+/* y = silu(gate) * up over [rows, n] bf16. */
+int ifab_swiglu_pair(const void* gate, long ldg, const void* up, long ldu, void* y, long ldy, int rows, int n, void* stream);
 
 /* ---- hyper-connection / hybrid-model operators (hc_ops.cu); all mixing arithmetic in f32 ---- */
 /* causal depthwise conv with residual; w f32 [C_total, taps] (this rank's channels start at c_offset); state bf16 [slots, taps-1, C] */

@@ -90,6 +90,7 @@ _SIGS = {
     "ifab_rope_prefix": [_P, c_long, _P, _P, c_long, c_int, c_int, c_int, c_int, c_float, _P],
     "ifab_index_cache_append": [_P, c_long, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, _P, _P],
     "ifab_add_rows": [_P, c_long, _P, c_long, _P, c_long, c_int, c_int, _P],
+    "ifab_swiglu_pair": [_P, c_long, _P, c_long, _P, c_long, c_int, c_int, _P],
     "ifab_zc_rmsnorm": [_P, c_long, _P, c_float, _P, c_long, c_int, c_int, c_int, _P],
     "ifab_hybrid_qk_prepare": [_P, c_long, _P, c_long, _P, _P, c_float, _P, c_long, _P, c_long, c_int, c_int, c_int, c_int, _P],
     "ifab_sigmoid_mul": [_P, c_long, _P, c_long, _P, c_long, c_int, c_int, _P],

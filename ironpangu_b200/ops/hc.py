@@ -105,3 +105,12 @@ def add_rows(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = Non
     out = torch.empty(rows, n, dtype=BF16, device=a.device) if out is None else out
     check(_lib.load().ifab_add_rows(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0), rows, n, _s()), "add_rows")
     return out
+
+
+def swiglu_pair(gate: torch.Tensor, up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gate) * up`` for two bf16 ``[rows, n]`` projections (row-strided views are fine)."""
+    rows, n = gate.shape
+    out = torch.empty(rows, n, dtype=BF16, device=gate.device) if out is None else out
+    check(_lib.load().ifab_swiglu_pair(gate.data_ptr(), gate.stride(0), up.data_ptr(), up.stride(0), out.data_ptr(), out.stride(0), rows, n, _s()),
+          "swiglu_pair")
+    return out

@@ -134,6 +134,36 @@ def load_parameters(init_plan: dict, ckpt: SafetensorsDir, device, *, staging_by
     return params
 
 
+def random_parameters(init_plan: dict, device, seed: int = 0, std: float = 0.02) -> Dict[str, torch.Tensor]:
+    """Random-init tensors for every parameter of one rank's initialization plan, without a checkpoint: each load slice is
+    drawn from a generator keyed by (checkpoint tensor name, byte offset, seed), so a replicated tensor is identical on every
+    rank and the shards of a split tensor differ. N(0, ``std``); tensors whose name says they are a norm gain get 1 + N(0, ``std``).
+    For benchmarks and tests of programs whose checkpoint is too large to write (a bundle compiled without a checkpoint
+    records the same loads against a synthetic layout)."""
+    meta = {p["id"]: p for p in init_plan["parameters"]}
+    raw, cursors = {}, {}
+    for p in init_plan["parameters"]:
+        dt, _ = _DT[p["dtype"]]
+        raw[p["id"]] = torch.empty(int(np.prod(p["dims"])), dtype=dt, device=device)
+        cursors[p["id"]] = 0
+    gen = torch.Generator(device=device)
+    for l in init_plan["loads"]:
+        n = l["bytes"] // _DT[l["src_dtype"]][1]
+        gen.manual_seed(_fnv1a64(f"{l.get('tensor', l['shard'])}@{l['offset']}#{seed}".encode()) & 0x7FFFFFFFFFFFFFFF)
+        piece = torch.empty(n, dtype=torch.float32, device=device).normal_(0.0, std, generator=gen)
+        if "norm" in l.get("tensor", ""):
+            piece += 1.0
+        c = cursors[l["dest"]]
+        raw[l["dest"]][c:c + n].copy_(piece)
+        cursors[l["dest"]] = c + n
+    out = {}
+    for pid, p in meta.items():
+        if cursors[pid] != raw[pid].numel():
+            raise ValueError(f"parameter {p['name']} was filled with {cursors[pid]} of {raw[pid].numel()} elements")
+        out[p["name"]] = raw[pid].view(*p["dims"])
+    return out
+
+
 def _fnv1a64(data: bytes) -> int:
     h = 0xcbf29ce484222325
     for b in data:
@@ -736,6 +766,12 @@ class PlanEngine:
                                 ctx=self.max_context, topk=int(a["topk"]), status_ptr=st, scores=self._index_scores[:T], out=val(k))
             elif op == "add":
                 HC.add_rows(val(ins[0]), val(ins[1]), out=val(k))
+            elif op == "swiglu":
+                if len(ins) == 2:
+                    HC.swiglu_pair(val(ins[0]), val(ins[1]), out=val(k))
+                else:
+                    gu = val(ins[0])
+                    HC.swiglu_pair(gu[:, :gu.shape[1] // 2], gu[:, gu.shape[1] // 2:], out=val(k))
             elif op == "repeat":
                 n = int(a["count"])
                 x = val(ins[0])

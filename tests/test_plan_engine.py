@@ -244,3 +244,44 @@ def test_hyper_connected_program_on_the_device_matches_the_interpreter(tmp_path,
     eng.reset()
     run(toks[:8], 0, ref, 8)                 # after a reset the histories are empty again
     fab.close()
+
+
+@pytest.mark.gpu
+def test_generated_hyper_mla_moe_program_matches_the_interpreter(tmp_path):
+    """The family generator (dense first layer, routed experts with sigmoid scoring and a sharded shared expert, windows that
+    alternate by layer, sinks, convolutions, hyper-connections) at its tiny size: device logits equal the CPU oracle's."""
+    from ironpangu_b200 import compiler
+    from ironpangu_b200.compiler.sources import HyperMlaMoeConfig, hyper_mla_moe_source
+    from ironpangu_b200.parallel.fabric import Fabric
+    from ironpangu_b200.runtime.plan_engine import PlanEngine
+
+    src, ck, bundle = tmp_path / "m.inferfabric", tmp_path / "ck", tmp_path / "b"
+    src.write_text(hyper_mla_moe_source(HyperMlaMoeConfig.tiny(3), 1, context=128))
+    assert compiler.cli("synth-checkpoint", str(src), str(ck), "--seed", "11").returncode == 0
+    compiler.write_bundle(str(src), str(bundle), checkpoint_dir=str(ck), prefill_tokens=8)
+    toks = torch.randint(1, 512, (37,), generator=torch.Generator().manual_seed(6)).tolist()     # longer than the short window (16)
+    fab = Fabric(0, 1)
+    eng = PlanEngine(str(bundle), str(ck), fab, max_tokens=8, keep_logits=True)
+    routers = [k for k, i in enumerate(eng.ins) if i["op"] == "router_topk"]
+    assert len(routers) == 2
+    oracle = compiler.interpret(src.read_text(), str(ck), toks, all_logits=True, watch=[eng.ins[k]["name"] for k in routers])
+    ref = torch.tensor(oracle["prompt_logits"])
+    picked = {}
+    eng.probe = lambda k, T: picked.__setitem__(k, eng.vals[k][0][:T].tolist()) if k in routers else None
+    same_routes = 0
+    for s in range(0, len(toks), 8):
+        n = min(8, len(toks) - s)
+        eng.tokens[:n].copy_(torch.tensor(toks[s:s + n], dtype=torch.int32))
+        eng.positions[:n].copy_(torch.arange(s, s + n, dtype=torch.int32))
+        eng.slots[:n].zero_()
+        eng.forward(n)
+        torch.cuda.synchronize()
+        for i in range(n):
+            # two experts whose scores are a bf16 rounding apart may swap; such a row is compared on its routes only
+            agree = all(sorted(picked[k][i]) == sorted(oracle["watched"][s + i][eng.ins[k]["name"]]["ids"]) for k in routers)
+            same_routes += agree
+            if agree:
+                torch.testing.assert_close(eng.logits[i].cpu(), ref[s + i], rtol=4e-2, atol=4e-2)
+    assert same_routes >= len(toks) * 0.8, same_routes
+    assert fab.status() == 0
+    fab.close()
