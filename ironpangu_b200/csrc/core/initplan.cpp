@@ -401,6 +401,8 @@ std::vector<ParamSpec> specs_of(const Program& p) {
       s.name = *i.attr("weight");
       s.parts.push_back({s.name + ".weight", {in_width(i, 0)}, Need::Full, DType::Bf16});
       out.push_back(s);
+    } else if (op == "mhc_post") {
+      norm_spec(i, in_width(i, 1));          // the branch norm folded into the mixing kernel, when there is one
     } else if (op == "mhc_pre" || op == "mhc_merge") {
       // the mixing module of a hyper-connection: four f32 tensors under the module's scope (no ".weight" suffix)
       const uint64_t S = attr_u(i, "streams"), total = in_width(i), M = S * S + 2 * S;

@@ -142,6 +142,8 @@ struct Lowering {
     if (users[i].empty()) return false;
     for (uint32_t u : users[i]) {
       const Node& c = N(u);
+      // the branch that returns into a hyper-connection: its norm runs inside the mixing kernel
+      if (c.op == "mhc_post" && c.inputs.size() == 2 && c.inputs[1] == i && c.inputs[0] != i && N(i).op == "norm" && !N(i).has("zero_centered")) continue;
       if (c.inputs[0] != i) return false;
       if (c.op != "linear" && c.op != "router" && c.op != "expert_linear") return false;
     }
@@ -417,7 +419,13 @@ struct Lowering {
         if (n.op == "router") ins.op = "router_topk";
         ins.dtype = dtype_of(n, ins.inputs);
       } else {
-        for (uint32_t in : n.inputs) ins.inputs.push_back(value_of(in));
+        if (n.op == "mhc_post" && folded_norm[n.inputs[1]]) {
+          Src s = source(n.inputs[1]);
+          ins.inputs = {value_of(n.inputs[0]), s.value};
+          for (auto& kv : s.norm) ins.attrs.push_back(kv);
+        } else {
+          for (uint32_t in : n.inputs) ins.inputs.push_back(value_of(in));
+        }
         // the streams a hyper-connection mixed are read again when its branch returns: name them, so that they stay alive
         if (n.op == "mhc_post") ins.inputs.push_back(value_of(N(n.inputs[0]).inputs[0]));
         if (n.op == "cache_norm_rope_append") ins.op = "mla_kv_write";

@@ -28,7 +28,8 @@ using namespace ifab::mla;
 namespace {
 
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) mla_kv_write_kernel(const bf16* kv, long ldkv, const bf16* norm_w, float eps,
+// `kr` (optional): the rotary columns when they do not follow the latent columns in `kv` (e.g. a convolved latent)
+__global__ void __launch_bounds__(128) mla_kv_write_kernel(const bf16* kv, long ldkv, const bf16* kr, long ldkr, const bf16* norm_w, float eps,
                                                            float theta, const int32_t* positions, const int32_t* slots,
                                                            const int32_t* page_table, int max_pages, int page_tokens,
                                                            bf16* cache, int num_pages, int latent, int rope,
@@ -70,7 +71,8 @@ __global__ void __launch_bounds__(128) mla_kv_write_kernel(const bf16* kv, long 
   if (tid < half) {
     float c, s;
     rope_cos_sin(pos, tid, rope, theta, &c, &s);
-    const float a = __bfloat162float(src[latent + tid]), b = __bfloat162float(src[latent + tid + half]);
+    const bf16* rs = kr ? kr + (long)t * ldkr : src + latent;
+    const float a = __bfloat162float(rs[tid]), b = __bfloat162float(rs[tid + half]);
     dst[latent + tid] = __float2bfloat16_rn(a * c - b * s);
     dst[latent + tid + half] = __float2bfloat16_rn(b * c + a * s);
   }
@@ -390,7 +392,16 @@ extern "C" int ifab_mla_kv_write(const void* kv, long ldkv, const void* norm_w, 
                                  int max_pages, int page_tokens, void* cache, int num_pages, int T, int latent, int rope,
                                  uint32_t* status, void* stream) {
   if (latent % 8 != 0 || latent > 1024 || rope % 2 != 0 || rope > 256 || ldkv % 8 != 0) return -1;
-  return launch_chain(mla_kv_write_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream, (const bf16*)kv, ldkv,
+  return launch_chain(mla_kv_write_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream, (const bf16*)kv, ldkv, (const bf16*)nullptr, 0L,
+                      (const bf16*)norm_w, eps, theta, positions, slots, page_table, max_pages, page_tokens,
+                      (bf16*)cache, num_pages, latent, rope, status);
+}
+
+extern "C" int ifab_mla_kv_write_split(const void* latent_rows, long ldl, const void* rope_rows, long ldr, const void* norm_w, float eps, float theta,
+                                       const int32_t* positions, const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens,
+                                       void* cache, int num_pages, int T, int latent, int rope, uint32_t* status, void* stream) {
+  if (latent % 8 != 0 || latent > 1024 || rope % 2 != 0 || rope > 256 || ldl % 8 != 0 || !rope_rows) return -1;
+  return launch_chain(mla_kv_write_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream, (const bf16*)latent_rows, ldl, (const bf16*)rope_rows, ldr,
                       (const bf16*)norm_w, eps, theta, positions, slots, page_table, max_pages, page_tokens,
                       (bf16*)cache, num_pages, latent, rope, status);
 }

@@ -166,6 +166,34 @@ __global__ void __launch_bounds__(256) mhc_post_kernel(const bf16* X, const bf16
   }
 }
 
+// The same with RMSNorm(branch) * gain folded in: every CTA first reduces the whole branch row (W values, a few KB) to its
+// statistic, then mixes its 256 columns. The normalised value is rounded to bf16 as the stand-alone norm would store it.
+__global__ void __launch_bounds__(256) mhc_post_norm_kernel(const bf16* X, const bf16* branch, long ldb, const bf16* gain, float eps, const float* post,
+                                                            const float* comb, bf16* Y, int S, int W) {
+  __shared__ float red[8];
+  grid_dep_launch();
+  grid_dep_wait();
+  const int t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  const bf16* br_row = branch + (long)t * ldb;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = __bfloat162float(br_row[i]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  if (c >= W) return;
+  const float inv = rsqrtf(ss / (float)W + eps);
+  const float br = __bfloat162float(__float2bfloat16_rn(__bfloat162float(br_row[c]) * inv * __bfloat162float(gain[c])));
+  const bf16* Xt = X + (long)t * S * W;
+  float xv[8];
+  for (int k = 0; k < S; ++k) xv[k] = __bfloat162float(Xt[(long)k * W + c]);
+  for (int i = 0; i < S; ++i) {
+    float v = post[(long)t * S + i] * br;
+    for (int k = 0; k < S; ++k) v += comb[(long)t * S * S + k * S + i] * xv[k];
+    Y[((long)t * S + i) * W + c] = __float2bfloat16_rn(v);
+  }
+}
+
 // ---- gated delta rule, one token ------------------------------------------------------------------------------------
 // grid (H, rows); blockDim = dv (<= 256); thread j owns column j of the state of (slot, head).
 // q, k [rows, H, dk] bf16; v [rows, H, dv] bf16; g, beta [rows, H] f32; state f32 [slots, H, dk, dv]; out [rows, H, dv] bf16.
@@ -324,6 +352,13 @@ extern "C" int ifab_mhc_post(const void* X, const void* branch, long ldb, const 
   if (T < 1 || S < 1 || S > 8 || W < 1) return -1;
   return launch_chain(mhc_post_kernel, dim3((W + 255) / 256, T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)X, (const bf16*)branch, ldb,
                       post, comb, (bf16*)Y, S, W);
+}
+
+extern "C" int ifab_mhc_post_norm(const void* X, const void* branch, long ldb, const void* norm_w, float eps, const float* post, const float* comb, void* Y,
+                                  int T, int S, int W, void* stream) {
+  if (T < 1 || S < 1 || S > 8 || W < 1) return -1;
+  return launch_chain(mhc_post_norm_kernel, dim3((W + 255) / 256, T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)X, (const bf16*)branch, ldb,
+                      (const bf16*)norm_w, eps, post, comb, (bf16*)Y, S, W);
 }
 
 extern "C" int ifab_delta_rule_decode(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state,

@@ -171,6 +171,10 @@ int ifab_sample_topk(const float* logits, long ld, int T, int V_local, int vocab
 int ifab_mla_kv_write(const void* kv, long ldkv, const void* norm_w, float eps, float theta, const int32_t* positions,
                       const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens, void* cache,
                       int num_pages, int T, int latent, int rope, uint32_t* status, void* stream);
+/* the same with the rotary columns in rows of their own (latent_rows [T, >= latent], rope_rows [T, >= rope]) */
+int ifab_mla_kv_write_split(const void* latent_rows, long ldl, const void* rope_rows, long ldr, const void* norm_w, float eps, float theta,
+                            const int32_t* positions, const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens,
+                            void* cache, int num_pages, int T, int latent, int rope, uint32_t* status, void* stream);
 int ifab_mla_q_absorb(const void* q, long ldq, const void* w_kvb, float theta, const int32_t* positions, void* q_lat,
                       int T, int H, int nope, int rope, int latent, int vdim, void* stream);
 int ifab_mla_decode_attention(const void* q_lat, const void* cache, const int32_t* positions, const int32_t* slots,
@@ -215,6 +219,9 @@ int ifab_mhc_pre(const void* X, const float* phi, const float* gamma, const floa
                  float* comb, int T, int S, int W, int sinkhorn_iters, float eps, void* stream);
 int ifab_mhc_post(const void* X, const void* branch, long ldb, const float* post, const float* comb, void* Y, int T, int S, int W,
                   void* stream);
+/* the same with the branch RMS-normalised first (gain norm_w bf16 [W], result rounded to bf16 like a stand-alone norm) */
+int ifab_mhc_post_norm(const void* X, const void* branch, long ldb, const void* norm_w, float eps, const float* post, const float* comb, void* Y,
+                       int T, int S, int W, void* stream);
 /* gated delta rule, one token per row: q, k bf16 [rows, H, dk]; v bf16 [rows, H, dv]; g, beta f32 [rows, H]; state f32 [slots, H, dk, dv] */
 int ifab_delta_rule_decode(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state,
                            const int32_t* slots, void* out, int rows, int H, int dk, int dv, void* stream);

@@ -77,6 +77,7 @@ _SIGS = {
     "ifab_sample_topk": [_P, c_long, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_long, _P, _P, _P, _P, c_u64, _P, _P,
                          C.POINTER(IfabFabric), _P],
     "ifab_mla_kv_write": [_P, c_long, _P, c_float, c_float, _P, _P, _P, c_int, c_int, _P, c_int, c_int, c_int, c_int, _P, _P],
+    "ifab_mla_kv_write_split": [_P, c_long, _P, c_long, _P, c_float, c_float, _P, _P, _P, c_int, c_int, _P, c_int, c_int, c_int, c_int, _P, _P],
     "ifab_mla_q_absorb": [_P, c_long, _P, c_float, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "ifab_mla_decode_attention": [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_float, c_int, c_int, c_int,
                                   c_int, c_int, c_int, _P, c_u64, _P, c_int, c_int, _P, c_long, _P, _P],
@@ -87,6 +88,7 @@ _SIGS = {
     "ifab_mome": [_P, c_long, _P, _P, _P, _P, _P, c_long, c_int, c_int, c_int, c_int, _P],
     "ifab_mhc_pre": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P],
     "ifab_mhc_post": [_P, _P, c_long, _P, _P, _P, c_int, c_int, c_int, _P],
+    "ifab_mhc_post_norm": [_P, _P, c_long, _P, c_float, _P, _P, _P, c_int, c_int, c_int, _P],
     "ifab_rope_prefix": [_P, c_long, _P, _P, c_long, c_int, c_int, c_int, c_int, c_float, _P],
     "ifab_index_cache_append": [_P, c_long, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, _P, _P],
     "ifab_add_rows": [_P, c_long, _P, c_long, _P, c_long, c_int, c_int, _P],

@@ -292,6 +292,17 @@ def mla_kv_write(kv: torch.Tensor, norm_w: torch.Tensor, positions: torch.Tensor
           "mla_kv_write")
 
 
+def mla_kv_write_split(latent_rows: torch.Tensor, rope_rows: torch.Tensor, norm_w: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                       page_table: torch.Tensor, cache: torch.Tensor, *, eps: float, theta: float, status_ptr: Optional[int] = None) -> None:
+    """:func:`mla_kv_write` for latent and rotary columns that live in different rows (``[T, latent]`` and ``[T, rope]`` views)."""
+    T, latent = latent_rows.shape
+    num_pages, page_tokens, _ = cache.shape
+    check(_lib.load().ifab_mla_kv_write_split(latent_rows.data_ptr(), _rows(latent_rows), rope_rows.data_ptr(), _rows(rope_rows), norm_w.data_ptr(),
+                                              eps, theta, positions.data_ptr(), slots.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+                                              page_tokens, cache.data_ptr(), num_pages, T, latent, rope_rows.shape[1], status_ptr, _stream()),
+          "mla_kv_write_split")
+
+
 def mla_kv_write_q8(kv: torch.Tensor, norm_w: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
                     page_table: torch.Tensor, cache: torch.Tensor, *, eps: float, theta: float,
                     status_ptr: Optional[int] = None) -> None:

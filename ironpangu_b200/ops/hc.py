@@ -44,10 +44,17 @@ def mhc_pre(X: torch.Tensor, phi: torch.Tensor, gamma: torch.Tensor, alpha: torc
     return y, post, comb
 
 
-def mhc_post(X: torch.Tensor, branch: torch.Tensor, post: torch.Tensor, comb: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def mhc_post(X: torch.Tensor, branch: torch.Tensor, post: torch.Tensor, comb: torch.Tensor, out: Optional[torch.Tensor] = None,
+             norm_w: Optional[torch.Tensor] = None, eps: float = 1e-5) -> torch.Tensor:
+    """``Y[t, i] = post[t, i] * branch[t] + sum_k comb[t, k, i] * X[t, k]``; with ``norm_w`` the branch is RMS-normalised (gain
+    ``norm_w``, rounded to bf16) inside the same launch."""
     T, S, W = X.shape
     Y = torch.empty(T, S, W, dtype=BF16, device=X.device) if out is None else out
     assert Y.is_contiguous() and X.is_contiguous()
+    if norm_w is not None:
+        check(_lib.load().ifab_mhc_post_norm(X.data_ptr(), branch.data_ptr(), branch.stride(0), norm_w.data_ptr(), eps, post.data_ptr(), comb.data_ptr(),
+                                             Y.data_ptr(), T, S, W, _s()), "mhc_post_norm")
+        return Y
     check(_lib.load().ifab_mhc_post(X.data_ptr(), branch.data_ptr(), branch.stride(0), post.data_ptr(), comb.data_ptr(), Y.data_ptr(), T, S, W,
                                     _s()), "mhc_post")
     return Y

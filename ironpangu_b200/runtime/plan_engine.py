@@ -288,7 +288,6 @@ class PlanEngine:
         self.caches: List[torch.Tensor] = []              # the same tensors in program order (one per attention layer)
         self._kv_of: Dict[int, tuple] = {}                # K / V append instruction -> (key pages, value pages)
         self._kv_pack = None                              # [k | v] rows of a step, for an append outside the fused group
-        self._latent_pack = None                          # [latent | rope] rows of a step, when the two are not adjacent slices
         self._conv_state: Dict[int, torch.Tensor] = {}    # token-convolution instruction -> the previous taps-1 rows per sequence slot
         self._sink_rows: Dict[int, torch.Tensor] = {}     # sink_normalize instruction -> its rows [count, latent + rope]
         self._sinks_of: Dict[int, torch.Tensor] = {}      # cache-write instruction -> the sink rows its readers also attend to
@@ -564,8 +563,6 @@ class PlanEngine:
             if op == "mla_kv_write":
                 self._cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
                 self.caches.append(self._cache_of[k])
-                if self._latent_pack is None or self._latent_pack.shape[1] < w:
-                    self._latent_pack = torch.empty(T, w, dtype=BF16, device=dev)
             elif op in ("mhc_pre", "mhc_merge"):
                 S = int(i["attrs"]["streams"])
                 if S + S * S > 64:
@@ -734,15 +731,15 @@ class PlanEngine:
                 K.rmsnorm(val(ins[0]), self._param(a["weight"]), float(a["eps"]), out=val(k))
             elif op == "mla_kv_write":
                 lat, kr = val(ins[0]), val(ins[1])
-                if kr.data_ptr() != lat.data_ptr() + lat.shape[1] * 2 or kr.stride(0) != lat.stride(0):
-                    # e.g. a convolved latent beside the raw rope columns: bring the two side by side first
-                    kv = self._latent_pack[:T, :lat.shape[1] + kr.shape[1]]
-                    kv[:, :lat.shape[1]].copy_(lat)
-                    kv[:, lat.shape[1]:].copy_(kr)
-                else:
-                    kv = torch.as_strided(lat, (T, lat.shape[1] + kr.shape[1]), (lat.stride(0), 1))
                 if len(ins) > 2:
                     self._sinks_of[k] = self._sink_rows[ins[2]]
+                V[k] = k
+                if kr.data_ptr() != lat.data_ptr() + lat.shape[1] * 2 or kr.stride(0) != lat.stride(0):
+                    # e.g. a convolved latent and the raw rope columns of the projection: the kernel reads them where they are
+                    K.mla_kv_write_split(lat, kr, self._param(a["weight"]), pos, slot, self.page_table, self._cache_of[k], eps=float(a["eps"]),
+                                         theta=float(a["theta"]), status_ptr=st)
+                    continue
+                kv = torch.as_strided(lat, (T, lat.shape[1] + kr.shape[1]), (lat.stride(0), 1))
                 K.mla_kv_write(kv, self._param(a["weight"]), pos, slot, self.page_table, self._cache_of[k], latent=lat.shape[1],
                                rope=kr.shape[1], eps=float(a["eps"]), theta=float(a["theta"]), status_ptr=st)
                 V[k] = k
@@ -798,7 +795,7 @@ class PlanEngine:
                 _, post, comb = V[ins[0]]
                 S = post.shape[1]
                 X, Y = val(ins[2]), val(k)
-                HC.mhc_post(X.view(T, S, X.shape[1] // S), val(ins[1]), post[:T], comb[:T], out=Y.view(T, S, Y.shape[1] // S))
+                HC.mhc_post(X.view(T, S, X.shape[1] // S), val(ins[1]), post[:T], comb[:T], out=Y.view(T, S, Y.shape[1] // S), norm_w=norm_w, eps=eps)
             elif op == "mome":
                 w = self._param(a["weight"])
                 x = val(ins[0])

@@ -219,6 +219,15 @@ def test_mla_kv_write_and_attention(env):
     rows = torch.stack([cache[page_table[1, p // 16], p % 16] for p in range(ctx)]).float()
     torch.testing.assert_close(rows[:, :latent], lat_ref, rtol=1e-2, atol=1e-2)
     torch.testing.assert_close(rows[:, latent:], kr_ref, rtol=1e-2, atol=2e-2)
+    # the same rows with the rotary columns taken from rows of their own: identical cache contents
+    other = torch.zeros_like(cache)
+    lat_rows, rope_rows = kv_all[:, :latent].contiguous(), torch.cat([rnd(ctx, 24), kv_all[:, latent:]], 1)[:, 24:]
+    for s in range(0, ctx, 8):
+        n = min(8, ctx - s)
+        pos = torch.arange(s, s + n, dtype=torch.int32, device="cuda")
+        slot = torch.ones(n, dtype=torch.int32, device="cuda")
+        K.mla_kv_write_split(lat_rows[s:s + n], rope_rows[s:s + n], kvn, pos, slot, page_table, other, eps=eps, theta=theta, status_ptr=fab.desc.status)
+    assert torch.equal(other, cache)
 
     # attention for 3 query rows at different positions of slot 1 (+ windowed variant)
     T = 3

@@ -73,6 +73,15 @@ def test_mhc_pre_and_post():
     Y = hc.mhc_post(X, branch, post, comb)
     want = _r(rpost[:, :, None] * branch.float()[:, None, :] + torch.einsum("tki,tkw->tiw", rcomb, X.float()))
     torch.testing.assert_close(Y.float(), want, rtol=1e-2, atol=1e-2)
+    # the branch norm folded into the same launch equals the stand-alone norm followed by the plain kernel, bit for bit or a rounding apart
+    from ironpangu_b200.ops import decode as K
+
+    gain = (1 + 0.1 * torch.randn(W, generator=g, device="cuda")).to(BF16)
+    wide = torch.randn(T, W + 64, generator=g, device="cuda").to(BF16)[:, 32:32 + W]          # a row-strided branch
+    fused = hc.mhc_post(X, wide, post, comb, norm_w=gain, eps=1e-5)
+    two = hc.mhc_post(X, K.rmsnorm(wide, gain, 1e-5), post, comb)
+    torch.testing.assert_close(fused.float(), two.float(), rtol=1e-2, atol=1e-2)
+    assert (fused != two).float().mean() < 0.02
 
 
 def test_delta_rule_matches_recurrence():
