@@ -41,13 +41,14 @@ uint64_t value_bytes(const Program& p, const Instruction& ins, uint32_t tokens) 
   }
 }
 
-Arena plan_arena(const Program& p, uint32_t tokens) {
+Arena plan_arena(const Program& p, uint32_t tokens, const std::set<uint32_t>& pass_through) {
   Arena a;
   a.tokens = tokens;
   const uint32_t n = (uint32_t)p.instructions.size();
-  // a view keeps its source alive
+  // a view - and an instruction that passes its input through - keeps its source alive
   std::vector<uint32_t> root(n);
-  for (uint32_t i = 0; i < n; ++i) root[i] = p.instructions[i].kind == program::kKindView ? root[p.instructions[i].inputs[0]] : i;
+  for (uint32_t i = 0; i < n; ++i)
+    root[i] = (p.instructions[i].kind == program::kKindView || pass_through.count(i)) ? root[p.instructions[i].inputs[0]] : i;
   std::vector<uint32_t> last(n);
   for (uint32_t i = 0; i < n; ++i) last[i] = i;
   for (uint32_t i = 0; i < n; ++i)
@@ -56,7 +57,7 @@ Arena plan_arena(const Program& p, uint32_t tokens) {
   struct Live { uint64_t off, bytes; uint32_t until; };
   std::vector<Live> live;
   for (uint32_t i = 0; i < n; ++i) {
-    const uint64_t need = align_up(value_bytes(p, p.instructions[i], tokens), 512);
+    const uint64_t need = pass_through.count(i) ? 0 : align_up(value_bytes(p, p.instructions[i], tokens), 512);
     // an in-place residual update may reuse its residual's slot, but the packing stays conservative:
     live.erase(std::remove_if(live.begin(), live.end(), [&](const Live& l) { return l.until < i; }), live.end());
     if (need == 0) continue;
@@ -310,7 +311,19 @@ BundleSummary write_bundle(const BundleInputs& in, const std::string& out_dir) {
   std::vector<init::Plan> plans = init::plan_all(p, ckpt);
   serving::Manifest man = serving::lower(p, sha);
   const uint32_t arena_tokens = std::max<uint32_t>(std::max(in.options.prefill_tokens, in.options.resident_sequences), 1);
-  Arena arena = plan_arena(p, arena_tokens);
+  // optional norms whose gain no rank loads pass their rows through: the arena lets their source live on instead of a copy
+  std::set<uint32_t> pass_through;
+  for (uint32_t i = 0; i < p.instructions.size(); ++i) {
+    const auto& ins = p.instructions[i];
+    if (ins.op != "optional_norm" || ins.inputs.size() != 1 || !ins.attr("weight")) continue;
+    const auto& src = p.instructions[ins.inputs[0]];
+    if (src.kind != ins.kind || src.width != ins.width || src.dtype != ins.dtype || src.kind == program::kKindView) continue;
+    bool loaded = false;
+    for (const auto& pl : plans)
+      for (const auto& prm : pl.parameters) loaded = loaded || prm.name == *ins.attr("weight");
+    if (!loaded) pass_through.insert(i);
+  }
+  Arena arena = plan_arena(p, arena_tokens, pass_through);
   const std::string bfp = backend_fingerprint(in.kernel_source_dir);
   const uint64_t pf = fnv1a64(exec.data(), exec.size()), bf = fnv1a64(bfp.data(), bfp.size());
 

@@ -11,6 +11,7 @@
 // directory is never overwritten. Reference: crates/inferfabric-compiler/src/token.rs:338-458,
 // native/include/frozen_arena.h:14-99, token_physical.rs:14-273.
 #pragma once
+#include <set>
 #include "initplan.h"
 #include "physical.h"
 #include "serving.h"
@@ -34,7 +35,9 @@ struct Arena {
   void verify() const;               // 512-byte alignment, ascending, no two live-overlapping slots share bytes
 };
 // Live-interval first-fit packing of every instruction result for `tokens` query rows.
-Arena plan_arena(const program::Program& p, uint32_t tokens);
+// `pass_through`: instructions that hand their first input on unchanged (an optional norm whose gain the checkpoint lacks): they
+// get no slot, and their source's slot lives on for as long as they are read.
+Arena plan_arena(const program::Program& p, uint32_t tokens, const std::set<uint32_t>& pass_through = {});
 uint64_t value_bytes(const program::Program& p, const program::Instruction& ins, uint32_t tokens);
 
 // ---- inspection plan -------------------------------------------------------------------------------

@@ -65,8 +65,16 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 //
 // mhc_logits_kernel: grid (M + 1, T), M = S*S + 2S. CTA j < M: raw[t][j] = sum_c phi[j][c] * gamma[c] * X[t][c]; CTA M: the sum of
 // squares. The M + 1 floats land in the first bytes of the token's row of y (the tail kernel reads them before it writes y).
-__global__ void __launch_bounds__(256) mhc_logits_kernel(const bf16* X, const float* phi, const float* gamma, float* raw, long raw_stride, int S, int W) {
+__device__ __forceinline__ void mhc_mix_token(const bf16* X, const float* raw, long raw_stride, const float* alpha, const float* beta, bf16* y, float* post,
+                                              float* comb, int S, int W, int iters, float eps, int t);
+// With `tickets` (one zeroed word per token, left zero again): the CTA that finishes a token's sums last also runs the token's
+// tail (mhc_mix_token) - the whole pre step in one launch.
+template <bool FUSED>
+__global__ void __launch_bounds__(256) mhc_logits_kernel(const bf16* X, const float* phi, const float* gamma, float* raw, long raw_stride, int S, int W,
+                                                         uint32_t* tickets, const float* alpha, const float* beta, float* post, float* comb, int iters,
+                                                         float eps) {
   __shared__ float red[8];
+  __shared__ bool is_last;
   grid_dep_launch();
   grid_dep_wait();
   const int j = blockIdx.x, t = blockIdx.y, M = S * S + 2 * S;
@@ -97,19 +105,29 @@ __global__ void __launch_bounds__(256) mhc_logits_kernel(const bf16* X, const fl
   }
   s = block_sum(s, red);
   if (threadIdx.x == 0) raw[(long)t * raw_stride + j] = s;
+  if (!FUSED) return;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t tk = atomicAdd(tickets + t, 1u);
+    is_last = (tk == gridDim.x - 1);
+    if (is_last) tickets[t] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  mhc_mix_token(X, raw, raw_stride, alpha, beta, reinterpret_cast<bf16*>(raw), post, comb, S, W, iters, eps, t);
 }
 
 // mhc_mix_kernel: one CTA per token. Reads the M + 1 raw sums, then: sigmoid gates (pre, post), the S x S logits through a row
 // softmax and `iters` rounds of Sinkhorn normalisation (one thread per matrix entry, two buffers, one barrier per pass), and the
 // branch input y = sum_s pre_s * X_s. S <= 8.
-__global__ void __launch_bounds__(256) mhc_mix_kernel(const bf16* X, const float* raw, long raw_stride, const float* alpha, const float* beta, bf16* y,
-                                                      float* post, float* comb, int S, int W, int iters, float eps) {
+__device__ __forceinline__ void mhc_mix_token(const bf16* X, const float* raw, long raw_stride, const float* alpha, const float* beta, bf16* y, float* post,
+                                              float* comb, int S, int W, int iters, float eps, int t) {
   __shared__ float m[8 * 8 + 16 + 1];
   __shared__ float R[2][64];
   __shared__ float pre_s[8];
-  grid_dep_launch();
-  grid_dep_wait();
-  const int t = blockIdx.x, M = S * S + 2 * S, n = S * S, tid = threadIdx.x;
+  const int M = S * S + 2 * S, n = S * S, tid = threadIdx.x;
   const long total = (long)S * W;
   const bf16* Xt = X + (long)t * total;
   if (tid <= M) m[tid] = raw[(long)t * raw_stride + tid];
@@ -146,6 +164,13 @@ __global__ void __launch_bounds__(256) mhc_mix_kernel(const bf16* X, const float
     for (int k = 0; k < S; ++k) v += pre_s[k] * __bfloat162float(Xt[(long)k * W + c]);
     y[(long)t * W + c] = __float2bfloat16_rn(v);
   }
+}
+
+__global__ void __launch_bounds__(256) mhc_mix_kernel(const bf16* X, const float* raw, long raw_stride, const float* alpha, const float* beta, bf16* y,
+                                                      float* post, float* comb, int S, int W, int iters, float eps) {
+  grid_dep_launch();
+  grid_dep_wait();
+  mhc_mix_token(X, raw, raw_stride, alpha, beta, y, post, comb, S, W, iters, eps, blockIdx.x);
 }
 
 // grid (ceil(W/256), T): Y[t, i, c] = post[t, i] * branch[t, c] + sum_k comb[t, k, i] * X[t, k, c]
@@ -336,15 +361,30 @@ extern "C" int ifab_mome(const void* x, long ldx, const float* w, void* state, c
                       slots, (bf16*)y, ldy, T, C, taps, c_offset);
 }
 
-extern "C" int ifab_mhc_pre(const void* X, const float* phi, const float* gamma, const float* alpha, const float* beta, void* y, float* post,
-                            float* comb, int T, int S, int W, int sinkhorn_iters, float eps, void* stream) {
+static int mhc_pre_launch(const void* X, const float* phi, const float* gamma, const float* alpha, const float* beta, void* y, float* post, float* comb,
+                          int T, int S, int W, int sinkhorn_iters, float eps, uint32_t* tickets, void* stream) {
   const int M = S * S + 2 * S;
   // the raw sums of a token travel in the first (M + 1) floats of its row of y
   if (T < 1 || S < 1 || S > 8 || W < 1 || sinkhorn_iters < 1 || (W & 1) || (long)W * 2 < (long)(M + 1) * 4) return -1;
-  if (int rc = launch_chain(mhc_logits_kernel, dim3(M + 1, T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)X, phi, gamma, (float*)y, (long)(W / 2), S, W))
+  if (tickets)
+    return launch_chain(mhc_logits_kernel<true>, dim3(M + 1, T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)X, phi, gamma, (float*)y, (long)(W / 2), S,
+                        W, tickets, alpha, beta, post, comb, sinkhorn_iters, eps);
+  if (int rc = launch_chain(mhc_logits_kernel<false>, dim3(M + 1, T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)X, phi, gamma, (float*)y,
+                            (long)(W / 2), S, W, (uint32_t*)nullptr, alpha, beta, post, comb, sinkhorn_iters, eps))
     return rc;
   return launch_chain(mhc_mix_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)X, (const float*)y, (long)(W / 2), alpha, beta, (bf16*)y,
                       post, comb, S, W, sinkhorn_iters, eps);
+}
+
+extern "C" int ifab_mhc_pre(const void* X, const float* phi, const float* gamma, const float* alpha, const float* beta, void* y, float* post,
+                            float* comb, int T, int S, int W, int sinkhorn_iters, float eps, void* stream) {
+  return mhc_pre_launch(X, phi, gamma, alpha, beta, y, post, comb, T, S, W, sinkhorn_iters, eps, nullptr, stream);
+}
+
+extern "C" int ifab_mhc_pre_ticketed(const void* X, const float* phi, const float* gamma, const float* alpha, const float* beta, void* y, float* post,
+                                     float* comb, int T, int S, int W, int sinkhorn_iters, float eps, uint32_t* tickets, void* stream) {
+  if (!tickets) return -1;
+  return mhc_pre_launch(X, phi, gamma, alpha, beta, y, post, comb, T, S, W, sinkhorn_iters, eps, tickets, stream);
 }
 
 extern "C" int ifab_mhc_post(const void* X, const void* branch, long ldb, const float* post, const float* comb, void* Y, int T, int S, int W,

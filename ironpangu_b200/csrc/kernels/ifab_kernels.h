@@ -217,6 +217,9 @@ int ifab_mome(const void* x, long ldx, const float* w, void* state, const int32_
 /* X bf16 [T, S, W]; phi f32 [S*S+2S, S*W]; gamma [S*W]; alpha [3]; beta [S*S+2S] -> y bf16 [T, W], post f32 [T, S], comb f32 [T, S, S] */
 int ifab_mhc_pre(const void* X, const float* phi, const float* gamma, const float* alpha, const float* beta, void* y, float* post,
                  float* comb, int T, int S, int W, int sinkhorn_iters, float eps, void* stream);
+/* the same in ONE launch: `tickets` = T zeroed 32-bit words (left zero again); the CTA that finishes a token's sums last runs its tail */
+int ifab_mhc_pre_ticketed(const void* X, const float* phi, const float* gamma, const float* alpha, const float* beta, void* y, float* post,
+                          float* comb, int T, int S, int W, int sinkhorn_iters, float eps, uint32_t* tickets, void* stream);
 int ifab_mhc_post(const void* X, const void* branch, long ldb, const float* post, const float* comb, void* Y, int T, int S, int W,
                   void* stream);
 /* the same with the branch RMS-normalised first (gain norm_w bf16 [W], result rounded to bf16 like a stand-alone norm) */

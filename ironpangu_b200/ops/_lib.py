@@ -87,6 +87,7 @@ _SIGS = {
                                c_float, _P, _P],
     "ifab_mome": [_P, c_long, _P, _P, _P, _P, _P, c_long, c_int, c_int, c_int, c_int, _P],
     "ifab_mhc_pre": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P],
+    "ifab_mhc_pre_ticketed": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P, _P],
     "ifab_mhc_post": [_P, _P, c_long, _P, _P, _P, c_int, c_int, c_int, _P],
     "ifab_mhc_post_norm": [_P, _P, c_long, _P, c_float, _P, _P, _P, c_int, c_int, c_int, _P],
     "ifab_rope_prefix": [_P, c_long, _P, _P, c_long, c_int, c_int, c_int, c_int, c_float, _P],

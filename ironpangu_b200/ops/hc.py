@@ -28,9 +28,11 @@ def mome(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, positions: torch
 
 
 def mhc_pre(X: torch.Tensor, phi: torch.Tensor, gamma: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor, *, sinkhorn: int = 20,
-            eps: float = 1e-6, out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+            eps: float = 1e-6, out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
+            tickets_ptr: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Returns ``(y bf16 [T, W], post f32 [T, S], comb f32 [T, S, S])`` for residual streams ``X`` bf16 ``[T, S, W]``; ``out``
-    names three contiguous tensors of those shapes to write into."""
+    names three contiguous tensors of those shapes to write into. ``tickets_ptr``: the address of ``T`` zeroed 32-bit words
+    (left zero again) - the step then runs as one launch (the CTA that finishes a token's sums last runs its tail)."""
     T, S, W = X.shape
     if out is not None:
         y, post, comb = out
@@ -39,6 +41,10 @@ def mhc_pre(X: torch.Tensor, phi: torch.Tensor, gamma: torch.Tensor, alpha: torc
         y = torch.empty(T, W, dtype=BF16, device=X.device)
         post = torch.empty(T, S, dtype=torch.float32, device=X.device)
         comb = torch.empty(T, S, S, dtype=torch.float32, device=X.device)
+    if tickets_ptr:
+        check(_lib.load().ifab_mhc_pre_ticketed(X.data_ptr(), phi.data_ptr(), gamma.data_ptr(), alpha.data_ptr(), beta.data_ptr(), y.data_ptr(),
+                                                post.data_ptr(), comb.data_ptr(), T, S, W, sinkhorn, eps, tickets_ptr, _s()), "mhc_pre")
+        return y, post, comb
     check(_lib.load().ifab_mhc_pre(X.data_ptr(), phi.data_ptr(), gamma.data_ptr(), alpha.data_ptr(), beta.data_ptr(), y.data_ptr(),
                                    post.data_ptr(), comb.data_ptr(), T, S, W, sinkhorn, eps, _s()), "mhc_pre")
     return y, post, comb

@@ -199,10 +199,12 @@ class FrozenArena:
             raise ValueError(f"arena was planned for {self.tokens} query rows, the engine runs {rows}: compile the bundle with "
                              f"prefill_tokens >= {rows}")
         self.slots: Dict[int, tuple] = {}
+        self.live: Dict[int, tuple] = {}          # instruction -> (first, last) instruction index during which its slot is its own
         for (off, size), (ins, first, last) in zip(sizes, owners):
             if off % 512 or size % 512 or off + size > self.bytes:
                 raise ValueError(f"arena slot of instruction {ins} is misaligned or outside the arena")
             self.slots[ins] = (off, size)
+            self.live[ins] = (first, last)
         ws = (bundle / f"workspace-rank-{rank}.txt").read_text().split()
         if len(ws) != 4 or ws[0] != "IFWORKSPACE1" or int(ws[1], 16) != want:
             raise ValueError("workspace file does not belong to this bundle's program")
@@ -556,10 +558,18 @@ class PlanEngine:
             esize = torch.empty((), dtype=dtype).element_size()
             return self.arena.lease(k, n * esize).view(dtype).view(*shape)
 
+        # an optional norm whose gain the checkpoint lacks passes its rows through: the compiler then gave it no slot and let
+        # its source's slot live on, so the rows are handed on without a copy
+        self._pass_through = {k for k, i in enumerate(self.ins) if i["op"] == "optional_norm" and k not in self.arena.slots}
+        for k in self._pass_through:
+            if self._param(self.ins[k]["attrs"]["weight"], True) is not None:
+                raise ValueError(f"the bundle was compiled without {self.ins[k]['attrs']['weight']}, the parameters have it: recompile against this checkpoint")
         for k, i in enumerate(self.ins):
             op, w = i["op"], i["width"]
             if op == "view":
                 continue
+            if op == "optional_norm" and k in self._pass_through:
+                continue                                                   # no slot of its own is touched
             if op == "mla_kv_write":
                 self._cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
                 self.caches.append(self._cache_of[k])
@@ -777,9 +787,11 @@ class PlanEngine:
                 val(k).copy_(val(ins[0]))
             elif op == "optional_norm":
                 w = self._param(a["weight"], True)
-                if w is None:
-                    val(k).copy_(val(ins[0]))      # the checkpoint has no such gain: the rows pass through (into this instruction's
-                                                   # own slot - the source's slot is free for reuse after this instruction)
+                if w is None and k in self._pass_through:
+                    V[k] = V[ins[0]]               # the checkpoint has no such gain and the source's slot stays intact for as long
+                                                   # as this value is read: the rows pass through without a copy
+                elif w is None:
+                    val(k).copy_(val(ins[0]))      # ... otherwise into this instruction's own slot
                 else:
                     K.rmsnorm(val(ins[0]), w, float(a["eps"]), out=val(k))
             elif op in ("mhc_pre", "mhc_merge"):
@@ -788,7 +800,8 @@ class PlanEngine:
                 X = val(ins[0])
                 b = a["weight"]
                 HC.mhc_pre(X.view(T, S, X.shape[1] // S), self._param(b + ".phi"), self._param(b + ".gamma"), self._param(b + ".alpha"),
-                           self._param(b + ".beta"), sinkhorn=int(a["sinkhorn"]), eps=float(a["eps"]), out=(y[:T], post[:T], comb[:T]))
+                           self._param(b + ".beta"), sinkhorn=int(a["sinkhorn"]), eps=float(a["eps"]), out=(y[:T], post[:T], comb[:T]),
+                           tickets_ptr=fab.ticket_ptr + 32 if T <= 8 else None)        # eight ticket words after the router's
             elif op == "mhc_input":
                 V[k] = V[ins[0]][0]
             elif op == "mhc_post":

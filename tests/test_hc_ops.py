@@ -65,6 +65,12 @@ def test_mhc_pre_and_post():
     beta = torch.randn(M, generator=g, device="cuda") * 0.3
     y, post, comb = hc.mhc_pre(X, phi, gamma, alpha, beta, sinkhorn=20, eps=1e-6)
     ry, rpost, rcomb = _mhc_ref(X, phi, gamma, alpha, beta, 20, 1e-6)
+    # the one-launch form (last CTA of a token runs the tail) gives the same bits, twice in a row (the tickets reset themselves)
+    tickets = torch.zeros(8, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        y1, post1, comb1 = hc.mhc_pre(X, phi, gamma, alpha, beta, sinkhorn=20, eps=1e-6, tickets_ptr=tickets.data_ptr())
+        assert torch.equal(y1, y) and torch.equal(post1, post) and torch.equal(comb1, comb)
+    assert int(tickets.abs().sum()) == 0
     torch.testing.assert_close(post, rpost, rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(comb, rcomb, rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(comb.sum(1), torch.ones(T, S, device="cuda"), rtol=1e-3, atol=1e-3)   # doubly stochastic

@@ -56,11 +56,31 @@ def test_lowering_keeps_the_mixed_streams_alive_for_the_return_of_the_branch(tmp
     for k, p in enumerate(ins):
         if p["op"] != "mhc_post":
             continue
-        s_off, s_size, _, s_last = slots[p["inputs"][2]]
+        streams = p["inputs"][2]
+        while streams not in slots and ins[streams]["op"] == "optional_norm":
+            streams = ins[streams]["inputs"][0]       # a norm the checkpoint lacks hands its source's slot on
+        s_off, s_size, _, s_last = slots[streams]
         assert s_last >= k
         for owner, (off, size, first, last) in slots.items():
-            if owner != p["inputs"][2] and p["inputs"][0] <= owner < k:
+            if owner != streams and p["inputs"][0] <= owner < k:
                 assert off + size <= s_off or s_off + s_size <= off, (owner, k)
+
+
+def test_an_optional_norm_the_checkpoint_lacks_gets_no_slot_and_keeps_its_source_alive(tmp_path):
+    src, ck, bundle = _compiled(tmp_path, layers=2)
+    ins = json.loads((bundle / "device-program.json").read_text())["instructions"]
+    arena = (bundle / "arena-rank-0.txt").read_text().split("\n")
+    n = int(arena[0].split()[4])
+    live = {int(l.split()[0]): (int(l.split()[1]), int(l.split()[2])) for l in arena[2 + n:2 + 2 * n]}
+    users = {}
+    for k, i in enumerate(ins):
+        for j in i["inputs"]:
+            users.setdefault(j, []).append(k)
+    optional = [k for k, i in enumerate(ins) if i["op"] == "optional_norm"]
+    assert len(optional) == 2
+    for k in optional:
+        assert k not in live
+        assert live[ins[k]["inputs"][0]][1] >= max(users[k])
 
 
 def test_sink_rows_must_come_from_a_sink_normalize(tmp_path):

@@ -48,3 +48,27 @@ def test_flagship_example_is_the_generated_source_at_tp8(tmp_path):
     strip = lambda i: (i["op"], i["width"], i["dtype"], i["inputs"], {k: (float(v) if k in ("norm_eps", "eps", "scale", "theta") else v)
                                                                       for k, v in i["attrs"].items()})
     assert [strip(i) for i in pa] == [strip(i) for i in pb]
+
+
+def test_hyper_and_dense_examples_are_the_generated_sources(tmp_path):
+    """`examples/hyper_mla_moe_92b_tp8.inferfabric` (46 layers, 4 residual streams, 256 experts, 128 sinks) and
+    `examples/dense_gqa_2b_tp2.inferfabric` are what the generators write; the 92B program needs 35,085 checkpoint tensors."""
+    from ironpangu_b200 import compiler
+    from ironpangu_b200.compiler.sources import HyperMlaMoeConfig, dense_gqa_source, hyper_mla_moe_source
+    from ironpangu_b200.models.dense_gqa import DenseConfig
+
+    root = Path(__file__).resolve().parents[1] / "examples"
+    assert (root / "hyper_mla_moe_92b_tp8.inferfabric").read_text() == hyper_mla_moe_source(HyperMlaMoeConfig.pangu92b(), 8, context=512,
+                                                                                             name="HyperMlaMoe92B")
+    assert (root / "dense_gqa_2b_tp2.inferfabric").read_text() == dense_gqa_source(DenseConfig.qwen2b(), 2, context=2048, name="DenseGqa2B")
+    r = compiler.cli("explain", str(root / "hyper_mla_moe_92b_tp8.inferfabric"))
+    assert r.returncode == 0, r.stderr
+    e = json.loads(r.stdout)
+    assert e["checkpoint_tensors"] == 35085 and e["checkpoint_bytes"] == 183188067132 and e["parallel"]["tp"] == 8
+    ops = e["physical_ops"]
+    assert ops["mhc_pre"] == 92 and ops["mhc_post"] == 92 and ops["mome"] == 138 and ops["sink_normalize"] == 46 and ops["moe_down_allreduce"] == 44
+    assert "norm" not in ops          # every norm is folded: into a projection, the router, or the return of a hyper-connection
+    out = compiler.write_bundle(str(root / "hyper_mla_moe_92b_tp8.inferfabric"), str(tmp_path / "b"))
+    assert compiler.validate_bundle(out["dir"])["ranks"] == 8
+    d = compiler.cli("explain", str(root / "dense_gqa_2b_tp2.inferfabric"))
+    assert d.returncode == 0 and json.loads(d.stdout)["physical_ops"]["paged_attention"] == 24
