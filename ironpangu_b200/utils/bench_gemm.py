@@ -29,6 +29,7 @@ def time_fn(fn, flush, iters=10):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shapes", default="4096x4096x4096,4096x2112x4096,4096x3072x4096,4096x4096x1536,8192x8192x8192,128x3072x4096")
+    ap.add_argument("--two-sm", action="store_true", help="also time the CTA-pair kernel (shapes with M and N multiples of 256) and check it against the one-CTA kernel")
     ap.add_argument("--persistent-ar", action="store_true",
                     help="also time the persistent GEMM + all-reduce kernel at world 1 (its main loop and epilogue without any exchange)")
     args = ap.parse_args()
@@ -51,6 +52,19 @@ def main():
         fl = 2.0 * M * N * K
         out.append({"shape": s, "ours_ms": round(t_ours, 4), "ours_tflops": round(fl / t_ours / 1e9, 1),
                     "cublas_ms": round(t_lib, 4), "cublas_tflops": round(fl / t_lib / 1e9, 1)})
+        if args.two_sm and M % 256 == 0 and N % 256 == 0:
+            from ironpangu_b200.ops.gemm import gemm_2sm
+
+            st = torch.zeros(1, dtype=torch.int32, device="cuda")
+            c2 = torch.empty_like(c)
+            gemm(a, b, out=c)
+            gemm_2sm(a, b, out=c2, status_ptr=st.data_ptr())
+            torch.cuda.synchronize()
+            out[-1].update({"two_sm_status": int(st[0]), "two_sm_equals_one_cta": bool(torch.equal(c, c2)),
+                            "two_sm_max_abs_diff": float((c.float() - c2.float()).abs().max())})
+            if int(st[0]) == 0:
+                t2 = time_fn(lambda: gemm_2sm(a, b, out=c2), flush)
+                out[-1].update({"two_sm_ms": round(t2, 4), "two_sm_tflops": round(fl / t2 / 1e9, 1)})
         if fab is not None:
             sym = fab.symmetric_empty((M, N))
             res = torch.randn(M, N, device="cuda").to(torch.bfloat16)
