@@ -66,6 +66,10 @@ int ifab_gemm_bf16(const void* a, long lda, const void* b, long ldb, void* c, lo
 int ifab_gemm_bf16_2sm(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int out_f32, const void* residual,
                        long ldr, int M, int N, int K, uint32_t* status, void* stream);
 
+/* CTA pairs, persistent grid (one pair per SM pair), two accumulators in tensor memory: the epilogue of a tile runs under the next tile's MMAs */
+int ifab_gemm_bf16_2sm_persistent(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int out_f32, const void* residual,
+                                  long ldr, int M, int N, int K, uint32_t* status, void* stream);
+
 int ifab_gemm_allreduce_bf16(const void* a, long lda, const void* b, long ldb, void* const* out_peers, long ldc, const void* residual,
                              long ldr, int M, int N, int K, const IfabFabric* fab, void* stream);
 

@@ -11,6 +11,8 @@
 // stored everywhere in this library, so no transposes are needed. M, N and K tails are handled by
 // TMA zero fill plus masked stores. Used for prefill chunks and batched decode (M >= 16); the
 // reference's counterpart is aclnnMatmul on [T<=4096, K] activations (token_executor.h:387-456).
+#include <cstdlib>
+
 #include "tc_gemm_core.cuh"
 #include "ifab_kernels.h"
 
@@ -142,10 +144,26 @@ int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t batch, uint64
 
 }  // namespace ifab::tc
 
+// IFAB_GEMM_2SM=0 keeps every shape on the one-CTA kernel (for A/B timing)
+static bool two_sm_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("IFAB_GEMM_2SM");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
 // C[M,N] = A[M,K] * B[N,K]^T (+ residual). A: row stride lda, B: row stride ldb (elements), K % 8 == 0.
 extern "C" int ifab_gemm_bf16(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int out_f32,
                               const void* residual, long ldr, int M, int N, int K, uint32_t* status, void* stream) {
   if (M < 1 || N < 1 || K < 8 || K % 8 || lda % 8 || ldb % 8) return -1;
+  // whole 256 x 256 tiles: CTA pairs (tcgen05.mma cta_group::2; same accumulation order, same bits) - persistent with two
+  // accumulators when there is more than one tile per SM pair, one tile per pair otherwise
+  if (M % 256 == 0 && N % 256 == 0 && two_sm_enabled()) {
+    const long tiles = (long)(M / 256) * (N / 256);
+    return tiles > 74 ? ifab_gemm_bf16_2sm_persistent(a, lda, b, ldb, c, ldc, out_f32, residual, ldr, M, N, K, status, stream)
+                      : ifab_gemm_bf16_2sm(a, lda, b, ldb, c, ldc, out_f32, residual, ldr, M, N, K, status, stream);
+  }
   CUtensorMap ta, tb;
   const int BN = N > 128 ? 256 : 128;
   if (int rc = make_tmap_bf16_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return rc;

@@ -13,6 +13,8 @@
 // Six stages of 32 KB. No TMA load is multicast: every CTA fetches its own tiles. Every mbarrier wait is bounded; a wait that
 // runs out raises the CTA's abort flag and a status bit, and both CTAs still meet at the closing cluster barrier.
 // Shapes: M and N multiples of 256 (other shapes take the one-CTA kernel), K % 8 == 0 (K tail by TMA zero fill).
+#include <algorithm>
+
 #include "tc_gemm_core.cuh"
 #include "ifab_kernels.h"
 
@@ -203,6 +205,137 @@ __global__ void __launch_bounds__(192) tc_gemm_2sm_kernel(const __grid_constant_
   }
 }
 
+// ---- persistent form -------------------------------------------------------------------------------------------------------
+// One CTA pair per SM pair (at most 74 pairs) walks the 256 x 256 tiles round-robin. Tensor memory holds TWO accumulators
+// (2 x 256 columns = all 512): while the epilogue warps of both CTAs drain tile j, the leader already issues the MMAs of tile
+// j + 1 into the other half, and the producers keep the stage ring full across tile boundaries. An accumulator half goes back
+// to the issuer when the eight epilogue warps of the pair (four per CTA) have arrived on the leader's acc_empty barrier.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+// grid (2 * pairs), clusters of 2; 192 threads
+__global__ void __launch_bounds__(192) tc_gemm_2sm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                                                                     Gemm2Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE2_BYTES);
+  uint64_t* empty = full + STAGES2;
+  uint64_t* acc_full = empty + STAGES2;          // [2], one arrival each (the leader's commit, multicast to both CTAs)
+  uint64_t* acc_empty = acc_full + 2;            // [2], used in the leader only: eight arrivals each (epilogue warps of both CTAs)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = (int)(blockIdx.x >> 1), pairs = (int)(gridDim.x >> 1);
+  const int tiles_n = p.N / TN, tiles = (p.M / (2 * BM)) * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, 2 * TN);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  grid_dep_launch();
+  grid_dep_wait();
+  if (warp == 0 && lane == 0) {
+    // ---- producer (both CTAs): one ring across all tiles ----
+    uint32_t it = 0;
+    for (int t = pair; t < tiles && !*abort_flag; t += pairs) {
+      const int m0 = (t / tiles_n) * 2 * BM + (int)rank * BM, n0 = (t % tiles_n) * TN + (int)rank * HALF_N;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = (int)(it % STAGES2);
+        const uint32_t round = it / STAGES2;
+        if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, p.spin_limit)) { *abort_flag = 1; break; }
+        if (*abort_flag) break;
+        unsigned char* a_dst = smem + s * STAGE2_BYTES;
+        if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE2_BYTES);
+        const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+        tma_load_2d_pair(a_dst, &tmap_a, bar, kb * BK, m0);
+        tma_load_2d_pair(a_dst + A2_BYTES, &tmap_b, bar, kb * BK, n0);
+      }
+    }
+    if (*abort_flag && p.status) atomicOr(p.status, IFAB_STATUS_MBAR_TIMEOUT);
+  } else if (warp == 1 && lane == 0 && rank == 0) {
+    // ---- MMA issuer (leader only) ----
+    constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, TN);
+    uint32_t it = 0;
+    bool ok = true;
+    int j = 0;
+    for (int t = pair; t < tiles && ok; t += pairs, ++j) {
+      const int b = j & 1;
+      // the accumulator half must have been drained by the epilogue of tile j - 2
+      if (j >= 2 && !mbar_wait(&acc_empty[b], ((j >> 1) - 1) & 1, p.spin_limit)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d = tmem_base + (uint32_t)(b * TN);
+      for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+        const int s = (int)(it % STAGES2);
+        if (!mbar_wait(&full[s], (it / STAGES2) & 1, p.spin_limit) || *abort_flag) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * STAGE2_BYTES);
+        const uint64_t da = umma_desc_sw128(a_addr), db = umma_desc_sw128(a_addr + A2_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16_pair(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, kb > 0 || k > 0);
+        umma_commit_pair(&empty[s]);
+      }
+      umma_commit_pair(&acc_full[b]);
+    }
+    if (!ok) {
+      *abort_flag = 1;
+      if (p.status) atomicOr(p.status, IFAB_STATUS_MBAR_TIMEOUT);
+      // wake the epilogues of both CTAs for every tile they still expect, so that they run into their own bounded waits only once
+      for (int b = 0; b < 2; ++b) umma_commit_pair(&acc_full[b]);
+    }
+  } else if (warp >= 2) {
+    // ---- epilogue (both CTAs) ----
+    const int q = warp & 3;
+    int j = 0;
+    for (int t = pair; t < tiles; t += pairs, ++j) {
+      const int b = j & 1;
+      const bool ready = mbar_wait(&acc_full[b], (j >> 1) & 1, p.spin_limit);
+      tc_fence_after();
+      if (!ready || *abort_flag) {
+        *abort_flag = 1;
+        if (lane == 0 && p.status) atomicOr(p.status, IFAB_STATUS_MBAR_TIMEOUT);
+        break;
+      }
+      const int m0 = (t / tiles_n) * 2 * BM + (int)rank * BM, n0 = (t % tiles_n) * TN;
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 32) {
+        float v[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TN + c0), v);
+        tmem_ld_wait();
+        store_row32_2(p, row, n0 + c0, v);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[b]), 0));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 2 * TN);
+  }
+}
+
 }  // namespace
 
 // C[M,N] = A[M,K] * B[N,K]^T (+ residual) with CTA pairs on 256 x 256 tiles. M % 256 == 0, N % 256 == 0, K % 8 == 0.
@@ -216,4 +349,21 @@ extern "C" int ifab_gemm_bf16_2sm(const void* a, long lda, const void* b, long l
   if (int rc = opt_in_smem(tc_gemm_2sm_kernel, SMEM2)) return rc;
   dim3 grid(2 * (M / 256), N / 256);
   return launch_chain_cluster(tc_gemm_2sm_kernel, grid, dim3(192), 2, (size_t)SMEM2, (cudaStream_t)stream, ta, tb, p);
+}
+
+// The same with a persistent grid (one CTA pair per SM pair) and two accumulators in tensor memory.
+extern "C" int ifab_gemm_bf16_2sm_persistent(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int out_f32, const void* residual,
+                                             long ldr, int M, int N, int K, uint32_t* status, void* stream) {
+  if (M < 256 || N < 256 || M % 256 || N % 256 || K < 8 || K % 8 || lda % 8 || ldb % 8) return -1;
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_bf16_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, HALF_N)) return rc;
+  Gemm2Params p{c, ldc, out_f32, (const bf16*)residual, ldr, M, N, K, status, 4000000u};
+  if (int rc = opt_in_smem(tc_gemm_2sm_persistent_kernel, SMEM2)) return rc;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int tiles = (M / 256) * (N / 256);
+  const int pairs = std::max(1, std::min(tiles, sms / 2));
+  return launch_chain_cluster(tc_gemm_2sm_persistent_kernel, dim3(2 * pairs), dim3(192), 2, (size_t)SMEM2, (cudaStream_t)stream, ta, tb, p);
 }

@@ -28,18 +28,19 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, residual: Optional[torch.Tensor] =
 
 
 def gemm_2sm(a: torch.Tensor, b: torch.Tensor, *, residual: Optional[torch.Tensor] = None, out_f32: bool = False,
-             out: Optional[torch.Tensor] = None, status_ptr: Optional[int] = None) -> torch.Tensor:
+             out: Optional[torch.Tensor] = None, status_ptr: Optional[int] = None, persistent: bool = False) -> torch.Tensor:
     """:func:`gemm` on CTA pairs: 256 x 256 tiles, ``tcgen05.mma.cta_group::2``, every CTA streams half of the tile's A rows and
-    half of its B rows. ``M`` and ``N`` must be multiples of 256."""
+    half of its B rows. ``M`` and ``N`` must be multiples of 256. ``persistent``: one pair per SM pair walks the tiles with two
+    accumulators in tensor memory (epilogue under the next tile's MMAs)."""
     M, K = a.shape
     N = b.shape[0]
     assert b.shape[1] == K and a.dtype == BF16 and b.dtype == BF16 and a.stride(1) == 1 and b.stride(1) == 1
     if out is None:
         out = torch.empty(M, N, dtype=torch.float32 if out_f32 else BF16, device=a.device)
-    check(_lib.load().ifab_gemm_bf16_2sm(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0),
-                                         int(out.dtype == torch.float32), None if residual is None else residual.data_ptr(),
-                                         0 if residual is None else residual.stride(0), M, N, K, status_ptr,
-                                         torch.cuda.current_stream().cuda_stream), "gemm_2sm")
+    fn = _lib.load().ifab_gemm_bf16_2sm_persistent if persistent else _lib.load().ifab_gemm_bf16_2sm
+    check(fn(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0),
+             int(out.dtype == torch.float32), None if residual is None else residual.data_ptr(),
+             0 if residual is None else residual.stride(0), M, N, K, status_ptr, torch.cuda.current_stream().cuda_stream), "gemm_2sm")
     return out
 
 

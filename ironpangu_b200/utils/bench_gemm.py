@@ -47,7 +47,7 @@ def main():
         a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
         b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
         c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-        t_ours = time_fn(lambda: gemm(a, b, out=c), flush)
+        t_ours = time_fn(lambda: gemm(a, b, out=c), flush)          # IFAB_GEMM_2SM=0 in the environment: the one-CTA kernel for every shape
         t_lib = time_fn(lambda: torch.matmul(a, b.T, out=c), flush)
         fl = 2.0 * M * N * K
         out.append({"shape": s, "ours_ms": round(t_ours, 4), "ours_tflops": round(fl / t_ours / 1e9, 1),
@@ -65,6 +65,13 @@ def main():
             if int(st[0]) == 0:
                 t2 = time_fn(lambda: gemm_2sm(a, b, out=c2), flush)
                 out[-1].update({"two_sm_ms": round(t2, 4), "two_sm_tflops": round(fl / t2 / 1e9, 1)})
+                c3 = torch.empty_like(c)
+                gemm_2sm(a, b, out=c3, status_ptr=st.data_ptr(), persistent=True)
+                torch.cuda.synchronize()
+                out[-1].update({"two_sm_persistent_status": int(st[0]), "two_sm_persistent_equals_one_cta": bool(torch.equal(c, c3))})
+                if int(st[0]) == 0:
+                    t3 = time_fn(lambda: gemm_2sm(a, b, out=c3, persistent=True), flush)
+                    out[-1].update({"two_sm_persistent_ms": round(t3, 4), "two_sm_persistent_tflops": round(fl / t3 / 1e9, 1)})
         if fab is not None:
             sym = fab.symmetric_empty((M, N))
             res = torch.randn(M, N, device="cuda").to(torch.bfloat16)

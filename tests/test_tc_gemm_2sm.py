@@ -1,4 +1,5 @@
-"""The CTA-pair tcgen05 GEMM (tcgen05.mma cta_group::2, 256 x 256 tiles) against a plain PyTorch fp32 product."""
+"""The CTA-pair tcgen05 GEMM (tcgen05.mma cta_group::2, 256 x 256 tiles) against a plain PyTorch fp32 product: one tile per
+pair, and the persistent form (several tiles per pair, two accumulators in tensor memory; 4096 x 5120 gives 320 tiles on 74 pairs)."""
 import pytest
 import torch
 
@@ -6,22 +7,23 @@ pytestmark = pytest.mark.gpu
 BF16 = torch.bfloat16
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (256, 512, 200), (512, 256, 1024), (1024, 768, 4096)])
-def test_two_sm_gemm_matches_fp32(M, N, K):
+@pytest.mark.parametrize("persistent", [False, True])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (256, 512, 200), (512, 256, 1024), (1024, 768, 4096), (4096, 5120, 512)])
+def test_two_sm_gemm_matches_fp32(M, N, K, persistent):
     from ironpangu_b200.ops.gemm import gemm, gemm_2sm
 
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     a = torch.randn(M, K, generator=g, device="cuda").to(BF16)
     b = torch.randn(N, K, generator=g, device="cuda").to(BF16)
     st = torch.zeros(1, dtype=torch.int32, device="cuda")
-    c = gemm_2sm(a, b, status_ptr=st.data_ptr())
+    c = gemm_2sm(a, b, status_ptr=st.data_ptr(), persistent=persistent)
     torch.cuda.synchronize()
     assert int(st[0]) == 0
     ref = a.float() @ b.float().T
     torch.testing.assert_close(c.float(), ref, rtol=2e-2, atol=2e-1)
     assert torch.equal(c, gemm(a, b))                              # same accumulation order as the one-CTA kernel
     res = torch.randn(M, N, generator=g, device="cuda").to(BF16)
-    cf = gemm_2sm(a, b, residual=res, out_f32=True, status_ptr=st.data_ptr())
+    cf = gemm_2sm(a, b, residual=res, out_f32=True, status_ptr=st.data_ptr(), persistent=persistent)
     torch.cuda.synchronize()
     assert int(st[0]) == 0
     torch.testing.assert_close(cf, ref.to(BF16).float() + res.float(), rtol=2e-2, atol=2e-1)
