@@ -210,6 +210,18 @@ __global__ void __launch_bounds__(192) tc_gemm_2sm_kernel(const __grid_constant_
 // (2 x 256 columns = all 512): while the epilogue warps of both CTAs drain tile j, the leader already issues the MMAs of tile
 // j + 1 into the other half, and the producers keep the stage ring full across tile boundaries. An accumulator half goes back
 // to the issuer when the eight epilogue warps of the pair (four per CTA) have arrived on the leader's acc_empty barrier.
+// Tile order of the persistent walk: groups of RASTER_M tile rows, inside a group the row index runs fastest. The 74 pairs
+// that work at the same time then share a few B tiles (each read by up to RASTER_M pairs back to back) and keep RASTER_M
+// tile rows of A in L2, instead of sweeping all of B for every tile row (at 8192^3 B alone is 128 MB - more than L2).
+constexpr int RASTER_M = 8;
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int* tm, int* tn) {
+  const int per_group = RASTER_M * tiles_n;
+  const int g = t / per_group, within = t - g * per_group;
+  const int first = g * RASTER_M, rows = min(RASTER_M, tiles_m - first);
+  *tm = first + within % rows;
+  *tn = within / rows;
+}
+
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
@@ -228,7 +240,7 @@ __global__ void __launch_bounds__(192) tc_gemm_2sm_persistent_kernel(const __gri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const int pair = (int)(blockIdx.x >> 1), pairs = (int)(gridDim.x >> 1);
-  const int tiles_n = p.N / TN, tiles = (p.M / (2 * BM)) * tiles_n;
+  const int tiles_n = p.N / TN, tiles_m = p.M / (2 * BM), tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) {
@@ -256,7 +268,9 @@ __global__ void __launch_bounds__(192) tc_gemm_2sm_persistent_kernel(const __gri
     // ---- producer (both CTAs): one ring across all tiles ----
     uint32_t it = 0;
     for (int t = pair; t < tiles && !*abort_flag; t += pairs) {
-      const int m0 = (t / tiles_n) * 2 * BM + (int)rank * BM, n0 = (t % tiles_n) * TN + (int)rank * HALF_N;
+      int tm, tn;
+      tile_coords(t, tiles_m, tiles_n, &tm, &tn);
+      const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * TN + (int)rank * HALF_N;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = (int)(it % STAGES2);
         const uint32_t round = it / STAGES2;
@@ -313,7 +327,9 @@ __global__ void __launch_bounds__(192) tc_gemm_2sm_persistent_kernel(const __gri
         if (lane == 0 && p.status) atomicOr(p.status, IFAB_STATUS_MBAR_TIMEOUT);
         break;
       }
-      const int m0 = (t / tiles_n) * 2 * BM + (int)rank * BM, n0 = (t % tiles_n) * TN;
+      int tm, tn;
+      tile_coords(t, tiles_m, tiles_n, &tm, &tn);
+      const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * TN;
       const int row = m0 + q * 32 + lane;
 #pragma unroll 1
       for (int c0 = 0; c0 < TN; c0 += 32) {
