@@ -238,8 +238,8 @@ def main():
         dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1,
                             expert_fp8=args.expert_fp8, kv_int8=args.kv_int8,
                             fused_moe=None if args.fused_moe < 0 else bool(args.fused_moe))
-        if args.expert_fp8 or args.kv_int8:
-            args.prefill = "decode"        # the quantised layouts prefill through the decode kernels
+        if args.kv_int8:
+            args.prefill = "decode"        # the int8 cache prefills through the decode kernels (fp8 experts are widened per layer)
     else:
         from baseline.nccl_cublas import NcclCublasDecoder
         dec = NcclCublasDecoder(cfg, weights, rank, world, max_tokens=8, max_context=max_context)

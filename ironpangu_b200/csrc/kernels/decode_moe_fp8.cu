@@ -10,6 +10,8 @@
 // Reference: W8A8 expert matrices of the 92B program (dequantising grouped matmul, native/src/token_executor.h:640-700).
 #include <cuda_fp8.h>
 
+#include <algorithm>
+
 #include "gemv.cuh"
 #include "ifab_kernels.h"
 #include "oneshot_ar.cuh"
@@ -75,6 +77,29 @@ __global__ void __launch_bounds__(256) quantize_fp8_block_kernel(const bf16* __r
   for (int i = 0; i < 4; ++i) {
     const int k = b * QBLOCK + lane * 4 + i;
     if (k < K) q[row * (long)K + k] = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(v[i], scale), __NV_SATFINITE, __NV_E4M3);
+  }
+}
+
+// ---- dequantiser: 16 values per thread (one 16-byte load, two 16-byte stores); K % 16 == 0 ------------------------------------------
+// out = bf16(fp8(q) * scale): the operand form of the tensor-core prompt path, which widens one layer's experts at a time
+__global__ void __launch_bounds__(256) dequantize_fp8_block_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scales, long rows, int K,
+                                                                   bf16* __restrict__ out) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int per_row = K / 16, nb = (K + QBLOCK - 1) / QBLOCK;
+  const long total = rows * per_row;
+  for (long item = (long)blockIdx.x * blockDim.x + threadIdx.x; item < total; item += (long)gridDim.x * blockDim.x) {
+    const long row = item / per_row;
+    const int c = (int)(item % per_row) * 16;
+    const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(q + row * (long)K + c));
+    const float sc = scales[row * nb + c / QBLOCK];
+    const uint8_t* b = reinterpret_cast<const uint8_t*>(&raw);
+    float f[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) f[i] = __half2float(__half(__nv_cvt_fp8_to_halfraw(b[i], __NV_E4M3))) * sc;
+    uint4* dst = reinterpret_cast<uint4*>(out + row * (long)K + c);
+    dst[0] = pack8(f);
+    dst[1] = pack8(f + 8);
   }
 }
 
@@ -402,6 +427,14 @@ extern "C" int ifab_quantize_fp8_block(const void* w, long ldw, long rows, int K
   const long items = rows * ((K + QBLOCK - 1) / QBLOCK);
   quantize_fp8_block_kernel<<<(unsigned)((items + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)w, ldw, rows, K, (uint8_t*)q, scales);
   return (int)cudaGetLastError();
+}
+
+// q: u8 [rows, K], scales: f32 [rows, ceil(K / 128)] -> out: bf16 [rows, K] (contiguous); K % 16 == 0
+extern "C" int ifab_dequantize_fp8_block(const void* q, const float* scales, long rows, int K, void* out, void* stream) {
+  if (rows < 1 || K < 16 || K % 16) return -1;
+  const long items = rows * (K / 16);
+  const unsigned blocks = (unsigned)std::min<long>((items + 255) / 256, 148L * 16);
+  return launch_chain(dequantize_fp8_block_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (const uint8_t*)q, scales, rows, K, (bf16*)out);
 }
 
 extern "C" int ifab_moe_gate_up_decode_fp8(const void* x, long ldx, const void* norm_w, float eps, const int32_t* ids, int T, int D, int F,

@@ -58,6 +58,18 @@ int ifab_gemv_bf16(const void* x, long ldx, const void* w, const void* norm_w, f
 int ifab_gemv_allreduce_bf16(const void* x, long ldx, const void* w, const void* residual, long ldr, void* y, long ldy,
                              void* y_f32, int T, int N, int K, const IfabFabric* fab, void* stream);
 
+/* ---- block-scaled fp8 (e4m3, one f32 scale per 1 x 128 block of a row) expert weights (decode_moe_fp8.cu) ---- */
+/* w: bf16 [rows, K] (row stride ldw) -> q: u8 [rows, K], scales: f32 [rows, ceil(K / 128)] */
+int ifab_quantize_fp8_block(const void* w, long ldw, long rows, int K, void* q, float* scales, void* stream);
+/* the inverse, rounded to bf16 -> out: bf16 [rows, K] contiguous; K % 16 == 0 (the prompt path widens one layer's experts at a time) */
+int ifab_dequantize_fp8_block(const void* q, const float* scales, long rows, int K, void* out, void* stream);
+int ifab_moe_gate_up_decode_fp8(const void* x, long ldx, const void* norm_w, float eps, const int32_t* ids, int T, int D, int F, int topk, int e0,
+                                int e_local, const void* w_gu, const float* s_gu, const void* w_shared_gu, const float* s_shared_gu, int Fs, void* act,
+                                void* stream);
+int ifab_moe_down_allreduce_decode_fp8(const void* act, const int32_t* ids, const float* wts, int T, int D, int F, int topk, int e0, int e_local,
+                                       const void* w_down, const float* s_down, const void* w_shared_down, const float* s_shared_down, int Fs,
+                                       const void* residual, long ldr, void* y, long ldy, const IfabFabric* fab, void* stream);
+
 /* ---- tensor-core GEMM (tcgen05 + TMEM + TMA): C[M,N] = A[M,K] * B[N,K]^T (+ residual) ---- */
 int ifab_gemm_bf16(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int out_f32, const void* residual,
                    long ldr, int M, int N, int K, uint32_t* status, void* stream);

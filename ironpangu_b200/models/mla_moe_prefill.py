@@ -71,6 +71,13 @@ class MlaMoePrefill:
             st[i, 1], st[i, 2] = i * 128, 128
         self.shared_tiles = st.to(dev)
         self.shared_ntiles = torch.zeros(1, dtype=torch.int32, device=dev)
+        # block-scaled fp8 experts: the tensor-core kernels take bf16 operands, so one layer's expert matrices are widened into
+        # this scratch right before the layer's grouped GEMMs (read 1 byte, write 2 per weight: a fraction of the GEMMs' time
+        # for chunks of a few hundred rows and up)
+        self.w8 = getattr(dec, "w8", None) if getattr(dec, "expert_fp8", False) else None
+        if self.w8 is not None:
+            self.wide = {"gate_up": e(el, 2 * c.expert_ffn, c.hidden), "down": e(el, c.hidden, c.expert_ffn),
+                         "shared_gate_up": e(2 * fs, c.hidden), "shared_down": e(c.hidden, fs)}
         self.parts = [fab.symmetric_empty((M, c.hidden), torch.float32) for _ in range(2)] if fab.world > 1 else None
         self._calls = 0
         # W_uk^T per head: [hl, latent, nope], the [N, K] operand of the absorb GEMM
@@ -192,9 +199,14 @@ class MlaMoePrefill:
                            scoring=c.scoring, scale=c.route_scale, xn=h)
             P.moe_dispatch(self.ids[:m], d.rank * d.el, d.el, self.route)
             P.moe_gather(h, self.route, self.xp)
-            P.grouped_gemm(self.xp, w[p + "gate_up"], self.route.tiles, self.route.num_tiles, self.act, swiglu=True, status_ptr=st)
-            P.grouped_gemm(self.act, w[p + "down"], self.route.tiles, self.route.num_tiles, self.y, status_ptr=st)
-            sgu, sdn = w[p + "shared_gate_up"], w[p + "shared_down"]
+            if self.w8 is not None:
+                ew = {name: K.dequantize_fp8_block(self.w8[p + name], out=buf) for name, buf in self.wide.items()}
+                n_launch += 4
+            else:
+                ew = {name: w[p + name] for name in ("gate_up", "down", "shared_gate_up", "shared_down")}
+            P.grouped_gemm(self.xp, ew["gate_up"], self.route.tiles, self.route.num_tiles, self.act, swiglu=True, status_ptr=st)
+            P.grouped_gemm(self.act, ew["down"], self.route.tiles, self.route.num_tiles, self.y, status_ptr=st)
+            sgu, sdn = ew["shared_gate_up"], ew["shared_down"]
             P.grouped_gemm(h, sgu.unsqueeze(0), self.shared_tiles, self.shared_ntiles, self.sact[:m], swiglu=True, status_ptr=st)
             G.gemm(self.sact[:m], sdn, out=self.sd[:m], status_ptr=st)
             if fab.world > 1:

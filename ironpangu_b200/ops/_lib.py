@@ -71,6 +71,7 @@ _SIGS = {
     "ifab_mla_head_decode_pf": [_P, c_long, _P, _P, c_float, c_float, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_float,
                                 c_int, c_int, c_int, c_int, c_int, _P, c_long, _P, _P, C.c_uint64, _P, C.c_uint64, _P, C.c_uint64, _P],
     "ifab_quantize_fp8_block": [_P, c_long, c_long, c_int, _P, _P, _P],
+    "ifab_dequantize_fp8_block": [_P, _P, c_long, c_int, _P, _P],
     "ifab_moe_gate_up_decode_fp8": [_P, c_long, _P, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P],
     "ifab_moe_down_allreduce_decode_fp8": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, c_long, _P,
                                            c_long, C.POINTER(IfabFabric), _P],

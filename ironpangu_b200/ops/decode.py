@@ -225,6 +225,18 @@ def quantize_fp8_block(w: torch.Tensor):
     return q, scales
 
 
+def dequantize_fp8_block(qs, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``bf16(fp8(q) * scale)`` of a ``(q, scales)`` pair from :func:`quantize_fp8_block`; ``out`` bf16 of ``q``'s shape."""
+    q, scales = qs
+    K = q.shape[-1]
+    rows = q.numel() // K
+    if out is None:
+        out = torch.empty(q.shape, dtype=BF16, device=q.device)
+    assert out.is_contiguous() and out.numel() == q.numel() and q.is_contiguous() and scales.is_contiguous()
+    check(_lib.load().ifab_dequantize_fp8_block(q.data_ptr(), scales.data_ptr(), rows, K, out.data_ptr(), _stream()), "dequantize_fp8_block")
+    return out
+
+
 def moe_gate_up_fp8(x: torch.Tensor, ids: torch.Tensor, w_gu, e0: int, *, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-5,
                     w_shared_gu=None, act: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``moe_gate_up`` over block-scaled fp8 weights: ``w_gu`` and ``w_shared_gu`` are ``(q, scales)`` pairs."""

@@ -532,8 +532,9 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
                             fused_head=ro.fused_head if ro is not None else None)
     mark("state", "KV cache, recurrent state and step workspace")
     prefill = None
-    if args.prefill_chunk > 8 and not args.kv_int8 and not args.expert_fp8:
-        # prompt chunks on the tensor cores (bf16 cache and bf16 experts; the quantised layouts prefill through the decode kernels)
+    if args.prefill_chunk > 8 and not args.kv_int8:
+        # prompt chunks on the tensor cores (bf16 cache; fp8 experts are widened one layer at a time; the int8 cache prefills through
+        # the decode kernels)
         from ironpangu_b200.models.mla_moe_prefill import MlaMoePrefill
 
         prefill = MlaMoePrefill(dec, max_rows=args.prefill_chunk)

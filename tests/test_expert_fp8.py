@@ -96,3 +96,49 @@ def test_model_over_fp8_experts_tracks_the_bf16_oracle():
         torch.testing.assert_close(dec.logits[:8], ref[s:s + 8], rtol=0.1, atol=0.15)
     assert fab.status() == 0
     fab.close()
+
+
+def test_dequantise_fp8_block_is_the_rounded_product():
+    from ironpangu_b200.ops import decode as K
+
+    for shape in ((7, 256), (3, 5, 192), (2, 4096)):
+        w = rnd(*shape, scale=0.05)
+        q, s = K.quantize_fp8_block(w)
+        got = K.dequantize_fp8_block((q, s))
+        assert got.shape == w.shape and got.dtype == BF16
+        assert torch.equal(got.float(), _dequant(q, s).to(BF16).float())
+
+
+def test_prompt_path_over_fp8_experts_matches_the_decode_kernels_over_the_same_weights():
+    """The tensor-core prompt executor widens one layer's fp8 experts at a time; its cache rows and first token agree with a
+    prompt run through the eight-row fp8 decode kernels on the same quantised weights."""
+    from ironpangu_b200.models.mla_moe import MlaMoeConfig, MlaMoeDecoder, random_full_weights, shard_weights
+    from ironpangu_b200.models.mla_moe_prefill import MlaMoePrefill
+    from ironpangu_b200.parallel.fabric import Fabric
+
+    cfg = MlaMoeConfig.tiny(2)
+    full = random_full_weights(cfg, seed=0)
+    fab = Fabric(0, 1)
+    mk = lambda: MlaMoeDecoder(cfg, shard_weights(cfg, full, 0, 1, "cuda"), fab, max_tokens=8, max_context=256, keep_logits=True, expert_fp8=True)
+    a, b = mk(), mk()
+    n = 150
+    toks = torch.randint(0, cfg.vocab, (n,), generator=torch.Generator().manual_seed(5)).to(torch.int32).cuda()
+    pre = MlaMoePrefill(a, max_rows=64)
+    assert pre.w8 is not None
+    for s in range(0, n, 64):
+        nxt = pre.forward(toks[s:s + 64], s, 0)
+    for s in range(0, n, 8):
+        m = min(8, n - s)
+        b.tokens[:m].copy_(toks[s:s + m])
+        b.positions[:m].copy_(torch.arange(s, s + m, dtype=torch.int32))
+        b.slots[:m].zero_()
+        b.forward(m)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(a.logits[0], b.logits[(n - 1) % 8], rtol=5e-2, atol=5e-2)
+    for l in range(cfg.layers):
+        torch.testing.assert_close(a.caches[l].float(), b.caches[l].float(), rtol=5e-2, atol=5e-2)
+    gap = b.logits[(n - 1) % 8].topk(2).values
+    if float(gap[0] - gap[1]) > 0.1:
+        assert int(nxt[0]) == int(b.logits[(n - 1) % 8].argmax())
+    assert fab.status() == 0
+    fab.close()
