@@ -238,8 +238,7 @@ def main():
         dec = MlaMoeDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1,
                             expert_fp8=args.expert_fp8, kv_int8=args.kv_int8,
                             fused_moe=None if args.fused_moe < 0 else bool(args.fused_moe))
-        if args.kv_int8:
-            args.prefill = "decode"        # the int8 cache prefills through the decode kernels (fp8 experts are widened per layer)
+        # fp8 experts are widened per layer for the prompt's GEMMs; over the int8 cache a prompt chunk attends in the latent form
     else:
         from baseline.nccl_cublas import NcclCublasDecoder
         dec = NcclCublasDecoder(cfg, weights, rank, world, max_tokens=8, max_context=max_context)

@@ -170,8 +170,12 @@ class MlaMoePrefill:
             # ---- attention ----
             K.rmsnorm(x, w[p + "attn_norm"], c.eps, out=h)
             qkv = G.gemm(h, w[p + "qkv_a"], out=self.qkv[:m], status_ptr=st)
-            K.mla_kv_write(qkv[:, c.q_lora:], w[p + "kv_a_norm"], pos, sl, d.page_table, d.caches[l], latent=c.kv_lora,
-                           rope=c.rope, eps=c.eps, theta=c.theta, status_ptr=st)
+            if d.kv_int8:
+                K.mla_kv_write_q8(qkv[:, c.q_lora:], w[p + "kv_a_norm"], pos, sl, d.page_table, d.caches[l], eps=c.eps, theta=c.theta,
+                                  status_ptr=st)
+            else:
+                K.mla_kv_write(qkv[:, c.q_lora:], w[p + "kv_a_norm"], pos, sl, d.page_table, d.caches[l], latent=c.kv_lora,
+                               rope=c.rope, eps=c.eps, theta=c.theta, status_ptr=st)
             K.rmsnorm(qkv[:, :c.q_lora], w[p + "q_a_norm"], c.eps, out=self.qn[:m])
             q = G.gemm(self.qn[:m], w[p + "q_b"], out=self.q[:m], status_ptr=st)
             q_lat, o_lat, attn = self.q_lat[:m], self.o_lat[:m], self.attn[:m]
@@ -234,7 +238,7 @@ class MlaMoePrefill:
         for q0 in range(0, m, self.QC):
             q1 = min(m, q0 + self.QC)
             P.mla_split(q_lat[q0:q1], d.caches[l], pos[q0:q1], sl[q0:q1], d.page_table, self.scratch, scale=c.scale,
-                        window=c.window, keys_per_split=d.kps, max_splits=d.max_splits, status_ptr=st)
+                        window=c.window, keys_per_split=d.kps, max_splits=d.max_splits, status_ptr=st, packed=d.kv_int8)
             P.mla_merge(self.scratch, pos[q0:q1], o_lat[q0:q1], window=c.window, keys_per_split=d.kps, max_splits=d.max_splits)
         kvb = w[p + "kv_b"]
         for hh in range(hl):

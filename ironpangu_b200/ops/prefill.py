@@ -95,13 +95,14 @@ def mla_q_rope(q: torch.Tensor, positions: torch.Tensor, q_lat: torch.Tensor, *,
 
 def mla_split(q_lat: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
               scratch: torch.Tensor, *, scale: float, window: int, keys_per_split: int, max_splits: int,
-              status_ptr: Optional[int] = None) -> None:
-    """Split-KV partials only (no value up-projection): ``scratch`` = f32 ``[T, H, max_splits, 514]``."""
+              status_ptr: Optional[int] = None, packed: bool = False) -> None:
+    """Split-KV partials only (no value up-projection): ``scratch`` = f32 ``[T, H, max_splits, 514]``. ``packed``: the cache holds
+    656-byte int8 rows (``uint8 [pages, page_tokens, 656]``)."""
     T, H, row = q_lat.shape
     num_pages, page_tokens, _ = cache.shape
     check(_lib.load().ifab_mla_decode_attention(
         q_lat.data_ptr(), cache.data_ptr(), positions.data_ptr(), slots.data_ptr(), page_table.data_ptr(), page_table.shape[1],
-        page_tokens, num_pages, None, 0, window, scale, T, H, 512, row - 512, keys_per_split, max_splits, scratch.data_ptr(),
+        page_tokens, num_pages, None, 0, window, scale, T, H, 512, -(row - 512) if packed else row - 512, keys_per_split, max_splits, scratch.data_ptr(),
         scratch.numel() * 4, None, 0, 0, None, 0, status_ptr, _s()), "mla_split")
 
 

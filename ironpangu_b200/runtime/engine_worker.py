@@ -532,9 +532,9 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
                             fused_head=ro.fused_head if ro is not None else None)
     mark("state", "KV cache, recurrent state and step workspace")
     prefill = None
-    if args.prefill_chunk > 8 and not args.kv_int8:
-        # prompt chunks on the tensor cores (bf16 cache; fp8 experts are widened one layer at a time; the int8 cache prefills through
-        # the decode kernels)
+    if args.prefill_chunk > 8:
+        # prompt chunks on the tensor cores (fp8 experts are widened one layer at a time; over the int8 cache the attention of a
+        # chunk runs in the latent form on the split-KV kernels, everything else as GEMMs)
         from ironpangu_b200.models.mla_moe_prefill import MlaMoePrefill
 
         prefill = MlaMoePrefill(dec, max_rows=args.prefill_chunk)
