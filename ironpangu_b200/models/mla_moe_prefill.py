@@ -76,6 +76,9 @@ class MlaMoePrefill:
         # for chunks of a few hundred rows and up)
         self.w8 = getattr(dec, "w8", None) if getattr(dec, "expert_fp8", False) else None
         if self.w8 is not None:
+            # widening every expert of a layer costs as much as streaming them twice: steps of a few dozen rows of many sequences
+            # are cheaper as passes of the eight-row fp8 decode kernels, which read the experts as they are
+            self.batch_threshold = 64
             self.wide = {"gate_up": e(el, 2 * c.expert_ffn, c.hidden), "down": e(el, c.hidden, c.expert_ffn),
                          "shared_gate_up": e(2 * fs, c.hidden), "shared_down": e(c.hidden, fs)}
         self.parts = [fab.symmetric_empty((M, c.hidden), torch.float32) for _ in range(2)] if fab.world > 1 else None
