@@ -74,7 +74,7 @@ int ifab_moe_down_allreduce_decode_fp8(const void* act, const int32_t* ids, cons
 int ifab_gemm_bf16(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int out_f32, const void* residual,
                    long ldr, int M, int N, int K, uint32_t* status, void* stream);
 
-/* the same on CTA pairs (tcgen05.mma cta_group::2, 256 x 256 tiles, each CTA loads half of A and half of B); M % 256 == 0, N % 256 == 0 */
+/* the same on CTA pairs (tcgen05.mma cta_group::2, 256 x 256 tiles, each CTA loads half of A and half of B); N % 32 == 0 */
 int ifab_gemm_bf16_2sm(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int out_f32, const void* residual,
                        long ldr, int M, int N, int K, uint32_t* status, void* stream);
 

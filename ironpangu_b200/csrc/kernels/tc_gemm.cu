@@ -157,10 +157,10 @@ static bool two_sm_enabled() {
 extern "C" int ifab_gemm_bf16(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int out_f32,
                               const void* residual, long ldr, int M, int N, int K, uint32_t* status, void* stream) {
   if (M < 1 || N < 1 || K < 8 || K % 8 || lda % 8 || ldb % 8) return -1;
-  // whole 256 x 256 tiles: CTA pairs (tcgen05.mma cta_group::2; same accumulation order, same bits) - persistent with two
+  // from 256 x 256 up: CTA pairs (tcgen05.mma cta_group::2; same accumulation order, same bits) - persistent with two
   // accumulators when there is more than one tile per SM pair, one tile per pair otherwise
-  if (M % 256 == 0 && N % 256 == 0 && two_sm_enabled()) {
-    const long tiles = (long)(M / 256) * (N / 256);
+  if (M >= 256 && N >= 256 && N % 32 == 0 && two_sm_enabled()) {
+    const long tiles = (long)((M + 255) / 256) * ((N + 255) / 256);
     return tiles > 74 ? ifab_gemm_bf16_2sm_persistent(a, lda, b, ldb, c, ldc, out_f32, residual, ldr, M, N, K, status, stream)
                       : ifab_gemm_bf16_2sm(a, lda, b, ldb, c, ldc, out_f32, residual, ldr, M, N, K, status, stream);
   }

@@ -12,7 +12,8 @@
 //   warps 2-5 (both)     epilogue of this CTA's 128 rows: tcgen05.ld, convert, residual, store
 // Six stages of 32 KB. No TMA load is multicast: every CTA fetches its own tiles. Every mbarrier wait is bounded; a wait that
 // runs out raises the CTA's abort flag and a status bit, and both CTAs still meet at the closing cluster barrier.
-// Shapes: M and N multiples of 256 (other shapes take the one-CTA kernel), K % 8 == 0 (K tail by TMA zero fill).
+// Shapes: N % 32 == 0 (rows are stored 32 columns at a time), K % 8 == 0; M, N and K tails by TMA zero fill and masked stores.
+// `ifab_gemm_bf16` uses these kernels from 256 rows and 256 columns up; below that a pair's 256 x 256 tile is mostly padding.
 #include <algorithm>
 
 #include "tc_gemm_core.cuh"
@@ -240,7 +241,7 @@ __global__ void __launch_bounds__(192) tc_gemm_2sm_persistent_kernel(const __gri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const int pair = (int)(blockIdx.x >> 1), pairs = (int)(gridDim.x >> 1);
-  const int tiles_n = p.N / TN, tiles_m = p.M / (2 * BM), tiles = tiles_m * tiles_n;
+  const int tiles_n = (p.N + TN - 1) / TN, tiles_m = (p.M + 2 * BM - 1) / (2 * BM), tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) {
@@ -354,23 +355,23 @@ __global__ void __launch_bounds__(192) tc_gemm_2sm_persistent_kernel(const __gri
 
 }  // namespace
 
-// C[M,N] = A[M,K] * B[N,K]^T (+ residual) with CTA pairs on 256 x 256 tiles. M % 256 == 0, N % 256 == 0, K % 8 == 0.
+// C[M,N] = A[M,K] * B[N,K]^T (+ residual) with CTA pairs on 256 x 256 tiles. N % 32 == 0, K % 8 == 0.
 extern "C" int ifab_gemm_bf16_2sm(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int out_f32, const void* residual, long ldr,
                                   int M, int N, int K, uint32_t* status, void* stream) {
-  if (M < 256 || N < 256 || M % 256 || N % 256 || K < 8 || K % 8 || lda % 8 || ldb % 8) return -1;
+  if (M < 1 || N < 32 || N % 32 || K < 8 || K % 8 || lda % 8 || ldb % 8) return -1;
   CUtensorMap ta, tb;
   if (int rc = make_tmap_bf16_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return rc;
   if (int rc = make_tmap_bf16_2d(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, HALF_N)) return rc;
   Gemm2Params p{c, ldc, out_f32, (const bf16*)residual, ldr, M, N, K, status, 4000000u};
   if (int rc = opt_in_smem(tc_gemm_2sm_kernel, SMEM2)) return rc;
-  dim3 grid(2 * (M / 256), N / 256);
+  dim3 grid(2 * ((M + 255) / 256), (N + 255) / 256);
   return launch_chain_cluster(tc_gemm_2sm_kernel, grid, dim3(192), 2, (size_t)SMEM2, (cudaStream_t)stream, ta, tb, p);
 }
 
 // The same with a persistent grid (one CTA pair per SM pair) and two accumulators in tensor memory.
 extern "C" int ifab_gemm_bf16_2sm_persistent(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int out_f32, const void* residual,
                                              long ldr, int M, int N, int K, uint32_t* status, void* stream) {
-  if (M < 256 || N < 256 || M % 256 || N % 256 || K < 8 || K % 8 || lda % 8 || ldb % 8) return -1;
+  if (M < 1 || N < 32 || N % 32 || K < 8 || K % 8 || lda % 8 || ldb % 8) return -1;
   CUtensorMap ta, tb;
   if (int rc = make_tmap_bf16_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return rc;
   if (int rc = make_tmap_bf16_2d(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, HALF_N)) return rc;
@@ -379,7 +380,7 @@ extern "C" int ifab_gemm_bf16_2sm_persistent(const void* a, long lda, const void
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int tiles = (M / 256) * (N / 256);
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
   const int pairs = std::max(1, std::min(tiles, sms / 2));
   return launch_chain_cluster(tc_gemm_2sm_persistent_kernel, dim3(2 * pairs), dim3(192), 2, (size_t)SMEM2, (cudaStream_t)stream, ta, tb, p);
 }

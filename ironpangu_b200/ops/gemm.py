@@ -30,7 +30,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, residual: Optional[torch.Tensor] =
 def gemm_2sm(a: torch.Tensor, b: torch.Tensor, *, residual: Optional[torch.Tensor] = None, out_f32: bool = False,
              out: Optional[torch.Tensor] = None, status_ptr: Optional[int] = None, persistent: bool = False) -> torch.Tensor:
     """:func:`gemm` on CTA pairs: 256 x 256 tiles, ``tcgen05.mma.cta_group::2``, every CTA streams half of the tile's A rows and
-    half of its B rows. ``M`` and ``N`` must be multiples of 256. ``persistent``: one pair per SM pair walks the tiles with two
+    half of its B rows. ``N`` must be a multiple of 32; tails in M, N and K are zero-filled on load and masked on store. ``persistent``: one pair per SM pair walks the tiles with two
     accumulators in tensor memory (epilogue under the next tile's MMAs)."""
     M, K = a.shape
     N = b.shape[0]

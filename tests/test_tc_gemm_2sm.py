@@ -8,7 +8,7 @@ BF16 = torch.bfloat16
 
 
 @pytest.mark.parametrize("persistent", [False, True])
-@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (256, 512, 200), (512, 256, 1024), (1024, 768, 4096), (4096, 5120, 512)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (256, 512, 200), (512, 256, 1024), (1024, 768, 4096), (4096, 5120, 512), (300, 2112, 520), (513, 288, 64), (1000, 4128, 1536)])
 def test_two_sm_gemm_matches_fp32(M, N, K, persistent):
     from ironpangu_b200.ops.gemm import gemm, gemm_2sm
 
@@ -33,6 +33,6 @@ def test_two_sm_gemm_refuses_other_shapes():
     from ironpangu_b200.ops.gemm import gemm_2sm
 
     a = torch.zeros(128, 64, dtype=BF16, device="cuda")
-    b = torch.zeros(256, 64, dtype=BF16, device="cuda")
+    b = torch.zeros(250, 64, dtype=BF16, device="cuda")          # N must be a multiple of 32
     with pytest.raises(RuntimeError):
         gemm_2sm(a, b)
