@@ -1,4 +1,5 @@
 // Unit tests of the host runtime services (no device needed). Exit code 0 = all passed.
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <filesystem>
@@ -6,6 +7,8 @@
 #include <functional>
 #include <iostream>
 
+#include "bundle.h"
+#include "interp.h"
 #include "chat_parse.h"
 #include "contract.h"
 #include "cpu_plan.h"
@@ -514,6 +517,102 @@ static void test_contract_validator() {
   { init::Plan b = plans[0]; b.loads[0].dest = 100000; CHECK_THROWS(Invalid, contract::validate_bindings(p, b)); }
 }
 
+// ---- a hyper-connected program: residual streams mixed by mHC modules, token convolutions, attention sinks ----------------
+static const char* kHyperSource = R"SRC(language inferfabric 1;
+module Attn(x, w) {
+    let qkv = linear(x, weight = w.qa, paired_weight = w.kva, width = 128, paired_width = 576, placement = "replicated");
+    let qc = mome(slice(qkv, start = 0, width = 128), weight = w.q_conv, taps = 3);
+    let q = linear(norm(qc, weight = w.q_norm, eps = 1e-5), weight = w.qb, width = 384, placement = "tp_rows");
+    let kc = mome(slice(qkv, start = 128, width = 512), weight = w.kv_conv, taps = 3);
+    let kr = slice(qkv, start = 640, width = 64);
+    let sinks = sink_normalize(weight = w, norm = w.kv_norm, count = 3, latent = 512, rope = 64, eps = 1e-5);
+    let cache = cache_norm_rope_append(kc, kr, sinks, weight = w.kv_norm, eps = 1e-5, theta = 10000);
+    let query = mla_query(q, weight = w.kvb, theta = 10000, heads = 2, nope = 128, rope = 64, latent = 512, value = 128, input_layout = "rank_local");
+    let att = latent_attention(query, cache, scale_dim = 192, window = 0, selection = "all_causal_within_window");
+    let value = mla_value(att, weight = w.kvb, heads = 2, latent = 512, value = 128, nope = 128);
+    let out = allreduce(linear(mome(value, weight = w.o_conv, taps = 3, placement = "tp_channels"), weight = w.o, width = 64, placement = "tp_columns"));
+    yield out;
+}
+model Hyper {
+    context = 32;
+    eos = 2;
+    let w = weights("m");
+    let streams = repeat(embedding(weight = w.embed, width = 64, vocab = 96), count = 4);
+    let hc = mhc_pre(streams, weight = w.mhc, streams = 4, sinkhorn = 20, eps = 1e-6);
+    let branch = Attn(norm(mhc_input(hc), weight = w.in_norm, eps = 1e-5), w.attn);
+    let mixed = mhc_post(hc, norm(branch, weight = w.out_norm, eps = 1e-5));
+    let passed = optional_norm(mixed, weight = w.block_norm, eps = 1e-5);
+    let merged = mhc_input(mhc_merge(passed, weight = w.merge, streams = 4, sinkhorn = 20, eps = 1e-6));
+    let logits = gather(linear(norm(merged, weight = w.final_norm, eps = 1e-5), weight = weights("head"), width = 96, placement = "tp_rows"));
+    yield logits;
+}
+plan P for Hyper { target = b200_token_v1; tp = 1; ep = 1; devices = [0]; max_num_seqs = 1; max_num_batched_tokens = 1; max_model_len = 32; }
+)SRC";
+
+static void test_hyper_connected_program() {
+  graph::Graph g = graph::compile_source(kHyperSource);
+  program::Program p = program::lower(g);
+  auto find = [&](const char* op) -> size_t {
+    for (size_t i = 0; i < p.instructions.size(); ++i) if (p.instructions[i].op == op) return i;
+    return p.instructions.size();
+  };
+  // the checkpoint must hold the mixing tensors (f32, no ".weight" suffix), the taps of every convolution and the sink rows
+  auto need = init::required_tensors(p);
+  CHECK(need.count("m.mhc.phi") && need.at("m.mhc.phi").second == (std::vector<uint64_t>{24, 256}) && need.at("m.mhc.phi").first == init::DType::F32);
+  CHECK(need.count("m.mhc.gamma") && need.count("m.mhc.alpha") && need.count("m.merge.beta") && need.at("m.merge.beta").second == (std::vector<uint64_t>{24}));
+  CHECK(need.count("m.attn.q_conv.weight") && need.at("m.attn.q_conv.weight").second == (std::vector<uint64_t>{128, 1, 3}));
+  CHECK(need.count("m.attn.o_conv.weight") && need.at("m.attn.o_conv.weight").second == (std::vector<uint64_t>{256, 1, 3}));
+  CHECK(need.count("m.attn.param_sink_compressed_kv") && need.at("m.attn.param_sink_k_pe").second == (std::vector<uint64_t>{3, 64}));
+  CHECK(!need.count("m.block_norm.weight"));                           // optional
+  init::Checkpoint ck = init::Checkpoint::synthetic(need);
+  std::vector<init::Plan> plans = init::plan_all(p, ck);
+  const init::Parameter* taps = nullptr;
+  for (auto& prm : plans.at(0).parameters) if (prm.name == "m.attn.kv_conv") taps = &prm;
+  CHECK(taps && taps->dims == (std::vector<uint64_t>{512, 3}) && taps->dtype == init::DType::F32);   // [channels, 1, taps] loads as [channels, taps]
+  contract::validate_kernels(p);
+  contract::validate_bindings(p, plans[0]);
+  { init::Plan b = plans[0];                                           // a mixing tensor the rank does not load
+    for (size_t k = 0; k < b.parameters.size(); ++k) if (b.parameters[k].name == "m.mhc.phi") b.parameters[k].name = "m.mhc.psi";
+    CHECK_THROWS(Invalid, contract::validate_bindings(p, b)); }
+  { program::Program q = p;                                            // sink rows must come from a sink_normalize
+    q.instructions[find("mla_kv_write")].inputs[2] = q.instructions[find("mla_kv_write")].inputs[0];
+    CHECK_THROWS(Invalid, contract::validate_kernels(q)); }
+  // lowering: the branch norm is folded into the return of the hyper-connection, which also names the streams it mixes
+  const program::Instruction& post = p.instructions[find("mhc_post")];
+  CHECK(post.inputs.size() == 3 && post.attr("norm_weight") && *post.attr("norm_weight") == "m.out_norm");
+  CHECK(p.instructions[post.inputs[0]].op == "mhc_pre" && p.instructions[post.inputs[0]].inputs[0] == post.inputs[2]);
+  size_t norms = 0;
+  for (auto& i : p.instructions) norms += i.op == "norm";
+  CHECK(norms == 0);
+  // arena: an optional norm that passes its rows through gets no slot and keeps its source alive as long as it is read
+  const uint32_t opt = (uint32_t)find("optional_norm");
+  bundle::Arena plain = bundle::plan_arena(p, 8), aliased = bundle::plan_arena(p, 8, {opt});
+  auto slot_of = [](const bundle::Arena& a, uint32_t ins) -> const bundle::ArenaSlot* {
+    for (auto& sl : a.slots) if (sl.instruction == ins) return &sl;
+    return nullptr;
+  };
+  CHECK(slot_of(plain, opt) != nullptr && slot_of(aliased, opt) == nullptr);
+  const uint32_t src = p.instructions[opt].inputs[0];
+  uint32_t last_reader = 0;
+  for (uint32_t k = 0; k < p.instructions.size(); ++k)
+    for (uint32_t in : p.instructions[k].inputs) if (in == opt) last_reader = k;
+  CHECK(slot_of(aliased, src) && slot_of(aliased, src)->last >= last_reader && slot_of(plain, src)->last == opt);
+  aliased.verify();
+  // the oracle runs it: finite logits, and the convolution history makes a repeated token see a different past
+  interp::Weights w = interp::Weights::random(need, 7);
+  interp::Interpreter it(g, w);
+  std::vector<float> l0, l2;
+  it.step(5, 0, &l0);
+  it.step(5, 1, nullptr);
+  it.step(5, 2, &l2);
+  bool finite = l0.size() == 96, differs = false;
+  for (size_t i = 0; i < l0.size(); ++i) {
+    finite = finite && std::isfinite(l0[i]) && std::isfinite(l2[i]);
+    differs = differs || std::fabs(l0[i] - l2[i]) > 1e-4f;
+  }
+  CHECK(finite && differs);
+}
+
 // ---- chat post-processing: reasoning sections and tool calls ---------------------------------------------------------
 static void test_chat_parsers() {
   using namespace ifab::chat;
@@ -772,7 +871,8 @@ int main() {
       {"api_tokenizer", test_api_tokenizer_and_sampling_json}, {"kernel_plugin", test_kernel_plugin_loader},
       {"state_pool", test_state_pool}, {"prefix_index", test_prefix_index}, {"paging", test_paging},
       {"rankplan_runtime", test_rankplan_and_runtime}, {"transfer", test_transfer}, {"scheduler", test_scheduler}, {"cpu_plan", test_cpu_plan},
-      {"contract_validator", test_contract_validator}, {"chat_parsers", test_chat_parsers}};
+      {"contract_validator", test_contract_validator}, {"hyper_connected_program", test_hyper_connected_program},
+      {"chat_parsers", test_chat_parsers}};
   for (auto& t : tests) {
     int before = failures;
     try {
