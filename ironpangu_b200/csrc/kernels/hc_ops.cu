@@ -92,13 +92,21 @@ __global__ void __launch_bounds__(256) mhc_logits_kernel(const bf16* X, const fl
       const float4* p4 = reinterpret_cast<const float4*>(pj);
       const float4* g4 = reinterpret_cast<const float4*>(gamma);
       const uint2* x4 = reinterpret_cast<const uint2*>(Xt);
-      for (long c = threadIdx.x; c < total / 4; c += blockDim.x) {
-        const float4 a = p4[c], g = g4[c];
-        const uint2 xr = x4[c];
+      auto dot4 = [](const float4& a, const float4& g, const uint2& xr) {
         const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xr.x));
         const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xr.y));
-        s += a.x * g.x * x01.x + a.y * g.y * x01.y + a.z * g.z * x23.x + a.w * g.w * x23.y;
+        return a.x * g.x * x01.x + a.y * g.y * x01.y + a.z * g.z * x23.x + a.w * g.w * x23.y;
+      };
+      // four independent chunks per trip: twelve 8 / 16-byte loads in flight per thread
+      const long n4 = total / 4, step = blockDim.x;
+      long c = threadIdx.x;
+      for (; c + 3 * step < n4; c += 4 * step) {
+        const float4 a0 = p4[c], a1 = p4[c + step], a2 = p4[c + 2 * step], a3 = p4[c + 3 * step];
+        const float4 g0 = g4[c], g1 = g4[c + step], g2 = g4[c + 2 * step], g3 = g4[c + 3 * step];
+        const uint2 x0 = x4[c], x1 = x4[c + step], x2 = x4[c + 2 * step], x3 = x4[c + 3 * step];
+        s += dot4(a0, g0, x0) + dot4(a1, g1, x1) + dot4(a2, g2, x2) + dot4(a3, g3, x3);
       }
+      for (; c < n4; c += step) s += dot4(p4[c], g4[c], x4[c]);
     } else {
       for (long c = threadIdx.x; c < total; c += blockDim.x) s += pj[c] * gamma[c] * __bfloat162float(Xt[c]);
     }
