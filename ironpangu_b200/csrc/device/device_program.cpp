@@ -149,6 +149,14 @@ struct DeviceProgram::Impl {
   char *gqa_qkv = nullptr, *kv_pack = nullptr;                  // [rows, q | k | v] of a step; [rows, k | v] for an append outside a group
   long gqa_ld = 0, kv_pack_ld = 0;
   std::vector<void*> owned;                                     // packed operands and pack buffers
+  // hyper-connected programs: mixing weights of a hyper-connection live behind its mixed row in the instruction's slot; token
+  // convolutions keep the previous taps-1 rows per resident; sink rows are computed once from the parameters
+  struct HcAux { float* post; float* comb; int S; };
+  std::map<uint32_t, HcAux> hc_of;
+  std::map<uint32_t, std::pair<void*, uint64_t>> conv_state;    // instruction -> (state, bytes)
+  std::map<uint32_t, std::pair<const void*, int>> sink_rows;    // sink_normalize instruction -> (rows, count)
+  std::map<uint32_t, std::pair<const void*, int>> sinks_of;     // cache-write instruction -> the sink rows its readers also attend to
+  std::set<uint32_t> aliased;                                   // instructions that hand a value on without a launch
   // control block (device): tokens | positions | slots | next ids | next values, page table; pinned mirror on the host
   int32_t *d_tokens = nullptr, *d_positions = nullptr, *d_slots = nullptr, *d_next = nullptr, *d_page_table = nullptr;
   float* d_next_vals = nullptr;
@@ -167,6 +175,7 @@ struct DeviceProgram::Impl {
     for (auto& g : graphs) cudaGraphExecDestroy(g.second);
     for (auto& c : cache_of) cudaFree(c.second);
     for (void* o : owned) cudaFree(o);
+    for (auto& c : conv_state) cudaFree(c.second.first);
     if (block) cudaFree(block);
     if (fabric_block) cudaFree(fabric_block);
     if (d_page_table) cudaFree(d_page_table);
@@ -315,6 +324,41 @@ void DeviceProgram::Impl::load(const std::string& bundle, const std::string& che
       dmalloc(&pages, bytes, "KV pages");
       cu(cudaMemset(pages, 0, bytes), "KV clear");
       cache_of[k] = pages;
+    } else if (x.op == "mhc_pre" || x.op == "mhc_merge") {
+      const int S = x.i("streams");
+      if (S + S * S > 64) fail(ErrorKind::NotImplemented, "device program: a hyper-connection slot holds at most 64 mixing weights per row");
+      val[k] = lease(k, (uint64_t)T * x.width * 2 + (uint64_t)T * 64 * 4, x.width, 2);     // mixed rows | post weights | stream-to-stream weights
+      float* post = (float*)(val[k].ptr + (uint64_t)T * x.width * 2);
+      hc_of[k] = HcAux{post, post + (uint64_t)T * S, S};
+    } else if (x.op == "mhc_input") {
+      val[k] = val[x.in.at(0)];                            // the mixed row of its hyper-connection
+      aliased.insert(k);
+    } else if (x.op == "optional_norm" && !slot_of.count(k)) {
+      // compiled against a checkpoint without this gain: the rows pass through, the arena kept the source's slot alive
+      if (P_optional(x.s("weight"))) invalid("device program: the bundle was compiled without " + x.s("weight") + ", the checkpoint has it");
+      val[k] = val[x.in.at(0)];
+      aliased.insert(k);
+    } else if (x.op == "mome") {
+      const uint64_t bytes = (uint64_t)residents * (x.i("taps") - 1) * x.width * 2;
+      void* st = nullptr;
+      dmalloc(&st, bytes, "convolution history");
+      cu(cudaMemset(st, 0, bytes), "convolution history clear");
+      conv_state[k] = {st, bytes};
+      val[k] = lease(k, (uint64_t)T * x.width * 2, x.width, 2);
+    } else if (x.op == "sink_normalize") {
+      const int count = x.i("count"), lat = x.i("latent"), rope = x.i("rope");
+      void* rows_ptr = nullptr;
+      dmalloc(&rows_ptr, (uint64_t)count * (lat + rope) * 2, "sink rows");
+      owned.push_back(rows_ptr);
+      kernel(ifab_rmsnorm_bf16(P(x.s("weight") + ".param_sink_compressed_kv"), lat, P(x.s("norm")), rows_ptr, lat + rope, count, lat, x.f("eps", 1e-5f), 0, stream),
+             x.name);
+      cu(cudaMemcpy2DAsync((char*)rows_ptr + (size_t)lat * 2, (size_t)(lat + rope) * 2, P(x.s("weight") + ".param_sink_k_pe"), (size_t)rope * 2, (size_t)rope * 2,
+                           count, cudaMemcpyDeviceToDevice, stream),
+         "sink rows");
+      cu(cudaStreamSynchronize(stream), "sink rows");
+      sink_rows[k] = {rows_ptr, count};
+      val[k] = Val{(char*)rows_ptr, lat + rope, 2};
+      aliased.insert(k);
     } else if (x.op == "kv_cache_append") {
       // key pages, then value pages: [pages, page_tokens, local kv heads, head_dim] each
       if (x.has("cache_dtype") && x.s("cache_dtype") != "bf16") fail(ErrorKind::NotImplemented, "device program: K / V pages are bf16");
@@ -441,7 +485,7 @@ void DeviceProgram::Impl::dispatch(int T) {
   auto V = [&](uint32_t k) -> const Val& { return val[k]; };
   for (uint32_t k = 0; k < ins.size(); ++k) {
     const Ins& x = ins[k];
-    if (x.op == "view") continue;
+    if (x.op == "view" || aliased.count(k)) continue;
     if (head && head_members.count(k)) continue;
     if (gqa_members.count(k)) continue;
     const void* norm_w = x.has("norm_weight") ? (x.has("norm_optional") ? P_optional(x.s("norm_weight")) : P(x.s("norm_weight"))) : nullptr;
@@ -473,6 +517,48 @@ void DeviceProgram::Impl::dispatch(int T) {
       kernel(ifab_gqa_decode_attention(gqa_qkv, gqa_ld, kv, vpages, d_positions, d_slots, d_page_table, max_pages, page_tokens, num_pages, x.f("scale", 1.f), T, H,
                                        KVH, hd, kps, max_splits, (float*)workspace(scratch), scratch, V(k).ptr, V(k).ld, status, st),
              x.name);
+    } else if (x.op == "repeat") {
+      const Val& in = V(x.in.at(0));
+      const int n = x.i("count"), w = (int)ins[x.in[0]].width;
+      for (int c = 0; c < n; ++c)
+        cu(cudaMemcpy2DAsync(V(k).ptr + (size_t)c * w * 2, (size_t)V(k).ld * 2, in.ptr, (size_t)in.ld * 2, (size_t)w * 2, T, cudaMemcpyDeviceToDevice,
+                             (cudaStream_t)st),
+           "repeat");
+      count += n - 1;
+    } else if (x.op == "optional_norm") {
+      const Val& in = V(x.in.at(0));
+      const void* g = P_optional(x.s("weight"));
+      if (g) kernel(ifab_rmsnorm_bf16(in.ptr, in.ld, g, V(k).ptr, V(k).ld, T, (int)x.width, x.f("eps", 1e-5f), 0, st), x.name);
+      else cu(cudaMemcpy2DAsync(V(k).ptr, (size_t)V(k).ld * 2, in.ptr, (size_t)in.ld * 2, (size_t)x.width * 2, T, cudaMemcpyDeviceToDevice, (cudaStream_t)st), "pass-through");
+    } else if (x.op == "mhc_pre" || x.op == "mhc_merge") {
+      const HcAux& h = hc_of.at(k);
+      const Val& in = V(x.in.at(0));
+      const std::string b = x.s("weight");
+      if (in.ld != (long)ins[x.in[0]].width) fail(ErrorKind::NotImplemented, "device program: the streams of a hyper-connection must be whole rows");
+      kernel(ifab_mhc_pre_ticketed(in.ptr, (const float*)P(b + ".phi"), (const float*)P(b + ".gamma"), (const float*)P(b + ".alpha"), (const float*)P(b + ".beta"),
+                                   V(k).ptr, h.post, h.comb, T, h.S, (int)x.width, x.i("sinkhorn"), x.f("eps", 1e-6f), ticket + 8, st),
+             x.name);
+    } else if (x.op == "mhc_post") {
+      const HcAux& h = hc_of.at(x.in.at(0));
+      const Val &br = V(x.in.at(1)), &X = V(x.in.at(2));
+      const int W = (int)x.width / h.S;
+      if (norm_w)
+        kernel(ifab_mhc_post_norm(X.ptr, br.ptr, br.ld, norm_w, eps, h.post, h.comb, V(k).ptr, T, h.S, W, st), x.name);
+      else
+        kernel(ifab_mhc_post(X.ptr, br.ptr, br.ld, h.post, h.comb, V(k).ptr, T, h.S, W, st), x.name);
+    } else if (x.op == "mome") {
+      const Val& in = V(x.in.at(0));
+      kernel(ifab_mome(in.ptr, in.ld, (const float*)P(x.s("weight")), conv_state.at(k).first, d_positions, d_slots, V(k).ptr, V(k).ld, T, (int)x.width, x.i("taps"), 0,
+                       st),
+             x.name);
+    } else if (x.op == "swiglu") {
+      if (x.in.size() == 2) {
+        const Val &g = V(x.in[0]), &u = V(x.in[1]);
+        kernel(ifab_swiglu_pair(g.ptr, g.ld, u.ptr, u.ld, V(k).ptr, V(k).ld, T, (int)x.width, st), x.name);
+      } else {
+        const Val& gu = V(x.in.at(0));
+        kernel(ifab_swiglu_pair(gu.ptr, gu.ld, gu.ptr + (size_t)x.width * 2, gu.ld, V(k).ptr, V(k).ld, T, (int)x.width, st), x.name);
+      }
     } else if (x.op == "rotary_prefix") {
       const Val& in = V(x.in.at(0));
       kernel(ifab_rope_prefix(in.ptr, in.ld, d_positions, V(k).ptr, V(k).ld, T, x.i("heads"), x.i("head_dim"), x.i("rotary_dim"), x.f("theta", 10000.f), st), x.name);
@@ -525,10 +611,16 @@ void DeviceProgram::Impl::dispatch(int T) {
     } else if (x.op == "mla_kv_write") {
       const Val &lat = V(x.in.at(0)), &kr = V(x.in.at(1));
       const int latent = (int)ins[x.in[0]].width, rope = (int)ins[x.in[1]].width;
-      if (kr.ptr != lat.ptr + (long)latent * 2 || kr.ld != lat.ld) fail(ErrorKind::NotImplemented, "device program: latent and rotary columns must be adjacent slices of one projection");
-      kernel(ifab_mla_kv_write(lat.ptr, lat.ld, P(x.s("weight")), x.f("eps", 1e-5f), x.f("theta", 10000.f), d_positions, d_slots, d_page_table, max_pages,
-                               page_tokens, cache_of.at(k), num_pages, T, latent, rope, status, st),
-             x.name);
+      if (x.in.size() > 2) sinks_of[k] = sink_rows.at(x.in[2]);
+      if (kr.ptr != lat.ptr + (long)latent * 2 || kr.ld != lat.ld)
+        // e.g. a convolved latent and the raw rotary columns of the projection: the kernel reads them where they are
+        kernel(ifab_mla_kv_write_split(lat.ptr, lat.ld, kr.ptr, kr.ld, P(x.s("weight")), x.f("eps", 1e-5f), x.f("theta", 10000.f), d_positions, d_slots,
+                                       d_page_table, max_pages, page_tokens, cache_of.at(k), num_pages, T, latent, rope, status, st),
+               x.name);
+      else
+        kernel(ifab_mla_kv_write(lat.ptr, lat.ld, P(x.s("weight")), x.f("eps", 1e-5f), x.f("theta", 10000.f), d_positions, d_slots, d_page_table, max_pages,
+                                 page_tokens, cache_of.at(k), num_pages, T, latent, rope, status, st),
+               x.name);
     } else if (x.op == "mla_q_absorb") {
       const Val& q = V(x.in.at(0));
       const int nope = x.i("nope"), vdim = x.has("value") ? x.i("value") : nope;
@@ -539,8 +631,10 @@ void DeviceProgram::Impl::dispatch(int T) {
       const int H = x.i("heads"), latent = x.i("latent"), vdim = x.i("value"), nope = x.has("nope") ? x.i("nope") : vdim;
       const uint64_t scratch = (uint64_t)T * H * max_splits * (latent + 2) * 4;
       ++count;                                                         // split + merge
-      kernel(ifab_mla_decode_attention(V(x.in.at(0)).ptr, cache_of.at(x.in.at(1)), d_positions, d_slots, d_page_table, max_pages, page_tokens, num_pages, nullptr,
-                                       0, x.i("window"), 1.f / std::sqrt((float)x.i("scale_dim")), T, H, latent, 64, kps, max_splits,
+      auto sk = sinks_of.find(x.in.at(1));
+      kernel(ifab_mla_decode_attention(V(x.in.at(0)).ptr, cache_of.at(x.in.at(1)), d_positions, d_slots, d_page_table, max_pages, page_tokens, num_pages,
+                                       sk == sinks_of.end() ? nullptr : sk->second.first, sk == sinks_of.end() ? 0 : sk->second.second, x.i("window"),
+                                       1.f / std::sqrt((float)x.i("scale_dim")), T, H, latent, 64, kps, max_splits,
                                        (float*)workspace(scratch), scratch, P(x.s("weight")), nope, vdim, V(k).ptr, V(k).ld, status, st),
              x.name);
     } else if (x.op == "router_topk") {
@@ -653,6 +747,7 @@ void DeviceProgram::run_rows(const int32_t* tokens, const int32_t* positions, co
   p_->step(tokens, positions, slots, rows, next_tokens);
 }
 void DeviceProgram::reset() {
+  for (auto& c : p_->conv_state) cu(cudaMemset(c.second.first, 0, c.second.second), "convolution history clear");
   for (auto& c : p_->cache_of) {
     const Ins& x = p_->ins[c.first];
     cu(cudaMemset(c.second, 0, (uint64_t)p_->num_pages * p_->page_tokens * x.width * 2), "KV clear");

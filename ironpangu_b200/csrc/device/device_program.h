@@ -6,8 +6,9 @@
 //                     compiler's offset inside ONE device block (the frozen arena + workspace, fingerprint and row count checked),
 //                     keeps the latent KV pages per resident sequence slot beside it, dispatches instructions to the kernel
 //                     library's C entry points - the group {q_b linear, cache write, absorb, attention} as the one-launch
-//                     cluster-per-head kernel for steps of one or two rows and short contexts - and replays one CUDA graph per
-//                     step width after the first eager run of that width
+//                     cluster-per-head kernel for steps of one or two rows and short contexts, the grouped-query group as a packed
+//                     projection + rotate-and-append + attention, hyper-connections / token convolutions / sink rows of the
+//                     hyper-connected programs - and replays one CUDA graph per step width after the first eager run of that width
 //   make_device_program_engine
 //                     the same executor as a server engine (`ifab-server --program BUNDLE CHECKPOINT --gpus 1`): packed steps
 //                     of prompt slices and decode rows in launch groups of up to eight rows, greedy tokens

@@ -207,3 +207,72 @@ def test_dense_bundle_runs_natively_like_the_plan_engine(tmp_path):
     audit = json.loads(buf.value)
     assert audit["device_allocations_after_ready"] == 0 and audit["launches_per_step"] == 1 + cfg.layers * 7 + 1
     assert lib.ifab_device_program_close(h) == 0
+
+
+def test_hyper_connected_bundle_runs_natively_like_the_plan_engine(tmp_path):
+    """Residual streams mixed by mHC modules, token convolutions with per-resident history, sink rows, a folded branch norm and
+    an optional norm the checkpoint lacks: the native executor gives the plan engine's tokens row for row, and the CPU
+    interpreter's wherever its logits are decisive; the two residents keep separate histories."""
+    import sys
+
+    sys.path.insert(0, str(ROOT / "tests"))
+    from hyper_source import source
+
+    from ironpangu_b200 import _build, compiler
+    from ironpangu_b200.parallel.fabric import Fabric
+    from ironpangu_b200.runtime.plan_engine import PlanEngine
+
+    src, ck, bundle = tmp_path / "hyper.inferfabric", tmp_path / "ck", tmp_path / "bundle"
+    src.write_text(source(layers=2))
+    assert compiler.cli("synth-checkpoint", str(src), str(ck), "--seed", "7").returncode == 0
+    r = compiler.cli("compile-token", str(src), str(ck), str(bundle), "--resident-sequences", "2", "--prefill-tokens", "8")
+    assert r.returncode == 0, r.stderr
+    lib = C.CDLL(str(_build.build_device()))
+    lib.ifab_device_program_error.restype = C.c_char_p
+    h = C.c_void_p()
+    assert lib.ifab_device_program_open(str(bundle).encode(), str(ck).encode(), 0, 2, C.byref(h)) == 0, lib.ifab_device_program_error()
+
+    def run(tokens, positions, slots):
+        n = len(tokens)
+        arr = lambda v: (C.c_int32 * n)(*v)
+        out = (C.c_int32 * n)()
+        assert lib.ifab_device_program_rows(h, arr(tokens), arr(positions), arr(slots), n, out) == 0, lib.ifab_device_program_error()
+        return list(out)
+
+    seq = torch.randint(1, 512, (21,), generator=torch.Generator().manual_seed(4)).tolist()
+    other = torch.randint(1, 512, (9,), generator=torch.Generator().manual_seed(5)).tolist()
+    ref = torch.tensor(compiler.interpret(src.read_text(), str(ck), seq, all_logits=True)["prompt_logits"])
+    got = run(seq[:8], list(range(8)), [0] * 8)
+    run(other[:8], list(range(8)), [1] * 8)                        # another resident in between: its history and pages are its own
+    got += run(seq[8:16], list(range(8, 16)), [0] * 8)
+    got += [run([seq[i]], [i], [0])[0] for i in range(16, 21)]     # single rows: a graph per width
+    decisive = 0
+    for i, t in enumerate(got):
+        top2 = ref[i].topk(2).values
+        if float(top2[0] - top2[1]) > 2e-2:
+            decisive += 1
+            assert t == int(ref[i].argmax()), (i, t)
+    assert decisive >= len(seq) // 2
+    fab = Fabric(0, 1)
+    eng = PlanEngine(str(bundle), str(ck), fab, max_tokens=8, num_slots=2)
+    same = []
+    for s in (0, 8):
+        eng.tokens[:8].copy_(torch.tensor(seq[s:s + 8], dtype=torch.int32))
+        eng.positions[:8].copy_(torch.arange(s, s + 8, dtype=torch.int32))
+        eng.slots[:8].zero_()
+        eng.forward(8)
+        same += eng.next_ids[:8].tolist()
+    for i in range(16, 21):
+        eng.tokens[:1].fill_(seq[i])
+        eng.positions[:1].fill_(i)
+        eng.slots[:1].zero_()
+        eng.forward(1)
+        same.append(int(eng.next_ids[0]))
+    assert got == same
+    fab.close()
+    assert lib.ifab_device_program_reset(h) == 0
+    assert run(seq[:8], list(range(8)), [0] * 8) == got[:8]       # after a reset the histories are empty again
+    buf = C.create_string_buffer(1 << 16)
+    assert lib.ifab_device_program_audit(h, buf, len(buf)) == 0
+    assert json.loads(buf.value)["device_allocations_after_ready"] == 0
+    assert lib.ifab_device_program_close(h) == 0
