@@ -217,7 +217,7 @@ def main():
         if args.impl != "native":
             raise SystemExit("--model dense2b runs on the native path only")
         dec = G.DenseDecoder(cfg, weights, fab, max_tokens=8, max_context=max_context, num_slots=1)
-    elif args.impl == "native" and args.executor == "bundle" and not (args.expert_fp8 or args.kv_int8):
+    elif args.impl == "native" and args.executor == "bundle" and not args.expert_fp8:
         # compile the model's source for this tensor-parallel width and run the bundle's program: the dispatcher of the plan
         # engine picks the kernels, the activations live in the bundle's frozen arena, the weights are the tensors above
         import tempfile
@@ -228,7 +228,7 @@ def main():
         work = tempfile.mkdtemp(prefix=f"ifab-bench-r{rank}-")
         src = os.path.join(work, "model.inferfabric")
         with open(src, "w") as f:
-            f.write(mla_moe_source(cfg, world, context=max_context))
+            f.write(mla_moe_source(cfg, world, context=max_context, kv_int8=args.kv_int8))      # packed int8 cache: declared in the source
         compiled = compiler.write_bundle(src, os.path.join(work, "bundle"), prefill_tokens=8)
         dec = PlanEngine(compiled["dir"], None, fab, max_tokens=8, num_slots=1, parameters=bundle_parameters(cfg, weights),
                          fused_moe=None if args.fused_moe < 0 else bool(args.fused_moe),

@@ -13,9 +13,14 @@ def _num(x: float) -> str:
     return repr(int(x)) if float(x) == int(x) else repr(float(x))
 
 
-def mla_moe_source(cfg, tp: int, context: int = 1024, name: str = "MlaMoe") -> str:
-    """DSL source of the multi-head-latent-attention + routed-experts decoder ``cfg`` (``models.mla_moe.MlaMoeConfig``)."""
+_PACKED_CACHE = ', cache_dtype = int8_ds_mla, cache_scale_dtype = f32, cache_quantization = pertile128, cache_rope_dtype = bf16'
+
+
+def mla_moe_source(cfg, tp: int, context: int = 1024, name: str = "MlaMoe", kv_int8: bool = False) -> str:
+    """DSL source of the multi-head-latent-attention + routed-experts decoder ``cfg`` (``models.mla_moe.MlaMoeConfig``).
+    ``kv_int8``: every layer keeps its latent cache as packed int8 rows (one f32 scale per 128 columns, rotary columns in bf16)."""
     c = cfg
+    packed = _PACKED_CACHE if kv_int8 else ""
     if c.heads % tp or c.experts % tp or c.vocab % tp or c.shared_ffn % tp:
         raise ValueError(f"tp={tp} does not divide heads / experts / vocab / shared width of the model")
     qw, lat, theta, eps = c.q_lora, c.kv_lora, _num(c.theta), repr(c.eps)
@@ -35,7 +40,7 @@ module MLAAttention(x, w, window) {{
 
     let latent = slice(qkv, start = {qw}, width = {lat});
     let kr = slice(qkv, start = {qw + lat}, width = {c.rope});
-    let cache = cache_norm_rope_append(latent, kr, weight = w.kv_a_layernorm, eps = {eps}, theta = {theta});
+    let cache = cache_norm_rope_append(latent, kr, weight = w.kv_a_layernorm, eps = {eps}, theta = {theta}{packed});
 
     let query = mla_query(q, weight = w.kv_b_proj, theta = {theta}, heads = {c.heads}, nope = {c.nope}, rope = {c.rope},
                           latent = {lat}, value = {c.vdim}, input_layout = "rank_local");
@@ -200,6 +205,7 @@ class HyperMlaMoeConfig:
     route_scale: float = 2.5
     scoring: str = "sigmoid_bias_group_topk"
     eos: int = 2
+    packed_every: int = 0          # > 0: layers whose index is a multiple of it keep a packed int8 latent cache (the long-window layers at 3)
 
     @staticmethod
     def pangu92b() -> "HyperMlaMoeConfig":
@@ -225,6 +231,7 @@ def hyper_mla_moe_source(cfg: HyperMlaMoeConfig, tp: int, context: int = 512, na
     qw, lat, theta, eps = c.q_lora, c.kv_lora, _num(c.theta), repr(c.eps)
     H, S = c.hidden, c.streams
     mhc = f"streams = {S}, sinkhorn = {c.sinkhorn}, eps = 1e-6"
+    packed_expr = f"eq(mod(index, {c.packed_every}), 0)" if c.packed_every > 0 else "lt(index, 0)"
     devices = ", ".join(str(i) for i in range(tp))
     return f"""language inferfabric 1;
 
@@ -232,14 +239,16 @@ def hyper_mla_moe_source(cfg: HyperMlaMoeConfig, tp: int, context: int = 512, na
 // MLA: {c.heads} heads, q_lora {qw}, kv_lora {lat}, nope {c.nope}, rope {c.rope}, v {c.vdim}, {c.sinks} sink rows, token convolutions of {c.taps} taps;
 // MoE: {c.experts} routed experts (FFN {c.expert_ffn}), top-{c.topk} {c.scoring}, shared expert (FFN {c.shared_ffn}); tp = ep = {tp}.
 
-module Attention(x, w, window) {{
+module Attention(x, w, window, packed) {{
     let qkv = linear(x, weight = w.q_a_proj, paired_weight = w.kv_a_proj_with_mqa, width = {qw}, paired_width = {lat + c.rope}, placement = "replicated");
     let qc = mome(slice(qkv, start = 0, width = {qw}), weight = w.qa_conv, taps = {c.taps});
     let q = linear(norm(qc, weight = w.q_a_layernorm, eps = {eps}), weight = w.q_b_proj, width = div({c.heads * c.qk_dim}, {tp}), placement = "tp_rows");
     let kc = mome(slice(qkv, start = {qw}, width = {lat}), weight = w.compresskv_conv, taps = {c.taps});
     let kr = slice(qkv, start = {qw + lat}, width = {c.rope});
     let sinks = sink_normalize(weight = w, norm = w.kv_a_layernorm, count = {c.sinks}, latent = {lat}, rope = {c.rope}, eps = {eps});
-    let cache = cache_norm_rope_append(kc, kr, sinks, weight = w.kv_a_layernorm, eps = {eps}, theta = {theta});
+    let cache = choose(packed,
+        cache_norm_rope_append(kc, kr, sinks, weight = w.kv_a_layernorm, eps = {eps}, theta = {theta}{_PACKED_CACHE}),
+        cache_norm_rope_append(kc, kr, sinks, weight = w.kv_a_layernorm, eps = {eps}, theta = {theta}));
     let query = mla_query(q, weight = w.kv_b_proj, theta = {theta}, heads = {c.heads}, nope = {c.nope}, rope = {c.rope}, latent = {lat},
                           value = {c.vdim}, input_layout = "rank_local");
     let attended = latent_attention(query, cache, scale_dim = {c.qk_dim}, window = window, selection = "all_causal_within_window");
@@ -271,7 +280,7 @@ module RoutedMoE(x, w) {{
 
 module Block(x, w, index, window) {{
     let attn_hc = mhc_pre(x, weight = w.attn_mhc_module, {mhc});
-    let attention = Attention(norm(mhc_input(attn_hc), weight = w.input_layernorm, eps = {eps}), w.self_attn, window);
+    let attention = Attention(norm(mhc_input(attn_hc), weight = w.input_layernorm, eps = {eps}), w.self_attn, window, {packed_expr});
     let residual = mhc_post(attn_hc, norm(attention, weight = w.post_attention_layernorm, eps = {eps}));
     let ffn_hc = mhc_pre(residual, weight = w.mlp_mhc_module, {mhc});
     let ffn_in = norm(mhc_input(ffn_hc), weight = w.pre_mlp_layernorm, eps = {eps});

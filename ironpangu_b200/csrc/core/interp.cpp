@@ -535,6 +535,21 @@ void Interpreter::run_node(uint32_t idx, uint32_t token, uint32_t position) {
       std::vector<float> lat = rmsnorm(as_bf16(in(0), 0), W("weight"), (float)n.num_attr("eps"), false);
       std::vector<float> kr = as_bf16(in(1), 0);
       rope_inplace(kr.data(), (uint32_t)kr.size(), position, (float)n.num_attr("theta"));
+      if (n.has("cache_dtype") && n.need("cache_dtype") == "int8_ds_mla") {
+        // packed int8 latent: one f32 scale per tile of 128 columns (max|v| / 127, 1 for an all-zero tile), values rounded half
+        // away from zero and clamped to +-127; the rotary columns stay bf16. The row holds what attention will read back.
+        for (size_t t0 = 0; t0 < lat.size(); t0 += 128) {
+          const size_t t1 = std::min(lat.size(), t0 + 128);
+          float amax = 0.f;
+          for (size_t i = t0; i < t1; ++i) amax = std::max(amax, std::fabs(lat[i]));
+          const float scale = amax > 0.f ? amax / 127.f : 1.f;
+          for (size_t i = t0; i < t1; ++i) {
+            const float q = lat[i] / scale;
+            const int r = (int)(q >= 0.f ? q + 0.5f : q - 0.5f);
+            lat[i] = (float)std::max(-127, std::min(127, r)) * scale;
+          }
+        }
+      }
       row = lat;
       row.insert(row.end(), kr.begin(), kr.end());
       if (n.inputs.size() == 3 && c.sinks.empty()) {

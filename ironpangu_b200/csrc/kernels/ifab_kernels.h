@@ -259,6 +259,9 @@ int ifab_sparse_index(const void* q, const float* w, const void* keys, const int
 int ifab_mla_kv_write_q8(const void* kv, long ldkv, const void* norm_w, float eps, float theta, const int32_t* positions,
                          const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens, void* cache,
                          int num_pages, int T, uint32_t* status, void* stream);
+int ifab_mla_kv_write_q8_split(const void* latent_rows, long ldl, const void* rope_rows, long ldr, const void* norm_w, float eps, float theta,
+                               const int32_t* positions, const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens,
+                               void* cache, int num_pages, int T, uint32_t* status, void* stream);
 int ifab_kv_dequantize_q8(const void* cache, void* out /* bf16 [rows, 576] */, long rows, void* stream);
 /* symmetric int8, ties away from zero; group_cols = K: per-row scale, 128: per-tile scales [T, ceil(K/128)] */
 int ifab_quantize_int8(const void* x, long ldx, void* q, long ldq, float* scales, long lds, int T, int K, int group_cols,

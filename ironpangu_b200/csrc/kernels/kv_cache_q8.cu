@@ -30,7 +30,8 @@ __device__ __forceinline__ int quant_round(float v, float scale) {
 }
 
 // 128 threads; thread i owns latent columns [4i, 4i+4); a 128-column tile is one warp
-__global__ void __launch_bounds__(128) mla_kv_write_q8_kernel(const bf16* kv, long ldkv, const bf16* norm_w, float eps, float theta,
+// `kr` (optional): the rotary columns when they do not follow the latent columns in `kv`
+__global__ void __launch_bounds__(128) mla_kv_write_q8_kernel(const bf16* kv, long ldkv, const bf16* kr, long ldkr, const bf16* norm_w, float eps, float theta,
                                                               const int32_t* positions, const int32_t* slots, const int32_t* page_table,
                                                               int max_pages, int page_tokens, unsigned char* cache, int num_pages,
                                                               uint32_t* status) {
@@ -76,7 +77,8 @@ __global__ void __launch_bounds__(128) mla_kv_write_q8_kernel(const bf16* kv, lo
   if (tid < half) {
     float c, s;
     rope_cos_sin(pos, tid, ROPE, theta, &c, &s);
-    const float a = __bfloat162float(src[LATENT + tid]), b = __bfloat162float(src[LATENT + tid + half]);
+    const bf16* rs = kr ? kr + (long)t * ldkr : src + LATENT;
+    const float a = __bfloat162float(rs[tid]), b = __bfloat162float(rs[tid + half]);
     bf16* rp = reinterpret_cast<bf16*>(dst + LATENT);
     rp[tid] = __float2bfloat16_rn(a * c - b * s);
     rp[tid + half] = __float2bfloat16_rn(b * c + a * s);
@@ -122,8 +124,17 @@ extern "C" int ifab_mla_kv_write_q8(const void* kv, long ldkv, const void* norm_
                                     const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens, void* cache,
                                     int num_pages, int T, uint32_t* status, void* stream) {
   if (T < 1 || ldkv % 2) return -1;
-  return launch_chain(mla_kv_write_q8_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream, (const bf16*)kv, ldkv, (const bf16*)norm_w, eps,
-                      theta, positions, slots, page_table, max_pages, page_tokens, (unsigned char*)cache, num_pages, status);
+  return launch_chain(mla_kv_write_q8_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream, (const bf16*)kv, ldkv, (const bf16*)nullptr, 0L,
+                      (const bf16*)norm_w, eps, theta, positions, slots, page_table, max_pages, page_tokens, (unsigned char*)cache, num_pages, status);
+}
+
+// the same with the rotary columns in rows of their own (latent_rows [T, >= 512], rope_rows [T, >= 64])
+extern "C" int ifab_mla_kv_write_q8_split(const void* latent_rows, long ldl, const void* rope_rows, long ldr, const void* norm_w, float eps, float theta,
+                                          const int32_t* positions, const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens,
+                                          void* cache, int num_pages, int T, uint32_t* status, void* stream) {
+  if (T < 1 || ldl % 2 || !rope_rows) return -1;
+  return launch_chain(mla_kv_write_q8_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream, (const bf16*)latent_rows, ldl, (const bf16*)rope_rows, ldr,
+                      (const bf16*)norm_w, eps, theta, positions, slots, page_table, max_pages, page_tokens, (unsigned char*)cache, num_pages, status);
 }
 
 extern "C" int ifab_kv_dequantize_q8(const void* cache, void* out, long rows, void* stream) {

@@ -106,6 +106,7 @@ _SIGS = {
     "ifab_delta_rule_decode": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "ifab_sparse_index": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],
     "ifab_mla_kv_write_q8": [_P, c_long, _P, c_float, c_float, _P, _P, _P, c_int, c_int, _P, c_int, c_int, _P, _P],
+    "ifab_mla_kv_write_q8_split": [_P, c_long, _P, c_long, _P, c_float, c_float, _P, _P, _P, c_int, c_int, _P, c_int, c_int, _P, _P],
     "ifab_kv_dequantize_q8": [_P, _P, c_long, _P],
     "ifab_quantize_int8": [_P, c_long, _P, c_long, _P, c_long, c_int, c_int, c_int, _P],
     "ifab_grouped_gemm_bf16": [_P, c_long, c_int, _P, c_int, c_int, c_int, _P, _P, c_int, _P, c_long, c_int, _P, _P],

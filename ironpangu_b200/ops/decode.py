@@ -327,6 +327,17 @@ def mla_kv_write_q8(kv: torch.Tensor, norm_w: torch.Tensor, positions: torch.Ten
                                            num_pages, T, status_ptr, _stream()), "mla_kv_write_q8")
 
 
+def mla_kv_write_q8_split(latent_rows: torch.Tensor, rope_rows: torch.Tensor, norm_w: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                          page_table: torch.Tensor, cache: torch.Tensor, *, eps: float, theta: float, status_ptr: Optional[int] = None) -> None:
+    """:func:`mla_kv_write_q8` for latent and rotary columns that live in different rows."""
+    T = latent_rows.shape[0]
+    num_pages, page_tokens, row = cache.shape
+    assert cache.dtype == torch.uint8 and row == 656 and latent_rows.shape[1] == 512 and rope_rows.shape[1] == 64
+    check(_lib.load().ifab_mla_kv_write_q8_split(latent_rows.data_ptr(), _rows(latent_rows), rope_rows.data_ptr(), _rows(rope_rows), norm_w.data_ptr(),
+                                                 eps, theta, positions.data_ptr(), slots.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+                                                 page_tokens, cache.data_ptr(), num_pages, T, status_ptr, _stream()), "mla_kv_write_q8_split")
+
+
 def kv_dequantize_q8(cache: torch.Tensor) -> torch.Tensor:
     """Packed int8 cache -> bf16 ``[pages, page_tokens, 576]`` (test utility)."""
     num_pages, page_tokens, _ = cache.shape

@@ -508,9 +508,10 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
         cfg.layers = args.layers
     weights = random_rank_weights(cfg, rank, world, dev, seed=args.seed)
     mark("weights")
-    if args.executor == "bundle" and not (args.kv_int8 or args.expert_fp8):
+    if args.executor == "bundle" and not args.expert_fp8:
         # the model's .inferfabric source, compiled for this job's width; the plan engine's dispatcher picks the kernels, the
-        # activations live in the bundle's frozen arena (the quantised layouts are not in the language yet: hand-wired class)
+        # activations live in the bundle's frozen arena (a packed int8 cache is declared in the source; fp8 expert storage is not
+        # in the language: hand-wired class)
         import tempfile
 
         from ironpangu_b200 import compiler
@@ -521,7 +522,7 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
         work = tempfile.mkdtemp(prefix=f"ifab-worker-r{rank}-")
         src = os.path.join(work, "model.inferfabric")
         with open(src, "w") as f:
-            f.write(mla_moe_source(cfg, world, context=args.max_model_len))
+            f.write(mla_moe_source(cfg, world, context=args.max_model_len, kv_int8=args.kv_int8))
         compiled = compiler.write_bundle(src, os.path.join(work, "bundle"), prefill_tokens=8)
         dec = PlanEngine(compiled["dir"], None, fab, max_tokens=8, num_slots=args.max_num_seqs, keep_logits=not args.greedy_only,
                          parameters=bundle_parameters(cfg, weights), fused_head=ro.fused_head if ro is not None else None)

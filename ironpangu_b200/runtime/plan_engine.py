@@ -288,6 +288,7 @@ class PlanEngine:
         self._index_scores = None
         self._cache_of: Dict[int, torch.Tensor] = {}     # cache-write instruction -> its pages
         self.caches: List[torch.Tensor] = []              # the same tensors in program order (one per attention layer)
+        self._packed: set = set()                         # cache-write instructions whose pages hold packed int8 rows
         self._kv_of: Dict[int, tuple] = {}                # K / V append instruction -> (key pages, value pages)
         self._kv_pack = None                              # [k | v] rows of a step, for an append outside the fused group
         self._conv_state: Dict[int, torch.Tensor] = {}    # token-convolution instruction -> the previous taps-1 rows per sequence slot
@@ -365,7 +366,7 @@ class PlanEngine:
                                        "q_norm": qb["attrs"]["norm_weight"], "kv_norm": ins[kw]["attrs"]["weight"], "w_qb": qb["attrs"]["weight"],
                                        "w_kvb": a["weight"], "eps": float(qb["attrs"].get("norm_eps", 1e-5)), "theta": float(aa["theta"]),
                                        "scale": 1.0 / math.sqrt(float(a["scale_dim"])), "window": int(a["window"]), "cache": kw,
-                                       "ok": private and shapes_ok and aa["weight"] == a["weight"]}
+                                       "ok": private and shapes_ok and aa["weight"] == a["weight"] and ins[kw]["dtype"] == "bf16"}
             elif i["op"] == "moe_down_allreduce" and len(i["inputs"]) > 2:
                 kgu, kr, kres = i["inputs"][:3]
                 if ins[kgu]["op"] != "moe_gate_up" or ins[kr]["op"] != "router_topk":
@@ -460,7 +461,7 @@ class PlanEngine:
         configuration record and the parameters by role. The prompt executor (``models/mla_moe_prefill.py``) and the batch
         engine read a decoder through these attributes, so they run on a bundle's engine as they do on ``MlaMoeDecoder``.
         Left undefined (``cfg is None``) for programs that are not a stack of {latent attention, routed experts} layers."""
-        self.cfg, self.w, self.kv_int8 = None, {}, False
+        self.cfg, self.w, self.kv_int8 = None, {}, bool(self._packed) and len(self._packed) == len(self._cache_of)
         ins = self.ins
         heads, moes = sorted(self.head_groups), sorted(self.moe_groups)
         emb = next((i for i in ins if i["op"] == "embedding"), None)
@@ -571,7 +572,16 @@ class PlanEngine:
             if op == "optional_norm" and k in self._pass_through:
                 continue                                                   # no slot of its own is touched
             if op == "mla_kv_write":
-                self._cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
+                if i["dtype"] == "int8_ds_mla":
+                    # packed rows: 512 int8 latent values, 64 bf16 rotary values, four f32 tile scales
+                    if w != 576:
+                        raise NotImplementedError("the packed int8 cache holds 512 latent + 64 rotary columns")
+                    self._cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, 656, dtype=torch.uint8, device=dev)
+                    self._packed.add(k)
+                elif i["dtype"] != "bf16":
+                    raise NotImplementedError(f"cache dtype {i['dtype']} has no device layout")
+                else:
+                    self._cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
                 self.caches.append(self._cache_of[k])
             elif op in ("mhc_pre", "mhc_merge"):
                 S = int(i["attrs"]["streams"])
@@ -746,10 +756,15 @@ class PlanEngine:
                 V[k] = k
                 if kr.data_ptr() != lat.data_ptr() + lat.shape[1] * 2 or kr.stride(0) != lat.stride(0):
                     # e.g. a convolved latent and the raw rope columns of the projection: the kernel reads them where they are
-                    K.mla_kv_write_split(lat, kr, self._param(a["weight"]), pos, slot, self.page_table, self._cache_of[k], eps=float(a["eps"]),
-                                         theta=float(a["theta"]), status_ptr=st)
+                    write = K.mla_kv_write_q8_split if k in self._packed else K.mla_kv_write_split
+                    write(lat, kr, self._param(a["weight"]), pos, slot, self.page_table, self._cache_of[k], eps=float(a["eps"]),
+                          theta=float(a["theta"]), status_ptr=st)
                     continue
                 kv = torch.as_strided(lat, (T, lat.shape[1] + kr.shape[1]), (lat.stride(0), 1))
+                if k in self._packed:
+                    K.mla_kv_write_q8(kv, self._param(a["weight"]), pos, slot, self.page_table, self._cache_of[k], eps=float(a["eps"]),
+                                      theta=float(a["theta"]), status_ptr=st)
+                    continue
                 K.mla_kv_write(kv, self._param(a["weight"]), pos, slot, self.page_table, self._cache_of[k], latent=lat.shape[1],
                                rope=kr.shape[1], eps=float(a["eps"]), theta=float(a["theta"]), status_ptr=st)
                 V[k] = k
@@ -825,7 +840,7 @@ class PlanEngine:
                                        scale=1.0 / math.sqrt(float(a["scale_dim"])), window=int(a["window"]),
                                        keys_per_split=self.kps, max_splits=self.max_splits, scratch=self.scratch,
                                        out=val(k), status_ptr=st, indices=val(ins[2]) if len(ins) > 2 else None,
-                                       sinks=self._sinks_of.get(V[ins[1]]))
+                                       sinks=self._sinks_of.get(V[ins[1]]), packed=V[ins[1]] in self._packed)
             elif op == "router_topk":
                 ids, wts, logits = V[k]
                 # when the expert kernels read the same rows under the same norm, the router leaves the normalised rows in the

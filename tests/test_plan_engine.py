@@ -285,3 +285,70 @@ def test_generated_hyper_mla_moe_program_matches_the_interpreter(tmp_path):
     assert same_routes >= len(toks) * 0.8, same_routes
     assert fab.status() == 0
     fab.close()
+
+
+@pytest.mark.gpu
+def test_packed_int8_caches_in_compiled_programs(tmp_path):
+    """`cache_dtype = int8_ds_mla` in the source: the plan engine keeps 656-byte packed rows, writes them with per-128 scales and
+    attends over them; the CPU oracle simulates the same quantisation. Once for the latent-attention + routed-experts family
+    (every layer packed; equal to the hand-wired decoder with an int8 cache), once for the hyper-connected family with a
+    packed cache on every second layer (convolved latent: the split cache write)."""
+    import dataclasses
+
+    from ironpangu_b200 import compiler
+    from ironpangu_b200.compiler.sources import HyperMlaMoeConfig, hyper_mla_moe_source, mla_moe_source
+    from ironpangu_b200.models.mla_moe import MlaMoeConfig, MlaMoeDecoder, bundle_parameters, random_rank_weights
+    from ironpangu_b200.parallel.fabric import Fabric
+    from ironpangu_b200.runtime.plan_engine import PlanEngine
+
+    fab = Fabric(0, 1)
+    dev = torch.device("cuda", 0)
+    # ---- latent attention + routed experts, every layer packed ----
+    cfg = dataclasses.replace(MlaMoeConfig.tiny(2), eos=2)
+    src = tmp_path / "a.inferfabric"
+    src.write_text(mla_moe_source(cfg, 1, context=128, kv_int8=True))
+    out = compiler.write_bundle(str(src), str(tmp_path / "a"), prefill_tokens=8)
+    W = random_rank_weights(cfg, 0, 1, dev, seed=0)
+    eng = PlanEngine(out["dir"], None, fab, max_tokens=8, keep_logits=True, parameters=bundle_parameters(cfg, W))
+    assert eng.kv_int8 and all(c.dtype == torch.uint8 and c.shape[-1] == 656 for c in eng.caches) and not eng.fused_head
+    ref = MlaMoeDecoder(cfg, W, fab, max_tokens=8, max_context=128, keep_logits=True, kv_int8=True)
+    toks = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(8)).to(torch.int32)
+    for s in range(0, 24, 8):
+        for d in (eng, ref):
+            d.tokens[:8].copy_(toks[s:s + 8])
+            d.positions[:8].copy_(torch.arange(s, s + 8, dtype=torch.int32))
+            d.slots[:8].zero_()
+            d.forward(8)
+        torch.cuda.synchronize()
+        assert torch.equal(eng.logits[:8], ref.logits[:8]) and torch.equal(eng.next_ids[:8], ref.next_ids[:8])
+    for a, b in zip(eng.caches, ref.caches):
+        assert torch.equal(a, b)
+    # ---- hyper-connected family, packed cache on layers 0 and 2 ----
+    hc = dataclasses.replace(HyperMlaMoeConfig.tiny(3), packed_every=2)
+    hsrc, ck = tmp_path / "h.inferfabric", tmp_path / "ck"
+    hsrc.write_text(hyper_mla_moe_source(hc, 1, context=128))
+    assert compiler.cli("synth-checkpoint", str(hsrc), str(ck), "--seed", "11").returncode == 0
+    compiler.write_bundle(str(hsrc), str(tmp_path / "h"), checkpoint_dir=str(ck), prefill_tokens=8)
+    heng = PlanEngine(str(tmp_path / "h"), str(ck), fab, max_tokens=8, keep_logits=True)
+    assert [c.dtype for c in heng.caches] == [torch.uint8, torch.bfloat16, torch.uint8]
+    seq = torch.randint(1, 512, (21,), generator=torch.Generator().manual_seed(6)).tolist()
+    routers = [k for k, i in enumerate(heng.ins) if i["op"] == "router_topk"]
+    oracle = compiler.interpret(hsrc.read_text(), str(ck), seq, all_logits=True, watch=[heng.ins[k]["name"] for k in routers])
+    want = torch.tensor(oracle["prompt_logits"])
+    picked = {}
+    heng.probe = lambda k, T: picked.__setitem__(k, heng.vals[k][0][:T].tolist()) if k in routers else None
+    agree = 0
+    for s in range(0, len(seq), 8):
+        n = min(8, len(seq) - s)
+        heng.tokens[:n].copy_(torch.tensor(seq[s:s + n], dtype=torch.int32))
+        heng.positions[:n].copy_(torch.arange(s, s + n, dtype=torch.int32))
+        heng.slots[:n].zero_()
+        heng.forward(n)
+        torch.cuda.synchronize()
+        for i in range(n):
+            same = all(sorted(picked[k][i]) == sorted(oracle["watched"][s + i][heng.ins[k]["name"]]["ids"]) for k in routers)
+            agree += same
+            if same:
+                torch.testing.assert_close(heng.logits[i].cpu(), want[s + i], rtol=5e-2, atol=5e-2)
+    assert agree >= len(seq) * 0.8 and fab.status() == 0
+    fab.close()
