@@ -72,3 +72,27 @@ def test_hyper_and_dense_examples_are_the_generated_sources(tmp_path):
     assert compiler.validate_bundle(out["dir"])["ranks"] == 8
     d = compiler.cli("explain", str(root / "dense_gqa_2b_tp2.inferfabric"))
     assert d.returncode == 0 and json.loads(d.stdout)["physical_ops"]["paged_attention"] == 24
+
+
+def test_packed_cache_source_quantises_in_the_oracle(tmp_path):
+    """`kv_int8=True` declares packed int8 latent caches; the CPU oracle then reads back quantised latent rows: logits move by
+    the quantisation noise (not zero, not large) and the cache instructions carry the packed dtype."""
+    import dataclasses
+
+    from ironpangu_b200 import compiler
+    from ironpangu_b200.compiler.sources import mla_moe_source
+    from ironpangu_b200.models.mla_moe import MlaMoeConfig
+
+    cfg = dataclasses.replace(MlaMoeConfig.tiny(2), eos=2)
+    plain, packed = tmp_path / "plain.inferfabric", tmp_path / "packed.inferfabric"
+    plain.write_text(mla_moe_source(cfg, 1, context=64))
+    packed.write_text(mla_moe_source(cfg, 1, context=64, kv_int8=True))
+    assert compiler.cli("synth-checkpoint", str(plain), str(tmp_path / "ck"), "--seed", "2").returncode == 0
+    out = compiler.write_bundle(str(packed), str(tmp_path / "b"), checkpoint_dir=str(tmp_path / "ck"))
+    ins = json.loads((Path(out["dir"]) / "device-program.json").read_text())["instructions"]
+    assert [i["dtype"] for i in ins if i["op"] == "mla_kv_write"] == ["int8_ds_mla"] * cfg.layers
+    toks = [5, 17, 99, 3, 64, 120, 8, 41]
+    a = torch.tensor(compiler.interpret(plain.read_text(), str(tmp_path / "ck"), toks, all_logits=True)["prompt_logits"])
+    b = torch.tensor(compiler.interpret(packed.read_text(), str(tmp_path / "ck"), toks, all_logits=True)["prompt_logits"])
+    diff = float((a - b).abs().max())
+    assert 0.0 < diff < 0.1, diff
