@@ -17,6 +17,8 @@
 // aclnnLightningIndexerEnhance (native/src/resident_index.h).
 #include <algorithm>
 
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "ifab_kernels.h"
 
@@ -263,10 +265,13 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(const bf16* q, const bf
 
 // ---- sparse-attention indexer -----------------------------------------------------------------------------------------
 // grid (ceil(ctx/8), T): one warp per key position; keys: paged bf16 [pages, page_tokens, dim]; scores f32 [T, ctx]
-__global__ void __launch_bounds__(256) index_score_kernel(const bf16* q /*[T, Hi, dim]*/, const float* w /*[T, Hi]*/, const bf16* keys,
-                                                          const int32_t* positions, const int32_t* slots, const int32_t* page_table,
-                                                          int max_pages, int page_tokens, int num_pages, float* scores, int ctx, int Hi,
-                                                          int dim, uint32_t* status) {
+// Q8: the keys are int8 rows with one half-precision scale per row (index_cache_append_q8_kernel), and every query head is
+// quantised the same way before scoring - the arithmetic of the CPU oracle for an int8 index cache.
+template <bool Q8>
+__global__ void __launch_bounds__(256) index_score_kernel(const bf16* q /*[T, Hi, dim]*/, const float* w /*[T, Hi]*/, const void* keys_raw,
+                                                          const __half* key_scales, const int32_t* positions, const int32_t* slots,
+                                                          const int32_t* page_table, int max_pages, int page_tokens, int num_pages, float* scores,
+                                                          int ctx, int Hi, int dim, uint32_t* status) {
   extern __shared__ float qs[];   // [Hi][dim] then w [Hi]
   grid_dep_launch();
   grid_dep_wait();
@@ -274,6 +279,17 @@ __global__ void __launch_bounds__(256) index_score_kernel(const bf16* q /*[T, Hi
   for (int i = threadIdx.x; i < Hi * dim; i += blockDim.x) qs[i] = __bfloat162float(q[(long)t * Hi * dim + i]);
   for (int i = threadIdx.x; i < Hi; i += blockDim.x) qs[Hi * dim + i] = w[(long)t * Hi + i];
   __syncthreads();
+  if (Q8) {
+    for (int h = warp; h < Hi; h += (int)(blockDim.x >> 5)) {          // one warp per head row
+      float amax = 0.f;
+      for (int i = lane; i < dim; i += 32) amax = fmaxf(amax, fabsf(qs[h * dim + i]));
+      amax = warp_max(amax);
+      const float sc = __half2float(__float2half_rn(amax / 127.f));
+      if (sc > 0.f)
+        for (int i = lane; i < dim; i += 32) qs[h * dim + i] = fmaxf(-127.f, fminf(127.f, rintf(qs[h * dim + i] / sc))) * sc;
+    }
+    __syncthreads();
+  }
   const int s = blockIdx.x * 8 + warp;
   if (s >= ctx) return;
   const int pos = positions[t];
@@ -284,10 +300,17 @@ __global__ void __launch_bounds__(256) index_score_kernel(const bf16* q /*[T, Hi
     if (page < 0 || page >= num_pages) {
       if (lane == 0 && status) atomicOr(status, IFAB_STATUS_BAD_INDEX);
     } else {
-      const bf16* kr = keys + ((long)page * page_tokens + s % page_tokens) * dim;
+      const long krow = (long)page * page_tokens + s % page_tokens;
       float kf[8];
       const int per = dim / 32;   // dim = 128 -> 4 elements per lane
-      for (int i = 0; i < per; ++i) kf[i] = __bfloat162float(kr[lane * per + i]);
+      if (Q8) {
+        const signed char* kr = reinterpret_cast<const signed char*>(keys_raw) + krow * dim;
+        const float ks = __half2float(key_scales[krow]);
+        for (int i = 0; i < per; ++i) kf[i] = (float)kr[lane * per + i] * ks;
+      } else {
+        const bf16* kr = reinterpret_cast<const bf16*>(keys_raw) + krow * dim;
+        for (int i = 0; i < per; ++i) kf[i] = __bfloat162float(kr[lane * per + i]);
+      }
       sc = 0.f;
       for (int h = 0; h < Hi; ++h) {
         float d = 0.f;
@@ -424,9 +447,23 @@ extern "C" int ifab_sparse_index(const void* q, const float* w, const void* keys
   if (T < 1 || ctx < 1 || heads < 1 || dim % 32 || dim > 256 || topk < 1) return -1;
   cudaStream_t s = (cudaStream_t)stream;
   const size_t smem = (size_t)(heads * dim + heads) * sizeof(float);
-  if (int rc = opt_in_smem(index_score_kernel, smem)) return rc;
-  if (int rc = launch_chain(index_score_kernel, dim3((ctx + 7) / 8, T), dim3(256), smem, s, (const bf16*)q, w, (const bf16*)keys, positions, slots,
-                            page_table, max_pages, page_tokens, num_pages, scores, ctx, heads, dim, status))
+  if (int rc = opt_in_smem(index_score_kernel<false>, smem)) return rc;
+  if (int rc = launch_chain(index_score_kernel<false>, dim3((ctx + 7) / 8, T), dim3(256), smem, s, (const bf16*)q, w, keys, (const __half*)nullptr,
+                            positions, slots, page_table, max_pages, page_tokens, num_pages, scores, ctx, heads, dim, status))
+    return rc;
+  return launch_chain(index_select_kernel, dim3(T), dim3(256), 0, s, (const float*)scores, positions, ctx, topk, out);
+}
+
+// The same over an int8 index cache: keys int8 [pages, page_tokens, dim], key_scales half [pages, page_tokens].
+extern "C" int ifab_sparse_index_q8(const void* q, const float* w, const void* keys, const void* key_scales, const int32_t* positions,
+                                    const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens, int num_pages, float* scores,
+                                    int ctx, int T, int heads, int dim, int topk, int32_t* out, uint32_t* status, void* stream) {
+  if (T < 1 || ctx < 1 || heads < 1 || dim % 32 || dim > 256 || topk < 1 || !key_scales) return -1;
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t smem = (size_t)(heads * dim + heads) * sizeof(float);
+  if (int rc = opt_in_smem(index_score_kernel<true>, smem)) return rc;
+  if (int rc = launch_chain(index_score_kernel<true>, dim3((ctx + 7) / 8, T), dim3(256), smem, s, (const bf16*)q, w, keys, (const __half*)key_scales,
+                            positions, slots, page_table, max_pages, page_tokens, num_pages, scores, ctx, heads, dim, status))
     return rc;
   return launch_chain(index_select_kernel, dim3(T), dim3(256), 0, s, (const float*)scores, positions, ctx, topk, out);
 }

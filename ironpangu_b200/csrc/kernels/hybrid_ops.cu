@@ -18,6 +18,8 @@
 // delta_rule_kernel (hc_ops.cu), attention is the GQA pair of decode_gqa.cu (partial rotary, head_dim 64 / 128 / 256).
 // Reference: the typed plan of the checkpoint-bound compile path (crates/inferfabric-compiler/src/bound.rs:520-830) and the
 // device operators behind it (native/src/inferfabric_acl.cpp:889-960 delta_prepare, native/src/qwen_model.cpp).
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "ifab_kernels.h"
 
@@ -215,6 +217,37 @@ __global__ void __launch_bounds__(256) index_cache_append_kernel(const bf16* key
   for (int i = lane; i < dim; i += 32) dst[i] = key[(long)t * ldk + i];
 }
 
+// The same into an int8 index cache: q = rint(x / s) clamped to +-127 with one scale per row, s = max|x| / 127 rounded to half
+// precision (what the CPU oracle keeps: rint(x / s) * s). cache int8 [pages, page_tokens, dim], scales half [pages, page_tokens].
+__global__ void __launch_bounds__(256) index_cache_append_q8_kernel(const bf16* key, long ldk, const int32_t* positions, const int32_t* slots,
+                                                                   const int32_t* page_table, int max_pages, int page_tokens, int num_pages,
+                                                                   signed char* cache, __half* scales, int T, int dim, uint32_t* status) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const int pos = positions[t];
+  if (pos < 0) return;
+  const int lp = pos / page_tokens;
+  const int page = lp < max_pages ? page_table[(long)slots[t] * max_pages + lp] : -1;
+  if (page < 0 || page >= num_pages) {
+    if (lane == 0 && status) atomicOr(status, IFAB_STATUS_BAD_INDEX);
+    return;
+  }
+  const long row = (long)page * page_tokens + pos % page_tokens;
+  float amax = 0.f;
+  for (int i = lane; i < dim; i += 32) amax = fmaxf(amax, fabsf(__bfloat162float(key[(long)t * ldk + i])));
+  amax = warp_max(amax);
+  const __half sh = __float2half_rn(amax / 127.f);
+  const float sc = __half2float(sh);
+  if (lane == 0) scales[row] = sh;
+  signed char* dst = cache + row * dim;
+  for (int i = lane; i < dim; i += 32) {
+    const float v = __bfloat162float(key[(long)t * ldk + i]);
+    dst[i] = sc > 0.f ? (signed char)fmaxf(-127.f, fminf(127.f, rintf(v / sc))) : (signed char)0;
+  }
+}
+
 // y = a + b, bf16 rows
 __global__ void __launch_bounds__(256) add_rows_kernel(const bf16* a, long lda, const bf16* b, long ldb, bf16* y, long ldy, int rows, int n) {
   grid_dep_launch();
@@ -256,6 +289,14 @@ extern "C" int ifab_index_cache_append(const void* key, long ldk, const int32_t*
   if (T < 1 || dim < 1) return -1;
   return launch_chain(index_cache_append_kernel, dim3((T + 7) / 8), dim3(256), 0, (cudaStream_t)stream, (const bf16*)key, ldk, positions, slots, page_table,
                       max_pages, page_tokens, num_pages, (bf16*)cache, T, dim, status);
+}
+
+extern "C" int ifab_index_cache_append_q8(const void* key, long ldk, const int32_t* positions, const int32_t* slots, const int32_t* page_table,
+                                          int max_pages, int page_tokens, int num_pages, void* cache, void* scales, int T, int dim, uint32_t* status,
+                                          void* stream) {
+  if (T < 1 || dim < 1) return -1;
+  return launch_chain(index_cache_append_q8_kernel, dim3((T + 7) / 8), dim3(256), 0, (cudaStream_t)stream, (const bf16*)key, ldk, positions, slots,
+                      page_table, max_pages, page_tokens, num_pages, (signed char*)cache, (__half*)scales, T, dim, status);
 }
 
 extern "C" int ifab_add_rows(const void* a, long lda, const void* b, long ldb, void* y, long ldy, int rows, int n, void* stream) {

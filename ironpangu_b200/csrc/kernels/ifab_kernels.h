@@ -253,6 +253,13 @@ int ifab_delta_rule_decode(const void* q, const void* k, const void* v, const fl
 int ifab_sparse_index(const void* q, const float* w, const void* keys, const int32_t* positions, const int32_t* slots,
                       const int32_t* page_table, int max_pages, int page_tokens, int num_pages, float* scores, int ctx, int T,
                       int heads, int dim, int topk, int32_t* out, uint32_t* status, void* stream);
+/* the same over an int8 index cache (keys int8 [pages, page_tokens, dim], one half-precision scale per row; the query heads are
+ * quantised the same way before scoring) and the append that fills it */
+int ifab_sparse_index_q8(const void* q, const float* w, const void* keys, const void* key_scales, const int32_t* positions, const int32_t* slots,
+                         const int32_t* page_table, int max_pages, int page_tokens, int num_pages, float* scores, int ctx, int T, int heads, int dim,
+                         int topk, int32_t* out, uint32_t* status, void* stream);
+int ifab_index_cache_append_q8(const void* key, long ldk, const int32_t* positions, const int32_t* slots, const int32_t* page_table, int max_pages,
+                               int page_tokens, int num_pages, void* cache, void* scales, int T, int dim, uint32_t* status, void* stream);
 
 /* ---- packed int8 latent cache (656-byte rows: 512 int8 | 64 bf16 rope | 4 f32 tile scales) and activation quantisation ----
  * Attention over a packed cache: ifab_mla_decode_attention with rope = -64 and `cache` pointing at the packed rows. */

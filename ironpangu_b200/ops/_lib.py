@@ -95,6 +95,7 @@ _SIGS = {
     "ifab_mhc_post_norm": [_P, _P, c_long, _P, c_float, _P, _P, _P, c_int, c_int, c_int, _P],
     "ifab_rope_prefix": [_P, c_long, _P, _P, c_long, c_int, c_int, c_int, c_int, c_float, _P],
     "ifab_index_cache_append": [_P, c_long, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, _P, _P],
+    "ifab_index_cache_append_q8": [_P, c_long, _P, _P, _P, c_int, c_int, c_int, _P, _P, c_int, c_int, _P, _P],
     "ifab_add_rows": [_P, c_long, _P, c_long, _P, c_long, c_int, c_int, _P],
     "ifab_swiglu_pair": [_P, c_long, _P, c_long, _P, c_long, c_int, c_int, _P],
     "ifab_zc_rmsnorm": [_P, c_long, _P, c_float, _P, c_long, c_int, c_int, c_int, _P],
@@ -105,6 +106,7 @@ _SIGS = {
     "ifab_gated_rmsnorm": [_P, _P, c_long, _P, c_float, _P, c_long, c_int, c_int, c_int, _P],
     "ifab_delta_rule_decode": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "ifab_sparse_index": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],
+    "ifab_sparse_index_q8": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],
     "ifab_mla_kv_write_q8": [_P, c_long, _P, c_float, c_float, _P, _P, _P, c_int, c_int, _P, c_int, c_int, _P, _P],
     "ifab_mla_kv_write_q8_split": [_P, c_long, _P, c_long, _P, c_float, c_float, _P, _P, _P, c_int, c_int, _P, c_int, c_int, _P, _P],
     "ifab_kv_dequantize_q8": [_P, _P, c_long, _P],

@@ -80,14 +80,21 @@ def delta_rule_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torc
 
 def sparse_index(q: torch.Tensor, w: torch.Tensor, keys: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
                  page_table: torch.Tensor, *, ctx: int, topk: int, status_ptr: Optional[int] = None, scores: Optional[torch.Tensor] = None,
-                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 out: Optional[torch.Tensor] = None, key_scales: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Top-``topk`` key positions per query by ``sum_h w_h * relu(q_h . key)``; ``keys`` paged bf16 ``[pages, page_tokens, dim]``.
-    Positions come out ascending, padded with -1; ``scores`` (f32 ``[T, ctx]``) is scratch."""
+    Positions come out ascending, padded with -1; ``scores`` (f32 ``[T, ctx]``) is scratch. With ``key_scales`` (half
+    ``[pages, page_tokens]``) the keys are int8 rows with one scale each and the query heads are quantised the same way."""
     T, H, dim = q.shape
     num_pages, page_tokens, _ = keys.shape
     scores = torch.empty(T, ctx, dtype=torch.float32, device=q.device) if scores is None else scores
     out = torch.empty(T, topk, dtype=torch.int32, device=q.device) if out is None else out
     assert scores.is_contiguous() and scores.shape[1] == ctx and out.is_contiguous() and w.dtype == torch.float32 and w.is_contiguous()
+    if key_scales is not None:
+        assert keys.dtype == torch.int8 and key_scales.dtype == torch.float16 and key_scales.is_contiguous()
+        check(_lib.load().ifab_sparse_index_q8(q.data_ptr(), w.data_ptr(), keys.data_ptr(), key_scales.data_ptr(), positions.data_ptr(), slots.data_ptr(),
+                                               page_table.data_ptr(), page_table.shape[1], page_tokens, num_pages, scores.data_ptr(), ctx, T, H,
+                                               dim, topk, out.data_ptr(), status_ptr, _s()), "sparse_index_q8")
+        return out
     check(_lib.load().ifab_sparse_index(q.data_ptr(), w.data_ptr(), keys.data_ptr(), positions.data_ptr(), slots.data_ptr(),
                                         page_table.data_ptr(), page_table.shape[1], page_tokens, num_pages, scores.data_ptr(), ctx, T, H,
                                         dim, topk, out.data_ptr(), status_ptr, _s()), "sparse_index")
@@ -105,9 +112,16 @@ def rope_prefix(x: torch.Tensor, positions: torch.Tensor, *, heads: int, head_di
 
 
 def index_cache_append(key: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
-                       status_ptr: Optional[int] = None) -> None:
-    """Index keys ``[T, dim]`` of the step's rows into the paged index cache ``[pages, page_tokens, dim]`` (bf16)."""
+                       status_ptr: Optional[int] = None, scales: Optional[torch.Tensor] = None) -> None:
+    """Index keys ``[T, dim]`` of the step's rows into the paged index cache ``[pages, page_tokens, dim]`` (bf16), or - with
+    ``scales`` (half ``[pages, page_tokens]``) - into an int8 cache with one half-precision scale per row."""
     T, dim = key.shape
+    if scales is not None:
+        assert cache.dtype == torch.int8 and scales.dtype == torch.float16
+        check(_lib.load().ifab_index_cache_append_q8(key.data_ptr(), key.stride(0), positions.data_ptr(), slots.data_ptr(), page_table.data_ptr(),
+                                                     page_table.shape[1], cache.shape[1], cache.shape[0], cache.data_ptr(), scales.data_ptr(), T, dim,
+                                                     status_ptr, _s()), "index_cache_append_q8")
+        return
     check(_lib.load().ifab_index_cache_append(key.data_ptr(), key.stride(0), positions.data_ptr(), slots.data_ptr(), page_table.data_ptr(),
                                               page_table.shape[1], cache.shape[1], cache.shape[0], cache.data_ptr(), T, dim, status_ptr, _s()),
           "index_cache_append")

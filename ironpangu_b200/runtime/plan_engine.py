@@ -285,6 +285,7 @@ class PlanEngine:
         self.logits = None
         self.vals: List[object] = [None] * len(self.ins)
         self._index_cache_of: Dict[int, torch.Tensor] = {}     # index-cache instruction -> its pages of index keys
+        self._index_scales_of: Dict[int, torch.Tensor] = {}    # int8 index caches: the per-row scales
         self._index_scores = None
         self._cache_of: Dict[int, torch.Tensor] = {}     # cache-write instruction -> its pages
         self.caches: List[torch.Tensor] = []              # the same tensors in program order (one per attention layer)
@@ -621,9 +622,15 @@ class PlanEngine:
                     raise NotImplementedError("windowed grouped-query attention has no device kernel")
                 self.vals[k] = view(k, (T, w), BF16)
             elif op == "index_cache_append":
-                if i["attrs"].get("cache_dtype", "bf16") != "bf16":
-                    raise NotImplementedError("the device index cache holds bf16 keys (int8 index keys are an oracle-only layout)")
-                self._index_cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
+                kind = i["attrs"].get("cache_dtype", "bf16")
+                if kind == "int8":
+                    # int8 keys with one half-precision scale per row (the selector quantises the query heads the same way)
+                    self._index_cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=torch.int8, device=dev)
+                    self._index_scales_of[k] = torch.zeros(self.num_pages, self.page_tokens, dtype=torch.float16, device=dev)
+                elif kind == "bf16":
+                    self._index_cache_of[k] = torch.zeros(self.num_pages, self.page_tokens, w, dtype=BF16, device=dev)
+                else:
+                    raise NotImplementedError(f"index cache dtype {kind} has no device layout")
             elif op == "sparse_index":
                 self.vals[k] = view(k, (T, w), i32)
                 self._index_scores = torch.empty(T, self.max_context, dtype=f32, device=dev)      # selector scratch: one score per key
@@ -777,7 +784,8 @@ class PlanEngine:
                 HC.rope_prefix(val(ins[0]), pos, heads=int(a["heads"]), head_dim=int(a["head_dim"]), rotary_dim=int(a["rotary_dim"]),
                                theta=float(a["theta"]), out=val(k))
             elif op == "index_cache_append":
-                HC.index_cache_append(val(ins[0]), self._index_cache_of[k], pos, slot, self.page_table, status_ptr=st)
+                HC.index_cache_append(val(ins[0]), self._index_cache_of[k], pos, slot, self.page_table, status_ptr=st,
+                                      scales=self._index_scales_of.get(k))
                 V[k] = k
             elif op == "sparse_index":
                 Hi, dim = int(a["heads"]), int(a["head_dim"])
@@ -785,7 +793,8 @@ class PlanEngine:
                 if not q.is_contiguous():
                     raise NotImplementedError("the index query must be a whole instruction result")
                 HC.sparse_index(q.view(T, Hi, dim), val(ins[1]).float(), self._index_cache_of[V[ins[2]]], pos, slot, self.page_table,
-                                ctx=self.max_context, topk=int(a["topk"]), status_ptr=st, scores=self._index_scores[:T], out=val(k))
+                                ctx=self.max_context, topk=int(a["topk"]), status_ptr=st, scores=self._index_scores[:T], out=val(k),
+                                key_scales=self._index_scales_of.get(V[ins[2]]))
             elif op == "add":
                 HC.add_rows(val(ins[0]), val(ins[1]), out=val(k))
             elif op == "swiglu":
@@ -892,5 +901,5 @@ class PlanEngine:
         return g
 
     def reset(self) -> None:
-        for c in list(self.caches) + list(self._index_cache_of.values()) + [t for kv in self._kv_of.values() for t in kv] + list(self._conv_state.values()):
+        for c in list(self.caches) + list(self._index_cache_of.values()) + list(self._index_scales_of.values()) + [t for kv in self._kv_of.values() for t in kv] + list(self._conv_state.values()):
             c.zero_()

@@ -1,12 +1,12 @@
 """The .inferfabric source of a one-layer latent-attention model with a sparse indexer, at dimensions the device kernels take."""
-def source(topk, learned=True, window=0):
+def source(topk, learned=True, window=0, index_dtype="bf16"):
     sel = ('latent_attention(query, cache, picked, scale_dim = 192, window = %d, selection = "learned_indices")' % window if learned else
            'latent_attention(query, cache, scale_dim = 192, window = %d, selection = "all_causal_within_window")' % window)
     indexer = f"""
     let iq = rotary_prefix(linear(xn, weight = w.iq, width = 512, placement = "replicated"), heads = 8, head_dim = 64, rotary_dim = 32, theta = 10000);
     let ik = rotary_prefix(linear(xn, weight = w.ik, width = 64, placement = "replicated"), heads = 1, head_dim = 64, rotary_dim = 32, theta = 10000);
     let iw = linear(xn, weight = w.iw, width = 8, placement = "replicated");
-    let icache = index_cache_append(ik, width = 64, page_tokens = 16);
+    let icache = index_cache_append(ik, width = 64, page_tokens = 16, cache_dtype = "{index_dtype}");
     let picked = sparse_index(iq, iw, icache, heads = 8, head_dim = 64, topk = {topk}, scoring = "weighted_relu");""" if learned else ""
     return f"""language inferfabric 1;
 model Indexed {{

@@ -156,8 +156,8 @@ def test_bundle_engine_equals_the_hand_wired_decoder(tmp_path, fused_head, fused
     fab.close()
 
 
-@pytest.mark.parametrize("topk,window", [(5, 0), (64, 0), (6, 12)])
-def test_sparse_indexer_program_on_the_device_matches_the_interpreter(tmp_path, topk, window):
+@pytest.mark.parametrize("topk,window,index_dtype", [(5, 0, "bf16"), (64, 0, "bf16"), (6, 12, "bf16"), (5, 0, "int8"), (6, 12, "int8")])
+def test_sparse_indexer_program_on_the_device_matches_the_interpreter(tmp_path, topk, window, index_dtype):
     """A program with an index cache, the weighted-ReLU selector and attention over the learned selection: the plan engine binds
     rotary_prefix, index_cache_append, sparse_index, add and the indexed split-KV attention; selections equal the CPU oracle's
     and logits agree within bf16 noise."""
@@ -168,7 +168,7 @@ def test_sparse_indexer_program_on_the_device_matches_the_interpreter(tmp_path, 
     from ironpangu_b200.runtime.plan_engine import PlanEngine
 
     src, ck, bundle = tmp_path / "m.inferfabric", tmp_path / "ck", tmp_path / "b"
-    src.write_text(source(topk, True, window))
+    src.write_text(source(topk, True, window, index_dtype))       # int8: keys and query heads quantised row-wise, as in the oracle
     assert compiler.cli("synth-checkpoint", str(src), str(ck), "--seed", "5").returncode == 0
     compiler.write_bundle(str(src), str(bundle), checkpoint_dir=str(ck), prefill_tokens=8)
     toks = torch.randint(1, 512, (40,), generator=torch.Generator().manual_seed(2)).tolist()
