@@ -206,11 +206,22 @@ class HyperMlaMoeConfig:
     scoring: str = "sigmoid_bias_group_topk"
     eos: int = 2
     packed_every: int = 0          # > 0: layers whose index is a multiple of it keep a packed int8 latent cache (the long-window layers at 3)
+    learned: bool = False          # those layers also attend over a learned selection: a sparse indexer (int8 index cache) picks
+                                   # `index_topk` positions on every second one of them, the other ones reuse the previous selection
+    index_heads: int = 24
+    index_dim: int = 128
+    index_rotary: int = 64
+    index_topk: int = 2048
 
     @staticmethod
     def pangu92b() -> "HyperMlaMoeConfig":
         """The published 92B configuration of this family (46 layers, 256 experts of 1024, 48 heads, 4 streams, 128 sinks)."""
         return HyperMlaMoeConfig()
+
+    @staticmethod
+    def pangu92b_learned() -> "HyperMlaMoeConfig":
+        """The same with packed int8 caches and learned sparse attention on the long-window layers (every third layer)."""
+        return HyperMlaMoeConfig(packed_every=3, learned=True)
 
     @staticmethod
     def tiny(layers: int = 3) -> "HyperMlaMoeConfig":
@@ -232,6 +243,10 @@ def hyper_mla_moe_source(cfg: HyperMlaMoeConfig, tp: int, context: int = 512, na
     H, S = c.hidden, c.streams
     mhc = f"streams = {S}, sinkhorn = {c.sinkhorn}, eps = 1e-6"
     packed_expr = f"eq(mod(index, {c.packed_every}), 0)" if c.packed_every > 0 else "lt(index, 0)"
+    if c.learned and c.packed_every <= 0:
+        raise ValueError("learned selection runs on the packed layers: set packed_every")
+    if c.learned:
+        return _hyper_learned_source(c, tp, context, name, mhc, packed_expr, ", ".join(str(i) for i in range(tp)))
     devices = ", ".join(str(i) for i in range(tp))
     return f"""language inferfabric 1;
 
@@ -303,6 +318,121 @@ model {name} {{
     }};
 
     let merged = mhc_input(mhc_merge(hidden, weight = w.merge_mhc_module, {mhc}));
+    let local_logits = linear(norm(merged, weight = w.norm, eps = {eps}), weight = weights("lm_head"), width = div({c.vocab}, {tp}), placement = "tp_rows");
+    let logits = gather(local_logits);
+    yield logits;
+}}
+
+plan TP{tp}EP{tp} for {name} {{
+    target = b200_token_v1;
+    tp = {tp};
+    ep = {tp};
+    devices = [{devices}];
+    max_num_seqs = 1;
+    max_num_batched_tokens = 1;
+    max_model_len = {context};
+}}
+"""
+
+
+def _hyper_learned_source(c: HyperMlaMoeConfig, tp: int, context: int, name: str, mhc: str, packed_expr: str, devices: str) -> str:
+    """The variant with a sparse indexer: the fold carries a record (residual streams, last selection); a packed layer attends
+    over the selection - computed by its own indexer when its index is a multiple of ``2 * packed_every``, else the one carried
+    from the previous packed layer."""
+    qw, lat, theta, eps = c.q_lora, c.kv_lora, _num(c.theta), repr(c.eps)
+    H, S = c.hidden, c.streams
+    iw = c.index_heads * c.index_dim
+    fresh_expr = f"eq(mod(index, {2 * c.packed_every}), 0)"
+    return f"""language inferfabric 1;
+
+// {c.layers} layers ({c.first_dense} with a dense FFN), hidden {H} x {S} residual streams, vocab {c.vocab};
+// MLA: {c.heads} heads, q_lora {qw}, kv_lora {lat}, nope {c.nope}, rope {c.rope}, v {c.vdim}, {c.sinks} sink rows, token convolutions of {c.taps} taps;
+// every {c.packed_every}th layer: packed int8 latent cache + attention over a learned selection ({c.index_heads} index heads x {c.index_dim},
+// top-{c.index_topk}, int8 index keys), recomputed on every second one of them;
+// MoE: {c.experts} routed experts (FFN {c.expert_ffn}), top-{c.topk} {c.scoring}, shared expert (FFN {c.shared_ffn}); tp = ep = {tp}.
+
+module Selector(x, qr, w) {{
+    let iq = rotary_prefix(linear(qr, weight = w.wq_b, width = {iw}, placement = "replicated"),
+                           heads = {c.index_heads}, head_dim = {c.index_dim}, rotary_dim = {c.index_rotary}, theta = {theta});
+    let ik = rotary_prefix(norm(linear(x, weight = w.wk, width = {c.index_dim}, placement = "replicated"), weight = w.k_norm, eps = {eps}),
+                           heads = 1, head_dim = {c.index_dim}, rotary_dim = {c.index_rotary}, theta = {theta});
+    let gains = linear(x, weight = w.weights_proj, width = {c.index_heads}, placement = "replicated");
+    let keys = index_cache_append(ik, width = {c.index_dim}, page_tokens = 16, cache_dtype = "int8");
+    let picked = sparse_index(iq, gains, keys, heads = {c.index_heads}, head_dim = {c.index_dim}, topk = {c.index_topk}, scoring = "weighted_relu");
+    yield picked;
+}}
+
+module Attention(x, w, window, packed, fresh, carried) {{
+    let qkv = linear(x, weight = w.q_a_proj, paired_weight = w.kv_a_proj_with_mqa, width = {qw}, paired_width = {lat + c.rope}, placement = "replicated");
+    let qc = mome(slice(qkv, start = 0, width = {qw}), weight = w.qa_conv, taps = {c.taps});
+    let qn = norm(qc, weight = w.q_a_layernorm, eps = {eps});
+    let q = linear(qn, weight = w.q_b_proj, width = div({c.heads * c.qk_dim}, {tp}), placement = "tp_rows");
+    let kc = mome(slice(qkv, start = {qw}, width = {lat}), weight = w.compresskv_conv, taps = {c.taps});
+    let kr = slice(qkv, start = {qw + lat}, width = {c.rope});
+    let sinks = sink_normalize(weight = w, norm = w.kv_a_layernorm, count = {c.sinks}, latent = {lat}, rope = {c.rope}, eps = {eps});
+    let cache = choose(packed,
+        cache_norm_rope_append(kc, kr, sinks, weight = w.kv_a_layernorm, eps = {eps}, theta = {theta}{_PACKED_CACHE}),
+        cache_norm_rope_append(kc, kr, sinks, weight = w.kv_a_layernorm, eps = {eps}, theta = {theta}));
+    let query = mla_query(q, weight = w.kv_b_proj, theta = {theta}, heads = {c.heads}, nope = {c.nope}, rope = {c.rope}, latent = {lat},
+                          value = {c.vdim}, input_layout = "rank_local");
+    let selection = choose(packed, choose(fresh, Selector(x, qn, w.indexer), carried), carried);
+    let attended = choose(packed,
+        latent_attention(query, cache, selection, scale_dim = {c.qk_dim}, window = window, selection = "learned_indices"),
+        latent_attention(query, cache, scale_dim = {c.qk_dim}, window = window, selection = "all_causal_within_window"));
+    let value = mla_value(attended, weight = w.kv_b_proj, heads = {c.heads}, latent = {lat}, value = {c.vdim}, nope = {c.nope});
+    let oc = mome(value, weight = w.o_conv, taps = {c.taps}, placement = "tp_channels");
+    let output = allreduce(linear(oc, weight = w.o_proj, width = {H}, placement = "tp_columns"));
+    let result = record(hidden = output, selection = selection);
+    yield result;
+}}
+
+module DenseFFN(x, w) {{
+    let act = swiglu(linear(x, weight = w.gate_proj, paired_weight = w.up_proj, width = div({c.dense_ffn}, {tp}),
+                            paired_width = div({c.dense_ffn}, {tp}), placement = "tp_rows"));
+    let output = allreduce(linear(act, weight = w.down_proj, width = {H}, placement = "tp_columns"));
+    yield output;
+}}
+
+module RoutedMoE(x, w) {{
+    let routes = router(x, weight = w.gate, experts = {c.experts}, topk = {c.topk}, scoring = "{c.scoring}", scale = {repr(float(c.route_scale))});
+    let expert = child(w.experts, "{{expert}}");
+    let gate_up = expert_linear(x, routes, weight = expert.gate_proj, paired_weight = expert.up_proj, width = {c.expert_ffn});
+    let down = expert_swiglu_down(gate_up, routes, weight = expert.down_proj, width = {H});
+    let local = expert_reduce(down, routes);
+    let shared_act = swiglu(linear(x, weight = w.shared_experts.gate_proj, paired_weight = w.shared_experts.up_proj,
+                                   width = div({c.shared_ffn}, {tp}), paired_width = div({c.shared_ffn}, {tp}), placement = "tp_rows"));
+    let shared_partial = linear(shared_act, weight = w.shared_experts.down_proj, width = {H}, placement = "tp_columns");
+    let output = allreduce(add(local, shared_partial));
+    yield output;
+}}
+
+module Block(x, w, index, window) {{
+    let attn_hc = mhc_pre(x.hidden, weight = w.attn_mhc_module, {mhc});
+    let attention = Attention(norm(mhc_input(attn_hc), weight = w.input_layernorm, eps = {eps}), w.self_attn, window, {packed_expr}, {fresh_expr}, x.selection);
+    let residual = mhc_post(attn_hc, norm(attention.hidden, weight = w.post_attention_layernorm, eps = {eps}));
+    let ffn_hc = mhc_pre(residual, weight = w.mlp_mhc_module, {mhc});
+    let ffn_in = norm(mhc_input(ffn_hc), weight = w.pre_mlp_layernorm, eps = {eps});
+    let ffn = choose(lt(index, {c.first_dense}), DenseFFN(ffn_in, w.mlp), RoutedMoE(ffn_in, w.mlp));
+    let mixed = mhc_post(ffn_hc, norm(ffn, weight = w.post_mlp_layernorm, eps = {eps}));
+    let output = optional_norm(mixed, weight = w.block_post_layernorm, eps = {eps});
+    let result = record(hidden = output, selection = attention.selection);
+    yield result;
+}}
+
+model {name} {{
+    context = {context};
+    eos = {c.eos};
+    let w = weights("model");
+    let embedded = embedding(weight = w.embed_tokens, width = {H}, vocab = {c.vocab});
+
+    // the first layer computes its own selection, so the carried one only needs a value to start from
+    let hidden = fold i in range(0, {c.layers}) carry(x = record(hidden = repeat(embedded, count = {S}), selection = embedded)) {{
+        let window = choose(eq(mod(i, {c.long_every}), 0), {c.long_window}, {c.short_window});
+        let block = Block(x, child(w.layers, i), i, window);
+        yield block;
+    }};
+
+    let merged = mhc_input(mhc_merge(hidden.hidden, weight = w.merge_mhc_module, {mhc}));
     let local_logits = linear(norm(merged, weight = w.norm, eps = {eps}), weight = weights("lm_head"), width = div({c.vocab}, {tp}), placement = "tp_rows");
     let logits = gather(local_logits);
     yield logits;

@@ -22,7 +22,7 @@ import time
 
 def parse(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model", default="hyper-tiny", help="pangu92b | hyper-tiny | flagship | tiny | dense2b | dense-tiny")
+    ap.add_argument("--model", default="hyper-tiny", help="pangu92b | pangu92b-learned (packed int8 caches + learned sparse attention on every third layer) | hyper-tiny | flagship | tiny | dense2b | dense-tiny")
     ap.add_argument("--source", default="", help="a .inferfabric file instead of a built-in generator (compiled as written)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0)
@@ -42,13 +42,14 @@ def source_of(args, world: int) -> tuple:
 
     if args.source:
         return open(args.source).read(), os.path.basename(args.source)
-    if args.model in ("pangu92b", "hyper-tiny"):
-        c = S.HyperMlaMoeConfig.pangu92b() if args.model == "pangu92b" else S.HyperMlaMoeConfig.tiny()
+    if args.model in ("pangu92b", "pangu92b-learned", "hyper-tiny"):
+        c = {"pangu92b": S.HyperMlaMoeConfig.pangu92b, "pangu92b-learned": S.HyperMlaMoeConfig.pangu92b_learned,
+             "hyper-tiny": S.HyperMlaMoeConfig.tiny}[args.model]()
         if args.layers:
             c.layers = args.layers
         return S.hyper_mla_moe_source(c, world, context=args.context), (
             f"{c.layers}L hidden {c.hidden} x {c.streams} streams, {c.heads} heads, q_lora {c.q_lora}, {c.experts} experts x {c.expert_ffn} "
-            f"top-{c.topk}, {c.sinks} sinks, vocab {c.vocab}")
+            f"top-{c.topk}, {c.sinks} sinks, vocab {c.vocab}" + (f", packed cache + learned top-{c.index_topk} selection every {c.packed_every} layers" if c.learned else ""))
     if args.model in ("flagship", "tiny"):
         from ironpangu_b200.models.mla_moe import MlaMoeConfig
 

@@ -352,3 +352,49 @@ def test_packed_int8_caches_in_compiled_programs(tmp_path):
                 torch.testing.assert_close(heng.logits[i].cpu(), want[s + i], rtol=5e-2, atol=5e-2)
     assert agree >= len(seq) * 0.8 and fab.status() == 0
     fab.close()
+
+
+@pytest.mark.gpu
+def test_learned_selection_variant_of_the_hyper_family_matches_the_interpreter(tmp_path):
+    """The family's variant with packed int8 caches and learned sparse attention on every second layer: the first packed layer
+    runs its indexer (int8 index keys), the next one reuses the carried selection; with a top-k that covers the whole context
+    the selection is every causal position and logits follow the oracle."""
+    import dataclasses
+
+    from ironpangu_b200 import compiler
+    from ironpangu_b200.compiler.sources import HyperMlaMoeConfig, hyper_mla_moe_source
+    from ironpangu_b200.parallel.fabric import Fabric
+    from ironpangu_b200.runtime.plan_engine import PlanEngine
+
+    cfg = dataclasses.replace(HyperMlaMoeConfig.tiny(3), packed_every=2, learned=True, index_heads=8, index_dim=64, index_rotary=32, index_topk=64)
+    src, ck = tmp_path / "m.inferfabric", tmp_path / "ck"
+    src.write_text(hyper_mla_moe_source(cfg, 1, context=128))
+    assert compiler.cli("synth-checkpoint", str(src), str(ck), "--seed", "13").returncode == 0
+    compiler.write_bundle(str(src), str(tmp_path / "b"), checkpoint_dir=str(ck), prefill_tokens=8)
+    fab = Fabric(0, 1)
+    eng = PlanEngine(str(tmp_path / "b"), str(ck), fab, max_tokens=8, keep_logits=True)
+    att = [i for i in eng.ins if i["op"] == "mla_attention"]
+    sel = [k for k, i in enumerate(eng.ins) if i["op"] == "sparse_index"]
+    assert len(sel) == 1 and [len(a["inputs"]) for a in att] == [3, 2, 3] and att[0]["inputs"][2] == att[2]["inputs"][2] == sel[0]
+    seq = torch.randint(1, 512, (21,), generator=torch.Generator().manual_seed(9)).tolist()
+    routers = [k for k, i in enumerate(eng.ins) if i["op"] == "router_topk"]
+    oracle = compiler.interpret(src.read_text(), str(ck), seq, all_logits=True, watch=[eng.ins[k]["name"] for k in routers + sel])
+    want = torch.tensor(oracle["prompt_logits"])
+    seen = {}
+    eng.probe = lambda k, T: seen.__setitem__(k, (eng.vals[k][0] if k in routers else eng.vals[k])[:T].tolist()) if k in routers or k in sel else None
+    agree = 0
+    for s in range(0, len(seq), 8):
+        n = min(8, len(seq) - s)
+        eng.tokens[:n].copy_(torch.tensor(seq[s:s + n], dtype=torch.int32))
+        eng.positions[:n].copy_(torch.arange(s, s + n, dtype=torch.int32))
+        eng.slots[:n].zero_()
+        eng.forward(n)
+        torch.cuda.synchronize()
+        for i in range(n):
+            assert [p for p in seen[sel[0]][i] if p >= 0] == oracle["watched"][s + i][eng.ins[sel[0]]["name"]]["ids"] == list(range(s + i + 1))
+            same = all(sorted(seen[k][i]) == sorted(oracle["watched"][s + i][eng.ins[k]["name"]]["ids"]) for k in routers)
+            agree += same
+            if same:
+                torch.testing.assert_close(eng.logits[i].cpu(), want[s + i], rtol=5e-2, atol=5e-2)
+    assert agree >= len(seq) * 0.8 and fab.status() == 0
+    fab.close()

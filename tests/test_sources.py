@@ -70,6 +70,14 @@ def test_hyper_and_dense_examples_are_the_generated_sources(tmp_path):
     assert "norm" not in ops          # every norm is folded: into a projection, the router, or the return of a hyper-connection
     out = compiler.write_bundle(str(root / "hyper_mla_moe_92b_tp8.inferfabric"), str(tmp_path / "b"))
     assert compiler.validate_bundle(out["dir"])["ranks"] == 8
+    # the variant with packed int8 caches and learned sparse attention on every third layer (eight of those sixteen layers run the indexer)
+    assert (root / "hyper_mla_moe_92b_learned_tp8.inferfabric").read_text() == hyper_mla_moe_source(HyperMlaMoeConfig.pangu92b_learned(), 8,
+                                                                                                     context=512, name="HyperMlaMoe92BLearned")
+    r = compiler.cli("explain", str(root / "hyper_mla_moe_92b_learned_tp8.inferfabric"))
+    assert r.returncode == 0, r.stderr
+    e = json.loads(r.stdout)
+    assert e["checkpoint_tensors"] == 35117 and e["checkpoint_bytes"] == 183244626748
+    assert e["physical_ops"]["sparse_index"] == 8 and e["physical_ops"]["index_cache_append"] == 8
     d = compiler.cli("explain", str(root / "dense_gqa_2b_tp2.inferfabric"))
     assert d.returncode == 0 and json.loads(d.stdout)["physical_ops"]["paged_attention"] == 24
 
