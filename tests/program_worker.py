@@ -86,6 +86,11 @@ def main():
         hc.heads = world
     run_program(hyper_mla_moe_source(hc, world, context=128), rank, world, fab, "hyper", 11, True)
     print("ok hyper program", flush=True)
+    import dataclasses
+
+    lc = dataclasses.replace(hc, packed_every=2, learned=True, index_heads=8, index_dim=64, index_rotary=32, index_topk=64)
+    run_program(hyper_mla_moe_source(lc, world, context=128), rank, world, fab, "learned", 13, True)
+    print("ok learned program", flush=True)
     dc = DenseConfig.tiny(2)
     if world > 2:
         dc.kv_heads, dc.heads = world, 2 * world

@@ -85,10 +85,10 @@ def test_dense_decoder_tensor_parallel_decode_prefill_and_batched_rows(world):
 
 @pytest.mark.parametrize("world", [2, 4])
 def test_compiled_programs_across_ranks(world):
-    """The hyper-connected latent-attention + routed-experts program and the dense grouped-query program, compiled for the
-    job's width and run by every rank's plan engine: logits equal the CPU interpreter's (this rank's vocabulary shard), every
+    """The hyper-connected latent-attention + routed-experts program (also with packed caches and learned sparse attention) and
+    the dense grouped-query program, compiled for the job's width and run by every rank's plan engine: logits equal the CPU interpreter's (this rank's vocabulary shard), every
     rank samples the same tokens, and the captured one-row step continues the sequence."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     out = _run(world, "program_worker.py")
-    assert out.count("ok hyper program") == world and out.count("ok dense program") == world
+    assert out.count("ok hyper program") == world and out.count("ok learned program") == world and out.count("ok dense program") == world
