@@ -141,6 +141,7 @@ struct DeviceProgram::Impl {
   std::map<uint32_t, std::pair<uint64_t, uint64_t>> slot_of;   // instruction -> (offset, size)
   std::vector<Val> val;
   std::map<uint32_t, void*> cache_of;                           // cache-write instruction -> pages
+  std::map<uint32_t, uint64_t> cache_bytes;                     // ... and their size (reset)
   std::map<uint32_t, HeadGroup> heads;                          // attention instruction -> its group
   std::set<uint32_t> head_members;
   bool fused_head = false;
@@ -157,6 +158,9 @@ struct DeviceProgram::Impl {
   std::map<uint32_t, std::pair<const void*, int>> sink_rows;    // sink_normalize instruction -> (rows, count)
   std::map<uint32_t, std::pair<const void*, int>> sinks_of;     // cache-write instruction -> the sink rows its readers also attend to
   std::set<uint32_t> aliased;                                   // instructions that hand a value on without a launch
+  std::set<uint32_t> packed;                                    // cache-write instructions whose pages hold packed int8 rows (656 bytes)
+  std::map<uint32_t, void*> index_scales;                       // int8 index caches: one half-precision scale per row
+  float* index_scores = nullptr;                                // selector scratch [rows, context]
   // control block (device): tokens | positions | slots | next ids | next values, page table; pinned mirror on the host
   int32_t *d_tokens = nullptr, *d_positions = nullptr, *d_slots = nullptr, *d_next = nullptr, *d_page_table = nullptr;
   float* d_next_vals = nullptr;
@@ -320,10 +324,39 @@ void DeviceProgram::Impl::load(const std::string& bundle, const std::string& che
     if (x.op == "view") continue;
     if (x.op == "mla_kv_write") {
       void* pages = nullptr;
-      const uint64_t bytes = (uint64_t)num_pages * page_tokens * x.width * 2;
+      if (x.dtype == "int8_ds_mla") {
+        if (x.width != 576) fail(ErrorKind::NotImplemented, "device program: the packed int8 cache holds 512 latent + 64 rotary columns");
+        packed.insert(k);
+      } else if (x.dtype != "bf16") {
+        fail(ErrorKind::NotImplemented, "device program: cache dtype " + x.dtype + " has no device layout");
+      }
+      const uint64_t bytes = (uint64_t)num_pages * page_tokens * (packed.count(k) ? 656 : x.width * 2);
       dmalloc(&pages, bytes, "KV pages");
       cu(cudaMemset(pages, 0, bytes), "KV clear");
       cache_of[k] = pages;
+      cache_bytes[k] = bytes;
+    } else if (x.op == "index_cache_append") {
+      const bool q8 = x.has("cache_dtype") && x.s("cache_dtype") == "int8";
+      if (x.has("cache_dtype") && !q8 && x.s("cache_dtype") != "bf16") fail(ErrorKind::NotImplemented, "device program: index cache dtype " + x.s("cache_dtype"));
+      void* pages = nullptr;
+      const uint64_t bytes = (uint64_t)num_pages * page_tokens * x.width * (q8 ? 1 : 2);
+      dmalloc(&pages, bytes, "index key pages");
+      cu(cudaMemset(pages, 0, bytes), "index keys clear");
+      cache_of[k] = pages;
+      cache_bytes[k] = bytes;
+      if (q8) {
+        void* sc = nullptr;
+        dmalloc(&sc, (uint64_t)num_pages * page_tokens * 2, "index key scales");
+        cu(cudaMemset(sc, 0, (uint64_t)num_pages * page_tokens * 2), "index scales clear");
+        index_scales[k] = sc;
+        owned.push_back(sc);
+      }
+    } else if (x.op == "sparse_index") {
+      val[k] = lease(k, (uint64_t)T * x.width * 4, x.width, 4);
+      if (!index_scores) {
+        dmalloc((void**)&index_scores, (uint64_t)rows * context * 4, "selector scores");
+        owned.push_back(index_scores);
+      }
     } else if (x.op == "mhc_pre" || x.op == "mhc_merge") {
       const int S = x.i("streams");
       if (S + S * S > 64) fail(ErrorKind::NotImplemented, "device program: a hyper-connection slot holds at most 64 mixing weights per row");
@@ -367,6 +400,7 @@ void DeviceProgram::Impl::load(const std::string& bundle, const std::string& che
       dmalloc(&pages, bytes, "K/V pages");
       cu(cudaMemset(pages, 0, bytes), "K/V clear");
       cache_of[k] = pages;
+      cache_bytes[k] = bytes;
       kv_pack_ld = std::max<long>(kv_pack_ld, x.width);
     } else if (x.op == "router_topk") {
       const int E = x.i("experts");
@@ -412,7 +446,7 @@ void DeviceProgram::Impl::load(const std::string& bundle, const std::string& che
     const int q_lora = vq.i("width"), latent = ab.i("latent"), rope = ab.i("rope"), nope = ab.i("nope"), vdim = x.i("value");
     const bool layout = vq.i("start") == 0 && vl.i("start") == q_lora && vr.i("start") == q_lora + latent;
     const bool priv = only_user(g.qb, g.absorb) && only_user(g.absorb, k) && only_user(g.write, k);
-    g.ok = layout && priv && latent == 512 && rope == 64 && nope % 32 == 0 && nope <= 128 && vdim <= 128 && q_lora % 8 == 0 && ab.s("weight") == x.s("weight");
+    g.ok = ins[g.write].dtype == "bf16" && x.in.size() == 2 && layout && priv && latent == 512 && rope == 64 && nope % 32 == 0 && nope <= 128 && vdim <= 128 && q_lora % 8 == 0 && ab.s("weight") == x.s("weight");
     heads[k] = g;
     any = true;
     all_ok = all_ok && g.ok;
@@ -517,6 +551,27 @@ void DeviceProgram::Impl::dispatch(int T) {
       kernel(ifab_gqa_decode_attention(gqa_qkv, gqa_ld, kv, vpages, d_positions, d_slots, d_page_table, max_pages, page_tokens, num_pages, x.f("scale", 1.f), T, H,
                                        KVH, hd, kps, max_splits, (float*)workspace(scratch), scratch, V(k).ptr, V(k).ld, status, st),
              x.name);
+    } else if (x.op == "index_cache_append") {
+      const Val& key = V(x.in.at(0));
+      auto sc = index_scales.find(k);
+      if (sc != index_scales.end())
+        kernel(ifab_index_cache_append_q8(key.ptr, key.ld, d_positions, d_slots, d_page_table, max_pages, page_tokens, num_pages, cache_of.at(k), sc->second, T,
+                                          (int)x.width, status, st),
+               x.name);
+      else
+        kernel(ifab_index_cache_append(key.ptr, key.ld, d_positions, d_slots, d_page_table, max_pages, page_tokens, num_pages, cache_of.at(k), T, (int)x.width,
+                                       status, st),
+               x.name);
+    } else if (x.op == "sparse_index") {
+      const Val &q = V(x.in.at(0)), &g = V(x.in.at(1));
+      const uint32_t keys = x.in.at(2);
+      if (q.ld != (long)ins[x.in[0]].width) fail(ErrorKind::NotImplemented, "device program: the index query must be a whole instruction result");
+      auto sc = index_scales.find(keys);
+      ++count;                                                         // score + select
+      kernel(ifab_sparse_index_general(q.ptr, g.ptr, g.ld, g.esize == 2 ? 1 : 0, cache_of.at(keys), sc == index_scales.end() ? nullptr : sc->second, d_positions,
+                                       d_slots, d_page_table, max_pages, page_tokens, num_pages, index_scores, (int)context, T, x.i("heads"), x.i("head_dim"),
+                                       x.i("topk"), (int32_t*)V(k).ptr, status, st),
+             x.name);
     } else if (x.op == "repeat") {
       const Val& in = V(x.in.at(0));
       const int n = x.i("count"), w = (int)ins[x.in[0]].width;
@@ -612,7 +667,16 @@ void DeviceProgram::Impl::dispatch(int T) {
       const Val &lat = V(x.in.at(0)), &kr = V(x.in.at(1));
       const int latent = (int)ins[x.in[0]].width, rope = (int)ins[x.in[1]].width;
       if (x.in.size() > 2) sinks_of[k] = sink_rows.at(x.in[2]);
-      if (kr.ptr != lat.ptr + (long)latent * 2 || kr.ld != lat.ld)
+      if (packed.count(k)) {
+        if (kr.ptr != lat.ptr + (long)latent * 2 || kr.ld != lat.ld)
+          kernel(ifab_mla_kv_write_q8_split(lat.ptr, lat.ld, kr.ptr, kr.ld, P(x.s("weight")), x.f("eps", 1e-5f), x.f("theta", 10000.f), d_positions, d_slots,
+                                            d_page_table, max_pages, page_tokens, cache_of.at(k), num_pages, T, status, st),
+                 x.name);
+        else
+          kernel(ifab_mla_kv_write_q8(lat.ptr, lat.ld, P(x.s("weight")), x.f("eps", 1e-5f), x.f("theta", 10000.f), d_positions, d_slots, d_page_table,
+                                      max_pages, page_tokens, cache_of.at(k), num_pages, T, status, st),
+                 x.name);
+      } else if (kr.ptr != lat.ptr + (long)latent * 2 || kr.ld != lat.ld)
         // e.g. a convolved latent and the raw rotary columns of the projection: the kernel reads them where they are
         kernel(ifab_mla_kv_write_split(lat.ptr, lat.ld, kr.ptr, kr.ld, P(x.s("weight")), x.f("eps", 1e-5f), x.f("theta", 10000.f), d_positions, d_slots,
                                        d_page_table, max_pages, page_tokens, cache_of.at(k), num_pages, T, latent, rope, status, st),
@@ -632,10 +696,12 @@ void DeviceProgram::Impl::dispatch(int T) {
       const uint64_t scratch = (uint64_t)T * H * max_splits * (latent + 2) * 4;
       ++count;                                                         // split + merge
       auto sk = sinks_of.find(x.in.at(1));
-      kernel(ifab_mla_decode_attention(V(x.in.at(0)).ptr, cache_of.at(x.in.at(1)), d_positions, d_slots, d_page_table, max_pages, page_tokens, num_pages,
-                                       sk == sinks_of.end() ? nullptr : sk->second.first, sk == sinks_of.end() ? 0 : sk->second.second, x.i("window"),
-                                       1.f / std::sqrt((float)x.i("scale_dim")), T, H, latent, 64, kps, max_splits,
-                                       (float*)workspace(scratch), scratch, P(x.s("weight")), nope, vdim, V(k).ptr, V(k).ld, status, st),
+      const int32_t* picked = x.in.size() > 2 ? (const int32_t*)V(x.in[2]).ptr : nullptr;
+      kernel(ifab_mla_decode_attention_indexed(V(x.in.at(0)).ptr, cache_of.at(x.in.at(1)), d_positions, d_slots, d_page_table, max_pages, page_tokens, num_pages,
+                                               sk == sinks_of.end() ? nullptr : sk->second.first, sk == sinks_of.end() ? 0 : sk->second.second, x.i("window"),
+                                               1.f / std::sqrt((float)x.i("scale_dim")), T, H, latent, packed.count(x.in[1]) ? -64 : 64, kps, max_splits,
+                                               (float*)workspace(scratch), scratch, P(x.s("weight")), nope, vdim, V(k).ptr, V(k).ld, status, picked,
+                                               picked ? (int)ins[x.in[2]].width : 0, st),
              x.name);
     } else if (x.op == "router_topk") {
       const int E = x.i("experts"), topk = x.i("topk");
@@ -748,10 +814,8 @@ void DeviceProgram::run_rows(const int32_t* tokens, const int32_t* positions, co
 }
 void DeviceProgram::reset() {
   for (auto& c : p_->conv_state) cu(cudaMemset(c.second.first, 0, c.second.second), "convolution history clear");
-  for (auto& c : p_->cache_of) {
-    const Ins& x = p_->ins[c.first];
-    cu(cudaMemset(c.second, 0, (uint64_t)p_->num_pages * p_->page_tokens * x.width * 2), "KV clear");
-  }
+  for (auto& c : p_->cache_of) cu(cudaMemset(c.second, 0, p_->cache_bytes.at(c.first)), "KV clear");
+  for (auto& c : p_->index_scales) cu(cudaMemset(c.second, 0, (uint64_t)p_->num_pages * p_->page_tokens * 2), "index scales clear");
 }
 Json DeviceProgram::audit() const {
   Json j = Json::object();

@@ -268,7 +268,8 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(const bf16* q, const bf
 // Q8: the keys are int8 rows with one half-precision scale per row (index_cache_append_q8_kernel), and every query head is
 // quantised the same way before scoring - the arithmetic of the CPU oracle for an int8 index cache.
 template <bool Q8>
-__global__ void __launch_bounds__(256) index_score_kernel(const bf16* q /*[T, Hi, dim]*/, const float* w /*[T, Hi]*/, const void* keys_raw,
+__global__ void __launch_bounds__(256) index_score_kernel(const bf16* q /*[T, Hi, dim]*/, const void* w_raw /*[T, Hi] f32, or bf16 rows of stride ldw*/,
+                                                          long ldw, int w_bf16, const void* keys_raw,
                                                           const __half* key_scales, const int32_t* positions, const int32_t* slots,
                                                           const int32_t* page_table, int max_pages, int page_tokens, int num_pages, float* scores,
                                                           int ctx, int Hi, int dim, uint32_t* status) {
@@ -277,7 +278,8 @@ __global__ void __launch_bounds__(256) index_score_kernel(const bf16* q /*[T, Hi
   grid_dep_wait();
   const int t = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < Hi * dim; i += blockDim.x) qs[i] = __bfloat162float(q[(long)t * Hi * dim + i]);
-  for (int i = threadIdx.x; i < Hi; i += blockDim.x) qs[Hi * dim + i] = w[(long)t * Hi + i];
+  for (int i = threadIdx.x; i < Hi; i += blockDim.x)
+    qs[Hi * dim + i] = w_bf16 ? __bfloat162float(reinterpret_cast<const bf16*>(w_raw)[(long)t * ldw + i]) : reinterpret_cast<const float*>(w_raw)[(long)t * ldw + i];
   __syncthreads();
   if (Q8) {
     for (int h = warp; h < Hi; h += (int)(blockDim.x >> 5)) {          // one warp per head row
@@ -441,29 +443,41 @@ extern "C" int ifab_delta_rule_decode(const void* q, const void* k, const void* 
 }
 
 // scores: scratch f32 [T, ctx]; out: int32 [T, topk], ascending key positions, -1 padded
+// Gains `w` are f32 [T, heads] (w_bf16 = 0) or bf16 rows of stride ldw (w_bf16 = 1, e.g. a projection's result where it lies);
+// key_scales = null: bf16 keys; else int8 keys with one half-precision scale per row.
+extern "C" int ifab_sparse_index_general(const void* q, const void* w, long ldw, int w_bf16, const void* keys, const void* key_scales,
+                                         const int32_t* positions, const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens,
+                                         int num_pages, float* scores, int ctx, int T, int heads, int dim, int topk, int32_t* out, uint32_t* status,
+                                         void* stream) {
+  if (T < 1 || ctx < 1 || heads < 1 || dim % 32 || dim > 256 || topk < 1 || ldw < heads) return -1;
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t smem = (size_t)(heads * dim + heads) * sizeof(float);
+  int rc;
+  if (key_scales) {
+    if ((rc = opt_in_smem(index_score_kernel<true>, smem))) return rc;
+    rc = launch_chain(index_score_kernel<true>, dim3((ctx + 7) / 8, T), dim3(256), smem, s, (const bf16*)q, w, ldw, w_bf16, keys, (const __half*)key_scales,
+                      positions, slots, page_table, max_pages, page_tokens, num_pages, scores, ctx, heads, dim, status);
+  } else {
+    if ((rc = opt_in_smem(index_score_kernel<false>, smem))) return rc;
+    rc = launch_chain(index_score_kernel<false>, dim3((ctx + 7) / 8, T), dim3(256), smem, s, (const bf16*)q, w, ldw, w_bf16, keys, (const __half*)nullptr,
+                      positions, slots, page_table, max_pages, page_tokens, num_pages, scores, ctx, heads, dim, status);
+  }
+  if (rc) return rc;
+  return launch_chain(index_select_kernel, dim3(T), dim3(256), 0, s, (const float*)scores, positions, ctx, topk, out);
+}
+
 extern "C" int ifab_sparse_index(const void* q, const float* w, const void* keys, const int32_t* positions, const int32_t* slots,
                                  const int32_t* page_table, int max_pages, int page_tokens, int num_pages, float* scores, int ctx, int T,
                                  int heads, int dim, int topk, int32_t* out, uint32_t* status, void* stream) {
-  if (T < 1 || ctx < 1 || heads < 1 || dim % 32 || dim > 256 || topk < 1) return -1;
-  cudaStream_t s = (cudaStream_t)stream;
-  const size_t smem = (size_t)(heads * dim + heads) * sizeof(float);
-  if (int rc = opt_in_smem(index_score_kernel<false>, smem)) return rc;
-  if (int rc = launch_chain(index_score_kernel<false>, dim3((ctx + 7) / 8, T), dim3(256), smem, s, (const bf16*)q, w, keys, (const __half*)nullptr,
-                            positions, slots, page_table, max_pages, page_tokens, num_pages, scores, ctx, heads, dim, status))
-    return rc;
-  return launch_chain(index_select_kernel, dim3(T), dim3(256), 0, s, (const float*)scores, positions, ctx, topk, out);
+  return ifab_sparse_index_general(q, w, heads, 0, keys, nullptr, positions, slots, page_table, max_pages, page_tokens, num_pages, scores, ctx, T, heads, dim,
+                                   topk, out, status, stream);
 }
 
 // The same over an int8 index cache: keys int8 [pages, page_tokens, dim], key_scales half [pages, page_tokens].
 extern "C" int ifab_sparse_index_q8(const void* q, const float* w, const void* keys, const void* key_scales, const int32_t* positions,
                                     const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens, int num_pages, float* scores,
                                     int ctx, int T, int heads, int dim, int topk, int32_t* out, uint32_t* status, void* stream) {
-  if (T < 1 || ctx < 1 || heads < 1 || dim % 32 || dim > 256 || topk < 1 || !key_scales) return -1;
-  cudaStream_t s = (cudaStream_t)stream;
-  const size_t smem = (size_t)(heads * dim + heads) * sizeof(float);
-  if (int rc = opt_in_smem(index_score_kernel<true>, smem)) return rc;
-  if (int rc = launch_chain(index_score_kernel<true>, dim3((ctx + 7) / 8, T), dim3(256), smem, s, (const bf16*)q, w, keys, (const __half*)key_scales,
-                            positions, slots, page_table, max_pages, page_tokens, num_pages, scores, ctx, heads, dim, status))
-    return rc;
-  return launch_chain(index_select_kernel, dim3(T), dim3(256), 0, s, (const float*)scores, positions, ctx, topk, out);
+  if (!key_scales) return -1;
+  return ifab_sparse_index_general(q, w, heads, 0, keys, key_scales, positions, slots, page_table, max_pages, page_tokens, num_pages, scores, ctx, T, heads,
+                                   dim, topk, out, status, stream);
 }

@@ -260,6 +260,20 @@ int ifab_sparse_index_q8(const void* q, const float* w, const void* keys, const 
                          int topk, int32_t* out, uint32_t* status, void* stream);
 int ifab_index_cache_append_q8(const void* key, long ldk, const int32_t* positions, const int32_t* slots, const int32_t* page_table, int max_pages,
                                int page_tokens, int num_pages, void* cache, void* scales, int T, int dim, uint32_t* status, void* stream);
+/* bf16 index keys [T, dim] into the paged bf16 index cache [pages, page_tokens, dim] */
+int ifab_index_cache_append(const void* key, long ldk, const int32_t* positions, const int32_t* slots, const int32_t* page_table, int max_pages,
+                            int page_tokens, int num_pages, void* cache, int T, int dim, uint32_t* status, void* stream);
+/* the general selector: gains f32 [T, heads] (w_bf16 = 0, ldw = heads) or bf16 rows of stride ldw (w_bf16 = 1); key_scales null = bf16 keys */
+int ifab_sparse_index_general(const void* q, const void* w, long ldw, int w_bf16, const void* keys, const void* key_scales, const int32_t* positions,
+                              const int32_t* slots, const int32_t* page_table, int max_pages, int page_tokens, int num_pages, float* scores, int ctx,
+                              int T, int heads, int dim, int topk, int32_t* out, uint32_t* status, void* stream);
+/* split-KV attention restricted to `indices` (int32 [T, n_index], ascending key positions padded with -1; null = every causal key);
+ * rope < 0: the cache holds packed int8 rows (656 bytes) */
+int ifab_mla_decode_attention_indexed(const void* q_lat, const void* cache, const int32_t* positions, const int32_t* slots, const int32_t* page_table,
+                                      int max_pages, int page_tokens, int num_pages, const void* sinks, int n_sinks, int window, float scale, int T,
+                                      int H, int latent, int rope, int keys_per_split, int max_splits, float* scratch, uint64_t scratch_bytes,
+                                      const void* w_kvb, int nope, int vdim, void* out, long ldo, uint32_t* status, const int32_t* indices, int n_index,
+                                      void* stream);
 
 /* ---- packed int8 latent cache (656-byte rows: 512 int8 | 64 bf16 rope | 4 f32 tile scales) and activation quantisation ----
  * Attention over a packed cache: ifab_mla_decode_attention with rope = -64 and `cache` pointing at the packed rows. */

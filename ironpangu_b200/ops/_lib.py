@@ -106,6 +106,7 @@ _SIGS = {
     "ifab_gated_rmsnorm": [_P, _P, c_long, _P, c_float, _P, c_long, c_int, c_int, c_int, _P],
     "ifab_delta_rule_decode": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "ifab_sparse_index": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],
+    "ifab_sparse_index_general": [_P, _P, c_long, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],
     "ifab_sparse_index_q8": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P],
     "ifab_mla_kv_write_q8": [_P, c_long, _P, c_float, c_float, _P, _P, _P, c_int, c_int, _P, c_int, c_int, _P, _P],
     "ifab_mla_kv_write_q8_split": [_P, c_long, _P, c_long, _P, c_float, c_float, _P, _P, _P, c_int, c_int, _P, c_int, c_int, _P, _P],

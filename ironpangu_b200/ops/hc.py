@@ -88,16 +88,14 @@ def sparse_index(q: torch.Tensor, w: torch.Tensor, keys: torch.Tensor, positions
     num_pages, page_tokens, _ = keys.shape
     scores = torch.empty(T, ctx, dtype=torch.float32, device=q.device) if scores is None else scores
     out = torch.empty(T, topk, dtype=torch.int32, device=q.device) if out is None else out
-    assert scores.is_contiguous() and scores.shape[1] == ctx and out.is_contiguous() and w.dtype == torch.float32 and w.is_contiguous()
+    assert scores.is_contiguous() and scores.shape[1] == ctx and out.is_contiguous() and w.dtype in (torch.float32, BF16) and w.stride(1) == 1
     if key_scales is not None:
         assert keys.dtype == torch.int8 and key_scales.dtype == torch.float16 and key_scales.is_contiguous()
-        check(_lib.load().ifab_sparse_index_q8(q.data_ptr(), w.data_ptr(), keys.data_ptr(), key_scales.data_ptr(), positions.data_ptr(), slots.data_ptr(),
-                                               page_table.data_ptr(), page_table.shape[1], page_tokens, num_pages, scores.data_ptr(), ctx, T, H,
-                                               dim, topk, out.data_ptr(), status_ptr, _s()), "sparse_index_q8")
-        return out
-    check(_lib.load().ifab_sparse_index(q.data_ptr(), w.data_ptr(), keys.data_ptr(), positions.data_ptr(), slots.data_ptr(),
-                                        page_table.data_ptr(), page_table.shape[1], page_tokens, num_pages, scores.data_ptr(), ctx, T, H,
-                                        dim, topk, out.data_ptr(), status_ptr, _s()), "sparse_index")
+    # the gains may be the bf16 rows of a projection, read where they lie (no f32 copy)
+    check(_lib.load().ifab_sparse_index_general(q.data_ptr(), w.data_ptr(), w.stride(0), int(w.dtype == BF16), keys.data_ptr(),
+                                                None if key_scales is None else key_scales.data_ptr(), positions.data_ptr(), slots.data_ptr(),
+                                                page_table.data_ptr(), page_table.shape[1], page_tokens, num_pages, scores.data_ptr(), ctx, T, H,
+                                                dim, topk, out.data_ptr(), status_ptr, _s()), "sparse_index")
     return out
 
 

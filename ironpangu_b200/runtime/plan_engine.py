@@ -792,7 +792,7 @@ class PlanEngine:
                 q = val(ins[0])
                 if not q.is_contiguous():
                     raise NotImplementedError("the index query must be a whole instruction result")
-                HC.sparse_index(q.view(T, Hi, dim), val(ins[1]).float(), self._index_cache_of[V[ins[2]]], pos, slot, self.page_table,
+                HC.sparse_index(q.view(T, Hi, dim), val(ins[1]), self._index_cache_of[V[ins[2]]], pos, slot, self.page_table,
                                 ctx=self.max_context, topk=int(a["topk"]), status_ptr=st, scores=self._index_scores[:T], out=val(k),
                                 key_scales=self._index_scales_of.get(V[ins[2]]))
             elif op == "add":

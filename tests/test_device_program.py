@@ -276,3 +276,58 @@ def test_hyper_connected_bundle_runs_natively_like_the_plan_engine(tmp_path):
     assert lib.ifab_device_program_audit(h, buf, len(buf)) == 0
     assert json.loads(buf.value)["device_allocations_after_ready"] == 0
     assert lib.ifab_device_program_close(h) == 0
+
+
+def test_learned_selection_bundle_runs_natively_like_the_plan_engine(tmp_path):
+    """Packed int8 latent caches, an int8 index cache, the selector and attention over its selection (one layer computing it, a
+    later one reusing it): the native executor's tokens equal the plan engine's."""
+    import dataclasses
+
+    from ironpangu_b200 import _build, compiler
+    from ironpangu_b200.compiler.sources import HyperMlaMoeConfig, hyper_mla_moe_source
+    from ironpangu_b200.parallel.fabric import Fabric
+    from ironpangu_b200.runtime.plan_engine import PlanEngine
+
+    cfg = dataclasses.replace(HyperMlaMoeConfig.tiny(3), packed_every=2, learned=True, index_heads=8, index_dim=64, index_rotary=32, index_topk=6)
+    src, ck, bundle = tmp_path / "m.inferfabric", tmp_path / "ck", tmp_path / "bundle"
+    src.write_text(hyper_mla_moe_source(cfg, 1, context=128))
+    assert compiler.cli("synth-checkpoint", str(src), str(ck), "--seed", "13").returncode == 0
+    r = compiler.cli("compile-token", str(src), str(ck), str(bundle), "--resident-sequences", "2", "--prefill-tokens", "8")
+    assert r.returncode == 0, r.stderr
+    lib = C.CDLL(str(_build.build_device()))
+    lib.ifab_device_program_error.restype = C.c_char_p
+    h = C.c_void_p()
+    assert lib.ifab_device_program_open(str(bundle).encode(), str(ck).encode(), 0, 2, C.byref(h)) == 0, lib.ifab_device_program_error()
+
+    def run(tokens, positions, slots):
+        n = len(tokens)
+        arr = lambda v: (C.c_int32 * n)(*v)
+        out = (C.c_int32 * n)()
+        assert lib.ifab_device_program_rows(h, arr(tokens), arr(positions), arr(slots), n, out) == 0, lib.ifab_device_program_error()
+        return list(out)
+
+    seq = torch.randint(1, 512, (26,), generator=torch.Generator().manual_seed(9)).tolist()
+    got = []
+    for s in range(0, 24, 8):
+        got += run(seq[s:s + 8], list(range(s, s + 8)), [1] * 8)
+    got += [run([seq[i]], [i], [1])[0] for i in (24, 25)]
+    fab = Fabric(0, 1)
+    eng = PlanEngine(str(bundle), str(ck), fab, max_tokens=8, num_slots=2)
+    same = []
+    for s in range(0, 24, 8):
+        eng.tokens[:8].copy_(torch.tensor(seq[s:s + 8], dtype=torch.int32))
+        eng.positions[:8].copy_(torch.arange(s, s + 8, dtype=torch.int32))
+        eng.slots[:8].fill_(1)
+        eng.forward(8)
+        same += eng.next_ids[:8].tolist()
+    for i in (24, 25):
+        eng.tokens[:1].fill_(seq[i])
+        eng.positions[:1].fill_(i)
+        eng.slots[:1].fill_(1)
+        eng.forward(1)
+        same.append(int(eng.next_ids[0]))
+    assert got == same
+    fab.close()
+    assert lib.ifab_device_program_reset(h) == 0
+    assert run(seq[:8], list(range(8)), [1] * 8) == got[:8]
+    assert lib.ifab_device_program_close(h) == 0
