@@ -394,7 +394,7 @@ std::shared_ptr<Stream> Service::generate(GenerateRequest req) {
   }
   if (req.request_id.empty()) req.request_id = "req-" + std::to_string(next_id_);
   if (ids_.count(req.request_id)) invalid("request: duplicate request id");
-  if (inbox_.size() + counters_.queued >= opt_.queue) {
+  if (inbox_.size() + handing_over_ + counters_.queued >= opt_.queue) {
     ++counters_.rejected_overloaded;
     fail(ErrorKind::Capacity, "overloaded: the admission queue is full");
   }
@@ -510,6 +510,7 @@ void Service::run() {
     {
       std::lock_guard<std::mutex> lk(mu_);
       fresh.swap(inbox_);
+      handing_over_ = (uint32_t)fresh.size();       // still counted at the door until the scheduler's queue length includes them
       aborts.swap(aborts_);
       audits.swap(audit_waiters_);
       counters_.queued = (uint32_t)sch.queued();
@@ -528,14 +529,19 @@ void Service::run() {
       try {
         sch.submit(std::move(req));
       } catch (const Error& e) {
-        // the submit-side check races with requests still in the inbox; a request the scheduler's queue cannot take is
-        // refused as overloaded (429), like one refused at the door
+        // the door counts the inbox, the requests being handed over and the scheduler's queue, so this is not expected; a
+        // request the scheduler's queue cannot take is still refused as overloaded (429), like one refused at the door
         if (e.kind() == ErrorKind::Capacity) {
           std::lock_guard<std::mutex> lk(mu_);
           ++counters_.rejected_overloaded;
         }
         finish(id, StreamItem{std::nullopt, sched::Finish::Error, e.what(), e.kind()});
       }
+    }
+    if (!fresh.empty()) {
+      std::lock_guard<std::mutex> lk(mu_);
+      counters_.queued = (uint32_t)sch.queued();
+      handing_over_ = 0;
     }
     for (auto& [id, lv] : live)
       if (lv.stream->reader_gone()) aborts.push_back(id);
@@ -603,22 +609,14 @@ void Service::run() {
     uint64_t generated = 0;
     Histogram ttft_now, itl_now;
     const double t_emit = now_seconds();
+    // the step's counters first, the tokens second: a reader that sees the last token of a request must also see it counted
     for (auto& ev : events) {
       auto it = live.find(ev.request);
-      if (it == live.end()) continue;
-      if (ev.token) {
-        ++generated;
-        if (it->second.t_last == 0.0) ttft_now.observe(t_emit - it->second.t_submit);
-        else itl_now.observe(t_emit - it->second.t_last);
-        it->second.t_last = t_emit;
-        if (ev.finish) {
-          finish(ev.request, StreamItem{ev.token, ev.finish, ""});
-          continue;
-        }
-        it->second.stream->push(StreamItem{ev.token, std::nullopt, ""});
-      } else if (ev.finish) {
-        finish(ev.request, StreamItem{std::nullopt, ev.finish, *ev.finish == sched::Finish::Error ? "engine produced an invalid token" : ""});
-      }
+      if (it == live.end() || !ev.token) continue;
+      ++generated;
+      if (it->second.t_last == 0.0) ttft_now.observe(t_emit - it->second.t_submit);
+      else itl_now.observe(t_emit - it->second.t_last);
+      it->second.t_last = t_emit;
     }
     {
       std::lock_guard<std::mutex> lk(mu_);
@@ -632,6 +630,16 @@ void Service::run() {
         for (int i = 0; i < Histogram::N; ++i) dst.bucket[i] += pair->bucket[i];
         dst.count += pair->count;
         dst.sum += pair->sum;
+      }
+    }
+    for (auto& ev : events) {
+      auto it = live.find(ev.request);
+      if (it == live.end()) continue;
+      if (ev.token) {
+        if (ev.finish) finish(ev.request, StreamItem{ev.token, ev.finish, ""});
+        else it->second.stream->push(StreamItem{ev.token, std::nullopt, ""});
+      } else if (ev.finish) {
+        finish(ev.request, StreamItem{std::nullopt, ev.finish, *ev.finish == sched::Finish::Error ? "engine produced an invalid token" : ""});
       }
     }
   }

@@ -206,6 +206,7 @@ class Service {
   runtime::HealthGuard health_;
   mutable std::mutex mu_;
   std::deque<std::pair<sched::Request, Live>> inbox_;
+  uint32_t handing_over_ = 0;   // requests taken out of the inbox that the scheduler has not counted yet (guarded by mu_)
   std::vector<uint64_t> aborts_;
   std::unordered_map<std::string, uint64_t> ids_;
   uint64_t next_id_ = 1;
