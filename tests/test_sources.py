@@ -104,3 +104,33 @@ def test_packed_cache_source_quantises_in_the_oracle(tmp_path):
     b = torch.tensor(compiler.interpret(packed.read_text(), str(tmp_path / "ck"), toks, all_logits=True)["prompt_logits"])
     diff = float((a - b).abs().max())
     assert 0.0 < diff < 0.1, diff
+
+
+def test_random_parameters_follow_the_init_plan(tmp_path):
+    """Random init without a checkpoint: every parameter of a rank's plan is filled with its planned shape and dtype, replicated
+    tensors come out identical on every rank, the shards of a split tensor differ, gains of norms are near one, and the same seed
+    gives the same values."""
+    from ironpangu_b200 import compiler
+    from ironpangu_b200.compiler.sources import HyperMlaMoeConfig, hyper_mla_moe_source
+    from ironpangu_b200.runtime.plan_engine import random_parameters
+
+    src = tmp_path / "m.inferfabric"
+    src.write_text(hyper_mla_moe_source(HyperMlaMoeConfig.tiny(3), 2, context=64))
+    out = compiler.write_bundle(str(src), str(tmp_path / "b"), prefill_tokens=8)
+    plans = [json.loads((Path(out["dir"]) / f"rank-{r}.init.json").read_text()) for r in range(2)]
+    P = [random_parameters(pl, "cpu", seed=4) for pl in plans]
+    for pl, params in zip(plans, P):
+        assert set(params) == {p["name"] for p in pl["parameters"]}
+        for p in pl["parameters"]:
+            t = params[p["name"]]
+            assert list(t.shape) == p["dims"] and t.dtype == {"bf16": torch.bfloat16, "f32": torch.float32}[p["dtype"]], p["name"]
+    router, q_b, norm = "model.layers.1.mlp.gate", "model.layers.0.self_attn.q_b_proj", "model.layers.0.input_layernorm"
+    assert torch.equal(P[0][router], P[1][router]) and torch.equal(P[0][norm], P[1][norm])            # replicated
+    assert not torch.equal(P[0][q_b], P[1][q_b])                                                      # row shards of one tensor
+    experts = "model.layers.1.mlp.experts.{expert}.down_proj"
+    assert not torch.equal(P[0][experts], P[1][experts])                                              # different experts per rank
+    assert abs(float(P[0][norm].float().mean()) - 1.0) < 0.02 and abs(float(P[0][q_b].float().std()) - 0.02) < 0.004
+    again = random_parameters(plans[0], "cpu", seed=4)
+    assert all(torch.equal(again[k], v) for k, v in P[0].items())
+    other = random_parameters(plans[0], "cpu", seed=5)
+    assert not torch.equal(other[q_b], P[0][q_b])
