@@ -82,6 +82,10 @@ int ifab_gemm_bf16_2sm(const void* a, long lda, const void* b, long ldb, void* c
 int ifab_gemm_bf16_2sm_persistent(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int out_f32, const void* residual,
                                   long ldr, int M, int N, int K, uint32_t* status, void* stream);
 
+/* packed gate / up projection of a SwiGLU block on CTA pairs: b = [gate rows | up rows] ([2F, K]), c[M, F] = silu(a gate^T) * (a up^T) */
+int ifab_gemm_swiglu_bf16_2sm(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int M, int F, int K, uint32_t* status,
+                              void* stream);
+
 int ifab_gemm_allreduce_bf16(const void* a, long lda, const void* b, long ldb, void* const* out_peers, long ldc, const void* residual,
                              long ldr, int M, int N, int K, const IfabFabric* fab, void* stream);
 

@@ -36,6 +36,7 @@ struct Gemm2Params {
   int M, N, K;
   uint32_t* status;
   uint32_t spin_limit;
+  int swiglu_f;   // > 0 (persistent kernel only): B = [gate rows 0..F) | up rows F..2F), C[M, F] = silu(A gate^T) * (A up^T)
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -82,7 +83,7 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 }
 
 __device__ __forceinline__ void store_row32_2(const Gemm2Params& p, int row, int col, float* v) {
-  if (row >= p.M || col >= p.N) return;
+  if (row >= p.M || col >= (p.swiglu_f > 0 ? p.swiglu_f : p.N)) return;
   if (p.residual) {
     const bf16* r = p.residual + (long)row * p.ldr + col;
 #pragma unroll
@@ -241,7 +242,10 @@ __global__ void __launch_bounds__(192) tc_gemm_2sm_persistent_kernel(const __gri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const int pair = (int)(blockIdx.x >> 1), pairs = (int)(gridDim.x >> 1);
-  const int tiles_n = (p.N + TN - 1) / TN, tiles_m = (p.M + 2 * BM - 1) / (2 * BM), tiles = tiles_m * tiles_n;
+  // SwiGLU mode: a tile is 256 rows x 128 output columns; the leader CTA streams the 128 gate rows of B, its peer the 128
+  // matching up rows, so the accumulator holds gate in columns 0..127 and up in 128..255
+  const int F = p.swiglu_f;
+  const int tiles_n = F > 0 ? (F + HALF_N - 1) / HALF_N : (p.N + TN - 1) / TN, tiles_m = (p.M + 2 * BM - 1) / (2 * BM), tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) {
@@ -271,7 +275,7 @@ __global__ void __launch_bounds__(192) tc_gemm_2sm_persistent_kernel(const __gri
     for (int t = pair; t < tiles && !*abort_flag; t += pairs) {
       int tm, tn;
       tile_coords(t, tiles_m, tiles_n, &tm, &tn);
-      const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * TN + (int)rank * HALF_N;
+      const int m0 = tm * 2 * BM + (int)rank * BM, n0 = F > 0 ? tn * HALF_N + (int)rank * F : tn * TN + (int)rank * HALF_N;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = (int)(it % STAGES2);
         const uint32_t round = it / STAGES2;
@@ -330,14 +334,31 @@ __global__ void __launch_bounds__(192) tc_gemm_2sm_persistent_kernel(const __gri
       }
       int tm, tn;
       tile_coords(t, tiles_m, tiles_n, &tm, &tn);
-      const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * TN;
+      const int m0 = tm * 2 * BM + (int)rank * BM, n0 = F > 0 ? tn * HALF_N : tn * TN;
       const int row = m0 + q * 32 + lane;
+      const uint32_t tm_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TN);
+      if (F > 0) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < TN; c0 += 32) {
-        float v[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TN + c0), v);
-        tmem_ld_wait();
-        store_row32_2(p, row, n0 + c0, v);
+        for (int c0 = 0; c0 < HALF_N; c0 += 32) {
+          float v[32], u[32];
+          tmem_ld_32x32(tm_row + (uint32_t)c0, v);
+          tmem_ld_32x32(tm_row + (uint32_t)(HALF_N + c0), u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float g = bf16_round(v[i]);
+            v[i] = g / (1.f + __expf(-g)) * bf16_round(u[i]);
+          }
+          store_row32_2(p, row, n0 + c0, v);
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < TN; c0 += 32) {
+          float v[32];
+          tmem_ld_32x32(tm_row + (uint32_t)c0, v);
+          tmem_ld_wait();
+          store_row32_2(p, row, n0 + c0, v);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -362,7 +383,7 @@ extern "C" int ifab_gemm_bf16_2sm(const void* a, long lda, const void* b, long l
   CUtensorMap ta, tb;
   if (int rc = make_tmap_bf16_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return rc;
   if (int rc = make_tmap_bf16_2d(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, HALF_N)) return rc;
-  Gemm2Params p{c, ldc, out_f32, (const bf16*)residual, ldr, M, N, K, status, 4000000u};
+  Gemm2Params p{c, ldc, out_f32, (const bf16*)residual, ldr, M, N, K, status, 4000000u, 0};
   if (int rc = opt_in_smem(tc_gemm_2sm_kernel, SMEM2)) return rc;
   dim3 grid(2 * ((M + 255) / 256), (N + 255) / 256);
   return launch_chain_cluster(tc_gemm_2sm_kernel, grid, dim3(192), 2, (size_t)SMEM2, (cudaStream_t)stream, ta, tb, p);
@@ -375,12 +396,30 @@ extern "C" int ifab_gemm_bf16_2sm_persistent(const void* a, long lda, const void
   CUtensorMap ta, tb;
   if (int rc = make_tmap_bf16_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return rc;
   if (int rc = make_tmap_bf16_2d(&tb, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, HALF_N)) return rc;
-  Gemm2Params p{c, ldc, out_f32, (const bf16*)residual, ldr, M, N, K, status, 4000000u};
+  Gemm2Params p{c, ldc, out_f32, (const bf16*)residual, ldr, M, N, K, status, 4000000u, 0};
   if (int rc = opt_in_smem(tc_gemm_2sm_persistent_kernel, SMEM2)) return rc;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  const int pairs = std::max(1, std::min(tiles, sms / 2));
+  return launch_chain_cluster(tc_gemm_2sm_persistent_kernel, dim3(2 * pairs), dim3(192), 2, (size_t)SMEM2, (cudaStream_t)stream, ta, tb, p);
+}
+
+// C[M, F] = silu(A gate^T) * (A up^T) with B = [gate rows | up rows] ([2F, K]): the packed gate / up projection of a SwiGLU block in
+// one persistent CTA-pair launch (gate and up of the same 128 output columns share an accumulator). F % 32 == 0, K % 8 == 0.
+extern "C" int ifab_gemm_swiglu_bf16_2sm(const void* a, long lda, const void* b, long ldb, void* c, long ldc, int M, int F, int K, uint32_t* status,
+                                         void* stream) {
+  if (M < 1 || F < 32 || F % 32 || K < 8 || K % 8 || lda % 8 || ldb % 8) return -1;
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_bf16_2d(&ta, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tb, b, (uint64_t)2 * F, (uint64_t)K, (uint64_t)ldb, HALF_N)) return rc;
+  Gemm2Params p{c, ldc, 0, nullptr, 0, M, 2 * F, K, status, 4000000u, F};
+  if (int rc = opt_in_smem(tc_gemm_2sm_persistent_kernel, SMEM2)) return rc;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int tiles = ((M + 255) / 256) * ((F + HALF_N - 1) / HALF_N);
   const int pairs = std::max(1, std::min(tiles, sms / 2));
   return launch_chain_cluster(tc_gemm_2sm_persistent_kernel, dim3(2 * pairs), dim3(192), 2, (size_t)SMEM2, (cudaStream_t)stream, ta, tb, p);
 }

@@ -181,7 +181,11 @@ class DensePrefill:
             else:
                 G.gemm(self.attn[:m], w[p + "o_proj"], residual=x, out=x, status_ptr=st)
             K.rmsnorm(x, w[p + "ffn_norm"], c.eps, out=h)
-            P.grouped_gemm(self.h, w[p + "gate_up"].unsqueeze(0), self.tiles, self.ntiles, self.act[:m], swiglu=True, status_ptr=st)
+            if m >= 256:
+                # whole 256-row tile pairs: the packed gate | up projection and its activation on CTA pairs, one persistent launch
+                G.gemm_swiglu(h, w[p + "gate_up"], out=self.act[:m], status_ptr=st)
+            else:
+                P.grouped_gemm(self.h, w[p + "gate_up"].unsqueeze(0), self.tiles, self.ntiles, self.act[:m], swiglu=True, status_ptr=st)
             if fab.world > 1:
                 G.gemm_allreduce(self.act[:m], w[p + "down"], fab, self._sym_rows(m), residual=x)
             else:

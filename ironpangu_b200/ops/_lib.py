@@ -57,6 +57,7 @@ _SIGS = {
     "ifab_gemv_allreduce_bf16": [_P, c_long, _P, _P, c_long, _P, c_long, _P, c_int, c_int, c_int, C.POINTER(IfabFabric), _P],
     "ifab_gemm_bf16": [_P, c_long, _P, c_long, _P, c_long, c_int, _P, c_long, c_int, c_int, c_int, _P, _P],
     "ifab_gemm_bf16_2sm": [_P, c_long, _P, c_long, _P, c_long, c_int, _P, c_long, c_int, c_int, c_int, _P, _P],
+    "ifab_gemm_swiglu_bf16_2sm": [_P, c_long, _P, c_long, _P, c_long, c_int, c_int, c_int, _P, _P],
     "ifab_gemm_bf16_2sm_persistent": [_P, c_long, _P, c_long, _P, c_long, c_int, _P, c_long, c_int, c_int, c_int, _P, _P],
     "ifab_gemm_allreduce_bf16": [_P, c_long, _P, c_long, _P, c_long, _P, c_long, c_int, c_int, c_int, C.POINTER(IfabFabric), _P],
     "ifab_gemm_reduce_scatter_bf16": [_P, c_long, _P, c_long, _P, c_long, _P, c_long, c_int, c_int, c_int, C.POINTER(IfabFabric), _P],

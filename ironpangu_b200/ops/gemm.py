@@ -44,6 +44,20 @@ def gemm_2sm(a: torch.Tensor, b: torch.Tensor, *, residual: Optional[torch.Tenso
     return out
 
 
+def gemm_swiglu(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None, status_ptr: Optional[int] = None) -> torch.Tensor:
+    """``silu(A @ gate.T) * (A @ up.T)`` for the packed projection ``b`` = ``[2F, K]`` (gate rows, then up rows) on CTA pairs
+    (persistent, gate and up of the same 128 output columns under one accumulator); returns bf16 ``[M, F]``. ``F % 32 == 0``."""
+    M, K = a.shape
+    F = b.shape[0] // 2
+    assert b.shape[1] == K and b.shape[0] == 2 * F and a.dtype == BF16 and b.dtype == BF16 and a.stride(1) == 1 and b.stride(1) == 1
+    if out is None:
+        out = torch.empty(M, F, dtype=BF16, device=a.device)
+    assert out.shape == (M, F) and out.stride(1) == 1
+    check(_lib.load().ifab_gemm_swiglu_bf16_2sm(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0), M, F, K,
+                                                status_ptr, torch.cuda.current_stream().cuda_stream), "gemm_swiglu")
+    return out
+
+
 def gemm_allreduce(a: torch.Tensor, b: torch.Tensor, fabric, out, *, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Row-parallel GEMM fused with a two-shot all-reduce over NVLink peer memory:
     ``C = sum_ranks A_r @ B_r.T (+ residual)``; ``A_r`` = ``[M, K_local]``, ``B_r`` = ``[N, K_local]``.

@@ -36,3 +36,32 @@ def test_two_sm_gemm_refuses_other_shapes():
     b = torch.zeros(250, 64, dtype=BF16, device="cuda")          # N must be a multiple of 32
     with pytest.raises(RuntimeError):
         gemm_2sm(a, b)
+
+
+@pytest.mark.parametrize("M,F,K", [(256, 128, 64), (512, 6144, 2048), (300, 160, 520), (1024, 1536, 4096)])
+def test_two_sm_swiglu_projection(M, F, K):
+    """Packed gate | up projection with its activation on CTA pairs: equal to the one-CTA grouped kernel's SwiGLU mode (same
+    accumulation order, same rounding points) and close to the fp32 product."""
+    from ironpangu_b200.ops import prefill as P
+    from ironpangu_b200.ops.gemm import gemm_swiglu
+
+    g = torch.Generator(device="cuda").manual_seed(M + F + K)
+    a = (torch.randn(M, K, generator=g, device="cuda") * 0.5).to(BF16)
+    b = (torch.randn(2 * F, K, generator=g, device="cuda") * 0.05).to(BF16)
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = gemm_swiglu(a, b, status_ptr=st.data_ptr())
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    gu = a.float() @ b.float().T
+    gate, up = gu[:, :F].to(BF16).float(), gu[:, F:].to(BF16).float()
+    ref = torch.nn.functional.silu(gate) * up
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    nt = (M + 127) // 128
+    tiles = torch.zeros(nt, 4, dtype=torch.int32)
+    for i in range(nt):
+        tiles[i, 1], tiles[i, 2] = i * 128, min(128, M - i * 128)
+    ap = torch.zeros(nt * 128, K, dtype=BF16, device="cuda")
+    ap[:M] = a
+    one = torch.empty(nt * 128, F, dtype=BF16, device="cuda")
+    P.grouped_gemm(ap, b.unsqueeze(0), tiles.cuda(), torch.tensor([nt], dtype=torch.int32, device="cuda"), one, swiglu=True)
+    assert torch.equal(out, one[:M])
