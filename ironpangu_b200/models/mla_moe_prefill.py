@@ -214,7 +214,10 @@ class MlaMoePrefill:
             P.grouped_gemm(self.xp, ew["gate_up"], self.route.tiles, self.route.num_tiles, self.act, swiglu=True, status_ptr=st)
             P.grouped_gemm(self.act, ew["down"], self.route.tiles, self.route.num_tiles, self.y, status_ptr=st)
             sgu, sdn = ew["shared_gate_up"], ew["shared_down"]
-            P.grouped_gemm(h, sgu.unsqueeze(0), self.shared_tiles, self.shared_ntiles, self.sact[:m], swiglu=True, status_ptr=st)
+            if m >= 256 and (sgu.shape[0] // 2) % 32 == 0:
+                G.gemm_swiglu(h, sgu, out=self.sact[:m], status_ptr=st)      # the shared expert's gate | up on CTA pairs
+            else:
+                P.grouped_gemm(h, sgu.unsqueeze(0), self.shared_tiles, self.shared_ntiles, self.sact[:m], swiglu=True, status_ptr=st)
             G.gemm(self.sact[:m], sdn, out=self.sd[:m], status_ptr=st)
             if fab.world > 1:
                 part = self.parts[self._calls & 1]
