@@ -613,6 +613,77 @@ static void test_hyper_connected_program() {
   CHECK(finite && differs);
 }
 
+// ---- a dense grouped-query program at tp = 2: lowering, sharded init plans, contracts, arena ---------------------------------
+static const char* kDenseSource = R"SRC(language inferfabric 1;
+module Attn(x, w) {
+    let q = rotary_prefix(linear(x, weight = w.q, width = div(256, 2), placement = "tp_rows"), heads = div(4, 2), head_dim = 64, rotary_dim = 64, theta = 10000);
+    let k = rotary_prefix(linear(x, weight = w.k, width = div(128, 2), placement = "tp_rows"), heads = div(2, 2), head_dim = 64, rotary_dim = 64, theta = 10000);
+    let v = linear(x, weight = w.v, width = div(128, 2), placement = "tp_rows");
+    let cache = kv_cache_append(k, v, kv_heads = 2, head_dim = 64);
+    let att = paged_attention(q, cache, heads = 4, kv_heads = 2, head_dim = 64, scale = 0.125);
+    yield allreduce(linear(att, weight = w.o, width = 128, placement = "tp_columns"));
+}
+model Dense {
+    context = 64;
+    eos = 2;
+    let w = weights("m");
+    let x = embedding(weight = w.embed, width = 128, vocab = 256);
+    let h = add(x, Attn(norm(x, weight = w.n1, eps = 1e-6), w.attn));
+    let act = swiglu(linear(norm(h, weight = w.n2, eps = 1e-6), weight = w.gate, paired_weight = w.up, width = div(192, 2), paired_width = div(192, 2), placement = "tp_rows"));
+    let y = add(h, allreduce(linear(act, weight = w.down, width = 128, placement = "tp_columns")));
+    let logits = gather(linear(norm(y, weight = w.nf, eps = 1e-6), weight = weights("head"), width = div(256, 2), placement = "tp_rows"));
+    yield logits;
+}
+plan P for Dense { target = b200_token_v1; tp = 2; ep = 2; devices = [0, 1]; max_num_seqs = 1; max_num_batched_tokens = 1; max_model_len = 64; }
+)SRC";
+
+static void test_dense_program_at_two_ranks() {
+  graph::Graph g = graph::compile_source(kDenseSource);
+  program::Program p = program::lower(g);
+  std::vector<std::string> ops;
+  for (auto& i : p.instructions) ops.push_back(i.op);
+  const std::vector<std::string> want = {"embedding", "linear", "rotary_prefix", "linear", "rotary_prefix", "linear", "kv_cache_append", "paged_attention",
+                                         "linear_allreduce", "linear", "linear_allreduce", "lm_head"};
+  CHECK(ops == want);                                                   // norms folded, residuals absorbed, SwiGLU fused, head fused
+  const program::Instruction& gu = p.instructions[9];
+  CHECK(gu.attr("activation") && *gu.attr("activation") == "swiglu" && gu.attr("paired_width") && *gu.attr("paired_width") == "96");
+  CHECK(p.instructions[8].inputs.size() == 2 && p.instructions[10].inputs.size() == 2);      // residual operands of the fused all-reduces
+  init::Checkpoint ck = init::Checkpoint::synthetic(init::required_tensors(p));
+  std::vector<init::Plan> plans = init::plan_all(p, ck);
+  CHECK(plans.size() == 2);
+  for (auto& pl : plans) {
+    contract::validate_bindings(p, pl);
+    for (auto& prm : pl.parameters) {
+      if (prm.name == "m.attn.q") CHECK(prm.dims == (std::vector<uint64_t>{128, 128}));                  // 2 of 4 heads
+      if (prm.name == "m.attn.o") CHECK(prm.dims == (std::vector<uint64_t>{128, 128}));                  // half of the input columns
+      if (prm.name == "m.gate|m.up") CHECK(prm.dims == (std::vector<uint64_t>{192, 128}));               // gate rows, then up rows, of this rank
+      if (prm.name == "head") CHECK(prm.dims == (std::vector<uint64_t>{128, 128}));
+    }
+  }
+  contract::validate_kernels(p);
+  auto load_of = [](const init::Plan& pl, const std::string& tensor) -> const init::LoadSlice* {
+    for (auto& l : pl.loads) if (l.tensor == tensor) return &l;
+    return nullptr;
+  };
+  const init::LoadSlice *q0 = load_of(plans[0], "m.attn.q.weight"), *q1 = load_of(plans[1], "m.attn.q.weight");
+  CHECK(q0 && q1 && q0->tag == 1 && q1->offset == q0->offset + q0->bytes);                                 // row shards: consecutive byte ranges
+  const init::LoadSlice *o0 = load_of(plans[0], "m.attn.o.weight"), *o1 = load_of(plans[1], "m.attn.o.weight");
+  CHECK(o0 && o1 && o0->tag == 2 && o0->row_bytes == 256 && o0->stride_bytes == 512 && o1->offset == o0->offset + 256);   // column shards: strided rows
+  bundle::Arena a = bundle::plan_arena(p, 8);
+  a.verify();
+  CHECK(a.tokens == 8 && a.bytes > 0 && a.workspace_bytes > 0);
+  for (auto& sl : a.slots) CHECK(p.instructions[sl.instruction].op != "kv_cache_append");                 // sequence state lives outside the arena
+  // the oracle simulates both ranks
+  interp::Weights w = interp::Weights::random(init::required_tensors(p), 3);
+  interp::Interpreter it(g, w);
+  std::vector<float> logits;
+  it.step(7, 0, &logits);
+  it.step(9, 1, &logits);
+  bool finite = logits.size() == 256;
+  for (float v : logits) finite = finite && std::isfinite(v);
+  CHECK(finite);
+}
+
 // ---- chat post-processing: reasoning sections and tool calls ---------------------------------------------------------
 static void test_chat_parsers() {
   using namespace ifab::chat;
@@ -872,6 +943,7 @@ int main() {
       {"state_pool", test_state_pool}, {"prefix_index", test_prefix_index}, {"paging", test_paging},
       {"rankplan_runtime", test_rankplan_and_runtime}, {"transfer", test_transfer}, {"scheduler", test_scheduler}, {"cpu_plan", test_cpu_plan},
       {"contract_validator", test_contract_validator}, {"hyper_connected_program", test_hyper_connected_program},
+      {"dense_program_two_ranks", test_dense_program_at_two_ranks},
       {"chat_parsers", test_chat_parsers}};
   for (auto& t : tests) {
     int before = failures;
