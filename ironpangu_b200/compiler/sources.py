@@ -448,3 +448,53 @@ plan TP{tp}EP{tp} for {name} {{
     max_model_len = {context};
 }}
 """
+
+
+def main(argv=None) -> int:
+    """``python -m ironpangu_b200.compiler.sources FAMILY [--tp N] [--context N] [--layers N] [--kv-int8] [--learned]`` prints the
+    ``.inferfabric`` source of a built-in family at a built-in size: ``flagship`` / ``tiny`` (latent attention + routed experts),
+    ``dense2b`` / ``dense-tiny`` (grouped-query attention), ``pangu92b`` / ``hyper-tiny`` (hyper-connected latent attention +
+    routed experts; ``--learned``: packed caches and learned sparse attention on every third layer)."""
+    import argparse
+    import sys
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("family", choices=["flagship", "tiny", "dense2b", "dense-tiny", "pangu92b", "hyper-tiny"])
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--context", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--kv-int8", action="store_true")
+    ap.add_argument("--learned", action="store_true")
+    a = ap.parse_args(argv)
+    if a.family in ("flagship", "tiny"):
+        from ..models.mla_moe import MlaMoeConfig
+
+        c = MlaMoeConfig.flagship() if a.family == "flagship" else MlaMoeConfig.tiny(2)
+        if a.layers:
+            c.layers = a.layers
+        text = mla_moe_source(c, a.tp, context=a.context, kv_int8=a.kv_int8)
+    elif a.family in ("dense2b", "dense-tiny"):
+        from ..models.dense_gqa import DenseConfig
+
+        c = DenseConfig.qwen2b() if a.family == "dense2b" else DenseConfig.tiny(2)
+        if a.layers:
+            c.layers = a.layers
+        text = dense_gqa_source(c, a.tp, context=a.context)
+    else:
+        if a.family == "pangu92b":
+            c = HyperMlaMoeConfig.pangu92b_learned() if a.learned else HyperMlaMoeConfig.pangu92b()
+        else:
+            c = HyperMlaMoeConfig.tiny()
+            if a.learned:
+                c.packed_every, c.learned, c.index_heads, c.index_dim, c.index_rotary, c.index_topk = 2, True, 8, 64, 32, 64
+        if a.layers:
+            c.layers = a.layers
+        if a.kv_int8 and not c.packed_every:
+            c.packed_every = 1
+        text = hyper_mla_moe_source(c, a.tp, context=a.context)
+    sys.stdout.write(text)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

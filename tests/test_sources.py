@@ -134,3 +134,22 @@ def test_random_parameters_follow_the_init_plan(tmp_path):
     assert all(torch.equal(again[k], v) for k, v in P[0].items())
     other = random_parameters(plans[0], "cpu", seed=5)
     assert not torch.equal(other[q_b], P[0][q_b])
+
+
+@pytest.mark.parametrize("args", [["tiny", "--tp", "2", "--kv-int8"], ["dense-tiny", "--tp", "2"], ["hyper-tiny", "--learned"],
+                                  ["hyper-tiny", "--kv-int8", "--layers", "2"], ["pangu92b", "--tp", "8", "--learned"]])
+def test_source_printer_writes_programs_that_compile(tmp_path, args):
+    import subprocess
+    import sys
+
+    from ironpangu_b200 import compiler
+
+    r = subprocess.run([sys.executable, "-m", "ironpangu_b200.compiler.sources", *args], capture_output=True, text=True,
+                       cwd=str(Path(__file__).resolve().parents[1]))
+    assert r.returncode == 0 and r.stdout.startswith("language inferfabric 1;"), r.stderr
+    src = tmp_path / "m.inferfabric"
+    src.write_text(r.stdout)
+    e = compiler.cli("explain", str(src))
+    assert e.returncode == 0, e.stderr
+    tp = int(args[args.index("--tp") + 1]) if "--tp" in args else 1
+    assert json.loads(e.stdout)["parallel"]["tp"] == tp
