@@ -436,6 +436,31 @@ def build_engine(args, rank: int, world: int, rec=None) -> BatchEngine:
         vocab = int(eng._param(head["attrs"]["weight"]).shape[0]) * world
         return BatchEngine(eng, os.path.basename(os.path.normpath(args.bundle)), min(args.max_model_len, eng.max_context), vocab,
                            greedy_only=True)
+    if args.model in ("hyper-tiny", "pangu92b", "pangu92b-learned"):
+        # the hyper-connected latent-attention + routed-experts family: its generated source compiled for this job's width, random
+        # parameters drawn per init-plan load slice (replicated tensors identical on every rank), run by the plan engine
+        import tempfile
+
+        from ironpangu_b200 import compiler
+        from ironpangu_b200.compiler.sources import HyperMlaMoeConfig, hyper_mla_moe_source
+        from ironpangu_b200.runtime.plan_engine import PlanEngine, random_parameters
+
+        hcfg = {"hyper-tiny": HyperMlaMoeConfig.tiny, "pangu92b": HyperMlaMoeConfig.pangu92b,
+                "pangu92b-learned": HyperMlaMoeConfig.pangu92b_learned}[args.model]()
+        if args.layers:
+            hcfg.layers = args.layers
+        work = tempfile.mkdtemp(prefix=f"ifab-worker-r{rank}-")
+        src = os.path.join(work, "model.inferfabric")
+        with open(src, "w") as f:
+            f.write(hyper_mla_moe_source(hcfg, world, context=args.max_model_len))
+        compiled = compiler.write_bundle(src, os.path.join(work, "bundle"), prefill_tokens=8)
+        with open(os.path.join(compiled["dir"], f"rank-{rank}.init.json")) as f:
+            plan = json.load(f)
+        params = random_parameters(plan, dev, seed=args.seed)
+        mark("weights")
+        eng = PlanEngine(compiled["dir"], None, fab, max_tokens=8, num_slots=args.max_num_seqs, parameters=params)
+        mark("bundle", f"program {compiled['program_sha256'][:16]}, arena {eng.arena.bytes + eng.arena.workspace_bytes} bytes")
+        return BatchEngine(eng, f"ifab-{args.model}", min(args.max_model_len, eng.max_context), hcfg.vocab, greedy_only=True)
     if args.model.startswith("hybrid"):
         # gated delta-rule + gated full-attention family (one GPU): K / V pages, f32 delta state and conv history per sequence slot
         from ironpangu_b200.models import hybrid_delta as H
@@ -691,7 +716,7 @@ def serve(engine, rank: int, world: int, sock_path: str, group=None, agreement="
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model", default="tiny", choices=["tiny", "flagship", "dense-tiny", "dense2b", "hybrid-tiny", "hybrid2b", "hybrid"])
+    ap.add_argument("--model", default="tiny", choices=["tiny", "flagship", "dense-tiny", "dense2b", "hybrid-tiny", "hybrid2b", "hybrid", "hyper-tiny", "pangu92b", "pangu92b-learned"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--bundle", default="")

@@ -226,6 +226,36 @@ def test_gpu_engine_worker_serves_the_tiny_model():
         s.close()
 
 
+@pytest.mark.gpu
+def test_gpu_engine_worker_serves_the_hyper_connected_family():
+    """The worker compiles the generated hyper-connected source (residual streams, sink rows, token convolution, routed experts),
+    draws its parameters from the init plan and serves it through the plan engine: three sequences batched into one step
+    generate the tokens each of them generates alone (sequence slots reused: the convolution history and the caches of a
+    slot's previous sequence are never read)."""
+    s = Server("--spawn", f"{sys.executable} -m ironpangu_b200.runtime.engine_worker --model hyper-tiny --layers 3 --max-num-seqs 3 "
+               "--max-model-len 128 --greedy-only", "--accept-seconds", "300", timeout=400)
+    try:
+        prompts = [[5, 77, 300, 12, 99, 41, 8, 65, 3, 17, 256], [9], [100, 200, 300]]
+        out = {}
+
+        def client(i):
+            out[i] = s.post("/inference/v1/generate", {"token_ids": prompts[i], "sampling_params": {"max_tokens": 6}}, timeout=120)
+
+        threads = [threading.Thread(target=client, args=(i,)) for i in range(3)]
+        [t.start() for t in threads]
+        [t.join() for t in threads]
+        for i in range(3):
+            st, g = out[i]
+            assert st == 200, g
+            assert len(g["token_ids"]) == 6 and all(0 <= t < 512 for t in g["token_ids"])
+        for i in (2, 0, 1):                          # other slots than the first time
+            st, g = s.post("/inference/v1/generate", {"token_ids": prompts[i], "sampling_params": {"max_tokens": 6}}, timeout=120)
+            assert st == 200, g
+            assert g["token_ids"] == out[i][1]["token_ids"]
+    finally:
+        s.close()
+
+
 def test_program_engine_abi_and_cpu_server(tmp_path):
     """A compiled bundle + synthetic checkpoint served on the host: the program-engine C ABI and `--program ... --cpu` agree
     with the interpreter, token for token."""
