@@ -92,22 +92,6 @@ def sequence_parallel_check(cfg, full, fab, rank, world):
     for l in range(cfg.layers):
         torch.testing.assert_close(c2.k_cache[l].float(), c1.k_cache[l].float(), rtol=3e-2, atol=3e-2)
         torch.testing.assert_close(c2.v_cache[l].float(), c1.v_cache[l].float(), rtol=3e-2, atol=3e-2)
-    if os.environ.get("DENSE_SP_BENCH"):
-        for name, run in (("all-reduce", lambda: p1.forward(toks, 0, 0)), ("sequence-parallel", lambda: p2.forward(toks, 0, 0, sequence_parallel=True))):
-            for _ in range(3):
-                run()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            dist.barrier()
-            torch.cuda.synchronize()
-            e0.record()
-            for _ in range(10):
-                run()
-            e1.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) / 10], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            if rank == 0:
-                print(f"prefill chunk of {m} rows, {name}: {t.item():.3f} ms (max over ranks)", flush=True)
 
 
 if __name__ == "__main__":
